@@ -1,0 +1,33 @@
+"""Gated MLP with the up and gate projections fused into one GEMM ([up; gate] rows, up first).
+
+Parity: surogate/dsl/modules/mlp.py:19-225 (GenericMLP).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .. import functional as F
+from .. import hf
+from ..nn import Module
+
+
+@dataclass
+class MLPConfig:
+    activation: str = "swiglu"
+
+
+class GenericMLP(Module):
+    def __init__(self, d_model: int, d_ff: int, config: MLPConfig | None = None, prefix: str = "model.layers.{L}.mlp"):
+        super().__init__()
+        self.cfg = config or MLPConfig()
+        m = prefix
+        self.declare_param("up_weight", (2 * d_ff, d_model), quantizable=True,
+                           hf=hf.fuse([f"{m}.up_proj.weight", f"{m}.gate_proj.weight"], sizes=[d_ff, d_ff]),
+                           lora_targets=[("up_proj", 0, d_ff), ("gate_proj", d_ff, d_ff)])
+        self.declare_param("down_weight", (d_model, d_ff), quantizable=True, hf=hf.direct(f"{m}.down_proj.weight"),
+                           lora_targets=[("down_proj", 0, d_model)])
+
+    def forward(self, x):
+        up = F.matmul(x, self.p("up_weight"), name="mlp_up", role="mlp_up")
+        act = F.swiglu(up)
+        return F.matmul(act, self.p("down_weight"), name="mlp_down", role="mlp_down")

@@ -1,0 +1,261 @@
+"""Graph executor: runs compiled forward/backward op lists against a parameter store.
+
+One flat interpreter loop per graph: look up the op's implementation on the
+backend object, call it, bind outputs, and drop every tensor after its last
+reader (liveness is computed once per graph, ahead of time).  The block stack is
+unrolled here, which is where per-layer behaviour lives:
+
+* ``store.layer_start / layer_end`` hooks (ZeRO-3 weight gather + prefetch,
+  gradient bucket reduce overlapped with the next layer's backward),
+* which forward tensors a layer keeps for its backward (the AOT "saved" list) or,
+  with ``recompute``, only the block inputs followed by a replay of the layer's
+  forward just before its backward.
+
+Parity: csrc/src/runtime/executor/ (GraphExecutor graph_executor.h:185,
+CompiledExecutor, handle_layer_start/end compiled_ops.cpp:982-1074,
+replay_layer_forward compiled_ops_execute.cpp:85).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Set, Tuple
+
+import torch
+
+from ..dsl.autodiff import GRAD_PREFIX
+from ..dsl.compiler import CompiledModel
+from ..dsl.ir import Graph, OpNode, eval_shape
+
+_DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16, "int32": torch.int32}
+
+
+@dataclass
+class ExecOptions:
+    recompute: bool = False
+    act_dtype: torch.dtype = torch.float32
+    check_finite: bool = False
+    dump_tensors: Optional[Callable[[str, Optional[int], torch.Tensor], None]] = None
+
+
+class ExecContext:
+    """Per-call state handed to every op implementation."""
+
+    def __init__(self, executor: "Executor"):
+        ex = executor
+        self.ex = ex
+        self.device = ex.device
+        self.act_dtype = ex.options.act_dtype
+        self.recipe = ex.recipe
+        self.training = True
+        self.dims: Dict[str, int] = {}
+        self.layer: Optional[int] = None
+        self.graph: Optional[Graph] = None
+        self.stash: Dict[str, Any] = {}
+        self.loss_scale: Any = 1.0
+        self.aux_scale: float = 1.0
+        self.doc_ids: Optional[torch.Tensor] = None
+        self.ep = ex.ep
+        self.micro_step = 0
+        self.phase = "fwd"
+        self.moe_stats: List[Tuple[int, torch.Tensor, torch.Tensor]] = []
+        self.lora = ex.lora
+
+    def eval_shape(self, shape) -> Tuple[int, ...]:
+        return eval_shape(tuple(shape), self.dims)
+
+    def dtype_of(self, tag: str) -> torch.dtype:
+        return self.act_dtype if tag in ("act", "param") else _DTYPES[tag]
+
+    def full_name(self, local: str) -> str:
+        return f"blocks.{self.layer}.{local}" if self.layer is not None else local
+
+    def grad_target(self, out_name: Optional[str]):
+        """(gradient buffer view, accumulate?) for a ``grad::<param>`` output, or (None, False) if frozen/absent."""
+        if out_name is None:
+            return None, False
+        local = out_name[len(GRAD_PREFIX):] if out_name.startswith(GRAD_PREFIX) else out_name
+        return self.ex.store.grad_target(self.full_name(local))
+
+    def local_experts(self, w: torch.Tensor) -> torch.Tensor:
+        return w
+
+    def record_moe_stats(self, counts: torch.Tensor, probs: torch.Tensor) -> None:
+        if self.phase == "fwd" and self.layer is not None:
+            self.moe_stats.append((self.layer, counts.detach(), probs.detach().mean(0)))
+
+
+class Executor:
+    def __init__(self, compiled: CompiledModel, store, backend, recipe=None, options: Optional[ExecOptions] = None,
+                 device: Optional[torch.device] = None, ep=None, lora=None):
+        self.cm = compiled
+        self.store = store
+        self.backend = backend
+        self.recipe = recipe
+        self.options = options or ExecOptions()
+        self.device = device or torch.device("cpu")
+        self.ep = ep
+        self.lora = lora
+        self._liveness: Dict[int, Dict[str, int]] = {}
+        self._saved_sets: Dict[str, Set[str]] = {}
+        for bt, bwd in self.cm.block_bwd.items():
+            self._saved_sets[bt] = set(bwd.meta["saved"])
+        self._top_saved: Set[str] = set(self.cm.bwd.meta["saved"])
+        self._layer_saved: List[Optional[Dict[str, Any]]] = [None] * self.cm.n_layers
+        self._top_env: Dict[str, Any] = {}
+
+    # ------------------------------------------------------------------ generic graph run
+    def _last_use(self, g: Graph) -> Dict[str, int]:
+        key = id(g)
+        if key not in self._liveness:
+            self._liveness[key] = g.last_use()
+        return self._liveness[key]
+
+    def run_graph(self, g: Graph, env: Dict[str, Any], ctx: ExecContext, keep: Set[str]) -> None:
+        last = self._last_use(g)
+        prev_graph = ctx.graph
+        ctx.graph = g
+        be = self.backend
+        params = g.params
+        for op in g.ops:
+            if op.kind == "block_stack":
+                outs = self._block_stack_forward(op, env, ctx)
+            elif op.kind == "block_stack_backward":
+                outs = self._block_stack_backward(op, env, ctx)
+            else:
+                ins = []
+                for n in op.inputs:
+                    if n is None:
+                        ins.append(None)
+                    elif n in params:
+                        ins.append(self.store.get(ctx.full_name(n)))
+                    else:
+                        ins.append(env.get(n))
+                fn = getattr(be, op.kind, None)
+                if fn is None:
+                    raise NotImplementedError(f"[E030] backend '{be.name}' has no implementation of op '{op.kind}'")
+                outs = fn(ctx, op, *ins)
+            for name, val in zip(op.outputs, outs):
+                if name is None:
+                    continue
+                if name.startswith(GRAD_PREFIX):
+                    if val is not None:
+                        self._accumulate_grad(ctx, name, val)
+                    continue
+                env[name] = val
+                if self.options.dump_tensors is not None and torch.is_tensor(val):
+                    self.options.dump_tensors(name, ctx.layer, val)
+                if self.options.check_finite and torch.is_tensor(val) and val.is_floating_point() and not torch.isfinite(val).all():
+                    raise FloatingPointError(f"non-finite values in '{name}' (layer {ctx.layer}, op {op.kind})")
+            for n in op.inputs:
+                if n is not None and n in env and last.get(n, -1) == op.idx and n not in keep and n not in g.inputs:
+                    del env[n]
+        ctx.graph = prev_graph
+
+    def _accumulate_grad(self, ctx: ExecContext, out_name: str, val: torch.Tensor) -> None:
+        tgt, acc = ctx.grad_target(out_name)
+        if tgt is None:
+            return
+        v = val.reshape(tgt.shape).to(tgt.dtype)
+        if acc:
+            tgt.add_(v)
+        else:
+            tgt.copy_(v)
+
+    # ------------------------------------------------------------------ block stack
+    def _block_stack_forward(self, op: OpNode, env, ctx: ExecContext):
+        x, res, pos = (env[n] for n in op.inputs)
+        aux_names: List[str] = op.attrs.get("aux", [])
+        aux_tot = [None] * len(aux_names)
+        n = self.cm.n_layers
+        for L in range(n):
+            bt = self.cm.layer_types[L]
+            g = self.cm.block_fwd[bt]
+            ctx.layer = L
+            self.store.layer_start(L, "fwd")
+            benv = {"x": x, "residual": res, "position_ids": pos}
+            if ctx.training and self.options.recompute:
+                keep: Set[str] = set(g.outputs)
+                self._layer_saved[L] = {"x": x, "residual": res, "position_ids": pos, "__recompute__": True}
+            else:
+                keep = (self._saved_sets[bt] if ctx.training else set()) | set(g.outputs)
+            self.run_graph(g, benv, ctx, keep)
+            outs = [benv[o] for o in g.outputs]
+            x, res = outs[0], outs[1]
+            for i, a in enumerate(outs[2:]):
+                aux_tot[i] = a if aux_tot[i] is None else aux_tot[i] + a
+            if ctx.training and not self.options.recompute:
+                self._layer_saved[L] = {k: v for k, v in benv.items() if k in self._saved_sets[bt]}
+            self.store.layer_end(L, "fwd")
+        ctx.layer = None
+        return [x, res] + aux_tot
+
+    def _block_stack_backward(self, op: OpNode, env, ctx: ExecContext):
+        d_x, d_res = env.get(op.inputs[0]), env.get(op.inputs[1])
+        d_aux = [env.get(n) if n is not None else None for n in op.inputs[2:]]
+        aux_names: List[str] = op.attrs.get("aux", [])
+        for L in reversed(range(self.cm.n_layers)):
+            bt = self.cm.layer_types[L]
+            fg, bg = self.cm.block_fwd[bt], self.cm.block_bwd[bt]
+            ctx.layer = L
+            self.store.layer_start(L, "bwd")
+            saved = self._layer_saved[L]
+            self._layer_saved[L] = None
+            if saved.get("__recompute__"):
+                benv = {k: v for k, v in saved.items() if k != "__recompute__"}
+                ctx.phase = "recompute"
+                self.run_graph(fg, benv, ctx, self._saved_sets[bt] | set(fg.outputs))
+                ctx.phase = "bwd"
+                saved = {k: v for k, v in benv.items() if k in self._saved_sets[bt]}
+            benv = dict(saved)
+            og = bg.meta["out_grads"]
+            benv[og[fg.outputs[0]]] = d_x
+            benv[og[fg.outputs[1]]] = d_res
+            for i, a in enumerate(fg.outputs[2:]):
+                benv[og[a]] = d_aux[i] if i < len(d_aux) else None
+            if d_res is None:
+                # residual stream gradient absent (never happens after a final norm, kept for generality)
+                benv[og[fg.outputs[1]]] = torch.zeros_like(d_x)
+            self.run_graph(bg, benv, ctx, set(bg.outputs))
+            ig = bg.meta["input_grads"]
+            d_x, d_res = benv[ig["x"]], benv[ig["residual"]]
+            self.store.layer_end(L, "bwd")
+        ctx.layer = None
+        return [d_x, d_res]
+
+    # ------------------------------------------------------------------ public API
+    def new_context(self, token_ids: torch.Tensor, training: bool) -> ExecContext:
+        ctx = ExecContext(self)
+        ctx.training = training
+        ctx.dims = {"B": int(token_ids.shape[0]), "T": int(token_ids.shape[1])}
+        return ctx
+
+    def forward(self, token_ids, position_ids, targets, *, training: bool = True, loss_scale: Any = 1.0,
+                aux_scale: float = 1.0, doc_ids=None, micro_step: int = 0) -> Tuple[ExecContext, List[Any]]:
+        """Run the forward graph.  In training mode the LM-head op also produces d_x / d_w (fused loss backward)."""
+        ctx = self.new_context(token_ids, training)
+        ctx.loss_scale, ctx.aux_scale, ctx.doc_ids, ctx.micro_step = loss_scale, aux_scale, doc_ids, micro_step
+        ctx.phase = "fwd"
+        g = self.cm.fwd
+        env = {"token_ids": token_ids, "position_ids": position_ids, "targets": targets}
+        self.store.group_start("embedding", "fwd")
+        keep = (self._top_saved if training else set()) | set(g.outputs)
+        self.run_graph(g, env, ctx, keep)
+        self._top_env = env
+        return ctx, [env[o] for o in g.outputs]
+
+    def backward(self, ctx: ExecContext) -> None:
+        g, bg = self.cm.fwd, self.cm.bwd
+        env = {k: v for k, v in self._top_env.items() if k in self._top_saved or k in g.inputs}
+        self._top_env = {}
+        og = bg.meta["out_grads"]
+        env[og[g.outputs[0]]] = 1.0
+        for o in g.outputs[1:]:
+            env[og[o]] = ctx.aux_scale
+        ctx.phase = "bwd"
+        self.run_graph(bg, env, ctx, set())
+        self.store.group_end("embedding", "bwd")
+
+    def forward_backward(self, token_ids, position_ids, targets, **kw):
+        ctx, outs = self.forward(token_ids, position_ids, targets, training=True, **kw)
+        self.backward(ctx)
+        return ctx, outs

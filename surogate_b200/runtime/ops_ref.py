@@ -1,0 +1,513 @@
+"""Reference implementations of every IR op in plain PyTorch (explicit forward AND backward, no autograd).
+
+This backend is (a) the numerical oracle for the CUDA kernels, (b) the CPU path
+used by the fp32 plumbing tests and by gloo multi-rank tests, and (c) on a GPU
+the "library" baseline arm (torch matmul -> cuBLAS, torch SDPA).  The CUDA
+backend subclasses it and overrides the hot ops with hand-written sm_100a
+kernels.
+
+Op implementations are methods named after the op kind; each takes
+``(ctx, op, *inputs)`` and returns a tuple of outputs (one per declared output).
+A backward op may return ``None`` for a ``grad::`` output it has already
+accumulated in place through ``ctx.grad_sink``.
+
+Parity: csrc/src/runtime/ops/*.cpp (per-op forward/backward dispatch).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as TF
+
+IGNORE_INDEX = -100
+
+
+@dataclass
+class MoEPlan:
+    """Routing plan shared by permute / grouped GEMM / un-permute (all tensors live on the device)."""
+    sorted_src: torch.Tensor  # [N*K] int64: flat (token*K + k) index of each permuted row
+    counts: torch.Tensor  # [E] int32 rows per (local) expert
+    offsets: torch.Tensor  # [E+1] int32 exclusive scan
+    num_tokens: int
+    top_k: int
+    num_experts: int
+    x_shape: Tuple[int, ...] = ()  # shape of the un-permuted activation
+    local: Optional["MoEPlan"] = None  # set on an EP plan: the sender-side permutation
+    ep: Any = None  # EP bookkeeping (send/recv splits)
+
+
+class RefOps:
+    name = "ref"
+
+    def __init__(self, lmhead_chunk_rows: int = 4096):
+        self.lmhead_chunk_rows = lmhead_chunk_rows
+
+    # ------------------------------------------------------------------ helpers
+    def compute_dtype(self, t: torch.Tensor):
+        return torch.float32 if t.dtype in (torch.bfloat16, torch.float16) else t.dtype
+
+    def rope_cos_sin(self, position_ids: torch.Tensor, rotary_dim: int, theta: float):
+        half = rotary_dim // 2
+        inv = theta ** (-torch.arange(0, half, device=position_ids.device, dtype=torch.float32) * 2.0 / rotary_dim)
+        ang = position_ids.to(torch.float32).unsqueeze(-1) * inv  # [B,T,half]
+        return ang.cos(), ang.sin()
+
+    # ------------------------------------------------------------------ simple ops
+    def zeros(self, ctx, op):
+        shape = ctx.eval_shape(op.attrs["shape"])
+        return (torch.zeros(shape, dtype=ctx.dtype_of(op.attrs.get("dtype", "act")), device=ctx.device),)
+
+    def add(self, ctx, op, a, b):
+        return (a + b,)
+
+    def mul(self, ctx, op, a, b):
+        return (a * b,)
+
+    def scale(self, ctx, op, a):
+        return (a * op.attrs["factor"],)
+
+    def view(self, ctx, op, a):
+        return (a.reshape(ctx.eval_shape(op.attrs["shape"])),)
+
+    def silu(self, ctx, op, x):
+        return (TF.silu(x),)
+
+    def silu_backward(self, ctx, op, dy, x):
+        xf = x.float()
+        s = torch.sigmoid(xf)
+        return ((dy.float() * s * (1 + xf * (1 - s))).to(x.dtype),)
+
+    def gelu(self, ctx, op, x):
+        return (TF.gelu(x, approximate="tanh"),)
+
+    def gelu_backward(self, ctx, op, dy, x):
+        xf = x.float()
+        c = math.sqrt(2.0 / math.pi)
+        u = c * (xf + 0.044715 * xf ** 3)
+        t = torch.tanh(u)
+        d = 0.5 * (1 + t) + 0.5 * xf * (1 - t * t) * c * (1 + 3 * 0.044715 * xf * xf)
+        return ((dy.float() * d).to(x.dtype),)
+
+    # ------------------------------------------------------------------ embedding
+    def embedding(self, ctx, op, token_ids, weight):
+        return (weight[token_ids.long()].to(ctx.act_dtype),)
+
+    def embedding_backward(self, ctx, op, d_x, token_ids):
+        pname = op.outputs[0]
+        C = d_x.shape[-1]
+        tgt, acc = ctx.grad_target(pname)
+        if tgt is None:
+            return (None,)
+        if not acc:
+            tgt.zero_()
+        tgt.index_add_(0, token_ids.reshape(-1).long(), d_x.reshape(-1, C).to(tgt.dtype))
+        return (None,)
+
+    # ------------------------------------------------------------------ norms
+    def rmsnorm(self, ctx, op, x, w):
+        xf = x.float()
+        rstd = torch.rsqrt(xf.pow(2).mean(-1) + op.attrs["eps"])
+        y = xf * rstd.unsqueeze(-1) * w.float()
+        return y.to(x.dtype), rstd
+
+    def fused_residual_rmsnorm(self, ctx, op, residual, x, w):
+        r = residual + x
+        y, rstd = self.rmsnorm(ctx, op, r, w)
+        return r, y, rstd
+
+    def rmsnorm_backward(self, ctx, op, dy, x, w, rstd, d_res):
+        xf, dyf = x.float(), dy.float()
+        xhat = xf * rstd.unsqueeze(-1)
+        dn = dyf * w.float()
+        dx = rstd.unsqueeze(-1) * (dn - xhat * (dn * xhat).mean(-1, keepdim=True))
+        if d_res is not None:
+            dx = dx + d_res.float()
+        dw = (dyf * xhat).reshape(-1, x.shape[-1]).sum(0)
+        return dx.to(x.dtype), dw
+
+    # ------------------------------------------------------------------ matmul
+    def matmul(self, ctx, op, x, w, bias):
+        y = ctx.recipe.forward_matmul(ctx, op, x, w, bias) if ctx.recipe is not None else None
+        if y is None:
+            y = TF.linear(x, w.to(x.dtype), bias.to(x.dtype) if bias is not None else None)
+        return (y,)
+
+    def matmul_backward(self, ctx, op, dy, x, w):
+        K = x.shape[-1]
+        N = dy.shape[-1]
+        dy2, x2 = dy.reshape(-1, N), x.reshape(-1, K)
+        r = ctx.recipe.backward_matmul(ctx, op, dy2, x2, w) if ctx.recipe is not None else None
+        if r is not None:
+            dx, dw = r
+        else:
+            dx = dy2 @ w.to(dy.dtype)
+            dw = self._wgrad(ctx, op.outputs[1], dy2, x2)
+        db = None
+        if op.outputs[2] is not None:
+            db = dy2.float().sum(0)
+        return dx.reshape(x.shape), dw, db
+
+    def _wgrad(self, ctx, pname, dy2, x2):
+        """dW = dy^T x, accumulated straight into the gradient buffer when one is bound."""
+        tgt, acc = ctx.grad_target(pname)
+        if tgt is None:
+            return None  # frozen parameter (e.g. LoRA base weight): no weight gradient
+        if tgt.dtype == dy2.dtype and tgt.is_contiguous():
+            if acc:
+                tgt.addmm_(dy2.t(), x2)
+            else:
+                torch.mm(dy2.t(), x2, out=tgt)
+        else:
+            g = (dy2.t() @ x2).to(tgt.dtype)
+            if acc:
+                tgt.add_(g)
+            else:
+                tgt.copy_(g)
+        return None
+
+    # ------------------------------------------------------------------ qk-norm + rope
+    def qkv_qk_norm_rope(self, ctx, op, qkv, qw, kw, pos):
+        a = op.attrs
+        Hq, Hkv, D, R = a["num_q_heads"], a["num_kv_heads"], a["head_dim"], a["rotary_dim"]
+        lead = qkv.shape[:-1]
+        x = qkv.float().reshape(*lead, Hq + 2 * Hkv, D)
+        q, k, v = x[..., :Hq, :], x[..., Hq:Hq + Hkv, :], x[..., Hq + Hkv:, :]
+        q_rstd = k_rstd = None
+        if qw is not None:
+            q_rstd = torch.rsqrt(q.pow(2).mean(-1) + a["eps"])
+            k_rstd = torch.rsqrt(k.pow(2).mean(-1) + a["eps"])
+            q = q * q_rstd.unsqueeze(-1) * qw.float()
+            k = k * k_rstd.unsqueeze(-1) * kw.float()
+        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"])
+        q, k = self._rope(q, cos, sin, R, False), self._rope(k, cos, sin, R, False)
+        out = torch.cat([q, k, v], dim=-2).reshape(qkv.shape).to(qkv.dtype)
+        return out, q_rstd, k_rstd
+
+    @staticmethod
+    def _rope(x, cos, sin, R, conj):
+        # x [..., H, D]; cos/sin [..., R/2] broadcast over heads
+        h = R // 2
+        c, s = cos.unsqueeze(-2), sin.unsqueeze(-2)
+        if conj:
+            s = -s
+        x1, x2, rest = x[..., :h], x[..., h:R], x[..., R:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
+
+    def qkv_qk_norm_rope_backward(self, ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos):
+        a = op.attrs
+        Hq, Hkv, D, R = a["num_q_heads"], a["num_kv_heads"], a["head_dim"], a["rotary_dim"]
+        lead = qkv.shape[:-1]
+        g = dy.float().reshape(*lead, Hq + 2 * Hkv, D)
+        x = qkv.float().reshape(*lead, Hq + 2 * Hkv, D)
+        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"])
+        gq, gk, gv = g[..., :Hq, :], g[..., Hq:Hq + Hkv, :], g[..., Hq + Hkv:, :]
+        gq, gk = self._rope(gq, cos, sin, R, True), self._rope(gk, cos, sin, R, True)
+        dqw = dkw = None
+        if qw is not None:
+            def nb(gy, xin, w, rstd):
+                xhat = xin * rstd.unsqueeze(-1)
+                dn = gy * w.float()
+                dx = rstd.unsqueeze(-1) * (dn - xhat * (dn * xhat).mean(-1, keepdim=True))
+                return dx, (gy * xhat).reshape(-1, D).sum(0)
+            gq, dqw = nb(gq, x[..., :Hq, :], qw, q_rstd)
+            gk, dkw = nb(gk, x[..., Hq:Hq + Hkv, :], kw, k_rstd)
+        dx = torch.cat([gq, gk, gv], dim=-2).reshape(qkv.shape).to(qkv.dtype)
+        return dx, dqw, dkw
+
+    # ------------------------------------------------------------------ attention
+    def _split_heads(self, qkv, a):
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        B, T = qkv.shape[0], qkv.shape[1]
+        x = qkv.reshape(B, T, Hq + 2 * Hkv, D)
+        return x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
+
+    def flash_attention(self, ctx, op, qkv):
+        a = op.attrs
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        q, k, v = self._split_heads(qkv, a)
+        B, T = qkv.shape[:2]
+        if qkv.is_cuda:
+            return self._attention_library(ctx, op, q, k, v, scale)
+        G = Hq // Hkv
+        qf = q.float().permute(0, 2, 1, 3)  # B,Hq,T,D
+        kf = k.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+        vf = v.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+        s = qf @ kf.transpose(-1, -2) * scale
+        s = s + self._mask(T, a, s.device, ctx.doc_ids)
+        lse = torch.logsumexp(s, dim=-1)  # B,Hq,T
+        o = torch.exp(s - lse.unsqueeze(-1)) @ vf
+        att = o.permute(0, 2, 1, 3).reshape(B, T, Hq * D).to(qkv.dtype)
+        return att, lse.permute(0, 2, 1).contiguous()
+
+    @staticmethod
+    def _mask(T, a, device, doc_ids=None):
+        i = torch.arange(T, device=device)
+        ok = torch.ones(T, T, dtype=torch.bool, device=device)
+        if a.get("causal", True):
+            ok &= i[:, None] >= i[None, :]
+        if a.get("window", 0):
+            ok &= (i[:, None] - i[None, :]) < a["window"]
+        m = torch.zeros(T, T, device=device).masked_fill(~ok, float("-inf"))
+        if doc_ids is not None:  # packed documents: tokens attend within their own document only
+            same = doc_ids[:, :, None] == doc_ids[:, None, :]
+            m = m.unsqueeze(0).expand(doc_ids.shape[0], T, T).masked_fill(~same, float("-inf")).unsqueeze(1)
+        return m
+
+    def flash_attention_backward(self, ctx, op, d_att, qkv, att, lse):
+        a = op.attrs
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        B, T = qkv.shape[:2]
+        if qkv.is_cuda:
+            return self._attention_library_backward(ctx, op, d_att, qkv, att, lse)
+        G = Hq // Hkv
+        q, k, v = self._split_heads(qkv, a)
+        qf = q.float().permute(0, 2, 1, 3)
+        kf = k.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+        vf = v.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+        do = d_att.float().reshape(B, T, Hq, D).permute(0, 2, 1, 3)
+        o = att.float().reshape(B, T, Hq, D).permute(0, 2, 1, 3)
+        s = qf @ kf.transpose(-1, -2) * scale + self._mask(T, a, qkv.device, ctx.doc_ids)
+        p = torch.exp(s - lse.permute(0, 2, 1).unsqueeze(-1))
+        dv = p.transpose(-1, -2) @ do
+        dp = do @ vf.transpose(-1, -2)
+        delta = (do * o).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq = ds @ kf
+        dk = ds.transpose(-1, -2) @ qf
+        dk = dk.reshape(B, Hkv, G, T, D).sum(2)
+        dv = dv.reshape(B, Hkv, G, T, D).sum(2)
+        out = torch.cat([dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)], dim=2)
+        return (out.reshape(qkv.shape).to(qkv.dtype),)
+
+    # library attention on a GPU: torch SDPA (cuDNN / flash kernels); the autograd node is kept as the "lse" slot
+    def _attention_library(self, ctx, op, q, k, v, scale):
+        a = op.attrs
+        B, T = q.shape[:2]
+        with torch.enable_grad():
+            qh = q.transpose(1, 2).detach().requires_grad_(ctx.training)
+            kh = k.transpose(1, 2).detach().requires_grad_(ctx.training)
+            vh = v.transpose(1, 2).detach().requires_grad_(ctx.training)
+            o = TF.scaled_dot_product_attention(qh, kh, vh, is_causal=a.get("causal", True), scale=scale,
+                                                enable_gqa=a["num_q_heads"] != a["num_kv_heads"])
+        att = o.detach().transpose(1, 2).reshape(B, T, -1)
+        return att, _AutogradHandle(o, (qh, kh, vh)) if ctx.training else None
+
+    def _attention_library_backward(self, ctx, op, d_att, qkv, att, handle):
+        a = op.attrs
+        B, T = qkv.shape[:2]
+        do = d_att.reshape(B, T, a["num_q_heads"], a["head_dim"]).transpose(1, 2)
+        dq, dk, dv = torch.autograd.grad(handle.out, handle.inputs, do)
+        out = torch.cat([dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)], dim=2)
+        return (out.reshape(qkv.shape),)
+
+    # ------------------------------------------------------------------ swiglu
+    def swiglu(self, ctx, op, x):
+        M = x.shape[-1] // 2
+        up, gate = x[..., :M].float(), x[..., M:].float()
+        return ((TF.silu(gate) * up).to(x.dtype),)
+
+    def swiglu_backward(self, ctx, op, dy, x):
+        M = x.shape[-1] // 2
+        up, gate = x[..., :M].float(), x[..., M:].float()
+        s = torch.sigmoid(gate)
+        g = dy.float()
+        d_up = g * gate * s
+        d_gate = g * up * s * (1 + gate * (1 - s))
+        return (torch.cat([d_up, d_gate], dim=-1).to(x.dtype),)
+
+    # ------------------------------------------------------------------ LM head + loss
+    def fused_lm_head_loss(self, ctx, op, x, w, targets):
+        """Returns the summed CE over valid tokens.  In training mode also computes d_x (stashed) and d_w now."""
+        C = x.shape[-1]
+        x2, t = x.reshape(-1, C), targets.reshape(-1).long()
+        n = x2.shape[0]
+        loss = torch.zeros((), dtype=torch.float32, device=x.device)
+        train = ctx.training
+        dx = torch.empty_like(x2) if train else None
+        pname = None
+        if train:
+            pname = "grad::" + op.inputs[1]
+            tgt, acc = ctx.grad_target(pname)
+        scale = ctx.loss_scale
+        cap = op.attrs.get("softcap", 0.0)
+        rows = self.lmhead_chunk_rows
+        for s in range(0, n, rows):
+            xs, ts = x2[s:s + rows], t[s:s + rows]
+            logits = (xs @ w.to(xs.dtype).t()).float()
+            if cap:
+                th = torch.tanh(logits / cap)
+                logits = th * cap
+            valid = ts != IGNORE_INDEX
+            tsafe = ts.clamp_min(0)
+            lse = torch.logsumexp(logits, dim=-1)
+            tok_loss = (lse - logits.gather(1, tsafe[:, None]).squeeze(1)) * valid
+            loss += tok_loss.sum()
+            if train:
+                p = torch.exp(logits - lse[:, None])
+                p.scatter_add_(1, tsafe[:, None], -torch.ones_like(p[:, :1]))
+                p *= (valid[:, None] * scale)
+                if cap:
+                    p *= (1 - th * th)
+                pd = p.to(xs.dtype)
+                dx[s:s + rows] = pd @ w.to(xs.dtype)
+                if tgt is not None:
+                    g = pd.t() @ xs
+                    if acc:
+                        tgt.add_(g.to(tgt.dtype))
+                    else:
+                        tgt.copy_(g.to(tgt.dtype))
+                        acc = True
+        if train:
+            ctx.stash[op.outputs[0]] = dx.reshape(x.shape)
+        return (loss,)
+
+    def fused_lm_head_loss_backward(self, ctx, op, d_loss, x, w, targets, loss):
+        dx = ctx.stash.pop(op.inputs[4])
+        return dx, None
+
+    # ------------------------------------------------------------------ MoE
+    def moe_router(self, ctx, op, x, rw):
+        a = op.attrs
+        E, K = a["num_experts"], a["top_k"]
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        logits = x2.float() @ rw.float().t()
+        probs = torch.softmax(logits, -1) if a["scoring"] == "softmax" else torch.sigmoid(logits)
+        tw, ti = torch.topk(probs, K, dim=-1)
+        if a["norm_topk_prob"]:
+            tw = tw / tw.sum(-1, keepdim=True)
+        N = x2.shape[0]
+        counts = torch.bincount(ti.reshape(-1), minlength=E).float()
+        aux = a["aux_loss_coef"] * E * ((counts / N) * probs.mean(0)).sum()
+        if a.get("z_loss_coef", 0.0):
+            aux = aux + a["z_loss_coef"] * torch.logsumexp(logits, -1).pow(2).mean()
+        ctx.record_moe_stats(counts, probs)
+        lead = x.shape[:-1]
+        return tw.reshape(*lead, K), ti.to(torch.int32).reshape(*lead, K), aux
+
+    def moe_router_backward(self, ctx, op, d_tw, d_aux, x, rw, tw, ti):
+        a = op.attrs
+        E, K = a["num_experts"], a["top_k"]
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        N = x2.shape[0]
+        logits = x2.float() @ rw.float().t()
+        soft = a["scoring"] == "softmax"
+        probs = torch.softmax(logits, -1) if soft else torch.sigmoid(logits)
+        til = ti.reshape(N, K).long()
+        sel = probs.gather(1, til)
+        d_sel = torch.zeros_like(sel)
+        if d_tw is not None:
+            g = d_tw.reshape(N, K).float()
+            if a["norm_topk_prob"]:
+                ssum = sel.sum(-1, keepdim=True)
+                d_sel = g / ssum - (g * sel).sum(-1, keepdim=True) / (ssum * ssum)
+            else:
+                d_sel = g
+        d_probs = torch.zeros_like(probs).scatter_add_(1, til, d_sel)
+        d_logits_extra = None
+        if d_aux is not None:
+            da = d_aux if torch.is_tensor(d_aux) else torch.tensor(float(d_aux), device=x.device)
+            counts = torch.bincount(til.reshape(-1), minlength=E).float()
+            d_probs = d_probs + da * a["aux_loss_coef"] * E * (counts / N) / N
+            if a.get("z_loss_coef", 0.0):
+                lse = torch.logsumexp(logits, -1, keepdim=True)
+                d_logits_extra = da * a["z_loss_coef"] * 2 * lse / N * torch.softmax(logits, -1)
+        if soft:
+            d_logits = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
+        else:
+            d_logits = d_probs * probs * (1 - probs)
+        if d_logits_extra is not None:
+            d_logits = d_logits + d_logits_extra
+        dx = (d_logits @ rw.float()).to(x.dtype).reshape(x.shape)
+        drw = d_logits.t() @ x2.float()
+        return dx, drw
+
+    def moe_permute(self, ctx, op, x, ti):
+        a = op.attrs
+        E, K = a["num_experts"], a["top_k"]
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        flat = ti.reshape(-1).long()
+        sorted_src = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=E).to(torch.int32)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=x.device)
+        offsets[1:] = torch.cumsum(counts, 0)
+        xp = x2[sorted_src // K]
+        return xp, MoEPlan(sorted_src, counts, offsets, x2.shape[0], K, E, tuple(x.shape))
+
+    def moe_permute_backward(self, ctx, op, d_xp, plan):
+        plan = plan.local or plan
+        C = d_xp.shape[-1]
+        dx = torch.zeros(plan.num_tokens, C, dtype=torch.float32, device=d_xp.device)
+        dx.index_add_(0, plan.sorted_src // plan.top_k, d_xp.float())
+        return (dx.to(d_xp.dtype).reshape(plan.x_shape),)
+
+    def _expert_ranges(self, plan):
+        off = plan.offsets.tolist()  # host sync: reference path only
+        return [(e, off[e], off[e + 1]) for e in range(len(off) - 1) if off[e + 1] > off[e]]
+
+    def moe_grouped_gemm(self, ctx, op, x, w, plan):
+        y = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+        w = ctx.local_experts(w)
+        for e, s, t in self._expert_ranges(plan):
+            y[s:t] = x[s:t] @ w[e].to(x.dtype).t()
+        return (y,)
+
+    def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
+        dx = torch.empty_like(x)
+        wl = ctx.local_experts(w)
+        tgt, acc = ctx.grad_target(op.outputs[1])
+        if tgt is not None:
+            tgt = ctx.local_experts(tgt)
+            if not acc:
+                tgt.zero_()
+        for e, s, t in self._expert_ranges(plan):
+            dx[s:t] = dy[s:t] @ wl[e].to(dy.dtype)
+            if tgt is not None:
+                tgt[e] += (dy[s:t].t() @ x[s:t]).to(tgt.dtype)
+        return dx, None
+
+    def moe_unpermute(self, ctx, op, yp, tw, plan):
+        plan = plan.local or plan
+        N, K = plan.num_tokens, plan.top_k
+        C = yp.shape[-1]
+        wflat = tw.reshape(-1).float()[plan.sorted_src]  # weight of each permuted row
+        y = torch.zeros(N, C, dtype=torch.float32, device=yp.device)
+        y.index_add_(0, plan.sorted_src // K, yp.float() * wflat[:, None])
+        return (y.to(yp.dtype).reshape(plan.x_shape),)
+
+    def moe_unpermute_backward(self, ctx, op, dy, yp, tw, plan):
+        plan = plan.local or plan
+        N, K = plan.num_tokens, plan.top_k
+        C = yp.shape[-1]
+        dy2 = dy.reshape(N, C).float()
+        tok = plan.sorted_src // K
+        wflat = tw.reshape(-1).float()[plan.sorted_src]
+        d_yp = (dy2[tok] * wflat[:, None]).to(yp.dtype)
+        d_w_sorted = (yp.float() * dy2[tok]).sum(-1)
+        d_tw = torch.zeros(N * K, dtype=torch.float32, device=yp.device)
+        d_tw[plan.sorted_src] = d_w_sorted
+        return d_yp, d_tw.reshape(tw.shape)
+
+    # EP ops: identity unless a parallel context overrides them
+    def ep_dispatch(self, ctx, op, xp, plan):
+        return ctx.ep.dispatch(ctx, xp, plan) if ctx.ep is not None else (xp, plan)
+
+    def ep_combine(self, ctx, op, y, plan):
+        return (ctx.ep.combine(ctx, y, plan),) if ctx.ep is not None else (y,)
+
+    def ep_dispatch_backward(self, ctx, op, dy, plan):
+        return (ctx.ep.dispatch_backward(ctx, dy, plan),) if ctx.ep is not None else (dy,)
+
+
+class _AutogradHandle:
+    """Keeps a library attention call's autograd graph alive between forward and backward."""
+
+    def __init__(self, out, inputs):
+        self.out, self.inputs = out, inputs

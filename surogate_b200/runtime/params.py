@@ -1,0 +1,392 @@
+"""Parameter / gradient storage in flat per-layer buckets, with ZeRO-1/2/3 sharding.
+
+Every layer (and each of embedding / final norm / LM head) owns one contiguous
+*bucket*.  A bucket is the concatenation of its parameters, each starting on a
+256-byte boundary, padded so that it splits evenly across ranks.  Rank ``r``
+owns elements ``[r*S, (r+1)*S)`` of every bucket (master weights, optimizer
+state).  Consequences:
+
+* a ZeRO-3 weight gather and a gradient reduce-scatter are each ONE contiguous
+  collective per layer, and the element-wise optimizer runs on the flat shard;
+* parameters are views into the gathered bucket, gradients views into the
+  bucket-sized gradient buffer that weight-gradient GEMMs accumulate into.
+
+Sharding levels (``zero_level``): 0 = replicated + all-reduce; 1 = gradients
+reduce-scattered at the last micro-step, optimizer state and master weights
+sharded, updated weights all-gathered once per step; 2 = additionally the
+bucket-sized gradient buffers are transient (reduce-scatter every micro-step
+into an fp32 shard accumulator); 3 = additionally the gathered work weights are
+transient: gathered per layer one layer ahead of use and released after use
+(or kept for the rest of the step when ``keep_gathered`` and memory allow).
+
+Parity: csrc/src/runtime/dsl/dsl_param_store, dsl_grad_store.cpp:457-678
+(notify_block / scatter_reduce_layer), dsl_weight_manager.cpp:779-1076 (gather_block).
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from ..dsl.compiler import CompiledModel, ParamEntry
+
+ALIGN_ELEMS = 128
+
+
+@dataclass
+class Slot:
+    name: str
+    offset: int
+    numel: int
+    shape: Tuple[int, ...]
+    decay: bool
+    entry: ParamEntry
+    trainable: bool = True
+
+
+class Bucket:
+    def __init__(self, name: str, layer: Optional[int]):
+        self.name = name
+        self.layer = layer
+        self.slots: List[Slot] = []
+        self.numel = 0  # padded
+        self.shard_numel = 0
+        self.master: Optional[torch.Tensor] = None  # [shard_numel] (or full when world == 1 / level 0)
+        self.work: Optional[torch.Tensor] = None  # [numel] gathered work weights (None when released)
+        self.grad: Optional[torch.Tensor] = None  # [numel] full-size gradient buffer
+        self.grad_shard: Optional[torch.Tensor] = None  # [shard_numel] reduced gradient owned by this rank
+        self.gather_work: Any = None
+        self.reduce_work: Any = None
+        self.written: set = set()
+        self.trainable = True
+        self.decay_mask_cache: Optional[torch.Tensor] = None
+
+    def slot(self, name: str) -> Slot:
+        for s in self.slots:
+            if s.name == name:
+                return s
+        raise KeyError(name)
+
+
+class SingleProcessComm:
+    """Collectives for world size 1 (all are copies / no-ops)."""
+    rank, world = 0, 1
+
+    def all_gather(self, shard, full, async_op=False):
+        if full.data_ptr() != shard.data_ptr():
+            full.copy_(shard)
+        return None
+
+    def reduce_scatter(self, full, shard, async_op=False, average=True):
+        if shard.data_ptr() != full.data_ptr():
+            shard.copy_(full)
+        return None
+
+    def all_reduce(self, t, op="sum", async_op=False):
+        return None
+
+    def barrier(self):
+        pass
+
+
+class ParamStore:
+    def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
+                 comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
+                 expert_parallel: int = 1):
+        self.cm = cm
+        self.device = torch.device(device)
+        self.param_dtype = param_dtype
+        self.grad_dtype = grad_dtype or param_dtype
+        self.master_dtype = master_dtype or param_dtype
+        self.comm = comm or SingleProcessComm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.zero_level = zero_level if self.world > 1 else 0
+        self.keep_gathered = keep_gathered
+        self.frozen = frozen or (lambda name: False)
+        self.buckets: "OrderedDict[str, Bucket]" = OrderedDict()
+        self.where: Dict[str, Tuple[Bucket, Slot]] = {}
+        self.alias: Dict[str, str] = {}
+        self.first_micro_step = True
+        self.last_micro_step = True
+        self.grads_enabled = True
+        self.post_gather: Optional[Callable[[Bucket], None]] = None
+        self._build()
+
+    # ------------------------------------------------------------------ layout
+    def _build(self) -> None:
+        for e in self.cm.params:
+            if e.tied_to:
+                self.alias[e.name] = e.tied_to
+                continue
+            b = self.buckets.get(e.group)
+            if b is None:
+                b = self.buckets[e.group] = Bucket(e.group, e.layer)
+            n = math.prod(e.spec.shape)
+            slot = Slot(e.name, b.numel, n, tuple(e.spec.shape), e.spec.decay, e, trainable=not self.frozen(e.name))
+            b.slots.append(slot)
+            b.numel += (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
+            self.where[e.name] = (b, slot)
+        quantum = self.world * ALIGN_ELEMS
+        for b in self.buckets.values():
+            b.numel = (b.numel + quantum - 1) // quantum * quantum
+            b.shard_numel = b.numel // self.world if self.sharded else b.numel
+            b.trainable = any(s.trainable for s in b.slots)
+            b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, device=self.device)
+            if not self.sharded and self.master_dtype == self.param_dtype:
+                b.work = b.master
+            elif self.zero_level < 3:
+                b.work = torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
+
+    @property
+    def sharded(self) -> bool:
+        return self.zero_level >= 1
+
+    def resolve(self, name: str) -> str:
+        return self.alias.get(name, name)
+
+    def shard_range(self, b: Bucket) -> Tuple[int, int]:
+        if not self.sharded:
+            return 0, b.numel
+        return self.rank * b.shard_numel, (self.rank + 1) * b.shard_numel
+
+    # ------------------------------------------------------------------ init / import / export
+    def init_weights(self, seed: int = 0, std: float = 0.02, zero_projections: bool = False) -> None:
+        """Seeded N(0, std) init, identical for every world size (each parameter has its own generator stream)."""
+        for bi, b in enumerate(self.buckets.values()):
+            lo, hi = self.shard_range(b)
+            for si, s in enumerate(b.slots):
+                gen = torch.Generator(device="cpu").manual_seed(seed * 1000003 + bi * 1009 + si)
+                if s.entry.spec.init == "ones":
+                    full = torch.ones(s.numel)
+                elif s.entry.spec.init == "zeros" or (zero_projections and s.entry.local in ("out_weight", "mlp_down_weight", "experts_down")):
+                    full = torch.zeros(s.numel)
+                else:
+                    full = torch.empty(s.numel).normal_(0.0, std, generator=gen)
+                self._write_master(b, s, full)
+        self.sync_work_from_master()
+
+    def _write_master(self, b: Bucket, s: Slot, flat_cpu: torch.Tensor) -> None:
+        lo, hi = self.shard_range(b)
+        a, z = max(s.offset, lo), min(s.offset + s.numel, hi)
+        if a < z:
+            b.master[a - lo:z - lo].copy_(flat_cpu[a - s.offset:z - s.offset].to(self.master_dtype))
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        name = self.resolve(name)
+        b, s = self.where[name]
+        assert tuple(tensor.shape) == s.shape, f"{name}: expected {s.shape}, got {tuple(tensor.shape)}"
+        self._write_master(b, s, tensor.reshape(-1))
+
+    def full_tensor(self, name: str) -> torch.Tensor:
+        """Gather one parameter in full on every rank (export / debug)."""
+        name = self.resolve(name)
+        b, s = self.where[name]
+        if not self.sharded:
+            return b.master[s.offset:s.offset + s.numel].reshape(s.shape)
+        full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
+        self.comm.all_gather(b.master, full)
+        return full[s.offset:s.offset + s.numel].reshape(s.shape)
+
+    def named_full_tensors(self) -> Iterable[Tuple[str, torch.Tensor]]:
+        for b in self.buckets.values():
+            if self.sharded:
+                full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
+                self.comm.all_gather(b.master, full)
+            else:
+                full = b.master
+            for s in b.slots:
+                yield s.name, full[s.offset:s.offset + s.numel].reshape(s.shape)
+
+    def sync_work_from_master(self) -> None:
+        """Refresh the gathered work weights after the masters changed (init, load, optimizer step)."""
+        for b in self.buckets.values():
+            if self.zero_level >= 3:
+                b.work = None
+                b.gather_work = None
+                continue
+            if b.work is b.master:
+                continue
+            self._gather_into(b, b.work)
+            if self.post_gather is not None:
+                self.post_gather(b)
+
+    def _gather_into(self, b: Bucket, full: torch.Tensor, async_op: bool = False):
+        src = b.master if b.master.dtype == full.dtype else b.master.to(full.dtype)
+        if not self.sharded:
+            full.copy_(src)
+            return None
+        return self.comm.all_gather(src, full, async_op=async_op)
+
+    # ------------------------------------------------------------------ executor hooks
+    def _ensure_gathered(self, b: Bucket, prefetch_only: bool = False) -> None:
+        if b.work is None:
+            b.work = torch.empty(b.numel, dtype=self.param_dtype, device=self.device)
+            b.gather_work = self._gather_into(b, b.work, async_op=True)
+            b._needs_post = True
+        if not prefetch_only:
+            if b.gather_work is not None:
+                b.gather_work.wait()
+                b.gather_work = None
+            if getattr(b, "_needs_post", False):
+                b._needs_post = False
+                if self.post_gather is not None:
+                    self.post_gather(b)
+
+    def _release(self, b: Bucket) -> None:
+        if self.zero_level >= 3:
+            b.work = None
+
+    def _layer_bucket(self, L: int) -> Optional[Bucket]:
+        return self.buckets.get(f"layer{L}")
+
+    def layer_start(self, L: int, phase: str) -> None:
+        if self.zero_level < 3:
+            return
+        b = self._layer_bucket(L)
+        self._ensure_gathered(b)
+        nxt = L + 1 if phase == "fwd" else L - 1
+        nb = self._layer_bucket(nxt)
+        if nb is not None:
+            self._ensure_gathered(nb, prefetch_only=True)
+
+    def layer_end(self, L: int, phase: str) -> None:
+        b = self._layer_bucket(L)
+        if b is None:
+            return
+        if phase == "bwd":
+            self._reduce_bucket(b)
+            self._release(b)
+        elif not self.keep_gathered:
+            self._release(b)
+
+    def group_start(self, group: str, phase: str) -> None:
+        pass
+
+    def group_end(self, group: str, phase: str) -> None:
+        """Called after the whole backward: reduce the non-layer buckets (embedding, final norm, LM head)."""
+        for b in self.buckets.values():
+            if b.layer is None:
+                self._reduce_bucket(b)
+                if self.zero_level >= 3:
+                    self._release(b)
+
+    def get(self, name: str) -> torch.Tensor:
+        name = self.resolve(name)
+        b, s = self.where[name]
+        if b.work is None or b.gather_work is not None or getattr(b, "_needs_post", False):
+            self._ensure_gathered(b)
+        return b.work[s.offset:s.offset + s.numel].view(s.shape)
+
+    # ------------------------------------------------------------------ gradients
+    def begin_step(self) -> None:
+        for b in self.buckets.values():
+            b.written.clear()
+        self.first_micro_step = True
+
+    def begin_micro_step(self, index: int, total: int) -> None:
+        self.first_micro_step = index == 0
+        self.last_micro_step = index == total - 1
+        if self.zero_level >= 2:
+            for b in self.buckets.values():
+                b.written.clear()
+
+    def grad_target(self, name: str):
+        if not self.grads_enabled:
+            return None, False
+        name = self.resolve(name)
+        b, s = self.where[name]
+        if not s.trainable:
+            return None, False
+        if b.grad is None:
+            b.grad = torch.zeros(b.numel, dtype=self.grad_dtype, device=self.device)
+        acc = name in b.written
+        b.written.add(name)
+        return b.grad[s.offset:s.offset + s.numel].view(s.shape), acc
+
+    def _reduce_bucket(self, b: Bucket) -> None:
+        """Start the (async) gradient reduction of one bucket; called as soon as its backward is complete."""
+        if b.grad is None or not b.trainable:
+            return
+        for s in b.slots:  # parameters that received no gradient this micro-step contribute zeros
+            if s.trainable and s.name not in b.written and self.zero_level >= 2:
+                b.grad[s.offset:s.offset + s.numel].zero_()
+        if self.world == 1:
+            b.grad_shard = b.grad
+            return
+        if self.zero_level == 0:
+            if self.last_micro_step:
+                b.reduce_work = self.comm.all_reduce(b.grad, op="avg", async_op=True)
+                b.grad_shard = b.grad
+            return
+        if self.zero_level == 1:
+            if self.last_micro_step:
+                b.grad_shard = torch.empty(b.shard_numel, dtype=self.grad_dtype, device=self.device)
+                b.reduce_work = self.comm.reduce_scatter(b.grad, b.grad_shard, async_op=True)
+            return
+        # level 2/3: reduce-scatter every micro-step into an fp32 accumulator; the full buffer is transient
+        tmp = torch.empty(b.shard_numel, dtype=self.grad_dtype, device=self.device)
+        w = self.comm.reduce_scatter(b.grad, tmp, async_op=True)
+        if w is not None:
+            w.wait()
+        if b.grad_shard is None or self.first_micro_step:
+            b.grad_shard = tmp.float() if not self.last_micro_step else tmp
+        else:
+            b.grad_shard = b.grad_shard + tmp.float()
+        b.grad = None
+
+    def finish_reduce(self) -> None:
+        for b in self.buckets.values():
+            if b.reduce_work is not None:
+                b.reduce_work.wait()
+                b.reduce_work = None
+            if b.grad_shard is None and b.grad is not None and b.trainable:
+                b.grad_shard = b.grad
+
+    def trainable_buckets(self) -> List[Bucket]:
+        return [b for b in self.buckets.values() if b.trainable]
+
+    def decay_mask(self, b: Bucket) -> torch.Tensor:
+        """Per-element 0/1 weight-decay mask of this rank's shard (1 for matrices, 0 for norms/biases/padding)."""
+        if b.decay_mask_cache is None:
+            lo, hi = self.shard_range(b)
+            m = torch.zeros(hi - lo, dtype=torch.uint8, device=self.device)
+            for s in b.slots:
+                if s.decay and s.trainable:
+                    a, z = max(s.offset, lo), min(s.offset + s.numel, hi)
+                    if a < z:
+                        m[a - lo:z - lo] = 1
+            b.decay_mask_cache = m
+        return b.decay_mask_cache
+
+    def grad_of(self, name: str) -> Optional[torch.Tensor]:
+        """Full (reduced) gradient of one parameter — debugging / tests; gathers when sharded."""
+        name = self.resolve(name)
+        b, s = self.where[name]
+        g = b.grad_shard if b.grad_shard is not None else b.grad
+        if g is None:
+            return None
+        if g.numel() != b.numel:
+            full = torch.empty(b.numel, dtype=g.dtype, device=self.device)
+            self.comm.all_gather(g.contiguous(), full)
+            g = full
+        return g[s.offset:s.offset + s.numel].view(s.shape)
+
+    def release_grads(self) -> None:
+        for b in self.buckets.values():
+            if self.zero_level >= 1:
+                b.grad_shard = None
+            if self.zero_level >= 2:
+                b.grad = None
+
+    def memory_breakdown(self) -> Dict[str, int]:
+        out = {"master": 0, "work": 0, "grad": 0}
+        for b in self.buckets.values():
+            out["master"] += b.master.numel() * b.master.element_size()
+            if b.work is not None and b.work is not b.master:
+                out["work"] += b.work.numel() * b.work.element_size()
+            if b.grad is not None:
+                out["grad"] += b.grad.numel() * b.grad.element_size()
+        return out
