@@ -1,0 +1,318 @@
+// Python bindings (pybind11 through torch's extension machinery) for the sm_100a kernels.
+// Tensors are validated here (device, dtype, contiguity, alignment) so that kernels can assume their layout.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "gemm_sm100.h"
+#include "kernels.h"
+#include "ext_api.h"
+
+namespace {
+
+using torch::Tensor;
+
+int num_sms() {
+    static int n = 0;
+    if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    return n;
+}
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_cuda(const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+}
+void check_bf16(const Tensor& t, const char* name) {
+    check_cuda(t, name);
+    TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bf16");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+const float* opt_f32(const c10::optional<Tensor>& t) {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat, "scale/amax tensors must be CUDA fp32");
+    return t->data_ptr<float>();
+}
+float* opt_f32_mut(const c10::optional<Tensor>& t) { return const_cast<float*>(opt_f32(t)); }
+const void* opt_ptr(const c10::optional<Tensor>& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+
+Tensor g_error_flag;
+int* error_flag_ptr() {
+    if (!g_error_flag.defined()) g_error_flag = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+    return g_error_flag.data_ptr<int>();
+}
+
+// fmt: bf16 -> 1 ; float8_e4m3fn -> 0 ; float8_e5m2 -> 1 (uint8 tensors take the explicit *_fmt argument)
+int fp8_fmt_of(const Tensor& t, int64_t explicit_fmt) {
+    if (t.scalar_type() == at::kFloat8_e5m2) return 1;
+    if (t.scalar_type() == at::kFloat8_e4m3fn) return 0;
+    return static_cast<int>(explicit_fmt);
+}
+
+// D = alpha * sa * sb * op(A) op(B)^T (+ D).   a: [M,K] (a_mn=false) or [K,M] (a_mn=true); b: [N,K] or [K,N].
+void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, bool accumulate, double alpha, const c10::optional<Tensor>& scale_a,
+          const c10::optional<Tensor>& scale_b, const c10::optional<Tensor>& amax_out, int64_t a_fmt, int64_t b_fmt, int64_t tile_n) {
+    check_cuda(a, "a");
+    check_cuda(b, "b");
+    check_cuda(d, "d");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm operands must be 2-D");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm operands need a contiguous inner dimension");
+    TORCH_CHECK(a.element_size() == b.element_size(), "gemm operands must have the same element width");
+    const int es = static_cast<int>(a.element_size());
+    TORCH_CHECK(es == 1 || (es == 2 && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16), "gemm inputs must be bf16 or fp8");
+    TORCH_CHECK(d.scalar_type() == at::kBFloat16 || d.scalar_type() == at::kFloat, "gemm output must be bf16 or fp32");
+    const c10::cuda::CUDAGuard guard(a.device());
+    sg::GemmParams p{};
+    p.M = static_cast<int>(a_mn ? a.size(1) : a.size(0));
+    p.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
+    p.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+    const int64_t kb = b_mn ? b.size(0) : b.size(1);
+    TORCH_CHECK(kb == p.K, "gemm: contraction sizes differ (", p.K, " vs ", kb, ")");
+    TORCH_CHECK(d.size(0) == p.M && d.size(1) == p.N, "gemm: output must be [", p.M, ", ", p.N, "]");
+    p.elem_bytes = es;
+    p.a_fmt = es == 2 ? 1 : fp8_fmt_of(a, a_fmt);
+    p.b_fmt = es == 2 ? 1 : fp8_fmt_of(b, b_fmt);
+    p.a_mn = a_mn;
+    p.b_mn = b_mn;
+    p.D = d.data_ptr();
+    p.ldd = static_cast<int>(d.stride(0));
+    p.out_fp32 = d.scalar_type() == at::kFloat;
+    p.accumulate = accumulate;
+    p.alpha = static_cast<float>(alpha);
+    p.scale_a = opt_f32(scale_a);
+    p.scale_b = opt_f32(scale_b);
+    p.amax_out = opt_f32_mut(amax_out);
+    p.error_flag = error_flag_ptr();
+    p.tile_n = static_cast<int>(tile_n);
+    sg::GemmOperand A{a.data_ptr(), static_cast<uint64_t>(a.stride(0)) * es};
+    sg::GemmOperand B{b.data_ptr(), static_cast<uint64_t>(b.stride(0)) * es};
+    const char* err = sg::gemm_sm100(A, B, p, num_sms(), cur_stream());
+    TORCH_CHECK(err == nullptr, err ? err : "");
+}
+
+int64_t read_error_flag(bool reset) {
+    if (!g_error_flag.defined()) return 0;
+    const int64_t v = g_error_flag.item<int>();
+    if (reset && v) g_error_flag.zero_();
+    return v;
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, double eps, bool want_y,
+                                const c10::optional<Tensor>& fp8_scale, const c10::optional<Tensor>& amax_out, bool want_fp8) {
+    check_bf16(x, "x");
+    check_bf16(w, "w");
+    const int C = static_cast<int>(x.size(-1));
+    TORCH_CHECK(C % 8 == 0 && w.numel() == C, "rmsnorm: C must be a multiple of 8 and match the weight");
+    const int rows = static_cast<int>(x.numel() / C);
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor res_out, y, y8;
+    if (residual.has_value() && residual->defined()) {
+        check_bf16(*residual, "residual");
+        res_out = torch::empty_like(x);
+    }
+    if (want_y) y = torch::empty_like(x);
+    if (want_fp8) y8 = torch::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+    auto lead = x.sizes().vec();
+    lead.pop_back();
+    Tensor rstd = torch::empty(lead, x.options().dtype(at::kFloat));
+    sg::rmsnorm_fwd(x.data_ptr(), opt_ptr(residual), w.data_ptr(), res_out.defined() ? res_out.data_ptr() : nullptr, y.defined() ? y.data_ptr() : nullptr,
+                    rstd.data_ptr<float>(), y8.defined() ? y8.data_ptr() : nullptr, opt_f32(fp8_scale), opt_f32_mut(amax_out), rows, C,
+                    static_cast<float>(eps), cur_stream());
+    return {res_out, y, rstd, y8};
+}
+
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, const c10::optional<Tensor>& d_res) {
+    check_bf16(dy, "dy");
+    check_bf16(x, "x");
+    check_bf16(w, "w");
+    const int C = static_cast<int>(x.size(-1));
+    TORCH_CHECK(C % 8 == 0 && C <= 16384, "rmsnorm_bwd: C must be a multiple of 8 and <= 16384");
+    const int rows = static_cast<int>(x.numel() / C);
+    const c10::cuda::CUDAGuard guard(x.device());
+    if (d_res.has_value() && d_res->defined()) check_bf16(*d_res, "d_res");
+    Tensor dx = torch::empty_like(x);
+    const int blocks = sg::rmsnorm_bwd_blocks(rows, num_sms());
+    Tensor partial = torch::empty({blocks, C}, x.options().dtype(at::kFloat));
+    Tensor dw = torch::empty({C}, x.options().dtype(at::kFloat));
+    sg::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), opt_ptr(d_res), dx.data_ptr(), partial.data_ptr<float>(),
+                    dw.data_ptr<float>(), rows, C, num_sms(), cur_stream());
+    return {dx, dw};
+}
+
+std::vector<Tensor> swiglu_fwd(const Tensor& x, bool want_y, const c10::optional<Tensor>& fp8_scale, const c10::optional<Tensor>& amax_out, bool want_fp8) {
+    check_bf16(x, "x");
+    const int M = static_cast<int>(x.size(-1) / 2);
+    TORCH_CHECK(M % 8 == 0, "swiglu: M must be a multiple of 8");
+    const size_t rows = x.numel() / (2 * M);
+    const c10::cuda::CUDAGuard guard(x.device());
+    auto shape = x.sizes().vec();
+    shape.back() = M;
+    Tensor y, y8;
+    if (want_y) y = torch::empty(shape, x.options());
+    if (want_fp8) y8 = torch::empty(shape, x.options().dtype(at::kFloat8_e4m3fn));
+    sg::swiglu_fwd(x.data_ptr(), y.defined() ? y.data_ptr() : nullptr, y8.defined() ? y8.data_ptr() : nullptr, opt_f32(fp8_scale), opt_f32_mut(amax_out),
+                   rows, M, num_sms(), cur_stream());
+    return {y, y8};
+}
+
+Tensor swiglu_bwd(const Tensor& dy, const Tensor& x) {
+    check_bf16(dy, "dy");
+    check_bf16(x, "x");
+    const int M = static_cast<int>(x.size(-1) / 2);
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx = torch::empty_like(x);
+    sg::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel() / (2 * M), M, num_sms(), cur_stream());
+    return dx;
+}
+
+std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, const Tensor& pos, int64_t Hq,
+                                     int64_t Hkv, int64_t D, double eps, double theta) {
+    check_bf16(qkv, "qkv");
+    TORCH_CHECK(D == 128, "qk_norm_rope kernel supports head_dim 128");
+    TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kInt && pos.is_contiguous(), "position_ids must be contiguous CUDA int32");
+    const size_t tokens = qkv.numel() / ((Hq + 2 * Hkv) * D);
+    TORCH_CHECK(static_cast<size_t>(pos.numel()) == tokens, "position_ids must have one entry per token");
+    const c10::cuda::CUDAGuard guard(qkv.device());
+    Tensor out = torch::empty_like(qkv);
+    const bool norm = qw.has_value() && qw->defined();
+    Tensor q_rstd, k_rstd;
+    if (norm) {
+        check_bf16(*qw, "q_norm_weight");
+        check_bf16(*kw, "k_norm_weight");
+        auto lead = qkv.sizes().vec();
+        lead.back() = Hq;
+        q_rstd = torch::empty(lead, qkv.options().dtype(at::kFloat));
+        lead.back() = Hkv;
+        k_rstd = torch::empty(lead, qkv.options().dtype(at::kFloat));
+    }
+    sg::qk_norm_rope_fwd(qkv.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), out.data_ptr(), norm ? q_rstd.data_ptr<float>() : nullptr,
+                         norm ? k_rstd.data_ptr<float>() : nullptr, tokens, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps),
+                         static_cast<float>(theta), num_sms(), cur_stream());
+    return {out, q_rstd, k_rstd};
+}
+
+std::vector<Tensor> qk_norm_rope_bwd(const Tensor& d_out, const Tensor& qkv_pre, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw,
+                                     const c10::optional<Tensor>& q_rstd, const c10::optional<Tensor>& k_rstd, const Tensor& pos, int64_t Hq,
+                                     int64_t Hkv, int64_t D, double eps, double theta) {
+    check_bf16(d_out, "d_out");
+    check_bf16(qkv_pre, "qkv");
+    TORCH_CHECK(D == 128, "qk_norm_rope kernel supports head_dim 128");
+    const size_t tokens = d_out.numel() / ((Hq + 2 * Hkv) * D);
+    const c10::cuda::CUDAGuard guard(d_out.device());
+    Tensor dx = torch::empty_like(d_out);
+    const bool norm = qw.has_value() && qw->defined();
+    Tensor dqw, dkw;
+    if (norm) {
+        dqw = torch::zeros({D}, d_out.options().dtype(at::kFloat));
+        dkw = torch::zeros({D}, d_out.options().dtype(at::kFloat));
+    }
+    sg::qk_norm_rope_bwd(d_out.data_ptr(), qkv_pre.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), dx.data_ptr(), opt_f32_mut(q_rstd),
+                         opt_f32_mut(k_rstd), norm ? dqw.data_ptr<float>() : nullptr, norm ? dkw.data_ptr<float>() : nullptr, tokens,
+                         static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps), static_cast<float>(theta), num_sms(), cur_stream());
+    return {dx, dqw, dkw};
+}
+
+Tensor embedding_fwd(const Tensor& tokens, const Tensor& table) {
+    check_bf16(table, "table");
+    TORCH_CHECK(tokens.is_cuda() && tokens.scalar_type() == at::kInt && tokens.is_contiguous(), "tokens must be contiguous CUDA int32");
+    const int C = static_cast<int>(table.size(1));
+    TORCH_CHECK(C % 8 == 0, "embedding: C must be a multiple of 8");
+    const c10::cuda::CUDAGuard guard(table.device());
+    auto shape = tokens.sizes().vec();
+    shape.push_back(C);
+    Tensor out = torch::empty(shape, table.options());
+    sg::embedding_fwd(tokens.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tokens.numel(), C, num_sms(), cur_stream());
+    return out;
+}
+
+void embedding_bwd(const Tensor& tokens, const Tensor& d_out, Tensor& d_table) {
+    check_bf16(d_out, "d_out");
+    TORCH_CHECK(d_table.is_cuda() && d_table.is_contiguous(), "d_table must be contiguous CUDA");
+    TORCH_CHECK(d_table.scalar_type() == at::kFloat || d_table.scalar_type() == at::kBFloat16, "d_table must be fp32 or bf16");
+    const int C = static_cast<int>(d_table.size(1));
+    const c10::cuda::CUDAGuard guard(d_out.device());
+    sg::embedding_bwd(tokens.data_ptr<int>(), d_out.data_ptr(), d_table.data_ptr(), d_table.scalar_type() == at::kFloat, tokens.numel(), C, num_sms(),
+                      cur_stream());
+}
+
+// logits [rows, V] bf16 (row stride ld) are overwritten with d_logits when write_grad; returns per-row losses.
+Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& scale, double scale_host, bool write_grad) {
+    check_cuda(logits, "logits");
+    TORCH_CHECK(logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be 2-D bf16 with contiguous rows");
+    TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kInt && targets.is_contiguous(), "targets must be contiguous CUDA int32");
+    const int rows = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1)), ld = static_cast<int>(logits.stride(0));
+    TORCH_CHECK(V % 8 == 0 && ld % 8 == 0, "cross_entropy: V and row stride must be multiples of 8");
+    TORCH_CHECK(targets.numel() == rows, "one target per row");
+    const c10::cuda::CUDAGuard guard(logits.device());
+    Tensor loss = torch::empty({rows}, logits.options().dtype(at::kFloat));
+    sg::cross_entropy_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), loss.data_ptr<float>(), opt_f32(scale), static_cast<float>(scale_host), rows, V,
+                              ld, write_grad, cur_stream());
+    return loss;
+}
+
+Tensor quantize_fp8(const Tensor& x, const c10::optional<Tensor>& scale, const c10::optional<Tensor>& amax_out, bool e5m2) {
+    check_bf16(x, "x");
+    TORCH_CHECK(x.numel() % 8 == 0, "quantize_fp8: numel must be a multiple of 8");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor q = torch::empty(x.sizes(), x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+    sg::quantize_fp8(x.data_ptr(), q.data_ptr(), opt_f32(scale), opt_f32_mut(amax_out), x.numel(), e5m2, num_sms(), cur_stream());
+    return q;
+}
+
+void amax(const Tensor& x, Tensor& amax_out) {
+    check_bf16(x, "x");
+    TORCH_CHECK(x.numel() % 8 == 0, "amax: numel must be a multiple of 8");
+    const c10::cuda::CUDAGuard guard(x.device());
+    sg::amax_bf16(x.data_ptr(), amax_out.data_ptr<float>(), x.numel(), num_sms(), cur_stream());
+}
+
+Tensor sumsq(const Tensor& x) {
+    check_cuda(x, "x");
+    TORCH_CHECK(x.is_contiguous() && (x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16), "sumsq: contiguous fp32/bf16");
+    const c10::cuda::CUDAGuard guard(x.device());
+    const int nblocks = num_sms() * 2;
+    Tensor partial = torch::empty({nblocks}, x.options().dtype(at::kFloat));
+    sg::sumsq(x.data_ptr(), x.scalar_type() == at::kFloat, partial.data_ptr<float>(), nblocks, x.numel(), cur_stream());
+    return partial.sum();
+}
+
+void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::optional<Tensor>& mask, const Tensor& hp) {
+    check_cuda(p, "p");
+    TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous tensors");
+    TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && hp.scalar_type() == at::kFloat && hp.numel() >= 8, "adamw: fp32 state");
+    const c10::cuda::CUDAGuard guard(p.device());
+    sg::adamw_fp32(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr<float>(), v.data_ptr<float>(),
+                   static_cast<const uint8_t*>(opt_ptr(mask)), hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
+}
+
+void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms, Tensor& vs, const c10::optional<Tensor>& mask, const Tensor& hp) {
+    check_cuda(p, "p");
+    TORCH_CHECK(p.is_contiguous() && g.is_contiguous(), "adamw8: contiguous tensors");
+    TORCH_CHECK(m8.scalar_type() == at::kChar && v8.scalar_type() == at::kByte && ms.scalar_type() == at::kHalf && vs.scalar_type() == at::kHalf,
+                "adamw8: state dtypes int8/uint8/fp16/fp16");
+    TORCH_CHECK(static_cast<size_t>(ms.numel()) * 32 >= static_cast<size_t>(p.numel()), "adamw8: one scale per 32 elements");
+    const c10::cuda::CUDAGuard guard(p.device());
+    sg::adamw_8bit(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m8.data_ptr(), v8.data_ptr(), ms.data_ptr(),
+                   vs.data_ptr(), static_cast<const uint8_t*>(opt_ptr(mask)), hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("gemm", &gemm, "tcgen05 GEMM");
+    m.def("read_error_flag", &read_error_flag);
+    m.def("rmsnorm_fwd", &rmsnorm_fwd);
+    m.def("rmsnorm_bwd", &rmsnorm_bwd);
+    m.def("swiglu_fwd", &swiglu_fwd);
+    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
+    m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+    m.def("embedding_fwd", &embedding_fwd);
+    m.def("embedding_bwd", &embedding_bwd);
+    m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
+    m.def("quantize_fp8", &quantize_fp8);
+    m.def("amax", &amax);
+    m.def("sumsq", &sumsq);
+    m.def("adamw_step", &adamw_step);
+    m.def("adamw8_step", &adamw8_step);
+    sg_register_extra(m);
+}

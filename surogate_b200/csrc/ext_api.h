@@ -1,0 +1,4 @@
+// Registration hook that lets further binding files add functions to the one extension module.
+#pragma once
+#include <pybind11/pybind11.h>
+void sg_register_extra(pybind11::module_& m);

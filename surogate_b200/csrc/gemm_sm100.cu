@@ -1,0 +1,322 @@
+// Dense GEMM for sm_100a: D[M,N] = alpha * sa * sb * (A[M,K] . B[N,K]^T) (+ D), fp32 accumulation in TMEM.
+//
+// * Inputs bf16 (tcgen05 kind::f16) or FP8 e4m3/e5m2 in any mix (kind::f8f6f4).
+// * Each operand may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major).  Forward (x.W^T),
+//   dgrad (dy.W) and wgrad (dy^T.x) therefore all read the tensors as they lie in memory: no transposed
+//   copies of weights or activations are ever made, for bf16 or FP8.
+// * Persistent, warp-specialised: warp 0 issues TMA loads into a multi-stage shared-memory ring, warp 1
+//   issues tcgen05.mma (one elected thread), warps 2-5 drain the accumulator from TMEM (tcgen05.ld), apply
+//   the scales and write bf16 / fp32.  Two accumulators (2 x BN TMEM columns) let the epilogue of tile i
+//   overlap the main loop of tile i+1.
+// * Optional epilogue extras: accumulate into D (gradient accumulation), running abs-max of the output.
+// * No cluster multicast anywhere (loads are per-CTA), so the same kernel is used at any GPU count.
+//
+// Replaces the cuBLASLt calls of the reference (csrc/src/kernels/matmul.cpp:447-1000).
+#include <cuda_fp8.h>
+
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace sg {
+
+constexpr int BM = 128;
+constexpr int TILE_K_BYTES = 128;   // one swizzle row
+constexpr int A_STAGE_BYTES = BM * TILE_K_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 8;
+
+template <int BN> struct Cfg {
+    static constexpr int B_STAGE_BYTES = BN * TILE_K_BYTES;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+    const int per_group = GROUP_M * num_n;
+    const int group = tile / per_group;
+    const int first_m = group * GROUP_M;
+    const int gsize = min(num_m - first_m, GROUP_M);
+    const int r = tile - group * per_group;
+    m_blk = first_m + r % gsize;
+    n_blk = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+    // barrier layout (8 B each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + 2 + a); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int elems_per_row = TILE_K_BYTES / p.elem_bytes;  // K elements per stage (K-major) = BK
+    const int BK = elems_per_row;
+    const int num_k = (p.K + BK - 1) / BK;
+    const int num_m = (p.M + BM - 1) / BM;
+    const int num_n = (p.N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 128);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            const int a_chunks = p.a_mn ? (BM * p.elem_bytes) / TILE_K_BYTES : 1;
+            const int b_chunks = p.b_mn ? (BN * p.elem_bytes) / TILE_K_BYTES : 1;
+            const int chunk_bytes = BK * TILE_K_BYTES;   // MN-major chunk: BK rows of 128 B
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, m_blk, n_blk);
+                const int m0 = m_blk * BM, n0 = n_blk * BN;
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &tmA, k0, m0, full_bar(stage));
+                    } else {
+                        for (int c = 0; c < a_chunks; ++c) tma_load_2d(sa + c * chunk_bytes, &tmA, m0 + c * elems_per_row, k0, full_bar(stage));
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(sb, &tmB, k0, n0, full_bar(stage));
+                    } else {
+                        for (int c = 0; c < b_chunks; ++c) tma_load_2d(sb + c * chunk_bytes, &tmB, n0 + c * elems_per_row, k0, full_bar(stage));
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int local_tile = 0;
+            const uint32_t idesc = make_idesc(p.a_fmt, p.b_fmt, p.a_mn, p.b_mn, BM, BN);
+            const uint32_t lbo = BK * TILE_K_BYTES;                 // MN-major: stride between 128-byte MN chunks
+            const uint32_t a_kstep = p.a_mn ? (BK / 4) * TILE_K_BYTES : 32;
+            const uint32_t b_kstep = p.b_mn ? (BK / 4) * TILE_K_BYTES : 32;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const int acc = local_tile & 1;
+                if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, &abort_flag)) { ok = false; break; }
+                acc_phase[acc] ^= 1u;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = make_smem_desc(sa + j * a_kstep, p.a_mn ? lbo : 16, 1024);
+                        const uint64_t db = make_smem_desc(sb + j * b_kstep, p.b_mn ? lbo : 16, 1024);
+                        const uint32_t accum = (kb > 0 || j > 0) ? 1u : 0u;
+                        if (p.elem_bytes == 2) mma_f16(d_tmem, da, db, idesc, accum);
+                        else mma_f8(d_tmem, da, db, idesc, accum);
+                    }
+                    tc_commit(empty_bar(stage));   // frees the smem stage once these MMAs have read it
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(tfull_bar(acc));   // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3;          // TMEM lane quarter this warp may access
+        uint32_t acc_phase[2] = {0, 0};
+        int local_tile = 0;
+        float scale = p.alpha;
+        if (p.scale_a) scale *= __ldg(p.scale_a);
+        if (p.scale_b) scale *= __ldg(p.scale_b);
+        float amax = 0.f;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            int m_blk, n_blk;
+            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            const int acc = local_tile & 1;
+            if (!mbar_wait(tfull_bar(acc), acc_phase[acc], &abort_flag)) { ok = false; break; }
+            acc_phase[acc] ^= 1u;
+            tc_fence_after();
+            const int row = m_blk * BM + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + c, r);
+                tmem_ld_wait();
+                const int col0 = n_blk * BN + c;
+                if (row < p.M && col0 < p.N) {
+                    if (p.out_fp32) {
+                        float* drow = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            if (col0 + g * 4 < p.N) {
+                                float4 v = make_float4(__uint_as_float(r[g * 4]) * scale, __uint_as_float(r[g * 4 + 1]) * scale,
+                                                       __uint_as_float(r[g * 4 + 2]) * scale, __uint_as_float(r[g * 4 + 3]) * scale);
+                                float4* dst = reinterpret_cast<float4*>(drow + g * 4);
+                                if (p.accumulate) {
+                                    const float4 o = *dst;
+                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                }
+                                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                                *dst = v;
+                            }
+                        }
+                    } else {
+                        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col0 + g * 8 < p.N) {
+                                float v[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * scale;
+                                uint4* dst = reinterpret_cast<uint4*>(drow + g * 8);
+                                if (p.accumulate) {
+                                    const uint4 o = *dst;
+                                    const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const float2 f = __bfloat1622float2(ob[i]);
+                                        v[2 * i] += f.x;
+                                        v[2 * i + 1] += f.y;
+                                    }
+                                }
+                                uint4 out;
+                                __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    pb[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+                                }
+                                *dst = out;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty_bar(acc));
+        }
+        if (p.amax_out) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0 && amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax_out), __float_as_uint(amax));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, 1);
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !ptr)
+            return nullptr;
+        fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    return fn;
+}
+
+const char* make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                               uint32_t box_inner, uint32_t box_outer) {
+    EncodeFn enc = get_encode_fn();
+    if (!enc) return "cuTensorMapEncodeTiled unavailable";
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return "TMA base address must be 16-byte aligned";
+    if (row_stride_bytes % 16 != 0) return "TMA row stride must be a multiple of 16 bytes";
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+}
+
+template <int BN> static const char* launch(const GemmOperand& A, const GemmOperand& B, const GemmParams& p, int num_sms, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    const int BK = TILE_K_BYTES / p.elem_bytes;
+    CUtensorMap tmA, tmB;
+    const char* e;
+    // K-major: inner = K, outer = rows, box {BK, rows_per_tile}.  MN-major: inner = rows, outer = K, box {128 B of rows, BK}.
+    if (!p.a_mn) e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.K, p.M, A.row_stride_bytes, BK, BM);
+    else e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.M, p.K, A.row_stride_bytes, BK, BK);
+    if (e) return e;
+    if (!p.b_mn) e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.K, p.N, B.row_stride_bytes, BK, BN);
+    else e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.N, p.K, B.row_stride_bytes, BK, BK);
+    if (e) return e;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
+        attr_set = true;
+    }
+    const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
+}
+
+const char* gemm_sm100(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0) return nullptr;
+    if (p.N % 8 != 0 || p.ldd % 8 != 0) return "gemm_sm100: N and ldd must be multiples of 8";
+    if ((reinterpret_cast<uintptr_t>(p.D) & 15) != 0) return "gemm_sm100: D must be 16-byte aligned";
+    // 128-wide N tiles when the wide tile would leave SMs idle or N is small
+    const long tiles256 = static_cast<long>((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+    const bool narrow = p.N <= 128 || (p.tile_n == 128) || (p.tile_n == 0 && tiles256 < num_sms);
+    return narrow ? launch<128>(A, B, p, num_sms, stream) : launch<256>(A, B, p, num_sms, stream);
+}
+
+}  // namespace sg

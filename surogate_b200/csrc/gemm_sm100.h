@@ -1,0 +1,36 @@
+// Host API of the sm_100a tcgen05 GEMM (see gemm_sm100.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sg {
+
+struct GemmOperand {
+    const void* ptr;            // first element of the 2-D view
+    uint64_t row_stride_bytes;  // stride between rows of the stored matrix (inner dimension is contiguous)
+};
+
+struct GemmParams {
+    int M, N, K;
+    int elem_bytes;   // 2 = bf16 (kind::f16), 1 = fp8 (kind::f8f6f4)
+    int a_fmt, b_fmt; // bf16: 1 ; fp8: 0 = e4m3, 1 = e5m2
+    int a_mn, b_mn;   // 0: operand stored [rows, K] (K-major); 1: stored [K, rows] (MN-major)
+    void* D;          // [M, N] row-major, leading dimension ldd (elements)
+    int ldd;
+    int out_fp32;     // 0: bf16 output, 1: fp32 output
+    int accumulate;   // 1: D += result
+    float alpha;
+    const float* scale_a;  // optional device scalars multiplied into the result (FP8 de-scales)
+    const float* scale_b;
+    float* amax_out;       // optional: running max |D| (atomicMax on the bit pattern)
+    int* error_flag;       // set to 1 if a pipeline wait ran out of budget
+    int tile_n;            // 0 = auto, 128 or 256
+};
+
+const char* gemm_sm100(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream);
+
+const char* make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                               uint32_t box_inner, uint32_t box_outer);
+
+}  // namespace sg

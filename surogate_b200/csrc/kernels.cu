@@ -1,0 +1,627 @@
+// Memory-bound training kernels for sm_100a: RMSNorm (+residual, +FP8 output) fwd/bwd, QK-norm + RoPE
+// fwd/bwd on packed QKV, SwiGLU fwd/bwd (+FP8 output), embedding fwd/bwd, softmax cross-entropy fwd+bwd in
+// place, FP8 quantise / abs-max, sum of squares, AdamW (fp32 state and 8-bit state).
+// All loads/stores are 16-byte vectors; reductions are warp shuffles + one shared-memory hop.
+//
+// Replaces csrc/src/kernels/{rmsnorm,qk_norm,rope,swiglu,encoder,fused_classifier,global_norm}.cu,
+// recipes/fp8_hybrid/kernels/quant.cu and runtime/optimizers/{adamw,flash_adamw_8bit}.cu of the reference.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace sg {
+
+using bf16 = __nv_bfloat16;
+using bf162 = __nv_bfloat162;
+
+struct alignas(16) Vec8 { bf162 v[4]; };
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+    const Vec8 t = *reinterpret_cast<const Vec8*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(t.v[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+    Vec8 t;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<Vec8*>(p) = t;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+template <bool IS_MAX> __device__ __forceinline__ float block_reduce(float v, float* sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    v = (lane < nw) ? sh[lane] : (IS_MAX ? -INFINITY : 0.f);
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    return v;
+}
+__device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
+    if (v > 0.f) atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+template <bool E5M2> __device__ __forceinline__ uint8_t to_fp8(float v) {
+    return E5M2 ? __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2) : __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm forward
+// one CTA per row.  res_out = residual + x (optional) ; y = res_out * rstd * w ; optionally y also as FP8.
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, const bf16* __restrict__ w,
+                                                          bf16* __restrict__ res_out, bf16* __restrict__ y, float* __restrict__ rstd_out,
+                                                          uint8_t* __restrict__ y_fp8, const float* __restrict__ fp8_scale, float* __restrict__ amax_out,
+                                                          int C, float eps) {
+    __shared__ float sh[32];
+    const size_t row = blockIdx.x;
+    const bf16* xr = x + row * C;
+    const bf16* rr = residual ? residual + row * C : nullptr;
+    bf16* ro = res_out ? res_out + row * C : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 8; c < C; c += blockDim.x * 8) {
+        float a[8];
+        load8(xr + c, a);
+        if (rr) {
+            float b[8];
+            load8(rr + c, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] += b[i];
+            // round to the stored precision so forward and backward see the same residual stream
+            store8(ro + c, a);
+            load8(ro + c, a);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += a[i] * a[i];
+    }
+    ss = block_reduce<false>(ss, sh);
+    const float rstd = rsqrtf(ss / C + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    const bf16* src = rr ? ro : xr;
+    const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
+    float amax = 0.f;
+    for (int c = threadIdx.x * 8; c < C; c += blockDim.x * 8) {
+        float a[8], g[8];
+        load8(src + c, a);
+        load8(w + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { a[i] = a[i] * rstd * g[i]; amax = fmaxf(amax, fabsf(a[i])); }
+        if (y) store8(y + row * C + c, a);
+        if (y_fp8) {
+            uint2 o;
+            uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ob[i] = to_fp8<false>(a[i] * qs);
+            *reinterpret_cast<uint2*>(y_fp8 + row * C + c) = o;
+        }
+    }
+    if (amax_out) {
+        amax = block_reduce<true>(amax, sh);
+        if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm backward
+// Persistent CTAs stride over rows; each thread owns fixed columns and keeps dw partial sums in registers.
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ d_res) ; dw_partial[block, C] reduced by a second kernel.
+constexpr int RB_THREADS = 256;
+constexpr int RB_MAX_ITERS = 8;  // supports C <= 256*8*8 = 16384
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                 const float* __restrict__ rstd, const bf16* __restrict__ d_res,
+                                                                 bf16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int C) {
+    __shared__ float sh[32];
+    float dw[RB_MAX_ITERS][8];
+#pragma unroll
+    for (int it = 0; it < RB_MAX_ITERS; ++it)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dw[it][i] = 0.f;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = static_cast<size_t>(row) * C;
+        const float rs = rstd[row];
+        float dot = 0.f;
+#pragma unroll
+        for (int it = 0; it < RB_MAX_ITERS; ++it) {
+            const int c = (it * RB_THREADS + threadIdx.x) * 8;
+            if (c < C) {
+                float g[8], a[8], ww[8];
+                load8(dy + base + c, g);
+                load8(x + base + c, a);
+                load8(w + c, ww);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float xhat = a[i] * rs;
+                    dot += g[i] * ww[i] * xhat;
+                    dw[it][i] += g[i] * xhat;
+                }
+            }
+        }
+        dot = block_reduce<false>(dot, sh) / C;
+#pragma unroll
+        for (int it = 0; it < RB_MAX_ITERS; ++it) {
+            const int c = (it * RB_THREADS + threadIdx.x) * 8;
+            if (c < C) {
+                float g[8], a[8], ww[8], o[8];
+                load8(dy + base + c, g);
+                load8(x + base + c, a);
+                load8(w + c, ww);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[i] - a[i] * rs * dot);
+                if (d_res) {
+                    float r[8];
+                    load8(d_res + base + c, r);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] += r[i];
+                }
+                store8(dx + base + c, o);
+            }
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < RB_MAX_ITERS; ++it) {
+        const int c = (it * RB_THREADS + threadIdx.x) * 8;
+        if (c < C) {
+            float* o = dw_partial + static_cast<size_t>(blockIdx.x) * C + c;
+            *reinterpret_cast<float4*>(o) = make_float4(dw[it][0], dw[it][1], dw[it][2], dw[it][3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(dw[it][4], dw[it][5], dw[it][6], dw[it][7]);
+        }
+    }
+}
+__global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int C) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float s = 0.f;
+    for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * C + c];
+    out[c] = s;
+}
+
+// ------------------------------------------------------------------------------------------ SwiGLU
+// x = [up | gate] per row (2M); y = silu(gate) * up.  Optional FP8 copy of y with scale + abs-max.
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ y_fp8,
+                                                         const float* __restrict__ fp8_scale, float* __restrict__ amax_out, size_t rows, int M) {
+    __shared__ float sh[32];
+    const size_t nvec = rows * (M / 8);
+    const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
+    float amax = 0.f;
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = v / (M / 8);
+        const int c = static_cast<int>(v % (M / 8)) * 8;
+        float up[8], gate[8], o[8];
+        load8(x + row * 2 * M + c, up);
+        load8(x + row * 2 * M + M + c, gate);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { o[i] = gate[i] / (1.f + __expf(-gate[i])) * up[i]; amax = fmaxf(amax, fabsf(o[i])); }
+        if (y) store8(y + row * M + c, o);
+        if (y_fp8) {
+            uint2 q;
+            uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qb[i] = to_fp8<false>(o[i] * qs);
+            *reinterpret_cast<uint2*>(y_fp8 + row * M + c) = q;
+        }
+    }
+    if (amax_out) {
+        amax = block_reduce<true>(amax, sh);
+        if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
+    }
+}
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, size_t rows, int M) {
+    const size_t nvec = rows * (M / 8);
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = v / (M / 8);
+        const int c = static_cast<int>(v % (M / 8)) * 8;
+        float up[8], gate[8], g[8], du[8], dg[8];
+        load8(x + row * 2 * M + c, up);
+        load8(x + row * 2 * M + M + c, gate);
+        load8(dy + row * M + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float s = 1.f / (1.f + __expf(-gate[i]));
+            du[i] = g[i] * gate[i] * s;
+            dg[i] = g[i] * up[i] * s * (1.f + gate[i] * (1.f - s));
+        }
+        store8(dx + row * 2 * M + c, du);
+        store8(dx + row * 2 * M + M + c, dg);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ QK-norm + RoPE
+// One warp per (token, head); head_dim 128: lane l holds elements [4l, 4l+4); rotary partner (i +/- 64) lives in lane l^16.
+// Layout per token: [Hq heads | Hkv heads (K) | Hkv heads (V)] x D.  V heads are copied (forward) / passed through (backward).
+template <bool BACKWARD>
+__global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restrict__ in, const bf16* __restrict__ qkv_pre, const bf16* __restrict__ qw,
+                                                           const bf16* __restrict__ kw, const int* __restrict__ pos, bf16* __restrict__ out,
+                                                           float* __restrict__ q_rstd, float* __restrict__ k_rstd, float* __restrict__ dqw,
+                                                           float* __restrict__ dkw, size_t tokens, int Hq, int Hkv, float eps, float log2_theta) {
+    constexpr int D = 128;
+    __shared__ float sdw[2][D];
+    if (BACKWARD) {
+        for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+        __syncthreads();
+    }
+    const int H = Hq + 2 * Hkv;
+    const int lane = threadIdx.x & 31;
+    const size_t warps_total = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
+    const size_t items = tokens * H;
+    const bool use_norm = qw != nullptr;
+    float dw_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // this lane's 4 elements: [q|k] norm-weight grads
+    for (size_t it = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += warps_total) {
+        const size_t tok = it / H;
+        const int h = static_cast<int>(it % H);
+        const size_t off = it * D + lane * 4;
+        const uint2 raw = *reinterpret_cast<const uint2*>(in + off);
+        if (h >= Hq + Hkv) {  // V: identity
+            *reinterpret_cast<uint2*>(out + off) = raw;
+            continue;
+        }
+        const bool is_q = h < Hq;
+        float v[4];
+        {
+            const bf162* pb = reinterpret_cast<const bf162*>(&raw);
+            const float2 a = __bfloat1622float2(pb[0]), b = __bfloat1622float2(pb[1]);
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        }
+        // rotation angles for this lane's 4 element indices (index mod 64)
+        const float p = static_cast<float>(pos[tok]);
+        float cs[4], sn[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = (lane * 4 + i) & 63;
+            const float inv = exp2f(-log2_theta * (2.f * j) / D);
+            sincosf(p * inv, &sn[i], &cs[i]);
+        }
+        const float sign = (lane < 16) ? -1.f : 1.f;  // first half: x1*c - x2*s ; second half: x2*c + x1*s
+        if (!BACKWARD) {
+            float rstd = 1.f;
+            if (use_norm) {
+                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+                ss = warp_sum(ss);
+                rstd = rsqrtf(ss / D + eps);
+                const bf16* wv = is_q ? qw : kw;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * __bfloat162float(wv[lane * 4 + i]);
+                if (lane == 0) {
+                    if (is_q) q_rstd[tok * Hq + h] = rstd;
+                    else k_rstd[tok * Hkv + (h - Hq)] = rstd;
+                }
+            }
+            float o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                o[i] = v[i] * cs[i] + sign * partner * sn[i];
+            }
+            uint2 w2;
+            bf162* pw = reinterpret_cast<bf162*>(&w2);
+            pw[0] = __floats2bfloat162_rn(o[0], o[1]);
+            pw[1] = __floats2bfloat162_rn(o[2], o[3]);
+            *reinterpret_cast<uint2*>(out + off) = w2;
+        } else {
+            // v = d(out).  Inverse rotation: g1 = d1*c + d2*s ; g2 = d2*c - d1*s
+            float g[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                g[i] = v[i] * cs[i] - sign * partner * sn[i];
+            }
+            if (use_norm) {
+                const uint2 xr = *reinterpret_cast<const uint2*>(qkv_pre + off);
+                const bf162* px = reinterpret_cast<const bf162*>(&xr);
+                const float2 a = __bfloat1622float2(px[0]), b = __bfloat1622float2(px[1]);
+                const float xin[4] = {a.x, a.y, b.x, b.y};
+                const float rstd = is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)];
+                const bf16* wv = is_q ? qw : kw;
+                float dot = 0.f, dn[4], xhat[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    xhat[i] = xin[i] * rstd;
+                    dn[i] = g[i] * __bfloat162float(wv[lane * 4 + i]);
+                    dot += dn[i] * xhat[i];
+                    dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
+                }
+                dot = warp_sum(dot) / D;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) g[i] = rstd * (dn[i] - xhat[i] * dot);
+            }
+            uint2 w2;
+            bf162* pw = reinterpret_cast<bf162*>(&w2);
+            pw[0] = __floats2bfloat162_rn(g[0], g[1]);
+            pw[1] = __floats2bfloat162_rn(g[2], g[3]);
+            *reinterpret_cast<uint2*>(out + off) = w2;
+        }
+    }
+    if (BACKWARD && use_norm) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            atomicAdd(&sdw[0][lane * 4 + i], dw_acc[0][i]);
+            atomicAdd(&sdw[1][lane * 4 + i], dw_acc[1][i]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            atomicAdd(dqw + i, sdw[0][i]);
+            atomicAdd(dkw + i, sdw[1][i]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ embedding
+__global__ void embedding_fwd_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ out, size_t n, int C) {
+    const size_t nvec = n * (C / 8);
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = v / (C / 8);
+        const int c = static_cast<int>(v % (C / 8)) * 8;
+        *reinterpret_cast<uint4*>(out + t * C + c) = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(tokens[t]) * C + c);
+    }
+}
+template <typename G> __global__ void embedding_bwd_kernel(const int* __restrict__ tokens, const bf16* __restrict__ d_out, G* __restrict__ d_table, size_t n, int C) {
+    const size_t npair = n * (C / 2);
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < npair; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = v / (C / 2);
+        const int c = static_cast<int>(v % (C / 2)) * 2;
+        const bf162 g = *reinterpret_cast<const bf162*>(d_out + t * C + c);
+        G* dst = d_table + static_cast<size_t>(tokens[t]) * C + c;
+        if constexpr (sizeof(G) == 2) {
+            atomicAdd(reinterpret_cast<bf162*>(dst), g);
+        } else {
+            const float2 f = __bfloat1622float2(g);
+            atomicAdd(dst, f.x);
+            atomicAdd(dst + 1, f.y);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ cross-entropy (fwd + bwd in place)
+// One CTA per row of bf16 logits [rows, V].  loss[row] = lse - logit[target]; logits are overwritten with
+// d_logits = (softmax - onehot) * scale (scale read from device memory), zero for ignored rows.
+__global__ void __launch_bounds__(1024) cross_entropy_fwd_bwd_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ loss,
+                                                                     const float* __restrict__ scale_ptr, float scale_host, int V, int ld,
+                                                                     int write_grad) {
+    __shared__ float sh[32];
+    const size_t row = blockIdx.x;
+    bf16* lr = logits + row * ld;
+    const int tgt = targets[row];
+    if (tgt < 0) {
+        if (threadIdx.x == 0) loss[row] = 0.f;
+        if (write_grad) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) *reinterpret_cast<uint4*>(lr + c) = z;
+        }
+        return;
+    }
+    float mx = -INFINITY, sum = 0.f;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+        float a[8];
+        load8(lr + c, a);
+        float m = a[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, a[i]);
+        if (m > mx) { sum *= __expf(mx - m); mx = m; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += __expf(a[i] - mx);
+    }
+    const float gmax = block_reduce<true>(mx, sh);
+    sum *= __expf(mx - gmax);
+    const float gsum = block_reduce<false>(sum, sh);
+    const float lse = gmax + __logf(gsum);
+    if (threadIdx.x == 0) loss[row] = lse - __bfloat162float(lr[tgt]);
+    if (!write_grad) return;
+    __syncthreads();
+    const float scale = scale_host * (scale_ptr ? __ldg(scale_ptr) : 1.f);
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+        float a[8];
+        load8(lr + c, a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float pr = __expf(a[i] - lse);
+            if (c + i == tgt) pr -= 1.f;
+            a[i] = pr * scale;
+        }
+        store8(lr + c, a);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ FP8 quantise / abs-max / sum of squares
+template <bool E5M2>
+__global__ void __launch_bounds__(256) quantize_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, const float* __restrict__ scale,
+                                                           float* __restrict__ amax_out, size_t n) {
+    __shared__ float sh[32];
+    const float s = scale ? __ldg(scale) : 1.f;
+    float amax = 0.f;
+    const size_t nvec = n / 8;
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float a[8];
+        load8(x + v * 8, a);
+        uint2 o;
+        uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { amax = fmaxf(amax, fabsf(a[i])); ob[i] = to_fp8<E5M2>(a[i] * s); }
+        *reinterpret_cast<uint2*>(q + v * 8) = o;
+    }
+    if (amax_out) {
+        amax = block_reduce<true>(amax, sh);
+        if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
+    }
+}
+__global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, float* __restrict__ amax_out, size_t n) {
+    __shared__ float sh[32];
+    float amax = 0.f;
+    const size_t nvec = n / 8;
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float a[8];
+        load8(x + v * 8, a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(a[i]));
+    }
+    amax = block_reduce<true>(amax, sh);
+    if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
+}
+template <typename T> __global__ void __launch_bounds__(512) sumsq_kernel(const T* __restrict__ x, float* __restrict__ partial, size_t n) {
+    __shared__ float sh[32];
+    float s = 0.f;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float v;
+        if constexpr (sizeof(T) == 2) v = __bfloat162float(x[i]); else v = x[i];
+        s += v * v;
+    }
+    s = block_reduce<false>(s, sh);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;   // fixed grid -> deterministic second stage on the host side tensor
+}
+
+// ------------------------------------------------------------------------------------------ AdamW
+// hp (device): [lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale] so a captured graph can be replayed.
+template <typename P, typename G>
+__global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, const G* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                                                         const uint8_t* __restrict__ decay_mask, const float* __restrict__ hp, size_t n) {
+    const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float gv, pv;
+        if constexpr (sizeof(G) == 2) gv = __bfloat162float(g[i]); else gv = g[i];
+        if constexpr (sizeof(P) == 2) pv = __bfloat162float(p[i]); else pv = p[i];
+        gv *= gs;
+        const float mi = b1 * m[i] + (1.f - b1) * gv;
+        const float vi = b2 * v[i] + (1.f - b2) * gv * gv;
+        m[i] = mi;
+        v[i] = vi;
+        const float dec = (decay_mask && decay_mask[i]) ? wd : 0.f;
+        pv = pv * (1.f - lr * dec) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+        if constexpr (sizeof(P) == 2) p[i] = __float2bfloat16_rn(pv); else p[i] = pv;
+    }
+}
+
+// 8-bit state: momentum int8 through softsign (2x/(1+|x|) of the group-normalised value), variance uint8 of sqrt(v),
+// groups of 32 with fp16 scales.  One warp handles one group per iteration (lane = element) so the group abs-max is a shuffle.
+template <typename P, typename G>
+__global__ void __launch_bounds__(256) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
+                                                         __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
+                                                         const float* __restrict__ hp, size_t n) {
+    const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
+    const int lane = threadIdx.x & 31;
+    const size_t ngroups = (n + 31) / 32;
+    const size_t warps_total = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
+    for (size_t grp = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); grp < ngroups; grp += warps_total) {
+        const size_t i = grp * 32 + lane;
+        const bool live = i < n;
+        float gv = 0.f, pv = 0.f, mi = 0.f, vi = 0.f;
+        if (live) {
+            if constexpr (sizeof(G) == 2) gv = __bfloat162float(g[i]); else gv = g[i];
+            if constexpr (sizeof(P) == 2) pv = __bfloat162float(p[i]); else pv = p[i];
+            gv *= gs;
+            const float y = static_cast<float>(m8[i]) * (1.f / 127.f);
+            mi = y / (2.f - fabsf(y)) * __half2float(ms[grp]);
+            const float sq = static_cast<float>(v8[i]) * (1.f / 255.f) * __half2float(vs[grp]);
+            vi = sq * sq;
+            mi = b1 * mi + (1.f - b1) * gv;
+            vi = b2 * vi + (1.f - b2) * gv * gv;
+            const float dec = (decay_mask && decay_mask[i]) ? wd : 0.f;
+            pv = pv * (1.f - lr * dec) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+            if constexpr (sizeof(P) == 2) p[i] = __float2bfloat16_rn(pv); else p[i] = pv;
+        }
+        const float sv = sqrtf(vi);
+        // fp16 scales: round up so the normalised values stay within [-1, 1]
+        float am = fmaxf(warp_max(fabsf(mi)), 1e-30f), av = fmaxf(warp_max(sv), 1e-30f);
+        __half hm = __float2half_ru(am), hv = __float2half_ru(av);
+        am = fmaxf(__half2float(hm), 6e-8f);
+        av = fmaxf(__half2float(hv), 6e-8f);
+        if (live) {
+            const float xn = mi / am;
+            m8[i] = static_cast<int8_t>(__float2int_rn(2.f * xn / (1.f + fabsf(xn)) * 127.f));
+            v8[i] = static_cast<uint8_t>(min(255, __float2int_rn(sv / av * 255.f)));
+        }
+        if (lane == 0) { ms[grp] = __float2half(am); vs[grp] = __float2half(av); }
+    }
+}
+
+// ============================================================================================ launchers
+static inline int grid_for(size_t work_items, int threads, int num_sms, int per_sm = 8) {
+    size_t g = (work_items + threads - 1) / threads;
+    const size_t cap = static_cast<size_t>(num_sms) * per_sm;
+    return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+void rmsnorm_fwd(const void* x, const void* residual, const void* w, void* res_out, void* y, float* rstd, void* y_fp8, const float* fp8_scale,
+                 float* amax, int rows, int C, float eps, cudaStream_t s) {
+    int threads = C / 8;
+    threads = threads > 256 ? 256 : (threads < 32 ? 32 : (threads + 31) / 32 * 32);
+    rmsnorm_fwd_kernel<<<rows, threads, 0, s>>>((const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)res_out, (bf16*)y, rstd, (uint8_t*)y_fp8,
+                                                fp8_scale, amax, C, eps);
+}
+int rmsnorm_bwd_blocks(int rows, int num_sms) { return rows < num_sms * 2 ? rows : num_sms * 2; }
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
+                 int C, int num_sms, cudaStream_t s) {
+    const int blocks = rmsnorm_bwd_blocks(rows, num_sms);
+    rmsnorm_bwd_kernel<<<blocks, RB_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)d_res, (bf16*)dx, dw_partial,
+                                                     rows, C);
+    column_sum_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_partial, dw, blocks, C);
+}
+void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s) {
+    swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M);
+}
+void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s) {
+    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M);
+}
+void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
+                      int Hkv, float eps, float theta, int num_sms, cudaStream_t s) {
+    const size_t items = tokens * (Hq + 2 * Hkv);
+    qk_norm_rope_kernel<false><<<grid_for(items * 32, 256, num_sms), 256, 0, s>>>((const bf16*)qkv, nullptr, (const bf16*)qw, (const bf16*)kw, pos,
+                                                                                   (bf16*)out, q_rstd, k_rstd, nullptr, nullptr, tokens, Hq, Hkv, eps,
+                                                                                   log2f(theta));
+}
+void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,
+                      float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int num_sms, cudaStream_t s) {
+    const size_t items = tokens * (Hq + 2 * Hkv);
+    qk_norm_rope_kernel<true><<<grid_for(items * 32, 256, num_sms, 4), 256, 0, s>>>((const bf16*)d_out, (const bf16*)qkv_pre, (const bf16*)qw,
+                                                                                     (const bf16*)kw, pos, (bf16*)d_qkv, q_rstd, k_rstd, dqw, dkw, tokens,
+                                                                                     Hq, Hkv, eps, log2f(theta));
+}
+void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int num_sms, cudaStream_t s) {
+    embedding_fwd_kernel<<<grid_for(n * (C / 8), 256, num_sms), 256, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, n, C);
+}
+void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad_fp32, size_t n, int C, int num_sms, cudaStream_t s) {
+    const int grid = grid_for(n * (C / 2), 256, num_sms);
+    if (grad_fp32) embedding_bwd_kernel<float><<<grid, 256, 0, s>>>(tokens, (const bf16*)d_out, (float*)d_table, n, C);
+    else embedding_bwd_kernel<bf16><<<grid, 256, 0, s>>>(tokens, (const bf16*)d_out, (bf16*)d_table, n, C);
+}
+void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,
+                           int write_grad, cudaStream_t s) {
+    cross_entropy_fwd_bwd_kernel<<<rows, 1024, 0, s>>>((bf16*)logits, targets, loss, scale_ptr, scale_host, V, ld, write_grad);
+}
+void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s) {
+    const int grid = grid_for(n / 8, 256, num_sms);
+    if (e5m2) quantize_fp8_kernel<true><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n);
+    else quantize_fp8_kernel<false><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n);
+}
+void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s) {
+    amax_kernel<<<grid_for(n / 8, 256, num_sms), 256, 0, s>>>((const bf16*)x, amax, n);
+}
+void sumsq(const void* x, int is_fp32, float* partial, int nblocks, size_t n, cudaStream_t s) {
+    if (is_fp32) sumsq_kernel<float><<<nblocks, 512, 0, s>>>((const float*)x, partial, n);
+    else sumsq_kernel<bf16><<<nblocks, 512, 0, s>>>((const bf16*)x, partial, n);
+}
+void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float* v, const uint8_t* mask, const float* hp, size_t n, int num_sms,
+                cudaStream_t s) {
+    const int grid = grid_for(n, 256, num_sms);
+    if (p_fp32 && g_fp32) adamw_fp32_kernel<float, float><<<grid, 256, 0, s>>>((float*)p, (const float*)g, m, v, mask, hp, n);
+    else if (p_fp32) adamw_fp32_kernel<float, bf16><<<grid, 256, 0, s>>>((float*)p, (const bf16*)g, m, v, mask, hp, n);
+    else if (g_fp32) adamw_fp32_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, m, v, mask, hp, n);
+    else adamw_fp32_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)p, (const bf16*)g, m, v, mask, hp, n);
+}
+void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, const float* hp,
+                size_t n, int num_sms, cudaStream_t s) {
+    const int grid = grid_for(n, 256, num_sms);
+    if (p_fp32 && g_fp32) adamw_8bit_kernel<float, float><<<grid, 256, 0, s>>>((float*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
+    else if (p_fp32) adamw_8bit_kernel<float, bf16><<<grid, 256, 0, s>>>((float*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
+    else if (g_fp32) adamw_8bit_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
+    else adamw_8bit_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
+}
+
+}  // namespace sg

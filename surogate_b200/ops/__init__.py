@@ -1,0 +1,21 @@
+"""Python entry points of the hand-written sm_100a kernels (see ``csrc/``)."""
+from __future__ import annotations
+
+
+def ext():
+    """The compiled extension module.  Raises with a clear message when it cannot be loaded."""
+    from . import _build
+
+    try:
+        return _build.load()
+    except Exception as e:  # noqa: BLE001
+        raise RuntimeError(
+            "surogate_b200 CUDA extension (sm_100a) is not available: build it with "
+            "`python -c 'import __graft_entry__ as g; g.build()'` — GPU ops do not fall back to PyTorch") from e
+
+
+def check_device_errors(reset: bool = True) -> None:
+    """Raise if any kernel reported a pipeline time-out (bounded waits) since the last check. Synchronises."""
+    flag = ext().read_error_flag(reset)
+    if flag:
+        raise RuntimeError(f"a surogate_b200 kernel reported a device-side wait time-out (flag={flag})")

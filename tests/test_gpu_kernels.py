@@ -1,0 +1,240 @@
+"""Numerics of each hand-written sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from surogate_b200.ops import ext as load
+
+    return load()
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _check_flag():
+    from surogate_b200.ops import check_device_errors
+
+    check_device_errors()
+
+
+# ----------------------------------------------------------------------------- GEMM
+GEMM_SHAPES = [(256, 256, 128), (128, 128, 64), (384, 512, 320), (300, 264, 200), (1024, 1536, 1024), (136, 8, 64), (4096, 512, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16(ext, M, N, K, a_mn, b_mn):
+    from surogate_b200.runtime.ops_cuda import gemm
+
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        pytest.skip("row stride must be a multiple of 16 bytes")
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device=DEV)
+    B = torch.randn(N, K, device=DEV)
+    a = (A.t().contiguous() if a_mn else A).bfloat16()
+    b = (B.t().contiguous() if b_mn else B).bfloat16()
+    ref = (a.t() if a_mn else a).float() @ (b.t() if b_mn else b).float().t()
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    _check_flag()
+    assert _rel_err(out, ref) < 6e-3, _rel_err(out, ref)
+
+
+def test_gemm_accumulate_fp32_and_alpha(ext):
+    from surogate_b200.runtime.ops_cuda import gemm
+
+    M, N, K = 512, 384, 256
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = torch.randn(N, K, device=DEV).bfloat16()
+    base = torch.randn(M, N, device=DEV)
+    out = base.clone()
+    gemm(a, b, out, accumulate=True, alpha=0.5)
+    ref = base + 0.5 * (a.float() @ b.float().t())
+    assert _rel_err(out, ref) < 1e-4
+    out16 = base.bfloat16()
+    ref16 = out16.float() + a.float() @ b.float().t()
+    gemm(a, b, out16, accumulate=True)
+    assert _rel_err(out16, ref16) < 6e-3
+    # strided output / strided inputs (views into wider buffers)
+    wide = torch.zeros(M, N + 64, device=DEV, dtype=torch.bfloat16)
+    gemm(a, b, wide[:, 32:32 + N])
+    assert _rel_err(wide[:, 32:32 + N], a.float() @ b.float().t()) < 6e-3
+    assert wide[:, :32].abs().max() == 0 and wide[:, 32 + N:].abs().max() == 0
+    _check_flag()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (384, 512, 384), (1024, 768, 2048), (272, 264, 144)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("a_e5m2", [False, True])
+def test_gemm_fp8(ext, M, N, K, a_mn, b_mn, a_e5m2):
+    from surogate_b200.runtime.ops_cuda import gemm
+
+    if (a_mn and M % 16) or (b_mn and N % 16) or K % 16:
+        pytest.skip("row stride must be a multiple of 16 bytes")
+    torch.manual_seed(1)
+    A = torch.randn(M, K, device=DEV)
+    B = torch.randn(N, K, device=DEV)
+    a = (A.t().contiguous() if a_mn else A).to(torch.float8_e5m2 if a_e5m2 else torch.float8_e4m3fn)
+    b = (B.t().contiguous() if b_mn else B).to(torch.float8_e4m3fn)
+    sa = torch.tensor([0.5], device=DEV)
+    sb = torch.tensor([2.5], device=DEV)
+    ref = 1.25 * ((a.float().t() if a_mn else a.float()) @ (b.float().t() if b_mn else b.float()).t())
+    amax = torch.zeros(1, device=DEV)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, scale_a=sa, scale_b=sb, amax_out=amax)
+    torch.cuda.synchronize()
+    _check_flag()
+    assert _rel_err(out, ref) < 6e-3, _rel_err(out, ref)
+    assert abs(amax.item() - out.float().abs().max().item()) <= 0.01 * amax.item()
+
+
+# ----------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("C", [1024, 4096, 5120])
+def test_rmsnorm_fwd_bwd(ext, C):
+    rows = 333
+    x = torch.randn(rows, C, device=DEV).bfloat16()
+    r = torch.randn(rows, C, device=DEV).bfloat16()
+    w = (1 + 0.1 * torch.randn(C, device=DEV)).bfloat16()
+    res, y, rstd, _ = ext.rmsnorm_fwd(x, r, w, 1e-6, True, None, None, False)
+    rf = (x.float() + r.float()).bfloat16().float()
+    ref_rstd = torch.rsqrt(rf.pow(2).mean(-1) + 1e-6)
+    assert torch.equal(res, rf.bfloat16())
+    assert torch.allclose(rstd, ref_rstd, rtol=1e-4)
+    assert _rel_err(y, rf * ref_rstd[:, None] * w.float()) < 5e-3
+    dy = torch.randn(rows, C, device=DEV).bfloat16()
+    dres = torch.randn(rows, C, device=DEV).bfloat16()
+    dx, dw = ext.rmsnorm_bwd(dy, res, w, rstd, dres)
+    xhat = rf * ref_rstd[:, None]
+    dn = dy.float() * w.float()
+    ref_dx = ref_rstd[:, None] * (dn - xhat * (dn * xhat).mean(-1, keepdim=True)) + dres.float()
+    assert _rel_err(dx, ref_dx) < 5e-3
+    assert _rel_err(dw, (dy.float() * xhat).sum(0)) < 1e-4
+    # fp8 output with scale and abs-max
+    scale = torch.tensor([3.0], device=DEV)
+    amax = torch.zeros(1, device=DEV)
+    _, _, _, y8 = ext.rmsnorm_fwd(x, r, w, 1e-6, False, scale, amax, True)
+    yref = rf * ref_rstd[:, None] * w.float()
+    assert _rel_err(y8.float() / 3.0, yref) < 0.05
+    assert abs(amax.item() - yref.abs().max().item()) < 0.02 * amax.item()
+
+
+def test_swiglu(ext):
+    rows, M = 517, 3072
+    x = torch.randn(rows, 2 * M, device=DEV).bfloat16()
+    y = ext.swiglu_fwd(x, True, None, None, False)[0]
+    up, gate = x[:, :M].float(), x[:, M:].float()
+    assert _rel_err(y, torch.nn.functional.silu(gate) * up) < 5e-3
+    dy = torch.randn(rows, M, device=DEV).bfloat16()
+    dx = ext.swiglu_bwd(dy, x)
+    s = torch.sigmoid(gate)
+    ref = torch.cat([dy.float() * gate * s, dy.float() * up * s * (1 + gate * (1 - s))], -1)
+    assert _rel_err(dx, ref) < 5e-3
+
+
+def test_qk_norm_rope(ext):
+    from surogate_b200.dsl.ir import OpNode
+    from surogate_b200.runtime.ops_ref import RefOps
+
+    B, T, Hq, Hkv, D = 2, 96, 8, 2, 128
+    qkv = torch.randn(B, T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    pos = torch.arange(T, device=DEV, dtype=torch.int32)[None].repeat(B, 1).contiguous()
+    attrs = dict(num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, eps=1e-6, rope_theta=1e6, rotary_dim=D)
+    ref = RefOps()
+    op = OpNode("qkv_qk_norm_rope", [], [], attrs)
+    r_out, r_q, r_k = ref.qkv_qk_norm_rope(None, op, qkv.float(), qw.float(), kw.float(), pos)
+    out, q_rstd, k_rstd = ext.qk_norm_rope_fwd(qkv, qw, kw, pos, Hq, Hkv, D, 1e-6, 1e6)
+    assert _rel_err(out, r_out) < 5e-3
+    assert torch.allclose(q_rstd, r_q, rtol=1e-4) and torch.allclose(k_rstd, r_k, rtol=1e-4)
+    dy = torch.randn_like(qkv)
+    r_dx, r_dq, r_dk = ref.qkv_qk_norm_rope_backward(None, op, dy.float(), qkv.float(), qw.float(), kw.float(), r_q, r_k, pos)
+    dx, dqw, dkw = ext.qk_norm_rope_bwd(dy, qkv, qw, kw, q_rstd, k_rstd, pos, Hq, Hkv, D, 1e-6, 1e6)
+    assert _rel_err(dx, r_dx) < 5e-3
+    assert _rel_err(dqw, r_dq) < 2e-3 and _rel_err(dkw, r_dk) < 2e-3
+    # without qk-norm (Llama-style)
+    out2, _, _ = ext.qk_norm_rope_fwd(qkv, None, None, pos, Hq, Hkv, D, 1e-6, 1e4)
+    attrs2 = dict(attrs, rope_theta=1e4)
+    r2, _, _ = ref.qkv_qk_norm_rope(None, OpNode("x", [], [], attrs2), qkv.float(), None, None, pos)
+    assert _rel_err(out2, r2) < 5e-3
+
+
+def test_embedding(ext):
+    V, C, n = 1000, 512, 4096
+    table = torch.randn(V, C, device=DEV).bfloat16()
+    tok = torch.randint(0, V, (4, n // 4), device=DEV, dtype=torch.int32)
+    out = ext.embedding_fwd(tok, table)
+    assert torch.equal(out, table[tok.long()])
+    dout = torch.randn(4, n // 4, C, device=DEV).bfloat16()
+    g = torch.zeros(V, C, device=DEV, dtype=torch.float32)
+    ext.embedding_bwd(tok, dout, g)
+    ref = torch.zeros(V, C, device=DEV).index_add_(0, tok.reshape(-1).long(), dout.reshape(-1, C).float())
+    assert _rel_err(g, ref) < 1e-5
+
+
+def test_cross_entropy(ext):
+    rows, V = 257, 151936 // 8
+    logits = (3 * torch.randn(rows, V, device=DEV)).bfloat16()
+    tgt = torch.randint(0, V, (rows,), device=DEV, dtype=torch.int32)
+    tgt[::7] = -100
+    ref_logits = logits.float().requires_grad_(True)
+    ref_loss = torch.nn.functional.cross_entropy(ref_logits, tgt.long(), ignore_index=-100, reduction="none")
+    (ref_loss.sum() * 0.25).backward()
+    scale = torch.tensor([0.5], device=DEV)
+    work = logits.clone()
+    loss = ext.cross_entropy_fwd_bwd(work, tgt, scale, 0.5, True)
+    assert torch.allclose(loss, ref_loss.detach(), rtol=1e-3, atol=1e-3)
+    assert _rel_err(work, ref_logits.grad) < 1e-2
+    assert work[::7].abs().max() == 0
+
+
+def test_quantize_fp8_and_sumsq(ext):
+    x = (5 * torch.randn(1 << 20, device=DEV)).bfloat16()
+    scale = torch.tensor([4.0], device=DEV)
+    amax = torch.zeros(1, device=DEV)
+    q = ext.quantize_fp8(x, scale, amax, False)
+    assert torch.equal(q.view(torch.uint8), (x.float() * 4).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8))
+    assert amax.item() == x.float().abs().max().item()
+    q2 = ext.quantize_fp8(x, scale, None, True)
+    assert torch.equal(q2.view(torch.uint8), (x.float() * 4).to(torch.float8_e5m2).view(torch.uint8))
+    assert abs(ext.sumsq(x).item() / x.float().pow(2).sum().item() - 1) < 1e-4
+    xf = torch.randn(12345, device=DEV)
+    assert abs(ext.sumsq(xf).item() / xf.pow(2).sum().item() - 1) < 1e-5
+
+
+def test_adamw_kernels(ext):
+    n = 100000
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV) * 0.1
+    mask = (torch.arange(n, device=DEV) % 3 != 0).to(torch.uint8)
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
+    p_ref, m_ref, v_ref = p.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p32, m, v = p.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p8 = p.clone()
+    m8, v8 = torch.zeros(n, dtype=torch.int8, device=DEV), torch.zeros(n, dtype=torch.uint8, device=DEV)
+    ng = (n + 31) // 32
+    ms, vs = torch.zeros(ng, dtype=torch.float16, device=DEV), torch.zeros(ng, dtype=torch.float16, device=DEV)
+    for step in range(1, 6):
+        gs = g * (1 + 0.1 * step)
+        hp = torch.tensor([lr, b1, b2, eps, wd, 1 - b1 ** step, 1 - b2 ** step, 1.0], device=DEV)
+        m_ref = b1 * m_ref + (1 - b1) * gs
+        v_ref = b2 * v_ref + (1 - b2) * gs * gs
+        p_ref = p_ref * (1 - lr * wd * mask) - lr * (m_ref / (1 - b1 ** step)) / ((v_ref / (1 - b2 ** step)).sqrt() + eps)
+        ext.adamw_step(p32, gs, m, v, mask, hp)
+        ext.adamw8_step(p8, gs, m8, v8, ms, vs, mask, hp)
+    assert _rel_err(p32, p_ref) < 1e-5
+    # 8-bit state: updates stay close to the fp32-state trajectory
+    assert _rel_err(p8 - p, p_ref - p) < 0.1
+    # bf16 params / grads variant
+    pb = p.bfloat16()
+    ext.adamw_step(pb, g.bfloat16(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV), None,
+                   torch.tensor([lr, b1, b2, eps, 0.0, 1 - b1, 1 - b2, 1.0], device=DEV))
+    assert torch.isfinite(pb.float()).all()
