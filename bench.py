@@ -1,0 +1,243 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of the flagship configuration on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Default model: Qwen3-8B pre-training, FP8-hybrid recipe (E4M3 forward / E5M2 gradients, per-tensor delayed
+scaling, history 16), ZeRO-3 sharding of weights, gradients and 8-bit AdamW state over the N ranks,
+sequence 4096, micro-batch 2 per GPU, synthetic uniform token ids, random-init weights N(0, 0.02).
+Every step is a full forward + backward + gradient reduction + clipping + optimizer update.
+
+Two timings are taken after the warm-up:
+* ``value``: K steps timed with CUDA events on the device (inputs already resident), max over ranks;
+* ``e2e``:  K steps through the public ``Trainer.step`` API including the pinned-host -> device copy of each
+  step's tokens/targets and the device -> host read of loss and gradient norm.
+
+``--impl reference`` would run the unmodified reference; it cannot be installed offline in this image, so that
+arm prints an ``unavailable`` line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+MODELS = {
+    # name: (architecture kwargs, seq_len, micro_batch, recipe, optimizer, zero_level, extra)
+    "qwen3-8b": dict(model=dict(architecture="Qwen3ForCausalLM", vocab_size=151936, d_model=4096, n_layers=36, num_query_heads=32,
+                                num_kv_heads=8, head_size=128, d_ff=12288, tie_word_embeddings=False),
+                     seq_len=4096, batch=2, recipe="fp8_hybrid", optimizer="adamw_8bit", zero=3, label="Qwen3-8B",
+                     metric="tokens/sec Qwen3-8B FP8-hybrid pretrain (ZeRO-3, 8-bit AdamW)"),
+    "qwen3-0.6b": dict(model=dict(architecture="Qwen3ForCausalLM", vocab_size=151936, d_model=1024, n_layers=28, num_query_heads=16,
+                                  num_kv_heads=8, head_size=128, d_ff=3072, tie_word_embeddings=True),
+                       seq_len=2048, batch=8, recipe="bf16", optimizer="adamw", zero=1, label="Qwen3-0.6B",
+                       metric="tokens/sec Qwen3-0.6B BF16 full fine-tune (DP)"),
+    "qwen3-30b-a3b": dict(model=dict(architecture="Qwen3MoeForCausalLM", vocab_size=151936, d_model=2048, n_layers=48, num_query_heads=32,
+                                     num_kv_heads=4, head_size=128, moe_d_ff=768, num_experts=128, num_experts_per_tok=8,
+                                     aux_loss_coef=1e-3, tie_word_embeddings=False),
+                          seq_len=4096, batch=1, recipe="nvfp4", optimizer="adamw_8bit", zero=1, label="Qwen3-30B-A3B",
+                          metric="tokens/sec Qwen3-30B-A3B NVFP4 (EP)"),
+    "tiny": dict(model=dict(architecture="Qwen3ForCausalLM", vocab_size=4096, d_model=512, n_layers=2, num_query_heads=4, num_kv_heads=2,
+                            head_size=128, d_ff=1536, tie_word_embeddings=True),
+                 seq_len=512, batch=2, recipe="bf16", optimizer="adamw_8bit", zero=1, label="tiny", metric="tokens/sec tiny"),
+}
+
+# the reference publishes no B200 number for this metric (its B200 table is all TODO): no vs_baseline denominator
+PUBLISHED_BASELINE = None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()  # our own child, by handle
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                pass
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 4:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    print(json.dumps({"impl": "reference", "unavailable": "reference cannot be installed offline: pip build of /root/reference fails "
+                      "(scikit-build metadata needs setuptools_scm; CMake FetchContent needs network for CUTLASS 4.6.1, "
+                      "flash-attention, cudnn-frontend, nanobind)"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "library"])
+    ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
+    ap.add_argument("--recipe", default=None)
+    ap.add_argument("--optimizer", default=None)
+    ap.add_argument("--zero", type=int, default=None)
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--recompute", action="store_true")
+    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "symm"])
+    ap.add_argument("--ep", type=int, default=None)
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from surogate_b200.parallel.dist import TorchComm, init_distributed
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    info = init_distributed()
+    world = info.world
+    if world != args.gpus and info.rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
+    dev = torch.device("cuda", info.local_rank)
+    torch.cuda.set_device(dev)
+    comm = TorchComm() if world > 1 else None
+
+    spec = MODELS[args.model]
+    seq = args.seq_len or spec["seq_len"]
+    mb = args.batch or spec["batch"]
+    recipe = args.recipe or spec["recipe"]
+    zero = args.zero if args.zero is not None else spec["zero"]
+    ep = args.ep if args.ep is not None else (world if args.model == "qwen3-30b-a3b" else 1)
+    cfg = TrainerConfig(model=spec["model"], batch_size=mb, seq_len=seq, grad_accum=1, recipe=recipe, optimizer=args.optimizer or spec["optimizer"],
+                        learning_rate=1e-4, weight_decay=0.1, zero_level=zero, recompute=args.recompute,
+                        backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep)
+    tr = Trainer(cfg, device=dev, comm=comm)
+    tr.init_weights(seed=0)
+    V = spec["model"]["vocab_size"]
+    rng = np.random.default_rng(1234 + info.rank)
+    n_batches = 4
+    host_batches = [rng.integers(0, V, size=(mb, seq + 1), dtype=np.int64).astype(np.int32) for _ in range(n_batches)]
+    dev_batches = [(torch.from_numpy(b[:, :-1].copy()).to(dev), torch.from_numpy(b[:, 1:].copy()).to(dev)) for b in host_batches]
+
+    def barrier():
+        if world > 1:
+            comm.barrier()
+        torch.cuda.synchronize()
+
+    def device_step(i):
+        x, y = dev_batches[i % n_batches]
+        tr.forward_backward(x, y)
+        tr.optimizer_step()
+
+    ext = tr.backend.ext if tr.backend.name == "cuda" else None
+    for i in range(args.warmup):
+        device_step(i)
+    barrier()
+    sampler = ClockSampler(info.local_rank)
+    sampler.start()
+    launches0 = ext.launch_count() if ext is not None else 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        device_step(i)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = (ext.launch_count() - launches0) if ext is not None else 0
+    clocks = sampler.stop()
+
+    # end-to-end through the public API: numpy batches from host memory in, python floats out, every step
+    e2e = None
+    if not args.no_e2e:
+        tr.h2d_bytes = tr.d2h_bytes = 0
+        out = tr.step(host_batches[0][:, :-1], host_batches[0][:, 1:])  # one warm step through this path (allocates the pinned buffers)
+        tr.h2d_bytes = tr.d2h_bytes = 0
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(args.steps):
+            b = host_batches[(i + 1) % n_batches]
+            out = tr.step(b[:, :-1], b[:, 1:])
+        e1.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = max(e0.elapsed_time(e1), wall_ms)
+        e2e = (e2e_ms, tr.h2d_bytes // args.steps, tr.d2h_bytes // args.steps, out)
+
+    t = torch.tensor([ms, e2e[0] if e2e else 0.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        comm.all_reduce(t, "max")
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if info.rank == 0:
+        tokens_per_step = world * mb * seq
+        value = tokens_per_step * args.steps / (ms / 1e3)
+        par = f"zero{zero}-dp{world}" if ep <= 1 else f"ep{ep}-zero{zero}"
+        line = {
+            "metric": spec["metric"], "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None, "dtype": "fp8" if recipe.startswith("fp8") else recipe,
+            "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": args.impl,
+            "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
+                       "optimizer": cfg.optimizer, "recompute": bool(args.recompute), "micro_batch_per_gpu": mb,
+                       "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
+                       "timing": "CUDA events on the launching stream, barrier+synchronize on both sides, max over ranks"},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+        }
+        if e2e:
+            line["e2e"] = {"value": round(tokens_per_step * args.steps / (e2e_ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
+                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "last_loss": e2e[3]["loss"]}
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

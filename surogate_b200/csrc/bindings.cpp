@@ -35,6 +35,9 @@ const float* opt_f32(const c10::optional<Tensor>& t) {
 float* opt_f32_mut(const c10::optional<Tensor>& t) { return const_cast<float*>(opt_f32(t)); }
 const void* opt_ptr(const c10::optional<Tensor>& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
 
+int64_t g_launches = 0;  // kernels of this extension launched so far (host-side count)
+int64_t launch_count() { return g_launches; }
+
 Tensor g_error_flag;
 int* error_flag_ptr() {
     if (!g_error_flag.defined()) g_error_flag = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA));
@@ -85,6 +88,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, boo
     p.tile_n = static_cast<int>(tile_n);
     sg::GemmOperand A{a.data_ptr(), static_cast<uint64_t>(a.stride(0)) * es};
     sg::GemmOperand B{b.data_ptr(), static_cast<uint64_t>(b.stride(0)) * es};
+    g_launches += 1;
     const char* err = sg::gemm_sm100(A, B, p, num_sms(), cur_stream());
     TORCH_CHECK(err == nullptr, err ? err : "");
 }
@@ -114,6 +118,7 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& re
     auto lead = x.sizes().vec();
     lead.pop_back();
     Tensor rstd = torch::empty(lead, x.options().dtype(at::kFloat));
+    g_launches += 1;
     sg::rmsnorm_fwd(x.data_ptr(), opt_ptr(residual), w.data_ptr(), res_out.defined() ? res_out.data_ptr() : nullptr, y.defined() ? y.data_ptr() : nullptr,
                     rstd.data_ptr<float>(), y8.defined() ? y8.data_ptr() : nullptr, opt_f32(fp8_scale), opt_f32_mut(amax_out), rows, C,
                     static_cast<float>(eps), cur_stream());
@@ -133,6 +138,7 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
     const int blocks = sg::rmsnorm_bwd_blocks(rows, num_sms());
     Tensor partial = torch::empty({blocks, C}, x.options().dtype(at::kFloat));
     Tensor dw = torch::empty({C}, x.options().dtype(at::kFloat));
+    g_launches += 2;
     sg::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), opt_ptr(d_res), dx.data_ptr(), partial.data_ptr<float>(),
                     dw.data_ptr<float>(), rows, C, num_sms(), cur_stream());
     return {dx, dw};
@@ -149,6 +155,7 @@ std::vector<Tensor> swiglu_fwd(const Tensor& x, bool want_y, const c10::optional
     Tensor y, y8;
     if (want_y) y = torch::empty(shape, x.options());
     if (want_fp8) y8 = torch::empty(shape, x.options().dtype(at::kFloat8_e4m3fn));
+    g_launches += 1;
     sg::swiglu_fwd(x.data_ptr(), y.defined() ? y.data_ptr() : nullptr, y8.defined() ? y8.data_ptr() : nullptr, opt_f32(fp8_scale), opt_f32_mut(amax_out),
                    rows, M, num_sms(), cur_stream());
     return {y, y8};
@@ -160,6 +167,7 @@ Tensor swiglu_bwd(const Tensor& dy, const Tensor& x) {
     const int M = static_cast<int>(x.size(-1) / 2);
     const c10::cuda::CUDAGuard guard(x.device());
     Tensor dx = torch::empty_like(x);
+    g_launches += 1;
     sg::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel() / (2 * M), M, num_sms(), cur_stream());
     return dx;
 }
@@ -184,6 +192,7 @@ std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tens
         lead.back() = Hkv;
         k_rstd = torch::empty(lead, qkv.options().dtype(at::kFloat));
     }
+    g_launches += 1;
     sg::qk_norm_rope_fwd(qkv.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), out.data_ptr(), norm ? q_rstd.data_ptr<float>() : nullptr,
                          norm ? k_rstd.data_ptr<float>() : nullptr, tokens, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps),
                          static_cast<float>(theta), num_sms(), cur_stream());
@@ -205,6 +214,7 @@ std::vector<Tensor> qk_norm_rope_bwd(const Tensor& d_out, const Tensor& qkv_pre,
         dqw = torch::zeros({D}, d_out.options().dtype(at::kFloat));
         dkw = torch::zeros({D}, d_out.options().dtype(at::kFloat));
     }
+    g_launches += 1;
     sg::qk_norm_rope_bwd(d_out.data_ptr(), qkv_pre.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), dx.data_ptr(), opt_f32_mut(q_rstd),
                          opt_f32_mut(k_rstd), norm ? dqw.data_ptr<float>() : nullptr, norm ? dkw.data_ptr<float>() : nullptr, tokens,
                          static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps), static_cast<float>(theta), num_sms(), cur_stream());
@@ -220,6 +230,7 @@ Tensor embedding_fwd(const Tensor& tokens, const Tensor& table) {
     auto shape = tokens.sizes().vec();
     shape.push_back(C);
     Tensor out = torch::empty(shape, table.options());
+    g_launches += 1;
     sg::embedding_fwd(tokens.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tokens.numel(), C, num_sms(), cur_stream());
     return out;
 }
@@ -230,6 +241,7 @@ void embedding_bwd(const Tensor& tokens, const Tensor& d_out, Tensor& d_table) {
     TORCH_CHECK(d_table.scalar_type() == at::kFloat || d_table.scalar_type() == at::kBFloat16, "d_table must be fp32 or bf16");
     const int C = static_cast<int>(d_table.size(1));
     const c10::cuda::CUDAGuard guard(d_out.device());
+    g_launches += 1;
     sg::embedding_bwd(tokens.data_ptr<int>(), d_out.data_ptr(), d_table.data_ptr(), d_table.scalar_type() == at::kFloat, tokens.numel(), C, num_sms(),
                       cur_stream());
 }
@@ -244,6 +256,7 @@ Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::o
     TORCH_CHECK(targets.numel() == rows, "one target per row");
     const c10::cuda::CUDAGuard guard(logits.device());
     Tensor loss = torch::empty({rows}, logits.options().dtype(at::kFloat));
+    g_launches += 1;
     sg::cross_entropy_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), loss.data_ptr<float>(), opt_f32(scale), static_cast<float>(scale_host), rows, V,
                               ld, write_grad, cur_stream());
     return loss;
@@ -254,6 +267,7 @@ Tensor quantize_fp8(const Tensor& x, const c10::optional<Tensor>& scale, const c
     TORCH_CHECK(x.numel() % 8 == 0, "quantize_fp8: numel must be a multiple of 8");
     const c10::cuda::CUDAGuard guard(x.device());
     Tensor q = torch::empty(x.sizes(), x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+    g_launches += 1;
     sg::quantize_fp8(x.data_ptr(), q.data_ptr(), opt_f32(scale), opt_f32_mut(amax_out), x.numel(), e5m2, num_sms(), cur_stream());
     return q;
 }
@@ -262,6 +276,7 @@ void amax(const Tensor& x, Tensor& amax_out) {
     check_bf16(x, "x");
     TORCH_CHECK(x.numel() % 8 == 0, "amax: numel must be a multiple of 8");
     const c10::cuda::CUDAGuard guard(x.device());
+    g_launches += 1;
     sg::amax_bf16(x.data_ptr(), amax_out.data_ptr<float>(), x.numel(), num_sms(), cur_stream());
 }
 
@@ -271,6 +286,7 @@ Tensor sumsq(const Tensor& x) {
     const c10::cuda::CUDAGuard guard(x.device());
     const int nblocks = num_sms() * 2;
     Tensor partial = torch::empty({nblocks}, x.options().dtype(at::kFloat));
+    g_launches += 1;
     sg::sumsq(x.data_ptr(), x.scalar_type() == at::kFloat, partial.data_ptr<float>(), nblocks, x.numel(), cur_stream());
     return partial.sum();
 }
@@ -280,6 +296,7 @@ void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::opt
     TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous tensors");
     TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && hp.scalar_type() == at::kFloat && hp.numel() >= 8, "adamw: fp32 state");
     const c10::cuda::CUDAGuard guard(p.device());
+    g_launches += 1;
     sg::adamw_fp32(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr<float>(), v.data_ptr<float>(),
                    static_cast<const uint8_t*>(opt_ptr(mask)), hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
 }
@@ -291,6 +308,7 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
                 "adamw8: state dtypes int8/uint8/fp16/fp16");
     TORCH_CHECK(static_cast<size_t>(ms.numel()) * 32 >= static_cast<size_t>(p.numel()), "adamw8: one scale per 32 elements");
     const c10::cuda::CUDAGuard guard(p.device());
+    g_launches += 1;
     sg::adamw_8bit(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m8.data_ptr(), v8.data_ptr(), ms.data_ptr(),
                    vs.data_ptr(), static_cast<const uint8_t*>(opt_ptr(mask)), hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
 }
@@ -300,6 +318,7 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm", &gemm, "tcgen05 GEMM");
     m.def("read_error_flag", &read_error_flag);
+    m.def("launch_count", &launch_count, "number of kernels this extension has launched");
     m.def("rmsnorm_fwd", &rmsnorm_fwd);
     m.def("rmsnorm_bwd", &rmsnorm_bwd);
     m.def("swiglu_fwd", &swiglu_fwd);

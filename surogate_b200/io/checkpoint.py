@@ -1,0 +1,156 @@
+"""Step checkpoints: per-rank shards of weights and optimizer state + run metadata, resumable bit-exactly.
+
+Layout (same as the reference): ``<dir>/step_%08d/`` with ``weights.shard_RRR_of_NNN.safetensors``,
+``adam.m.shard_*``, ``adam.v.shard_*`` and, for 8-bit state, ``adam.m.scales.*`` / ``adam.v.scales.*``;
+``checkpoint.json`` (written by rank 0 after a barrier) holds run state (step, RNG), the data-loader
+cursor and the distributed shape.  LoRA runs store only the adapter and its optimizer state.
+Unlike the reference, loading under a different world size is supported: shards are re-cut from the
+flat bucket layout (padding included) because every rank's slice is a contiguous range.
+
+Parity: csrc/src/runtime/training/checkpoint.cpp:31-380 (save :56, load :186, retention :317-380).
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import re
+import shutil
+from typing import Any, Dict, List, Optional
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+
+STEP_RE = re.compile(r"step_(\d{8})$")
+
+
+def step_dir(root: str, step: int) -> str:
+    return os.path.join(root, f"step_{step:08d}")
+
+
+def find_latest_checkpoint(root: str) -> Optional[int]:
+    best = None
+    for d in glob.glob(os.path.join(root, "step_*")):
+        m = STEP_RE.search(d)
+        if m and os.path.exists(os.path.join(d, "checkpoint.json")):
+            best = max(best or -1, int(m.group(1)))
+    return best
+
+
+def clean_old_checkpoints(root: str, keep: int, major_every: int = 0) -> List[int]:
+    """Keep the newest ``keep`` checkpoints (and every ``major_every``-th step); returns the removed steps."""
+    steps = sorted(int(STEP_RE.search(d).group(1)) for d in glob.glob(os.path.join(root, "step_*")) if STEP_RE.search(d))
+    removed = []
+    for s in steps[:-keep] if keep > 0 else []:
+        if major_every and s % major_every == 0:
+            continue
+        shutil.rmtree(step_dir(root, s), ignore_errors=True)
+        removed.append(s)
+    return removed
+
+
+def _shard_name(kind: str, rank: int, world: int) -> str:
+    return f"{kind}.shard_{rank:03d}_of_{world:03d}.safetensors"
+
+
+def save_checkpoint(trainer, root: str, step: int, extra: Dict[str, Any]) -> str:
+    d = step_dir(root, step)
+    os.makedirs(d, exist_ok=True)
+    store, opt = trainer.store, trainer.optimizer
+    rank, world = trainer.rank, trainer.world
+    shard_world = world if store.sharded else 1
+    if store.sharded or rank == 0:
+        r = rank if store.sharded else 0
+        save_file({b.name: b.master.detach().cpu().contiguous() for b in store.buckets.values()}, os.path.join(d, _shard_name("weights", r, shard_world)))
+        kinds: Dict[str, Dict[str, torch.Tensor]] = {}
+        for b in store.trainable_buckets():
+            for k, t in opt.state_tensors(b).items():
+                kinds.setdefault(k, {})[b.name] = t.detach().cpu().contiguous()
+        for k, tensors in kinds.items():
+            save_file(tensors, os.path.join(d, _shard_name(f"adam.{k}", r, shard_world)))
+        extra_state = getattr(opt, "mom", None)
+        if extra_state:
+            save_file({k: v.cpu() for k, v in {**opt.mom, **{f"second::{k}": v for k, v in opt.second.items()}}.items()},
+                      os.path.join(d, _shard_name("normuon", r, shard_world)))
+    if trainer.lora is not None:
+        trainer.lora.save_state(d, rank)
+    rs = trainer.recipe.state_dict()
+    if rs and rank == 0:
+        torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in rs.items()}, os.path.join(d, "recipe_state.pt"))
+    trainer.comm.barrier()
+    if rank == 0:
+        meta = {
+            "run": {"step": step, "optimizer_step": trainer.step_index, "torch_rng": torch.get_rng_state().tolist()[:16],
+                    "past_losses": extra.get("past_losses", []), "past_norms": extra.get("past_norms", [])},
+            "data-loader": extra.get("data_loader", {}),
+            "distributed": {"world": world, "ep_size": trainer.cfg.ep_size, "zero_level": store.zero_level, "sharded": store.sharded},
+            "layout": {b.name: {"numel": b.numel, "shard_numel": b.shard_numel} for b in store.buckets.values()},
+            "optimizer": trainer.cfg.optimizer, "recipe": trainer.cfg.recipe,
+        }
+        tmp = os.path.join(d, "checkpoint.json.tmp")
+        with open(tmp, "w") as f:
+            json.dump(meta, f, indent=1)
+        os.replace(tmp, os.path.join(d, "checkpoint.json"))  # atomic: a directory without checkpoint.json is incomplete
+    trainer.comm.barrier()
+    return d
+
+
+def _read_flat(d: str, kind: str, bucket: str, saved_world: int, lo: int, hi: int, shard_numel: int) -> torch.Tensor:
+    """Elements [lo, hi) of a bucket-flat tensor reassembled from the shards saved under ``saved_world``."""
+    parts = []
+    for r in range(saved_world):
+        a, z = r * shard_numel, (r + 1) * shard_numel
+        if z <= lo or a >= hi:
+            continue
+        with safe_open(os.path.join(d, _shard_name(kind, r, saved_world)), framework="pt") as f:
+            t = f.get_tensor(bucket)
+        parts.append(t[max(lo, a) - a:min(hi, z) - a])
+    return torch.cat(parts) if len(parts) != 1 else parts[0]
+
+
+def load_checkpoint(trainer, root: str, step: Optional[int] = None) -> Dict[str, Any]:
+    if step is None:
+        step = find_latest_checkpoint(root)
+        if step is None:
+            raise FileNotFoundError(f"no complete checkpoint under {root}")
+    d = step_dir(root, step)
+    with open(os.path.join(d, "checkpoint.json")) as f:
+        meta = json.load(f)
+    dist_meta = meta["distributed"]
+    if dist_meta.get("ep_size", 1) != trainer.cfg.ep_size:
+        raise ValueError(f"checkpoint was written with ep_size={dist_meta.get('ep_size')} but the run uses {trainer.cfg.ep_size}")
+    saved_world = dist_meta["world"] if dist_meta.get("sharded") else 1
+    store, opt = trainer.store, trainer.optimizer
+    for b in store.buckets.values():
+        lay = meta["layout"][b.name]
+        lo, hi = store.shard_range(b)
+        total_saved = lay["shard_numel"] * saved_world
+        hi_c = min(hi, total_saved)
+        w = _read_flat(d, "weights", b.name, saved_world, lo, hi_c, lay["shard_numel"])
+        b.master[: hi_c - lo].copy_(w.to(b.master.dtype))
+        if not b.trainable:
+            continue
+        for k, t in opt.state_tensors(b).items():
+            kind = f"adam.{k}"
+            if not os.path.exists(os.path.join(d, _shard_name(kind, 0, saved_world))):
+                continue
+            per = 32 if k.endswith("scales") else 1
+            if per == 32 and (lo % 32 or lay["shard_numel"] % 32):
+                raise ValueError("8-bit optimizer scales cannot be re-sharded at this alignment")
+            s = _read_flat(d, kind, b.name, saved_world, lo // per, (hi_c + per - 1) // per, max(1, lay["shard_numel"] // per))
+            t[: s.numel()].copy_(s.to(t.dtype))
+    nm = os.path.join(d, _shard_name("normuon", trainer.rank if store.sharded else 0, saved_world))
+    if hasattr(opt, "mom") and os.path.exists(nm):
+        with safe_open(nm, framework="pt") as f:
+            for k in f.keys():
+                (opt.second if k.startswith("second::") else opt.mom)[k.replace("second::", "")] = f.get_tensor(k).to(store.device)
+    if trainer.lora is not None:
+        trainer.lora.load_state(d, trainer.rank)
+    rp = os.path.join(d, "recipe_state.pt")
+    if os.path.exists(rp):
+        trainer.recipe.load_state_dict(torch.load(rp, map_location=store.device))
+    trainer.step_index = meta["run"].get("optimizer_step", step)
+    store.sync_work_from_master()
+    trainer.recipe.on_weights_updated(store)
+    return meta

@@ -1,0 +1,334 @@
+"""Trainer: owns the compiled model, parameter store, recipe, optimizer and the step loop.
+
+One process drives one GPU.  ``step(inputs, targets)`` takes int32 numpy arrays
+``[B * grad_accum, T]`` for this rank (or ``[world * B * grad_accum, T]`` for the whole
+job, of which the rank takes its slice), stages them through pinned host memory, runs
+forward/backward for every micro-batch, reduces gradients (overlapped with backward),
+computes the global gradient norm and clip scale on the device, runs the optimizer on
+this rank's shards and returns ``{"loss", "norm"}`` as Python floats — the only
+host synchronisation of the step is that final read-back.
+
+Parity: csrc/src/binding/py_train.h:55-501 (MultiGPUPyTrainer: step / update_with_config /
+train_step_graphed / validate / import / export / checkpoints), docs/reference/python-api.md.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..dsl.compiler import CompiledModel, compile_model, model_from_hf_config
+from ..dsl.nn import model_class_for
+from ..optim import OptimizerConfig, make_optimizer
+from ..recipes import make_recipe
+from .executor import ExecOptions, Executor
+from .params import ParamStore, SingleProcessComm
+
+
+@dataclass
+class TrainerConfig:
+    model: Dict[str, Any] = field(default_factory=dict)  # HF config.json dict, or ctor kwargs + "architecture"
+    batch_size: int = 2
+    seq_len: int = 1024
+    grad_accum: int = 1
+    recipe: str = "bf16"
+    optimizer: str = "adamw_8bit"
+    learning_rate: float = 2e-4
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    max_grad_norm: float = 1.0
+    zero_level: int = 1
+    recompute: bool = False
+    backend: str = "auto"  # auto | cuda | ref
+    attention: str = "auto"
+    param_dtype: str = "bf16"
+    grad_dtype: str = "bf16"
+    master_dtype: Optional[str] = None
+    lmhead_chunk_rows: int = 4096
+    keep_gathered: bool = True
+    collectives: str = "auto"  # auto | nccl | symm
+    ep_size: int = 1
+    lora: Optional[Dict[str, Any]] = None
+    fp8_amax_history: int = 16
+    skip_quant_first_layers: int = 0
+    skip_quant_last_layers: int = 0
+    offload_optimizer: bool = False
+    offload_master: bool = False
+    normuon_momentum: float = 0.95
+    normuon_beta2: float = 0.95
+    normuon_cautious_wd: bool = True
+    init_projections_to_zero: bool = False
+    seed: int = 0
+
+
+_DT = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16, None: None}
+
+
+def build_model(spec: Dict[str, Any], **overrides):
+    spec = dict(spec)
+    if "architectures" in spec or "model_type" in spec:
+        return model_from_hf_config(spec, **overrides)
+    arch = spec.pop("architecture")
+    spec.update(overrides)
+    return model_class_for(arch)(**spec)
+
+
+class Trainer:
+    def __init__(self, cfg: TrainerConfig, device: Optional[torch.device] = None, comm=None):
+        self.cfg = cfg
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        self.comm = comm or SingleProcessComm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        on_gpu = self.device.type == "cuda"
+        extra = {"ep_size": cfg.ep_size} if cfg.ep_size > 1 else {}
+        self.model = build_model(cfg.model, **extra)
+        self.cm: CompiledModel = compile_model(self.model)
+        pd = _DT[cfg.param_dtype] if on_gpu else torch.float32
+        gd = _DT[cfg.grad_dtype] if on_gpu else torch.float32
+        md = _DT[cfg.master_dtype] if cfg.master_dtype else pd
+        self.lora = None
+        frozen = None
+        if cfg.lora:
+            from .lora import LoRAManager
+
+            self.lora = LoRAManager(self.cm, cfg.lora, device=self.device, comm=self.comm, dtype=pd)
+            frozen = self.lora.freezes
+        self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
+                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen)
+        if cfg.collectives in ("auto", "symm") and on_gpu and self.world > 1:
+            from ..parallel import symm
+
+            symm.maybe_enable(self.store, self.comm, required=cfg.collectives == "symm")
+        from .ops_cuda import make_backend
+
+        self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
+        rname = cfg.recipe if (on_gpu and self.backend.name == "cuda") else "bf16"
+        self.recipe = make_recipe(rname, self.cm, self.device, **self._recipe_kwargs(rname))
+        self.ep = None
+        if cfg.ep_size > 1:
+            from ..parallel.ep import ExpertParallel
+
+            self.ep = ExpertParallel(self.comm, cfg.ep_size, self.device)
+        self.executor = Executor(self.cm, self.store, self.backend, recipe=self.recipe,
+                                 options=ExecOptions(recompute=cfg.recompute, act_dtype=pd), device=self.device, ep=self.ep, lora=self.lora)
+        self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
+                                       cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd)
+        self.optimizer = make_optimizer(self.opt_cfg, self.store)
+        self.step_index = 0
+        self.kernel_launch_estimate = 0
+        self._pinned: Dict[str, torch.Tensor] = {}
+        self._hp = torch.zeros(8, dtype=torch.float32, device=self.device)
+        self.last_moe_stats = None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def _recipe_kwargs(self, name: str) -> Dict[str, Any]:
+        n = name.replace("-", "_")
+        if n == "fp8_hybrid":
+            return dict(history=self.cfg.fp8_amax_history, skip_first_layers=self.cfg.skip_quant_first_layers,
+                        skip_last_layers=self.cfg.skip_quant_last_layers)
+        if n == "nvfp4":
+            return dict(skip_first_layers=self.cfg.skip_quant_first_layers, skip_last_layers=self.cfg.skip_quant_last_layers)
+        return {}
+
+    # ------------------------------------------------------------------ weights
+    def init_weights(self, seed: Optional[int] = None) -> None:
+        self.store.init_weights(seed if seed is not None else self.cfg.seed, zero_projections=self.cfg.init_projections_to_zero)
+        self.recipe.on_weights_updated(self.store)
+        if self.lora is not None:
+            self.lora.init_weights(seed if seed is not None else self.cfg.seed)
+
+    def import_weights(self, path: str) -> None:
+        from ..io.hf_checkpoint import import_hf_weights
+
+        import_hf_weights(self.cm, self.store, path)
+        self.store.sync_work_from_master()
+        self.recipe.on_weights_updated(self.store)
+
+    def export_model(self, out_dir: str, hf_config: Optional[Dict[str, Any]] = None) -> None:
+        from ..io.hf_checkpoint import export_hf_weights
+
+        export_hf_weights(self.cm, self.store, out_dir, hf_config or self.cfg.model, write=self.rank == 0)
+
+    def export_adapter(self, out_dir: str, base_model: str = "") -> None:
+        if self.lora is None:
+            raise RuntimeError("export_adapter: LoRA is not enabled")
+        self.lora.export_peft(out_dir, base_model, write=self.rank == 0)
+
+    def save_checkpoint(self, ckpt_dir: str, step: Optional[int] = None, extra: Optional[Dict[str, Any]] = None) -> str:
+        from ..io.checkpoint import save_checkpoint
+
+        return save_checkpoint(self, ckpt_dir, self.step_index if step is None else step, extra or {})
+
+    def load_checkpoint(self, ckpt_dir: str, step: Optional[int] = None) -> Dict[str, Any]:
+        from ..io.checkpoint import load_checkpoint
+
+        return load_checkpoint(self, ckpt_dir, step)
+
+    # ------------------------------------------------------------------ data staging
+    def _stage(self, name: str, arr, dtype=torch.int32) -> torch.Tensor:
+        """numpy / CPU tensor -> pinned host buffer -> device (async).  Counts the bytes moved."""
+        t = torch.from_numpy(np.ascontiguousarray(arr)) if isinstance(arr, np.ndarray) else arr
+        if t.device.type != "cpu":
+            return t.to(self.device, dtype=dtype)
+        t = t.to(dtype)
+        if self.device.type != "cuda":
+            return t
+        buf = self._pinned.get(name)
+        if buf is None or buf.shape != t.shape:
+            buf = self._pinned[name] = torch.empty(t.shape, dtype=dtype, pin_memory=True)
+        buf.copy_(t)
+        self.h2d_bytes += buf.numel() * buf.element_size()
+        return buf.to(self.device, non_blocking=True)
+
+    def _local_slice(self, arr):
+        B, GA = self.cfg.batch_size, self.cfg.grad_accum
+        if arr.shape[0] == self.world * B * GA and self.world > 1:
+            return arr[self.rank * B * GA:(self.rank + 1) * B * GA]
+        assert arr.shape[0] == B * GA, f"expected {B * GA} (or {self.world * B * GA}) rows, got {arr.shape[0]}"
+        return arr
+
+    # ------------------------------------------------------------------ the step
+    def forward_backward(self, inputs, targets, position_ids=None) -> Dict[str, torch.Tensor]:
+        """All micro-batches of one optimizer step; leaves reduced gradients in the store.  Returns device scalars."""
+        cfg = self.cfg
+        B, GA, T = cfg.batch_size, cfg.grad_accum, inputs.shape[1]
+        inp = self._stage("inputs", self._local_slice(inputs))
+        tgt = self._stage("targets", self._local_slice(targets))
+        if position_ids is None:
+            pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(B * GA, T).contiguous()
+            doc_ids = None
+        else:
+            pos = self._stage("position_ids", self._local_slice(position_ids))
+            doc_ids = None
+            if bool((position_ids[:, 1:] <= position_ids[:, :-1]).any()) if isinstance(position_ids, np.ndarray) else False:
+                doc_ids = torch.cumsum((pos == 0).to(torch.int32), dim=1)  # packed documents: id increments at each reset
+        n_valid = (tgt != -100).sum().to(torch.float32)
+        if self.world > 1:
+            self.comm.all_reduce(n_valid, "sum")
+        loss_scale = (1.0 / n_valid.clamp_min(1.0)).reshape(1)
+        if self.device.type != "cuda":
+            loss_scale = float(loss_scale)
+        aux_scale = 1.0 / (GA * self.world)
+        self.store.begin_step()
+        self.recipe.begin_step(self.step_index)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        aux_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        stats = []
+        for i in range(GA):
+            self.store.begin_micro_step(i, GA)
+            sl = slice(i * B, (i + 1) * B)
+            ctx, outs = self.executor.forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale=loss_scale, aux_scale=aux_scale,
+                                                       doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i)
+            loss_sum += outs[0]
+            if len(outs) > 1 and outs[1] is not None:
+                aux_sum += outs[1] * aux_scale
+            stats.extend(ctx.moe_stats)
+        self.last_moe_stats = stats
+        if self.lora is not None:
+            self.lora.reduce_grads()
+        self.store.finish_reduce()
+        return {"loss_sum": loss_sum, "n_valid": n_valid, "aux": aux_sum}
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the (already reduced) gradients, as a device scalar."""
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        on_gpu = self.device.type == "cuda" and self.backend.name == "cuda"
+        for b in self.store.trainable_buckets():
+            g = b.grad_shard
+            if g is None:
+                continue
+            total += self.backend.ext.sumsq(g) if on_gpu else g.float().pow(2).sum()
+        if self.lora is not None:
+            total += self.lora.grad_sumsq()
+        if self.world > 1 and self.store.sharded:
+            self.comm.all_reduce(total, "sum")
+        return total.sqrt()
+
+    def optimizer_step(self, lr: Optional[float] = None) -> torch.Tensor:
+        cfg = self.opt_cfg
+        self.step_index += 1
+        t = self.step_index
+        lr = cfg.learning_rate if lr is None else lr
+        norm = self.grad_norm()
+        clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm and cfg.max_grad_norm > 0 else torch.ones_like(norm)
+        clip = torch.where(torch.isfinite(norm), clip, torch.zeros_like(clip))  # a non-finite gradient skips the update
+        host = (lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, 1 - cfg.beta1 ** t, 1 - cfg.beta2 ** t)
+        hp_cpu = torch.tensor(list(host) + [1.0], dtype=torch.float32)
+        self._hp.copy_(hp_cpu, non_blocking=True)
+        self._hp[7] = clip
+        for b in self.store.trainable_buckets():
+            if b.grad_shard is None:
+                continue
+            self.optimizer.step_bucket(b, b.grad_shard, self._hp, host)
+        if self.lora is not None:
+            self.lora.optimizer_step(self._hp, host)
+        self.store.release_grads()
+        self.store.sync_work_from_master()
+        self.recipe.on_weights_updated(self.store)
+        self.recipe.end_step()
+        return norm
+
+    def step(self, inputs, targets, position_ids=None, lr: Optional[float] = None) -> Dict[str, float]:
+        r = self.forward_backward(inputs, targets, position_ids)
+        norm = self.optimizer_step(lr)
+        loss = r["loss_sum"].clone()
+        if self.world > 1:
+            self.comm.all_reduce(loss, "sum")
+        out = torch.stack([loss / r["n_valid"].clamp_min(1.0) + r["aux"], norm, r["aux"]]).to("cpu")  # the step's only D2H sync
+        self.d2h_bytes += out.numel() * 4
+        if self.device.type == "cuda" and self.backend.name == "cuda":
+            from ..ops import check_device_errors
+
+            check_device_errors()
+        return {"loss": float(out[0]), "norm": float(out[1]), "aux_loss": float(out[2])}
+
+    @torch.no_grad()
+    def validate(self, inputs, targets, position_ids=None) -> Dict[str, float]:
+        inp = self._stage("v_inputs", inputs)
+        tgt = self._stage("v_targets", targets)
+        T = inp.shape[1]
+        pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(inp.shape[0], T).contiguous()
+        self.store.grads_enabled = False
+        try:
+            ctx, outs = self.executor.forward(inp, pos, tgt, training=False)
+        finally:
+            self.store.grads_enabled = True
+        n = (tgt != -100).sum().clamp_min(1).float()
+        loss = outs[0].clone()
+        if self.world > 1:
+            self.comm.all_reduce(loss, "sum")
+            self.comm.all_reduce(n, "sum")
+        return {"loss": float(loss / n)}
+
+    # ------------------------------------------------------------------ introspection
+    def get_gradients(self) -> Dict[str, torch.Tensor]:
+        return {p.name: self.store.grad_of(p.name) for p in self.cm.params if not p.tied_to}
+
+    def get_moe_stats(self):
+        from ..utils.moe_stats import summarize
+
+        return summarize(self.last_moe_stats or [])
+
+    def get_gpu_info(self):
+        from ..utils.gpu_info import gpu_info
+
+        return gpu_info(self.device)
+
+    def num_parameters(self) -> int:
+        return self.cm.num_parameters()
+
+    def memory_breakdown(self) -> Dict[str, int]:
+        out = self.store.memory_breakdown()
+        if self.device.type == "cuda":
+            out["allocated"] = torch.cuda.memory_allocated(self.device)
+            out["reserved"] = torch.cuda.memory_reserved(self.device)
+            out["peak"] = torch.cuda.max_memory_allocated(self.device)
+        return out
