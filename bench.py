@@ -123,6 +123,7 @@ def main():
     ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "symm"])
     ap.add_argument("--ep", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -143,7 +144,11 @@ def main():
     torch.cuda.set_device(dev)
     comm = TorchComm() if world > 1 else None
 
-    spec = MODELS[args.model]
+    spec = dict(MODELS[args.model])
+    if args.layers:
+        spec["model"] = dict(spec["model"], n_layers=args.layers)
+        spec["label"] = f"{spec['label']}-truncated-{args.layers}-layers"
+        spec["metric"] += f" [TRUNCATED to {args.layers} layers: profiling run, not a benchmark value]"
     seq = args.seq_len or spec["seq_len"]
     mb = args.batch or spec["batch"]
     recipe = args.recipe or spec["recipe"]

@@ -37,6 +37,7 @@ const void* opt_ptr(const c10::optional<Tensor>& t) { return (t.has_value() && t
 
 int64_t g_launches = 0;  // kernels of this extension launched so far (host-side count)
 int64_t launch_count() { return g_launches; }
+Tensor error_flag_tensor();
 
 Tensor g_error_flag;
 int* error_flag_ptr() {
@@ -91,6 +92,11 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, boo
     g_launches += 1;
     const char* err = sg::gemm_sm100(A, B, p, num_sms(), cur_stream());
     TORCH_CHECK(err == nullptr, err ? err : "");
+}
+
+Tensor error_flag_tensor() {
+    error_flag_ptr();
+    return g_error_flag;
 }
 
 int64_t read_error_flag(bool reset) {
@@ -295,6 +301,7 @@ void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::opt
     check_cuda(p, "p");
     TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous tensors");
     TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && hp.scalar_type() == at::kFloat && hp.numel() >= 8, "adamw: fp32 state");
+    TORCH_CHECK(p.numel() % 8 == 0, "adamw: element count must be a multiple of 8");
     const c10::cuda::CUDAGuard guard(p.device());
     g_launches += 1;
     sg::adamw_fp32(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr<float>(), v.data_ptr<float>(),
@@ -307,6 +314,7 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
     TORCH_CHECK(m8.scalar_type() == at::kChar && v8.scalar_type() == at::kByte && ms.scalar_type() == at::kHalf && vs.scalar_type() == at::kHalf,
                 "adamw8: state dtypes int8/uint8/fp16/fp16");
     TORCH_CHECK(static_cast<size_t>(ms.numel()) * 32 >= static_cast<size_t>(p.numel()), "adamw8: one scale per 32 elements");
+    TORCH_CHECK(p.numel() % 32 == 0, "adamw8: element count must be a multiple of 32");
     const c10::cuda::CUDAGuard guard(p.device());
     g_launches += 1;
     sg::adamw_8bit(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m8.data_ptr(), v8.data_ptr(), ms.data_ptr(),
@@ -315,7 +323,10 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
 
 }  // namespace
 
+void sg_count_launch(int n) { g_launches += n; }
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("error_flag_tensor", &error_flag_tensor, "the device int32 word kernels set when a bounded wait runs out");
     m.def("gemm", &gemm, "tcgen05 GEMM");
     m.def("read_error_flag", &read_error_flag);
     m.def("launch_count", &launch_count, "number of kernels this extension has launched");

@@ -2,3 +2,5 @@
 #pragma once
 #include <pybind11/pybind11.h>
 void sg_register_extra(pybind11::module_& m);
+// Adds n to the extension-wide count of kernels launched (read through launch_count()).
+void sg_count_launch(int n);

@@ -465,10 +465,25 @@ __global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, f
     amax = block_reduce<true>(amax, sh);
     if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
 }
+// vectorised sum of squares: 16-byte loads, tail handled by the first threads
 template <typename T> __global__ void __launch_bounds__(512) sumsq_kernel(const T* __restrict__ x, float* __restrict__ partial, size_t n) {
     __shared__ float sh[32];
+    constexpr int VEC = 16 / sizeof(T);
     float s = 0.f;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t nvec = n / VEC;
+    const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t v = tid; v < nvec; v += stride) {
+        if constexpr (sizeof(T) == 2) {
+            float a[8];
+            load8(reinterpret_cast<const bf16*>(x) + v * 8, a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += a[i] * a[i];
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(x + v * 4);
+            s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    for (size_t i = nvec * VEC + tid; i < n; i += stride) {
         float v;
         if constexpr (sizeof(T) == 2) v = __bfloat162float(x[i]); else v = x[i];
         s += v * v;
@@ -479,65 +494,122 @@ template <typename T> __global__ void __launch_bounds__(512) sumsq_kernel(const 
 
 // ------------------------------------------------------------------------------------------ AdamW
 // hp (device): [lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale] so a captured graph can be replayed.
+// Every thread owns 8 consecutive elements (n must be a multiple of 8; shards are multiples of 128).
+template <typename T> __device__ __forceinline__ void load8_any(const T* p, float (&f)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        load8(reinterpret_cast<const bf16*>(p), f);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+}
+template <typename T> __device__ __forceinline__ void store8_any(T* p, const float (&f)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        store8(reinterpret_cast<bf16*>(p), f);
+    } else {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
 template <typename P, typename G>
 __global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, const G* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                                                          const uint8_t* __restrict__ decay_mask, const float* __restrict__ hp, size_t n) {
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float gv, pv;
-        if constexpr (sizeof(G) == 2) gv = __bfloat162float(g[i]); else gv = g[i];
-        if constexpr (sizeof(P) == 2) pv = __bfloat162float(p[i]); else pv = p[i];
-        gv *= gs;
-        const float mi = b1 * m[i] + (1.f - b1) * gv;
-        const float vi = b2 * v[i] + (1.f - b2) * gv * gv;
-        m[i] = mi;
-        v[i] = vi;
-        const float dec = (decay_mask && decay_mask[i]) ? wd : 0.f;
-        pv = pv * (1.f - lr * dec) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-        if constexpr (sizeof(P) == 2) p[i] = __float2bfloat16_rn(pv); else p[i] = pv;
+    const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+    const size_t nvec = n / 8;
+    for (size_t vi = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; vi < nvec; vi += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t i = vi * 8;
+        float pv[8], gv[8], mv[8], vv[8];
+        load8_any(p + i, pv);
+        load8_any(g + i, gv);
+        load8_any(m + i, mv);
+        load8_any(v + i, vv);
+        uint2 mk = make_uint2(0, 0);
+        if (decay_mask) mk = *reinterpret_cast<const uint2*>(decay_mask + i);
+        const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float gk = gv[k] * gs;
+            mv[k] = b1 * mv[k] + (1.f - b1) * gk;
+            vv[k] = b2 * vv[k] + (1.f - b2) * gk * gk;
+            const float dec = mb[k] ? wd : 0.f;
+            pv[k] = pv[k] * (1.f - lr * dec) - lr * (mv[k] * ibc1) / (sqrtf(vv[k] * ibc2) + eps);
+        }
+        store8_any(m + i, mv);
+        store8_any(v + i, vv);
+        store8_any(p + i, pv);
     }
 }
 
 // 8-bit state: momentum int8 through softsign (2x/(1+|x|) of the group-normalised value), variance uint8 of sqrt(v),
-// groups of 32 with fp16 scales.  One warp handles one group per iteration (lane = element) so the group abs-max is a shuffle.
+// groups of 32 with fp16 scales.  Four adjacent lanes (8 elements each) form one group; the group abs-max is two shuffles.
+// n must be a multiple of 32.
 template <typename P, typename G>
 __global__ void __launch_bounds__(256) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
                                                          __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
                                                          const float* __restrict__ hp, size_t n) {
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
-    const int lane = threadIdx.x & 31;
-    const size_t ngroups = (n + 31) / 32;
-    const size_t warps_total = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
-    for (size_t grp = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); grp < ngroups; grp += warps_total) {
-        const size_t i = grp * 32 + lane;
-        const bool live = i < n;
-        float gv = 0.f, pv = 0.f, mi = 0.f, vi = 0.f;
+    const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+    const size_t nvec = n / 8;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    // warp-uniform trip count so the shuffles always see all 32 lanes
+    for (size_t base = blockIdx.x * static_cast<size_t>(blockDim.x) + (threadIdx.x & ~31); base < nvec; base += stride) {
+        const size_t vi = base + (threadIdx.x & 31);
+        const bool live = vi < nvec;
+        const size_t i = vi * 8, grp = vi >> 2;
+        float pv[8], gv[8], mv[8], sv[8];
+        float am = 0.f, av = 0.f;
         if (live) {
-            if constexpr (sizeof(G) == 2) gv = __bfloat162float(g[i]); else gv = g[i];
-            if constexpr (sizeof(P) == 2) pv = __bfloat162float(p[i]); else pv = p[i];
-            gv *= gs;
-            const float y = static_cast<float>(m8[i]) * (1.f / 127.f);
-            mi = y / (2.f - fabsf(y)) * __half2float(ms[grp]);
-            const float sq = static_cast<float>(v8[i]) * (1.f / 255.f) * __half2float(vs[grp]);
-            vi = sq * sq;
-            mi = b1 * mi + (1.f - b1) * gv;
-            vi = b2 * vi + (1.f - b2) * gv * gv;
-            const float dec = (decay_mask && decay_mask[i]) ? wd : 0.f;
-            pv = pv * (1.f - lr * dec) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-            if constexpr (sizeof(P) == 2) p[i] = __float2bfloat16_rn(pv); else p[i] = pv;
+            load8_any(p + i, pv);
+            load8_any(g + i, gv);
+            const uint2 mraw = *reinterpret_cast<const uint2*>(m8 + i), vraw = *reinterpret_cast<const uint2*>(v8 + i);
+            const int8_t* mq = reinterpret_cast<const int8_t*>(&mraw);
+            const uint8_t* vq = reinterpret_cast<const uint8_t*>(&vraw);
+            uint2 mk = make_uint2(0, 0);
+            if (decay_mask) mk = *reinterpret_cast<const uint2*>(decay_mask + i);
+            const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk);
+            const float sm = __half2float(ms[grp]), sq = __half2float(vs[grp]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float gk = gv[k] * gs;
+                const float y = static_cast<float>(mq[k]) * (1.f / 127.f);
+                float mi = y / (2.f - fabsf(y)) * sm;
+                const float r = static_cast<float>(vq[k]) * (1.f / 255.f) * sq;
+                float vi2 = r * r;
+                mi = b1 * mi + (1.f - b1) * gk;
+                vi2 = b2 * vi2 + (1.f - b2) * gk * gk;
+                const float dec = mb[k] ? wd : 0.f;
+                pv[k] = pv[k] * (1.f - lr * dec) - lr * (mi * ibc1) / (sqrtf(vi2 * ibc2) + eps);
+                mv[k] = mi;
+                sv[k] = sqrtf(vi2);
+                am = fmaxf(am, fabsf(mi));
+                av = fmaxf(av, sv[k]);
+            }
+            store8_any(p + i, pv);
         }
-        const float sv = sqrtf(vi);
-        // fp16 scales: round up so the normalised values stay within [-1, 1]
-        float am = fmaxf(warp_max(fabsf(mi)), 1e-30f), av = fmaxf(warp_max(sv), 1e-30f);
-        __half hm = __float2half_ru(am), hv = __float2half_ru(av);
-        am = fmaxf(__half2float(hm), 6e-8f);
-        av = fmaxf(__half2float(hv), 6e-8f);
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 1));
+        av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
         if (live) {
-            const float xn = mi / am;
-            m8[i] = static_cast<int8_t>(__float2int_rn(2.f * xn / (1.f + fabsf(xn)) * 127.f));
-            v8[i] = static_cast<uint8_t>(min(255, __float2int_rn(sv / av * 255.f)));
+            // fp16 scales rounded up so normalised values stay within [-1, 1]
+            const __half hm = __float2half_ru(fmaxf(am, 1e-30f)), hv = __float2half_ru(fmaxf(av, 1e-30f));
+            const float fm = fmaxf(__half2float(hm), 6e-8f), fv = fmaxf(__half2float(hv), 6e-8f);
+            const float im = 1.f / fm, iv = 255.f / fv;
+            uint2 mo, vo;
+            int8_t* mq = reinterpret_cast<int8_t*>(&mo);
+            uint8_t* vq = reinterpret_cast<uint8_t*>(&vo);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float xn = mv[k] * im;
+                mq[k] = static_cast<int8_t>(__float2int_rn(2.f * xn / (1.f + fabsf(xn)) * 127.f));
+                vq[k] = static_cast<uint8_t>(min(255, __float2int_rn(sv[k] * iv)));
+            }
+            *reinterpret_cast<uint2*>(m8 + i) = mo;
+            *reinterpret_cast<uint2*>(v8 + i) = vo;
+            if ((threadIdx.x & 3) == 0) { ms[grp] = __float2half(fm); vs[grp] = __float2half(fv); }
         }
-        if (lane == 0) { ms[grp] = __float2half(am); vs[grp] = __float2half(av); }
     }
 }
 
@@ -609,7 +681,7 @@ void sumsq(const void* x, int is_fp32, float* partial, int nblocks, size_t n, cu
 }
 void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float* v, const uint8_t* mask, const float* hp, size_t n, int num_sms,
                 cudaStream_t s) {
-    const int grid = grid_for(n, 256, num_sms);
+    const int grid = grid_for(n / 8, 256, num_sms);
     if (p_fp32 && g_fp32) adamw_fp32_kernel<float, float><<<grid, 256, 0, s>>>((float*)p, (const float*)g, m, v, mask, hp, n);
     else if (p_fp32) adamw_fp32_kernel<float, bf16><<<grid, 256, 0, s>>>((float*)p, (const bf16*)g, m, v, mask, hp, n);
     else if (g_fp32) adamw_fp32_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, m, v, mask, hp, n);
@@ -617,7 +689,7 @@ void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float*
 }
 void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, const float* hp,
                 size_t n, int num_sms, cudaStream_t s) {
-    const int grid = grid_for(n, 256, num_sms);
+    const int grid = grid_for(n / 8, 256, num_sms);
     if (p_fp32 && g_fp32) adamw_8bit_kernel<float, float><<<grid, 256, 0, s>>>((float*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
     else if (p_fp32) adamw_8bit_kernel<float, bf16><<<grid, 256, 0, s>>>((float*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
     else if (g_fp32) adamw_8bit_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);

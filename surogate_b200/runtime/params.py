@@ -60,6 +60,7 @@ class Bucket:
         self.grad_shard: Optional[torch.Tensor] = None  # [shard_numel] reduced gradient owned by this rank
         self.gather_work: Any = None
         self.reduce_work: Any = None
+        self.grad_persistent = False  # gradient buffer lives in the symmetric arena for the whole run
         self.written: set = set()
         self.trainable = True
         self.decay_mask_cache: Optional[torch.Tensor] = None
@@ -134,7 +135,29 @@ class ParamStore:
             b.numel = (b.numel + quantum - 1) // quantum * quantum
             b.shard_numel = b.numel // self.world if self.sharded else b.numel
             b.trainable = any(s.trainable for s in b.slots)
-            b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, device=self.device)
+        # Peer-addressable placement: when the communicator runs its own kernels over symmetric memory, master shards
+        # and bucket-sized gradient buffers live in one arena so that peers can load them directly.
+        self.arena = None
+        self.fused_sumsq = None
+        self.sumsq_valid = False
+        self.micro_total = 1
+        if hasattr(self.comm, "create_arena") and self.sharded and self.master_dtype == torch.bfloat16 and self.grad_dtype == torch.bfloat16:
+            need = 0
+            for b in self.buckets.values():
+                need += (b.shard_numel * 2 + 255) // 256 * 256 + 256
+                if b.trainable:
+                    need += (b.numel * 2 + 255) // 256 * 256 + 256
+            self.arena = self.comm.create_arena(need)
+            self.arena.tensor.zero_()
+            self.fused_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for b in self.buckets.values():
+            if self.arena is not None:
+                b.master = self.arena.take(b.shard_numel, self.master_dtype)
+                if b.trainable:
+                    b.grad = self.arena.take(b.numel, self.grad_dtype)
+                    b.grad_persistent = True
+            else:
+                b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, device=self.device)
             if not self.sharded and self.master_dtype == self.param_dtype:
                 b.work = b.master
             elif self.zero_level < 3:
@@ -285,10 +308,14 @@ class ParamStore:
         for b in self.buckets.values():
             b.written.clear()
         self.first_micro_step = True
+        if self.fused_sumsq is not None:
+            self.fused_sumsq.zero_()
+            self.sumsq_valid = True
 
     def begin_micro_step(self, index: int, total: int) -> None:
         self.first_micro_step = index == 0
         self.last_micro_step = index == total - 1
+        self.micro_total = total
         if self.zero_level >= 2:
             for b in self.buckets.values():
                 b.written.clear()
@@ -311,31 +338,44 @@ class ParamStore:
         if b.grad is None or not b.trainable:
             return
         for s in b.slots:  # parameters that received no gradient this micro-step contribute zeros
-            if s.trainable and s.name not in b.written and self.zero_level >= 2:
+            if s.trainable and s.name not in b.written and (self.zero_level >= 2 or b.grad_persistent):
                 b.grad[s.offset:s.offset + s.numel].zero_()
         if self.world == 1:
             b.grad_shard = b.grad
             return
         if self.zero_level == 0:
+            self.sumsq_valid = False
             if self.last_micro_step:
-                b.reduce_work = self.comm.all_reduce(b.grad, op="avg", async_op=True)
+                b.reduce_work = self.comm.all_reduce(b.grad, op="sum", async_op=True)  # loss is normalised by the global token count
                 b.grad_shard = b.grad
             return
-        if self.zero_level == 1:
+        if self.zero_level == 1 or self.micro_total == 1:
+            # one reduction per bucket per step: asynchronous, overlapped with the rest of backward, and (with the
+            # peer-memory kernels) fused with the sum of squares for the gradient norm
             if self.last_micro_step:
                 b.grad_shard = torch.empty(b.shard_numel, dtype=self.grad_dtype, device=self.device)
-                b.reduce_work = self.comm.reduce_scatter(b.grad, b.grad_shard, async_op=True)
+                b.reduce_work = self._reduce_scatter(b.grad, b.grad_shard)
+                if not b.grad_persistent and self.zero_level >= 2:
+                    b.grad = None
             return
-        # level 2/3: reduce-scatter every micro-step into an fp32 accumulator; the full buffer is transient
+        # level 2/3 with gradient accumulation: reduce-scatter every micro-step into an fp32 accumulator
+        self.sumsq_valid = False
         tmp = torch.empty(b.shard_numel, dtype=self.grad_dtype, device=self.device)
         w = self.comm.reduce_scatter(b.grad, tmp, async_op=True)
         if w is not None:
             w.wait()
         if b.grad_shard is None or self.first_micro_step:
-            b.grad_shard = tmp.float() if not self.last_micro_step else tmp
+            b.grad_shard = tmp.float()
         else:
             b.grad_shard = b.grad_shard + tmp.float()
-        b.grad = None
+        if not b.grad_persistent:
+            b.grad = None
+
+    def _reduce_scatter(self, full: torch.Tensor, shard: torch.Tensor):
+        if self.fused_sumsq is not None and self.arena.offset_of(full) is not None:
+            return self.comm.reduce_scatter(full, shard, async_op=True, sumsq_out=self.fused_sumsq)
+        self.sumsq_valid = False
+        return self.comm.reduce_scatter(full, shard, async_op=True)
 
     def finish_reduce(self) -> None:
         for b in self.buckets.values():
@@ -378,7 +418,7 @@ class ParamStore:
         for b in self.buckets.values():
             if self.zero_level >= 1:
                 b.grad_shard = None
-            if self.zero_level >= 2:
+            if self.zero_level >= 2 and not b.grad_persistent:
                 b.grad = None
 
     def memory_breakdown(self) -> Dict[str, int]:

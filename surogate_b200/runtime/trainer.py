@@ -100,12 +100,12 @@ class Trainer:
 
             self.lora = LoRAManager(self.cm, cfg.lora, device=self.device, comm=self.comm, dtype=pd)
             frozen = self.lora.freezes
-        self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
-                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen)
-        if cfg.collectives in ("auto", "symm") and on_gpu and self.world > 1:
+        if cfg.collectives in ("auto", "symm") and on_gpu and self.world > 1 and cfg.zero_level >= 1:
             from ..parallel import symm
 
-            symm.maybe_enable(self.store, self.comm, required=cfg.collectives == "symm")
+            self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
+        self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
+                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen)
         from .ops_cuda import make_backend
 
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
@@ -239,8 +239,13 @@ class Trainer:
 
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of the (already reduced) gradients, as a device scalar."""
-        total = torch.zeros((), dtype=torch.float32, device=self.device)
         on_gpu = self.device.type == "cuda" and self.backend.name == "cuda"
+        if self.store.fused_sumsq is not None and self.store.sumsq_valid and self.lora is None:
+            # the reduce-scatter kernels already accumulated this rank's shard norms
+            total = self.store.fused_sumsq.clone().reshape(())
+            self.comm.all_reduce(total, "sum")
+            return total.sqrt()
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
         for b in self.store.trainable_buckets():
             g = b.grad_shard
             if g is None:
@@ -264,12 +269,17 @@ class Trainer:
         hp_cpu = torch.tensor(list(host) + [1.0], dtype=torch.float32)
         self._hp.copy_(hp_cpu, non_blocking=True)
         self._hp[7] = clip
+        fence = getattr(self.comm, "fence", None)
+        if fence is not None:
+            fence()  # every rank has finished reading master shards / gradient buckets of this step
         for b in self.store.trainable_buckets():
             if b.grad_shard is None:
                 continue
             self.optimizer.step_bucket(b, b.grad_shard, self._hp, host)
         if self.lora is not None:
             self.lora.optimizer_step(self._hp, host)
+        if fence is not None:
+            fence()  # every rank's master shards are updated before anyone gathers them
         self.store.release_grads()
         self.store.sync_work_from_master()
         self.recipe.on_weights_updated(self.store)

@@ -1,0 +1,61 @@
+"""Worker for multi-process tests: trains a tiny model for a few steps and prints one JSON line from rank 0.
+
+Launched with ``python -m torch.distributed.run --nproc-per-node N tests/mp_worker.py <json-args>`` (or directly for N=1).
+Every rank sees the same global batch and takes its slice, so runs at different world sizes are comparable.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from surogate_b200.parallel.dist import TorchComm, init_distributed  # noqa: E402
+from surogate_b200.runtime.trainer import Trainer, TrainerConfig  # noqa: E402
+
+
+def main():
+    a = json.loads(sys.argv[1]) if len(sys.argv) > 1 else {}
+    use_gpu = a.get("device", "cuda") == "cuda" and torch.cuda.is_available()
+    info = init_distributed(backend="nccl" if use_gpu else "gloo", timeout_s=a.get("timeout_s", 120))
+    dev = torch.device("cuda", info.local_rank) if use_gpu else torch.device("cpu")
+    if use_gpu:
+        torch.cuda.set_device(dev)
+    comm = TorchComm() if info.world > 1 else None
+    gb, T = a.get("global_batch", 4), a.get("seq_len", 128)
+    model = a.get("model") or dict(architecture="Qwen3ForCausalLM", vocab_size=1024, d_model=256, n_layers=2, num_query_heads=2,
+                                   num_kv_heads=1, head_size=128, d_ff=512, tie_word_embeddings=True)
+    cfg = TrainerConfig(model=model, batch_size=gb // info.world // a.get("grad_accum", 1), seq_len=T, grad_accum=a.get("grad_accum", 1),
+                        recipe=a.get("recipe", "bf16"), optimizer=a.get("optimizer", "adamw"), learning_rate=1e-3, zero_level=a.get("zero", 1),
+                        collectives=a.get("collectives", "auto"), keep_gathered=a.get("keep_gathered", True), ep_size=a.get("ep", 1),
+                        lora=a.get("lora"))
+    tr = Trainer(cfg, device=dev, comm=comm)
+    tr.init_weights(seed=0)
+    rng = np.random.default_rng(7)
+    V = model["vocab_size"]
+    losses, norms = [], []
+    per_rank = gb // info.world
+    for step in range(a.get("steps", 4)):
+        tok = rng.integers(0, V, (gb, T + 1)).astype(np.int32)
+        x, y = tok[:, :-1], tok[:, 1:]
+        sl = slice(info.rank * per_rank, (info.rank + 1) * per_rank)
+        out = tr.step(x[sl], y[sl])
+        losses.append(out["loss"])
+        norms.append(out["norm"])
+    extra = {}
+    if a.get("checkpoint_dir"):
+        tr.save_checkpoint(a["checkpoint_dir"], step=len(losses))
+    if info.rank == 0:
+        print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "comm": type(tr.comm).__name__,
+                                      "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid), **extra}), flush=True)
+    if info.world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -211,7 +211,7 @@ def test_quantize_fp8_and_sumsq(ext):
 
 
 def test_adamw_kernels(ext):
-    n = 100000
+    n = 100000 - 100000 % 32
     p = torch.randn(n, device=DEV)
     g = torch.randn(n, device=DEV) * 0.1
     mask = (torch.arange(n, device=DEV) % 3 != 0).to(torch.uint8)
