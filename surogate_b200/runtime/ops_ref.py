@@ -133,6 +133,8 @@ class RefOps:
         y = ctx.recipe.forward_matmul(ctx, op, x, w, bias) if ctx.recipe is not None else None
         if y is None:
             y = TF.linear(x, w.to(x.dtype), bias.to(x.dtype) if bias is not None else None)
+        if ctx.lora is not None:
+            y = ctx.lora.forward(ctx, op, x, y)
         return (y,)
 
     def matmul_backward(self, ctx, op, dy, x, w):
@@ -145,6 +147,10 @@ class RefOps:
         else:
             dx = dy2 @ w.to(dy.dtype)
             dw = self._wgrad(ctx, op.outputs[1], dy2, x2)
+        if ctx.lora is not None:
+            extra = ctx.lora.backward(ctx, op, dy2, x2)
+            if extra is not None:
+                dx = dx + extra
         db = None
         if op.outputs[2] is not None:
             db = dy2.float().sum(0)

@@ -84,5 +84,5 @@ def model_loss(p, tokens, pos, targets, cfg):
     x = rms(x, p["final_norm"], cfg["eps"])
     w = p["lm_head"] if "lm_head" in p else p["embedding"]
     logits = x @ w.t()
-    loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.view(-1).long(), ignore_index=-100, reduction="sum")
+    loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1).long(), ignore_index=-100, reduction="sum")
     return loss, aux_total
