@@ -225,6 +225,9 @@ class ParamStore:
 
     def sync_work_from_master(self) -> None:
         """Refresh the gathered work weights after the masters changed (init, load, optimizer step)."""
+        fence = getattr(self.comm, "fence", None)
+        if fence is not None and self.sharded:
+            fence()  # peers pull master shards directly: every rank must have finished writing its own first
         for b in self.buckets.values():
             if self.zero_level >= 3:
                 b.work = None

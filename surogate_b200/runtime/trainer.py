@@ -243,6 +243,10 @@ class Trainer:
         if self.store.fused_sumsq is not None and self.store.sumsq_valid and self.lora is None:
             # the reduce-scatter kernels already accumulated this rank's shard norms
             total = self.store.fused_sumsq.clone().reshape(())
+            if os.environ.get("SUROGATE_CHECK_FUSED_NORM") == "1":  # self-check: recompute from the reduced shards
+                ref = sum(self.backend.ext.sumsq(b.grad_shard) for b in self.store.trainable_buckets() if b.grad_shard is not None)
+                if abs(float(ref) - float(total)) > 1e-2 * abs(float(ref)):
+                    raise RuntimeError(f"fused gradient norm mismatch on rank {self.rank}: fused {float(total)} vs recomputed {float(ref)}")
             self.comm.all_reduce(total, "sum")
             return total.sqrt()
         total = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -278,8 +282,6 @@ class Trainer:
             self.optimizer.step_bucket(b, b.grad_shard, self._hp, host)
         if self.lora is not None:
             self.lora.optimizer_step(self._hp, host)
-        if fence is not None:
-            fence()  # every rank's master shards are updated before anyone gathers them
         self.store.release_grads()
         self.store.sync_work_from_master()
         self.recipe.on_weights_updated(self.store)
