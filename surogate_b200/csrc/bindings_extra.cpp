@@ -4,6 +4,8 @@
 #include <torch/extension.h>
 
 #include "comm_kernels.h"
+#include "gemm_sm100.h"
+#include "moe_kernels.h"
 #include "ext_api.h"
 
 namespace {
@@ -79,6 +81,134 @@ void all_reduce_small(const std::vector<int64_t>& arenas, const std::vector<int6
                          static_cast<int>(slot_base), error_flag.data_ptr<int>(), budget_s, cur_stream());
 }
 
+
+int sms() {
+    static int n = 0;
+    if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    return n;
+}
+
+// ---------------------------------------------------------------------------------------- MoE
+// logits fp32 [tokens, E] -> (topk weights fp32 [tokens, K], topk index int32 [tokens, K]); counts / prob_sum / lse_sq are accumulated.
+std::vector<Tensor> moe_softmax_topk(const Tensor& logits, int64_t K, bool renorm, Tensor& counts, Tensor& prob_sum, const c10::optional<Tensor>& lse_sq,
+                                     bool want_probs) {
+    TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2, "logits: fp32 [tokens, E]");
+    const int tokens = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+    TORCH_CHECK(E <= 256 && K <= 16 && K <= E, "moe_softmax_topk supports E <= 256, K <= 16");
+    TORCH_CHECK(counts.scalar_type() == at::kInt && counts.numel() == E && prob_sum.scalar_type() == at::kFloat && prob_sum.numel() == E, "counts/prob_sum [E]");
+    const c10::cuda::CUDAGuard guard(logits.device());
+    Tensor w = torch::empty({tokens, K}, logits.options());
+    Tensor idx = torch::empty({tokens, K}, logits.options().dtype(at::kInt));
+    Tensor probs;
+    if (want_probs) probs = torch::empty_like(logits);
+    float* lse = (lse_sq.has_value() && lse_sq->defined()) ? lse_sq->data_ptr<float>() : nullptr;
+    sg_count_launch(1);
+    sg::moe_softmax_topk(logits.data_ptr<float>(), w.data_ptr<float>(), idx.data_ptr<int>(), want_probs ? probs.data_ptr<float>() : nullptr,
+                         counts.data_ptr<int>(), prob_sum.data_ptr<float>(), lse, tokens, E, static_cast<int>(K), renorm, sms(), cur_stream());
+    return {w, idx, probs};
+}
+
+// counts int32 [E_local] -> padded offsets int32 [E_local + 1]; cursors zeroed.
+void moe_offsets(const Tensor& counts, Tensor& offsets, Tensor& cursors, int64_t capacity_rows, Tensor& error_flag) {
+    const int E = static_cast<int>(counts.numel());
+    TORCH_CHECK(E <= 256 && offsets.numel() == E + 1 && cursors.numel() >= E, "moe_offsets: E <= 256");
+    sg_count_launch(1);
+    sg::moe_offsets(counts.data_ptr<int>(), offsets.data_ptr<int>(), cursors.data_ptr<int>(), E, static_cast<int>(capacity_rows),
+                    error_flag.data_ptr<int>(), cur_stream());
+}
+
+void moe_permute(const Tensor& x, const Tensor& topk_idx, const Tensor& offsets, Tensor& cursors, Tensor& row_map, Tensor& xp, int64_t expert_base,
+                 int64_t num_local) {
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && xp.scalar_type() == at::kBFloat16 && xp.is_contiguous(), "bf16 contiguous");
+    const int C = static_cast<int>(x.size(-1));
+    const int tokens = static_cast<int>(x.numel() / C), K = static_cast<int>(topk_idx.size(-1));
+    TORCH_CHECK(C % 8 == 0 && K <= 16 && row_map.numel() == static_cast<int64_t>(tokens) * K, "moe_permute shapes");
+    sg_count_launch(1);
+    sg::moe_permute(x.data_ptr(), topk_idx.data_ptr<int>(), offsets.data_ptr<int>(), cursors.data_ptr<int>(), row_map.data_ptr<int>(), xp.data_ptr(),
+                    tokens, C, K, static_cast<int>(expert_base), static_cast<int>(num_local), static_cast<int>(xp.size(0)), cur_stream());
+}
+
+Tensor moe_unpermute(const Tensor& yp, const c10::optional<Tensor>& w, const Tensor& row_map, int64_t tokens, int64_t K) {
+    TORCH_CHECK(yp.scalar_type() == at::kBFloat16 && yp.is_contiguous(), "yp: bf16 contiguous");
+    const int C = static_cast<int>(yp.size(-1));
+    Tensor y = torch::empty({tokens, C}, yp.options());
+    const float* wp = (w.has_value() && w->defined()) ? w->data_ptr<float>() : nullptr;
+    sg_count_launch(1);
+    sg::moe_unpermute(yp.data_ptr(), wp, row_map.data_ptr<int>(), y.data_ptr(), static_cast<int>(tokens), C, static_cast<int>(K), cur_stream());
+    return y;
+}
+
+std::vector<Tensor> moe_unpermute_bwd(const Tensor& dy, const Tensor& yp, const Tensor& w, const Tensor& row_map) {
+    TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && yp.is_contiguous(), "bf16 contiguous");
+    const int C = static_cast<int>(yp.size(-1));
+    const int tokens = static_cast<int>(dy.numel() / C), K = static_cast<int>(w.size(-1));
+    Tensor d_yp = torch::zeros_like(yp);
+    Tensor d_w = torch::empty_like(w);
+    sg_count_launch(1);
+    sg::moe_unpermute_bwd(dy.data_ptr(), yp.data_ptr(), w.data_ptr<float>(), row_map.data_ptr<int>(), d_yp.data_ptr(), d_w.data_ptr<float>(), tokens, C, K,
+                          cur_stream());
+    return {d_yp, d_w};
+}
+
+// Grouped GEMM (see gemm_sm100.h).  mode 1: a [R, K] (rows grouped), b = weights [G, N, K] (b_mn=false) or [G, K, N]-as-stored
+// [G, Kc, N] (b_mn=true, contraction Kc); d [R, N].  mode 2: a [R, M], b [R, N] (both MN-major), d [G, M, N].
+void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& d, const Tensor& offsets, int64_t mode, bool b_mn, bool accumulate, double alpha,
+                  const c10::optional<Tensor>& scale_a, const c10::optional<Tensor>& scale_b, Tensor& error_flag) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda() && a.is_contiguous() && b.is_contiguous() && d.is_contiguous(), "contiguous CUDA tensors");
+    TORCH_CHECK(a.element_size() == b.element_size() && (a.element_size() == 2 || a.element_size() == 1), "bf16 or fp8 operands");
+    TORCH_CHECK(offsets.scalar_type() == at::kInt && offsets.is_cuda(), "offsets: CUDA int32");
+    const c10::cuda::CUDAGuard guard(a.device());
+    const int es = static_cast<int>(a.element_size());
+    auto fmt = [&](const Tensor& t) { return es == 2 ? 1 : (t.scalar_type() == at::kFloat8_e5m2 ? 1 : 0); };
+    sg::GemmParams p{};
+    p.elem_bytes = es;
+    p.a_fmt = fmt(a);
+    p.b_fmt = fmt(b);
+    p.mode = static_cast<int>(mode);
+    p.num_groups = static_cast<int>(offsets.numel() - 1);
+    p.group_offsets = offsets.data_ptr<int>();
+    p.D = d.data_ptr();
+    p.out_fp32 = d.scalar_type() == at::kFloat;
+    p.accumulate = accumulate;
+    p.alpha = static_cast<float>(alpha);
+    p.scale_a = (scale_a.has_value() && scale_a->defined()) ? scale_a->data_ptr<float>() : nullptr;
+    p.scale_b = (scale_b.has_value() && scale_b->defined()) ? scale_b->data_ptr<float>() : nullptr;
+    p.error_flag = error_flag.data_ptr<int>();
+    p.tile_n = 0;
+    sg::GemmOperand A{a.data_ptr(), 0}, B{b.data_ptr(), 0};
+    if (mode == 1) {
+        TORCH_CHECK(a.dim() == 2 && b.dim() == 3 && d.dim() == 2 && b.size(0) == p.num_groups, "mode 1: a [R,K], b [G,*,*], d [R,N]");
+        p.a_mn = 0;
+        p.b_mn = b_mn;
+        p.K = static_cast<int>(a.size(1));
+        p.N = static_cast<int>(b_mn ? b.size(2) : b.size(1));
+        TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == p.K, "mode 1: contraction mismatch");
+        p.M = static_cast<int>(a.size(0));
+        TORCH_CHECK(d.size(0) == a.size(0) && d.size(1) == p.N, "mode 1: d must be [R, N]");
+        p.a_total_rows = a.size(0);
+        p.b_total_rows = b.size(0) * b.size(1);
+        A.row_stride_bytes = static_cast<uint64_t>(p.K) * es;
+        B.row_stride_bytes = static_cast<uint64_t>(b.size(2)) * es;
+        p.ldd = p.N;
+    } else {
+        TORCH_CHECK(mode == 2 && a.dim() == 2 && b.dim() == 2 && d.dim() == 3 && d.size(0) == p.num_groups && a.size(0) == b.size(0), "mode 2 shapes");
+        p.a_mn = 1;
+        p.b_mn = 1;
+        p.M = static_cast<int>(a.size(1));
+        p.N = static_cast<int>(b.size(1));
+        p.K = 1;
+        TORCH_CHECK(d.size(1) == p.M && d.size(2) == p.N, "mode 2: d must be [G, M, N]");
+        p.a_total_rows = a.size(0);
+        p.b_total_rows = b.size(0);
+        A.row_stride_bytes = static_cast<uint64_t>(p.M) * es;
+        B.row_stride_bytes = static_cast<uint64_t>(p.N) * es;
+        p.ldd = p.N;
+    }
+    sg_count_launch(1);
+    const char* err = sg::gemm_sm100(A, B, p, sms(), cur_stream());
+    TORCH_CHECK(err == nullptr, err ? err : "");
+}
+
 }  // namespace
 
 void sg_register_extra(pybind11::module_& m) {
@@ -87,4 +217,10 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("reduce_scatter_multimem", &reduce_scatter_multimem);
     m.def("all_gather_fused", &all_gather_fused);
     m.def("all_reduce_small", &all_reduce_small);
+    m.def("moe_softmax_topk", &moe_softmax_topk);
+    m.def("moe_offsets", &moe_offsets);
+    m.def("moe_permute", &moe_permute);
+    m.def("moe_unpermute", &moe_unpermute);
+    m.def("moe_unpermute_bwd", &moe_unpermute_bwd);
+    m.def("gemm_grouped", &gemm_grouped);
 }

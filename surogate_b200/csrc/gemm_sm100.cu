@@ -33,15 +33,83 @@ template <int BN> struct Cfg {
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-    const int per_group = GROUP_M * num_n;
-    const int group = tile / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(num_m - first_m, GROUP_M);
-    const int r = tile - group * per_group;
-    m_blk = first_m + r % gsize;
-    n_blk = r / gsize;
+// What one output tile needs to know.  Coordinates are TMA coordinates (elements).
+struct TileInfo {
+    int a_row0;   // A: row (K-major) or M-column (MN-major) coordinate of the tile
+    int b_row0;   // B: row (K-major) or N-column (MN-major) coordinate of the tile
+    int a_k0;     // first contraction coordinate in A
+    int b_k0;     // first contraction coordinate in B
+    int num_k;    // contraction blocks
+    int d_row0, d_col0;   // output tile origin
+    int m_end, n_end;     // exclusive store limits
+    long long d_off;      // element offset of this tile's output matrix inside D
+};
+
+// Tile schedules.  mode 0: one dense problem.  mode 1: rows of A / D are grouped (MoE forward and dgrad): group g owns rows
+// [offs[g], offs[g+1]) (multiples of 128) and uses B block g.  mode 2: the contraction is grouped (MoE wgrad): group g
+// contracts rows [offs[g], offs[g+1]) of both operands into output matrix g.
+__device__ __forceinline__ int find_group(const int* tile_start, int num_groups, int tile) {
+    int lo = 0, hi = num_groups;  // largest g with tile_start[g] <= tile
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_start[mid] <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
 }
+
+template <int BN>
+__device__ __forceinline__ TileInfo get_tile(const GemmParams& p, const int* tile_start, int tile, int BK) {
+    TileInfo t;
+    const int num_n = (p.N + BN - 1) / BN;
+    if (p.mode == 0) {
+        const int num_m = (p.M + BM - 1) / BM;
+        const int per_group = GROUP_M * num_n;
+        const int group = tile / per_group;
+        const int first_m = group * GROUP_M;
+        const int gsize = min(num_m - first_m, GROUP_M);
+        const int r = tile - group * per_group;
+        const int m_blk = first_m + r % gsize, n_blk = r / gsize;
+        t.a_row0 = t.d_row0 = m_blk * BM;
+        t.b_row0 = t.d_col0 = n_blk * BN;
+        t.a_k0 = t.b_k0 = 0;
+        t.num_k = (p.K + BK - 1) / BK;
+        t.m_end = p.M;
+        t.n_end = p.N;
+        t.d_off = 0;
+    } else if (p.mode == 1) {
+        const int g = find_group(tile_start, p.num_groups, tile);
+        const int local = tile - tile_start[g];
+        const int m_tiles = (p.group_offsets[g + 1] - p.group_offsets[g]) / BM;
+        const int m_blk = local % m_tiles, n_blk = local / m_tiles;
+        t.a_row0 = t.d_row0 = p.group_offsets[g] + m_blk * BM;
+        t.d_col0 = n_blk * BN;
+        // B block g: K-major weights are stacked on rows ([G*N, K]); MN-major weights are stacked on the contraction ([G*K, N])
+        t.b_row0 = p.b_mn ? n_blk * BN : g * p.N + n_blk * BN;
+        t.a_k0 = 0;
+        t.b_k0 = p.b_mn ? g * p.K : 0;
+        t.num_k = (p.K + BK - 1) / BK;
+        t.m_end = p.group_offsets[g + 1];
+        t.n_end = p.N;
+        t.d_off = 0;
+    } else {
+        const int num_m = (p.M + BM - 1) / BM;
+        const int per = num_m * num_n;
+        const int g = find_group(tile_start, p.num_groups, tile);
+        const int local = tile - tile_start[g];
+        const int m_blk = local % num_m, n_blk = local / num_m;
+        t.a_row0 = t.d_row0 = m_blk * BM;
+        t.b_row0 = t.d_col0 = n_blk * BN;
+        t.a_k0 = t.b_k0 = p.group_offsets[g];
+        t.num_k = (p.group_offsets[g + 1] - p.group_offsets[g]) / BK;
+        t.m_end = p.M;
+        t.n_end = p.N;
+        t.d_off = static_cast<long long>(g) * p.M * p.N;
+        (void)per;
+    }
+    return t;
+}
+
+constexpr int MAX_GROUPS = 256;
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -62,10 +130,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int lane = threadIdx.x & 31;
     const int elems_per_row = TILE_K_BYTES / p.elem_bytes;  // K elements per stage (K-major) = BK
     const int BK = elems_per_row;
-    const int num_k = (p.K + BK - 1) / BK;
-    const int num_m = (p.M + BM - 1) / BM;
-    const int num_n = (p.N + BN - 1) / BN;
-    const int num_tiles = num_m * num_n;
+    __shared__ int tile_start[MAX_GROUPS + 1];
+    __shared__ int num_tiles_sh;
+    if (p.mode == 0) {
+        if (threadIdx.x == 0) num_tiles_sh = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    } else if (threadIdx.x == 0) {
+        // prefix of tiles per group (<= 256 groups: a serial scan by one thread costs well under a microsecond)
+        const int num_n = (p.N + BN - 1) / BN;
+        int acc = 0;
+        for (int g = 0; g < p.num_groups; ++g) {
+            tile_start[g] = acc;
+            const int rows = p.group_offsets[g + 1] - p.group_offsets[g];
+            if (p.mode == 1) acc += (rows / BM) * num_n;
+            else acc += rows > 0 ? ((p.M + BM - 1) / BM) * num_n : 0;   // empty groups contribute no tiles
+        }
+        tile_start[p.num_groups] = acc;
+        num_tiles_sh = acc;
+    }
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -89,6 +170,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    const int num_tiles = num_tiles_sh;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -100,24 +182,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int chunk_bytes = BK * TILE_K_BYTES;   // MN-major chunk: BK rows of 128 B
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int m_blk, n_blk;
-                tile_coords(tile, num_m, num_n, m_blk, n_blk);
-                const int m0 = m_blk * BM, n0 = n_blk * BN;
-                for (int kb = 0; kb < num_k; ++kb) {
+                const TileInfo t = get_tile<BN>(p, tile_start, tile, BK);
+                const int m0 = t.a_row0, n0 = t.b_row0;
+                for (int kb = 0; kb < t.num_k; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) { ok = false; break; }
                     const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
                     const uint32_t sb = sa + A_STAGE_BYTES;
                     mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
-                    const int k0 = kb * BK;
+                    const int ka = t.a_k0 + kb * BK, kbb = t.b_k0 + kb * BK;
                     if (!p.a_mn) {
-                        tma_load_2d(sa, &tmA, k0, m0, full_bar(stage));
+                        tma_load_2d(sa, &tmA, ka, m0, full_bar(stage));
                     } else {
-                        for (int c = 0; c < a_chunks; ++c) tma_load_2d(sa + c * chunk_bytes, &tmA, m0 + c * elems_per_row, k0, full_bar(stage));
+                        for (int c = 0; c < a_chunks; ++c) tma_load_2d(sa + c * chunk_bytes, &tmA, m0 + c * elems_per_row, ka, full_bar(stage));
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(sb, &tmB, k0, n0, full_bar(stage));
+                        tma_load_2d(sb, &tmB, kbb, n0, full_bar(stage));
                     } else {
-                        for (int c = 0; c < b_chunks; ++c) tma_load_2d(sb + c * chunk_bytes, &tmB, n0 + c * elems_per_row, k0, full_bar(stage));
+                        for (int c = 0; c < b_chunks; ++c) tma_load_2d(sb + c * chunk_bytes, &tmB, n0 + c * elems_per_row, kbb, full_bar(stage));
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -141,6 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 acc_phase[acc] ^= 1u;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                const int num_k = get_tile<BN>(p, tile_start, tile, BK).num_k;
                 for (int kb = 0; kb < num_k; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -171,26 +253,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float amax = 0.f;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-            int m_blk, n_blk;
-            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            const TileInfo t = get_tile<BN>(p, tile_start, tile, BK);
             const int acc = local_tile & 1;
             if (!mbar_wait(tfull_bar(acc), acc_phase[acc], &abort_flag)) { ok = false; break; }
             acc_phase[acc] ^= 1u;
             tc_fence_after();
-            const int row = m_blk * BM + quad * 32 + lane;
+            const int row = t.d_row0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(t_row + c, r);
                 tmem_ld_wait();
-                const int col0 = n_blk * BN + c;
-                if (row < p.M && col0 < p.N) {
+                const int col0 = t.d_col0 + c;
+                if (row < t.m_end && col0 < t.n_end) {
                     if (p.out_fp32) {
-                        float* drow = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+                        float* drow = reinterpret_cast<float*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
-                            if (col0 + g * 4 < p.N) {
+                            if (col0 + g * 4 < t.n_end) {
                                 float4 v = make_float4(__uint_as_float(r[g * 4]) * scale, __uint_as_float(r[g * 4 + 1]) * scale,
                                                        __uint_as_float(r[g * 4 + 2]) * scale, __uint_as_float(r[g * 4 + 3]) * scale);
                                 float4* dst = reinterpret_cast<float4*>(drow + g * 4);
@@ -203,10 +284,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             }
                         }
                     } else {
-                        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+                        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
-                            if (col0 + g * 8 < p.N) {
+                            if (col0 + g * 8 < t.n_end) {
                                 float v[8];
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * scale;
@@ -291,11 +372,14 @@ template <int BN> static const char* launch(const GemmOperand& A, const GemmOper
     CUtensorMap tmA, tmB;
     const char* e;
     // K-major: inner = K, outer = rows, box {BK, rows_per_tile}.  MN-major: inner = rows, outer = K, box {128 B of rows, BK}.
-    if (!p.a_mn) e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.K, p.M, A.row_stride_bytes, BK, BM);
-    else e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.M, p.K, A.row_stride_bytes, BK, BK);
+    // Extents of the stored 2-D operands.  Grouped modes: a_rows / b_rows are the totals over all groups.
+    const uint64_t a_rows = p.mode == 0 ? (p.a_mn ? p.K : p.M) : p.a_total_rows;
+    const uint64_t b_rows = p.mode == 0 ? (p.b_mn ? p.K : p.N) : p.b_total_rows;
+    if (!p.a_mn) e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.K, a_rows, A.row_stride_bytes, BK, BM);
+    else e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.M, a_rows, A.row_stride_bytes, BK, BK);
     if (e) return e;
-    if (!p.b_mn) e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.K, p.N, B.row_stride_bytes, BK, BN);
-    else e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.N, p.K, B.row_stride_bytes, BK, BK);
+    if (!p.b_mn) e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.K, b_rows, B.row_stride_bytes, BK, BN);
+    else e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.N, b_rows, B.row_stride_bytes, BK, BK);
     if (e) return e;
     static bool attr_set = false;
     if (!attr_set) {
@@ -303,7 +387,7 @@ template <int BN> static const char* launch(const GemmOperand& A, const GemmOper
             return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
         attr_set = true;
     }
-    const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int num_tiles = p.mode == 0 ? ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) : num_sms;  // grouped: tile count lives on the device
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
     gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
     return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
@@ -311,6 +395,7 @@ template <int BN> static const char* launch(const GemmOperand& A, const GemmOper
 
 const char* gemm_sm100(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream) {
     if (p.M <= 0 || p.N <= 0 || p.K <= 0) return nullptr;
+    if (p.mode != 0 && (p.num_groups <= 0 || p.num_groups > MAX_GROUPS || !p.group_offsets)) return "gemm_sm100: grouped mode needs 1..256 groups and offsets";
     if (p.N % 8 != 0 || p.ldd % 8 != 0) return "gemm_sm100: N and ldd must be multiples of 8";
     if ((reinterpret_cast<uintptr_t>(p.D) & 15) != 0) return "gemm_sm100: D must be 16-byte aligned";
     // 128-wide N tiles when the wide tile would leave SMs idle or N is small

@@ -26,6 +26,14 @@ struct GemmParams {
     float* amax_out;       // optional: running max |D| (atomicMax on the bit pattern)
     int* error_flag;       // set to 1 if a pipeline wait ran out of budget
     int tile_n;            // 0 = auto, 128 or 256
+    // Grouped problems (MoE).  mode 0: dense.  mode 1: rows of A and D are grouped, group g = rows [offs[g], offs[g+1]) (each a
+    // multiple of 128) and multiplies weight block g (M is unused; N, K are per-group sizes).  mode 2: the contraction is grouped:
+    // output matrix g [M, N] = A[rows of g]^T . B[rows of g] (both operands MN-major, stored [total_rows, M] / [total_rows, N]).
+    int mode;
+    int num_groups;
+    const int* group_offsets;    // device, num_groups + 1 entries
+    long long a_total_rows;      // stored rows of A (grouped modes)
+    long long b_total_rows;      // stored rows of B (grouped modes)
 };
 
 const char* gemm_sm100(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream);

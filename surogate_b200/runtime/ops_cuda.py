@@ -221,6 +221,154 @@ class CudaOps(RefOps):
         return (losses.sum(),)
 
 
+class CudaMoEPlan:
+    """Device-side routing plan: padded per-expert row ranges and the row each (token, k) copy landed on."""
+
+    def __init__(self, row_map, offsets, counts, capacity, num_tokens, top_k, num_experts, x_shape):
+        self.row_map, self.offsets, self.counts, self.capacity = row_map, offsets, counts, capacity
+        self.num_tokens, self.top_k, self.num_experts, self.x_shape = num_tokens, top_k, num_experts, x_shape
+        self.local = None
+        self.ep = None
+
+
+def _moe_mixin():
+    """MoE ops of the CUDA backend (kept together; attached to CudaOps below)."""
+
+    def moe_router(self, ctx, op, x, rw):
+        a = op.attrs
+        E, K = a["num_experts"], a["top_k"]
+        if a["scoring"] != "softmax" or x.dtype != torch.bfloat16 or E > 256:
+            return RefOps.moe_router(self, ctx, op, x, rw)
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        N = x2.shape[0]
+        logits = gemm(x2, rw, out_dtype=torch.float32)
+        counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+        psum = torch.zeros(E, dtype=torch.float32, device=x.device)
+        lse_sq = torch.zeros(1, dtype=torch.float32, device=x.device) if a.get("z_loss_coef", 0.0) else None
+        tw, ti, _ = self.ext.moe_softmax_topk(logits, K, bool(a["norm_topk_prob"]), counts, psum, lse_sq, False)
+        aux = a["aux_loss_coef"] * E * ((counts.float() / N) * (psum / N)).sum()
+        if lse_sq is not None:
+            aux = aux + a["z_loss_coef"] * lse_sq[0] / N
+        ctx.stash[("moe_counts", ctx.layer, ctx.phase)] = counts
+        ctx.record_moe_stats(counts.float(), (psum / N).unsqueeze(0))
+        lead = x.shape[:-1]
+        return tw.reshape(*lead, K), ti.reshape(*lead, K), aux
+
+    def moe_router_backward(self, ctx, op, d_tw, d_aux, x, rw, tw, ti):
+        a = op.attrs
+        if a["scoring"] != "softmax" or x.dtype != torch.bfloat16:
+            return RefOps.moe_router_backward(self, ctx, op, d_tw, d_aux, x, rw, tw, ti)
+        E, K = a["num_experts"], a["top_k"]
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        N = x2.shape[0]
+        logits = gemm(x2, rw, out_dtype=torch.float32)
+        probs = torch.softmax(logits, -1)
+        til = ti.reshape(N, K).long()
+        sel = probs.gather(1, til)
+        if d_tw is not None:
+            g = d_tw.reshape(N, K).float()
+            if a["norm_topk_prob"]:
+                ssum = sel.sum(-1, keepdim=True)
+                d_sel = g / ssum - (g * sel).sum(-1, keepdim=True) / (ssum * ssum)
+            else:
+                d_sel = g
+        else:
+            d_sel = torch.zeros_like(sel)
+        d_probs = torch.zeros_like(probs).scatter_add_(1, til, d_sel)
+        extra = None
+        if d_aux is not None:
+            da = d_aux if torch.is_tensor(d_aux) else float(d_aux)
+            counts = torch.bincount(til.reshape(-1), minlength=E).float()
+            d_probs = d_probs + da * a["aux_loss_coef"] * E * (counts / N) / N
+            if a.get("z_loss_coef", 0.0):
+                extra = da * a["z_loss_coef"] * 2 * torch.logsumexp(logits, -1, keepdim=True) / N * probs
+        d_logits = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
+        if extra is not None:
+            d_logits = d_logits + extra
+        dl = d_logits.to(torch.bfloat16)
+        dx = gemm(dl, rw, b_mn=True).reshape(x.shape)          # [N,E] . [E,C]
+        drw = gemm(dl, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)   # [E,N] . [N,C]
+        return dx, drw
+
+    def moe_permute(self, ctx, op, x, ti):
+        a = op.attrs
+        E, K = a["num_experts"], a["top_k"]
+        if x.dtype != torch.bfloat16 or E > 256:
+            return RefOps.moe_permute(self, ctx, op, x, ti)
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        N = x2.shape[0]
+        counts = ctx.stash.pop(("moe_counts", ctx.layer, ctx.phase), None)
+        if counts is None:
+            counts = torch.bincount(ti.reshape(-1).long(), minlength=E).to(torch.int32)
+        cap = N * K + E * 128                      # exact upper bound of the padded row count: no host read of the routing
+        cap = (cap + 127) // 128 * 128
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
+        cursors = torch.empty(E, dtype=torch.int32, device=x.device)
+        self.ext.moe_offsets(counts, offsets, cursors, cap, self.ext.error_flag_tensor())
+        row_map = torch.empty(N * K, dtype=torch.int32, device=x.device)
+        xp = torch.zeros(cap, C, dtype=x.dtype, device=x.device)   # pad rows must be zero (they enter the wgrad contraction)
+        self.ext.moe_permute(x2, ti.reshape(N, K).contiguous(), offsets, cursors, row_map, xp, 0, E)
+        return xp, CudaMoEPlan(row_map, offsets, counts, cap, N, K, E, tuple(x.shape))
+
+    def moe_permute_backward(self, ctx, op, d_xp, plan):
+        plan = plan.local or plan
+        if not isinstance(plan, CudaMoEPlan):
+            return RefOps.moe_permute_backward(self, ctx, op, d_xp, plan)
+        dx = self.ext.moe_unpermute(d_xp.contiguous(), None, plan.row_map, plan.num_tokens, plan.top_k)
+        return (dx.reshape(plan.x_shape),)
+
+    def moe_grouped_gemm(self, ctx, op, x, w, plan):
+        if not isinstance(plan, CudaMoEPlan):
+            return RefOps.moe_grouped_gemm(self, ctx, op, x, w, plan)
+        r = ctx.recipe.forward_grouped(ctx, op, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "forward_grouped") else None
+        if r is not None:
+            return (r,)
+        y = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+        self.ext.gemm_grouped(x, w, y, plan.offsets, 1, False, False, 1.0, None, None, self.ext.error_flag_tensor())
+        return (y,)
+
+    def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
+        if not isinstance(plan, CudaMoEPlan):
+            return RefOps.moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan)
+        r = ctx.recipe.backward_grouped(ctx, op, dy, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "backward_grouped") else None
+        if r is not None:
+            return r, None
+        err = self.ext.error_flag_tensor()
+        dy = dy.contiguous()
+        dx = torch.zeros_like(x)
+        self.ext.gemm_grouped(dy, w, dx, plan.offsets, 1, True, False, 1.0, None, None, err)     # dy [R,N] . W[g] [N,K]
+        tgt, acc = ctx.grad_target(op.outputs[1])
+        if tgt is not None:
+            if not acc:
+                tgt.zero_()                                                                     # experts without tokens keep a zero gradient
+            self.ext.gemm_grouped(dy, x, tgt, plan.offsets, 2, True, True, 1.0, None, None, err)  # dW[g] += dy_g^T . x_g
+        return dx, None
+
+    def moe_unpermute(self, ctx, op, yp, tw, plan):
+        plan = plan.local or plan
+        if not isinstance(plan, CudaMoEPlan):
+            return RefOps.moe_unpermute(self, ctx, op, yp, tw, plan)
+        y = self.ext.moe_unpermute(yp, tw.reshape(-1, plan.top_k).contiguous(), plan.row_map, plan.num_tokens, plan.top_k)
+        return (y.reshape(plan.x_shape),)
+
+    def moe_unpermute_backward(self, ctx, op, dy, yp, tw, plan):
+        plan = plan.local or plan
+        if not isinstance(plan, CudaMoEPlan):
+            return RefOps.moe_unpermute_backward(self, ctx, op, dy, yp, tw, plan)
+        d_yp, d_tw = self.ext.moe_unpermute_bwd(dy.reshape(plan.num_tokens, -1).contiguous(), yp, tw.reshape(-1, plan.top_k).contiguous(), plan.row_map)
+        return d_yp, d_tw.reshape(tw.shape)
+
+    for f in (moe_router, moe_router_backward, moe_permute, moe_permute_backward, moe_grouped_gemm, moe_grouped_gemm_backward, moe_unpermute,
+              moe_unpermute_backward):
+        setattr(CudaOps, f.__name__, f)
+
+
+_moe_mixin()
+
+
 def make_backend(device: torch.device, kind: str = "auto", **kw):
     """``cuda`` = hand-written kernels (required on a GPU unless ``ref`` is asked for), ``ref`` = PyTorch reference."""
     if kind == "auto":

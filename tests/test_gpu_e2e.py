@@ -72,3 +72,32 @@ def test_smoke_entry():
     import __graft_entry__ as g
 
     g.smoke()
+
+
+MOE_MODEL = dict(architecture="Qwen3MoeForCausalLM", vocab_size=2048, d_model=256, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=128,
+                 moe_d_ff=128, num_experts=16, num_experts_per_tok=4, aux_loss_coef=1e-2, tie_word_embeddings=False)
+
+
+def test_moe_cuda_backend_matches_reference_backend():
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    def make(backend):
+        cfg = TrainerConfig(model=MOE_MODEL, batch_size=2, seq_len=128, recipe="bf16", optimizer="adamw", backend=backend, learning_rate=1e-3,
+                            lmhead_chunk_rows=200)
+        tr = Trainer(cfg, device=torch.device("cuda:0"))
+        tr.init_weights(seed=0)
+        return tr
+
+    x, y = _batch(5, T=128)
+    a, b = make("cuda"), make("ref")
+    ra, rb = a.forward_backward(x, y), b.forward_backward(x, y)
+    la, lb = (ra["loss_sum"] / ra["n_valid"]).item(), (rb["loss_sum"] / rb["n_valid"]).item()
+    assert abs(la - lb) < 2e-2 * abs(lb), (la, lb)
+    assert abs(ra["aux"].item() - rb["aux"].item()) < 2e-2 * abs(rb["aux"].item()) + 1e-5
+    ga, gb = a.get_gradients(), b.get_gradients()
+    for name in gb:
+        den = gb[name].float().norm() + 1e-12
+        ea = (ga[name].float() - gb[name].float()).norm() / den
+        assert ea < 0.1, f"{name}: rel err {ea.item():.4f}"
+    losses = [a.step(x, y)["loss"] for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.3, losses

@@ -238,3 +238,75 @@ def test_adamw_kernels(ext):
     ext.adamw_step(pb, g.bfloat16(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV), None,
                    torch.tensor([lr, b1, b2, eps, 0.0, 1 - b1, 1 - b2, 1.0], device=DEV))
     assert torch.isfinite(pb.float()).all()
+
+
+# ----------------------------------------------------------------------------- MoE
+def test_moe_softmax_topk(ext):
+    tokens, E, K = 1000, 128, 8
+    logits = torch.randn(tokens, E, device=DEV)
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    psum = torch.zeros(E, device=DEV)
+    lse = torch.zeros(1, device=DEV)
+    w, idx, probs = ext.moe_softmax_topk(logits, K, True, counts, psum, lse, True)
+    ref_p = torch.softmax(logits, -1)
+    rw, ri = torch.topk(ref_p, K, -1)
+    assert torch.equal(idx.long(), ri)
+    assert torch.allclose(w, rw / rw.sum(-1, keepdim=True), rtol=1e-4, atol=1e-6)
+    assert torch.allclose(probs, ref_p, rtol=1e-4, atol=1e-7)
+    assert torch.equal(counts.long(), torch.bincount(ri.reshape(-1), minlength=E))
+    assert torch.allclose(psum, ref_p.sum(0), rtol=1e-3)
+    assert abs(lse.item() - torch.logsumexp(logits, -1).pow(2).sum().item()) < 1e-2 * lse.item()
+
+
+def test_moe_permute_grouped_gemm_unpermute(ext):
+    torch.manual_seed(0)
+    tokens, C, E, K, Nout = 700, 256, 16, 4, 384
+    x = torch.randn(tokens, C, device=DEV).bfloat16()
+    ti = torch.stack([torch.randperm(E, device=DEV)[:K] for _ in range(tokens)]).to(torch.int32)
+    ti[:, 0] = torch.where(ti[:, 0] == 5, (ti[:, 0] + 1) % E, ti[:, 0])  # leave expert 5 under-used
+    counts = torch.bincount(ti.reshape(-1).long(), minlength=E).to(torch.int32)
+    cap = tokens * K + E * 128
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    cursors = torch.empty(E, dtype=torch.int32, device=DEV)
+    err = ext.error_flag_tensor()
+    ext.moe_offsets(counts, offsets, cursors, cap, err)
+    ref_off = torch.cat([torch.zeros(1, device=DEV), torch.cumsum((counts + 127) // 128 * 128, 0)]).int()
+    assert torch.equal(offsets, ref_off)
+    row_map = torch.empty(tokens * K, dtype=torch.int32, device=DEV)
+    xp = torch.zeros(cap, C, dtype=torch.bfloat16, device=DEV)
+    ext.moe_permute(x, ti, offsets, cursors, row_map, xp, 0, E)
+    rm = row_map.view(tokens, K).long()
+    assert torch.equal(xp[rm.reshape(-1)], x.repeat_interleave(K, 0))
+    e_of_row = torch.bucketize(rm, offsets[1:].long(), right=True)
+    assert torch.equal(e_of_row, ti.long())
+    assert len(torch.unique(rm)) == tokens * K
+    # grouped forward
+    w = torch.randn(E, Nout, C, device=DEV).bfloat16() * 0.1
+    y = torch.zeros(cap, Nout, dtype=torch.bfloat16, device=DEV)
+    ext.gemm_grouped(xp, w, y, offsets, 1, False, False, 1.0, None, None, err)
+    ref_y = torch.einsum("rc,rnc->rn", x.repeat_interleave(K, 0).float(), w[ti.reshape(-1).long()].float())
+    assert _rel_err(y[rm.reshape(-1)], ref_y) < 6e-3
+    # grouped dgrad: dy [R, Nout] . W[g]
+    dy = torch.zeros(cap, Nout, dtype=torch.bfloat16, device=DEV)
+    dy_rows = torch.randn(tokens * K, Nout, device=DEV).bfloat16()
+    dy[rm.reshape(-1)] = dy_rows
+    dx = torch.zeros(cap, C, dtype=torch.bfloat16, device=DEV)
+    ext.gemm_grouped(dy, w, dx, offsets, 1, True, False, 1.0, None, None, err)
+    ref_dx = torch.einsum("rn,rnc->rc", dy_rows.float(), w[ti.reshape(-1).long()].float())
+    assert _rel_err(dx[rm.reshape(-1)], ref_dx) < 6e-3
+    # grouped wgrad: dW[g] = dy_g^T x_g
+    dw = torch.zeros(E, Nout, C, dtype=torch.float32, device=DEV)
+    ext.gemm_grouped(dy, xp, dw, offsets, 2, True, True, 1.0, None, None, err)
+    ref_dw = torch.zeros_like(dw)
+    ref_dw.index_add_(0, ti.reshape(-1).long(), torch.einsum("rn,rc->rnc", dy_rows.float(), x.repeat_interleave(K, 0).float()))
+    assert _rel_err(dw, ref_dw) < 6e-3
+    # weighted combine + backward
+    tw = torch.rand(tokens, K, device=DEV)
+    out = ext.moe_unpermute(y, tw, row_map, tokens, K)
+    ref_out = (y[rm].float() * tw[..., None]).sum(1)
+    assert _rel_err(out, ref_out) < 5e-3
+    dout = torch.randn(tokens, Nout, device=DEV).bfloat16()
+    d_yp, d_tw = ext.moe_unpermute_bwd(dout, y, tw, row_map)
+    assert _rel_err(d_yp[rm.reshape(-1)], (dout.float()[:, None] * tw[..., None]).reshape(-1, Nout)) < 5e-3
+    assert _rel_err(d_tw, (y[rm].float() * dout.float()[:, None]).sum(-1)) < 5e-3
+    _check_flag()
