@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include "comm_kernels.h"
+#include "ep_kernels.h"
 #include "gemm_sm100.h"
 #include "moe_kernels.h"
 #include "ext_api.h"
@@ -209,6 +210,54 @@ void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& d, const Tensor& off
     TORCH_CHECK(err == nullptr, err ? err : "");
 }
 
+// ---------------------------------------------------------------------------------------- expert parallel
+void ep_plan(const std::vector<int64_t>& ctrl, int64_t ctrl_byte_offset, const std::vector<int64_t>& pads, const Tensor& counts, Tensor& offsets,
+             Tensor& dst_base, Tensor& cursors, int64_t rank, int64_t epoch, int64_t slot_base, int64_t capacity_rows, Tensor& error_flag,
+             double budget_s) {
+    const int E = static_cast<int>(counts.numel()), world = static_cast<int>(ctrl.size());
+    TORCH_CHECK(E <= 256 && E % world == 0 && offsets.numel() == E / world + 1 && dst_base.numel() == E && cursors.numel() == E, "ep_plan shapes");
+    sg_count_launch(1);
+    sg::ep_plan(to_peers(ctrl, ctrl_byte_offset), to_peers(pads), counts.data_ptr<int>(), offsets.data_ptr<int>(), dst_base.data_ptr<int>(),
+                cursors.data_ptr<int>(), E, static_cast<int>(rank), world, static_cast<uint32_t>(epoch), static_cast<int>(slot_base),
+                static_cast<int>(capacity_rows), error_flag.data_ptr<int>(), budget_s, cur_stream());
+}
+
+void ep_dispatch(const Tensor& x, const c10::optional<Tensor>& topk_idx, const c10::optional<Tensor>& w, const c10::optional<Tensor>& dst_base,
+                 const c10::optional<Tensor>& cursors, Tensor& row_map, const std::vector<int64_t>& recv, int64_t recv_byte_offset, int64_t K,
+                 int64_t experts_per_rank, int64_t capacity_rows, bool reuse_map) {
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x: bf16 contiguous");
+    const int C = static_cast<int>(x.size(-1));
+    const int tokens = static_cast<int>(x.numel() / C);
+    TORCH_CHECK(C % 8 == 0 && K <= 16 && row_map.numel() == static_cast<int64_t>(tokens) * K, "ep_dispatch shapes");
+    auto iptr = [](const c10::optional<Tensor>& t) { return (t.has_value() && t->defined()) ? t->data_ptr<int>() : nullptr; };
+    const float* wp = (w.has_value() && w->defined()) ? w->data_ptr<float>() : nullptr;
+    sg_count_launch(1);
+    sg::ep_dispatch(x.data_ptr(), iptr(topk_idx), wp, iptr(dst_base), iptr(cursors), row_map.data_ptr<int>(), to_peers(recv, recv_byte_offset), tokens, C,
+                    static_cast<int>(K), static_cast<int>(experts_per_rank), static_cast<int>(capacity_rows), reuse_map, cur_stream());
+}
+
+std::vector<Tensor> ep_combine(const std::vector<int64_t>& outs, int64_t out_byte_offset, const c10::optional<Tensor>& w, const Tensor& row_map,
+                               int64_t tokens, int64_t C, int64_t K, int64_t capacity_rows, bool keep_rows) {
+    auto opts = torch::TensorOptions().dtype(at::kBFloat16).device(row_map.device());
+    Tensor y = torch::empty({tokens, C}, opts);
+    Tensor rows;
+    if (keep_rows) rows = torch::empty({tokens * K, C}, opts);
+    const float* wp = (w.has_value() && w->defined()) ? w->data_ptr<float>() : nullptr;
+    sg_count_launch(1);
+    sg::ep_combine(to_peers(outs, out_byte_offset), wp, row_map.data_ptr<int>(), y.data_ptr(), keep_rows ? rows.data_ptr() : nullptr,
+                   static_cast<int>(tokens), static_cast<int>(C), static_cast<int>(K), static_cast<int>(capacity_rows), cur_stream());
+    return {y, rows};
+}
+
+Tensor ep_weight_grad(const Tensor& rows, const Tensor& dy, int64_t K) {
+    const int C = static_cast<int>(dy.size(-1));
+    const int tokens = static_cast<int>(dy.numel() / C);
+    Tensor d_w = torch::empty({tokens, K}, dy.options().dtype(at::kFloat));
+    sg_count_launch(1);
+    sg::ep_weight_grad(rows.data_ptr(), dy.data_ptr(), d_w.data_ptr<float>(), tokens, C, static_cast<int>(K), cur_stream());
+    return d_w;
+}
+
 }  // namespace
 
 void sg_register_extra(pybind11::module_& m) {
@@ -223,4 +272,8 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("moe_unpermute", &moe_unpermute);
     m.def("moe_unpermute_bwd", &moe_unpermute_bwd);
     m.def("gemm_grouped", &gemm_grouped);
+    m.def("ep_plan", &ep_plan);
+    m.def("ep_dispatch", &ep_dispatch);
+    m.def("ep_combine", &ep_combine);
+    m.def("ep_weight_grad", &ep_weight_grad);
 }

@@ -1,0 +1,155 @@
+"""Expert parallelism over symmetric memory: token dispatch / combine done by this framework's own kernels.
+
+Mesh: ``world = dp x ep`` with ``ep_rank = rank % ep``; this implementation covers ``ep == world`` (every rank owns
+``E / ep`` experts of every MoE layer and all non-expert parameters are data-parallel).  Per MoE layer, forward:
+
+1. ``ep_plan``     counts exchange (P2P stores + in-kernel flag barrier) -> padded receive layout and per-expert write cursors,
+2. ``ep_dispatch`` each token's activation row is stored straight into the owning rank's receive buffer (routing
+                   permutation and all-to-all are the same pass),
+3. grouped tcgen05 GEMMs over the received rows (device-side offsets, no host read of any count),
+4. ``ep_combine``  every token pulls its K expert outputs from the owners and forms the weighted sum.
+
+Backward runs the mirror image (push ``w * dy`` to the owners, grouped dgrad/wgrad there, pull ``d_x`` back).  Four
+symmetric buffers (receive / output for activations and for gradients) are allocated once and reused by every layer;
+the in-kernel barrier of step 1 (and an explicit one in backward) also guarantees that every rank is done with the
+previous layer's buffers before they are overwritten.  The receive capacity is ``capacity_factor x tokens x K`` rows
+(+ padding); exceeding it raises the device error word instead of writing out of bounds.
+
+Least-loaded balancing: per-expert global token counts of every layer are kept from the last step
+(``last_global_counts``) and summarised by ``imbalance()``; the LPT planner in :mod:`surogate_b200.parallel.lpt`
+turns them into an expert->rank placement that the next re-shard applies.
+
+Parity: csrc/src/runtime/ep/ep_strategy.cpp:1347-1980 (dispatch_forward / combine), lpt_planner.h:56-80,
+csrc/src/utilities/comm.cpp:515-646 (EP groups, variable-split all-to-all).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+
+SLOT_EP = 24  # signal-pad channel used by the in-kernel barrier of ep_plan (compute stream)
+
+
+class EpPlan:
+    def __init__(self, offsets, row_map, capacity, num_tokens, top_k, x_shape, topk_idx):
+        self.offsets, self.row_map, self.capacity = offsets, row_map, capacity
+        self.num_tokens, self.top_k, self.x_shape, self.topk_idx = num_tokens, top_k, x_shape, topk_idx
+        self.kept_rows = None
+        self.local = None
+        self.ep = True
+
+
+class PrePlan:
+    """Output of moe_permute under EP: nothing is moved yet, the dispatch kernel permutes while it sends."""
+
+    def __init__(self, topk_idx, counts, num_tokens, top_k, num_experts, x_shape):
+        self.topk_idx, self.counts, self.num_tokens, self.top_k, self.num_experts, self.x_shape = topk_idx, counts, num_tokens, top_k, num_experts, x_shape
+        self.local = None
+        self.ep_plan = None
+
+
+class ExpertParallel:
+    def __init__(self, comm, ep_size: int, device, capacity_factor: float = 1.5):
+        if not hasattr(comm, "create_arena"):
+            raise RuntimeError("expert parallelism needs the symmetric-memory communicator (collectives: symm)")
+        if ep_size != comm.world:
+            raise NotImplementedError("this build supports ep_size == number of ranks (dp = 1 inside the expert group)")
+        self.comm, self.ep, self.rank, self.device = comm, ep_size, comm.rank, device
+        self.capacity_factor = capacity_factor
+        self.ext = comm.ext
+        self.err = comm.err
+        self.bufs: Optional[Dict[str, Any]] = None
+        self.epoch = 0
+        self.last_global_counts: Dict[int, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ buffers
+    def _ensure(self, tokens: int, K: int, C: int, E: int):
+        if self.bufs is not None:
+            return self.bufs
+        El = E // self.ep
+        cap = int(self.capacity_factor * tokens * K) + El * 128
+        cap = (cap + 127) // 128 * 128
+        row_bytes = C * 2
+        sizes = {"counts": self.ep * E * 4, "recv_x": cap * row_bytes, "out_y": cap * row_bytes, "recv_dy": cap * row_bytes, "out_dx": cap * row_bytes}
+        total = sum((v + 255) // 256 * 256 + 256 for v in sizes.values())
+        arena = self.comm._alloc_symmetric(total)
+        arena.tensor.zero_()
+        b: Dict[str, Any] = {"arena": arena, "cap": cap, "C": C, "E": E, "El": El}
+        for k, n in sizes.items():
+            t = arena.take(n, torch.uint8)
+            b[k] = t.view(torch.int32) if k == "counts" else t.view(torch.bfloat16).view(cap, C)
+            b[k + "_off"] = arena.offset_of(t)
+        torch.cuda.synchronize(self.device)
+        self.comm.base.barrier()
+        self.bufs = b
+        return b
+
+    def _barrier(self):
+        self.comm.fence()
+
+    # ------------------------------------------------------------------ forward
+    def dispatch(self, ctx, x2: torch.Tensor, pre: PrePlan):
+        N, K, E = pre.num_tokens, pre.top_k, pre.num_experts
+        C = x2.shape[-1]
+        b = self._ensure(N, K, C, E)
+        cap, El = b["cap"], b["El"]
+        dev = x2.device
+        offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+        dst_base = torch.empty(E, dtype=torch.int32, device=dev)
+        cursors = torch.empty(E, dtype=torch.int32, device=dev)
+        row_map = torch.empty(N * K, dtype=torch.int32, device=dev)
+        b["recv_x"].zero_()  # pad rows feed the wgrad contraction and must be zero; peers write only after the barrier inside ep_plan
+        self.epoch += 1
+        pb = b["arena"].peer_bases
+        self.ext.ep_plan(pb, b["counts_off"], self.comm.ctrl.peer_bases, pre.counts, offsets, dst_base, cursors, self.rank, self.epoch & 0x7FFFFFFF,
+                         SLOT_EP, cap, self.err, self.comm.wait_budget_s)
+        self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, cursors, row_map, pb, b["recv_x_off"], K, El, cap, False)
+        self._barrier()  # every rank's rows have landed
+        xp = b["recv_x"].clone()
+        if ctx.layer is not None and ctx.phase == "fwd":
+            self.last_global_counts[ctx.layer] = b["counts"].view(self.ep, E).sum(0)
+        plan = EpPlan(offsets, row_map, cap, N, K, pre.x_shape, pre.topk_idx)
+        pre.ep_plan = plan
+        return xp, plan
+
+    def publish_outputs(self, ctx, h: torch.Tensor, plan: EpPlan, backward: bool = False):
+        """Expert outputs (or d_x of the experts in backward) become visible to the token owners."""
+        b = self.bufs
+        buf = b["out_dx"] if backward else b["out_y"]
+        buf.copy_(h)
+        self._barrier()
+        return buf
+
+    def combine(self, ctx, buf: torch.Tensor, weights: Optional[torch.Tensor], plan: EpPlan, backward: bool = False):
+        b = self.bufs
+        off = b["out_dx_off"] if backward else b["out_y_off"]
+        w = weights.reshape(-1, plan.top_k).contiguous() if weights is not None else None
+        y, rows = self.ext.ep_combine(b["arena"].peer_bases, off, w, plan.row_map, plan.num_tokens, b["C"], plan.top_k, plan.capacity,
+                                      (not backward) and ctx.training)
+        if rows is not None and rows.numel():
+            plan.kept_rows = rows
+        return y.reshape(plan.x_shape)
+
+    # ------------------------------------------------------------------ backward
+    def combine_backward(self, ctx, dy: torch.Tensor, weights: torch.Tensor, plan: EpPlan):
+        """d_yp rows (w * dy) are pushed to the experts' owners; d_weights come from the rows kept in forward."""
+        b = self.bufs
+        K = plan.top_k
+        dy2 = dy.reshape(plan.num_tokens, -1).contiguous()
+        w = weights.reshape(-1, K).contiguous()
+        d_w = self.ext.ep_weight_grad(plan.kept_rows, dy2, K)
+        b["recv_dy"].zero_()
+        self._barrier()  # peers are done with the previous contents of their gradient buffers
+        self.ext.ep_dispatch(dy2, None, w, None, None, plan.row_map, b["arena"].peer_bases, b["recv_dy_off"], K, b["El"], plan.capacity, True)
+        self._barrier()
+        return b["recv_dy"].clone(), d_w.reshape(weights.shape)
+
+    # ------------------------------------------------------------------ balancing
+    def imbalance(self) -> float:
+        """max over layers of (busiest rank's tokens / mean rank tokens) in the last step."""
+        worst = 1.0
+        for c in self.last_global_counts.values():
+            per_rank = c.view(self.ep, -1).sum(1).float()
+            worst = max(worst, float(per_rank.max() / per_rank.mean().clamp_min(1)))
+        return worst

@@ -303,6 +303,10 @@ def _moe_mixin():
         counts = ctx.stash.pop(("moe_counts", ctx.layer, ctx.phase), None)
         if counts is None:
             counts = torch.bincount(ti.reshape(-1).long(), minlength=E).to(torch.int32)
+        if ctx.ep is not None:  # expert parallel: the dispatch kernel permutes while it sends; nothing moves here
+            from ..parallel.ep import PrePlan
+
+            return x2, PrePlan(ti.reshape(N, K).contiguous(), counts, N, K, E, tuple(x.shape))
         cap = N * K + E * 128                      # exact upper bound of the padded row count: no host read of the routing
         cap = (cap + 127) // 128 * 128
         offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
@@ -314,6 +318,9 @@ def _moe_mixin():
         return xp, CudaMoEPlan(row_map, offsets, counts, cap, N, K, E, tuple(x.shape))
 
     def moe_permute_backward(self, ctx, op, d_xp, plan):
+        plan = getattr(plan, "ep_plan", None) or plan  # under EP the permutation happened inside the dispatch kernel
+        if getattr(plan, "ep", None) is True:
+            return (ctx.ep.combine(ctx, d_xp, None, plan, backward=True),)
         plan = plan.local or plan
         if not isinstance(plan, CudaMoEPlan):
             return RefOps.moe_permute_backward(self, ctx, op, d_xp, plan)
@@ -321,7 +328,7 @@ def _moe_mixin():
         return (dx.reshape(plan.x_shape),)
 
     def moe_grouped_gemm(self, ctx, op, x, w, plan):
-        if not isinstance(plan, CudaMoEPlan):
+        if not hasattr(plan, "offsets") or not hasattr(plan, "capacity"):
             return RefOps.moe_grouped_gemm(self, ctx, op, x, w, plan)
         r = ctx.recipe.forward_grouped(ctx, op, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "forward_grouped") else None
         if r is not None:
@@ -331,7 +338,7 @@ def _moe_mixin():
         return (y,)
 
     def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
-        if not isinstance(plan, CudaMoEPlan):
+        if not hasattr(plan, "offsets") or not hasattr(plan, "capacity"):
             return RefOps.moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan)
         r = ctx.recipe.backward_grouped(ctx, op, dy, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "backward_grouped") else None
         if r is not None:
@@ -348,6 +355,8 @@ def _moe_mixin():
         return dx, None
 
     def moe_unpermute(self, ctx, op, yp, tw, plan):
+        if getattr(plan, "ep", None) is True:
+            return (ctx.ep.combine(ctx, yp, tw, plan),)
         plan = plan.local or plan
         if not isinstance(plan, CudaMoEPlan):
             return RefOps.moe_unpermute(self, ctx, op, yp, tw, plan)
@@ -355,11 +364,26 @@ def _moe_mixin():
         return (y.reshape(plan.x_shape),)
 
     def moe_unpermute_backward(self, ctx, op, dy, yp, tw, plan):
+        if getattr(plan, "ep", None) is True:
+            return ctx.ep.combine_backward(ctx, dy, tw, plan)
         plan = plan.local or plan
         if not isinstance(plan, CudaMoEPlan):
             return RefOps.moe_unpermute_backward(self, ctx, op, dy, yp, tw, plan)
         d_yp, d_tw = self.ext.moe_unpermute_bwd(dy.reshape(plan.num_tokens, -1).contiguous(), yp, tw.reshape(-1, plan.top_k).contiguous(), plan.row_map)
         return d_yp, d_tw.reshape(tw.shape)
+
+    def ep_dispatch(self, ctx, op, xp, plan):
+        return ctx.ep.dispatch(ctx, xp, plan)
+
+    def ep_combine(self, ctx, op, y, plan):
+        # forward: expert outputs become pullable; as the backward of ep_dispatch: the experts' d_x become pullable
+        return (ctx.ep.publish_outputs(ctx, y, plan, backward=bool(op.attrs.get("backward", False))),)
+
+    def ep_dispatch_backward(self, ctx, op, dy, plan):
+        return (dy,)  # combine_backward already delivered d_yp to the experts' owner
+
+    for f in (ep_dispatch, ep_combine, ep_dispatch_backward):
+        setattr(CudaOps, f.__name__, f)
 
     for f in (moe_router, moe_router_backward, moe_permute, moe_permute_backward, moe_grouped_gemm, moe_grouped_gemm_backward, moe_unpermute,
               moe_unpermute_backward):

@@ -25,6 +25,7 @@ Parity: csrc/src/runtime/dsl/dsl_param_store, dsl_grad_store.cpp:457-678
 from __future__ import annotations
 
 import math
+import zlib
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
@@ -63,6 +64,7 @@ class Bucket:
         self.grad_persistent = False  # gradient buffer lives in the symmetric arena for the whole run
         self.written: set = set()
         self.trainable = True
+        self.expert = False  # expert-parallel bucket: this rank owns whole experts; never sharded or reduced across the EP group
         self.decay_mask_cache: Optional[torch.Tensor] = None
 
     def slot(self, name: str) -> Slot:
@@ -107,6 +109,7 @@ class ParamStore:
         self.zero_level = zero_level if self.world > 1 else 0
         self.keep_gathered = keep_gathered
         self.frozen = frozen or (lambda name: False)
+        self.ep = max(1, int(expert_parallel))
         self.buckets: "OrderedDict[str, Bucket]" = OrderedDict()
         self.where: Dict[str, Tuple[Bucket, Slot]] = {}
         self.alias: Dict[str, str] = {}
@@ -122,18 +125,26 @@ class ParamStore:
             if e.tied_to:
                 self.alias[e.name] = e.tied_to
                 continue
-            b = self.buckets.get(e.group)
+            shape = tuple(e.spec.shape)
+            gname = e.group
+            is_expert = self.ep > 1 and e.local.startswith("experts_")
+            if is_expert:
+                assert shape[0] % self.ep == 0, f"{e.name}: {shape[0]} experts do not divide over ep={self.ep}"
+                shape = (shape[0] // self.ep,) + shape[1:]
+                gname = e.group + ".experts"
+            b = self.buckets.get(gname)
             if b is None:
-                b = self.buckets[e.group] = Bucket(e.group, e.layer)
-            n = math.prod(e.spec.shape)
-            slot = Slot(e.name, b.numel, n, tuple(e.spec.shape), e.spec.decay, e, trainable=not self.frozen(e.name))
+                b = self.buckets[gname] = Bucket(gname, e.layer)
+                b.expert = is_expert
+            n = math.prod(shape)
+            slot = Slot(e.name, b.numel, n, shape, e.spec.decay, e, trainable=not self.frozen(e.name))
             b.slots.append(slot)
             b.numel += (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
             self.where[e.name] = (b, slot)
         quantum = self.world * ALIGN_ELEMS
         for b in self.buckets.values():
             b.numel = (b.numel + quantum - 1) // quantum * quantum
-            b.shard_numel = b.numel // self.world if self.sharded else b.numel
+            b.shard_numel = b.numel // self.world if (self.sharded and not b.expert) else b.numel
             b.trainable = any(s.trainable for s in b.slots)
         # Peer-addressable placement: when the communicator runs its own kernels over symmetric memory, master shards
         # and bucket-sized gradient buffers live in one arena so that peers can load them directly.
@@ -144,6 +155,8 @@ class ParamStore:
         if hasattr(self.comm, "create_arena") and self.sharded and self.master_dtype == torch.bfloat16 and self.grad_dtype == torch.bfloat16:
             need = 0
             for b in self.buckets.values():
+                if b.expert:
+                    continue
                 need += (b.shard_numel * 2 + 255) // 256 * 256 + 256
                 if b.trainable:
                     need += (b.numel * 2 + 255) // 256 * 256 + 256
@@ -151,6 +164,10 @@ class ParamStore:
             self.arena.tensor.zero_()
             self.fused_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         for b in self.buckets.values():
+            if b.expert:
+                b.master = torch.zeros(b.numel, dtype=self.master_dtype, device=self.device)
+                b.work = b.master if self.master_dtype == self.param_dtype else torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
+                continue
             if self.arena is not None:
                 b.master = self.arena.take(b.shard_numel, self.master_dtype)
                 if b.trainable:
@@ -171,25 +188,39 @@ class ParamStore:
         return self.alias.get(name, name)
 
     def shard_range(self, b: Bucket) -> Tuple[int, int]:
-        if not self.sharded:
+        if not self.sharded or b.expert:
             return 0, b.numel
         return self.rank * b.shard_numel, (self.rank + 1) * b.shard_numel
 
     # ------------------------------------------------------------------ init / import / export
     def init_weights(self, seed: int = 0, std: float = 0.02, zero_projections: bool = False) -> None:
-        """Seeded N(0, std) init, identical for every world size (each parameter has its own generator stream)."""
+        """Seeded N(0, std) init.  Every parameter (every expert of an expert parameter) has its own generator stream, so the
+        values do not depend on the world size or the expert-parallel layout.  Large slots are generated on the GPU."""
+        big = 1 << 24
         for bi, b in enumerate(self.buckets.values()):
-            lo, hi = self.shard_range(b)
             for si, s in enumerate(b.slots):
-                gen = torch.Generator(device="cpu").manual_seed(seed * 1000003 + bi * 1009 + si)
-                if s.entry.spec.init == "ones":
-                    full = torch.ones(s.numel)
-                elif s.entry.spec.init == "zeros" or (zero_projections and s.entry.local in ("out_weight", "mlp_down_weight", "experts_down")):
-                    full = torch.zeros(s.numel)
-                else:
-                    full = torch.empty(s.numel).normal_(0.0, std, generator=gen)
-                self._write_master(b, s, full)
+                base_seed = seed * 1000003 + (zlib.crc32(s.name.encode()) & 0xFFFFF) * 1009
+                kind = s.entry.spec.init
+                zero = kind == "zeros" or (zero_projections and s.entry.local in ("out_weight", "mlp_down_weight", "experts_down"))
+                if b.expert:
+                    El = s.shape[0]
+                    per = s.numel // El
+                    for j in range(El):
+                        ge = self.rank * El + j
+                        t = self._gen(per, base_seed + 7 * ge, kind, zero, std, per >= big)
+                        b.master[s.offset + j * per:s.offset + (j + 1) * per].copy_(t.to(self.master_dtype))
+                    continue
+                self._write_master(b, s, self._gen(s.numel, base_seed, kind, zero, std, s.numel >= big))
         self.sync_work_from_master()
+
+    def _gen(self, n: int, seed: int, kind: str, zero: bool, std: float, on_device: bool) -> torch.Tensor:
+        dev = self.device if (on_device and self.device.type == "cuda") else torch.device("cpu")
+        if kind == "ones":
+            return torch.ones(n, device=dev)
+        if zero:
+            return torch.zeros(n, device=dev)
+        gen = torch.Generator(device=dev).manual_seed(seed & 0x7FFFFFFFFFFF)
+        return torch.empty(n, device=dev).normal_(0.0, std, generator=gen)
 
     def _write_master(self, b: Bucket, s: Slot, flat_cpu: torch.Tensor) -> None:
         lo, hi = self.shard_range(b)
@@ -197,9 +228,15 @@ class ParamStore:
         if a < z:
             b.master[a - lo:z - lo].copy_(flat_cpu[a - s.offset:z - s.offset].to(self.master_dtype))
 
+    def _expert_slice(self, s: Slot, tensor: torch.Tensor) -> torch.Tensor:
+        El = s.shape[0]
+        return tensor[self.rank * El:(self.rank + 1) * El]
+
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         name = self.resolve(name)
         b, s = self.where[name]
+        if b.expert and tensor.shape[0] == s.shape[0] * self.ep:
+            tensor = self._expert_slice(s, tensor)  # a full [E, ...] tensor: keep this rank's experts
         assert tuple(tensor.shape) == s.shape, f"{name}: expected {s.shape}, got {tuple(tensor.shape)}"
         self._write_master(b, s, tensor.reshape(-1))
 
@@ -207,14 +244,27 @@ class ParamStore:
         """Gather one parameter in full on every rank (export / debug)."""
         name = self.resolve(name)
         b, s = self.where[name]
+        if b.expert:
+            return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
         if not self.sharded:
             return b.master[s.offset:s.offset + s.numel].reshape(s.shape)
         full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
         self.comm.all_gather(b.master, full)
         return full[s.offset:s.offset + s.numel].reshape(s.shape)
 
+    def _gather_experts(self, local: torch.Tensor) -> torch.Tensor:
+        """[E/ep, ...] on every rank -> [E, ...] (ranks own consecutive expert ranges)."""
+        local = local.contiguous()
+        full = torch.empty((self.ep * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        getattr(self.comm, "base", self.comm).all_gather(local.reshape(-1), full.reshape(-1))
+        return full
+
     def named_full_tensors(self) -> Iterable[Tuple[str, torch.Tensor]]:
         for b in self.buckets.values():
+            if b.expert:
+                for s in b.slots:
+                    yield s.name, self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
+                continue
             if self.sharded:
                 full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
                 self.comm.all_gather(b.master, full)
@@ -229,6 +279,10 @@ class ParamStore:
         if fence is not None and self.sharded:
             fence()  # peers pull master shards directly: every rank must have finished writing its own first
         for b in self.buckets.values():
+            if b.expert:
+                if b.work is not b.master:
+                    b.work.copy_(b.master)
+                continue
             if self.zero_level >= 3:
                 b.work = None
                 b.gather_work = None
@@ -262,7 +316,7 @@ class ParamStore:
                     self.post_gather(b)
 
     def _release(self, b: Bucket) -> None:
-        if self.zero_level >= 3:
+        if self.zero_level >= 3 and not b.expert:
             b.work = None
 
     def _layer_bucket(self, L: int) -> Optional[Bucket]:
@@ -285,6 +339,9 @@ class ParamStore:
         if phase == "bwd":
             self._reduce_bucket(b)
             self._release(b)
+            eb = self.buckets.get(f"layer{L}.experts")
+            if eb is not None:
+                self._reduce_bucket(eb)
         elif not self.keep_gathered:
             self._release(b)
 
@@ -343,8 +400,8 @@ class ParamStore:
         for s in b.slots:  # parameters that received no gradient this micro-step contribute zeros
             if s.trainable and s.name not in b.written and (self.zero_level >= 2 or b.grad_persistent):
                 b.grad[s.offset:s.offset + s.numel].zero_()
-        if self.world == 1:
-            b.grad_shard = b.grad
+        if self.world == 1 or b.expert:
+            b.grad_shard = b.grad  # whole experts live on this rank (dp = 1 inside the expert group): nothing to reduce
             return
         if self.zero_level == 0:
             self.sumsq_valid = False
@@ -411,6 +468,8 @@ class ParamStore:
         g = b.grad_shard if b.grad_shard is not None else b.grad
         if g is None:
             return None
+        if b.expert:
+            return self._gather_experts(g[s.offset:s.offset + s.numel].view(s.shape))
         if g.numel() != b.numel:
             full = torch.empty(b.numel, dtype=g.dtype, device=self.device)
             self.comm.all_gather(g.contiguous(), full)
@@ -419,6 +478,9 @@ class ParamStore:
 
     def release_grads(self) -> None:
         for b in self.buckets.values():
+            if b.expert:
+                b.grad_shard = None
+                continue
             if self.zero_level >= 1:
                 b.grad_shard = None
             if self.zero_level >= 2 and not b.grad_persistent:

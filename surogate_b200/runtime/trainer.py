@@ -55,6 +55,7 @@ class TrainerConfig:
     keep_gathered: bool = True
     collectives: str = "auto"  # auto | nccl | symm
     ep_size: int = 1
+    ep_capacity_factor: float = 1.5
     lora: Optional[Dict[str, Any]] = None
     fp8_amax_history: int = 16
     skip_quant_first_layers: int = 0
@@ -105,7 +106,7 @@ class Trainer:
 
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
         self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
-                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen)
+                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size)
         from .ops_cuda import make_backend
 
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
@@ -115,7 +116,7 @@ class Trainer:
         if cfg.ep_size > 1:
             from ..parallel.ep import ExpertParallel
 
-            self.ep = ExpertParallel(self.comm, cfg.ep_size, self.device)
+            self.ep = ExpertParallel(self.comm, cfg.ep_size, self.device, capacity_factor=cfg.ep_capacity_factor)
         self.executor = Executor(self.cm, self.store, self.backend, recipe=self.recipe,
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd), device=self.device, ep=self.ep, lora=self.lora)
         self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
@@ -243,8 +244,11 @@ class Trainer:
         if self.store.fused_sumsq is not None and self.store.sumsq_valid and self.lora is None:
             # the reduce-scatter kernels already accumulated this rank's shard norms
             total = self.store.fused_sumsq.clone().reshape(())
+            for b in self.store.trainable_buckets():  # expert-parallel buckets are not reduce-scattered: add their norms here
+                if b.expert and b.grad_shard is not None:
+                    total += self.backend.ext.sumsq(b.grad_shard)
             if os.environ.get("SUROGATE_CHECK_FUSED_NORM") == "1":  # self-check: recompute from the reduced shards
-                ref = sum(self.backend.ext.sumsq(b.grad_shard) for b in self.store.trainable_buckets() if b.grad_shard is not None)
+                ref = sum(self.backend.ext.sumsq(b.grad_shard) for b in self.store.trainable_buckets() if b.grad_shard is not None)  # incl. experts
                 if abs(float(ref) - float(total)) > 1e-2 * abs(float(ref)):
                     raise RuntimeError(f"fused gradient norm mismatch on rank {self.rank}: fused {float(total)} vs recomputed {float(ref)}")
             self.comm.all_reduce(total, "sum")
@@ -257,8 +261,15 @@ class Trainer:
             total += self.backend.ext.sumsq(g) if on_gpu else g.float().pow(2).sum()
         if self.lora is not None:
             total += self.lora.grad_sumsq()
-        if self.world > 1 and self.store.sharded:
-            self.comm.all_reduce(total, "sum")
+        if self.world > 1 and (self.store.sharded or self.store.ep > 1):
+            if not self.store.sharded:  # replicated gradients: only the expert buckets differ between ranks
+                rep = sum((self.backend.ext.sumsq(b.grad_shard) if on_gpu else b.grad_shard.float().pow(2).sum())
+                          for b in self.store.trainable_buckets() if not b.expert and b.grad_shard is not None)
+                total = total - rep
+                self.comm.all_reduce(total, "sum")
+                total = total + rep
+            else:
+                self.comm.all_reduce(total, "sum")
         return total.sqrt()
 
     def optimizer_step(self, lr: Optional[float] = None) -> torch.Tensor:

@@ -29,3 +29,17 @@ def test_two_gpus_match_one_gpu(single, zero, collectives):
 def test_two_gpus_fp8_zero3_symm(single):
     r = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29731)
     assert all(l == l for l in r["losses"]) and r["losses"][-1] < r["losses"][0] + 0.5
+
+
+MOE = dict(architecture="Qwen3MoeForCausalLM", vocab_size=1024, d_model=256, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=128,
+           moe_d_ff=128, num_experts=8, num_experts_per_tok=2, aux_loss_coef=1e-2, tie_word_embeddings=False)
+
+
+def test_expert_parallel_matches_one_gpu():
+    """EP=2: tokens are dispatched to the expert's owner by the peer-memory kernels; the run reproduces the 1-GPU run."""
+    one = run_worker(1, dict(ARGS, model=MOE))
+    two = run_worker(2, dict(ARGS, model=MOE, ep=2, zero=1, collectives="symm"), port=29741)
+    for a, b in zip(two["losses"], one["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (two["losses"], one["losses"])
+    for a, b in zip(two["norms"], one["norms"]):
+        assert abs(a - b) < 6e-2 * abs(b), (two["norms"], one["norms"])
