@@ -7,6 +7,7 @@
 #include "ep_kernels.h"
 #include "gemm_sm100.h"
 #include "moe_kernels.h"
+#include "nvfp4_kernels.h"
 #include "ext_api.h"
 
 namespace {
@@ -258,6 +259,64 @@ Tensor ep_weight_grad(const Tensor& rows, const Tensor& dy, int64_t K) {
     return d_w;
 }
 
+// ---------------------------------------------------------------------------------------- NVFP4
+int64_t nvfp4_sf_bytes(int64_t rows, int64_t K) { return ((rows + 127) / 128) * ((K / 16 + 3) / 4) * 512; }
+
+// x [rows, K] bf16 -> (packed e2m1 [rows, K/2] uint8, scale factors in atom layout uint8)
+std::vector<Tensor> nvfp4_quantize(const Tensor& x, const Tensor& amax, bool stochastic, int64_t seed, bool block2d) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: bf16 [rows, K]");
+    const int rows = static_cast<int>(x.size(0)), K = static_cast<int>(x.size(1));
+    TORCH_CHECK(K % 16 == 0 && (!block2d || rows % 16 == 0), "nvfp4_quantize: K (and rows for 2-D blocks) must be multiples of 16");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor q = torch::empty({rows, K / 2}, x.options().dtype(at::kByte));
+    Tensor sf = torch::zeros({nvfp4_sf_bytes(rows, K)}, x.options().dtype(at::kByte));
+    sg_count_launch(1);
+    sg::nvfp4_quantize_rows(x.data_ptr(), q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), rows, K, stochastic, static_cast<uint32_t>(seed), block2d,
+                            sms(), cur_stream());
+    return {q, sf};
+}
+
+// x [R, C] bf16 -> quantised transpose: (q [C, R/2], sf for rows = C, K = R); optional random Hadamard along R
+std::vector<Tensor> nvfp4_quantize_transpose(const Tensor& x, const Tensor& amax, bool stochastic, bool hadamard, int64_t seed, int64_t sign_mask) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: bf16 [R, C]");
+    const int R = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1));
+    TORCH_CHECK(R % 64 == 0 && C % 64 == 0, "nvfp4_quantize_transpose: both dimensions must be multiples of 64");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor q = torch::empty({C, R / 2}, x.options().dtype(at::kByte));
+    Tensor sf = torch::zeros({nvfp4_sf_bytes(C, R)}, x.options().dtype(at::kByte));
+    sg_count_launch(1);
+    sg::nvfp4_quantize_transpose(x.data_ptr(), q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), R, C, stochastic, hadamard,
+                                 static_cast<uint32_t>(seed), static_cast<uint32_t>(sign_mask), cur_stream());
+    return {q, sf};
+}
+
+Tensor nvfp4_dequantize(const Tensor& q, const Tensor& sf, const Tensor& amax, double amax_div) {
+    const int rows = static_cast<int>(q.size(0)), K = static_cast<int>(q.size(1)) * 2;
+    const c10::cuda::CUDAGuard guard(q.device());
+    Tensor out = torch::empty({rows, K}, q.options().dtype(at::kBFloat16));
+    sg_count_launch(1);
+    sg::nvfp4_dequantize(q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), static_cast<float>(amax_div), out.data_ptr(), rows, K, sms(), cur_stream());
+    return out;
+}
+
+// d [M, N] = alpha * sa * sb * dequant(a) . dequant(b)^T on the tensor cores (block scales applied in hardware)
+void gemm_nvfp4(const Tensor& a, const Tensor& sfa, const Tensor& b, const Tensor& sfb, Tensor& d, bool accumulate, double alpha,
+                const c10::optional<Tensor>& scale_a, const c10::optional<Tensor>& scale_b, Tensor& error_flag) {
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kByte && a.is_contiguous() && b.scalar_type() == at::kByte && b.is_contiguous(), "packed uint8 operands");
+    const int M = static_cast<int>(a.size(0)), N = static_cast<int>(b.size(0)), K = static_cast<int>(a.size(1)) * 2;
+    TORCH_CHECK(b.size(1) * 2 == K && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_nvfp4 shapes");
+    TORCH_CHECK(sfa.numel() >= nvfp4_sf_bytes(M, K) && sfb.numel() >= nvfp4_sf_bytes(N, K), "scale-factor buffers too small");
+    TORCH_CHECK(d.scalar_type() == at::kBFloat16 || d.scalar_type() == at::kFloat, "output bf16 or fp32");
+    const c10::cuda::CUDAGuard guard(a.device());
+    const float* sa = (scale_a.has_value() && scale_a->defined()) ? scale_a->data_ptr<float>() : nullptr;
+    const float* sb = (scale_b.has_value() && scale_b->defined()) ? scale_b->data_ptr<float>() : nullptr;
+    sg_count_launch(1);
+    const char* err = sg::gemm_nvfp4_sm100(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), d.data_ptr(), M, N, K, static_cast<int>(d.stride(0)),
+                                           d.scalar_type() == at::kFloat, accumulate, static_cast<float>(alpha), sa, sb, error_flag.data_ptr<int>(), sms(),
+                                           cur_stream());
+    TORCH_CHECK(err == nullptr, err ? err : "");
+}
+
 }  // namespace
 
 void sg_register_extra(pybind11::module_& m) {
@@ -272,6 +331,11 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("moe_unpermute", &moe_unpermute);
     m.def("moe_unpermute_bwd", &moe_unpermute_bwd);
     m.def("gemm_grouped", &gemm_grouped);
+    m.def("nvfp4_sf_bytes", &nvfp4_sf_bytes);
+    m.def("nvfp4_quantize", &nvfp4_quantize);
+    m.def("nvfp4_quantize_transpose", &nvfp4_quantize_transpose);
+    m.def("nvfp4_dequantize", &nvfp4_dequantize);
+    m.def("gemm_nvfp4", &gemm_nvfp4);
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_combine", &ep_combine);

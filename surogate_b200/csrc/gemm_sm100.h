@@ -42,3 +42,10 @@ const char* make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_byte
                                uint32_t box_inner, uint32_t box_outer);
 
 }  // namespace sg
+
+namespace sg {
+// NVFP4 block-scaled GEMM (gemm_nvfp4_sm100.cu): a [M, K/2] and b [N, K/2] packed E2M1, sfa / sfb UE4M3 scales in atom layout.
+const char* gemm_nvfp4_sm100(const void* a, const void* b, const void* sfa, const void* sfb, void* d, int M, int N, int K, int ldd, int out_fp32,
+                             int accumulate, float alpha, const float* scale_a, const float* scale_b, int* error_flag, int num_sms,
+                             cudaStream_t stream);
+}  // namespace sg

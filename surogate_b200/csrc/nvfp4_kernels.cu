@@ -143,9 +143,13 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
     const float ge = at > 0.f ? 2688.f / at : 1.f;
     const int kblocks = K / 16;
     const size_t total = static_cast<size_t>(rows) * kblocks;
-    for (size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; b < total; b += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        int r, kb;
-        if (block2d) {   // consecutive threads walk down the 16 rows of a tile so the tile abs-max is a 16-lane shuffle
+    // warp-uniform trip count: the 16x16-tile path shuffles across lanes
+    for (size_t base = blockIdx.x * static_cast<size_t>(blockDim.x) + (threadIdx.x & ~31); base < total; base += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t b = base + (threadIdx.x & 31);
+        const bool live = b < total;   // total is a multiple of 16 in the tile path, so 16-lane groups are all-live or all-dead
+        int r = 0, kb = 0;
+        if (!live) {
+        } else if (block2d) {   // consecutive threads walk down the 16 rows of a tile so the tile abs-max is a 16-lane shuffle
             const size_t tile = b >> 4;
             const int tiles_k = kblocks;
             r = static_cast<int>(tile / tiles_k) * 16 + static_cast<int>(b & 15);
@@ -155,7 +159,9 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
             kb = static_cast<int>(b % kblocks);
         }
         float v[16];
-        load16(x + static_cast<size_t>(r) * K + kb * 16, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        if (live) load16(x + static_cast<size_t>(r) * K + kb * 16, v);
         float forced = -1.f;
         if (block2d) {
             float m = 0.f;
@@ -165,6 +171,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
             for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             forced = m;
         }
+        if (!live) continue;
         uint32_t out[2];
         const uint8_t sfb = quant_block16<SR>(v, ge, forced, seed, static_cast<uint64_t>(r) * K + kb * 16, out);
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * (K / 2) + kb * 8) = make_uint2(out[0], out[1]);

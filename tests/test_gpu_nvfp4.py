@@ -1,0 +1,94 @@
+"""NVFP4 quantisers and the block-scaled tcgen05 GEMM against the PyTorch emulation of the format."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from surogate_b200.ops import ext as load
+
+    return load()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("rows,K,block2d", [(128, 256, False), (200, 512, False), (256, 256, True), (384, 1024, True)])
+def test_quantize_rows_matches_emulation(ext, rows, K, block2d):
+    from surogate_b200.ops import nvfp4_ref as ref
+
+    torch.manual_seed(0)
+    x = (torch.randn(rows, K, device=DEV) * torch.rand(rows, 1, device=DEV) * 3).bfloat16()
+    amax = x.float().abs().max().reshape(1)
+    q, sf = ext.nvfp4_quantize(x, amax, False, 0, block2d)
+    codes, sfd, ge = ref.quantize(x.float(), amax[0], block2d)
+    sf_k = ref.atoms_to_sf(sf, rows, K // 16)
+    assert torch.equal(sf_k.view(torch.float8_e4m3fn).float(), sfd)
+    got = ref.unpack_codes(q)
+    mismatch = (got != codes).float().mean().item()
+    assert mismatch < 2e-3, mismatch   # bf16->fp32 products can land on a rounding boundary differently
+    deq = ext.nvfp4_dequantize(q, sf, amax, 1.0)
+    assert _rel(deq, ref.dequantize(got, sfd, ge)) < 4e-3
+    assert _rel(deq, x) < 0.12
+
+
+def test_quantize_transpose_and_hadamard(ext):
+    from surogate_b200.ops import nvfp4_ref as ref
+
+    torch.manual_seed(1)
+    R, C = 256, 192
+    x = torch.randn(R, C, device=DEV).bfloat16()
+    amax = x.float().abs().max().reshape(1)
+    q, sf = ext.nvfp4_quantize_transpose(x, amax, False, False, 0, 0)
+    codes, sfd, ge = ref.quantize(x.float().t().contiguous(), amax[0])
+    assert torch.equal(ref.atoms_to_sf(sf, C, R // 16).view(torch.float8_e4m3fn).float(), sfd)
+    assert (ref.unpack_codes(q) != codes).float().mean().item() < 2e-3
+    # random Hadamard: quantised transform de-quantises back to (approximately) the transform of x^T
+    mask = 0b1011001110001101
+    q2, sf2 = ext.nvfp4_quantize_transpose(x, amax, False, True, 0, mask)
+    deq = ext.nvfp4_dequantize(q2, sf2, amax, 2.0)
+    want = ref.hadamard16(x.float().t().contiguous(), mask)
+    assert _rel(deq, want) < 0.13
+    # the transform is orthonormal: products along the transformed dimension are preserved
+    y = torch.randn(R, 64, device=DEV).bfloat16()
+    hy = ref.hadamard16(y.float().t().contiguous(), mask)
+    assert _rel(want @ hy.t(), x.float().t() @ y.float()) < 1e-3
+
+
+def test_stochastic_rounding_is_unbiased(ext):
+    x = torch.full((128, 256), 0.7, device=DEV).bfloat16()
+    x[:, ::16] = 6.0   # pins every block scale so that 0.7 falls strictly between two grid points
+    amax = torch.tensor([6.0], device=DEV)
+    acc = torch.zeros(128, 256, device=DEV)
+    n = 32
+    for seed in range(n):
+        q, sf = ext.nvfp4_quantize(x, amax, True, seed, False)
+        acc += ext.nvfp4_dequantize(q, sf, amax, 1.0).float()
+    mean = (acc / n)[:, 1:16].mean().item()
+    assert abs(mean - 0.7) < 0.02, mean
+    q, sf = ext.nvfp4_quantize(x, amax, False, 0, False)
+    rn = ext.nvfp4_dequantize(q, sf, amax, 1.0).float()[:, 1:16].mean().item()
+    assert abs(rn - 0.7) > 0.04   # round-to-nearest is biased on this input
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (256, 384, 512), (1024, 768, 2048), (300, 264, 768)])
+def test_gemm_nvfp4(ext, M, N, K):
+    torch.manual_seed(2)
+    a = (torch.randn(M, K, device=DEV) * (1 + torch.rand(M, 1, device=DEV))).bfloat16()
+    b = (torch.randn(N, K, device=DEV) * (1 + torch.rand(N, 1, device=DEV))).bfloat16()
+    am_a, am_b = a.float().abs().max().reshape(1), b.float().abs().max().reshape(1)
+    qa, sfa = ext.nvfp4_quantize(a, am_a, False, 0, False)
+    qb, sfb = ext.nvfp4_quantize(b, am_b, False, 0, False)
+    da, db = ext.nvfp4_dequantize(qa, sfa, am_a, 1.0), ext.nvfp4_dequantize(qb, sfb, am_b, 1.0)
+    ref = da.float() @ db.float().t()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    inv_a, inv_b = am_a / 2688.0, am_b / 2688.0
+    ext.gemm_nvfp4(qa, sfa, qb, sfb, out, False, 1.0, inv_a, inv_b, ext.error_flag_tensor())
+    torch.cuda.synchronize()
+    assert ext.read_error_flag(True) == 0
+    assert _rel(out, ref) < 8e-3, _rel(out, ref)
+    assert _rel(out, a.float() @ b.float().t()) < 0.2
