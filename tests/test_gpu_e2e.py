@@ -40,7 +40,7 @@ def test_cuda_backend_matches_reference_backend():
     assert abs(a.grad_norm().item() - b.grad_norm().item()) < 0.03 * b.grad_norm().item()
 
 
-@pytest.mark.parametrize("recipe,optimizer", [("bf16", "adamw_8bit"), ("fp8_hybrid", "adamw_8bit"), ("bf16", "normuon")])
+@pytest.mark.parametrize("recipe,optimizer", [("bf16", "adamw_8bit"), ("fp8_hybrid", "adamw_8bit"), ("bf16", "normuon"), ("nvfp4", "adamw_8bit")])
 def test_loss_decreases(recipe, optimizer):
     tr = _trainer("cuda", recipe=recipe, optimizer=optimizer)
     x, y = _batch(1)
@@ -101,3 +101,12 @@ def test_moe_cuda_backend_matches_reference_backend():
         assert ea < 0.1, f"{name}: rel err {ea.item():.4f}"
     losses = [a.step(x, y)["loss"] for _ in range(6)]
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+def test_nvfp4_close_to_bf16():
+    x, y = _batch(2)
+    a, b = _trainer("cuda", recipe="nvfp4"), _trainer("cuda", recipe="bf16")
+    la = [a.step(x, y)["loss"] for _ in range(4)]
+    lb = [b.step(x, y)["loss"] for _ in range(4)]
+    assert abs(la[0] - lb[0]) < 0.03 * lb[0], (la, lb)
+    assert abs(la[-1] - lb[-1]) < 0.15 * lb[-1], (la, lb)
