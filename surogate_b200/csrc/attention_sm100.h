@@ -1,0 +1,15 @@
+// Host API of the tcgen05 flash-attention kernels (attention_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace sg {
+
+// qkv: packed [B, T, (Hq + 2*Hkv) * 128] bf16.  out: [B, T, Hq*128] bf16.  lse: [B, T, Hq] fp32 (natural log).
+const char* flash_attn_fwd_sm100(const void* qkv, void* out, float* lse, int B, int T, int Hq, int Hkv, float softmax_scale, int* error_flag,
+                                 cudaStream_t stream);
+
+// Backward: d_qkv (same packed layout as qkv) from d_out; `delta` is a [B, T, Hq] fp32 workspace.
+const char* flash_attn_bwd_sm100(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta, void* d_qkv, int B, int T, int Hq,
+                                 int Hkv, float softmax_scale, int* error_flag, int num_sms, cudaStream_t stream);
+
+}  // namespace sg

@@ -324,6 +324,7 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
 }  // namespace
 
 void sg_count_launch(int n) { g_launches += n; }
+int* sg_error_flag() { return error_flag_ptr(); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("error_flag_tensor", &error_flag_tensor, "the device int32 word kernels set when a bounded wait runs out");

@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "attention_sm100.h"
 #include "comm_kernels.h"
 #include "ep_kernels.h"
 #include "gemm_sm100.h"
@@ -317,6 +318,42 @@ void gemm_nvfp4(const Tensor& a, const Tensor& sfa, const Tensor& b, const Tenso
     TORCH_CHECK(err == nullptr, err ? err : "");
 }
 
+// ---------------------------------------------------------------------------------------- attention
+std::vector<Tensor> flash_attn_fwd(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale, Tensor& error_flag) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.is_contiguous() && qkv.dim() == 3, "qkv: bf16 [B, T, (Hq+2Hkv)*128]");
+    const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
+    TORCH_CHECK(qkv.size(2) == (Hq + 2 * Hkv) * 128, "flash_attn: head_dim must be 128");
+    const c10::cuda::CUDAGuard guard(qkv.device());
+    Tensor out = torch::empty({B, T, Hq * 128}, qkv.options());
+    Tensor lse = torch::empty({B, T, Hq}, qkv.options().dtype(at::kFloat));
+    sg_count_launch(1);
+    const char* err = sg::flash_attn_fwd_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv),
+                                               static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream());
+    TORCH_CHECK(err == nullptr, err ? err : "");
+    return {out, lse};
+}
+
+std::vector<Tensor> flash_attn_fwd2(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale) {
+    Tensor flag = torch::from_blob(sg_error_flag(), {1}, torch::TensorOptions().dtype(at::kInt).device(qkv.device()));
+    return flash_attn_fwd(qkv, Hq, Hkv, scale, flag);
+}
+
+// d_out [B, T, Hq*128], qkv packed, out [B, T, Hq*128], lse [B, T, Hq] -> d_qkv (packed layout)
+Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out, const Tensor& lse, int64_t Hq, int64_t Hkv, double scale) {
+    TORCH_CHECK(d_out.is_cuda() && d_out.scalar_type() == at::kBFloat16 && d_out.is_contiguous() && out.is_contiguous() && qkv.is_contiguous(), "bf16 contiguous");
+    TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse: fp32 contiguous");
+    const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
+    const c10::cuda::CUDAGuard guard(qkv.device());
+    Tensor d_qkv = torch::empty_like(qkv);
+    Tensor delta = torch::empty_like(lse);
+    sg_count_launch(3);
+    const char* err = sg::flash_attn_bwd_sm100(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                                               d_qkv.data_ptr(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(scale),
+                                               sg_error_flag(), sms(), cur_stream());
+    TORCH_CHECK(err == nullptr, err ? err : "");
+    return d_qkv;
+}
+
 }  // namespace
 
 void sg_register_extra(pybind11::module_& m) {
@@ -336,6 +373,9 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("nvfp4_quantize_transpose", &nvfp4_quantize_transpose);
     m.def("nvfp4_dequantize", &nvfp4_dequantize);
     m.def("gemm_nvfp4", &gemm_nvfp4);
+    m.def("flash_attn_fwd_raw", &flash_attn_fwd);
+    m.def("flash_attn_fwd", &flash_attn_fwd2);
+    m.def("flash_attn_bwd", &flash_attn_bwd);
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_combine", &ep_combine);

@@ -4,3 +4,5 @@
 void sg_register_extra(pybind11::module_& m);
 // Adds n to the extension-wide count of kernels launched (read through launch_count()).
 void sg_count_launch(int n);
+// The device int32 word that kernels set when a bounded wait runs out.
+int* sg_error_flag();

@@ -89,7 +89,7 @@ __device__ __forceinline__ uint8_t quant_block16(const float (&v)[16], float ge,
 #pragma unroll
         for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
     }
-    const uint8_t sfb = __nv_cvt_float_to_fp8(amax * ge * (1.f / 6.f), __NV_SATFINITE, __NV_E4M3);
+    const uint8_t sfb = __nv_cvt_float_to_fp8(__fdiv_rn(__fmul_rn(amax, ge), 6.f), __NV_SATFINITE, __NV_E4M3);
     const float sfd = decode_e4m3(sfb);
     const float mul = sfd > 0.f ? ge / sfd : 0.f;
     out[0] = out[1] = 0;
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
                                                                   const float* __restrict__ amax_tensor, int rows, int K, int atoms_k, uint32_t seed,
                                                                   int block2d) {
     const float at = __ldg(amax_tensor);
-    const float ge = at > 0.f ? 2688.f / at : 1.f;
+    const float ge = at > 0.f ? __fdiv_rn(2688.f, at) : 1.f;
     const int kblocks = K / 16;
     const size_t total = static_cast<size_t>(rows) * kblocks;
     // warp-uniform trip count: the 16x16-tile path shuffles across lanes

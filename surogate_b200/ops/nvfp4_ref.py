@@ -30,7 +30,8 @@ def quantize(x: torch.Tensor, amax: float | torch.Tensor | None = None, block2d:
     x = x.float()
     rows, K = x.shape
     at = x.abs().max() if amax is None else torch.as_tensor(amax, dtype=torch.float32, device=x.device)
-    ge = torch.where(at > 0, ENCODE / at, torch.ones_like(at))
+    # correctly rounded fp32 quotient (GPU tensor division may be off by an ulp, which flips exact rounding ties)
+    ge = torch.tensor(float(torch.tensor(ENCODE / float(at), dtype=torch.float32)) if float(at) > 0 else 1.0, device=x.device)
     xb = x.view(rows, K // 16, 16)
     bmax = xb.abs().amax(-1)
     if block2d:

@@ -168,6 +168,8 @@ class SymmComm:
             self.ext.all_gather_fused(self.arena.peer_bases, off, shard.numel(), lo, hi, full, out_fp8, scale, self.max_blocks)
             if full is not None:
                 full.record_stream(self.stream)
+            if scale is not None:
+                scale.record_stream(self.stream)
             if out_fp8 is not None:
                 out_fp8.record_stream(self.stream)
         return self._done(async_op)

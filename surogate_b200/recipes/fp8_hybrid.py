@@ -129,7 +129,13 @@ class FP8HybridRecipe(Recipe):
         return Fp8Tensor(y8, self.scale_inv[q:q + 1])
 
     # ------------------------------------------------------------------ GEMMs
-    def _weight(self, ctx, ext, role: str, w: torch.Tensor) -> Fp8Tensor:
+    def quantizes(self, layer, role: str) -> bool:
+        return layer is not None and layer not in self.skip and role in QUANT_ROLES
+
+    def _weight(self, ctx, ext, role: str, w: torch.Tensor, pname: str = "") -> Fp8Tensor:
+        pre = ctx.ex.store.get_fp8(ctx.full_name(pname)) if pname else None
+        if pre is not None:   # already E4M3: written by the quantise-on-gather kernel with this tensor's scale
+            return Fp8Tensor(pre[0], pre[1])
         key = (ctx.layer, role)
         cached = self.weight_cache.get(key)
         if cached is not None:
@@ -161,7 +167,7 @@ class FP8HybridRecipe(Recipe):
             x = self._quantize(ext, x.reshape(-1, K), self.slot(ctx.layer, role, "x"), False)
             ctx.stash[("fp8x", ctx.layer, op.outputs[0])] = x
         x2 = x.reshape(-1, K)
-        w8 = self._weight(ctx, ext, role, w)
+        w8 = self._weight(ctx, ext, role, w, op.inputs[1])
         y = gemm(x2.data, w8.data, scale_a=x2.scale_inv, scale_b=w8.scale_inv)
         y = y.reshape(*lead, w.shape[0])
         if bias is not None:
@@ -179,7 +185,7 @@ class FP8HybridRecipe(Recipe):
             saved = ctx.stash.pop(("fp8x", ctx.layer, op.attrs.get("fwd_out")), None)
             x2 = saved if saved is not None else self._quantize(ext, x2, self.slot(ctx.layer, role, "x"), False)
         dy8 = self._quantize(ext, dy2, self.slot(ctx.layer, role, "dy"), True)
-        w8 = self._weight(ctx, ext, role, w)
+        w8 = self._weight(ctx, ext, role, w, op.inputs[2])
         dx = gemm(dy8.data, w8.data, a_mn=False, b_mn=True, scale_a=dy8.scale_inv, scale_b=w8.scale_inv)
         tgt, acc = ctx.grad_target(op.outputs[1])
         if tgt is not None:

@@ -57,6 +57,7 @@ class Bucket:
         self.shard_numel = 0
         self.master: Optional[torch.Tensor] = None  # [shard_numel] (or full when world == 1 / level 0)
         self.work: Optional[torch.Tensor] = None  # [numel] gathered work weights (None when released)
+        self.work_fp8: Optional[torch.Tensor] = None  # [numel] bytes: E4M3 copy written by the quantise-on-gather kernel
         self.grad: Optional[torch.Tensor] = None  # [numel] full-size gradient buffer
         self.grad_shard: Optional[torch.Tensor] = None  # [shard_numel] reduced gradient owned by this rank
         self.gather_work: Any = None
@@ -117,6 +118,8 @@ class ParamStore:
         self.last_micro_step = True
         self.grads_enabled = True
         self.post_gather: Optional[Callable[[Bucket], None]] = None
+        self.fp8_gather = False  # quantise-on-gather (ZeRO-3 + FP8 recipe + peer-memory kernels)
+        self.fp8_roles: Dict[str, str] = {}
         self._build()
 
     # ------------------------------------------------------------------ layout
@@ -278,6 +281,8 @@ class ParamStore:
         fence = getattr(self.comm, "fence", None)
         if fence is not None and self.sharded:
             fence()  # peers pull master shards directly: every rank must have finished writing its own first
+        if self.fp8_gather:
+            self.refresh_weight_scales()
         for b in self.buckets.values():
             if b.expert:
                 if b.work is not b.master:
@@ -285,6 +290,7 @@ class ParamStore:
                 continue
             if self.zero_level >= 3:
                 b.work = None
+                b.work_fp8 = None
                 b.gather_work = None
                 continue
             if b.work is b.master:
@@ -292,6 +298,79 @@ class ParamStore:
             self._gather_into(b, b.work)
             if self.post_gather is not None:
                 self.post_gather(b)
+
+    # ------------------------------------------------------------------ FP8 quantise-on-gather
+    FP8_SLOT_ROLES = {"qkv_weight": "qkv", "out_weight": "out", "mlp_up_weight": "mlp_up", "mlp_down_weight": "mlp_down"}
+
+    def enable_fp8_gather(self, wants: Callable[[Optional[int], str], bool]) -> bool:
+        """Gather ZeRO-3 weights straight into FP8: the gather kernel pulls the peers' bf16 shards and writes E4M3 with the
+        tensor's scale, so the gathered bf16 copy and the separate abs-max / quantise passes disappear.  ``wants(layer, role)``
+        says which projections the recipe runs in FP8.  Needs the peer-memory communicator and an arena."""
+        if self.zero_level < 3 or self.arena is None or self.param_dtype != torch.bfloat16:
+            return False
+        self.q_index: Dict[str, int] = {}
+        for b in self.buckets.values():
+            if b.layer is None or b.expert:
+                continue
+            for sl in b.slots:
+                role = self.FP8_SLOT_ROLES.get(sl.entry.local)
+                if role and wants(b.layer, role):
+                    self.q_index[sl.name] = len(self.q_index)
+        if not self.q_index or len(self.q_index) > 1024:
+            return False
+        n = len(self.q_index)
+        self.w_amax = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.w_scale = torch.ones(n, dtype=torch.float32, device=self.device)
+        self.w_scale_inv = torch.ones(n, dtype=torch.float32, device=self.device)
+        self.fp8_gather = True
+        return True
+
+    def refresh_weight_scales(self) -> None:
+        """Per-tensor scales of the FP8 weights from the current masters: shard-local abs-max, one small max all-reduce."""
+        from ..ops import ext
+
+        e = ext()
+        self.w_amax.zero_()
+        for b in self.buckets.values():
+            lo, hi = self.shard_range(b)
+            for sl in b.slots:
+                i = self.q_index.get(sl.name)
+                if i is None:
+                    continue
+                a, z = max(sl.offset, lo), min(sl.offset + sl.numel, hi)
+                if a < z:
+                    e.amax(b.master[a - lo:z - lo], self.w_amax[i:i + 1])
+        self.comm.all_reduce(self.w_amax, "max")
+        torch.where(self.w_amax > 0, 448.0 / self.w_amax, torch.ones_like(self.w_amax), out=self.w_scale)
+        torch.reciprocal(self.w_scale, out=self.w_scale_inv)
+
+    def get_fp8(self, name: str):
+        """(E4M3 weight view, de-scale) of a parameter gathered in FP8, or None."""
+        if not self.fp8_gather:
+            return None
+        name = self.resolve(name)
+        i = self.q_index.get(name)
+        if i is None:
+            return None
+        b, sl = self.where[name]
+        if b.work_fp8 is None or b.gather_work is not None:
+            self._ensure_gathered(b)
+        return b.work_fp8[sl.offset:sl.offset + sl.numel].view(sl.shape).view(torch.float8_e4m3fn), self.w_scale_inv[i:i + 1]
+
+    def _gather_fp8(self, b: Bucket):
+        """One fused pull per parameter: FP8 for the quantised projections, bf16 for the rest (norm weights ...)."""
+        b.work = torch.empty(b.numel, dtype=self.param_dtype, device=self.device)
+        b.work_fp8 = torch.empty(b.numel, dtype=torch.uint8, device=self.device)
+        works = []
+        for sl in b.slots:
+            end = (sl.offset + sl.numel + 7) // 8 * 8
+            i = self.q_index.get(sl.name)
+            if i is not None:
+                w = self.comm.all_gather(b.master, None, async_op=True, out_fp8=b.work_fp8, scale=self.w_scale[i:i + 1], segment=(sl.offset, end))
+            else:
+                w = self.comm.all_gather(b.master, b.work, async_op=True, segment=(sl.offset, end))
+            works.append(w)
+        return works[-1] if works else None   # same communication stream: the last event covers all of them
 
     def _gather_into(self, b: Bucket, full: torch.Tensor, async_op: bool = False):
         src = b.master if b.master.dtype == full.dtype else b.master.to(full.dtype)
@@ -303,8 +382,11 @@ class ParamStore:
     # ------------------------------------------------------------------ executor hooks
     def _ensure_gathered(self, b: Bucket, prefetch_only: bool = False) -> None:
         if b.work is None:
-            b.work = torch.empty(b.numel, dtype=self.param_dtype, device=self.device)
-            b.gather_work = self._gather_into(b, b.work, async_op=True)
+            if self.fp8_gather and b.layer is not None and not b.expert:
+                b.gather_work = self._gather_fp8(b)
+            else:
+                b.work = torch.empty(b.numel, dtype=self.param_dtype, device=self.device)
+                b.gather_work = self._gather_into(b, b.work, async_op=True)
             b._needs_post = True
         if not prefetch_only:
             if b.gather_work is not None:
@@ -318,6 +400,7 @@ class ParamStore:
     def _release(self, b: Bucket) -> None:
         if self.zero_level >= 3 and not b.expert:
             b.work = None
+            b.work_fp8 = None
 
     def _layer_bucket(self, L: int) -> Optional[Bucket]:
         return self.buckets.get(f"layer{L}")

@@ -112,6 +112,8 @@ class Trainer:
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
         rname = cfg.recipe if (on_gpu and self.backend.name == "cuda") else "bf16"
         self.recipe = make_recipe(rname, self.cm, self.device, **self._recipe_kwargs(rname))
+        if hasattr(self.recipe, "quantizes") and rname.replace("-", "_") == "fp8_hybrid" and cfg.lora is None:
+            self.store.enable_fp8_gather(self.recipe.quantizes)
         self.ep = None
         if cfg.ep_size > 1:
             from ..parallel.ep import ExpertParallel

@@ -49,7 +49,8 @@ def main():
         tr.save_checkpoint(a["checkpoint_dir"], step=len(losses))
     if info.rank == 0:
         print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "comm": type(tr.comm).__name__,
-                                      "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid), **extra}), flush=True)
+                                      "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),
+                                      "fp8_gather": bool(tr.store.fp8_gather), **extra}), flush=True)
     if info.world > 1:
         import torch.distributed as dist
 
