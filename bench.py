@@ -123,6 +123,7 @@ def main():
     ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "symm"])
     ap.add_argument("--ep", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--attention", default="auto", choices=["auto", "native", "library"], help="native = tcgen05 flash attention of this repo")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -156,7 +157,7 @@ def main():
     ep = args.ep if args.ep is not None else (world if args.model == "qwen3-30b-a3b" else 1)
     cfg = TrainerConfig(model=spec["model"], batch_size=mb, seq_len=seq, grad_accum=1, recipe=recipe, optimizer=args.optimizer or spec["optimizer"],
                         learning_rate=1e-4, weight_decay=0.1, zero_level=zero, recompute=args.recompute,
-                        backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep)
+                        backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention)
     tr = Trainer(cfg, device=dev, comm=comm)
     tr.init_weights(seed=0)
     V = spec["model"]["vocab_size"]
@@ -226,7 +227,7 @@ def main():
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None, "dtype": "fp8" if recipe.startswith("fp8") else recipe,
             "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": args.impl,
             "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
-                       "optimizer": cfg.optimizer, "recompute": bool(args.recompute), "micro_batch_per_gpu": mb,
+                       "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(args.recompute), "micro_batch_per_gpu": mb,
                        "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events on the launching stream, barrier+synchronize on both sides, max over ranks"},
             "clocks": clocks, "gpu_launches": int(launches),

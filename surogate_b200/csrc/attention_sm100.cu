@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd_dkv_kernel(const __grid_con
 #pragma unroll
                 for (int k = 0; k < 32; ++k) {
                     const int qc = c * 32 + k;   // query column
-                    float pr = exp2f(__uint_as_float(rs[k]) * p.scale_log2 - lse2[qc]);
+                    float pr = ex2_approx(fmaf(__uint_as_float(rs[k]), p.scale_log2, -lse2[qc]));
                     if (diag && r > qc) pr = 0.f;
                     pv[k] = pr;
                     ds[k] = pr * (__uint_as_float(rd[k]) - dl[qc]) * p.scale;
@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd_dq_kernel(const __grid_cons
 #pragma unroll
                 for (int k = 0; k < 32; ++k) {
                     const int kc = c * 32 + k;   // key column
-                    float pr = exp2f(__uint_as_float(rs[k]) * p.scale_log2 - lse2);
+                    float pr = ex2_approx(fmaf(__uint_as_float(rs[k]), p.scale_log2, -lse2));
                     if (diag && kc > r) pr = 0.f;
                     ds[k] = pr * (__uint_as_float(rd[k]) - dl) * p.scale;
                 }
@@ -567,7 +567,7 @@ const char* flash_attn_fwd_sm100(const void* qkv, void* out, float* lse, int B, 
 }
 
 const char* flash_attn_bwd_sm100(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta, void* d_qkv, int B, int T, int Hq,
-                                 int Hkv, float softmax_scale, int* error_flag, int num_sms, cudaStream_t stream) {
+                                 int Hkv, float softmax_scale, int* error_flag, int num_sms, cudaStream_t stream, int variant) {
     using namespace fa;
     if (T % 128 != 0) return "flash_attn_bwd: T must be a multiple of 128";
     CUtensorMap tm_qkv, tm_do;
@@ -587,6 +587,7 @@ const char* flash_attn_bwd_sm100(const void* qkv, const void* out, const void* d
     int grid = static_cast<int>((items + 7) / 8);
     if (grid > num_sms * 8) grid = num_sms * 8;
     fa_delta_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, items);
+    if (variant != 128) return flash_attn_bwd64_sm100(qkv, d_out, lse, delta, d_qkv, B, T, Hq, Hkv, softmax_scale, error_flag, stream);
     BwdParams p{static_cast<__nv_bfloat16*>(d_qkv), lse, delta, T, Hq, Hkv, softmax_scale, softmax_scale * 1.4426950408889634f, error_flag};
     fa_bwd_dkv_kernel<<<dim3(T / 128, Hkv, B), THREADS, DKV_SMEM, stream>>>(tm_qkv, tm_do, p);
     fa_bwd_dq_kernel<<<dim3(T / 128, Hq, B), THREADS, DQ_SMEM, stream>>>(tm_qkv, tm_do, p);

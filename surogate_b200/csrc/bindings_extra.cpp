@@ -3,6 +3,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+#include <string>
+
 #include "attention_sm100.h"
 #include "comm_kernels.h"
 #include "ep_kernels.h"
@@ -327,10 +330,36 @@ std::vector<Tensor> flash_attn_fwd(const Tensor& qkv, int64_t Hq, int64_t Hkv, d
     Tensor out = torch::empty({B, T, Hq * 128}, qkv.options());
     Tensor lse = torch::empty({B, T, Hq}, qkv.options().dtype(at::kFloat));
     sg_count_launch(1);
-    const char* err = sg::flash_attn_fwd_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv),
-                                               static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream());
+    static const bool use_v1 = []() { const char* v = std::getenv("SUROGATE_ATTN_FWD"); return v && std::string(v) == "128"; }();
+    const char* err = use_v1 ? sg::flash_attn_fwd_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq),
+                                                        static_cast<int>(Hkv), static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream())
+                             : sg::flash_attn_fwd64_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq),
+                                                          static_cast<int>(Hkv), static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream());
     TORCH_CHECK(err == nullptr, err ? err : "");
     return {out, lse};
+}
+
+Tensor flash_attn_fwd_profile(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale) {
+    const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
+    Tensor out = torch::empty({B, T, Hq * 128}, qkv.options());
+    Tensor lse = torch::empty({B, T, Hq}, qkv.options().dtype(at::kFloat));
+    Tensor prof = torch::zeros({8}, qkv.options().dtype(at::kLong));
+    const char* err = sg::flash_attn_fwd64_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv),
+                                                 static_cast<float>(scale), sg_error_flag(), cur_stream(), reinterpret_cast<long long*>(prof.data_ptr<int64_t>()));
+    TORCH_CHECK(err == nullptr, err ? err : "");
+    return prof;
+}
+
+Tensor flash_attn_bwd_profile(const Tensor& d_out, const Tensor& qkv, const Tensor& lse, int64_t Hq, int64_t Hkv, double scale) {
+    const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
+    Tensor d_qkv = torch::empty_like(qkv);
+    Tensor delta = torch::zeros_like(lse);
+    Tensor prof = torch::zeros({16}, qkv.options().dtype(at::kLong));
+    const char* err = sg::flash_attn_bwd64_sm100(qkv.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(), d_qkv.data_ptr(), B, T,
+                                                 static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(scale), sg_error_flag(), cur_stream(),
+                                                 reinterpret_cast<long long*>(prof.data_ptr<int64_t>()));
+    TORCH_CHECK(err == nullptr, err ? err : "");
+    return prof;
 }
 
 std::vector<Tensor> flash_attn_fwd2(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale) {
@@ -344,12 +373,13 @@ Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out,
     TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse: fp32 contiguous");
     const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
     const c10::cuda::CUDAGuard guard(qkv.device());
+    static const int bwd_variant = []() { const char* v = std::getenv("SUROGATE_ATTN_BWD"); return (v && std::string(v) == "128") ? 128 : 64; }();
     Tensor d_qkv = torch::empty_like(qkv);
     Tensor delta = torch::empty_like(lse);
     sg_count_launch(3);
     const char* err = sg::flash_attn_bwd_sm100(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
                                                d_qkv.data_ptr(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(scale),
-                                               sg_error_flag(), sms(), cur_stream());
+                                               sg_error_flag(), sms(), cur_stream(), bwd_variant);
     TORCH_CHECK(err == nullptr, err ? err : "");
     return d_qkv;
 }
@@ -376,6 +406,8 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("flash_attn_fwd_raw", &flash_attn_fwd);
     m.def("flash_attn_fwd", &flash_attn_fwd2);
     m.def("flash_attn_bwd", &flash_attn_bwd);
+    m.def("flash_attn_bwd_profile", &flash_attn_bwd_profile, "per-phase cycle counters of the backward passes (development aid)");
+    m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_combine", &ep_combine);

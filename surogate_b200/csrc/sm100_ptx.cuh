@@ -143,6 +143,13 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x on the special-function unit, flush-to-zero (inputs here are <= ~8; large negative inputs give 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle.  Byte offsets are encoded >> 4.
 //   K-major operand  : rows of 128 B (one swizzle atom = 8 rows = 1024 B); sbo = 1024, lbo unused.
