@@ -1,0 +1,45 @@
+// Declarations shared by the host runtime sources and their Python bindings.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace sg {
+
+// cpu_optim.cpp
+void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool grad_is_bf16, uint16_t* work_bf16, int64_t n, float lr, float beta1,
+                    float beta2, float eps, float weight_decay, float grad_scale, int64_t step);
+double cpu_sum_squares(const void* x, bool is_bf16, int64_t n);
+
+// lpt_planner.cpp
+struct ExpertChunk {
+    int gpu, token_start, token_end;
+};
+struct WeightMove {
+    int expert, src_rank, dst_rank;
+};
+struct LptPlan {
+    std::vector<std::vector<ExpertChunk>> assignments;  // per expert
+    std::vector<WeightMove> moves;
+    std::vector<int64_t> gpu_loads;
+    std::vector<int> expert_to_gpu;  // rank that handles most of the expert's tokens
+    bool uses_lpt = false;
+    float imbalance = 1.0f;
+};
+float imbalance_ratio(const int64_t* counts, int num_experts, int ep_size);
+LptPlan compute_lpt_plan(const int64_t* counts, int num_experts, int ep_size, float threshold, float capacity_factor, int min_tokens_per_gemm);
+
+// crash_handler.cpp
+void install_crash_handler(const std::string& tag);
+
+// nvml_info.cpp
+struct GpuTelemetry {
+    bool ok = false;
+    std::string name, error;
+    unsigned sm_clock_mhz = 0, sm_clock_max_mhz = 0, mem_clock_mhz = 0, power_mw = 0, power_limit_mw = 0, temperature_c = 0, gpu_util = 0, mem_util = 0;
+    unsigned long long mem_used = 0, mem_total = 0, throttle_reasons = 0, pcie_rx_kbs = 0, pcie_tx_kbs = 0;
+};
+GpuTelemetry query_gpu(int index);  // read-only NVML queries through a dlopen'ed libnvidia-ml
+
+}  // namespace sg

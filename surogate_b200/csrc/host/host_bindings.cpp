@@ -1,0 +1,140 @@
+// Python bindings of the host runtime (no CUDA dependency): tokenizer, token-shard loader, safetensors I/O, CPU AdamW,
+// expert-parallel LPT planner, crash handler, NVML telemetry.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "bpe_tokenizer.h"
+#include "host_api.h"
+#include "safetensors_io.h"
+#include "token_loader.h"
+
+namespace py = pybind11;
+using namespace sg;
+
+static void* ptr(uintptr_t p) { return reinterpret_cast<void*>(p); }
+
+PYBIND11_MODULE(sg_b200_host, m) {
+    m.doc() = "surogate_b200 native host runtime";
+
+    py::class_<BpeTokenizer, std::shared_ptr<BpeTokenizer>>(m, "BpeTokenizer")
+        .def_static("from_file", &BpeTokenizer::from_file)
+        .def_static("from_json", &BpeTokenizer::from_json)
+        .def("encode", [](const BpeTokenizer& t, const std::string& s, bool added) {
+                 py::gil_scoped_release rel;
+                 return t.encode(s, added);
+             }, py::arg("text"), py::arg("allow_added_tokens") = true)
+        .def("encode_batch", [](const BpeTokenizer& t, const std::vector<std::string>& v, bool added, int threads) {
+                 py::gil_scoped_release rel;
+                 return t.encode_batch(v, added, threads);
+             }, py::arg("texts"), py::arg("allow_added_tokens") = true, py::arg("threads") = 0)
+        .def("decode", [](const BpeTokenizer& t, const std::vector<int32_t>& ids, bool skip) { return py::bytes(t.decode(ids, skip)); },
+             py::arg("ids"), py::arg("skip_special") = false)
+        .def("pre_tokenize", [](const BpeTokenizer& t, const std::string& s) {
+                 std::vector<py::bytes> out;
+                 for (auto& w : t.pre_tokenize(s)) out.emplace_back(w);
+                 return out;
+             })
+        .def("vocab_size", &BpeTokenizer::vocab_size)
+        .def("token_to_id", [](const BpeTokenizer& t, const py::bytes& b) { return t.token_to_id(std::string(b)); })
+        .def("id_to_token", [](const BpeTokenizer& t, int32_t id) { return py::bytes(t.id_to_token(id)); })
+        .def("is_special", &BpeTokenizer::is_special)
+        .def("added_tokens", &BpeTokenizer::added_tokens)
+        .def("style", [](const BpeTokenizer& t) {
+            auto s = t.style();
+            return py::dict(py::arg("legacy_gpt2") = s.legacy_gpt2, py::arg("contractions_ignore_case") = s.contractions_ignore_case,
+                            py::arg("max_digits") = s.max_digits);
+        });
+    m.def("unicode_class", [](uint32_t cp) { return unicode_is_letter(cp) ? "L" : unicode_is_number(cp) ? "N" : unicode_is_space(cp) ? "S" : "O"; });
+
+    py::class_<TokenLoader>(m, "TokenLoader")
+        .def(py::init<const std::vector<std::string>&, int, int, int64_t, int, int, bool, int>(), py::arg("files"), py::arg("batch"), py::arg("seq_len"),
+             py::arg("seed") = 0, py::arg("rank") = 0, py::arg("world") = 1, py::arg("shuffle") = true, py::arg("prefetch") = 2)
+        .def("next_into", [](TokenLoader& l, uintptr_t x, uintptr_t y, uintptr_t p) {
+                 py::gil_scoped_release rel;
+                 l.next(static_cast<int32_t*>(ptr(x)), static_cast<int32_t*>(ptr(y)), static_cast<int32_t*>(ptr(p)));
+             })
+        .def("state", [](const TokenLoader& l) {
+                 auto s = l.state();
+                 return py::dict(py::arg("seed") = s.seed, py::arg("epoch") = s.epoch, py::arg("file_index") = s.file_index, py::arg("chunk_index") = s.chunk_index);
+             })
+        .def("set_state", [](TokenLoader& l, int64_t seed, int64_t epoch, int64_t fi, int64_t ci) { l.set_state(LoaderState{seed, epoch, fi, ci}); })
+        .def("steps_per_epoch", &TokenLoader::steps_per_epoch)
+        .def("total_chunks", &TokenLoader::total_chunks)
+        .def("vocab", &TokenLoader::vocab);
+    m.def("shuffled_order", &shuffled_order);
+
+    py::class_<SafetensorsFile>(m, "SafetensorsFile")
+        .def(py::init<const std::string&>())
+        .def("entries", [](const SafetensorsFile& f) {
+                 py::dict d;
+                 for (auto& e : f.entries()) d[py::str(e.name)] = py::make_tuple(e.dtype, e.shape, e.begin, e.end);
+                 return d;
+             })
+        .def("metadata", &SafetensorsFile::metadata)
+        .def("read_into", [](const SafetensorsFile& f, const std::string& name, uintptr_t dst, uint64_t nbytes, uint64_t off, int threads) {
+                 py::gil_scoped_release rel;
+                 f.read_into(name, ptr(dst), nbytes, off, threads);
+             }, py::arg("name"), py::arg("dst"), py::arg("nbytes"), py::arg("offset") = 0, py::arg("threads") = 8)
+        .def("read_rows", [](const SafetensorsFile& f, const std::string& name, uintptr_t dst, int64_t r0, int64_t r1, int threads) {
+                 py::gil_scoped_release rel;
+                 f.read_rows(name, ptr(dst), r0, r1, threads);
+             }, py::arg("name"), py::arg("dst"), py::arg("row_begin"), py::arg("row_end"), py::arg("threads") = 8);
+    m.def("write_safetensors", [](const std::string& path, const std::vector<std::tuple<std::string, std::string, std::vector<int64_t>, uintptr_t, uint64_t>>& items,
+                                  const std::map<std::string, std::string>& meta, int threads) {
+              std::vector<StWriteItem> v;
+              for (auto& it : items) v.push_back({std::get<0>(it), std::get<1>(it), std::get<2>(it), ptr(std::get<3>(it)), std::get<4>(it)});
+              py::gil_scoped_release rel;
+              return write_safetensors(path, v, meta, threads);
+          }, py::arg("path"), py::arg("items"), py::arg("metadata") = std::map<std::string, std::string>{}, py::arg("threads") = 8);
+    m.def("dtype_size", &dtype_size);
+
+    m.def("cpu_adamw_step", [](uintptr_t param, uintptr_t mm, uintptr_t vv, uintptr_t grad, bool grad_bf16, uintptr_t work, int64_t n, float lr, float b1,
+                               float b2, float eps, float wd, float grad_scale, int64_t step) {
+              py::gil_scoped_release rel;
+              cpu_adamw_step(static_cast<float*>(ptr(param)), static_cast<float*>(ptr(mm)), static_cast<float*>(ptr(vv)), ptr(grad), grad_bf16,
+                             static_cast<uint16_t*>(ptr(work)), n, lr, b1, b2, eps, wd, grad_scale, step);
+          });
+    m.def("cpu_sum_squares", [](uintptr_t x, bool bf16, int64_t n) {
+        py::gil_scoped_release rel;
+        return cpu_sum_squares(ptr(x), bf16, n);
+    });
+
+    m.def("imbalance_ratio", [](const std::vector<int64_t>& counts, int ep) { return imbalance_ratio(counts.data(), static_cast<int>(counts.size()), ep); });
+    m.def("compute_lpt_plan", [](const std::vector<int64_t>& counts, int ep, float threshold, float cap, int min_chunk) {
+              LptPlan p = compute_lpt_plan(counts.data(), static_cast<int>(counts.size()), ep, threshold, cap, min_chunk);
+              py::list assign;
+              for (auto& chunks : p.assignments) {
+                  py::list l;
+                  for (auto& c : chunks) l.append(py::make_tuple(c.gpu, c.token_start, c.token_end));
+                  assign.append(l);
+              }
+              py::list moves;
+              for (auto& mv : p.moves) moves.append(py::make_tuple(mv.expert, mv.src_rank, mv.dst_rank));
+              return py::dict(py::arg("assignments") = assign, py::arg("moves") = moves, py::arg("gpu_loads") = p.gpu_loads,
+                              py::arg("expert_to_gpu") = p.expert_to_gpu, py::arg("uses_lpt") = p.uses_lpt, py::arg("imbalance") = p.imbalance);
+          }, py::arg("counts"), py::arg("ep_size"), py::arg("threshold") = 1.3f, py::arg("capacity_factor") = 1.1f, py::arg("min_tokens_per_gemm") = 1024);
+
+    m.def("install_crash_handler", &install_crash_handler, py::arg("tag") = "surogate_b200");
+    m.def("query_gpu", [](int index) {
+        GpuTelemetry t = query_gpu(index);
+        py::dict d;
+        d["ok"] = t.ok;
+        d["error"] = t.error;
+        d["name"] = t.name;
+        d["sm_clock_mhz"] = t.sm_clock_mhz;
+        d["sm_clock_max_mhz"] = t.sm_clock_max_mhz;
+        d["mem_clock_mhz"] = t.mem_clock_mhz;
+        d["power_w"] = t.power_mw / 1000.0;
+        d["power_limit_w"] = t.power_limit_mw / 1000.0;
+        d["temperature_c"] = t.temperature_c;
+        d["gpu_util"] = t.gpu_util;
+        d["mem_util"] = t.mem_util;
+        d["mem_used"] = t.mem_used;
+        d["mem_total"] = t.mem_total;
+        d["throttle_reasons"] = t.throttle_reasons;
+        d["pcie_rx_kbs"] = t.pcie_rx_kbs;
+        d["pcie_tx_kbs"] = t.pcie_tx_kbs;
+        return d;
+    });
+}

@@ -4,8 +4,9 @@ Serves ``batch x seq_len`` int32 (inputs, targets, position_ids) per call.  Orde
 shuffle (files, then chunks inside a file) that depends only on (seed, epoch), so a run can be resumed
 from ``state_dict()`` = (seed, epoch, file_index, chunk_index) and a rank can take every world-th chunk.
 Targets are the inputs shifted by one; positions whose loss mask is 0 and the last position of a packed row
-become -100.  The heavy lifting (mmap, shuffle, gather into a pinned batch) is done by the native helper in
-``csrc/dataloader.cpp`` when the extension is present, by numpy otherwise.
+become -100.  The heavy lifting (mmap, shuffle, batch assembly on a prefetch thread) is done by the native
+``TokenLoader`` (``csrc/host/token_loader.cpp``) when the host runtime is built; the numpy path below produces the
+same batches in the same order and is what runs otherwise.
 
 Parity: csrc/src/runtime/training/dataloader.{h,cpp} (DataLoader dataloader.h:39).
 """
@@ -18,14 +19,48 @@ import numpy as np
 from .tokfile import read_token_file
 
 IGNORE = -100
+_M64 = (1 << 64) - 1
+
+
+def shuffled_order(n: int, seed: int, epoch: int, salt: int, shuffle: bool = True) -> np.ndarray:
+    """Fisher-Yates driven by splitmix64: the same permutation as the native loader's ``shuffled_order``."""
+    v = np.arange(n, dtype=np.int64)
+    if not shuffle or n < 2:
+        return v
+    s = ((seed & _M64) * 0x9E3779B97F4A7C15 & _M64) ^ (((epoch + 0x1000) & _M64) * 0xC2B2AE3D27D4EB4F & _M64) ^ \
+        (((salt + 0x2000) & _M64) * 0x165667B19E3779F9 & _M64)
+    out = v.tolist()
+    for i in range(n - 1, 0, -1):
+        s = (s + 0x9E3779B97F4A7C15) & _M64
+        z = s
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+        z ^= z >> 31
+        j = z % (i + 1)
+        out[i], out[j] = out[j], out[i]
+    return np.asarray(out, dtype=np.int64)
+
+
+def _native():
+    try:
+        from ..ops import host
+
+        return host()
+    except Exception:  # noqa: BLE001
+        return None
 
 
 class DataLoader:
-    def __init__(self, files: Sequence[str], batch: int, seq_len: int, seed: int = 0, rank: int = 0, world: int = 1, shuffle: bool = True):
+    def __init__(self, files: Sequence[str], batch: int, seq_len: int, seed: int = 0, rank: int = 0, world: int = 1, shuffle: bool = True,
+                 native: Optional[bool] = None, prefetch: int = 2):
         if not files:
             raise ValueError("DataLoader needs at least one token file")
         self.files = list(files)
         self.batch, self.T, self.seed, self.rank, self.world, self.shuffle = batch, seq_len, seed, rank, world, shuffle
+        mod = _native() if native in (None, True) else None
+        if native is True and mod is None:
+            raise RuntimeError("the native host runtime is not built")
+        self._nat = mod.TokenLoader(self.files, batch, seq_len, seed, rank, world, shuffle, prefetch) if mod is not None else None
         self.epoch = 0
         self.file_index = 0
         self.chunk_index = 0
@@ -42,9 +77,7 @@ class DataLoader:
         return n_tokens // self.T if non_overlapping else max(0, (n_tokens - 1) // self.T)
 
     def _order(self, n: int, salt: int) -> np.ndarray:
-        if not self.shuffle:
-            return np.arange(n)
-        return np.random.default_rng([self.seed, self.epoch, salt]).permutation(n)
+        return shuffled_order(n, self.seed, self.epoch, salt, self.shuffle)
 
     def _open(self, fi: int):
         path = self.files[self._file_order[fi]]
@@ -71,6 +104,11 @@ class DataLoader:
         x = np.empty((B, T), np.int32)
         y = np.empty((B, T), np.int32)
         p = np.empty((B, T), np.int32)
+        if self._nat is not None:
+            self._nat.next_into(x.ctypes.data, y.ctypes.data, p.ctypes.data)
+            st = self._nat.state()
+            self.epoch, self.file_index, self.chunk_index = st["epoch"], st["file_index"], st["chunk_index"]
+            return x, y, p
         row = 0
         guard = 0
         while row < B:
@@ -111,6 +149,20 @@ class DataLoader:
         self.file_index, self.chunk_index = int(st["file_index"]), int(st["chunk_index"])
         self._file_order = self._order(len(self.files), salt=0)
         self._cur = None
+        if self._nat is not None:
+            self._nat.set_state(self.seed, self.epoch, self.file_index, self.chunk_index)
+
+    def next_batch_pinned(self, x, y, p) -> None:
+        """Native path: write the batch straight into caller-owned (pinned) int32 tensors of shape [batch, seq_len]."""
+        if self._nat is None:
+            a, b, c = self.next_batch()
+            x.numpy()[...] = a
+            y.numpy()[...] = b
+            p.numpy()[...] = c
+            return
+        self._nat.next_into(x.data_ptr(), y.data_ptr(), p.data_ptr())
+        st = self._nat.state()
+        self.epoch, self.file_index, self.chunk_index = st["epoch"], st["file_index"], st["chunk_index"]
 
 
 def write_synthetic_tokens(path: str, n_rows: int, seq_len: int, vocab: int, seed: int = 0) -> str:

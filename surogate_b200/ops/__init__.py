@@ -14,6 +14,19 @@ def ext():
             "`python -c 'import __graft_entry__ as g; g.build()'` — GPU ops do not fall back to PyTorch") from e
 
 
+def host():
+    """The CUDA-free native host runtime (tokenizer, token loader, safetensors I/O, CPU AdamW, LPT planner, telemetry)."""
+    from . import _build
+
+    return _build.load_host()
+
+
+def host_available() -> bool:
+    from . import _build
+
+    return _build.host_available()
+
+
 def check_device_errors(reset: bool = True) -> None:
     """Raise if any kernel reported a pipeline time-out (bounded waits) since the last check. Synchronises."""
     flag = ext().read_error_flag(reset)

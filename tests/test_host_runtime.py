@@ -1,0 +1,181 @@
+"""Native host runtime (CUDA-free C++): tokenizer, token loader, safetensors I/O, CPU AdamW, LPT planner, telemetry."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from surogate_b200.ops import host, host_available
+
+pytestmark = pytest.mark.skipif(not host_available(), reason="host runtime not built")
+
+CORPUS = [
+    "Hello world! It's a test, isn't it? We'll see what they've done.",
+    "def f(x):\n    return x**2 + 12345  # comment\n\n\nclass A:  pass",
+    "Ünïcödé tèxt — 中文字符 和 日本語 テキスト 1234567 ٣٤٥",
+    "   leading spaces\tand\ttabs \n trailing  \r\n windows line   ",
+    "I'M SHOUTING, DON'T YOU'RE — emojis 🙂🙃 and symbols ###$$$ ...",
+]
+
+
+def _train_tokenizer(pattern, tmp_path, name):
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pattern), behavior="isolated"),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(CORPUS * 4, trainer)
+    path = os.path.join(tmp_path, name)
+    os.makedirs(path, exist_ok=True)
+    tok.save(os.path.join(path, "tokenizer.json"))
+    return tok, path
+
+
+QWEN_PATTERN = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+LLAMA3_PATTERN = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+GPT2_PATTERN = r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"
+
+
+@pytest.mark.parametrize("pattern,name", [(QWEN_PATTERN, "qwen"), (LLAMA3_PATTERN, "llama3"), (GPT2_PATTERN, "gpt2")])
+def test_bpe_matches_hf_tokenizers(tmp_path, pattern, name):
+    ref, path = _train_tokenizer(pattern, str(tmp_path), name)
+    from surogate_b200.data.tokenizer import Tokenizer
+
+    tok = Tokenizer.from_pretrained(path)
+    extra = ["", " ", "a", "x  y   z", "12 345 6789012", "tail space ", "\n\n\nthree", "<|im_start|>user\nhi<|im_end|>\n<|endoftext|>",
+             "mixed<|im_end|>inline 's 'S 'Re", "🙂" * 5]
+    for text in CORPUS + extra:
+        want = ref.encode(text).ids
+        got = tok.encode(text)
+        assert got == want, (name, text, got, want)
+        assert tok.decode(got) == text
+    assert tok.encode_batch(CORPUS, threads=3) == [ref.encode(t).ids for t in CORPUS]
+    assert tok.is_special_token(tok.core.token_to_id(b"<|im_end|>"))
+
+
+def test_chat_template_training_mask(tmp_path):
+    _, path = _train_tokenizer(QWEN_PATTERN, str(tmp_path), "chat")
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<|im_end|>", "pad_token": "<|endoftext|>"}, f)
+    from surogate_b200.data.tokenizer import IGNORE, Tokenizer
+
+    tok = Tokenizer.from_pretrained(path)
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "Hello world"}, {"role": "assistant", "content": "It's a test"},
+            {"role": "user", "content": "more"}, {"role": "assistant", "content": "done"}]
+    ids, labels = tok.encode_for_training(msgs)
+    assert len(ids) == len(labels)
+    trained = tok.decode([l for l in labels if l != IGNORE])
+    assert trained == "It's a test<|im_end|>\ndone<|im_end|>\n"
+    _, last = tok.encode_for_training(msgs, train_on="last")
+    assert tok.decode([l for l in last if l != IGNORE]) == "done<|im_end|>\n"
+    assert tok.eos_token_id == tok.core.token_to_id(b"<|im_end|>")
+
+
+def test_token_loader_native_matches_python_and_resumes(tmp_path):
+    from surogate_b200.data.loader import DataLoader
+    from surogate_b200.data.tokfile import TokenFileWriter
+
+    rng = np.random.default_rng(0)
+    files = []
+    for i, rows in enumerate([9, 14]):
+        p = os.path.join(tmp_path, f"train-{i:03d}.bin")
+        w = TokenFileWriter(p, 1000, has_masks=True, non_overlapping=True)
+        for _ in range(rows):
+            t = rng.integers(0, 1000, 16).astype(np.int32)
+            pos = np.concatenate([np.arange(7), np.arange(9)]).astype(np.int32)
+            w.add(t, pos, (rng.random(16) > 0.3).astype(np.uint8))
+        w.close()
+        files.append(p)
+    for rank in range(2):
+        nat = DataLoader(files, 3, 16, seed=7, rank=rank, world=2, native=True)
+        ref = DataLoader(files, 3, 16, seed=7, rank=rank, world=2, native=False)
+        assert nat.steps_per_epoch() == ref.steps_per_epoch()
+        for step in range(9):  # crosses file and epoch boundaries
+            a, b = nat.next_batch(), ref.next_batch()
+            for u, v in zip(a, b):
+                np.testing.assert_array_equal(u, v)
+            assert nat.state_dict() == ref.state_dict()
+            if step == 4:
+                saved = nat.state_dict()
+        resumed = DataLoader(files, 3, 16, seed=7, rank=rank, world=2, native=True)
+        resumed.load_state_dict(saved)
+        again = DataLoader(files, 3, 16, seed=7, rank=rank, world=2, native=False)
+        again.load_state_dict(saved)
+        for _ in range(3):
+            for u, v in zip(resumed.next_batch(), again.next_batch()):
+                np.testing.assert_array_equal(u, v)
+    x, y, p = ref.next_batch()
+    assert (y[:, -1] == -100).all() and (y[:, 6] == -100).all()  # row end and document boundary carry no target
+
+
+def test_safetensors_native_roundtrip(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    from surogate_b200.io.safetensors_native import NativeSafetensors, save_file_native
+
+    torch.manual_seed(0)
+    tensors = {"a.weight": torch.randn(64, 32).bfloat16(), "b": torch.arange(10, dtype=torch.int32), "c": torch.randn(3, 5, 7),
+               "big": torch.randn(3000, 1024)}
+    p1, p2 = os.path.join(tmp_path, "lib.safetensors"), os.path.join(tmp_path, "native.safetensors")
+    save_file(tensors, p1, metadata={"format": "pt"})
+    f = NativeSafetensors(p1, threads=4)
+    assert sorted(f.keys()) == sorted(tensors) and f.metadata() == {"format": "pt"}
+    for k, t in tensors.items():
+        assert torch.equal(f.get_tensor(k), t)
+    assert torch.equal(f.get_rows("big", 1000, 2500), tensors["big"][1000:2500])
+    save_file_native(tensors, p2, metadata={"format": "pt"}, threads=4)
+    back = load_file(p2)
+    for k, t in tensors.items():
+        assert torch.equal(back[k], t)
+
+
+def test_cpu_adamw_matches_torch():
+    h = host()
+    torch.manual_seed(0)
+    n = 10007
+    p = torch.randn(n)
+    ref = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v, work = torch.zeros(n), torch.zeros(n), torch.zeros(n, dtype=torch.bfloat16)
+    for step in range(1, 4):
+        g = torch.randn(n)
+        ref.grad = g.clone()
+        opt.step()
+        gb = g.bfloat16() if step == 3 else g
+        if step == 3:
+            ref.data.copy_(p)  # redo the reference with the rounded gradient
+            opt.state[ref]["exp_avg"].copy_(m)
+            opt.state[ref]["exp_avg_sq"].copy_(v)
+            opt.state[ref]["step"].fill_(2)
+            ref.grad = gb.float()
+            opt.step()
+        h.cpu_adamw_step(p.data_ptr(), m.data_ptr(), v.data_ptr(), gb.data_ptr(), gb.dtype == torch.bfloat16, work.data_ptr(), n, 1e-2, 0.9, 0.95, 1e-8,
+                         0.1, 1.0, step)
+        torch.testing.assert_close(p, ref.detach(), rtol=1e-5, atol=1e-6)
+    assert torch.equal(work, p.bfloat16())
+    assert abs(h.cpu_sum_squares(p.data_ptr(), False, n) - float((p.double() ** 2).sum())) < 1e-6 * n
+
+
+def test_lpt_plan_balances_and_conserves_tokens():
+    h = host()
+    counts = [9000, 200, 100, 300, 500, 400, 300, 200, 250, 250, 250, 250, 100, 100, 100, 100]
+    assert h.compute_lpt_plan(counts, 4, 100.0, 1.1, 64)["uses_lpt"] is False
+    plan = h.compute_lpt_plan(counts, 4, 1.3, 1.1, 64)
+    assert plan["uses_lpt"] and plan["imbalance"] > 1.3
+    for e, chunks in enumerate(plan["assignments"]):
+        assert sum(b - a for _, a, b in chunks) == counts[e]
+        assert chunks[0][1] == 0 and all(chunks[i][2] == chunks[i + 1][1] for i in range(len(chunks) - 1))
+    assert sum(plan["gpu_loads"]) == sum(counts)
+    assert max(plan["gpu_loads"]) < 0.5 * 9000 + 2000  # the hot expert was spread
+    assert all(src == e // 4 for e, src, _ in plan["moves"])
+
+
+def test_crash_handler_and_telemetry_are_safe_without_gpu():
+    h = host()
+    h.install_crash_handler("test")
+    info = h.query_gpu(0)
+    assert "ok" in info and (info["ok"] or info["error"])
