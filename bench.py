@@ -44,6 +44,13 @@ MODELS = {
                                      aux_loss_coef=1e-3, tie_word_embeddings=False),
                           seq_len=4096, batch=1, recipe="nvfp4", optimizer="adamw_8bit", zero=1, label="Qwen3-30B-A3B",
                           metric="tokens/sec Qwen3-30B-A3B NVFP4 (EP)"),
+    "qwen3-14b-lora": dict(model=dict(architecture="Qwen3ForCausalLM", vocab_size=151936, d_model=5120, n_layers=40, num_query_heads=40,
+                                      num_kv_heads=8, head_size=128, d_ff=17408, tie_word_embeddings=False),
+                           seq_len=8192, batch=1, recipe="bf16", optimizer="adamw_8bit", zero=3, label="Qwen3-14B-LoRA-r16",
+                           metric="tokens/sec Qwen3-14B LoRA SFT (BF16 base in pinned host memory, ZeRO-3 gather per layer)",
+                           lora=dict(rank=16, alpha=32, dropout=0.0, dtype="fp32", rslora=False, train_router=False,
+                                     targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]),
+                           offload=True, recompute=True, mask_first_fraction=0.25),
     "tiny": dict(model=dict(architecture="Qwen3ForCausalLM", vocab_size=4096, d_model=512, n_layers=2, num_query_heads=4, num_kv_heads=2,
                             head_size=128, d_ff=1536, tie_word_embeddings=True),
                  seq_len=512, batch=2, recipe="bf16", optimizer="adamw_8bit", zero=1, label="tiny", metric="tokens/sec tiny"),
@@ -123,6 +130,7 @@ def main():
     ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "symm"])
     ap.add_argument("--ep", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-offload", action="store_true", help="keep weights and optimizer state on the device for configs that offload by default")
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "library"], help="native = tcgen05 flash attention of this repo")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
     args = ap.parse_args()
@@ -157,14 +165,23 @@ def main():
     ep = args.ep if args.ep is not None else (world if args.model == "qwen3-30b-a3b" else 1)
     cfg = TrainerConfig(model=spec["model"], batch_size=mb, seq_len=seq, grad_accum=1, recipe=recipe, optimizer=args.optimizer or spec["optimizer"],
                         learning_rate=1e-4, weight_decay=0.1, zero_level=zero, recompute=args.recompute,
-                        backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention)
+                        backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention,
+                        lora=spec.get("lora"), offload_master=bool(spec.get("offload")) and not args.no_offload,
+                        offload_optimizer=bool(spec.get("offload")) and not args.no_offload, keep_gathered=not spec.get("offload"))
+    if spec.get("recompute"):
+        cfg.recompute = True
     tr = Trainer(cfg, device=dev, comm=comm)
     tr.init_weights(seed=0)
     V = spec["model"]["vocab_size"]
     rng = np.random.default_rng(1234 + info.rank)
     n_batches = 4
     host_batches = [rng.integers(0, V, size=(mb, seq + 1), dtype=np.int64).astype(np.int32) for _ in range(n_batches)]
-    dev_batches = [(torch.from_numpy(b[:, :-1].copy()).to(dev), torch.from_numpy(b[:, 1:].copy()).to(dev)) for b in host_batches]
+    host_inputs = [np.ascontiguousarray(b[:, :-1]) for b in host_batches]
+    host_targets = [np.ascontiguousarray(b[:, 1:]) for b in host_batches]
+    if spec.get("mask_first_fraction"):  # supervised fine-tuning shape: no loss on the prompt part of each sequence
+        for t in host_targets:
+            t[:, : int(seq * spec["mask_first_fraction"])] = -100
+    dev_batches = [(torch.from_numpy(x).to(dev), torch.from_numpy(y).to(dev)) for x, y in zip(host_inputs, host_targets)]
 
     def barrier():
         if world > 1:
@@ -198,15 +215,15 @@ def main():
     e2e = None
     if not args.no_e2e:
         tr.h2d_bytes = tr.d2h_bytes = 0
-        out = tr.step(host_batches[0][:, :-1], host_batches[0][:, 1:])  # one warm step through this path (allocates the pinned buffers)
+        out = tr.step(host_inputs[0], host_targets[0])  # one warm step through this path (allocates the pinned buffers)
         tr.h2d_bytes = tr.d2h_bytes = 0
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record()
         for i in range(args.steps):
-            b = host_batches[(i + 1) % n_batches]
-            out = tr.step(b[:, :-1], b[:, 1:])
+            k = (i + 1) % n_batches
+            out = tr.step(host_inputs[k], host_targets[k])
         e1.record()
         barrier()
         wall_ms = (time.perf_counter() - t0) * 1e3
@@ -227,7 +244,9 @@ def main():
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None, "dtype": "fp8" if recipe.startswith("fp8") else recipe,
             "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": args.impl,
             "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
-                       "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(args.recompute), "micro_batch_per_gpu": mb,
+                       "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(cfg.recompute), "micro_batch_per_gpu": mb,
+                       "lora_rank": (spec.get("lora") or {}).get("rank"), "offload": bool(cfg.offload_master),
+                       "weight_h2d_bytes_per_step": int(tr.store.h2d_bytes // max(1, args.steps + args.warmup + (0 if args.no_e2e else args.steps + 1))),
                        "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events on the launching stream, barrier+synchronize on both sides, max over ranks"},
             "clocks": clocks, "gpu_launches": int(launches),

@@ -289,7 +289,8 @@ class SFTConfig:
             master_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.master_dtype or "", None),
             lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, lora=self.lora_dict(),
             fp8_amax_history=self.fp8_amax_history, skip_quant_first_layers=self.skip_quant_first_layers,
-            skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer, offload_master=self.offload_master,
+            skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer and not self.cpu_training,
+            offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training,
             normuon_momentum=self.normuon_momentum, normuon_beta2=self.normuon_beta2, normuon_cautious_wd=self.normuon_cautious_wd,
             init_projections_to_zero=self.init_projections_to_zero, seed=self.train_seed, collectives=self.collectives)
 

@@ -25,7 +25,7 @@ static inline uint16_t f32_to_bf16(float f) {
 }
 
 void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool grad_is_bf16, uint16_t* work_bf16, int64_t n, float lr, float beta1,
-                    float beta2, float eps, float weight_decay, float grad_scale, int64_t step) {
+                    float beta2, float eps, float weight_decay, float grad_scale, int64_t step, const uint8_t* decay_mask) {
     const float bc1 = 1.0f - std::pow(beta1, static_cast<float>(step));
     const float bc2 = 1.0f - std::pow(beta2, static_cast<float>(step));
     const float step_size = lr / bc1;
@@ -40,7 +40,7 @@ void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool gra
         m[i] = mi;
         v[i] = vi;
         float p = param[i];
-        p -= lr * weight_decay * p;
+        if (!decay_mask || decay_mask[i]) p -= lr * weight_decay * p;
         p -= step_size * mi / (std::sqrt(vi) * inv_sqrt_bc2 + eps);
         param[i] = p;
         if (work_bf16) work_bf16[i] = f32_to_bf16(p);

@@ -9,7 +9,7 @@ namespace sg {
 
 // cpu_optim.cpp
 void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool grad_is_bf16, uint16_t* work_bf16, int64_t n, float lr, float beta1,
-                    float beta2, float eps, float weight_decay, float grad_scale, int64_t step);
+                    float beta2, float eps, float weight_decay, float grad_scale, int64_t step, const uint8_t* decay_mask = nullptr);
 double cpu_sum_squares(const void* x, bool is_bf16, int64_t n);
 
 // lpt_planner.cpp

@@ -90,11 +90,12 @@ PYBIND11_MODULE(sg_b200_host, m) {
     m.def("dtype_size", &dtype_size);
 
     m.def("cpu_adamw_step", [](uintptr_t param, uintptr_t mm, uintptr_t vv, uintptr_t grad, bool grad_bf16, uintptr_t work, int64_t n, float lr, float b1,
-                               float b2, float eps, float wd, float grad_scale, int64_t step) {
+                               float b2, float eps, float wd, float grad_scale, int64_t step, uintptr_t mask) {
               py::gil_scoped_release rel;
               cpu_adamw_step(static_cast<float*>(ptr(param)), static_cast<float*>(ptr(mm)), static_cast<float*>(ptr(vv)), ptr(grad), grad_bf16,
-                             static_cast<uint16_t*>(ptr(work)), n, lr, b1, b2, eps, wd, grad_scale, step);
-          });
+                             static_cast<uint16_t*>(ptr(work)), n, lr, b1, b2, eps, wd, grad_scale, step, static_cast<const uint8_t*>(ptr(mask)));
+          }, py::arg("param"), py::arg("m"), py::arg("v"), py::arg("grad"), py::arg("grad_is_bf16"), py::arg("work_bf16"), py::arg("n"), py::arg("lr"),
+          py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"), py::arg("decay_mask") = 0);
     m.def("cpu_sum_squares", [](uintptr_t x, bool bf16, int64_t n) {
         py::gil_scoped_release rel;
         return cpu_sum_squares(ptr(x), bf16, n);

@@ -66,18 +66,23 @@ class AdamW:
         self.cfg = cfg
         self.store = store
         self.state: Dict[str, Dict[str, torch.Tensor]] = {}
+        self.offload_state = False  # moments in pinned host memory (streamed through the GPU by StreamedOptimizerStep)
         self.use_kernels = store.device.type == "cuda"
         if self.use_kernels:
             from ..ops import ext
 
             self.ext = ext()
 
+    def _zeros(self, n: int, dtype) -> torch.Tensor:
+        if self.offload_state and self.store.device.type == "cuda":
+            return torch.zeros(n, dtype=dtype, pin_memory=True)
+        return torch.zeros(n, dtype=dtype, device=self.store.device)
+
     def _state(self, b):
         st = self.state.get(b.name)
         if st is None:
             n = b.master.numel()
-            st = self.state[b.name] = {"m": torch.zeros(n, dtype=torch.float32, device=self.store.device),
-                                       "v": torch.zeros(n, dtype=torch.float32, device=self.store.device)}
+            st = self.state[b.name] = {"m": self._zeros(n, torch.float32), "v": self._zeros(n, torch.float32)}
         return st
 
     def step_bucket(self, b, grad: torch.Tensor, hp: torch.Tensor, hp_host) -> None:
@@ -107,10 +112,8 @@ class AdamW8bit(AdamW):
         if st is None:
             n = b.master.numel()
             ng = (n + 31) // 32
-            dev = self.store.device
-            st = self.state[b.name] = {"m": torch.zeros(n, dtype=torch.int8, device=dev), "v": torch.zeros(n, dtype=torch.uint8, device=dev),
-                                       "m.scales": torch.zeros(ng, dtype=torch.float16, device=dev),
-                                       "v.scales": torch.zeros(ng, dtype=torch.float16, device=dev)}
+            st = self.state[b.name] = {"m": self._zeros(n, torch.int8), "v": self._zeros(n, torch.uint8),
+                                       "m.scales": self._zeros(ng, torch.float16), "v.scales": self._zeros(ng, torch.float16)}
         return st
 
     def step_bucket(self, b, grad, hp, hp_host) -> None:

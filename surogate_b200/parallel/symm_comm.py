@@ -174,6 +174,20 @@ class SymmComm:
                 out_fp8.record_stream(self.stream)
         return self._done(async_op)
 
+    def all_gather_from_host(self, host_shard: torch.Tensor, stage: torch.Tensor, full: torch.Tensor, async_op: bool = False):
+        """ZeRO-3 gather of a shard that lives in pinned host memory: the H2D copy lands in a peer-visible arena slot, a
+        device-side barrier says that every rank's copy has landed, then the gather kernel pulls the peers' slots.  All on
+        the communication stream, so the PCIe copy and the NVLink pulls overlap the compute stream.  Callers alternate
+        between two slots: the barrier of gather k+1 also proves that every peer finished pulling slot k."""
+        off = self.arena.offset_of(stage)
+        assert off is not None and stage.dtype == torch.bfloat16 and host_shard.numel() == stage.numel()
+        with self._side():
+            stage.copy_(host_shard, non_blocking=True)
+            self._barrier(SLOT_SIDE)
+            self.ext.all_gather_fused(self.arena.peer_bases, off, stage.numel(), 0, stage.numel() * self.world, full, None, None, self.max_blocks)
+            full.record_stream(self.stream)
+        return self._done(async_op)
+
     def all_reduce(self, t: torch.Tensor, op: str = "sum", async_op: bool = False):
         if t.dtype == torch.float32 and t.numel() <= 1024 and t.is_contiguous() and op in ("sum", "max", "avg"):
             self.ar_epoch += 1

@@ -96,10 +96,23 @@ class SingleProcessComm:
         pass
 
 
+class _HostGatherWork:
+    """Completion handle of a host-sourced gather: makes the current stream wait for the copy (and the collective)."""
+
+    def __init__(self, event, inner, keep):
+        self.event, self.inner, self.keep = event, inner, keep
+
+    def wait(self):
+        if self.inner is not None:
+            self.inner.wait()
+        torch.cuda.current_stream().wait_event(self.event)
+        self.keep = None
+
+
 class ParamStore:
     def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
                  comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
-                 expert_parallel: int = 1):
+                 expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False):
         self.cm = cm
         self.device = torch.device(device)
         self.param_dtype = param_dtype
@@ -111,6 +124,15 @@ class ParamStore:
         self.keep_gathered = keep_gathered
         self.frozen = frozen or (lambda name: False)
         self.ep = max(1, int(expert_parallel))
+        # Host residency: master shards live in pinned host memory and are streamed to the device per layer (H2D copy on a
+        # side stream, then the usual gather).  ``host_work_copy`` keeps an extra pinned copy in the parameter dtype next to
+        # masters of another dtype (fp32 masters updated by the CPU optimizer, bf16 copy streamed to the GPU).
+        self.offload_master = bool(offload_master)
+        self.host_work_copy = bool(host_work_copy) and self.offload_master
+        self.h2d_stream = torch.cuda.Stream(device=self.device) if (self.offload_master and self.device.type == "cuda") else None
+        self.stage_slots: List[torch.Tensor] = []
+        self._stage_rr = 0
+        self.h2d_bytes = 0
         self.buckets: "OrderedDict[str, Bucket]" = OrderedDict()
         self.where: Dict[str, Tuple[Bucket, Slot]] = {}
         self.alias: Dict[str, str] = {}
@@ -155,21 +177,41 @@ class ParamStore:
         self.fused_sumsq = None
         self.sumsq_valid = False
         self.micro_total = 1
-        if hasattr(self.comm, "create_arena") and self.sharded and self.master_dtype == torch.bfloat16 and self.grad_dtype == torch.bfloat16:
+        stream_dtype_ok = self.param_dtype == torch.bfloat16 and (self.master_dtype == torch.bfloat16 or self.host_work_copy)
+        if hasattr(self.comm, "create_arena") and self.sharded and self.grad_dtype == torch.bfloat16 and \
+                (stream_dtype_ok if self.offload_master else self.master_dtype == torch.bfloat16):
             need = 0
+            max_shard = 0
             for b in self.buckets.values():
                 if b.expert:
                     continue
-                need += (b.shard_numel * 2 + 255) // 256 * 256 + 256
+                if self.offload_master:
+                    max_shard = max(max_shard, b.shard_numel)
+                else:
+                    need += (b.shard_numel * 2 + 255) // 256 * 256 + 256
                 if b.trainable:
                     need += (b.numel * 2 + 255) // 256 * 256 + 256
+            need += 2 * ((max_shard * 2 + 255) // 256 * 256 + 256)
             self.arena = self.comm.create_arena(need)
             self.arena.tensor.zero_()
             self.fused_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+            if self.offload_master:  # two peer-visible landing slots for the H2D copies that feed the gather kernel
+                self.stage_slots = [self.arena.take(max_shard, torch.bfloat16) for _ in range(2)]
+        pin = self.device.type == "cuda"
         for b in self.buckets.values():
             if b.expert:
                 b.master = torch.zeros(b.numel, dtype=self.master_dtype, device=self.device)
                 b.work = b.master if self.master_dtype == self.param_dtype else torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
+                continue
+            if self.offload_master:
+                b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, pin_memory=pin)
+                b.work_host = torch.zeros(b.shard_numel, dtype=self.param_dtype, pin_memory=pin) if (
+                    self.host_work_copy and self.master_dtype != self.param_dtype) else None
+                if self.arena is not None and b.trainable:
+                    b.grad = self.arena.take(b.numel, self.grad_dtype)
+                    b.grad_persistent = True
+                if self.zero_level < 3:
+                    b.work = torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
                 continue
             if self.arena is not None:
                 b.master = self.arena.take(b.shard_numel, self.master_dtype)
@@ -250,10 +292,13 @@ class ParamStore:
         if b.expert:
             return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
         if not self.sharded:
-            return b.master[s.offset:s.offset + s.numel].reshape(s.shape)
+            return self._master_on_device(b)[s.offset:s.offset + s.numel].reshape(s.shape)
         full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
-        self.comm.all_gather(b.master, full)
+        self.comm.all_gather(self._master_on_device(b), full)
         return full[s.offset:s.offset + s.numel].reshape(s.shape)
+
+    def _master_on_device(self, b: Bucket) -> torch.Tensor:
+        return b.master if b.master.device == self.device else b.master.to(self.device)
 
     def _gather_experts(self, local: torch.Tensor) -> torch.Tensor:
         """[E/ep, ...] on every rank -> [E, ...] (ranks own consecutive expert ranges)."""
@@ -270,9 +315,9 @@ class ParamStore:
                 continue
             if self.sharded:
                 full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
-                self.comm.all_gather(b.master, full)
+                self.comm.all_gather(self._master_on_device(b), full)
             else:
-                full = b.master
+                full = self._master_on_device(b)
             for s in b.slots:
                 yield s.name, full[s.offset:s.offset + s.numel].reshape(s.shape)
 
@@ -288,6 +333,9 @@ class ParamStore:
                 if b.work is not b.master:
                     b.work.copy_(b.master)
                 continue
+            if getattr(b, "work_host", None) is not None and not getattr(b, "work_host_fresh", False):
+                b.work_host.copy_(b.master)  # host-side conversion (init / load); the CPU optimizer writes it itself afterwards
+            b.work_host_fresh = False
             if self.zero_level >= 3:
                 b.work = None
                 b.work_fp8 = None
@@ -306,7 +354,7 @@ class ParamStore:
         """Gather ZeRO-3 weights straight into FP8: the gather kernel pulls the peers' bf16 shards and writes E4M3 with the
         tensor's scale, so the gathered bf16 copy and the separate abs-max / quantise passes disappear.  ``wants(layer, role)``
         says which projections the recipe runs in FP8.  Needs the peer-memory communicator and an arena."""
-        if self.zero_level < 3 or self.arena is None or self.param_dtype != torch.bfloat16:
+        if self.zero_level < 3 or self.arena is None or self.param_dtype != torch.bfloat16 or self.offload_master:
             return False
         self.q_index: Dict[str, int] = {}
         for b in self.buckets.values():
@@ -372,7 +420,44 @@ class ParamStore:
             works.append(w)
         return works[-1] if works else None   # same communication stream: the last event covers all of them
 
+    def host_source(self, b: Bucket) -> torch.Tensor:
+        """The pinned host tensor streamed to the GPU for this bucket (in the parameter dtype when one exists)."""
+        wh = getattr(b, "work_host", None)
+        return wh if wh is not None else b.master
+
+    def _gather_from_host(self, b: Bucket, full: torch.Tensor, async_op: bool):
+        """Pinned host shard -> device -> (all-gather) -> ``full``, entirely on side streams."""
+        src = self.host_source(b)
+        self.h2d_bytes += src.numel() * src.element_size()
+        if self.sharded and self.stage_slots and src.dtype == torch.bfloat16 and full.dtype == torch.bfloat16 and hasattr(self.comm, "all_gather_from_host"):
+            k = self._stage_rr
+            self._stage_rr ^= 1
+            return self.comm.all_gather_from_host(src, self.stage_slots[k][:src.numel()], full, async_op=async_op)
+        cur = torch.cuda.current_stream(self.device)
+        hs = self.h2d_stream
+        hs.wait_stream(cur)  # blocks handed out by the allocator may still be in use by kernels queued on the compute stream
+        with torch.cuda.stream(hs):
+            stage = torch.empty(src.numel(), dtype=src.dtype, device=self.device)
+            stage.copy_(src, non_blocking=True)
+            dev = stage if stage.dtype == full.dtype else stage.to(full.dtype)
+            inner = None
+            if not self.sharded:
+                full.copy_(dev)
+            else:
+                inner = self.comm.all_gather(dev, full, async_op=True)
+            ev = torch.cuda.Event()
+            ev.record(hs)
+            for t in (stage, dev, full):
+                t.record_stream(hs)
+        h = _HostGatherWork(ev, inner, (stage, dev))
+        if not async_op:
+            h.wait()
+            return None
+        return h
+
     def _gather_into(self, b: Bucket, full: torch.Tensor, async_op: bool = False):
+        if b.master.device.type == "cpu" and self.device.type == "cuda":
+            return self._gather_from_host(b, full, async_op)
         src = b.master if b.master.dtype == full.dtype else b.master.to(full.dtype)
         if not self.sharded:
             full.copy_(src)
@@ -570,9 +655,9 @@ class ParamStore:
                 b.grad = None
 
     def memory_breakdown(self) -> Dict[str, int]:
-        out = {"master": 0, "work": 0, "grad": 0}
+        out = {"master": 0, "work": 0, "grad": 0, "host_master": 0}
         for b in self.buckets.values():
-            out["master"] += b.master.numel() * b.master.element_size()
+            out["master" if b.master.device.type != "cpu" or self.device.type == "cpu" else "host_master"] += b.master.numel() * b.master.element_size()
             if b.work is not None and b.work is not b.master:
                 out["work"] += b.work.numel() * b.work.element_size()
             if b.grad is not None:

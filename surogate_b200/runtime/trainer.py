@@ -62,6 +62,7 @@ class TrainerConfig:
     skip_quant_last_layers: int = 0
     offload_optimizer: bool = False
     offload_master: bool = False
+    cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
     normuon_cautious_wd: bool = True
@@ -94,6 +95,8 @@ class Trainer:
         pd = _DT[cfg.param_dtype] if on_gpu else torch.float32
         gd = _DT[cfg.grad_dtype] if on_gpu else torch.float32
         md = _DT[cfg.master_dtype] if cfg.master_dtype else pd
+        if cfg.cpu_training:
+            md = torch.float32
         self.lora = None
         frozen = None
         if cfg.lora:
@@ -106,7 +109,8 @@ class Trainer:
 
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
         self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
-                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size)
+                                zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size,
+                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training)
         from .ops_cuda import make_backend
 
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
@@ -123,7 +127,22 @@ class Trainer:
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd), device=self.device, ep=self.ep, lora=self.lora)
         self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
                                        cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd)
-        self.optimizer = make_optimizer(self.opt_cfg, self.store)
+        self.streamed = None
+        if cfg.cpu_training:
+            from .offload import CpuAdamW
+
+            if cfg.optimizer not in ("adamw", "adamw_8bit"):
+                raise ValueError("cpu_training runs AdamW on the host: choose optimizer adamw (adamw_8bit is treated as adamw)")
+            self.optimizer = CpuAdamW(self.opt_cfg, self.store)
+        else:
+            self.optimizer = make_optimizer(self.opt_cfg, self.store)
+            if cfg.offload_optimizer or cfg.offload_master:
+                from .offload import StreamedOptimizerStep
+
+                if cfg.optimizer == "normuon":
+                    raise ValueError("offload_optimizer / offload_master are implemented for adamw and adamw_8bit")
+                self.optimizer.offload_state = bool(cfg.offload_optimizer)
+                self.streamed = StreamedOptimizerStep(self.store, self.optimizer, self.device)
         self.step_index = 0
         self.kernel_launch_estimate = 0
         self._pinned: Dict[str, torch.Tensor] = {}
@@ -289,10 +308,15 @@ class Trainer:
         fence = getattr(self.comm, "fence", None)
         if fence is not None:
             fence()  # every rank has finished reading master shards / gradient buckets of this step
-        for b in self.store.trainable_buckets():
-            if b.grad_shard is None:
-                continue
-            self.optimizer.step_bucket(b, b.grad_shard, self._hp, host)
+        if self.cfg.cpu_training:
+            self.optimizer.step_all([b for b in self.store.trainable_buckets() if not b.expert], lr, float(clip), t)  # host sync: clip scale
+        elif self.streamed is not None:
+            self.streamed.run(self.store.trainable_buckets(), self._hp, host)
+        else:
+            for b in self.store.trainable_buckets():
+                if b.grad_shard is None:
+                    continue
+                self.optimizer.step_bucket(b, b.grad_shard, self._hp, host)
         if self.lora is not None:
             self.lora.optimizer_step(self._hp, host)
         self.store.release_grads()

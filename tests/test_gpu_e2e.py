@@ -110,3 +110,30 @@ def test_nvfp4_close_to_bf16():
     lb = [b.step(x, y)["loss"] for _ in range(4)]
     assert abs(la[0] - lb[0]) < 0.03 * lb[0], (la, lb)
     assert abs(la[-1] - lb[-1]) < 0.15 * lb[-1], (la, lb)
+
+
+@pytest.mark.parametrize("mode", ["offload", "cpu_training"])
+def test_host_resident_state_matches_device_resident(mode):
+    """Pinned-host masters / optimizer moments streamed through the GPU (or updated on the CPU) follow the plain run."""
+    x, y = _batch(4)
+    kw = dict(offload_master=True, offload_optimizer=True) if mode == "offload" else dict(cpu_training=True)
+    a = _trainer("cuda", optimizer="adamw", **kw)
+    b = _trainer("cuda", optimizer="adamw", **({} if mode == "offload" else dict(master_dtype="fp32")))
+    la = [a.step(x, y)["loss"] for _ in range(4)]
+    lb = [b.step(x, y)["loss"] for _ in range(4)]
+    assert all(m.master.device.type == "cpu" and m.master.is_pinned() for m in a.store.buckets.values())
+    for u, v in zip(la, lb):
+        assert abs(u - v) < 5e-3 * abs(v), (la, lb)
+    assert a.store.h2d_bytes > 0
+
+
+def test_lora_gpu_loss_decreases_and_base_is_frozen():
+    lora = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+                rslora=False, train_router=False)
+    tr = _trainer("cuda", optimizer="adamw", lora=lora)
+    before = {n: t.clone() for n, t in tr.store.named_full_tensors()}
+    x, y = _batch(6)
+    losses = [tr.step(x, y, lr=5e-3)["loss"] for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    for n, t in tr.store.named_full_tensors():
+        assert torch.equal(t, before[n]), n

@@ -49,3 +49,29 @@ def test_expert_parallel_matches_one_gpu():
         assert abs(a - b) < 2e-2 * abs(b), (two["losses"], one["losses"])
     for a, b in zip(two["norms"], one["norms"]):
         assert abs(a - b) < 6e-2 * abs(b), (two["norms"], one["norms"])
+
+
+LORA = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+            rslora=False, train_router=False)
+
+
+@pytest.mark.parametrize("collectives", ["nccl", "symm"])
+def test_two_gpus_lora_zero3_host_resident_base(collectives):
+    """LoRA over a frozen base whose shards live in pinned host memory: H2D into a peer-visible slot + peer-memory gather
+    (or H2D + NCCL) reproduces the run with device-resident weights."""
+    ref = run_worker(2, dict(ARGS, zero=3, collectives=collectives, lora=LORA, keep_gathered=False), port=29751)
+    off = run_worker(2, dict(ARGS, zero=3, collectives=collectives, lora=LORA, keep_gathered=False, offload_master=True, offload_optimizer=True),
+                     port=29752)
+    assert off["h2d_weight_bytes"] > 0
+    if collectives == "symm":
+        assert off["stage_slots"] == 2
+    for a, b in zip(off["losses"], ref["losses"]):
+        assert abs(a - b) < 1e-3 * abs(b), (off["losses"], ref["losses"])
+
+
+def test_two_gpus_full_finetune_offloaded_state():
+    ref = run_worker(2, dict(ARGS, zero=3, collectives="symm", optimizer="adamw_8bit", keep_gathered=False), port=29753)
+    off = run_worker(2, dict(ARGS, zero=3, collectives="symm", optimizer="adamw_8bit", keep_gathered=False, offload_master=True, offload_optimizer=True),
+                     port=29754)
+    for a, b in zip(off["losses"], ref["losses"]):
+        assert abs(a - b) < 5e-3 * abs(b), (off["losses"], ref["losses"])
