@@ -176,8 +176,8 @@ def main():
     rng = np.random.default_rng(1234 + info.rank)
     n_batches = 4
     host_batches = [rng.integers(0, V, size=(mb, seq + 1), dtype=np.int64).astype(np.int32) for _ in range(n_batches)]
-    host_inputs = [np.ascontiguousarray(b[:, :-1]) for b in host_batches]
-    host_targets = [np.ascontiguousarray(b[:, 1:]) for b in host_batches]
+    host_inputs = [b[:, :-1].copy() for b in host_batches]   # copies: the target mask below must not touch the inputs
+    host_targets = [b[:, 1:].copy() for b in host_batches]
     if spec.get("mask_first_fraction"):  # supervised fine-tuning shape: no loss on the prompt part of each sequence
         for t in host_targets:
             t[:, : int(seq * spec["mask_first_fraction"])] = -100
@@ -208,6 +208,10 @@ def main():
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
+    if ext is not None:
+        from surogate_b200.ops import check_device_errors
+
+        check_device_errors()  # a kernel that timed out on a wait or met an invalid token id invalidates the run
     launches = (ext.launch_count() - launches0) if ext is not None else 0
     clocks = sampler.stop()
 

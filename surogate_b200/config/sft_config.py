@@ -27,7 +27,25 @@ class DatasetConfig:
     subset: Optional[str] = None
     text_field: str = "text"
     samples: Optional[int] = None
+    # instruction / alpaca
+    system_prompt_type: Optional[str] = None  # field | fixed
+    system_prompt_field: Optional[str] = None
     system_prompt: Optional[str] = None
+    instruction_field: str = "instruction"
+    input_field: Optional[str] = "input"
+    output_field: str = "output"
+    prompt_format: Optional[str] = None
+    prompt_format_no_input: Optional[str] = None
+    # conversation / messages
+    system_field: Optional[str] = None
+    messages_field: str = "messages"
+    completion_field: Optional[str] = None
+    tools_field: Optional[str] = None
+    message_property_mappings: Dict[str, str] = field(default_factory=dict)
+    # preference (DPO)
+    prompt_field: str = "prompt"
+    chosen_field: str = "chosen"
+    rejected_field: str = "rejected"
     fields: Dict[str, str] = field(default_factory=dict)
 
     @staticmethod

@@ -237,7 +237,8 @@ Tensor embedding_fwd(const Tensor& tokens, const Tensor& table) {
     shape.push_back(C);
     Tensor out = torch::empty(shape, table.options());
     g_launches += 1;
-    sg::embedding_fwd(tokens.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tokens.numel(), C, num_sms(), cur_stream());
+    sg::embedding_fwd(tokens.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tokens.numel(), C, static_cast<int>(table.size(0)), error_flag_ptr(), num_sms(),
+                      cur_stream());
     return out;
 }
 

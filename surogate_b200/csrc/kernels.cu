@@ -355,12 +355,20 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
 }
 
 // ------------------------------------------------------------------------------------------ embedding
-__global__ void embedding_fwd_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ out, size_t n, int C) {
+// A token id outside [0, V) writes zeros for that row and raises the error flag instead of reading outside the table.
+__global__ void embedding_fwd_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ out, size_t n, int C, int V,
+                                     int* __restrict__ error_flag) {
     const size_t nvec = n * (C / 8);
     for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t t = v / (C / 8);
         const int c = static_cast<int>(v % (C / 8)) * 8;
-        *reinterpret_cast<uint4*>(out + t * C + c) = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(tokens[t]) * C + c);
+        const int tok = tokens[t];
+        if (tok < 0 || tok >= V) {
+            *reinterpret_cast<uint4*>(out + t * C + c) = make_uint4(0, 0, 0, 0);
+            if (c == 0 && error_flag) atomicExch(error_flag, 2);
+            continue;
+        }
+        *reinterpret_cast<uint4*>(out + t * C + c) = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(tok) * C + c);
     }
 }
 template <typename G> __global__ void embedding_bwd_kernel(const int* __restrict__ tokens, const bf16* __restrict__ d_out, G* __restrict__ d_table, size_t n, int C) {
@@ -655,8 +663,8 @@ void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, co
                                                                                      (const bf16*)kw, pos, (bf16*)d_qkv, q_rstd, k_rstd, dqw, dkw, tokens,
                                                                                      Hq, Hkv, eps, log2f(theta));
 }
-void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int num_sms, cudaStream_t s) {
-    embedding_fwd_kernel<<<grid_for(n * (C / 8), 256, num_sms), 256, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, n, C);
+void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int V, int* error_flag, int num_sms, cudaStream_t s) {
+    embedding_fwd_kernel<<<grid_for(n * (C / 8), 256, num_sms), 256, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, n, C, V, error_flag);
 }
 void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad_fp32, size_t n, int C, int num_sms, cudaStream_t s) {
     const int grid = grid_for(n * (C / 2), 256, num_sms);

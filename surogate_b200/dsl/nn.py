@@ -286,3 +286,8 @@ def model_class_for(name: str) -> Type[Model]:
 
 def registered_models() -> Dict[str, Type[Model]]:
     return dict(_MODEL_REGISTRY)
+
+
+def registered_architectures() -> List[str]:
+    """HF ``architectures`` names (those ending in ForCausalLM / ForConditionalGeneration) that have a DSL model."""
+    return sorted(k for k in _MODEL_REGISTRY if k[:1].isupper())

@@ -31,4 +31,5 @@ def check_device_errors(reset: bool = True) -> None:
     """Raise if any kernel reported a pipeline time-out (bounded waits) since the last check. Synchronises."""
     flag = ext().read_error_flag(reset)
     if flag:
-        raise RuntimeError(f"a surogate_b200 kernel reported a device-side wait time-out (flag={flag})")
+        what = {1: "a bounded device-side wait timed out", 2: "a token id outside [0, vocab_size) reached the embedding"}.get(flag, "a kernel reported an error")
+        raise RuntimeError(f"surogate_b200 device error flag = {flag}: {what}")

@@ -42,7 +42,7 @@ def resolve_model_config(cfg: SFTConfig) -> Dict[str, Any]:
     return load_hf_config(download_model(m))
 
 
-def prepare_data(cfg: SFTConfig, hf_cfg: Dict[str, Any], rank: int) -> Dict[str, List[str]]:
+def prepare_data(cfg: SFTConfig, hf_cfg: Dict[str, Any], rank: int, comm=None) -> Dict[str, List[str]]:
     """Token shards for training / evaluation (tokenises datasets on first use, cached by content hash)."""
     out = os.path.join(cfg.output_dir, "tokens")
     vocab = hf_cfg.get("vocab_size", 151936)
@@ -56,7 +56,14 @@ def prepare_data(cfg: SFTConfig, hf_cfg: Dict[str, Any], rank: int) -> Dict[str,
         return {"train": [train], "eval": [ev]}
     from .tokenize import TokenizeDatasets
 
-    return TokenizeDatasets(cfg, hf_cfg, out).run(write=rank == 0)
+    job = TokenizeDatasets(cfg, hf_cfg, out)
+    if rank == 0:
+        files = job.run(write=True)
+    if comm is not None:
+        comm.barrier()  # the shards and their manifest are on disk
+    if rank != 0:
+        files = job.run(write=False)
+    return files
 
 
 class SurogateSFT:
@@ -102,7 +109,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     hf_cfg = resolve_model_config(cfg)
     if cfg.router_aux_loss_coef is not None:
         hf_cfg["router_aux_loss_coef"] = cfg.router_aux_loss_coef
-    files = prepare_data(cfg, hf_cfg, info.rank)
+    files = prepare_data(cfg, hf_cfg, info.rank, comm)
     if comm is not None:
         comm.barrier()
     tcfg = cfg.to_trainer_config(hf_cfg)

@@ -310,3 +310,19 @@ def test_moe_permute_grouped_gemm_unpermute(ext):
     assert _rel_err(d_yp[rm.reshape(-1)], (dout.float()[:, None] * tw[..., None]).reshape(-1, Nout)) < 5e-3
     assert _rel_err(d_tw, (y[rm].float() * dout.float()[:, None]).sum(-1)) < 5e-3
     _check_flag()
+
+
+def test_embedding_rejects_out_of_range_token_ids():
+    """An invalid token id must not read outside the table: the row is zero-filled and the error flag is raised."""
+    from surogate_b200.ops import check_device_errors, ext
+
+    e = ext()
+    check_device_errors()
+    table = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16)
+    tok = torch.tensor([[3, -100, 63, 64]], device="cuda", dtype=torch.int32)
+    out = e.embedding_fwd(tok, table)
+    assert torch.equal(out[0, 0], table[3]) and torch.equal(out[0, 2], table[63])
+    assert out[0, 1].abs().sum() == 0 and out[0, 3].abs().sum() == 0
+    with pytest.raises(RuntimeError, match="token id"):
+        check_device_errors()
+    check_device_errors()  # the flag was reset by the failed check
