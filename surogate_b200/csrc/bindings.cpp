@@ -254,7 +254,9 @@ void embedding_bwd(const Tensor& tokens, const Tensor& d_out, Tensor& d_table) {
 }
 
 // logits [rows, V] bf16 (row stride ld) are overwritten with d_logits when write_grad; returns per-row losses.
-Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& scale, double scale_host, bool write_grad) {
+Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& scale, double scale_host, bool write_grad,
+                             const c10::optional<Tensor>& row_weight, const c10::optional<Tensor>& kd_idx, const c10::optional<Tensor>& kd_logp,
+                             double kd_weight, const c10::optional<Tensor>& kd_loss_out) {
     check_cuda(logits, "logits");
     TORCH_CHECK(logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be 2-D bf16 with contiguous rows");
     TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kInt && targets.is_contiguous(), "targets must be contiguous CUDA int32");
@@ -263,9 +265,33 @@ Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::o
     TORCH_CHECK(targets.numel() == rows, "one target per row");
     const c10::cuda::CUDAGuard guard(logits.device());
     Tensor loss = torch::empty({rows}, logits.options().dtype(at::kFloat));
+    const float* rw = nullptr;
+    if (row_weight.has_value() && row_weight->defined()) {
+        TORCH_CHECK(row_weight->is_cuda() && row_weight->scalar_type() == at::kFloat && row_weight->is_contiguous() && row_weight->numel() == rows,
+                    "row_weight must be contiguous CUDA float32 with one value per row");
+        rw = row_weight->data_ptr<float>();
+    }
+    const int* ki = nullptr;
+    const float* kl = nullptr;
+    float* ko = nullptr;
+    int K = 0;
+    if (kd_idx.has_value() && kd_idx->defined()) {
+        TORCH_CHECK(kd_logp.has_value() && kd_logp->defined(), "kd_idx needs kd_logp");
+        TORCH_CHECK(kd_idx->is_cuda() && kd_idx->scalar_type() == at::kInt && kd_idx->is_contiguous() && kd_idx->dim() == 2 && kd_idx->size(0) == rows,
+                    "kd_idx must be contiguous CUDA int32 [rows, K]");
+        TORCH_CHECK(kd_logp->is_cuda() && kd_logp->scalar_type() == at::kFloat && kd_logp->is_contiguous() && kd_logp->sizes() == kd_idx->sizes(),
+                    "kd_logp must be contiguous CUDA float32 [rows, K]");
+        K = static_cast<int>(kd_idx->size(1));
+        ki = kd_idx->data_ptr<int>();
+        kl = kd_logp->data_ptr<float>();
+        if (kd_loss_out.has_value() && kd_loss_out->defined()) {
+            TORCH_CHECK(kd_loss_out->is_cuda() && kd_loss_out->scalar_type() == at::kFloat && kd_loss_out->numel() == rows, "kd_loss_out: float32 [rows]");
+            ko = kd_loss_out->data_ptr<float>();
+        }
+    }
     g_launches += 1;
     sg::cross_entropy_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), loss.data_ptr<float>(), opt_f32(scale), static_cast<float>(scale_host), rows, V,
-                              ld, write_grad, cur_stream());
+                              ld, write_grad, rw, ki, kl, K, static_cast<float>(kd_weight), ko, cur_stream());
     return loss;
 }
 
@@ -340,7 +366,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
     m.def("embedding_fwd", &embedding_fwd);
     m.def("embedding_bwd", &embedding_bwd);
-    m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
+    m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd, py::arg("logits"), py::arg("targets"), py::arg("scale"), py::arg("scale_host"),
+          py::arg("write_grad"), py::arg("row_weight") = py::none(), py::arg("kd_idx") = py::none(), py::arg("kd_logp") = py::none(),
+          py::arg("kd_weight") = 0.0, py::arg("kd_loss_out") = py::none());
     m.def("quantize_fp8", &quantize_fp8);
     m.def("amax", &amax);
     m.def("sumsq", &sumsq);

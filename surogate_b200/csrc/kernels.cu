@@ -390,16 +390,27 @@ template <typename G> __global__ void embedding_bwd_kernel(const int* __restrict
 
 // ------------------------------------------------------------------------------------------ cross-entropy (fwd + bwd in place)
 // One CTA per row of bf16 logits [rows, V].  loss[row] = lse - logit[target]; logits are overwritten with
-// d_logits = (softmax - onehot) * scale (scale read from device memory), zero for ignored rows.
+// d_logits = (softmax - onehot) * scale * row_weight[row] (scale read from device memory), zero for ignored rows.
+// row_weight is the hook for sequence-level objectives whose gradient is a per-token multiple of the log-likelihood gradient
+// (DPO: +-beta*sigmoid(-margin) per sequence; GRPO: clipped ratio x advantage per token).
+// Optional knowledge distillation on a teacher's top-K log-probabilities: kd_loss[row] = sum_k p_k (log p_k - log q_k) with
+// q the student softmax, and d_logits += kd_weight * (S * q - scatter(p)), S = sum_k p_k.  A row with an ignored target
+// contributes neither term.
 __global__ void __launch_bounds__(1024) cross_entropy_fwd_bwd_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ loss,
                                                                      const float* __restrict__ scale_ptr, float scale_host, int V, int ld,
-                                                                     int write_grad) {
+                                                                     int write_grad, const float* __restrict__ row_weight,
+                                                                     const int* __restrict__ kd_idx, const float* __restrict__ kd_logp, int kd_k,
+                                                                     float kd_weight, float* __restrict__ kd_loss) {
     __shared__ float sh[32];
+    __shared__ float kd_sum_p;
     const size_t row = blockIdx.x;
     bf16* lr = logits + row * ld;
     const int tgt = targets[row];
     if (tgt < 0) {
-        if (threadIdx.x == 0) loss[row] = 0.f;
+        if (threadIdx.x == 0) {
+            loss[row] = 0.f;
+            if (kd_loss) kd_loss[row] = 0.f;
+        }
         if (write_grad) {
             const uint4 z = make_uint4(0, 0, 0, 0);
             for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) *reinterpret_cast<uint4*>(lr + c) = z;
@@ -422,19 +433,55 @@ __global__ void __launch_bounds__(1024) cross_entropy_fwd_bwd_kernel(bf16* __res
     const float gsum = block_reduce<false>(sum, sh);
     const float lse = gmax + __logf(gsum);
     if (threadIdx.x == 0) loss[row] = lse - __bfloat162float(lr[tgt]);
+    float S = 0.f;
+    if (kd_k > 0) {  // the first warp walks the teacher's top-K entries of this row
+        if (threadIdx.x < 32) {
+            float kl = 0.f, sp = 0.f;
+            for (int k = threadIdx.x; k < kd_k; k += 32) {
+                const int j = kd_idx[row * kd_k + k];
+                if (j < 0 || j >= V) continue;
+                const float lp = kd_logp[row * kd_k + k];
+                const float pk = __expf(lp);
+                kl += pk * (lp - (__bfloat162float(lr[j]) - lse));
+                sp += pk;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) { kl += __shfl_xor_sync(0xffffffffu, kl, o); sp += __shfl_xor_sync(0xffffffffu, sp, o); }
+            if (threadIdx.x == 0) { kd_sum_p = sp; if (kd_loss) kd_loss[row] = kl; }
+        }
+        __syncthreads();
+        S = kd_sum_p;
+    }
     if (!write_grad) return;
     __syncthreads();
     const float scale = scale_host * (scale_ptr ? __ldg(scale_ptr) : 1.f);
+    const float w_ce = scale * (row_weight ? row_weight[row] : 1.f);
+    const float w_kd = kd_k > 0 ? scale * kd_weight : 0.f;
+    const float w_soft = w_ce + w_kd * S;
     for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
         float a[8];
         load8(lr + c, a);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            float pr = __expf(a[i] - lse);
-            if (c + i == tgt) pr -= 1.f;
-            a[i] = pr * scale;
+            float g = __expf(a[i] - lse) * w_soft;
+            if (c + i == tgt) g -= w_ce;
+            a[i] = g;
         }
         store8(lr + c, a);
+    }
+    if (kd_k > 0) {
+        __syncthreads();  // every gradient of the row is written; now subtract the teacher mass at its K positions
+        for (int k = threadIdx.x; k < kd_k; k += blockDim.x) {
+            const int j = kd_idx[row * kd_k + k];
+            if (j < 0 || j >= V) continue;
+            bool first = true;  // a repeated index is applied once per occurrence by the lowest k only (sequentially below)
+            for (int q = 0; q < k; ++q) first = first && kd_idx[row * kd_k + q] != j;
+            if (!first) continue;
+            float pm = 0.f;
+            for (int q = k; q < kd_k; ++q)
+                if (kd_idx[row * kd_k + q] == j) pm += __expf(kd_logp[row * kd_k + q]);
+            lr[j] = __float2bfloat16(__bfloat162float(lr[j]) - w_kd * pm);
+        }
     }
 }
 
@@ -672,8 +719,10 @@ void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad
     else embedding_bwd_kernel<bf16><<<grid, 256, 0, s>>>(tokens, (const bf16*)d_out, (bf16*)d_table, n, C);
 }
 void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,
-                           int write_grad, cudaStream_t s) {
-    cross_entropy_fwd_bwd_kernel<<<rows, 1024, 0, s>>>((bf16*)logits, targets, loss, scale_ptr, scale_host, V, ld, write_grad);
+                           int write_grad, const float* row_weight, const int* kd_idx, const float* kd_logp, int kd_k, float kd_weight, float* kd_loss,
+                           cudaStream_t s) {
+    cross_entropy_fwd_bwd_kernel<<<rows, 1024, 0, s>>>((bf16*)logits, targets, loss, scale_ptr, scale_host, V, ld, write_grad, row_weight, kd_idx,
+                                                       kd_logp, kd_k, kd_weight, kd_loss);
 }
 void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s) {
     const int grid = grid_for(n / 8, 256, num_sms);

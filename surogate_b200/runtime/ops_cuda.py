@@ -206,11 +206,21 @@ class CudaOps(RefOps):
             tgt, acc = ctx.grad_target("grad::" + op.inputs[1])
         scale_t = ctx.loss_scale if torch.is_tensor(ctx.loss_scale) else None
         scale_h = 1.0 if scale_t is not None else float(ctx.loss_scale)
+        rw = ctx.row_weights.reshape(-1).float().contiguous() if ctx.row_weights is not None else None
+        kd = ctx.kd
+        kd_idx = kd["idx"].reshape(n, -1).to(torch.int32).contiguous() if kd else None
+        kd_logp = kd["logp"].reshape(n, -1).float().contiguous() if kd else None
+        kd_losses = torch.zeros(n, dtype=torch.float32, device=x.device) if kd else None
+        if kd and kd.get("ce_weight", 1.0) != 1.0:  # total = ce_weight * CE + weight * KD
+            cw = torch.full((n,), float(kd["ce_weight"]), dtype=torch.float32, device=x.device)
+            rw = cw if rw is None else rw * cw
         for s in range(0, n, rows):
             e = min(s + rows, n)
             lg = logits[: e - s]
             gemm(x2[s:e], w, lg)
-            losses[s:e] = self.ext.cross_entropy_fwd_bwd(lg, t[s:e], scale_t, scale_h, train)
+            losses[s:e] = self.ext.cross_entropy_fwd_bwd(lg, t[s:e], scale_t, scale_h, train, rw[s:e] if rw is not None else None,
+                                                         kd_idx[s:e] if kd else None, kd_logp[s:e] if kd else None, float(kd["weight"]) if kd else 0.0,
+                                                         kd_losses[s:e] if kd else None)
             if train:
                 gemm(lg, w, dx[s:e], a_mn=False, b_mn=True)
                 if tgt is not None:
@@ -218,7 +228,14 @@ class CudaOps(RefOps):
                     acc = True
         if train:
             ctx.stash[op.outputs[0]] = dx.reshape(x.shape)
-        return (losses.sum(),)
+        if ctx.want_token_losses:
+            ctx.stash["token_losses"] = losses
+            if kd:
+                ctx.stash["token_kd"] = kd_losses
+        total = losses.sum()
+        if kd:  # reported loss = ce_weight * CE + weight * KD (the gradient above already carries both)
+            total = float(kd.get("ce_weight", 1.0)) * total + float(kd["weight"]) * kd_losses.sum()
+        return (total,)
 
 
 class CudaMoEPlan:

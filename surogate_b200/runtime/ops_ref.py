@@ -328,7 +328,8 @@ class RefOps:
 
     # ------------------------------------------------------------------ LM head + loss
     def fused_lm_head_loss(self, ctx, op, x, w, targets):
-        """Returns the summed CE over valid tokens.  In training mode also computes d_x (stashed) and d_w now."""
+        """Returns the summed CE over valid tokens.  In training mode also computes d_x (stashed) and d_w now.
+        Objective hooks (see ExecContext): per-token weights on the log-likelihood gradient, top-K distillation."""
         C = x.shape[-1]
         x2, t = x.reshape(-1, C), targets.reshape(-1).long()
         n = x2.shape[0]
@@ -342,6 +343,15 @@ class RefOps:
         scale = ctx.loss_scale
         cap = op.attrs.get("softcap", 0.0)
         rows = self.lmhead_chunk_rows
+        rw = ctx.row_weights.reshape(-1).float() if getattr(ctx, "row_weights", None) is not None else None
+        kd = getattr(ctx, "kd", None)
+        ce_w = float(kd.get("ce_weight", 1.0)) if kd else 1.0
+        kd_w = float(kd["weight"]) if kd else 0.0
+        kd_idx = kd["idx"].reshape(n, -1).long() if kd else None
+        kd_logp = kd["logp"].reshape(n, -1).float() if kd else None
+        tok_all = torch.zeros(n, dtype=torch.float32, device=x.device) if getattr(ctx, "want_token_losses", False) else None
+        kd_all = torch.zeros(n, dtype=torch.float32, device=x.device) if (kd and tok_all is not None) else None
+        kd_total = torch.zeros((), dtype=torch.float32, device=x.device)
         for s in range(0, n, rows):
             xs, ts = x2[s:s + rows], t[s:s + rows]
             logits = (xs @ w.to(xs.dtype).t()).float()
@@ -353,9 +363,24 @@ class RefOps:
             lse = torch.logsumexp(logits, dim=-1)
             tok_loss = (lse - logits.gather(1, tsafe[:, None]).squeeze(1)) * valid
             loss += tok_loss.sum()
+            if tok_all is not None:
+                tok_all[s:s + rows] = tok_loss
+            if kd:
+                ki, kl = kd_idx[s:s + rows], kd_logp[s:s + rows]
+                pk = torch.exp(kl)
+                kd_tok = (pk * (kl - (logits.gather(1, ki) - lse[:, None]))).sum(1) * valid
+                kd_total += kd_tok.sum()
+                if kd_all is not None:
+                    kd_all[s:s + rows] = kd_tok
             if train:
-                p = torch.exp(logits - lse[:, None])
-                p.scatter_add_(1, tsafe[:, None], -torch.ones_like(p[:, :1]))
+                q = torch.exp(logits - lse[:, None])
+                w_row = torch.ones_like(lse) if rw is None else rw[s:s + rows]
+                w_row = w_row * ce_w
+                p = q * w_row[:, None]
+                p.scatter_add_(1, tsafe[:, None], -w_row[:, None])
+                if kd:
+                    p += kd_w * pk.sum(1, keepdim=True) * q
+                    p.scatter_add_(1, ki, -kd_w * pk)
                 p *= (valid[:, None] * scale)
                 if cap:
                     p *= (1 - th * th)
@@ -370,6 +395,12 @@ class RefOps:
                         acc = True
         if train:
             ctx.stash[op.outputs[0]] = dx.reshape(x.shape)
+        if tok_all is not None:
+            ctx.stash["token_losses"] = tok_all
+            if kd_all is not None:
+                ctx.stash["token_kd"] = kd_all
+        if kd:
+            loss = ce_w * loss + kd_w * kd_total
         return (loss,)
 
     def fused_lm_head_loss_backward(self, ctx, op, d_loss, x, w, targets, loss):

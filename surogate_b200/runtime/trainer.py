@@ -218,8 +218,12 @@ class Trainer:
         return arr
 
     # ------------------------------------------------------------------ the step
-    def forward_backward(self, inputs, targets, position_ids=None) -> Dict[str, torch.Tensor]:
-        """All micro-batches of one optimizer step; leaves reduced gradients in the store.  Returns device scalars."""
+    def forward_backward(self, inputs, targets, position_ids=None, row_weights=None, kd=None, loss_scale_override=None) -> Dict[str, torch.Tensor]:
+        """All micro-batches of one optimizer step; leaves reduced gradients in the store.  Returns device scalars.
+
+        ``row_weights`` ([rows, T] float) multiplies each token's log-likelihood gradient (sequence-level objectives: DPO,
+        GRPO); ``kd`` = {"idx", "logp", "weight", "ce_weight"} adds top-K distillation; ``loss_scale_override`` replaces the
+        default 1 / (global number of target tokens) normalisation."""
         cfg = self.cfg
         B, GA, T = cfg.batch_size, cfg.grad_accum, inputs.shape[1]
         inp = self._stage("inputs", self._local_slice(inputs))
@@ -236,6 +240,12 @@ class Trainer:
         if self.world > 1:
             self.comm.all_reduce(n_valid, "sum")
         loss_scale = (1.0 / n_valid.clamp_min(1.0)).reshape(1)
+        if loss_scale_override is not None:
+            loss_scale = torch.full((1,), float(loss_scale_override), dtype=torch.float32, device=self.device)
+        if row_weights is not None:
+            row_weights = self._stage("row_weights", self._local_slice(row_weights), dtype=torch.float32)
+        if kd is not None:
+            kd = dict(kd, idx=self._stage("kd_idx", self._local_slice(kd["idx"])), logp=self._stage("kd_logp", self._local_slice(kd["logp"]), dtype=torch.float32))
         if self.device.type != "cuda":
             loss_scale = float(loss_scale)
         aux_scale = 1.0 / (GA * self.world)
@@ -248,7 +258,9 @@ class Trainer:
             self.store.begin_micro_step(i, GA)
             sl = slice(i * B, (i + 1) * B)
             ctx, outs = self.executor.forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale=loss_scale, aux_scale=aux_scale,
-                                                       doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i)
+                                                       doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i,
+                                                       row_weights=row_weights[sl] if row_weights is not None else None,
+                                                       kd=dict(kd, idx=kd["idx"][sl], logp=kd["logp"][sl]) if kd is not None else None)
             loss_sum += outs[0]
             if len(outs) > 1 and outs[1] is not None:
                 aux_sum += outs[1] * aux_scale
@@ -338,6 +350,32 @@ class Trainer:
 
             check_device_errors()
         return {"loss": float(out[0]), "norm": float(out[1]), "aux_loss": float(out[2])}
+
+    @torch.no_grad()
+    def token_logprobs(self, inputs, targets, position_ids=None, use_adapters: bool = True) -> torch.Tensor:
+        """log p(target_t | prefix) for every position ([rows, T] float32 on the device, 0 where the target is ignored).
+        ``use_adapters=False`` runs the frozen base model of a LoRA run (the DPO / GRPO reference policy)."""
+        inp = self._stage("lp_inputs", inputs)
+        tgt = self._stage("lp_targets", targets)
+        rows, T = inp.shape
+        if position_ids is None:
+            pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(rows, T).contiguous()
+        else:
+            pos = self._stage("lp_pos", position_ids)
+        out = torch.empty(rows, T, dtype=torch.float32, device=self.device)
+        self.store.grads_enabled = False
+        saved_lora = self.executor.lora
+        if not use_adapters:
+            self.executor.lora = None
+        try:
+            B = max(1, self.cfg.batch_size)
+            for s in range(0, rows, B):
+                ctx, _ = self.executor.forward(inp[s:s + B], pos[s:s + B], tgt[s:s + B], training=False, want_token_losses=True)
+                out[s:s + B] = -ctx.stash["token_losses"].reshape(-1, T)
+        finally:
+            self.store.grads_enabled = True
+            self.executor.lora = saved_lora
+        return out
 
     @torch.no_grad()
     def validate(self, inputs, targets, position_ids=None) -> Dict[str, float]:

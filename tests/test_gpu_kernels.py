@@ -326,3 +326,33 @@ def test_embedding_rejects_out_of_range_token_ids():
     with pytest.raises(RuntimeError, match="token id"):
         check_device_errors()
     check_device_errors()  # the flag was reset by the failed check
+
+
+def test_cross_entropy_row_weights_and_topk_distillation():
+    """The CE kernel's per-row weights (DPO / GRPO) and top-K KD term against an fp32 autograd reference."""
+    from surogate_b200.ops import ext
+
+    e = ext()
+    torch.manual_seed(0)
+    rows, V, K = 48, 4096, 16
+    logits = (torch.randn(rows, V, device="cuda") * 3).bfloat16()
+    tgt = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    tgt[5] = -100
+    rw = torch.randn(rows, device="cuda")
+    teacher = torch.log_softmax(torch.randn(rows, V, device="cuda") * 2, -1)
+    kl, ki = teacher.topk(K, -1)
+    scale = torch.tensor([0.5], device="cuda")
+    ref = logits.float().clone().requires_grad_(True)
+    lp = torch.log_softmax(ref, -1)
+    valid = (tgt >= 0).float()
+    ce = -lp.gather(1, tgt.clamp_min(0).long()[:, None]).squeeze(1) * valid
+    kd = (kl.exp() * (kl - lp.gather(1, ki))).sum(1) * valid
+    (0.5 * ((ce * rw).sum() + 0.25 * kd.sum())).backward()
+    work = logits.clone()
+    kd_out = torch.empty(rows, device="cuda")
+    loss = e.cross_entropy_fwd_bwd(work, tgt, scale, 1.0, True, rw, ki.to(torch.int32).contiguous(), kl.contiguous(), 0.25, kd_out)
+    torch.testing.assert_close(loss, ce.detach(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(kd_out, kd.detach(), rtol=5e-3, atol=5e-3)
+    err = (work.float() - ref.grad).abs().max().item()
+    assert err < 2e-2 * ref.grad.abs().max().item() + 1e-3, err
+    assert work[5].abs().sum() == 0

@@ -67,6 +67,21 @@ def moe_mlp(h, p, L, cfg):
     return y.view(B, T, C), aux
 
 
+def model_logits(p, tokens, cfg, pos=None):
+    """Logits [B, T, V] of a dense model (same math as model_loss, in the dtype of the parameters)."""
+    if pos is None:
+        pos = torch.arange(tokens.shape[1], dtype=torch.int32)[None].expand(tokens.shape[0], -1)
+    x = p["embedding"][tokens]
+    for L in range(cfg["n_layers"]):
+        h = rms(x, p[f"blocks.{L}.ln1_weight"], cfg["eps"])
+        x = x + attention(h, p, L, cfg, pos)
+        h = rms(x, p[f"blocks.{L}.ln2_weight"], cfg["eps"])
+        x = x + dense_mlp(h, p, L)
+    x = rms(x, p["final_norm"], cfg["eps"])
+    w = p["lm_head"] if "lm_head" in p else p["embedding"]
+    return x @ w.t()
+
+
 def model_loss(p, tokens, pos, targets, cfg):
     """Returns (sum CE over valid tokens, sum of aux losses)."""
     x = p["embedding"][tokens]
