@@ -1,0 +1,150 @@
+"""GRPO orchestrator: prompts -> rollouts from an OpenAI-compatible inference server -> rewards -> group advantages ->
+packed batches -> transport to the trainer, kept at most ``max_async_level`` policy versions ahead of the trainer.
+
+The inference client is an interface (``generate(prompt_ids | messages, n, sampling) -> [(token_ids, logprobs, text)]``);
+``OpenAIClient`` talks to vLLM's ``/v1/completions`` with ``logprobs`` and ``return_token_ids``; tests inject a fake.
+The depth controller blocks generation of step ``s`` until the trainer has published policy version
+``s - max_async_level`` — rollouts are never more than that many updates stale, and their recorded
+``policy_version`` lets the trainer's ratio cap drop what is too far off-policy.
+
+Parity: surogate/grpo/orchestrator/grpo_orch.py (rollout loop, buffer, scheduler, depth controller).
+"""
+from __future__ import annotations
+
+import json
+import time
+import urllib.request
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .config import OrchestratorConfig
+from .loss import group_advantages
+from .packer import PackedBatch, Rollout, pack_rollouts
+from .rewards import resolve_reward
+
+
+class OpenAIClient:
+    def __init__(self, base_url: str, model: str, timeout_s: float = 600.0, api_key: str = "EMPTY"):
+        self.url, self.model, self.timeout, self.key = base_url.rstrip("/") + "/completions", model, timeout_s, api_key
+
+    def generate(self, prompt_ids: List[int], n: int, sampling: Dict[str, Any]) -> List[Tuple[List[int], List[float], str]]:
+        body = {"model": self.model, "prompt": prompt_ids, "n": n, "logprobs": 1, "return_token_ids": True, **sampling}
+        req = urllib.request.Request(self.url, data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json", "Authorization": f"Bearer {self.key}"})
+        with urllib.request.urlopen(req, timeout=self.timeout) as r:
+            resp = json.loads(r.read())
+        out = []
+        for ch in resp["choices"]:
+            lp = ch.get("logprobs") or {}
+            ids = ch.get("token_ids") or []
+            out.append((list(ids), [float(x) for x in (lp.get("token_logprobs") or [])], ch.get("text", "")))
+        return out
+
+
+class DepthController:
+    """Keeps generation within ``max_async_level`` policy versions of the trainer."""
+
+    def __init__(self, max_async_level: int, current_version: Callable[[], int], poll_s: float = 0.05, timeout_s: float = 3600.0):
+        self.k, self.version, self.poll, self.timeout = max_async_level, current_version, poll_s, timeout_s
+
+    def wait_until_allowed(self, step: int) -> int:
+        t0 = time.time()
+        while True:
+            v = self.version()
+            if step - v <= self.k:
+                return v
+            if time.time() - t0 > self.timeout:
+                raise TimeoutError(f"trainer did not reach policy version {step - self.k} (at {v})")
+            time.sleep(self.poll)
+
+
+@dataclass
+class StepStats:
+    step: int
+    reward_mean: float
+    reward_std: float
+    completion_len: float
+    groups_kept: int
+    groups_total: int
+    policy_version: int
+    rows: int
+
+
+class Orchestrator:
+    def __init__(self, cfg: OrchestratorConfig, tokenizer, client, transport, policy_version: Callable[[], int], reward_fn=None):
+        self.cfg, self.tok, self.client, self.transport = cfg, tokenizer, client, transport
+        self.reward_fn = reward_fn or resolve_reward(cfg.reward)
+        self.depth = DepthController(cfg.max_async_level, policy_version)
+        self.rng = np.random.default_rng(cfg.seed)
+        self.prompts: List[Dict[str, Any]] = []
+        self.buffer: List[Rollout] = []
+        self.history: List[StepStats] = []
+
+    def load_prompts(self, rows: Optional[Sequence[Dict[str, Any]]] = None) -> None:
+        if rows is None:
+            with open(self.cfg.prompts) as f:
+                rows = [json.loads(l) for l in f if l.strip()]
+        self.prompts = list(rows)
+
+    def _prompt_ids(self, row: Dict[str, Any]) -> List[int]:
+        p = row["prompt"]
+        if isinstance(p, list):
+            return self.tok.apply_chat_template_and_encode(p, add_generation_prompt=True)
+        return self.tok.apply_chat_template_and_encode([{"role": "user", "content": str(p)}], add_generation_prompt=True)
+
+    def collect(self, step: int, version: int) -> Tuple[List[Rollout], Dict[str, float]]:
+        c = self.cfg
+        idx = self.rng.choice(len(self.prompts), size=min(c.prompts_per_step, len(self.prompts)), replace=False)
+        sampling = {"max_tokens": c.max_tokens, "temperature": c.temperature, "top_p": c.top_p, **c.extra_sampling}
+        rollouts: List[Rollout] = []
+        rewards_all, lens, kept = [], [], 0
+        for g, i in enumerate(idx):
+            row = self.prompts[int(i)]
+            pids = self._prompt_ids(row)
+            gens = self.client.generate(pids, c.group_size, sampling)
+            rewards = [float(r) for r in self.reward_fn(row, [t for _, _, t in gens])]
+            if c.length_penalty:
+                rewards = [r - c.length_penalty * len(ids) for r, (ids, _, _) in zip(rewards, gens)]
+            rewards_all += rewards
+            lens += [len(ids) for ids, _, _ in gens]
+            adv = group_advantages(torch.tensor(rewards), len(rewards), c.advantage_std_eps).tolist()
+            if c.filter_zero_advantage and max(rewards) - min(rewards) < 1e-12:
+                continue
+            kept += 1
+            for (ids, lps, _), a, r in zip(gens, adv, rewards):
+                if ids and len(lps) == len(ids):
+                    rollouts.append(Rollout(pids, ids, lps, a, r, version, g))
+        stats = {"reward_mean": float(np.mean(rewards_all)) if rewards_all else 0.0, "reward_std": float(np.std(rewards_all)) if rewards_all else 0.0,
+                 "completion_len": float(np.mean(lens)) if lens else 0.0, "groups_kept": kept, "groups_total": len(idx)}
+        return rollouts, stats
+
+    def run_step(self, step: int) -> StepStats:
+        version = self.depth.wait_until_allowed(step)
+        need_rows = self.cfg.rows_per_step
+        stats: Dict[str, float] = {}
+        attempts = 0
+        batches: List[PackedBatch] = []
+        while not batches or batches[0].n_samples == 0:
+            rollouts, stats = self.collect(step, version)
+            self.buffer += rollouts
+            batches = pack_rollouts(self.buffer, self.cfg.sequence_len, need_rows, self.tok.pad_token_id if self.tok.pad_token_id >= 0 else 0)
+            attempts += 1
+            if attempts > 16:
+                raise RuntimeError("no rollout group with a reward spread after 16 attempts: the reward function gives no signal")
+        first = batches[0]
+        self.buffer = []  # what did not fit into the first batch is dropped rather than trained on stale
+        self.transport.send(step, first.arrays(), {"policy_version": first.policy_version, "n_samples": first.n_samples, **stats})
+        st = StepStats(step, stats["reward_mean"], stats["reward_std"], stats["completion_len"], int(stats["groups_kept"]), int(stats["groups_total"]),
+                       version, need_rows)
+        self.history.append(st)
+        return st
+
+    def run(self, start_step: int = 0) -> List[StepStats]:
+        for step in range(start_step, self.cfg.max_steps):
+            self.run_step(step)
+            if hasattr(self.transport, "acked"):
+                self.transport.cleanup(self.transport.acked() - 1)
+        return self.history

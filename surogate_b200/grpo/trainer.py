@@ -1,0 +1,111 @@
+"""GRPO trainer: consumes packed rollout batches, takes one clipped-policy-gradient step per batch, publishes weights.
+
+Step: (1) current-policy token log-probs (no-grad forward); (2) reference log-probs with adapters disabled when a KL
+term is configured; (3) per-token weights from ``grpo/loss.py``; (4) forward+backward where the fused LM-head loss kernel
+scales each token's log-likelihood gradient by its weight; (5) clip + optimizer; (6) every ``broadcast_every`` steps the
+new policy is published and the version counter advances.
+
+Parity: surogate/grpo/trainer.py, surogate/grpo/loss.py.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Any, Dict, Optional
+
+import numpy as np
+import torch
+
+from ..runtime.trainer import Trainer
+from .config import GRPOConfig, GRPOLossConfig
+from .loss import grpo_token_weights
+
+
+class GRPOTrainer:
+    def __init__(self, trainer: Trainer, loss: Optional[GRPOLossConfig] = None):
+        self.t = trainer
+        self.loss = loss or GRPOLossConfig()
+        self.policy_version = 0
+
+    def _slice(self, a: np.ndarray) -> np.ndarray:
+        t = self.t
+        rows = t.cfg.batch_size * t.cfg.grad_accum
+        if a.shape[0] == rows * t.world and t.world > 1:
+            return a[t.rank * rows:(t.rank + 1) * rows]
+        assert a.shape[0] == rows, f"batch has {a.shape[0]} rows, expected {rows} per rank"
+        return a
+
+    def step(self, batch: Dict[str, np.ndarray], lr: Optional[float] = None) -> Dict[str, float]:
+        t, L = self.t, self.loss
+        x, y, pos = self._slice(batch["inputs"]), self._slice(batch["targets"]), self._slice(batch["position_ids"])
+        dev = t.device
+        adv = torch.from_numpy(self._slice(batch["advantages"])).to(dev)
+        old = torch.from_numpy(self._slice(batch["old_logprobs"])).to(dev)
+        seq = torch.from_numpy(self._slice(batch["seq_ids"])).to(dev)
+        mask = torch.from_numpy((y != -100)).to(dev)
+        if L.advantage_clip:
+            adv = adv.clamp(-L.advantage_clip, L.advantage_clip)
+        logp = t.token_logprobs(x, y, pos)
+        ref = t.token_logprobs(x, y, pos, use_adapters=False) if (L.kl_coef and t.lora is not None) else None
+        loss, w, metrics = grpo_token_weights(logp, old, adv, mask, ref, L.clip_eps_low, L.clip_eps_high, L.kl_coef, L.ratio_cap, L.normalization, seq)
+        if t.world > 1:  # the normaliser above is per rank: average the ranks' objectives
+            w = w / t.world
+        t.forward_backward(x, y, pos, row_weights=w, loss_scale_override=1.0)
+        norm = t.optimizer_step(lr)
+        keys = sorted(metrics)
+        vals = torch.stack([loss, norm] + [metrics[k].float() for k in keys]).float()
+        if t.world > 1:
+            red = vals.clone()
+            t.comm.all_reduce(red, "sum")
+            red /= t.world
+            red[1] = vals[1]
+            vals = red
+        host = vals.to("cpu").tolist()
+        out = {"loss": host[0], "norm": host[1], **{k: v for k, v in zip(keys, host[2:])}}
+        return out
+
+
+def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
+    from ..parallel.dist import TorchComm, init_distributed
+    from ..train.logging import TrainingRunLogger
+    from ..train.lr_schedule import LRSchedule
+    from ..train.sft import resolve_model_config
+    from .transport import make_transport
+    from .weight_broadcast import FilesystemBroadcast
+
+    info = init_distributed()
+    comm = TorchComm() if info.world > 1 else None
+    device = torch.device("cuda", info.local_rank) if torch.cuda.is_available() else torch.device("cpu")
+    hf_cfg = resolve_model_config(cfg)
+    trainer = Trainer(cfg.to_trainer_config(hf_cfg), device=device, comm=comm)
+    if isinstance(cfg.model, str) and os.path.isdir(cfg.model):
+        trainer.import_weights(cfg.model)
+        if trainer.lora is not None:
+            trainer.lora.init_weights(cfg.train_seed)
+    else:
+        trainer.init_weights(cfg.train_seed)
+    transport = make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="consumer")
+    bcast = FilesystemBroadcast(cfg.weight_dir)
+    g = GRPOTrainer(trainer, cfg.loss)
+    bcast.publish(trainer, 0, hf_cfg)  # version 0 = the initial policy: lets the orchestrator start
+    max_steps = cfg.max_steps if cfg.max_steps > 0 else 100
+    sched = LRSchedule(cfg.learning_rate, max_steps, cfg.warmup_steps, cfg.cooldown_steps, cfg.final_lr_fraction * cfg.learning_rate,
+                       cfg.lr_scheduler_type, cfg.wsd_decay_steps_fraction)
+    logger = TrainingRunLogger(cfg.log_file, None, is_main=info.is_main)
+    history = []
+    for step in range(max_steps):
+        t0 = time.perf_counter()
+        batch, meta = transport.receive(step)
+        wait_ms = (time.perf_counter() - t0) * 1e3
+        out = g.step(batch, lr=sched.get_lr(step))
+        out.update(wait_ms=wait_ms, ms=(time.perf_counter() - t0) * 1e3, off_policy=g.policy_version - int(meta.get("policy_version", 0)),
+                   reward_mean=meta.get("reward_mean"))
+        if (step + 1) % cfg.broadcast_every == 0:
+            g.policy_version += 1
+            bcast.publish(trainer, g.policy_version, hf_cfg)
+        if info.is_main:
+            transport.ack(step)
+        logger.log_record("grpo", step=step + 1, **out)
+        history.append(out)
+    logger.close()
+    return {"steps": len(history), "history": history}
