@@ -111,6 +111,7 @@ class DataLoader:
             return x, y, p
         row = 0
         guard = 0
+        self.last_rows = []  # (file path, chunk index) of every row served: lets sidecar data (teacher log-probs) follow the batch
         while row < B:
             if self._cur is None:
                 self._open(self.file_index)
@@ -123,6 +124,7 @@ class DataLoader:
                 continue
             c = int(order[self.chunk_index])
             self.chunk_index += 1
+            self.last_rows.append((self.files[self._file_order[self.file_index]], c))
             s = c * T
             x[row] = tok[s:s + T]
             p[row] = pos[s:s + T] if pos is not None else np.arange(T, dtype=np.int32)
@@ -163,6 +165,27 @@ class DataLoader:
         self._nat.next_into(x.data_ptr(), y.data_ptr(), p.data_ptr())
         st = self._nat.state()
         self.epoch, self.file_index, self.chunk_index = st["epoch"], st["file_index"], st["chunk_index"]
+
+
+class DistillationFeed:
+    """Teacher top-K log-probs (``.kd`` sidecars) for the rows a numpy-path ``DataLoader`` just served."""
+
+    def __init__(self, loader: "DataLoader"):
+        from ..distill.sidecar import SidecarReader, sidecar_path
+
+        if loader._nat is not None:
+            raise ValueError("distillation needs DataLoader(native=False): the sidecar rows follow the loader's row bookkeeping")
+        self.loader = loader
+        self.readers = {f: SidecarReader(sidecar_path(f)) for f in loader.files}
+        self.K = next(iter(self.readers.values())).K
+
+    def batch(self):
+        T = self.loader.T
+        idx = np.empty((len(self.loader.last_rows), T, self.K), np.int32)
+        lp = np.empty((len(self.loader.last_rows), T, self.K), np.float32)
+        for r, (f, c) in enumerate(self.loader.last_rows):
+            idx[r], lp[r] = self.readers[f].rows(c * T, T)
+        return idx, lp
 
 
 def write_synthetic_tokens(path: str, n_rows: int, seq_len: int, vocab: int, seed: int = 0) -> str:

@@ -1,0 +1,92 @@
+"""Teacher capture (``surogate distill-capture``): run a teacher over token shards and store its top-K log-probs.
+
+Teachers: a model trained / loadable by this framework (forward through the Trainer's executor with a hook on the
+logits), a HuggingFace ``transformers`` model (local directory), or an OpenAI-compatible API that returns
+``top_logprobs`` for a prompt (vLLM's ``prompt_logprobs``).  One ``.kd`` file is written next to each shard.
+
+Parity: surogate/distill/capture.py.
+"""
+from __future__ import annotations
+
+import json
+import os
+import urllib.request
+from typing import Callable, Dict, Iterable, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..data.tokfile import read_token_file
+from .sidecar import SidecarWriter, sidecar_path
+
+TeacherFn = Callable[[np.ndarray], torch.Tensor]  # int32 [rows, T] -> logits [rows, T, V]
+
+
+def topk_logprobs(logits: torch.Tensor, k: int, temperature: float = 1.0) -> Tuple[np.ndarray, np.ndarray]:
+    lp = torch.log_softmax(logits.float() / temperature, dim=-1)
+    v, i = lp.topk(k, dim=-1)
+    return i.to(torch.int32).cpu().numpy(), v.cpu().numpy()
+
+
+def hf_teacher(model_dir: str, device: str = "cuda", dtype=torch.bfloat16) -> TeacherFn:
+    from transformers import AutoModelForCausalLM
+
+    model = AutoModelForCausalLM.from_pretrained(model_dir, torch_dtype=dtype).to(device).eval()
+
+    @torch.no_grad()
+    def fn(tokens: np.ndarray) -> torch.Tensor:
+        return model(torch.from_numpy(tokens.astype(np.int64)).to(device)).logits
+
+    return fn
+
+
+def native_teacher(trainer) -> TeacherFn:
+    """A model held by this framework's Trainer: logits = final hidden states x LM head (computed in row chunks)."""
+
+    @torch.no_grad()
+    def fn(tokens: np.ndarray) -> torch.Tensor:
+        return trainer.logits(tokens)
+
+    return fn
+
+
+def api_teacher_rows(base_url: str, model: str, k: int, timeout_s: float = 600.0):
+    """vLLM-style ``prompt_logprobs``: returns a function rows -> (indices, logprobs) directly (no logits leave the server)."""
+    url = base_url.rstrip("/") + "/completions"
+
+    def fn(tokens: np.ndarray):
+        idx = np.zeros(tokens.shape + (k,), np.int32)
+        lp = np.full(tokens.shape + (k,), -30.0, np.float32)
+        for r, row in enumerate(tokens):
+            body = {"model": model, "prompt": [int(t) for t in row], "max_tokens": 1, "prompt_logprobs": k, "temperature": 0.0}
+            req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=timeout_s) as resp:
+                pl = json.loads(resp.read())["choices"][0]["prompt_logprobs"]
+            # entry t (t >= 1) is the distribution that predicted token t: store it at position t-1
+            for t in range(1, len(pl)):
+                items = sorted(((int(tok), d["logprob"]) for tok, d in (pl[t] or {}).items()), key=lambda x: -x[1])[:k]
+                for j, (tok, l) in enumerate(items):
+                    idx[r, t - 1, j], lp[r, t - 1, j] = tok, l
+        return idx, lp
+
+    return fn
+
+
+def capture_shard(shard: str, teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, temperature: float = 1.0, rows_per_call: int = 4,
+                  out_path: Optional[str] = None, direct=None) -> str:
+    tok, _, _, h = read_token_file(shard)
+    n_rows = h["n_tokens"] // seq_len
+    w = SidecarWriter(out_path or sidecar_path(shard), top_k, vocab, temperature)
+    for s in range(0, n_rows, rows_per_call):
+        rows = np.stack([np.asarray(tok[r * seq_len:(r + 1) * seq_len]) for r in range(s, min(n_rows, s + rows_per_call))])
+        if direct is not None:
+            idx, lp = direct(rows)
+        else:
+            idx, lp = topk_logprobs(teacher(rows), top_k, temperature)
+        w.add(idx.reshape(-1, top_k), lp.reshape(-1, top_k))
+    w.close()
+    return w.path
+
+
+def capture(shards: Iterable[str], teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, **kw) -> List[str]:
+    return [capture_shard(s, teacher, seq_len, top_k, vocab, **kw) for s in shards]

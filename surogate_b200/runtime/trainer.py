@@ -337,8 +337,8 @@ class Trainer:
         self.recipe.end_step()
         return norm
 
-    def step(self, inputs, targets, position_ids=None, lr: Optional[float] = None) -> Dict[str, float]:
-        r = self.forward_backward(inputs, targets, position_ids)
+    def step(self, inputs, targets, position_ids=None, lr: Optional[float] = None, kd=None, row_weights=None) -> Dict[str, float]:
+        r = self.forward_backward(inputs, targets, position_ids, row_weights=row_weights, kd=kd)
         norm = self.optimizer_step(lr)
         loss = r["loss_sum"].clone()
         if self.world > 1:
@@ -376,6 +376,31 @@ class Trainer:
             self.store.grads_enabled = True
             self.executor.lora = saved_lora
         return out
+
+    @torch.no_grad()
+    def logits(self, inputs, position_ids=None) -> torch.Tensor:
+        """Full logits [rows, T, V] (fp32) — for teacher capture and debugging, not a training path."""
+        inp = self._stage("lg_inputs", inputs)
+        rows, T = inp.shape
+        pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(rows, T).contiguous() if position_ids is None \
+            else self._stage("lg_pos", position_ids)
+        tgt = torch.full_like(inp, -100)
+        captured = {}
+        prev = self.executor.options.dump_tensors
+        self.executor.options.dump_tensors = lambda name, layer, val: captured.__setitem__(name, val) if layer is None else None
+        self.store.grads_enabled = False
+        try:
+            self.executor.forward(inp, pos, tgt, training=False)
+        finally:
+            self.executor.options.dump_tensors = prev
+            self.store.grads_enabled = True
+        fwd = self.cm.fwd
+        head = next(op for op in fwd.ops if op.kind == "fused_lm_head_loss")
+        x = captured[head.inputs[0]]
+        if hasattr(x, "dequantize"):
+            x = x.hp if getattr(x, "hp", None) is not None else x.dequantize()
+        w = self.store.get(head.inputs[1])
+        return (x.reshape(-1, x.shape[-1]).float() @ w.float().t()).reshape(rows, T, -1)
 
     @torch.no_grad()
     def validate(self, inputs, targets, position_ids=None) -> Dict[str, float]:

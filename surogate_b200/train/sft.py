@@ -118,7 +118,13 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     logger.log_record("options", config=json.loads(cfg.to_json()))
 
     B, GA, T = cfg.per_device_train_batch_size, cfg.gradient_accumulation_steps, cfg.sequence_len
-    loader = DataLoader(files["train"], B * GA, T, seed=cfg.train_seed, rank=info.rank, world=info.world)
+    distill = cfg.distillation if (cfg.distillation is not None and cfg.distillation.enabled) else None
+    loader = DataLoader(files["train"], B * GA, T, seed=cfg.train_seed, rank=info.rank, world=info.world, native=False if distill else None)
+    kd_feed = None
+    if distill:
+        from ..data.loader import DistillationFeed
+
+        kd_feed = DistillationFeed(loader)  # needs train-NNN.kd next to every shard (surogate distill-capture)
     eval_loader = DataLoader(files["eval"], B, T, seed=cfg.eval_seed, rank=info.rank, world=info.world, shuffle=False) if files.get("eval") else None
     steps_per_epoch = max(1, loader.steps_per_epoch())
     max_steps = cfg.max_steps if cfg.max_steps > 0 else steps_per_epoch * cfg.num_epochs
@@ -166,7 +172,11 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
         if cfg.loss_scale == "all":
             pass  # every token is a target (pre-training); masks in the shard are already all ones
         lr = sched.get_lr(step)
-        out = trainer.step(x, y, p if cfg.sample_packing else None, lr=lr)
+        kd = None
+        if kd_feed is not None:
+            ki, kl = kd_feed.batch()
+            kd = {"idx": ki, "logp": kl, "weight": distill.kd_weight, "ce_weight": 1.0 - distill.kd_weight}
+        out = trainer.step(x, y, p if cfg.sample_packing else None, lr=lr, kd=kd)
         ms = (time.perf_counter() - t0) * 1e3
         losses.append(out["loss"])
         norms.append(out["norm"])

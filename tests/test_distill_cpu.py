@@ -1,0 +1,62 @@
+"""KD sidecars: format round trip, capture from a teacher held by the Trainer, training with the distillation term."""
+import os
+
+import numpy as np
+import torch
+
+from surogate_b200.data.loader import write_synthetic_tokens
+from surogate_b200.distill.capture import capture_shard, native_teacher
+from surogate_b200.distill.sidecar import KD_MAGIC, SidecarReader, SidecarWriter
+from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+MODEL = dict(architecture="Qwen3ForCausalLM", vocab_size=96, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64,
+             tie_word_embeddings=True)
+
+
+def _trainer(seed):
+    t = Trainer(TrainerConfig(model=MODEL, batch_size=2, seq_len=16, recipe="bf16", optimizer="adamw", learning_rate=2e-2, zero_level=0),
+                device=torch.device("cpu"))
+    t.init_weights(seed=seed)
+    return t
+
+
+def test_sidecar_round_trip(tmp_path):
+    p = os.path.join(tmp_path, "a.kd")
+    w = SidecarWriter(p, top_k=4, vocab_size=96, temperature=2.0)
+    idx = np.arange(40, dtype=np.int32).reshape(10, 4)
+    lp = -np.linspace(0.1, 4.0, 40, dtype=np.float32).reshape(10, 4)
+    w.add(idx, lp)
+    assert w.close() == 10
+    with open(p, "rb") as f:
+        assert f.read(8) == KD_MAGIC
+    r = SidecarReader(p)
+    assert (r.K, r.N, r.vocab, r.temperature) == (4, 10, 96, 2.0)
+    i2, l2 = r.rows(3, 5)
+    assert np.array_equal(i2, idx[3:8]) and np.allclose(l2, lp[3:8], atol=2e-3)
+
+
+def test_capture_and_distill(tmp_path):
+    shard = write_synthetic_tokens(os.path.join(tmp_path, "train-000.bin"), 4, 16, 96, seed=1)
+    teacher, student = _trainer(11), _trainer(22)
+    kd_path = capture_shard(shard, native_teacher(teacher), 16, top_k=8, vocab=96, rows_per_call=2)
+    r = SidecarReader(kd_path)
+    assert r.N == 64 and r.K == 8
+    from surogate_b200.data.tokfile import read_token_file
+
+    tok, _, _, _ = read_token_file(shard)
+    x = np.asarray(tok[:32]).reshape(2, 16)
+    # the sidecar holds the teacher's own top-K log-probs
+    lg = teacher.logits(x)
+    lp = torch.log_softmax(lg, -1).topk(8, -1)
+    i0, l0 = r.rows(0, 32)
+    assert np.array_equal(i0.reshape(2, 16, 8), lp.indices.numpy()) and np.allclose(l0.reshape(2, 16, 8), lp.values.numpy(), atol=5e-3)
+    y = np.concatenate([x[:, 1:], np.full((2, 1), -100, np.int32)], axis=1)
+    kd = {"idx": torch.from_numpy(i0.reshape(2, 16, 8)), "logp": torch.from_numpy(l0.reshape(2, 16, 8)), "weight": 1.0, "ce_weight": 0.0}
+    first = last = None
+    for _ in range(25):
+        res = student.forward_backward(x, y, kd=kd)
+        student.optimizer_step()
+        v = float(res["loss_sum"] / res["n_valid"])
+        first = v if first is None else first
+        last = v
+    assert last < 0.5 * first, (first, last)  # the student moves toward the teacher's distribution
