@@ -1,0 +1,48 @@
+"""``surogate debug {weights,registry,activations,gradients,diff}``.  Parity: surogate/cli/debug.py."""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+
+def main(argv, command: str = "debug") -> int:
+    p = argparse.ArgumentParser(prog="surogate debug")
+    sub = p.add_subparsers(dest="what", required=True)
+    for name in ("weights", "registry", "activations", "gradients", "diff"):
+        s = sub.add_parser(name)
+        s.add_argument("model", nargs="?" if name == "registry" else None, help="model directory (or architecture name for `registry`)")
+        s.add_argument("--out", default=None, help="JSONL report path")
+        s.add_argument("--seq-len", type=int, default=128)
+        s.add_argument("--batch", type=int, default=1)
+        s.add_argument("--seed", type=int, default=0)
+    a = p.parse_args(argv)
+    from ..debug import tools
+
+    if a.what == "weights":
+        print(json.dumps(tools.audit_weights(a.model, a.out), indent=1))
+        return 0
+    if a.what == "registry":
+        for r in tools.registry_report(a.model, a.out)[:4]:
+            print(json.dumps(r)[:2000])
+        return 0
+    import torch
+
+    from ..dsl.compiler import load_hf_config
+    from ..runtime.trainer import Trainer, TrainerConfig
+
+    cfg = load_hf_config(a.model)
+    rng = np.random.default_rng(a.seed)
+    tok = rng.integers(0, cfg.get("vocab_size", 1000), (a.batch, a.seq_len + 1)).astype(np.int32)
+    if a.what == "diff":
+        rows = tools.diff_against_transformers(a.model, tok[:, :-1], "cuda" if torch.cuda.is_available() else "cpu", a.out)
+    else:
+        dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        tr = Trainer(TrainerConfig(model=cfg, batch_size=a.batch, seq_len=a.seq_len, zero_level=0), device=dev)
+        tr.import_weights(a.model)
+        fn = tools.activation_stats if a.what == "activations" else tools.gradient_stats
+        rows = fn(tr, tok[:, :-1], tok[:, 1:], a.out)
+    for r in rows[:20]:
+        print(json.dumps(r))
+    return 0

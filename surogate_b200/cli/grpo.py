@@ -1,0 +1,60 @@
+"""``surogate grpo | grpo-orch | grpo-infer config.yaml``: the three processes of asynchronous GRPO.
+
+``grpo`` is the trainer (consumes rollout batches, publishes weights), ``grpo-orch`` the orchestrator (prompts -> rollouts
+-> rewards -> batches), ``grpo-infer`` launches the rollout engine and keeps it on the newest published weights.
+``grpo --trainer-gpus 0,1`` pins the trainer's devices before CUDA is initialised (handled in cli/main.py).
+
+Parity: surogate/cli (grpo, grpo-orch, grpo-infer), surogate/grpo/{trainer,split,colocate}.py.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+
+def main(argv, command: str = "grpo") -> int:
+    p = argparse.ArgumentParser(prog=f"surogate {command}")
+    p.add_argument("config")
+    p.add_argument("--trainer-gpus", default=None)
+    p.add_argument("--max-steps", type=int, default=None, dest="max_steps")
+    a = p.parse_args(argv)
+    from ..config.loader import load_config, read_yaml
+
+    if command == "grpo":
+        from ..grpo.config import GRPOConfig
+        from ..grpo.trainer import run_grpo
+
+        r = run_grpo(load_config(GRPOConfig, a.config, max_steps=a.max_steps))
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"steps": r["steps"], "final": r["history"][-1] if r["history"] else None}))
+        return 0
+    raw = read_yaml(a.config)
+    if command == "grpo-orch":
+        from ..data.tokenizer import Tokenizer
+        from ..grpo.config import OrchestratorConfig
+        from ..grpo.orchestrator import OpenAIClient, Orchestrator
+        from ..grpo.transport import make_transport
+        from ..grpo.weight_broadcast import FilesystemBroadcast
+
+        cfg = OrchestratorConfig(**{k: v for k, v in raw.items() if k in OrchestratorConfig.__dataclass_fields__})
+        if a.max_steps:
+            cfg.max_steps = a.max_steps
+        b = FilesystemBroadcast(cfg.weight_dir)
+        orch = Orchestrator(cfg, Tokenizer.from_pretrained(cfg.model), OpenAIClient(cfg.base_url, cfg.model, cfg.request_timeout_s),
+                            make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="producer"),
+                            lambda: (b.latest() or {"version": -1})["version"])
+        orch.load_prompts()
+        hist = orch.run()
+        print(json.dumps({"steps": len(hist), "last_reward_mean": hist[-1].reward_mean if hist else None}))
+        return 0
+    from ..grpo.config import InferenceConfig
+    from ..grpo.inference import launch_server, watch_and_reload
+
+    cfg = InferenceConfig(**{k: v for k, v in raw.items() if k in InferenceConfig.__dataclass_fields__})
+    proc = launch_server(cfg)
+    try:
+        watch_and_reload(cfg, f"http://{cfg.host}:{cfg.port}/v1")
+    finally:
+        proc.terminate()
+    return 0

@@ -1,0 +1,144 @@
+"""Introspection helpers that write JSON-lines reports.
+
+* ``audit_weights``   — static comparison of a checkpoint's tensor names / shapes with what the DSL model maps.
+* ``registry_report`` — architectures, parameters, ops of the forward / backward graphs.
+* ``activation_stats`` / ``gradient_stats`` — per-tensor mean / std / abs-max / non-finite counts for one batch.
+* ``diff_against_transformers`` — layer-by-layer hidden-state comparison with the HuggingFace implementation.
+
+Parity: surogate/debug/{weights,registry,activations,gradients,diff,tensor_*}.py, cli/debug.py.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Dict, Iterable, List, Optional
+
+import numpy as np
+import torch
+
+
+def _stats(t: torch.Tensor) -> Dict[str, float]:
+    f = t.detach().float()
+    finite = torch.isfinite(f)
+    g = f[finite] if not bool(finite.all()) else f
+    return {"shape": list(t.shape), "dtype": str(t.dtype).replace("torch.", ""), "mean": float(g.mean()) if g.numel() else 0.0,
+            "std": float(g.std()) if g.numel() > 1 else 0.0, "absmax": float(g.abs().max()) if g.numel() else 0.0,
+            "nonfinite": int((~finite).sum()), "norm": float(g.norm()) if g.numel() else 0.0}
+
+
+def write_jsonl(path: Optional[str], rows: Iterable[Dict[str, Any]]) -> List[Dict[str, Any]]:
+    rows = list(rows)
+    if path:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+    return rows
+
+
+def audit_weights(model_dir: str, out: Optional[str] = None) -> Dict[str, Any]:
+    from ..dsl.compiler import compile_model, load_hf_config, model_from_hf_config
+    from ..io.hf_checkpoint import LazyCheckpoint
+
+    cfg = load_hf_config(model_dir)
+    cm = compile_model(model_from_hf_config(cfg))
+    ckpt = LazyCheckpoint(model_dir)
+    have = set(ckpt.names())
+    used, missing, rows = set(), [], []
+    for p in cm.params:
+        m = p.spec.hf
+        if m is None or p.tied_to:
+            continue
+        names = m.hf_names(p.layer)
+        absent = [n for n in names if n not in have]
+        used.update(n for n in names if n in have)
+        rows.append({"param": p.name, "hf": names, "shape": list(p.spec.shape), "status": "missing" if absent else "ok", "absent": absent})
+        if absent:
+            missing.append(p.name)
+    unused = sorted(have - used)
+    rows.append({"summary": True, "mapped": len(rows), "missing": missing, "unused_checkpoint_tensors": unused})
+    write_jsonl(out, rows)
+    return {"mapped": len(rows) - 1, "missing": missing, "unused": unused}
+
+
+def registry_report(arch_or_dir: Optional[str] = None, out: Optional[str] = None) -> List[Dict[str, Any]]:
+    from ..dsl import models  # noqa: F401
+    from ..dsl.nn import registered_architectures, registered_models
+
+    rows: List[Dict[str, Any]] = [{"architectures": registered_architectures()}]
+    if arch_or_dir:
+        from ..dsl.compiler import compile_model, load_hf_config, model_from_hf_config
+
+        if os.path.isdir(arch_or_dir):
+            cm = compile_model(model_from_hf_config(load_hf_config(arch_or_dir)))
+            rows += [{"param": p.name, "shape": list(p.spec.shape), "layer": p.layer, "group": p.group, "tied_to": p.tied_to} for p in cm.params]
+            for gname, g in [("forward", cm.fwd), ("backward", cm.bwd)] + [(f"block:{k}", v) for k, v in cm.block_fwd.items()]:
+                rows.append({"graph": gname, "ops": [op.kind for op in g.ops]})
+        else:
+            rows.append({"model_class": registered_models()[arch_or_dir].__name__})
+    return write_jsonl(out, rows)
+
+
+def activation_stats(trainer, inputs: np.ndarray, targets: np.ndarray, out: Optional[str] = None) -> List[Dict[str, Any]]:
+    rows: List[Dict[str, Any]] = []
+
+    def hook(name, layer, val):
+        if torch.is_tensor(val) and val.is_floating_point():
+            rows.append({"tensor": name, "layer": layer, **_stats(val)})
+
+    prev = trainer.executor.options.dump_tensors
+    trainer.executor.options.dump_tensors = hook
+    try:
+        trainer.validate(inputs, targets)
+    finally:
+        trainer.executor.options.dump_tensors = prev
+    return write_jsonl(out, rows)
+
+
+def gradient_stats(trainer, inputs: np.ndarray, targets: np.ndarray, out: Optional[str] = None) -> List[Dict[str, Any]]:
+    trainer.forward_backward(inputs, targets)
+    rows = []
+    for name, g in trainer.get_gradients().items():
+        if g is not None:
+            rows.append({"param": name, **_stats(g)})
+    trainer.store.release_grads()
+    rows.sort(key=lambda r: -r["absmax"])
+    return write_jsonl(out, rows)
+
+
+def diff_against_transformers(model_dir: str, tokens: np.ndarray, device: str = "cpu", out: Optional[str] = None, backend: str = "auto"):
+    """Hidden state after every block (and the logits) from both implementations on the same tokens."""
+    from transformers import AutoModelForCausalLM
+
+    from ..dsl.compiler import load_hf_config
+    from ..runtime.trainer import Trainer, TrainerConfig
+
+    hf = AutoModelForCausalLM.from_pretrained(model_dir, torch_dtype=torch.float32).to(device).eval()
+    with torch.no_grad():
+        ref = hf(torch.from_numpy(tokens.astype(np.int64)).to(device), output_hidden_states=True)
+    cfg = load_hf_config(model_dir)
+    tr = Trainer(TrainerConfig(model=cfg, batch_size=tokens.shape[0], seq_len=tokens.shape[1], zero_level=0, backend=backend, param_dtype="fp32" if device == "cpu" else "bf16"),
+                 device=torch.device(device))
+    tr.import_weights(model_dir)
+    mine: Dict[int, torch.Tensor] = {}
+
+    def hook(name, layer, val):
+        if layer is not None and name in ("x_out", "residual_out") and torch.is_tensor(val):
+            mine.setdefault(layer, {})[name] = val.detach().float()
+
+    prev = tr.executor.options.dump_tensors
+    tr.executor.options.dump_tensors = hook
+    try:
+        logits = tr.logits(tokens)
+    finally:
+        tr.executor.options.dump_tensors = prev
+    rows = []
+    for L in sorted(mine):
+        h = sum(mine[L].values())  # block output = deferred residual stream + last branch output
+        r = ref.hidden_states[L + 1].float()
+        if L == len(mine) - 1 and r.shape == h.shape and (r - h).abs().max() > 1.0:
+            continue  # transformers applies the final norm to the last hidden state
+        rows.append({"layer": L, "max_abs_diff": float((h - r).abs().max()), "rel": float((h - r).norm() / (r.norm() + 1e-12))})
+    rows.append({"logits": True, "max_abs_diff": float((logits - ref.logits.float()).abs().max()),
+                 "rel": float((logits - ref.logits.float()).norm() / (ref.logits.float().norm() + 1e-12))})
+    return write_jsonl(out, rows)

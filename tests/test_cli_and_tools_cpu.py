@@ -1,0 +1,101 @@
+"""CLI plumbing and offline tools on CPU: export -> audit -> merge -> debug stats; tokenise pipeline; every command imports."""
+import importlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+MODEL = dict(architecture="Qwen3ForCausalLM", vocab_size=600, d_model=32, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64,
+             tie_word_embeddings=False)
+LORA = dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+            rslora=False, train_router=False)
+
+
+def test_every_cli_command_module_imports():
+    from surogate_b200.cli.main import COMMAND_MAPPING, cli_main
+
+    for mod in set(COMMAND_MAPPING.values()):
+        assert hasattr(importlib.import_module(mod), "main"), mod
+    assert cli_main(["--help"]) == 0 and cli_main(["nonsense"]) == 2
+
+
+def _trained_lora(tmp_path):
+    tr = Trainer(TrainerConfig(model=MODEL, batch_size=2, seq_len=16, recipe="bf16", optimizer="adamw", learning_rate=5e-2, zero_level=0, lora=LORA),
+                 device=torch.device("cpu"))
+    tr.init_weights(seed=0)
+    rng = np.random.default_rng(0)
+    tok = rng.integers(0, 600, (2, 17)).astype(np.int32)
+    for _ in range(3):
+        tr.step(tok[:, :-1], tok[:, 1:])
+    base, adapter = os.path.join(tmp_path, "base"), os.path.join(tmp_path, "adapter")
+    tr.export_model(base, MODEL)
+    tr.export_adapter(adapter, base_model=base)
+    return tr, tok, base, adapter
+
+
+def test_merge_adapter_on_safetensors_matches_in_memory_merge(tmp_path):
+    from safetensors.torch import load_file
+
+    from surogate_b200.cli.main import cli_main
+    from surogate_b200.debug.tools import audit_weights
+
+    tr, tok, base, adapter = _trained_lora(str(tmp_path))
+    merged = os.path.join(tmp_path, "merged")
+    assert cli_main(["merge", "--base", base, "--adapter", adapter, "--output", merged]) == 0
+    tr.lora.merge_into(tr.store)
+    ref = os.path.join(tmp_path, "ref")
+    tr.export_model(ref, MODEL)
+    a, b = load_file(os.path.join(merged, "model.safetensors")), load_file(os.path.join(ref, "model.safetensors"))
+    assert a.keys() == b.keys()
+    changed = 0
+    base_t = load_file(os.path.join(base, "model.safetensors"))
+    for k in a:
+        assert torch.allclose(a[k].float(), b[k].float(), atol=2e-2, rtol=2e-2), k
+        changed += int(not torch.equal(a[k], base_t[k]))
+    assert changed >= 2 * 7  # every adapted projection of both layers moved
+    rep = audit_weights(merged)
+    assert rep["missing"] == [] and rep["unused"] == []
+
+
+def test_debug_stats_and_registry(tmp_path):
+    from surogate_b200.debug import tools
+
+    tr, tok, base, _ = _trained_lora(str(tmp_path))
+    acts = tools.activation_stats(tr, tok[:, :-1], tok[:, 1:], os.path.join(tmp_path, "acts.jsonl"))
+    assert any(r["layer"] == 1 for r in acts) and all(r["nonfinite"] == 0 for r in acts)
+    grads = tools.gradient_stats(tr, tok[:, :-1], tok[:, 1:])
+    assert grads == [] or all("param" in g for g in grads)  # base is frozen under LoRA
+    reg = tools.registry_report(base)
+    assert "Qwen3ForCausalLM" in reg[0]["architectures"] and any(r.get("graph") == "forward" for r in reg)
+
+
+def test_tokenize_pipeline_packs_and_caches(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    from test_host_runtime import QWEN_PATTERN, _train_tokenizer
+
+    from surogate_b200.config.sft_config import SFTConfig
+    from surogate_b200.data.tokfile import read_token_file
+    from surogate_b200.train.tokenize import TokenizeDatasets
+
+    _, mdir = _train_tokenizer(QWEN_PATTERN, str(tmp_path), "model")
+    with open(os.path.join(mdir, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<|im_end|>", "pad_token": "<|endoftext|>"}, f)
+    data = os.path.join(tmp_path, "chat.jsonl")
+    with open(data, "w") as f:
+        for i in range(12):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"Hello world {i}"}, {"role": "assistant", "content": "It's a test " * (1 + i % 3)}]}) + "\n")
+    cfg = SFTConfig.from_dict(dict(model=mdir, datasets=[{"path": data}], sequence_len=64, output_dir=str(tmp_path / "out"), validation_split_ratio=0.25))
+    job = TokenizeDatasets(cfg, {"vocab_size": 600}, os.path.join(tmp_path, "tok"))
+    files = job.run()
+    assert job.stats["train_documents"] == 9 and job.stats["eval_documents"] == 3
+    assert job.stats["train_rows"] < job.stats["train_documents"]  # packing put several conversations into one row
+    tok, pos, mask, h = read_token_file(files["train"][0])
+    assert h["non_overlapping"] == 1 and h["has_masks"] == 1 and len(tok) == job.stats["train_rows"] * 64
+    assert (pos[:64] == 0).sum() >= 2  # position ids restart per document
+    assert 0 < mask.sum() < len(mask)  # only assistant tokens are trained
+    again = TokenizeDatasets(cfg, {"vocab_size": 600}, os.path.join(tmp_path, "tok"))
+    assert again.run() == files and not hasattr(again, "stats")  # served from the cache
