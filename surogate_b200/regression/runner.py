@@ -1,0 +1,140 @@
+"""Run small training cases and compare them with stored baselines.
+
+A case fixes model shape, recipe, optimizer, sharding level, offload mode and seeds, trains a few steps on synthetic
+tokens and records: the loss curve, gradient norms, step-time p50 / p95, peak device memory and a summary of the
+parameter-store layout (bucket count, bytes per category).  ``compare`` checks a fresh artifact against a baseline with
+tolerances per field; the CLI entry (``python -m surogate_b200.regression.runner``) runs the matrix and writes
+``regression_baselines/<case>.json`` or reports differences.
+
+Parity: surogate/regression/baseline_runner.py, regression_baselines/.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import statistics
+import sys
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+
+
+@dataclass
+class Case:
+    name: str
+    model: Dict[str, Any]
+    recipe: str = "bf16"
+    optimizer: str = "adamw_8bit"
+    zero_level: int = 0
+    lora: Optional[Dict[str, Any]] = None
+    offload: str = "none"  # none | offload | cpu_training
+    recompute: bool = False
+    batch: int = 2
+    seq_len: int = 64
+    steps: int = 6
+    lr: float = 1e-3
+    seed: int = 0
+    needs_gpu: bool = False
+
+
+TINY = dict(architecture="Qwen3ForCausalLM", vocab_size=512, d_model=128, n_layers=2, num_query_heads=4, num_kv_heads=2, head_size=32, d_ff=256,
+            tie_word_embeddings=True)
+TINY_GPU = dict(TINY, head_size=128, d_model=512, d_ff=1024)
+TINY_MOE = dict(architecture="Qwen3MoeForCausalLM", vocab_size=512, d_model=128, n_layers=2, num_query_heads=4, num_kv_heads=2, head_size=32, moe_d_ff=64,
+                num_experts=8, num_experts_per_tok=2, aux_loss_coef=1e-2, tie_word_embeddings=False)
+LORA = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"], rslora=False,
+            train_router=False)
+
+
+def default_matrix(gpu: bool) -> List[Case]:
+    cases = [Case("dense-bf16-adamw", TINY, optimizer="adamw"), Case("dense-bf16-adamw8", TINY), Case("dense-bf16-recompute", TINY, recompute=True),
+             Case("dense-lora", TINY, lora=LORA, optimizer="adamw"), Case("dense-offload", TINY, offload="offload", optimizer="adamw"),
+             Case("dense-cpu-training", TINY, offload="cpu_training", optimizer="adamw"), Case("moe-bf16", TINY_MOE, optimizer="adamw")]
+    if gpu:
+        cases += [Case("gpu-dense-fp8", TINY_GPU, recipe="fp8_hybrid", seq_len=256, needs_gpu=True),
+                  Case("gpu-dense-nvfp4", TINY_GPU, recipe="nvfp4", seq_len=256, needs_gpu=True),
+                  Case("gpu-dense-normuon", TINY_GPU, optimizer="normuon", seq_len=256, needs_gpu=True)]
+    return cases
+
+
+def run_case(case: Case, device: Optional[str] = None) -> Dict[str, Any]:
+    import torch
+
+    from ..runtime.trainer import Trainer, TrainerConfig
+
+    dev = torch.device(device or ("cuda" if (torch.cuda.is_available() and case.needs_gpu) else "cpu"))
+    kw = {"offload": dict(offload_master=True, offload_optimizer=True), "cpu_training": dict(cpu_training=True)}.get(case.offload, {})
+    cfg = TrainerConfig(model=case.model, batch_size=case.batch, seq_len=case.seq_len, recipe=case.recipe, optimizer=case.optimizer, learning_rate=case.lr,
+                        zero_level=case.zero_level, recompute=case.recompute, lora=case.lora, seed=case.seed, **kw)
+    tr = Trainer(cfg, device=dev)
+    tr.init_weights(case.seed)
+    rng = np.random.default_rng(case.seed + 1)
+    V = case.model["vocab_size"]
+    tok = rng.integers(0, V, (case.batch, case.seq_len + 1)).astype(np.int32)
+    losses, norms, times = [], [], []
+    if dev.type == "cuda":
+        torch.cuda.reset_peak_memory_stats(dev)
+    for _ in range(case.steps):
+        t0 = time.perf_counter()
+        out = tr.step(tok[:, :-1], tok[:, 1:])
+        times.append((time.perf_counter() - t0) * 1e3)
+        losses.append(out["loss"])
+        norms.append(out["norm"])
+    mem = tr.memory_breakdown()
+    ts = sorted(times[1:] or times)
+    return {"case": dataclasses.asdict(case), "device": dev.type, "losses": losses, "norms": norms,
+            "step_ms_p50": statistics.median(ts), "step_ms_p95": ts[min(len(ts) - 1, int(0.95 * len(ts)))],
+            "peak_memory": mem.get("peak", 0), "store": {"buckets": len(tr.store.buckets), **{k: v for k, v in mem.items() if k in ("master", "work", "grad", "host_master")}},
+            "num_parameters": tr.num_parameters()}
+
+
+def compare(new: Dict[str, Any], base: Dict[str, Any], loss_rtol: float = 2e-2, time_factor: float = 1.5, mem_factor: float = 1.15) -> List[str]:
+    problems = []
+    if len(new["losses"]) != len(base["losses"]):
+        problems.append(f"step count {len(new['losses'])} != {len(base['losses'])}")
+    for i, (a, b) in enumerate(zip(new["losses"], base["losses"])):
+        if abs(a - b) > loss_rtol * max(abs(b), 1e-6):
+            problems.append(f"loss[{i}] {a:.5f} vs baseline {b:.5f}")
+            break
+    if new["device"] == base["device"] and new["step_ms_p50"] > time_factor * base["step_ms_p50"]:
+        problems.append(f"step time p50 {new['step_ms_p50']:.1f} ms > {time_factor}x baseline {base['step_ms_p50']:.1f} ms")
+    if base.get("peak_memory") and new.get("peak_memory", 0) > mem_factor * base["peak_memory"]:
+        problems.append(f"peak memory {new['peak_memory']} > {mem_factor}x baseline {base['peak_memory']}")
+    if new["store"]["buckets"] != base["store"]["buckets"] or new["num_parameters"] != base["num_parameters"]:
+        problems.append("parameter-store layout changed")
+    return problems
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="python -m surogate_b200.regression.runner")
+    p.add_argument("--baselines", default="regression_baselines")
+    p.add_argument("--update", action="store_true", help="write / overwrite baselines instead of comparing")
+    p.add_argument("--only", default=None)
+    a = p.parse_args(argv)
+    import torch
+
+    os.makedirs(a.baselines, exist_ok=True)
+    failed = 0
+    for case in default_matrix(torch.cuda.is_available()):
+        if a.only and a.only not in case.name:
+            continue
+        art = run_case(case)
+        path = os.path.join(a.baselines, case.name + ".json")
+        if a.update or not os.path.exists(path):
+            with open(path, "w") as f:
+                json.dump(art, f, indent=1)
+            print(f"[baseline] {case.name}: wrote {path}")
+            continue
+        with open(path) as f:
+            problems = compare(art, json.load(f))
+        print(f"[{'FAIL' if problems else ' ok '}] {case.name}" + ("".join("\n    " + x for x in problems)))
+        failed += bool(problems)
+    return 1 if failed else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

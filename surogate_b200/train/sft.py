@@ -77,7 +77,7 @@ class SurogateSFT:
         if cfg.distributed is not None and cfg.distributed.num_nodes > 1:
             from .distributed import run_multinode
 
-            return run_multinode(cfg, type(self))
+            return run_multinode(cfg, type(self), command="pt" if isinstance(self, SurogatePT) else "sft", config_path=getattr(cfg, "_config_path", None))
         return train_with_oom_recovery(cfg)
 
 
@@ -147,8 +147,13 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
         trainer.import_weights(model_dir)
         if trainer.lora is not None:
             trainer.lora.init_weights(cfg.train_seed)
-    if cfg.adapter_path and trainer.lora is not None:
-        trainer.lora.load_peft(cfg.adapter_path)
+    if cfg.adapter_path and trainer.lora is not None and latest is None:
+        from .adapter_init import apply_adapter_init
+
+        logger.message(f"adapter {cfg.adapter_path}: {apply_adapter_init(trainer, cfg.adapter_path, cfg.adapter_init_mode, cfg.output_dir)}")
+    from .reporter import make_reporters
+
+    reporters = make_reporters([r for r in cfg.report_to if r != "surogate"], cfg.run_name, config=json.loads(cfg.to_json())) if info.is_main else []
 
     flops = transformer_flops_per_token(
         d_model=hf_cfg.get("hidden_size", hf_cfg.get("d_model", 0)), n_layers=hf_cfg.get("num_hidden_layers", hf_cfg.get("n_layers", 0)),
@@ -196,6 +201,8 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
             tps = 1000.0 * step_tokens / ms
             sol = speed_of_light_fraction(flops, tps, dev_name, cfg.recipe, info.world) if flops["total"] else None
             logger.log_step(step + 1, max_steps, (step + 1) / steps_per_epoch, out["loss"], out["norm"], lr, step_tokens, ms, sol, phase)
+            for rep in reporters:
+                rep.log(step + 1, {"loss": out["loss"], "norm": out["norm"], "lr": lr, "tps": tps, "ms": ms})
         if trainer.last_moe_stats:
             stats = trainer.get_moe_stats()
             if (step + 1) % max(1, cfg.logging_steps) == 0:
@@ -229,6 +236,8 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
             trainer.export_model(os.path.join(cfg.output_dir, "merged"), hf_cfg)
     else:
         trainer.export_model(cfg.output_dir, hf_cfg)
+    for rep in reporters:
+        rep.finish()
     logger.close()
     return {"final": last, "losses": losses, "norms": norms, "steps": len(losses)}
 
@@ -236,11 +245,14 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
 def sft_main(config_path: str, **overrides):
     from ..config.loader import load_config
 
-    return SurogateSFT(load_config(SFTConfig, config_path, **overrides)).run()
+    cfg = load_config(SFTConfig, config_path, **overrides)
+    cfg._config_path = config_path
+    return SurogateSFT(cfg).run()
 
 
 def pt_main(config_path: str, **overrides):
     from ..config.loader import load_config
 
     cfg = load_config(PTConfig, config_path, **overrides)
+    cfg._config_path = config_path
     return SurogatePT(cfg).run()
