@@ -291,6 +291,8 @@ class ParamStore:
         b, s = self.where[name]
         if b.expert:
             return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
+        if getattr(b, "qstate", None) is not None:
+            return self._dequantized(b)[s.offset:s.offset + s.numel].reshape(s.shape)
         if not self.sharded:
             return self._master_on_device(b)[s.offset:s.offset + s.numel].reshape(s.shape)
         full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
@@ -313,7 +315,9 @@ class ParamStore:
                 for s in b.slots:
                     yield s.name, self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
                 continue
-            if self.sharded:
+            if getattr(b, "qstate", None) is not None:
+                full = self._dequantized(b)
+            elif self.sharded:
                 full = torch.empty(b.numel, dtype=self.master_dtype, device=self.device)
                 self.comm.all_gather(self._master_on_device(b), full)
             else:
@@ -333,6 +337,9 @@ class ParamStore:
                 if b.work is not b.master:
                     b.work.copy_(b.master)
                 continue
+            if getattr(b, "qstate", None) is not None:
+                b.work = None
+                continue
             if getattr(b, "work_host", None) is not None and not getattr(b, "work_host_fresh", False):
                 b.work_host.copy_(b.master)  # host-side conversion (init / load); the CPU optimizer writes it itself afterwards
             b.work_host_fresh = False
@@ -346,6 +353,29 @@ class ParamStore:
             self._gather_into(b, b.work)
             if self.post_gather is not None:
                 self.post_gather(b)
+
+    # ------------------------------------------------------------------ QLoRA: frozen buckets stored block-quantised
+    def quantize_frozen(self, codec) -> int:
+        """Replace the master copy of every frozen, non-expert layer bucket by its block-quantised form.  The bf16 work
+        weights are then rebuilt per layer when the executor reaches it and dropped afterwards, so at any time only one or
+        two layers exist in bf16.  Returns the number of bytes saved."""
+        assert self.zero_level == 0 or self.world == 1, "quantised base weights are replicated: use zero_level 0/1 with QLoRA"
+        self.codec = codec
+        saved = 0
+        for b in self.buckets.values():
+            if b.trainable or b.expert or b.layer is None or getattr(b, "qstate", None) is not None:
+                continue
+            src = b.master if b.master.device == self.device else b.master.to(self.device)
+            b.qstate = codec.quantize(src)
+            before = b.master.numel() * b.master.element_size()
+            after = sum(t.numel() * t.element_size() for t in b.qstate.values())
+            saved += before - after
+            b.master = torch.empty(0, dtype=self.master_dtype, device=self.device)
+            b.work = None
+        return saved
+
+    def _dequantized(self, b: Bucket) -> torch.Tensor:
+        return self.codec.dequantize(b.qstate, self.param_dtype)
 
     # ------------------------------------------------------------------ FP8 quantise-on-gather
     FP8_SLOT_ROLES = {"qkv_weight": "qkv", "out_weight": "out", "mlp_up_weight": "mlp_up", "mlp_down_weight": "mlp_down"}
@@ -466,6 +496,9 @@ class ParamStore:
 
     # ------------------------------------------------------------------ executor hooks
     def _ensure_gathered(self, b: Bucket, prefetch_only: bool = False) -> None:
+        if b.work is None and getattr(b, "qstate", None) is not None:
+            b.work = self._dequantized(b)
+            b._needs_post = True
         if b.work is None:
             if self.fp8_gather and b.layer is not None and not b.expert:
                 b.gather_work = self._gather_fp8(b)
@@ -483,6 +516,9 @@ class ParamStore:
                     self.post_gather(b)
 
     def _release(self, b: Bucket) -> None:
+        if getattr(b, "qstate", None) is not None:
+            b.work = None
+            return
         if self.zero_level >= 3 and not b.expert:
             b.work = None
             b.work_fp8 = None
@@ -492,6 +528,9 @@ class ParamStore:
 
     def layer_start(self, L: int, phase: str) -> None:
         if self.zero_level < 3:
+            b = self._layer_bucket(L)
+            if b is not None and getattr(b, "qstate", None) is not None:
+                self._ensure_gathered(b)
             return
         b = self._layer_bucket(L)
         self._ensure_gathered(b)
@@ -510,7 +549,7 @@ class ParamStore:
             eb = self.buckets.get(f"layer{L}.experts")
             if eb is not None:
                 self._reduce_bucket(eb)
-        elif not self.keep_gathered:
+        elif not self.keep_gathered or getattr(b, "qstate", None) is not None:
             self._release(b)
 
     def group_start(self, group: str, phase: str) -> None:

@@ -62,6 +62,10 @@ class TrainerConfig:
     skip_quant_last_layers: int = 0
     offload_optimizer: bool = False
     offload_master: bool = False
+    qlora: Optional[str] = None  # bnb_nf4 | fp8_block | nvfp4: frozen base weights stored block-quantised, rebuilt per layer
+    qlora_block_size: int = 64
+    qlora_double_quant: bool = True
+    qlora_four_over_six: bool = True
     cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
@@ -161,8 +165,21 @@ class Trainer:
         return {}
 
     # ------------------------------------------------------------------ weights
+    def _apply_qlora(self) -> None:
+        c = self.cfg
+        if not c.qlora:
+            return
+        if self.lora is None:
+            raise ValueError("qlora needs LoRA adapters (the quantised base is frozen)")
+        from ..quant import make_codec
+
+        kw = {"bnb_nf4": dict(block=c.qlora_block_size, double_quant=c.qlora_double_quant), "fp8_block": dict(block=max(64, c.qlora_block_size)),
+              "nvfp4": dict(four_over_six=c.qlora_four_over_six)}[c.qlora]
+        self.qlora_bytes_saved = self.store.quantize_frozen(make_codec(c.qlora, **kw))
+
     def init_weights(self, seed: Optional[int] = None) -> None:
         self.store.init_weights(seed if seed is not None else self.cfg.seed, zero_projections=self.cfg.init_projections_to_zero)
+        self._apply_qlora()
         self.recipe.on_weights_updated(self.store)
         if self.lora is not None:
             self.lora.init_weights(seed if seed is not None else self.cfg.seed)
@@ -172,6 +189,7 @@ class Trainer:
 
         import_hf_weights(self.cm, self.store, path)
         self.store.sync_work_from_master()
+        self._apply_qlora()
         self.recipe.on_weights_updated(self.store)
 
     def export_model(self, out_dir: str, hf_config: Optional[Dict[str, Any]] = None) -> None:
