@@ -220,7 +220,7 @@ void ep_plan(const std::vector<int64_t>& ctrl, int64_t ctrl_byte_offset, const s
              Tensor& dst_base, Tensor& cursors, int64_t rank, int64_t epoch, int64_t slot_base, int64_t capacity_rows, Tensor& error_flag,
              double budget_s) {
     const int E = static_cast<int>(counts.numel()), world = static_cast<int>(ctrl.size());
-    TORCH_CHECK(E <= 256 && E % world == 0 && offsets.numel() == E / world + 1 && dst_base.numel() == E && cursors.numel() == E, "ep_plan shapes");
+    TORCH_CHECK(E <= 256 && E % world == 0 && offsets.numel() == E / world + 2 && dst_base.numel() == E && cursors.numel() == E, "ep_plan shapes");
     sg_count_launch(1);
     sg::ep_plan(to_peers(ctrl, ctrl_byte_offset), to_peers(pads), counts.data_ptr<int>(), offsets.data_ptr<int>(), dst_base.data_ptr<int>(),
                 cursors.data_ptr<int>(), E, static_cast<int>(rank), world, static_cast<uint32_t>(epoch), static_cast<int>(slot_base),

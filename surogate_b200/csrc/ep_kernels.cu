@@ -34,7 +34,7 @@ __device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
 }
 
 // ctrl layout per rank (ints): [0, W*E) all_counts[src][expert] ; pads (uint32) live in the communicator's signal pad.
-// Outputs (local, ints): offsets[El+1] (padded rows of my experts), dst_base[E] (first row I may write per global expert),
+// Outputs (local, ints): offsets[El+2] (padded rows of my experts, clamped to the buffer; last entry = overflow rows), dst_base[E] (first row I may write per global expert),
 // cursors[E] = 0.
 __global__ void __launch_bounds__(256) ep_plan_kernel(PeerPtrs ctrl, PeerPtrs pads, const int* __restrict__ counts, int* __restrict__ offsets,
                                                       int* __restrict__ dst_base, int* __restrict__ cursors, int E, int rank, int world,
@@ -78,12 +78,13 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(PeerPtrs ctrl, PeerPtrs pa
         for (int j = 0; j < el; ++j) off += (tot[owner * El + j] + 127) / 128 * 128;   // padded start of this expert on its owner
         int before = 0;
         for (int r = 0; r < rank; ++r) before += all[r * E + e];                       // rows of lower-ranked sources come first
-        dst_base[e] = off + before;
-        if (owner == rank) offsets[el] = off;
+        dst_base[e] = off + before;   // rows at or beyond capacity_rows are dropped by the dispatch kernel (token dropping)
+        // The grouped GEMMs walk offsets[]: clamp them so that nothing beyond the receive buffer is ever touched.
+        if (owner == rank) offsets[el] = off < capacity_rows ? off : capacity_rows;
         if (owner == rank && el == El - 1) {
             const int end = off + (tot[e] + 127) / 128 * 128;
-            offsets[El] = end;
-            if (end > capacity_rows) atomicExch(error_flag, 3);
+            offsets[El] = end < capacity_rows ? end : capacity_rows;
+            offsets[El + 1] = end > capacity_rows ? end - capacity_rows : 0;           // rows that did not fit (statistics)
         }
     }
 }

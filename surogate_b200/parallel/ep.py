@@ -13,7 +13,7 @@ Backward runs the mirror image (push ``w * dy`` to the owners, grouped dgrad/wgr
 symmetric buffers (receive / output for activations and for gradients) are allocated once and reused by every layer;
 the in-kernel barrier of step 1 (and an explicit one in backward) also guarantees that every rank is done with the
 previous layer's buffers before they are overwritten.  The receive capacity is ``capacity_factor x tokens x K`` rows
-(+ padding); exceeding it raises the device error word instead of writing out of bounds.
+(+ padding); token copies beyond it are dropped (they contribute zero to the combine) and counted per layer.
 
 Least-loaded balancing: per-expert global token counts of every layer are kept from the last step
 (``last_global_counts``) and summarised by ``imbalance()``; the LPT planner in :mod:`surogate_b200.parallel.lpt`
@@ -62,6 +62,7 @@ class ExpertParallel:
         self.bufs: Optional[Dict[str, Any]] = None
         self.epoch = 0
         self.last_global_counts: Dict[int, torch.Tensor] = {}
+        self.last_overflow: Dict[int, torch.Tensor] = {}  # rows per layer that exceeded this rank's receive capacity (dropped)
 
     # ------------------------------------------------------------------ buffers
     def _ensure(self, tokens: int, K: int, C: int, E: int):
@@ -95,7 +96,7 @@ class ExpertParallel:
         b = self._ensure(N, K, C, E)
         cap, El = b["cap"], b["El"]
         dev = x2.device
-        offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+        offsets = torch.zeros(El + 2, dtype=torch.int32, device=dev)  # [El+1] padded row ranges + overflow count
         dst_base = torch.empty(E, dtype=torch.int32, device=dev)
         cursors = torch.empty(E, dtype=torch.int32, device=dev)
         row_map = torch.empty(N * K, dtype=torch.int32, device=dev)
@@ -109,7 +110,8 @@ class ExpertParallel:
         xp = b["recv_x"].clone()
         if ctx.layer is not None and ctx.phase == "fwd":
             self.last_global_counts[ctx.layer] = b["counts"].view(self.ep, E).sum(0)
-        plan = EpPlan(offsets, row_map, cap, N, K, pre.x_shape, pre.topk_idx)
+            self.last_overflow[ctx.layer] = offsets[El + 1:El + 2]
+        plan = EpPlan(offsets[:El + 1], row_map, cap, N, K, pre.x_shape, pre.topk_idx)
         pre.ep_plan = plan
         return xp, plan
 
@@ -146,6 +148,10 @@ class ExpertParallel:
         return b["recv_dy"].clone(), d_w.reshape(weights.shape)
 
     # ------------------------------------------------------------------ balancing
+    def dropped_rows(self) -> int:
+        """Token copies dropped on this rank in the last step because an expert group overflowed the receive buffer."""
+        return int(sum(int(v.item()) for v in self.last_overflow.values()))
+
     def imbalance(self) -> float:
         """max over layers of (busiest rank's tokens / mean rank tokens) in the last step."""
         worst = 1.0

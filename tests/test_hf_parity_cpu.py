@@ -1,0 +1,61 @@
+"""Checkpoint compatibility with HuggingFace transformers: a randomly initialised HF model is saved, imported through the
+DSL's weight mappings and must produce the same logits; exporting back must reproduce the HF tensors."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from surogate_b200.dsl.compiler import load_hf_config  # noqa: E402
+from surogate_b200.runtime.trainer import Trainer, TrainerConfig  # noqa: E402
+
+COMMON = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=96,
+              max_position_embeddings=128, rms_norm_eps=1e-6)
+
+
+def _cases():
+    from transformers import LlamaConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
+
+    yield "qwen3", Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=True)
+    yield "qwen3-untied", Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=False)
+    yield "qwen2", Qwen2Config(**COMMON, rope_theta=1e6, tie_word_embeddings=False)
+    yield "llama", LlamaConfig(**COMMON, rope_theta=10000.0, tie_word_embeddings=False)
+    yield "mistral", MistralConfig(**COMMON, head_dim=16, rope_theta=10000.0, sliding_window=None, tie_word_embeddings=False)
+    yield "qwen3-moe", Qwen3MoeConfig(**COMMON, head_dim=16, rope_theta=1e6, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                                      norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False)
+
+
+@pytest.mark.parametrize("name,config", list(_cases()), ids=[n for n, _ in _cases()])
+def test_logits_match_transformers_and_export_round_trips(tmp_path, name, config):
+    from transformers import AutoModelForCausalLM
+
+    torch.manual_seed(0)
+    hf = AutoModelForCausalLM.from_config(config).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():  # make norms / biases non-trivial
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    src = os.path.join(tmp_path, "hf")
+    hf.save_pretrained(src, safe_serialization=True)
+    tok = np.random.default_rng(0).integers(0, 320, (2, 24)).astype(np.int32)
+    with torch.no_grad():
+        want = hf(torch.from_numpy(tok).long()).logits
+    cfg = load_hf_config(src)
+    tr = Trainer(TrainerConfig(model=cfg, batch_size=2, seq_len=24, zero_level=0), device=torch.device("cpu"))
+    tr.import_weights(src)
+    got = tr.logits(tok)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (name, float((got - want).abs().max()))
+    out = os.path.join(tmp_path, "export")
+    tr.export_model(out, cfg)
+    from safetensors.torch import load_file
+
+    a, b = load_file(os.path.join(src, "model.safetensors")), load_file(os.path.join(out, "model.safetensors"))
+    for k, v in a.items():
+        assert k in b, k
+        assert torch.allclose(b[k].float(), v.float(), atol=1e-2), k  # export writes bf16
+    back = AutoModelForCausalLM.from_pretrained(out, torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        again = back(torch.from_numpy(tok).long()).logits
+    assert (again - want).abs().max() < 0.05 * want.abs().max()

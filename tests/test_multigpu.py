@@ -75,3 +75,11 @@ def test_two_gpus_full_finetune_offloaded_state():
                      port=29754)
     for a, b in zip(off["losses"], ref["losses"]):
         assert abs(a - b) < 5e-3 * abs(b), (off["losses"], ref["losses"])
+
+
+def test_expert_parallel_overflow_drops_tokens_instead_of_overrunning():
+    """A receive buffer far too small for the routed rows: the overflow is dropped and counted, nothing is written or read
+    outside the buffer, and training continues with finite numbers."""
+    r = run_worker(2, dict(ARGS, model=MOE, ep=2, zero=1, collectives="symm", ep_capacity_factor=0.05), port=29761)
+    assert r["ep_dropped"] > 0
+    assert all(l == l and abs(l) < 50 for l in r["losses"]), r["losses"]
