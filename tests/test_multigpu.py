@@ -80,6 +80,6 @@ def test_two_gpus_full_finetune_offloaded_state():
 def test_expert_parallel_overflow_drops_tokens_instead_of_overrunning():
     """A receive buffer far too small for the routed rows: the overflow is dropped and counted, nothing is written or read
     outside the buffer, and training continues with finite numbers."""
-    r = run_worker(2, dict(ARGS, model=MOE, ep=2, zero=1, collectives="symm", ep_capacity_factor=0.05), port=29761)
+    r = run_worker(2, dict(ARGS, global_batch=8, seq_len=256, model=MOE, ep=2, zero=1, collectives="symm", ep_capacity_factor=0.05), port=29761)
     assert r["ep_dropped"] > 0
     assert all(l == l and abs(l) < 50 for l in r["losses"]), r["losses"]
