@@ -251,13 +251,27 @@ class Model(Module):
     @classmethod
     def from_hf_config(cls, cfg: Dict[str, Any], **overrides) -> "Model":
         kw = {}
+        aliases = {"num_experts": ("num_local_experts", "n_routed_experts"), "head_dim": ("head_size",)}  # spellings used by other writers of config.json
         for mine, theirs in cls.hf_config_map.items():
-            if theirs in cfg and cfg[theirs] is not None:
-                kw[mine] = cfg[theirs]
+            for key in (theirs,) + aliases.get(theirs, ()):
+                if key in cfg and cfg[key] is not None:
+                    kw[mine] = cfg[key]
+                    break
+        rp = cfg.get("rope_parameters") or cfg.get("rope_scaling")
+        if "rope_theta" not in kw and isinstance(rp, dict) and rp.get("rope_theta") is not None:
+            kw["rope_theta"] = rp["rope_theta"]  # newer config.json files keep the RoPE base inside rope_parameters
         kw.update(overrides)
         import inspect
 
-        accepted = set(inspect.signature(cls.__init__).parameters)
+        accepted = set()
+        for klass in cls.__mro__:  # a subclass may forward **kwargs to its parent: collect the names along the chain
+            init = klass.__dict__.get("__init__")
+            if init is None:
+                continue
+            params = inspect.signature(init).parameters
+            accepted |= {n for n, p in params.items() if p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)}
+            if not any(p.kind == p.VAR_KEYWORD for p in params.values()):
+                break
         return cls(**{k: v for k, v in kw.items() if k in accepted})
 
 
