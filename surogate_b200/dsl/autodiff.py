@@ -250,6 +250,31 @@ def _block_stack(b, op, dy):
     return {x: gx, res: gr}
 
 
+@register_autodiff("torch_fn")
+def _torch_fn(b, op, dy):
+    """Backward = replay under autograd: inputs are re-read (saved tensors / parameters), gradients flow to every floating
+    input; parameter gradients go to ``grad::<param>``."""
+    ins = list(op.inputs)
+    grads, outs, contrib = [], [], {}
+    for n in ins:
+        if n is None:
+            grads.append(None)
+            continue
+        if b.is_param(n):
+            grads.append(b.param_grad(n))
+        else:
+            spec = b.fwd.tensors.get(n)
+            if spec is not None and spec.dtype in ("int32", "opaque"):
+                grads.append(None)
+            else:
+                g = b.new_grad(n)
+                grads.append(g)
+                contrib[n] = g
+    b.emit("torch_fn_backward", list(dy) + [b.fwd_tensor(n) if (n is not None and not b.is_param(n)) else n for n in ins], grads,
+           **{**op.attrs, "n_in": len(ins)})
+    return contrib
+
+
 # ---- MoE
 
 @register_autodiff("moe_router")

@@ -66,7 +66,8 @@ def matmul(x: Proxy, w: Proxy, bias: Optional[Proxy] = None, name: str = "mm", r
 
 def qkv_qk_norm_rope(qkv: Proxy, q_norm_w: Optional[Proxy], k_norm_w: Optional[Proxy], position_ids: Proxy, *,
                      num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, rope_theta: float,
-                     rotary_dim: Optional[int] = None, name: str = "qkv_rope") -> Tuple[Proxy, Optional[Proxy], Optional[Proxy]]:
+                     rotary_dim: Optional[int] = None, rope_scaling=None, max_pos: Optional[int] = None,
+                     name: str = "qkv_rope") -> Tuple[Proxy, Optional[Proxy], Optional[Proxy]]:
     """Per-head RMSNorm on Q and K (optional) followed by rotary embedding on the packed [.., (Hq+2Hkv)*D] tensor."""
     use_norm = q_norm_w is not None
     lead = qkv.shape[:-1]
@@ -76,7 +77,7 @@ def qkv_qk_norm_rope(qkv: Proxy, q_norm_w: Optional[Proxy], k_norm_w: Optional[P
          ("q_rstd", lead + (num_q_heads,), "fp32") if use_norm else None,
          ("k_rstd", lead + (num_kv_heads,), "fp32") if use_norm else None],
         num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, eps=eps, rope_theta=rope_theta,
-        rotary_dim=rotary_dim or head_dim)
+        rotary_dim=rotary_dim or head_dim, **({"rope_scaling": dict(rope_scaling), "max_pos": max_pos} if rope_scaling else {}))
     return outs[0], outs[1], outs[2]
 
 
@@ -156,3 +157,13 @@ def moe_grouped_gemm(x: Proxy, w: Proxy, plan: Proxy, name: str, role: str) -> P
 def moe_unpermute(y: Proxy, topk_weights: Proxy, plan: Proxy, out_shape: Shape, name: str = "moe_out") -> Proxy:
     """Weighted sum of each token's K expert outputs, back in token order."""
     return _t().emit("moe_unpermute", [y, topk_weights, plan], [(name, tuple(out_shape), "act")])[0]
+
+
+# ---------------------------------------------------------------------------- generic torch-function op
+
+def torch_fn(fn: str, inputs: Sequence[Optional[Proxy]], out_specs: Sequence[Tuple[str, Shape, str]], **attrs):
+    """An op implemented by a registered PyTorch function (``runtime/torch_fns.py``); its backward is obtained by replaying the
+    function under autograd.  This is how architectures outside the tuned kernel set (sliding-window / sink attention,
+    state-space mixers, short convolutions, biased MoE ...) run through the same graph machinery."""
+    outs = _t().emit("torch_fn", list(inputs), list(out_specs), fn=fn, n_out=len(out_specs), **attrs)
+    return outs[0] if len(outs) == 1 else tuple(outs)

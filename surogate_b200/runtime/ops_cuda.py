@@ -147,7 +147,7 @@ class CudaOps(RefOps):
     # ------------------------------------------------------------------ qk-norm + rope
     def qkv_qk_norm_rope(self, ctx, op, qkv, qw, kw, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16:
+        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling"):
             return super().qkv_qk_norm_rope(ctx, op, qkv, qw, kw, pos)
         out, q_rstd, k_rstd = self.ext.qk_norm_rope_fwd(qkv, qw, kw, pos.contiguous(), a["num_q_heads"], a["num_kv_heads"], 128, a["eps"],
                                                         a["rope_theta"])
@@ -155,7 +155,7 @@ class CudaOps(RefOps):
 
     def qkv_qk_norm_rope_backward(self, ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16:
+        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling"):
             return super().qkv_qk_norm_rope_backward(ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos)
         dx, dqw, dkw = self.ext.qk_norm_rope_bwd(dy.contiguous(), qkv, qw, kw, q_rstd, k_rstd, pos.contiguous(), a["num_q_heads"],
                                                  a["num_kv_heads"], 128, a["eps"], a["rope_theta"])

@@ -49,11 +49,45 @@ class RefOps:
     def compute_dtype(self, t: torch.Tensor):
         return torch.float32 if t.dtype in (torch.bfloat16, torch.float16) else t.dtype
 
-    def rope_cos_sin(self, position_ids: torch.Tensor, rotary_dim: int, theta: float):
-        half = rotary_dim // 2
-        inv = theta ** (-torch.arange(0, half, device=position_ids.device, dtype=torch.float32) * 2.0 / rotary_dim)
+    def rope_cos_sin(self, position_ids: torch.Tensor, rotary_dim: int, theta: float, scaling=None, max_pos=None):
+        from ..config.rope import rope_inv_freq
+
+        inv, att = rope_inv_freq(rotary_dim, theta, scaling, max_pos, device=position_ids.device)
         ang = position_ids.to(torch.float32).unsqueeze(-1) * inv  # [B,T,half]
-        return ang.cos(), ang.sin()
+        return ang.cos() * att, ang.sin() * att
+
+    # ------------------------------------------------------------------ generic torch-function op
+    @staticmethod
+    def _fn_kwargs(op):
+        return {k: v for k, v in op.attrs.items() if k not in ("fn", "n_out", "n_in")}
+
+    def torch_fn(self, ctx, op, *ins):
+        from .torch_fns import TORCH_FNS
+
+        with torch.no_grad():
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op))
+        return out if isinstance(out, tuple) else (out,)
+
+    def torch_fn_backward(self, ctx, op, *args):
+        from .torch_fns import TORCH_FNS
+
+        n_out = op.attrs["n_out"]
+        d_outs, ins = args[:n_out], list(args[n_out:])
+        req = []
+        for i, t in enumerate(ins):
+            if torch.is_tensor(t) and t.is_floating_point():
+                ins[i] = t.detach().requires_grad_(True)
+                req.append(i)
+        with torch.enable_grad():
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op))
+            outs = out if isinstance(out, tuple) else (out,)
+            pairs = [(o, d) for o, d in zip(outs, d_outs) if d is not None and torch.is_tensor(o) and o.requires_grad]
+            gs = torch.autograd.grad([o for o, _ in pairs], [ins[i] for i in req],
+                                     [d.to(o.dtype) if torch.is_tensor(d) else torch.full_like(o, float(d)) for o, d in pairs], allow_unused=True)
+        res = [None] * len(ins)
+        for i, g in zip(req, gs):
+            res[i] = g
+        return tuple(res)
 
     # ------------------------------------------------------------------ simple ops
     def zeros(self, ctx, op):
@@ -187,7 +221,7 @@ class RefOps:
             k_rstd = torch.rsqrt(k.pow(2).mean(-1) + a["eps"])
             q = q * q_rstd.unsqueeze(-1) * qw.float()
             k = k * k_rstd.unsqueeze(-1) * kw.float()
-        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"])
+        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"))
         q, k = self._rope(q, cos, sin, R, False), self._rope(k, cos, sin, R, False)
         out = torch.cat([q, k, v], dim=-2).reshape(qkv.shape).to(qkv.dtype)
         return out, q_rstd, k_rstd
@@ -208,7 +242,7 @@ class RefOps:
         lead = qkv.shape[:-1]
         g = dy.float().reshape(*lead, Hq + 2 * Hkv, D)
         x = qkv.float().reshape(*lead, Hq + 2 * Hkv, D)
-        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"])
+        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"))
         gq, gk, gv = g[..., :Hq, :], g[..., Hq:Hq + Hkv, :], g[..., Hq + Hkv:, :]
         gq, gk = self._rope(gq, cos, sin, R, True), self._rope(gk, cos, sin, R, True)
         dqw = dkw = None

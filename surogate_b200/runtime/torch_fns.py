@@ -1,0 +1,222 @@
+"""PyTorch implementations behind the generic ``torch_fn`` op.
+
+Architectures outside the hand-tuned set (sliding-window and sink attention, GeGLU / ReLU^2 MLPs, LayerNorm, biased
+clamp-SwiGLU experts, short convolutions, state-space and delta-rule mixers) are expressed with these functions; the
+executor calls them in forward and replays them under autograd for backward.  Each function takes tensors first and
+plain-Python keyword attributes after, and returns a tensor or a tuple of tensors.
+
+Parity: csrc/src/runtime/ops/ (gelu_glu, relu2, layernorm, gpt_oss_moe_act, moe_expert_bias_add, mamba_*,
+chunk_gated_delta_rule), csrc/src/runtime/attention/attention_custom.cu (sliding window / sinks).
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+TORCH_FNS: Dict[str, Callable] = {}
+
+
+def register(name: str):
+    def deco(fn):
+        TORCH_FNS[name] = fn
+        return fn
+
+    return deco
+
+
+# ---------------------------------------------------------------------------------------------- element-wise / norms
+@register("geglu")
+def geglu(x, *, approximate: str = "tanh", gate_first: bool = False):
+    """x = [up | gate] (or [gate | up]); y = gelu(gate) * up."""
+    a, b = x.chunk(2, dim=-1)
+    up, gate = (b, a) if gate_first else (a, b)
+    return F.gelu(gate.float(), approximate=approximate).to(x.dtype) * up
+
+
+@register("relu2")
+def relu2(x):
+    return F.relu(x).square()
+
+
+@register("layernorm")
+def layernorm(x, w, b, *, eps: float = 1e-5):
+    return F.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float() if b is not None else None, eps).to(x.dtype)
+
+
+@register("rmsnorm_offset")
+def rmsnorm_offset(x, w, *, eps: float = 1e-6, offset: float = 1.0):
+    """Gemma-style RMSNorm: y = x / rms(x) * (offset + w), computed in fp32."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (offset + w.float())).to(x.dtype)
+
+
+@register("scale_by")
+def scale_by(x, s):
+    return x * s.to(x.dtype)
+
+
+@register("softcap")
+def softcap(x, *, cap: float):
+    return torch.tanh(x.float() / cap).mul(cap).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- attention
+@register("attention_general")
+def attention_general(qkv, sinks=None, *, num_q_heads: int, num_kv_heads: int, head_dim: int, window: int = 0, softmax_scale: Optional[float] = None,
+                      softcap: float = 0.0, causal: bool = True, v_head_dim: Optional[int] = None):
+    """Grouped-query attention on packed [B, T, (Hq + 2 Hkv) D] with optional sliding window, logit soft-capping and learned
+    per-head sink logits (a virtual key that only absorbs probability mass)."""
+    B, T = qkv.shape[:2]
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    x = qkv.reshape(B, T, Hq + 2 * Hkv, D)
+    q, k, v = x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
+    G = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    s = qf @ kf.transpose(-1, -2) * (softmax_scale or 1.0 / math.sqrt(D))
+    if softcap:
+        s = torch.tanh(s / softcap) * softcap
+    i = torch.arange(T, device=qkv.device)
+    ok = torch.ones(T, T, dtype=torch.bool, device=qkv.device)
+    if causal:
+        ok &= i[:, None] >= i[None, :]
+    if window:
+        ok &= (i[:, None] - i[None, :]) < window
+    s = s.masked_fill(~ok, float("-inf"))
+    if sinks is not None:
+        sk = sinks.float().reshape(1, Hq, 1, 1).expand(B, Hq, T, 1)
+        p = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :-1]
+    else:
+        p = torch.softmax(s, dim=-1)
+    o = p @ vf
+    return o.permute(0, 2, 1, 3).reshape(B, T, Hq * D).to(qkv.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- GPT-OSS style MoE
+@register("moe_biased_clamp_swiglu")
+def moe_biased_clamp_swiglu(x, router_w, router_b, gate_up, gate_up_b, down, down_b, *, top_k: int, alpha: float = 1.702, limit: float = 7.0):
+    """Router = linear(+bias) -> top-k -> softmax over the k selected logits.  Experts: interleaved (gate, up) columns with
+    biases, gate clamped above and up clamped on both sides at ``limit``, y = (up + 1) * gate * sigmoid(alpha * gate), then the
+    biased down projection.  gate_up [E, C, 2M], down [E, M, C] (input-major, as stored in the checkpoint)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    logits = F.linear(x2.float(), router_w.float(), router_b.float())
+    top_v, top_i = torch.topk(logits, top_k, dim=-1)
+    w = torch.softmax(top_v, dim=-1)
+    out = torch.zeros_like(x2, dtype=torch.float32)
+    E = router_w.shape[0]
+    for e in range(E):
+        tok, slot = torch.where(top_i == e)
+        if tok.numel() == 0:
+            continue
+        h = x2[tok].float() @ gate_up[e].float() + gate_up_b[e].float()
+        gate, up = h[..., ::2].clamp(max=limit), h[..., 1::2].clamp(min=-limit, max=limit)
+        act = (up + 1) * gate * torch.sigmoid(gate * alpha)
+        y = act @ down[e].float() + down_b[e].float()
+        out.index_add_(0, tok, y * w[tok, slot, None])
+    return out.reshape(shape).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- short convolution (LFM2)
+@register("short_conv")
+def short_conv(x, in_w, conv_w, out_w, in_b=None, conv_b=None, out_b=None, *, kernel: int = 3):
+    """Gated depth-wise causal convolution: (B, C, x') = in_proj(x) split in three; y = out_proj(C * conv1d(B * x'))."""
+    Bx, T, D = x.shape
+    bcx = F.linear(x, in_w, in_b).transpose(1, 2)  # [B, 3D, T]
+    b, c, xx = bcx.chunk(3, dim=1)
+    u = b * xx
+    conv = F.conv1d(F.pad(u, (kernel - 1, 0)), conv_w.reshape(D, 1, kernel).to(u.dtype), conv_b, groups=D)
+    return F.linear((c * conv).transpose(1, 2).contiguous(), out_w, out_b)
+
+
+# ---------------------------------------------------------------------------------------------- Mamba-2 mixer (Nemotron-H)
+def _segsum(x):
+    T = x.shape[-1]
+    x = x[..., None].expand(*x.shape, T)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool, device=x.device), diagonal=-1)
+    x = x.masked_fill(~mask, 0)
+    seg = torch.cumsum(x, dim=-2)
+    mask2 = torch.tril(torch.ones(T, T, dtype=torch.bool, device=x.device), diagonal=0)
+    return seg.masked_fill(~mask2, float("-inf"))
+
+
+def ssd_scan(xh, dt, A, Bm, Cm, D, *, chunk: int):
+    """Structured state-space duality scan.  xh [B,T,H,P], dt [B,T,H] (after softplus), A [H] (negative), Bm/Cm [B,T,G,N], D [H]."""
+    Bsz, T, H, P = xh.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    pad = (-T) % chunk
+    if pad:
+        xh, dt, Bm, Cm = (torch.cat([t, t.new_zeros(t.shape[0], pad, *t.shape[2:])], 1) for t in (xh, dt, Bm, Cm))
+    Tp = T + pad
+    rep = H // G
+    Bh, Ch = Bm.repeat_interleave(rep, dim=2), Cm.repeat_interleave(rep, dim=2)
+    xd = xh * dt[..., None]
+    a = A[None, None, :] * dt  # [B,T,H]
+    nc = Tp // chunk
+    r = lambda t: t.reshape(Bsz, nc, chunk, *t.shape[2:])  # noqa: E731
+    xd, a, Bh, Ch = r(xd), r(a), r(Bh), r(Ch)
+    a = a.permute(0, 3, 1, 2)  # [B,H,c,l]
+    a_cum = torch.cumsum(a, dim=-1)
+    L = torch.exp(_segsum(a))
+    y_diag = torch.einsum("bclhn,bcshn,bhcls,bcshp->bclhp", Ch, Bh, L, xd)
+    decay_states = torch.exp(a_cum[..., -1:] - a_cum)
+    states = torch.einsum("bclhn,bhcl,bclhp->bchpn", Bh, decay_states, xd)
+    init = states.new_zeros(Bsz, 1, H, P, N)
+    states = torch.cat([init, states], dim=1)
+    decay_chunk = torch.exp(_segsum(F.pad(a_cum[..., -1], (1, 0))))
+    new_states = torch.einsum("bhzc,bchpn->bzhpn", decay_chunk, states)
+    states = new_states[:, :-1]
+    y_off = torch.einsum("bclhn,bchpn,bhcl->bclhp", Ch, states, torch.exp(a_cum))
+    y = (y_diag + y_off).reshape(Bsz, Tp, H, P)[:, :T]
+    return y + xh[:, :T] * D[None, None, :, None]
+
+
+@register("mamba2_mixer")
+def mamba2_mixer(x, in_w, conv_w, conv_b, dt_bias, A_log, D, norm_w, out_w, *, num_heads: int, head_dim: int, n_groups: int, state_size: int,
+                 conv_kernel: int = 4, chunk: int = 64, eps: float = 1e-5, in_b=None, out_b=None):
+    """Mamba-2 block: in_proj -> (gate z, conv input [x, B, C], dt) -> causal depth-wise conv + SiLU -> SSD scan -> gated grouped
+    RMSNorm -> out_proj."""
+    Bsz, T, _ = x.shape
+    H, P, G, N = num_heads, head_dim, n_groups, state_size
+    inner = H * P
+    proj = F.linear(x, in_w, in_b).float()
+    z, xBC, dt = torch.split(proj, [inner, inner + 2 * G * N, H], dim=-1)
+    xBC = F.conv1d(F.pad(xBC.transpose(1, 2), (conv_kernel - 1, 0)), conv_w.float().reshape(-1, 1, conv_kernel), conv_b.float(), groups=xBC.shape[-1])
+    xBC = F.silu(xBC.transpose(1, 2))
+    xs, Bm, Cm = torch.split(xBC, [inner, G * N, G * N], dim=-1)
+    dt = F.softplus(dt + dt_bias.float())
+    y = ssd_scan(xs.reshape(Bsz, T, H, P), dt, -torch.exp(A_log.float()), Bm.reshape(Bsz, T, G, N), Cm.reshape(Bsz, T, G, N), D.float(), chunk=chunk)
+    y = y.reshape(Bsz, T, inner) * F.silu(z)
+    yg = y.reshape(Bsz, T, G, inner // G)
+    yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + eps)
+    y = yg.reshape(Bsz, T, inner) * norm_w.float()
+    return F.linear(y.to(x.dtype), out_w, out_b)
+
+
+# ---------------------------------------------------------------------------------------------- gated delta rule (Qwen3.5 / Qwen3-Next)
+def gated_delta_rule(q, k, v, g, beta, *, scale: Optional[float] = None):
+    """Recurrent form of the gated delta rule.  q,k [B,T,H,Dk], v [B,T,H,Dv], g [B,T,H] (log decay, <= 0), beta [B,T,H].
+    S_t = exp(g_t) S_{t-1} + beta_t k_t (v_t - exp(g_t) S_{t-1}^T k_t)^T ; o_t = S_t^T q_t."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    q = F.normalize(q.float(), dim=-1) * (scale if scale is not None else Dk ** -0.5)
+    k = F.normalize(k.float(), dim=-1)
+    v, g, beta = v.float(), g.float(), beta.float()
+    S = q.new_zeros(B, H, Dk, Dv)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[:, t])[..., None, None]
+        kv = torch.einsum("bhk,bhkv->bhv", k[:, t], S)
+        delta = (v[:, t] - kv) * beta[:, t][..., None]
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, t], delta)
+        outs.append(torch.einsum("bhk,bhkv->bhv", q[:, t], S))
+    return torch.stack(outs, dim=1)
+
+
+@register("gated_delta_rule")
+def gated_delta_rule_op(q, k, v, g, beta, *, scale: Optional[float] = None):
+    return gated_delta_rule(q, k, v, g, beta, scale=scale).to(v.dtype)

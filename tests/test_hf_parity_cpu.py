@@ -16,7 +16,7 @@ COMMON = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention
 
 
 def _cases():
-    from transformers import LlamaConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
+    from transformers import GptOssConfig, LlamaConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
 
     yield "qwen3", Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=True)
     yield "qwen3-untied", Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=False)
@@ -25,6 +25,10 @@ def _cases():
     yield "mistral", MistralConfig(**COMMON, head_dim=16, rope_theta=10000.0, sliding_window=None, tie_word_embeddings=False)
     yield "qwen3-moe", Qwen3MoeConfig(**COMMON, head_dim=16, rope_theta=1e6, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                       norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False)
+    yield "gpt-oss", GptOssConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                  intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8, max_position_embeddings=256,
+                                  rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                                   "truncate": False, "original_max_position_embeddings": 64}, tie_word_embeddings=False)
 
 
 @pytest.mark.parametrize("name,config", list(_cases()), ids=[n for n, _ in _cases()])
@@ -34,8 +38,8 @@ def test_logits_match_transformers_and_export_round_trips(tmp_path, name, config
     torch.manual_seed(0)
     hf = AutoModelForCausalLM.from_config(config).float().eval()
     with torch.no_grad():
-        for p in hf.parameters():  # make norms / biases non-trivial
-            if p.dim() == 1:
+        for n, p in hf.named_parameters():  # make norms / biases non-trivial
+            if p.dim() == 1 or "bias" in n:
                 p.add_(0.1 * torch.randn_like(p))
     src = os.path.join(tmp_path, "hf")
     hf.save_pretrained(src, safe_serialization=True)
@@ -47,6 +51,20 @@ def test_logits_match_transformers_and_export_round_trips(tmp_path, name, config
     tr.import_weights(src)
     got = tr.logits(tok)
     assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (name, float((got - want).abs().max()))
+    # backward: same loss and same global gradient norm as autograd through the transformers model
+    tgt = np.roll(tok, -1, axis=1).astype(np.int32)
+    tgt[:, -1] = -100
+    r = tr.forward_backward(tok, tgt)
+    lg = hf(torch.from_numpy(tok).long()).logits
+    loss = torch.nn.functional.cross_entropy(lg.reshape(-1, lg.shape[-1]), torch.from_numpy(tgt).long().reshape(-1), ignore_index=-100, reduction="mean")
+    hf.zero_grad()
+    loss.backward()
+    want_norm = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in hf.parameters() if p.grad is not None))
+    assert abs(float(r["loss_sum"] / r["n_valid"]) - float(loss)) < 1e-4
+    got_norm = float(tr.grad_norm())
+    if name != "qwen3-moe":  # the MoE model adds its load-balancing loss to the gradient
+        assert abs(got_norm - float(want_norm)) < 2e-3 * float(want_norm), (name, got_norm, float(want_norm))
+    tr.store.release_grads()
     out = os.path.join(tmp_path, "export")
     tr.export_model(out, cfg)
     from safetensors.torch import load_file
