@@ -132,6 +132,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-offload", action="store_true", help="keep weights and optimizer state on the device for configs that offload by default")
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "library"], help="native = tcgen05 flash attention of this repo")
+    ap.add_argument("--profile", default=None, help="write a per-kernel time table of one extra step (torch.profiler, rank 0) to this path; not a timed run")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -215,6 +216,19 @@ def main():
         check_device_errors()  # a kernel that timed out on a wait or met an invalid token id invalidates the run
     launches = (ext.launch_count() - launches0) if ext is not None else 0
     clocks = sampler.stop()
+
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            device_step(0)
+            torch.cuda.synchronize()
+        if info.rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(args.profile)), exist_ok=True)
+            with open(args.profile, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=70))
+        barrier()
 
     # end-to-end through the public API: numpy batches from host memory in, python floats out, every step
     e2e = None

@@ -343,9 +343,17 @@ void adamw8_step(Tensor& p, const Tensor& g, Tensor& m8, Tensor& v8, Tensor& ms,
     TORCH_CHECK(static_cast<size_t>(ms.numel()) * 32 >= static_cast<size_t>(p.numel()), "adamw8: one scale per 32 elements");
     TORCH_CHECK(p.numel() % 32 == 0, "adamw8: element count must be a multiple of 32");
     const c10::cuda::CUDAGuard guard(p.device());
+    int block_mask = 0;  // the weight-decay mask is one byte per parameter, or one byte per 128 parameters
+    if (mask.has_value() && mask->defined()) {
+        TORCH_CHECK(mask->scalar_type() == at::kByte && mask->is_contiguous(), "adamw8: mask must be contiguous uint8");
+        if (mask->numel() != p.numel()) {
+            TORCH_CHECK(p.numel() % 128 == 0 && mask->numel() * 128 == p.numel(), "adamw8: mask needs one byte per parameter or per 128 parameters");
+            block_mask = 1;
+        }
+    }
     g_launches += 1;
     sg::adamw_8bit(p.data_ptr(), p.scalar_type() == at::kFloat, g.data_ptr(), g.scalar_type() == at::kFloat, m8.data_ptr(), v8.data_ptr(), ms.data_ptr(),
-                   vs.data_ptr(), static_cast<const uint8_t*>(opt_ptr(mask)), hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
+                   vs.data_ptr(), static_cast<const uint8_t*>(opt_ptr(mask)), block_mask, hp.data_ptr<float>(), p.numel(), num_sms(), cur_stream());
 }
 
 }  // namespace

@@ -599,71 +599,94 @@ __global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, cons
 
 // 8-bit state: momentum int8 through softsign (2x/(1+|x|) of the group-normalised value), variance uint8 of sqrt(v),
 // groups of 32 with fp16 scales.  Four adjacent lanes (8 elements each) form one group; the group abs-max is two shuffles.
-// n must be a multiple of 32.
-template <typename P, typename G>
-__global__ void __launch_bounds__(256) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
-                                                         __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
-                                                         const float* __restrict__ hp, size_t n) {
+// n must be a multiple of 32.  The kernel is bandwidth-bound by design (10.25 bytes per parameter): divisions and square
+// roots use the fast hardware approximations, each thread keeps two 8-element vectors in flight, and the weight-decay mask is
+// one byte per 128 parameters (BLOCK_MASK) instead of one per parameter.
+template <typename P, typename G, bool BLOCK_MASK>
+__global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
+                                                            __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
+                                                            const float* __restrict__ hp, size_t n) {
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
-    const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+    const float step_size = lr / bc1, sib2 = rsqrtf(bc2), omb1 = 1.f - b1, omb2 = 1.f - b2;
     const size_t nvec = n / 8;
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    constexpr int U = 2;  // vectors per thread per trip
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * U;
     // warp-uniform trip count so the shuffles always see all 32 lanes
-    for (size_t base = blockIdx.x * static_cast<size_t>(blockDim.x) + (threadIdx.x & ~31); base < nvec; base += stride) {
-        const size_t vi = base + (threadIdx.x & 31);
-        const bool live = vi < nvec;
-        const size_t i = vi * 8, grp = vi >> 2;
-        float pv[8], gv[8], mv[8], sv[8];
-        float am = 0.f, av = 0.f;
-        if (live) {
-            load8_any(p + i, pv);
-            load8_any(g + i, gv);
-            const uint2 mraw = *reinterpret_cast<const uint2*>(m8 + i), vraw = *reinterpret_cast<const uint2*>(v8 + i);
-            const int8_t* mq = reinterpret_cast<const int8_t*>(&mraw);
-            const uint8_t* vq = reinterpret_cast<const uint8_t*>(&vraw);
-            uint2 mk = make_uint2(0, 0);
-            if (decay_mask) mk = *reinterpret_cast<const uint2*>(decay_mask + i);
-            const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk);
-            const float sm = __half2float(ms[grp]), sq = __half2float(vs[grp]);
+    for (size_t base = (blockIdx.x * static_cast<size_t>(blockDim.x) + (threadIdx.x & ~31)) * U; base < nvec; base += stride) {
+        float pv[U][8], gv[U][8];
+        uint2 mraw[U], vraw[U], mk[U];
+        float sm[U], sq[U];
+        bool live[U];
+        size_t idx[U];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float gk = gv[k] * gs;
-                const float y = static_cast<float>(mq[k]) * (1.f / 127.f);
-                float mi = y / (2.f - fabsf(y)) * sm;
-                const float r = static_cast<float>(vq[k]) * (1.f / 255.f) * sq;
-                float vi2 = r * r;
-                mi = b1 * mi + (1.f - b1) * gk;
-                vi2 = b2 * vi2 + (1.f - b2) * gk * gk;
-                const float dec = mb[k] ? wd : 0.f;
-                pv[k] = pv[k] * (1.f - lr * dec) - lr * (mi * ibc1) / (sqrtf(vi2 * ibc2) + eps);
-                mv[k] = mi;
-                sv[k] = sqrtf(vi2);
-                am = fmaxf(am, fabsf(mi));
-                av = fmaxf(av, sv[k]);
+        for (int u = 0; u < U; ++u) {   // issue every load of both vectors before any arithmetic
+            const size_t vi = base + u * 32 + (threadIdx.x & 31);
+            live[u] = vi < nvec;
+            idx[u] = vi * 8;
+            mk[u] = make_uint2(0x01010101u, 0x01010101u);
+            if (live[u]) {
+                load8_any(p + idx[u], pv[u]);
+                load8_any(g + idx[u], gv[u]);
+                mraw[u] = *reinterpret_cast<const uint2*>(m8 + idx[u]);
+                vraw[u] = *reinterpret_cast<const uint2*>(v8 + idx[u]);
+                sm[u] = __half2float(ms[vi >> 2]);
+                sq[u] = __half2float(vs[vi >> 2]);
+                if (decay_mask) {
+                    if (BLOCK_MASK) { if (!decay_mask[idx[u] >> 7]) mk[u] = make_uint2(0, 0); }
+                    else mk[u] = *reinterpret_cast<const uint2*>(decay_mask + idx[u]);
+                }
             }
-            store8_any(p + i, pv);
         }
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-        av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 1));
-        av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
-        if (live) {
-            // fp16 scales rounded up so normalised values stay within [-1, 1]
-            const __half hm = __float2half_ru(fmaxf(am, 1e-30f)), hv = __float2half_ru(fmaxf(av, 1e-30f));
-            const float fm = fmaxf(__half2float(hm), 6e-8f), fv = fmaxf(__half2float(hv), 6e-8f);
-            const float im = 1.f / fm, iv = 255.f / fv;
-            uint2 mo, vo;
-            int8_t* mq = reinterpret_cast<int8_t*>(&mo);
-            uint8_t* vq = reinterpret_cast<uint8_t*>(&vo);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float xn = mv[k] * im;
-                mq[k] = static_cast<int8_t>(__float2int_rn(2.f * xn / (1.f + fabsf(xn)) * 127.f));
-                vq[k] = static_cast<uint8_t>(min(255, __float2int_rn(sv[k] * iv)));
+        for (int u = 0; u < U; ++u) {
+            float mv[8], sv[8];
+            float am = 0.f, av = 0.f;
+            if (live[u]) {
+                const int8_t* mq = reinterpret_cast<const int8_t*>(&mraw[u]);
+                const uint8_t* vq = reinterpret_cast<const uint8_t*>(&vraw[u]);
+                const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk[u]);
+                const float smu = sm[u], squ = sq[u] * (1.f / 255.f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float gk = gv[u][k] * gs;
+                    const float y = static_cast<float>(mq[k]) * (1.f / 127.f);
+                    float mi = __fdividef(y, 2.f - fabsf(y)) * smu;
+                    const float r = static_cast<float>(vq[k]) * squ;
+                    float vi2 = r * r;
+                    mi = b1 * mi + omb1 * gk;
+                    vi2 = b2 * vi2 + omb2 * gk * gk;
+                    const float s = vi2 > 0.f ? vi2 * rsqrtf(vi2) : 0.f;   // sqrt(v)
+                    const float dec = mb[k] ? wd : 0.f;
+                    pv[u][k] = pv[u][k] * (1.f - lr * dec) - step_size * __fdividef(mi, s * sib2 + eps);
+                    mv[k] = mi;
+                    sv[k] = s;
+                    am = fmaxf(am, fabsf(mi));
+                    av = fmaxf(av, s);
+                }
+                store8_any(p + idx[u], pv[u]);
             }
-            *reinterpret_cast<uint2*>(m8 + i) = mo;
-            *reinterpret_cast<uint2*>(v8 + i) = vo;
-            if ((threadIdx.x & 3) == 0) { ms[grp] = __float2half(fm); vs[grp] = __float2half(fv); }
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 1));
+            av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
+            if (live[u]) {
+                // fp16 scales rounded up so normalised values stay within [-1, 1]
+                const __half hm = __float2half_ru(fmaxf(am, 1e-30f)), hv = __float2half_ru(fmaxf(av, 1e-30f));
+                const float fm = fmaxf(__half2float(hm), 6e-8f), fv = fmaxf(__half2float(hv), 6e-8f);
+                const float im = __fdividef(1.f, fm), iv = __fdividef(255.f, fv);
+                uint2 mo, vo;
+                int8_t* mq = reinterpret_cast<int8_t*>(&mo);
+                uint8_t* vq = reinterpret_cast<uint8_t*>(&vo);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float xn = fminf(fmaxf(mv[k] * im, -1.f), 1.f);
+                    mq[k] = static_cast<int8_t>(__float2int_rn(__fdividef(254.f * xn, 1.f + fabsf(xn))));
+                    vq[k] = static_cast<uint8_t>(min(255, __float2int_rn(sv[k] * iv)));
+                }
+                *reinterpret_cast<uint2*>(m8 + idx[u]) = mo;
+                *reinterpret_cast<uint2*>(v8 + idx[u]) = vo;
+                if ((threadIdx.x & 3) == 0) { ms[idx[u] >> 5] = __float2half(fm); vs[idx[u] >> 5] = __float2half(fv); }
+            }
         }
     }
 }
@@ -744,13 +767,16 @@ void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float*
     else if (g_fp32) adamw_fp32_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, m, v, mask, hp, n);
     else adamw_fp32_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)p, (const bf16*)g, m, v, mask, hp, n);
 }
-void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, const float* hp,
-                size_t n, int num_sms, cudaStream_t s) {
-    const int grid = grid_for(n / 8, 256, num_sms);
-    if (p_fp32 && g_fp32) adamw_8bit_kernel<float, float><<<grid, 256, 0, s>>>((float*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
-    else if (p_fp32) adamw_8bit_kernel<float, bf16><<<grid, 256, 0, s>>>((float*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
-    else if (g_fp32) adamw_8bit_kernel<bf16, float><<<grid, 256, 0, s>>>((bf16*)p, (const float*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
-    else adamw_8bit_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
+void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, int block_mask,
+                const float* hp, size_t n, int num_sms, cudaStream_t s) {
+    const int grid = grid_for(n / 16, 256, num_sms, 16);
+#define SG_A8(PT, GT, BM) adamw_8bit_kernel<PT, GT, BM><<<grid, 256, 0, s>>>((PT*)p, (const GT*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n)
+    if (block_mask) {
+        if (p_fp32 && g_fp32) SG_A8(float, float, true); else if (p_fp32) SG_A8(float, bf16, true); else if (g_fp32) SG_A8(bf16, float, true); else SG_A8(bf16, bf16, true);
+    } else {
+        if (p_fp32 && g_fp32) SG_A8(float, float, false); else if (p_fp32) SG_A8(float, bf16, false); else if (g_fp32) SG_A8(bf16, float, false); else SG_A8(bf16, bf16, false);
+    }
+#undef SG_A8
 }
 
 }  // namespace sg

@@ -27,7 +27,7 @@ void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s
 void sumsq(const void* x, int is_fp32, float* partial, int nblocks, size_t n, cudaStream_t s);
 void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float* v, const uint8_t* mask, const float* hp, size_t n, int num_sms,
                 cudaStream_t s);
-void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, const float* hp,
-                size_t n, int num_sms, cudaStream_t s);
+void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, int block_mask,
+                const float* hp, size_t n, int num_sms, cudaStream_t s);
 
 }  // namespace sg

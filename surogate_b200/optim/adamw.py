@@ -118,10 +118,10 @@ class AdamW8bit(AdamW):
 
     def step_bucket(self, b, grad, hp, hp_host) -> None:
         st = self._state(b)
-        mask = self.store.decay_mask(b)
         if self.use_kernels:
-            self.ext.adamw8_step(b.master, grad.contiguous(), st["m"], st["v"], st["m.scales"], st["v.scales"], mask, hp)
+            self.ext.adamw8_step(b.master, grad.contiguous(), st["m"], st["v"], st["m.scales"], st["v.scales"], self.store.decay_mask_blocks(b), hp)
             return
+        mask = self.store.decay_mask(b)
         lr, b1, b2, eps, wd, bc1, bc2 = hp_host
         m, v = _softsign_dequant_reference(st["m"], st["v"], st["m.scales"], st["v.scales"])
         g = grad.float() * hp[7]

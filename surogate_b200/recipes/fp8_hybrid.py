@@ -18,6 +18,8 @@ recipes/fp8_hybrid/kernels/{quant,delayed_scaling}.cu.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, Tuple
 
 import torch
@@ -33,8 +35,10 @@ QUANT_ROLES = ("qkv", "out", "mlp_up", "mlp_down")
 class FP8HybridRecipe(Recipe):
     name = "fp8_hybrid"
 
-    def __init__(self, cm, device, history: int = 16, margin: int = 0, skip_first_layers: int = 0, skip_last_layers: int = 0):
+    def __init__(self, cm, device, history: int = 16, margin: int = 0, skip_first_layers: int = 0, skip_last_layers: int = 0,
+                 fp8_lm_head: bool = True):
         self.device = device
+        self.fp8_lm_head = bool(fp8_lm_head) and os.environ.get("SUROGATE_FP8_LM_HEAD", "1") != "0"
         self.history = history
         self.margin = margin
         self.n_layers = cm.n_layers
@@ -127,6 +131,21 @@ class FP8HybridRecipe(Recipe):
             return self._quantize(ext, y, q, False)
         _, y8 = ext.swiglu_fwd(x, False, self.scale[q:q + 1], self.amax_cur[q:q + 1], True)
         return Fp8Tensor(y8, self.scale_inv[q:q + 1])
+
+    # ------------------------------------------------------------------ LM head
+    def quantize_now(self, ext, x: torch.Tensor):
+        """E4M3 with the scale of this very tensor (one abs-max pass): used where no amax history exists (LM-head input)."""
+        am = torch.zeros(1, dtype=torch.float32, device=x.device)
+        ext.amax(x, am)
+        s = torch.where(am > 0, 448.0 / am, torch.ones_like(am))
+        return ext.quantize_fp8(x, s, None, False), 1.0 / s
+
+    def lm_head_weight(self, ext, w: torch.Tensor):
+        """E4M3 copy of the LM-head matrix, rebuilt once per optimizer step (dropped by on_weights_updated)."""
+        c = self.weight_cache.get(("lm_head", w.data_ptr()))
+        if c is None:
+            c = self.weight_cache[("lm_head", w.data_ptr())] = self.quantize_now(ext, w)
+        return c
 
     # ------------------------------------------------------------------ GEMMs
     def quantizes(self, layer, role: str) -> bool:

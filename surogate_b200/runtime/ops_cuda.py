@@ -214,14 +214,34 @@ class CudaOps(RefOps):
         if kd and kd.get("ce_weight", 1.0) != 1.0:  # total = ce_weight * CE + weight * KD
             cw = torch.full((n,), float(kd["ce_weight"]), dtype=torch.float32, device=x.device)
             rw = cw if rw is None else rw * cw
+        # FP8 LM head (FP8 recipe, plain cross-entropy): x and W in E4M3, d_logits in E5M2 with a scale known in advance
+        # (|softmax - onehot| <= 1, times the loss scale), so all three GEMMs of the head run at FP8 rate.
+        fp8 = (getattr(ctx.recipe, "fp8_lm_head", False) and rw is None and kd is None and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+               and C % 16 == 0 and V % 16 == 0)
+        if fp8:
+            x8, x_inv = ctx.recipe.quantize_now(self.ext, x2)
+            w8, w_inv = ctx.recipe.lm_head_weight(self.ext, w)
+            if train:
+                ls = scale_t.reshape(1).float() * scale_h if scale_t is not None else torch.full((1,), scale_h, dtype=torch.float32, device=x.device)
+                d_scale = (57344.0 * 0.5) / ls.clamp_min(1e-30)
+                d_inv = 1.0 / d_scale
         for s in range(0, n, rows):
             e = min(s + rows, n)
             lg = logits[: e - s]
-            gemm(x2[s:e], w, lg)
+            if fp8:
+                gemm(x8[s:e], w8, lg, scale_a=x_inv, scale_b=w_inv)
+            else:
+                gemm(x2[s:e], w, lg)
             losses[s:e] = self.ext.cross_entropy_fwd_bwd(lg, t[s:e], scale_t, scale_h, train, rw[s:e] if rw is not None else None,
                                                          kd_idx[s:e] if kd else None, kd_logp[s:e] if kd else None, float(kd["weight"]) if kd else 0.0,
                                                          kd_losses[s:e] if kd else None)
-            if train:
+            if train and fp8:
+                d8 = self.ext.quantize_fp8(lg, d_scale, None, True)
+                gemm(d8, w8, dx[s:e], a_mn=False, b_mn=True, scale_a=d_inv, scale_b=w_inv)
+                if tgt is not None:
+                    gemm(d8, x8[s:e], tgt, a_mn=True, b_mn=True, accumulate=acc, scale_a=d_inv, scale_b=x_inv)
+                    acc = True
+            elif train:
                 gemm(lg, w, dx[s:e], a_mn=False, b_mn=True)
                 if tgt is not None:
                     gemm(lg, x2[s:e], tgt, a_mn=True, b_mn=True, accumulate=acc)

@@ -668,6 +668,16 @@ class ParamStore:
             b.decay_mask_cache = m
         return b.decay_mask_cache
 
+    def decay_mask_blocks(self, b: Bucket) -> torch.Tensor:
+        """The same mask at one byte per 128 elements (slots start on 128-element boundaries and shards are multiples of 128,
+        so nothing is lost); what the optimizer kernels read."""
+        m = getattr(b, "decay_blocks_cache", None)
+        if m is None:
+            full = self.decay_mask(b)
+            assert full.numel() % ALIGN_ELEMS == 0
+            m = b.decay_blocks_cache = full.view(-1, ALIGN_ELEMS).amax(1).contiguous()
+        return m
+
     def grad_of(self, name: str) -> Optional[torch.Tensor]:
         """Full (reduced) gradient of one parameter — debugging / tests; gathers when sharded."""
         name = self.resolve(name)
