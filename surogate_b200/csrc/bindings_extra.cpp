@@ -220,11 +220,28 @@ void ep_plan(const std::vector<int64_t>& ctrl, int64_t ctrl_byte_offset, const s
              Tensor& dst_base, Tensor& cursors, int64_t rank, int64_t epoch, int64_t slot_base, int64_t capacity_rows, Tensor& error_flag,
              double budget_s) {
     const int E = static_cast<int>(counts.numel()), world = static_cast<int>(ctrl.size());
-    TORCH_CHECK(E <= 256 && E % world == 0 && offsets.numel() == E / world + 2 && dst_base.numel() == E && cursors.numel() == E, "ep_plan shapes");
+    TORCH_CHECK(E <= 256 && E % world == 0 && offsets.numel() == 2 * (E / world) + 2 && dst_base.numel() == E && cursors.numel() == E, "ep_plan shapes");
     sg_count_launch(1);
     sg::ep_plan(to_peers(ctrl, ctrl_byte_offset), to_peers(pads), counts.data_ptr<int>(), offsets.data_ptr<int>(), dst_base.data_ptr<int>(),
                 cursors.data_ptr<int>(), E, static_cast<int>(rank), world, static_cast<uint32_t>(epoch), static_cast<int>(slot_base),
                 static_cast<int>(capacity_rows), error_flag.data_ptr<int>(), budget_s, cur_stream());
+}
+
+void ep_zero_pad_rows(Tensor& buf, const Tensor& offsets, int64_t El, int64_t capacity_rows) {
+    TORCH_CHECK(buf.is_cuda() && buf.scalar_type() == at::kBFloat16 && buf.is_contiguous() && buf.dim() == 2 && buf.size(1) % 8 == 0, "buf: bf16 [rows, C]");
+    TORCH_CHECK(offsets.scalar_type() == at::kInt && offsets.numel() >= 2 * El + 2 && capacity_rows <= buf.size(0), "offsets / capacity");
+    const c10::cuda::CUDAGuard guard(buf.device());
+    sg_count_launch(1);
+    sg::ep_zero_pad_rows(buf.data_ptr(), offsets.data_ptr<int>(), static_cast<int>(El), static_cast<int>(buf.size(1)), static_cast<int>(capacity_rows), cur_stream());
+}
+
+void copy_rows_upto(const Tensor& src, Tensor& dst, const Tensor& n_rows) {
+    TORCH_CHECK(src.is_cuda() && dst.is_cuda() && src.is_contiguous() && dst.is_contiguous() && src.dim() == 2 && src.sizes() == dst.sizes(), "same-shape 2-D tensors");
+    TORCH_CHECK(src.element_size() == 2 && dst.element_size() == 2 && src.size(1) % 8 == 0, "16-bit elements, row length a multiple of 8");
+    TORCH_CHECK(n_rows.scalar_type() == at::kInt && n_rows.is_cuda() && n_rows.numel() == 1, "n_rows: one CUDA int32");
+    const c10::cuda::CUDAGuard guard(src.device());
+    sg_count_launch(1);
+    sg::copy_rows_upto(src.data_ptr(), dst.data_ptr(), n_rows.data_ptr<int>(), static_cast<int>(src.size(1)), sms(), cur_stream());
 }
 
 void ep_dispatch(const Tensor& x, const c10::optional<Tensor>& topk_idx, const c10::optional<Tensor>& w, const c10::optional<Tensor>& dst_base,
@@ -410,6 +427,8 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
+    m.def("ep_zero_pad_rows", &ep_zero_pad_rows);
+    m.def("copy_rows_upto", &copy_rows_upto);
     m.def("ep_combine", &ep_combine);
     m.def("ep_weight_grad", &ep_weight_grad);
 }

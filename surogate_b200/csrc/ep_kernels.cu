@@ -34,7 +34,8 @@ __device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
 }
 
 // ctrl layout per rank (ints): [0, W*E) all_counts[src][expert] ; pads (uint32) live in the communicator's signal pad.
-// Outputs (local, ints): offsets[El+2] (padded rows of my experts, clamped to the buffer; last entry = overflow rows), dst_base[E] (first row I may write per global expert),
+// Outputs (local, ints): offsets[2*El+2] = padded start rows of my experts (El+1 entries, clamped to the buffer), overflow rows,
+// then the real row count of each of my experts; dst_base[E] (first row I may write per global expert),
 // cursors[E] = 0.
 __global__ void __launch_bounds__(256) ep_plan_kernel(PeerPtrs ctrl, PeerPtrs pads, const int* __restrict__ counts, int* __restrict__ offsets,
                                                       int* __restrict__ dst_base, int* __restrict__ cursors, int E, int rank, int world,
@@ -86,7 +87,26 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(PeerPtrs ctrl, PeerPtrs pa
             offsets[El] = end < capacity_rows ? end : capacity_rows;
             offsets[El + 1] = end > capacity_rows ? end - capacity_rows : 0;           // rows that did not fit (statistics)
         }
+        if (owner == rank) offsets[El + 2 + el] = tot[e];                              // real (unpadded) rows of my expert el
     }
+}
+
+// Zero the padding rows of every local expert's region (rows [start + real, next start), inside the buffer).  Only padding is
+// touched, so it is safe while peers are already storing real rows.
+__global__ void __launch_bounds__(256) ep_zero_pad_rows_kernel(bf16* __restrict__ buf, const int* __restrict__ offsets, int El, int C, int capacity_rows) {
+    const int el = blockIdx.y;
+    const int lo = min(offsets[el] + offsets[El + 2 + el], capacity_rows), hi = min(offsets[el + 1], capacity_rows);
+    const int vec_per_row = C / 8;
+    const long long total = static_cast<long long>(hi - lo) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x)
+        reinterpret_cast<uint4*>(buf + static_cast<size_t>(lo) * C)[i] = make_uint4(0, 0, 0, 0);
+}
+
+// dst[0:n) = src[0:n) rows, n read from device memory (the padded row count of this step): cost follows the rows in use, not
+// the capacity of the buffer.
+__global__ void __launch_bounds__(256) copy_rows_upto_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int* __restrict__ n_rows, int C) {
+    const long long total = static_cast<long long>(*n_rows) * (C / 8);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) dst[i] = src[i];
 }
 
 // x [tokens, C] bf16; recv = peers' receive buffers ([capacity, C] each).  row_map[tok*K+k] = owner * capacity + row (or -1).
@@ -213,6 +233,12 @@ void ep_plan(const PeerPtrs& ctrl, const PeerPtrs& pads, const int* counts, int*
              uint32_t epoch, int slot_base, int capacity_rows, int* error_flag, double budget_s, cudaStream_t s) {
     ep_plan_kernel<<<1, 256, 0, s>>>(ctrl, pads, counts, offsets, dst_base, cursors, E, rank, world, epoch, slot_base, capacity_rows, error_flag,
                                      static_cast<long long>(budget_s * 2.0e9));
+}
+void ep_zero_pad_rows(void* buf, const int* offsets, int El, int C, int capacity_rows, cudaStream_t s) {
+    ep_zero_pad_rows_kernel<<<dim3(8, El), 256, 0, s>>>((bf16*)buf, offsets, El, C, capacity_rows);
+}
+void copy_rows_upto(const void* src, void* dst, const int* n_rows, int C, int num_sms, cudaStream_t s) {
+    copy_rows_upto_kernel<<<num_sms * 8, 256, 0, s>>>((const uint4*)src, (uint4*)dst, n_rows, C);
 }
 void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, int* cursors, int* row_map, const PeerPtrs& recv, int tokens,
                  int C, int K, int El, int capacity_rows, int reuse_map, cudaStream_t s) {

@@ -15,4 +15,7 @@ void ep_combine(const PeerPtrs& outs, const float* w, const int* row_map, void* 
                 cudaStream_t s);
 void ep_weight_grad(const void* rows, const void* dy, float* d_w, int tokens, int C, int K, cudaStream_t s);
 
+void ep_zero_pad_rows(void* buf, const int* offsets, int El, int C, int capacity_rows, cudaStream_t s);
+void copy_rows_upto(const void* src, void* dst, const int* n_rows, int C, int num_sms, cudaStream_t s);
+
 }  // namespace sg

@@ -96,22 +96,25 @@ class ExpertParallel:
         b = self._ensure(N, K, C, E)
         cap, El = b["cap"], b["El"]
         dev = x2.device
-        offsets = torch.zeros(El + 2, dtype=torch.int32, device=dev)  # [El+1] padded row ranges + overflow count
+        offsets = torch.zeros(2 * El + 2, dtype=torch.int32, device=dev)  # El+1 padded row starts, overflow count, El real row counts
         dst_base = torch.empty(E, dtype=torch.int32, device=dev)
         cursors = torch.empty(E, dtype=torch.int32, device=dev)
         row_map = torch.empty(N * K, dtype=torch.int32, device=dev)
-        b["recv_x"].zero_()  # pad rows feed the wgrad contraction and must be zero; peers write only after the barrier inside ep_plan
         self.epoch += 1
         pb = b["arena"].peer_bases
         self.ext.ep_plan(pb, b["counts_off"], self.comm.ctrl.peer_bases, pre.counts, offsets, dst_base, cursors, self.rank, self.epoch & 0x7FFFFFFF,
                          SLOT_EP, cap, self.err, self.comm.wait_budget_s)
+        # pad rows feed the wgrad contraction and must be zero; only they are touched, so peers may already be storing real rows
+        self.ext.ep_zero_pad_rows(b["recv_x"], offsets, El, cap)
         self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, cursors, row_map, pb, b["recv_x_off"], K, El, cap, False)
         self._barrier()  # every rank's rows have landed
-        xp = b["recv_x"].clone()
+        xp = torch.empty_like(b["recv_x"])  # rows beyond the used range stay uninitialised: nothing downstream reads them into a result
+        self.ext.copy_rows_upto(b["recv_x"], xp, offsets[El:El + 1])
         if ctx.layer is not None and ctx.phase == "fwd":
             self.last_global_counts[ctx.layer] = b["counts"].view(self.ep, E).sum(0)
             self.last_overflow[ctx.layer] = offsets[El + 1:El + 2]
         plan = EpPlan(offsets[:El + 1], row_map, cap, N, K, pre.x_shape, pre.topk_idx)
+        plan.layout = offsets
         pre.ep_plan = plan
         return xp, plan
 
@@ -119,7 +122,7 @@ class ExpertParallel:
         """Expert outputs (or d_x of the experts in backward) become visible to the token owners."""
         b = self.bufs
         buf = b["out_dx"] if backward else b["out_y"]
-        buf.copy_(h)
+        self.ext.copy_rows_upto(h.contiguous(), buf, plan.layout[b["El"]:b["El"] + 1])
         self._barrier()
         return buf
 
@@ -141,11 +144,13 @@ class ExpertParallel:
         dy2 = dy.reshape(plan.num_tokens, -1).contiguous()
         w = weights.reshape(-1, K).contiguous()
         d_w = self.ext.ep_weight_grad(plan.kept_rows, dy2, K)
-        b["recv_dy"].zero_()
         self._barrier()  # peers are done with the previous contents of their gradient buffers
+        self.ext.ep_zero_pad_rows(b["recv_dy"], plan.layout, b["El"], plan.capacity)
         self.ext.ep_dispatch(dy2, None, w, None, None, plan.row_map, b["arena"].peer_bases, b["recv_dy_off"], K, b["El"], plan.capacity, True)
         self._barrier()
-        return b["recv_dy"].clone(), d_w.reshape(weights.shape)
+        dyp = torch.empty_like(b["recv_dy"])
+        self.ext.copy_rows_upto(b["recv_dy"], dyp, plan.layout[b["El"]:b["El"] + 1])
+        return dyp, d_w.reshape(weights.shape)
 
     # ------------------------------------------------------------------ balancing
     def dropped_rows(self) -> int:

@@ -317,7 +317,8 @@ def _moe_mixin():
         extra = None
         if d_aux is not None:
             da = d_aux if torch.is_tensor(d_aux) else float(d_aux)
-            counts = torch.bincount(til.reshape(-1), minlength=E).float()
+            flat = til.reshape(-1)
+            counts = torch.zeros(E, dtype=torch.float32, device=x.device).scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.float32))  # no host sync
             d_probs = d_probs + da * a["aux_loss_coef"] * E * (counts / N) / N
             if a.get("z_loss_coef", 0.0):
                 extra = da * a["z_loss_coef"] * 2 * torch.logsumexp(logits, -1, keepdim=True) / N * probs
