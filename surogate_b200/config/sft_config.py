@@ -305,7 +305,8 @@ class SFTConfig:
             eps=self.adamw_epsilon, weight_decay=self.weight_decay, max_grad_norm=self.max_grad_norm, zero_level=self.zero_level,
             recompute=self.recompute, grad_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.gradient_dtype or "", "bf16"),
             master_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.master_dtype or "", None),
-            lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, lora=self.lora_dict(),
+            lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, ep_load_balance_threshold=self.ep_load_balance_threshold,
+            ep_plan_refresh_interval=self.ep_plan_refresh_interval, lora=self.lora_dict(),
             fp8_amax_history=self.fp8_amax_history, skip_quant_first_layers=self.skip_quant_first_layers,
             skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer and not self.cpu_training,
             offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training,

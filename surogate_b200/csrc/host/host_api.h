@@ -28,6 +28,7 @@ struct LptPlan {
     float imbalance = 1.0f;
 };
 float imbalance_ratio(const int64_t* counts, int num_experts, int ep_size);
+std::vector<int> balanced_placement(const int64_t* counts, int num_experts, int ep_size, const int* current, float tolerance, int* moved_out);
 LptPlan compute_lpt_plan(const int64_t* counts, int num_experts, int ep_size, float threshold, float capacity_factor, int min_tokens_per_gemm);
 
 // crash_handler.cpp

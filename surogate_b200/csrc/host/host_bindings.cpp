@@ -116,6 +116,12 @@ PYBIND11_MODULE(sg_b200_host, m) {
                               py::arg("expert_to_gpu") = p.expert_to_gpu, py::arg("uses_lpt") = p.uses_lpt, py::arg("imbalance") = p.imbalance);
           }, py::arg("counts"), py::arg("ep_size"), py::arg("threshold") = 1.3f, py::arg("capacity_factor") = 1.1f, py::arg("min_tokens_per_gemm") = 1024);
 
+    m.def("balanced_placement", [](const std::vector<int64_t>& counts, int ep, const std::vector<int>& current, float tol) {
+              int moved = 0;
+              auto p = balanced_placement(counts.data(), static_cast<int>(counts.size()), ep, current.data(), tol, &moved);
+              return py::make_tuple(p, moved);
+          }, py::arg("counts"), py::arg("ep_size"), py::arg("current"), py::arg("tolerance") = 0.05f);
+
     m.def("install_crash_handler", &install_crash_handler, py::arg("tag") = "surogate_b200");
     m.def("query_gpu", [](int index) {
         GpuTelemetry t = query_gpu(index);

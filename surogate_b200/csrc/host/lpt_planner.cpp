@@ -84,4 +84,47 @@ LptPlan compute_lpt_plan(const int64_t* counts, int E, int ep, float threshold, 
     return plan;
 }
 
+// Expert re-placement: every rank keeps exactly E/ep experts, but WHICH experts is chosen so that the per-rank token load is
+// even.  Experts are visited from the most to the least loaded; one stays where it is while that rank has a free slot and its
+// load stays within (1 + tolerance) of the mean, otherwise it goes to the least-loaded rank that still has a free slot.
+// placement[e] = rank * (E/ep) + slot.  Experts that do not change rank keep their slot, so only real moves cost traffic.
+std::vector<int> balanced_placement(const int64_t* counts, int E, int ep, const int* current, float tolerance, int* moved_out) {
+    const int El = E / ep;
+    int64_t total = 0;
+    for (int e = 0; e < E; ++e) total += counts[e];
+    const double target = static_cast<double>(total) / ep * (1.0 + tolerance);
+    std::vector<int> order(E), rank_of(E, -1), free_slots(ep, El);
+    std::vector<int64_t> load(ep, 0);
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return counts[a] > counts[b]; });
+    for (int e : order) {
+        const int cur = current[e] / El;
+        int pick = -1;
+        if (free_slots[cur] > 0 && static_cast<double>(load[cur] + counts[e]) <= target) pick = cur;
+        if (pick < 0) {
+            for (int r = 0; r < ep; ++r)
+                if (free_slots[r] > 0 && (pick < 0 || load[r] < load[pick] || (load[r] == load[pick] && r == cur))) pick = r;
+        }
+        rank_of[e] = pick;
+        load[pick] += counts[e];
+        free_slots[pick] -= 1;
+    }
+    std::vector<int> placement(E, -1);
+    std::vector<std::vector<char>> used(ep, std::vector<char>(El, 0));
+    int moved = 0;
+    for (int e = 0; e < E; ++e)
+        if (rank_of[e] == current[e] / El) { placement[e] = current[e]; used[rank_of[e]][current[e] % El] = 1; }
+    for (int e = 0; e < E; ++e) {
+        if (placement[e] >= 0) continue;
+        const int r = rank_of[e];
+        int slot = 0;
+        while (used[r][slot]) ++slot;
+        used[r][slot] = 1;
+        placement[e] = r * El + slot;
+        ++moved;
+    }
+    if (moved_out) *moved_out = moved;
+    return placement;
+}
+
 }  // namespace sg

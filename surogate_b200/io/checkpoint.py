@@ -87,6 +87,8 @@ def save_checkpoint(trainer, root: str, step: int, extra: Dict[str, Any]) -> str
             "distributed": {"world": world, "ep_size": trainer.cfg.ep_size, "zero_level": store.zero_level, "sharded": store.sharded},
             "layout": {b.name: {"numel": b.numel, "shard_numel": b.shard_numel} for b in store.buckets.values()},
             "optimizer": trainer.cfg.optimizer, "recipe": trainer.cfg.recipe,
+            # which (rank, slot) holds each global expert of each layer (identity unless experts were re-placed for load balance)
+            "ep_placement": {str(k): v for k, v in getattr(trainer.store, "expert_placement", {}).items()},
         }
         tmp = os.path.join(d, "checkpoint.json.tmp")
         with open(tmp, "w") as f:
@@ -122,8 +124,25 @@ def load_checkpoint(trainer, root: str, step: Optional[int] = None) -> Dict[str,
         raise ValueError(f"checkpoint was written with ep_size={dist_meta.get('ep_size')} but the run uses {trainer.cfg.ep_size}")
     saved_world = dist_meta["world"] if dist_meta.get("sharded") else 1
     store, opt = trainer.store, trainer.optimizer
+    placement = {int(k): list(v) for k, v in (meta.get("ep_placement") or {}).items()}
+    if placement and trainer.ep is not None:
+        store.expert_placement = dict(placement)
+        trainer.ep.placement_host = dict(placement)
+        trainer.ep.placement = {L: torch.tensor(v, dtype=torch.int32, device=store.device) for L, v in placement.items()}
     for b in store.buckets.values():
         lay = meta["layout"][b.name]
+        if b.expert:  # whole experts live on one rank: each rank reads back exactly what it wrote
+            if dist_meta["world"] != trainer.world:
+                raise ValueError("expert-parallel checkpoints must be loaded with the world size they were written with")
+            with safe_open(os.path.join(d, _shard_name("weights", trainer.rank, saved_world)), framework="pt") as f:
+                b.master.copy_(f.get_tensor(b.name).to(b.master.dtype))
+            for k, t in opt.state_tensors(b).items():
+                fn = os.path.join(d, _shard_name(f"adam.{k}", trainer.rank, saved_world))
+                if os.path.exists(fn):
+                    with safe_open(fn, framework="pt") as f:
+                        if b.name in f.keys():
+                            t.copy_(f.get_tensor(b.name).to(t.dtype))
+            continue
         lo, hi = store.shard_range(b)
         total_saved = lay["shard_numel"] * saved_world
         hi_c = min(hi, total_saved)

@@ -63,6 +63,10 @@ class ExpertParallel:
         self.epoch = 0
         self.last_global_counts: Dict[int, torch.Tensor] = {}
         self.last_overflow: Dict[int, torch.Tensor] = {}  # rows per layer that exceeded this rank's receive capacity (dropped)
+        # Least-loaded placement: placement[layer][e] = rank * El + slot that currently holds global expert e (identity at start).
+        self.placement: Dict[int, torch.Tensor] = {}
+        self.placement_host: Dict[int, list] = {}
+        self.moves_done = 0
 
     # ------------------------------------------------------------------ buffers
     def _ensure(self, tokens: int, K: int, C: int, E: int):
@@ -152,13 +156,102 @@ class ExpertParallel:
         self.ext.copy_rows_upto(b["recv_dy"], dyp, plan.layout[b["El"]:b["El"] + 1])
         return dyp, d_w.reshape(weights.shape)
 
+    # ------------------------------------------------------------------ least-loaded expert placement
+    def place(self, layer, topk_idx: torch.Tensor, counts: torch.Tensor):
+        """Router output (global expert ids, per-expert counts) -> ids / counts in placed order, which is what the dispatch
+        kernels understand (owner = id // El, local slot = id % El)."""
+        p = self.placement.get(layer)
+        if p is None:
+            return topk_idx, counts
+        placed = p[topk_idx.long()]
+        c = torch.zeros_like(counts).scatter_(0, p.long(), counts)
+        return placed.contiguous(), c
+
+    def rebalance(self, store, optimizer, threshold: float = 1.3, tolerance: float = 0.05) -> Dict[str, Any]:
+        """Re-place experts so that every rank sees about the same number of routed rows (from the last step's counts).
+
+        Ownership itself moves: the expert's master weights, work weights and optimizer moments travel to the new owner
+        (point-to-point over NCCL, once per refresh), so later steps need no per-step weight shipping or gradient return.
+        Layers whose rank imbalance is below ``threshold`` are left alone.  Collective: every rank must call it."""
+        import torch.distributed as dist
+
+        from ..ops import host
+
+        if not self.last_global_counts:
+            return {"layers": 0, "moved": 0}
+        layers = sorted(self.last_global_counts)
+        counts_all = torch.stack([self.last_global_counts[L].to(torch.int64) for L in layers]).cpu()  # the one host sync of a refresh
+        h = host()
+        E = counts_all.shape[1]
+        El = E // self.ep
+        changed, moved_total = 0, 0
+        for li, L in enumerate(layers):
+            cur = self.placement_host.get(L) or list(range(E))
+            placed_counts = counts_all[li].tolist()           # the kernels count in placed order
+            counts = [placed_counts[cur[e]] for e in range(E)]  # -> per global expert
+            per_rank = [0] * self.ep
+            for e, c in enumerate(counts):
+                per_rank[cur[e] // El] += c
+            mean = max(1.0, sum(per_rank) / self.ep)
+            if max(per_rank) / mean <= threshold:
+                continue
+            new, moved = h.balanced_placement(counts, self.ep, cur, tolerance)
+            if moved == 0:
+                continue
+            self._move_experts(store, optimizer, L, cur, list(new), El, dist)
+            self.placement_host[L] = list(new)
+            self.placement[L] = torch.tensor(new, dtype=torch.int32, device=self.device)
+            store.expert_placement[L] = list(new)
+            changed += 1
+            moved_total += moved
+        self.moves_done += moved_total
+        return {"layers": changed, "moved": moved_total}
+
+    def _move_experts(self, store, optimizer, L: int, cur, new, El: int, dist) -> None:
+        b = store.buckets.get(f"layer{L}.experts")
+        if b is None:
+            return
+        tensors = [b.master]
+        if b.work is not None and b.work is not b.master:
+            tensors.append(b.work)
+        st = optimizer.state.get(b.name) if hasattr(optimizer, "state") else None
+        for t in (st or {}).values():
+            tensors.append(t)
+        n_master = b.master.numel()
+        sends, recvs = [], []   # (tensor, range) pairs on this rank
+        ops, temps = [], []
+        group = getattr(self.comm.base, "group", None)
+        for e in range(len(cur)):
+            if cur[e] == new[e]:
+                continue
+            src_r, src_s, dst_r, dst_s = cur[e] // El, cur[e] % El, new[e] // El, new[e] % El
+            for sl in b.slots:
+                per = sl.numel // El
+                for t in tensors:
+                    div = n_master // t.numel() if t.numel() < n_master else 1   # fp16 scales: one per 32 elements
+                    a0, a1 = (sl.offset + src_s * per) // div, (sl.offset + (src_s + 1) * per) // div
+                    d0, d1 = (sl.offset + dst_s * per) // div, (sl.offset + (dst_s + 1) * per) // div
+                    if self.rank == src_r and self.rank == dst_r:
+                        temps.append((t, d0, d1, t[a0:a1].clone()))
+                    elif self.rank == src_r:
+                        ops.append(dist.P2POp(dist.isend, t[a0:a1].clone(), dist.get_global_rank(group, dst_r) if group is not None else dst_r, group))
+                    elif self.rank == dst_r:
+                        buf = torch.empty(d1 - d0, dtype=t.dtype, device=t.device)
+                        temps.append((t, d0, d1, buf))
+                        ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(group, src_r) if group is not None else src_r, group))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        for t, d0, d1, buf in temps:   # only now overwrite: a slot's previous occupant has been copied out above
+            t[d0:d1].copy_(buf)
+
     # ------------------------------------------------------------------ balancing
     def dropped_rows(self) -> int:
         """Token copies dropped on this rank in the last step because an expert group overflowed the receive buffer."""
         return int(sum(int(v.item()) for v in self.last_overflow.values()))
 
     def imbalance(self) -> float:
-        """max over layers of (busiest rank's tokens / mean rank tokens) in the last step."""
+        """max over layers of (busiest rank's tokens / mean rank tokens) in the last step (counts are in placed order)."""
         worst = 1.0
         for c in self.last_global_counts.values():
             per_rank = c.view(self.ep, -1).sum(1).float()

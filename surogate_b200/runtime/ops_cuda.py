@@ -344,7 +344,8 @@ def _moe_mixin():
         if ctx.ep is not None:  # expert parallel: the dispatch kernel permutes while it sends; nothing moves here
             from ..parallel.ep import PrePlan
 
-            return x2, PrePlan(ti.reshape(N, K).contiguous(), counts, N, K, E, tuple(x.shape))
+            ti_p, counts_p = ctx.ep.place(ctx.layer, ti.reshape(N, K).contiguous(), counts)  # least-loaded placement: expert id -> (rank, slot)
+            return x2, PrePlan(ti_p, counts_p, N, K, E, tuple(x.shape))
         cap = N * K + E * 128                      # exact upper bound of the padded row count: no host read of the routing
         cap = (cap + 127) // 128 * 128
         offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)

@@ -140,6 +140,7 @@ class ParamStore:
         self.last_micro_step = True
         self.grads_enabled = True
         self.post_gather: Optional[Callable[[Bucket], None]] = None
+        self.expert_placement: Dict[int, List[int]] = {}  # layer -> placed index of every global expert (expert parallelism with re-placement)
         self.fp8_gather = False  # quantise-on-gather (ZeRO-3 + FP8 recipe + peer-memory kernels)
         self.fp8_roles: Dict[str, str] = {}
         self._build()
@@ -290,7 +291,7 @@ class ParamStore:
         name = self.resolve(name)
         b, s = self.where[name]
         if b.expert:
-            return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
+            return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
         if getattr(b, "qstate", None) is not None:
             return self._dequantized(b)[s.offset:s.offset + s.numel].reshape(s.shape)
         if not self.sharded:
@@ -302,18 +303,22 @@ class ParamStore:
     def _master_on_device(self, b: Bucket) -> torch.Tensor:
         return b.master if b.master.device == self.device else b.master.to(self.device)
 
-    def _gather_experts(self, local: torch.Tensor) -> torch.Tensor:
-        """[E/ep, ...] on every rank -> [E, ...] (ranks own consecutive expert ranges)."""
+    def _gather_experts(self, local: torch.Tensor, layer: Optional[int] = None) -> torch.Tensor:
+        """[E/ep, ...] on every rank -> [E, ...] in global expert order (ranks hold E/ep slots each; which expert sits in
+        which slot is the identity unless experts were re-placed for load balance)."""
         local = local.contiguous()
         full = torch.empty((self.ep * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
         getattr(self.comm, "base", self.comm).all_gather(local.reshape(-1), full.reshape(-1))
+        place = self.expert_placement.get(layer) if layer is not None else None
+        if place is not None:
+            full = full.index_select(0, torch.tensor(place, dtype=torch.long, device=full.device))
         return full
 
     def named_full_tensors(self) -> Iterable[Tuple[str, torch.Tensor]]:
         for b in self.buckets.values():
             if b.expert:
                 for s in b.slots:
-                    yield s.name, self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape))
+                    yield s.name, self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
                 continue
             if getattr(b, "qstate", None) is not None:
                 full = self._dequantized(b)
@@ -686,7 +691,7 @@ class ParamStore:
         if g is None:
             return None
         if b.expert:
-            return self._gather_experts(g[s.offset:s.offset + s.numel].view(s.shape))
+            return self._gather_experts(g[s.offset:s.offset + s.numel].view(s.shape), b.layer)
         if g.numel() != b.numel:
             full = torch.empty(b.numel, dtype=g.dtype, device=self.device)
             self.comm.all_gather(g.contiguous(), full)

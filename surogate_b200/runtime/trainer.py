@@ -56,6 +56,8 @@ class TrainerConfig:
     collectives: str = "auto"  # auto | nccl | symm
     ep_size: int = 1
     ep_capacity_factor: float = 1.5
+    ep_load_balance_threshold: float = 1.3   # re-place experts when a layer's busiest rank exceeds this multiple of the mean load
+    ep_plan_refresh_interval: int = 16       # steps between placement refreshes (0 = never)
     lora: Optional[Dict[str, Any]] = None
     fp8_amax_history: int = 16
     skip_quant_first_layers: int = 0
@@ -351,6 +353,9 @@ class Trainer:
             self.lora.optimizer_step(self._hp, host)
         self.store.release_grads()
         self.store.sync_work_from_master()
+        if self.ep is not None and self.cfg.ep_plan_refresh_interval > 0 and self.step_index % self.cfg.ep_plan_refresh_interval == 0 \
+                and self.cfg.optimizer in ("adamw", "adamw_8bit") and not self.cfg.cpu_training:
+            self.last_rebalance = self.ep.rebalance(self.store, self.optimizer, self.cfg.ep_load_balance_threshold)
         self.recipe.on_weights_updated(self.store)
         self.recipe.end_step()
         return norm

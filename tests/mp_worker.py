@@ -31,7 +31,8 @@ def main():
                         recipe=a.get("recipe", "bf16"), optimizer=a.get("optimizer", "adamw"), learning_rate=1e-3, zero_level=a.get("zero", 1),
                         collectives=a.get("collectives", "auto"), keep_gathered=a.get("keep_gathered", True), ep_size=a.get("ep", 1),
                         lora=a.get("lora"), offload_master=a.get("offload_master", False), offload_optimizer=a.get("offload_optimizer", False),
-                        cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5))
+                        cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5),
+                        ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
     tr = Trainer(cfg, device=dev, comm=comm)
     tr.init_weights(seed=0)
     rng = np.random.default_rng(7)
@@ -53,7 +54,9 @@ def main():
                                       "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),
                                       "fp8_gather": bool(tr.store.fp8_gather), "h2d_weight_bytes": int(tr.store.h2d_bytes),
                                       "stage_slots": len(tr.store.stage_slots),
-                                      "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0, **extra}), flush=True)
+                                      "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0,
+                                      "ep_moves": tr.ep.moves_done if tr.ep is not None else 0,
+                                      "ep_imbalance": tr.ep.imbalance() if tr.ep is not None else 1.0, **extra}), flush=True)
     if info.world > 1:
         import torch.distributed as dist
 

@@ -83,3 +83,14 @@ def test_expert_parallel_overflow_drops_tokens_instead_of_overrunning():
     r = run_worker(2, dict(ARGS, global_batch=8, seq_len=256, model=MOE, ep=2, zero=1, collectives="symm", ep_capacity_factor=0.05), port=29761)
     assert r["ep_dropped"] > 0
     assert all(l == l and abs(l) < 50 for l in r["losses"]), r["losses"]
+
+
+def test_expert_replacement_keeps_the_trajectory():
+    """Least-loaded placement: experts (weights + optimizer moments) move between ranks every 2 steps with a threshold that
+    always triggers; the run must still reproduce the 1-GPU trajectory, because only WHERE an expert lives changes."""
+    args = dict(ARGS, model=MOE, steps=6, optimizer="adamw_8bit")
+    one = run_worker(1, dict(args))
+    two = run_worker(2, dict(args, ep=2, zero=1, collectives="symm", ep_refresh=2, ep_threshold=1.0), port=29771)
+    assert two["ep_moves"] > 0
+    for a, b in zip(two["losses"], one["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (two["losses"], one["losses"])
