@@ -169,7 +169,8 @@ def main():
                         backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention,
                         lora=spec.get("lora"), offload_master=bool(spec.get("offload")) and not args.no_offload,
                         offload_optimizer=bool(spec.get("offload")) and not args.no_offload, keep_gathered=not spec.get("offload"),
-                        ep_capacity_factor=float(max(1, ep)))  # room for every routed row even if all tokens pick one rank: nothing is dropped
+                        ep_capacity_factor=float(max(1, ep)),  # room for every routed row even if all tokens pick one rank: nothing is dropped
+                        ep_plan_refresh_interval=2)            # least-loaded placement settles during warm-up; later refreshes are inside the timed region
     if spec.get("recompute"):
         cfg.recompute = True
     tr = Trainer(cfg, device=dev, comm=comm)
@@ -269,7 +270,8 @@ def main():
                        "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events on the launching stream, barrier+synchronize on both sides, max over ranks"},
             "clocks": clocks, "gpu_launches": int(launches),
-            **({"ep_dropped_rows_rank0": tr.ep.dropped_rows(), "ep_rank_imbalance": round(tr.ep.imbalance(), 3)} if tr.ep is not None else {}),
+            **({"ep_dropped_rows_rank0": tr.ep.dropped_rows(), "ep_rank_imbalance": round(tr.ep.imbalance(), 3), "ep_experts_moved": tr.ep.moves_done}
+               if tr.ep is not None else {}),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
         }
         if e2e:
