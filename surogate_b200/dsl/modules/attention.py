@@ -24,24 +24,25 @@ class AttentionConfig:
 
 class GenericGQAttention(Module):
     def __init__(self, d_model: int, num_query_heads: int, num_kv_heads: int, head_size: int, max_seq: int = 0,
-                 config: AttentionConfig | None = None, prefix: str = "model.layers.{L}.self_attn"):
+                 config: AttentionConfig | None = None, prefix: str = "model.layers.{L}.self_attn", names: dict | None = None):
         super().__init__()
         self.cfg = config or AttentionConfig()
         self.Hq, self.Hkv, self.D = num_query_heads, num_kv_heads, head_size
         qd, kd = num_query_heads * head_size, num_kv_heads * head_size
         a = prefix
+        n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm", **(names or {})}  # checkpoint leaf names
         self.declare_param(
             "qkv_weight", (qd + 2 * kd, d_model), quantizable=True,
-            hf=hf.fuse([f"{a}.q_proj.weight", f"{a}.k_proj.weight", f"{a}.v_proj.weight"], sizes=[qd, kd, kd]),
+            hf=hf.fuse([f"{a}.{n['q']}.weight", f"{a}.{n['k']}.weight", f"{a}.{n['v']}.weight"], sizes=[qd, kd, kd]),
             lora_targets=[("q_proj", 0, qd), ("k_proj", qd, kd), ("v_proj", qd + kd, kd)])
         if self.cfg.qkv_bias:
             self.declare_param("qkv_bias", (qd + 2 * kd,), init="zeros", decay=False,
-                               hf=hf.fuse([f"{a}.q_proj.bias", f"{a}.k_proj.bias", f"{a}.v_proj.bias"], sizes=[qd, kd, kd]))
-        self.declare_param("out_weight", (d_model, qd), quantizable=True, hf=hf.direct(f"{a}.o_proj.weight"),
+                               hf=hf.fuse([f"{a}.{n['q']}.bias", f"{a}.{n['k']}.bias", f"{a}.{n['v']}.bias"], sizes=[qd, kd, kd]))
+        self.declare_param("out_weight", (d_model, qd), quantizable=True, hf=hf.direct(f"{a}.{n['o']}.weight"),
                            lora_targets=[("o_proj", 0, d_model)])
         if self.cfg.qk_norm:
-            self.declare_param("q_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.q_norm.weight"))
-            self.declare_param("k_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.k_norm.weight"))
+            self.declare_param("q_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.{n['q_norm']}.weight"))
+            self.declare_param("k_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.{n['k_norm']}.weight"))
 
     def forward(self, x, position_ids):
         c = self.cfg

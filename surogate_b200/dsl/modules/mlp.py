@@ -17,14 +17,16 @@ class MLPConfig:
 
 
 class GenericMLP(Module):
-    def __init__(self, d_model: int, d_ff: int, config: MLPConfig | None = None, prefix: str = "model.layers.{L}.mlp"):
+    def __init__(self, d_model: int, d_ff: int, config: MLPConfig | None = None, prefix: str = "model.layers.{L}.mlp",
+                 names: tuple = ("up_proj", "gate_proj", "down_proj")):
         super().__init__()
         self.cfg = config or MLPConfig()
         m = prefix
+        up_n, gate_n, down_n = names  # checkpoint leaf names of the up / gate / down projections
         self.declare_param("up_weight", (2 * d_ff, d_model), quantizable=True,
-                           hf=hf.fuse([f"{m}.up_proj.weight", f"{m}.gate_proj.weight"], sizes=[d_ff, d_ff]),
+                           hf=hf.fuse([f"{m}.{up_n}.weight", f"{m}.{gate_n}.weight"], sizes=[d_ff, d_ff]),
                            lora_targets=[("up_proj", 0, d_ff), ("gate_proj", d_ff, d_ff)])
-        self.declare_param("down_weight", (d_model, d_ff), quantizable=True, hf=hf.direct(f"{m}.down_proj.weight"),
+        self.declare_param("down_weight", (d_model, d_ff), quantizable=True, hf=hf.direct(f"{m}.{down_n}.weight"),
                            lora_targets=[("down_proj", 0, d_model)])
 
     def forward(self, x):

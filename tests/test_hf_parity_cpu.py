@@ -16,7 +16,7 @@ COMMON = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention
 
 
 def _cases():
-    from transformers import GptOssConfig, LlamaConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
+    from transformers import GptOssConfig, Lfm2Config, LlamaConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
 
     yield "qwen3", Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=True)
     yield "qwen3-untied", Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=False)
@@ -25,6 +25,9 @@ def _cases():
     yield "mistral", MistralConfig(**COMMON, head_dim=16, rope_theta=10000.0, sliding_window=None, tie_word_embeddings=False)
     yield "qwen3-moe", Qwen3MoeConfig(**COMMON, head_dim=16, rope_theta=1e6, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                       norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False)
+    yield "lfm2", Lfm2Config(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, intermediate_size=96,
+                             conv_L_cache=3, block_auto_adjust_ff_dim=False, layer_types=["conv", "full_attention", "conv", "full_attention"],
+                             max_position_embeddings=256, tie_word_embeddings=True)
     yield "gpt-oss", GptOssConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                                   intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8, max_position_embeddings=256,
                                   rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
