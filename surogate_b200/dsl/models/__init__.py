@@ -3,5 +3,6 @@ from .dense import Qwen3Model, Qwen2Model, LlamaModel, MistralModel
 from .moe import Qwen3MoEModel
 from .gpt_oss import GptOssModel
 from .lfm2 import Lfm2Model
+from .nemotron_h import NemotronHModel
 
-__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model"]
+__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model", "NemotronHModel"]

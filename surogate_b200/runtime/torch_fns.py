@@ -220,3 +220,36 @@ def gated_delta_rule(q, k, v, g, beta, *, scale: Optional[float] = None):
 @register("gated_delta_rule")
 def gated_delta_rule_op(q, k, v, g, beta, *, scale: Optional[float] = None):
     return gated_delta_rule(q, k, v, g, beta, scale=scale).to(v.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- Nemotron-H style MoE
+@register("moe_sigmoid_relu2")
+def moe_sigmoid_relu2(x, gate_w, score_bias, up, down, shared_up, shared_down, *, top_k: int, n_group: int = 1, topk_group: int = 1,
+                      norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0):
+    """Sigmoid router with a selection-only score bias and group-limited top-k; non-gated ReLU^2 experts (up [E, M, C],
+    down [E, C, M]) plus an always-on shared ReLU^2 expert."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    E = gate_w.shape[0]
+    scores = torch.sigmoid(F.linear(x2.float(), gate_w.float()))
+    choice = scores + score_bias.float()
+    if n_group > 1:
+        gs = choice.view(-1, n_group, E // n_group).topk(2, dim=-1)[0].sum(-1)
+        gi = torch.topk(gs, k=topk_group, dim=-1, sorted=False)[1]
+        gmask = torch.zeros_like(gs).scatter_(1, gi, 1.0)
+        mask = gmask.unsqueeze(-1).expand(-1, n_group, E // n_group).reshape(-1, E).bool()
+        choice = choice.masked_fill(~mask, 0.0)
+    top_i = torch.topk(choice.detach(), k=top_k, dim=-1, sorted=False)[1]
+    w = scores.gather(1, top_i)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    w = w * routed_scaling_factor
+    out = torch.zeros_like(x2, dtype=torch.float32)
+    for e in range(E):
+        tok, slot = torch.where(top_i == e)
+        if tok.numel() == 0:
+            continue
+        h = F.relu(F.linear(x2[tok].float(), up[e].float())).square()
+        out.index_add_(0, tok, F.linear(h, down[e].float()) * w[tok, slot, None])
+    shared = F.linear(F.relu(F.linear(x2.float(), shared_up.float())).square(), shared_down.float())
+    return (out + shared).reshape(shape).to(x.dtype)
