@@ -4,5 +4,6 @@ from .moe import Qwen3MoEModel
 from .gpt_oss import GptOssModel
 from .lfm2 import Lfm2Model
 from .nemotron_h import NemotronHModel
+from .qwen3_5 import Qwen35Model
 
-__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model", "NemotronHModel"]
+__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model", "NemotronHModel", "Qwen35Model"]

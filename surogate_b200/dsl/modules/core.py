@@ -35,10 +35,13 @@ class LMHead(Module):
 class RMSNorm(Module):
     """One-argument form: y = rmsnorm(x).  Two-argument form: residual += x ; y = rmsnorm(residual) in one op."""
 
-    def __init__(self, d_model: int, eps: float = 1e-6, hf_name: str | None = None, out_name: str = "ln", res_name: str = "res"):
+    def __init__(self, d_model: int, eps: float = 1e-6, hf_name: str | None = None, out_name: str = "ln", res_name: str = "res",
+                 zero_centered: bool = False):
         super().__init__()
         self.eps, self.out_name, self.res_name = eps, out_name, res_name
-        self.declare_param("weight", (d_model,), init="ones", decay=False, hf=hf.direct(hf_name) if hf_name else None)
+        # zero_centered: the checkpoint stores w - 1 (y = x_hat * (1 + w)); one is added on load and removed on export
+        mapping = (hf.transform(hf_name, "plus_one") if zero_centered else hf.direct(hf_name)) if hf_name else None
+        self.declare_param("weight", (d_model,), init="ones", decay=False, hf=mapping)
 
     def forward(self, a, b=None):
         if b is None:

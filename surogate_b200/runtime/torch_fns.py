@@ -253,3 +253,73 @@ def moe_sigmoid_relu2(x, gate_w, score_bias, up, down, shared_up, shared_down, *
         out.index_add_(0, tok, F.linear(h, down[e].float()) * w[tok, slot, None])
     shared = F.linear(F.relu(F.linear(x2.float(), shared_up.float())).square(), shared_down.float())
     return (out + shared).reshape(shape).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- Qwen3.5 / Qwen3-Next mixers
+def _rms(x, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+@register("qwen35_gated_attention")
+def qwen35_gated_attention(x, q_w, k_w, v_w, o_w, qn_w, kn_w, pos, *, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, rope_theta: float,
+                           rotary_dim: int):
+    """Attention whose query projection also yields a per-channel output gate: q_proj -> [q | gate] per head, zero-centred
+    QK RMSNorm, partial rotary embedding, causal GQA, output multiplied by sigmoid(gate) before o_proj."""
+    B, T, _ = x.shape
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    qg = F.linear(x, q_w).float().view(B, T, Hq, 2 * D)
+    q, gate = qg[..., :D], qg[..., D:].reshape(B, T, Hq * D)
+    k = F.linear(x, k_w).float().view(B, T, Hkv, D)
+    v = F.linear(x, v_w).float().view(B, T, Hkv, D)
+    q = _rms(q, eps) * (1.0 + qn_w.float())
+    k = _rms(k, eps) * (1.0 + kn_w.float())
+    half = rotary_dim // 2
+    inv = rope_theta ** (-torch.arange(0, half, device=x.device, dtype=torch.float32) * 2.0 / rotary_dim)
+    ang = pos.float().unsqueeze(-1) * inv
+    cos, sin = ang.cos().unsqueeze(2), ang.sin().unsqueeze(2)
+
+    def rope(t):
+        a, b, rest = t[..., :half], t[..., half:rotary_dim], t[..., rotary_dim:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], dim=-1)
+
+    q, k = rope(q), rope(k)
+    G = Hq // Hkv
+    qf = q.permute(0, 2, 1, 3)
+    kf = k.permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    vf = v.permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    s = qf @ kf.transpose(-1, -2) * (D ** -0.5)
+    i = torch.arange(T, device=x.device)
+    s = s.masked_fill(~(i[:, None] >= i[None, :]), float("-inf"))
+    o = (torch.softmax(s, dim=-1) @ vf).permute(0, 2, 1, 3).reshape(B, T, Hq * D)
+    return F.linear((o * torch.sigmoid(gate)).to(x.dtype), o_w)
+
+
+@register("qwen35_gated_delta_net")
+def qwen35_gated_delta_net(x, qkv_w, z_w, b_w, a_w, conv_w, dt_bias, A_log, norm_w, out_w, *, num_k_heads: int, num_v_heads: int, head_k_dim: int,
+                           head_v_dim: int, conv_kernel: int, eps: float):
+    """Gated DeltaNet mixer: qkv projection -> causal depth-wise conv + SiLU -> L2-normalised q, k; per-head decay
+    g = -exp(A_log) softplus(a + dt_bias) and write strength beta = sigmoid(b); gated delta rule; RMSNorm gated by silu(z)."""
+    B, T, _ = x.shape
+    Hk, Hv, Dk, Dv = num_k_heads, num_v_heads, head_k_dim, head_v_dim
+    key_dim, value_dim = Hk * Dk, Hv * Dv
+    mixed = F.linear(x, qkv_w).float().transpose(1, 2)
+    mixed = F.silu(F.conv1d(F.pad(mixed, (conv_kernel - 1, 0)), conv_w.float().reshape(-1, 1, conv_kernel), None, groups=mixed.shape[1])).transpose(1, 2)
+    q, k, v = torch.split(mixed, [key_dim, key_dim, value_dim], dim=-1)
+    q, k, v = q.reshape(B, T, Hk, Dk), k.reshape(B, T, Hk, Dk), v.reshape(B, T, Hv, Dv)
+    beta = torch.sigmoid(F.linear(x, b_w).float())
+    g = -torch.exp(A_log.float()) * F.softplus(F.linear(x, a_w).float() + dt_bias.float())
+    if Hv // Hk > 1:
+        q, k = q.repeat_interleave(Hv // Hk, dim=2), k.repeat_interleave(Hv // Hk, dim=2)
+    l2 = lambda t: t * torch.rsqrt((t * t).sum(-1, keepdim=True) + 1e-6)  # noqa: E731
+    q, k = l2(q) * (Dk ** -0.5), l2(k)
+    S = q.new_zeros(B, Hv, Dk, Dv)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[:, t])[..., None, None]
+        kv = torch.einsum("bhk,bhkv->bhv", k[:, t], S)
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, t], (v[:, t] - kv) * beta[:, t][..., None])
+        outs.append(torch.einsum("bhk,bhkv->bhv", q[:, t], S))
+    o = torch.stack(outs, dim=1).reshape(-1, Dv)
+    z = F.linear(x, z_w).float().reshape(-1, Dv)
+    o = (norm_w.float() * _rms(o, eps)) * F.silu(z)
+    return F.linear(o.reshape(B, T, value_dim).to(x.dtype), out_w)

@@ -16,7 +16,7 @@ COMMON = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention
 
 
 def _cases():
-    from transformers import GptOssConfig, Lfm2Config, LlamaConfig, NemotronHConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
+    from transformers import GptOssConfig, Lfm2Config, LlamaConfig, NemotronHConfig, Qwen3_5TextConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
 
     yield "qwen3", Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=True)
     yield "qwen3-untied", Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=False)
@@ -32,6 +32,9 @@ def _cases():
                                         num_key_value_heads=2, head_dim=16, intermediate_size=96, ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=16,
                                         n_groups=2, conv_kernel=4, chunk_size=8, max_position_embeddings=128, n_routed_experts=4, num_experts_per_tok=2,
                                         moe_intermediate_size=32, moe_shared_expert_intermediate_size=48, tie_word_embeddings=False)
+    yield "qwen3.5", Qwen3_5TextConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                       intermediate_size=96, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8,
+                                       linear_conv_kernel_dim=4, max_position_embeddings=256, tie_word_embeddings=False)
     yield "gpt-oss", GptOssConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                                   intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8, max_position_embeddings=256,
                                   rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
