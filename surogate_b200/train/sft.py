@@ -6,6 +6,7 @@ train/trainer.py (run_training_loop :1160-1553).
 """
 from __future__ import annotations
 
+import contextlib
 import glob
 import json
 import math
@@ -164,15 +165,50 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
         moe_d_ff=hf_cfg.get("moe_intermediate_size", hf_cfg.get("moe_d_ff", 0)), num_experts=hf_cfg.get("num_experts", 0),
         lora_rank=cfg.lora_rank if cfg.lora else 0, recompute=cfg.recompute)
     dev_name = torch.cuda.get_device_name(device) if device.type == "cuda" else "cpu"
+    losses: List[float] = []
+    norms: List[float] = []
+    from ..parallel.watchdog import RemoteRankFailed, install as install_watchdog
+
+    # failure detection: heartbeats + root-cause notes between ranks; a failed or silent peer ends this rank at its next step
+    watchdog = install_watchdog(info.rank, info.world) if info.world > 1 and os.environ.get("SUROGATE_WATCHDOG", "1") != "0" else None
+    try:
+        last = _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info, hf_cfg, device, start_step, max_steps, steps_per_epoch, warmup,
+                          flops, dev_name, kd_feed, distill, reporters, losses, norms)
+    except BaseException as e:  # noqa: BLE001
+        if watchdog is not None and not isinstance(e, RemoteRankFailed):
+            watchdog.report_failure(e)  # the other ranks learn why the job ended
+        raise
+    finally:
+        if watchdog is not None:
+            watchdog.stop()
+    # final artefacts: adapter (LoRA) or full model in HF format
+    if trainer.lora is not None:
+        trainer.export_adapter(os.path.join(cfg.output_dir, "adapter"), base_model=cfg.model if isinstance(cfg.model, str) else "")
+        if cfg.merge_adapter:
+            trainer.lora.merge_into(trainer.store)
+            trainer.export_model(os.path.join(cfg.output_dir, "merged"), hf_cfg)
+    else:
+        trainer.export_model(cfg.output_dir, hf_cfg)
+    for rep in reporters:
+        rep.finish()
+    logger.close()
+    return {"final": last, "losses": losses, "norms": norms, "steps": len(losses)}
+
+
+def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info, hf_cfg, device, start_step, max_steps, steps_per_epoch, warmup, flops, dev_name,
+               kd_feed, distill, reporters, losses, norms) -> Dict[str, Any]:
+    """The optimizer-step loop of a run: data, step, monitors, logging, evaluation, checkpoints.  Returns the last step's result."""
+    B, GA, T = cfg.per_device_train_batch_size, cfg.gradient_accumulation_steps, cfg.sequence_len
     guard = LossGuard(enabled=cfg.auto_lr_reduction)
     phase_det, grads, moe_mon, advisor = PhaseDetector(warmup), GradientTracker(), MoEMonitor(), TrainingAdvisor()
     stopper = EarlyStopping(cfg.early_stop)
     step_tokens = B * GA * T * info.world
-    losses: List[float] = []
-    norms: List[float] = []
-    last = {}
+    last: Dict[str, Any] = {}
     for step in range(start_step, max_steps):
         t0 = time.perf_counter()
+        if watchdog is not None:
+            watchdog.tick(step)
+            watchdog.check()  # a failed / silent peer ends the run here, before this step's first collective
         x, y, p = loader.next_batch()
         if cfg.loss_scale == "all":
             pass  # every token is a target (pre-training); masks in the shard are already all ones
@@ -228,18 +264,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
         if stopper.should_stop(out["loss"], phase):
             logger.message("[early-stop] stopping")
             break
-    # final artefacts: adapter (LoRA) or full model in HF format
-    if trainer.lora is not None:
-        trainer.export_adapter(os.path.join(cfg.output_dir, "adapter"), base_model=cfg.model if isinstance(cfg.model, str) else "")
-        if cfg.merge_adapter:
-            trainer.lora.merge_into(trainer.store)
-            trainer.export_model(os.path.join(cfg.output_dir, "merged"), hf_cfg)
-    else:
-        trainer.export_model(cfg.output_dir, hf_cfg)
-    for rep in reporters:
-        rep.finish()
-    logger.close()
-    return {"final": last, "losses": losses, "norms": norms, "steps": len(losses)}
+    return last
 
 
 def sft_main(config_path: str, **overrides):

@@ -1,5 +1,6 @@
 """Numerics of each hand-written sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
 import math
+import time
 
 import pytest
 import torch
@@ -356,3 +357,23 @@ def test_cross_entropy_row_weights_and_topk_distillation():
     err = (work.float() - ref.grad).abs().max().item()
     assert err < 2e-2 * ref.grad.abs().max().item() + 1e-3, err
     assert work[5].abs().sum() == 0
+
+
+def test_barrier_wait_runs_out_and_reports_instead_of_hanging():
+    """A peer that never arrives: the barrier kernel gives up after its cycle budget, raises the error word and returns; the
+    context stays usable.  (Two local signal pads stand in for two ranks; nothing ever writes the absent rank's arrival.)"""
+    from surogate_b200.ops import check_device_errors, ext
+
+    e = ext()
+    check_device_errors()
+    pads = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    err = e.error_flag_tensor()
+    t0 = time.time()
+    e.symm_barrier([p.data_ptr() for p in pads], 0, 1, 0, err, 0.05)   # I am rank 0 of 2; rank 1 never signals
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    with pytest.raises(RuntimeError, match="wait timed out|error flag"):
+        check_device_errors()
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0  # the context survived
+    check_device_errors()
