@@ -216,6 +216,14 @@ def _swiglu(b, op, dy):
     return {x: g}
 
 
+@register_autodiff("tiled_mlp")
+def _tiled_mlp(b, op, dy):
+    x, up_w, down_w = op.inputs
+    g = b.new_grad(x)
+    b.emit("tiled_mlp_backward", [dy[0], b.fwd_tensor(x), up_w, down_w], [g, b.param_grad(up_w), b.param_grad(down_w)], **op.attrs)
+    return {x: g}
+
+
 @register_autodiff("silu")
 def _silu(b, op, dy):
     x = op.inputs[0]

@@ -19,7 +19,7 @@ class DenseBlock(Block):
 
     def __init__(self, d_model: int, num_query_heads: int, num_kv_heads: int, head_size: int, d_ff: int, max_seq: int = 0,
                  eps: float = 1e-6, use_qkv_bias: bool = False, use_qk_norm: bool = False, rope_theta: float = 1e6,
-                 sliding_window: int = 0, rotary_dim: int | None = None):
+                 sliding_window: int = 0, rotary_dim: int | None = None, mlp_tile_rows: int = 0):
         super().__init__()
         self.attn_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.input_layernorm.weight")
         self.self_attn = GenericGQAttention(
@@ -27,7 +27,7 @@ class DenseBlock(Block):
             config=AttentionConfig(qk_norm=use_qk_norm, qkv_bias=use_qkv_bias, eps=eps, rope_theta=rope_theta,
                                    sliding_window=sliding_window, rotary_dim=rotary_dim))
         self.mlp_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.post_attention_layernorm.weight")
-        self.mlp = GenericMLP(d_model, d_ff, config=MLPConfig())
+        self.mlp = GenericMLP(d_model, d_ff, config=MLPConfig(tile_rows=mlp_tile_rows))
 
     def forward(self, x, residual, position_ids):
         residual, h = self.attn_norm(residual, x)

@@ -97,6 +97,13 @@ def swiglu(x: Proxy, name: str = "swiglu") -> Proxy:
     return _t().emit("swiglu", [x], [(name, x.shape[:-1] + (M2 // 2,), "act")])[0]
 
 
+def tiled_mlp(x: Proxy, up_w: Proxy, down_w: Proxy, tile_rows: int, name: str = "mlp_down") -> Proxy:
+    """Gated MLP evaluated over row tiles: y = down(swiglu(up(x))) without ever holding the [tokens, 2*d_ff] intermediate for more
+    than ``tile_rows`` tokens; the backward recomputes each tile.  For very long sequences, where that intermediate dominates
+    activation memory."""
+    return _t().emit("tiled_mlp", [x, up_w, down_w], [(name, x.shape[:-1] + (down_w.shape[0],), "act")], tile_rows=int(tile_rows))[0]
+
+
 def silu(x: Proxy, name: str = "silu") -> Proxy:
     return _t().emit("silu", [x], [(name, x.shape, x.dtype)])[0]
 

@@ -14,6 +14,7 @@ from ..nn import Module
 @dataclass
 class MLPConfig:
     activation: str = "swiglu"
+    tile_rows: int = 0  # > 0: evaluate the MLP over row tiles of this many tokens and recompute each tile in backward (long context)
 
 
 class GenericMLP(Module):
@@ -30,6 +31,8 @@ class GenericMLP(Module):
                            lora_targets=[("down_proj", 0, d_model)])
 
     def forward(self, x):
+        if self.cfg.tile_rows > 0:
+            return F.tiled_mlp(x, self.p("up_weight"), self.p("down_weight"), self.cfg.tile_rows)
         up = F.matmul(x, self.p("up_weight"), name="mlp_up", role="mlp_up")
         act = F.swiglu(up)
         return F.matmul(act, self.p("down_weight"), name="mlp_down", role="mlp_down")

@@ -170,6 +170,41 @@ class CudaOps(RefOps):
     def swiglu_backward(self, ctx, op, dy, x):
         return (self.ext.swiglu_bwd(dy.contiguous(), x),)
 
+    # ------------------------------------------------------------------ tiled MLP (long context): same tiles on the tcgen05 GEMM + SwiGLU kernels
+    def tiled_mlp(self, ctx, op, x, up_w, down_w):
+        if x.dtype != torch.bfloat16 or up_w.dtype != torch.bfloat16:
+            return super().tiled_mlp(ctx, op, x, up_w, down_w)
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        rows = max(128, int(op.attrs["tile_rows"]) // 128 * 128)
+        y = torch.empty(x2.shape[0], down_w.shape[0], dtype=x.dtype, device=x.device)
+        for s in range(0, x2.shape[0], rows):
+            a = self.ext.swiglu_fwd(gemm(x2[s:s + rows], up_w), True, None, None, False)[0]
+            gemm(a, down_w, y[s:s + rows])
+        return (y.reshape(*x.shape[:-1], down_w.shape[0]),)
+
+    def tiled_mlp_backward(self, ctx, op, dy, x, up_w, down_w):
+        if x.dtype != torch.bfloat16 or up_w.dtype != torch.bfloat16:
+            return super().tiled_mlp_backward(ctx, op, dy, x, up_w, down_w)
+        C = x.shape[-1]
+        x2, dy2 = x.reshape(-1, C), dy.reshape(-1, dy.shape[-1]).contiguous()
+        rows = max(128, int(op.attrs["tile_rows"]) // 128 * 128)
+        dx = torch.empty_like(x2)
+        g_up, acc_up = ctx.grad_target(op.outputs[1])
+        g_down, acc_down = ctx.grad_target(op.outputs[2])
+        for s in range(0, x2.shape[0], rows):
+            xc, dyc = x2[s:s + rows], dy2[s:s + rows]
+            u = gemm(xc, up_w)
+            a = self.ext.swiglu_fwd(u, True, None, None, False)[0]
+            da = gemm(dyc, down_w, b_mn=True)
+            du = self.ext.swiglu_bwd(da, u)
+            gemm(du, up_w, dx[s:s + rows], b_mn=True)
+            if g_down is not None:
+                gemm(dyc, a, g_down, a_mn=True, b_mn=True, accumulate=acc_down or s > 0)
+            if g_up is not None:
+                gemm(du, xc, g_up, a_mn=True, b_mn=True, accumulate=acc_up or s > 0)
+        return dx.reshape(x.shape), None, None
+
     # ------------------------------------------------------------------ attention
     def flash_attention(self, ctx, op, qkv):
         from ..ops import attention as att_ops

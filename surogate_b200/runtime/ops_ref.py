@@ -351,6 +351,40 @@ class RefOps:
         up, gate = x[..., :M].float(), x[..., M:].float()
         return ((TF.silu(gate) * up).to(x.dtype),)
 
+    # ------------------------------------------------------------------ tiled MLP (long context)
+    def _mlp_tile_fwd(self, xc, up_w, down_w):
+        u = TF.linear(xc, up_w.to(xc.dtype))
+        a = self.swiglu(None, None, u)[0]
+        return u, a, TF.linear(a, down_w.to(xc.dtype))
+
+    def tiled_mlp(self, ctx, op, x, up_w, down_w):
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        rows = max(1, int(op.attrs["tile_rows"]))
+        y = torch.empty(x2.shape[0], down_w.shape[0], dtype=x.dtype, device=x.device)
+        for s in range(0, x2.shape[0], rows):
+            y[s:s + rows] = self._mlp_tile_fwd(x2[s:s + rows], up_w, down_w)[2]
+        return (y.reshape(*x.shape[:-1], down_w.shape[0]),)
+
+    def tiled_mlp_backward(self, ctx, op, dy, x, up_w, down_w):
+        C = x.shape[-1]
+        x2, dy2 = x.reshape(-1, C), dy.reshape(-1, dy.shape[-1])
+        rows = max(1, int(op.attrs["tile_rows"]))
+        dx = torch.empty_like(x2)
+        g_up, acc_up = ctx.grad_target(op.outputs[1])
+        g_down, acc_down = ctx.grad_target(op.outputs[2])
+        for s in range(0, x2.shape[0], rows):
+            xc, dyc = x2[s:s + rows], dy2[s:s + rows]
+            u, a, _ = self._mlp_tile_fwd(xc, up_w, down_w)          # recompute this tile
+            da = dyc @ down_w.to(dyc.dtype)
+            du = self.swiglu_backward(None, None, da, u)[0]
+            dx[s:s + rows] = du @ up_w.to(du.dtype)
+            for tgt, acc, lhs, rhs in ((g_down, acc_down, dyc, a), (g_up, acc_up, du, xc)):
+                if tgt is not None:
+                    g = (lhs.t().float() @ rhs.float()).to(tgt.dtype)
+                    tgt.add_(g) if (acc or s > 0) else tgt.copy_(g)
+        return dx.reshape(x.shape), None, None
+
     def swiglu_backward(self, ctx, op, dy, x):
         M = x.shape[-1] // 2
         up, gate = x[..., :M].float(), x[..., M:].float()

@@ -68,6 +68,7 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    long_context: bool = False  # tiled MLP: tile = min(tokens, hidden size) rows, recomputed per tile in backward (dense models)
     cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
@@ -96,6 +97,9 @@ class Trainer:
         self.world, self.rank = self.comm.world, self.comm.rank
         on_gpu = self.device.type == "cuda"
         extra = {"ep_size": cfg.ep_size} if cfg.ep_size > 1 else {}
+        if cfg.long_context:
+            hidden = cfg.model.get("hidden_size", cfg.model.get("d_model", 4096))
+            extra["mlp_tile_rows"] = max(128, min(cfg.batch_size * cfg.seq_len, hidden))
         self.model = build_model(cfg.model, **extra)
         self.cm: CompiledModel = compile_model(self.model)
         pd = _DT[cfg.param_dtype] if on_gpu else torch.float32

@@ -81,3 +81,8 @@ def test_qwen3_moe_tiny():
     m = Qwen3MoEModel(vocab_size=512, d_model=64, n_layers=2, num_query_heads=4, num_kv_heads=2, head_size=16, moe_d_ff=32,
                       num_experts=8, num_experts_per_tok=2, aux_loss_coef=1e-2, tie_word_embeddings=False)
     _run(m, dict(V=512, n_layers=2, Hq=4, Hkv=2, D=16, eps=1e-6, theta=1e6, E=8, K=2, aux_coef=1e-2))
+
+
+def test_tiled_mlp_matches_autograd_and_the_untiled_model():
+    """long_context: the MLP runs over row tiles and recomputes them in backward; results equal the ordinary path."""
+    _run(Qwen3Model(**TINY, mlp_tile_rows=48), TINY_CFG)

@@ -137,3 +137,14 @@ def test_lora_gpu_loss_decreases_and_base_is_frozen():
     assert losses[-1] < losses[0] - 0.2, losses
     for n, t in tr.store.named_full_tensors():
         assert torch.equal(t, before[n]), n
+
+
+def test_long_context_tiled_mlp_matches_untiled():
+    x, y = _batch(7)
+    a, b = _trainer("cuda", long_context=True), _trainer("cuda")
+    ra, rb = a.forward_backward(x, y), b.forward_backward(x, y)
+    assert abs(float(ra["loss_sum"]) - float(rb["loss_sum"])) < 2e-3 * abs(float(rb["loss_sum"]))
+    ga, gb = a.get_gradients(), b.get_gradients()
+    for name in gb:
+        err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
+        assert err < 0.02, (name, float(err))
