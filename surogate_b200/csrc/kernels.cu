@@ -602,10 +602,22 @@ __global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, cons
 // n must be a multiple of 32.  The kernel is bandwidth-bound by design (10.25 bytes per parameter): divisions and square
 // roots use the fast hardware approximations, each thread keeps two 8-element vectors in flight, and the weight-decay mask is
 // one byte per 128 parameters (BLOCK_MASK) instead of one per parameter.
+// Integer <-> float conversions on the ordinary ALU (the conversion unit shares its issue slot with the special-function unit,
+// which this kernel already needs for rsqrt and two reciprocals per element).
+__device__ __forceinline__ float u8_to_float(unsigned v) { return __uint_as_float(0x4B000000u | v) - 8388608.f; }
+__device__ __forceinline__ int float_to_int_rn(float x) { return __float_as_int(x + 12582912.f) - 0x4B400000; }   // |x| < 2^22
+
 template <typename P, typename G, bool BLOCK_MASK>
 __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
                                                             __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
                                                             const float* __restrict__ hp, size_t n) {
+    // softsign decode table of the momentum code: y = c/127, m = y / (2 - |y|) (times the group scale)
+    __shared__ float m_lut[256];
+    {
+        const float y = static_cast<float>(static_cast<int>(threadIdx.x) - 128) * (1.f / 127.f);
+        m_lut[threadIdx.x] = y / (2.f - fabsf(y));
+    }
+    __syncthreads();
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
     const float step_size = lr / bc1, sib2 = rsqrtf(bc2), omb1 = 1.f - b1, omb2 = 1.f - b2;
     const size_t nvec = n / 8;
@@ -642,16 +654,15 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
             float mv[8], sv[8];
             float am = 0.f, av = 0.f;
             if (live[u]) {
-                const int8_t* mq = reinterpret_cast<const int8_t*>(&mraw[u]);
+                const uint8_t* mq = reinterpret_cast<const uint8_t*>(&mraw[u]);
                 const uint8_t* vq = reinterpret_cast<const uint8_t*>(&vraw[u]);
                 const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk[u]);
                 const float smu = sm[u], squ = sq[u] * (1.f / 255.f);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const float gk = gv[u][k] * gs;
-                    const float y = static_cast<float>(mq[k]) * (1.f / 127.f);
-                    float mi = __fdividef(y, 2.f - fabsf(y)) * smu;
-                    const float r = static_cast<float>(vq[k]) * squ;
+                    float mi = m_lut[mq[k] ^ 0x80u] * smu;           // two's-complement code + 128
+                    const float r = u8_to_float(vq[k]) * squ;
                     float vi2 = r * r;
                     mi = b1 * mi + omb1 * gk;
                     vi2 = b2 * vi2 + omb2 * gk * gk;
@@ -675,13 +686,13 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
                 const float fm = fmaxf(__half2float(hm), 6e-8f), fv = fmaxf(__half2float(hv), 6e-8f);
                 const float im = __fdividef(1.f, fm), iv = __fdividef(255.f, fv);
                 uint2 mo, vo;
-                int8_t* mq = reinterpret_cast<int8_t*>(&mo);
+                uint8_t* mq = reinterpret_cast<uint8_t*>(&mo);
                 uint8_t* vq = reinterpret_cast<uint8_t*>(&vo);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const float xn = fminf(fmaxf(mv[k] * im, -1.f), 1.f);
-                    mq[k] = static_cast<int8_t>(__float2int_rn(__fdividef(254.f * xn, 1.f + fabsf(xn))));
-                    vq[k] = static_cast<uint8_t>(min(255, __float2int_rn(sv[k] * iv)));
+                    mq[k] = static_cast<uint8_t>(float_to_int_rn(__fdividef(254.f * xn, 1.f + fabsf(xn))) & 0xFF);
+                    vq[k] = static_cast<uint8_t>(min(255, float_to_int_rn(sv[k] * iv)));
                 }
                 *reinterpret_cast<uint2*>(m8 + idx[u]) = mo;
                 *reinterpret_cast<uint2*>(v8 + idx[u]) = vo;
