@@ -27,6 +27,7 @@ COMMAND_MAPPING: Dict[str, str] = {
     "transplant-tokenizer": "surogate_b200.cli.transplant",
     "export": "surogate_b200.cli.export",
     "info": "surogate_b200.cli.info",
+    "chat": "surogate_b200.cli.chat",
 }
 
 BANNER = r"""

@@ -99,3 +99,40 @@ def test_tokenize_pipeline_packs_and_caches(tmp_path):
     assert 0 < mask.sum() < len(mask)  # only assistant tokens are trained
     again = TokenizeDatasets(cfg, {"vocab_size": 600}, os.path.join(tmp_path, "tok"))
     assert again.run() == files and not hasattr(again, "stats")  # served from the cache
+
+
+def test_upcycle_quantize_and_generate(tmp_path):
+    """Dense -> MoE upcycling keeps the function (every expert = the dense MLP, weights renormalised over top-k sum to 1);
+    block-FP8 quantisation round-trips within FP8 error; the chat helper decodes greedily."""
+    from safetensors.torch import load_file
+
+    from surogate_b200.cli.chat import generate
+    from surogate_b200.dsl.compiler import load_hf_config
+    from surogate_b200.quant.codecs import BlockFP8
+    from surogate_b200.utils.quantize_fp8 import quantize_checkpoint
+    from surogate_b200.utils.upcycle_moe import upcycle
+
+    dense = dict(MODEL)
+    tr = Trainer(TrainerConfig(model=dense, batch_size=1, seq_len=16, zero_level=0), device=torch.device("cpu"))
+    tr.init_weights(seed=0)
+    src = os.path.join(tmp_path, "dense")
+    tr.export_model(src, dense)
+    moe_dir = os.path.join(tmp_path, "moe")
+    info = upcycle(src, moe_dir, num_experts=4, top_k=2)
+    assert info["experts"] == 4
+    moe = Trainer(TrainerConfig(model=load_hf_config(moe_dir), batch_size=1, seq_len=16, zero_level=0), device=torch.device("cpu"))
+    moe.import_weights(moe_dir)
+    tok = np.random.default_rng(0).integers(0, 600, (1, 16)).astype(np.int32)
+    a, b = tr.logits(tok), moe.logits(tok)
+    assert torch.allclose(a, b, atol=2e-2, rtol=2e-2)  # bf16 export in between
+    out = generate(tr, None, tok[0, :4].tolist(), max_new_tokens=5, eos_id=None)
+    assert len(out) == 5 and all(0 <= t < 600 for t in out)
+    q_dir = os.path.join(tmp_path, "fp8")
+    rep = quantize_checkpoint(src, q_dir)
+    assert rep["quantized"] == 2 * 7  # q, k, v, o, gate, up, down per layer; embeddings, norms and the head keep their dtype
+    t = load_file(os.path.join(q_dir, "model.safetensors"))
+    name = "model.layers.0.mlp.down_proj.weight"
+    back = BlockFP8.dequantize_2d(t[name], t[name + "_scale_inv"], dtype=torch.float32)
+    ref = load_file(os.path.join(src, "model.safetensors"))[name].float()
+    assert ((back - ref).norm() / ref.norm()).item() < 0.05
+    assert json.load(open(os.path.join(q_dir, "config.json")))["quantization_config"]["quant_method"] == "fp8"
