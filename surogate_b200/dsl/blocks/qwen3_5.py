@@ -84,3 +84,48 @@ class Qwen35LinearBlock(_Qwen35Base):
 
     def operator(self, h, position_ids):
         return self.linear_attn(h)
+
+
+class _Qwen35MoEBase(Block):
+    """Qwen3.5-MoE layer: the same two token mixers, followed by routed experts plus a sigmoid-gated shared expert.
+    Returns (y, residual, aux_loss).  Parity: surogate/dsl/blocks/qwen3_5_moe.py."""
+    _name_remap_ = {**DENSE_BLOCK_NAME_REMAP, "linear_attn.*": ""}
+
+    def __init__(self, d_model, moe_d_ff, shared_d_ff, num_experts, num_experts_per_tok, norm_topk_prob, ep_size, aux_loss_coef, eps):
+        super().__init__()
+        from ..modules import MoEExpertsGated, MoESharedExpert
+
+        self.attn_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.input_layernorm.weight", zero_centered=True)
+        self.mlp_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.post_attention_layernorm.weight", zero_centered=True)
+        self.mlp = MoEExpertsGated(d_model, moe_d_ff, num_experts, num_experts_per_tok, norm_topk_prob, ep_size, aux_loss_coef,
+                                   prefix=f"{_P}.mlp")  # saved checkpoints list every expert separately
+        self.has_shared = shared_d_ff > 0
+        if self.has_shared:
+            self.shared_expert = MoESharedExpert(d_model, shared_d_ff, prefix=f"{_P}.mlp.shared_expert", gate_name=f"{_P}.mlp.shared_expert_gate.weight")
+
+    def forward(self, x, residual, position_ids):
+        residual, h = self.attn_norm(residual, x)
+        h = self.operator(h, position_ids)
+        residual, h = self.mlp_norm(residual, h)
+        y, aux = self.mlp(h)
+        if self.has_shared:
+            y = F.add(y, self.shared_expert(h), name="moe_plus_shared")
+        return y, residual, aux
+
+
+class Qwen35MoEAttentionBlock(_Qwen35MoEBase):
+    def __init__(self, num_query_heads, num_kv_heads, head_size, rope_theta, rotary_dim, **kw):
+        super().__init__(**kw)
+        self.self_attn = GatedAttention(kw["d_model"], num_query_heads, num_kv_heads, head_size, kw["eps"], rope_theta, rotary_dim)
+
+    def operator(self, h, position_ids):
+        return self.self_attn(h, position_ids)
+
+
+class Qwen35MoELinearBlock(_Qwen35MoEBase):
+    def __init__(self, num_k_heads, num_v_heads, head_k_dim, head_v_dim, conv_kernel, **kw):
+        super().__init__(**kw)
+        self.linear_attn = GatedDeltaNet(kw["d_model"], num_k_heads, num_v_heads, head_k_dim, head_v_dim, conv_kernel, kw["eps"])
+
+    def operator(self, h, position_ids):
+        return self.linear_attn(h)

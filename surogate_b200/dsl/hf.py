@@ -79,7 +79,7 @@ class fuse(Mapping):
 class transform(Mapping):
     """Apply an invertible function on load (and its inverse on export)."""
     template: str
-    fn: str = "identity"  # identity | transpose | plus_one (gemma-style norm offsets)
+    fn: str = "identity"  # identity | transpose | plus_one (gemma-style norm offsets) | swap_row_halves ([gate; up] <-> [up; gate])
 
     def hf_names(self, layer):
         return [_fmt(self.template, layer)]
@@ -89,6 +89,9 @@ class transform(Mapping):
             return t.transpose(-1, -2).contiguous()
         if self.fn == "plus_one":
             return t - 1 if inverse else t + 1
+        if self.fn == "swap_row_halves":  # its own inverse
+            a, b = t.chunk(2, dim=-2)
+            return torch.cat([b, a], dim=-2).contiguous()
         return t
 
     def load(self, get, layer):

@@ -53,6 +53,12 @@ def rmsnorm_offset(x, w, *, eps: float = 1e-6, offset: float = 1.0):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (offset + w.float())).to(x.dtype)
 
 
+@register("sigmoid_gate_mul")
+def sigmoid_gate_mul(x, w, y):
+    """y * sigmoid(x @ w^T) with a [1, C] weight: the per-token gate on a shared expert."""
+    return y * torch.sigmoid(F.linear(x.float(), w.float())).to(y.dtype)
+
+
 @register("scale_by")
 def scale_by(x, s):
     return x * s.to(x.dtype)

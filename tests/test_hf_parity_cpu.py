@@ -16,7 +16,7 @@ COMMON = dict(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention
 
 
 def _cases():
-    from transformers import GptOssConfig, Lfm2Config, LlamaConfig, NemotronHConfig, Qwen3_5TextConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
+    from transformers import Qwen3_5MoeTextConfig, GptOssConfig, Lfm2Config, LlamaConfig, NemotronHConfig, Qwen3_5TextConfig, MistralConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig
 
     yield "qwen3", Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=True)
     yield "qwen3-untied", Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=False)
@@ -35,6 +35,10 @@ def _cases():
     yield "qwen3.5", Qwen3_5TextConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                                        intermediate_size=96, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8,
                                        linear_conv_kernel_dim=4, max_position_embeddings=256, tie_word_embeddings=False)
+    yield "qwen3.5-moe", Qwen3_5MoeTextConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                              moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=4, num_experts_per_tok=2,
+                                              linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8,
+                                              linear_conv_kernel_dim=4, max_position_embeddings=256, tie_word_embeddings=False)
     yield "gpt-oss", GptOssConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                                   intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8, max_position_embeddings=256,
                                   rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
@@ -72,7 +76,7 @@ def test_logits_match_transformers_and_export_round_trips(tmp_path, name, config
     want_norm = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in hf.parameters() if p.grad is not None))
     assert abs(float(r["loss_sum"] / r["n_valid"]) - float(loss)) < 1e-4
     got_norm = float(tr.grad_norm())
-    if name != "qwen3-moe":  # the MoE model adds its load-balancing loss to the gradient
+    if name not in ("qwen3-moe", "qwen3.5-moe"):  # the MoE model adds its load-balancing loss to the gradient
         assert abs(got_norm - float(want_norm)) < 2e-3 * float(want_norm), (name, got_norm, float(want_norm))
     tr.store.release_grads()
     out = os.path.join(tmp_path, "export")
@@ -87,3 +91,15 @@ def test_logits_match_transformers_and_export_round_trips(tmp_path, name, config
     with torch.no_grad():
         again = back(torch.from_numpy(tok).long()).logits
     assert (again - want).abs().max() < 0.05 * want.abs().max()
+
+
+def test_fused_expert_tensor_mapping_swaps_gate_and_up_and_inverts():
+    """Checkpoints that store a layer's experts as one [E, 2F, C] tensor with the gate rows first load into the [up; gate] layout
+    and export back unchanged."""
+    from surogate_b200.dsl import hf as hfmap
+
+    m = hfmap.transform("layers.{L}.mlp.experts.gate_up_proj", fn="swap_row_halves")
+    t = torch.arange(2 * 6 * 3, dtype=torch.float32).reshape(2, 6, 3)
+    got = m.load(lambda name: {"layers.1.mlp.experts.gate_up_proj": t}[name], 1)
+    assert torch.equal(got[:, :3], t[:, 3:]) and torch.equal(got[:, 3:], t[:, :3])
+    assert torch.equal(m.export(got, 1)["layers.1.mlp.experts.gate_up_proj"], t)
