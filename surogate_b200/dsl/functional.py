@@ -66,9 +66,11 @@ def matmul(x: Proxy, w: Proxy, bias: Optional[Proxy] = None, name: str = "mm", r
 
 def qkv_qk_norm_rope(qkv: Proxy, q_norm_w: Optional[Proxy], k_norm_w: Optional[Proxy], position_ids: Proxy, *,
                      num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, rope_theta: float,
-                     rotary_dim: Optional[int] = None, rope_scaling=None, max_pos: Optional[int] = None,
+                     rotary_dim: Optional[int] = None, rope_scaling=None, max_pos: Optional[int] = None, mrope_section=None,
                      name: str = "qkv_rope") -> Tuple[Proxy, Optional[Proxy], Optional[Proxy]]:
-    """Per-head RMSNorm on Q and K (optional) followed by rotary embedding on the packed [.., (Hq+2Hkv)*D] tensor."""
+    """Per-head RMSNorm on Q and K (optional) followed by rotary embedding on the packed [.., (Hq+2Hkv)*D] tensor.
+    ``mrope_section`` = (t, h, w): when the batch carries the side input ``mrope_position_ids`` [3, B, T], frequency i uses the
+    height positions if i % 3 == 1 and i < 3h, the width positions if i % 3 == 2 and i < 3w, else the temporal ones."""
     use_norm = q_norm_w is not None
     lead = qkv.shape[:-1]
     outs = _t().emit(
@@ -77,7 +79,8 @@ def qkv_qk_norm_rope(qkv: Proxy, q_norm_w: Optional[Proxy], k_norm_w: Optional[P
          ("q_rstd", lead + (num_q_heads,), "fp32") if use_norm else None,
          ("k_rstd", lead + (num_kv_heads,), "fp32") if use_norm else None],
         num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, eps=eps, rope_theta=rope_theta,
-        rotary_dim=rotary_dim or head_dim, **({"rope_scaling": dict(rope_scaling), "max_pos": max_pos} if rope_scaling else {}))
+        rotary_dim=rotary_dim or head_dim, **({"rope_scaling": dict(rope_scaling), "max_pos": max_pos} if rope_scaling else {}),
+        **({"mrope_section": [int(v) for v in mrope_section]} if mrope_section else {}))
     return outs[0], outs[1], outs[2]
 
 

@@ -20,6 +20,7 @@ class AttentionConfig:
     rotary_dim: int | None = None
     sliding_window: int = 0
     causal: bool = True
+    mrope_section: tuple | None = None  # (t, h, w) frequency split for multi-axis rotary positions (vision-language models)
 
 
 class GenericGQAttention(Module):
@@ -50,7 +51,8 @@ class GenericGQAttention(Module):
         qn = self.p("q_norm_weight") if c.qk_norm else None
         kn = self.p("k_norm_weight") if c.qk_norm else None
         qkv_rope, _, _ = F.qkv_qk_norm_rope(qkv, qn, kn, position_ids, num_q_heads=self.Hq, num_kv_heads=self.Hkv,
-                                            head_dim=self.D, eps=c.eps, rope_theta=c.rope_theta, rotary_dim=c.rotary_dim)
+                                            head_dim=self.D, eps=c.eps, rope_theta=c.rope_theta, rotary_dim=c.rotary_dim,
+                                            mrope_section=c.mrope_section)
         att, _ = F.flash_attention(qkv_rope, num_q_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D,
                                    causal=c.causal, window=c.sliding_window)
         return F.matmul(att, self.p("out_weight"), name="att_out", role="out")

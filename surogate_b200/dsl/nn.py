@@ -252,10 +252,19 @@ class Model(Module):
     def from_hf_config(cls, cfg: Dict[str, Any], **overrides) -> "Model":
         kw = {}
         aliases = {"num_experts": ("num_local_experts", "n_routed_experts"), "head_dim": ("head_size",)}  # spellings used by other writers of config.json
+        def lookup(path: str):
+            node = cfg
+            for part in path.split("."):  # "text_config.hidden_size" reaches into a nested sub-config
+                if not isinstance(node, dict) or part not in node:
+                    return None
+                node = node[part]
+            return node
+
         for mine, theirs in cls.hf_config_map.items():
             for key in (theirs,) + aliases.get(theirs, ()):
-                if key in cfg and cfg[key] is not None:
-                    kw[mine] = cfg[key]
+                val = lookup(key)
+                if val is not None:
+                    kw[mine] = val
                     break
         rp = cfg.get("rope_parameters") or cfg.get("rope_scaling")
         if "rope_theta" not in kw and isinstance(rp, dict) and rp.get("rope_theta") is not None:

@@ -83,8 +83,10 @@ def import_hf_weights(cm: CompiledModel, store, path: str, strict: bool = True) 
 
 
 def export_hf_weights(cm: CompiledModel, store, out_dir: str, hf_config: Optional[Dict[str, Any]] = None, write: bool = True,
-                      dtype: torch.dtype = torch.bfloat16, max_shard_bytes: int = 5 << 30) -> None:
-    """Gather every parameter (collective when sharded), split back to HF names; rank with ``write`` saves."""
+                      dtype: torch.dtype = torch.bfloat16, max_shard_bytes: int = 5 << 30, passthrough_from: Optional[str] = None) -> None:
+    """Gather every parameter (collective when sharded), split back to HF names; rank with ``write`` saves.
+    Tensors of ``passthrough_from`` (the imported checkpoint) that no parameter maps to, such as a frozen vision tower,
+    are copied unchanged so the exported directory stays loadable as the full model."""
     tensors: Dict[str, torch.Tensor] = {}
     entries = {p.name: p for p in cm.params}
     for name, full in store.named_full_tensors():
@@ -100,6 +102,16 @@ def export_hf_weights(cm: CompiledModel, store, out_dir: str, hf_config: Optiona
             tensors[p.spec.hf.hf_names(None)[0]] = tensors[src.spec.hf.hf_names(None)[0]].clone()
     if not write:
         return
+    if passthrough_from:
+        try:
+            src_ckpt = LazyCheckpoint(passthrough_from)
+        except FileNotFoundError:
+            src_ckpt = None
+        if src_ckpt is not None:
+            owned = {n for p in cm.params if p.spec.hf is not None for n in p.spec.hf.hf_names(p.layer)}
+            for n in src_ckpt.names():
+                if n not in tensors and n not in owned:
+                    tensors[n] = src_ckpt.get(n).contiguous()
     os.makedirs(out_dir, exist_ok=True)
     total = sum(t.numel() * t.element_size() for t in tensors.values())
     if total <= max_shard_bytes:

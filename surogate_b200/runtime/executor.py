@@ -63,6 +63,9 @@ class ExecContext:
         self.row_weights: Optional[torch.Tensor] = None    # [tokens] multiplier on each token's log-likelihood gradient (DPO / GRPO)
         self.kd: Optional[Dict[str, Any]] = None           # {"idx": int32 [tokens, K], "logp": fp32 [tokens, K], "weight": float, "ce_weight": float}
         self.want_token_losses = False                     # leave per-token CE in stash["token_losses"] (and KD in stash["token_kd"])
+        # per-batch side inputs that are not graph values (multimodal: visual_pos_masks, visual_embeds, deepstack_visual_embeds,
+        # mrope_position_ids); ``torch_fn`` ops name the ones they read in their ``side_inputs`` attribute
+        self.extras: Dict[str, Any] = {}
 
     def eval_shape(self, shape) -> Tuple[int, ...]:
         return eval_shape(tuple(shape), self.dims)
@@ -235,11 +238,12 @@ class Executor:
 
     def forward(self, token_ids, position_ids, targets, *, training: bool = True, loss_scale: Any = 1.0,
                 aux_scale: float = 1.0, doc_ids=None, micro_step: int = 0, row_weights=None, kd=None,
-                want_token_losses: bool = False) -> Tuple[ExecContext, List[Any]]:
+                want_token_losses: bool = False, extras: Optional[Dict[str, Any]] = None) -> Tuple[ExecContext, List[Any]]:
         """Run the forward graph.  In training mode the LM-head op also produces d_x / d_w (fused loss backward)."""
         ctx = self.new_context(token_ids, training)
         ctx.loss_scale, ctx.aux_scale, ctx.doc_ids, ctx.micro_step = loss_scale, aux_scale, doc_ids, micro_step
         ctx.row_weights, ctx.kd, ctx.want_token_losses = row_weights, kd, want_token_losses
+        ctx.extras = dict(extras or {})
         ctx.phase = "fwd"
         g = self.cm.fwd
         env = {"token_ids": token_ids, "position_ids": position_ids, "targets": targets}

@@ -145,9 +145,14 @@ class CudaOps(RefOps):
         return dx.reshape(x.shape), None, db
 
     # ------------------------------------------------------------------ qk-norm + rope
+    @staticmethod
+    def _multi_axis(ctx, a) -> bool:
+        """A batch with image / video tokens carries (t, h, w) positions: those steps take the PyTorch rotary path."""
+        return bool(a.get("mrope_section")) and ctx.extras.get("mrope_position_ids") is not None
+
     def qkv_qk_norm_rope(self, ctx, op, qkv, qw, kw, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling"):
+        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling") or self._multi_axis(ctx, a):
             return super().qkv_qk_norm_rope(ctx, op, qkv, qw, kw, pos)
         out, q_rstd, k_rstd = self.ext.qk_norm_rope_fwd(qkv, qw, kw, pos.contiguous(), a["num_q_heads"], a["num_kv_heads"], 128, a["eps"],
                                                         a["rope_theta"])
@@ -155,7 +160,7 @@ class CudaOps(RefOps):
 
     def qkv_qk_norm_rope_backward(self, ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling"):
+        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling") or self._multi_axis(ctx, a):
             return super().qkv_qk_norm_rope_backward(ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos)
         dx, dqw, dkw = self.ext.qk_norm_rope_bwd(dy.contiguous(), qkv, qw, kw, q_rstd, k_rstd, pos.contiguous(), a["num_q_heads"],
                                                  a["num_kv_heads"], 128, a["eps"], a["rope_theta"])

@@ -56,16 +56,36 @@ class RefOps:
         ang = position_ids.to(torch.float32).unsqueeze(-1) * inv  # [B,T,half]
         return ang.cos() * att, ang.sin() * att
 
+    def _rope_tables(self, ctx, a, pos):
+        """cos / sin for this op: multi-axis (t, h, w) positions when the op has ``mrope_section`` and the batch has them."""
+        p3 = ctx.extras.get("mrope_position_ids") if a.get("mrope_section") else None
+        if p3 is None:
+            return self.rope_cos_sin(pos, a["rotary_dim"], a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"))
+        from ..config.rope import rope_inv_freq
+
+        inv, att = rope_inv_freq(a["rotary_dim"], a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"), device=pos.device)
+        ang3 = p3.to(torch.float32).unsqueeze(-1) * inv  # [3, B, T, half]
+        ang = ang3[0].clone()
+        for axis in (1, 2):
+            idx = slice(axis, a["mrope_section"][axis] * 3, 3)
+            ang[..., idx] = ang3[axis][..., idx]
+        return ang.cos() * att, ang.sin() * att
+
     # ------------------------------------------------------------------ generic torch-function op
     @staticmethod
-    def _fn_kwargs(op):
-        return {k: v for k, v in op.attrs.items() if k not in ("fn", "n_out", "n_in")}
+    def _fn_kwargs(op, ctx=None):
+        kw = {k: v for k, v in op.attrs.items() if k not in ("fn", "n_out", "n_in", "side_inputs", "pass_layer")}
+        for name in op.attrs.get("side_inputs", ()):  # per-batch tensors outside the graph (None when the batch has none)
+            kw[name] = ctx.extras.get(name) if ctx is not None else None
+        if op.attrs.get("pass_layer"):
+            kw["layer"] = ctx.layer if ctx is not None else None
+        return kw
 
     def torch_fn(self, ctx, op, *ins):
         from .torch_fns import TORCH_FNS
 
         with torch.no_grad():
-            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op))
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op, ctx))
         return out if isinstance(out, tuple) else (out,)
 
     def torch_fn_backward(self, ctx, op, *args):
@@ -79,7 +99,7 @@ class RefOps:
                 ins[i] = t.detach().requires_grad_(True)
                 req.append(i)
         with torch.enable_grad():
-            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op))
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op, ctx))
             outs = out if isinstance(out, tuple) else (out,)
             pairs = [(o, d) for o, d in zip(outs, d_outs) if d is not None and torch.is_tensor(o) and o.requires_grad]
             gs = torch.autograd.grad([o for o, _ in pairs], [ins[i] for i in req],
@@ -221,7 +241,7 @@ class RefOps:
             k_rstd = torch.rsqrt(k.pow(2).mean(-1) + a["eps"])
             q = q * q_rstd.unsqueeze(-1) * qw.float()
             k = k * k_rstd.unsqueeze(-1) * kw.float()
-        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"))
+        cos, sin = self._rope_tables(ctx, a, pos)
         q, k = self._rope(q, cos, sin, R, False), self._rope(k, cos, sin, R, False)
         out = torch.cat([q, k, v], dim=-2).reshape(qkv.shape).to(qkv.dtype)
         return out, q_rstd, k_rstd
@@ -242,7 +262,7 @@ class RefOps:
         lead = qkv.shape[:-1]
         g = dy.float().reshape(*lead, Hq + 2 * Hkv, D)
         x = qkv.float().reshape(*lead, Hq + 2 * Hkv, D)
-        cos, sin = self.rope_cos_sin(pos, R, a["rope_theta"], a.get("rope_scaling"), a.get("max_pos"))
+        cos, sin = self._rope_tables(ctx, a, pos)
         gq, gk, gv = g[..., :Hq, :], g[..., Hq:Hq + Hkv, :], g[..., Hq + Hkv:, :]
         gq, gk = self._rope(gq, cos, sin, R, True), self._rope(gk, cos, sin, R, True)
         dqw = dkw = None

@@ -59,6 +59,25 @@ def sigmoid_gate_mul(x, w, y):
     return y * torch.sigmoid(F.linear(x.float(), w.float())).to(y.dtype)
 
 
+@register("visual_scatter")
+def visual_scatter(x, *, visual_pos_masks=None, visual_embeds=None):
+    """Token embeddings with the rows at image / video placeholder positions replaced by the vision tower's outputs
+    (``visual_embeds`` [n_visual, C] in row-major order of the mask).  No gradient reaches the replaced embedding rows."""
+    if visual_pos_masks is None or visual_embeds is None:
+        return x + 0
+    m = visual_pos_masks.to(torch.bool)
+    return torch.where(m.unsqueeze(-1), torch.zeros_like(x), x).masked_scatter(m.unsqueeze(-1), visual_embeds.to(x.dtype))
+
+
+@register("deepstack_add")
+def deepstack_add(y, *, layer=None, visual_pos_masks=None, deepstack_visual_embeds=None):
+    """Add the ``layer``-th intermediate vision feature to the hidden state at the visual positions (first few layers only)."""
+    if visual_pos_masks is None or not deepstack_visual_embeds or layer is None or layer >= len(deepstack_visual_embeds):
+        return y + 0
+    m = visual_pos_masks.to(torch.bool).unsqueeze(-1)
+    return y + torch.zeros_like(y).masked_scatter(m, deepstack_visual_embeds[layer].to(y.dtype))
+
+
 @register("scale_by")
 def scale_by(x, s):
     return x * s.to(x.dtype)

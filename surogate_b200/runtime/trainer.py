@@ -156,6 +156,7 @@ class Trainer:
         self.step_index = 0
         self.kernel_launch_estimate = 0
         self._pinned: Dict[str, torch.Tensor] = {}
+        self._visual: Optional[Dict[str, Any]] = None  # see set_visual_inputs
         self._hp = torch.zeros(8, dtype=torch.float32, device=self.device)
         self.last_moe_stats = None
         self.h2d_bytes = 0
@@ -194,6 +195,7 @@ class Trainer:
         from ..io.hf_checkpoint import import_hf_weights
 
         import_hf_weights(self.cm, self.store, path)
+        self._imported_from = path
         self.store.sync_work_from_master()
         self._apply_qlora()
         self.recipe.on_weights_updated(self.store)
@@ -201,7 +203,8 @@ class Trainer:
     def export_model(self, out_dir: str, hf_config: Optional[Dict[str, Any]] = None) -> None:
         from ..io.hf_checkpoint import export_hf_weights
 
-        export_hf_weights(self.cm, self.store, out_dir, hf_config or self.cfg.model, write=self.rank == 0)
+        export_hf_weights(self.cm, self.store, out_dir, hf_config or self.cfg.model, write=self.rank == 0,
+                          passthrough_from=getattr(self, "_imported_from", None))
 
     def export_adapter(self, out_dir: str, base_model: str = "") -> None:
         if self.lora is None:
@@ -240,6 +243,42 @@ class Trainer:
             return arr[self.rank * B * GA:(self.rank + 1) * B * GA]
         assert arr.shape[0] == B * GA, f"expected {B * GA} (or {self.world * B * GA}) rows, got {arr.shape[0]}"
         return arr
+
+    # ------------------------------------------------------------------ multimodal side inputs
+    def set_visual_inputs(self, visual_pos_masks=None, visual_embeds=None, deepstack_visual_embeds=None, mrope_position_ids=None) -> None:
+        """Vision-tower outputs for the NEXT batches of this rank (kept until replaced; call with no arguments to clear).
+
+        ``visual_pos_masks`` [rows, T] marks image / video placeholder tokens; ``visual_embeds`` [n_visual, C] are their
+        embeddings in row-major mask order; ``deepstack_visual_embeds`` is a list (one per early layer) of [n_visual, C];
+        ``mrope_position_ids`` [3, rows, T] are the temporal / height / width positions.
+        Parity: csrc/src/binding/py_train.cpp (set_visual_inputs)."""
+        if visual_pos_masks is None and mrope_position_ids is None:
+            self._visual = None
+            return
+        v: Dict[str, Any] = {"mask": None, "embeds": None, "deep": [], "pos3": None, "cum": None}
+        if visual_pos_masks is not None:
+            m = torch.as_tensor(np.asarray(visual_pos_masks) if not torch.is_tensor(visual_pos_masks) else visual_pos_masks).to(torch.bool)
+            v["cum"] = [0] + torch.cumsum(m.reshape(m.shape[0], -1).sum(1).cpu(), 0).tolist()
+            v["mask"] = m.to(self.device)
+            v["embeds"] = torch.as_tensor(visual_embeds).to(self.device) if visual_embeds is not None else None
+            v["deep"] = [torch.as_tensor(d).to(self.device) for d in (deepstack_visual_embeds or [])]
+        if mrope_position_ids is not None:
+            v["pos3"] = torch.as_tensor(np.asarray(mrope_position_ids) if not torch.is_tensor(mrope_position_ids) else mrope_position_ids).to(self.device, torch.int32)
+        self._visual = v
+
+    def _extras(self, rows: slice) -> Optional[Dict[str, Any]]:
+        v = getattr(self, "_visual", None)
+        if v is None:
+            return None
+        out: Dict[str, Any] = {}
+        if v["mask"] is not None:
+            a, b = v["cum"][rows.start], v["cum"][min(rows.stop, len(v["cum"]) - 1)]
+            out["visual_pos_masks"] = v["mask"][rows]
+            out["visual_embeds"] = v["embeds"][a:b] if v["embeds"] is not None else None
+            out["deepstack_visual_embeds"] = [d[a:b] for d in v["deep"]]
+        if v["pos3"] is not None:
+            out["mrope_position_ids"] = v["pos3"][:, rows]
+        return out
 
     # ------------------------------------------------------------------ the step
     def forward_backward(self, inputs, targets, position_ids=None, row_weights=None, kd=None, loss_scale_override=None) -> Dict[str, torch.Tensor]:
@@ -284,7 +323,8 @@ class Trainer:
             ctx, outs = self.executor.forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale=loss_scale, aux_scale=aux_scale,
                                                        doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i,
                                                        row_weights=row_weights[sl] if row_weights is not None else None,
-                                                       kd=dict(kd, idx=kd["idx"][sl], logp=kd["logp"][sl]) if kd is not None else None)
+                                                       kd=dict(kd, idx=kd["idx"][sl], logp=kd["logp"][sl]) if kd is not None else None,
+                                                       extras=self._extras(sl))
             loss_sum += outs[0]
             if len(outs) > 1 and outs[1] is not None:
                 aux_sum += outs[1] * aux_scale
@@ -397,7 +437,8 @@ class Trainer:
         try:
             B = max(1, self.cfg.batch_size)
             for s in range(0, rows, B):
-                ctx, _ = self.executor.forward(inp[s:s + B], pos[s:s + B], tgt[s:s + B], training=False, want_token_losses=True)
+                ctx, _ = self.executor.forward(inp[s:s + B], pos[s:s + B], tgt[s:s + B], training=False, want_token_losses=True,
+                                               extras=self._extras(slice(s, s + B)))
                 out[s:s + B] = -ctx.stash["token_losses"].reshape(-1, T)
         finally:
             self.store.grads_enabled = True
@@ -417,7 +458,7 @@ class Trainer:
         self.executor.options.dump_tensors = lambda name, layer, val: captured.__setitem__(name, val) if layer is None else None
         self.store.grads_enabled = False
         try:
-            self.executor.forward(inp, pos, tgt, training=False)
+            self.executor.forward(inp, pos, tgt, training=False, extras=self._extras(slice(0, rows)))
         finally:
             self.executor.options.dump_tensors = prev
             self.store.grads_enabled = True
@@ -437,7 +478,7 @@ class Trainer:
         pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(inp.shape[0], T).contiguous()
         self.store.grads_enabled = False
         try:
-            ctx, outs = self.executor.forward(inp, pos, tgt, training=False)
+            ctx, outs = self.executor.forward(inp, pos, tgt, training=False, extras=self._extras(slice(0, inp.shape[0])))
         finally:
             self.store.grads_enabled = True
         n = (tgt != -100).sum().clamp_min(1).float()

@@ -103,3 +103,63 @@ def test_fused_expert_tensor_mapping_swaps_gate_and_up_and_inverts():
     got = m.load(lambda name: {"layers.1.mlp.experts.gate_up_proj": t}[name], 1)
     assert torch.equal(got[:, :3], t[:, 3:]) and torch.equal(got[:, 3:], t[:, :3])
     assert torch.equal(m.export(got, 1)["layers.1.mlp.experts.gate_up_proj"], t)
+
+
+def test_qwen3_vl_text_decoder_with_visual_side_inputs_matches_transformers(tmp_path):
+    """Multi-axis rotary positions, scatter of vision features into the embeddings and deepstack injection: the decoder fed
+    with synthetic vision-tower outputs gives the logits of transformers' Qwen3-VL language model fed with the same."""
+    from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+
+    text = dict(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=96,
+                max_position_embeddings=256, rms_norm_eps=1e-6, rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2], "mrope_interleaved": True},
+                tie_word_embeddings=False)
+    vision = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, out_hidden_size=64, patch_size=4, spatial_merge_size=2, temporal_patch_size=2,
+                  deepstack_visual_indexes=[0, 1], num_position_embeddings=16)
+    torch.manual_seed(0)
+    hf = Qwen3VLForConditionalGeneration(Qwen3VLConfig(text_config=text, vision_config=vision, tie_word_embeddings=False)).float().eval()
+    src = os.path.join(tmp_path, "hf")
+    hf.save_pretrained(src, safe_serialization=True)
+    rows, T, C = 2, 24, 64
+    rng = np.random.default_rng(0)
+    tok = rng.integers(0, 320, (rows, T)).astype(np.int32)
+    mask = np.zeros((rows, T), bool)
+    mask[0, 3:11] = True
+    mask[1, 5:9] = True
+    n_vis = int(mask.sum())
+    vis = torch.randn(n_vis, C)
+    deep = [0.5 * torch.randn(n_vis, C) for _ in range(2)]
+    pos3 = np.tile(np.arange(T, dtype=np.int64), (3, rows, 1))
+    pos3[1, 0, 3:11] = 3 + np.repeat(np.arange(2), 4)  # a 2 x 4 grid of patches: height index
+    pos3[2, 0, 3:11] = 3 + np.tile(np.arange(4), 2)    # width index
+    pos3[0, 0, 3:11] = 3
+    pos3[:, 0, 11:] = pos3[:, 0, 11:] - 4              # text resumes after max(grid) + 1
+    lm = hf.model.language_model
+    with torch.no_grad():
+        emb = lm.embed_tokens(torch.from_numpy(tok).long())
+        emb = emb.masked_scatter(torch.from_numpy(mask)[..., None], vis)
+        hidden = lm(inputs_embeds=emb, position_ids=torch.from_numpy(pos3), visual_pos_masks=torch.from_numpy(mask), deepstack_visual_embeds=deep).last_hidden_state
+        want = hf.lm_head(hidden)
+        want_text = hf.lm_head(lm(inputs_embeds=lm.embed_tokens(torch.from_numpy(tok).long())).last_hidden_state)
+    cfg = load_hf_config(src)
+    tr = Trainer(TrainerConfig(model=cfg, batch_size=1, seq_len=T, grad_accum=2, zero_level=0), device=torch.device("cpu"))
+    tr.import_weights(src)
+    assert torch.allclose(tr.logits(tok), want_text, atol=2e-4, rtol=1e-3)  # text-only batch: plain rotary positions
+    tr.set_visual_inputs(mask, vis, deep, pos3)
+    got = tr.logits(tok)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
+    # a training step with two micro-batches slices the packed vision features per row; embedding rows under the mask get no gradient
+    tgt = np.roll(tok, -1, axis=1).astype(np.int32)
+    tgt[:, -1] = -100
+    r = tr.forward_backward(tok, tgt)
+    loss = torch.nn.functional.cross_entropy(want.reshape(-1, 320), torch.from_numpy(tgt).long().reshape(-1), ignore_index=-100)
+    assert abs(float(r["loss_sum"] / r["n_valid"]) - float(loss)) < 1e-4
+    tr.set_visual_inputs()
+    assert torch.allclose(tr.logits(tok), want_text, atol=2e-4, rtol=1e-3)
+    # export keeps the vision tower of the imported checkpoint, so the directory loads as the full model again
+    tr.store.release_grads()
+    out = os.path.join(tmp_path, "export")
+    tr.export_model(out, cfg)
+    back = Qwen3VLForConditionalGeneration.from_pretrained(out, torch_dtype=torch.float32)
+    assert any(k.startswith("model.visual.") for k in back.state_dict())
+    for (ka, va), (kb, vb) in zip(sorted(hf.state_dict().items()), sorted(back.state_dict().items())):
+        assert ka == kb and torch.allclose(va.float(), vb.float(), atol=1e-2, rtol=1e-2), ka
