@@ -160,6 +160,7 @@ class SFTConfig:
     lmhead_drop_ignored_rows: bool = False
     attn_bwd_chunks: int = 1
     long_context: bool = False
+    train_vision: bool = False  # vision-language fine-tuning: rows with images, frozen vision tower, decoder trained (train/vision.py)
     sequence_chunks: int = 1
     use_cuda_graphs: bool = True
     # parallelism

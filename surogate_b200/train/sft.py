@@ -110,7 +110,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     hf_cfg = resolve_model_config(cfg)
     if cfg.router_aux_loss_coef is not None:
         hf_cfg["router_aux_loss_coef"] = cfg.router_aux_loss_coef
-    files = prepare_data(cfg, hf_cfg, info.rank, comm)
+    files = prepare_data(cfg, hf_cfg, info.rank, comm) if not cfg.train_vision else {}
     if comm is not None:
         comm.barrier()
     tcfg = cfg.to_trainer_config(hf_cfg)
@@ -120,7 +120,12 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
 
     B, GA, T = cfg.per_device_train_batch_size, cfg.gradient_accumulation_steps, cfg.sequence_len
     distill = cfg.distillation if (cfg.distillation is not None and cfg.distillation.enabled) else None
-    loader = DataLoader(files["train"], B * GA, T, seed=cfg.train_seed, rank=info.rank, world=info.world, native=False if distill else None)
+    if cfg.train_vision:
+        if distill or cfg.sample_packing:
+            raise ValueError("train_vision builds batches on the fly: it cannot be combined with distillation sidecars or sample packing")
+        loader = _vision_loader(cfg, hf_cfg, trainer, info, device, B * GA, T)
+    else:
+        loader = DataLoader(files["train"], B * GA, T, seed=cfg.train_seed, rank=info.rank, world=info.world, native=False if distill else None)
     kd_feed = None
     if distill:
         from ..data.loader import DistillationFeed
@@ -195,6 +200,20 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     return {"final": last, "losses": losses, "norms": norms, "steps": len(losses)}
 
 
+def _vision_loader(cfg, hf_cfg, trainer, info, device, rows_per_step: int, seq_len: int):
+    """Multimodal rows of this rank (``rank::world``) -> on-the-fly batches through the frozen vision tower."""
+    from . import vision
+
+    paths = [d.path for d in cfg.datasets]
+    rows = vision.load_multimodal_rows(paths)[info.rank::info.world]
+    if not rows:
+        raise ValueError(f"train_vision: no rows for rank {info.rank} in {paths}")
+    _, enc, tower = vision.init_mm_helpers(cfg.model, device)
+    batcher = vision.OnTheFlyMultimodalBatcher(rows, enc.encode, tower, rows_per_step, seq_len, image_token_id=hf_cfg["image_token_id"],
+                                               video_token_id=hf_cfg.get("video_token_id"), pad_token_id=int(hf_cfg.get("pad_token_id") or 0))
+    return vision.VisionTrainLoader(batcher, trainer)
+
+
 def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info, hf_cfg, device, start_step, max_steps, steps_per_epoch, warmup, flops, dev_name,
                kd_feed, distill, reporters, losses, norms) -> Dict[str, Any]:
     """The optimizer-step loop of a run: data, step, monitors, logging, evaluation, checkpoints.  Returns the last step's result."""
@@ -217,7 +236,7 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
         if kd_feed is not None:
             ki, kl = kd_feed.batch()
             kd = {"idx": ki, "logp": kl, "weight": distill.kd_weight, "ce_weight": 1.0 - distill.kd_weight}
-        out = trainer.step(x, y, p if cfg.sample_packing else None, lr=lr, kd=kd)
+        out = trainer.step(x, y, p if (cfg.sample_packing or cfg.train_vision) else None, lr=lr, kd=kd)
         ms = (time.perf_counter() - t0) * 1e3
         losses.append(out["loss"])
         norms.append(out["norm"])
