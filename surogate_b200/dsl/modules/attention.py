@@ -21,6 +21,9 @@ class AttentionConfig:
     sliding_window: int = 0
     causal: bool = True
     mrope_section: tuple | None = None  # (t, h, w) frequency split for multi-axis rotary positions (vision-language models)
+    rope_scaling: dict | None = None    # {"rope_type": "yarn" | "linear" | "llama3" | "dynamic", ...}
+    max_pos: int | None = None
+    output_gate: str = ""               # "" | "softplus_head" | "softplus_element": y *= softplus(x @ g_proj^T) before o_proj
 
 
 class GenericGQAttention(Module):
@@ -41,6 +44,9 @@ class GenericGQAttention(Module):
                                hf=hf.fuse([f"{a}.{n['q']}.bias", f"{a}.{n['k']}.bias", f"{a}.{n['v']}.bias"], sizes=[qd, kd, kd]))
         self.declare_param("out_weight", (d_model, qd), quantizable=True, hf=hf.direct(f"{a}.{n['o']}.weight"),
                            lora_targets=[("o_proj", 0, d_model)])
+        if self.cfg.output_gate:
+            gate_dim = num_query_heads if self.cfg.output_gate == "softplus_head" else qd
+            self.declare_param("g_weight", (gate_dim, d_model), hf=hf.direct(f"{a}.g_proj.weight"))
         if self.cfg.qk_norm:
             self.declare_param("q_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.{n['q_norm']}.weight"))
             self.declare_param("k_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.{n['k_norm']}.weight"))
@@ -52,7 +58,10 @@ class GenericGQAttention(Module):
         kn = self.p("k_norm_weight") if c.qk_norm else None
         qkv_rope, _, _ = F.qkv_qk_norm_rope(qkv, qn, kn, position_ids, num_q_heads=self.Hq, num_kv_heads=self.Hkv,
                                             head_dim=self.D, eps=c.eps, rope_theta=c.rope_theta, rotary_dim=c.rotary_dim,
-                                            mrope_section=c.mrope_section)
+                                            mrope_section=c.mrope_section, rope_scaling=c.rope_scaling, max_pos=c.max_pos)
         att, _ = F.flash_attention(qkv_rope, num_q_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D,
                                    causal=c.causal, window=c.sliding_window)
+        if c.output_gate:
+            gate = F.matmul(x, self.p("g_weight"), name="att_gate", role="att_gate")
+            att = F.torch_fn("softplus_gate_mul", [att, gate], [("att_gated", att.shape, "act")], head_dim=self.D)
         return F.matmul(att, self.p("out_weight"), name="att_out", role="out")

@@ -78,6 +78,27 @@ def deepstack_add(y, *, layer=None, visual_pos_masks=None, deepstack_visual_embe
     return y + torch.zeros_like(y).masked_scatter(m, deepstack_visual_embeds[layer].to(y.dtype))
 
 
+@register("softplus_gate_mul")
+def softplus_gate_mul(att, gate, *, head_dim: int):
+    """att [.., H*D] scaled by softplus(gate): one gate per head ([.., H]) or per channel ([.., H*D])."""
+    g = F.softplus(gate.float())
+    if g.shape[-1] != att.shape[-1]:
+        g = g.repeat_interleave(head_dim, dim=-1)
+    return (att.float() * g).to(att.dtype)
+
+
+@register("sigmoid_bias_router")
+def sigmoid_bias_router(x, router_w, bias, *, top_k: int, scaling_factor: float = 1.0):
+    """Sigmoid router with a selection-only bias: experts are chosen by sigmoid(logits) + bias, weighted by the unbiased
+    scores renormalised over the chosen ones, times ``scaling_factor``.  Returns (weights fp32 [.., K], indices int32 [.., K])."""
+    lead = x.shape[:-1]
+    scores = torch.sigmoid(F.linear(x.reshape(-1, x.shape[-1]).float(), router_w.float()))
+    idx = torch.topk(scores.detach() + bias.float(), top_k, dim=-1).indices
+    w = scores.gather(1, idx)
+    w = w / w.sum(-1, keepdim=True) * scaling_factor
+    return w.reshape(*lead, top_k), idx.to(torch.int32).reshape(*lead, top_k)
+
+
 @register("scale_by")
 def scale_by(x, s):
     return x * s.to(x.dtype)
