@@ -46,6 +46,12 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling: Optional[Dict[str, Any
         mid = (1 - smooth) * inv / factor + smooth * inv
         is_mid = (wavelen <= old / lo) & (wavelen >= old / hi)
         return torch.where(is_mid, mid, scaled), 1.0
+    if kind == "proportional":
+        # only the first fraction of the frequency pairs rotates; the rest get angle 0 (identity), and the exponent's
+        # denominator stays the full head size, so the rotated pairs keep the frequencies they would have in a full rotation
+        angles = int(float(scaling.get("partial_rotary_factor", 1.0)) * rotary_dim // 2)
+        rot = 1.0 / (theta ** (torch.arange(0, 2 * angles, 2, dtype=torch.float32, device=device) / rotary_dim))
+        return torch.cat([rot, torch.zeros(rotary_dim // 2 - angles, dtype=torch.float32, device=device)]) / factor, 1.0
     if kind == "yarn":
         orig = int(scaling.get("original_max_position_embeddings") or max_position_embeddings or 4096)
         beta_fast, beta_slow = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))

@@ -8,5 +8,6 @@ from .qwen3_5 import Qwen35Model
 from .qwen3_5_moe import Qwen35MoEModel
 from .qwen3_vl import Qwen3VLModel
 from .laguna import LagunaModel
+from .gemma4 import Gemma4Model
 
-__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model", "NemotronHModel", "Qwen35Model", "Qwen35MoEModel", "Qwen3VLModel", "LagunaModel"]
+__all__ = ["Qwen3Model", "Qwen2Model", "LlamaModel", "MistralModel", "Qwen3MoEModel", "GptOssModel", "Lfm2Model", "NemotronHModel", "Qwen35Model", "Qwen35MoEModel", "Qwen3VLModel", "LagunaModel", "Gemma4Model"]

@@ -34,5 +34,8 @@ class GenericMLP(Module):
         if self.cfg.tile_rows > 0:
             return F.tiled_mlp(x, self.p("up_weight"), self.p("down_weight"), self.cfg.tile_rows)
         up = F.matmul(x, self.p("up_weight"), name="mlp_up", role="mlp_up")
-        act = F.swiglu(up)
+        if self.cfg.activation == "geglu":  # gelu(gate) * up with the tanh approximation (Gemma family)
+            act = F.torch_fn("geglu", [up], [("geglu", up.shape[:-1] + (up.shape[-1] // 2,), "act")], approximate="tanh")
+        else:
+            act = F.swiglu(up)
         return F.matmul(act, self.p("down_weight"), name="mlp_down", role="mlp_down")

@@ -94,8 +94,10 @@ def export_hf_weights(cm: CompiledModel, store, out_dir: str, hf_config: Optiona
         if p.spec.hf is None:
             continue
         if write:
-            for hf_name, t in p.spec.hf.export(full.detach().to("cpu", dtype), p.layer).items():
-                tensors[hf_name] = t.contiguous()
+            # inverse mappings run at the master's precision, the cast comes last: a zero-centred norm weight stored as w - 1
+            # would lose most of its bits if 1 + w were rounded to bfloat16 first
+            for hf_name, t in p.spec.hf.export(full.detach().to("cpu"), p.layer).items():
+                tensors[hf_name] = t.to(dtype).contiguous()
     for p in cm.params:  # untied export of tied heads keeps HF loaders happy only if the config says untied
         if p.tied_to and write and hf_config is not None and not hf_config.get("tie_word_embeddings", True):
             src = entries[p.tied_to]

@@ -99,6 +99,48 @@ def sigmoid_bias_router(x, router_w, bias, *, top_k: int, scaling_factor: float 
     return w.reshape(*lead, top_k), idx.to(torch.int32).reshape(*lead, top_k)
 
 
+@register("scale_by_buffer")
+def scale_by_buffer(x, s):
+    """x times a checkpoint buffer (a value that is loaded and saved but never trained)."""
+    return x * s.detach().to(x.dtype)
+
+
+@register("gemma4_qkv_norm_rope")
+def gemma4_qkv_norm_rope(qkv, qn_w, kn_w, pos, *, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, rope_theta: float, rope_scaling=None,
+                         k_eq_v: bool = False):
+    """Packed [.., (Hq + 2 Hkv) D] (or [.., (Hq + Hkv) D] when values reuse the key projection) -> packed q, k, v with
+    RMSNorm(scale) on q and k, scale-free RMSNorm on v, and rotary embedding over the whole head (pairs i, i + D/2)."""
+    from ..config.rope import rope_inv_freq
+
+    lead = qkv.shape[:-1]
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    x = qkv.float().reshape(*lead, -1, D)
+    q, k = x[..., :Hq, :], x[..., Hq:Hq + Hkv, :]
+    v = k if k_eq_v else x[..., Hq + Hkv:, :]
+    q, k, v = _rms(q, eps) * qn_w.float(), _rms(k, eps) * kn_w.float(), _rms(v, eps)
+    inv, att = rope_inv_freq(D, rope_theta, rope_scaling, None, device=qkv.device)
+    ang = pos.float().unsqueeze(-1) * inv
+    cos, sin = (ang.cos() * att).unsqueeze(-2), (ang.sin() * att).unsqueeze(-2)
+
+    def rope(t):
+        a, b = t[..., :D // 2], t[..., D // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+    return torch.cat([rope(q), rope(k), v], dim=-2).reshape(*lead, (Hq + 2 * Hkv) * D).to(qkv.dtype)
+
+
+@register("gemma4_router")
+def gemma4_router(x, proj_w, scale, per_expert_scale, *, top_k: int, eps: float):
+    """Scale-free RMSNorm, a learned per-channel scale and 1/sqrt(C), linear -> softmax -> top-k renormalised to sum 1, then a
+    learned per-expert multiplier.  Returns (weights fp32 [.., K], indices int32 [.., K])."""
+    lead, C = x.shape[:-1], x.shape[-1]
+    h = _rms(x.reshape(-1, C).float(), eps) * scale.float() * (C ** -0.5)
+    probs = torch.softmax(F.linear(h, proj_w.float()), dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    w = w / w.sum(-1, keepdim=True) * per_expert_scale.float()[idx]
+    return w.reshape(*lead, top_k), idx.to(torch.int32).reshape(*lead, top_k)
+
+
 @register("scale_by")
 def scale_by(x, s):
     return x * s.to(x.dtype)

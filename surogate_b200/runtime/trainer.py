@@ -468,7 +468,9 @@ class Trainer:
         if hasattr(x, "dequantize"):
             x = x.hp if getattr(x, "hp", None) is not None else x.dequantize()
         w = self.store.get(head.inputs[1])
-        return (x.reshape(-1, x.shape[-1]).float() @ w.float().t()).reshape(rows, T, -1)
+        out = (x.reshape(-1, x.shape[-1]).float() @ w.float().t()).reshape(rows, T, -1)
+        cap = float(head.attrs.get("softcap") or 0.0)
+        return cap * torch.tanh(out / cap) if cap else out
 
     @torch.no_grad()
     def validate(self, inputs, targets, position_ids=None) -> Dict[str, float]:
