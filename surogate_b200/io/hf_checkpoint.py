@@ -69,6 +69,8 @@ def import_hf_weights(cm: CompiledModel, store, path: str, strict: bool = True) 
         names = m.hf_names(p.layer)
         if p.tied_to:
             continue  # shares storage with its target
+        if hasattr(store, "holds") and not store.holds(p.name):
+            continue  # held by another pipeline stage
         if not all(n in ckpt for n in names):
             if type(m).__name__ == "tied_to":
                 continue

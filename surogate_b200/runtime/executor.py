@@ -109,6 +109,7 @@ class Executor:
         self._top_saved: Set[str] = set(self.cm.bwd.meta["saved"])
         self._layer_saved: List[Optional[Dict[str, Any]]] = [None] * self.cm.n_layers
         self._top_env: Dict[str, Any] = {}
+        self.layer_range: Optional[Tuple[int, int]] = None  # pipeline stage: the block stack runs only layers [first, last)
 
     # ------------------------------------------------------------------ generic graph run
     def _last_use(self, g: Graph) -> Dict[str, int]:
@@ -117,13 +118,15 @@ class Executor:
             self._liveness[key] = g.last_use()
         return self._liveness[key]
 
-    def run_graph(self, g: Graph, env: Dict[str, Any], ctx: ExecContext, keep: Set[str]) -> None:
+    def run_graph(self, g: Graph, env: Dict[str, Any], ctx: ExecContext, keep: Set[str], ops: Optional[List[OpNode]] = None) -> None:
+        """Interpret ``g`` (or only ``ops``, a subsequence of its ops: pipeline stages run the part of the top-level graph
+        before, inside or after the block stack)."""
         last = self._last_use(g)
         prev_graph = ctx.graph
         ctx.graph = g
         be = self.backend
         params = g.params
-        for op in g.ops:
+        for op in (g.ops if ops is None else ops):
             if op.kind == "block_stack":
                 outs = self._block_stack_forward(op, env, ctx)
             elif op.kind == "block_stack_backward":
@@ -173,8 +176,8 @@ class Executor:
         x, res, pos = (env[n] for n in op.inputs)
         aux_names: List[str] = op.attrs.get("aux", [])
         aux_tot = [None] * len(aux_names)
-        n = self.cm.n_layers
-        for L in range(n):
+        lo, hi = self.layer_range or (0, self.cm.n_layers)
+        for L in range(lo, hi):
             bt = self.cm.layer_types[L]
             g = self.cm.block_fwd[bt]
             ctx.layer = L
@@ -200,7 +203,8 @@ class Executor:
         d_x, d_res = env.get(op.inputs[0]), env.get(op.inputs[1])
         d_aux = [env.get(n) if n is not None else None for n in op.inputs[2:]]
         aux_names: List[str] = op.attrs.get("aux", [])
-        for L in reversed(range(self.cm.n_layers)):
+        lo, hi = self.layer_range or (0, self.cm.n_layers)
+        for L in reversed(range(lo, hi)):
             bt = self.cm.layer_types[L]
             fg, bg = self.cm.block_fwd[bt], self.cm.block_bwd[bt]
             ctx.layer = L
@@ -269,3 +273,70 @@ class Executor:
         ctx, outs = self.forward(token_ids, position_ids, targets, training=True, **kw)
         self.backward(ctx)
         return ctx, outs
+
+    # ------------------------------------------------------------------ pipeline stages
+    # A stage is a contiguous layer range.  The first stage also runs the top-level ops before the block stack (embedding),
+    # the last one those after it (final norm, LM head + loss).  Several micro-batches are in flight per stage, so the saved
+    # tensors of a forward are detached from the executor and attached again for the matching backward.
+    @staticmethod
+    def _op_index(g: Graph, kind: str) -> int:
+        return next(i for i, op in enumerate(g.ops) if op.kind == kind)
+
+    def stage_forward(self, ctx: ExecContext, layers: Tuple[int, int], is_first: bool, is_last: bool, position_ids, token_ids=None, targets=None,
+                      x=None, residual=None):
+        """Returns (x, residual, aux losses of this stage's layers) and, on the last stage, also the model outputs."""
+        g = self.cm.fwd
+        i = self._op_index(g, "block_stack")
+        stack = g.ops[i]
+        env: Dict[str, Any] = {"position_ids": position_ids, "token_ids": token_ids, "targets": targets}
+        ctx.phase = "fwd"
+        keep = (self._top_saved if ctx.training else set()) | set(g.outputs) | {n for n in stack.outputs if n} | set(stack.inputs)
+        if is_first:
+            self.run_graph(g, env, ctx, keep, ops=g.ops[:i])
+        else:
+            env[stack.inputs[0]], env[stack.inputs[1]] = x, residual
+        self.layer_range = tuple(layers)
+        try:
+            self.run_graph(g, env, ctx, keep, ops=[stack])
+        finally:
+            self.layer_range = None
+        outs = None
+        if is_last:
+            self.run_graph(g, env, ctx, keep, ops=g.ops[i + 1:])
+            outs = [env.get(o) for o in g.outputs]
+        self._top_env = env
+        return env[stack.outputs[0]], env[stack.outputs[1]], [env[n] for n in stack.outputs[2:]], outs
+
+    def stage_backward(self, ctx: ExecContext, layers: Tuple[int, int], is_first: bool, is_last: bool, d_x=None, d_residual=None):
+        """Backward of one stage; returns the gradients of its incoming (x, residual)."""
+        g, bg = self.cm.fwd, self.cm.bwd
+        j = self._op_index(bg, "block_stack_backward")
+        sb = bg.ops[j]
+        env = {k: v for k, v in self._top_env.items() if k in self._top_saved or k in g.inputs}
+        self._top_env = {}
+        og = bg.meta["out_grads"]
+        for o in g.outputs[1:]:
+            env[og[o]] = ctx.aux_scale
+        ctx.phase = "bwd"
+        if is_last:
+            env[og[g.outputs[0]]] = 1.0
+            self.run_graph(bg, env, ctx, set(sb.inputs), ops=bg.ops[:j])
+        else:
+            env[sb.inputs[0]], env[sb.inputs[1]] = d_x, d_residual
+        self.layer_range = tuple(layers)
+        try:
+            self.run_graph(bg, env, ctx, {n for n in sb.outputs if n}, ops=[sb])
+        finally:
+            self.layer_range = None
+        out = env.get(sb.outputs[0]), env.get(sb.outputs[1])
+        if is_first:
+            self.run_graph(bg, env, ctx, set(), ops=bg.ops[j + 1:])
+        return out
+
+    def detach_state(self):
+        state = (self._layer_saved, self._top_env)
+        self._layer_saved, self._top_env = [None] * self.cm.n_layers, {}
+        return state
+
+    def attach_state(self, state) -> None:
+        self._layer_saved, self._top_env = state

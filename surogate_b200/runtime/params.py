@@ -112,8 +112,12 @@ class _HostGatherWork:
 class ParamStore:
     def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
                  comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
-                 expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False):
+                 expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False,
+                 owned: Optional[Callable[[Any], bool]] = None):
         self.cm = cm
+        # pipeline stages: ``owned(entry)`` says whether this process holds the parameter at all; the others are never
+        # allocated, initialised, loaded or stepped here
+        self.owned = owned
         self.device = torch.device(device)
         self.param_dtype = param_dtype
         self.grad_dtype = grad_dtype or param_dtype
@@ -148,6 +152,8 @@ class ParamStore:
     # ------------------------------------------------------------------ layout
     def _build(self) -> None:
         for e in self.cm.params:
+            if self.owned is not None and not self.owned(e):
+                continue
             if e.tied_to:
                 self.alias[e.name] = e.tied_to
                 continue
@@ -278,8 +284,13 @@ class ParamStore:
         El = s.shape[0]
         return tensor[self.rank * El:(self.rank + 1) * El]
 
+    def holds(self, name: str) -> bool:
+        return self.resolve(name) in self.where
+
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         name = self.resolve(name)
+        if self.owned is not None and name not in self.where:
+            return  # another pipeline stage's parameter
         b, s = self.where[name]
         if b.expert and tensor.shape[0] == s.shape[0] * self.ep:
             tensor = self._expert_slice(s, tensor)  # a full [E, ...] tensor: keep this rank's experts

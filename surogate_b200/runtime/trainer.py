@@ -90,7 +90,8 @@ def build_model(spec: Dict[str, Any], **overrides):
 
 
 class Trainer:
-    def __init__(self, cfg: TrainerConfig, device: Optional[torch.device] = None, comm=None):
+    def __init__(self, cfg: TrainerConfig, device: Optional[torch.device] = None, comm=None, owned=None):
+        """``owned(param entry) -> bool`` restricts the parameters this process holds (pipeline stages)."""
         self.cfg = cfg
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self.comm = comm or SingleProcessComm()
@@ -120,7 +121,7 @@ class Trainer:
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
         self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
                                 zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size,
-                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training)
+                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training, owned=owned)
         from .ops_cuda import make_backend
 
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)
@@ -369,12 +370,13 @@ class Trainer:
                 self.comm.all_reduce(total, "sum")
         return total.sqrt()
 
-    def optimizer_step(self, lr: Optional[float] = None) -> torch.Tensor:
+    def optimizer_step(self, lr: Optional[float] = None, norm: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``norm``: the global gradient norm when this process holds only part of the model (pipeline stages)."""
         cfg = self.opt_cfg
         self.step_index += 1
         t = self.step_index
         lr = cfg.learning_rate if lr is None else lr
-        norm = self.grad_norm()
+        norm = self.grad_norm() if norm is None else norm
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm and cfg.max_grad_norm > 0 else torch.ones_like(norm)
         clip = torch.where(torch.isfinite(norm), clip, torch.zeros_like(clip))  # a non-finite gradient skips the update
         host = (lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, 1 - cfg.beta1 ** t, 1 - cfg.beta2 ** t)

@@ -3,7 +3,7 @@
 Layers are cut into small stages of ``stage_layers`` blocks (default 4), at least as many stages as GPUs; stage ``s`` runs
 on GPU ``s % gpus``.  ``M = gpus * grad_accum`` micro-batches travel through the stages in a diagonal wavefront: at tick
 ``t`` stage ``s`` processes micro-batch ``t - s`` (forward), and the backward wave runs the same diagonal in reverse.
-``wavefront`` returns that schedule; the executor for it lives in ``parallel/dispatch_pp.py``.
+``wavefront`` returns that schedule; ``parallel/dispatch_pp.py`` (PipelineTrainer) executes it.
 
 Parity: surogate/train/dispatch_pp.py:22-54, docs/guides/dispatch-pp.md.
 """

@@ -114,7 +114,14 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     if comm is not None:
         comm.barrier()
     tcfg = cfg.to_trainer_config(hf_cfg)
-    trainer = Trainer(tcfg, device=device, comm=comm)
+    pp = cfg.parallelism == "dispatch_pp" and info.world > 1
+    if pp:  # pipeline stages: layer ranges per rank, micro-batches in a wavefront, boundaries sent GPU to GPU
+        from ..parallel.dispatch_pp import PipelineTrainer
+
+        tcfg.zero_level = 0
+        trainer = PipelineTrainer(tcfg, device=device, stage_layers=int(cfg.dispatch_pp.get("stage_layers", cfg.dispatch_pp.get("stage_blocks", 0)) or 0))
+    else:
+        trainer = Trainer(tcfg, device=device, comm=comm)
     logger = TrainingRunLogger(cfg.log_file, cfg.surogate_metrics_path if "surogate" in cfg.report_to else None, is_main=info.is_main)
     logger.log_record("options", config=json.loads(cfg.to_json()))
 
@@ -125,13 +132,16 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
             raise ValueError("train_vision builds batches on the fly: it cannot be combined with distillation sidecars or sample packing")
         loader = _vision_loader(cfg, hf_cfg, trainer, info, device, B * GA, T)
     else:
-        loader = DataLoader(files["train"], B * GA, T, seed=cfg.train_seed, rank=info.rank, world=info.world, native=False if distill else None)
+        # pipeline stages: every rank reads the same rows (world * GA micro-batches of B); only the end stages use them
+        loader = DataLoader(files["train"], B * GA * (info.world if pp else 1), T, seed=cfg.train_seed, rank=0 if pp else info.rank,
+                            world=1 if pp else info.world, native=False if distill else None)
     kd_feed = None
     if distill:
         from ..data.loader import DistillationFeed
 
         kd_feed = DistillationFeed(loader)  # needs train-NNN.kd next to every shard (surogate distill-capture)
-    eval_loader = DataLoader(files["eval"], B, T, seed=cfg.eval_seed, rank=info.rank, world=info.world, shuffle=False) if files.get("eval") else None
+    eval_loader = DataLoader(files["eval"], B, T, seed=cfg.eval_seed, rank=0 if pp else info.rank, world=1 if pp else info.world,
+                             shuffle=False) if files.get("eval") else None
     steps_per_epoch = max(1, loader.steps_per_epoch())
     max_steps = cfg.max_steps if cfg.max_steps > 0 else steps_per_epoch * cfg.num_epochs
     warmup = cfg.warmup_steps or int(cfg.warmup_ratio * max_steps)
@@ -140,7 +150,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
 
     start_step = 0
     model_dir = cfg.model if isinstance(cfg.model, str) and os.path.isdir(cfg.model) else None
-    latest = find_latest_checkpoint(cfg.checkpoint_dir) if cfg.resume_from_checkpoint else None
+    latest = (trainer.latest_checkpoint(cfg.checkpoint_dir) if pp else find_latest_checkpoint(cfg.checkpoint_dir)) if cfg.resume_from_checkpoint else None
     if latest is not None:
         meta = trainer.load_checkpoint(cfg.checkpoint_dir, latest)
         start_step = meta["run"]["step"]

@@ -33,7 +33,14 @@ def main():
                         lora=a.get("lora"), offload_master=a.get("offload_master", False), offload_optimizer=a.get("offload_optimizer", False),
                         cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5),
                         ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
-    tr = Trainer(cfg, device=dev, comm=comm)
+    pp = a.get("pp", False)
+    if pp:  # pipeline stages: every rank gets the whole global batch and cuts it into world * grad_accum micro-batches
+        from surogate_b200.parallel.dispatch_pp import PipelineTrainer
+
+        cfg.zero_level = 0
+        tr = PipelineTrainer(cfg, device=dev, stage_layers=a.get("stage_layers", 0))
+    else:
+        tr = Trainer(cfg, device=dev, comm=comm)
     tr.init_weights(seed=0)
     rng = np.random.default_rng(7)
     V = model["vocab_size"]
@@ -43,10 +50,21 @@ def main():
         tok = rng.integers(0, V, (gb, T + 1)).astype(np.int32)
         x, y = tok[:, :-1], tok[:, 1:]
         sl = slice(info.rank * per_rank, (info.rank + 1) * per_rank)
-        out = tr.step(x[sl], y[sl])
+        out = tr.step(x, y) if pp else tr.step(x[sl], y[sl])
         losses.append(out["loss"])
         norms.append(out["norm"])
     extra = {}
+    if pp:
+        if a.get("export_dir"):
+            tr.export_model(a["export_dir"])
+        if info.rank == 0:
+            print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "stages": [[s.first_layer, s.last_layer, s.gpu] for s in tr.stages],
+                                          "held_params": len(tr.inner.store.where)}), flush=True)
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if a.get("checkpoint_dir"):
         tr.save_checkpoint(a["checkpoint_dir"], step=len(losses))
     if info.rank == 0:

@@ -45,3 +45,53 @@ def test_grad_accumulation_with_sharded_gradients(single):
     r = run_worker(2, dict(device="cpu", model=TINY, global_batch=4, seq_len=32, steps=3, zero=2, grad_accum=2), port=29621)
     # same tokens per step, split into 2 micro-batches per rank of 1 row: rows are assigned differently, so compare loosely
     assert abs(r["losses"][0] - single["losses"][0]) < 5e-2
+
+
+FOUR = dict(TINY, n_layers=4)
+
+
+@pytest.mark.parametrize("tied,stage_layers,port", [(True, 0, 29641), (False, 1, 29642)])
+def test_pipeline_stages_match_single_process(tmp_path, tied, stage_layers, port):
+    """Layer ranges on two ranks, boundaries sent point to point, a diagonal wavefront of micro-batches: same losses and
+    gradient norms as the unpartitioned run; with one layer per stage every rank interleaves two stages.  The tied
+    embedding / LM-head weight is held by both end ranks and stays equal."""
+    model = dict(FOUR, tie_word_embeddings=tied)
+    one = run_worker(1, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0, grad_accum=2))
+    out = os.path.join(tmp_path, "export")
+    r = run_worker(2, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, pp=True, grad_accum=1, stage_layers=stage_layers, export_dir=out), port=port)
+    assert r["world"] == 2 and len(r["stages"]) == (4 if stage_layers == 1 else 2)
+    assert {s[2] for s in r["stages"]} == {0, 1}
+    for a, b in zip(r["losses"], one["losses"]):
+        assert abs(a - b) < 2e-4 * abs(b), (r["losses"], one["losses"])
+    for a, b in zip(r["norms"], one["norms"]):
+        assert abs(a - b) < 1e-3 * abs(b), (r["norms"], one["norms"])
+    index = json.load(open(os.path.join(out, "model.safetensors.index.json")))
+    names = set(index["weight_map"])
+    assert {f"model.layers.{L}.mlp.down_proj.weight" for L in range(4)} <= names and "model.embed_tokens.weight" in names and "model.norm.weight" in names
+    assert len(set(index["weight_map"].values())) == 2
+
+
+def test_sft_loop_with_pipeline_stages_checkpoints_and_resumes(tmp_path):
+    """`parallelism: dispatch_pp` through the SFT loop on two ranks: trains, evaluates, checkpoints per stage rank, exports a
+    sharded HF directory and resumes from the per-stage checkpoints."""
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=256, d_model=32, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64,
+                 tie_word_embeddings=True)
+    base = dict(model=json.dumps(model), synthetic_data=True, sequence_len=32, per_device_train_batch_size=2, gradient_accumulation_steps=1, max_steps=4,
+                lora=False, optimizer="adamw", learning_rate=1e-2, save_steps=2, eval_steps=2, recipe="bf16", zero_level=0, from_scratch=True, parallelism="dispatch_pp",
+                output_dir=str(tmp_path / "out"), report_to=[])
+
+    def run(cfg, port):
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2", SUROGATE_NO_BANNER="1")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", str(port),
+               os.path.join(HERE, "pp_sft_worker.py"), json.dumps(cfg)]
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+        assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
+        return json.loads([l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+
+    r = run(base, 29651)
+    assert r["steps"] == 4 and all(l == l for l in r["losses"])
+    out = tmp_path / "out"
+    assert (out / "model.safetensors.index.json").exists() and (out / "stage_rank_000" / "step_00000002" / "checkpoint.json").exists()
+    assert (out / "stage_rank_001" / "step_00000002" / "checkpoint.json").exists()
+    r2 = run(dict(base, max_steps=6, save_steps=0, resume_from_checkpoint=True), 29652)
+    assert r2["steps"] == 4  # resumed at step 2 of 6
