@@ -66,6 +66,8 @@ class ExecContext:
         # per-batch side inputs that are not graph values (multimodal: visual_pos_masks, visual_embeds, deepstack_visual_embeds,
         # mrope_position_ids); ``torch_fn`` ops name the ones they read in their ``side_inputs`` attribute
         self.extras: Dict[str, Any] = {}
+        # chunked-sequence training: the attention op reads / extends the per-layer key-value prefix kept here
+        self.chunk: Optional["ChunkState"] = None
 
     def eval_shape(self, shape) -> Tuple[int, ...]:
         return eval_shape(tuple(shape), self.dims)
@@ -89,6 +91,39 @@ class ExecContext:
     def record_moe_stats(self, counts: torch.Tensor, probs: torch.Tensor) -> None:
         if self.phase == "fwd" and self.layer is not None:
             self.moe_stats.append((self.layer, counts.detach(), probs.detach().mean(0)))
+
+
+class ChunkState:
+    """Key / value prefix and its gradient accumulators for training one long sequence in ``n_chunks`` pieces.
+
+    Pass A runs the chunks left to right without saving activations; each attention layer appends its rotated keys and values
+    here.  Pass B runs them right to left as ordinary forward + backward steps: a chunk attends to the frozen prefix plus its own
+    rows, its backward adds dK / dV for every row it attended to into the fp32 accumulators, and the gradient it takes for its
+    own keys and values is the accumulated one, which by then holds the contributions of all later chunks.
+    Parity: csrc/src/binding/py_train.cpp:649-714, csrc/src/runtime/attention/backend_kvprefix.cpp."""
+
+    def __init__(self, n_chunks: int, chunk_len: int):
+        self.n_chunks, self.chunk_len = int(n_chunks), int(chunk_len)
+        self.index = 0
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.dk: Dict[int, torch.Tensor] = {}
+        self.dv: Dict[int, torch.Tensor] = {}
+
+    def store_kv(self, layer: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        B, Tc = k.shape[:2]
+        if layer not in self.k:
+            shape = (B, self.n_chunks * self.chunk_len) + tuple(k.shape[2:])
+            self.k[layer], self.v[layer] = torch.empty(shape, dtype=k.dtype, device=k.device), torch.empty(shape, dtype=v.dtype, device=v.device)
+        a = self.index * self.chunk_len
+        self.k[layer][:, a:a + Tc].copy_(k)
+        self.v[layer][:, a:a + Tc].copy_(v)
+
+    def grad_buffers(self, layer: int):
+        if layer not in self.dk:
+            self.dk[layer] = torch.zeros(self.k[layer].shape, dtype=torch.float32, device=self.k[layer].device)
+            self.dv[layer] = torch.zeros(self.v[layer].shape, dtype=torch.float32, device=self.v[layer].device)
+        return self.dk[layer], self.dv[layer]
 
 
 class Executor:
@@ -242,12 +277,13 @@ class Executor:
 
     def forward(self, token_ids, position_ids, targets, *, training: bool = True, loss_scale: Any = 1.0,
                 aux_scale: float = 1.0, doc_ids=None, micro_step: int = 0, row_weights=None, kd=None,
-                want_token_losses: bool = False, extras: Optional[Dict[str, Any]] = None) -> Tuple[ExecContext, List[Any]]:
+                want_token_losses: bool = False, extras: Optional[Dict[str, Any]] = None, chunk=None) -> Tuple[ExecContext, List[Any]]:
         """Run the forward graph.  In training mode the LM-head op also produces d_x / d_w (fused loss backward)."""
         ctx = self.new_context(token_ids, training)
         ctx.loss_scale, ctx.aux_scale, ctx.doc_ids, ctx.micro_step = loss_scale, aux_scale, doc_ids, micro_step
         ctx.row_weights, ctx.kd, ctx.want_token_losses = row_weights, kd, want_token_losses
         ctx.extras = dict(extras or {})
+        ctx.chunk = chunk
         ctx.phase = "fwd"
         g = self.cm.fwd
         env = {"token_ids": token_ids, "position_ids": position_ids, "targets": targets}

@@ -214,14 +214,14 @@ class CudaOps(RefOps):
     def flash_attention(self, ctx, op, qkv):
         from ..ops import attention as att_ops
 
-        if att_ops.native_supported(op.attrs, qkv, ctx) and self.attention_impl in ("auto", "native"):
+        if ctx.chunk is None and att_ops.native_supported(op.attrs, qkv, ctx) and self.attention_impl in ("auto", "native"):
             return att_ops.forward(self.ext, op.attrs, qkv, ctx)
-        return super().flash_attention(ctx, op, qkv)
+        return super().flash_attention(ctx, op, qkv)  # incl. chunked sequences: blockwise PyTorch attention against the key/value prefix
 
     def flash_attention_backward(self, ctx, op, d_att, qkv, att, lse):
         from ..ops import attention as att_ops
 
-        if torch.is_tensor(lse):
+        if torch.is_tensor(lse) and ctx.chunk is None:
             return att_ops.backward(self.ext, op.attrs, d_att, qkv, att, lse, ctx)
         return super().flash_attention_backward(ctx, op, d_att, qkv, att, lse)
 

@@ -284,7 +284,81 @@ class RefOps:
         x = qkv.reshape(B, T, Hq + 2 * Hkv, D)
         return x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
 
+    # ------------------------------------------------------------------ attention against a key / value prefix (chunked sequences)
+    @staticmethod
+    def _prefix_mask(Tc, q0, k0, kn, a, device):
+        """Additive mask for queries at absolute positions q0.. against keys k0..k0+kn."""
+        qi = (q0 + torch.arange(Tc, device=device))[:, None]
+        kj = (k0 + torch.arange(kn, device=device))[None, :]
+        ok = kj <= qi if a.get("causal", True) else torch.ones(Tc, kn, dtype=torch.bool, device=device)
+        if a.get("window", 0):
+            ok = ok & ((qi - kj) < a["window"])
+        return torch.zeros(Tc, kn, device=device).masked_fill(~ok, float("-inf"))
+
+    def _chunk_attention(self, ctx, op, qkv):
+        """Queries of the current chunk against all keys up to its end, one key block (= chunk) at a time with a running
+        log-sum-exp, so the score matrix never exceeds chunk x chunk."""
+        a, cs = op.attrs, ctx.chunk
+        if ctx.doc_ids is not None:
+            raise NotImplementedError("chunked-sequence training does not combine with packed documents")
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        q, k, v = self._split_heads(qkv, a)
+        B, Tc = qkv.shape[:2]
+        cs.store_kv(ctx.layer, k, v)
+        G, c, L = Hq // Hkv, cs.index, cs.chunk_len
+        qf = q.float().permute(0, 2, 1, 3)
+        m = torch.full((B, Hq, Tc), float("-inf"), device=qkv.device)
+        den = torch.zeros(B, Hq, Tc, device=qkv.device)
+        acc = torch.zeros(B, Hq, Tc, D, device=qkv.device)
+        for j in range(c + 1):
+            kn = Tc if j == c else L
+            kf = cs.k[ctx.layer][:, j * L:j * L + kn].float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+            vf = cs.v[ctx.layer][:, j * L:j * L + kn].float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+            s = qf @ kf.transpose(-1, -2) * scale + self._prefix_mask(Tc, c * L, j * L, kn, a, qkv.device)
+            m_new = torch.maximum(m, s.amax(-1))
+            safe = torch.where(torch.isfinite(m_new), m_new, torch.zeros_like(m_new))  # rows with nothing visible yet
+            alpha = torch.exp(torch.where(torch.isfinite(m), m - safe, torch.full_like(m, float("-inf"))))
+            p = torch.exp(s - safe.unsqueeze(-1))
+            den = den * alpha + p.sum(-1)
+            acc = acc * alpha.unsqueeze(-1) + p @ vf
+            m = m_new
+        o = acc / den.unsqueeze(-1)
+        lse = m + torch.log(den)
+        return o.permute(0, 2, 1, 3).reshape(B, Tc, Hq * D).to(qkv.dtype), lse.permute(0, 2, 1).contiguous()
+
+    def _chunk_attention_backward(self, ctx, op, d_att, qkv, att, lse):
+        a, cs = op.attrs, ctx.chunk
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        B, Tc = qkv.shape[:2]
+        G, c, L = Hq // Hkv, cs.index, cs.chunk_len
+        q, _, _ = self._split_heads(qkv, a)
+        qf = q.float().permute(0, 2, 1, 3)
+        do = d_att.float().reshape(B, Tc, Hq, D).permute(0, 2, 1, 3)
+        o = att.float().reshape(B, Tc, Hq, D).permute(0, 2, 1, 3)
+        delta = (do * o).sum(-1, keepdim=True)
+        lse_h = lse.permute(0, 2, 1).unsqueeze(-1)
+        dk_acc, dv_acc = cs.grad_buffers(ctx.layer)
+        dq = torch.zeros_like(qf)
+        for j in range(c + 1):
+            kn = Tc if j == c else L
+            rows = slice(j * L, j * L + kn)
+            kf = cs.k[ctx.layer][:, rows].float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+            vf = cs.v[ctx.layer][:, rows].float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+            s = qf @ kf.transpose(-1, -2) * scale + self._prefix_mask(Tc, c * L, j * L, kn, a, qkv.device)
+            p = torch.exp(s - lse_h)
+            ds = p * (do @ vf.transpose(-1, -2) - delta) * scale
+            dq += ds @ kf
+            dk_acc[:, rows] += (ds.transpose(-1, -2) @ qf).reshape(B, Hkv, G, kn, D).sum(2).permute(0, 2, 1, 3)
+            dv_acc[:, rows] += (p.transpose(-1, -2) @ do).reshape(B, Hkv, G, kn, D).sum(2).permute(0, 2, 1, 3)
+        own = slice(c * L, c * L + Tc)  # by now these rows also hold what the later chunks contributed
+        out = torch.cat([dq.permute(0, 2, 1, 3), dk_acc[:, own], dv_acc[:, own]], dim=2)
+        return (out.reshape(qkv.shape).to(qkv.dtype),)
+
     def flash_attention(self, ctx, op, qkv):
+        if ctx.chunk is not None:
+            return self._chunk_attention(ctx, op, qkv)
         a = op.attrs
         Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
         scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
@@ -318,6 +392,8 @@ class RefOps:
         return m
 
     def flash_attention_backward(self, ctx, op, d_att, qkv, att, lse):
+        if ctx.chunk is not None:
+            return self._chunk_attention_backward(ctx, op, d_att, qkv, att, lse)
         a = op.attrs
         Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
         scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)

@@ -68,6 +68,7 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    sequence_chunks: int = 1    # > 1: each sequence is trained in this many pieces against a key/value prefix (attention models only)
     long_context: bool = False  # tiled MLP: tile = min(tokens, hidden size) rows, recomputed per tile in backward (dense models)
     cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
     normuon_momentum: float = 0.95
@@ -321,11 +322,16 @@ class Trainer:
         for i in range(GA):
             self.store.begin_micro_step(i, GA)
             sl = slice(i * B, (i + 1) * B)
-            ctx, outs = self.executor.forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale=loss_scale, aux_scale=aux_scale,
-                                                       doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i,
-                                                       row_weights=row_weights[sl] if row_weights is not None else None,
-                                                       kd=dict(kd, idx=kd["idx"][sl], logp=kd["logp"][sl]) if kd is not None else None,
-                                                       extras=self._extras(sl))
+            if cfg.sequence_chunks > 1:
+                if doc_ids is not None or row_weights is not None or kd is not None or self._visual is not None:
+                    raise NotImplementedError("sequence_chunks runs the plain next-token objective on unpacked, text-only rows")
+                ctx, outs = self._chunked_forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale, aux_scale, i, GA)
+            else:
+                ctx, outs = self.executor.forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale=loss_scale, aux_scale=aux_scale,
+                                                           doc_ids=doc_ids[sl] if doc_ids is not None else None, micro_step=i,
+                                                           row_weights=row_weights[sl] if row_weights is not None else None,
+                                                           kd=dict(kd, idx=kd["idx"][sl], logp=kd["logp"][sl]) if kd is not None else None,
+                                                           extras=self._extras(sl))
             loss_sum += outs[0]
             if len(outs) > 1 and outs[1] is not None:
                 aux_sum += outs[1] * aux_scale
@@ -335,6 +341,37 @@ class Trainer:
             self.lora.reduce_grads()
         self.store.finish_reduce()
         return {"loss_sum": loss_sum, "n_valid": n_valid, "aux": aux_sum}
+
+    def _chunked_forward_backward(self, inp, pos, tgt, loss_scale, aux_scale, micro_index: int, micro_total: int):
+        """One micro-batch of long rows in ``sequence_chunks`` pieces: pass A fills the per-layer key/value prefix left to
+        right (block stack only, nothing saved), pass B walks right to left doing forward + backward per piece, so activation
+        memory is that of one piece while keys / values (and their fp32 gradient accumulators) cover the whole row."""
+        from .executor import ChunkState
+
+        N, T = self.cfg.sequence_chunks, inp.shape[1]
+        if T % N:
+            raise ValueError(f"sequence length {T} is not divisible by sequence_chunks={N}")
+        Tc = T // N
+        ex = self.executor
+        cs = ChunkState(N, Tc)
+        for c in range(N):
+            cs.index = c
+            cols = slice(c * Tc, (c + 1) * Tc)
+            ctx = ex.new_context(inp[:, cols], False)
+            ctx.chunk = cs
+            ex.stage_forward(ctx, (0, self.cm.n_layers), True, False, pos[:, cols].contiguous(), token_ids=inp[:, cols].contiguous())
+            ex.detach_state()
+        total = None
+        for k, c in enumerate(reversed(range(N))):
+            cs.index = c
+            cols = slice(c * Tc, (c + 1) * Tc)
+            self.store.begin_micro_step(micro_index * N + k, micro_total * N)
+            ctx, outs = ex.forward_backward(inp[:, cols].contiguous(), pos[:, cols].contiguous(), tgt[:, cols].contiguous(), loss_scale=loss_scale,
+                                            aux_scale=aux_scale / N, micro_step=micro_index * N + k, chunk=cs)
+            total = list(outs) if total is None else [a + b if (a is not None and b is not None) else a for a, b in zip(total, outs)]
+        if len(total) > 1 and total[1] is not None:
+            total[1] = total[1] / N  # the auxiliary loss is a per-piece mean
+        return ctx, total
 
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of the (already reduced) gradients, as a device scalar."""
