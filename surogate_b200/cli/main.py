@@ -1,7 +1,7 @@
 """``surogate`` command: argparse front end that dispatches to the workflow modules.
 
 Commands: sft, pt, merge, tokenize, debug, dpo, grpo, grpo-infer, grpo-orch, distill-capture,
-transplant-tokenizer, eval, export, chat, info.
+transplant-tokenizer, eval, export, chat, monitor, info.
 
 Parity: surogate/cli/main.py:42-58 (COMMAND_MAPPING), :193-204 (cli_main).
 """
@@ -28,6 +28,7 @@ COMMAND_MAPPING: Dict[str, str] = {
     "export": "surogate_b200.cli.export",
     "info": "surogate_b200.cli.info",
     "chat": "surogate_b200.cli.chat",
+    "monitor": "surogate_b200.cli.monitor",
 }
 
 BANNER = r"""

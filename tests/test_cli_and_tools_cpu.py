@@ -136,3 +136,31 @@ def test_upcycle_quantize_and_generate(tmp_path):
     ref = load_file(os.path.join(src, "model.safetensors"))[name].float()
     assert ((back - ref).norm() / ref.norm()).item() < 0.05
     assert json.load(open(os.path.join(q_dir, "config.json")))["quantization_config"]["quant_method"] == "fp8"
+
+
+def test_monitor_tails_the_metrics_feed(tmp_path, capsys):
+    """The dashboard reads the feed incrementally (partial last lines wait, a truncated file restarts) and renders a frame."""
+    from surogate_b200.cli import monitor
+
+    feed = tmp_path / "metrics.jsonl"
+    with open(feed, "w") as f:
+        f.write(json.dumps({"log": "options", "config": {"run_name": "demo", "max_steps": 40}}) + "\n")
+        for i in range(20):
+            f.write(json.dumps({"log": "step", "step": i + 1, "loss": 3.0 - 0.1 * i, "lr": 1e-3, "norm": 1.5, "tps": 1000.0 + i}) + "\n")
+        f.write(json.dumps({"log": "eval", "step": 20, "loss": 1.25}) + "\n")
+        f.write(json.dumps({"log": "gpu", "index": 0, "gpu_util": 90, "mem_used": 2**34, "mem_total": 2**35}) + "\n")
+        f.write('{"log": "step", "step": 21, "lo')  # writer is mid-line
+    st = monitor.FeedState(str(feed))
+    assert st.poll() == 23 and st.steps[-1] == 20 and st.max_steps == 40 and st.run_name == "demo"
+    with open(feed, "a") as f:
+        f.write('ss": 0.9, "lr": 0.001, "norm": 1.0, "tps": 1100.0}\n')
+    assert st.poll() == 1 and st.steps[-1] == 21 and abs(st.series["loss"][-1] - 0.9) < 1e-9
+    frame = monitor.render(st, 100)
+    assert "TRAINING LOSS" in frame and "step 21/40" in frame and "gpu0" in frame and "EVAL" in frame and "demo" in frame
+    rows = monitor.chart([3.0, 2.0, 1.0], 10, 4)
+    assert len(rows) == 4 and "█" in rows[-1]
+    with open(feed, "w") as f:
+        f.write(json.dumps({"log": "step", "step": 1, "loss": 5.0, "lr": 1e-3, "norm": 1.0, "tps": 10.0}) + "\n")
+    assert st.poll() == 1 and st.steps == [1]
+    assert monitor.main(["--feed", str(feed), "--once"]) == 0
+    assert "TRAINING LOSS" in capsys.readouterr().out
