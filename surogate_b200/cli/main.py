@@ -1,7 +1,7 @@
 """``surogate`` command: argparse front end that dispatches to the workflow modules.
 
 Commands: sft, pt, merge, tokenize, debug, dpo, grpo, grpo-infer, grpo-orch, distill-capture,
-transplant-tokenizer, eval, export, chat, monitor, info.
+transplant-tokenizer, eval, export, chat, monitor, vf-init, vf-eval, info.
 
 Parity: surogate/cli/main.py:42-58 (COMMAND_MAPPING), :193-204 (cli_main).
 """
@@ -29,6 +29,8 @@ COMMAND_MAPPING: Dict[str, str] = {
     "info": "surogate_b200.cli.info",
     "chat": "surogate_b200.cli.chat",
     "monitor": "surogate_b200.cli.monitor",
+    "vf-init": "surogate_b200.cli.vf",
+    "vf-eval": "surogate_b200.cli.vf",
 }
 
 BANNER = r"""

@@ -123,3 +123,71 @@ def test_grpo_trainer_step_raises_rewarded_tokens(tmp_path):
     adv = arr["advantages"]
     assert (lp[m & (adv > 0)].sum() > lp0[m & (adv > 0)].sum()) and (lp[m & (adv < 0)].sum() < lp0[m & (adv < 0)].sum())
     assert np.isfinite(out["loss"]) and out["ratio_mean"] > 0
+
+
+def test_environments_generate_verify_and_evaluate(tmp_path):
+    """Three built-in environments: gold answers are recomputed from the data, an oracle policy scores 1, a wrong one 0, the
+    tool loop feeds lookups back, and a scaffolded environment loads and evaluates."""
+    import json as _json
+    import os
+    import re as _re
+
+    from surogate_b200.cli.vf import init_environment
+    from surogate_b200.grpo.environments import as_reward_fn, evaluate, load_environment
+    from surogate_b200.grpo.environments import markdown_table_qa as mt
+
+    env = load_environment("markdown-table-qa", num_train=40, num_eval=12, seed=1)
+    by_q = {e["prompt"][0]["content"]: e for e in env.dataset + env.eval_dataset}
+
+    def oracle(msgs):
+        e = by_q[msgs[-1]["content"]]
+        return f"<think>work</think>\n{e['answer']}"
+
+    assert msgs_have_system(env, oracle)
+    r = evaluate(env, oracle, 12, 1)
+    assert r["mean_reward"] > 0.99 and r["n"] == 12
+    assert evaluate(env, lambda m: "<think>hm</think>\nbanana -1", 12)["mean_reward"] < 0.05
+    df = mt.parse_markdown_table("| Name | Region | Revenue | Units |\n|---|---|---|---|\n| A | North | 10 | 1 |\n| B | South | 30 | 2 |")
+    assert list(df.columns) == ["Name", "Region", "Revenue", "Units"] and len(df) == 2
+    assert mt.compute_gold("| Name | Region | Revenue | Units |\n|---|---|---|---|\n| A | North | 10 | 1 |\n| B | South | 30 | 2 |", "percentage", "Revenue", "South")["value"] == 75.0
+    assert mt.correctness_reward("<think>x</think> 75.2", 75.0, {"qtype": "percentage"}) == 1.0
+    assert 0 < mt.correctness_reward("the answer is 60", 75.0, {"qtype": "sum"}) < 1
+    scores = as_reward_fn(env)(env.dataset[0], [oracle(env.initial_messages(env.dataset[0])), "no idea"])
+    assert scores[0] > 0.99 and scores[1] < 0.5
+
+    tools = load_environment("multihop-tools", num_train=4, num_eval=4, hops=3, seed=2)
+
+    def tool_user(msgs):  # follows the chain with lookups, then answers
+        ex = next(e for e in tools.eval_dataset + tools.dataset if e["prompt"][0]["content"] == msgs[1]["content"])
+        q = ex["prompt"][0]["content"]
+        field = _re.match(r"What is the (\w+) of", q).group(1)
+        rels = list(reversed(_re.findall(r"the (\w+) of", q)[1:]))
+        start = _re.search(r"of ([A-Z]\w* \w+)\?$", q).group(1)
+        results = [m["content"] for m in msgs if m["role"] == "tool"]
+        ent = start if not results else results[-1]
+        k = len(results)
+        if k < len(rels):
+            return '<tool>{"name": "lookup", "args": {"entity": "%s", "field": "%s"}}</tool>' % (ent, rels[k])
+        if k == len(rels):
+            return '<tool>{"name": "lookup", "args": {"entity": "%s", "field": "%s"}}</tool>' % (ent, field)
+        return f"<answer>{results[-1]}</answer>"
+
+    r2 = evaluate(tools, tool_user, 4)
+    assert r2["mean_reward"] == 1.0 and all(s["turns"] == 4 for s in r2["samples"])
+    assert evaluate(tools, lambda m: "<answer>nowhere</answer>", 4)["mean_reward"] == 0.0
+
+    data = tmp_path / "rows.jsonl"
+    data.write_text("\n".join(_json.dumps({"question": f"capital of country {i}?", "answer": f"city{i}"}) for i in range(5)))
+    ruler = load_environment("ruler-task", dataset_path=str(data), user_template="Q: {question}", system_prompt="Be brief.")
+    assert ruler.dataset[2]["prompt"][0]["content"] == "Q: capital of country 2?"
+    assert ruler.score_group(ruler.dataset[2], ["it is city2", "unknown"]) == [1.0, 0.0]
+
+    root = init_environment("my-task", str(tmp_path / "envs"))
+    assert sorted(os.listdir(root)) == ["README.md", "my_task.py", "pyproject.toml"]
+    mine = load_environment("my-task", path=str(tmp_path / "envs"))
+    assert evaluate(mine, lambda m: "4", 1)["mean_reward"] == 1.0
+
+
+def msgs_have_system(env, policy):
+    msgs = env.initial_messages(env.dataset[0])
+    return msgs[0]["role"] == "system" and msgs[-1]["role"] == "user" and isinstance(policy(msgs), str)
