@@ -63,6 +63,9 @@ class OrchestratorConfig:
     base_url: str = "http://127.0.0.1:8000/v1"
     prompts: str = ""                    # jsonl with {"prompt": str | messages, "answer": optional}
     reward: str = "exact_match"          # name in grpo.rewards.REWARDS or "module:function"
+    environment: str = ""                # an environment id (grpo/environments, or a scaffolded one): supplies prompts and the reward
+    environment_args: Dict[str, Any] = field(default_factory=dict)
+    environments_path: str = "./environments"
     group_size: int = 8                  # rollouts per prompt
     prompts_per_step: int = 8
     max_tokens: int = 512

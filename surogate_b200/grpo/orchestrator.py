@@ -76,6 +76,12 @@ class StepStats:
 class Orchestrator:
     def __init__(self, cfg: OrchestratorConfig, tokenizer, client, transport, policy_version: Callable[[], int], reward_fn=None):
         self.cfg, self.tok, self.client, self.transport = cfg, tokenizer, client, transport
+        self.env = None
+        if cfg.environment and reward_fn is None:  # single-turn scoring of the sampled completions by the environment's rubric
+            from .environments import as_reward_fn, load_environment
+
+            self.env = load_environment(cfg.environment, path=cfg.environments_path, **cfg.environment_args)
+            reward_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
         self.reward_fn = reward_fn or resolve_reward(cfg.reward)
         self.depth = DepthController(cfg.max_async_level, policy_version)
         self.rng = np.random.default_rng(cfg.seed)
@@ -84,6 +90,8 @@ class Orchestrator:
         self.history: List[StepStats] = []
 
     def load_prompts(self, rows: Optional[Sequence[Dict[str, Any]]] = None) -> None:
+        if rows is None and self.env is not None:
+            rows = [dict(ex, prompt=self.env.initial_messages(ex)) for ex in self.env.dataset]
         if rows is None:
             with open(self.cfg.prompts) as f:
                 rows = [json.loads(l) for l in f if l.strip()]
