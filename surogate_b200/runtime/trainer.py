@@ -68,6 +68,7 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    use_cuda_graphs: bool = False  # capture each micro-batch's forward + backward in a CUDA graph (one GPU, dense models, bf16 / fp8 recipes)
     sequence_chunks: int = 1    # > 1: each sequence is trained in this many pieces against a key/value prefix (attention models only)
     long_context: bool = False  # tiled MLP: tile = min(tokens, hidden size) rows, recomputed per tile in backward (dense models)
     cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
@@ -322,7 +323,9 @@ class Trainer:
         for i in range(GA):
             self.store.begin_micro_step(i, GA)
             sl = slice(i * B, (i + 1) * B)
-            if cfg.sequence_chunks > 1:
+            if self._graphs_allowed(doc_ids, row_weights, kd):
+                ctx, outs = self._graphed_forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale, aux_scale, i, GA)
+            elif cfg.sequence_chunks > 1:
                 if doc_ids is not None or row_weights is not None or kd is not None or self._visual is not None:
                     raise NotImplementedError("sequence_chunks runs the plain next-token objective on unpacked, text-only rows")
                 ctx, outs = self._chunked_forward_backward(inp[sl], pos[sl], tgt[sl], loss_scale, aux_scale, i, GA)
@@ -341,6 +344,55 @@ class Trainer:
             self.lora.reduce_grads()
         self.store.finish_reduce()
         return {"loss_sum": loss_sum, "n_valid": n_valid, "aux": aux_sum}
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _graphs_allowed(self, doc_ids, row_weights, kd) -> bool:
+        """Graph replay needs a step whose launches do not depend on Python state that changes between steps: one GPU (the
+        peer-memory collectives pass a barrier epoch as a kernel argument), dense model, no streamed weights or optimizer
+        state, no per-batch side inputs, a recipe without step-dependent seeds, and scaling history already present (the
+        first two steps run eagerly: they also serve as the warm-up that graph capture requires)."""
+        c = self.cfg
+        return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and self.world == 1 and self.lora is None
+                    and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora) and c.sequence_chunks <= 1
+                    and doc_ids is None and row_weights is None and kd is None and self._visual is None and not getattr(self.model, "num_experts", 0)
+                    and type(self.recipe).__name__ in ("BF16Recipe", "Recipe", "FP8HybridRecipe") and self.step_index >= 2)
+
+    def _graphed_forward_backward(self, inp, pos, tgt, loss_scale, aux_scale, index: int, total: int):
+        """One micro-batch through a captured graph.  Inputs are copied into static buffers; there is one graph per
+        (first micro-batch?, last micro-batch?) combination because the first one overwrites the gradient buffers and the
+        later ones accumulate.  All graphs share one memory pool: tensors cached across micro-batches of a step (quantised
+        weights) are produced by the first graph and read by the others."""
+        g = self.__dict__.setdefault("_graphs", {"pool": None, "static": None, "by_key": {}})
+        if g["static"] is None or g["static"]["inp"].shape != inp.shape:
+            g["by_key"].clear()
+            g["static"] = {"inp": inp.clone(), "pos": pos.clone(), "tgt": tgt.clone(), "scale": loss_scale.clone()}
+            g["pool"] = torch.cuda.graph_pool_handle()
+        st = g["static"]
+        st["inp"].copy_(inp)
+        st["pos"].copy_(pos)
+        st["tgt"].copy_(tgt)
+        st["scale"].copy_(loss_scale)
+        key = (index == 0, index == total - 1)
+        self.store.begin_micro_step(index, total)
+        entry = g["by_key"].get(key)
+        if entry is None:
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph, pool=g["pool"], capture_error_mode="thread_local"):  # other threads (data prefetch) may pin memory meanwhile
+                    ctx, outs = self.executor.forward_backward(st["inp"], st["pos"], st["tgt"], loss_scale=st["scale"], aux_scale=aux_scale, micro_step=index)
+            except Exception as e:  # noqa: BLE001 - an op in this configuration is not capturable: nothing ran, so run the step eagerly from here on
+                import warnings
+
+                warnings.warn(f"CUDA graph capture failed ({type(e).__name__}: {e}); continuing without graphs")
+                self.cfg.use_cuda_graphs = False
+                g["by_key"].clear()
+                self.store.begin_micro_step(index, total)
+                return self.executor.forward_backward(inp, pos, tgt, loss_scale=loss_scale, aux_scale=aux_scale, micro_step=index)
+            entry = g["by_key"][key] = (graph, ctx, outs)
+        entry[0].replay()  # capture records without executing, so a freshly captured graph is replayed too
+        self.graph_replays = getattr(self, "graph_replays", 0) + 1
+        return entry[1], entry[2]
 
     def _chunked_forward_backward(self, inp, pos, tgt, loss_scale, aux_scale, micro_index: int, micro_total: int):
         """One micro-batch of long rows in ``sequence_chunks`` pieces: pass A fills the per-layer key/value prefix left to

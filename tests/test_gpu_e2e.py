@@ -148,3 +148,38 @@ def test_long_context_tiled_mlp_matches_untiled():
     for name in gb:
         err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
         assert err < 0.02, (name, float(err))
+
+
+@pytest.mark.parametrize("recipe,optimizer", [("bf16", "adamw"), ("fp8_hybrid", "adamw_8bit")])
+def test_cuda_graph_steps_match_eager_steps(recipe, optimizer):
+    """Forward + backward of each micro-batch replayed from a CUDA graph (first two steps eager, then captured: one graph for
+    the micro-batch that overwrites the gradients, one for the one that accumulates) follows the eager trajectory."""
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    def run(graphs):
+        cfg = TrainerConfig(model=MODEL, batch_size=2, grad_accum=2, seq_len=256, recipe=recipe, optimizer=optimizer, backend="cuda", learning_rate=1e-3,
+                            lmhead_chunk_rows=200, use_cuda_graphs=graphs)
+        tr = Trainer(cfg, device=torch.device("cuda:0"))
+        tr.init_weights(seed=0)
+        out = []
+        for s in range(6):
+            x, y = _batch(s, B=4)
+            out.append(tr.step(x, y)["loss"])
+        return out, getattr(tr, "graph_replays", 0), tr.cfg.use_cuda_graphs
+
+    eager, n0, _ = run(False)
+    graphed, n1, still_on = run(True)
+    assert n0 == 0 and still_on and n1 == 4 * 2, (n1, still_on)  # steps 3..6, two micro-batches each
+    for a, b in zip(eager, graphed):
+        assert abs(a - b) < 2e-3 * abs(a), (eager, graphed)
+
+
+def test_sequence_chunks_match_the_unchunked_step_on_gpu():
+    x, y = _batch(9)
+    a, b = _trainer("cuda", sequence_chunks=2), _trainer("cuda")
+    ra, rb = a.forward_backward(x, y), b.forward_backward(x, y)
+    assert abs(float(ra["loss_sum"]) - float(rb["loss_sum"])) < 5e-3 * abs(float(rb["loss_sum"]))
+    ga, gb = a.get_gradients(), b.get_gradients()
+    for name in gb:
+        err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
+        assert err < 0.03, (name, float(err))
