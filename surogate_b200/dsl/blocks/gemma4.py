@@ -19,8 +19,14 @@ _P = "model.layers.{L}"
 
 
 class Gemma4Attention(Module):
-    def __init__(self, d_model, num_query_heads, num_kv_heads, head_size, window, rope_theta, rope_scaling, k_eq_v, eps, prefix=f"{_P}.self_attn"):
+    """``kv_role``: "" (own keys / values), "producer" (own, and published under ``kv_key`` for later layers) or "shared"
+    (queries only; keys / values come from the producer of the same attention kind, the layer's own k / v weights stay
+    untouched in the checkpoint)."""
+
+    def __init__(self, d_model, num_query_heads, num_kv_heads, head_size, window, rope_theta, rope_scaling, k_eq_v, eps, prefix=f"{_P}.self_attn",
+                 kv_role: str = "", kv_key: str = ""):
         super().__init__()
+        self.kv_role, self.kv_key = kv_role, kv_key
         self.Hq, self.Hkv, self.D, self.window, self.k_eq_v = num_query_heads, num_kv_heads, head_size, int(window or 0), bool(k_eq_v)
         self.fn_attrs = dict(num_q_heads=num_query_heads, num_kv_heads=num_kv_heads, head_dim=head_size, eps=eps, rope_theta=float(rope_theta),
                              rope_scaling=dict(rope_scaling) if rope_scaling else None, k_eq_v=self.k_eq_v)
@@ -38,9 +44,19 @@ class Gemma4Attention(Module):
         self.declare_param("k_norm_weight", (head_size,), init="ones", decay=False, hf=hf.direct(f"{a}.k_norm.weight"))
 
     def forward(self, x, position_ids):
-        qkv = F.matmul(x, self.p("qkv_weight"), name="qkv", role="qkv")
         packed = x.shape[:-1] + ((self.Hq + 2 * self.Hkv) * self.D,)
-        qkv = F.torch_fn("gemma4_qkv_norm_rope", [qkv, self.p("q_norm_weight"), self.p("k_norm_weight"), position_ids], [("qkv_rope", packed, "act")], **self.fn_attrs)
+        if self.kv_role == "shared":
+            qd = self.Hq * self.D
+            x = F.torch_fn("keep_params", [x, self.p("k_norm_weight")], [("x_keep", x.shape, "act")])
+            qkv_all = F.matmul(x, self.p("qkv_weight"), name="qkv", role="qkv")  # the k / v columns are computed and dropped: one fused weight per layer kind
+            q = F.torch_fn("slice_last", [qkv_all], [("q_only", x.shape[:-1] + (qd,), "act")], start=0, size=qd)
+            attrs = {k: v for k, v in self.fn_attrs.items() if k != "k_eq_v"}
+            qkv = F.torch_fn("gemma4_q_norm_rope_shared", [q, self.p("q_norm_weight"), position_ids], [("qkv_rope", packed, "act")], shared_in=[self.kv_key], **attrs)
+        else:
+            qkv = F.matmul(x, self.p("qkv_weight"), name="qkv", role="qkv")
+            extra = {"shared_out": [[self.kv_key, 0]]} if self.kv_role == "producer" else {}
+            qkv = F.torch_fn("gemma4_qkv_norm_rope", [qkv, self.p("q_norm_weight"), self.p("k_norm_weight"), position_ids], [("qkv_rope", packed, "act")],
+                             **self.fn_attrs, **extra)
         att, _ = F.flash_attention(qkv, num_q_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, causal=True, window=self.window, softmax_scale=1.0)
         return F.matmul(att, self.p("out_weight"), name="att_out", role="out")
 
@@ -79,10 +95,16 @@ class Gemma4Block(Block):
     _name_remap_ = DENSE_BLOCK_NAME_REMAP
 
     def __init__(self, d_model, num_query_heads, num_kv_heads, head_size, d_ff, window=0, rope_theta=10000.0, rope_scaling=None, k_eq_v=False, eps=1e-6,
-                 moe=False, moe_d_ff=0, num_experts=0, top_k=0, ep_size=1):
+                 moe=False, moe_d_ff=0, num_experts=0, top_k=0, ep_size=1, kv_role="", kv_key="", d_pli=0):
         super().__init__()
+        self.eps, self.d_pli = eps, int(d_pli)
         self.attn_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.input_layernorm.weight")
-        self.self_attn = Gemma4Attention(d_model, num_query_heads, num_kv_heads, head_size, window, rope_theta, rope_scaling, k_eq_v, eps)
+        self.self_attn = Gemma4Attention(d_model, num_query_heads, num_kv_heads, head_size, window, rope_theta, rope_scaling, k_eq_v, eps,
+                                         kv_role=kv_role, kv_key=kv_key)
+        if self.d_pli:
+            self.declare_param("pli_gate_weight", (self.d_pli, d_model), hf=hf.direct(f"{_P}.per_layer_input_gate.weight"))
+            self.declare_param("pli_proj_weight", (d_model, self.d_pli), hf=hf.direct(f"{_P}.per_layer_projection.weight"))
+            self.declare_param("pli_norm_weight", (d_model,), init="ones", decay=False, hf=hf.direct(f"{_P}.post_per_layer_input_norm.weight"))
         self.post_attn_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.post_attention_layernorm.weight", out_name="post_attn_ln")
         self.mlp_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.pre_feedforward_layernorm.weight")
         self.mlp = GenericMLP(d_model, d_ff, config=MLPConfig(activation="geglu"))
@@ -105,6 +127,10 @@ class Gemma4Block(Block):
             m2 = self.post_moe_norm(self.experts(stream, self.pre_moe_norm(stream)))  # router and experts read the un-normalised stream
             m = F.add(m1, m2, name="mlp_plus_moe")
         m = self.post_mlp_norm(m)
+        if self.d_pli:  # the per-layer input acts on the hidden state after the feed-forward residual add
+            stream = F.add(stream, m, name="hidden_after_mlp")
+            m = F.torch_fn("gemma4_pli_apply", [stream, self.p("pli_gate_weight"), self.p("pli_proj_weight"), self.p("pli_norm_weight")],
+                           [("pli_out", stream.shape, "act")], pass_layer=True, shared_in=["pli"], eps=self.eps)
         s = self.p("layer_scalar")
         out = F.torch_fn("scale_by_buffer", [m, s], [("mlp_scaled", m.shape, "act")])
         stream = F.torch_fn("scale_by_buffer", [stream, s], [("stream_scaled", stream.shape, "act")])

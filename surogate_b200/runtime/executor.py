@@ -68,6 +68,9 @@ class ExecContext:
         self.extras: Dict[str, Any] = {}
         # chunked-sequence training: the attention op reads / extends the per-layer key-value prefix kept here
         self.chunk: Optional["ChunkState"] = None
+        # values that cross layer boundaries outside the block interface, and the gradients flowing back to their producers
+        self.shared: Dict[str, torch.Tensor] = {}
+        self.shared_grad: Dict[str, torch.Tensor] = {}
 
     def eval_shape(self, shape) -> Tuple[int, ...]:
         return eval_shape(tuple(shape), self.dims)

@@ -74,39 +74,62 @@ class RefOps:
     # ------------------------------------------------------------------ generic torch-function op
     @staticmethod
     def _fn_kwargs(op, ctx=None):
-        kw = {k: v for k, v in op.attrs.items() if k not in ("fn", "n_out", "n_in", "side_inputs", "pass_layer")}
+        kw = {k: v for k, v in op.attrs.items() if k not in ("fn", "n_out", "n_in", "side_inputs", "pass_layer", "shared_in", "shared_out")}
         for name in op.attrs.get("side_inputs", ()):  # per-batch tensors outside the graph (None when the batch has none)
             kw[name] = ctx.extras.get(name) if ctx is not None else None
         if op.attrs.get("pass_layer"):
             kw["layer"] = ctx.layer if ctx is not None else None
         return kw
 
+    # ``shared_out`` = [[key, output index], ...]: the output is also left in ``ctx.shared[key]`` for ops of LATER layers that
+    # name the key in ``shared_in`` (they get it as a keyword tensor).  Their backward runs first and accumulates the gradient
+    # of the shared tensor in ``ctx.shared_grad[key]``; the producer's backward adds it to that output's incoming gradient.
+    # This is how a value crosses layer boundaries without being part of the (x, residual) interface of a block:
+    # keys / values reused by later layers, per-layer input embeddings computed once at the top.
     def torch_fn(self, ctx, op, *ins):
         from .torch_fns import TORCH_FNS
 
+        kw = self._fn_kwargs(op, ctx)
+        for key in op.attrs.get("shared_in", ()):
+            kw[key] = ctx.shared[key]
         with torch.no_grad():
-            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op, ctx))
-        return out if isinstance(out, tuple) else (out,)
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **kw)
+        outs = out if isinstance(out, tuple) else (out,)
+        for key, idx in op.attrs.get("shared_out", ()):
+            ctx.shared[key] = outs[idx]
+        return outs
 
     def torch_fn_backward(self, ctx, op, *args):
         from .torch_fns import TORCH_FNS
 
         n_out = op.attrs["n_out"]
-        d_outs, ins = args[:n_out], list(args[n_out:])
+        d_outs, ins = list(args[:n_out]), list(args[n_out:])
+        for key, idx in op.attrs.get("shared_out", ()):
+            extra = ctx.shared_grad.pop(key, None)
+            if extra is not None:
+                d_outs[idx] = extra if d_outs[idx] is None else d_outs[idx] + extra.to(d_outs[idx].dtype)
         req = []
         for i, t in enumerate(ins):
             if torch.is_tensor(t) and t.is_floating_point():
                 ins[i] = t.detach().requires_grad_(True)
                 req.append(i)
+        kw = self._fn_kwargs(op, ctx)
+        shared = []
+        for key in op.attrs.get("shared_in", ()):
+            kw[key] = ctx.shared[key].detach().requires_grad_(True)
+            shared.append(key)
         with torch.enable_grad():
-            out = TORCH_FNS[op.attrs["fn"]](*ins, **self._fn_kwargs(op, ctx))
+            out = TORCH_FNS[op.attrs["fn"]](*ins, **kw)
             outs = out if isinstance(out, tuple) else (out,)
             pairs = [(o, d) for o, d in zip(outs, d_outs) if d is not None and torch.is_tensor(o) and o.requires_grad]
-            gs = torch.autograd.grad([o for o, _ in pairs], [ins[i] for i in req],
+            gs = torch.autograd.grad([o for o, _ in pairs], [ins[i] for i in req] + [kw[k] for k in shared],
                                      [d.to(o.dtype) if torch.is_tensor(d) else torch.full_like(o, float(d)) for o, d in pairs], allow_unused=True)
         res = [None] * len(ins)
         for i, g in zip(req, gs):
             res[i] = g
+        for key, g in zip(shared, gs[len(req):]):
+            if g is not None:
+                ctx.shared_grad[key] = g if key not in ctx.shared_grad else ctx.shared_grad[key] + g
         return tuple(res)
 
     # ------------------------------------------------------------------ simple ops

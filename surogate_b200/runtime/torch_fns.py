@@ -129,6 +129,53 @@ def gemma4_qkv_norm_rope(qkv, qn_w, kn_w, pos, *, num_q_heads: int, num_kv_heads
     return torch.cat([rope(q), rope(k), v], dim=-2).reshape(*lead, (Hq + 2 * Hkv) * D).to(qkv.dtype)
 
 
+@register("gemma4_q_norm_rope_shared")
+def gemma4_q_norm_rope_shared(q, qn_w, pos, *, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, rope_theta: float, rope_scaling=None, **shared):
+    """Query side of a layer that reuses an earlier layer's keys and values: normalise and rotate q, take k and v from the
+    producer's packed tensor (the one keyword tensor in ``shared``)."""
+    from ..config.rope import rope_inv_freq
+
+    (kv,) = shared.values()
+    lead, Hq, Hkv, D = q.shape[:-1], num_q_heads, num_kv_heads, head_dim
+    qh = _rms(q.float().reshape(*lead, Hq, D), eps) * qn_w.float()
+    inv, att = rope_inv_freq(D, rope_theta, rope_scaling, None, device=q.device)
+    ang = pos.float().unsqueeze(-1) * inv
+    cos, sin = (ang.cos() * att).unsqueeze(-2), (ang.sin() * att).unsqueeze(-2)
+    a, b = qh[..., :D // 2], qh[..., D // 2:]
+    qh = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+    return torch.cat([qh.reshape(*lead, Hq * D).to(q.dtype), kv[..., Hq * D:].to(q.dtype)], dim=-1)
+
+
+@register("slice_last")
+def slice_last(x, *, start: int, size: int):
+    return x[..., start:start + size].contiguous()
+
+
+@register("keep_params")
+def keep_params(x, *params):
+    """Identity on ``x``.  Lists parameters that exist in the checkpoint but are not used by this layer (so they are loaded,
+    kept and exported unchanged)."""
+    return x + 0
+
+
+@register("gemma4_pli")
+def gemma4_pli(x, token_ids, emb_w, proj_w, norm_w, *, n_layers: int, d_pli: int, eps: float):
+    """Per-layer input embeddings: a second (scaled) token embedding of width L * P plus a projection of the main embedding,
+    RMS-normalised per layer, averaged with 1/sqrt(2).  Returns (x unchanged, per-layer inputs [B, T, L, P])."""
+    B, T, C = x.shape
+    emb = F.embedding(token_ids.long(), emb_w).float() * float(torch.tensor(d_pli ** 0.5).to(emb_w.dtype))
+    proj = F.linear(x.float(), proj_w.float()) * (C ** -0.5)
+    proj = _rms(proj.reshape(B, T, n_layers, d_pli), eps) * norm_w.float()
+    return x + 0, ((proj + emb.reshape(B, T, n_layers, d_pli)) * (2.0 ** -0.5)).to(x.dtype)
+
+
+@register("gemma4_pli_apply")
+def gemma4_pli_apply(h, gate_w, proj_w, norm_w, *, layer: int, pli, eps: float):
+    """gelu(h W_gate) * per-layer input of this layer -> projection back to the model width -> RMSNorm."""
+    g = F.gelu(F.linear(h, gate_w).float(), approximate="tanh") * pli[:, :, layer].float()
+    return (_rms(F.linear(g.to(h.dtype), proj_w).float(), eps) * norm_w.float()).to(h.dtype)
+
+
 @register("gemma4_router")
 def gemma4_router(x, proj_w, scale, per_expert_scale, *, top_k: int, eps: float):
     """Scale-free RMSNorm, a learned per-channel scale and 1/sqrt(C), linear -> softmax -> top-k renormalised to sum 1, then a

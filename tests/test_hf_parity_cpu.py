@@ -45,6 +45,10 @@ def _cases():
     yield "gemma4", Gemma4TextConfig(**g4)
     yield "gemma4-moe-keqv", Gemma4TextConfig(**{**g4, "tie_word_embeddings": True}, attention_k_eq_v=True, num_global_key_value_heads=1, enable_moe_block=True,
                                                num_experts=4, top_k_experts=2, moe_intermediate_size=32)
+    yield "gemma4-pli-kvshare", Gemma4TextConfig(**{**g4, "num_hidden_layers": 6, "hidden_size_per_layer_input": 8, "vocab_size_per_layer_input": 320,
+                                                    "num_kv_shared_layers": 2, "use_double_wide_mlp": True,
+                                                    "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention",
+                                                                    "sliding_attention", "full_attention"]})
     yield "gpt-oss", GptOssConfig(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                                   intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8, max_position_embeddings=256,
                                   rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
