@@ -34,6 +34,8 @@ class ExecOptions:
     recompute: bool = False
     act_dtype: torch.dtype = torch.float32
     check_finite: bool = False
+    lmhead_drop_ignored_rows: bool = False  # compact away rows with ignored targets before the LM head (one host sync per micro-batch)
+    offload_saved: bool = False              # park each layer's saved tensors (or, with recompute, its input checkpoint) in pinned host memory
     dump_tensors: Optional[Callable[[str, Optional[int], torch.Tensor], None]] = None
 
 
@@ -96,6 +98,102 @@ class ExecContext:
             self.moe_stats.append((self.layer, counts.detach(), probs.detach().mean(0)))
 
 
+class SavedTensorOffload:
+    """Per-layer saved tensors in pinned host memory between a layer's forward and its backward.
+
+    ``push`` starts device -> host copies on a side stream as soon as the layer's forward has produced the tensors and lets the
+    caching allocator reuse the device memory once the copies are done; ``prefetch`` starts the copies back one layer ahead of
+    the backward sweep; ``fetch`` makes the compute stream wait for them.  With per-layer recompute only the layer's input
+    checkpoint is saved, so activation memory on the device stays O(1) in the number of layers.
+    Parity: offload_saved_tensors / offload_residual (csrc/src/runtime/executor/compiled_ops.cpp:982-1055, docs/guides/offloading.md)."""
+
+    MIN_BYTES = 1 << 16
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device)
+        self.free: Dict[Tuple[Tuple[int, ...], torch.dtype], List[torch.Tensor]] = {}
+        self.inflight: Dict[int, Tuple[Dict[str, Any], Any]] = {}
+        self.bytes_out = 0
+
+    def _pinned(self, t: torch.Tensor) -> torch.Tensor:
+        key = (tuple(t.shape), t.dtype)
+        pool = self.free.setdefault(key, [])
+        return pool.pop() if pool else torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+
+    def _out(self, v):
+        if torch.is_tensor(v) and v.is_cuda and v.numel() * v.element_size() >= self.MIN_BYTES:
+            h = self._pinned(v)
+            h.copy_(v, non_blocking=True)
+            v.record_stream(self.stream)
+            self.bytes_out += h.numel() * h.element_size()
+            return ("host", h)
+        return ("keep", v)
+
+    def push(self, saved: Dict[str, Any]) -> Dict[str, Any]:
+        ready = torch.cuda.Event()
+        ready.record()
+        self.stream.wait_event(ready)
+        out: Dict[str, Any] = {}
+        with torch.cuda.stream(self.stream):
+            for k, v in saved.items():
+                if hasattr(v, "data") and hasattr(v, "scale_inv") and not torch.is_tensor(v):  # quantised activation: move its payload
+                    out[k] = ("fp8", v, self._out(v.data), self._out(v.hp) if getattr(v, "hp", None) is not None else None)
+                    v.data = None
+                    if getattr(v, "hp", None) is not None:
+                        v.hp = None
+                else:
+                    out[k] = self._out(v)
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        return {"__offloaded__": out, "__done__": done}
+
+    def _in(self, item):
+        kind, v = item
+        if kind == "keep":
+            return v, None
+        d = torch.empty(v.shape, dtype=v.dtype, device=self.device)
+        d.copy_(v, non_blocking=True)
+        return d, v
+
+    def prefetch(self, layer: int, parked: Dict[str, Any]) -> None:
+        if layer in self.inflight or "__offloaded__" not in parked:
+            return
+        self.stream.wait_event(parked["__done__"])
+        out: Dict[str, Any] = {}
+        used: List[torch.Tensor] = []
+        with torch.cuda.stream(self.stream):
+            for k, item in parked["__offloaded__"].items():
+                if item[0] == "fp8":
+                    _, obj, data, hp = item
+                    obj.data, h = self._in(data)
+                    used += [h] if h is not None else []
+                    if hp is not None:
+                        obj.hp, h2 = self._in(hp)
+                        used += [h2] if h2 is not None else []
+                    out[k] = obj
+                else:
+                    out[k], h = self._in(item)
+                    used += [h] if h is not None else []
+        ev = torch.cuda.Event()
+        ev.record(self.stream)
+        self.inflight[layer] = (out, (ev, used))
+
+    def fetch(self, layer: int, parked: Dict[str, Any]) -> Dict[str, Any]:
+        if "__offloaded__" not in parked:
+            return parked
+        self.prefetch(layer, parked)
+        out, (ev, used) = self.inflight.pop(layer)
+        torch.cuda.current_stream(self.device).wait_event(ev)
+        for v in out.values():
+            for t in ((v,) if torch.is_tensor(v) else (getattr(v, "data", None), getattr(v, "hp", None))):
+                if torch.is_tensor(t) and t.is_cuda:
+                    t.record_stream(torch.cuda.current_stream(self.device))
+        for h in used:  # the pinned buffers are free again once the copies back have been issued and awaited by the consumer
+            self.free.setdefault((tuple(h.shape), h.dtype), []).append(h)
+        return out
+
+
 class ChunkState:
     """Key / value prefix and its gradient accumulators for training one long sequence in ``n_chunks`` pieces.
 
@@ -148,6 +246,7 @@ class Executor:
         self._layer_saved: List[Optional[Dict[str, Any]]] = [None] * self.cm.n_layers
         self._top_env: Dict[str, Any] = {}
         self.layer_range: Optional[Tuple[int, int]] = None  # pipeline stage: the block stack runs only layers [first, last)
+        self.offload = SavedTensorOffload(self.device) if (self.options.offload_saved and self.device.type == "cuda") else None
 
     # ------------------------------------------------------------------ generic graph run
     def _last_use(self, g: Graph) -> Dict[str, int]:
@@ -233,6 +332,8 @@ class Executor:
                 aux_tot[i] = a if aux_tot[i] is None else aux_tot[i] + a
             if ctx.training and not self.options.recompute:
                 self._layer_saved[L] = {k: v for k, v in benv.items() if k in self._saved_sets[bt]}
+            if ctx.training and self.offload is not None and self._layer_saved[L] is not None and L < hi - 1:  # the last layer's backward starts right away
+                self._layer_saved[L] = self.offload.push(self._layer_saved[L])
             self.store.layer_end(L, "fwd")
         ctx.layer = None
         return [x, res] + aux_tot
@@ -249,6 +350,10 @@ class Executor:
             self.store.layer_start(L, "bwd")
             saved = self._layer_saved[L]
             self._layer_saved[L] = None
+            if self.offload is not None:
+                saved = self.offload.fetch(L, saved)
+                if L - 1 >= lo and self._layer_saved[L - 1] is not None:
+                    self.offload.prefetch(L - 1, self._layer_saved[L - 1])  # copies back overlap this layer's backward
             if saved.get("__recompute__"):
                 benv = {k: v for k, v in saved.items() if k != "__recompute__"}
                 ctx.phase = "recompute"

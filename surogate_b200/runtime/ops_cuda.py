@@ -229,6 +229,9 @@ class CudaOps(RefOps):
     def fused_lm_head_loss(self, ctx, op, x, w, targets):
         """Chunked over rows: logits chunk by GEMM (bf16), cross-entropy forward+backward in place, then the
         dgrad / wgrad GEMMs consume the in-place d_logits.  The full [tokens, vocab] matrix never exists."""
+        dropped = self._drop_ignored_rows(ctx, op, x, w, targets)
+        if dropped is not None:
+            return dropped
         if isinstance(x, Fp8Tensor):
             x = x.hp if x.hp is not None else x.dequantize()
         C = x.shape[-1]

@@ -514,9 +514,43 @@ class RefOps:
         return (torch.cat([d_up, d_gate], dim=-1).to(x.dtype),)
 
     # ------------------------------------------------------------------ LM head + loss
+    def _drop_ignored_rows(self, ctx, op, x, w, targets):
+        """Optional compaction before the LM head: rows whose target is ignored (prompt tokens of an instruction dataset,
+        padding) contribute neither loss nor gradient, so only the other rows go through the vocabulary GEMMs.  The row count
+        is data dependent: one host sync per micro-batch sizes the compacted problem.  Returns None when nothing applies.
+        Parity: lmhead_drop_ignored_rows (csrc/src/runtime/core/runtime_options.h)."""
+        if not getattr(ctx.ex.options, "lmhead_drop_ignored_rows", False) or getattr(ctx, "_dropping", False):
+            return None
+        if ctx.row_weights is not None or ctx.kd is not None or ctx.want_token_losses:
+            return None
+        if hasattr(x, "dequantize"):
+            x = x.hp if getattr(x, "hp", None) is not None else x.dequantize()
+        C = x.shape[-1]
+        x2, t = x.reshape(-1, C), targets.reshape(-1)
+        keep = (t != IGNORE_INDEX).nonzero(as_tuple=False).squeeze(1)
+        if keep.numel() == t.numel():
+            return None
+        pad = (-keep.numel()) % 8 if keep.numel() else 8  # keep the row count a multiple of 8 (GEMM tile alignment); padded rows are ignored ones
+        if pad:
+            ignored = (t == IGNORE_INDEX).nonzero(as_tuple=False).squeeze(1)[:pad]
+            keep = torch.cat([keep, ignored])
+        ctx._dropping = True
+        try:
+            out = self.fused_lm_head_loss(ctx, op, x2.index_select(0, keep).unsqueeze(0), w, t.index_select(0, keep).unsqueeze(0))
+        finally:
+            ctx._dropping = False
+        if ctx.training:
+            dx = torch.zeros_like(x2)
+            dx.index_copy_(0, keep, ctx.stash[op.outputs[0]].reshape(-1, C))
+            ctx.stash[op.outputs[0]] = dx.reshape(x.shape)
+        return out
+
     def fused_lm_head_loss(self, ctx, op, x, w, targets):
         """Returns the summed CE over valid tokens.  In training mode also computes d_x (stashed) and d_w now.
         Objective hooks (see ExecContext): per-token weights on the log-likelihood gradient, top-K distillation."""
+        dropped = self._drop_ignored_rows(ctx, op, x, w, targets)
+        if dropped is not None:
+            return dropped
         C = x.shape[-1]
         x2, t = x.reshape(-1, C), targets.reshape(-1).long()
         n = x2.shape[0]

@@ -118,3 +118,22 @@ def test_sequence_chunks_match_the_unchunked_step(arch):
         assert abs(l1 - l4) < 1e-5 and abs(n1 - n4) < 1e-4 * n1, (l1, l4, n1, n4)
         for k in g1:
             assert torch.allclose(g1[k], g4[k], atol=2e-5, rtol=1e-3), k
+
+
+def test_dropping_ignored_rows_before_the_lm_head_changes_nothing():
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=200, d_model=64, n_layers=1, num_query_heads=4, num_kv_heads=2, head_size=16, d_ff=96,
+                 tie_word_embeddings=False)
+    rng = np.random.default_rng(0)
+    tok = rng.integers(0, 200, (2, 33)).astype(np.int32)
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    y[0, :19] = -100
+    y[1, 5:9] = -100
+
+    def run(drop):
+        tr = Trainer(TrainerConfig(model=model, batch_size=2, seq_len=32, zero_level=0, lmhead_drop_ignored_rows=drop, lmhead_chunk_rows=16), device=torch.device("cpu"))
+        tr.init_weights(seed=3)
+        r = tr.forward_backward(x, y)
+        return float(r["loss_sum"]), float(tr.grad_norm()), tr.store.grad_of("lm_head").clone()
+
+    a, b = run(False), run(True)
+    assert abs(a[0] - b[0]) < 1e-4 and abs(a[1] - b[1]) < 1e-5 * a[1] and torch.allclose(a[2], b[2], atol=1e-6)

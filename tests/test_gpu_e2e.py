@@ -183,3 +183,38 @@ def test_sequence_chunks_match_the_unchunked_step_on_gpu():
     for name in gb:
         err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
         assert err < 0.03, (name, float(err))
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_saved_tensors_parked_on_the_host_match_resident_ones(recompute):
+    """Saved activations (or, with recompute, the per-layer input checkpoints) wait in pinned host memory between forward and
+    backward; the step is unchanged."""
+    x, y = _batch(11)
+    model = dict(MODEL, n_layers=4)
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    def run(offload):
+        tr = Trainer(TrainerConfig(model=model, batch_size=2, seq_len=256, recipe="fp8_hybrid", backend="cuda", lmhead_chunk_rows=200, recompute=recompute,
+                                   offload_saved_tensors=offload), device=torch.device("cuda:0"))
+        tr.init_weights(seed=0)
+        r = tr.forward_backward(x, y)
+        return float(r["loss_sum"]), tr.get_gradients(), (tr.executor.offload.bytes_out if tr.executor.offload is not None else 0)
+
+    la, ga, out_a = run(True)
+    lb, gb, _ = run(False)
+    assert out_a > 0 and abs(la - lb) < 1e-3 * abs(lb)
+    for name in gb:
+        err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
+        assert err < 1e-3, (name, float(err))
+
+
+def test_dropping_ignored_rows_on_gpu():
+    x, y = _batch(12)
+    y[0, :150] = -100
+    a, b = _trainer("cuda", lmhead_drop_ignored_rows=True), _trainer("cuda")
+    ra, rb = a.forward_backward(x, y), b.forward_backward(x, y)
+    assert abs(float(ra["loss_sum"]) - float(rb["loss_sum"])) < 2e-3 * abs(float(rb["loss_sum"]))
+    ga, gb = a.get_gradients(), b.get_gradients()
+    for name in gb:
+        err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
+        assert err < 0.02, (name, float(err))
