@@ -162,7 +162,7 @@ class SFTConfig:
     long_context: bool = False
     train_vision: bool = False  # vision-language fine-tuning: rows with images, frozen vision tower, decoder trained (train/vision.py)
     sequence_chunks: int = 1
-    use_cuda_graphs: bool = True
+    use_cuda_graphs: bool = False  # capture forward + backward per micro-batch (one GPU, dense models, bf16 / fp8 recipes)
     # parallelism
     gpus: int = 1
     zero_level: int = 1

@@ -164,3 +164,36 @@ def test_monitor_tails_the_metrics_feed(tmp_path, capsys):
     assert st.poll() == 1 and st.steps == [1]
     assert monitor.main(["--feed", str(feed), "--once"]) == 0
     assert "TRAINING LOSS" in capsys.readouterr().out
+
+
+def test_every_example_configuration_loads_and_validates():
+    """The shipped example YAML files parse into their config classes and pass validation."""
+    import glob
+
+    import yaml
+
+    from surogate_b200.config.sft_config import SFTConfig
+    from surogate_b200.dpo.config import DPOConfig
+    from surogate_b200.grpo.config import GRPOConfig, InferenceConfig, OrchestratorConfig
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    files = sorted(glob.glob(os.path.join(root, "**", "*.yaml"), recursive=True))
+    assert len(files) >= 15
+    for f in files:
+        d = yaml.safe_load(open(f))
+        rel = os.path.relpath(f, root)
+        if rel.startswith("dpo"):
+            cfg = DPOConfig.from_dict(d)
+        elif rel == os.path.join("grpo", "train.yaml"):
+            cfg = GRPOConfig.from_dict(d)
+        elif rel == os.path.join("grpo", "infer.yaml"):
+            cfg = InferenceConfig(**d)
+        elif rel == os.path.join("grpo", "orch.yaml"):
+            cfg = OrchestratorConfig(**d)
+        else:
+            cfg = SFTConfig.from_dict(d)
+        assert cfg.model, rel
+        if hasattr(cfg, "to_trainer_config") and not rel.startswith("grpo"):
+            hf = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=64, num_hidden_layers=8, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=16, intermediate_size=96, vocab_size=320)
+            assert cfg.to_trainer_config(hf).seq_len == cfg.sequence_len, rel
