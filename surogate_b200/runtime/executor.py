@@ -35,6 +35,7 @@ class ExecOptions:
     act_dtype: torch.dtype = torch.float32
     check_finite: bool = False
     lmhead_drop_ignored_rows: bool = False  # compact away rows with ignored targets before the LM head (one host sync per micro-batch)
+    time_breakdown: bool = False             # CUDA-event marks around forward / LM head / backward / optimizer (read with PhaseTimer.totals)
     offload_saved: bool = False              # park each layer's saved tensors (or, with recompute, its input checkpoint) in pinned host memory
     dump_tensors: Optional[Callable[[str, Optional[int], torch.Tensor], None]] = None
 
@@ -96,6 +97,37 @@ class ExecContext:
     def record_moe_stats(self, counts: torch.Tensor, probs: torch.Tensor) -> None:
         if self.phase == "fwd" and self.layer is not None:
             self.moe_stats.append((self.layer, counts.detach(), probs.detach().mean(0)))
+
+
+class PhaseTimer:
+    """Marks on the launching stream; the time between two marks is attributed to the later mark's name.
+    Parity: debug_time_breakdown (csrc/src/runtime/training/model.h:323-333, py_train.cpp:577-597)."""
+
+    def __init__(self, device: torch.device):
+        self.cuda = device.type == "cuda"
+        self.marks: List[Tuple[str, Any]] = []
+
+    def mark(self, name: str) -> None:
+        if self.cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.marks.append((name, e))
+        else:
+            import time
+
+            self.marks.append((name, time.perf_counter()))
+
+    def totals(self) -> Dict[str, float]:
+        """Milliseconds per phase since the last call (synchronises the device once)."""
+        out: Dict[str, float] = {}
+        if self.cuda and self.marks:
+            self.marks[-1][1].synchronize()
+        for (_, a), (name, b) in zip(self.marks, self.marks[1:]):
+            if name == "start":
+                continue
+            out[name + "_ms"] = out.get(name + "_ms", 0.0) + (a.elapsed_time(b) if self.cuda else (b - a) * 1e3)
+        self.marks = []
+        return out
 
 
 class SavedTensorOffload:
@@ -246,6 +278,7 @@ class Executor:
         self._layer_saved: List[Optional[Dict[str, Any]]] = [None] * self.cm.n_layers
         self._top_env: Dict[str, Any] = {}
         self.layer_range: Optional[Tuple[int, int]] = None  # pipeline stage: the block stack runs only layers [first, last)
+        self.timer = PhaseTimer(self.device) if self.options.time_breakdown else None
         self.offload = SavedTensorOffload(self.device) if (self.options.offload_saved and self.device.type == "cuda") else None
 
     # ------------------------------------------------------------------ generic graph run
@@ -264,6 +297,8 @@ class Executor:
         be = self.backend
         params = g.params
         for op in (g.ops if ops is None else ops):
+            if self.timer is not None and op.kind == "fused_lm_head_loss":
+                self.timer.mark("forward")
             if op.kind == "block_stack":
                 outs = self._block_stack_forward(op, env, ctx)
             elif op.kind == "block_stack_backward":
@@ -281,6 +316,8 @@ class Executor:
                 if fn is None:
                     raise NotImplementedError(f"[E030] backend '{be.name}' has no implementation of op '{op.kind}'")
                 outs = fn(ctx, op, *ins)
+            if self.timer is not None and op.kind == "fused_lm_head_loss":
+                self.timer.mark("lm_head")  # in training mode this includes the head's own backward (fused)
             for name, val in zip(op.outputs, outs):
                 if name is None:
                     continue
@@ -393,12 +430,16 @@ class Executor:
         ctx.extras = dict(extras or {})
         ctx.chunk = chunk
         ctx.phase = "fwd"
+        if self.timer is not None:
+            self.timer.mark("start")
         g = self.cm.fwd
         env = {"token_ids": token_ids, "position_ids": position_ids, "targets": targets}
         self.store.group_start("embedding", "fwd")
         keep = (self._top_saved if training else set()) | set(g.outputs)
         self.run_graph(g, env, ctx, keep)
         self._top_env = env
+        if self.timer is not None:
+            self.timer.mark("forward")
         return ctx, [env[o] for o in g.outputs]
 
     def backward(self, ctx: ExecContext) -> None:
@@ -412,6 +453,8 @@ class Executor:
         ctx.phase = "bwd"
         self.run_graph(bg, env, ctx, set())
         self.store.group_end("embedding", "bwd")
+        if self.timer is not None:
+            self.timer.mark("backward")
 
     def forward_backward(self, token_ids, position_ids, targets, **kw):
         ctx, outs = self.forward(token_ids, position_ids, targets, training=True, **kw)

@@ -68,6 +68,7 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    time_breakdown: bool = False            # per-step milliseconds of forward / LM head / backward / optimizer in Trainer.last_time_breakdown
     lmhead_drop_ignored_rows: bool = False  # only rows with a target go through the LM head
     offload_saved_tensors: bool = False     # saved activations (or, with recompute, the per-layer input checkpoints) wait in pinned host memory
     use_cuda_graphs: bool = False  # capture each micro-batch's forward + backward in a CUDA graph (one GPU, dense models, bf16 / fp8 recipes)
@@ -140,7 +141,7 @@ class Trainer:
             self.ep = ExpertParallel(self.comm, cfg.ep_size, self.device, capacity_factor=cfg.ep_capacity_factor)
         self.executor = Executor(self.cm, self.store, self.backend, recipe=self.recipe,
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd, lmhead_drop_ignored_rows=cfg.lmhead_drop_ignored_rows,
-                                                     offload_saved=cfg.offload_saved_tensors), device=self.device, ep=self.ep, lora=self.lora)
+                                                     offload_saved=cfg.offload_saved_tensors, time_breakdown=cfg.time_breakdown), device=self.device, ep=self.ep, lora=self.lora)
         self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
                                        cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd)
         self.streamed = None
@@ -356,7 +357,7 @@ class Trainer:
         first two steps run eagerly: they also serve as the warm-up that graph capture requires)."""
         c = self.cfg
         return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and self.world == 1 and self.lora is None
-                    and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora or c.offload_saved_tensors or c.lmhead_drop_ignored_rows)
+                    and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora or c.offload_saved_tensors or c.lmhead_drop_ignored_rows or c.time_breakdown)
                     and c.sequence_chunks <= 1
                     and doc_ids is None and row_weights is None and kd is None and self._visual is None and not getattr(self.model, "num_experts", 0)
                     and type(self.recipe).__name__ in ("BF16Recipe", "Recipe", "FP8HybridRecipe") and self.step_index >= 2)
@@ -501,7 +502,13 @@ class Trainer:
 
     def step(self, inputs, targets, position_ids=None, lr: Optional[float] = None, kd=None, row_weights=None) -> Dict[str, float]:
         r = self.forward_backward(inputs, targets, position_ids, row_weights=row_weights, kd=kd)
+        timer = self.executor.timer
+        if timer is not None:
+            timer.mark("start")
         norm = self.optimizer_step(lr)
+        if timer is not None:
+            timer.mark("optimizer")
+            self.last_time_breakdown = timer.totals()
         loss = r["loss_sum"].clone()
         if self.world > 1:
             self.comm.all_reduce(loss, "sum")

@@ -248,6 +248,14 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
             kd = {"idx": ki, "logp": kl, "weight": distill.kd_weight, "ce_weight": 1.0 - distill.kd_weight}
         out = trainer.step(x, y, p if (cfg.sample_packing or cfg.train_vision) else None, lr=lr, kd=kd)
         ms = (time.perf_counter() - t0) * 1e3
+        if cfg.debug_time_breakdown and getattr(trainer, "last_time_breakdown", None):
+            logger.log_record("timing", step=step + 1, **{k: round(v, 3) for k, v in trainer.last_time_breakdown.items()})
+        if cfg.debug_memory_breakdown and step == start_step and hasattr(trainer, "memory_breakdown"):
+            mem = dict(trainer.memory_breakdown())
+            if device.type == "cuda":
+                mem.update(cuda_allocated=int(torch.cuda.memory_allocated(device)), cuda_reserved=int(torch.cuda.memory_reserved(device)),
+                           cuda_peak=int(torch.cuda.max_memory_allocated(device)))
+            logger.log_record("memory", step=step + 1, **mem)
         losses.append(out["loss"])
         norms.append(out["norm"])
         phase = phase_det.update(step, out["loss"])

@@ -93,3 +93,20 @@ def test_dpo_step_improves_margin_with_lora_reference():
     hist = [dpo.step(x, y, lr=5e-2) for _ in range(12)]
     assert abs(hist[0]["rewards/margin"]) < 1e-6  # adapters start as identity: policy == reference
     assert hist[-1]["rewards/margin"] > 0.05 and hist[-1]["loss"] < hist[0]["loss"]
+
+
+def test_phase_timing_reports_forward_head_backward_and_optimizer():
+    import numpy as np
+    import torch
+
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=200, d_model=32, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64, tie_word_embeddings=True)
+    tr = Trainer(TrainerConfig(model=model, batch_size=1, grad_accum=2, seq_len=16, zero_level=0, time_breakdown=True), device=torch.device("cpu"))
+    tr.init_weights(seed=0)
+    tok = np.random.default_rng(0).integers(0, 200, (2, 17)).astype(np.int32)
+    tr.step(tok[:, :-1], tok[:, 1:])
+    t = tr.last_time_breakdown
+    assert set(t) == {"forward_ms", "lm_head_ms", "backward_ms", "optimizer_ms"} and all(v > 0 for v in t.values())
+    tr.step(tok[:, :-1], tok[:, 1:])
+    assert tr.last_time_breakdown["forward_ms"] < 10 * t["forward_ms"] + 50  # marks are reset per step, not accumulated over the run
