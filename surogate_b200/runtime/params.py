@@ -616,13 +616,17 @@ class ParamStore:
         b.written.add(name)
         return b.grad[s.offset:s.offset + s.numel].view(s.shape), acc
 
-    def _reduce_bucket(self, b: Bucket) -> None:
-        """Start the (async) gradient reduction of one bucket; called as soon as its backward is complete."""
+    def _reduce_bucket(self, b: Bucket, zero_unwritten: bool = True) -> None:
+        """Start the (async) gradient reduction of one bucket; called as soon as its backward is complete.
+        With ``defer_reduce`` (forward + backward captured in a CUDA graph: the collectives stay outside the graph) only the
+        zero-fill of parameters without a gradient happens here; ``reduce_deferred`` starts the reductions afterwards."""
         if b.grad is None or not b.trainable:
             return
-        for s in b.slots:  # parameters that received no gradient this micro-step contribute zeros
+        for s in (b.slots if zero_unwritten else ()):  # parameters that received no gradient this micro-step contribute zeros
             if s.trainable and s.name not in b.written and (self.zero_level >= 2 or b.grad_persistent):
                 b.grad[s.offset:s.offset + s.numel].zero_()
+        if getattr(self, "defer_reduce", False):
+            return
         if self.world == 1 or b.expert:
             b.grad_shard = b.grad  # whole experts live on this rank (dp = 1 inside the expert group): nothing to reduce
             return
@@ -659,6 +663,13 @@ class ParamStore:
             return self.comm.reduce_scatter(full, shard, async_op=True, sumsq_out=self.fused_sumsq)
         self.sumsq_valid = False
         return self.comm.reduce_scatter(full, shard, async_op=True)
+
+    def reduce_deferred(self) -> None:
+        """Reductions of every bucket after a graph-replayed backward (the write bookkeeping of a replay lives in the graph, so
+        nothing is zero-filled here)."""
+        self.defer_reduce = False
+        for b in self.buckets.values():
+            self._reduce_bucket(b, zero_unwritten=False)
 
     def finish_reduce(self) -> None:
         for b in self.buckets.values():

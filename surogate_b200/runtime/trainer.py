@@ -351,12 +351,14 @@ class Trainer:
 
     # ------------------------------------------------------------------ CUDA graphs
     def _graphs_allowed(self, doc_ids, row_weights, kd) -> bool:
-        """Graph replay needs a step whose launches do not depend on Python state that changes between steps: one GPU (the
-        peer-memory collectives pass a barrier epoch as a kernel argument), dense model, no streamed weights or optimizer
+        """Graph replay needs a step whose launches do not depend on Python state that changes between steps: no collective
+        inside the captured region (the peer-memory kernels pass a barrier epoch as a kernel argument; so one GPU, or replicated
+        weights with the gradient reductions issued after the replay), dense model, no streamed weights or optimizer
         state, no per-batch side inputs, a recipe without step-dependent seeds, and scaling history already present (the
         first two steps run eagerly: they also serve as the warm-up that graph capture requires)."""
         c = self.cfg
-        return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and self.world == 1 and self.lora is None
+        multi_ok = self.world == 1 or c.zero_level <= 1  # replicated weights: the gradient reductions run after the replay, outside the graph
+        return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and multi_ok and self.lora is None
                     and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora or c.offload_saved_tensors or c.lmhead_drop_ignored_rows or c.time_breakdown)
                     and c.sequence_chunks <= 1
                     and doc_ids is None and row_weights is None and kd is None and self._visual is None and not getattr(self.model, "num_experts", 0)
@@ -379,6 +381,7 @@ class Trainer:
         st["scale"].copy_(loss_scale)
         key = (index == 0, index == total - 1)
         self.store.begin_micro_step(index, total)
+        self.store.defer_reduce = self.world > 1
         entry = g["by_key"].get(key)
         if entry is None:
             torch.cuda.synchronize(self.device)
@@ -392,10 +395,15 @@ class Trainer:
                 warnings.warn(f"CUDA graph capture failed ({type(e).__name__}: {e}); continuing without graphs")
                 self.cfg.use_cuda_graphs = False
                 g["by_key"].clear()
+                self.store.defer_reduce = False
                 self.store.begin_micro_step(index, total)
                 return self.executor.forward_backward(inp, pos, tgt, loss_scale=loss_scale, aux_scale=aux_scale, micro_step=index)
             entry = g["by_key"][key] = (graph, ctx, outs)
         entry[0].replay()  # capture records without executing, so a freshly captured graph is replayed too
+        if self.world > 1:
+            if index == total - 1:
+                self.store.reduce_deferred()
+            self.store.defer_reduce = False
         self.graph_replays = getattr(self, "graph_replays", 0) + 1
         return entry[1], entry[2]
 

@@ -32,7 +32,7 @@ def main():
                         collectives=a.get("collectives", "auto"), keep_gathered=a.get("keep_gathered", True), ep_size=a.get("ep", 1),
                         lora=a.get("lora"), offload_master=a.get("offload_master", False), offload_optimizer=a.get("offload_optimizer", False),
                         cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5),
-                        ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
+                        use_cuda_graphs=a.get("graphs", False), ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
     pp = a.get("pp", False)
     if pp:  # pipeline stages: every rank gets the whole global batch and cuts it into world * grad_accum micro-batches
         from surogate_b200.parallel.dispatch_pp import PipelineTrainer
@@ -70,7 +70,7 @@ def main():
     if info.rank == 0:
         print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "comm": type(tr.comm).__name__,
                                       "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),
-                                      "fp8_gather": bool(tr.store.fp8_gather), "h2d_weight_bytes": int(tr.store.h2d_bytes),
+                                      "fp8_gather": bool(tr.store.fp8_gather), "graph_replays": getattr(tr, "graph_replays", 0), "h2d_weight_bytes": int(tr.store.h2d_bytes),
                                       "stage_slots": len(tr.store.stage_slots),
                                       "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0,
                                       "ep_moves": tr.ep.moves_done if tr.ep is not None else 0,

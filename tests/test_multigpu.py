@@ -108,3 +108,13 @@ def test_pipeline_stages_on_two_gpus_match_one_gpu():
         assert abs(a - b) < 2e-2 * abs(b), (r["losses"], one["losses"])
     for a, b in zip(r["norms"], one["norms"]):
         assert abs(a - b) < 5e-2 * abs(b), (r["norms"], one["norms"])
+
+
+@pytest.mark.parametrize("collectives", ["nccl", "symm"])
+def test_two_gpus_graph_replay_with_deferred_reductions(single, collectives):
+    """Forward + backward replayed from CUDA graphs on each rank, gradient reduce-scatter issued after the replay."""
+    r = run_worker(2, dict(ARGS, zero=1, collectives=collectives, graphs=True, steps=6), port=29771 + (1 if collectives == "symm" else 0))
+    one = run_worker(1, dict(ARGS, steps=6))
+    assert r["graph_replays"] == 4, r["graph_replays"]
+    for a, b in zip(r["losses"], one["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (r["losses"], one["losses"])
