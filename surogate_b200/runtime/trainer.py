@@ -528,6 +528,28 @@ class Trainer:
             check_device_errors()
         return {"loss": float(out[0]), "norm": float(out[1]), "aux_loss": float(out[2])}
 
+    # ------------------------------------------------------------------ call-compatible spellings of the reference's Python API
+    def train_step_graphed(self, inputs, targets, position_ids=None, lr: Optional[float] = None) -> Dict[str, float]:
+        """``step`` with CUDA-graph replay of forward + backward switched on (falls back to eager where graphs do not apply).
+        Parity: SurogateTrainer.train_step_graphed (csrc/src/binding/py_train.h)."""
+        self.cfg.use_cuda_graphs = True
+        return self.step(inputs, targets, position_ids, lr=lr)
+
+    def update_with_config(self, opt_config: Any, step: Optional[int] = None) -> Dict[str, float]:
+        """Optimizer update after one or more ``forward_backward`` calls, with hyper-parameters taken from ``opt_config`` (a dict
+        or an object with learning_rate / weight_decay / beta1 / beta2 / eps / max_grad_norm).  Returns {"norm": ...}.
+        Parity: SurogateTrainer.update_with_config."""
+        get = opt_config.get if isinstance(opt_config, dict) else (lambda k, d=None: getattr(opt_config, k, d))
+        for mine, theirs in (("weight_decay", "weight_decay"), ("beta1", "beta1"), ("beta2", "beta2"), ("eps", "eps"), ("max_grad_norm", "max_grad_norm"),
+                             ("beta1", "adamw_beta1"), ("beta2", "adamw_beta2"), ("eps", "adamw_epsilon")):
+            v = get(theirs, None)
+            if v is not None:
+                setattr(self.opt_cfg, mine, float(v))
+        if step is not None:
+            self.step_index = int(step)
+        norm = self.optimizer_step(get("learning_rate", None))
+        return {"norm": float(norm)}
+
     @torch.no_grad()
     def token_logprobs(self, inputs, targets, position_ids=None, use_adapters: bool = True) -> torch.Tensor:
         """log p(target_t | prefix) for every position ([rows, T] float32 on the device, 0 where the target is ignored).
