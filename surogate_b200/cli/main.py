@@ -26,6 +26,7 @@ COMMAND_MAPPING: Dict[str, str] = {
     "distill-capture": "surogate_b200.cli.distill",
     "transplant-tokenizer": "surogate_b200.cli.transplant",
     "export": "surogate_b200.cli.export",
+    "eval": "surogate_b200.cli.eval",
     "info": "surogate_b200.cli.info",
     "chat": "surogate_b200.cli.chat",
     "monitor": "surogate_b200.cli.monitor",

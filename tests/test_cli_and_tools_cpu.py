@@ -197,3 +197,20 @@ def test_every_example_configuration_loads_and_validates():
             hf = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=64, num_hidden_layers=8, num_attention_heads=4, num_key_value_heads=2,
                       head_dim=16, intermediate_size=96, vocab_size=320)
             assert cfg.to_trainer_config(hf).seq_len == cfg.sequence_len, rel
+
+
+def test_eval_command_reports_loss_and_perplexity(tmp_path, capsys):
+    import yaml
+
+    from surogate_b200.cli.main import cli_main
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=256, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64,
+                 tie_word_embeddings=True)
+    cfg = dict(model=json.dumps(model), synthetic_data=True, sequence_len=32, per_device_train_batch_size=2, output_dir=str(tmp_path / "out"), lora=False,
+               recipe="bf16", zero_level=0)
+    path = tmp_path / "cfg.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    os.environ["SUROGATE_NO_BANNER"] = "1"
+    assert cli_main(["eval", str(path), "--batches", "2"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["batches"] == 2 and 4.0 < out["eval_loss"] < 7.0 and abs(out["perplexity"] - np.exp(out["eval_loss"])) < 1e-6 * out["perplexity"]
