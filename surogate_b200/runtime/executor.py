@@ -167,26 +167,29 @@ class SavedTensorOffload:
         ready.record()
         self.stream.wait_event(ready)
         out: Dict[str, Any] = {}
+        seen: Dict[int, str] = {}
         with torch.cuda.stream(self.stream):
             for k, v in saved.items():
-                if hasattr(v, "data") and hasattr(v, "scale_inv") and not torch.is_tensor(v):  # quantised activation: move its payload
-                    out[k] = ("fp8", v, self._out(v.data), self._out(v.hp) if getattr(v, "hp", None) is not None else None)
-                    v.data = None
-                    if getattr(v, "hp", None) is not None:
-                        v.hp = None
+                if id(v) in seen:  # the same object saved under two names: move it once
+                    out[k] = ("same", seen[id(v)])
+                    continue
+                seen[id(v)] = k
+                if hasattr(v, "scale_inv") and not torch.is_tensor(v):  # quantised activation: move its payload, rebuild the wrapper on the way back
+                    out[k] = ("fp8", type(v), v.scale_inv, self._out(v.data), self._out(v.hp) if getattr(v, "hp", None) is not None else None)
                 else:
                     out[k] = self._out(v)
         done = torch.cuda.Event()
         done.record(self.stream)
         return {"__offloaded__": out, "__done__": done}
 
-    def _in(self, item):
+    def _in(self, item, used: List[torch.Tensor]):
         kind, v = item
         if kind == "keep":
-            return v, None
+            return v
         d = torch.empty(v.shape, dtype=v.dtype, device=self.device)
         d.copy_(v, non_blocking=True)
-        return d, v
+        used.append(v)
+        return d
 
     def prefetch(self, layer: int, parked: Dict[str, Any]) -> None:
         if layer in self.inflight or "__offloaded__" not in parked:
@@ -196,17 +199,16 @@ class SavedTensorOffload:
         used: List[torch.Tensor] = []
         with torch.cuda.stream(self.stream):
             for k, item in parked["__offloaded__"].items():
+                if item[0] == "same":
+                    continue
                 if item[0] == "fp8":
-                    _, obj, data, hp = item
-                    obj.data, h = self._in(data)
-                    used += [h] if h is not None else []
-                    if hp is not None:
-                        obj.hp, h2 = self._in(hp)
-                        used += [h2] if h2 is not None else []
-                    out[k] = obj
+                    _, cls, scale_inv, data, hp = item
+                    out[k] = cls(self._in(data, used), scale_inv, self._in(hp, used) if hp is not None else None)
                 else:
-                    out[k], h = self._in(item)
-                    used += [h] if h is not None else []
+                    out[k] = self._in(item, used)
+            for k, item in parked["__offloaded__"].items():
+                if item[0] == "same":
+                    out[k] = out[item[1]]
         ev = torch.cuda.Event()
         ev.record(self.stream)
         self.inflight[layer] = (out, (ev, used))
@@ -216,12 +218,13 @@ class SavedTensorOffload:
             return parked
         self.prefetch(layer, parked)
         out, (ev, used) = self.inflight.pop(layer)
-        torch.cuda.current_stream(self.device).wait_event(ev)
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(ev)
         for v in out.values():
             for t in ((v,) if torch.is_tensor(v) else (getattr(v, "data", None), getattr(v, "hp", None))):
                 if torch.is_tensor(t) and t.is_cuda:
-                    t.record_stream(torch.cuda.current_stream(self.device))
-        for h in used:  # the pinned buffers are free again once the copies back have been issued and awaited by the consumer
+                    t.record_stream(cur)
+        for h in used:  # pinned buffers return to the pool: their copies back were issued, and later pushes run on the same side stream
             self.free.setdefault((tuple(h.shape), h.dtype), []).append(h)
         return out
 
