@@ -178,13 +178,16 @@ Tensor swiglu_bwd(const Tensor& dy, const Tensor& x) {
     return dx;
 }
 
+// ``pos`` is [tokens] int32, or [3, tokens] (temporal / height / width rows) when sec_h or sec_w is non-zero: frequency j then
+// reads the height row if j % 3 == 1 and j < 3 * sec_h, the width row if j % 3 == 2 and j < 3 * sec_w.
 std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, const Tensor& pos, int64_t Hq,
-                                     int64_t Hkv, int64_t D, double eps, double theta) {
+                                     int64_t Hkv, int64_t D, double eps, double theta, int64_t sec_h, int64_t sec_w) {
     check_bf16(qkv, "qkv");
     TORCH_CHECK(D == 128, "qk_norm_rope kernel supports head_dim 128");
     TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kInt && pos.is_contiguous(), "position_ids must be contiguous CUDA int32");
     const size_t tokens = qkv.numel() / ((Hq + 2 * Hkv) * D);
-    TORCH_CHECK(static_cast<size_t>(pos.numel()) == tokens, "position_ids must have one entry per token");
+    const bool multi_axis = sec_h > 0 || sec_w > 0;
+    TORCH_CHECK(static_cast<size_t>(pos.numel()) == (multi_axis ? 3 : 1) * tokens, "position_ids must have one entry per token (three rows of them for multi-axis positions)");
     const c10::cuda::CUDAGuard guard(qkv.device());
     Tensor out = torch::empty_like(qkv);
     const bool norm = qw.has_value() && qw->defined();
@@ -201,17 +204,20 @@ std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tens
     g_launches += 1;
     sg::qk_norm_rope_fwd(qkv.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), out.data_ptr(), norm ? q_rstd.data_ptr<float>() : nullptr,
                          norm ? k_rstd.data_ptr<float>() : nullptr, tokens, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps),
-                         static_cast<float>(theta), num_sms(), cur_stream());
+                         static_cast<float>(theta), static_cast<int>(3 * sec_h), static_cast<int>(3 * sec_w), num_sms(), cur_stream());
     return {out, q_rstd, k_rstd};
 }
 
 std::vector<Tensor> qk_norm_rope_bwd(const Tensor& d_out, const Tensor& qkv_pre, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw,
                                      const c10::optional<Tensor>& q_rstd, const c10::optional<Tensor>& k_rstd, const Tensor& pos, int64_t Hq,
-                                     int64_t Hkv, int64_t D, double eps, double theta) {
+                                     int64_t Hkv, int64_t D, double eps, double theta, int64_t sec_h, int64_t sec_w) {
     check_bf16(d_out, "d_out");
     check_bf16(qkv_pre, "qkv");
     TORCH_CHECK(D == 128, "qk_norm_rope kernel supports head_dim 128");
     const size_t tokens = d_out.numel() / ((Hq + 2 * Hkv) * D);
+    TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kInt && pos.is_contiguous() &&
+                    static_cast<size_t>(pos.numel()) == ((sec_h > 0 || sec_w > 0) ? 3 : 1) * tokens,
+                "position_ids must be contiguous CUDA int32 with one entry per token (three rows for multi-axis positions)");
     const c10::cuda::CUDAGuard guard(d_out.device());
     Tensor dx = torch::empty_like(d_out);
     const bool norm = qw.has_value() && qw->defined();
@@ -223,7 +229,8 @@ std::vector<Tensor> qk_norm_rope_bwd(const Tensor& d_out, const Tensor& qkv_pre,
     g_launches += 1;
     sg::qk_norm_rope_bwd(d_out.data_ptr(), qkv_pre.data_ptr(), opt_ptr(qw), opt_ptr(kw), pos.data_ptr<int>(), dx.data_ptr(), opt_f32_mut(q_rstd),
                          opt_f32_mut(k_rstd), norm ? dqw.data_ptr<float>() : nullptr, norm ? dkw.data_ptr<float>() : nullptr, tokens,
-                         static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps), static_cast<float>(theta), num_sms(), cur_stream());
+                         static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(eps), static_cast<float>(theta), static_cast<int>(3 * sec_h),
+                         static_cast<int>(3 * sec_w), num_sms(), cur_stream());
     return {dx, dqw, dkw};
 }
 
@@ -370,8 +377,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("rmsnorm_bwd", &rmsnorm_bwd);
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);
-    m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
-    m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+    m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd, py::arg("qkv"), py::arg("q_norm_weight"), py::arg("k_norm_weight"), py::arg("position_ids"), py::arg("num_q_heads"),
+          py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("theta"), py::arg("sec_h") = 0, py::arg("sec_w") = 0);
+    m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd, py::arg("d_out"), py::arg("qkv"), py::arg("q_norm_weight"), py::arg("k_norm_weight"), py::arg("q_rstd"),
+          py::arg("k_rstd"), py::arg("position_ids"), py::arg("num_q_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("theta"),
+          py::arg("sec_h") = 0, py::arg("sec_w") = 0);
     m.def("embedding_fwd", &embedding_fwd);
     m.def("embedding_bwd", &embedding_bwd);
     m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd, py::arg("logits"), py::arg("targets"), py::arg("scale"), py::arg("scale_host"),

@@ -242,9 +242,14 @@ template <bool BACKWARD>
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restrict__ in, const bf16* __restrict__ qkv_pre, const bf16* __restrict__ qw,
                                                            const bf16* __restrict__ kw, const int* __restrict__ pos, bf16* __restrict__ out,
                                                            float* __restrict__ q_rstd, float* __restrict__ k_rstd, float* __restrict__ dqw,
-                                                           float* __restrict__ dkw, size_t tokens, int Hq, int Hkv, float eps, float log2_theta) {
+                                                           float* __restrict__ dkw, size_t tokens, int Hq, int Hkv, float eps, float log2_theta,
+                                                           int lim_h, int lim_w) {
+    // Multi-axis rotary positions (vision-language models): when lim_h or lim_w is non-zero, ``pos`` holds three rows of
+    // ``tokens`` entries (temporal, height, width) and frequency j uses the height row if j % 3 == 1 and j < lim_h, the width
+    // row if j % 3 == 2 and j < lim_w, else the temporal row.
     constexpr int D = 128;
     __shared__ float sdw[2][D];
+    const bool multi_axis = (lim_h | lim_w) != 0;
     if (BACKWARD) {
         for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
         __syncthreads();
@@ -273,12 +278,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
         }
         // rotation angles for this lane's 4 element indices (index mod 64)
         const float p = static_cast<float>(pos[tok]);
+        float p_h = p, p_w = p;
+        if (multi_axis) {
+            p_h = static_cast<float>(pos[tokens + tok]);
+            p_w = static_cast<float>(pos[2 * tokens + tok]);
+        }
         float cs[4], sn[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int j = (lane * 4 + i) & 63;
             const float inv = exp2f(-log2_theta * (2.f * j) / D);
-            sincosf(p * inv, &sn[i], &cs[i]);
+            const int m3 = j % 3;
+            const float pj = (m3 == 1 && j < lim_h) ? p_h : ((m3 == 2 && j < lim_w) ? p_w : p);
+            sincosf(pj * inv, &sn[i], &cs[i]);
         }
         const float sign = (lane < 16) ? -1.f : 1.f;  // first half: x1*c - x2*s ; second half: x2*c + x1*s
         if (!BACKWARD) {
@@ -731,18 +743,19 @@ void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int
     swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M);
 }
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
-                      int Hkv, float eps, float theta, int num_sms, cudaStream_t s) {
+                      int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s) {
     const size_t items = tokens * (Hq + 2 * Hkv);
     qk_norm_rope_kernel<false><<<grid_for(items * 32, 256, num_sms), 256, 0, s>>>((const bf16*)qkv, nullptr, (const bf16*)qw, (const bf16*)kw, pos,
                                                                                    (bf16*)out, q_rstd, k_rstd, nullptr, nullptr, tokens, Hq, Hkv, eps,
-                                                                                   log2f(theta));
+                                                                                   log2f(theta), lim_h, lim_w);
 }
 void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,
-                      float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int num_sms, cudaStream_t s) {
+                      float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms,
+                      cudaStream_t s) {
     const size_t items = tokens * (Hq + 2 * Hkv);
     qk_norm_rope_kernel<true><<<grid_for(items * 32, 256, num_sms, 4), 256, 0, s>>>((const bf16*)d_out, (const bf16*)qkv_pre, (const bf16*)qw,
                                                                                      (const bf16*)kw, pos, (bf16*)d_qkv, q_rstd, k_rstd, dqw, dkw, tokens,
-                                                                                     Hq, Hkv, eps, log2f(theta));
+                                                                                     Hq, Hkv, eps, log2f(theta), lim_h, lim_w);
 }
 void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int V, int* error_flag, int num_sms, cudaStream_t s) {
     embedding_fwd_kernel<<<grid_for(n * (C / 8), 256, num_sms), 256, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, n, C, V, error_flag);

@@ -14,9 +14,10 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
 void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s);
 void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s);
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
-                      int Hkv, float eps, float theta, int num_sms, cudaStream_t s);
+                      int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s);
 void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,
-                      float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int num_sms, cudaStream_t s);
+                      float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms,
+                      cudaStream_t s);
 void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int V, int* error_flag, int num_sms, cudaStream_t s);
 void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad_fp32, size_t n, int C, int num_sms, cudaStream_t s);
 void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,

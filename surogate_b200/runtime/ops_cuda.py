@@ -147,23 +147,35 @@ class CudaOps(RefOps):
     # ------------------------------------------------------------------ qk-norm + rope
     @staticmethod
     def _multi_axis(ctx, a) -> bool:
-        """A batch with image / video tokens carries (t, h, w) positions: those steps take the PyTorch rotary path."""
+        """A batch with image / video tokens carries (t, h, w) positions."""
         return bool(a.get("mrope_section")) and ctx.extras.get("mrope_position_ids") is not None
+
+    def _rope_positions(self, ctx, a, pos):
+        """(position tensor, sec_h, sec_w) for the kernel: three rows and the section sizes when the batch carries (t, h, w)
+        positions and the op is a multi-axis one, else the plain [B, T] positions."""
+        if self._multi_axis(ctx, a):
+            sec = a["mrope_section"]
+            return ctx.extras["mrope_position_ids"].to(torch.int32).contiguous(), int(sec[1]), int(sec[2])
+        return pos.contiguous(), 0, 0
+
+    def _rope_kernel_ok(self, a, qkv) -> bool:
+        return a["head_dim"] == 128 and a["rotary_dim"] == 128 and qkv.dtype == torch.bfloat16 and not a.get("rope_scaling")
 
     def qkv_qk_norm_rope(self, ctx, op, qkv, qw, kw, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling") or self._multi_axis(ctx, a):
+        if not self._rope_kernel_ok(a, qkv):
             return super().qkv_qk_norm_rope(ctx, op, qkv, qw, kw, pos)
-        out, q_rstd, k_rstd = self.ext.qk_norm_rope_fwd(qkv, qw, kw, pos.contiguous(), a["num_q_heads"], a["num_kv_heads"], 128, a["eps"],
-                                                        a["rope_theta"])
+        p, sh, sw = self._rope_positions(ctx, a, pos)
+        out, q_rstd, k_rstd = self.ext.qk_norm_rope_fwd(qkv, qw, kw, p, a["num_q_heads"], a["num_kv_heads"], 128, a["eps"], a["rope_theta"], sh, sw)
         return out, (q_rstd if qw is not None else None), (k_rstd if qw is not None else None)
 
     def qkv_qk_norm_rope_backward(self, ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos):
         a = op.attrs
-        if a["head_dim"] != 128 or a["rotary_dim"] != 128 or qkv.dtype != torch.bfloat16 or a.get("rope_scaling") or self._multi_axis(ctx, a):
+        if not self._rope_kernel_ok(a, qkv):
             return super().qkv_qk_norm_rope_backward(ctx, op, dy, qkv, qw, kw, q_rstd, k_rstd, pos)
-        dx, dqw, dkw = self.ext.qk_norm_rope_bwd(dy.contiguous(), qkv, qw, kw, q_rstd, k_rstd, pos.contiguous(), a["num_q_heads"],
-                                                 a["num_kv_heads"], 128, a["eps"], a["rope_theta"])
+        p, sh, sw = self._rope_positions(ctx, a, pos)
+        dx, dqw, dkw = self.ext.qk_norm_rope_bwd(dy.contiguous(), qkv, qw, kw, q_rstd, k_rstd, p, a["num_q_heads"], a["num_kv_heads"], 128, a["eps"],
+                                                 a["rope_theta"], sh, sw)
         return dx, (dqw if qw is not None else None), (dkw if qw is not None else None)
 
     # ------------------------------------------------------------------ swiglu

@@ -168,6 +168,34 @@ def test_qk_norm_rope(ext):
     assert _rel_err(out2, r2) < 5e-3
 
 
+def test_qk_norm_rope_multi_axis_positions(ext):
+    """(t, h, w) rotary positions: frequency j reads the height row if j % 3 == 1 and j < 3 * sec_h, the width row if
+    j % 3 == 2 and j < 3 * sec_w, else the temporal row; forward and backward against the PyTorch op."""
+    from types import SimpleNamespace
+
+    from surogate_b200.dsl.ir import OpNode
+    from surogate_b200.runtime.ops_ref import RefOps
+
+    B, T, Hq, Hkv, D = 2, 64, 4, 2, 128
+    qkv = torch.randn(B, T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    pos3 = torch.stack([torch.arange(T, device=DEV)[None].repeat(B, 1), torch.randint(0, 40, (B, T), device=DEV), torch.randint(0, 40, (B, T), device=DEV)]).to(torch.int32)
+    attrs = dict(num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, eps=1e-6, rope_theta=5e6, rotary_dim=D, mrope_section=[24, 20, 20])
+    ctx = SimpleNamespace(extras={"mrope_position_ids": pos3})
+    op = OpNode("qkv_qk_norm_rope", [], [], attrs)
+    ref = RefOps()
+    r_out, r_q, r_k = ref.qkv_qk_norm_rope(ctx, op, qkv.float(), qw.float(), kw.float(), pos3[0])
+    out, q_rstd, k_rstd = ext.qk_norm_rope_fwd(qkv, qw, kw, pos3.contiguous(), Hq, Hkv, D, 1e-6, 5e6, 20, 20)
+    assert _rel_err(out, r_out) < 5e-3
+    plain, _, _ = ext.qk_norm_rope_fwd(qkv, qw, kw, pos3[0].contiguous(), Hq, Hkv, D, 1e-6, 5e6)
+    assert _rel_err(plain, r_out) > 0.05  # the height / width rows matter
+    dy = torch.randn_like(qkv)
+    r_dx, r_dq, r_dk = ref.qkv_qk_norm_rope_backward(ctx, op, dy.float(), qkv.float(), qw.float(), kw.float(), r_q, r_k, pos3[0])
+    dx, dqw, dkw = ext.qk_norm_rope_bwd(dy, qkv, qw, kw, q_rstd, k_rstd, pos3.contiguous(), Hq, Hkv, D, 1e-6, 5e6, 20, 20)
+    assert _rel_err(dx, r_dx) < 5e-3 and _rel_err(dqw, r_dq) < 2e-3 and _rel_err(dkw, r_dk) < 2e-3
+
+
 def test_embedding(ext):
     V, C, n = 1000, 512, 4096
     table = torch.randn(V, C, device=DEV).bfloat16()
