@@ -91,7 +91,7 @@ class Orchestrator:
 
     def load_prompts(self, rows: Optional[Sequence[Dict[str, Any]]] = None) -> None:
         if rows is None and self.env is not None:
-            rows = [dict(ex, prompt=self.env.initial_messages(ex)) for ex in self.env.dataset]
+            rows = [dict(ex, prompt=self.env.initial_messages(ex)) for ex in self.env.dataset] if not hasattr(self.env, "env_response") else list(self.env.dataset)
         if rows is None:
             with open(self.cfg.prompts) as f:
                 rows = [json.loads(l) for l in f if l.strip()]
@@ -103,6 +103,44 @@ class Orchestrator:
             return self.tok.apply_chat_template_and_encode(p, add_generation_prompt=True)
         return self.tok.apply_chat_template_and_encode([{"role": "user", "content": str(p)}], add_generation_prompt=True)
 
+    def multi_turn_group(self, row: Dict[str, Any], sampling: Dict[str, Any]):
+        """``group_size`` episodes of a multi-turn environment for one example.  Each episode alternates a sampled assistant turn
+        and the environment's reply; the conversation is re-encoded with the chat template after every reply and the tokens
+        it added (end-of-turn marker, tool message, next generation prompt) join the sequence as context that is not trained
+        on.  If re-encoding does not reproduce the tokens sampled so far the episode ends at that turn.
+        Returns [(prompt_ids, token_ids, logprobs, mask, reward)]."""
+        env = self.env
+        out = []
+        for _ in range(self.cfg.group_size):
+            msgs = env.initial_messages(row)
+            state = dict(env.setup_state(row), example=row)
+            prompt0 = self.tok.apply_chat_template_and_encode(msgs, add_generation_prompt=True)
+            ctx, comp, lps, mask, text, turns = list(prompt0), [], [], [], "", 0
+            while turns < env.max_turns and len(ctx) < self.cfg.sequence_len:
+                ids, lp, text = self.client.generate(ctx, 1, sampling)[0]
+                if not ids or len(lp) != len(ids):
+                    break
+                comp += ids
+                lps += lp
+                mask += [1] * len(ids)
+                msgs = msgs + [{"role": "assistant", "content": text}]
+                turns += 1
+                if env.is_completed(msgs, state):
+                    break
+                msgs = msgs + env.env_response(msgs, state)
+                new_ctx = self.tok.apply_chat_template_and_encode(msgs, add_generation_prompt=True)
+                full = prompt0 + comp
+                if new_ctx[:len(full)] != full:
+                    break
+                extra = new_ctx[len(full):]
+                comp += extra
+                lps += [0.0] * len(extra)
+                mask += [0] * len(extra)
+                ctx = new_ctx
+            reward, _ = env.score(row, dict(state, messages=msgs, completion=text, turns=turns))
+            out.append((prompt0, comp, lps, mask, float(reward)))
+        return out
+
     def collect(self, step: int, version: int) -> Tuple[List[Rollout], Dict[str, float]]:
         c = self.cfg
         idx = self.rng.choice(len(self.prompts), size=min(c.prompts_per_step, len(self.prompts)), replace=False)
@@ -111,6 +149,19 @@ class Orchestrator:
         rewards_all, lens, kept = [], [], 0
         for g, i in enumerate(idx):
             row = self.prompts[int(i)]
+            if self.env is not None and hasattr(self.env, "env_response"):  # multi-turn environment: episodes instead of single completions
+                eps = self.multi_turn_group(row, sampling)
+                rewards = [e[4] for e in eps]
+                rewards_all += rewards
+                lens += [sum(e[3]) for e in eps]
+                adv = group_advantages(torch.tensor(rewards), len(rewards), c.advantage_std_eps).tolist()
+                if c.filter_zero_advantage and max(rewards) - min(rewards) < 1e-12:
+                    continue
+                kept += 1
+                for (pids, ids, lps, mask, r), a in zip(eps, adv):
+                    if ids:
+                        rollouts.append(Rollout(pids, ids, lps, a, r, version, g, completion_mask=mask))
+                continue
             pids = self._prompt_ids(row)
             gens = self.client.generate(pids, c.group_size, sampling)
             rewards = [float(r) for r in self.reward_fn(row, [t for _, _, t in gens])]

@@ -10,7 +10,7 @@ Parity: surogate/grpo/packer.py.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Sequence
+from typing import Optional, Dict, List, Sequence
 
 import numpy as np
 
@@ -27,6 +27,9 @@ class Rollout:
     policy_version: int = 0
     group: int = 0
     meta: Dict = field(default_factory=dict)
+    # multi-turn rollouts: 1 for tokens the policy produced, 0 for environment tokens (tool results, turn markers) that sit
+    # between its turns; None means every completion token is the policy's
+    completion_mask: Optional[List[int]] = None
 
     def __len__(self) -> int:
         return len(self.prompt_ids) + len(self.completion_ids)
@@ -53,9 +56,11 @@ def _truncate(r: Rollout, T: int) -> Rollout:
         return r
     keep_c = max(1, T - len(r.prompt_ids))
     if keep_c < len(r.completion_ids) and len(r.prompt_ids) < T:
-        return Rollout(r.prompt_ids, r.completion_ids[:keep_c], r.logprobs[:keep_c], r.advantage, r.reward, r.policy_version, r.group, r.meta)
+        return Rollout(r.prompt_ids, r.completion_ids[:keep_c], r.logprobs[:keep_c], r.advantage, r.reward, r.policy_version, r.group, r.meta,
+                       r.completion_mask[:keep_c] if r.completion_mask is not None else None)
     p = r.prompt_ids[-(T - 1):]
-    return Rollout(p, r.completion_ids[:1], r.logprobs[:1], r.advantage, r.reward, r.policy_version, r.group, r.meta)
+    return Rollout(p, r.completion_ids[:1], r.logprobs[:1], r.advantage, r.reward, r.policy_version, r.group, r.meta,
+                   r.completion_mask[:1] if r.completion_mask is not None else None)
 
 
 def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: int = 0) -> List[PackedBatch]:
@@ -106,6 +111,10 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
                     y[r, lo:hi] = ids[P:]
                     old[r, lo:hi] = np.asarray(s.logprobs, np.float32)
                 adv[r, lo:hi] = s.advantage
+                if s.completion_mask is not None:  # environment tokens are context only
+                    m = np.asarray(s.completion_mask[(1 if P == 0 else 0):], bool)
+                    y[r, lo:hi][~m] = IGNORE
+                    adv[r, lo:hi][~m] = 0.0
                 seq[r, at:at + n] = sid
                 sid += 1
                 at += n

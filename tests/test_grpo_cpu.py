@@ -130,7 +130,6 @@ def test_environments_generate_verify_and_evaluate(tmp_path):
     tool loop feeds lookups back, and a scaffolded environment loads and evaluates."""
     import json as _json
     import os
-    import re as _re
 
     from surogate_b200.cli.vf import init_environment
     from surogate_b200.grpo.environments import as_reward_fn, evaluate, load_environment
@@ -191,3 +190,84 @@ def test_environments_generate_verify_and_evaluate(tmp_path):
 def msgs_have_system(env, policy):
     msgs = env.initial_messages(env.dataset[0])
     return msgs[0]["role"] == "system" and msgs[-1]["role"] == "user" and isinstance(policy(msgs), str)
+
+
+def test_orchestrator_runs_multi_turn_tool_episodes(tmp_path):
+    """A multi-turn environment drives episodes: assistant turns are sampled one by one, tool replies are inserted as context
+    tokens that carry no loss, and the episode's reward becomes the advantage of every assistant token."""
+    import json as _json
+
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.orchestrator import Orchestrator
+    from surogate_b200.grpo.transport import FilesystemTransport
+
+    class Tok:  # one token per character, messages joined by a separator token; re-encoding is prefix-stable
+        pad_token_id = 0
+
+        def apply_chat_template_and_encode(self, msgs, add_generation_prompt=True):
+            ids = []
+            for m in msgs:
+                ids += [1] + [ord(c) + 10 for c in m["content"]] + ([2] if m["role"] != "assistant" else [])
+            return ids + ([3] if add_generation_prompt else [])
+
+    tok = Tok()
+
+    class Engine:  # even episodes follow the lookups and answer correctly, odd ones answer wrongly at once
+        def __init__(self):
+            self.k = 0
+            self.turn = {}
+
+        def generate(self, prompt_ids, n, sampling):
+            text = "".join(chr(t - 10) for t in prompt_ids if t >= 10)
+            episode = self.k
+            if "RESULT" not in text and not self.turn.get(episode):
+                self.turn[episode] = 1
+                reply = '<tool>{"name": "lookup", "args": {"entity": "E", "field": "city"}}</tool>' if episode % 2 == 0 else "<answer>nowhere</answer>"
+            else:
+                reply = "<answer>Oslo</answer>"
+            if "<answer>" in reply:
+                self.k += 1
+            ids = [ord(c) + 10 for c in reply] + [4]  # 4 = end of turn, part of the sampled tokens
+            return [(ids, [-0.25] * len(ids), reply)]
+
+    from surogate_b200.grpo.environments.base import MultiTurnEnv, Rubric
+
+    class Env(MultiTurnEnv):
+        env_id = "toy-tools"
+
+        def is_completed(self, messages, state):
+            return "<answer>" in messages[-1]["content"]
+
+        def env_response(self, messages, state):
+            return [{"role": "tool", "content": "RESULT Oslo"}]
+
+    def correct(completion, answer, **_):
+        return 1.0 if f"<answer>{answer}</answer>" in completion else 0.0
+
+    cfg = OrchestratorConfig(group_size=4, prompts_per_step=1, sequence_len=400, rows_per_step=2, max_steps=1, transport_dir=str(tmp_path), max_tokens=64)
+    orch = Orchestrator(cfg, tok, Engine(), FilesystemTransport(str(tmp_path)), lambda: 0)
+    orch.env = Env([{"prompt": [{"role": "user", "content": "city of E?"}], "answer": "Oslo"}], Rubric([correct]), max_turns=4)
+    orch.load_prompts()
+
+    class PrefixTok(Tok):  # the sampled end-of-turn token 4 must reappear when the conversation is re-encoded
+        def apply_chat_template_and_encode(self, msgs, add_generation_prompt=True):
+            ids = []
+            for m in msgs:
+                ids += ([3] if m["role"] == "assistant" else [1]) + [ord(c) + 10 for c in m["content"]] + ([4] if m["role"] == "assistant" else [2])
+            return ids + ([3] if add_generation_prompt else [])  # the generation prompt is the assistant header
+
+    orch.tok = PrefixTok()
+    rollouts, stats = orch.collect(0, 0)
+    assert stats["groups_kept"] == 1 and abs(stats["reward_mean"] - 0.5) < 1e-9 and len(rollouts) == 4
+    good = [r for r in rollouts if r.reward == 1.0]
+    bad = [r for r in rollouts if r.reward == 0.0]
+    assert len(good) == 2 and len(bad) == 2 and good[0].advantage > 0 > bad[0].advantage
+    g = good[0]
+    assert 0 in g.completion_mask and g.completion_mask[0] == 1 and g.completion_mask[-1] == 1  # tool reply in the middle is context
+    n_env = g.completion_mask.count(0)
+    assert n_env == len("RESULT Oslo") + 3  # [1] + text + [2] + generation prompt [3]
+    assert all(m == 1 for m in bad[0].completion_mask)
+    st = orch.run_step(0)
+    arrays, meta = orch.transport.receive(0, timeout_s=1)
+    trained = arrays["targets"] != -100
+    assert trained.sum() == sum(sum(r.completion_mask) for r in rollouts) and np.all(arrays["old_logprobs"][trained] == -0.25)
