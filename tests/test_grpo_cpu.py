@@ -130,6 +130,7 @@ def test_environments_generate_verify_and_evaluate(tmp_path):
     tool loop feeds lookups back, and a scaffolded environment loads and evaluates."""
     import json as _json
     import os
+    import re as _re
 
     from surogate_b200.cli.vf import init_environment
     from surogate_b200.grpo.environments import as_reward_fn, evaluate, load_environment
