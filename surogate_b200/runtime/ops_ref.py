@@ -523,7 +523,7 @@ class RefOps:
             return None
         if ctx.row_weights is not None or ctx.kd is not None or ctx.want_token_losses:
             return None
-        if hasattr(x, "dequantize"):
+        if not torch.is_tensor(x):  # a quantised activation wrapper (plain tensors also have a ``dequantize`` method: do not ask for it)
             x = x.hp if getattr(x, "hp", None) is not None else x.dequantize()
         C = x.shape[-1]
         x2, t = x.reshape(-1, C), targets.reshape(-1)

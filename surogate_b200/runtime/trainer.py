@@ -597,7 +597,7 @@ class Trainer:
         fwd = self.cm.fwd
         head = next(op for op in fwd.ops if op.kind == "fused_lm_head_loss")
         x = captured[head.inputs[0]]
-        if hasattr(x, "dequantize"):
+        if not torch.is_tensor(x):
             x = x.hp if getattr(x, "hp", None) is not None else x.dequantize()
         w = self.store.get(head.inputs[1])
         out = (x.reshape(-1, x.shape[-1]).float() @ w.float().t()).reshape(rows, T, -1)
