@@ -54,6 +54,43 @@ def _iter_file(path: str) -> Iterator[Dict[str, Any]]:
         raise ValueError(f"unsupported dataset file type: {path}")
 
 
+def fetch_remote(url: str, split: str = "train", cache_dir: Optional[str] = None) -> List[str]:
+    """Copy the data files under an object-store URL (``s3://bucket/prefix``, ``gs://...``, any fsspec protocol) into a local
+    cache directory and return the local paths.  A URL that names one file fetches that file; a prefix fetches every data file
+    below it (those whose name contains ``split`` when any does).  Files already present with the same size are reused."""
+    import hashlib
+
+    try:
+        import fsspec
+    except ImportError as e:  # pragma: no cover - fsspec ships with the image
+        raise RuntimeError(f"{url}: object-store datasets need the `fsspec` package") from e
+    proto = url.split("://", 1)[0]
+    try:
+        fs = fsspec.filesystem(proto)
+    except (ImportError, ValueError) as e:
+        raise RuntimeError(f"{url}: no fsspec backend for '{proto}://' is installed (s3 needs s3fs, gs needs gcsfs)") from e
+    exts = (".jsonl", ".ndjson", ".json", ".parquet", ".csv", ".tsv", ".txt")
+    if fs.isdir(url):
+        names = sorted(n for n in fs.find(url) if os.path.splitext(n)[1].lower() in exts)
+        names = [n for n in names if split in os.path.basename(n)] or names
+    else:
+        names = [url]
+    if not names:
+        raise FileNotFoundError(f"{url}: no data files ({', '.join(exts)}) found")
+    root = cache_dir or os.path.join(os.environ.get("SUROGATE_CACHE", os.path.expanduser("~/.cache/surogate_b200")), "datasets",
+                                     hashlib.sha1(url.encode()).hexdigest()[:16])
+    os.makedirs(root, exist_ok=True)
+    out = []
+    for n in names:
+        local = os.path.join(root, os.path.basename(n))
+        size = fs.size(n)
+        if not (os.path.exists(local) and os.path.getsize(local) == size):
+            fs.get(n, local + ".part")
+            os.replace(local + ".part", local)
+        out.append(local)
+    return out
+
+
 def load_rows(cfg, max_rows: Optional[int] = None) -> List[Dict[str, Any]]:
     """Rows of one dataset config (``DatasetConfig``) as a list of dicts."""
     path = cfg.path
@@ -67,8 +104,8 @@ def load_rows(cfg, max_rows: Optional[int] = None) -> List[Dict[str, Any]]:
         it: Iterable = (r for f in chosen for r in _iter_file(f))
     elif os.path.exists(path):
         it = _iter_file(path)
-    elif path.startswith(("s3://", "gs://")):
-        raise RuntimeError(f"{path}: object-store datasets need fsspec credentials and a network, neither is available here; copy the file locally")
+    elif "://" in path and not path.startswith(("http://", "https://")):
+        it = (r for f in fetch_remote(path, cfg.split or "train") for r in _iter_file(f))
     else:
         try:
             import datasets as hf_datasets  # type: ignore

@@ -214,3 +214,27 @@ def test_eval_command_reports_loss_and_perplexity(tmp_path, capsys):
     assert cli_main(["eval", str(path), "--batches", "2"]) == 0
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert out["batches"] == 2 and 4.0 < out["eval_loss"] < 7.0 and abs(out["perplexity"] - np.exp(out["eval_loss"])) < 1e-6 * out["perplexity"]
+
+
+def test_object_store_datasets_are_fetched_through_fsspec(tmp_path, monkeypatch):
+    """Any fsspec URL works as a dataset path (memory:// stands in for s3:// / gs://): files are cached locally and parsed."""
+    import fsspec
+
+    from surogate_b200.config.sft_config import DatasetConfig
+    from surogate_b200.data.datasets import fetch_remote, load_rows
+
+    fs = fsspec.filesystem("memory")
+    with fs.open("/bucket/set/train-0.jsonl", "w") as f:
+        f.write("\n".join(json.dumps({"text": f"row {i}"}) for i in range(5)))
+    with fs.open("/bucket/set/eval-0.jsonl", "w") as f:
+        f.write(json.dumps({"text": "held out"}))
+    monkeypatch.setenv("SUROGATE_CACHE", str(tmp_path))
+    rows = load_rows(DatasetConfig(path="memory://bucket/set", type="text", split="train"))
+    assert [r["text"] for r in rows] == [f"row {i}" for i in range(5)]
+    again = fetch_remote("memory://bucket/set/eval-0.jsonl")
+    assert len(again) == 1 and os.path.getsize(again[0]) > 0 and fetch_remote("memory://bucket/set/eval-0.jsonl") == again
+    try:
+        load_rows(DatasetConfig(path="nosuchproto://x/y"))
+        raise AssertionError("expected an error for an unknown protocol")
+    except RuntimeError as e:
+        assert "fsspec backend" in str(e)
