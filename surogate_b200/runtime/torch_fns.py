@@ -333,7 +333,56 @@ def mamba2_mixer(x, in_w, conv_w, conv_b, dt_bias, A_log, D, norm_w, out_w, *, n
 
 
 # ---------------------------------------------------------------------------------------------- gated delta rule (Qwen3.5 / Qwen3-Next)
-def gated_delta_rule(q, k, v, g, beta, *, scale: Optional[float] = None):
+def gated_delta_rule(q, k, v, g, beta, *, scale: Optional[float] = None, chunk: int = 64):
+    """Gated delta rule  S_t = exp(g_t) S_{t-1} + beta_t k_t (v_t - exp(g_t) S_{t-1}^T k_t)^T,  o_t = S_t^T q_t,  evaluated chunk
+    by chunk: inside a chunk of ``chunk`` positions the rank-one updates are folded into two triangular matrix products (the
+    inverse of I + strict_lower(beta k k^T * decay) built by forward substitution), so the sequential part runs over T / chunk
+    state updates made of matrix products instead of T outer products.  Short sequences use the step-by-step form.
+    q, k [B,T,H,Dk]; v [B,T,H,Dv]; g [B,T,H] (log decay, <= 0); beta [B,T,H].
+    Parity: surogate/kernels/triton/gated_delta_rule.py (chunk_gated_delta_rule)."""
+    B, T, H, Dk = q.shape
+    if T <= chunk:
+        return gated_delta_rule_recurrent(q, k, v, g, beta, scale=scale)
+    Dv = v.shape[-1]
+    C = chunk
+    q = F.normalize(q.float(), dim=-1) * (scale if scale is not None else Dk ** -0.5)
+    k = F.normalize(k.float(), dim=-1)
+    v, g, beta = v.float(), g.float(), beta.float()
+    pad = (-T) % C
+    if pad:  # padded steps: beta = 0 (no write), g = 0 (no decay), outputs dropped
+        q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        g, beta = F.pad(g, (0, 0, 0, pad)), F.pad(beta, (0, 0, 0, pad))
+    N = (T + pad) // C
+    # [B, H, N, C, D]
+    q, k, v = (t.permute(0, 2, 1, 3).reshape(B, H, N, C, -1) for t in (q, k, v))
+    g, beta = (t.permute(0, 2, 1).reshape(B, H, N, C) for t in (g, beta))
+    gc = g.cumsum(-1)
+    decay = torch.exp(gc.unsqueeze(-1) - gc.unsqueeze(-2)).tril()          # exp(gc_i - gc_j), i >= j
+    kb, vb = k * beta.unsqueeze(-1), v * beta.unsqueeze(-1)
+    strict = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(-1)
+    A = -(kb @ k.transpose(-1, -2) * decay).masked_fill(~strict, 0.0)
+    rows = [A[..., 0, :]]
+    for i in range(1, C):  # forward substitution: row i of (I - A_strict)^-1 - I from the rows above it
+        prev = torch.stack(rows, dim=-2)                                   # [.., i, C]
+        rows.append(A[..., i, :] + (A[..., i, :i].unsqueeze(-2) @ prev).squeeze(-2))
+    Tm = torch.stack(rows, dim=-2) + torch.eye(C, device=q.device)
+    w = Tm @ (kb * torch.exp(gc).unsqueeze(-1))
+    u = Tm @ vb
+    local = (q @ k.transpose(-1, -2) * decay).masked_fill(~(strict | torch.eye(C, dtype=torch.bool, device=q.device)), 0.0)
+    q_in = q * torch.exp(gc).unsqueeze(-1)
+    last = gc[..., -1]
+    k_out = k * torch.exp(last.unsqueeze(-1) - gc).unsqueeze(-1)
+    S = q.new_zeros(B, H, Dk, Dv)
+    outs = []
+    for n in range(N):
+        v_new = u[:, :, n] - w[:, :, n] @ S
+        outs.append(q_in[:, :, n] @ S + local[:, :, n] @ v_new)
+        S = S * torch.exp(last[:, :, n])[..., None, None] + k_out[:, :, n].transpose(-1, -2) @ v_new
+    o = torch.stack(outs, dim=2).reshape(B, H, N * C, Dv)[:, :, :T]
+    return o.permute(0, 2, 1, 3)
+
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, *, scale: Optional[float] = None):
     """Recurrent form of the gated delta rule.  q,k [B,T,H,Dk], v [B,T,H,Dv], g [B,T,H] (log decay, <= 0), beta [B,T,H].
     S_t = exp(g_t) S_{t-1} + beta_t k_t (v_t - exp(g_t) S_{t-1}^T k_t)^T ; o_t = S_t^T q_t."""
     B, T, H, Dk = q.shape

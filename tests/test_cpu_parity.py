@@ -137,3 +137,21 @@ def test_dropping_ignored_rows_before_the_lm_head_changes_nothing():
 
     a, b = run(False), run(True)
     assert abs(a[0] - b[0]) < 1e-4 and abs(a[1] - b[1]) < 1e-5 * a[1] and torch.allclose(a[2], b[2], atol=1e-6)
+
+
+def test_chunked_gated_delta_rule_equals_the_recurrence():
+    """The chunk-wise evaluation (triangular solve inside chunks of 64, state carried between chunks) reproduces the
+    step-by-step recurrence and its gradients, including a ragged last chunk."""
+    from surogate_b200.runtime.torch_fns import gated_delta_rule, gated_delta_rule_recurrent
+
+    torch.manual_seed(0)
+    B, T, H, Dk, Dv = 2, 150, 3, 16, 24
+    ins = [torch.randn(B, T, H, Dk), torch.randn(B, T, H, Dk), torch.randn(B, T, H, Dv), -torch.rand(B, T, H) * 0.5, torch.rand(B, T, H)]
+    for t in ins:
+        t.requires_grad_(True)
+    a, b = gated_delta_rule(*ins), gated_delta_rule_recurrent(*ins)
+    assert torch.allclose(a, b, atol=1e-5)
+    ga = torch.autograd.grad(a.square().sum(), ins)
+    gb = torch.autograd.grad(b.square().sum(), ins)
+    for x, y in zip(ga, gb):
+        assert torch.allclose(x, y, atol=1e-4 * float(y.abs().max()))
