@@ -68,8 +68,9 @@ class NemotronHAttentionBlock(_MixerBlock):
 
 class NemotronHMoEBlock(_MixerBlock):
     def __init__(self, d_model, num_experts, num_experts_per_tok, moe_d_ff, shared_d_ff, n_group=1, topk_group=1, norm_topk_prob=True,
-                 routed_scaling_factor=1.0, eps=1e-5, **_):
+                 routed_scaling_factor=1.0, eps=1e-5, ep_size=1, **_):
         super().__init__(d_model, eps)
+        self.E, self.K, self.ep_size = num_experts, num_experts_per_tok, ep_size
         self.attrs = dict(top_k=num_experts_per_tok, n_group=n_group, topk_group=topk_group, norm_topk_prob=norm_topk_prob,
                           routed_scaling_factor=routed_scaling_factor)
         self.declare_param("router_weight", (num_experts, d_model), hf=hf.direct(f"{_M}.gate.weight"))
@@ -80,5 +81,20 @@ class NemotronHMoEBlock(_MixerBlock):
         self.declare_param("shared_down_weight", (d_model, shared_d_ff), hf=hf.direct(f"{_M}.shared_experts.down_proj.weight"))
 
     def mixer(self, h, position_ids):
-        names = ("router_weight", "router_score_bias", "experts_up", "experts_down", "shared_up_weight", "shared_down_weight")
-        return F.torch_fn("moe_sigmoid_relu2", [h] + [self.p(n) for n in names], [("moe_out", h.shape, "act")], **self.attrs)
+        """Router as a PyTorch function; the experts run on the grouped GEMM path (permute -> up -> ReLU^2 -> down -> weighted
+        un-permute, expert-parallel when ``ep_size`` > 1); the shared expert is two dense GEMMs."""
+        lead = h.shape[:-1]
+        tw, ti = F.torch_fn("sigmoid_group_router", [h, self.p("router_weight"), self.p("router_score_bias")],
+                            [("topk_weights", lead + (self.K,), "fp32"), ("topk_index", lead + (self.K,), "int32")], **self.attrs)
+        xp, plan = F.moe_permute(h, ti, num_experts=self.E, top_k=self.K)
+        if self.ep_size > 1:
+            xp, plan = F.ep_dispatch(xp, plan)
+        u = F.moe_grouped_gemm(xp, self.p("experts_up"), plan, name="moe_up", role="experts_gate_up")
+        a = F.torch_fn("relu2", [u], [("moe_relu2", u.shape, "act")])
+        d = F.moe_grouped_gemm(a, self.p("experts_down"), plan, name="moe_down", role="experts_down")
+        if self.ep_size > 1:
+            d = F.ep_combine(d, plan)
+        y = F.moe_unpermute(d, tw, plan, h.shape)
+        su = F.matmul(h, self.p("shared_up_weight"), name="shared_up", role="shared_up")
+        sa = F.torch_fn("relu2", [su], [("shared_relu2", su.shape, "act")])
+        return F.add(y, F.matmul(sa, self.p("shared_down_weight"), name="shared_down", role="shared_down"), name="moe_plus_shared")

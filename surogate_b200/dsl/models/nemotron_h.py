@@ -28,14 +28,15 @@ class NemotronHModel(nn.Model):
     def __init__(self, vocab_size: int = 131072, d_model: int = 4096, layer_types: Optional[List[str]] = None, num_query_heads: int = 32, num_kv_heads: int = 8,
                  head_size: int = 128, eps: float = 1e-5, mamba_num_heads: int = 128, mamba_head_dim: int = 64, n_groups: int = 8, ssm_state_size: int = 128,
                  conv_kernel: int = 4, chunk_size: int = 128, num_experts: int = 8, num_experts_per_tok: int = 2, moe_d_ff: int = 7688, shared_d_ff: int = 7688,
-                 n_group: int = 1, topk_group: int = 1, norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, tie_word_embeddings: bool = False):
+                 n_group: int = 1, topk_group: int = 1, norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, tie_word_embeddings: bool = False, ep_size: int = 1):
         super().__init__()
         types = list(layer_types or ["mamba", "moe", "attention", "moe"])
+        self.ep_size = ep_size
         self.vocab_size, self.d_model, self.n_layers = vocab_size, d_model, len(types)
         kinds = {"mamba": (NemotronHMambaBlock, dict(d_model=d_model, mamba_num_heads=mamba_num_heads, mamba_head_dim=mamba_head_dim, n_groups=n_groups,
                                                      ssm_state_size=ssm_state_size, conv_kernel=conv_kernel, chunk_size=chunk_size, eps=eps)),
                  "attention": (NemotronHAttentionBlock, dict(d_model=d_model, num_query_heads=num_query_heads, num_kv_heads=num_kv_heads, head_size=head_size, eps=eps)),
-                 "moe": (NemotronHMoEBlock, dict(d_model=d_model, num_experts=num_experts, num_experts_per_tok=num_experts_per_tok, moe_d_ff=moe_d_ff,
+                 "moe": (NemotronHMoEBlock, dict(ep_size=ep_size, d_model=d_model, num_experts=num_experts, num_experts_per_tok=num_experts_per_tok, moe_d_ff=moe_d_ff,
                                                  shared_d_ff=shared_d_ff, n_group=n_group, topk_group=topk_group, norm_topk_prob=norm_topk_prob,
                                                  routed_scaling_factor=routed_scaling_factor, eps=eps))}
         unknown = sorted(set(types) - set(kinds))

@@ -407,6 +407,31 @@ def gated_delta_rule_op(q, k, v, g, beta, *, scale: Optional[float] = None):
 
 
 # ---------------------------------------------------------------------------------------------- Nemotron-H style MoE
+@register("sigmoid_group_router")
+def sigmoid_group_router(x, gate_w, score_bias, *, top_k: int, n_group: int = 1, topk_group: int = 1, norm_topk_prob: bool = True,
+                         routed_scaling_factor: float = 1.0):
+    """Sigmoid router with a selection-only score bias and group-limited top-k (experts are chosen only inside the ``topk_group``
+    best of ``n_group`` groups, a group's score being the sum of its two best experts).  Weights are the unbiased scores of the
+    chosen experts, renormalised and scaled.  Returns (weights fp32 [.., K], indices int32 [.., K])."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    E = gate_w.shape[0]
+    scores = torch.sigmoid(F.linear(x2.float(), gate_w.float()))
+    choice = scores.detach() + score_bias.float()
+    if n_group > 1:
+        gs = choice.view(-1, n_group, E // n_group).topk(2, dim=-1)[0].sum(-1)
+        gi = torch.topk(gs, k=topk_group, dim=-1, sorted=False)[1]
+        gmask = torch.zeros_like(gs).scatter_(1, gi, 1.0)
+        mask = gmask.unsqueeze(-1).expand(-1, n_group, E // n_group).reshape(-1, E).bool()
+        choice = choice.masked_fill(~mask, 0.0)
+    top_i = torch.topk(choice, k=top_k, dim=-1, sorted=False)[1]
+    w = scores.gather(1, top_i)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    w = w * routed_scaling_factor
+    return w.reshape(*lead, top_k), top_i.to(torch.int32).reshape(*lead, top_k)
+
+
 @register("moe_sigmoid_relu2")
 def moe_sigmoid_relu2(x, gate_w, score_bias, up, down, shared_up, shared_down, *, top_k: int, n_group: int = 1, topk_group: int = 1,
                       norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0):
