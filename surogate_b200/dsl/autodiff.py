@@ -329,6 +329,14 @@ def _moe_gg(b, op, dy):
     return {x: g}
 
 
+@register_autodiff("moe_expert_bias_add")
+def _moe_bias_add(b, op, dy):
+    y, bias, plan = op.inputs
+    g = b.new_grad(y)
+    b.emit("moe_expert_bias_add_backward", [dy[0], bias, b.fwd_tensor(plan)], [g, b.param_grad(bias)])
+    return {y: g}
+
+
 @register_autodiff("moe_unpermute")
 def _moe_unpermute(b, op, dy):
     y, tw, plan = op.inputs

@@ -43,33 +43,47 @@ class SinkAttention(Module):
 
 
 class BiasedClampMoE(Module):
-    def __init__(self, d_model, d_ff, num_experts, top_k, alpha=1.702, limit=7.0, prefix=f"{_P}.mlp"):
+    """Router with bias and softmax over the chosen logits; experts with biases, interleaved gate / up columns and the clamped
+    activation.  The checkpoint stores expert weights input-major ([E, C, 2M], [E, M, C]); they are kept output-major here
+    (transposed on load / export) so that the experts run on the grouped GEMM path, expert-parallel when ``ep_size`` > 1."""
+
+    def __init__(self, d_model, d_ff, num_experts, top_k, alpha=1.702, limit=7.0, prefix=f"{_P}.mlp", ep_size=1):
         super().__init__()
-        self.top_k, self.alpha, self.limit = top_k, alpha, limit
+        self.E, self.top_k, self.alpha, self.limit, self.ep_size = num_experts, top_k, alpha, limit, ep_size
         self.declare_param("router_weight", (num_experts, d_model), hf=hf.direct(f"{prefix}.router.weight"))
         self.declare_param("router_bias", (num_experts,), init="zeros", decay=False, hf=hf.direct(f"{prefix}.router.bias"))
-        self.declare_param("experts_gate_up", (num_experts, d_model, 2 * d_ff), hf=hf.direct(f"{prefix}.experts.gate_up_proj"))
+        self.declare_param("experts_gate_up", (num_experts, 2 * d_ff, d_model), quantizable=True, hf=hf.transform(f"{prefix}.experts.gate_up_proj", fn="transpose"))
         self.declare_param("experts_gate_up_bias", (num_experts, 2 * d_ff), init="zeros", decay=False, hf=hf.direct(f"{prefix}.experts.gate_up_proj_bias"))
-        self.declare_param("experts_down", (num_experts, d_ff, d_model), hf=hf.direct(f"{prefix}.experts.down_proj"))
+        self.declare_param("experts_down", (num_experts, d_model, d_ff), quantizable=True, hf=hf.transform(f"{prefix}.experts.down_proj", fn="transpose"))
         self.declare_param("experts_down_bias", (num_experts, d_model), init="zeros", decay=False, hf=hf.direct(f"{prefix}.experts.down_proj_bias"))
 
     def forward(self, x):
-        return F.torch_fn("moe_biased_clamp_swiglu",
-                          [x, self.p("router_weight"), self.p("router_bias"), self.p("experts_gate_up"), self.p("experts_gate_up_bias"),
-                           self.p("experts_down"), self.p("experts_down_bias")], [("moe_out", x.shape, "act")],
-                          top_k=self.top_k, alpha=self.alpha, limit=self.limit)
+        lead = x.shape[:-1]
+        tw, ti = F.torch_fn("topk_softmax_router", [x, self.p("router_weight"), self.p("router_bias")],
+                            [("topk_weights", lead + (self.top_k,), "fp32"), ("topk_index", lead + (self.top_k,), "int32")], top_k=self.top_k)
+        xp, plan = F.moe_permute(x, ti, num_experts=self.E, top_k=self.top_k)
+        if self.ep_size > 1:
+            xp, plan = F.ep_dispatch(xp, plan)
+        h = F.moe_grouped_gemm(xp, self.p("experts_gate_up"), plan, name="moe_gate_up", role="experts_gate_up")
+        h = F.moe_expert_bias_add(h, self.p("experts_gate_up_bias"), plan, name="moe_gate_up_biased")
+        h = F.torch_fn("clamped_glu_interleaved", [h], [("moe_act", h.shape[:-1] + (h.shape[-1] // 2,), "act")], alpha=self.alpha, limit=self.limit)
+        h = F.moe_grouped_gemm(h, self.p("experts_down"), plan, name="moe_down", role="experts_down")
+        h = F.moe_expert_bias_add(h, self.p("experts_down_bias"), plan, name="moe_down_biased")
+        if self.ep_size > 1:
+            h = F.ep_combine(h, plan)
+        return F.moe_unpermute(h, tw, plan, x.shape)
 
 
 class GptOssBlock(Block):
     _name_remap_ = {**DENSE_BLOCK_NAME_REMAP, "mlp.*": ""}
 
     def __init__(self, d_model, num_query_heads, num_kv_heads, head_size, d_ff, num_experts, num_experts_per_tok, eps=1e-5, rope_theta=150000.0,
-                 rope_scaling=None, sliding_window=0, max_seq=131072):
+                 rope_scaling=None, sliding_window=0, max_seq=131072, ep_size=1):
         super().__init__()
         self.attn_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.input_layernorm.weight")
         self.self_attn = SinkAttention(d_model, num_query_heads, num_kv_heads, head_size, sliding_window, rope_theta, rope_scaling, max_seq)
         self.mlp_norm = RMSNorm(d_model, eps=eps, hf_name=f"{_P}.post_attention_layernorm.weight")
-        self.mlp = BiasedClampMoE(d_model, d_ff, num_experts, num_experts_per_tok)
+        self.mlp = BiasedClampMoE(d_model, d_ff, num_experts, num_experts_per_tok, ep_size=ep_size)
 
     def forward(self, x, residual, position_ids):
         residual, h = self.attn_norm(residual, x)

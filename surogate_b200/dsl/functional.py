@@ -164,6 +164,11 @@ def moe_grouped_gemm(x: Proxy, w: Proxy, plan: Proxy, name: str, role: str) -> P
     return _t().emit("moe_grouped_gemm", [x, w, plan], [(name, (x.shape[0], N), "act")], role=role)[0]
 
 
+def moe_expert_bias_add(y: Proxy, bias: Proxy, plan: Proxy, name: str = "moe_biased") -> Proxy:
+    """Adds each expert's bias row ([E, N]) to the permuted rows that belong to that expert."""
+    return _t().emit("moe_expert_bias_add", [y, bias, plan], [(name, y.shape, "act")])[0]
+
+
 def moe_unpermute(y: Proxy, topk_weights: Proxy, plan: Proxy, out_shape: Shape, name: str = "moe_out") -> Proxy:
     """Weighted sum of each token's K expert outputs, back in token order."""
     return _t().emit("moe_unpermute", [y, topk_weights, plan], [(name, tuple(out_shape), "act")])[0]

@@ -24,14 +24,15 @@ class GptOssModel(nn.Model):
     def __init__(self, vocab_size: int = 201088, d_model: int = 2880, n_layers: int = 24, num_query_heads: int = 64, num_kv_heads: int = 8,
                  d_ff: int = 2880, max_seq: int = 131072, head_size: int = 64, eps: float = 1e-5, rope_theta: float = 150000.0, num_experts: int = 32,
                  num_experts_per_tok: int = 4, sliding_window: int = 128, layer_types: Optional[List[str]] = None, rope_scaling=None,
-                 tie_word_embeddings: bool = False):
+                 tie_word_embeddings: bool = False, ep_size: int = 1):
         super().__init__()
+        self.ep_size = ep_size
         self.vocab_size, self.d_model, self.n_layers = vocab_size, d_model, n_layers
         self.num_experts, self.num_experts_per_tok = num_experts, num_experts_per_tok
         types = list(layer_types) if layer_types else ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n_layers)]
         scaling = dict(rope_scaling) if isinstance(rope_scaling, dict) and (rope_scaling.get("rope_type") or rope_scaling.get("type", "default")) != "default" else None
         common = dict(d_model=d_model, num_query_heads=num_query_heads, num_kv_heads=num_kv_heads, head_size=head_size, d_ff=d_ff, num_experts=num_experts,
-                      num_experts_per_tok=num_experts_per_tok, eps=eps, rope_theta=float(rope_theta), rope_scaling=scaling, max_seq=max_seq)
+                      num_experts_per_tok=num_experts_per_tok, eps=eps, rope_theta=float(rope_theta), rope_scaling=scaling, max_seq=max_seq, ep_size=ep_size)
         classes = {}
         if "sliding_attention" in types:
             classes["sliding_attention"] = (_named(GptOssBlock, "GptOssSlidingBlock"), dict(common, sliding_window=sliding_window))

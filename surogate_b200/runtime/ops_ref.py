@@ -731,6 +731,35 @@ class RefOps:
                 tgt[e] += (dy[s:t].t() @ x[s:t]).to(tgt.dtype)
         return dx, None
 
+    @staticmethod
+    def _row_experts(plan, rows: int, device):
+        """(expert of each permuted row, whether the row is a real routed row) from the plan's device-side offsets / counts:
+        no host sync, and padding rows between experts (kernel plans pad each expert's range) are marked invalid."""
+        p = getattr(plan, "local", None) or plan
+        off = p.offsets.to(device=device, dtype=torch.int64)
+        E = off.numel() - 1 if off.numel() > p.counts.numel() else p.counts.numel()
+        r = torch.arange(rows, device=device)
+        eid = torch.bucketize(r, off[1:E + 1].contiguous(), right=True).clamp_max(E - 1)
+        valid = (r - off[eid]) < p.counts.to(device=device, dtype=torch.int64)[eid]
+        return eid, valid
+
+    def moe_expert_bias_add(self, ctx, op, y, bias, plan):
+        eid, valid = self._row_experts(plan, y.shape[0], y.device)
+        b = ctx.local_experts(bias)
+        return (y + (b.to(y.dtype)[eid] * valid.unsqueeze(-1)),)
+
+    def moe_expert_bias_add_backward(self, ctx, op, dy, bias, plan):
+        eid, valid = self._row_experts(plan, dy.shape[0], dy.device)
+        tgt, acc = ctx.grad_target(op.outputs[1])
+        if tgt is not None:
+            tgt = ctx.local_experts(tgt)
+            g = torch.zeros(tgt.shape, dtype=torch.float32, device=dy.device).index_add_(0, eid, dy.float() * valid.unsqueeze(-1))
+            if acc:
+                tgt.add_(g.to(tgt.dtype))
+            else:
+                tgt.copy_(g.to(tgt.dtype))
+        return dy, None
+
     def moe_unpermute(self, ctx, op, yp, tw, plan):
         plan = plan.local or plan
         N, K = plan.num_tokens, plan.top_k

@@ -232,6 +232,24 @@ def attention_general(qkv, sinks=None, *, num_q_heads: int, num_kv_heads: int, h
 
 
 # ---------------------------------------------------------------------------------------------- GPT-OSS style MoE
+@register("topk_softmax_router")
+def topk_softmax_router(x, router_w, router_b, *, top_k: int):
+    """linear (+ bias) -> top-k logits -> softmax over the chosen k.  Returns (weights fp32 [.., K], indices int32 [.., K])."""
+    lead = x.shape[:-1]
+    logits = F.linear(x.reshape(-1, x.shape[-1]).float(), router_w.float(), router_b.float() if router_b is not None else None)
+    top_v, top_i = torch.topk(logits, top_k, dim=-1)
+    return torch.softmax(top_v, dim=-1).reshape(*lead, top_k), top_i.to(torch.int32).reshape(*lead, top_k)
+
+
+@register("clamped_glu_interleaved")
+def clamped_glu_interleaved(h, *, alpha: float = 1.702, limit: float = 7.0):
+    """[.., 2M] with gate and up interleaved (even columns gate, odd columns up): gate clamped above, up clamped on both sides at
+    ``limit``, y = (up + 1) * gate * sigmoid(alpha * gate)."""
+    hf = h.float()
+    gate, up = hf[..., ::2].clamp(max=limit), hf[..., 1::2].clamp(min=-limit, max=limit)
+    return ((up + 1) * gate * torch.sigmoid(gate * alpha)).to(h.dtype)
+
+
 @register("moe_biased_clamp_swiglu")
 def moe_biased_clamp_swiglu(x, router_w, router_b, gate_up, gate_up_b, down, down_b, *, top_k: int, alpha: float = 1.702, limit: float = 7.0):
     """Router = linear(+bias) -> top-k -> softmax over the k selected logits.  Experts: interleaved (gate, up) columns with
