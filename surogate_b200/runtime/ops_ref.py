@@ -734,13 +734,21 @@ class RefOps:
     @staticmethod
     def _row_experts(plan, rows: int, device):
         """(expert of each permuted row, whether the row is a real routed row) from the plan's device-side offsets / counts:
-        no host sync, and padding rows between experts (kernel plans pad each expert's range) are marked invalid."""
+        no host sync, and padding rows between experts (kernel plans pad each expert's range) are marked invalid.
+        Plans with a ``counts`` tensor keep [E + 1] range starts in ``offsets``; expert-parallel receive plans keep
+        [El + 1 starts, overflow, El real counts] in one tensor."""
         p = getattr(plan, "local", None) or plan
         off = p.offsets.to(device=device, dtype=torch.int64)
-        E = off.numel() - 1 if off.numel() > p.counts.numel() else p.counts.numel()
+        counts = getattr(p, "counts", None)
+        if counts is not None:
+            E = counts.numel()
+            counts = counts.to(device=device, dtype=torch.int64)
+        else:
+            E = (off.numel() - 2) // 2
+            counts = off[E + 2:2 * E + 2]
         r = torch.arange(rows, device=device)
         eid = torch.bucketize(r, off[1:E + 1].contiguous(), right=True).clamp_max(E - 1)
-        valid = (r - off[eid]) < p.counts.to(device=device, dtype=torch.int64)[eid]
+        valid = (r - off[eid]) < counts[eid]
         return eid, valid
 
     def moe_expert_bias_add(self, ctx, op, y, bias, plan):
