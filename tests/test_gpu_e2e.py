@@ -218,3 +218,34 @@ def test_dropping_ignored_rows_on_gpu():
     for name in gb:
         err = (ga[name].float() - gb[name].float()).norm() / (gb[name].float().norm() + 1e-12)
         assert err < 0.02, (name, float(err))
+
+
+@pytest.mark.parametrize("arch", ["gpt_oss", "nemotron_h"])
+def test_biased_and_relu2_experts_on_the_grouped_gemm_path(arch):
+    """GPT-OSS (biased experts, interleaved clamped GLU) and Nemotron-H (sigmoid group router, ReLU^2 experts, shared expert) run
+    their experts on the grouped tcgen05 GEMM: same loss and gradients as the PyTorch backend."""
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    if arch == "gpt_oss":
+        model = dict(architecture="GptOssForCausalLM", vocab_size=2048, d_model=256, n_layers=2, num_query_heads=4, num_kv_heads=2, head_size=64, d_ff=128,
+                     num_experts=8, num_experts_per_tok=2, sliding_window=64, max_seq=1024)
+    else:
+        model = dict(architecture="NemotronHForCausalLM", vocab_size=2048, d_model=256, layer_types=["moe", "attention", "moe"], num_query_heads=4, num_kv_heads=2,
+                     head_size=64, num_experts=8, num_experts_per_tok=2, moe_d_ff=128, shared_d_ff=256)
+
+    def make(backend):
+        tr = Trainer(TrainerConfig(model=model, batch_size=2, seq_len=128, recipe="bf16", optimizer="adamw", backend=backend, learning_rate=1e-3,
+                                   lmhead_chunk_rows=200), device=torch.device("cuda:0"))
+        tr.init_weights(seed=0)
+        return tr
+
+    x, y = _batch(6, T=128)
+    a, b = make("cuda"), make("ref")
+    ra, rb = a.forward_backward(x, y), b.forward_backward(x, y)
+    la, lb = (ra["loss_sum"] / ra["n_valid"]).item(), (rb["loss_sum"] / rb["n_valid"]).item()
+    assert abs(la - lb) < 2e-2 * abs(lb), (la, lb)
+    ga, gb = a.get_gradients(), b.get_gradients()
+    for name in gb:
+        den = gb[name].float().norm() + 1e-12
+        ea = (ga[name].float() - gb[name].float()).norm() / den
+        assert ea < 0.1 or float(den) < 1e-6, f"{name}: rel err {ea.item():.4f}"
