@@ -64,6 +64,17 @@ class PipelineTrainer:
         self.tied_group = None
         if self._tied and self.first_rank != self.last_rank:
             self.tied_group = dist.new_group([self.first_rank, self.last_rank])
+        # One communicator per DIRECTED pair of neighbouring ranks.  With interleaved stages two ranks send to each other in
+        # the same tick; on one communicator each side's send would sit in front of the receive the other side is waiting
+        # for.  Separate communicators (own streams) keep the two directions independent.
+        self.link: Dict[Tuple[int, int], Any] = {}
+        pairs = []
+        for a, b in zip(self.stages, self.stages[1:]):
+            for pair in ((a.gpu, b.gpu), (b.gpu, a.gpu)):  # forward boundary, backward gradient
+                if pair[0] != pair[1] and pair not in pairs:
+                    pairs.append(pair)
+        for src, dst in pairs:  # every rank creates every group, in the same order
+            self.link[(src, dst)] = dist.new_group([src, dst]) if self.world > 2 or len(pairs) > 1 else group
 
     # ------------------------------------------------------------------ weights
     def init_weights(self, seed: Optional[int] = None) -> None:
@@ -105,15 +116,17 @@ class PipelineTrainer:
 
     # ------------------------------------------------------------------ point-to-point boundaries
     def _send(self, tensors: Tuple[torch.Tensor, ...], dst: int, pending: list) -> None:
+        g = self.link.get((self.rank, dst), self.group)
         for t in tensors:
             t = t.contiguous()
-            pending.append((dist.isend(t, dst, group=self.group), t))  # the tensor stays referenced until the send completes
+            pending.append((dist.isend(t, dst, group=g), t))  # the tensor stays referenced until the send completes
 
     def _recv(self, rows: int, T: int, src: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        g = self.link.get((src, self.rank), self.group)
         out = []
         for _ in range(2):
             buf = torch.empty(rows, T, self.d_model, dtype=self.act_dtype, device=self.device)
-            dist.recv(buf, src, group=self.group)
+            dist.recv(buf, src, group=g)
             out.append(buf)
         return out[0], out[1]
 

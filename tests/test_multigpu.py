@@ -96,14 +96,16 @@ def test_expert_replacement_keeps_the_trajectory():
         assert abs(a - b) < 2e-2 * abs(b), (two["losses"], one["losses"])
 
 
-def test_pipeline_stages_on_two_gpus_match_one_gpu():
+@pytest.mark.parametrize("stage_layers", [0, 1])
+def test_pipeline_stages_on_two_gpus_match_one_gpu(stage_layers):
     """Layer ranges per GPU with boundaries sent peer to peer (NCCL send / recv over NVLink): the trajectory of the one-GPU run
-    with the same micro-batches."""
+    with the same micro-batches.  ``stage_layers=1`` interleaves two stages per GPU, so both directions of the link are in use
+    in the same tick."""
     model = dict(architecture="Qwen3ForCausalLM", vocab_size=1024, d_model=256, n_layers=4, num_query_heads=2, num_kv_heads=1, head_size=128, d_ff=512,
                  tie_word_embeddings=True)
     one = run_worker(1, dict(ARGS, model=model, zero=0, grad_accum=2))
-    r = run_worker(2, dict(ARGS, model=model, pp=True, grad_accum=1), port=29761)
-    assert r["world"] == 2 and len(r["stages"]) == 2
+    r = run_worker(2, dict(ARGS, model=model, pp=True, grad_accum=1, stage_layers=stage_layers), port=29761 + stage_layers)
+    assert r["world"] == 2 and len(r["stages"]) == (4 if stage_layers else 2)
     for a, b in zip(r["losses"], one["losses"]):
         assert abs(a - b) < 2e-2 * abs(b), (r["losses"], one["losses"])
     for a, b in zip(r["norms"], one["norms"]):
