@@ -155,3 +155,21 @@ def test_chunked_gated_delta_rule_equals_the_recurrence():
     gb = torch.autograd.grad(b.square().sum(), ins)
     for x, y in zip(ga, gb):
         assert torch.allclose(x, y, atol=1e-4 * float(y.abs().max()))
+
+
+def test_expert_of_each_row_is_read_from_every_plan_layout():
+    """Per-expert bias rows are found from device-side range starts / counts: plain plans ([E + 1] starts + counts), kernel plans
+    with padded ranges, and expert-parallel receive plans ([El + 1 starts, overflow, El counts] in one tensor)."""
+    from types import SimpleNamespace
+
+    from surogate_b200.runtime.ops_ref import RefOps
+
+    plain = SimpleNamespace(offsets=torch.tensor([0, 2, 2, 5]), counts=torch.tensor([2, 0, 3]), local=None)
+    eid, valid = RefOps._row_experts(plain, 5, torch.device("cpu"))
+    assert eid.tolist() == [0, 0, 2, 2, 2] and valid.all()
+    padded = SimpleNamespace(offsets=torch.tensor([0, 4, 8, 12]), counts=torch.tensor([2, 0, 3]), local=None)  # ranges padded to 4 rows
+    eid, valid = RefOps._row_experts(padded, 12, torch.device("cpu"))
+    assert eid.tolist() == [0] * 4 + [1] * 4 + [2] * 4 and valid.tolist() == [True, True, False, False] + [False] * 4 + [True, True, True, False]
+    ep = SimpleNamespace(offsets=torch.tensor([0, 4, 8, 0, 3, 1]), local=None)  # El = 2: starts [0, 4, 8], overflow 0, counts [3, 1]
+    eid, valid = RefOps._row_experts(ep, 8, torch.device("cpu"))
+    assert eid.tolist() == [0] * 4 + [1] * 4 and valid.tolist() == [True, True, True, False, True, False, False, False]
