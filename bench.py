@@ -133,6 +133,7 @@ def main():
     ap.add_argument("--no-offload", action="store_true", help="keep weights and optimizer state on the device for configs that offload by default")
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "library"], help="native = tcgen05 flash attention of this repo")
     ap.add_argument("--profile", default=None, help="write a per-kernel time table of one extra step (torch.profiler, rank 0) to this path; not a timed run")
+    ap.add_argument("--resident-layers", type=int, default=0, help="offload configs: keep the frozen weights of the first N layers in device memory")
     ap.add_argument("--graphs", action="store_true", help="replay forward + backward from CUDA graphs (one GPU, dense models)")
     ap.add_argument("--drop-ignored-rows", action="store_true", help="compact rows without a target away before the LM head")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
@@ -172,7 +173,7 @@ def main():
                         lora=spec.get("lora"), offload_master=bool(spec.get("offload")) and not args.no_offload,
                         offload_optimizer=bool(spec.get("offload")) and not args.no_offload, keep_gathered=not spec.get("offload"),
                         ep_capacity_factor=float(max(1, ep)),  # room for every routed row even if all tokens pick one rank: nothing is dropped
-                        use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
+                        resident_layers=args.resident_layers, use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
                         ep_plan_refresh_interval=2)            # least-loaded placement settles during warm-up; later refreshes are inside the timed region
     if spec.get("recompute"):
         cfg.recompute = True
@@ -269,7 +270,7 @@ def main():
             "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
                        "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(cfg.recompute), "micro_batch_per_gpu": mb,
                        "lora_rank": (spec.get("lora") or {}).get("rank"), "offload": bool(cfg.offload_master),
-                       "cuda_graphs": bool(getattr(tr, "graph_replays", 0)), "drop_ignored_rows": bool(cfg.lmhead_drop_ignored_rows),
+                       "cuda_graphs": bool(getattr(tr, "graph_replays", 0)), "drop_ignored_rows": bool(cfg.lmhead_drop_ignored_rows), "resident_layers": int(args.resident_layers),
                        "weight_h2d_bytes_per_step": int(tr.store.h2d_bytes // max(1, args.steps + args.warmup + (0 if args.no_e2e else args.steps + 1))),
                        "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events on the launching stream, barrier+synchronize on both sides, max over ranks"},

@@ -113,8 +113,11 @@ class ParamStore:
     def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
                  comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
                  expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False,
-                 owned: Optional[Callable[[Any], bool]] = None):
+                 owned: Optional[Callable[[Any], bool]] = None, resident_layers: int = 0):
         self.cm = cm
+        # with host-resident masters: the frozen weights of the first ``resident_layers`` layers stay in device memory instead,
+        # so their per-traversal gather is NVLink / local traffic rather than PCIe (spend spare HBM on the layers used first)
+        self.resident_layers = int(resident_layers)
         # pipeline stages: ``owned(entry)`` says whether this process holds the parameter at all; the others are never
         # allocated, initialised, loaded or stepped here
         self.owned = owned
@@ -192,7 +195,7 @@ class ParamStore:
             for b in self.buckets.values():
                 if b.expert:
                     continue
-                if self.offload_master:
+                if self.offload_master and not self._resident(b):
                     max_shard = max(max_shard, b.shard_numel)
                 else:
                     need += (b.shard_numel * 2 + 255) // 256 * 256 + 256
@@ -210,7 +213,7 @@ class ParamStore:
                 b.master = torch.zeros(b.numel, dtype=self.master_dtype, device=self.device)
                 b.work = b.master if self.master_dtype == self.param_dtype else torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
                 continue
-            if self.offload_master:
+            if self.offload_master and not self._resident(b):
                 b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, pin_memory=pin)
                 b.work_host = torch.zeros(b.shard_numel, dtype=self.param_dtype, pin_memory=pin) if (
                     self.host_work_copy and self.master_dtype != self.param_dtype) else None
@@ -231,6 +234,11 @@ class ParamStore:
                 b.work = b.master
             elif self.zero_level < 3:
                 b.work = torch.zeros(b.numel, dtype=self.param_dtype, device=self.device)
+
+    def _resident(self, b: Bucket) -> bool:
+        """Frozen layer buckets below ``resident_layers`` keep their master shard on the device although masters are offloaded."""
+        return self.resident_layers > 0 and b.layer is not None and b.layer < self.resident_layers and not b.trainable and not b.expert \
+            and self.master_dtype == self.param_dtype
 
     @property
     def sharded(self) -> bool:

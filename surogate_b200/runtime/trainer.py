@@ -64,6 +64,7 @@ class TrainerConfig:
     skip_quant_last_layers: int = 0
     offload_optimizer: bool = False
     offload_master: bool = False
+    resident_layers: int = -1   # with offload_master: frozen weights of the first N layers stay in device memory (-1: SUROGATE_RESIDENT_LAYERS or 0)
     qlora: Optional[str] = None  # bnb_nf4 | fp8_block | nvfp4: frozen base weights stored block-quantised, rebuilt per layer
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
@@ -126,7 +127,8 @@ class Trainer:
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
         self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
                                 zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size,
-                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training, owned=owned)
+                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training, owned=owned,
+                                resident_layers=cfg.resident_layers if cfg.resident_layers >= 0 else int(os.environ.get("SUROGATE_RESIDENT_LAYERS", "0")))
         from .ops_cuda import make_backend
 
         self.backend = make_backend(self.device, cfg.backend, lmhead_chunk_rows=cfg.lmhead_chunk_rows, attention=cfg.attention)

@@ -45,3 +45,15 @@ def test_lora_with_host_resident_base():
     _, off = _run(optimizer="adamw", lora=lora, offload_master=True, offload_optimizer=True)
     for a, b in zip(base, off):
         assert abs(a["loss"] - b["loss"]) < 1e-6
+
+
+def test_resident_layers_keep_frozen_weights_on_the_device_side():
+    """With offloaded masters the first N layers' frozen weights can stay resident: same trajectory, and the flag only applies to
+    frozen layer buckets."""
+    lora = dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "v_proj", "down_proj"], rslora=False, train_router=False)
+    tr_a, a = _run(optimizer="adamw", lora=lora, offload_master=True, offload_optimizer=True)
+    tr_b, b = _run(optimizer="adamw", lora=lora, offload_master=True, offload_optimizer=True, resident_layers=1)
+    assert a == b
+    st = tr_b.store
+    assert st._resident(st.buckets["layer0"]) and not st._resident(st.buckets["layer1"]) and not st._resident(st.buckets["embedding"])
+
