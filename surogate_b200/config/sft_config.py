@@ -149,6 +149,7 @@ class SFTConfig:
     offload_saved_tensors: bool = False
     cpu_training: bool = False
     offload_master: bool = False
+    resident_layers: int = -1  # with offload_master: frozen weights of the first N layers stay on the device (-1: SUROGATE_RESIDENT_LAYERS or 0)
     offload_quants: bool = False
     offload_optimizer: bool = False
     offload_grads: bool = False
@@ -310,7 +311,7 @@ class SFTConfig:
             ep_plan_refresh_interval=self.ep_plan_refresh_interval, lora=self.lora_dict(),
             fp8_amax_history=self.fp8_amax_history, skip_quant_first_layers=self.skip_quant_first_layers,
             skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer and not self.cpu_training,
-            offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training, long_context=self.long_context, sequence_chunks=self.sequence_chunks, use_cuda_graphs=self.use_cuda_graphs, lmhead_drop_ignored_rows=self.lmhead_drop_ignored_rows, time_breakdown=self.debug_time_breakdown,
+            offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training, long_context=self.long_context, sequence_chunks=self.sequence_chunks, use_cuda_graphs=self.use_cuda_graphs, lmhead_drop_ignored_rows=self.lmhead_drop_ignored_rows, time_breakdown=self.debug_time_breakdown, resident_layers=self.resident_layers,
             offload_saved_tensors=self.offload_saved_tensors or self.offload_residual,
             qlora="bnb_nf4" if self.qlora_bnb else "fp8_block" if self.qlora_fp8 else "nvfp4" if self.qlora_fp4 else None,
             qlora_block_size=self.qlora_bnb_block_size if self.qlora_bnb else self.qlora_block_size, qlora_double_quant=self.qlora_bnb_double_quant,
