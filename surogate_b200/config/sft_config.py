@@ -163,7 +163,7 @@ class SFTConfig:
     long_context: bool = False
     train_vision: bool = False  # vision-language fine-tuning: rows with images, frozen vision tower, decoder trained (train/vision.py)
     sequence_chunks: int = 1
-    use_cuda_graphs: bool = False  # capture forward + backward per micro-batch (one GPU, dense models, bf16 / fp8 recipes)
+    use_cuda_graphs: bool = True  # replay forward + backward per micro-batch from CUDA graphs where that applies (dense models, replicated weights, bf16 / fp8)
     # parallelism
     gpus: int = 1
     zero_level: int = 1
