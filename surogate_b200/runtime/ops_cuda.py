@@ -223,8 +223,59 @@ class CudaOps(RefOps):
         return dx.reshape(x.shape), None, None
 
     # ------------------------------------------------------------------ attention
+    # ------------------------------------------------------------------ attention of a sequence chunk against its key/value prefix
+    # The tcgen05 kernels take equal query and key lengths.  A chunk's queries against all keys up to its end are therefore run
+    # as causal attention over prefix + chunk with zero queries in the prefix rows: those rows cost compute but nothing else
+    # (their output is dropped; in backward their dO is zero, so they add nothing to dK / dV).
+    def _chunk_native_ok(self, ctx, a, qkv) -> bool:
+        cs = ctx.chunk
+        return (self.attention_impl in ("auto", "native") and hasattr(self.ext, "flash_attn_fwd") and a["head_dim"] == 128 and a.get("causal", True)
+                and not a.get("window", 0) and qkv.dtype == torch.bfloat16 and ctx.doc_ids is None and cs.chunk_len % 128 == 0 and qkv.shape[1] == cs.chunk_len)
+
+    def _chunk_packed(self, ctx, a, q):
+        cs, L = ctx.chunk, ctx.layer
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        B, Tc = q.shape[:2]
+        n = cs.index * cs.chunk_len
+        full = torch.zeros(B, n + Tc, Hq + 2 * Hkv, D, dtype=torch.bfloat16, device=q.device)
+        full[:, :, Hq:Hq + Hkv] = cs.k[L][:, :n + Tc]
+        full[:, :, Hq + Hkv:] = cs.v[L][:, :n + Tc]
+        full[:, n:, :Hq] = q
+        return full.view(B, n + Tc, (Hq + 2 * Hkv) * D), n
+
+    def _chunk_attention_native(self, ctx, op, qkv):
+        a = op.attrs
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        q, k, v = self._split_heads(qkv, a)
+        ctx.chunk.store_kv(ctx.layer, k, v)
+        full, n = self._chunk_packed(ctx, a, q)
+        att, lse = self.ext.flash_attn_fwd(full, Hq, Hkv, float(scale))
+        return att[:, n:].contiguous(), lse[:, n:].contiguous()
+
+    def _chunk_attention_native_backward(self, ctx, op, d_att, qkv, att, lse):
+        a, cs = op.attrs, ctx.chunk
+        Hq, Hkv, D = a["num_q_heads"], a["num_kv_heads"], a["head_dim"]
+        scale = a.get("softmax_scale") or 1.0 / math.sqrt(D)
+        B, Tc = qkv.shape[:2]
+        q, _, _ = self._split_heads(qkv, a)
+        full, n = self._chunk_packed(ctx, a, q)
+        att_full, lse_full = self.ext.flash_attn_fwd(full, Hq, Hkv, float(scale))  # outputs / log-sum-exp of the prefix rows are needed by the kernel
+        d_full = torch.zeros_like(att_full)
+        d_full[:, n:] = d_att
+        dfull = self.ext.flash_attn_bwd(d_full, full, att_full, lse_full, Hq, Hkv, float(scale)).view(B, n + Tc, Hq + 2 * Hkv, D)
+        dk_acc, dv_acc = cs.grad_buffers(ctx.layer)
+        dk_acc[:, :n + Tc] += dfull[:, :, Hq:Hq + Hkv].float()
+        dv_acc[:, :n + Tc] += dfull[:, :, Hq + Hkv:].float()
+        own = slice(n, n + Tc)  # by now these rows also hold what the later chunks contributed
+        out = torch.cat([dfull[:, n:, :Hq].float(), dk_acc[:, own], dv_acc[:, own]], dim=2)
+        return (out.reshape(qkv.shape).to(qkv.dtype),)
+
     def flash_attention(self, ctx, op, qkv):
         from ..ops import attention as att_ops
+
+        if ctx.chunk is not None and self._chunk_native_ok(ctx, op.attrs, qkv):
+            return self._chunk_attention_native(ctx, op, qkv)
 
         if ctx.chunk is None and att_ops.native_supported(op.attrs, qkv, ctx) and self.attention_impl in ("auto", "native"):
             return att_ops.forward(self.ext, op.attrs, qkv, ctx)
@@ -233,6 +284,8 @@ class CudaOps(RefOps):
     def flash_attention_backward(self, ctx, op, d_att, qkv, att, lse):
         from ..ops import attention as att_ops
 
+        if ctx.chunk is not None and self._chunk_native_ok(ctx, op.attrs, qkv):
+            return self._chunk_attention_native_backward(ctx, op, d_att, qkv, att, lse)
         if torch.is_tensor(lse) and ctx.chunk is None:
             return att_ops.backward(self.ext, op.attrs, d_att, qkv, att, lse, ctx)
         return super().flash_attention_backward(ctx, op, d_att, qkv, att, lse)
