@@ -101,8 +101,6 @@ class PipelineTrainer:
             for hf_name, t in p.spec.hf.export(full.detach().to("cpu"), p.layer).items():
                 tensors[hf_name] = t.to(torch.bfloat16).contiguous()
         cfgd = hf_config or self.cfg.model
-        if self.rank == self.last_rank and self._tied and not cfgd.get("tie_word_embeddings", True):
-            pass  # an untied copy is only needed for configs that say untied; tied configs load the embedding for both
         fn = f"model-{self.rank + 1:05d}-of-{self.world:05d}.safetensors"
         save_file(tensors, os.path.join(out_dir, fn), metadata={"format": "pt"})
         names: List[Any] = [None] * self.world
