@@ -141,12 +141,12 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
     const c10::cuda::CUDAGuard guard(x.device());
     if (d_res.has_value() && d_res->defined()) check_bf16(*d_res, "d_res");
     Tensor dx = torch::empty_like(x);
-    const int blocks = sg::rmsnorm_bwd_blocks(rows, num_sms());
+    const int blocks = sg::rmsnorm_bwd_blocks_wide(rows, C, num_sms());
     Tensor partial = torch::empty({blocks, C}, x.options().dtype(at::kFloat));
     Tensor dw = torch::empty({C}, x.options().dtype(at::kFloat));
     g_launches += 2;
-    sg::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), opt_ptr(d_res), dx.data_ptr(), partial.data_ptr<float>(),
-                    dw.data_ptr<float>(), rows, C, num_sms(), cur_stream());
+    sg::rmsnorm_bwd_n(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), opt_ptr(d_res), dx.data_ptr(), partial.data_ptr<float>(),
+                      dw.data_ptr<float>(), rows, C, blocks, cur_stream());
     return {dx, dw};
 }
 

@@ -115,48 +115,62 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
 // ------------------------------------------------------------------------------------------ RMSNorm backward
 // Persistent CTAs stride over rows; each thread owns fixed columns and keeps dw partial sums in registers.
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ d_res) ; dw_partial[block, C] reduced by a second kernel.
+// ITERS = 8-element vectors per thread (C <= blockDim * 8 * ITERS).  The block size follows C (128 threads up to C = 1024, else
+// 256) so that no thread idles on narrow rows, and the number of CTAs follows the register budget: narrow rows run many small
+// CTAs per SM, which is what hides the two dependent passes (dot product, then dx) of each row.  With ITERS <= 2 the row stays in
+// registers between the passes instead of being read again.
 constexpr int RB_THREADS = 256;
-constexpr int RB_MAX_ITERS = 8;  // supports C <= 256*8*8 = 16384
+template <int ITERS>
 __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                  const float* __restrict__ rstd, const bf16* __restrict__ d_res,
                                                                  bf16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int C) {
+    constexpr bool KEEP = ITERS <= 2;
     __shared__ float sh[32];
-    float dw[RB_MAX_ITERS][8];
+    float dw[ITERS][8];
+    float ww[ITERS][8];
 #pragma unroll
-    for (int it = 0; it < RB_MAX_ITERS; ++it)
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 8;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dw[it][i] = 0.f;
+        for (int i = 0; i < 8; ++i) { dw[it][i] = 0.f; ww[it][i] = 0.f; }
+        if (c < C) load8(w + c, ww[it]);
+    }
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const size_t base = static_cast<size_t>(row) * C;
         const float rs = rstd[row];
         float dot = 0.f;
+        float gk[KEEP ? ITERS : 1][8], ak[KEEP ? ITERS : 1][8];
 #pragma unroll
-        for (int it = 0; it < RB_MAX_ITERS; ++it) {
-            const int c = (it * RB_THREADS + threadIdx.x) * 8;
+        for (int it = 0; it < ITERS; ++it) {
+            const int c = (it * blockDim.x + threadIdx.x) * 8;
             if (c < C) {
-                float g[8], a[8], ww[8];
+                float g[8], a[8];
                 load8(dy + base + c, g);
                 load8(x + base + c, a);
-                load8(w + c, ww);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float xhat = a[i] * rs;
-                    dot += g[i] * ww[i] * xhat;
+                    dot += g[i] * ww[it][i] * xhat;
                     dw[it][i] += g[i] * xhat;
+                    if (KEEP) { gk[it][i] = g[i]; ak[it][i] = a[i]; }
                 }
             }
         }
         dot = block_reduce<false>(dot, sh) / C;
 #pragma unroll
-        for (int it = 0; it < RB_MAX_ITERS; ++it) {
-            const int c = (it * RB_THREADS + threadIdx.x) * 8;
+        for (int it = 0; it < ITERS; ++it) {
+            const int c = (it * blockDim.x + threadIdx.x) * 8;
             if (c < C) {
-                float g[8], a[8], ww[8], o[8];
-                load8(dy + base + c, g);
-                load8(x + base + c, a);
-                load8(w + c, ww);
+                float g[8], a[8], o[8];
+                if (KEEP) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[i] - a[i] * rs * dot);
+                    for (int i = 0; i < 8; ++i) { g[i] = gk[it][i]; a[i] = ak[it][i]; }
+                } else {
+                    load8(dy + base + c, g);
+                    load8(x + base + c, a);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[it][i] - a[i] * rs * dot);
                 if (d_res) {
                     float r[8];
                     load8(d_res + base + c, r);
@@ -168,8 +182,8 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __r
         }
     }
 #pragma unroll
-    for (int it = 0; it < RB_MAX_ITERS; ++it) {
-        const int c = (it * RB_THREADS + threadIdx.x) * 8;
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 8;
         if (c < C) {
             float* o = dw_partial + static_cast<size_t>(blockIdx.x) * C + c;
             *reinterpret_cast<float4*>(o) = make_float4(dw[it][0], dw[it][1], dw[it][2], dw[it][3]);
@@ -177,12 +191,13 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __r
         }
     }
 }
+// out[c] += sum over a slice of the partial rows (gridDim.y slices; ``out`` is zeroed by the launcher)
 __global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int C) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     float s = 0.f;
-    for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * C + c];
-    out[c] = s;
+    for (int b = blockIdx.y; b < nblocks; b += gridDim.y) s += partial[static_cast<size_t>(b) * C + c];
+    atomicAdd(out + c, s);
 }
 
 // ------------------------------------------------------------------------------------------ SwiGLU
@@ -238,6 +253,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
 // ------------------------------------------------------------------------------------------ QK-norm + RoPE
 // One warp per (token, head); head_dim 128: lane l holds elements [4l, 4l+4); rotary partner (i +/- 64) lives in lane l^16.
 // Layout per token: [Hq heads | Hkv heads (K) | Hkv heads (V)] x D.  V heads are copied (forward) / passed through (backward).
+constexpr int ROPE_HEAD_GROUP = 8;
 template <bool BACKWARD>
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restrict__ in, const bf16* __restrict__ qkv_pre, const bf16* __restrict__ qw,
                                                            const bf16* __restrict__ kw, const int* __restrict__ pos, bf16* __restrict__ out,
@@ -257,26 +273,26 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
     const int H = Hq + 2 * Hkv;
     const int lane = threadIdx.x & 31;
     const size_t warps_total = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
-    const size_t items = tokens * H;
+    // One work item = one token x a group of ROPE_HEAD_GROUP heads: the rotation angles depend only on the token and the lane, so
+    // sin / cos are evaluated once per item and reused for every head of the group; the frequencies depend only on the lane and
+    // are computed once per thread.
+    const int groups = (H + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP;
+    const size_t items = tokens * groups;
     const bool use_norm = qw != nullptr;
     float dw_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // this lane's 4 elements: [q|k] norm-weight grads
+    float inv[4];
+    int axis[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = (lane * 4 + i) & 63;
+        inv[i] = exp2f(-log2_theta * (2.f * j) / D);
+        const int m3 = j % 3;
+        axis[i] = (m3 == 1 && j < lim_h) ? 1 : ((m3 == 2 && j < lim_w) ? 2 : 0);
+    }
     for (size_t it = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += warps_total) {
-        const size_t tok = it / H;
-        const int h = static_cast<int>(it % H);
-        const size_t off = it * D + lane * 4;
-        const uint2 raw = *reinterpret_cast<const uint2*>(in + off);
-        if (h >= Hq + Hkv) {  // V: identity
-            *reinterpret_cast<uint2*>(out + off) = raw;
-            continue;
-        }
-        const bool is_q = h < Hq;
-        float v[4];
-        {
-            const bf162* pb = reinterpret_cast<const bf162*>(&raw);
-            const float2 a = __bfloat1622float2(pb[0]), b = __bfloat1622float2(pb[1]);
-            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-        }
-        // rotation angles for this lane's 4 element indices (index mod 64)
+        const size_t tok = it / groups;
+        const int h0 = static_cast<int>(it % groups) * ROPE_HEAD_GROUP;
+        const int h1 = min(H, h0 + ROPE_HEAD_GROUP);
         const float p = static_cast<float>(pos[tok]);
         float p_h = p, p_w = p;
         if (multi_axis) {
@@ -285,71 +301,81 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
         }
         float cs[4], sn[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int j = (lane * 4 + i) & 63;
-            const float inv = exp2f(-log2_theta * (2.f * j) / D);
-            const int m3 = j % 3;
-            const float pj = (m3 == 1 && j < lim_h) ? p_h : ((m3 == 2 && j < lim_w) ? p_w : p);
-            sincosf(pj * inv, &sn[i], &cs[i]);
-        }
-        const float sign = (lane < 16) ? -1.f : 1.f;  // first half: x1*c - x2*s ; second half: x2*c + x1*s
-        if (!BACKWARD) {
-            float rstd = 1.f;
-            if (use_norm) {
-                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-                ss = warp_sum(ss);
-                rstd = rsqrtf(ss / D + eps);
-                const bf16* wv = is_q ? qw : kw;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * __bfloat162float(wv[lane * 4 + i]);
-                if (lane == 0) {
-                    if (is_q) q_rstd[tok * Hq + h] = rstd;
-                    else k_rstd[tok * Hkv + (h - Hq)] = rstd;
+        for (int i = 0; i < 4; ++i) sincosf((axis[i] == 1 ? p_h : (axis[i] == 2 ? p_w : p)) * inv[i], &sn[i], &cs[i]);
+#pragma unroll 2
+        for (int h = h0; h < h1; ++h) {
+            const size_t off = (tok * H + h) * D + lane * 4;
+            const uint2 raw = *reinterpret_cast<const uint2*>(in + off);
+            if (h >= Hq + Hkv) {  // V: identity
+                *reinterpret_cast<uint2*>(out + off) = raw;
+                continue;
+            }
+            const bool is_q = h < Hq;
+            float v[4];
+            {
+                const bf162* pb = reinterpret_cast<const bf162*>(&raw);
+                const float2 a = __bfloat1622float2(pb[0]), b = __bfloat1622float2(pb[1]);
+                v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+            }
+            const float sign = (lane < 16) ? -1.f : 1.f;  // first half: x1*c - x2*s ; second half: x2*c + x1*s
+            if (!BACKWARD) {
+                float rstd = 1.f;
+                if (use_norm) {
+                    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+                    ss = warp_sum(ss);
+                    rstd = rsqrtf(ss / D + eps);
+                    const bf16* wv = is_q ? qw : kw;
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * __bfloat162float(wv[lane * 4 + i]);
+                    if (lane == 0) {
+                        if (is_q) q_rstd[tok * Hq + h] = rstd;
+                        else k_rstd[tok * Hkv + (h - Hq)] = rstd;
+                    }
                 }
-            }
-            float o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                o[i] = v[i] * cs[i] + sign * partner * sn[i];
-            }
-            uint2 w2;
-            bf162* pw = reinterpret_cast<bf162*>(&w2);
-            pw[0] = __floats2bfloat162_rn(o[0], o[1]);
-            pw[1] = __floats2bfloat162_rn(o[2], o[3]);
-            *reinterpret_cast<uint2*>(out + off) = w2;
-        } else {
-            // v = d(out).  Inverse rotation: g1 = d1*c + d2*s ; g2 = d2*c - d1*s
-            float g[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                g[i] = v[i] * cs[i] - sign * partner * sn[i];
-            }
-            if (use_norm) {
-                const uint2 xr = *reinterpret_cast<const uint2*>(qkv_pre + off);
-                const bf162* px = reinterpret_cast<const bf162*>(&xr);
-                const float2 a = __bfloat1622float2(px[0]), b = __bfloat1622float2(px[1]);
-                const float xin[4] = {a.x, a.y, b.x, b.y};
-                const float rstd = is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)];
-                const bf16* wv = is_q ? qw : kw;
-                float dot = 0.f, dn[4], xhat[4];
-#pragma unroll
+                float o[4];
+    #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    xhat[i] = xin[i] * rstd;
-                    dn[i] = g[i] * __bfloat162float(wv[lane * 4 + i]);
-                    dot += dn[i] * xhat[i];
-                    dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
+                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                    o[i] = v[i] * cs[i] + sign * partner * sn[i];
                 }
-                dot = warp_sum(dot) / D;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) g[i] = rstd * (dn[i] - xhat[i] * dot);
+                uint2 w2;
+                bf162* pw = reinterpret_cast<bf162*>(&w2);
+                pw[0] = __floats2bfloat162_rn(o[0], o[1]);
+                pw[1] = __floats2bfloat162_rn(o[2], o[3]);
+                *reinterpret_cast<uint2*>(out + off) = w2;
+            } else {
+                // v = d(out).  Inverse rotation: g1 = d1*c + d2*s ; g2 = d2*c - d1*s
+                float g[4];
+    #pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                    g[i] = v[i] * cs[i] - sign * partner * sn[i];
+                }
+                if (use_norm) {
+                    const uint2 xr = *reinterpret_cast<const uint2*>(qkv_pre + off);
+                    const bf162* px = reinterpret_cast<const bf162*>(&xr);
+                    const float2 a = __bfloat1622float2(px[0]), b = __bfloat1622float2(px[1]);
+                    const float xin[4] = {a.x, a.y, b.x, b.y};
+                    const float rstd = is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)];
+                    const bf16* wv = is_q ? qw : kw;
+                    float dot = 0.f, dn[4], xhat[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        xhat[i] = xin[i] * rstd;
+                        dn[i] = g[i] * __bfloat162float(wv[lane * 4 + i]);
+                        dot += dn[i] * xhat[i];
+                        dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
+                    }
+                    dot = warp_sum(dot) / D;
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) g[i] = rstd * (dn[i] - xhat[i] * dot);
+                }
+                uint2 w2;
+                bf162* pw = reinterpret_cast<bf162*>(&w2);
+                pw[0] = __floats2bfloat162_rn(g[0], g[1]);
+                pw[1] = __floats2bfloat162_rn(g[2], g[3]);
+                *reinterpret_cast<uint2*>(out + off) = w2;
             }
-            uint2 w2;
-            bf162* pw = reinterpret_cast<bf162*>(&w2);
-            pw[0] = __floats2bfloat162_rn(g[0], g[1]);
-            pw[1] = __floats2bfloat162_rn(g[2], g[3]);
-            *reinterpret_cast<uint2*>(out + off) = w2;
         }
     }
     if (BACKWARD && use_norm) {
@@ -729,12 +755,35 @@ void rmsnorm_fwd(const void* x, const void* residual, const void* w, void* res_o
                                                 fp8_scale, amax, C, eps);
 }
 int rmsnorm_bwd_blocks(int rows, int num_sms) { return rows < num_sms * 2 ? rows : num_sms * 2; }
+static int rmsnorm_bwd_threads(int C) { return C <= 1024 ? 128 : RB_THREADS; }
+static int rmsnorm_bwd_iters(int C) {
+    const int per = rmsnorm_bwd_threads(C) * 8;
+    const int n = (C + per - 1) / per;
+    return n <= 1 ? 1 : (n <= 2 ? 2 : (n <= 4 ? 4 : 8));
+}
+// CTAs for a [rows, C] problem: as many per SM as the register budget of the variant allows (see the kernel comment)
+int rmsnorm_bwd_blocks_wide(int rows, int C, int num_sms) {
+    const int per_sm = C <= 1024 ? 8 : 2;
+    return rows < num_sms * per_sm ? rows : num_sms * per_sm;
+}
+void rmsnorm_bwd_n(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
+                   int C, int blocks, cudaStream_t s) {
+    const int threads = rmsnorm_bwd_threads(C);
+#define SG_RB(IT) rmsnorm_bwd_kernel<IT><<<blocks, threads, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)d_res, (bf16*)dx, dw_partial, rows, C)
+    switch (rmsnorm_bwd_iters(C)) {
+        case 1: SG_RB(1); break;
+        case 2: SG_RB(2); break;
+        case 4: SG_RB(4); break;
+        default: SG_RB(8); break;
+    }
+#undef SG_RB
+    cudaMemsetAsync(dw, 0, static_cast<size_t>(C) * sizeof(float), s);
+    const int slices = blocks >= 64 ? 8 : 1;
+    column_sum_kernel<<<dim3((C + 255) / 256, slices), 256, 0, s>>>(dw_partial, dw, blocks, C);
+}
 void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
                  int C, int num_sms, cudaStream_t s) {
-    const int blocks = rmsnorm_bwd_blocks(rows, num_sms);
-    rmsnorm_bwd_kernel<<<blocks, RB_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)d_res, (bf16*)dx, dw_partial,
-                                                     rows, C);
-    column_sum_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_partial, dw, blocks, C);
+    rmsnorm_bwd_n(dy, x, w, rstd, d_res, dx, dw_partial, dw, rows, C, rmsnorm_bwd_blocks(rows, num_sms), s);
 }
 void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s) {
     swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M);
@@ -744,7 +793,7 @@ void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int
 }
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
                       int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s) {
-    const size_t items = tokens * (Hq + 2 * Hkv);
+    const size_t items = tokens * ((Hq + 2 * Hkv + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP);
     qk_norm_rope_kernel<false><<<grid_for(items * 32, 256, num_sms), 256, 0, s>>>((const bf16*)qkv, nullptr, (const bf16*)qw, (const bf16*)kw, pos,
                                                                                    (bf16*)out, q_rstd, k_rstd, nullptr, nullptr, tokens, Hq, Hkv, eps,
                                                                                    log2f(theta), lim_h, lim_w);
@@ -752,7 +801,7 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
 void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,
                       float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms,
                       cudaStream_t s) {
-    const size_t items = tokens * (Hq + 2 * Hkv);
+    const size_t items = tokens * ((Hq + 2 * Hkv + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP);
     qk_norm_rope_kernel<true><<<grid_for(items * 32, 256, num_sms, 4), 256, 0, s>>>((const bf16*)d_out, (const bf16*)qkv_pre, (const bf16*)qw,
                                                                                      (const bf16*)kw, pos, (bf16*)d_qkv, q_rstd, k_rstd, dqw, dkw, tokens,
                                                                                      Hq, Hkv, eps, log2f(theta), lim_h, lim_w);

@@ -9,6 +9,9 @@ namespace sg {
 void rmsnorm_fwd(const void* x, const void* residual, const void* w, void* res_out, void* y, float* rstd, void* y_fp8, const float* fp8_scale,
                  float* amax, int rows, int C, float eps, cudaStream_t s);
 int rmsnorm_bwd_blocks(int rows, int num_sms);
+int rmsnorm_bwd_blocks_wide(int rows, int C, int num_sms);
+void rmsnorm_bwd_n(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
+                   int C, int blocks, cudaStream_t s);
 void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
                  int C, int num_sms, cudaStream_t s);
 void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s);
