@@ -280,8 +280,15 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
     const size_t items = tokens * groups;
     const bool use_norm = qw != nullptr;
     float dw_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // this lane's 4 elements: [q|k] norm-weight grads
-    float inv[4];
+    float inv[4], wq4[4] = {1.f, 1.f, 1.f, 1.f}, wk4[4] = {1.f, 1.f, 1.f, 1.f};
     int axis[4];
+    if (use_norm) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            wq4[i] = __bfloat162float(qw[lane * 4 + i]);
+            wk4[i] = __bfloat162float(kw[lane * 4 + i]);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int j = (lane * 4 + i) & 63;
@@ -302,10 +309,23 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
         float cs[4], sn[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) sincosf((axis[i] == 1 ? p_h : (axis[i] == 2 ? p_w : p)) * inv[i], &sn[i], &cs[i]);
-#pragma unroll 2
-        for (int h = h0; h < h1; ++h) {
+        // all loads of the group are issued before any of them is used
+        uint2 raws[ROPE_HEAD_GROUP], pres[ROPE_HEAD_GROUP];
+#pragma unroll
+        for (int u = 0; u < ROPE_HEAD_GROUP; ++u) {
+            const int h = h0 + u;
+            if (h < h1) {
+                const size_t off = (tok * H + h) * D + lane * 4;
+                raws[u] = *reinterpret_cast<const uint2*>(in + off);
+                if (BACKWARD && use_norm && h < Hq + Hkv) pres[u] = *reinterpret_cast<const uint2*>(qkv_pre + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < ROPE_HEAD_GROUP; ++u) {
+            const int h = h0 + u;
+            if (h >= h1) break;
             const size_t off = (tok * H + h) * D + lane * 4;
-            const uint2 raw = *reinterpret_cast<const uint2*>(in + off);
+            const uint2 raw = raws[u];
             if (h >= Hq + Hkv) {  // V: identity
                 *reinterpret_cast<uint2*>(out + off) = raw;
                 continue;
@@ -324,9 +344,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
                     float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
                     ss = warp_sum(ss);
                     rstd = rsqrtf(ss / D + eps);
-                    const bf16* wv = is_q ? qw : kw;
     #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * __bfloat162float(wv[lane * 4 + i]);
+                    for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * (is_q ? wq4[i] : wk4[i]);
                     if (lane == 0) {
                         if (is_q) q_rstd[tok * Hq + h] = rstd;
                         else k_rstd[tok * Hkv + (h - Hq)] = rstd;
@@ -352,17 +371,16 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
                     g[i] = v[i] * cs[i] - sign * partner * sn[i];
                 }
                 if (use_norm) {
-                    const uint2 xr = *reinterpret_cast<const uint2*>(qkv_pre + off);
+                    const uint2 xr = pres[u];
                     const bf162* px = reinterpret_cast<const bf162*>(&xr);
                     const float2 a = __bfloat1622float2(px[0]), b = __bfloat1622float2(px[1]);
                     const float xin[4] = {a.x, a.y, b.x, b.y};
                     const float rstd = is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)];
-                    const bf16* wv = is_q ? qw : kw;
                     float dot = 0.f, dn[4], xhat[4];
     #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         xhat[i] = xin[i] * rstd;
-                        dn[i] = g[i] * __bfloat162float(wv[lane * 4 + i]);
+                        dn[i] = g[i] * (is_q ? wq4[i] : wk4[i]);
                         dot += dn[i] * xhat[i];
                         dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
                     }
