@@ -357,14 +357,14 @@ class Trainer:
         inside the captured region (the peer-memory kernels pass a barrier epoch as a kernel argument; so one GPU, or replicated
         weights with the gradient reductions issued after the replay), dense model, no streamed weights or optimizer
         state, no per-batch side inputs, a recipe without step-dependent seeds, and scaling history already present (the
-        first two steps run eagerly: they also serve as the warm-up that graph capture requires)."""
+        first two steps of this process run eagerly, also after a resume: they are the warm-up that graph capture requires)."""
         c = self.cfg
         multi_ok = self.world == 1 or c.zero_level <= 1  # replicated weights: the gradient reductions run after the replay, outside the graph
         return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and multi_ok and self.lora is None
                     and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora or c.offload_saved_tensors or c.lmhead_drop_ignored_rows or c.time_breakdown)
                     and c.sequence_chunks <= 1
                     and doc_ids is None and row_weights is None and kd is None and self._visual is None and not getattr(self.model, "num_experts", 0)
-                    and type(self.recipe).__name__ in ("BF16Recipe", "Recipe", "FP8HybridRecipe") and self.step_index >= 2)
+                    and type(self.recipe).__name__ in ("BF16Recipe", "Recipe", "FP8HybridRecipe") and getattr(self, "_steps_here", 0) >= 2)
 
     def _graphed_forward_backward(self, inp, pos, tgt, loss_scale, aux_scale, index: int, total: int):
         """One micro-batch through a captured graph.  Inputs are copied into static buffers; there is one graph per
@@ -478,6 +478,7 @@ class Trainer:
         """``norm``: the global gradient norm when this process holds only part of the model (pipeline stages)."""
         cfg = self.opt_cfg
         self.step_index += 1
+        self._steps_here = getattr(self, "_steps_here", 0) + 1
         t = self.step_index
         lr = cfg.learning_rate if lr is None else lr
         norm = self.grad_norm() if norm is None else norm
