@@ -1,4 +1,4 @@
-"""``surogate debug {weights,registry,activations,gradients,diff}``.  Parity: surogate/cli/debug.py."""
+"""``surogate debug {weights,registry,activations,gradients,diff,determinism,sanitize}``.  Parity: surogate/cli/debug.py."""
 from __future__ import annotations
 
 import argparse
@@ -10,7 +10,8 @@ import numpy as np
 def main(argv, command: str = "debug") -> int:
     p = argparse.ArgumentParser(prog="surogate debug")
     sub = p.add_subparsers(dest="what", required=True)
-    for name in ("weights", "registry", "activations", "gradients", "diff"):
+    sub.add_parser("sanitize", help="run the C++ host runtime under AddressSanitizer + UBSan")
+    for name in ("weights", "registry", "activations", "gradients", "diff", "determinism"):
         s = sub.add_parser(name)
         s.add_argument("model", nargs="?" if name == "registry" else None, help="model directory (or architecture name for `registry`)")
         s.add_argument("--out", default=None, help="JSONL report path")
@@ -18,6 +19,10 @@ def main(argv, command: str = "debug") -> int:
         s.add_argument("--batch", type=int, default=1)
         s.add_argument("--seed", type=int, default=0)
     a = p.parse_args(argv)
+    if a.what == "sanitize":
+        from ..debug.sanitize import run
+
+        return run([])
     from ..debug import tools
 
     if a.what == "weights":
@@ -35,6 +40,16 @@ def main(argv, command: str = "debug") -> int:
     cfg = load_hf_config(a.model)
     rng = np.random.default_rng(a.seed)
     tok = rng.integers(0, cfg.get("vocab_size", 1000), (a.batch, a.seq_len + 1)).astype(np.int32)
+    if a.what == "determinism":
+        dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+
+        def make():
+            tr = Trainer(TrainerConfig(model=cfg, batch_size=a.batch, seq_len=a.seq_len, zero_level=0), device=dev)
+            tr.import_weights(a.model)
+            return tr
+
+        print(json.dumps(tools.determinism_report(make, tok[:, :-1], tok[:, 1:], out=a.out), indent=1))
+        return 0
     if a.what == "diff":
         rows = tools.diff_against_transformers(a.model, tok[:, :-1], "cuda" if torch.cuda.is_available() else "cpu", a.out)
     else:

@@ -142,3 +142,31 @@ def diff_against_transformers(model_dir: str, tokens: np.ndarray, device: str = 
     rows.append({"logits": True, "max_abs_diff": float((logits - ref.logits.float()).abs().max()),
                  "rel": float((logits - ref.logits.float()).norm() / (ref.logits.float().norm() + 1e-12))})
     return write_jsonl(out, rows)
+
+
+def determinism_report(make_trainer, inputs: np.ndarray, targets: np.ndarray, steps: int = 2, out: Optional[str] = None) -> Dict[str, Any]:
+    """Run the same ``steps`` optimizer steps twice from the same seed and compare, step by step, the loss, the gradient norm
+    and (after the last step's forward + backward) every parameter gradient.  On the PyTorch backend the two runs are identical
+    bit for bit.  The CUDA kernels accumulate a few gradients with atomics (embedding rows, norm weights), so small differences
+    there are expected; a large relative difference in any other tensor points at a race or at uninitialised memory.
+    ``make_trainer()`` must return a freshly initialised trainer each time.
+    Parity: the reference's deterministic-replay self-checks (SUROGATE_CHECK_REPLAY_SCOPE and friends)."""
+    runs = []
+    for _ in range(2):
+        tr = make_trainer()
+        hist = [tr.step(inputs, targets) for _ in range(max(0, steps - 1))]
+        r = tr.forward_backward(inputs, targets)
+        hist.append({"loss": float(r["loss_sum"] / r["n_valid"].clamp_min(1.0) if torch.is_tensor(r["n_valid"]) else r["loss_sum"] / max(1.0, r["n_valid"])),
+                     "norm": float(tr.grad_norm())})
+        runs.append((hist, {k: v.detach().float().cpu().clone() for k, v in tr.get_gradients().items()}))
+    (ha, ga), (hb, gb) = runs
+    rows = []
+    for name in ga:
+        den = float(ga[name].norm()) + 1e-30
+        rows.append({"param": name, "max_abs_diff": float((ga[name] - gb[name]).abs().max()), "rel_diff": float((ga[name] - gb[name]).norm()) / den,
+                     "bitwise_equal": bool(torch.equal(ga[name], gb[name]))})
+    rows.sort(key=lambda r: -r["rel_diff"])
+    write_jsonl(out, rows)
+    return {"steps": [{"loss_a": a["loss"], "loss_b": b["loss"], "norm_a": a["norm"], "norm_b": b["norm"]} for a, b in zip(ha, hb)],
+            "bitwise_equal": all(r["bitwise_equal"] for r in rows) and all(a["loss"] == b["loss"] for a, b in zip(ha, hb)),
+            "worst": rows[:5], "n_params": len(rows)}

@@ -238,3 +238,32 @@ def test_object_store_datasets_are_fetched_through_fsspec(tmp_path, monkeypatch)
         raise AssertionError("expected an error for an unknown protocol")
     except RuntimeError as e:
         assert "fsspec backend" in str(e)
+
+
+def test_determinism_report_and_sanitized_host_runtime():
+    """Two runs from the same seed agree bit for bit on the PyTorch backend; the host runtime's built-in workload is clean under
+    AddressSanitizer + UBSan (skipped where gcc has no sanitizer runtime)."""
+    import subprocess
+    import sys
+
+    from surogate_b200.debug import sanitize, tools
+
+    def make():
+        tr = Trainer(TrainerConfig(model=dict(MODEL), batch_size=1, seq_len=16, zero_level=0), device=torch.device("cpu"))
+        tr.init_weights(seed=0)
+        return tr
+
+    tok = np.random.default_rng(0).integers(0, 600, (1, 17)).astype(np.int32)
+    rep = tools.determinism_report(make, tok[:, :-1], tok[:, 1:], steps=2)
+    assert rep["bitwise_equal"] and rep["n_params"] > 5 and rep["steps"][0]["loss_a"] == rep["steps"][0]["loss_b"]
+    rt = sanitize.sanitizer_runtime()
+    if rt is None:
+        return
+    from surogate_b200.ops import _build
+
+    so = _build.build_host_sanitized()
+    env = dict(os.environ, LD_PRELOAD=rt, SUROGATE_HOST_SO=so, ASAN_OPTIONS="detect_leaks=0:halt_on_error=1", UBSAN_OPTIONS="halt_on_error=1", OMP_NUM_THREADS="2")
+    p = subprocess.run([sys.executable, "-c", "from surogate_b200.debug.sanitize import builtin_workload; builtin_workload()"], env=env, capture_output=True,
+                       text=True, timeout=600, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert p.returncode == 0 and "host workload ok" in p.stdout, p.stderr[-3000:]
+    assert "ERROR: AddressSanitizer" not in p.stderr and "runtime error" not in p.stderr
