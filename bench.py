@@ -174,7 +174,7 @@ def main():
                         offload_optimizer=bool(spec.get("offload")) and not args.no_offload, keep_gathered=not spec.get("offload"),
                         ep_capacity_factor=float(max(1, ep)),  # room for every routed row even if all tokens pick one rank: nothing is dropped
                         resident_layers=args.resident_layers, use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
-                        ep_plan_refresh_interval=2)            # least-loaded placement settles during warm-up; later refreshes are inside the timed region
+                        ep_plan_refresh_interval=4)            # counts are summed over 4 steps per decision; refreshes after warm-up are inside the timed region
     if spec.get("recompute"):
         cfg.recompute = True
     tr = Trainer(cfg, device=dev, comm=comm)

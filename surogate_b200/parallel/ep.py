@@ -49,6 +49,35 @@ class PrePlan:
         self.ep_plan = None
 
 
+def decide_placement(placed_counts, cur, ep: int, threshold: float = 1.3, tolerance: float = 0.05, min_gain: float = 0.25, max_moved_fraction: float = 0.5):
+    """New placement of one layer's experts, or the current one when moving is not worth it.
+
+    ``placed_counts[i]`` is the number of routed rows of the expert held at placed index i (rank * El + slot); ``cur[e]`` is the
+    placed index of global expert e.  Nothing moves when the busiest rank is within ``threshold`` of the mean, when the planner's
+    proposal removes less than the fraction ``min_gain`` of the excess over a perfect balance, or when it would move more than ``max_moved_fraction`` of the
+    experts at once (a sign that the counts are noise, not a stable skew).  Returns (placement, number of experts moved)."""
+    from ..ops import host
+
+    E = len(cur)
+    El = E // ep
+    counts = [placed_counts[cur[e]] for e in range(E)]  # per global expert
+
+    def imbalance(place):
+        per_rank = [0] * ep
+        for e, c in enumerate(counts):
+            per_rank[place[e] // El] += c
+        return max(per_rank) / max(1.0, sum(per_rank) / ep)
+
+    before = imbalance(cur)
+    if before <= threshold:
+        return list(cur), 0
+    new, moved = host().balanced_placement(counts, ep, list(cur), tolerance)
+    new = list(new)
+    if moved == 0 or moved > max(1, int(max_moved_fraction * E)) or before - imbalance(new) < min_gain * (before - 1.0):
+        return list(cur), 0
+    return new, int(moved)
+
+
 class ExpertParallel:
     def __init__(self, comm, ep_size: int, device, capacity_factor: float = 1.5):
         if not hasattr(comm, "create_arena"):
@@ -62,6 +91,7 @@ class ExpertParallel:
         self.bufs: Optional[Dict[str, Any]] = None
         self.epoch = 0
         self.last_global_counts: Dict[int, torch.Tensor] = {}
+        self.count_window: Dict[int, torch.Tensor] = {}
         self.last_overflow: Dict[int, torch.Tensor] = {}  # rows per layer that exceeded this rank's receive capacity (dropped)
         # Least-loaded placement: placement[layer][e] = rank * El + slot that currently holds global expert e (identity at start).
         self.placement: Dict[int, torch.Tensor] = {}
@@ -115,7 +145,13 @@ class ExpertParallel:
         xp = torch.empty_like(b["recv_x"])  # rows beyond the used range stay uninitialised: nothing downstream reads them into a result
         self.ext.copy_rows_upto(b["recv_x"], xp, offsets[El:El + 1])
         if ctx.layer is not None and ctx.phase == "fwd":
-            self.last_global_counts[ctx.layer] = b["counts"].view(self.ep, E).sum(0)
+            gc = b["counts"].view(self.ep, E).sum(0)
+            self.last_global_counts[ctx.layer] = gc
+            acc = self.count_window.get(ctx.layer)  # counts summed since the last placement refresh: what re-placement decides on
+            if acc is None:
+                self.count_window[ctx.layer] = gc.to(torch.int64).clone()
+            else:
+                acc.add_(gc)
             self.last_overflow[ctx.layer] = offsets[El + 1:El + 2]
         plan = EpPlan(offsets[:El + 1], row_map, cap, N, K, pre.x_shape, pre.topk_idx)
         plan.layout = offsets
@@ -168,7 +204,8 @@ class ExpertParallel:
         return placed.contiguous(), c
 
     def rebalance(self, store, optimizer, threshold: float = 1.3, tolerance: float = 0.05) -> Dict[str, Any]:
-        """Re-place experts so that every rank sees about the same number of routed rows (from the last step's counts).
+        """Re-place experts so that every rank sees about the same number of routed rows (from the counts summed over the steps
+        since the last refresh, which smooths the step-to-step noise of the router).
 
         Ownership itself moves: the expert's master weights, work weights and optimizer moments travel to the new owner
         (point-to-point over NCCL, once per refresh), so later steps need no per-step weight shipping or gradient return.
@@ -177,25 +214,17 @@ class ExpertParallel:
 
         from ..ops import host
 
-        if not self.last_global_counts:
+        if not self.count_window:
             return {"layers": 0, "moved": 0}
-        layers = sorted(self.last_global_counts)
-        counts_all = torch.stack([self.last_global_counts[L].to(torch.int64) for L in layers]).cpu()  # the one host sync of a refresh
-        h = host()
+        layers = sorted(self.count_window)
+        counts_all = torch.stack([self.count_window[L] for L in layers]).cpu()  # the one host sync of a refresh
         E = counts_all.shape[1]
         El = E // self.ep
         changed, moved_total = 0, 0
         for li, L in enumerate(layers):
             cur = self.placement_host.get(L) or list(range(E))
-            placed_counts = counts_all[li].tolist()           # the kernels count in placed order
-            counts = [placed_counts[cur[e]] for e in range(E)]  # -> per global expert
-            per_rank = [0] * self.ep
-            for e, c in enumerate(counts):
-                per_rank[cur[e] // El] += c
-            mean = max(1.0, sum(per_rank) / self.ep)
-            if max(per_rank) / mean <= threshold:
-                continue
-            new, moved = h.balanced_placement(counts, self.ep, cur, tolerance)
+            new, moved = decide_placement(counts_all[li].tolist(), cur, self.ep, threshold, tolerance)
+            self.count_window[L].zero_()  # a new window starts (and counts are kept in placed order, which may change now)
             if moved == 0:
                 continue
             self._move_experts(store, optimizer, L, cur, list(new), El, dist)

@@ -179,3 +179,16 @@ def test_crash_handler_and_telemetry_are_safe_without_gpu():
     h.install_crash_handler("test")
     info = h.query_gpu(0)
     assert "ok" in info and (info["ok"] or info["error"])
+
+
+def test_expert_replacement_moves_only_when_it_pays():
+    """Placement decisions: a stable skew is corrected, balanced or noisy counts and hot single experts leave the placement alone."""
+    from surogate_b200.parallel.ep import decide_placement
+
+    cur = list(range(8))
+    new, moved = decide_placement([100, 100, 100, 100, 10, 10, 10, 10], cur, 2)
+    per_rank = [sum(c for e, c in enumerate([100, 100, 100, 100, 10, 10, 10, 10]) if new[e] // 4 == r) for r in range(2)]
+    assert moved > 0 and sorted(new) == cur and max(per_rank) <= 1.1 * (sum(per_rank) / 2)
+    assert decide_placement([100, 90, 110, 100, 95, 105, 100, 100], cur, 2) == (cur, 0)   # within the threshold
+    assert decide_placement([400, 0, 0, 0, 100, 100, 100, 100], cur, 2) == (cur, 0)       # one hot expert: no placement helps
+    assert decide_placement([100, 100, 100, 100, 10, 10, 10, 10], cur, 2, max_moved_fraction=0.1) == (cur, 0)  # too many moves at once
