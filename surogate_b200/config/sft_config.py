@@ -175,6 +175,9 @@ class SFTConfig:
     ep_size: int = 1
     ep_load_balance_threshold: float = 1.3
     ep_plan_refresh_interval: int = 16
+    async_optimizer: Optional[str] = None                   # with cpu_training: overlap | inline (host update one step behind, overlapped with compute)
+    trainable_param_substrings: Optional[List[str]] = None  # full fine-tuning of a subset: names containing one of these train
+    gradient_mask_mode: Optional[str] = None                # allow_substrings | mlp_growth_new_half
     parallelism: str = "ddp"  # ddp | dispatch_pp
     dispatch_pp: Dict[str, Any] = field(default_factory=dict)
     distributed: Optional[DistributedConfig] = None
@@ -309,6 +312,7 @@ class SFTConfig:
             master_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.master_dtype or "", None),
             lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, ep_load_balance_threshold=self.ep_load_balance_threshold,
             ep_plan_refresh_interval=self.ep_plan_refresh_interval, lora=self.lora_dict(),
+            async_optimizer=self.async_optimizer, trainable_param_substrings=self.trainable_param_substrings, gradient_mask_mode=self.gradient_mask_mode,
             fp8_amax_history=self.fp8_amax_history, skip_quant_first_layers=self.skip_quant_first_layers,
             skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer and not self.cpu_training,
             offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training, long_context=self.long_context, sequence_chunks=self.sequence_chunks, use_cuda_graphs=self.use_cuda_graphs, lmhead_drop_ignored_rows=self.lmhead_drop_ignored_rows, time_breakdown=self.debug_time_breakdown, resident_layers=self.resident_layers,

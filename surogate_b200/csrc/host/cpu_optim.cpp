@@ -60,3 +60,119 @@ double cpu_sum_squares(const void* x, bool is_bf16, int64_t n) {
 }
 
 }  // namespace sg
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// One-step-stale optimizer worker: a dedicated thread drains a depth-1 queue of AdamW updates so that the host update of step N
+// overlaps the device compute of step N+1.  submit() first waits for the previous update, so at most one is in flight and the
+// weights a step reads are never more than one update old.  A failure inside the worker is kept and re-thrown by the next
+// submit() / drain().  Reference counterpart: csrc/src/runtime/optimizers/async_optimizer.{h,cpp}.
+#include <condition_variable>
+#include <exception>
+#include <mutex>
+#include <stdexcept>
+#include <thread>
+
+namespace sg {
+
+struct AsyncAdamW::Impl {
+    bool overlap;
+    std::thread worker;
+    std::mutex mu;
+    std::condition_variable work_cv, done_cv;
+    bool has_job = false, stop = false;
+    std::vector<AdamJob> jobs;
+    AdamHyper hyper{};
+    long submitted = 0, completed = 0;
+    std::exception_ptr error;
+
+    static void run(const std::vector<AdamJob>& jobs, const AdamHyper& h) {
+        for (const AdamJob& j : jobs) {
+            if (!j.param || !j.m || !j.v || !j.grad || j.n < 0) throw std::invalid_argument("async AdamW: null buffer or negative size in a job");
+            cpu_adamw_step(j.param, j.m, j.v, j.grad, j.grad_is_bf16, j.work_bf16, j.n, h.lr, h.beta1, h.beta2, h.eps, h.weight_decay, h.grad_scale, h.step,
+                           j.decay_mask);
+            if (j.work_f32) std::memcpy(j.work_f32, j.param, static_cast<size_t>(j.n) * sizeof(float));
+        }
+    }
+
+    void loop() {
+        std::unique_lock<std::mutex> lock(mu);
+        for (;;) {
+            work_cv.wait(lock, [&] { return has_job || stop; });
+            if (!has_job && stop) return;
+            std::vector<AdamJob> mine;
+            mine.swap(jobs);
+            AdamHyper h = hyper;
+            has_job = false;
+            lock.unlock();
+            std::exception_ptr err;
+            try {
+                run(mine, h);
+            } catch (...) {
+                err = std::current_exception();
+            }
+            lock.lock();
+            if (err && !error) error = err;
+            ++completed;
+            done_cv.notify_all();
+        }
+    }
+
+    void rethrow_locked() {
+        if (error) {
+            std::exception_ptr e = error;
+            error = nullptr;
+            std::rethrow_exception(e);
+        }
+    }
+};
+
+AsyncAdamW::AsyncAdamW(bool overlap) : impl_(new Impl) {
+    impl_->overlap = overlap;
+    if (overlap) impl_->worker = std::thread([this] { impl_->loop(); });
+}
+
+AsyncAdamW::~AsyncAdamW() {
+    if (impl_->overlap) {
+        {
+            std::lock_guard<std::mutex> lock(impl_->mu);
+            impl_->stop = true;
+        }
+        impl_->work_cv.notify_all();
+        if (impl_->worker.joinable()) impl_->worker.join();
+    }
+    delete impl_;
+}
+
+void AsyncAdamW::submit(std::vector<AdamJob> jobs, const AdamHyper& hyper) {
+    if (!impl_->overlap) {
+        Impl::run(jobs, hyper);
+        ++impl_->submitted;
+        ++impl_->completed;
+        return;
+    }
+    std::unique_lock<std::mutex> lock(impl_->mu);
+    impl_->done_cv.wait(lock, [&] { return impl_->completed == impl_->submitted; });  // the previous update is done: depth 1
+    impl_->rethrow_locked();
+    impl_->jobs = std::move(jobs);
+    impl_->hyper = hyper;
+    impl_->has_job = true;
+    ++impl_->submitted;
+    lock.unlock();
+    impl_->work_cv.notify_one();
+}
+
+void AsyncAdamW::drain() {
+    if (!impl_->overlap) return;
+    std::unique_lock<std::mutex> lock(impl_->mu);
+    impl_->done_cv.wait(lock, [&] { return impl_->completed == impl_->submitted; });
+    impl_->rethrow_locked();
+}
+
+long AsyncAdamW::completed() const {
+    std::lock_guard<std::mutex> lock(impl_->mu);
+    return impl_->completed;
+}
+
+bool AsyncAdamW::overlap() const { return impl_->overlap; }
+
+}  // namespace sg

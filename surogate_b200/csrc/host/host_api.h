@@ -11,6 +11,34 @@ namespace sg {
 void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool grad_is_bf16, uint16_t* work_bf16, int64_t n, float lr, float beta1,
                     float beta2, float eps, float weight_decay, float grad_scale, int64_t step, const uint8_t* decay_mask = nullptr);
 double cpu_sum_squares(const void* x, bool is_bf16, int64_t n);
+struct AdamJob {   // one flat buffer of an update; ``work_bf16`` / ``work_f32``: optional copy of the new values in the streaming dtype
+    float *param, *m, *v;
+    const void* grad;
+    bool grad_is_bf16;
+    uint16_t* work_bf16;
+    float* work_f32;
+    int64_t n;
+    const uint8_t* decay_mask;
+};
+struct AdamHyper {
+    float lr, beta1, beta2, eps, weight_decay, grad_scale;
+    int64_t step;
+};
+class AsyncAdamW {   // depth-1 queue + worker thread (overlap) or inline execution (overlap = false)
+public:
+    explicit AsyncAdamW(bool overlap);
+    ~AsyncAdamW();
+    AsyncAdamW(const AsyncAdamW&) = delete;
+    AsyncAdamW& operator=(const AsyncAdamW&) = delete;
+    void submit(std::vector<AdamJob> jobs, const AdamHyper& hyper);
+    void drain();
+    long completed() const;
+    bool overlap() const;
+
+private:
+    struct Impl;
+    Impl* impl_;
+};
 
 // lpt_planner.cpp
 struct ExpertChunk {

@@ -96,6 +96,28 @@ PYBIND11_MODULE(sg_b200_host, m) {
                              static_cast<uint16_t*>(ptr(work)), n, lr, b1, b2, eps, wd, grad_scale, step, static_cast<const uint8_t*>(ptr(mask)));
           }, py::arg("param"), py::arg("m"), py::arg("v"), py::arg("grad"), py::arg("grad_is_bf16"), py::arg("work_bf16"), py::arg("n"), py::arg("lr"),
           py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"), py::arg("decay_mask") = 0);
+    py::class_<AsyncAdamW>(m, "AsyncAdamW")
+        .def(py::init<bool>(), py::arg("overlap") = true)
+        .def("submit", [](AsyncAdamW& w, const std::vector<std::tuple<uintptr_t, uintptr_t, uintptr_t, uintptr_t, bool, uintptr_t, bool, int64_t, uintptr_t>>& jobs,
+                          float lr, float b1, float b2, float eps, float wd, float grad_scale, int64_t step) {
+                 // job = (param, m, v, grad, grad_is_bf16, work, work_is_bf16, n, decay_mask); the buffers must stay alive and untouched until drain()
+                 std::vector<AdamJob> v;
+                 for (auto& j : jobs) {
+                     void* work = ptr(std::get<5>(j));
+                     const bool wb = std::get<6>(j);
+                     v.push_back({static_cast<float*>(ptr(std::get<0>(j))), static_cast<float*>(ptr(std::get<1>(j))), static_cast<float*>(ptr(std::get<2>(j))),
+                                  ptr(std::get<3>(j)), std::get<4>(j), wb ? static_cast<uint16_t*>(work) : nullptr, wb ? nullptr : static_cast<float*>(work),
+                                  std::get<7>(j), static_cast<const uint8_t*>(ptr(std::get<8>(j)))});
+                 }
+                 py::gil_scoped_release rel;
+                 w.submit(std::move(v), AdamHyper{lr, b1, b2, eps, wd, grad_scale, step});
+             }, py::arg("jobs"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"))
+        .def("drain", [](AsyncAdamW& w) {
+            py::gil_scoped_release rel;
+            w.drain();
+        })
+        .def("completed", &AsyncAdamW::completed)
+        .def_property_readonly("overlap", &AsyncAdamW::overlap);
     m.def("cpu_sum_squares", [](uintptr_t x, bool bf16, int64_t n) {
         py::gil_scoped_release rel;
         return cpu_sum_squares(ptr(x), bf16, n);

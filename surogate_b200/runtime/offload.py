@@ -98,10 +98,19 @@ class CpuAdamW:
     """fp32 AdamW on host-resident masters (native OpenMP kernel; PyTorch CPU ops when the host runtime is not built)."""
     state_bytes_per_param = 8
 
-    def __init__(self, cfg, store):
+    def __init__(self, cfg, store, stale: Optional[str] = None):
+        """``stale``: None = the update runs inside ``step_all``; "overlap" = the update of step N runs on a native worker thread
+        while step N+1 computes with the weights of update N-1 (one-step stale; csrc/src/runtime/optimizers/async_optimizer.h);
+        "inline" = the same staleness and bookkeeping (double-buffered gradients and work copies) with the update run in place
+        instead of on the worker: the overlapped run must reproduce its trajectory bit for bit (the determinism check)."""
         self.cfg, self.store = cfg, store
         self.state: Dict[str, Dict[str, torch.Tensor]] = {}
         self.grad_host: Dict[str, torch.Tensor] = {}
+        self.stale = stale
+        self.worker = None
+        self._pending: list = []          # buckets whose ``work_next`` holds the weights of the update in flight
+        self._grad_sets = ({}, {})        # the worker reads one set while the next backward fills the other
+        self._parity = 0
         self.d2h_stream = torch.cuda.Stream(device=store.device) if store.device.type == "cuda" else None
         self.bytes_out = 0
         try:
@@ -128,14 +137,64 @@ class CpuAdamW:
         if g.device.type == "cpu":
             self.grad_host[b.name] = g
             return
-        h = self.grad_host.get(b.name)
+        pool = self._grad_sets[self._parity] if self.stale else self.grad_host
+        h = pool.get(b.name)
         if h is None or h.shape != g.shape or h.dtype != g.dtype:
-            h = self.grad_host[b.name] = torch.empty(g.shape, dtype=g.dtype, pin_memory=True)
+            h = pool[b.name] = torch.empty(g.shape, dtype=g.dtype, pin_memory=True)
+        self.grad_host[b.name] = h
         self.d2h_stream.wait_stream(torch.cuda.current_stream(self.store.device))
         with torch.cuda.stream(self.d2h_stream):
             h.copy_(g, non_blocking=True)
             g.record_stream(self.d2h_stream)
         self.bytes_out += g.numel() * g.element_size()
+
+    # ------------------------------------------------------------------ one-step-stale updates
+    def flush(self) -> None:
+        """Wait for the update in flight and publish its weights (swap the work copies).  Called before the next update is
+        queued and before anything reads masters or optimizer state (checkpoint, export, evaluation)."""
+        if self.worker is not None:
+            self.worker.drain()
+        for b in self._pending:
+            b.work_host, b.work_next = b.work_next, b.work_host
+        self._pending = []
+
+    def _submit_stale(self, buckets, lr: float, clip: float, step: int) -> None:
+        if self.host is None:
+            raise RuntimeError("the one-step-stale optimizer needs the native host runtime (surogate_b200.ops.build_host)")
+        if self.worker is None:
+            self.worker = self.host.AsyncAdamW(self.stale == "overlap")
+        self.flush()
+        c = self.cfg
+        jobs, keep = [], []
+        for b in buckets:
+            g = self.grad_host.get(b.name)
+            if g is None:
+                continue
+            if g.device.type != "cpu" or not g.is_contiguous():
+                raise RuntimeError("stale updates read gradients from host memory")
+            if g.data_ptr() == getattr(b.grad_shard, "data_ptr", lambda: 0)():  # CPU device: the gradient buffer itself is overwritten by the next backward
+                h = self._grad_sets[self._parity].get(b.name)
+                if h is None or h.shape != g.shape or h.dtype != g.dtype:
+                    h = self._grad_sets[self._parity][b.name] = torch.empty_like(g)
+                h.copy_(g)
+                g = h
+            st = self._state(b)
+            assert b.master.dtype == torch.float32 and b.master.device.type == "cpu", "the CPU optimizer needs fp32 host masters"
+            assert b.work_next is not None and b.work_host is not None, "stale updates need the double-buffered host work copy"
+            mask = getattr(b, "decay_mask_host", None)
+            if mask is None:
+                mask = b.decay_mask_host = self.store.decay_mask(b).to("cpu").contiguous()
+            if g.dtype not in (torch.float32, torch.bfloat16) or b.work_next.dtype not in (torch.float32, torch.bfloat16):
+                raise RuntimeError(f"stale updates support fp32 / bf16 gradients and weights, got {g.dtype} / {b.work_next.dtype}")
+            keep.append(g)
+            jobs.append((b.master.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(), g.data_ptr(), g.dtype == torch.bfloat16, b.work_next.data_ptr(),
+                         b.work_next.dtype == torch.bfloat16, b.master.numel(), mask.data_ptr()))
+            self._pending.append(b)
+            b.work_host_fresh = True  # the published copy stays what steps read; nothing may copy from the masters while they are being written
+        self._keep = keep  # the gradient buffers stay alive until the worker is done with them
+        self.worker.submit(jobs, lr, c.beta1, c.beta2, c.eps, c.weight_decay, clip, step)
+        self.grad_host.clear()
+        self._parity ^= 1
 
     def step_all(self, buckets, lr: float, clip: float, step: int) -> None:
         for b in buckets:
@@ -144,6 +203,9 @@ class CpuAdamW:
         if self.d2h_stream is not None:
             self.d2h_stream.synchronize()
         c = self.cfg
+        if self.stale:
+            self._submit_stale(buckets, lr, clip, step)
+            return
         for b in buckets:
             g = self.grad_host.get(b.name)
             if g is None:

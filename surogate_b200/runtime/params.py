@@ -113,7 +113,7 @@ class ParamStore:
     def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
                  comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
                  expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False,
-                 owned: Optional[Callable[[Any], bool]] = None, resident_layers: int = 0):
+                 owned: Optional[Callable[[Any], bool]] = None, resident_layers: int = 0, grad_mask=None):
         self.cm = cm
         # with host-resident masters: the frozen weights of the first ``resident_layers`` layers stay in device memory instead,
         # so their per-traversal gather is NVLink / local traffic rather than PCIe (spend spare HBM on the layers used first)
@@ -130,12 +130,14 @@ class ParamStore:
         self.zero_level = zero_level if self.world > 1 else 0
         self.keep_gathered = keep_gathered
         self.frozen = frozen or (lambda name: False)
+        self.grad_mask = grad_mask  # runtime.grad_mask.GradientMask: partial-update runs of a full model
         self.ep = max(1, int(expert_parallel))
         # Host residency: master shards live in pinned host memory and are streamed to the device per layer (H2D copy on a
         # side stream, then the usual gather).  ``host_work_copy`` keeps an extra pinned copy in the parameter dtype next to
         # masters of another dtype (fp32 masters updated by the CPU optimizer, bf16 copy streamed to the GPU).
         self.offload_master = bool(offload_master)
         self.host_work_copy = bool(host_work_copy) and self.offload_master
+        self.host_work_double = host_work_copy == "double" and self.offload_master  # two copies: one being read, one being written by a stale update
         self.h2d_stream = torch.cuda.Stream(device=self.device) if (self.offload_master and self.device.type == "cuda") else None
         self.stage_slots: List[torch.Tensor] = []
         self._stage_rr = 0
@@ -172,7 +174,9 @@ class ParamStore:
                 b = self.buckets[gname] = Bucket(gname, e.layer)
                 b.expert = is_expert
             n = math.prod(shape)
-            slot = Slot(e.name, b.numel, n, shape, e.spec.decay, e, trainable=not self.frozen(e.name))
+            gm = self.grad_mask
+            slot = Slot(e.name, b.numel, n, shape, e.spec.decay and (gm is None or gm.decays(e.name)), e,
+                        trainable=not self.frozen(e.name) and (gm is None or gm.trainable(e.name)))
             b.slots.append(slot)
             b.numel += (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
             self.where[e.name] = (b, slot)
@@ -215,8 +219,10 @@ class ParamStore:
                 continue
             if self.offload_master and not self._resident(b):
                 b.master = torch.zeros(b.shard_numel, dtype=self.master_dtype, pin_memory=pin)
+                double = self.host_work_double  # one-step-stale optimizer: the update writes ``work_next`` while steps read ``work_host``
                 b.work_host = torch.zeros(b.shard_numel, dtype=self.param_dtype, pin_memory=pin) if (
-                    self.host_work_copy and self.master_dtype != self.param_dtype) else None
+                    self.host_work_copy and (double or self.master_dtype != self.param_dtype)) else None
+                b.work_next = torch.zeros(b.shard_numel, dtype=self.param_dtype, pin_memory=pin) if (double and b.trainable) else None
                 if self.arena is not None and b.trainable:
                     b.grad = self.arena.take(b.numel, self.grad_dtype)
                     b.grad_persistent = True
@@ -512,7 +518,8 @@ class ParamStore:
     def _gather_into(self, b: Bucket, full: torch.Tensor, async_op: bool = False):
         if b.master.device.type == "cpu" and self.device.type == "cuda":
             return self._gather_from_host(b, full, async_op)
-        src = b.master if b.master.dtype == full.dtype else b.master.to(full.dtype)
+        base = self.host_source(b) if b.master.device.type == "cpu" else b.master  # host masters: the published copy (a stale update may be writing the masters)
+        src = base if base.dtype == full.dtype else base.to(full.dtype)
         if not self.sharded:
             full.copy_(src)
             return None
@@ -633,6 +640,10 @@ class ParamStore:
         for s in (b.slots if zero_unwritten else ()):  # parameters that received no gradient this micro-step contribute zeros
             if s.trainable and s.name not in b.written and (self.zero_level >= 2 or b.grad_persistent):
                 b.grad[s.offset:s.offset + s.numel].zero_()
+        if self.grad_mask is not None and zero_unwritten:  # before the reduction: the zeroed half costs no precision in the sum
+            for s in b.slots:
+                if s.trainable and self.grad_mask.has_partial(s.name):
+                    self.grad_mask.apply_partial(s.name, b.grad[s.offset:s.offset + s.numel].view(s.shape))
         if getattr(self, "defer_reduce", False):
             return
         if self.world == 1 or b.expert:

@@ -57,6 +57,8 @@ class TrainerConfig:
     ep_size: int = 1
     ep_capacity_factor: float = 1.5
     ep_load_balance_threshold: float = 1.3   # re-place experts when a layer's busiest rank exceeds this multiple of the mean load
+    trainable_param_substrings: Optional[List[str]] = None  # partial-update runs: only parameters whose name contains one of these train
+    gradient_mask_mode: Optional[str] = None  # allow_substrings | mlp_growth_new_half (None: the SUROGATE_GRADIENT_MASK_MODE variable)
     ep_plan_refresh_interval: int = 16       # steps between placement refreshes (0 = never)
     lora: Optional[Dict[str, Any]] = None
     fp8_amax_history: int = 16
@@ -75,6 +77,7 @@ class TrainerConfig:
     use_cuda_graphs: bool = False  # capture each micro-batch's forward + backward in a CUDA graph (one GPU, dense models, bf16 / fp8 recipes)
     sequence_chunks: int = 1    # > 1: each sequence is trained in this many pieces against a key/value prefix (attention models only)
     long_context: bool = False  # tiled MLP: tile = min(tokens, hidden size) rows, recomputed per tile in backward (dense models)
+    async_optimizer: Optional[str] = None  # with cpu_training: "overlap" runs the host update of step N while step N+1 computes on weights one update old; "inline" = same bookkeeping, no overlap
     cpu_training: bool = False  # fp32 masters + AdamW moments on the host, update on the CPU, bf16 weights streamed per layer
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
@@ -125,9 +128,13 @@ class Trainer:
             from ..parallel import symm
 
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
-        self.store = ParamStore(self.cm, device=self.device, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
+        from .grad_mask import GradientMask
+
+        self.grad_mask = None if cfg.lora else GradientMask.resolve(cfg.trainable_param_substrings, cfg.gradient_mask_mode)
+        self.store = ParamStore(self.cm, device=self.device, grad_mask=self.grad_mask, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
                                 zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size,
-                                offload_master=cfg.offload_master or cfg.cpu_training, host_work_copy=cfg.cpu_training, owned=owned,
+                                offload_master=cfg.offload_master or cfg.cpu_training,
+                                host_work_copy=("double" if cfg.async_optimizer else True) if cfg.cpu_training else False, owned=owned,
                                 resident_layers=cfg.resident_layers if cfg.resident_layers >= 0 else int(os.environ.get("SUROGATE_RESIDENT_LAYERS", "0")))
         from .ops_cuda import make_backend
 
@@ -147,12 +154,16 @@ class Trainer:
         self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
                                        cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd)
         self.streamed = None
+        if cfg.async_optimizer and not cfg.cpu_training:
+            raise ValueError("async_optimizer overlaps the HOST update with device compute: it needs cpu_training")
+        if cfg.async_optimizer not in (None, "overlap", "inline"):
+            raise ValueError(f"async_optimizer: '{cfg.async_optimizer}' (overlap | inline)")
         if cfg.cpu_training:
             from .offload import CpuAdamW
 
             if cfg.optimizer not in ("adamw", "adamw_8bit"):
                 raise ValueError("cpu_training runs AdamW on the host: choose optimizer adamw (adamw_8bit is treated as adamw)")
-            self.optimizer = CpuAdamW(self.opt_cfg, self.store)
+            self.optimizer = CpuAdamW(self.opt_cfg, self.store, stale=cfg.async_optimizer)
         else:
             self.optimizer = make_optimizer(self.opt_cfg, self.store)
             if cfg.offload_optimizer or cfg.offload_master:
@@ -201,6 +212,7 @@ class Trainer:
             self.lora.init_weights(seed if seed is not None else self.cfg.seed)
 
     def import_weights(self, path: str) -> None:
+        self.drain_optimizer()
         from ..io.hf_checkpoint import import_hf_weights
 
         import_hf_weights(self.cm, self.store, path)
@@ -210,6 +222,7 @@ class Trainer:
         self.recipe.on_weights_updated(self.store)
 
     def export_model(self, out_dir: str, hf_config: Optional[Dict[str, Any]] = None) -> None:
+        self.drain_optimizer()
         from ..io.hf_checkpoint import export_hf_weights
 
         export_hf_weights(self.cm, self.store, out_dir, hf_config or self.cfg.model, write=self.rank == 0,
@@ -221,11 +234,13 @@ class Trainer:
         self.lora.export_peft(out_dir, base_model, write=self.rank == 0)
 
     def save_checkpoint(self, ckpt_dir: str, step: Optional[int] = None, extra: Optional[Dict[str, Any]] = None) -> str:
+        self.drain_optimizer()
         from ..io.checkpoint import save_checkpoint
 
         return save_checkpoint(self, ckpt_dir, self.step_index if step is None else step, extra or {})
 
     def load_checkpoint(self, ckpt_dir: str, step: Optional[int] = None) -> Dict[str, Any]:
+        self.drain_optimizer()
         from ..io.checkpoint import load_checkpoint
 
         return load_checkpoint(self, ckpt_dir, step)
@@ -474,6 +489,15 @@ class Trainer:
                 self.comm.all_reduce(total, "sum")
         return total.sqrt()
 
+    def drain_optimizer(self) -> None:
+        """With ``async_optimizer``: wait for the update in flight and make its weights the ones the next step reads."""
+        flush = getattr(self.optimizer, "flush", None)
+        if flush is not None and getattr(self.optimizer, "_pending", None):
+            flush()
+            for b in self.store.buckets.values():
+                b.work_host_fresh = getattr(b, "work_host", None) is not None and getattr(b, "work_next", None) is not None
+            self.store.sync_work_from_master()
+
     def optimizer_step(self, lr: Optional[float] = None, norm: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``norm``: the global gradient norm when this process holds only part of the model (pipeline stages)."""
         cfg = self.opt_cfg
@@ -583,6 +607,7 @@ class Trainer:
     @torch.no_grad()
     def logits(self, inputs, position_ids=None) -> torch.Tensor:
         """Full logits [rows, T, V] (fp32) — for teacher capture and debugging, not a training path."""
+        self.drain_optimizer()
         inp = self._stage("lg_inputs", inputs)
         rows, T = inp.shape
         pos = torch.arange(T, dtype=torch.int32, device=self.device)[None].expand(rows, T).contiguous() if position_ids is None \
@@ -609,6 +634,7 @@ class Trainer:
 
     @torch.no_grad()
     def validate(self, inputs, targets, position_ids=None) -> Dict[str, float]:
+        self.drain_optimizer()
         inp = self._stage("v_inputs", inputs)
         tgt = self._stage("v_targets", targets)
         T = inp.shape[1]

@@ -110,3 +110,40 @@ def test_phase_timing_reports_forward_head_backward_and_optimizer():
     assert set(t) == {"forward_ms", "lm_head_ms", "backward_ms", "optimizer_ms"} and all(v > 0 for v in t.values())
     tr.step(tok[:, :-1], tok[:, 1:])
     assert tr.last_time_breakdown["forward_ms"] < 10 * t["forward_ms"] + 50  # marks are reset per step, not accumulated over the run
+
+
+def test_gradient_masks_train_only_what_they_allow():
+    """Partial-update runs of a full model: with an allow-list only the named parameters change; with the MLP-growth mask only
+    the new half of each MLP matrix changes (and is not decayed), everything else stays bit-identical."""
+    import torch
+
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=128, d_model=32, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64)
+    tok = torch.randint(0, 128, (2, 17), generator=torch.Generator().manual_seed(0))
+
+    def run(**kw):
+        tr = Trainer(TrainerConfig(model=model, batch_size=2, seq_len=16, zero_level=0, optimizer="adamw", weight_decay=0.1, learning_rate=1e-2, **kw),
+                     device=torch.device("cpu"))
+        tr.init_weights(0)
+        before = {n: tr.store.get(n).clone() for n in tr.store.where}
+        for _ in range(2):
+            tr.step(tok[:, :-1].numpy(), tok[:, 1:].numpy())
+        return before, {n: tr.store.get(n).clone() for n in tr.store.where}
+
+    before, after = run(trainable_param_substrings=["qkv_weight", "final_norm"])
+    for n in before:
+        changed = not torch.equal(before[n], after[n])
+        assert changed == ("qkv_weight" in n or "final_norm" in n), n
+
+    before, after = run(gradient_mask_mode="mlp_growth_new_half")
+    for n in before:
+        d = (after[n] - before[n]).abs()
+        if "mlp_up_weight" in n:
+            q = d.shape[0] // 4
+            assert d[:q].max() == 0 and d[2 * q:3 * q].max() == 0 and d[q:2 * q].max() > 0 and d[3 * q:].max() > 0, n
+        elif "mlp_down_weight" in n:
+            h = d.shape[1] // 2
+            assert d[:, :h].max() == 0 and d[:, h:].max() > 0, n
+        else:
+            assert d.max() == 0, n

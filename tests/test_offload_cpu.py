@@ -57,3 +57,62 @@ def test_resident_layers_keep_frozen_weights_on_the_device_side():
     st = tr_b.store
     assert st._resident(st.buckets["layer0"]) and not st._resident(st.buckets["layer1"]) and not st._resident(st.buckets["embedding"])
 
+
+
+def test_stale_optimizer_worker_matches_the_inline_update_and_reports_errors():
+    """The native depth-1 worker: two queued updates give exactly the buffers of two direct kernel calls; a bad job raises at
+    the next drain and the worker keeps working afterwards."""
+    from surogate_b200.ops import host
+
+    h = host()
+    n = 50_000
+
+    def buffers():
+        g = torch.Generator().manual_seed(0)
+        return [torch.randn(n, generator=g), torch.zeros(n), torch.zeros(n), torch.randn(n, generator=g).bfloat16(), torch.zeros(n, dtype=torch.bfloat16),
+                torch.ones(n, dtype=torch.uint8)]
+
+    a, b = buffers(), buffers()
+    w = h.AsyncAdamW(True)
+    for step in (1, 2):
+        h.cpu_adamw_step(a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), True, a[4].data_ptr(), n, 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.5, step, a[5].data_ptr())
+        w.submit([(b[0].data_ptr(), b[1].data_ptr(), b[2].data_ptr(), b[3].data_ptr(), True, b[4].data_ptr(), True, n, b[5].data_ptr())], 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.5, step)
+    w.drain()
+    assert w.completed() == 2 and all(torch.equal(x, y) for x, y in zip(a, b))
+    w.submit([(0, 0, 0, 0, False, 0, False, 4, 0)], 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.5, 1)
+    with pytest.raises(Exception, match="null buffer"):
+        w.drain()
+    w.submit([], 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.5, 1)
+    w.drain()
+    assert w.completed() == 4
+
+
+@pytest.mark.parametrize("zero", [0, 3])
+def test_one_step_stale_optimizer(tmp_path, zero):
+    """``async_optimizer``: the host update of step N runs while step N+1 computes with the weights of update N-1.  On a repeated
+    batch the first two losses are therefore equal and the third is the plain optimizer's second; the overlapped run reproduces the
+    inline run bit for bit; draining publishes the last update (evaluation and a checkpoint see it) and a resumed run continues."""
+    tok = np.random.default_rng(1).integers(0, 256, (2, 33)).astype(np.int32)
+
+    def run(mode, steps=4):
+        cfg = TrainerConfig(model=MODEL, batch_size=2, seq_len=32, recipe="bf16", learning_rate=1e-2, weight_decay=0.1, zero_level=zero, optimizer="adamw",
+                            cpu_training=True, async_optimizer=mode)
+        tr = Trainer(cfg, device=torch.device("cpu"))
+        tr.init_weights(seed=3)
+        return tr, [tr.step(tok[:, :-1], tok[:, 1:])["loss"] for _ in range(steps)]
+
+    _, plain = run(None)
+    tr_i, inline = run("inline")
+    tr_o, over = run("overlap")
+    assert over == inline
+    assert over[0] == over[1] == plain[0] and abs(over[2] - plain[1]) < 1e-6
+    v = tr_o.validate(tok[:, :-1], tok[:, 1:])["loss"]
+    assert v == tr_i.validate(tok[:, :-1], tok[:, 1:])["loss"] and v < over[-1]
+    assert not tr_o.optimizer._pending
+    for b in tr_o.store.trainable_buckets():
+        assert torch.equal(b.work_host, b.master.to(b.work_host.dtype))
+    path = tr_o.save_checkpoint(str(tmp_path), step=4)
+    tr_r, _ = run("overlap", steps=0)
+    tr_r.load_checkpoint(str(tmp_path))
+    a = tr_o.step(tok[:, :-1], tok[:, 1:])["loss"]
+    assert tr_r.step(tok[:, :-1], tok[:, 1:])["loss"] == a == v
