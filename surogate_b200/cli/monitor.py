@@ -174,10 +174,103 @@ def launch(config: str, command: str = "sft", ssh: Optional[str] = None, gpus: i
     return subprocess.Popen(base, stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT, start_new_session=True)
 
 
+def browse_models(query: str, limit: int = 20, search=None) -> List[Dict[str, Any]]:
+    """Models the Launch view can line up: a local path (``/...``, ``~/...``, ``./...``) lists the model directories below it,
+    anything else is a HuggingFace search.  Each row says whether this framework can train the architecture.
+    ``search(query, limit) -> [{"id", "architectures", "downloads"}]`` replaces the hub call (tests, air-gapped machines)."""
+    from ..models.registry import describe_config, supported_architectures
+
+    rows: List[Dict[str, Any]] = []
+    if query.startswith(("/", "~", ".")):
+        root = os.path.abspath(os.path.expanduser(query))
+        cands = [root] + sorted(os.path.join(root, d) for d in os.listdir(root) if os.path.isdir(os.path.join(root, d))) if os.path.isdir(root) else []
+        for d in cands:
+            cfg_path = os.path.join(d, "config.json")
+            if not os.path.exists(cfg_path):
+                continue
+            with open(cfg_path) as f:
+                info = describe_config(json.load(f))
+            rows.append({"id": d, "architecture": info["architecture"], "trainable": bool(info["supported"]), "moe": info["is_moe"],
+                         "quant": (info["quant_info"] or {}).get("kind"), "layers": info["num_hidden_layers"], "hidden": info["hidden_size"]})
+        return rows[:limit]
+    if search is None:
+        def search(q, n):
+            from huggingface_hub import HfApi
+
+            return [{"id": m.id, "architectures": ((getattr(m, "config", None) or {}).get("architectures") or []), "downloads": getattr(m, "downloads", 0)}
+                    for m in HfApi().list_models(search=q, limit=n, sort="downloads", direction=-1, expand=["config", "downloads"])]
+    ok = set(supported_architectures())
+    for m in search(query, limit):
+        arch = (m.get("architectures") or [""])[0]
+        rows.append({"id": m["id"], "architecture": arch, "trainable": arch in ok, "downloads": m.get("downloads", 0)})
+    return rows
+
+
+def browse_datasets(query: str, limit: int = 20, search=None) -> List[Dict[str, Any]]:
+    """Datasets for the Launch view: local ``.jsonl`` / ``.json`` / ``.parquet`` files below a path with the detected sample type,
+    or a HuggingFace dataset search."""
+    rows: List[Dict[str, Any]] = []
+    if query.startswith(("/", "~", ".")):
+        from ..data.datasets import detect_type
+
+        root = os.path.abspath(os.path.expanduser(query))
+        files = [root] if os.path.isfile(root) else sorted(os.path.join(root, f) for f in os.listdir(root)) if os.path.isdir(root) else []
+        for f in files:
+            if not f.endswith((".jsonl", ".json", ".parquet")):
+                continue
+            kind = None
+            if f.endswith(".jsonl"):
+                with open(f) as fh:
+                    line = fh.readline().strip()
+                try:
+                    kind = detect_type(json.loads(line).keys()) if line else None
+                except Exception:  # noqa: BLE001
+                    kind = None
+            rows.append({"id": f, "type": kind, "bytes": os.path.getsize(f)})
+        return rows[:limit]
+    if search is None:
+        def search(q, n):
+            from huggingface_hub import HfApi
+
+            return [{"id": d.id, "downloads": getattr(d, "downloads", 0)} for d in HfApi().list_datasets(search=q, limit=n, sort="downloads", direction=-1)]
+    return [{"id": d["id"], "downloads": d.get("downloads", 0)} for d in search(query, limit)]
+
+
+def past_runs(root: str) -> List[Dict[str, Any]]:
+    """Runs below ``root`` (output directories): last logged step and loss, checkpoints and exported model present."""
+    rows = []
+    for d in sorted(os.listdir(root)) if os.path.isdir(root) else []:
+        path = os.path.join(root, d)
+        if not os.path.isdir(path):
+            continue
+        logs = [f for f in os.listdir(path) if f.endswith(".jsonl")]
+        ckpts = sorted(c for c in os.listdir(path) if c.startswith(("step_", "checkpoint")))
+        last: Dict[str, Any] = {}
+        for lf in logs:
+            st = FeedState(os.path.join(path, lf))
+            st.poll()
+            if st.steps:
+                last = {"step": st.steps[-1], "loss": st.series["loss"][-1]}
+        if logs or ckpts or os.path.exists(os.path.join(path, "model.safetensors")) or os.path.exists(os.path.join(path, "config.json")):
+            rows.append({"run": d, **last, "checkpoints": len(ckpts), "exported": os.path.exists(os.path.join(path, "config.json"))})
+    return rows
+
+
+def table(rows: List[Dict[str, Any]]) -> str:
+    if not rows:
+        return "(nothing found)"
+    cols = list(dict.fromkeys(k for r in rows for k in r))
+    cell = lambda v: ("yes" if v else "no") if isinstance(v, bool) else ("" if v is None else (f"{v:.4g}" if isinstance(v, float) else str(v)))  # noqa: E731
+    w = {c: max(len(c), *(len(cell(r.get(c))) for r in rows)) for c in cols}
+    lines = ["  ".join(c.ljust(w[c]) for c in cols), "  ".join("-" * w[c] for c in cols)]
+    lines += ["  ".join(cell(r.get(c)).ljust(w[c]) for c in cols) for r in rows]
+    return "\n".join(lines)
+
+
 def main(argv, command: str = "monitor") -> int:
     p = argparse.ArgumentParser(prog="surogate monitor")
-    p.add_argument("action", nargs="?", default="watch", choices=["watch", "launch"])
-    p.add_argument("config", nargs="?", help="training config (launch)")
+    p.add_argument("action", nargs="?", default="watch", choices=["watch", "launch", "models", "datasets", "runs"])
+    p.add_argument("config", nargs="?", help="training config (launch) | search text or path (models, datasets) | output root (runs)")
     p.add_argument("--feed", default=DEFAULT_FEED)
     p.add_argument("--once", action="store_true", help="render one frame and exit")
     p.add_argument("--interval", type=float, default=1.0)
@@ -185,6 +278,11 @@ def main(argv, command: str = "monitor") -> int:
     p.add_argument("--gpus", type=int, default=0)
     p.add_argument("--command", default="sft")
     a = p.parse_args(argv)
+    if a.action in ("models", "datasets", "runs"):
+        if not a.config:
+            p.error(f"{a.action} needs a search text or a path")
+        print(table({"models": browse_models, "datasets": browse_datasets, "runs": past_runs}[a.action](a.config)))
+        return 0
     if a.action == "launch":
         if not a.config:
             p.error("launch needs a config file")

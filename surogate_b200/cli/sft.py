@@ -15,6 +15,7 @@ def build_parser(prog: str) -> argparse.ArgumentParser:
     p.add_argument("--max-steps", type=int, default=None, dest="max_steps")
     p.add_argument("--output-dir", default=None, dest="output_dir")
     p.add_argument("--model", default=None)
+    p.add_argument("--recipe", default=None, help="override `recipe` (bf16 | fp8-hybrid | nvfp4)")
     p.add_argument("--synthetic-data", action="store_true", default=None, dest="synthetic_data")
     return p
 

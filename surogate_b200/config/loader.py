@@ -44,6 +44,43 @@ def expand_env(obj: Any) -> Any:
     return obj
 
 
+def coerce_fields(cls, kw: Dict[str, Any]) -> Dict[str, Any]:
+    """Convert string values to the scalar type a dataclass field declares.  YAML 1.1 reads ``3e-4`` (no decimal point) as a
+    string, and every ``${ENV}`` expansion yields one; without this they would reach arithmetic as text.  A value that does not
+    parse raises an error naming the key."""
+    import dataclasses
+    import typing
+
+    hints = typing.get_type_hints(cls)
+    out = dict(kw)
+    for f in dataclasses.fields(cls):
+        v = out.get(f.name)
+        if not isinstance(v, (str, int)) or isinstance(v, bool):
+            continue
+        t = hints.get(f.name)
+        args = [a for a in typing.get_args(t) if a is not type(None)] if typing.get_origin(t) is typing.Union else [t]
+        if str in args and isinstance(v, str):
+            continue
+        try:
+            if isinstance(v, str):
+                if bool in args and v.strip().lower() in ("true", "false", "yes", "no", "on", "off", "1", "0"):
+                    out[f.name] = v.strip().lower() in ("true", "yes", "on", "1")
+                elif int in args and re.fullmatch(r"[+-]?\d+", v.strip()):
+                    out[f.name] = int(v)
+                elif float in args:
+                    out[f.name] = float(v)
+                elif int in args:
+                    fv = float(v)
+                    if fv != int(fv):
+                        raise ValueError(v)
+                    out[f.name] = int(fv)
+            elif float in args and int not in args:
+                out[f.name] = float(v)
+        except ValueError:
+            raise ValueError(f"[E100] config key '{f.name}': cannot read '{v}' as {getattr(t, '__name__', t)}") from None
+    return out
+
+
 def read_yaml(path: str) -> Dict[str, Any]:
     if path.startswith(("http://", "https://")):
         import requests

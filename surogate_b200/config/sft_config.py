@@ -233,7 +233,9 @@ class SFTConfig:
         if isinstance(kw.get("report_to"), str):
             kw["report_to"] = [kw["report_to"]]
         kw = {k: v for k, v in kw.items() if v is not None or k in ("run_name",)}
-        cfg = cls(**kw)
+        from .loader import coerce_fields
+
+        cfg = cls(**coerce_fields(cls, kw))
         cfg.finalize()
         return cfg
 

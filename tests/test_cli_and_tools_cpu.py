@@ -267,3 +267,55 @@ def test_determinism_report_and_sanitized_host_runtime():
                        text=True, timeout=600, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert p.returncode == 0 and "host workload ok" in p.stdout, p.stderr[-3000:]
     assert "ERROR: AddressSanitizer" not in p.stderr and "runtime error" not in p.stderr
+
+
+def test_dashboard_browses_models_datasets_and_runs(tmp_path, capsys):
+    """The dashboard's Models / Datasets / Runs views: local model directories with the 'trainable' badge from the architecture
+    registry, a hub search through an injected function, dataset files with their detected type, and past runs of an output root."""
+    import json
+
+    from surogate_b200.cli import monitor
+
+    (tmp_path / "models" / "a").mkdir(parents=True)
+    (tmp_path / "models" / "b").mkdir()
+    (tmp_path / "models" / "a" / "config.json").write_text(json.dumps({"architectures": ["Qwen3ForCausalLM"], "hidden_size": 64, "num_hidden_layers": 2}))
+    (tmp_path / "models" / "b" / "config.json").write_text(json.dumps({"architectures": ["SomethingElseForCausalLM"], "num_experts": 4}))
+    rows = monitor.browse_models(str(tmp_path / "models"))
+    assert [(os.path.basename(r["id"]), r["trainable"], r["moe"]) for r in rows] == [("a", True, False), ("b", False, True)]
+    hub = monitor.browse_models("qwen", search=lambda q, n: [{"id": "org/m1", "architectures": ["Qwen3MoeForCausalLM"], "downloads": 5},
+                                                              {"id": "org/m2", "architectures": ["BertModel"]}])
+    assert [(r["id"], r["trainable"]) for r in hub] == [("org/m1", True), ("org/m2", False)]
+
+    (tmp_path / "data").mkdir()
+    (tmp_path / "data" / "chat.jsonl").write_text(json.dumps({"messages": [{"role": "user", "content": "hi"}]}) + "\n")
+    (tmp_path / "data" / "pairs.jsonl").write_text(json.dumps({"prompt": "p", "chosen": "a", "rejected": "b"}) + "\n")
+    ds = {os.path.basename(r["id"]): r["type"] for r in monitor.browse_datasets(str(tmp_path / "data"))}
+    assert ds == {"chat.jsonl": "messages", "pairs.jsonl": "preference"}
+    assert monitor.browse_datasets("x", search=lambda q, n: [{"id": "org/d", "downloads": 3}]) == [{"id": "org/d", "downloads": 3}]
+
+    run = tmp_path / "out" / "run1"
+    (run / "step_00000010").mkdir(parents=True)
+    (run / "log.jsonl").write_text("".join(json.dumps({"log": "step", "step": i, "loss": 3.0 - 0.1 * i}) + "\n" for i in range(1, 11)))
+    runs = monitor.past_runs(str(tmp_path / "out"))
+    assert runs == [{"run": "run1", "step": 10, "loss": 2.0, "checkpoints": 1, "exported": False}]
+    assert monitor.main(["runs", str(tmp_path / "out")]) == 0
+    assert "run1" in capsys.readouterr().out
+
+
+def test_config_values_written_as_text_reach_their_declared_type(tmp_path, monkeypatch):
+    """`learning_rate: 3e-4` (a string for YAML 1.1) and `${ENV}` expansions become numbers / booleans of the field's type; text
+    that does not parse names the key."""
+    import pytest
+
+    from surogate_b200.config.loader import load_config
+    from surogate_b200.config.sft_config import SFTConfig
+
+    monkeypatch.setenv("MY_STEPS", "12")
+    p = tmp_path / "c.yaml"
+    p.write_text("model: m\nlearning_rate: 3e-4\nmax_steps: ${MY_STEPS}\nrecompute: 'false'\nweight_decay: 1\nwarmup_ratio: '0.1'\n")
+    c = load_config(SFTConfig, str(p))
+    assert c.learning_rate == 3e-4 and isinstance(c.learning_rate, float)
+    assert c.max_steps == 12 and c.recompute is False and isinstance(c.weight_decay, float) and c.warmup_ratio == 0.1
+    p.write_text("model: m\nlearning_rate: fast\n")
+    with pytest.raises(ValueError, match="learning_rate"):
+        load_config(SFTConfig, str(p))
