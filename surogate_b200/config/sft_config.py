@@ -276,6 +276,10 @@ class SFTConfig:
             raise ValueError("[E111] parallelism must be ddp or dispatch_pp")
         if self.from_scratch and self.lora:
             raise ValueError("[E112] from_scratch (pre-training) trains all weights: set lora: false")
+        if self.attn_bwd_chunks < 1 or (self.attn_bwd_chunks > 1 and self.per_device_train_batch_size % self.attn_bwd_chunks != 0):
+            raise ValueError("[E113] attn_bwd_chunks must be >= 1 and divide per_device_train_batch_size")
+        if self.async_optimizer and not self.cpu_training:
+            raise ValueError("[E114] async_optimizer overlaps the host optimizer with device compute: set cpu_training: true")
         if self.checkpoint_dir is None:
             self.checkpoint_dir = self.output_dir
         if self.run_name is None:

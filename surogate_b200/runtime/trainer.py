@@ -528,8 +528,9 @@ class Trainer:
             self.lora.optimizer_step(self._hp, host)
         self.store.release_grads()
         self.store.sync_work_from_master()
-        if self.ep is not None and self.cfg.ep_plan_refresh_interval > 0 and self.step_index % self.cfg.ep_plan_refresh_interval == 0 \
-                and self.cfg.optimizer in ("adamw", "adamw_8bit") and not self.cfg.cpu_training:
+        # the initial placement is arbitrary, so the first decision comes after two steps of this process; later ones every interval
+        refresh_now = self.cfg.ep_plan_refresh_interval > 0 and (self.step_index % self.cfg.ep_plan_refresh_interval == 0 or self._steps_here == 2)
+        if self.ep is not None and refresh_now and self.cfg.optimizer in ("adamw", "adamw_8bit") and not self.cfg.cpu_training:
             self.last_rebalance = self.ep.rebalance(self.store, self.optimizer, self.cfg.ep_load_balance_threshold)
         self.recipe.on_weights_updated(self.store)
         self.recipe.end_step()

@@ -127,6 +127,38 @@ def test_host_resident_state_matches_device_resident(mode):
     assert a.store.h2d_bytes > 0
 
 
+def test_one_step_stale_host_optimizer_on_the_gpu():
+    """``async_optimizer`` with the weights streamed from pinned host memory: the overlapped update (native worker thread) follows
+    the inline run with the same staleness; on a repeated batch the first two losses agree (both computed with the initial
+    weights) and the third is the plain run's second; draining publishes the last update to the device copy."""
+    x, y = _batch(4)
+    plain = _trainer("cuda", optimizer="adamw", cpu_training=True)
+    inline = _trainer("cuda", optimizer="adamw", cpu_training=True, async_optimizer="inline")
+    over = _trainer("cuda", optimizer="adamw", cpu_training=True, async_optimizer="overlap")
+    lp = [plain.step(x, y)["loss"] for _ in range(4)]
+    li = [inline.step(x, y)["loss"] for _ in range(4)]
+    lo = [over.step(x, y)["loss"] for _ in range(4)]
+    for u, v in zip(lo, li):
+        assert abs(u - v) < 5e-3 * abs(v), (lo, li)
+    assert abs(lo[0] - lo[1]) < 2e-3 * lo[0] and abs(lo[2] - lp[1]) < 5e-3 * lp[1], (lo, lp)
+    v = over.validate(x, y)["loss"]
+    assert not over.optimizer._pending and v < lo[-1]
+    for b in over.store.trainable_buckets():
+        assert torch.equal(b.work_host, b.master.to(b.work_host.dtype))
+
+
+def test_gradient_mask_on_the_gpu():
+    """An allow-list freezes everything else on the CUDA path too (no gradient buffer is written, the fused optimizer kernel
+    leaves frozen slots of a shared bucket untouched)."""
+    x, y = _batch(4)
+    tr = _trainer("cuda", optimizer="adamw_8bit", trainable_param_substrings=["mlp_up_weight"], weight_decay=0.1)
+    before = {n: t.clone() for n, t in tr.store.named_full_tensors()}
+    for _ in range(3):
+        tr.step(x, y)
+    for n, t in tr.store.named_full_tensors():
+        assert torch.equal(t, before[n]) == ("mlp_up_weight" not in n), n
+
+
 def test_lora_gpu_loss_decreases_and_base_is_frozen():
     lora = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
                 rslora=False, train_router=False)
