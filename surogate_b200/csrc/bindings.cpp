@@ -393,4 +393,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("adamw_step", &adamw_step);
     m.def("adamw8_step", &adamw8_step);
     sg_register_extra(m);
+    sg_register_device_io(m);
 }

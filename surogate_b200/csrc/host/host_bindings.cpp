@@ -72,6 +72,7 @@ PYBIND11_MODULE(sg_b200_host, m) {
                  return d;
              })
         .def("metadata", &SafetensorsFile::metadata)
+        .def("data_start", &SafetensorsFile::data_start)
         .def("read_into", [](const SafetensorsFile& f, const std::string& name, uintptr_t dst, uint64_t nbytes, uint64_t off, int threads) {
                  py::gil_scoped_release rel;
                  f.read_into(name, ptr(dst), nbytes, off, threads);

@@ -27,6 +27,7 @@ public:
     const std::vector<StEntry>& entries() const { return entries_; }
     const StEntry* find(const std::string& name) const;
     const std::map<std::string, std::string>& metadata() const { return metadata_; }
+    uint64_t data_start() const { return data_start_; }  // file offset of the data section (entry ranges are relative to it)
     // Copies bytes [offset, offset + nbytes) of the tensor's data into dst using `threads` concurrent preads.
     void read_into(const std::string& name, void* dst, uint64_t nbytes, uint64_t offset, int threads) const;
     // Rows [row_begin, row_end) of dimension 0.

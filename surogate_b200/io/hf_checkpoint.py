@@ -23,7 +23,11 @@ from ..dsl.compiler import CompiledModel
 class LazyCheckpoint:
     """Name -> tensor access over one or many safetensors files."""
 
-    def __init__(self, path: str):
+    def __init__(self, path: str, device: Optional[torch.device] = None):
+        """``device``: a CUDA device makes ``get`` read tensors straight into device memory through the native reader (pinned
+        double-buffered staging, or GPUDirect Storage with ``SUROGATE_GDS=1``), so fusing / stacking runs on the GPU."""
+        self.device = device if (device is not None and torch.device(device).type == "cuda") else None
+        self._native: Dict[str, Any] = {}
         self.dir = path if os.path.isdir(path) else os.path.dirname(path)
         self.files: Dict[str, str] = {}
         self._open: Dict[str, Any] = {}
@@ -50,6 +54,13 @@ class LazyCheckpoint:
 
     def get(self, name: str) -> torch.Tensor:
         fn = self.files[name]
+        if self.device is not None:
+            from .safetensors_native import NativeSafetensors
+
+            nat = self._native.get(fn)
+            if nat is None:
+                nat = self._native[fn] = NativeSafetensors(fn)
+            return nat.get_tensor_device(name, self.device)
         h = self._open.get(fn)
         if h is None:
             h = self._open[fn] = safe_open(fn, framework="pt")
@@ -60,7 +71,8 @@ class LazyCheckpoint:
 
 
 def import_hf_weights(cm: CompiledModel, store, path: str, strict: bool = True) -> Dict[str, int]:
-    ckpt = LazyCheckpoint(path)
+    direct = os.environ.get("SUROGATE_DEVICE_LOAD", "0") == "1" or os.environ.get("SUROGATE_GDS", "0") == "1"
+    ckpt = LazyCheckpoint(path, device=store.device if direct else None)
     loaded = missing = 0
     for p in cm.params:
         m = p.spec.hf

@@ -48,6 +48,21 @@ class NativeSafetensors:
         self._f.read_into(name, out.data_ptr(), e - b, 0, self.threads)
         return out
 
+    def get_tensor_device(self, name: str, device, gds: Optional[bool] = None) -> torch.Tensor:
+        """The tensor read straight into device memory: GPUDirect Storage (cuFile) when ``gds`` (default: the ``SUROGATE_GDS``
+        variable) asks for it and it works on this machine, else pread into pinned double buffers overlapped with the
+        host-to-device copies.  ``self.last_route`` says which route the last call took."""
+        import os
+
+        from ..ops import ext
+
+        st, shape, b, e = self.entries[name]
+        out = torch.empty(shape, dtype=ST_TO_TORCH[st], device=device)
+        if e > b:
+            want = os.environ.get("SUROGATE_GDS", "0") == "1" if gds is None else bool(gds)
+            self.last_route = ext().read_file_to_device(self.path, self._f.data_start() + b, e - b, out, want)
+        return out
+
     def get_rows(self, name: str, row_begin: int, row_end: int, out: Optional[torch.Tensor] = None, pin: bool = False) -> torch.Tensor:
         st, shape, _, _ = self.entries[name]
         if out is None:

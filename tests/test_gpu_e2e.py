@@ -147,6 +147,31 @@ def test_one_step_stale_host_optimizer_on_the_gpu():
         assert torch.equal(b.work_host, b.master.to(b.work_host.dtype))
 
 
+def test_checkpoint_tensors_read_straight_into_device_memory(tmp_path, monkeypatch):
+    """The native file -> device reader (pinned double-buffered staging): a tensor larger than two staging chunks arrives bit
+    exact, an empty range is fine, and importing a checkpoint through it gives the weights of the default import."""
+    from safetensors.torch import save_file
+
+    from surogate_b200.io.safetensors_native import NativeSafetensors
+
+    g = torch.Generator().manual_seed(0)
+    big = torch.randn(24 * 1024 * 1024 + 7, generator=g).bfloat16()   # 48 MiB + 14 bytes: two chunks and a ragged tail
+    small = torch.arange(10, dtype=torch.int32)
+    save_file({"big": big, "small": small}, str(tmp_path / "t.safetensors"))
+    f = NativeSafetensors(str(tmp_path / "t.safetensors"))
+    assert torch.equal(f.get_tensor_device("big", "cuda:0").cpu(), big) and f.last_route.startswith("staged")
+    assert torch.equal(f.get_tensor_device("small", "cuda:0").cpu(), small)
+
+    a = _trainer("cuda")
+    a.export_model(str(tmp_path / "m"))
+    b, c = _trainer("cuda"), _trainer("cuda")
+    b.import_weights(str(tmp_path / "m"))
+    monkeypatch.setenv("SUROGATE_DEVICE_LOAD", "1")
+    c.import_weights(str(tmp_path / "m"))
+    for (n, u), (_, v) in zip(b.store.named_full_tensors(), c.store.named_full_tensors()):
+        assert torch.equal(u, v), n
+
+
 def test_gradient_mask_on_the_gpu():
     """An allow-list freezes everything else on the CUDA path too (no gradient buffer is written, the fused optimizer kernel
     leaves frozen slots of a shared bucket untouched)."""
