@@ -1,6 +1,7 @@
 // Declarations shared by the host runtime sources and their Python bindings.
 #pragma once
 #include <cstdint>
+#include <map>
 #include <string>
 #include <utility>
 #include <vector>
@@ -38,6 +39,48 @@ public:
 private:
     struct Impl;
     Impl* impl_;
+};
+
+// memory_stack.cpp
+class MemoryStack {   // stack-ordered sub-allocation of one address range (bookkeeping only: the caller owns the memory)
+public:
+    MemoryStack(uint64_t base, uint64_t capacity, uint64_t align = 4096);
+    uint64_t allocate(uint64_t bytes, const std::string& name);   // address; throws with the live blocks listed when the range is full
+    size_t checkpoint() const { return live_.size(); }
+    void restore(size_t checkpoint);                              // frees everything allocated after the checkpoint
+    void free_last(uint64_t address);
+    uint64_t used() const { return used_; }
+    uint64_t capacity() const { return capacity_; }
+    uint64_t high_water() const { return high_water_; }
+    uint64_t allocations() const { return allocations_; }
+    std::vector<std::pair<std::string, uint64_t>> live() const;
+    const std::map<std::string, uint64_t>& peak_by_name() const { return peak_by_name_; }
+
+private:
+    struct Block {
+        std::string name;
+        uint64_t offset, bytes;
+    };
+    uint64_t base_, capacity_, align_, used_ = 0, high_water_ = 0, allocations_ = 0;
+    std::vector<Block> live_;
+    std::map<std::string, uint64_t> peak_by_name_;
+};
+class AllocationRegistry {   // named long-lived allocations by category (weights, gradients, ...) and memory kind
+public:
+    void record(const std::string& name, const std::string& category, const std::string& kind, uint64_t bytes);
+    void release(const std::string& name);
+    std::map<std::string, uint64_t> by_category(const std::string& kind = "") const;
+    std::map<std::string, uint64_t> by_kind(bool peak = false) const;
+    std::vector<std::pair<std::string, uint64_t>> largest(size_t n) const;
+    size_t size() const { return entries_.size(); }
+
+private:
+    struct Entry {
+        std::string category, kind;
+        uint64_t bytes;
+    };
+    std::map<std::string, Entry> entries_;
+    std::map<std::string, uint64_t> current_, peak_;
 };
 
 // lpt_planner.cpp

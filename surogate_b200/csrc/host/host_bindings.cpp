@@ -119,6 +119,26 @@ PYBIND11_MODULE(sg_b200_host, m) {
         })
         .def("completed", &AsyncAdamW::completed)
         .def_property_readonly("overlap", &AsyncAdamW::overlap);
+    py::class_<MemoryStack>(m, "MemoryStack")
+        .def(py::init<uint64_t, uint64_t, uint64_t>(), py::arg("base"), py::arg("capacity"), py::arg("align") = 4096)
+        .def("allocate", &MemoryStack::allocate, py::arg("bytes"), py::arg("name") = "")
+        .def("checkpoint", &MemoryStack::checkpoint)
+        .def("restore", &MemoryStack::restore)
+        .def("free_last", &MemoryStack::free_last)
+        .def("live", &MemoryStack::live)
+        .def("peak_by_name", &MemoryStack::peak_by_name)
+        .def_property_readonly("used", &MemoryStack::used)
+        .def_property_readonly("capacity", &MemoryStack::capacity)
+        .def_property_readonly("high_water", &MemoryStack::high_water)
+        .def_property_readonly("allocations", &MemoryStack::allocations);
+    py::class_<AllocationRegistry>(m, "AllocationRegistry")
+        .def(py::init<>())
+        .def("record", &AllocationRegistry::record, py::arg("name"), py::arg("category"), py::arg("kind"), py::arg("bytes"))
+        .def("release", &AllocationRegistry::release)
+        .def("by_category", &AllocationRegistry::by_category, py::arg("kind") = "")
+        .def("by_kind", &AllocationRegistry::by_kind, py::arg("peak") = false)
+        .def("largest", &AllocationRegistry::largest, py::arg("n") = 10)
+        .def("__len__", &AllocationRegistry::size);
     m.def("cpu_sum_squares", [](uintptr_t x, bool bf16, int64_t n) {
         py::gil_scoped_release rel;
         return cpu_sum_squares(ptr(x), bf16, n);

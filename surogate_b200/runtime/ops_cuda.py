@@ -76,6 +76,19 @@ class CudaOps(RefOps):
         super().__init__(lmhead_chunk_rows)
         self.ext = _ext()  # raises when the extension is unavailable
         self.attention_impl = attention
+        self.stack = None  # runtime.memory.DeviceStack: transients of the LM-head chunk loop (SUROGATE_DEVICE_STACK=0 switches it off)
+
+    def _transient_stack(self, device):
+        import os
+
+        if self.stack is None and os.environ.get("SUROGATE_DEVICE_STACK", "1") != "0":
+            try:
+                from .memory import DeviceStack
+
+                self.stack = DeviceStack(device, name="transients")
+            except Exception:  # noqa: BLE001 - host runtime not built: buffers come from the caching allocator
+                self.stack = False
+        return self.stack or None
 
     # ------------------------------------------------------------------ embedding
     def embedding(self, ctx, op, token_ids, weight):
@@ -306,7 +319,15 @@ class CudaOps(RefOps):
         n = x2.shape[0]
         train = ctx.training
         rows = min(self.lmhead_chunk_rows, n)
-        logits = torch.empty(rows, V, dtype=torch.bfloat16, device=x.device)
+        stack = self._transient_stack(x.device)
+        if stack is not None and stack.fits(rows * V * 2):
+            with stack.frame():  # the chunk buffer has the same address every step (also under graph replay) and never touches the allocator
+                return self._lm_head_chunks(ctx, op, x, w, x2, t, n, rows, stack.alloc((rows, V), torch.bfloat16, "lm_head.logits"))
+        return self._lm_head_chunks(ctx, op, x, w, x2, t, n, rows, torch.empty(rows, V, dtype=torch.bfloat16, device=x.device))
+
+    def _lm_head_chunks(self, ctx, op, x, w, x2, t, n, rows, logits):
+        C, V = x2.shape[-1], w.shape[0]
+        train = ctx.training
         losses = torch.empty(n, dtype=torch.float32, device=x.device)
         dx = torch.empty_like(x2) if train else None
         tgt = None

@@ -670,7 +670,20 @@ class Trainer:
         return self.cm.num_parameters()
 
     def memory_breakdown(self) -> Dict[str, int]:
+        """Bytes by use (``master`` / ``work`` / ``grad`` / ...), by category and memory kind from the native allocation registry
+        (``category.*``, ``kind.*``), the transient stack's high-water mark, and the allocator's totals on a GPU."""
         out = self.store.memory_breakdown()
+        try:
+            from .memory import registry_for
+
+            reg = registry_for(self)
+            out.update({f"category.{k}": int(v) for k, v in reg.by_category().items()})
+            out.update({f"kind.{k}": int(v) for k, v in reg.by_kind().items()})
+        except Exception:  # noqa: BLE001 - the host runtime is not built: the coarse numbers above remain
+            pass
+        stack = getattr(self.backend, "stack", None)
+        if stack is not None:
+            out["stack_high_water"] = stack.high_water
         if self.device.type == "cuda":
             out["allocated"] = torch.cuda.memory_allocated(self.device)
             out["reserved"] = torch.cuda.memory_reserved(self.device)

@@ -172,6 +172,21 @@ def test_checkpoint_tensors_read_straight_into_device_memory(tmp_path, monkeypat
         assert torch.equal(u, v), n
 
 
+def test_lm_head_chunk_buffer_comes_from_the_device_stack(monkeypatch):
+    """The LM-head chunk buffer is a frame of the native device stack (same address every step); the losses are those of the run
+    that takes it from the caching allocator, and the memory breakdown reports the stack."""
+    x, y = _batch(2)
+    a = _trainer("cuda")
+    la = [a.step(x, y)["loss"] for _ in range(3)]
+    st = a.backend.stack
+    assert st is not None and st.high_water >= 200 * 2048 * 2 and st.used == 0 and st.stats()["allocations"] >= 3
+    assert a.memory_breakdown()["category.stack"] >= st.high_water
+    monkeypatch.setenv("SUROGATE_DEVICE_STACK", "0")
+    b = _trainer("cuda")
+    lb = [b.step(x, y)["loss"] for _ in range(3)]
+    assert b.backend.stack is None and all(abs(u - v) < 2e-3 * abs(v) for u, v in zip(la, lb)), (la, lb)
+
+
 def test_gradient_mask_on_the_gpu():
     """An allow-list freezes everything else on the CUDA path too (no gradient buffer is written, the fused optimizer kernel
     leaves frozen slots of a shared bucket untouched)."""

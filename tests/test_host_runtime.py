@@ -192,3 +192,42 @@ def test_expert_replacement_moves_only_when_it_pays():
     assert decide_placement([100, 90, 110, 100, 95, 105, 100, 100], cur, 2) == (cur, 0)   # within the threshold
     assert decide_placement([400, 0, 0, 0, 100, 100, 100, 100], cur, 2) == (cur, 0)       # one hot expert: no placement helps
     assert decide_placement([100, 100, 100, 100, 10, 10, 10, 10], cur, 2, max_moved_fraction=0.1) == (cur, 0)  # too many moves at once
+
+
+def test_device_stack_frames_and_memory_registry():
+    """Stack-ordered transients: 4 KiB-aligned views of one buffer, a frame releases what it took, the same request gets the same
+    address again, an over-full stack names its live blocks, an empty one grows; the registry sums long-lived tensors by
+    category and memory kind without counting shared storage twice."""
+    import torch
+
+    from surogate_b200.runtime.memory import DeviceStack, registry_for
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    st = DeviceStack("cpu", 64 * 1024)
+    with st.frame():
+        a = st.alloc((100,), torch.float32, "a")
+        b = st.alloc((3, 5), torch.bfloat16, "b")
+        assert a.data_ptr() % 4096 == 0 and b.data_ptr() - a.data_ptr() == 4096 and b.shape == (3, 5)
+        a.fill_(1.0), b.fill_(2.0)
+        assert float(a.sum()) == 100.0 and st.used == 8192
+        first = a.data_ptr()
+        with pytest.raises(RuntimeError, match=r"live: \[\('a', 4096\)"):
+            st.alloc((1 << 20,), torch.float32, "too big")
+    assert st.used == 0 and st.high_water == 8192
+    with st.frame():
+        assert st.alloc((100,), torch.float32, "a").data_ptr() == first
+    big = st.alloc((1 << 20,), torch.uint8, "grown")   # empty stack: replaced by a larger one
+    assert st.capacity >= 1 << 20 and big.numel() == 1 << 20
+    assert st.stats()["peak_by_name"]["grown"] == 1 << 20
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=128, d_model=32, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64)
+    tr = Trainer(TrainerConfig(model=model, batch_size=2, seq_len=16, zero_level=0, optimizer="adamw"), device=torch.device("cpu"))
+    tr.init_weights(0)
+    tok = torch.randint(0, 128, (2, 17)).numpy()
+    tr.step(tok[:, :-1], tok[:, 1:])
+    reg = registry_for(tr)
+    cats = reg.by_category()
+    n = sum(b.master.numel() for b in tr.store.buckets.values())
+    assert cats["weights_master"] == 4 * n and cats["optimizer_state"] == 8 * n
+    mb = tr.memory_breakdown()
+    assert mb["category.weights_master"] == 4 * n and mb["kind.host"] >= 12 * n
