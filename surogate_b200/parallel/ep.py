@@ -221,12 +221,26 @@ class ExpertParallel:
         E = counts_all.shape[1]
         El = E // self.ep
         changed, moved_total = 0, 0
+        backoff = self.__dict__.setdefault("_backoff", {})  # layer -> [imbalance before its last move, refreshes to sit out, length of the last pause]
         for li, L in enumerate(layers):
             cur = self.placement_host.get(L) or list(range(E))
-            new, moved = decide_placement(counts_all[li].tolist(), cur, self.ep, threshold, tolerance)
+            counts = counts_all[li].tolist()
             self.count_window[L].zero_()  # a new window starts (and counts are kept in placed order, which may change now)
+            per_rank = [sum(counts[r * El:(r + 1) * El]) for r in range(self.ep)]
+            now = max(per_rank) / max(1.0, sum(per_rank) / self.ep)
+            st = backoff.get(L)
+            if st is not None and st[1] == 0 and st[0] is not None:
+                # the window since the last move shows what it was worth: if the imbalance did not drop by a tenth, the counts
+                # are noise rather than a stable skew, and this layer sits out twice as many refreshes as last time (at most 8)
+                st[2] = min(8, max(1, 2 * st[2])) if now > 0.9 * st[0] else 0
+                st[1], st[0] = st[2], None
+            if st is not None and st[1] > 0:
+                st[1] -= 1
+                continue
+            new, moved = decide_placement(counts, cur, self.ep, threshold, tolerance)
             if moved == 0:
                 continue
+            backoff[L] = [now, 0, st[2] if st is not None else 0]
             self._move_experts(store, optimizer, L, cur, list(new), El, dist)
             self.placement_host[L] = list(new)
             self.placement[L] = torch.tensor(new, dtype=torch.int32, device=self.device)
