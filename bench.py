@@ -108,7 +108,7 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference cannot be installed offline: pip build of /root/reference fails "
+    print(json.dumps({"impl": "reference", "unavailable": "reference cannot be installed offline: pip build of the reference source tree fails "
                       "(scikit-build metadata needs setuptools_scm; CMake FetchContent needs network for CUTLASS 4.6.1, "
                       "flash-attention, cudnn-frontend, nanobind)"}))
     return 0

@@ -72,45 +72,58 @@ __device__ __forceinline__ void acc8(float (&a)[8], const uint4& v) {
 }
 
 // bufs.p[r] + elem_offset = rank r's full gradient bucket (bf16).  This rank reduces elements [rank*S, (rank+1)*S).
-template <bool OUT_FP32, bool ACCUMULATE>
+template <bool OUT_FP32, bool ACCUMULATE, int U>
 __global__ void __launch_bounds__(512) reduce_scatter_fused_kernel(PeerPtrs bufs, size_t elem_offset, size_t shard_elems, int rank, int world,
                                                                    float scale, void* __restrict__ out, float* __restrict__ sumsq_out) {
+    // U output vectors per trip, world <= 8 / U: eight 16-byte peer loads are in flight per thread whatever the number of ranks
+    // (NVLink round trips are microseconds; one load per thread leaves the links idle at 2 and 4 ranks)
+    constexpr int R = 8 / U;
     __shared__ float sh[32];
     const size_t nvec = shard_elems / 8;
     const size_t base = elem_offset + static_cast<size_t>(rank) * shard_elems;
+    const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
     float ss = 0.f;
-    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        uint4 raw[8];
+    for (size_t v0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += nthreads * U) {
+        uint4 raw[U * R];
         // issue all peer loads first (independent, long latency over NVLink), then reduce in a fixed rank order
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (r < world) raw[r] = ld_peer_16(reinterpret_cast<const bf16*>(bufs.p[r]) + base + v * 8);
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + u * nthreads;
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (r < world) acc8(a, raw[r]);
-        if (OUT_FP32) {
-            float* o = reinterpret_cast<float*>(out) + v * 8;
-            float4 lo = make_float4(a[0] * scale, a[1] * scale, a[2] * scale, a[3] * scale);
-            float4 hi = make_float4(a[4] * scale, a[5] * scale, a[6] * scale, a[7] * scale);
-            if (ACCUMULATE) {
-                const float4 plo = *reinterpret_cast<const float4*>(o), phi = *reinterpret_cast<const float4*>(o + 4);
-                lo.x += plo.x; lo.y += plo.y; lo.z += plo.z; lo.w += plo.w;
-                hi.x += phi.x; hi.y += phi.y; hi.z += phi.z; hi.w += phi.w;
-            }
-            ss += lo.x * lo.x + lo.y * lo.y + lo.z * lo.z + lo.w * lo.w + hi.x * hi.x + hi.y * hi.y + hi.z * hi.z + hi.w * hi.w;
-            *reinterpret_cast<float4*>(o) = lo;
-            *reinterpret_cast<float4*>(o + 4) = hi;
-        } else {
-            uint4 o;
-            bf162* po = reinterpret_cast<bf162*>(&o);
+            for (int r = 0; r < R; ++r)
+                if (r < world && v < nvec) raw[u * R + r] = ld_peer_16(reinterpret_cast<const bf16*>(bufs.p[r]) + base + v * 8);
+        }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                po[i] = __floats2bfloat162_rn(a[2 * i] * scale, a[2 * i + 1] * scale);
-                const float2 f = __bfloat1622float2(po[i]);   // norm of what is actually stored
-                ss += f.x * f.x + f.y * f.y;
+        for (int u = 0; u < U; ++u) {
+            const size_t v = v0 + u * nthreads;
+            if (v >= nvec) break;
+            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (r < world) acc8(a, raw[u * R + r]);
+            if (OUT_FP32) {
+                float* o = reinterpret_cast<float*>(out) + v * 8;
+                float4 lo = make_float4(a[0] * scale, a[1] * scale, a[2] * scale, a[3] * scale);
+                float4 hi = make_float4(a[4] * scale, a[5] * scale, a[6] * scale, a[7] * scale);
+                if (ACCUMULATE) {
+                    const float4 plo = *reinterpret_cast<const float4*>(o), phi = *reinterpret_cast<const float4*>(o + 4);
+                    lo.x += plo.x; lo.y += plo.y; lo.z += plo.z; lo.w += plo.w;
+                    hi.x += phi.x; hi.y += phi.y; hi.z += phi.z; hi.w += phi.w;
+                }
+                ss += lo.x * lo.x + lo.y * lo.y + lo.z * lo.z + lo.w * lo.w + hi.x * hi.x + hi.y * hi.y + hi.z * hi.z + hi.w * hi.w;
+                *reinterpret_cast<float4*>(o) = lo;
+                *reinterpret_cast<float4*>(o + 4) = hi;
+            } else {
+                uint4 o;
+                bf162* po = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    po[i] = __floats2bfloat162_rn(a[2 * i] * scale, a[2 * i + 1] * scale);
+                    const float2 f = __bfloat1622float2(po[i]);   // norm of what is actually stored
+                    ss += f.x * f.x + f.y * f.y;
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(out) + v * 8) = o;
             }
-            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(out) + v * 8) = o;
         }
     }
     if (sumsq_out) {
@@ -189,23 +202,37 @@ __global__ void __launch_bounds__(512) all_gather_fused_kernel(PeerPtrs shards, 
                                                                const float* __restrict__ scale) {
     const float s = scale ? __ldg(scale) : 1.f;
     const size_t nvec = (seg_end - seg_begin) / 8;
-    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t i = seg_begin + v * 8;
-        const int r = static_cast<int>(i / shard_elems);
-        const size_t local = i - static_cast<size_t>(r) * shard_elems;
-        const uint4 raw = ld_peer_16(reinterpret_cast<const bf16*>(shards.p[r]) + shard_elem_offset + local);
-        if (out_bf16) *reinterpret_cast<uint4*>(out_bf16 + i) = raw;
-        if (out_fp8) {
-            const bf162* p = reinterpret_cast<const bf162*>(&raw);
-            uint2 q;
-            uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+    const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+    constexpr int U = 4;   // 16-byte peer loads in flight per thread: one load per thread leaves NVLink (microsecond round trips) idle
+    for (size_t v0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += nthreads * U) {
+        uint4 raw[U];
+        size_t idx[U];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 f = __bfloat1622float2(p[k]);
-                qb[2 * k] = __nv_cvt_float_to_fp8(f.x * s, __NV_SATFINITE, __NV_E4M3);
-                qb[2 * k + 1] = __nv_cvt_float_to_fp8(f.y * s, __NV_SATFINITE, __NV_E4M3);
+        for (int u = 0; u < U; ++u) {
+            const size_t v = min(v0 + u * nthreads, nvec - 1);   // past the end: a duplicate of the last vector, not stored
+            idx[u] = seg_begin + v * 8;
+            const int r = static_cast<int>(idx[u] / shard_elems);
+            const size_t local = idx[u] - static_cast<size_t>(r) * shard_elems;
+            raw[u] = ld_peer_16(reinterpret_cast<const bf16*>(shards.p[r]) + shard_elem_offset + local);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (v0 + u * nthreads >= nvec) continue;
+            const size_t i = idx[u];
+            const uint4 rv = raw[u];
+            if (out_bf16) *reinterpret_cast<uint4*>(out_bf16 + i) = rv;
+            if (out_fp8) {
+                const bf162* p = reinterpret_cast<const bf162*>(&rv);
+                uint2 q;
+                uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __bfloat1622float2(p[k]);
+                    qb[2 * k] = __nv_cvt_float_to_fp8(f.x * s, __NV_SATFINITE, __NV_E4M3);
+                    qb[2 * k + 1] = __nv_cvt_float_to_fp8(f.y * s, __NV_SATFINITE, __NV_E4M3);
+                }
+                *reinterpret_cast<uint2*>(out_fp8 + i) = q;
             }
-            *reinterpret_cast<uint2*>(out_fp8 + i) = q;
         }
     }
 }
@@ -267,9 +294,13 @@ void symm_barrier(const PeerPtrs& pads, int rank, int world, uint32_t epoch, int
 void reduce_scatter_fused(const PeerPtrs& bufs, size_t elem_offset, size_t shard_elems, int rank, int world, float scale, void* out, int out_fp32,
                           int accumulate, float* sumsq_out, int max_blocks, cudaStream_t s) {
     const int grid = comm_grid(shard_elems / 8, 512, max_blocks);
-    if (out_fp32 && accumulate) reduce_scatter_fused_kernel<true, true><<<grid, 512, 0, s>>>(bufs, elem_offset, shard_elems, rank, world, scale, out, sumsq_out);
-    else if (out_fp32) reduce_scatter_fused_kernel<true, false><<<grid, 512, 0, s>>>(bufs, elem_offset, shard_elems, rank, world, scale, out, sumsq_out);
-    else reduce_scatter_fused_kernel<false, false><<<grid, 512, 0, s>>>(bufs, elem_offset, shard_elems, rank, world, scale, out, sumsq_out);
+#define SG_RS(F32, ACC, UU) reduce_scatter_fused_kernel<F32, ACC, UU><<<grid, 512, 0, s>>>(bufs, elem_offset, shard_elems, rank, world, scale, out, sumsq_out)
+#define SG_RS_U(F32, ACC) do { if (world <= 2) SG_RS(F32, ACC, 4); else if (world <= 4) SG_RS(F32, ACC, 2); else SG_RS(F32, ACC, 1); } while (0)
+    if (out_fp32 && accumulate) SG_RS_U(true, true);
+    else if (out_fp32) SG_RS_U(true, false);
+    else SG_RS_U(false, false);
+#undef SG_RS_U
+#undef SG_RS
 }
 
 void reduce_scatter_multimem(const void* mc_base, size_t elem_offset, size_t shard_elems, int rank, float scale, void* out, int out_fp32,
