@@ -78,6 +78,33 @@ def decide_placement(placed_counts, cur, ep: int, threshold: float = 1.3, tolera
     return new, int(moved)
 
 
+class PlacementBackoff:
+    """Keeps re-placement from chasing noise.  The window after a move shows what the move was worth: if the layer's rank
+    imbalance did not drop by a tenth, its counts are noise rather than a stable skew, and the layer sits out 1, 2, 4, then 8
+    refreshes (doubling each time a move fails again); a move that helped resets the pause."""
+
+    def __init__(self, needed_drop: float = 0.1, max_pause: int = 8):
+        self.needed_drop, self.max_pause = needed_drop, max_pause
+        self.state: Dict[int, list] = {}  # layer -> [imbalance before the last move (None once judged), refreshes left to sit out, last pause length]
+
+    def sits_out(self, layer: int, imbalance_now: float) -> bool:
+        st = self.state.get(layer)
+        if st is None:
+            return False
+        if st[0] is not None:  # first refresh after a move: judge it
+            helped = imbalance_now <= (1.0 - self.needed_drop) * st[0]
+            st[2] = 0 if helped else min(self.max_pause, max(1, 2 * st[2]))
+            st[0], st[1] = None, st[2]
+        if st[1] > 0:
+            st[1] -= 1
+            return True
+        return False
+
+    def moved(self, layer: int, imbalance_before: float) -> None:
+        st = self.state.get(layer)
+        self.state[layer] = [imbalance_before, 0, st[2] if st is not None else 0]
+
+
 class ExpertParallel:
     def __init__(self, comm, ep_size: int, device, capacity_factor: float = 1.5):
         if not hasattr(comm, "create_arena"):
@@ -221,26 +248,19 @@ class ExpertParallel:
         E = counts_all.shape[1]
         El = E // self.ep
         changed, moved_total = 0, 0
-        backoff = self.__dict__.setdefault("_backoff", {})  # layer -> [imbalance before its last move, refreshes to sit out, length of the last pause]
+        backoff = self.__dict__.setdefault("_backoff", PlacementBackoff())
         for li, L in enumerate(layers):
             cur = self.placement_host.get(L) or list(range(E))
             counts = counts_all[li].tolist()
             self.count_window[L].zero_()  # a new window starts (and counts are kept in placed order, which may change now)
             per_rank = [sum(counts[r * El:(r + 1) * El]) for r in range(self.ep)]
             now = max(per_rank) / max(1.0, sum(per_rank) / self.ep)
-            st = backoff.get(L)
-            if st is not None and st[1] == 0 and st[0] is not None:
-                # the window since the last move shows what it was worth: if the imbalance did not drop by a tenth, the counts
-                # are noise rather than a stable skew, and this layer sits out twice as many refreshes as last time (at most 8)
-                st[2] = min(8, max(1, 2 * st[2])) if now > 0.9 * st[0] else 0
-                st[1], st[0] = st[2], None
-            if st is not None and st[1] > 0:
-                st[1] -= 1
+            if backoff.sits_out(L, now):
                 continue
             new, moved = decide_placement(counts, cur, self.ep, threshold, tolerance)
             if moved == 0:
                 continue
-            backoff[L] = [now, 0, st[2] if st is not None else 0]
+            backoff.moved(L, now)
             self._move_experts(store, optimizer, L, cur, list(new), El, dist)
             self.placement_host[L] = list(new)
             self.placement[L] = torch.tensor(new, dtype=torch.int32, device=self.device)

@@ -231,3 +231,24 @@ def test_device_stack_frames_and_memory_registry():
     assert cats["weights_master"] == 4 * n and cats["optimizer_state"] == 8 * n
     mb = tr.memory_breakdown()
     assert mb["category.weights_master"] == 4 * n and mb["kind.host"] >= 12 * n
+
+
+def test_placement_backoff_pauses_layers_whose_moves_do_not_help():
+    from surogate_b200.parallel.ep import PlacementBackoff
+
+    b = PlacementBackoff()
+    assert not b.sits_out(0, 1.9)            # never moved: free to decide
+    b.moved(0, 1.9)
+    assert b.sits_out(0, 1.85)               # the move did not lower the imbalance by a tenth: pause 1 refresh (this one)
+    assert not b.sits_out(0, 1.9)            # pause over: may decide again
+    b.moved(0, 1.9)
+    assert [b.sits_out(0, 1.88) for _ in range(3)] == [True, True, False]          # failed again: 2 refreshes
+    b.moved(0, 1.9)
+    assert [b.sits_out(0, 1.9) for _ in range(5)] == [True] * 4 + [False]          # 4
+    b.moved(0, 1.9)
+    assert sum(b.sits_out(0, 1.9) for _ in range(12)) == 8                         # capped at 8
+    b.moved(0, 1.9)
+    assert not b.sits_out(0, 1.2)            # this one helped: no pause, and the next failure starts at 1 again
+    b.moved(0, 1.5)
+    assert [b.sits_out(0, 1.5) for _ in range(2)] == [True, False]
+    assert not b.sits_out(7, 3.0)            # layers are independent
