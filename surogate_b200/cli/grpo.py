@@ -37,7 +37,9 @@ def main(argv, command: str = "grpo") -> int:
         from ..grpo.transport import make_transport
         from ..grpo.weight_broadcast import FilesystemBroadcast
 
-        cfg = OrchestratorConfig(**{k: v for k, v in raw.items() if k in OrchestratorConfig.__dataclass_fields__})
+        from ..config.loader import coerce_fields
+
+        cfg = OrchestratorConfig(**coerce_fields(OrchestratorConfig, {k: v for k, v in raw.items() if k in OrchestratorConfig.__dataclass_fields__}))
         if a.max_steps:
             cfg.max_steps = a.max_steps
         b = FilesystemBroadcast(cfg.weight_dir)
@@ -51,7 +53,9 @@ def main(argv, command: str = "grpo") -> int:
     from ..grpo.config import InferenceConfig
     from ..grpo.inference import launch_server, watch_and_reload
 
-    cfg = InferenceConfig(**{k: v for k, v in raw.items() if k in InferenceConfig.__dataclass_fields__})
+    from ..config.loader import coerce_fields
+
+    cfg = InferenceConfig(**coerce_fields(InferenceConfig, {k: v for k, v in raw.items() if k in InferenceConfig.__dataclass_fields__}))
     proc = launch_server(cfg)
     try:
         watch_and_reload(cfg, f"http://{cfg.host}:{cfg.port}/v1")

@@ -227,9 +227,13 @@ class SFTConfig:
         kw["datasets"] = [DatasetConfig.from_any(x) for x in (kw.get("datasets") or [])]
         kw["validation_datasets"] = [DatasetConfig.from_any(x) for x in (kw.get("validation_datasets") or [])]
         if kw.get("distributed"):
-            kw["distributed"] = DistributedConfig(**kw["distributed"])
+            from .loader import coerce_fields as _cf
+
+            kw["distributed"] = DistributedConfig(**_cf(DistributedConfig, dict(kw["distributed"])))
         if kw.get("distillation"):
-            kw["distillation"] = DistillationConfig(**kw["distillation"])
+            from .loader import coerce_fields as _cf
+
+            kw["distillation"] = DistillationConfig(**_cf(DistillationConfig, dict(kw["distillation"])))
         if isinstance(kw.get("report_to"), str):
             kw["report_to"] = [kw["report_to"]]
         kw = {k: v for k, v in kw.items() if v is not None or k in ("run_name",)}

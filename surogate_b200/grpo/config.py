@@ -39,7 +39,9 @@ class GRPOConfig(SFTConfig):
         loss = d.pop("loss", None)
         cfg = super().from_dict(d)
         if loss:
-            cfg.loss = GRPOLossConfig(**loss)
+            from ..config.loader import coerce_fields
+
+            cfg.loss = GRPOLossConfig(**coerce_fields(GRPOLossConfig, dict(loss)))
         return cfg
 
 
