@@ -162,7 +162,19 @@ class CpuAdamW:
         if self.host is None:
             raise RuntimeError("the one-step-stale optimizer needs the native host runtime (surogate_b200.ops.build_host)")
         if self.worker is None:
+            import atexit
+            import weakref
+
             self.worker = self.host.AsyncAdamW(self.stale == "overlap")
+            ref = weakref.ref(self)
+
+            def _join_worker_before_shutdown():  # the worker thread is joined while the interpreter and the OpenMP runtime are still whole
+                me = ref()
+                if me is not None and me.worker is not None:
+                    me.worker.drain()
+                    me.worker = None
+
+            atexit.register(_join_worker_before_shutdown)
         self.flush()
         c = self.cfg
         jobs, keep = [], []
