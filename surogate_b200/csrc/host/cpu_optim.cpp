@@ -32,6 +32,13 @@ void cpu_adamw_step(float* param, float* m, float* v, const void* grad, bool gra
     const float inv_sqrt_bc2 = 1.0f / std::sqrt(bc2);
     const float* g32 = static_cast<const float*>(grad);
     const uint16_t* g16 = static_cast<const uint16_t*>(grad);
+    if (grad_scale == 0.0f) {   // skipped update (non-finite gradient): weights and moments stay; the streamed copy is still refreshed
+        if (work_bf16) {
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) work_bf16[i] = f32_to_bf16(param[i]);
+        }
+        return;
+    }
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
         const float g = (grad_is_bf16 ? bf16_to_f32(g16[i]) : g32[i]) * grad_scale;

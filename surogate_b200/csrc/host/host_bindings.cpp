@@ -14,6 +14,21 @@ using namespace sg;
 
 static void* ptr(uintptr_t p) { return reinterpret_cast<void*>(p); }
 
+// AsyncAdamW plus the Python objects whose memory its job in flight touches.  The worker needs no GIL, so the destructor can wait
+// for it while holding the GIL; only then are the references dropped.
+struct OwnedAsyncAdamW {
+    AsyncAdamW w;
+    py::object keep = py::none();
+    explicit OwnedAsyncAdamW(bool overlap) : w(overlap) {}
+    ~OwnedAsyncAdamW() {
+        try {
+            py::gil_scoped_release rel;
+            w.drain();
+        } catch (...) {   // a failed update is reported by submit() / drain(); a destructor has nobody to tell
+        }
+    }
+};
+
 PYBIND11_MODULE(sg_b200_host, m) {
     m.doc() = "surogate_b200 native host runtime";
 
@@ -97,11 +112,13 @@ PYBIND11_MODULE(sg_b200_host, m) {
                              static_cast<uint16_t*>(ptr(work)), n, lr, b1, b2, eps, wd, grad_scale, step, static_cast<const uint8_t*>(ptr(mask)));
           }, py::arg("param"), py::arg("m"), py::arg("v"), py::arg("grad"), py::arg("grad_is_bf16"), py::arg("work_bf16"), py::arg("n"), py::arg("lr"),
           py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"), py::arg("decay_mask") = 0);
-    py::class_<AsyncAdamW>(m, "AsyncAdamW")
+    py::class_<OwnedAsyncAdamW>(m, "AsyncAdamW")
         .def(py::init<bool>(), py::arg("overlap") = true)
-        .def("submit", [](AsyncAdamW& w, const std::vector<std::tuple<uintptr_t, uintptr_t, uintptr_t, uintptr_t, bool, uintptr_t, bool, int64_t, uintptr_t>>& jobs,
-                          float lr, float b1, float b2, float eps, float wd, float grad_scale, int64_t step) {
-                 // job = (param, m, v, grad, grad_is_bf16, work, work_is_bf16, n, decay_mask); the buffers must stay alive and untouched until drain()
+        .def("submit", [](OwnedAsyncAdamW& o, const std::vector<std::tuple<uintptr_t, uintptr_t, uintptr_t, uintptr_t, bool, uintptr_t, bool, int64_t, uintptr_t>>& jobs,
+                          float lr, float b1, float b2, float eps, float wd, float grad_scale, int64_t step, py::object keepalive) {
+                 // job = (param, m, v, grad, grad_is_bf16, work, work_is_bf16, n, decay_mask).  ``keepalive`` (any Python object, normally the
+                 // list of tensors behind the addresses) is owned by the worker until this update has completed, so dropping the
+                 // optimizer or the trainer with an update in flight cannot free memory the worker thread still writes.
                  std::vector<AdamJob> v;
                  for (auto& j : jobs) {
                      void* work = ptr(std::get<5>(j));
@@ -110,15 +127,25 @@ PYBIND11_MODULE(sg_b200_host, m) {
                                   ptr(std::get<3>(j)), std::get<4>(j), wb ? static_cast<uint16_t*>(work) : nullptr, wb ? nullptr : static_cast<float*>(work),
                                   std::get<7>(j), static_cast<const uint8_t*>(ptr(std::get<8>(j)))});
                  }
+                 {
+                     py::gil_scoped_release rel;
+                     o.w.drain();   // the previous update is complete: its buffers may go
+                 }
+                 o.keep = std::move(keepalive);
                  py::gil_scoped_release rel;
-                 w.submit(std::move(v), AdamHyper{lr, b1, b2, eps, wd, grad_scale, step});
-             }, py::arg("jobs"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"))
-        .def("drain", [](AsyncAdamW& w) {
-            py::gil_scoped_release rel;
-            w.drain();
+                 o.w.submit(std::move(v), AdamHyper{lr, b1, b2, eps, wd, grad_scale, step});
+             }, py::arg("jobs"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("grad_scale"), py::arg("step"),
+             py::arg("keepalive") = py::none())
+        .def("drain", [](OwnedAsyncAdamW& o) {
+            {
+                py::gil_scoped_release rel;
+                o.w.drain();
+            }
+            o.keep = py::none();
         })
-        .def("completed", &AsyncAdamW::completed)
-        .def_property_readonly("overlap", &AsyncAdamW::overlap);
+        .def("completed", [](const OwnedAsyncAdamW& o) { return o.w.completed(); })
+        .def_property_readonly("holds_buffers", [](const OwnedAsyncAdamW& o) { return !o.keep.is_none(); })
+        .def_property_readonly("overlap", [](const OwnedAsyncAdamW& o) { return o.w.overlap(); });
     py::class_<MemoryStack>(m, "MemoryStack")
         .def(py::init<uint64_t, uint64_t, uint64_t>(), py::arg("base"), py::arg("capacity"), py::arg("align") = 4096)
         .def("allocate", &MemoryStack::allocate, py::arg("bytes"), py::arg("name") = "")

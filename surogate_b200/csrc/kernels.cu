@@ -627,6 +627,7 @@ template <typename P, typename G>
 __global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, const G* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                                                          const uint8_t* __restrict__ decay_mask, const float* __restrict__ hp, size_t n) {
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
+    if (gs == 0.f) return;   // clip scale 0 = the step's gradient was not finite: weights and moments stay as they are
     const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
     const size_t nvec = n / 8;
     for (size_t vi = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; vi < nvec; vi += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -675,6 +676,7 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
     }
     __syncthreads();
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
+    if (gs == 0.f) return;   // skipped update (non-finite gradient norm): nothing is read or written
     const float step_size = lr / bc1, sib2 = rsqrtf(bc2), omb1 = 1.f - b1, omb2 = 1.f - b2;
     const size_t nvec = n / 8;
     constexpr int U = 2;  // vectors per thread per trip

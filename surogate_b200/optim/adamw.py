@@ -92,6 +92,8 @@ class AdamW:
             self.ext.adamw_step(b.master, grad.contiguous(), st["m"], st["v"], mask, hp)
             return
         lr, b1, b2, eps, wd, bc1, bc2 = hp_host
+        if float(hp[7]) == 0.0:  # skipped update (non-finite gradient norm), as in the kernels
+            return
         g = grad.float() * hp[7]
         st["m"].mul_(b1).add_(g, alpha=1 - b1)
         st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
@@ -123,6 +125,8 @@ class AdamW8bit(AdamW):
             return
         mask = self.store.decay_mask(b)
         lr, b1, b2, eps, wd, bc1, bc2 = hp_host
+        if float(hp[7]) == 0.0:
+            return
         m, v = _softsign_dequant_reference(st["m"], st["v"], st["m.scales"], st["v.scales"])
         g = grad.float() * hp[7]
         m = b1 * m + (1 - b1) * g

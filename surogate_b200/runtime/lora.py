@@ -219,7 +219,7 @@ class LoRAManager:
             from ..ops import ext
 
             ext().adamw_step(self.master, self.grad, self.opt_state["m"], self.opt_state["v"], None, hp)
-        else:
+        elif float(hp[7]) != 0.0:  # a zero clip scale marks a skipped update (non-finite gradient norm)
             g = self.grad * hp[7]
             m, v = self.opt_state["m"], self.opt_state["v"]
             m.mul_(b1).add_(g, alpha=1 - b1)

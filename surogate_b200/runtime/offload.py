@@ -149,6 +149,22 @@ class CpuAdamW:
         self.bytes_out += g.numel() * g.element_size()
 
     # ------------------------------------------------------------------ one-step-stale updates
+    def close(self) -> None:
+        """Wait for the update in flight, publish its weights and stop the worker.  Safe to call more than once."""
+        if self.worker is not None:
+            try:
+                self.flush()
+            finally:
+                self.worker = None
+
+    def __del__(self):
+        try:
+            w = self.worker
+            if w is not None:
+                w.drain()
+        except Exception:  # noqa: BLE001  (interpreter shutdown: nothing to report to)
+            pass
+
     def flush(self) -> None:
         """Wait for the update in flight and publish its weights (swap the work copies).  Called before the next update is
         queued and before anything reads masters or optimizer state (checkpoint, export, evaluation)."""
@@ -198,13 +214,14 @@ class CpuAdamW:
                 mask = b.decay_mask_host = self.store.decay_mask(b).to("cpu").contiguous()
             if g.dtype not in (torch.float32, torch.bfloat16) or b.work_next.dtype not in (torch.float32, torch.bfloat16):
                 raise RuntimeError(f"stale updates support fp32 / bf16 gradients and weights, got {g.dtype} / {b.work_next.dtype}")
-            keep.append(g)
+            keep.extend((g, b.master, st["m"], st["v"], b.work_next, mask))
             jobs.append((b.master.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(), g.data_ptr(), g.dtype == torch.bfloat16, b.work_next.data_ptr(),
                          b.work_next.dtype == torch.bfloat16, b.master.numel(), mask.data_ptr()))
             self._pending.append(b)
             b.work_host_fresh = True  # the published copy stays what steps read; nothing may copy from the masters while they are being written
-        self._keep = keep  # the gradient buffers stay alive until the worker is done with them
-        self.worker.submit(jobs, lr, c.beta1, c.beta2, c.eps, c.weight_decay, clip, step)
+        # the worker owns a reference to every buffer of the update until it has completed (and waits for it in its own destructor),
+        # so an optimizer or trainer dropped with an update in flight frees nothing that is still being written
+        self.worker.submit(jobs, lr, c.beta1, c.beta2, c.eps, c.weight_decay, clip, step, keep)
         self.grad_host.clear()
         self._parity ^= 1
 
@@ -234,6 +251,11 @@ class CpuAdamW:
                                          wh.data_ptr() if wh is not None else 0, n, lr, c.beta1, c.beta2, c.eps, c.weight_decay, clip, step,
                                          mask.data_ptr())
             else:  # no native runtime (or an unusual gradient dtype)
+                if clip == 0.0:  # skipped update (non-finite gradient norm)
+                    if wh is not None:
+                        wh.copy_(b.master)
+                        b.work_host_fresh = True
+                    continue
                 gf = g.float() * clip
                 st["m"].mul_(c.beta1).add_(gf, alpha=1 - c.beta1)
                 st["v"].mul_(c.beta2).addcmul_(gf, gf, value=1 - c.beta2)

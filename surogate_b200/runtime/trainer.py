@@ -476,8 +476,6 @@ class Trainer:
             if g is None:
                 continue
             total += self.backend.ext.sumsq(g) if on_gpu else g.float().pow(2).sum()
-        if self.lora is not None:
-            total += self.lora.grad_sumsq()
         if self.world > 1 and (self.store.sharded or self.store.ep > 1):
             if not self.store.sharded:  # replicated gradients: only the expert buckets differ between ranks
                 rep = sum((self.backend.ext.sumsq(b.grad_shard) if on_gpu else b.grad_shard.float().pow(2).sum())
@@ -487,6 +485,9 @@ class Trainer:
                 total = total + rep
             else:
                 self.comm.all_reduce(total, "sum")
+        if self.lora is not None:
+            # the adapter gradient is already all-reduced (identical on every rank): it joins after the cross-rank sum
+            total = total + self.lora.grad_sumsq()
         return total.sqrt()
 
     def drain_optimizer(self) -> None:
@@ -507,7 +508,7 @@ class Trainer:
         lr = cfg.learning_rate if lr is None else lr
         norm = self.grad_norm() if norm is None else norm
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm and cfg.max_grad_norm > 0 else torch.ones_like(norm)
-        clip = torch.where(torch.isfinite(norm), clip, torch.zeros_like(clip))  # a non-finite gradient skips the update
+        clip = torch.where(torch.isfinite(norm), clip, torch.zeros_like(clip))  # a non-finite norm skips the update: the optimizer kernels and CPU paths return early on a zero scale
         host = (lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, 1 - cfg.beta1 ** t, 1 - cfg.beta2 ** t)
         hp_cpu = torch.tensor(list(host) + [1.0], dtype=torch.float32)
         self._hp.copy_(hp_cpu, non_blocking=True)

@@ -152,6 +152,11 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     model_dir = cfg.model if isinstance(cfg.model, str) and os.path.isdir(cfg.model) else None
     latest = (trainer.latest_checkpoint(cfg.checkpoint_dir) if pp else find_latest_checkpoint(cfg.checkpoint_dir)) if cfg.resume_from_checkpoint else None
     if latest is not None:
+        if getattr(trainer, "lora", None) is not None:  # adapter-only checkpoints: the frozen base comes from its source again
+            if cfg.from_scratch or model_dir is None or not glob.glob(os.path.join(model_dir, "*.safetensors")):
+                trainer.init_weights(cfg.train_seed)
+            else:
+                trainer.import_weights(model_dir)
         meta = trainer.load_checkpoint(cfg.checkpoint_dir, latest)
         start_step = meta["run"]["step"]
         if meta.get("data-loader"):
@@ -295,7 +300,7 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
                                                                        "past_norms": norms[-32:]})
                 if info.is_main:
                     clean_old_checkpoints(cfg.checkpoint_dir, cfg.save_total_limit)
-            except OSError as e:  # a failed save must not kill the run
+            except OSError as e:  # a failed save must not kill the run; save_checkpoint raises on every rank together
                 logger.message(f"[checkpoint] save failed: {e}")
         last = out
         if stopper.should_stop(out["loss"], phase):

@@ -66,7 +66,28 @@ def main():
         dist.destroy_process_group()
         return
     if a.get("checkpoint_dir"):
-        tr.save_checkpoint(a["checkpoint_dir"], step=len(losses))
+        fail_rank = a.get("checkpoint_fail_rank")
+        if fail_rank is not None and info.rank == fail_rank:  # this rank's shard cannot be written (a full disk, a lost mount)
+            import surogate_b200.io.checkpoint as ck
+
+            def refuse(*_a, **_k):
+                raise OSError(28, "No space left on device")
+
+            ck.save_file = refuse
+        try:
+            tr.save_checkpoint(a["checkpoint_dir"], step=len(losses))
+            extra["checkpoint"] = "written"
+        except OSError as e:
+            extra["checkpoint"] = type(e).__name__
+        if fail_rank is not None:  # every rank is still on the same collective sequence: one more step must work and agree
+            tok = rng.integers(0, V, (gb, T + 1)).astype(np.int32)
+            sl = slice(info.rank * per_rank, (info.rank + 1) * per_rank)
+            extra["loss_after"] = tr.step(tok[:, :-1][sl], tok[:, 1:][sl])["loss"]
+            flags = [None] * info.world
+            import torch.distributed as dist
+
+            dist.all_gather_object(flags, extra["checkpoint"])
+            extra["checkpoint_all_ranks"] = flags
     if info.rank == 0:
         print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "comm": type(tr.comm).__name__,
                                       "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),

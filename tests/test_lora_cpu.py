@@ -97,3 +97,23 @@ def test_merge_adapter_equals_adapted_forward():
     tr.executor.lora = None
     merged = tr.validate(x, y)["loss"]
     assert abs(adapted - merged) < 1e-5
+
+
+def test_lora_checkpoint_holds_only_the_adapter_and_resumes_with_dropout(tmp_path):
+    """A LoRA checkpoint leaves the frozen base out; a fresh trainer whose base was re-created from the same seed continues the
+    run exactly, including the dropout masks (the generator state is part of the checkpoint)."""
+    from safetensors import safe_open
+
+    x, y = _batch()
+    tr = _trainer(dropout=0.2)
+    for _ in range(3):
+        tr.step(x, y)
+    d = tr.save_checkpoint(str(tmp_path), step=3)
+    with safe_open(os.path.join(d, "weights.shard_000_of_001.safetensors"), framework="pt") as f:
+        assert not [k for k in f.keys() if k != "__empty__"]
+    assert os.path.getsize(os.path.join(d, "weights.shard_000_of_001.safetensors")) < 4096
+    cont = [tr.step(x, y)["loss"] for _ in range(3)]
+    torch.manual_seed(12345)  # a resumed process starts from some other generator state
+    tr2 = _trainer(dropout=0.2)
+    tr2.load_checkpoint(str(tmp_path))
+    assert [tr2.step(x, y)["loss"] for _ in range(3)] == cont

@@ -95,3 +95,31 @@ def test_sft_loop_with_pipeline_stages_checkpoints_and_resumes(tmp_path):
     assert (out / "stage_rank_001" / "step_00000002" / "checkpoint.json").exists()
     r2 = run(dict(base, max_steps=6, save_steps=0, resume_from_checkpoint=True), 29652)
     assert r2["steps"] == 4  # resumed at step 2 of 6
+
+
+@pytest.mark.parametrize("zero", [0, 2])
+def test_lora_gradient_norm_on_two_ranks_equals_the_single_process_norm(zero):
+    """The adapter gradient is all-reduced before the norm: it must be counted once, not once per rank (a norm sqrt(world) too
+    large would over-clip and leave the 1-rank trajectory)."""
+    lora = dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "v_proj", "down_proj"], rslora=False, train_router=False)
+    args = dict(device="cpu", model=TINY, global_batch=4, seq_len=32, steps=4, lora=lora)
+    one = run_worker(1, dict(args, zero=0))
+    two = run_worker(2, dict(args, zero=zero, keep_gathered=True), port=29661 + zero)
+    assert two["world"] == 2
+    for a, b in zip(two["norms"], one["norms"]):
+        assert abs(a - b) < 2e-3 * abs(b), (two["norms"], one["norms"])
+    for a, b in zip(two["losses"], one["losses"]):
+        assert abs(a - b) < 2e-4 * abs(b), (two["losses"], one["losses"])
+
+
+def test_checkpoint_write_failure_on_one_rank_is_abandoned_by_all_ranks(tmp_path):
+    """Rank 1 cannot write its shard: both ranks raise the same error after the same collectives, no checkpoint.json appears, and
+    the next training step still runs with the ranks in agreement."""
+    from surogate_b200.io.checkpoint import find_latest_checkpoint
+
+    r = run_worker(2, dict(device="cpu", model=TINY, global_batch=4, seq_len=32, steps=2, zero=2, checkpoint_dir=str(tmp_path), checkpoint_fail_rank=1), port=29671)
+    assert r["checkpoint_all_ranks"] == ["CheckpointWriteError", "CheckpointWriteError"]
+    assert find_latest_checkpoint(str(tmp_path)) is None
+    assert r["loss_after"] == r["loss_after"] and r["loss_after"] > 0
+    ok = run_worker(2, dict(device="cpu", model=TINY, global_batch=4, seq_len=32, steps=2, zero=2, checkpoint_dir=str(tmp_path)), port=29672)
+    assert ok["checkpoint"] == "written" and find_latest_checkpoint(str(tmp_path)) == 2

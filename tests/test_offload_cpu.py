@@ -116,3 +116,71 @@ def test_one_step_stale_optimizer(tmp_path, zero):
     tr_r.load_checkpoint(str(tmp_path))
     a = tr_o.step(tok[:, :-1], tok[:, 1:])["loss"]
     assert tr_r.step(tok[:, :-1], tok[:, 1:])["loss"] == a == v
+
+
+def test_dropping_a_trainer_with_an_update_in_flight_frees_nothing_the_worker_writes():
+    """The worker owns references to every buffer of its job: a trainer dropped right after a step (one update queued on the worker
+    thread) is collected without the worker touching freed memory, and the worker object reports when it still holds buffers."""
+    import gc
+
+    from surogate_b200.ops import host
+
+    h = host()
+    tok = np.random.default_rng(1).integers(0, 256, (2, 33)).astype(np.int32)
+    for _ in range(6):
+        cfg = TrainerConfig(model=MODEL, batch_size=2, seq_len=32, recipe="bf16", learning_rate=1e-2, zero_level=0, optimizer="adamw", cpu_training=True,
+                            async_optimizer="overlap")
+        tr = Trainer(cfg, device=torch.device("cpu"))
+        tr.init_weights(seed=3)
+        tr.step(tok[:, :-1], tok[:, 1:])
+        worker = tr.optimizer.worker
+        assert worker.holds_buffers
+        del tr
+        gc.collect()
+        junk = [torch.full((100_000,), 7.0) for _ in range(8)]  # recycle the allocator's blocks while the update may still run
+        worker.drain()
+        assert not worker.holds_buffers and all(bool((j == 7.0).all()) for j in junk)
+        del worker
+    # stand-alone: the buffers behind a queued job are dropped by the caller at once and live on inside the worker
+    n = 400_000
+    w = h.AsyncAdamW(True)
+    bufs = [torch.randn(n), torch.zeros(n), torch.zeros(n), torch.randn(n), torch.zeros(n), torch.ones(n, dtype=torch.uint8)]
+    job = [(bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(), False, bufs[4].data_ptr(), False, n, bufs[5].data_ptr())]
+    w.submit(job, 1e-3, 0.9, 0.999, 1e-8, 0.1, 1.0, 1, bufs)
+    del bufs, job
+    gc.collect()
+    del w  # the destructor waits for the update before the references go
+    gc.collect()
+
+
+def test_non_finite_gradient_skips_the_update():
+    """An Inf in the gradient makes the norm non-finite: weights, moments and the adapter stay bit-equal and finite, and the next
+    clean step trains again (fp32 and 8-bit state, CPU optimizer, LoRA)."""
+    tok = np.random.default_rng(1).integers(0, 256, (2, 33)).astype(np.int32)
+    lora = dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "v_proj"], rslora=False, train_router=False)
+    for kw in (dict(optimizer="adamw"), dict(optimizer="adamw_8bit"), dict(optimizer="adamw", cpu_training=True), dict(optimizer="adamw", lora=lora)):
+        cfg = TrainerConfig(model=MODEL, batch_size=2, seq_len=32, recipe="bf16", learning_rate=1e-2, weight_decay=0.1, zero_level=0, **kw)
+        tr = Trainer(cfg, device=torch.device("cpu"))
+        tr.init_weights(seed=3)
+        tr.step(tok[:, :-1], tok[:, 1:])
+
+        def snapshot():
+            out = [b.master.clone() for b in tr.store.buckets.values()]
+            out += [t.clone() for st in tr.optimizer.state.values() for t in st.values()]
+            if tr.lora is not None:
+                out += [tr.lora.master.clone()] + [t.clone() for t in (tr.lora.opt_state or {}).values()]
+            return out
+
+        before = snapshot()
+        tr.forward_backward(tok[:, :-1], tok[:, 1:])
+        if tr.lora is not None:
+            tr.lora.grad[3] = float("inf")
+        else:
+            next(b for b in tr.store.trainable_buckets() if b.grad_shard is not None).grad_shard[5] = float("inf")
+        norm = tr.optimizer_step()
+        assert not bool(torch.isfinite(norm)), kw
+        after = snapshot()
+        assert len(before) == len(after) and all(torch.equal(a, b) and bool(torch.isfinite(b.float()).all()) for a, b in zip(before, after)), kw
+        out = tr.step(tok[:, :-1], tok[:, 1:])
+        assert np.isfinite(out["loss"]) and np.isfinite(out["norm"])
+        assert any(not torch.equal(a, b) for a, b in zip(after, snapshot())), kw
