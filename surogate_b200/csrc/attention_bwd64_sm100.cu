@@ -1,4 +1,4 @@
-// Flash-attention backward, second generation (same math as the kernels in attention_sm100.cu, better overlapped):
+// Flash-attention backward (causal, GQA, head_dim 128; nothing but O and the log-sum-exp is kept from forward, scores are recomputed):
 //
 // One kernel template serves both passes.  A CTA keeps a RESIDENT pair of 128-row tiles and streams 64-row tile pairs through
 // a 3-stage TMA ring; two score accumulators (X = R1 . S1^T, Y = R2 . S2^T) are double-buffered in TMEM so the MMAs of item
@@ -6,6 +6,10 @@
 //   dK/dV pass: resident (K, V) of one 128-key tile of one KV head, streamed (Q, dO) tiles of the G query heads that share it:
 //               X = S^T, Y = dP^T, P^T = exp2(S^T - lse), dS^T = P^T o (dP^T - delta); dV += P^T dO, dK += dS^T Q.
 //   dQ pass   : resident (Q, dO) of one 128-query tile, streamed (K, V) tiles: X = S, Y = dP, dS = P o (dP - delta); dQ += dS K.
+// The GQA reduction of dK / dV happens in the TMEM accumulators (no atomics).  Every mbarrier wait is bounded.
+// Optional per-row lower bound `lo[b, t]` (HAS_LO; packed documents and sliding windows, see attention_fwd64_sm100.cu): the dQ pass
+// starts at key tile lo[first query] / 64; the dK/dV pass stops at `kv_qend[b, key tile]`, the first 64-row query tile in which no
+// query can see the key tile any more (lo is non-decreasing, so that is one number per key tile).
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
@@ -33,6 +37,8 @@ struct Params {
     float scale, scale_log2;
     int* error_flag;
     long long* prof;   // optional [16]: per-phase cycle counters of one softmax thread of each pass (development aid)
+    const int* lo;       // optional [B, T]: first key each query may attend
+    const int* kv_qend;  // with lo: [B, T / 128] exclusive end, in 64-row query tiles, of the queries that attend each 128-key tile
 };
 
 #define FB_PROF(k)                                   \
@@ -122,11 +128,12 @@ __device__ __forceinline__ void mma_acc_k64(uint32_t d_tmem, uint32_t a_rows, ui
 constexpr int RING = 3;
 constexpr int OFF_R2 = T128, OFF_RING = 2 * T128, STAGE = 2 * T64, OFF_PT = OFF_RING + RING * STAGE, OFF_DST = OFF_PT + ROWS128x64,
               OFF_BAR = OFF_DST + ROWS128x64, OFF_VEC = OFF_BAR + 256;
-constexpr int SMEM = OFF_VEC + 2 * 2 * 64 * 4;
+constexpr int OFF_VLO = OFF_VEC + 2 * 2 * 64 * 4;   // per-item lower bounds of the 64 streamed queries (dK/dV pass), double-buffered
+constexpr int SMEM = OFF_VLO + 2 * 64 * 4;
 // barriers: 0 res_full | 1-3 ring_full | 4-6 ring_empty | 7,8 xy_full | 9,10 xy_free | 11 pds_full | 12 pds_empty | 13 done | 14 vec_full
 constexpr int B_RES = 0, B_RFULL = 1, B_REMPTY = 4, B_XY = 7, B_XYFREE = 9, B_PDS = 11, B_PDSE = 12, B_DONE = 13, B_VEC = 14;
 
-template <bool IS_DQ>
+template <bool IS_DQ, bool HAS_LO>
 __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_constant__ CUtensorMap tm_qkv64,
                                                               const __grid_constant__ CUtensorMap tm_do128, const __grid_constant__ CUtensorMap tm_do64,
                                                               const Params p) {
@@ -136,6 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
     uint8_t* pt_tile = smem + OFF_PT;
     uint8_t* dst_tile = smem + OFF_DST;
     float* vec = reinterpret_cast<float*>(smem + OFF_VEC);
+    int* vec_lo = reinterpret_cast<int*>(smem + OFF_VLO);
     auto bar = [&](int i) { return bars + 8u * i; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + 136);
@@ -148,7 +156,11 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
     const int tile = IS_DQ ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
     const int head = blockIdx.y;
     const int hk = IS_DQ ? head / G : head;
-    const int per_head = IS_DQ ? 2 * (tile + 1) : (p.T / 64 - 2 * tile);
+    // streamed 64-row tiles [first_ct, first_ct + per_head): keys from the lower bound of the tile's first query up to the diagonal
+    // (dQ), queries from the diagonal to the last one that can still see this key tile (dK/dV)
+    const int first_ct = IS_DQ ? (HAS_LO ? __ldg(p.lo + row0 + tile * 128) / 64 : 0) : 2 * tile;
+    const int last_ct = IS_DQ ? 2 * (tile + 1) : (HAS_LO ? __ldg(p.kv_qend + b * (p.T / 128) + tile) : p.T / 64);
+    const int per_head = last_ct - first_ct;
     const int n_items = IS_DQ ? per_head : G * per_head;
     const int kcol = (p.Hq + hk) * D, vcol = (p.Hq + p.Hkv + hk) * D;
 
@@ -188,13 +200,13 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
                 mbar_expect_tx(bar(B_RFULL + st), STAGE);
                 const uint32_t d1 = s_ring + st * STAGE, d2 = d1 + T64;
                 if (IS_DQ) {
-                    const int kr = row0 + i * 64;
+                    const int kr = row0 + (first_ct + i) * 64;
                     tma_load_2d(d1, &tm_qkv64, kcol, kr, bar(B_RFULL + st));
                     tma_load_2d(d1 + H64, &tm_qkv64, kcol + 64, kr, bar(B_RFULL + st));
                     tma_load_2d(d2, &tm_qkv64, vcol, kr, bar(B_RFULL + st));
                     tma_load_2d(d2 + H64, &tm_qkv64, vcol + 64, kr, bar(B_RFULL + st));
                 } else {
-                    const int h = hk * G + i / per_head, qr = row0 + (2 * tile + i % per_head) * 64;
+                    const int h = hk * G + i / per_head, qr = row0 + (first_ct + i % per_head) * 64;
                     tma_load_2d(d1, &tm_qkv64, h * D, qr, bar(B_RFULL + st));
                     tma_load_2d(d1 + H64, &tm_qkv64, h * D + 64, qr, bar(B_RFULL + st));
                     tma_load_2d(d2, &tm_do64, h * D, qr, bar(B_RFULL + st));
@@ -245,16 +257,20 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
         const int row_abs = tile * 128 + r;              // key position (dK/dV) or query position (dQ)
         const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
         float row_neg_lse2 = 0.f, row_dl = 0.f;
+        int row_lo = 0;
         if (IS_DQ) {
             const size_t idx = static_cast<size_t>(row0 + row_abs) * p.Hq + head;
             row_neg_lse2 = -p.lse[idx] * LOG2E;
             row_dl = p.delta[idx];
+            if (HAS_LO) row_lo = __ldg(p.lo + row0 + row_abs);
         }
         float pre_lse = 0.f, pre_dl = 0.f;
+        int pre_lo = 0;
         if (!IS_DQ && t < 64 && n_items > 0) {
-            const size_t idx = static_cast<size_t>(row0 + 2 * tile * 64 + t) * p.Hq + hk * G;
+            const size_t idx = static_cast<size_t>(row0 + first_ct * 64 + t) * p.Hq + hk * G;
             pre_lse = p.lse[idx];
             pre_dl = p.delta[idx];
+            if (HAS_LO) pre_lo = __ldg(p.lo + row0 + first_ct * 64 + t);
         }
         bool ok = true;
         const bool do_prof = p.prof != nullptr && threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
@@ -262,18 +278,21 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
         long long t_ = clock64();
         for (int i = 0; i < n_items && ok; ++i) {
             const int xb = i & 1;
-            const int ct = IS_DQ ? i : (2 * tile + i % per_head);     // index of the streamed 64-row tile inside the sequence
+            const int ct = first_ct + (IS_DQ ? i : i % per_head);     // index of the streamed 64-row tile inside the sequence
             const float* neg_lse2 = vec + xb * 128;
             const float* dl = neg_lse2 + 64;
+            const int* q_lo = vec_lo + xb * 64;
             if (!IS_DQ) {
                 if (t < 64) {        // values were fetched one item ahead (pre_lse / pre_dl), so their global-load latency is hidden
                     vec[xb * 128 + t] = -pre_lse * LOG2E;
                     vec[xb * 128 + 64 + t] = pre_dl;
+                    if (HAS_LO) vec_lo[xb * 64 + t] = pre_lo;
                     if (i + 1 < n_items) {
-                        const int h = hk * G + (i + 1) / per_head, nt = 2 * tile + (i + 1) % per_head;
+                        const int h = hk * G + (i + 1) / per_head, nt = first_ct + (i + 1) % per_head;
                         const size_t idx = static_cast<size_t>(row0 + nt * 64 + t) * p.Hq + h;
                         pre_lse = p.lse[idx];
                         pre_dl = p.delta[idx];
+                        if (HAS_LO) pre_lo = __ldg(p.lo + row0 + nt * 64 + t);
                     }
                 }
                 mbar_arrive(bar(B_VEC));
@@ -291,11 +310,13 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
             FB_PROF(2);
             const int c0 = ct * 64 + half * 32;
             // causal mask: a key may not be later than the query.  dK/dV: row = key, column = query; dQ: row = query, column = key.
-            const bool diag = IS_DQ ? (i >= 2 * tile) : (ct < 2 * tile + 2);
+            const bool diag = IS_DQ ? (ct >= 2 * tile) : (ct < 2 * tile + 2);
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 float pr = ex2_approx(fmaf(x[c], p.scale_log2, IS_DQ ? row_neg_lse2 : neg_lse2[half * 32 + c]));
                 if (diag && (IS_DQ ? (c0 + c > row_abs) : (row_abs > c0 + c))) pr = 0.f;
+                // lower bound: a key before the query's first visible key contributes nothing
+                if (HAS_LO && (IS_DQ ? (c0 + c < row_lo) : (row_abs < q_lo[half * 32 + c]))) pr = 0.f;
                 x[c] = pr;
                 y[c] = pr * (y[c] - (IS_DQ ? row_dl : dl[half * 32 + c])) * p.scale;
             }
@@ -334,7 +355,7 @@ __global__ void __launch_bounds__(THREADS, 1) fa_bwd64_kernel(const __grid_const
 }  // namespace fb64
 
 const char* flash_attn_bwd64_sm100(const void* qkv, const void* d_out, const float* lse, const float* delta, void* d_qkv, int B, int T, int Hq, int Hkv,
-                                   float softmax_scale, int* error_flag, cudaStream_t stream, long long* prof) {
+                                   float softmax_scale, int* error_flag, cudaStream_t stream, long long* prof, const int* lo, const int* kv_qend) {
     using namespace fb64;
     if (T % 128 != 0) return "flash_attn_bwd: T must be a multiple of 128";
     CUtensorMap q128, q64, do128, do64;
@@ -346,15 +367,53 @@ const char* flash_attn_bwd64_sm100(const void* qkv, const void* d_out, const flo
     if ((e = make_tensor_map_2d(&do64, d_out, 2, owidth, rows, owidth * 2, 64, 64))) return e;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(fa_bwd64_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(fa_bwd64_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(fa_bwd64_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(fa_bwd64_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(fa_bwd64_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(fa_bwd64_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return "cudaFuncSetAttribute failed (flash_attn_bwd64)";
         attr_set = true;
     }
-    Params p{static_cast<__nv_bfloat16*>(d_qkv), lse, delta, T, Hq, Hkv, softmax_scale, softmax_scale * LOG2E, error_flag, prof};
-    fa_bwd64_kernel<false><<<dim3(T / 128, Hkv, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
-    fa_bwd64_kernel<true><<<dim3(T / 128, Hq, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
+    if ((lo == nullptr) != (kv_qend == nullptr)) return "flash_attn_bwd: the lower bounds and the per-key-tile query ends come together";
+    Params p{static_cast<__nv_bfloat16*>(d_qkv), lse, delta, T, Hq, Hkv, softmax_scale, softmax_scale * LOG2E, error_flag, prof, lo, kv_qend};
+    if (lo) {
+        fa_bwd64_kernel<false, true><<<dim3(T / 128, Hkv, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
+        fa_bwd64_kernel<true, true><<<dim3(T / 128, Hq, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
+    } else {
+        fa_bwd64_kernel<false, false><<<dim3(T / 128, Hkv, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
+        fa_bwd64_kernel<true, false><<<dim3(T / 128, Hq, B), THREADS, SMEM, stream>>>(q128, q64, do128, do64, p);
+    }
     return cudaGetLastError() == cudaSuccess ? nullptr : "flash_attn_bwd64 launch failed";
+}
+
+// delta[b, t, h] = sum_d dO * O   (one warp per (token, head))
+__global__ void __launch_bounds__(256) fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                                       size_t items) {
+    const int lane = threadIdx.x & 31;
+    for (size_t it = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += static_cast<size_t>(gridDim.x) * (blockDim.x >> 5)) {
+        const uint2 a = *reinterpret_cast<const uint2*>(o + it * 128 + lane * 4), g = *reinterpret_cast<const uint2*>(d_o + it * 128 + lane * 4);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pg = reinterpret_cast<const __nv_bfloat162*>(&g);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pg[i]);
+            s += x.x * y.x + x.y * y.y;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) delta[it] = s;
+    }
+}
+
+const char* flash_attn_bwd_sm100(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta, void* d_qkv, int B, int T, int Hq,
+                                 int Hkv, float softmax_scale, int* error_flag, int num_sms, cudaStream_t stream, const int* lo, const int* kv_qend) {
+    if (T % 128 != 0) return "flash_attn_bwd: T must be a multiple of 128";
+    const size_t items = static_cast<size_t>(B) * T * Hq;
+    int grid = static_cast<int>((items + 7) / 8);
+    if (grid > num_sms * 8) grid = num_sms * 8;
+    fa_delta_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, items);
+    return flash_attn_bwd64_sm100(qkv, d_out, lse, delta, d_qkv, B, T, Hq, Hkv, softmax_scale, error_flag, stream, nullptr, lo, kv_qend);
 }
 
 }  // namespace sg

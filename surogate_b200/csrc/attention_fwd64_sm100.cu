@@ -1,7 +1,16 @@
 // Flash-attention forward, second generation: 128 queries x 64 keys per step, sized so that TWO CTAs fit on one SM
 // (112 KB shared memory and 256 TMEM columns each).  While one CTA's softmax warps work on their scores, the other CTA's
 // MMAs keep the tensor core busy; the same overlap a two-tile ping-pong gives, obtained from the hardware scheduler.
-// Same math and interfaces as fa_fwd_kernel in attention_sm100.cu (causal, GQA, head_dim 128, packed QKV read by TMA).
+// Causal, GQA, head_dim 128, packed QKV [B, T, (Hq + 2 Hkv) * 128] read by TMA.
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles through two 2-deep rings
+//   warp 1      MMA issuer:   S_j = Q K_j^T into one of two TMEM score buffers, then O += P_j V_j (V read MN-major)
+//   warps 2-5   softmax:      thread r owns query row r: reads S_j from TMEM, online softmax in base 2, writes P_j (bf16) to shared
+//                             memory in the swizzled K-major layout the second MMA reads; the running output in TMEM is rescaled
+//                             only when a row maximum grew by more than 2^8 (exact, but rare)
+// Optional per-row LOWER BOUND `lo[b, t]` (HAS_LO): query t attends keys lo[t] <= k <= t.  One array covers packed documents
+// (lo = first position of the query's document), sliding windows (lo = t - window + 1) and both at once (the maximum).  `lo` must be
+// non-decreasing along a sequence, so a query tile starts at key tile lo[first row] / 64 and key tiles before it are never loaded.
+// Replaces the varlen FlashAttention call of the reference (csrc/src/runtime/attention/backend_flash_varlen.cpp:41-63).
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
@@ -32,6 +41,7 @@ struct Params {
     float scale_log2;
     int* error_flag;
     long long* prof;      // optional [8] cycle counters of one softmax thread (development aid; nullptr in production)
+    const int* lo;        // optional [B, T] first key each query may attend (position inside its sequence)
 };
 
 #define FA_PROF(k)                                   \
@@ -43,6 +53,7 @@ struct Params {
         }                                            \
     } while (0)
 
+template <bool HAS_LO>
 __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                                                               const Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -60,8 +71,10 @@ __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_const
     const int q_blk = gridDim.x - 1 - blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
-    const int n_kv = 2 * (q_blk + 1);
     const int row0 = b * p.T;
+    // key tiles [j0, j0 + n_kv) are visited; without a lower bound that is everything up to the diagonal
+    const int j0 = HAS_LO ? __ldg(p.lo + row0 + q_blk * BQ) / BKV : 0;
+    const int n_kv = 2 * (q_blk + 1) - j0;
 
     if (threadIdx.x == 0) {
         *abort_flag = (s0 & 1023u) ? 1 : 0;      // the swizzled tiles need a 1024-byte aligned base
@@ -96,16 +109,16 @@ __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_const
                     if (!mbar_wait(bar(3 + st), ((j >> 1) & 1) ^ 1u, abort_flag)) break;
                     const uint32_t k_dst = s_kv + st * 2 * KV_TILE;
                     mbar_expect_tx(bar(1 + st), KV_TILE);
-                    tma_load_2d(k_dst, &tm_kv, kc, row0 + j * BKV, bar(1 + st));
-                    tma_load_2d(k_dst + KV_HALF, &tm_kv, kc + 64, row0 + j * BKV, bar(1 + st));
+                    tma_load_2d(k_dst, &tm_kv, kc, row0 + (j0 + j) * BKV, bar(1 + st));
+                    tma_load_2d(k_dst + KV_HALF, &tm_kv, kc + 64, row0 + (j0 + j) * BKV, bar(1 + st));
                 }
                 if (j >= 1) {
                     const int i = j - 1, st = i & 1;
                     if (!mbar_wait(bar(14 + st), ((i >> 1) & 1) ^ 1u, abort_flag)) break;
                     const uint32_t v_dst = s_kv + st * 2 * KV_TILE + KV_TILE;
                     mbar_expect_tx(bar(12 + st), KV_TILE);
-                    tma_load_2d(v_dst, &tm_kv, vc, row0 + i * BKV, bar(12 + st));
-                    tma_load_2d(v_dst + KV_HALF, &tm_kv, vc + 64, row0 + i * BKV, bar(12 + st));
+                    tma_load_2d(v_dst, &tm_kv, vc, row0 + (j0 + i) * BKV, bar(12 + st));
+                    tma_load_2d(v_dst + KV_HALF, &tm_kv, vc + 64, row0 + (j0 + i) * BKV, bar(12 + st));
                 }
             }
         }
@@ -163,7 +176,9 @@ __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_const
         const int r = quad * 32 + lane;
         const int q_abs = q_blk * BQ + r;            // query position inside the sequence
         const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
-        float m_used = -CUDART_INF_F, l = 0.f;
+        // a finite floor instead of -inf: a row whose first visited key tile is entirely masked keeps exp2(s - m) = 0 instead of NaN
+        float m_used = -1e30f, l = 0.f;
+        const int lo_row = HAS_LO ? __ldg(p.lo + row0 + q_abs) : 0;
         bool ok = true;
         const bool do_prof = p.prof != nullptr && threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         long long acc_[6] = {0, 0, 0, 0, 0, 0};
@@ -185,18 +200,24 @@ __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_const
             tc_fence_before();
             mbar_arrive(bar(7 + st));
             FA_PROF(1);
-            if (j >= 2 * q_blk) {                      // the two key tiles that straddle the diagonal
-                const int k0 = j * BKV;
+            const int k0 = (j0 + j) * BKV;
+            if (j0 + j >= 2 * q_blk) {                 // the two key tiles that straddle the diagonal
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
                     if (k0 + i > q_abs) s[i] = -CUDART_INF_F;
+            }
+            if (HAS_LO && k0 < lo_row) {               // keys before the row's lower bound (another document / outside the window)
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (k0 + i < lo_row) s[i] = -CUDART_INF_F;
             }
             // four independent chains instead of one 64-long dependent chain (one warp per scheduler has no other work to hide latency)
             float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
             for (int i = 4; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], s[i]);
             const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
-            // a fully masked row (second diagonal tile, upper half of the rows) has m_blk = -inf: nothing to add, keep m_used
+            // a fully masked row (second diagonal tile, upper half of the rows; tiles before the row's lower bound) has m_blk = -inf:
+            // nothing to add, keep m_used
             const bool grow = m_blk > m_used + RESCALE_THRESHOLD;
             FA_PROF(2);
             if (j > 0) {
@@ -278,7 +299,7 @@ __global__ void __launch_bounds__(THREADS, 2) fa_fwd64_kernel(const __grid_const
 }  // namespace fa64
 
 const char* flash_attn_fwd64_sm100(const void* qkv, void* out, float* lse, int B, int T, int Hq, int Hkv, float softmax_scale, int* error_flag,
-                                   cudaStream_t stream, long long* prof) {
+                                   cudaStream_t stream, long long* prof, const int* lo) {
     using namespace fa64;
     if (T % 128 != 0) return "flash_attn_fwd: T must be a multiple of 128";
     if (Hq % Hkv != 0) return "flash_attn_fwd: Hq must be a multiple of Hkv";
@@ -290,12 +311,14 @@ const char* flash_attn_fwd64_sm100(const void* qkv, void* out, float* lse, int B
     if (e) return e;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(fa_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(fa_fwd64_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(fa_fwd64_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
             return "cudaFuncSetAttribute failed (flash_attn_fwd64)";
         attr_set = true;
     }
-    Params p{static_cast<__nv_bfloat16*>(out), lse, T, Hq, Hkv, softmax_scale * 1.4426950408889634f, error_flag, prof};
-    fa_fwd64_kernel<<<dim3(T / 128, Hq, B), THREADS, SMEM_BYTES, stream>>>(tm_q, tm_kv, p);
+    Params p{static_cast<__nv_bfloat16*>(out), lse, T, Hq, Hkv, softmax_scale * 1.4426950408889634f, error_flag, prof, lo};
+    if (lo) fa_fwd64_kernel<true><<<dim3(T / 128, Hq, B), THREADS, SMEM_BYTES, stream>>>(tm_q, tm_kv, p);
+    else fa_fwd64_kernel<false><<<dim3(T / 128, Hq, B), THREADS, SMEM_BYTES, stream>>>(tm_q, tm_kv, p);
     return cudaGetLastError() == cudaSuccess ? nullptr : "flash_attn_fwd64 launch failed";
 }
 

@@ -339,7 +339,16 @@ void gemm_nvfp4(const Tensor& a, const Tensor& sfa, const Tensor& b, const Tenso
 }
 
 // ---------------------------------------------------------------------------------------- attention
-std::vector<Tensor> flash_attn_fwd(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale, Tensor& error_flag) {
+// `lo` (optional int32 [B, T]): first key each query may attend; see attention_fwd64_sm100.cu
+static const int* lo_ptr(const c10::optional<Tensor>& lo, const Tensor& qkv) {
+    if (!lo.has_value() || !lo->defined()) return nullptr;
+    TORCH_CHECK(lo->is_cuda() && lo->scalar_type() == at::kInt && lo->is_contiguous() && lo->dim() == 2 && lo->size(0) == qkv.size(0) &&
+                    lo->size(1) == qkv.size(1),
+                "attention lower bounds: int32 [B, T] on the device");
+    return lo->data_ptr<int>();
+}
+
+std::vector<Tensor> flash_attn_fwd(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale, const c10::optional<Tensor>& lo) {
     TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.is_contiguous() && qkv.dim() == 3, "qkv: bf16 [B, T, (Hq+2Hkv)*128]");
     const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
     TORCH_CHECK(qkv.size(2) == (Hq + 2 * Hkv) * 128, "flash_attn: head_dim must be 128");
@@ -347,11 +356,8 @@ std::vector<Tensor> flash_attn_fwd(const Tensor& qkv, int64_t Hq, int64_t Hkv, d
     Tensor out = torch::empty({B, T, Hq * 128}, qkv.options());
     Tensor lse = torch::empty({B, T, Hq}, qkv.options().dtype(at::kFloat));
     sg_count_launch(1);
-    static const bool use_v1 = []() { const char* v = std::getenv("SUROGATE_ATTN_FWD"); return v && std::string(v) == "128"; }();
-    const char* err = use_v1 ? sg::flash_attn_fwd_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq),
-                                                        static_cast<int>(Hkv), static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream())
-                             : sg::flash_attn_fwd64_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq),
-                                                          static_cast<int>(Hkv), static_cast<float>(scale), error_flag.data_ptr<int>(), cur_stream());
+    const char* err = sg::flash_attn_fwd64_sm100(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv),
+                                                 static_cast<float>(scale), sg_error_flag(), cur_stream(), nullptr, lo_ptr(lo, qkv));
     TORCH_CHECK(err == nullptr, err ? err : "");
     return {out, lse};
 }
@@ -379,24 +385,28 @@ Tensor flash_attn_bwd_profile(const Tensor& d_out, const Tensor& qkv, const Tens
     return prof;
 }
 
-std::vector<Tensor> flash_attn_fwd2(const Tensor& qkv, int64_t Hq, int64_t Hkv, double scale) {
-    Tensor flag = torch::from_blob(sg_error_flag(), {1}, torch::TensorOptions().dtype(at::kInt).device(qkv.device()));
-    return flash_attn_fwd(qkv, Hq, Hkv, scale, flag);
-}
-
-// d_out [B, T, Hq*128], qkv packed, out [B, T, Hq*128], lse [B, T, Hq] -> d_qkv (packed layout)
-Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out, const Tensor& lse, int64_t Hq, int64_t Hkv, double scale) {
+// d_out [B, T, Hq*128], qkv packed, out [B, T, Hq*128], lse [B, T, Hq] -> d_qkv (packed layout).  With `lo`, `kv_qend` (int32
+// [B, T/128]) is the exclusive end, in 64-row query tiles, of the queries that attend each 128-key tile.
+Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out, const Tensor& lse, int64_t Hq, int64_t Hkv, double scale,
+                      const c10::optional<Tensor>& lo, const c10::optional<Tensor>& kv_qend) {
     TORCH_CHECK(d_out.is_cuda() && d_out.scalar_type() == at::kBFloat16 && d_out.is_contiguous() && out.is_contiguous() && qkv.is_contiguous(), "bf16 contiguous");
     TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse: fp32 contiguous");
     const int B = static_cast<int>(qkv.size(0)), T = static_cast<int>(qkv.size(1));
     const c10::cuda::CUDAGuard guard(qkv.device());
-    static const int bwd_variant = []() { const char* v = std::getenv("SUROGATE_ATTN_BWD"); return (v && std::string(v) == "128") ? 128 : 64; }();
+    const int* lo_p = lo_ptr(lo, qkv);
+    const int* qend_p = nullptr;
+    if (lo_p) {
+        TORCH_CHECK(kv_qend.has_value() && kv_qend->is_cuda() && kv_qend->scalar_type() == at::kInt && kv_qend->is_contiguous() &&
+                        kv_qend->numel() == static_cast<int64_t>(B) * (T / 128),
+                    "attention backward with lower bounds needs kv_qend: int32 [B, T/128]");
+        qend_p = kv_qend->data_ptr<int>();
+    }
     Tensor d_qkv = torch::empty_like(qkv);
     Tensor delta = torch::empty_like(lse);
     sg_count_launch(3);
     const char* err = sg::flash_attn_bwd_sm100(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
                                                d_qkv.data_ptr(), B, T, static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<float>(scale),
-                                               sg_error_flag(), sms(), cur_stream(), bwd_variant);
+                                               sg_error_flag(), sms(), cur_stream(), lo_p, qend_p);
     TORCH_CHECK(err == nullptr, err ? err : "");
     return d_qkv;
 }
@@ -420,9 +430,10 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("nvfp4_quantize_transpose", &nvfp4_quantize_transpose);
     m.def("nvfp4_dequantize", &nvfp4_dequantize);
     m.def("gemm_nvfp4", &gemm_nvfp4);
-    m.def("flash_attn_fwd_raw", &flash_attn_fwd);
-    m.def("flash_attn_fwd", &flash_attn_fwd2);
-    m.def("flash_attn_bwd", &flash_attn_bwd);
+    m.def("flash_attn_fwd", &flash_attn_fwd, pybind11::arg("qkv"), pybind11::arg("Hq"), pybind11::arg("Hkv"), pybind11::arg("scale"),
+          pybind11::arg("lo") = c10::optional<Tensor>());
+    m.def("flash_attn_bwd", &flash_attn_bwd, pybind11::arg("d_out"), pybind11::arg("qkv"), pybind11::arg("out"), pybind11::arg("lse"), pybind11::arg("Hq"),
+          pybind11::arg("Hkv"), pybind11::arg("scale"), pybind11::arg("lo") = c10::optional<Tensor>(), pybind11::arg("kv_qend") = c10::optional<Tensor>());
     m.def("flash_attn_bwd_profile", &flash_attn_bwd_profile, "per-phase cycle counters of the backward passes (development aid)");
     m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
     m.def("ep_plan", &ep_plan);

@@ -109,6 +109,58 @@ __device__ __forceinline__ TileInfo get_tile(const GemmParams& p, const int* til
     return t;
 }
 
+// 32 accumulator columns of one output row, straight from registers: 16-byte stores, optional D += and running abs-max.
+__device__ __forceinline__ void store_direct_32(const GemmParams& p, const TileInfo& t, int row, int col0, const uint32_t (&r)[32], float scale,
+                                                float& amax) {
+    if (row >= t.m_end || col0 >= t.n_end) return;
+    if (p.out_fp32) {
+        float* drow = reinterpret_cast<float*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 < t.n_end) {
+                float4 v = make_float4(__uint_as_float(r[g * 4]) * scale, __uint_as_float(r[g * 4 + 1]) * scale, __uint_as_float(r[g * 4 + 2]) * scale,
+                                       __uint_as_float(r[g * 4 + 3]) * scale);
+                float4* dst = reinterpret_cast<float4*>(drow + g * 4);
+                if (p.accumulate) {
+                    const float4 o = *dst;
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                *dst = v;
+            }
+        }
+    } else {
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 < t.n_end) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * scale;
+                uint4* dst = reinterpret_cast<uint4*>(drow + g * 8);
+                if (p.accumulate) {
+                    const uint4 o = *dst;
+                    const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(ob[i]);
+                        v[2 * i] += f.x;
+                        v[2 * i + 1] += f.y;
+                    }
+                }
+                uint4 out;
+                __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    pb[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+                }
+                *dst = out;
+            }
+        }
+    }
+}
+
 constexpr int MAX_GROUPS = 256;
 
 template <int BN>
@@ -265,55 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 uint32_t r[32];
                 tmem_ld_32x32(t_row + c, r);
                 tmem_ld_wait();
-                const int col0 = t.d_col0 + c;
-                if (row < t.m_end && col0 < t.n_end) {
-                    if (p.out_fp32) {
-                        float* drow = reinterpret_cast<float*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
-#pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            if (col0 + g * 4 < t.n_end) {
-                                float4 v = make_float4(__uint_as_float(r[g * 4]) * scale, __uint_as_float(r[g * 4 + 1]) * scale,
-                                                       __uint_as_float(r[g * 4 + 2]) * scale, __uint_as_float(r[g * 4 + 3]) * scale);
-                                float4* dst = reinterpret_cast<float4*>(drow + g * 4);
-                                if (p.accumulate) {
-                                    const float4 o = *dst;
-                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                                }
-                                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                                *dst = v;
-                            }
-                        }
-                    } else {
-                        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + t.d_off + static_cast<size_t>(row) * p.ldd + col0;
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (col0 + g * 8 < t.n_end) {
-                                float v[8];
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * scale;
-                                uint4* dst = reinterpret_cast<uint4*>(drow + g * 8);
-                                if (p.accumulate) {
-                                    const uint4 o = *dst;
-                                    const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        const float2 f = __bfloat1622float2(ob[i]);
-                                        v[2 * i] += f.x;
-                                        v[2 * i + 1] += f.y;
-                                    }
-                                }
-                                uint4 out;
-                                __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    pb[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                                    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
-                                }
-                                *dst = out;
-                            }
-                        }
-                    }
-                }
+                store_direct_32(p, t, row, t.d_col0 + c, r, scale, amax);
             }
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
@@ -331,6 +335,258 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ CTA-pair kernel
+// 256 x 256 output tile per CLUSTER of two CTAs (tcgen05 cta_group::2).  Each CTA stages its own 128 rows of A and its own 128 of
+// the tile's 256 B rows (16 KB + 16 KB per stage instead of 16 + 32 for the single-CTA 128 x 256 tile, so six stages fit and every
+// byte of B is read from shared memory by one SM, not two); the leader CTA's MMA thread issues M = 256, N = 256 instructions that
+// fill 128 TMEM lanes x 256 columns in both CTAs.  Loads are per-CTA TMA copies (no cluster broadcast) that complete on the
+// leader's barrier; the MMA completion is committed to both CTAs' barriers.  The epilogue leaves through shared memory: every
+// warp packs its 32 rows x 128 bytes into a swizzled staging tile and one lane issues a TMA store (or a TMA add for fp32
+// accumulation), so global writes are whole 128-byte lines and the tensor map clips the edges.  bf16 accumulation and the
+// running abs-max of accumulated outputs keep the register path.  Dense problems only (mode 0).
+constexpr int PAIR_BM = 256, PAIR_BN = 256;
+constexpr int PAIR_B_BYTES = 128 * TILE_K_BYTES;                 // this CTA's half of the B tile
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;   // 32 KB
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_EPI_WARP_BYTES = 2 * 4096;                    // two 32-row x 128-byte staging tiles per epilogue warp
+constexpr int PAIR_EPI_BYTES = 4 * PAIR_EPI_WARP_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct PairTile {
+    int m0, n0;   // origin of the 256 x 256 tile
+};
+__device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int tile) {
+    const int num_m = (p.M + PAIR_BM - 1) / PAIR_BM, num_n = (p.N + PAIR_BN - 1) / PAIR_BN;
+    const int per_group = GROUP_M * num_n;
+    const int group = tile / per_group;
+    const int first_m = group * GROUP_M;
+    const int gsize = min(num_m - first_m, GROUP_M);
+    const int r = tile - group * per_group;
+    return PairTile{(first_m + r % gsize) * PAIR_BM, (r / gsize) * PAIR_BN};
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
+                 const GemmParams p, const int use_tma_store) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // same offset in both CTAs: the MMA applies one descriptor to both
+    const uint32_t epi_base = smem_base + PAIR_STAGES * PAIR_STAGE_BYTES;
+    const uint32_t bar_base = epi_base + PAIR_EPI_BYTES;
+    // barriers (8 B each): full[STAGES] (used in the leader), empty[STAGES], tmem_full[2], tmem_empty[2] (used in the leader)
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (PAIR_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * PAIR_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * PAIR_STAGES + 2 + a); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int BK = TILE_K_BYTES / p.elem_bytes;
+    const int num_tiles = ((p.M + PAIR_BM - 1) / PAIR_BM) * ((p.N + PAIR_BN - 1) / PAIR_BN);
+    const int num_k = (p.K + BK - 1) / BK;
+    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);      // one lane of each epilogue warp of both CTAs
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        if (use_tma_store) tma_prefetch_desc(&tmD);
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(smem_u32(&tmem_base_slot), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();     // both CTAs' barriers are initialised before either CTA signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (one per CTA)
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            const int a_chunks = p.a_mn ? (BM * p.elem_bytes) / TILE_K_BYTES : 1;
+            const int b_chunks = p.b_mn ? (128 * p.elem_bytes) / TILE_K_BYTES : 1;
+            const int chunk_bytes = BK * TILE_K_BYTES;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                const PairTile t = pair_tile(p, tile);
+                const int m0 = t.m0 + static_cast<int>(rank) * 128, n0 = t.n0 + static_cast<int>(rank) * 128;
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const uint32_t bar = mapa_shared(full_bar(stage), 0);                 // the leader's barrier counts both CTAs' bytes
+                    if (leader) mbar_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d_pair(sa, &tmA, k0, m0, bar);
+                    } else {
+                        for (int c = 0; c < a_chunks; ++c) tma_load_2d_pair(sa + c * chunk_bytes, &tmA, m0 + c * BK, k0, bar);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d_pair(sb, &tmB, k0, n0, bar);
+                    } else {
+                        for (int c = 0; c < b_chunks; ++c) tma_load_2d_pair(sb + c * chunk_bytes, &tmB, n0 + c * BK, k0, bar);
+                    }
+                    if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (leader && elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int local_tile = 0;
+            const uint32_t idesc = make_idesc(p.a_fmt, p.b_fmt, p.a_mn, p.b_mn, PAIR_BM, PAIR_BN);
+            const uint32_t lbo = BK * TILE_K_BYTES;
+            const uint32_t a_kstep = p.a_mn ? (BK / 4) * TILE_K_BYTES : 32;
+            const uint32_t b_kstep = p.b_mn ? (BK / 4) * TILE_K_BYTES : 32;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+                const int acc = local_tile & 1;
+                if (!mbar_wait_cluster(tempty_bar(acc), acc_phase[acc] ^ 1u, &abort_flag)) { ok = false; break; }
+                acc_phase[acc] ^= 1u;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait_cluster(full_bar(stage), phase, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = make_smem_desc(sa + j * a_kstep, p.a_mn ? lbo : 16, 1024);
+                        const uint64_t db = make_smem_desc(sb + j * b_kstep, p.b_mn ? lbo : 16, 1024);
+                        const uint32_t accum = (kb > 0 || j > 0) ? 1u : 0u;
+                        if (p.elem_bytes == 2) mma_f16_pair(d_tmem, da, db, idesc, accum);
+                        else mma_f8_pair(d_tmem, da, db, idesc, accum);
+                    }
+                    tc_commit_pair(empty_bar(stage), 3);   // both CTAs' stage is free once these MMAs have read it
+                    if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit_pair(tfull_bar(acc), 3);  // both CTAs' halves of the accumulator are complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs; each CTA drains its own 128 rows)
+        const int quad = warp & 3;
+        uint32_t acc_phase[2] = {0, 0};
+        int local_tile = 0;
+        float scale = p.alpha;
+        if (p.scale_a) scale *= __ldg(p.scale_a);
+        if (p.scale_b) scale *= __ldg(p.scale_b);
+        float amax = 0.f;
+        bool ok = true;
+        const uint32_t tempty_leader[2] = {mapa_shared(tempty_bar(0), 0), mapa_shared(tempty_bar(1), 0)};
+        const uint32_t stage_smem = epi_base + quad * PAIR_EPI_WARP_BYTES;
+        uint8_t* stage_ptr = smem_raw + (stage_smem - smem_u32(smem_raw));
+        int buf = 0, stores_in_flight = 0;
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+            const PairTile pt = pair_tile(p, tile);
+            const int acc = local_tile & 1;
+            if (!mbar_wait(tfull_bar(acc), acc_phase[acc], &abort_flag)) { ok = false; break; }
+            acc_phase[acc] ^= 1u;
+            tc_fence_after();
+            const int row_w = pt.m0 + static_cast<int>(rank) * 128 + quad * 32;   // first row of this warp
+            const uint32_t t_row = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
+            if (use_tma_store) {
+                const int cols_per_store = p.out_fp32 ? 32 : 64;
+                if (row_w < p.M) {
+#pragma unroll 1
+                    for (int c = 0; c < PAIR_BN && pt.n0 + c < p.N; c += cols_per_store) {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld_32x32(t_row + c, r0);
+                        if (!p.out_fp32) tmem_ld_32x32(t_row + c + 32, r1);
+                        if (stores_in_flight >= 2) {      // the store that last read this staging tile has finished reading it
+                            if (lane == 0) tma_store_wait_read<1>();
+                            __syncwarp();
+                        }
+                        tmem_ld_wait();
+                        uint8_t* srow = stage_ptr + buf * 4096 + lane * 128;
+                        if (p.out_fp32) {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const float4 v = make_float4(__uint_as_float(r0[u * 4]) * scale, __uint_as_float(r0[u * 4 + 1]) * scale,
+                                                             __uint_as_float(r0[u * 4 + 2]) * scale, __uint_as_float(r0[u * 4 + 3]) * scale);
+                                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                                *reinterpret_cast<float4*>(srow + ((u ^ (lane & 7)) << 4)) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                uint4 o;
+                                __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int e = (u & 3) * 8 + 2 * i;
+                                    const float a = __uint_as_float(u < 4 ? r0[e] : r1[e]) * scale, b = __uint_as_float(u < 4 ? r0[e + 1] : r1[e + 1]) * scale;
+                                    amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+                                    pb[i] = __floats2bfloat162_rn(a, b);
+                                }
+                                *reinterpret_cast<uint4*>(srow + ((u ^ (lane & 7)) << 4)) = o;
+                            }
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (p.accumulate) tma_reduce_add_2d(&tmD, stage_smem + buf * 4096, pt.n0 + c, row_w);
+                            else tma_store_2d(&tmD, stage_smem + buf * 4096, pt.n0 + c, row_w);
+                            tma_store_commit();
+                        }
+                        ++stores_in_flight;
+                        buf ^= 1;
+                    }
+                }
+            } else {
+                TileInfo t;
+                t.m_end = p.M;
+                t.n_end = p.N;
+                t.d_off = 0;
+                const int row = row_w + lane;
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + c, r);
+                    tmem_ld_wait();
+                    store_direct_32(p, t, row, pt.n0 + c, r, scale, amax);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
+        }
+        if (use_tma_store && lane == 0) tma_store_wait_all();
+        if (p.amax_out) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0 && amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax_out), __float_as_uint(amax));
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();   // neither CTA leaves (or frees TMEM) while the other may still signal its barriers or read its shared memory
+    if (threadIdx.x == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, 1);
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -360,7 +616,7 @@ const char* make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_byte
     cuuint64_t strides[1] = {row_stride_bytes};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
     CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
@@ -393,11 +649,46 @@ template <int BN> static const char* launch(const GemmOperand& A, const GemmOper
     return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }
 
+static const char* launch_pair(const GemmOperand& A, const GemmOperand& B, const GemmParams& p, int num_sms, cudaStream_t stream) {
+    const int BK = TILE_K_BYTES / p.elem_bytes;
+    CUtensorMap tmA, tmB, tmD;
+    const char* e;
+    if (!p.a_mn) e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.K, p.M, A.row_stride_bytes, BK, BM);
+    else e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.M, p.K, A.row_stride_bytes, BK, BK);
+    if (e) return e;
+    if (!p.b_mn) e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.K, p.N, B.row_stride_bytes, BK, 128);
+    else e = make_tensor_map_2d(&tmB, B.ptr, p.elem_bytes, p.N, p.K, B.row_stride_bytes, BK, BK);
+    if (e) return e;
+    // The shared-memory epilogue serves plain stores and fp32 accumulation (TMA add).  bf16 accumulation (D is read, summed in
+    // fp32 and rounded once) and an abs-max that must include the accumulated values stay on the register path.
+    const int d_bytes = p.out_fp32 ? 4 : 2;
+    int use_tma_store = (!p.accumulate || (p.out_fp32 && !p.amax_out)) && (static_cast<uint64_t>(p.ldd) * d_bytes) % 16 == 0;
+    if (use_tma_store) {
+        e = make_tensor_map_2d(&tmD, p.D, d_bytes, p.N, p.M, static_cast<uint64_t>(p.ldd) * d_bytes, 128 / d_bytes, 32);
+        if (e) use_tma_store = 0;
+    }
+    if (!use_tma_store) tmD = tmA;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess)
+            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed (pair GEMM)";
+        attr_set = true;
+    }
+    const int num_tiles = ((p.M + PAIR_BM - 1) / PAIR_BM) * ((p.N + PAIR_BN - 1) / PAIR_BN);
+    const int clusters = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
+    gemm_pair_kernel<<<2 * clusters, GEMM_THREADS, PAIR_SMEM_BYTES, stream>>>(tmA, tmB, tmD, p, use_tma_store);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "pair gemm kernel launch failed";
+}
+
 const char* gemm_sm100(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream) {
     if (p.M <= 0 || p.N <= 0 || p.K <= 0) return nullptr;
     if (p.mode != 0 && (p.num_groups <= 0 || p.num_groups > MAX_GROUPS || !p.group_offsets)) return "gemm_sm100: grouped mode needs 1..256 groups and offsets";
     if (p.N % 8 != 0 || p.ldd % 8 != 0) return "gemm_sm100: N and ldd must be multiples of 8";
     if ((reinterpret_cast<uintptr_t>(p.D) & 15) != 0) return "gemm_sm100: D must be 16-byte aligned";
+    // CTA pairs (256 x 256 per cluster) for dense problems with at least one tile per cluster; tile_n = 512 forces them, 128 / 256
+    // force the single-CTA kernels
+    const long tiles_pair = static_cast<long>((p.M + PAIR_BM - 1) / PAIR_BM) * ((p.N + PAIR_BN - 1) / PAIR_BN);
+    if (p.mode == 0 && (p.tile_n == 512 || (p.tile_n == 0 && tiles_pair >= num_sms / 2))) return launch_pair(A, B, p, num_sms, stream);
     // 128-wide N tiles when the wide tile would leave SMs idle or N is small
     const long tiles256 = static_cast<long>((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
     const bool narrow = p.N <= 128 || (p.tile_n == 128) || (p.tile_n == 0 && tiles256 < num_sms);

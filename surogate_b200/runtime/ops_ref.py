@@ -451,8 +451,14 @@ class RefOps:
             qh = q.transpose(1, 2).detach().requires_grad_(ctx.training)
             kh = k.transpose(1, 2).detach().requires_grad_(ctx.training)
             vh = v.transpose(1, 2).detach().requires_grad_(ctx.training)
-            o = TF.scaled_dot_product_attention(qh, kh, vh, is_causal=a.get("causal", True), scale=scale,
-                                                enable_gqa=a["num_q_heads"] != a["num_kv_heads"])
+            if ctx.doc_ids is not None or a.get("window", 0):
+                # packed documents / sliding window: an explicit boolean mask (True = attend), never the plain causal shortcut
+                allowed = self._mask(T, a, q.device, ctx.doc_ids) == 0
+                allowed = allowed if allowed.dim() == 4 else allowed[None, None]
+                o = TF.scaled_dot_product_attention(qh, kh, vh, attn_mask=allowed, scale=scale, enable_gqa=a["num_q_heads"] != a["num_kv_heads"])
+            else:
+                o = TF.scaled_dot_product_attention(qh, kh, vh, is_causal=a.get("causal", True), scale=scale,
+                                                    enable_gqa=a["num_q_heads"] != a["num_kv_heads"])
         att = o.detach().transpose(1, 2).reshape(B, T, -1)
         return att, _AutogradHandle(o, (qh, kh, vh)) if ctx.training else None
 

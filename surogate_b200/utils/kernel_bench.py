@@ -66,24 +66,49 @@ def _report(name: str, ms: float, flops: float, nbytes: float, peaks, tensor_sca
 
 
 # ---------------------------------------------------------------------------------------------- cases
+QWEN3_8B_GEMM_SHAPES = [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 24576, 4096), (8192, 4096, 12288), (4096, 151936, 4096), (8192, 8192, 8192)]
+
+
 def case_gemm(e, t: Timer, peaks, small: bool, dtype: str = "bf16") -> List[Dict]:
+    """Own GEMM (automatic tile choice, single-CTA 128x256 tiles, CTA-pair 256x256 tiles) next to the library GEMM of the same
+    shape and dtype: ``torch.matmul`` (cuBLAS) for bf16, ``torch._scaled_mm`` (cuBLASLt FP8, per-tensor scales) for FP8.  The
+    library calls exist here as comparators only."""
     from ..runtime.ops_cuda import gemm
 
-    shapes = [(4096, 4096, 4096)] if small else [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 24576, 4096), (8192, 4096, 12288)]
+    shapes = [(4096, 4096, 4096)] if small else QWEN3_8B_GEMM_SHAPES
     out = []
     for M, N, K in shapes:
+        d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        one = torch.ones(1, device="cuda")
         if dtype == "bf16":
             a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
-            d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            fn = lambda: gemm(a, b, d)  # noqa: E731
+            kw = {}
+            lib = lambda: torch.matmul(a, b.t(), out=d)  # noqa: E731
             nb, scale = 2 * (M * K + N * K + M * N), 1.0
         else:
             a, b = torch.randn(M, K, device="cuda").to(torch.float8_e4m3fn), torch.randn(N, K, device="cuda").to(torch.float8_e4m3fn)
-            d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            one = torch.ones(1, device="cuda")
-            fn = lambda: gemm(a, b, d, scale_a=one, scale_b=one)  # noqa: E731
+            kw = dict(scale_a=one, scale_b=one)
+            lib = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=d)  # noqa: E731
             nb, scale = M * K + N * K + 2 * M * N, 2.0
-        out.append(_report(f"gemm_{dtype} {M}x{N}x{K}", t(fn), 2.0 * M * N * K, nb, peaks, scale))
+        fl = 2.0 * M * N * K
+        row = _report(f"gemm_{dtype} {M}x{N}x{K}", t(lambda: gemm(a, b, d, **kw)), fl, nb, peaks, scale)
+        ms1 = t(lambda: gemm(a, b, d, tile_n=256, **kw))
+        ms2 = t(lambda: gemm(a, b, d, tile_n=512, **kw))
+        try:
+            ms_lib = t(lib)
+        except Exception as ex:  # noqa: BLE001
+            ms_lib = float("nan")
+            row["library_error"] = str(ex)[:120]
+        bt = b.t().contiguous()    # [K, N]: the dgrad layout (second operand MN-major)
+        at = a.t().contiguous()    # [K, M]: the wgrad layout (both operands MN-major)
+        ms_nn = t(lambda: gemm(a, bt, d, b_mn=True, **kw))
+        ms_tn = t(lambda: gemm(at, bt, d, a_mn=True, b_mn=True, **kw))
+        row.update({"tflops_single_cta": round(fl / ms1 / 1e9, 1), "tflops_cta_pair": round(fl / ms2 / 1e9, 1), "tflops_library": round(fl / ms_lib / 1e9, 1),
+                    "ours_over_library": round(ms_lib / row["ms"], 3), "tflops_b_mn": round(fl / ms_nn / 1e9, 1), "tflops_both_mn": round(fl / ms_tn / 1e9, 1)})
+        print(json.dumps({"compare": row["kernel"], **{k: row[k] for k in ("tflops", "tflops_single_cta", "tflops_cta_pair", "tflops_library", "ours_over_library",
+                                                                          "tflops_b_mn", "tflops_both_mn")}}), flush=True)
+        out.append(row)
+        del a, b, at, bt, d
     return out
 
 

@@ -50,6 +50,53 @@ def test_gemm_bf16(ext, M, N, K, a_mn, b_mn):
     assert _rel_err(out, ref) < 6e-3, _rel_err(out, ref)
 
 
+PAIR_SHAPES = [(256, 256, 128), (512, 768, 320), (300, 264, 200), (1024, 1536, 1024), (2048, 1000, 4096), (4096, 512, 2048), (128, 520, 64)]
+
+
+@pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_cta_pair(ext, M, N, K, a_mn, b_mn, fp8):
+    """The cta_group::2 kernel (256 x 256 tile per two-CTA cluster, TMA-store epilogue), forced with tile_n=512: every operand
+    layout, bf16 and FP8, ragged edges in M, N and K, bf16 and fp32 outputs, fp32 accumulation (TMA add) and bf16 accumulation."""
+    from surogate_b200.runtime.ops_cuda import gemm
+
+    es = 1 if fp8 else 2
+    if (a_mn and M * es % 16) or (b_mn and N * es % 16) or K * es % 16 or N % 8:
+        pytest.skip("row stride must be a multiple of 16 bytes")
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device=DEV)
+    B = torch.randn(N, K, device=DEV)
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    a = (A.t().contiguous() if a_mn else A).to(dt)
+    b = (B.t().contiguous() if b_mn else B).to(dt)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float().t() if b_mn else b.float()).t()
+    kw = dict(scale_a=torch.tensor([0.5], device=DEV), scale_b=torch.tensor([2.0], device=DEV)) if fp8 else {}
+    amax = torch.zeros(1, device=DEV)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=512, amax_out=amax, **kw)
+    torch.cuda.synchronize()
+    _check_flag()
+    assert _rel_err(out, ref) < 6e-3, _rel_err(out, ref)
+    assert abs(amax.item() - out.float().abs().max().item()) <= 0.01 * amax.item()
+    out32 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=512, out_dtype=torch.float32, **kw)
+    assert _rel_err(out32, ref) < 1e-4 if not fp8 else _rel_err(out32, ref) < 1e-4
+    base = torch.randn(M, N, device=DEV)
+    acc32 = base.clone()
+    gemm(a, b, acc32, a_mn=a_mn, b_mn=b_mn, tile_n=512, accumulate=True, alpha=0.5, **kw)
+    assert _rel_err(acc32, base + 0.5 * ref) < 1e-4
+    acc16 = base.bfloat16()
+    ref16 = acc16.float() + ref
+    gemm(a, b, acc16, a_mn=a_mn, b_mn=b_mn, tile_n=512, accumulate=True, **kw)
+    assert _rel_err(acc16, ref16) < 6e-3
+    # a view into a wider buffer: the store must not touch the columns next to it
+    wide = torch.zeros(M, N + 64, device=DEV, dtype=torch.bfloat16)
+    gemm(a, b, wide[:, 32:32 + N], a_mn=a_mn, b_mn=b_mn, tile_n=512, **kw)
+    assert _rel_err(wide[:, 32:32 + N], ref) < 6e-3
+    assert wide[:, :32].abs().max() == 0 and wide[:, 32 + N:].abs().max() == 0
+    torch.cuda.synchronize()
+    _check_flag()
+
+
 def test_gemm_accumulate_fp32_and_alpha(ext):
     from surogate_b200.runtime.ops_cuda import gemm
 
