@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+
 #include "gemm_sm100.h"
 #include "kernels.h"
 #include "ext_api.h"
@@ -87,6 +89,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, boo
     p.amax_out = opt_f32_mut(amax_out);
     p.error_flag = error_flag_ptr();
     p.tile_n = static_cast<int>(tile_n);
+    if (const char* v = std::getenv("SUROGATE_GEMM_PREFETCH")) p.pair_prefetch = std::atoi(v);   // tuning aids; unset = the kernel's defaults
+    if (const char* v = std::getenv("SUROGATE_GEMM_GROUP_M")) p.pair_group_m = std::atoi(v);
     sg::GemmOperand A{a.data_ptr(), static_cast<uint64_t>(a.stride(0)) * es};
     sg::GemmOperand B{b.data_ptr(), static_cast<uint64_t>(b.stride(0)) * es};
     g_launches += 1;

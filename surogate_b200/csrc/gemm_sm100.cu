@@ -360,10 +360,10 @@ struct PairTile {
 };
 __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int tile) {
     const int num_m = (p.M + PAIR_BM - 1) / PAIR_BM, num_n = (p.N + PAIR_BN - 1) / PAIR_BN;
-    const int per_group = GROUP_M * num_n;
+    const int per_group = p.pair_group_m * num_n;
     const int group = tile / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(num_m - first_m, GROUP_M);
+    const int first_m = group * p.pair_group_m;
+    const int gsize = min(num_m - first_m, p.pair_group_m);
     const int r = tile - group * per_group;
     return PairTile{(first_m + r % gsize) * PAIR_BM, (r / gsize) * PAIR_BN};
 }
@@ -424,11 +424,36 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int b_chunks = p.b_mn ? (128 * p.elem_bytes) / TILE_K_BYTES : 1;
             const int chunk_bytes = BK * TILE_K_BYTES;
             bool ok = true;
+            // optional L2 prefetch cursor: runs `pair_prefetch` contraction blocks ahead of the load cursor (across tile boundaries)
+            int pf_tile = first_tile, pf_kb = 0, pf_m0 = 0, pf_n0 = 0;
+            auto pf_origin = [&]() {
+                const PairTile t = pair_tile(p, pf_tile);
+                pf_m0 = t.m0 + static_cast<int>(rank) * 128;
+                pf_n0 = t.n0 + static_cast<int>(rank) * 128;
+            };
+            auto pf_step = [&]() {
+                if (pf_tile >= num_tiles) return;
+                const int k0 = pf_kb * BK;
+                if (!p.a_mn) tma_prefetch_l2_2d(&tmA, k0, pf_m0);
+                else for (int c = 0; c < a_chunks; ++c) tma_prefetch_l2_2d(&tmA, pf_m0 + c * BK, k0);
+                if (!p.b_mn) tma_prefetch_l2_2d(&tmB, k0, pf_n0);
+                else for (int c = 0; c < b_chunks; ++c) tma_prefetch_l2_2d(&tmB, pf_n0 + c * BK, k0);
+                if (++pf_kb == num_k) {
+                    pf_kb = 0;
+                    pf_tile += tile_step;
+                    if (pf_tile < num_tiles) pf_origin();
+                }
+            };
+            if (p.pair_prefetch > 0 && first_tile < num_tiles) {
+                pf_origin();
+                for (int i = 0; i < PAIR_STAGES + p.pair_prefetch; ++i) pf_step();
+            }
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 const PairTile t = pair_tile(p, tile);
                 const int m0 = t.m0 + static_cast<int>(rank) * 128, n0 = t.n0 + static_cast<int>(rank) * 128;
                 for (int kb = 0; kb < num_k; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) { ok = false; break; }
+                    if (p.pair_prefetch > 0) pf_step();
                     const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
                     const uint32_t sb = sa + A_STAGE_BYTES;
                     const uint32_t bar = mapa_shared(full_bar(stage), 0);                 // the leader's barrier counts both CTAs' bytes
@@ -649,8 +674,18 @@ template <int BN> static const char* launch(const GemmOperand& A, const GemmOper
     return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }
 
-static const char* launch_pair(const GemmOperand& A, const GemmOperand& B, const GemmParams& p, int num_sms, cudaStream_t stream) {
+static const char* launch_pair(const GemmOperand& A, const GemmOperand& B, GemmParams p, int num_sms, cudaStream_t stream) {
     const int BK = TILE_K_BYTES / p.elem_bytes;
+    // L2 prefetch is off unless asked for: measured on B200 it costs 3-5 % (the kernel is bound by operand delivery bandwidth, not by
+    // DRAM latency: four, five and six ring stages run at the same speed, half the operand bytes run 15-18 % faster)
+    if (p.pair_group_m <= 0) {
+        // The group's A panel (group_m x 256 rows x K) is re-read from L2 by every tile of the sweep over N while B streams through
+        // once per group: make the panel as tall as a quarter of the L2 allows, so B is fetched from DRAM as few times as possible.
+        const long long panel_row_bytes = static_cast<long long>(PAIR_BM) * p.K * p.elem_bytes;
+        long long g = (32ll << 20) / (panel_row_bytes > 0 ? panel_row_bytes : 1);
+        g = g < 4 ? 4 : (g > 32 ? 32 : g);
+        p.pair_group_m = static_cast<int>(g);
+    }
     CUtensorMap tmA, tmB, tmD;
     const char* e;
     if (!p.a_mn) e = make_tensor_map_2d(&tmA, A.ptr, p.elem_bytes, p.K, p.M, A.row_stride_bytes, BK, BM);

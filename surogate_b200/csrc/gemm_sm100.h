@@ -25,7 +25,9 @@ struct GemmParams {
     const float* scale_b;
     float* amax_out;       // optional: running max |D| (atomicMax on the bit pattern)
     int* error_flag;       // set to 1 if a pipeline wait ran out of budget
-    int tile_n;            // 0 = auto, 128 or 256
+    int tile_n;            // 0 = auto; 128 / 256 = single-CTA tiles of that width; 512 = 256 x 256 tiles on CTA pairs
+    int pair_prefetch;     // CTA-pair kernel: L2 prefetch distance in contraction blocks beyond the shared-memory ring (<= 0 = off, the default)
+    int pair_group_m;      // CTA-pair kernel: 256-row tiles per rasterisation group (0 = chosen from the operand sizes)
     // Grouped problems (MoE).  mode 0: dense.  mode 1: rows of A and D are grouped, group g = rows [offs[g], offs[g+1]) (each a
     // multiple of 128) and multiplies weight block g (M is unused; N, K are per-group sizes).  mode 2: the contraction is grouped:
     // output matrix g [M, N] = A[rows of g]^T . B[rows of g] (both operands MN-major, stored [total_rows, M] / [total_rows, N]).

@@ -76,6 +76,16 @@ def case_gemm(e, t: Timer, peaks, small: bool, dtype: str = "bf16") -> List[Dict
     from ..runtime.ops_cuda import gemm
 
     shapes = [(4096, 4096, 4096)] if small else QWEN3_8B_GEMM_SHAPES
+    if os.environ.get("SUROGATE_BENCH_GEMM_SHAPE"):   # one shape "M,N,K" and only the own kernel: the form a profiler capture wants
+        M, N, K = (int(v) for v in os.environ["SUROGATE_BENCH_GEMM_SHAPE"].split(","))
+        dt = torch.bfloat16 if dtype == "bf16" else torch.float8_e4m3fn
+        a, b = torch.randn(M, K, device="cuda").to(dt), torch.randn(N, K, device="cuda").to(dt)
+        d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        one = torch.ones(1, device="cuda")
+        kw = {} if dtype == "bf16" else dict(scale_a=one, scale_b=one)
+        tile_n = int(os.environ.get("SUROGATE_BENCH_GEMM_TILE", "0"))
+        return [_report(f"gemm_{dtype} {M}x{N}x{K} tile_n={tile_n}", t(lambda: gemm(a, b, d, tile_n=tile_n, **kw)), 2.0 * M * N * K,
+                        (M * K + N * K) * a.element_size() + 2 * M * N, peaks, 1.0 if dtype == "bf16" else 2.0)]
     out = []
     for M, N, K in shapes:
         d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)

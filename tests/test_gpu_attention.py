@@ -110,7 +110,7 @@ def test_flash_attention_at_the_benchmark_shapes(B, T, Hq, Hkv):
 
 
 @pytest.mark.parametrize("B,T,Hq,Hkv,window,docs", [(2, 512, 4, 2, 0, True), (1, 1024, 8, 2, 200, False), (2, 1024, 4, 1, 128, True),
-                                                    (1, 2048, 4, 4, 1, False), (2, 4096, 8, 2, 0, True), (1, 4096, 8, 2, 1024, True)])
+                                                    (1, 2048, 4, 4, 3, False), (2, 4096, 8, 2, 0, True), (1, 4096, 8, 2, 1024, True)])
 def test_flash_attention_packed_documents_and_windows(B, T, Hq, Hkv, window, docs):
     """Per-query lower bounds: queries attend only inside their own document and / or the last `window` keys; tiles that no query of
     a block can see are skipped by the kernels, so boundaries inside and on tile edges are both covered."""
