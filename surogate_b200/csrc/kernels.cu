@@ -656,19 +656,49 @@ __global__ void __launch_bounds__(256) adamw_fp32_kernel(P* __restrict__ p, cons
 
 // 8-bit state: momentum int8 through softsign (2x/(1+|x|) of the group-normalised value), variance uint8 of sqrt(v),
 // groups of 32 with fp16 scales.  Four adjacent lanes (8 elements each) form one group; the group abs-max is two shuffles.
-// n must be a multiple of 32.  The kernel is bandwidth-bound by design (10.25 bytes per parameter): divisions and square
-// roots use the fast hardware approximations, each thread keeps two 8-element vectors in flight, and the weight-decay mask is
-// one byte per 128 parameters (BLOCK_MASK) instead of one per parameter.
-// Integer <-> float conversions on the ordinary ALU (the conversion unit shares its issue slot with the special-function unit,
-// which this kernel already needs for rsqrt and two reciprocals per element).
-__device__ __forceinline__ float u8_to_float(unsigned v) { return __uint_as_float(0x4B000000u | v) - 8388608.f; }
-__device__ __forceinline__ int float_to_int_rn(float x) { return __float_as_int(x + 12582912.f) - 0x4B400000; }   // |x| < 2^22
+// n must be a multiple of 32.  The kernel moves 10.25 bytes per parameter, so the work per element has to stay below about
+// 40 issued instructions to be bound by memory and not by instruction issue.  Hence:
+//  * element pairs go through the packed fp32 instructions of sm_100 (fma / mul / add .f32x2: two results per issue slot);
+//  * momentum codes are decoded through a 256-entry shared-memory table, variance codes by splicing the byte into the
+//    mantissa of 2^23 (one byte-permute), and both are re-encoded by adding 1.5 * 2^23, whose low mantissa byte then IS the
+//    rounded two's-complement code (no float<->int conversions, which share an issue port with the special-function unit);
+//  * square root and the two reciprocals per element use the hardware approximations;
+//  * the weight-decay mask is one byte per 128 parameters (BLOCK_MASK) instead of one per parameter.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d)) : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d)) : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)), "l"(reinterpret_cast<unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float sqrt_fast(float x) {
+    float y;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float2 splat2(float x) { return make_float2(x, x); }
+constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23: adding it rounds to the nearest integer and leaves it in the low mantissa bits
 
 template <typename P, typename G, bool BLOCK_MASK>
 __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
                                                             __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
                                                             const float* __restrict__ hp, size_t n) {
-    // softsign decode table of the momentum code: y = c/127, m = y / (2 - |y|) (times the group scale)
+    // softsign decode table of the momentum code, indexed by code + 128: y = c/127, m = y / (2 - |y|) (times the group scale)
     __shared__ float m_lut[256];
     {
         const float y = static_cast<float>(static_cast<int>(threadIdx.x) - 128) * (1.f / 127.f);
@@ -677,7 +707,11 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
     __syncthreads();
     const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6], gs = hp[7];
     if (gs == 0.f) return;   // skipped update (non-finite gradient norm): nothing is read or written
-    const float step_size = lr / bc1, sib2 = rsqrtf(bc2), omb1 = 1.f - b1, omb2 = 1.f - b2;
+    const float2 gs2 = splat2(gs), b1_2 = splat2(b1), omb1_2 = splat2(1.f - b1), b2_2 = splat2(b2), rt_omb2 = splat2(sqrtf(1.f - b2)),
+                 sib2_2 = splat2(rsqrtf(bc2)), eps_2 = splat2(eps), nstep_2 = splat2(-lr / bc1), one_2 = splat2(1.f), magic_2 = splat2(kRoundMagic),
+                 c254_2 = splat2(254.f), nbias_2 = splat2(-8388608.f);
+    const float decay_on = 1.f - lr * wd;
+    const char* lut_bytes = reinterpret_cast<const char*>(m_lut);
     const size_t nvec = n / 8;
     constexpr int U = 2;  // vectors per thread per trip
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * U;
@@ -709,28 +743,42 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            float mv[8], sv[8];
+            float2 mv[4], sv[4];
             float am = 0.f, av = 0.f;
             if (live[u]) {
-                const uint8_t* mq = reinterpret_cast<const uint8_t*>(&mraw[u]);
-                const uint8_t* vq = reinterpret_cast<const uint8_t*>(&vraw[u]);
+                const uint32_t mw[2] = {mraw[u].x ^ 0x80808080u, mraw[u].y ^ 0x80808080u};   // two's-complement codes -> table indices
+                const uint32_t vw[2] = {vraw[u].x, vraw[u].y};
                 const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk[u]);
-                const float smu = sm[u], squ = sq[u] * (1.f / 255.f);
+                const float2 smu2 = splat2(sm[u]), squ2 = splat2(sq[u] * (1.f / 255.f));
+                const float2 dec_vec = splat2(mk[u].x ? decay_on : 1.f);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float gk = gv[u][k] * gs;
-                    float mi = m_lut[mq[k] ^ 0x80u] * smu;           // two's-complement code + 128
-                    const float r = u8_to_float(vq[k]) * squ;
-                    float vi2 = r * r;
-                    mi = b1 * mi + omb1 * gk;
-                    vi2 = b2 * vi2 + omb2 * gk * gk;
-                    const float s = vi2 > 0.f ? vi2 * rsqrtf(vi2) : 0.f;   // sqrt(v)
-                    const float dec = mb[k] ? wd : 0.f;
-                    pv[u][k] = pv[u][k] * (1.f - lr * dec) - step_size * __fdividef(mi, s * sib2 + eps);
-                    mv[k] = mi;
-                    sv[k] = s;
-                    am = fmaxf(am, fabsf(mi));
-                    av = fmaxf(av, s);
+                for (int j = 0; j < 4; ++j) {       // elements 2j and 2j + 1
+                    const uint32_t mword = mw[j >> 1], vword = vw[j >> 1];
+                    const int b0 = (2 * j) & 3, b1i = b0 + 1;
+                    // table lookups: byte b of the word, times 4, as a byte offset into the table
+                    const uint32_t o0 = b0 == 0 ? (mword << 2) & 0x3FCu : (mword >> (8 * b0 - 2)) & 0x3FCu;
+                    const uint32_t o1 = (mword >> (8 * b1i - 2)) & 0x3FCu;
+                    float2 mi = mul2(make_float2(*reinterpret_cast<const float*>(lut_bytes + o0), *reinterpret_cast<const float*>(lut_bytes + o1)), smu2);
+                    // variance codes: 0x4B0000cc is the float 2^23 + cc
+                    const float2 vcode = make_float2(__uint_as_float(__byte_perm(vword, 0x4B000000u, 0x7440u | b0)),
+                                                     __uint_as_float(__byte_perm(vword, 0x4B000000u, 0x7440u | b1i)));
+                    const float2 r = mul2(add2(vcode, nbias_2), squ2);
+                    float2 vi2 = mul2(r, r);
+                    const float2 gk = mul2(make_float2(gv[u][2 * j], gv[u][2 * j + 1]), gs2);
+                    mi = fma2(b1_2, mi, mul2(omb1_2, gk));
+                    const float2 gc = mul2(gk, rt_omb2);
+                    vi2 = fma2(gc, gc, mul2(b2_2, vi2));
+                    const float2 sd = make_float2(sqrt_fast(vi2.x), sqrt_fast(vi2.y));     // sqrt(v)
+                    const float2 den = fma2(sd, sib2_2, eps_2);
+                    const float2 q = mul2(mi, make_float2(rcp_fast(den.x), rcp_fast(den.y)));
+                    const float2 dec = BLOCK_MASK ? dec_vec : make_float2(mb[2 * j] ? decay_on : 1.f, mb[2 * j + 1] ? decay_on : 1.f);
+                    const float2 pn = fma2(q, nstep_2, mul2(make_float2(pv[u][2 * j], pv[u][2 * j + 1]), dec));
+                    pv[u][2 * j] = pn.x;
+                    pv[u][2 * j + 1] = pn.y;
+                    mv[j] = mi;
+                    sv[j] = sd;
+                    am = fmaxf(am, fmaxf(fabsf(mi.x), fabsf(mi.y)));
+                    av = fmaxf(av, fmaxf(sd.x, sd.y));
                 }
                 store8_any(p + idx[u], pv[u]);
             }
@@ -739,19 +787,28 @@ __global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, c
             av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 1));
             av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
             if (live[u]) {
-                // fp16 scales rounded up so normalised values stay within [-1, 1]
+                // fp16 scales rounded up, so normalised values stay within [-1, 1] (up to one rounding of the product, which cannot
+                // move a code past +-127 / 255)
                 const __half hm = __float2half_ru(fmaxf(am, 1e-30f)), hv = __float2half_ru(fmaxf(av, 1e-30f));
                 const float fm = fmaxf(__half2float(hm), 6e-8f), fv = fmaxf(__half2float(hv), 6e-8f);
-                const float im = __fdividef(1.f, fm), iv = __fdividef(255.f, fv);
-                uint2 mo, vo;
-                uint8_t* mq = reinterpret_cast<uint8_t*>(&mo);
-                uint8_t* vq = reinterpret_cast<uint8_t*>(&vo);
+                const float2 im2 = splat2(rcp_fast(fm)), iv2 = splat2(255.f * rcp_fast(fv));
+                uint32_t mcode[4], vcode[4];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float xn = fminf(fmaxf(mv[k] * im, -1.f), 1.f);
-                    mq[k] = static_cast<uint8_t>(float_to_int_rn(__fdividef(254.f * xn, 1.f + fabsf(xn))) & 0xFF);
-                    vq[k] = static_cast<uint8_t>(min(255, float_to_int_rn(sv[k] * iv)));
+                for (int j = 0; j < 4; ++j) {
+                    const float2 xn = mul2(mv[j], im2);
+                    const float2 ax = make_float2(fabsf(xn.x), fabsf(xn.y));
+                    const float2 den = add2(ax, one_2);
+                    const float2 y = mul2(xn, make_float2(rcp_fast(den.x), rcp_fast(den.y)));
+                    const float2 mc = fma2(y, c254_2, magic_2);          // low mantissa byte = round(254 x / (1 + |x|)) in two's complement
+                    const float2 vc = fma2(sv[j], iv2, magic_2);         // low mantissa byte = round(255 s / scale)
+                    mcode[j] = __byte_perm(__float_as_uint(mc.x), __float_as_uint(mc.y), 0x0040u);
+                    vcode[j] = __byte_perm(__float_as_uint(vc.x), __float_as_uint(vc.y), 0x0040u);
                 }
+                uint2 mo, vo;
+                mo.x = __byte_perm(mcode[0], mcode[1], 0x5410u);
+                mo.y = __byte_perm(mcode[2], mcode[3], 0x5410u);
+                vo.x = __byte_perm(vcode[0], vcode[1], 0x5410u);
+                vo.y = __byte_perm(vcode[2], vcode[3], 0x5410u);
                 *reinterpret_cast<uint2*>(m8 + idx[u]) = mo;
                 *reinterpret_cast<uint2*>(v8 + idx[u]) = vo;
                 if ((threadIdx.x & 3) == 0) { ms[idx[u] >> 5] = __float2half(fm); vs[idx[u] >> 5] = __float2half(fv); }

@@ -41,8 +41,8 @@ def _softsign_quant_reference(mi, vi):
     am = mp.abs().amax(1).clamp_min(6e-8).half().float().clamp_min(6e-8)
     av = sp.amax(1).clamp_min(6e-8).half().float().clamp_min(6e-8)
     # scales are rounded up in the kernel; emulate by nudging when half rounding went below the true max
-    am = torch.where(am < mp.abs().amax(1), torch.nextafter(am.half(), torch.tensor(float("inf"), dtype=torch.half)).float(), am)
-    av = torch.where(av < sp.amax(1), torch.nextafter(av.half(), torch.tensor(float("inf"), dtype=torch.half)).float(), av)
+    am = torch.where(am < mp.abs().amax(1), torch.nextafter(am.half(), torch.tensor(float("inf"), dtype=torch.half, device=am.device)).float(), am)
+    av = torch.where(av < sp.amax(1), torch.nextafter(av.half(), torch.tensor(float("inf"), dtype=torch.half, device=av.device)).float(), av)
     xn = mp / am[:, None]
     m8 = torch.round(2 * xn / (1 + xn.abs()) * 127).clamp(-127, 127).to(torch.int8)
     v8 = torch.round(sp / av[:, None] * 255).clamp(0, 255).to(torch.uint8)

@@ -316,6 +316,49 @@ def test_adamw_kernels(ext):
     assert torch.isfinite(pb.float()).all()
 
 
+def test_adamw_8bit_kernel_matches_the_pytorch_twin_code_for_code(ext):
+    """Three steps of the 8-bit kernel against the PyTorch statement of the same state encoding (optim/adamw.py): the parameters
+    agree to fp32 rounding of the approximated divisions, the int8 / uint8 codes are equal except for values that sit on a rounding
+    boundary (off by one at most), the fp16 group scales are equal or one fp16 step apart."""
+    from surogate_b200.optim.adamw import _softsign_dequant_reference, _softsign_quant_reference
+
+    torch.manual_seed(3)
+    n = 32 * 4096
+    lr, b1, b2, eps, wd = 3e-3, 0.9, 0.95, 1e-8, 0.1
+    for pdt, gdt in ((torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)):
+        p = torch.randn(n, device=DEV).to(pdt)
+        blocks = (torch.arange(n // 128, device=DEV) % 2 == 0).to(torch.uint8)
+        mask = blocks.repeat_interleave(128).float()
+        m8, v8 = torch.zeros(n, dtype=torch.int8, device=DEV), torch.zeros(n, dtype=torch.uint8, device=DEV)
+        ms, vs = torch.zeros(n // 32, dtype=torch.float16, device=DEV), torch.zeros(n // 32, dtype=torch.float16, device=DEV)
+        rm8, rv8, rms, rvs, rp = m8.clone(), v8.clone(), ms.clone(), vs.clone(), p.clone()
+        for step in range(1, 4):
+            g = (torch.randn(n, device=DEV) * 0.05 * torch.rand(n, device=DEV).pow(4)).to(gdt)
+            bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+            hp = torch.tensor([lr, b1, b2, eps, wd, bc1, bc2, 0.7], device=DEV)
+            ext.adamw8_step(p, g, m8, v8, ms, vs, blocks, hp)
+            m, v = _softsign_dequant_reference(rm8, rv8, rms, rvs)
+            gf = g.float() * 0.7
+            m = b1 * m + (1 - b1) * gf
+            v = b2 * v + (1 - b2) * gf * gf
+            pn = rp.float() * (1 - lr * wd * mask) - lr * (m / bc1) / ((v / bc2).sqrt() + eps)
+            upd_ref, upd = pn - rp.float(), p.float() - rp.float()
+            rp = pn.to(pdt)
+            rm8, rv8, rms, rvs = _softsign_quant_reference(m, v)
+            if pdt == torch.float32:
+                assert _rel_err(upd, upd_ref) < 2e-3, (step, _rel_err(upd, upd_ref))
+            else:
+                assert (p.float() - rp.float()).abs().max() <= 2 * 2 ** -7 * rp.float().abs().max()
+            dm = (m8.int() - rm8.int()).abs()
+            dv = (v8.int() - rv8.int()).abs()
+            assert int(dm.max()) <= 1 and int(dv.max()) <= 1, (int(dm.max()), int(dv.max()))
+            assert float((dm > 0).float().mean()) < 0.03 and float((dv > 0).float().mean()) < 0.03
+            assert float((ms.float() - rms.float()).abs().max() / rms.float().abs().max()) < 2e-3
+            # the next step starts from the kernel's own state on both sides, so differences do not accumulate
+            rm8, rv8, rms, rvs, rp = m8.clone(), v8.clone(), ms.clone(), vs.clone(), p.clone()
+    _check_flag()
+
+
 # ----------------------------------------------------------------------------- MoE
 def test_moe_softmax_topk(ext):
     tokens, E, K = 1000, 128, 8
