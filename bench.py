@@ -10,7 +10,7 @@ scaling, history 16), ZeRO-3 sharding of weights, gradients and 8-bit AdamW stat
 sequence 4096, micro-batch 2 per GPU, synthetic uniform token ids, random-init weights N(0, 0.02).
 Every step is a full forward + backward + gradient reduction + clipping + optimizer update.
 
-Two timings are taken after the warm-up:
+Two timings are taken after the warm-up (every step of either sees a batch it has not seen before):
 * ``value``: K steps timed with CUDA events on the device (inputs already resident), max over ranks;
 * ``e2e``:  K steps through the public ``Trainer.step`` API including the pinned-host -> device copy of each
   step's tokens/targets and the device -> host read of loss and gradient norm.
@@ -114,7 +114,7 @@ def reference_arm(args):
     return 0
 
 
-def main():
+def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -137,37 +137,33 @@ def main():
     ap.add_argument("--graphs", action="store_true", help="replay forward + backward from CUDA graphs (one GPU, dense models)")
     ap.add_argument("--drop-ignored-rows", action="store_true", help="compact rows without a target away before the LM head")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: truncate the layer stack (the JSON line names the reduced model)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
-    if args.warmup < 3:
-        args.warmup = 3
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="with the default model on 2 or more GPUs the second half of the headline metric (Qwen3-30B-A3B NVFP4, EP = N) is measured "
+                         "after the first and attached to the same JSON line as `secondary`; this flag leaves it out")
+    return ap.parse_args()
 
+
+def measure(args, model_key, info, comm, dev):
+    """Build the trainer of one configuration, run warm-up + timed steps (device-timed and end to end) and return the JSON record
+    (rank 0; None elsewhere).  Every step of both timed regions gets a batch it has not seen before."""
     import numpy as np
     import torch
 
-    from surogate_b200.parallel.dist import TorchComm, init_distributed
     from surogate_b200.runtime.trainer import Trainer, TrainerConfig
 
-    info = init_distributed()
     world = info.world
-    if world != args.gpus and info.rank == 0:
-        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
-    dev = torch.device("cuda", info.local_rank)
-    torch.cuda.set_device(dev)
-    comm = TorchComm() if world > 1 else None
-
-    spec = dict(MODELS[args.model])
+    spec = dict(MODELS[model_key])
     if args.layers:
         spec["model"] = dict(spec["model"], n_layers=args.layers)
         spec["label"] = f"{spec['label']}-truncated-{args.layers}-layers"
         spec["metric"] += f" [TRUNCATED to {args.layers} layers: profiling run, not a benchmark value]"
-    seq = args.seq_len or spec["seq_len"]
-    mb = args.batch or spec["batch"]
-    recipe = args.recipe or spec["recipe"]
-    zero = args.zero if args.zero is not None else spec["zero"]
-    ep = args.ep if args.ep is not None else (world if args.model == "qwen3-30b-a3b" else 1)
-    cfg = TrainerConfig(model=spec["model"], batch_size=mb, seq_len=seq, grad_accum=1, recipe=recipe, optimizer=args.optimizer or spec["optimizer"],
+    primary = model_key == args.model
+    seq = (args.seq_len if primary else None) or spec["seq_len"]
+    mb = (args.batch if primary else None) or spec["batch"]
+    recipe = (args.recipe if primary else None) or spec["recipe"]
+    zero = args.zero if (primary and args.zero is not None) else spec["zero"]
+    ep = args.ep if (primary and args.ep is not None) else (world if model_key == "qwen3-30b-a3b" else 1)
+    cfg = TrainerConfig(model=spec["model"], batch_size=mb, seq_len=seq, grad_accum=1, recipe=recipe, optimizer=(args.optimizer if primary else None) or spec["optimizer"],
                         learning_rate=1e-4, weight_decay=0.1, zero_level=zero, recompute=args.recompute,
                         backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention,
                         lora=spec.get("lora"), offload_master=bool(spec.get("offload")) and not args.no_offload,
@@ -181,14 +177,18 @@ def main():
     tr.init_weights(seed=0)
     V = spec["model"]["vocab_size"]
     rng = np.random.default_rng(1234 + info.rank)
-    n_batches = 4
-    host_batches = [rng.integers(0, V, size=(mb, seq + 1), dtype=np.int64).astype(np.int32) for _ in range(n_batches)]
-    host_inputs = [b[:, :-1].copy() for b in host_batches]   # copies: the target mask below must not touch the inputs
-    host_targets = [b[:, 1:].copy() for b in host_batches]
-    if spec.get("mask_first_fraction"):  # supervised fine-tuning shape: no loss on the prompt part of each sequence
-        for t in host_targets:
-            t[:, : int(seq * spec["mask_first_fraction"])] = -100
-    dev_batches = [(torch.from_numpy(x).to(dev), torch.from_numpy(y).to(dev)) for x, y in zip(host_inputs, host_targets)]
+    n_dev = args.warmup + args.steps          # device-timed region: one fresh batch per step, resident before the clock starts
+    n_host = args.steps + 1                   # end-to-end region: one fresh batch per step, copied from pinned host memory inside the clock
+
+    def draw():
+        b = rng.integers(0, V, size=(mb, seq + 1), dtype=np.int64).astype(np.int32)
+        x, y = b[:, :-1].copy(), b[:, 1:].copy()   # copies: the target mask below must not touch the inputs
+        if spec.get("mask_first_fraction"):        # supervised fine-tuning shape: no loss on the prompt part of each sequence
+            y[:, : int(seq * spec["mask_first_fraction"])] = -100
+        return x, y
+
+    dev_batches = [tuple(torch.from_numpy(t).to(dev) for t in draw()) for _ in range(n_dev)]
+    host_batches = [draw() for _ in range(n_host)]
 
     def barrier():
         if world > 1:
@@ -196,7 +196,7 @@ def main():
         torch.cuda.synchronize()
 
     def device_step(i):
-        x, y = dev_batches[i % n_batches]
+        x, y = dev_batches[i]
         tr.forward_backward(x, y)
         tr.optimizer_step()
 
@@ -211,7 +211,7 @@ def main():
     barrier()
     ev0.record()
     for i in range(args.steps):
-        device_step(i)
+        device_step(args.warmup + i)
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
@@ -222,7 +222,7 @@ def main():
     launches = (ext.launch_count() - launches0) if ext is not None else 0
     clocks = sampler.stop()
 
-    if args.profile:
+    if args.profile and primary:
         from torch.profiler import ProfilerActivity, profile
 
         barrier()
@@ -235,29 +235,31 @@ def main():
                 f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=70))
         barrier()
 
-    # end-to-end through the public API: numpy batches from host memory in, python floats out, every step
+    # end to end through the public API: numpy batches from host memory in, python floats out, every step
     e2e = None
     if not args.no_e2e:
         tr.h2d_bytes = tr.d2h_bytes = 0
-        out = tr.step(host_inputs[0], host_targets[0])  # one warm step through this path (allocates the pinned buffers)
+        out = tr.step(*host_batches[0])  # one warm step through this path (allocates the pinned buffers)
         tr.h2d_bytes = tr.d2h_bytes = 0
         barrier()
+        sampler2 = ClockSampler(info.local_rank)
+        sampler2.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record()
         for i in range(args.steps):
-            k = (i + 1) % n_batches
-            out = tr.step(host_inputs[k], host_targets[k])
+            out = tr.step(*host_batches[1 + i])
         e1.record()
         barrier()
         wall_ms = (time.perf_counter() - t0) * 1e3
         e2e_ms = max(e0.elapsed_time(e1), wall_ms)
-        e2e = (e2e_ms, tr.h2d_bytes // args.steps, tr.d2h_bytes // args.steps, out)
+        e2e = (e2e_ms, tr.h2d_bytes // args.steps, tr.d2h_bytes // args.steps, out, sampler2.stop())
 
     t = torch.tensor([ms, e2e[0] if e2e else 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         comm.all_reduce(t, "max")
     ms, e2e_ms = float(t[0]), float(t[1])
+    line = None
     if info.rank == 0:
         tokens_per_step = world * mb * seq
         value = tokens_per_step * args.steps / (ms / 1e3)
@@ -266,10 +268,11 @@ def main():
             "metric": spec["metric"], "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None, "dtype": "fp8" if recipe.startswith("fp8") else recipe,
-            "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": args.impl,
+            "data": "synthetic uniform token ids (a fresh batch every step), random-init weights N(0,0.02)", "impl": args.impl,
             "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
                        "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(cfg.recompute), "micro_batch_per_gpu": mb,
                        "lora_rank": (spec.get("lora") or {}).get("rank"), "offload": bool(cfg.offload_master),
+                       "keep_gathered": bool(cfg.keep_gathered and zero >= 3),   # ZeRO-3: gathered layer weights stay from forward to backward (one gather per step, not two)
                        "cuda_graphs": bool(getattr(tr, "graph_replays", 0)), "drop_ignored_rows": bool(cfg.lmhead_drop_ignored_rows), "resident_layers": int(args.resident_layers),
                        "weight_h2d_bytes_per_step": int(tr.store.h2d_bytes // max(1, args.steps + args.warmup + (0 if args.no_e2e else args.steps + 1))),
                        "l2_policy": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2; no explicit flush",
@@ -281,7 +284,46 @@ def main():
         }
         if e2e:
             line["e2e"] = {"value": round(tokens_per_step * args.steps / (e2e_ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
-                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "last_loss": e2e[3]["loss"]}
+                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "last_loss": e2e[3]["loss"], "clocks": e2e[4]}
+    # give the memory back before another configuration is built in this process
+    del tr, dev_batches
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats(dev)
+    return line
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from surogate_b200.parallel.dist import TorchComm, init_distributed
+
+    info = init_distributed()
+    world = info.world
+    if world != args.gpus and info.rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
+    dev = torch.device("cuda", info.local_rank)
+    torch.cuda.set_device(dev)
+    comm = TorchComm() if world > 1 else None
+
+    line = measure(args, args.model, info, comm, dev)
+    if args.model == "qwen3-8b" and world >= 2 and not args.no_secondary and args.impl == "native" and not args.layers:
+        # the second half of the headline metric; a failure there must not lose the first half
+        try:
+            sec = measure(args, "qwen3-30b-a3b", info, comm, dev)
+        except Exception as e:  # noqa: BLE001
+            sec = {"error": f"{type(e).__name__}: {e}"[:400]}
+        if info.rank == 0:
+            line["secondary"] = sec
+    if info.rank == 0:
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
