@@ -22,6 +22,13 @@
 //     between calls.
 //   * The first call on each GPU resolves the workspace's device address (cudaGetSymbolAddress) and reads the
 //     SM count; make that first call outside any stream capture.  Later calls only launch kernels.
+//     The set-up is safe against several host threads making their first call at once (the record is published with
+//     release / acquire ordering under a mutex).
+//   * `stream` must belong to the GPU that is current on the calling thread (cudaSetDevice): the workspace address and the
+//     block count are those of the current device.
+//   * Every data pointer must be 16-byte aligned (the kernels move 16 bytes per lane); otherwise SG_NOALLOC_ERR_BAD_ARGUMENT.
+//   * The launch status is read with cudaPeekAtLastError: the thread's CUDA error state is left untouched.  If the thread
+//     already carries an unrelated CUDA error, this call reports SG_NOALLOC_ERR_CUDA and the error stays for the caller to read.
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine.
 //
 // Arguments are raw device pointers with the same meaning and layout as the allocating entry point
