@@ -168,7 +168,9 @@ def measure(args, model_key, info, comm, dev):
                         backend="ref" if args.impl == "library" else "cuda", collectives=args.collectives, ep_size=ep, attention=args.attention,
                         lora=spec.get("lora"), offload_master=bool(spec.get("offload")) and not args.no_offload,
                         offload_optimizer=bool(spec.get("offload")) and not args.no_offload, keep_gathered=not spec.get("offload"),
-                        ep_capacity_factor=float(max(1, ep)),  # room for every routed row even if all tokens pick one rank: nothing is dropped
+                        # receive room for 3x the mean load of a rank (all of it when ep <= 3); the busiest rank of a randomly initialised
+                        # router stays below 2x, and rows that would not fit are counted and reported in the JSON line (expected: 0)
+                        ep_capacity_factor=float(max(1, min(ep, 3))),
                         resident_layers=args.resident_layers, use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
                         ep_plan_refresh_interval=4)            # counts are summed over 4 steps per decision; refreshes after warm-up are inside the timed region
     if spec.get("recompute"):

@@ -154,7 +154,15 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
     return {dx, dw};
 }
 
-std::vector<Tensor> swiglu_fwd(const Tensor& x, bool want_y, const c10::optional<Tensor>& fp8_scale, const c10::optional<Tensor>& amax_out, bool want_fp8) {
+static const int* opt_i32(const c10::optional<Tensor>& t) {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->numel() >= 1, "expected a CUDA int32 tensor");
+    return t->data_ptr<int>();
+}
+
+// rows_limit (optional, one CUDA int32): only that many leading rows are in use; the rest of the (worst-case sized) buffer is not touched
+std::vector<Tensor> swiglu_fwd(const Tensor& x, bool want_y, const c10::optional<Tensor>& fp8_scale, const c10::optional<Tensor>& amax_out, bool want_fp8,
+                               const c10::optional<Tensor>& rows_limit) {
     check_bf16(x, "x");
     const int M = static_cast<int>(x.size(-1) / 2);
     TORCH_CHECK(M % 8 == 0, "swiglu: M must be a multiple of 8");
@@ -167,19 +175,30 @@ std::vector<Tensor> swiglu_fwd(const Tensor& x, bool want_y, const c10::optional
     if (want_fp8) y8 = torch::empty(shape, x.options().dtype(at::kFloat8_e4m3fn));
     g_launches += 1;
     sg::swiglu_fwd(x.data_ptr(), y.defined() ? y.data_ptr() : nullptr, y8.defined() ? y8.data_ptr() : nullptr, opt_f32(fp8_scale), opt_f32_mut(amax_out),
-                   rows, M, num_sms(), cur_stream());
+                   rows, M, num_sms(), cur_stream(), opt_i32(rows_limit));
     return {y, y8};
 }
 
-Tensor swiglu_bwd(const Tensor& dy, const Tensor& x) {
+Tensor swiglu_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& rows_limit) {
     check_bf16(dy, "dy");
     check_bf16(x, "x");
     const int M = static_cast<int>(x.size(-1) / 2);
     const c10::cuda::CUDAGuard guard(x.device());
     Tensor dx = torch::empty_like(x);
     g_launches += 1;
-    sg::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel() / (2 * M), M, num_sms(), cur_stream());
+    sg::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel() / (2 * M), M, num_sms(), cur_stream(), opt_i32(rows_limit));
     return dx;
+}
+
+void zero_empty_groups(Tensor& out, const Tensor& offsets) {
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() >= 2 && offsets.is_cuda() && offsets.scalar_type() == at::kInt, "out [G, ...] and CUDA int32 offsets");
+    const int64_t G = out.size(0);
+    TORCH_CHECK(offsets.numel() >= G + 1, "offsets needs G + 1 entries");
+    const size_t bytes = static_cast<size_t>(out.numel() / G) * out.element_size();
+    TORCH_CHECK(bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "group matrices must be multiples of 16 bytes");
+    const c10::cuda::CUDAGuard guard(out.device());
+    g_launches += 1;
+    sg::zero_empty_groups(out.data_ptr(), offsets.data_ptr<int>(), static_cast<int>(G), bytes, cur_stream());
 }
 
 // ``pos`` is [tokens] int32, or [3, tokens] (temporal / height / width rows) when sec_h or sec_w is non-zero: frequency j then
@@ -379,8 +398,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("launch_count", &launch_count, "number of kernels this extension has launched");
     m.def("rmsnorm_fwd", &rmsnorm_fwd);
     m.def("rmsnorm_bwd", &rmsnorm_bwd);
-    m.def("swiglu_fwd", &swiglu_fwd);
-    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("swiglu_fwd", &swiglu_fwd, pybind11::arg("x"), pybind11::arg("want_y"), pybind11::arg("fp8_scale"), pybind11::arg("amax_out"), pybind11::arg("want_fp8"),
+          pybind11::arg("rows_limit") = c10::optional<Tensor>());
+    m.def("swiglu_bwd", &swiglu_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("rows_limit") = c10::optional<Tensor>());
+    m.def("zero_empty_groups", &zero_empty_groups, "zero the [G, ...] slices of groups that own no rows");
     m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd, py::arg("qkv"), py::arg("q_norm_weight"), py::arg("k_norm_weight"), py::arg("position_ids"), py::arg("num_q_heads"),
           py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("theta"), py::arg("sec_h") = 0, py::arg("sec_w") = 0);
     m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd, py::arg("d_out"), py::arg("qkv"), py::arg("q_norm_weight"), py::arg("k_norm_weight"), py::arg("q_rstd"),

@@ -244,6 +244,16 @@ void copy_rows_upto(const Tensor& src, Tensor& dst, const Tensor& n_rows) {
     sg::copy_rows_upto(src.data_ptr(), dst.data_ptr(), n_rows.data_ptr<int>(), static_cast<int>(src.size(1)), sms(), cur_stream());
 }
 
+// Deterministic row claim: pos[tok*K+k] = how many earlier (in token order) copies of this rank go to the same expert.
+Tensor ep_row_positions(const Tensor& topk_idx, int64_t num_experts) {
+    TORCH_CHECK(topk_idx.is_cuda() && topk_idx.scalar_type() == at::kInt && topk_idx.is_contiguous(), "topk_idx: contiguous CUDA int32");
+    const c10::cuda::CUDAGuard guard(topk_idx.device());
+    Tensor pos = torch::empty_like(topk_idx);
+    sg_count_launch(1);
+    sg::ep_row_positions(topk_idx.data_ptr<int>(), pos.data_ptr<int>(), static_cast<int>(topk_idx.numel()), static_cast<int>(num_experts), cur_stream());
+    return pos;
+}
+
 void ep_dispatch(const Tensor& x, const c10::optional<Tensor>& topk_idx, const c10::optional<Tensor>& w, const c10::optional<Tensor>& dst_base,
                  const c10::optional<Tensor>& cursors, Tensor& row_map, const std::vector<int64_t>& recv, int64_t recv_byte_offset, int64_t K,
                  int64_t experts_per_rank, int64_t capacity_rows, bool reuse_map) {
@@ -438,6 +448,7 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
+    m.def("ep_row_positions", &ep_row_positions);
     m.def("ep_zero_pad_rows", &ep_zero_pad_rows);
     m.def("copy_rows_upto", &copy_rows_upto);
     m.def("ep_combine", &ep_combine);

@@ -4,7 +4,7 @@
 //   ep_plan     : every rank publishes its per-expert token counts into all peers' tables (P2P stores), a flag
 //                 barrier follows inside the kernel, then each rank derives (a) the padded row layout of its own
 //                 experts' receive buffer and (b) the first row it may write for every (global) expert on its owner.
-//   ep_dispatch : one CTA per token; each of the token's K copies claims a row on the expert's owner and the
+//   ep_dispatch : one CTA per token; each of the token's K copies takes its precomputed row on the expert's owner and the
 //                 token's activation row is stored straight into the owner's receive buffer (16-byte P2P stores),
 //                 optionally scaled (backward: d_yp = w * dy).  This is routing permutation + all-to-all in one pass.
 //   ep_combine  : one CTA per token; pulls its K expert-output rows from the owners (P2P loads) and forms the
@@ -109,9 +109,38 @@ __global__ void __launch_bounds__(256) copy_rows_upto_kernel(const uint4* __rest
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) dst[i] = src[i];
 }
 
+// Position of every (token, k) copy among this rank's copies for the same expert, in token order: a stable counting sort done by
+// one CTA per expert (ballot + running count).  Replaces claiming rows with atomics, so the row order inside an expert, and with
+// it the summation order of the weight gradients, is the same in every run.
+__global__ void __launch_bounds__(256) ep_row_positions_kernel(const int* __restrict__ topk_idx, int* __restrict__ pos, int n_entries) {
+    __shared__ int warp_count[8];
+    __shared__ int running;
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    for (int base = 0; base < n_entries; base += 256) {
+        const int i = base + threadIdx.x;
+        const bool mine = i < n_entries && topk_idx[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(m);
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) pos[i] = before + __popc(m & ((1u << lane) - 1u));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < 8; ++w) t += warp_count[w];
+            running += t;
+        }
+        __syncthreads();
+    }
+}
+
 // x [tokens, C] bf16; recv = peers' receive buffers ([capacity, C] each).  row_map[tok*K+k] = owner * capacity + row (or -1).
+// row_pos[tok*K+k] = position of the copy among this rank's copies for that expert (ep_row_positions_kernel).
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const bf16* __restrict__ x, const int* __restrict__ topk_idx, const float* __restrict__ w,
-                                                          const int* __restrict__ dst_base, int* __restrict__ cursors, int* __restrict__ row_map,
+                                                          const int* __restrict__ dst_base, const int* __restrict__ row_pos, int* __restrict__ row_map,
                                                           PeerPtrs recv, int C, int K, int El, int capacity_rows, int reuse_map) {
     __shared__ long long dst[16];
     __shared__ float ws[16];
@@ -122,7 +151,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const bf16* __restrict
             code = row_map[tok * K + threadIdx.x];
         } else {
             const int e = topk_idx[tok * K + threadIdx.x];
-            const int row = dst_base[e] + atomicAdd(&cursors[e], 1);
+            const int row = dst_base[e] + row_pos[tok * K + threadIdx.x];
             if (row < capacity_rows) code = static_cast<long long>(e / El) * capacity_rows + row;
             row_map[tok * K + threadIdx.x] = static_cast<int>(code);
         }
@@ -152,34 +181,48 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const bf16* __restrict
     }
 }
 
-// y[tok] = sum_k w[tok,k] * out_owner[row] ; optionally rows_out[tok*K+k] = out_owner[row]
+// y[tok] = sum_k w[tok,k] * out_owner[row] ; optionally rows_out[tok*K+k] = out_owner[row].  All of a token's peer loads (up to
+// eight per trip) are issued before the first is used, so their NVLink latencies overlap instead of adding up.
 __global__ void __launch_bounds__(256) ep_combine_kernel(PeerPtrs outs, const float* __restrict__ w, const int* __restrict__ row_map,
                                                          bf16* __restrict__ y, bf16* __restrict__ rows_out, int C, int K, int capacity_rows) {
-    __shared__ int code[16];
+    __shared__ const bf16* src_row[16];
     __shared__ float ws[16];
     const int tok = blockIdx.x;
     if (threadIdx.x < K) {
-        code[threadIdx.x] = row_map[tok * K + threadIdx.x];
+        const int code = row_map[tok * K + threadIdx.x];
+        const bf16* r = nullptr;
+        if (code >= 0) {
+            const int owner = code / capacity_rows;
+            r = reinterpret_cast<const bf16*>(outs.p[owner]) + static_cast<size_t>(code - owner * capacity_rows) * C;
+        }
+        src_row[threadIdx.x] = r;
         ws[threadIdx.x] = w ? w[tok * K + threadIdx.x] : 1.f;
     }
     __syncthreads();
     for (int c = threadIdx.x; c < C / 8; c += blockDim.x) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int k = 0; k < K; ++k) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (code[k] >= 0) {
-                const int owner = code[k] / capacity_rows;
-                const size_t row = static_cast<size_t>(code[k] - owner * capacity_rows);
-                const void* src = reinterpret_cast<const bf16*>(outs.p[owner]) + row * C + static_cast<size_t>(c) * 8;
-                asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
-            }
-            if (rows_out) reinterpret_cast<uint4*>(rows_out + (static_cast<size_t>(tok) * K + k) * C)[c] = v;
-            const bf162* p = reinterpret_cast<const bf162*>(&v);
+        for (int k0 = 0; k0 < K; k0 += 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(p[i]);
-                acc[2 * i] += ws[k] * f.x;
-                acc[2 * i + 1] += ws[k] * f.y;
+            for (int j = 0; j < 8; ++j) {
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (k0 + j < K && src_row[k0 + j] != nullptr) {
+                    const void* src = src_row[k0 + j] + static_cast<size_t>(c) * 8;
+                    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src) : "memory");
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (k0 + j >= K) break;
+                if (rows_out) reinterpret_cast<uint4*>(rows_out + (static_cast<size_t>(tok) * K + k0 + j) * C)[c] = v[j];
+                const bf162* p = reinterpret_cast<const bf162*>(&v[j]);
+                const float wk = ws[k0 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(p[i]);
+                    acc[2 * i] += wk * f.x;
+                    acc[2 * i + 1] += wk * f.y;
+                }
             }
         }
         uint4 o;
@@ -240,9 +283,12 @@ void ep_zero_pad_rows(void* buf, const int* offsets, int El, int C, int capacity
 void copy_rows_upto(const void* src, void* dst, const int* n_rows, int C, int num_sms, cudaStream_t s) {
     copy_rows_upto_kernel<<<num_sms * 8, 256, 0, s>>>((const uint4*)src, (uint4*)dst, n_rows, C);
 }
-void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, int* cursors, int* row_map, const PeerPtrs& recv, int tokens,
+void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, const int* row_pos, int* row_map, const PeerPtrs& recv, int tokens,
                  int C, int K, int El, int capacity_rows, int reuse_map, cudaStream_t s) {
-    ep_dispatch_kernel<<<tokens, 256, 0, s>>>((const bf16*)x, topk_idx, w, dst_base, cursors, row_map, recv, C, K, El, capacity_rows, reuse_map);
+    ep_dispatch_kernel<<<tokens, 256, 0, s>>>((const bf16*)x, topk_idx, w, dst_base, row_pos, row_map, recv, C, K, El, capacity_rows, reuse_map);
+}
+void ep_row_positions(const int* topk_idx, int* pos, int n_entries, int E, cudaStream_t s) {
+    ep_row_positions_kernel<<<E, 256, 0, s>>>(topk_idx, pos, n_entries);
 }
 void ep_combine(const PeerPtrs& outs, const float* w, const int* row_map, void* y, void* rows_out, int tokens, int C, int K, int capacity_rows,
                 cudaStream_t s) {

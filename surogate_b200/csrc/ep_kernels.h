@@ -9,8 +9,9 @@ namespace sg {
 
 void ep_plan(const PeerPtrs& ctrl, const PeerPtrs& pads, const int* counts, int* offsets, int* dst_base, int* cursors, int E, int rank, int world,
              uint32_t epoch, int slot_base, int capacity_rows, int* error_flag, double budget_s, cudaStream_t s);
-void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, int* cursors, int* row_map, const PeerPtrs& recv, int tokens,
+void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, const int* row_pos, int* row_map, const PeerPtrs& recv, int tokens,
                  int C, int K, int El, int capacity_rows, int reuse_map, cudaStream_t s);
+void ep_row_positions(const int* topk_idx, int* pos, int n_entries, int E, cudaStream_t s);
 void ep_combine(const PeerPtrs& outs, const float* w, const int* row_map, void* y, void* rows_out, int tokens, int C, int K, int capacity_rows,
                 cudaStream_t s);
 void ep_weight_grad(const void* rows, const void* dy, float* d_w, int tokens, int C, int K, cudaStream_t s);

@@ -203,8 +203,11 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, float* __re
 // ------------------------------------------------------------------------------------------ SwiGLU
 // x = [up | gate] per row (2M); y = silu(gate) * up.  Optional FP8 copy of y with scale + abs-max.
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ y_fp8,
-                                                         const float* __restrict__ fp8_scale, float* __restrict__ amax_out, size_t rows, int M) {
+                                                         const float* __restrict__ fp8_scale, float* __restrict__ amax_out, size_t rows, int M,
+                                                         const int* __restrict__ rows_limit) {
     __shared__ float sh[32];
+    // rows_limit (device): only the first *rows_limit rows are in use (expert buffers sized for the worst case); cost follows the use
+    if (rows_limit) rows = min(rows, static_cast<size_t>(max(0, __ldg(rows_limit))));
     const size_t nvec = rows * (M / 8);
     const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
     float amax = 0.f;
@@ -230,7 +233,9 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict_
         if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
     }
 }
-__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, size_t rows, int M) {
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, size_t rows, int M,
+                                                         const int* __restrict__ rows_limit) {
+    if (rows_limit) rows = min(rows, static_cast<size_t>(max(0, __ldg(rows_limit))));
     const size_t nvec = rows * (M / 8);
     for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t row = v / (M / 8);
@@ -862,11 +867,23 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  int C, int num_sms, cudaStream_t s) {
     rmsnorm_bwd_n(dy, x, w, rstd, d_res, dx, dw_partial, dw, rows, C, rmsnorm_bwd_blocks(rows, num_sms), s);
 }
-void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s) {
-    swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M);
+void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s,
+                const int* rows_limit) {
+    swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M, rows_limit);
 }
-void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s) {
-    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M);
+void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit) {
+    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M, rows_limit);
+}
+// Zero the output matrices of groups that own no rows (their wgrad tiles are never scheduled): out [G, per_group] of `elem` bytes.
+__global__ void __launch_bounds__(256) zero_empty_groups_kernel(uint4* __restrict__ out, const int* __restrict__ offsets, size_t vec_per_group) {
+    const int g = blockIdx.y;
+    if (offsets[g + 1] != offsets[g]) return;
+    uint4* dst = out + static_cast<size_t>(g) * vec_per_group;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < vec_per_group; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        dst[i] = make_uint4(0, 0, 0, 0);
+}
+void zero_empty_groups(void* out, const int* offsets, int groups, size_t bytes_per_group, cudaStream_t s) {
+    zero_empty_groups_kernel<<<dim3(32, groups), 256, 0, s>>>((uint4*)out, offsets, bytes_per_group / 16);
 }
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
                       int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s) {

@@ -14,8 +14,10 @@ void rmsnorm_bwd_n(const void* dy, const void* x, const void* w, const float* rs
                    int C, int blocks, cudaStream_t s);
 void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
                  int C, int num_sms, cudaStream_t s);
-void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s);
-void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s);
+void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s,
+                const int* rows_limit = nullptr);
+void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit = nullptr);
+void zero_empty_groups(void* out, const int* offsets, int groups, size_t bytes_per_group, cudaStream_t s);
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
                       int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s);
 void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,

@@ -167,10 +167,14 @@ class ExpertParallel:
                          SLOT_EP, cap, self.err, self.comm.wait_budget_s)
         # pad rows feed the wgrad contraction and must be zero; only they are touched, so peers may already be storing real rows
         self.ext.ep_zero_pad_rows(b["recv_x"], offsets, El, cap)
-        self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, cursors, row_map, pb, b["recv_x_off"], K, El, cap, False)
+        # rows are taken in token order (a stable counting sort per expert), not claimed with atomics: same layout in every run
+        row_pos = self.ext.ep_row_positions(pre.topk_idx.reshape(-1).contiguous(), E)
+        self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, row_pos, row_map, pb, b["recv_x_off"], K, El, cap, False)
         self._barrier()  # every rank's rows have landed
         xp = torch.empty_like(b["recv_x"])  # rows beyond the used range stay uninitialised: nothing downstream reads them into a result
-        self.ext.copy_rows_upto(b["recv_x"], xp, offsets[El:El + 1])
+        used = offsets[El:El + 1]           # padded rows in use this step (device side): element-wise kernels downstream stop there
+        self.ext.copy_rows_upto(b["recv_x"], xp, used)
+        xp._sg_rows = used
         if ctx.layer is not None and ctx.phase == "fwd":
             gc = b["counts"].view(self.ep, E).sum(0)
             self.last_global_counts[ctx.layer] = gc
@@ -216,7 +220,9 @@ class ExpertParallel:
         self.ext.ep_dispatch(dy2, None, w, None, None, plan.row_map, b["arena"].peer_bases, b["recv_dy_off"], K, b["El"], plan.capacity, True)
         self._barrier()
         dyp = torch.empty_like(b["recv_dy"])
-        self.ext.copy_rows_upto(b["recv_dy"], dyp, plan.layout[b["El"]:b["El"] + 1])
+        used = plan.layout[b["El"]:b["El"] + 1]
+        self.ext.copy_rows_upto(b["recv_dy"], dyp, used)
+        dyp._sg_rows = used
         return dyp, d_w.reshape(weights.shape)
 
     # ------------------------------------------------------------------ least-loaded expert placement

@@ -195,10 +195,20 @@ class CudaOps(RefOps):
     def swiglu(self, ctx, op, x):
         if ctx.recipe is not None and ctx.recipe.wants_fp8_activation(ctx, op, 0):
             return (ctx.recipe.swiglu_forward(ctx, op, self.ext, x),)
-        return (self.ext.swiglu_fwd(x, True, None, None, False)[0],)
+        used = getattr(x, "_sg_rows", None)   # expert rows in a worst-case sized buffer: only the rows in use are processed
+        y = self.ext.swiglu_fwd(x, True, None, None, False, used)[0]
+        if used is not None:
+            y._sg_rows = used
+        return (y,)
 
     def swiglu_backward(self, ctx, op, dy, x):
-        return (self.ext.swiglu_bwd(dy.contiguous(), x),)
+        used = getattr(x, "_sg_rows", None)
+        if used is None:
+            used = getattr(dy, "_sg_rows", None)
+        dx = self.ext.swiglu_bwd(dy.contiguous(), x, used)
+        if used is not None:
+            dx._sg_rows = used
+        return (dx,)
 
     # ------------------------------------------------------------------ tiled MLP (long context): same tiles on the tcgen05 GEMM + SwiGLU kernels
     def tiled_mlp(self, ctx, op, x, up_w, down_w):
@@ -501,8 +511,13 @@ def _moe_mixin():
         r = ctx.recipe.forward_grouped(ctx, op, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "forward_grouped") else None
         if r is not None:
             return (r,)
-        y = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+        used = getattr(x, "_sg_rows", None)
+        # every row of a group (padding included) is written by the GEMM; rows behind the last group are never read into a result,
+        # so a buffer sized for the worst case (expert parallel) is not cleared, only tagged with the row count in use
+        y = (torch.empty if used is not None else torch.zeros)(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
         self.ext.gemm_grouped(x, w, y, plan.offsets, 1, False, False, 1.0, None, None, self.ext.error_flag_tensor())
+        if used is not None:
+            y._sg_rows = used
         return (y,)
 
     def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
@@ -513,13 +528,19 @@ def _moe_mixin():
             return r, None
         err = self.ext.error_flag_tensor()
         dy = dy.contiguous()
-        dx = torch.zeros_like(x)
+        used = getattr(dy, "_sg_rows", None)
+        if used is None:
+            used = getattr(x, "_sg_rows", None)
+        dx = (torch.empty_like if used is not None else torch.zeros_like)(x)
         self.ext.gemm_grouped(dy, w, dx, plan.offsets, 1, True, False, 1.0, None, None, err)     # dy [R,N] . W[g] [N,K]
+        if used is not None:
+            dx._sg_rows = used
         tgt, acc = ctx.grad_target(op.outputs[1])
         if tgt is not None:
+            # dW[g] (+)= dy_g^T . x_g ; groups without rows schedule no tiles, so their slices are cleared here (only theirs)
+            self.ext.gemm_grouped(dy, x, tgt, plan.offsets, 2, True, acc, 1.0, None, None, err)
             if not acc:
-                tgt.zero_()                                                                     # experts without tokens keep a zero gradient
-            self.ext.gemm_grouped(dy, x, tgt, plan.offsets, 2, True, True, 1.0, None, None, err)  # dW[g] += dy_g^T . x_g
+                self.ext.zero_empty_groups(tgt, plan.offsets)
         return dx, None
 
     def moe_unpermute(self, ctx, op, yp, tw, plan):
