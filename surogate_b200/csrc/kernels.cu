@@ -549,10 +549,11 @@ __global__ void __launch_bounds__(1024) cross_entropy_fwd_bwd_kernel(bf16* __res
 // ------------------------------------------------------------------------------------------ FP8 quantise / abs-max / sum of squares
 template <bool E5M2>
 __global__ void __launch_bounds__(256) quantize_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, const float* __restrict__ scale,
-                                                           float* __restrict__ amax_out, size_t n) {
+                                                           float* __restrict__ amax_out, size_t n, const int* __restrict__ rows_limit, int row_len) {
     __shared__ float sh[32];
     const float s = scale ? __ldg(scale) : 1.f;
     float amax = 0.f;
+    if (rows_limit) n = min(n, static_cast<size_t>(max(0, __ldg(rows_limit))) * row_len);   // only the leading rows are in use
     const size_t nvec = n / 8;
     for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float a[8];
@@ -568,9 +569,11 @@ __global__ void __launch_bounds__(256) quantize_fp8_kernel(const bf16* __restric
         if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
     }
 }
-__global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, float* __restrict__ amax_out, size_t n) {
+__global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, float* __restrict__ amax_out, size_t n, const int* __restrict__ rows_limit,
+                                                   int row_len) {
     __shared__ float sh[32];
     float amax = 0.f;
+    if (rows_limit) n = min(n, static_cast<size_t>(max(0, __ldg(rows_limit))) * row_len);
     const size_t nvec = n / 8;
     for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float a[8];
@@ -914,13 +917,14 @@ void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const 
     cross_entropy_fwd_bwd_kernel<<<rows, 1024, 0, s>>>((bf16*)logits, targets, loss, scale_ptr, scale_host, V, ld, write_grad, row_weight, kd_idx,
                                                        kd_logp, kd_k, kd_weight, kd_loss);
 }
-void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s) {
+void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s, const int* rows_limit,
+                  int row_len) {
     const int grid = grid_for(n / 8, 256, num_sms);
-    if (e5m2) quantize_fp8_kernel<true><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n);
-    else quantize_fp8_kernel<false><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n);
+    if (e5m2) quantize_fp8_kernel<true><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n, rows_limit, row_len);
+    else quantize_fp8_kernel<false><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, scale, amax, n, rows_limit, row_len);
 }
-void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s) {
-    amax_kernel<<<grid_for(n / 8, 256, num_sms), 256, 0, s>>>((const bf16*)x, amax, n);
+void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s, const int* rows_limit, int row_len) {
+    amax_kernel<<<grid_for(n / 8, 256, num_sms), 256, 0, s>>>((const bf16*)x, amax, n, rows_limit, row_len);
 }
 void sumsq(const void* x, int is_fp32, float* partial, int nblocks, size_t n, cudaStream_t s) {
     if (is_fp32) sumsq_kernel<float><<<nblocks, 512, 0, s>>>((const float*)x, partial, n);

@@ -28,8 +28,9 @@ void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad
 void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,
                            int write_grad, const float* row_weight, const int* kd_idx, const float* kd_logp, int kd_k, float kd_weight, float* kd_loss,
                            cudaStream_t s);
-void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s);
-void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s);
+void quantize_fp8(const void* x, void* q, const float* scale, float* amax, size_t n, int e5m2, int num_sms, cudaStream_t s,
+                  const int* rows_limit = nullptr, int row_len = 0);
+void amax_bf16(const void* x, float* amax, size_t n, int num_sms, cudaStream_t s, const int* rows_limit = nullptr, int row_len = 0);
 void sumsq(const void* x, int is_fp32, float* partial, int nblocks, size_t n, cudaStream_t s);
 void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float* v, const uint8_t* mask, const float* hp, size_t n, int num_sms,
                 cudaStream_t s);

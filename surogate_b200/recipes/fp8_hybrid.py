@@ -7,6 +7,8 @@ Every GEMM of a block (qkv, out, mlp_up, mlp_down) runs on the tcgen05 FP8 path 
 * dgrad    : dy(e5m2) . W(e4m3)          (W read MN-major: no transposed weight copy)
 * wgrad    : dy(e5m2)^T . x(e4m3)        (both read MN-major: no transposed activation copies)
 
+The expert projections of MoE layers run the same three GEMMs as grouped FP8 GEMMs (``recipes/grouped_fp8.py``).
+
 Activations are quantised where they are produced (RMSNorm and SwiGLU kernels emit FP8 next to
 recording the abs-max), weights once per optimizer step into a per-layer FP8 cache, and the FP8 copy
 of an activation is what is saved for backward.  Scales follow the delayed-scaling rule: the scale
@@ -26,13 +28,14 @@ import torch
 
 from ..runtime.ops_cuda import Fp8Tensor, gemm
 from .base import Recipe
+from .grouped_fp8 import GroupedFp8Mixin
 
 E4M3_MAX = 448.0
 E5M2_MAX = 57344.0
 QUANT_ROLES = ("qkv", "out", "mlp_up", "mlp_down")
 
 
-class FP8HybridRecipe(Recipe):
+class FP8HybridRecipe(GroupedFp8Mixin, Recipe):
     name = "fp8_hybrid"
 
     def __init__(self, cm, device, history: int = 16, margin: int = 0, skip_first_layers: int = 0, skip_last_layers: int = 0,
@@ -59,6 +62,7 @@ class FP8HybridRecipe(Recipe):
         self.scale_inv = torch.ones(Q, dtype=torch.float32, device=device)
         self.have_history = False
         self.weight_cache: Dict[Tuple[int, str], Fp8Tensor] = {}
+        self.expert_weight_cache: Dict[Tuple[int, str], tuple] = {}
         self.weight_version = 0
 
     # ------------------------------------------------------------------ scaling state
@@ -91,9 +95,11 @@ class FP8HybridRecipe(Recipe):
         self.scale_inv.copy_(1.0 / s)
         self.amax_cur.zero_()
         self.have_history = True
+        self.grouped_end_step()
 
     def on_weights_updated(self, store) -> None:
         self.weight_cache.clear()
+        self.expert_weight_cache.clear()
         self.weight_version += 1
 
     def state_dict(self):
@@ -113,7 +119,23 @@ class FP8HybridRecipe(Recipe):
 
     def wants_fp8_activation(self, ctx, op, out_index: int) -> bool:
         name = op.outputs[out_index]
-        return ctx.layer is not None and ctx.layer not in self.skip and name in self._CONSUMER_ROLE
+        if ctx.layer is None or ctx.layer in self.skip or name not in self._CONSUMER_ROLE:
+            return False
+        return self._only_fp8_matmuls_read(ctx.graph, name)
+
+    def _only_fp8_matmuls_read(self, graph, name: str) -> bool:
+        """An activation is emitted as FP8 only when every op that reads it is a matmul of a quantised role: in MoE blocks the
+        second norm feeds the router and the token permutation, which want bf16."""
+        if graph is None:
+            return True
+        cache = self.__dict__.setdefault("_fp8_reader_cache", {})
+        key = (id(graph), name)
+        ok = cache.get(key)
+        if ok is None:
+            readers = [o for o in graph.ops if name in o.inputs]
+            ok = bool(readers) and all(o.kind == "matmul" and o.attrs.get("role", "") in QUANT_ROLES for o in readers)
+            cache[key] = ok
+        return ok
 
     def norm_forward(self, ctx, op, ext, x, residual, w):
         role = self._CONSUMER_ROLE[op.outputs[1 if residual is not None or len(op.outputs) == 3 else 0]]

@@ -9,8 +9,10 @@ Per dense projection (qkv, out, mlp_up, mlp_down) all three GEMMs run on the blo
             the product.
 
 Weights are quantised once per optimizer step (both orientations, cached); activations and gradients just in time
-from an abs-max pass.  Expert GEMMs of MoE layers stay in bf16, as in the reference's training path, and so do the
-LM head and the router.  Shapes whose contraction is not a multiple of 256 fall back to bf16.
+from an abs-max pass.  The expert projections of MoE layers run as grouped FP8 GEMMs (E4M3 forward, E5M2 gradients, per-tensor
+current scaling; ``recipes/grouped_fp8.py``): their rows arrive grouped by expert with device-side offsets, which the FP8 grouped
+kernel schedules directly.  The LM head and the router stay in bf16.  Shapes whose contraction is not a multiple of 256 fall
+back to bf16.
 
 Parity: csrc/src/recipes/nvfp4/nvfp4_recipe.cpp:629-1131, recipes/nvfp4/kernels/*.
 """
@@ -21,6 +23,7 @@ from typing import Dict, Tuple
 import torch
 
 from .base import Recipe
+from .grouped_fp8 import GroupedFp8Mixin
 
 QUANT_ROLES = ("qkv", "out", "mlp_up", "mlp_down")
 ENCODE = 2688.0
@@ -34,7 +37,7 @@ class Fp4Tensor:
         self.q, self.sf, self.inv_ge = q, sf, inv_ge
 
 
-class NVFP4Recipe(Recipe):
+class NVFP4Recipe(GroupedFp8Mixin, Recipe):
     name = "nvfp4"
 
     def __init__(self, cm, device, skip_first_layers: int = 0, skip_last_layers: int = 0, hadamard: bool = True, stochastic: bool = True):
@@ -42,9 +45,11 @@ class NVFP4Recipe(Recipe):
 
         self.ext = ext()
         self.device = device
+        self.n_layers = cm.n_layers
         self.skip = set(range(skip_first_layers)) | set(range(cm.n_layers - skip_last_layers, cm.n_layers))
         self.hadamard, self.stochastic = hadamard, stochastic
         self.weight_cache: Dict[Tuple[int, str, bool], Fp4Tensor] = {}
+        self.expert_weight_cache: Dict[Tuple[int, str], tuple] = {}
         self.step = 0
         self.calls = 0
 
@@ -52,8 +57,12 @@ class NVFP4Recipe(Recipe):
         self.step = step
         self.calls = 0
 
+    def end_step(self) -> None:
+        self.grouped_end_step()
+
     def on_weights_updated(self, store) -> None:
         self.weight_cache.clear()
+        self.expert_weight_cache.clear()
 
     # ------------------------------------------------------------------ helpers
     def _amax(self, x: torch.Tensor) -> torch.Tensor:

@@ -51,6 +51,15 @@ def test_expert_parallel_matches_one_gpu():
         assert abs(a - b) < 6e-2 * abs(b), (two["norms"], one["norms"])
 
 
+def test_expert_parallel_with_fp8_experts_trains_like_one_gpu():
+    """EP=2 under the FP8 recipe: the dispatched rows are quantised up to the device-side row count and run through the grouped FP8
+    GEMMs on the expert's owner; losses follow the 1-GPU FP8 run."""
+    one = run_worker(1, dict(ARGS, model=MOE, recipe="fp8_hybrid"))
+    two = run_worker(2, dict(ARGS, model=MOE, recipe="fp8_hybrid", ep=2, zero=1, collectives="symm"), port=29743)
+    for a, b in zip(two["losses"], one["losses"]):
+        assert abs(a - b) < 4e-2 * abs(b), (two["losses"], one["losses"])
+
+
 LORA = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
             rslora=False, train_router=False)
 
