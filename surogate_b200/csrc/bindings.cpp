@@ -272,8 +272,23 @@ Tensor embedding_fwd(const Tensor& tokens, const Tensor& table) {
     return out;
 }
 
-void embedding_bwd(const Tensor& tokens, const Tensor& d_out, Tensor& d_table) {
+// deterministic = true: positions sorted by token id, one CTA per run of equal ids, fp32 sums, no atomics (bit-reproducible);
+// false: bf16 / fp32 atomic adds in arrival order.
+void embedding_bwd(const Tensor& tokens, const Tensor& d_out, Tensor& d_table, bool deterministic) {
     check_bf16(d_out, "d_out");
+    if (deterministic) {
+        TORCH_CHECK(d_table.is_cuda() && d_table.is_contiguous() && (d_table.scalar_type() == at::kFloat || d_table.scalar_type() == at::kBFloat16) &&
+                        d_table.size(1) % 2 == 0,
+                    "d_table: contiguous fp32 / bf16 [V, C]");
+        const c10::cuda::CUDAGuard guard(d_out.device());
+        auto sorted = tokens.reshape({-1}).sort(/*stable=*/true, /*dim=*/0, /*descending=*/false);
+        Tensor ids = std::get<0>(sorted).contiguous(), order = std::get<1>(sorted).contiguous();
+        g_launches += 1;
+        sg::embedding_bwd_sorted(ids.data_ptr<int>(), reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), d_out.data_ptr(), d_table.data_ptr(),
+                                 d_table.scalar_type() == at::kFloat, static_cast<int>(ids.numel()), static_cast<int>(d_table.size(1)),
+                                 static_cast<int>(d_table.size(0)), cur_stream());
+        return;
+    }
     TORCH_CHECK(d_table.is_cuda() && d_table.is_contiguous(), "d_table must be contiguous CUDA");
     TORCH_CHECK(d_table.scalar_type() == at::kFloat || d_table.scalar_type() == at::kBFloat16, "d_table must be fp32 or bf16");
     const int C = static_cast<int>(d_table.size(1));
@@ -410,7 +425,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("k_rstd"), py::arg("position_ids"), py::arg("num_q_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("theta"),
           py::arg("sec_h") = 0, py::arg("sec_w") = 0);
     m.def("embedding_fwd", &embedding_fwd);
-    m.def("embedding_bwd", &embedding_bwd);
+    m.def("embedding_bwd", &embedding_bwd, py::arg("tokens"), py::arg("d_out"), py::arg("d_table"), py::arg("deterministic") = true);
     m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd, py::arg("logits"), py::arg("targets"), py::arg("scale"), py::arg("scale_host"),
           py::arg("write_grad"), py::arg("row_weight") = py::none(), py::arg("kd_idx") = py::none(), py::arg("kd_logp") = py::none(),
           py::arg("kd_weight") = 0.0, py::arg("kd_loss_out") = py::none());

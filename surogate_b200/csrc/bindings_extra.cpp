@@ -7,6 +7,7 @@
 #include <string>
 
 #include "attention_sm100.h"
+#include "qlora_kernels.h"
 #include "comm_kernels.h"
 #include "ep_kernels.h"
 #include "gemm_sm100.h"
@@ -112,6 +113,33 @@ std::vector<Tensor> moe_softmax_topk(const Tensor& logits, int64_t K, bool renor
     sg::moe_softmax_topk(logits.data_ptr<float>(), w.data_ptr<float>(), idx.data_ptr<int>(), want_probs ? probs.data_ptr<float>() : nullptr,
                          counts.data_ptr<int>(), prob_sum.data_ptr<float>(), lse, tokens, E, static_cast<int>(K), renorm, sms(), cur_stream());
     return {w, idx, probs};
+}
+
+// d_logits (bf16 [tokens, E]) of the router from d(top-k weights) [tokens, K] (optional), the forward's per-expert counts (optional: needed
+// with an auxiliary loss) and d_aux, the gradient of the auxiliary loss as a device scalar (optional).
+Tensor moe_router_bwd(const Tensor& logits, const Tensor& topk_idx, const c10::optional<Tensor>& d_topk_w, const c10::optional<Tensor>& counts,
+                      const c10::optional<Tensor>& d_aux, bool renorm, double aux_coef, double z_coef) {
+    TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.dim() == 2, "logits: fp32 [tokens, E]");
+    TORCH_CHECK(topk_idx.scalar_type() == at::kInt && topk_idx.is_contiguous(), "topk_idx: contiguous int32");
+    const int tokens = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+    const int K = static_cast<int>(topk_idx.numel() / tokens);
+    TORCH_CHECK(E <= 256 && K <= 16, "moe_router_bwd supports E <= 256, K <= 16");
+    auto fptr = [](const c10::optional<Tensor>& t) -> const float* {
+        if (!t.has_value() || !t->defined()) return nullptr;
+        TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous(), "expected contiguous fp32");
+        return t->data_ptr<float>();
+    };
+    const int* cp = nullptr;
+    if (counts.has_value() && counts->defined()) {
+        TORCH_CHECK(counts->scalar_type() == at::kInt && counts->numel() == E, "counts: int32 [E]");
+        cp = counts->data_ptr<int>();
+    }
+    const c10::cuda::CUDAGuard guard(logits.device());
+    Tensor d_logits = torch::empty({tokens, E}, logits.options().dtype(at::kBFloat16));
+    sg_count_launch(1);
+    sg::moe_router_bwd(logits.data_ptr<float>(), topk_idx.data_ptr<int>(), fptr(d_topk_w), cp, fptr(d_aux), d_logits.data_ptr(), tokens, E, K, renorm,
+                       static_cast<float>(aux_coef), static_cast<float>(z_coef), sms(), cur_stream());
+    return d_logits;
 }
 
 // counts int32 [E_local] -> padded offsets int32 [E_local + 1]; cursors zeroed.
@@ -294,7 +322,7 @@ Tensor ep_weight_grad(const Tensor& rows, const Tensor& dy, int64_t K) {
 int64_t nvfp4_sf_bytes(int64_t rows, int64_t K) { return ((rows + 127) / 128) * ((K / 16 + 3) / 4) * 512; }
 
 // x [rows, K] bf16 -> (packed e2m1 [rows, K/2] uint8, scale factors in atom layout uint8)
-std::vector<Tensor> nvfp4_quantize(const Tensor& x, const Tensor& amax, bool stochastic, int64_t seed, bool block2d) {
+std::vector<Tensor> nvfp4_quantize(const Tensor& x, const Tensor& amax, bool stochastic, int64_t seed, bool block2d, bool four_over_six) {
     TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: bf16 [rows, K]");
     const int rows = static_cast<int>(x.size(0)), K = static_cast<int>(x.size(1));
     TORCH_CHECK(K % 16 == 0 && (!block2d || rows % 16 == 0), "nvfp4_quantize: K (and rows for 2-D blocks) must be multiples of 16");
@@ -303,12 +331,13 @@ std::vector<Tensor> nvfp4_quantize(const Tensor& x, const Tensor& amax, bool sto
     Tensor sf = torch::zeros({nvfp4_sf_bytes(rows, K)}, x.options().dtype(at::kByte));
     sg_count_launch(1);
     sg::nvfp4_quantize_rows(x.data_ptr(), q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), rows, K, stochastic, static_cast<uint32_t>(seed), block2d,
-                            sms(), cur_stream());
+                            sms(), cur_stream(), four_over_six && !stochastic);
     return {q, sf};
 }
 
 // x [R, C] bf16 -> quantised transpose: (q [C, R/2], sf for rows = C, K = R); optional random Hadamard along R
-std::vector<Tensor> nvfp4_quantize_transpose(const Tensor& x, const Tensor& amax, bool stochastic, bool hadamard, int64_t seed, int64_t sign_mask) {
+std::vector<Tensor> nvfp4_quantize_transpose(const Tensor& x, const Tensor& amax, bool stochastic, bool hadamard, int64_t seed, int64_t sign_mask,
+                                             bool four_over_six) {
     TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: bf16 [R, C]");
     const int R = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1));
     TORCH_CHECK(R % 64 == 0 && C % 64 == 0, "nvfp4_quantize_transpose: both dimensions must be multiples of 64");
@@ -317,16 +346,17 @@ std::vector<Tensor> nvfp4_quantize_transpose(const Tensor& x, const Tensor& amax
     Tensor sf = torch::zeros({nvfp4_sf_bytes(C, R)}, x.options().dtype(at::kByte));
     sg_count_launch(1);
     sg::nvfp4_quantize_transpose(x.data_ptr(), q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), R, C, stochastic, hadamard,
-                                 static_cast<uint32_t>(seed), static_cast<uint32_t>(sign_mask), cur_stream());
+                                 static_cast<uint32_t>(seed), static_cast<uint32_t>(sign_mask), cur_stream(), four_over_six && !stochastic);
     return {q, sf};
 }
 
-Tensor nvfp4_dequantize(const Tensor& q, const Tensor& sf, const Tensor& amax, double amax_div) {
+Tensor nvfp4_dequantize(const Tensor& q, const Tensor& sf, const Tensor& amax, double amax_div, double encode) {
     const int rows = static_cast<int>(q.size(0)), K = static_cast<int>(q.size(1)) * 2;
     const c10::cuda::CUDAGuard guard(q.device());
     Tensor out = torch::empty({rows, K}, q.options().dtype(at::kBFloat16));
     sg_count_launch(1);
-    sg::nvfp4_dequantize(q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), static_cast<float>(amax_div), out.data_ptr(), rows, K, sms(), cur_stream());
+    sg::nvfp4_dequantize(q.data_ptr(), sf.data_ptr(), amax.data_ptr<float>(), static_cast<float>(amax_div), out.data_ptr(), rows, K, sms(), cur_stream(),
+                         static_cast<float>(encode));
     return out;
 }
 
@@ -421,6 +451,42 @@ Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out,
     return d_qkv;
 }
 
+// ---------------------------------------------------------------------------------------- QLoRA storage -> bf16
+// kind: "bnb_nf4" (a = absmax fp32, or a = int8 codes with b = fp32 scales per 256 blocks and c = fp32 offset), "fp8_block" (a = fp32
+// scales), "nvfp4" (a = UE4M3 scale bytes, b = fp32 tensor de-scale), "mxfp4" (a = E8M0 scale bytes).
+Tensor dequant_blockwise(const std::string& kind, const Tensor& codes, const Tensor& a, const c10::optional<Tensor>& b, const c10::optional<Tensor>& c,
+                         int64_t n, int64_t block) {
+    TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && a.is_cuda() && a.is_contiguous(), "contiguous CUDA tensors");
+    TORCH_CHECK(n % 8 == 0 && n > 0, "dequant: the element count must be a positive multiple of 8");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(codes.data_ptr()) & 7) == 0, "dequant: codes must be 8-byte aligned");
+    const c10::cuda::CUDAGuard guard(codes.device());
+    Tensor out = torch::empty({n}, codes.options().dtype(at::kBFloat16));
+    sg_count_launch(1);
+    if (kind == "bnb_nf4") {
+        TORCH_CHECK(codes.numel() * codes.element_size() * 2 >= n && block >= 8 && block % 8 == 0, "nf4: codes too short or bad block");
+        if (a.scalar_type() == at::kFloat) {
+            sg::dequant_nf4(codes.data_ptr(), a.data_ptr<float>(), nullptr, nullptr, nullptr, out.data_ptr(), n, static_cast<int>(block), sms(), cur_stream());
+        } else {
+            TORCH_CHECK(a.scalar_type() == at::kChar && b.has_value() && c.has_value() && b->scalar_type() == at::kFloat && c->scalar_type() == at::kFloat,
+                        "nf4 double quantisation: int8 codes, fp32 scales, fp32 offset");
+            sg::dequant_nf4(codes.data_ptr(), nullptr, a.data_ptr<int8_t>(), b->data_ptr<float>(), c->data_ptr<float>(), out.data_ptr(), n,
+                            static_cast<int>(block), sms(), cur_stream());
+        }
+    } else if (kind == "fp8_block") {
+        TORCH_CHECK(codes.numel() * codes.element_size() >= n && a.scalar_type() == at::kFloat && block % 8 == 0, "fp8_block operands");
+        sg::dequant_fp8_block(codes.data_ptr(), a.data_ptr<float>(), out.data_ptr(), n, static_cast<int>(block), sms(), cur_stream());
+    } else if (kind == "nvfp4") {
+        TORCH_CHECK(b.has_value() && b->scalar_type() == at::kFloat && a.element_size() == 1 && a.numel() * 16 >= n, "nvfp4 operands");
+        sg::dequant_nvfp4(codes.data_ptr(), a.data_ptr(), b->data_ptr<float>(), out.data_ptr(), n, sms(), cur_stream());
+    } else if (kind == "mxfp4") {
+        TORCH_CHECK(a.element_size() == 1 && a.numel() * 32 >= n, "mxfp4 operands");
+        sg::dequant_mxfp4(codes.data_ptr(), a.data_ptr(), out.data_ptr(), n, sms(), cur_stream());
+    } else {
+        TORCH_CHECK(false, "unknown storage kind '", kind, "'");
+    }
+    return out;
+}
+
 }  // namespace
 
 void sg_register_extra(pybind11::module_& m) {
@@ -430,15 +496,19 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("all_gather_fused", &all_gather_fused);
     m.def("all_reduce_small", &all_reduce_small);
     m.def("moe_softmax_topk", &moe_softmax_topk);
+    m.def("moe_router_bwd", &moe_router_bwd);
     m.def("moe_offsets", &moe_offsets);
     m.def("moe_permute", &moe_permute);
     m.def("moe_unpermute", &moe_unpermute);
     m.def("moe_unpermute_bwd", &moe_unpermute_bwd);
     m.def("gemm_grouped", &gemm_grouped);
     m.def("nvfp4_sf_bytes", &nvfp4_sf_bytes);
-    m.def("nvfp4_quantize", &nvfp4_quantize);
-    m.def("nvfp4_quantize_transpose", &nvfp4_quantize_transpose);
-    m.def("nvfp4_dequantize", &nvfp4_dequantize);
+    m.def("nvfp4_quantize", &nvfp4_quantize, pybind11::arg("x"), pybind11::arg("amax"), pybind11::arg("stochastic"), pybind11::arg("seed"), pybind11::arg("block2d"),
+          pybind11::arg("four_over_six") = false);
+    m.def("nvfp4_quantize_transpose", &nvfp4_quantize_transpose, pybind11::arg("x"), pybind11::arg("amax"), pybind11::arg("stochastic"), pybind11::arg("hadamard"),
+          pybind11::arg("seed"), pybind11::arg("sign_mask"), pybind11::arg("four_over_six") = false);
+    m.def("nvfp4_dequantize", &nvfp4_dequantize, pybind11::arg("q"), pybind11::arg("sf"), pybind11::arg("amax"), pybind11::arg("amax_div"),
+          pybind11::arg("encode") = 2688.0);
     m.def("gemm_nvfp4", &gemm_nvfp4);
     m.def("flash_attn_fwd", &flash_attn_fwd, pybind11::arg("qkv"), pybind11::arg("Hq"), pybind11::arg("Hkv"), pybind11::arg("scale"),
           pybind11::arg("lo") = c10::optional<Tensor>());
@@ -446,6 +516,8 @@ void sg_register_extra(pybind11::module_& m) {
           pybind11::arg("Hkv"), pybind11::arg("scale"), pybind11::arg("lo") = c10::optional<Tensor>(), pybind11::arg("kv_qend") = c10::optional<Tensor>());
     m.def("flash_attn_bwd_profile", &flash_attn_bwd_profile, "per-phase cycle counters of the backward passes (development aid)");
     m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
+    m.def("dequant_blockwise", &dequant_blockwise, pybind11::arg("kind"), pybind11::arg("codes"), pybind11::arg("a"), pybind11::arg("b") = c10::optional<Tensor>(),
+          pybind11::arg("c") = c10::optional<Tensor>(), pybind11::arg("n"), pybind11::arg("block") = 0);
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_row_positions", &ep_row_positions);

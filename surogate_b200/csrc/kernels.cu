@@ -449,6 +449,35 @@ template <typename G> __global__ void embedding_bwd_kernel(const int* __restrict
     }
 }
 
+// Deterministic variant: positions are sorted by token id first; CTA i owns the run of equal ids that STARTS at sorted position i
+// (other CTAs leave at once), sums the run's rows in fp32 in sorted order and adds the sum to the table row once.  No atomics, so
+// the result does not depend on scheduling.  Ids outside [0, V) are skipped.
+template <typename G>
+__global__ void __launch_bounds__(256) embedding_bwd_sorted_kernel(const int* __restrict__ sorted_ids, const long long* __restrict__ order,
+                                                                   const bf16* __restrict__ d_out, G* __restrict__ d_table, int n, int C, int V) {
+    const int i = blockIdx.x;
+    const int id = sorted_ids[i];
+    if (id < 0 || id >= V || (i > 0 && sorted_ids[i - 1] == id)) return;
+    int end = i + 1;
+    while (end < n && sorted_ids[end] == id) ++end;
+    for (int c = threadIdx.x * 2; c < C; c += blockDim.x * 2) {
+        float ax = 0.f, ay = 0.f;
+        for (int j = i; j < end; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(d_out + static_cast<size_t>(order[j]) * C + c));
+            ax += f.x;
+            ay += f.y;
+        }
+        G* dst = d_table + static_cast<size_t>(id) * C + c;
+        if constexpr (sizeof(G) == 2) {
+            const float2 o = __bfloat1622float2(*reinterpret_cast<const bf162*>(dst));
+            *reinterpret_cast<bf162*>(dst) = __floats2bfloat162_rn(o.x + ax, o.y + ay);
+        } else {
+            dst[0] += ax;
+            dst[1] += ay;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------ cross-entropy (fwd + bwd in place)
 // One CTA per row of bf16 logits [rows, V].  loss[row] = lse - logit[target]; logits are overwritten with
 // d_logits = (softmax - onehot) * scale * row_weight[row] (scale read from device memory), zero for ignored rows.
@@ -910,6 +939,12 @@ void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad
     const int grid = grid_for(n * (C / 2), 256, num_sms);
     if (grad_fp32) embedding_bwd_kernel<float><<<grid, 256, 0, s>>>(tokens, (const bf16*)d_out, (float*)d_table, n, C);
     else embedding_bwd_kernel<bf16><<<grid, 256, 0, s>>>(tokens, (const bf16*)d_out, (bf16*)d_table, n, C);
+}
+void embedding_bwd_sorted(const int* sorted_ids, const long long* order, const void* d_out, void* d_table, int grad_fp32, int n, int C, int V,
+                          cudaStream_t s) {
+    if (n <= 0) return;
+    if (grad_fp32) embedding_bwd_sorted_kernel<float><<<n, 256, 0, s>>>(sorted_ids, order, (const bf16*)d_out, (float*)d_table, n, C, V);
+    else embedding_bwd_sorted_kernel<bf16><<<n, 256, 0, s>>>(sorted_ids, order, (const bf16*)d_out, (bf16*)d_table, n, C, V);
 }
 void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,
                            int write_grad, const float* row_weight, const int* kd_idx, const float* kd_logp, int kd_k, float kd_weight, float* kd_loss,

@@ -25,6 +25,8 @@ void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, co
                       cudaStream_t s);
 void embedding_fwd(const int* tokens, const void* table, void* out, size_t n, int C, int V, int* error_flag, int num_sms, cudaStream_t s);
 void embedding_bwd(const int* tokens, const void* d_out, void* d_table, int grad_fp32, size_t n, int C, int num_sms, cudaStream_t s);
+void embedding_bwd_sorted(const int* sorted_ids, const long long* order, const void* d_out, void* d_table, int grad_fp32, int n, int C, int V,
+                          cudaStream_t s);
 void cross_entropy_fwd_bwd(void* logits, const int* targets, float* loss, const float* scale_ptr, float scale_host, int rows, int V, int ld,
                            int write_grad, const float* row_weight, const int* kd_idx, const float* kd_logp, int kd_k, float kd_weight, float* kd_loss,
                            cudaStream_t s);

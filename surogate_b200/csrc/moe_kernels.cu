@@ -100,6 +100,81 @@ __global__ void __launch_bounds__(256) moe_softmax_topk_kernel(const float* __re
     if (lse_sq_sum && lane == 0 && lse_acc != 0.f) atomicAdd(lse_sq_sum, lse_acc);
 }
 
+// ------------------------------------------------------------------------------------------ router backward
+// d_logits [tokens, E] (bf16) from the gradients of the top-k weights and of the auxiliary losses; one warp per token, E <= 256.
+//   probs = softmax(logits); sel_k = probs[idx_k]
+//   d_sel_k = renorm ? g_k / S - (sum_j g_j sel_j) / S^2 : g_k                      (S = sum_k sel_k)
+//   d_probs[e] = sum_k [idx_k == e] d_sel_k + aux_grad * counts[e]                  (aux_grad = d_aux * coef * E / tokens^2)
+//   d_logits = probs * (d_probs - <d_probs, probs>) + z_grad * lse * probs          (z_grad = d_aux * z_coef * 2 / tokens)
+// d_aux arrives as a device scalar (the loss scale); counts are the forward's per-expert assignment counts.
+template <int VPL>
+__global__ void __launch_bounds__(256) moe_router_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ topk_idx, const float* __restrict__ d_topk_w,
+                                                             const int* __restrict__ counts, const float* __restrict__ d_aux, bf16* __restrict__ d_logits,
+                                                             int tokens, int E, int K, int renorm, float aux_coef, float z_coef) {
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const float da = d_aux ? __ldg(d_aux) : 0.f;
+    const float aux_grad = da * aux_coef * static_cast<float>(E) / (static_cast<float>(tokens) * static_cast<float>(tokens));
+    const float z_grad = da * z_coef * 2.f / static_cast<float>(tokens);
+    float cnt[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int e = i * 32 + lane;
+        cnt[i] = (e < E && counts) ? static_cast<float>(counts[e]) : 0.f;
+    }
+    for (int tok = blockIdx.x * wpb + (threadIdx.x >> 5); tok < tokens; tok += gridDim.x * wpb) {
+        float p[VPL], dp[VPL];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int e = i * 32 + lane;
+            p[i] = e < E ? logits[static_cast<size_t>(tok) * E + e] : -INFINITY;
+            mx = fmaxf(mx, p[i]);
+        }
+        mx = wmax(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) { p[i] = (i * 32 + lane < E) ? __expf(p[i] - mx) : 0.f; sum += p[i]; }
+        sum = wsum(sum);
+        const float inv = 1.f / sum, lse = mx + __logf(sum);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) { p[i] *= inv; dp[i] = aux_grad * cnt[i]; }
+        // lane k < K owns the k-th selected expert of the token
+        const int my_idx = lane < K ? topk_idx[static_cast<size_t>(tok) * K + lane] : -1;
+        const float my_g = (lane < K && d_topk_w) ? d_topk_w[static_cast<size_t>(tok) * K + lane] : 0.f;
+        float my_sel = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const int e = __shfl_sync(0xffffffffu, my_idx, k);
+            float v = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i)
+                if (i * 32 + lane == e) v = p[i];
+            v = wsum(v);                          // probability of the k-th selected expert, in every lane
+            if (lane == k) my_sel = v;
+        }
+        float d_sel = my_g;
+        if (renorm) {
+            const float S = wsum(my_sel), gs = wsum(my_g * my_sel);
+            d_sel = my_g / S - gs / (S * S);
+        }
+        for (int k = 0; k < K; ++k) {
+            const int e = __shfl_sync(0xffffffffu, my_idx, k);
+            const float d = __shfl_sync(0xffffffffu, d_sel, k);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i)
+                if (i * 32 + lane == e) dp[i] += d;
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) dot += dp[i] * p[i];
+        dot = wsum(dot);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int e = i * 32 + lane;
+            if (e < E) d_logits[static_cast<size_t>(tok) * E + e] = __float2bfloat16(p[i] * (dp[i] - dot) + z_grad * lse * p[i]);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------ padded offsets
 // offsets[e] = sum_{j<e} round_up(counts[j], 128); one block, warp-level scan.  Also zeroes the per-expert cursors.
 __global__ void __launch_bounds__(256) moe_offsets_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ cursors, int E,
@@ -259,6 +334,14 @@ void moe_unpermute(const void* yp, const float* w, const int* row_map, void* y, 
 void moe_unpermute_bwd(const void* dy, const void* yp, const float* w, const int* row_map, void* d_yp, float* d_w, int tokens, int C, int K,
                        cudaStream_t s) {
     moe_unpermute_bwd_kernel<<<tokens, 256, 0, s>>>((const bf16*)dy, (const bf16*)yp, w, row_map, (bf16*)d_yp, d_w, C, K);
+}
+
+void moe_router_bwd(const float* logits, const int* topk_idx, const float* d_topk_w, const int* counts, const float* d_aux, void* d_logits, int tokens,
+                    int E, int K, int renorm, float aux_coef, float z_coef, int num_sms, cudaStream_t s) {
+    const int blocks = min((tokens + 7) / 8, num_sms * 8);
+#define SG_RB(V) moe_router_bwd_kernel<V><<<blocks, 256, 0, s>>>(logits, topk_idx, d_topk_w, counts, d_aux, (bf16*)d_logits, tokens, E, K, renorm, aux_coef, z_coef)
+    if (E <= 32) SG_RB(1); else if (E <= 64) SG_RB(2); else if (E <= 128) SG_RB(4); else SG_RB(8);
+#undef SG_RB
 }
 
 }  // namespace sg

@@ -102,6 +102,48 @@ __device__ __forceinline__ uint8_t quant_block16(const float (&v)[16], float ge,
     return sfb;
 }
 
+// Four-over-six (round to nearest only): the block is quantised twice, once with its abs-max mapped to the top grid value 6 and
+// once mapped to 4 (the grid {0, .5, 1, 1.5, 2, 3, 4} then has no gap between 4 and 6 to fall into), and the mapping with the smaller
+// squared reconstruction error is kept.  `err_group` > 1 shares the decision between that many adjacent lanes (16 for the 16 x 16
+// weight tiles, whose rows must agree on one scale).  The tensor encode factor is 1536 (= 256 * 6 = 384 * 4), so that both block
+// scales stay inside the UE4M3 range.
+__device__ __forceinline__ uint8_t quant_block16_4o6(const float (&v)[16], float ge, float forced_amax, uint32_t (&out)[2], int err_group) {
+    float amax = forced_amax;
+    if (forced_amax < 0.f) {
+        amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+    uint8_t sfb[2];
+    uint32_t codes[2][2];
+    float err[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        sfb[t] = __nv_cvt_float_to_fp8(__fdiv_rn(__fmul_rn(amax, ge), t == 0 ? 6.f : 4.f), __NV_SATFINITE, __NV_E4M3);
+        const float sfd = decode_e4m3(sfb[t]);
+        const float mul = sfd > 0.f ? ge / sfd : 0.f;
+        codes[t][0] = codes[t][1] = 0;
+        float e = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float s = v[i] * mul;
+            const uint32_t c = e2m1_rn(s);
+            const float d = (e2m1_value(c) - s) * sfd;      // error in units of x * ge
+            e += d * d;
+            codes[t][i >> 3] |= c << ((i & 7) * 4);
+        }
+        err[t] = e;
+    }
+    for (int o = err_group >> 1; o > 0; o >>= 1) {
+        err[0] += __shfl_xor_sync(0xffffffffu, err[0], o);
+        err[1] += __shfl_xor_sync(0xffffffffu, err[1], o);
+    }
+    const int pick = err[1] < err[0] ? 1 : 0;
+    out[0] = codes[pick][0];
+    out[1] = codes[pick][1];
+    return sfb[pick];
+}
+
 __device__ __forceinline__ void load16(const bf16* p, float (&v)[16]) {
     const uint4 a = *reinterpret_cast<const uint4*>(p), b = *reinterpret_cast<const uint4*>(p + 8);
     const bf162* pa = reinterpret_cast<const bf162*>(&a);
@@ -138,9 +180,9 @@ __device__ __forceinline__ void hadamard16(float (&v)[16], uint32_t sign_mask) {
 template <bool SR>
 __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                                                   const float* __restrict__ amax_tensor, int rows, int K, int atoms_k, uint32_t seed,
-                                                                  int block2d) {
+                                                                  int block2d, int four_over_six) {
     const float at = __ldg(amax_tensor);
-    const float ge = at > 0.f ? __fdiv_rn(2688.f, at) : 1.f;
+    const float ge = at > 0.f ? __fdiv_rn(four_over_six ? 1536.f : 2688.f, at) : 1.f;
     const int kblocks = K / 16;
     const size_t total = static_cast<size_t>(rows) * kblocks;
     // warp-uniform trip count: the 16x16-tile path shuffles across lanes
@@ -171,9 +213,15 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
             for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             forced = m;
         }
-        if (!live) continue;
         uint32_t out[2];
-        const uint8_t sfb = quant_block16<SR>(v, ge, forced, seed, static_cast<uint64_t>(r) * K + kb * 16, out);
+        uint8_t sfb;
+        if (!SR && four_over_six) {
+            sfb = quant_block16_4o6(v, ge, forced, out, block2d ? 16 : 1);   // before the `live` test: the tile decision is a lane shuffle
+            if (!live) continue;
+        } else {
+            if (!live) continue;
+            sfb = quant_block16<SR>(v, ge, forced, seed, static_cast<uint64_t>(r) * K + kb * 16, out);
+        }
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * (K / 2) + kb * 8) = make_uint2(out[0], out[1]);
         sf[sf_offset(r, kb, atoms_k)] = sfb;
     }
@@ -184,7 +232,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const bf16* __
 template <bool SR, bool RHT>
 __global__ void __launch_bounds__(256) nvfp4_quantize_transpose_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                                                        const float* __restrict__ amax_tensor, int R, int C, int atoms_k, uint32_t seed,
-                                                                       uint32_t sign_mask) {
+                                                                       uint32_t sign_mask, int four_over_six) {
     __shared__ float tile[64][65];
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     for (int i = threadIdx.x; i < 64 * 8; i += blockDim.x) {   // 64 rows x 8 vectors of 8
@@ -201,7 +249,8 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_transpose_kernel(const bf1
     __syncthreads();
     const float at = __ldg(amax_tensor);
     // the Hadamard transform is orthonormal, so the tensor abs-max bound grows by at most 4x; keep head-room for it
-    const float ge = at > 0.f ? (RHT ? 2688.f / (at * 2.f) : 2688.f / at) : 1.f;
+    const float enc = (!SR && four_over_six) ? 1536.f : 2688.f;
+    const float ge = at > 0.f ? (RHT ? enc / (at * 2.f) : enc / at) : 1.f;
     const int c = threadIdx.x & 63, rb = threadIdx.x >> 6;   // column, 16-row block within the tile
     float v[16];
 #pragma unroll
@@ -209,7 +258,8 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_transpose_kernel(const bf1
     if (RHT) hadamard16(v, sign_mask);
     uint32_t out[2];
     const int kb = (r0 >> 4) + rb;
-    const uint8_t sfb = quant_block16<SR>(v, ge, -1.f, seed, static_cast<uint64_t>(c0 + c) * R + r0 + rb * 16, out);
+    const uint8_t sfb = (!SR && four_over_six) ? quant_block16_4o6(v, ge, -1.f, out, 1)
+                                                : quant_block16<SR>(v, ge, -1.f, seed, static_cast<uint64_t>(c0 + c) * R + r0 + rb * 16, out);
     *reinterpret_cast<uint2*>(q + static_cast<size_t>(c0 + c) * (R / 2) + (r0 + rb * 16) / 2) = make_uint2(out[0], out[1]);
     sf[sf_offset(c0 + c, kb, atoms_k)] = sfb;
 }
@@ -217,9 +267,9 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_transpose_kernel(const bf1
 // ------------------------------------------------------------------------------------------ dequantise
 __global__ void __launch_bounds__(256) nvfp4_dequantize_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                                                const float* __restrict__ amax_tensor, float amax_div, bf16* __restrict__ out, int rows,
-                                                               int K, int atoms_k) {
+                                                               int K, int atoms_k, float encode) {
     const float at = __ldg(amax_tensor);
-    const float inv_ge = at > 0.f ? at * amax_div / 2688.f : 1.f;
+    const float inv_ge = at > 0.f ? at * amax_div / encode : 1.f;
     const int kblocks = K / 16;
     const size_t total = static_cast<size_t>(rows) * kblocks;
     for (size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; b < total; b += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -242,28 +292,29 @@ static int q_grid(size_t items, int num_sms) {
     return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
 }
 void nvfp4_quantize_rows(const void* x, void* q, void* sf, const float* amax_tensor, int rows, int K, int stochastic, uint32_t seed, int block2d,
-                         int num_sms, cudaStream_t s) {
+                         int num_sms, cudaStream_t s, int four_over_six) {
     const int atoms_k = (K / 16 + 3) / 4;
     const int grid = q_grid(static_cast<size_t>(rows) * (K / 16), num_sms);
-    if (stochastic) nvfp4_quantize_rows_kernel<true><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, amax_tensor, rows, K, atoms_k, seed, block2d);
-    else nvfp4_quantize_rows_kernel<false><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, amax_tensor, rows, K, atoms_k, seed, block2d);
+    if (stochastic) nvfp4_quantize_rows_kernel<true><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, amax_tensor, rows, K, atoms_k, seed, block2d, 0);
+    else nvfp4_quantize_rows_kernel<false><<<grid, 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, amax_tensor, rows, K, atoms_k, seed, block2d, four_over_six);
 }
 void nvfp4_quantize_transpose(const void* x, void* q, void* sf, const float* amax_tensor, int R, int C, int stochastic, int hadamard, uint32_t seed,
-                              uint32_t sign_mask, cudaStream_t s) {
+                              uint32_t sign_mask, cudaStream_t s, int four_over_six) {
     const int atoms_k = (R / 16 + 3) / 4;
     const dim3 grid(C / 64, R / 64);
     const bf16* xp = (const bf16*)x;
     uint8_t* qp = (uint8_t*)q;
     uint8_t* sp = (uint8_t*)sf;
-    if (stochastic && hadamard) nvfp4_quantize_transpose_kernel<true, true><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask);
-    else if (stochastic) nvfp4_quantize_transpose_kernel<true, false><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask);
-    else if (hadamard) nvfp4_quantize_transpose_kernel<false, true><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask);
-    else nvfp4_quantize_transpose_kernel<false, false><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask);
+    if (stochastic && hadamard) nvfp4_quantize_transpose_kernel<true, true><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask, four_over_six);
+    else if (stochastic) nvfp4_quantize_transpose_kernel<true, false><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask, four_over_six);
+    else if (hadamard) nvfp4_quantize_transpose_kernel<false, true><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask, four_over_six);
+    else nvfp4_quantize_transpose_kernel<false, false><<<grid, 256, 0, s>>>(xp, qp, sp, amax_tensor, R, C, atoms_k, seed, sign_mask, four_over_six);
 }
-void nvfp4_dequantize(const void* q, const void* sf, const float* amax_tensor, float amax_div, void* out, int rows, int K, int num_sms, cudaStream_t s) {
+void nvfp4_dequantize(const void* q, const void* sf, const float* amax_tensor, float amax_div, void* out, int rows, int K, int num_sms, cudaStream_t s,
+                      float encode) {
     const int atoms_k = (K / 16 + 3) / 4;
     nvfp4_dequantize_kernel<<<q_grid(static_cast<size_t>(rows) * (K / 16), num_sms), 256, 0, s>>>((const uint8_t*)q, (const uint8_t*)sf, amax_tensor,
-                                                                                                  amax_div, (bf16*)out, rows, K, atoms_k);
+                                                                                                  amax_div, (bf16*)out, rows, K, atoms_k, encode);
 }
 
 }  // namespace sg

@@ -325,7 +325,8 @@ def _ep_combine(b, op, dy):
 def _moe_gg(b, op, dy):
     x, w, plan = op.inputs
     g = b.new_grad(x)
-    b.emit("moe_grouped_gemm_backward", [dy[0], b.fwd_tensor(x), w, b.fwd_tensor(plan)], [g, b.param_grad(w)], role=op.attrs.get("role", ""))
+    b.emit("moe_grouped_gemm_backward", [dy[0], b.fwd_tensor(x), w, b.fwd_tensor(plan)], [g, b.param_grad(w)], role=op.attrs.get("role", ""),
+           fwd_out=op.outputs[0])
     return {x: g}
 
 

@@ -24,6 +24,16 @@ NF4_LEVELS = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.394917488098144
 E2M1_LEVELS = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
 
 
+def _cuda_ext(t: torch.Tensor):
+    """The kernel extension when ``t`` lives on a GPU (QLoRA rebuilds every frozen layer twice per step: that runs on the CUDA
+    dequantisers of csrc/qlora_kernels.cu); None on CPU, where the PyTorch statements below are used."""
+    if not t.is_cuda:
+        return None
+    from ..ops import ext
+
+    return ext()
+
+
 def _pack4(codes: torch.Tensor) -> torch.Tensor:
     c = codes.reshape(-1, 2).to(torch.uint8)
     return (c[:, 0] | (c[:, 1] << 4)).contiguous()
@@ -74,6 +84,18 @@ class BnbNF4:
         return (a.reshape(-1)[:nb] + st["absmax_offset"])
 
     def dequantize(self, st, dtype=torch.bfloat16) -> torch.Tensor:
+        e = _cuda_ext(st["codes"])
+        n = st["codes"].numel() * 2
+        if e is not None and n % 8 == 0 and self.block % 8 == 0:
+            if "absmax" in st:
+                out = e.dequant_blockwise("bnb_nf4", st["codes"], st["absmax"].float().contiguous(), None, None, n, self.block)
+            else:
+                out = e.dequant_blockwise("bnb_nf4", st["codes"], st["absmax_q"].contiguous(), st["absmax_scale"].float().contiguous(),
+                                          st["absmax_offset"].float().contiguous(), n, self.block)
+            return out if dtype == torch.bfloat16 else out.to(dtype)
+        return self.dequantize_reference(st, dtype)
+
+    def dequantize_reference(self, st, dtype=torch.bfloat16) -> torch.Tensor:
         lv = torch.tensor(NF4_LEVELS, device=st["codes"].device)
         v = lv[_unpack4(st["codes"]).long()].reshape(-1, self.block) * self._absmax(st)[:, None]
         return v.reshape(-1).to(dtype)
@@ -96,6 +118,13 @@ class BlockFP8:
         return {"q": (xb / scale[:, None]).to(torch.float8_e4m3fn).reshape(-1), "scale": scale}
 
     def dequantize(self, st, dtype=torch.bfloat16) -> torch.Tensor:
+        e = _cuda_ext(st["q"])
+        if e is not None and st["q"].numel() % 8 == 0:
+            out = e.dequant_blockwise("fp8_block", st["q"].contiguous(), st["scale"].float().contiguous(), None, None, st["q"].numel(), self.block)
+            return out if dtype == torch.bfloat16 else out.to(dtype)
+        return self.dequantize_reference(st, dtype)
+
+    def dequantize_reference(self, st, dtype=torch.bfloat16) -> torch.Tensor:
         return (st["q"].float().reshape(-1, self.block) * st["scale"][:, None]).reshape(-1).to(dtype)
 
     @staticmethod
@@ -128,7 +157,9 @@ class NVFP4Storage:
         assert x.numel() % 16 == 0
         xb = x.reshape(-1, 16).float()
         g = xb.abs().max().clamp_min(1e-12)
-        ge = (448.0 * 6.0) / g
+        # tensor encode factor: 2688 = 448 * 6 for plain NVFP4; 1536 = 256 * 6 = 384 * 4 with four-over-six, so that the block scale of
+        # either mapping stays inside the UE4M3 range (arXiv 2512.02010)
+        ge = (1536.0 if self.four_over_six else 448.0 * 6.0) / g
         idx, sf, deq = self._quant_blocks(xb, ge, 6.0)
         if self.four_over_six:  # per block, keep whichever of max=6 / max=4 mapping reconstructs better
             idx4, sf4, deq4 = self._quant_blocks(xb, ge, 4.0)
@@ -139,6 +170,14 @@ class NVFP4Storage:
         return {"codes": _pack4((idx.to(torch.uint8) | sign).reshape(-1)), "sf": sf.to(torch.float8_e4m3fn), "ge_inv": (1.0 / ge).reshape(1)}
 
     def dequantize(self, st, dtype=torch.bfloat16) -> torch.Tensor:
+        e = _cuda_ext(st["codes"])
+        n = st["codes"].numel() * 2
+        if e is not None and n % 16 == 0:
+            out = e.dequant_blockwise("nvfp4", st["codes"], st["sf"].contiguous().view(torch.uint8), st["ge_inv"].float().contiguous(), None, n, 16)
+            return out if dtype == torch.bfloat16 else out.to(dtype)
+        return self.dequantize_reference(st, dtype)
+
+    def dequantize_reference(self, st, dtype=torch.bfloat16) -> torch.Tensor:
         lv = torch.tensor(E2M1_LEVELS, device=st["codes"].device)
         c = _unpack4(st["codes"])
         v = lv[(c & 7).long()] * torch.where((c & 8) > 0, -1.0, 1.0)
@@ -153,6 +192,14 @@ class MXFP4:
     name = "mxfp4"
 
     def dequantize(self, st, dtype=torch.bfloat16) -> torch.Tensor:
+        e = _cuda_ext(st["blocks"])
+        n = st["blocks"].numel() * 2
+        if e is not None and n % 32 == 0:
+            out = e.dequant_blockwise("mxfp4", st["blocks"].reshape(-1).contiguous(), st["scales"].reshape(-1).contiguous(), None, None, n, 32)
+            return out if dtype == torch.bfloat16 else out.to(dtype)
+        return self.dequantize_reference(st, dtype)
+
+    def dequantize_reference(self, st, dtype=torch.bfloat16) -> torch.Tensor:
         lv = torch.tensor(E2M1_LEVELS, device=st["blocks"].device)
         c = _unpack4(st["blocks"].reshape(-1))
         v = lv[(c & 7).long()] * torch.where((c & 8) > 0, -1.0, 1.0)

@@ -2,6 +2,9 @@
 
 Per dense projection (qkv, out, mlp_up, mlp_down) all three GEMMs run on the block-scaled tcgen05 kernel:
 
+Round-to-nearest operands use four-over-six block scaling (``fp4_four_over_six``, on by default): each block of 16 is quantised with
+its abs-max mapped to 6 and to 4 and the better reconstruction is kept (tensor encode factor 1536; arXiv 2512.02010).
+
 * forward : x (row-wise blocks along K, round-to-nearest) . W (16x16 blocks) ^T
 * dgrad   : dy (blocks along N, stochastic rounding) . W^T (the transposed quantisation of the same 16x16 blocks)
 * wgrad   : dy^T . x^T with both operands passed through the same 16x16 random Hadamard transform along the token
@@ -26,7 +29,8 @@ from .base import Recipe
 from .grouped_fp8 import GroupedFp8Mixin
 
 QUANT_ROLES = ("qkv", "out", "mlp_up", "mlp_down")
-ENCODE = 2688.0
+ENCODE = 2688.0          # 448 * 6: tensor encode factor of plain NVFP4
+ENCODE_4O6 = 1536.0      # 256 * 6 = 384 * 4: with four-over-six both block-scale choices stay inside UE4M3
 HADAMARD_SIGNS = 0b1011001110001101
 
 
@@ -40,7 +44,8 @@ class Fp4Tensor:
 class NVFP4Recipe(GroupedFp8Mixin, Recipe):
     name = "nvfp4"
 
-    def __init__(self, cm, device, skip_first_layers: int = 0, skip_last_layers: int = 0, hadamard: bool = True, stochastic: bool = True):
+    def __init__(self, cm, device, skip_first_layers: int = 0, skip_last_layers: int = 0, hadamard: bool = True, stochastic: bool = True,
+                 four_over_six: bool = True):
         from ..ops import ext
 
         self.ext = ext()
@@ -48,6 +53,9 @@ class NVFP4Recipe(GroupedFp8Mixin, Recipe):
         self.n_layers = cm.n_layers
         self.skip = set(range(skip_first_layers)) | set(range(cm.n_layers - skip_last_layers, cm.n_layers))
         self.hadamard, self.stochastic = hadamard, stochastic
+        # round-to-nearest operands (activations and weights in forward, x^T in wgrad) pick, per block of 16, whichever of the two
+        # mappings abs-max -> 6 and abs-max -> 4 reconstructs the block better; stochastically rounded gradients keep the plain mapping
+        self.four_over_six = bool(four_over_six)
         self.weight_cache: Dict[Tuple[int, str, bool], Fp4Tensor] = {}
         self.expert_weight_cache: Dict[Tuple[int, str], tuple] = {}
         self.step = 0
@@ -77,14 +85,16 @@ class NVFP4Recipe(GroupedFp8Mixin, Recipe):
     def _q_rows(self, x: torch.Tensor, sr: bool = False, block2d: bool = False) -> Fp4Tensor:
         x = x.contiguous()
         am = self._amax(x)
-        q, sf = self.ext.nvfp4_quantize(x, am, sr, self._seed() if sr else 0, block2d)
-        return Fp4Tensor(q, sf, am / ENCODE)
+        fos = self.four_over_six and not sr
+        q, sf = self.ext.nvfp4_quantize(x, am, sr, self._seed() if sr else 0, block2d, fos)
+        return Fp4Tensor(q, sf, am / (ENCODE_4O6 if fos else ENCODE))
 
     def _q_transpose(self, x: torch.Tensor, sr: bool, rht: bool) -> Fp4Tensor:
         x = x.contiguous()
         am = self._amax(x)
-        q, sf = self.ext.nvfp4_quantize_transpose(x, am, sr, rht, self._seed() if sr else 0, HADAMARD_SIGNS)
-        return Fp4Tensor(q, sf, am * (2.0 if rht else 1.0) / ENCODE)
+        fos = self.four_over_six and not sr
+        q, sf = self.ext.nvfp4_quantize_transpose(x, am, sr, rht, self._seed() if sr else 0, HADAMARD_SIGNS, fos)
+        return Fp4Tensor(q, sf, am * (2.0 if rht else 1.0) / (ENCODE_4O6 if fos else ENCODE))
 
     def _weight(self, ctx, role: str, w: torch.Tensor, transposed: bool) -> Fp4Tensor:
         key = (ctx.layer, role, transposed)

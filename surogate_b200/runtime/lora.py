@@ -1,4 +1,4 @@
-"""LoRA on the fused projection weights.
+"""LoRA on the fused projection weights and on the per-expert matrices of MoE layers.
 
 Each target module (q/k/v/o/gate/up/down) is a row slice of a fused internal weight.  For one fused matmul
 with input ``x`` the adapters of all its targets share the first GEMM: ``h = x . A_cat^T`` with
@@ -6,6 +6,11 @@ with input ``x`` the adapters of all its targets share the first GEMM: ``h = x .
 column slice of the output through the GEMM's accumulate epilogue on a strided view.  Backward mirrors it
 with four small GEMMs.  On a GPU every one of these runs on the tcgen05 GEMM (small-N / small-K shapes use
 its zero-filled tiles); on CPU plain matmuls.
+
+Expert stacks ([E, N, K] parameters: ``experts_gate_up`` with the up / gate slices, ``experts_down``) get one adapter pair per expert,
+stored as [E, r, K] / [E, rows, r]; their forward and backward run as grouped GEMMs over the same expert row offsets as the base
+projections (csrc/src/runtime/lora/fast_expert_lora.h in the reference), and they export under
+``...layers.L.mlp.experts.E.up_proj.lora_A.weight`` style keys.
 
 Adapters are replicated across data-parallel ranks; their gradients are summed with one all-reduce of a flat
 buffer, and the optimizer (AdamW fp32 or 8-bit state) runs on that flat buffer.  Masters are fp32 by default.
@@ -42,8 +47,9 @@ class _Target:
 class _Group:
     """All adapters attached to one fused weight of one layer."""
 
-    def __init__(self, layer: int, param: str, in_features: int, targets: List[_Target]):
+    def __init__(self, layer: int, param: str, in_features: int, targets: List[_Target], experts: int = 0):
         self.layer, self.param, self.in_features, self.targets = layer, param, in_features, targets
+        self.experts = experts   # > 0: a stack of per-expert matrices [E, N, K]; every expert has its own A [r, K] and B [rows, r]
 
 
 class LoRAManager:
@@ -62,19 +68,21 @@ class LoRAManager:
         r = self.rank_dim
         n = 0
         for p in cm.params:
-            if p.layer is None or not p.spec.lora_targets or len(p.spec.shape) != 2:
+            if p.layer is None or not p.spec.lora_targets or len(p.spec.shape) not in (2, 3):
                 continue
+            E = p.spec.shape[0] if len(p.spec.shape) == 3 else 0   # expert stacks: one adapter pair per expert, stored [E, r, K] / [E, rows, r]
+            K = p.spec.shape[-1]
             tl = []
             for tname, off, rows in p.spec.lora_targets:
                 if tname not in self.wanted:
                     continue
                 a_off = n
-                n += r * p.spec.shape[1]
+                n += max(1, E) * r * K
                 b_off = n
-                n += rows * r
+                n += max(1, E) * rows * r
                 tl.append(_Target(tname, off, rows, a_off, b_off))
             if tl:
-                self.groups[(p.layer, p.local)] = _Group(p.layer, p.local, p.spec.shape[1], tl)
+                self.groups[(p.layer, p.local)] = _Group(p.layer, p.local, K, tl, experts=E)
         self.numel = (n + 127) // 128 * 128
         self.master = torch.zeros(self.numel, dtype=self.master_dtype, device=device)
         self.grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
@@ -97,6 +105,12 @@ class LoRAManager:
     def _B(self, buf, t: _Target):
         return buf[t.b_off:t.b_off + t.rows * self.rank_dim].view(t.rows, self.rank_dim)
 
+    def _EA(self, buf, g: _Group, t: _Target):
+        return buf[t.a_off:t.a_off + g.experts * self.rank_dim * g.in_features].view(g.experts, self.rank_dim, g.in_features)
+
+    def _EB(self, buf, g: _Group, t: _Target):
+        return buf[t.b_off:t.b_off + g.experts * t.rows * self.rank_dim].view(g.experts, t.rows, self.rank_dim)
+
     def _A_cat(self, buf, g: _Group):
         """A matrices of one group are contiguous in the flat buffer only if interleaved B's are skipped: build views."""
         return [self._A(buf, g, t) for t in g.targets]
@@ -108,7 +122,7 @@ class LoRAManager:
         for g in self.groups.values():
             bound = 1.0 / math.sqrt(g.in_features)
             for t in g.targets:
-                n = self.rank_dim * g.in_features
+                n = max(1, g.experts) * self.rank_dim * g.in_features
                 flat[t.a_off:t.a_off + n] = (torch.rand(n, generator=gen) * 2 - 1) * bound
         self.master.copy_(flat.to(self.master_dtype))
         self.sync_work()
@@ -128,7 +142,7 @@ class LoRAManager:
 
     def forward(self, ctx, op, x, y):
         g = self.groups.get((ctx.layer, op.inputs[1])) if ctx.layer is not None else None
-        if g is None:
+        if g is None or g.experts:
             return y
         if hasattr(x, "scale_inv"):
             x = x.hp if x.hp is not None else x.dequantize()
@@ -158,7 +172,7 @@ class LoRAManager:
     def backward(self, ctx, op, dy2, x2):
         """Accumulates adapter gradients; returns the extra d_x contribution (or None)."""
         g = self.groups.get((ctx.layer, op.inputs[2])) if ctx.layer is not None else None
-        if g is None:
+        if g is None or g.experts:
             return None
         if hasattr(x2, "scale_inv"):
             x2 = x2.hp if x2.hp is not None else x2.dequantize()
@@ -199,6 +213,102 @@ class LoRAManager:
             dx = dx * mask
         return dx
 
+    # ------------------------------------------------------------------ per-expert adapters (grouped GEMM ops of MoE layers)
+    def _local_expert_range(self, ctx, g: _Group, groups: int):
+        """Global ids [e0, e0 + groups) of the experts whose rows this rank's grouped GEMM sees.  Adapters are kept for all experts on
+        every rank (their gradients are summed like the dense adapters'); under expert parallelism a rank trains its own experts'
+        slices, which assumes the identity expert placement (adapters do not travel with re-placed experts)."""
+        ep = getattr(ctx, "ep", None)
+        if ep is None or groups == g.experts:
+            return 0
+        if getattr(ep, "placement", None):
+            raise RuntimeError("per-expert LoRA under expert parallelism needs the identity expert placement (ep_plan_refresh_interval: 0)")
+        return ep.rank * groups
+
+    def _ggemm(self, a, b, out, offsets, mode, b_mn=False, accumulate=False, alpha=1.0):
+        from ..ops import ext
+
+        e = ext()
+        e.gemm_grouped(a.contiguous(), b.contiguous(), out, offsets, mode, b_mn, accumulate, float(alpha), None, None, e.error_flag_tensor())
+        return out
+
+    def forward_grouped(self, ctx, op, x, y, plan):
+        """y[rows of expert e, slice t] += s * (x A_e,t^T) B_e,t^T for every adapted slice of an expert stack."""
+        g = self.groups.get((ctx.layer, op.inputs[1])) if ctx.layer is not None else None
+        if g is None or not g.experts:
+            return y
+        p = getattr(plan, "ep_plan", None) or getattr(plan, "local", None) or plan
+        offsets = p.offsets
+        G = offsets.numel() - 1 if not hasattr(p, "layout") else (p.layout.numel() - 2) // 2
+        offsets = offsets[:G + 1]
+        e0 = self._local_expert_range(ctx, g, G)
+        r, T = self.rank_dim, len(g.targets)
+        a_cat = torch.cat([self._EA(self.work, g, t)[e0:e0 + G] for t in g.targets], dim=1)     # [G, T*r, K]
+        kernels = self.use_kernels and x.dtype == torch.bfloat16 and a_cat.dtype == torch.bfloat16
+        if kernels:
+            h = self._ggemm(x, a_cat, torch.zeros(x.shape[0], T * r, dtype=x.dtype, device=x.device), offsets, 1)
+            for i, t in enumerate(g.targets):
+                d = self._ggemm(h[:, i * r:(i + 1) * r], self._EB(self.work, g, t)[e0:e0 + G], torch.zeros(x.shape[0], t.rows, dtype=x.dtype, device=x.device),
+                                offsets, 1, alpha=self.scaling)
+                y[:, t.row_off:t.row_off + t.rows] += d
+        else:
+            off = offsets.tolist()   # host sync: reference path only
+            h = torch.zeros(x.shape[0], T * r, dtype=x.dtype, device=x.device)
+            for e in range(G):
+                s0, s1 = off[e], off[e + 1]
+                if s1 <= s0:
+                    continue
+                h[s0:s1] = x[s0:s1] @ a_cat[e].to(x.dtype).t()
+                for i, t in enumerate(g.targets):
+                    y[s0:s1, t.row_off:t.row_off + t.rows] += (h[s0:s1, i * r:(i + 1) * r] @ self._EB(self.work, g, t)[e0 + e].to(x.dtype).t()) * self.scaling
+        ctx.stash[("lora_gh", ctx.layer, op.outputs[0])] = h
+        return y
+
+    def backward_grouped(self, ctx, op, dy, x, plan):
+        """Adapter gradients of an expert stack; returns the extra d_x (or None)."""
+        g = self.groups.get((ctx.layer, op.inputs[2])) if ctx.layer is not None else None
+        if g is None or not g.experts:
+            return None
+        p = getattr(plan, "ep_plan", None) or getattr(plan, "local", None) or plan
+        offsets = p.offsets
+        G = offsets.numel() - 1 if not hasattr(p, "layout") else (p.layout.numel() - 2) // 2
+        offsets = offsets[:G + 1]
+        e0 = self._local_expert_range(ctx, g, G)
+        r, T = self.rank_dim, len(g.targets)
+        a_cat = torch.cat([self._EA(self.work, g, t)[e0:e0 + G] for t in g.targets], dim=1)
+        h = ctx.stash.pop(("lora_gh", ctx.layer, op.attrs.get("fwd_out")), None)
+        kernels = self.use_kernels and x.dtype == torch.bfloat16 and a_cat.dtype == torch.bfloat16 and dy.dtype == torch.bfloat16
+        if kernels:
+            if h is None:
+                h = self._ggemm(x, a_cat, torch.zeros(x.shape[0], T * r, dtype=x.dtype, device=x.device), offsets, 1)
+            dh = torch.zeros_like(h)
+            for i, t in enumerate(g.targets):
+                dys = dy[:, t.row_off:t.row_off + t.rows].contiguous()
+                ht = h[:, i * r:(i + 1) * r].contiguous()
+                dh_t = self._ggemm(dys, self._EB(self.work, g, t)[e0:e0 + G], torch.zeros(x.shape[0], r, dtype=x.dtype, device=x.device), offsets, 1,
+                                   b_mn=True, alpha=self.scaling)                                    # s * dy_slice . B_e
+                dh[:, i * r:(i + 1) * r] = dh_t
+                self._ggemm(dys, ht, self._EB(self.grad, g, t)[e0:e0 + G], offsets, 2, b_mn=True, accumulate=True, alpha=self.scaling)   # dB_e += s dy^T h
+                self._ggemm(dh_t, x, self._EA(self.grad, g, t)[e0:e0 + G], offsets, 2, b_mn=True, accumulate=True)                        # dA_e += dh^T x
+            return self._ggemm(dh, a_cat, torch.zeros_like(x), offsets, 1, b_mn=True)
+        off = offsets.tolist()
+        dx = torch.zeros_like(x)
+        for e in range(G):
+            s0, s1 = off[e], off[e + 1]
+            if s1 <= s0:
+                continue
+            xe = x[s0:s1]
+            he = h[s0:s1] if h is not None else xe @ a_cat[e].to(x.dtype).t()
+            dhe = torch.zeros_like(he)
+            for i, t in enumerate(g.targets):
+                dys = dy[s0:s1, t.row_off:t.row_off + t.rows]
+                Be = self._EB(self.work, g, t)[e0 + e].to(dy.dtype)
+                dhe[:, i * r:(i + 1) * r] = (dys @ Be) * self.scaling
+                self._EB(self.grad, g, t)[e0 + e] += ((dys.t() @ he[:, i * r:(i + 1) * r]) * self.scaling).float()
+                self._EA(self.grad, g, t)[e0 + e] += (dhe[:, i * r:(i + 1) * r].t() @ xe).float()
+            dx[s0:s1] = dhe @ a_cat[e].to(x.dtype)
+        return dx
+
     def _acc(self, off: int, g: torch.Tensor) -> None:
         self.grad[off:off + g.numel()] += g.reshape(-1).float()
 
@@ -233,9 +343,19 @@ class LoRAManager:
     def _hf_key(self, layer: int, target: str, which: str) -> str:
         return f"base_model.model.model.layers.{layer}.{_MODULE_PATH[target]}.lora_{which}.weight"
 
+    def _hf_expert_key(self, layer: int, expert: int, target: str, which: str) -> str:
+        return f"base_model.model.model.layers.{layer}.mlp.experts.{expert}.{target}.lora_{which}.weight"
+
     def adapter_tensors(self) -> Dict[str, torch.Tensor]:
         out = {}
         for g in self.groups.values():
+            if g.experts:
+                for t in g.targets:
+                    A, B = self._EA(self.master, g, t).detach().float().cpu(), self._EB(self.master, g, t).detach().float().cpu()
+                    for e in range(g.experts):
+                        out[self._hf_expert_key(g.layer, e, t.name, "A")] = A[e].contiguous()
+                        out[self._hf_expert_key(g.layer, e, t.name, "B")] = B[e].contiguous()
+                continue
             for t in g.targets:
                 out[self._hf_key(g.layer, t.name, "A")] = self._A(self.master, g, t).detach().float().cpu().contiguous()
                 out[self._hf_key(g.layer, t.name, "B")] = self._B(self.master, t).detach().float().cpu().contiguous()
@@ -262,6 +382,15 @@ class LoRAManager:
         with safe_open(fn, framework="pt") as f:
             keys = set(f.keys())
             for g in self.groups.values():
+                if g.experts:
+                    for t in g.targets:
+                        for e in range(g.experts):
+                            ka, kb = self._hf_expert_key(g.layer, e, t.name, "A"), self._hf_expert_key(g.layer, e, t.name, "B")
+                            if ka in keys:
+                                self._EA(self.master, g, t)[e].copy_(f.get_tensor(ka).to(self.master.dtype))
+                            if kb in keys:
+                                self._EB(self.master, g, t)[e].copy_(f.get_tensor(kb).to(self.master.dtype))
+                    continue
                 for t in g.targets:
                     ka, kb = self._hf_key(g.layer, t.name, "A"), self._hf_key(g.layer, t.name, "B")
                     if ka in keys:
@@ -294,6 +423,9 @@ class LoRAManager:
             name = f"blocks.{g.layer}.{g.param}"
             w = store.full_tensor(name).float().clone()
             for t in g.targets:
+                if g.experts:   # [E, rows, r] x [E, r, K]
+                    w[:, t.row_off:t.row_off + t.rows] += self.scaling * torch.bmm(self._EB(self.master, g, t).float(), self._EA(self.master, g, t).float())
+                    continue
                 w[t.row_off:t.row_off + t.rows] += self.scaling * (self._B(self.master, t).float() @ self._A(self.master, g, t).float())
             store.load_tensor(name, w.cpu())
         store.sync_work_from_master()

@@ -433,38 +433,23 @@ def _moe_mixin():
 
     def moe_router_backward(self, ctx, op, d_tw, d_aux, x, rw, tw, ti):
         a = op.attrs
-        if a["scoring"] != "softmax" or x.dtype != torch.bfloat16:
+        if a["scoring"] != "softmax" or x.dtype != torch.bfloat16 or a["num_experts"] > 256:
             return RefOps.moe_router_backward(self, ctx, op, d_tw, d_aux, x, rw, tw, ti)
         E, K = a["num_experts"], a["top_k"]
         C = x.shape[-1]
         x2 = x.reshape(-1, C)
         N = x2.shape[0]
-        logits = gemm(x2, rw, out_dtype=torch.float32)
-        probs = torch.softmax(logits, -1)
-        til = ti.reshape(N, K).long()
-        sel = probs.gather(1, til)
-        if d_tw is not None:
-            g = d_tw.reshape(N, K).float()
-            if a["norm_topk_prob"]:
-                ssum = sel.sum(-1, keepdim=True)
-                d_sel = g / ssum - (g * sel).sum(-1, keepdim=True) / (ssum * ssum)
-            else:
-                d_sel = g
-        else:
-            d_sel = torch.zeros_like(sel)
-        d_probs = torch.zeros_like(probs).scatter_add_(1, til, d_sel)
-        extra = None
+        logits = gemm(x2, rw, out_dtype=torch.float32)   # recomputed: [N, E] fp32 is not kept from forward
+        til = ti.reshape(N, K).contiguous()
+        counts = da = None
         if d_aux is not None:
-            da = d_aux if torch.is_tensor(d_aux) else float(d_aux)
-            flat = til.reshape(-1)
-            counts = torch.zeros(E, dtype=torch.float32, device=x.device).scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.float32))  # no host sync
-            d_probs = d_probs + da * a["aux_loss_coef"] * E * (counts / N) / N
-            if a.get("z_loss_coef", 0.0):
-                extra = da * a["z_loss_coef"] * 2 * torch.logsumexp(logits, -1, keepdim=True) / N * probs
-        d_logits = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
-        if extra is not None:
-            d_logits = d_logits + extra
-        dl = d_logits.to(torch.bfloat16)
+            da = d_aux if torch.is_tensor(d_aux) else torch.tensor(float(d_aux), dtype=torch.float32, device=x.device)
+            da = da.to(torch.float32).reshape(1).contiguous()
+            flat = til.reshape(-1).long()
+            counts = torch.zeros(E, dtype=torch.int32, device=x.device).scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))  # no host sync
+        g = d_tw.reshape(N, K).float().contiguous() if d_tw is not None else None
+        # softmax, top-k selection gradient, auxiliary- and z-loss terms and the softmax Jacobian in one kernel (one warp per token)
+        dl = self.ext.moe_router_bwd(logits, til, g, counts, da, bool(a["norm_topk_prob"]), float(a["aux_loss_coef"]), float(a.get("z_loss_coef", 0.0)))
         dx = gemm(dl, rw, b_mn=True).reshape(x.shape)          # [N,E] . [E,C]
         drw = gemm(dl, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)   # [E,N] . [N,C]
         return dx, drw
@@ -510,6 +495,8 @@ def _moe_mixin():
             return RefOps.moe_grouped_gemm(self, ctx, op, x, w, plan)
         r = ctx.recipe.forward_grouped(ctx, op, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "forward_grouped") else None
         if r is not None:
+            if ctx.lora is not None:
+                r = ctx.lora.forward_grouped(ctx, op, x, r, plan)
             return (r,)
         used = getattr(x, "_sg_rows", None)
         # every row of a group (padding included) is written by the GEMM; rows behind the last group are never read into a result,
@@ -518,14 +505,25 @@ def _moe_mixin():
         self.ext.gemm_grouped(x, w, y, plan.offsets, 1, False, False, 1.0, None, None, self.ext.error_flag_tensor())
         if used is not None:
             y._sg_rows = used
+        if ctx.lora is not None:
+            y = ctx.lora.forward_grouped(ctx, op, x, y, plan)
         return (y,)
+
+    def _expert_lora_backward(self, ctx, op, dy, x, plan, dx):
+        extra = ctx.lora.backward_grouped(ctx, op, dy, x, plan) if ctx.lora is not None else None
+        if extra is not None:
+            used = getattr(dx, "_sg_rows", None)
+            dx = dx + extra
+            if used is not None:
+                dx._sg_rows = used
+        return dx
 
     def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
         if not hasattr(plan, "offsets") or not hasattr(plan, "capacity"):
             return RefOps.moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan)
         r = ctx.recipe.backward_grouped(ctx, op, dy, x, w, plan) if ctx.recipe is not None and hasattr(ctx.recipe, "backward_grouped") else None
         if r is not None:
-            return r, None
+            return self._expert_lora_backward(ctx, op, dy, x, plan, r), None
         err = self.ext.error_flag_tensor()
         dy = dy.contiguous()
         used = getattr(dy, "_sg_rows", None)
@@ -541,7 +539,7 @@ def _moe_mixin():
             self.ext.gemm_grouped(dy, x, tgt, plan.offsets, 2, True, acc, 1.0, None, None, err)
             if not acc:
                 self.ext.zero_empty_groups(tgt, plan.offsets)
-        return dx, None
+        return self._expert_lora_backward(ctx, op, dy, x, plan, dx), None
 
     def moe_unpermute(self, ctx, op, yp, tw, plan):
         if getattr(plan, "ep", None) is True:

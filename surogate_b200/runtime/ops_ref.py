@@ -721,6 +721,8 @@ class RefOps:
         w = ctx.local_experts(w)
         for e, s, t in self._expert_ranges(plan):
             y[s:t] = x[s:t] @ w[e].to(x.dtype).t()
+        if ctx.lora is not None:
+            y = ctx.lora.forward_grouped(ctx, op, x, y, plan)
         return (y,)
 
     def moe_grouped_gemm_backward(self, ctx, op, dy, x, w, plan):
@@ -735,6 +737,10 @@ class RefOps:
             dx[s:t] = dy[s:t] @ wl[e].to(dy.dtype)
             if tgt is not None:
                 tgt[e] += (dy[s:t].t() @ x[s:t]).to(tgt.dtype)
+        if ctx.lora is not None:
+            extra = ctx.lora.backward_grouped(ctx, op, dy, x, plan)
+            if extra is not None:
+                dx = dx + extra
         return dx, None
 
     @staticmethod

@@ -71,6 +71,7 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    fp4_four_over_six: bool = True   # NVFP4 recipe: per block of 16 keep the better of the abs-max -> 6 and abs-max -> 4 mappings (round-to-nearest operands)
     time_breakdown: bool = False            # per-step milliseconds of forward / LM head / backward / optimizer in Trainer.last_time_breakdown
     lmhead_drop_ignored_rows: bool = False  # only rows with a target go through the LM head
     offload_saved_tensors: bool = False     # saved activations (or, with recompute, the per-layer input checkpoints) wait in pinned host memory
@@ -188,7 +189,8 @@ class Trainer:
             return dict(history=self.cfg.fp8_amax_history, skip_first_layers=self.cfg.skip_quant_first_layers,
                         skip_last_layers=self.cfg.skip_quant_last_layers)
         if n == "nvfp4":
-            return dict(skip_first_layers=self.cfg.skip_quant_first_layers, skip_last_layers=self.cfg.skip_quant_last_layers)
+            return dict(skip_first_layers=self.cfg.skip_quant_first_layers, skip_last_layers=self.cfg.skip_quant_last_layers,
+                        four_over_six=self.cfg.fp4_four_over_six)
         return {}
 
     # ------------------------------------------------------------------ weights

@@ -254,6 +254,18 @@ def test_embedding(ext):
     ext.embedding_bwd(tok, dout, g)
     ref = torch.zeros(V, C, device=DEV).index_add_(0, tok.reshape(-1).long(), dout.reshape(-1, C).float())
     assert _rel_err(g, ref) < 1e-5
+    # the default (sorted, no atomics) is bit-reproducible, also into a bf16 table and with a heavily repeated id; the atomic variant agrees
+    tok[0, :700] = 7
+    ref = torch.zeros(V, C, device=DEV).index_add_(0, tok.reshape(-1).long(), dout.reshape(-1, C).float())
+    runs = []
+    for _ in range(2):
+        gb = torch.zeros(V, C, device=DEV, dtype=torch.bfloat16)
+        ext.embedding_bwd(tok, dout, gb)
+        runs.append(gb)
+    assert torch.equal(runs[0], runs[1]) and _rel_err(runs[0], ref) < 4e-3
+    ga = torch.zeros(V, C, device=DEV, dtype=torch.float32)
+    ext.embedding_bwd(tok, dout, ga, False)
+    assert _rel_err(ga, ref) < 1e-5
 
 
 def test_cross_entropy(ext):
@@ -375,6 +387,36 @@ def test_moe_softmax_topk(ext):
     assert torch.equal(counts.long(), torch.bincount(ri.reshape(-1), minlength=E))
     assert torch.allclose(psum, ref_p.sum(0), rtol=1e-3)
     assert abs(lse.item() - torch.logsumexp(logits, -1).pow(2).sum().item()) < 1e-2 * lse.item()
+
+
+@pytest.mark.parametrize("E,K,renorm,z", [(128, 8, True, 0.0), (16, 4, False, 1e-3), (60, 2, True, 1e-3), (256, 8, True, 0.0)])
+def test_moe_router_backward_kernel(ext, E, K, renorm, z):
+    """The fused router-backward kernel against the same formulas written with PyTorch ops in fp32."""
+    torch.manual_seed(E + K)
+    N, aux_coef = 777, 1e-2
+    logits = (torch.randn(N, E, device=DEV) * 2).contiguous()
+    probs = torch.softmax(logits, -1)
+    ti = torch.topk(probs, K, -1).indices.to(torch.int32).contiguous()
+    g = torch.randn(N, K, device=DEV)
+    counts = torch.bincount(ti.reshape(-1).long(), minlength=E).to(torch.int32)
+    da = torch.tensor([0.37], device=DEV)
+    dl = ext.moe_router_bwd(logits, ti, g, counts, da, renorm, aux_coef, z)
+    til = ti.long()
+    sel = probs.gather(1, til)
+    if renorm:
+        S = sel.sum(-1, keepdim=True)
+        d_sel = g / S - (g * sel).sum(-1, keepdim=True) / (S * S)
+    else:
+        d_sel = g
+    d_probs = torch.zeros_like(probs).scatter_add_(1, til, d_sel) + da * aux_coef * E * (counts.float() / N) / N
+    ref = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
+    ref = ref + da * z * 2 * torch.logsumexp(logits, -1, keepdim=True) / N * probs
+    assert _rel_err(dl, ref) < 6e-3, _rel_err(dl, ref)
+    # without the auxiliary term and without top-k gradients the pieces are independent
+    dl2 = ext.moe_router_bwd(logits, ti, g, None, None, renorm, aux_coef, z)
+    ref2 = probs * (torch.zeros_like(probs).scatter_add_(1, til, d_sel) - (torch.zeros_like(probs).scatter_add_(1, til, d_sel) * probs).sum(-1, keepdim=True))
+    assert _rel_err(dl2, ref2) < 6e-3
+    _check_flag()
 
 
 def test_moe_permute_grouped_gemm_unpermute(ext):

@@ -117,3 +117,72 @@ def test_lora_checkpoint_holds_only_the_adapter_and_resumes_with_dropout(tmp_pat
     tr2 = _trainer(dropout=0.2)
     tr2.load_checkpoint(str(tmp_path))
     assert [tr2.step(x, y)["loss"] for _ in range(3)] == cont
+
+
+MOE_MODEL = dict(architecture="Qwen3MoeForCausalLM", vocab_size=256, d_model=64, n_layers=2, num_query_heads=4, num_kv_heads=2, head_size=16,
+                 moe_d_ff=32, num_experts=4, num_experts_per_tok=2, aux_loss_coef=0.0, tie_word_embeddings=False)
+
+
+def _moe_trainer(lora=True, seed=0):
+    kw = dict(lora=dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "v_proj", "gate_proj", "up_proj", "down_proj"])) if lora else {}
+    cfg = TrainerConfig(model=MOE_MODEL, batch_size=2, seq_len=32, optimizer="adamw", learning_rate=1e-2, zero_level=0, **kw)
+    tr = Trainer(cfg)
+    tr.init_weights(seed)
+    return tr
+
+
+def test_expert_lora_gradients_follow_the_chain_rule_through_merged_weights(tmp_path):
+    """Per-expert adapters on the grouped expert projections: the adapted forward equals the forward with merged weights, the
+    adapter gradients equal s * B^T dW and s * dW A^T of the merged model's full weight gradient (exact chain rule), training lowers
+    the loss with the base frozen, and the PEFT export / import round-trips the per-expert keys."""
+    tr = _moe_trainer()
+    experts = [g for g in tr.lora.groups.values() if g.experts]
+    assert {g.param for g in experts} == {"experts_gate_up", "experts_down"} and all(g.experts == 4 for g in experts)
+    tr.lora.master.add_(0.05 * torch.randn(tr.lora.numel, generator=torch.Generator().manual_seed(3)))
+    tr.lora.sync_work()
+    x, y = _batch()
+    adapted = tr.validate(x, y)["loss"]
+    tr.forward_backward(x, y)
+    grad = tr.lora.grad.clone()
+    # the same model without adapters, holding the merged weights, trained in full
+    full = _moe_trainer(lora=False)
+    merged = _moe_trainer()
+    merged.lora.master.copy_(tr.lora.master)
+    merged.lora.merge_into(merged.store)
+    for name, t in merged.store.named_full_tensors():
+        full.store.load_tensor(name, t.cpu())
+    full.store.sync_work_from_master()
+    assert abs(full.validate(x, y)["loss"] - adapted) < 1e-5
+    full.forward_backward(x, y)
+    dW = full.get_gradients()
+    s = tr.lora.scaling
+    for g in experts:
+        w_grad = dW[f"blocks.{g.layer}.{g.param}"].float()
+        for t in g.targets:
+            A, B = tr.lora._EA(tr.lora.master, g, t).float(), tr.lora._EB(tr.lora.master, g, t).float()
+            sl = w_grad[:, t.row_off:t.row_off + t.rows]                     # [E, rows, K]
+            want_a = s * torch.bmm(B.transpose(1, 2), sl)                     # [E, r, K]
+            want_b = s * torch.bmm(sl, A.transpose(1, 2))                     # [E, rows, r]
+            got_a, got_b = tr.lora._EA(grad, g, t), tr.lora._EB(grad, g, t)
+            assert torch.allclose(got_a, want_a, rtol=2e-4, atol=1e-6), (g.param, t.name, (got_a - want_a).abs().max())
+            assert torch.allclose(got_b, want_b, rtol=2e-4, atol=1e-6), (g.param, t.name, (got_b - want_b).abs().max())
+    # training: adapters move, the base does not
+    base_before = {n: t.clone() for n, t in tr.store.named_full_tensors()}
+    losses = [tr.step(x, y)["loss"] for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.02, losses
+    for n, t in tr.store.named_full_tensors():
+        assert torch.equal(t, base_before[n]), n
+    # PEFT round trip with per-expert keys
+    out = tmp_path / "adapter"
+    tr.export_adapter(str(out))
+    from safetensors import safe_open
+
+    with safe_open(str(out / "adapter_model.safetensors"), framework="pt") as f:
+        keys = set(f.keys())
+        a = f.get_tensor("base_model.model.model.layers.1.mlp.experts.3.up_proj.lora_A.weight")
+        b = f.get_tensor("base_model.model.model.layers.0.mlp.experts.0.down_proj.lora_B.weight")
+    assert a.shape == (4, 64) and b.shape == (64, 4)
+    assert len([k for k in keys if ".experts." in k]) == 2 * 4 * 3 * 2   # layers x experts x (gate, up, down) x (A, B)
+    tr2 = _moe_trainer()
+    tr2.lora.load_peft(str(out))
+    assert abs(tr.validate(x, y)["loss"] - tr2.validate(x, y)["loss"]) < 1e-5
