@@ -1,7 +1,8 @@
 """Expert parallelism over symmetric memory: token dispatch / combine done by this framework's own kernels.
 
-Mesh: ``world = dp x ep`` with ``ep_rank = rank % ep``; this implementation covers ``ep == world`` (every rank owns
-``E / ep`` experts of every MoE layer and all non-expert parameters are data-parallel).  Per MoE layer, forward:
+Mesh: ``world = dp x ep`` with ``ep_rank = rank % ep`` (parallel/mesh.py).  ``comm`` is the symmetric-memory communicator of ONE
+expert group: the whole world when ``dp = 1``, otherwise the sub-group of ``ep`` consecutive ranks (every rank owns ``E / ep`` experts
+of every MoE layer; all non-expert parameters are data-parallel over the world, expert gradients over the replicas).  Per MoE layer, forward:
 
 1. ``ep_plan``     counts exchange (P2P stores + in-kernel flag barrier) -> padded receive layout and per-expert write cursors,
 2. ``ep_dispatch`` each token's activation row is stored straight into the owning rank's receive buffer (routing
@@ -110,7 +111,8 @@ class ExpertParallel:
         if not hasattr(comm, "create_arena"):
             raise RuntimeError("expert parallelism needs the symmetric-memory communicator (collectives: symm)")
         if ep_size != comm.world:
-            raise NotImplementedError("this build supports ep_size == number of ranks (dp = 1 inside the expert group)")
+            raise ValueError(f"the expert group's communicator has {comm.world} ranks but ep_size is {ep_size} "
+                             "(with ep_size < world the trainer passes the sub-group communicator of parallel/mesh.py)")
         self.comm, self.ep, self.rank, self.device = comm, ep_size, comm.rank, device
         self.capacity_factor = capacity_factor
         self.ext = comm.ext
@@ -250,7 +252,11 @@ class ExpertParallel:
         if not self.count_window:
             return {"layers": 0, "moved": 0}
         layers = sorted(self.count_window)
-        counts_all = torch.stack([self.count_window[L] for L in layers]).cpu()  # the one host sync of a refresh
+        stacked = torch.stack([self.count_window[L] for L in layers])
+        replica_comm = getattr(self, "replica_comm", None)
+        if replica_comm is not None and replica_comm.world > 1:
+            replica_comm.all_reduce(stacked, "sum")   # every replica of the expert group must take the same decision: decide on the global counts
+        counts_all = stacked.cpu()  # the one host sync of a refresh
         E = counts_all.shape[1]
         El = E // self.ep
         changed, moved_total = 0, 0

@@ -113,7 +113,7 @@ class ParamStore:
     def __init__(self, cm: CompiledModel, *, device, param_dtype=torch.float32, grad_dtype=None, master_dtype=None,
                  comm=None, zero_level: int = 0, keep_gathered: bool = True, frozen: Optional[Callable[[str], bool]] = None,
                  expert_parallel: int = 1, offload_master: bool = False, host_work_copy: bool = False,
-                 owned: Optional[Callable[[Any], bool]] = None, resident_layers: int = 0, grad_mask=None):
+                 owned: Optional[Callable[[Any], bool]] = None, resident_layers: int = 0, grad_mask=None, ep_comm=None, expert_dp_comm=None):
         self.cm = cm
         # with host-resident masters: the frozen weights of the first ``resident_layers`` layers stay in device memory instead,
         # so their per-traversal gather is NVLink / local traffic rather than PCIe (spend spare HBM on the layers used first)
@@ -132,6 +132,12 @@ class ParamStore:
         self.frozen = frozen or (lambda name: False)
         self.grad_mask = grad_mask  # runtime.grad_mask.GradientMask: partial-update runs of a full model
         self.ep = max(1, int(expert_parallel))
+        # expert-parallel x data-parallel mesh (parallel/mesh.py): the expert group is a sub-group of the world when dp > 1; expert
+        # weights are gathered inside it and expert gradients are summed over the ranks that hold the same experts
+        self.ep_comm = ep_comm if ep_comm is not None else self.comm
+        self.expert_dp_comm = expert_dp_comm
+        self.ep_rank = self.rank % self.ep
+        self.expert_dp = expert_dp_comm.world if expert_dp_comm is not None else 1
         # Host residency: master shards live in pinned host memory and are streamed to the device per layer (H2D copy on a
         # side stream, then the usual gather).  ``host_work_copy`` keeps an extra pinned copy in the parameter dtype next to
         # masters of another dtype (fp32 masters updated by the CPU optimizer, bf16 copy streamed to the GPU).
@@ -272,9 +278,15 @@ class ParamStore:
                     El = s.shape[0]
                     per = s.numel // El
                     for j in range(El):
-                        ge = self.rank * El + j
+                        ge = self.ep_rank * El + j
                         t = self._gen(per, base_seed + 7 * ge, kind, zero, std, per >= big)
                         b.master[s.offset + j * per:s.offset + (j + 1) * per].copy_(t.to(self.master_dtype))
+                    continue
+                if s.entry.local.startswith("experts_") and len(s.shape) == 3:
+                    # the same per-expert streams without expert parallelism, so a run does not depend on the expert-parallel degree
+                    per = s.numel // s.shape[0]
+                    flat = torch.cat([self._gen(per, base_seed + 7 * e, kind, zero, std, per >= big).cpu() for e in range(s.shape[0])])
+                    self._write_master(b, s, flat)
                     continue
                 self._write_master(b, s, self._gen(s.numel, base_seed, kind, zero, std, s.numel >= big))
         self.sync_work_from_master()
@@ -296,7 +308,7 @@ class ParamStore:
 
     def _expert_slice(self, s: Slot, tensor: torch.Tensor) -> torch.Tensor:
         El = s.shape[0]
-        return tensor[self.rank * El:(self.rank + 1) * El]
+        return tensor[self.ep_rank * El:(self.ep_rank + 1) * El]
 
     def holds(self, name: str) -> bool:
         return self.resolve(name) in self.where
@@ -333,7 +345,7 @@ class ParamStore:
         which slot is the identity unless experts were re-placed for load balance)."""
         local = local.contiguous()
         full = torch.empty((self.ep * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
-        getattr(self.comm, "base", self.comm).all_gather(local.reshape(-1), full.reshape(-1))
+        getattr(self.ep_comm, "base", self.ep_comm).all_gather(local.reshape(-1), full.reshape(-1))
         place = self.expert_placement.get(layer) if layer is not None else None
         if place is not None:
             full = full.index_select(0, torch.tensor(place, dtype=torch.long, device=full.device))
@@ -647,7 +659,10 @@ class ParamStore:
         if getattr(self, "defer_reduce", False):
             return
         if self.world == 1 or b.expert:
-            b.grad_shard = b.grad  # whole experts live on this rank (dp = 1 inside the expert group): nothing to reduce
+            b.grad_shard = b.grad  # whole experts live on this rank: nothing to reduce inside the expert group
+            if b.expert and self.expert_dp > 1 and self.last_micro_step:
+                # the replicas of the expert group saw different tokens: sum their expert gradients (and over nothing else)
+                b.reduce_work = self.expert_dp_comm.all_reduce(b.grad, op="sum", async_op=True)
             return
         if self.zero_level == 0:
             self.sumsq_valid = False

@@ -131,8 +131,18 @@ class Trainer:
             self.comm = symm.try_create(self.comm, self.device, required=cfg.collectives == "symm")
         from .grad_mask import GradientMask
 
+        # expert-parallel x data-parallel mesh: with ep_size < world the expert group is a sub-group (dispatch / combine inside it) and
+        # expert gradients are summed over the ranks that hold the same experts
+        self.ep_comm = self.expert_dp_comm = None
+        if cfg.ep_size > 1 and self.world > cfg.ep_size:
+            from ..parallel.mesh import build_ep_mesh
+
+            self.ep_comm, self.expert_dp_comm = build_ep_mesh(getattr(self.comm, "base", self.comm), cfg.ep_size)
+        elif cfg.ep_size > self.world:
+            raise ValueError(f"ep_size={cfg.ep_size} exceeds the {self.world} ranks of this run")
         self.grad_mask = None if cfg.lora else GradientMask.resolve(cfg.trainable_param_substrings, cfg.gradient_mask_mode)
         self.store = ParamStore(self.cm, device=self.device, grad_mask=self.grad_mask, param_dtype=pd, grad_dtype=gd, master_dtype=md, comm=self.comm,
+                                ep_comm=self.ep_comm, expert_dp_comm=self.expert_dp_comm,
                                 zero_level=cfg.zero_level, keep_gathered=cfg.keep_gathered, frozen=frozen, expert_parallel=cfg.ep_size,
                                 offload_master=cfg.offload_master or cfg.cpu_training,
                                 host_work_copy=("double" if cfg.async_optimizer else True) if cfg.cpu_training else False, owned=owned,
@@ -146,9 +156,20 @@ class Trainer:
             self.store.enable_fp8_gather(self.recipe.quantizes)
         self.ep = None
         if cfg.ep_size > 1:
-            from ..parallel.ep import ExpertParallel
+            group_comm = self.ep_comm if self.ep_comm is not None else self.comm
+            if on_gpu and self.backend.name == "cuda":
+                from ..parallel.ep import ExpertParallel
 
-            self.ep = ExpertParallel(self.comm, cfg.ep_size, self.device, capacity_factor=cfg.ep_capacity_factor)
+                if self.ep_comm is not None:   # the expert group's own symmetric arena, barriers and peer pointers
+                    from ..parallel import symm
+
+                    group_comm = symm.try_create(self.ep_comm, self.device, required=True)
+                self.ep = ExpertParallel(group_comm, cfg.ep_size, self.device, capacity_factor=cfg.ep_capacity_factor)
+                self.ep.replica_comm = self.expert_dp_comm
+            else:                              # PyTorch backend (CPU ranks over gloo included): the library all-to-all
+                from ..parallel.ep_ref import AllToAllExpertParallel
+
+                self.ep = AllToAllExpertParallel(getattr(group_comm, "base", group_comm), cfg.ep_size, self.device)
         self.executor = Executor(self.cm, self.store, self.backend, recipe=self.recipe,
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd, lmhead_drop_ignored_rows=cfg.lmhead_drop_ignored_rows,
                                                      offload_saved=cfg.offload_saved_tensors, time_breakdown=cfg.time_breakdown), device=self.device, ep=self.ep, lora=self.lora)
@@ -458,35 +479,39 @@ class Trainer:
         return ctx, total
 
     def grad_norm(self) -> torch.Tensor:
-        """Global L2 norm of the (already reduced) gradients, as a device scalar."""
+        """Global L2 norm of the (already reduced) gradients, as a device scalar.
+
+        Three kinds of terms, each counted exactly once: dense buckets (replicated after an all-reduce, or one shard per rank under
+        ZeRO), expert buckets (one copy per rank of an expert group; with an expert-parallel x data-parallel mesh the same copy exists
+        in every replica of the group) and the adapter buffer (already all-reduced, identical everywhere)."""
         on_gpu = self.device.type == "cuda" and self.backend.name == "cuda"
-        if self.store.fused_sumsq is not None and self.store.sumsq_valid and self.lora is None:
-            # the reduce-scatter kernels already accumulated this rank's shard norms
-            total = self.store.fused_sumsq.clone().reshape(())
-            for b in self.store.trainable_buckets():  # expert-parallel buckets are not reduce-scattered: add their norms here
-                if b.expert and b.grad_shard is not None:
-                    total += self.backend.ext.sumsq(b.grad_shard)
-            if os.environ.get("SUROGATE_CHECK_FUSED_NORM") == "1":  # self-check: recompute from the reduced shards
-                ref = sum(self.backend.ext.sumsq(b.grad_shard) for b in self.store.trainable_buckets() if b.grad_shard is not None)  # incl. experts
-                if abs(float(ref) - float(total)) > 1e-2 * abs(float(ref)):
-                    raise RuntimeError(f"fused gradient norm mismatch on rank {self.rank}: fused {float(total)} vs recomputed {float(ref)}")
-            self.comm.all_reduce(total, "sum")
-            return total.sqrt()
-        total = torch.zeros((), dtype=torch.float32, device=self.device)
+
+        def sumsq(g):
+            return self.backend.ext.sumsq(g) if on_gpu else g.float().pow(2).sum()
+
+        fused = self.store.fused_sumsq is not None and self.store.sumsq_valid and self.lora is None
+        parts = torch.zeros(2, dtype=torch.float32, device=self.device)   # [dense, experts]
         for b in self.store.trainable_buckets():
-            g = b.grad_shard
-            if g is None:
+            if b.grad_shard is None:
                 continue
-            total += self.backend.ext.sumsq(g) if on_gpu else g.float().pow(2).sum()
-        if self.world > 1 and (self.store.sharded or self.store.ep > 1):
-            if not self.store.sharded:  # replicated gradients: only the expert buckets differ between ranks
-                rep = sum((self.backend.ext.sumsq(b.grad_shard) if on_gpu else b.grad_shard.float().pow(2).sum())
-                          for b in self.store.trainable_buckets() if not b.expert and b.grad_shard is not None)
-                total = total - rep
-                self.comm.all_reduce(total, "sum")
-                total = total + rep
-            else:
-                self.comm.all_reduce(total, "sum")
+            if b.expert:
+                parts[1] += sumsq(b.grad_shard)
+            elif not fused:
+                parts[0] += sumsq(b.grad_shard)
+        if fused:  # the reduce-scatter kernels already accumulated this rank's shard norms
+            parts[0] += self.store.fused_sumsq.reshape(())
+            if os.environ.get("SUROGATE_CHECK_FUSED_NORM") == "1":  # self-check: recompute from the reduced shards
+                ref = sum(sumsq(b.grad_shard) for b in self.store.trainable_buckets() if b.grad_shard is not None and not b.expert)
+                if abs(float(ref) - float(parts[0])) > 1e-2 * abs(float(ref)):
+                    raise RuntimeError(f"fused gradient norm mismatch on rank {self.rank}: fused {float(parts[0])} vs recomputed {float(ref)}")
+        if self.world > 1:
+            dense_local = parts[0].clone()
+            if self.store.sharded or self.store.ep > 1:
+                self.comm.all_reduce(parts, "sum")
+            if not self.store.sharded:
+                parts[0] = dense_local                              # replicated gradients: every rank already holds the whole dense part
+            parts[1] = parts[1] / float(self.store.expert_dp)      # each expert's gradient exists once per replica of the expert group
+        total = parts[0] + parts[1]
         if self.lora is not None:
             # the adapter gradient is already all-reduced (identical on every rank): it joins after the cross-rank sum
             total = total + self.lora.grad_sumsq()

@@ -123,3 +123,21 @@ def test_checkpoint_write_failure_on_one_rank_is_abandoned_by_all_ranks(tmp_path
     assert r["loss_after"] == r["loss_after"] and r["loss_after"] > 0
     ok = run_worker(2, dict(device="cpu", model=TINY, global_batch=4, seq_len=32, steps=2, zero=2, checkpoint_dir=str(tmp_path)), port=29672)
     assert ok["checkpoint"] == "written" and find_latest_checkpoint(str(tmp_path)) == 2
+
+
+MOE_TINY = dict(architecture="Qwen3MoeForCausalLM", vocab_size=256, d_model=64, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=32, moe_d_ff=32,
+                num_experts=4, num_experts_per_tok=2, aux_loss_coef=0.0, tie_word_embeddings=False)   # (the load-balancing loss is a per-rank statistic)
+
+
+@pytest.mark.parametrize("nproc,ep,zero,port", [(2, 2, 1, 29681), (2, 1, 1, 29682), (4, 2, 0, 29683), (4, 2, 2, 29684)])
+def test_expert_parallel_mesh_matches_single_process(nproc, ep, zero, port):
+    """Expert parallelism over the library all-to-all on CPU ranks: ep = world (one expert group), ep = 1 (pure data parallel) and the
+    2 x 2 mesh (two replicas of a two-rank expert group: tokens dispatched inside a replica, expert gradients summed across replicas,
+    every gradient counted once in the norm) all reproduce the single-process losses and gradient norms."""
+    one = run_worker(1, dict(device="cpu", model=MOE_TINY, global_batch=4, seq_len=32, steps=3, zero=0))
+    r = run_worker(nproc, dict(device="cpu", model=MOE_TINY, global_batch=4, seq_len=32, steps=3, zero=zero, ep=ep), port=port)
+    assert r["world"] == nproc
+    for a, b in zip(r["losses"], one["losses"]):
+        assert abs(a - b) < 3e-4 * abs(b), (r["losses"], one["losses"])
+    for a, b in zip(r["norms"], one["norms"]):
+        assert abs(a - b) < 2e-3 * abs(b), (r["norms"], one["norms"])
