@@ -573,7 +573,7 @@ def _moe_mixin():
         setattr(CudaOps, f.__name__, f)
 
     for f in (moe_router, moe_router_backward, moe_permute, moe_permute_backward, moe_grouped_gemm, moe_grouped_gemm_backward, moe_unpermute,
-              moe_unpermute_backward):
+              moe_unpermute_backward, _expert_lora_backward):
         setattr(CudaOps, f.__name__, f)
 
 
