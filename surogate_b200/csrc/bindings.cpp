@@ -190,6 +190,19 @@ Tensor swiglu_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>
     return dx;
 }
 
+// The gradient as E5M2 only (its reader is an FP8 GEMM): scaled by `fp8_scale`, abs-max of the unscaled values recorded in `amax_out`.
+Tensor swiglu_bwd_fp8(const Tensor& dy, const Tensor& x, const Tensor& fp8_scale, const Tensor& amax_out) {
+    check_bf16(dy, "dy");
+    check_bf16(x, "x");
+    const int M = static_cast<int>(x.size(-1) / 2);
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx8 = torch::empty(x.sizes(), x.options().dtype(at::kFloat8_e5m2));
+    g_launches += 1;
+    sg::swiglu_bwd(dy.data_ptr(), x.data_ptr(), nullptr, x.numel() / (2 * M), M, num_sms(), cur_stream(), nullptr, dx8.data_ptr(), fp8_scale.data_ptr<float>(),
+                   amax_out.data_ptr<float>());
+    return dx8;
+}
+
 void zero_empty_groups(Tensor& out, const Tensor& offsets) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() >= 2 && offsets.is_cuda() && offsets.scalar_type() == at::kInt, "out [G, ...] and CUDA int32 offsets");
     const int64_t G = out.size(0);
@@ -418,6 +431,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("swiglu_fwd", &swiglu_fwd, pybind11::arg("x"), pybind11::arg("want_y"), pybind11::arg("fp8_scale"), pybind11::arg("amax_out"), pybind11::arg("want_fp8"),
           pybind11::arg("rows_limit") = c10::optional<Tensor>());
     m.def("swiglu_bwd", &swiglu_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("rows_limit") = c10::optional<Tensor>());
+    m.def("swiglu_bwd_fp8", &swiglu_bwd_fp8);
     m.def("zero_empty_groups", &zero_empty_groups, "zero the [G, ...] slices of groups that own no rows");
     m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd, py::arg("qkv"), py::arg("q_norm_weight"), py::arg("k_norm_weight"), py::arg("position_ids"), py::arg("num_q_heads"),
           py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("theta"), py::arg("sec_h") = 0, py::arg("sec_w") = 0);

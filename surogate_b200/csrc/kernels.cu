@@ -233,10 +233,16 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict_
         if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
     }
 }
+// dx (bf16) and / or dx_fp8 (E5M2 with the given scale, recording the abs-max of the unscaled values): when the only reader of the
+// gradient is an FP8 GEMM, the bf16 tensor is never written and no separate quantise pass reads it back.
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, size_t rows, int M,
-                                                         const int* __restrict__ rows_limit) {
+                                                         const int* __restrict__ rows_limit, uint8_t* __restrict__ dx_fp8, const float* __restrict__ fp8_scale,
+                                                         float* __restrict__ amax_out) {
+    __shared__ float sh[32];
     if (rows_limit) rows = min(rows, static_cast<size_t>(max(0, __ldg(rows_limit))));
     const size_t nvec = rows * (M / 8);
+    const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
+    float amax = 0.f;
     for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t row = v / (M / 8);
         const int c = static_cast<int>(v % (M / 8)) * 8;
@@ -250,8 +256,27 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
             du[i] = g[i] * gate[i] * s;
             dg[i] = g[i] * up[i] * s * (1.f + gate[i] * (1.f - s));
         }
-        store8(dx + row * 2 * M + c, du);
-        store8(dx + row * 2 * M + M + c, dg);
+        if (dx) {
+            store8(dx + row * 2 * M + c, du);
+            store8(dx + row * 2 * M + M + c, dg);
+        }
+        if (dx_fp8) {
+            uint2 qu, qg;
+            uint8_t* bu = reinterpret_cast<uint8_t*>(&qu);
+            uint8_t* bg = reinterpret_cast<uint8_t*>(&qg);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                amax = fmaxf(amax, fmaxf(fabsf(du[i]), fabsf(dg[i])));
+                bu[i] = to_fp8<true>(du[i] * qs);
+                bg[i] = to_fp8<true>(dg[i] * qs);
+            }
+            *reinterpret_cast<uint2*>(dx_fp8 + row * 2 * M + c) = qu;
+            *reinterpret_cast<uint2*>(dx_fp8 + row * 2 * M + M + c) = qg;
+        }
+    }
+    if (amax_out) {
+        amax = block_reduce<true>(amax, sh);
+        if (threadIdx.x == 0) atomic_max_pos(amax_out, amax);
     }
 }
 
@@ -903,8 +928,10 @@ void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, flo
                 const int* rows_limit) {
     swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M, rows_limit);
 }
-void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit) {
-    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M, rows_limit);
+void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit, void* dx_fp8,
+                const float* fp8_scale, float* amax_out) {
+    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M, rows_limit,
+                                                                             (uint8_t*)dx_fp8, fp8_scale, amax_out);
 }
 // Zero the output matrices of groups that own no rows (their wgrad tiles are never scheduled): out [G, per_group] of `elem` bytes.
 __global__ void __launch_bounds__(256) zero_empty_groups_kernel(uint4* __restrict__ out, const int* __restrict__ offsets, size_t vec_per_group) {

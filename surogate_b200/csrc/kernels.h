@@ -16,7 +16,8 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  int C, int num_sms, cudaStream_t s);
 void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s,
                 const int* rows_limit = nullptr);
-void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit = nullptr);
+void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit = nullptr,
+                void* dx_fp8 = nullptr, const float* fp8_scale = nullptr, float* amax_out = nullptr);
 void zero_empty_groups(void* out, const int* offsets, int groups, size_t bytes_per_group, cudaStream_t s);
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
                       int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s);

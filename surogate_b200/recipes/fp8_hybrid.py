@@ -137,6 +137,24 @@ class FP8HybridRecipe(GroupedFp8Mixin, Recipe):
             cache[key] = ok
         return ok
 
+    def swiglu_backward_fp8(self, ctx, op, ext, dy, x):
+        """d(MLP-up output) straight as E5M2 when its only reader is the FP8 backward of the up projection (no bias gradient, no
+        adapter): the bf16 gradient is never written and the separate quantise pass disappears.  None = take the bf16 path."""
+        if not self.have_history or ctx.layer is None or ctx.layer in self.skip or ctx.lora is not None or ctx.graph is None:
+            return None
+        cache = self.__dict__.setdefault("_fp8_grad_reader_cache", {})
+        key = (id(ctx.graph), op.outputs[0])
+        ok = cache.get(key)
+        if ok is None:
+            readers = [o for o in ctx.graph.ops if op.outputs[0] in o.inputs]
+            ok = cache[key] = (len(readers) == 1 and readers[0].kind == "matmul_backward" and readers[0].attrs.get("role", "") == "mlp_up"
+                               and readers[0].inputs[0] == op.outputs[0] and readers[0].outputs[2] is None)
+        if not ok or getattr(x, "_sg_rows", None) is not None:
+            return None
+        q = self.slot(ctx.layer, "mlp_up", "dy")
+        d8 = ext.swiglu_bwd_fp8(dy.contiguous(), x, self.scale[q:q + 1], self.amax_cur[q:q + 1])
+        return Fp8Tensor(d8, self.scale_inv[q:q + 1])
+
     def norm_forward(self, ctx, op, ext, x, residual, w):
         role = self._CONSUMER_ROLE[op.outputs[1 if residual is not None or len(op.outputs) == 3 else 0]]
         q = self.slot(ctx.layer, role, "x")
@@ -182,6 +200,13 @@ class FP8HybridRecipe(GroupedFp8Mixin, Recipe):
         if cached is not None:
             return cached
         q = self.slot(ctx.layer, role, "w")
+        if self.have_history:
+            # delayed scaling like the activations: one pass that quantises with the scale derived from the earlier steps' abs-max and
+            # records this step's (weights move by a learning-rate-sized step, so last step's abs-max is a tight bound)
+            data = ext.quantize_fp8(w, self.scale[q:q + 1], self.amax_cur[q:q + 1], False)
+            t = Fp8Tensor(data, self.scale_inv[q:q + 1])
+            self.weight_cache[key] = t
+            return t
         am = self.amax_cur[q:q + 1]
         am.zero_()
         ext.amax(w, am)
@@ -225,7 +250,7 @@ class FP8HybridRecipe(GroupedFp8Mixin, Recipe):
         if not isinstance(x2, Fp8Tensor):
             saved = ctx.stash.pop(("fp8x", ctx.layer, op.attrs.get("fwd_out")), None)
             x2 = saved if saved is not None else self._quantize(ext, x2, self.slot(ctx.layer, role, "x"), False)
-        dy8 = self._quantize(ext, dy2, self.slot(ctx.layer, role, "dy"), True)
+        dy8 = dy2 if isinstance(dy2, Fp8Tensor) else self._quantize(ext, dy2, self.slot(ctx.layer, role, "dy"), True)
         w8 = self._weight(ctx, ext, role, w, op.inputs[2])
         dx = gemm(dy8.data, w8.data, a_mn=False, b_mn=True, scale_a=dy8.scale_inv, scale_b=w8.scale_inv)
         tgt, acc = ctx.grad_target(op.outputs[1])

@@ -147,6 +147,8 @@ class CudaOps(RefOps):
         r = ctx.recipe.backward_matmul(ctx, op, dy2, x2, w) if ctx.recipe is not None else None
         if r is not None:
             dx = r[0]
+        elif isinstance(dy2, Fp8Tensor):
+            raise RuntimeError("an FP8 gradient reached a matmul whose backward is not FP8")
         else:
             dx = gemm(dy2, w, a_mn=False, b_mn=True)
             tgt, acc = ctx.grad_target(op.outputs[1])
@@ -202,6 +204,10 @@ class CudaOps(RefOps):
         return (y,)
 
     def swiglu_backward(self, ctx, op, dy, x):
+        if ctx.recipe is not None and hasattr(ctx.recipe, "swiglu_backward_fp8"):
+            d8 = ctx.recipe.swiglu_backward_fp8(ctx, op, self.ext, dy, x)
+            if d8 is not None:
+                return (d8,)
         used = getattr(x, "_sg_rows", None)
         if used is None:
             used = getattr(dy, "_sg_rows", None)
