@@ -208,24 +208,26 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict_
     __shared__ float sh[32];
     // rows_limit (device): only the first *rows_limit rows are in use (expert buffers sized for the worst case); cost follows the use
     if (rows_limit) rows = min(rows, static_cast<size_t>(max(0, __ldg(rows_limit))));
-    const size_t nvec = rows * (M / 8);
     const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
     float amax = 0.f;
-    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t row = v / (M / 8);
-        const int c = static_cast<int>(v % (M / 8)) * 8;
-        float up[8], gate[8], o[8];
-        load8(x + row * 2 * M + c, up);
-        load8(x + row * 2 * M + M + c, gate);
+    // grid.x x block covers the M / 8 column vectors, grid.y strides over the rows: no index division, and a thread's consecutive
+    // trips touch consecutive rows of the same columns
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c < M) {
+        for (size_t row = blockIdx.y; row < rows; row += gridDim.y) {
+            float up[8], gate[8], o[8];
+            load8(x + row * 2 * M + c, up);
+            load8(x + row * 2 * M + M + c, gate);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { o[i] = gate[i] / (1.f + __expf(-gate[i])) * up[i]; amax = fmaxf(amax, fabsf(o[i])); }
-        if (y) store8(y + row * M + c, o);
-        if (y_fp8) {
-            uint2 q;
-            uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+            for (int i = 0; i < 8; ++i) { o[i] = gate[i] / (1.f + __expf(-gate[i])) * up[i]; amax = fmaxf(amax, fabsf(o[i])); }
+            if (y) store8(y + row * M + c, o);
+            if (y_fp8) {
+                uint2 q;
+                uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) qb[i] = to_fp8<false>(o[i] * qs);
-            *reinterpret_cast<uint2*>(y_fp8 + row * M + c) = q;
+                for (int i = 0; i < 8; ++i) qb[i] = to_fp8<false>(o[i] * qs);
+                *reinterpret_cast<uint2*>(y_fp8 + row * M + c) = q;
+            }
         }
     }
     if (amax_out) {
@@ -240,12 +242,10 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
                                                          float* __restrict__ amax_out) {
     __shared__ float sh[32];
     if (rows_limit) rows = min(rows, static_cast<size_t>(max(0, __ldg(rows_limit))));
-    const size_t nvec = rows * (M / 8);
     const float qs = fp8_scale ? __ldg(fp8_scale) : 1.f;
     float amax = 0.f;
-    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t row = v / (M / 8);
-        const int c = static_cast<int>(v % (M / 8)) * 8;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    for (size_t row = blockIdx.y; c < M && row < rows; row += gridDim.y) {
         float up[8], gate[8], g[8], du[8], dg[8];
         load8(x + row * 2 * M + c, up);
         load8(x + row * 2 * M + M + c, gate);
@@ -924,13 +924,27 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  int C, int num_sms, cudaStream_t s) {
     rmsnorm_bwd_n(dy, x, w, rstd, d_res, dx, dw_partial, dw, rows, C, rmsnorm_bwd_blocks(rows, num_sms), s);
 }
+// blocks of 256 threads over the M / 8 column vectors; enough row-blocks to give every SM eight resident blocks
+static int swiglu_threads(int M) {
+    const int t = (M / 8 + 31) / 32 * 32;
+    return t < 256 ? t : 256;       // narrow expert projections: no idle warps in the block
+}
+static dim3 swiglu_grid(size_t rows, int M, int num_sms) {
+    const int threads = swiglu_threads(M);
+    const unsigned gx = static_cast<unsigned>((M / 8 + threads - 1) / threads);
+    size_t gy = (static_cast<size_t>(num_sms) * (2048 / threads) + gx - 1) / gx;
+    if (gy > rows) gy = rows;
+    if (gy < 1) gy = 1;
+    if (gy > 65535) gy = 65535;
+    return dim3(gx, static_cast<unsigned>(gy));
+}
 void swiglu_fwd(const void* x, void* y, void* y_fp8, const float* fp8_scale, float* amax, size_t rows, int M, int num_sms, cudaStream_t s,
                 const int* rows_limit) {
-    swiglu_fwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M, rows_limit);
+    swiglu_fwd_kernel<<<swiglu_grid(rows, M, num_sms), swiglu_threads(M), 0, s>>>((const bf16*)x, (bf16*)y, (uint8_t*)y_fp8, fp8_scale, amax, rows, M, rows_limit);
 }
 void swiglu_bwd(const void* dy, const void* x, void* dx, size_t rows, int M, int num_sms, cudaStream_t s, const int* rows_limit, void* dx_fp8,
                 const float* fp8_scale, float* amax_out) {
-    swiglu_bwd_kernel<<<grid_for(rows * (M / 8), 256, num_sms), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M, rows_limit,
+    swiglu_bwd_kernel<<<swiglu_grid(rows, M, num_sms), swiglu_threads(M), 0, s>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, rows, M, rows_limit,
                                                                              (uint8_t*)dx_fp8, fp8_scale, amax_out);
 }
 // Zero the output matrices of groups that own no rows (their wgrad tiles are never scheduled): out [G, per_group] of `elem` bytes.
