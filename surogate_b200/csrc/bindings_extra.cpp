@@ -7,6 +7,7 @@
 #include <string>
 
 #include "attention_sm100.h"
+#include "normuon_kernels.h"
 #include "qlora_kernels.h"
 #include "comm_kernels.h"
 #include "ep_kernels.h"
@@ -451,6 +452,47 @@ Tensor flash_attn_bwd(const Tensor& d_out, const Tensor& qkv, const Tensor& out,
     return d_qkv;
 }
 
+// ---------------------------------------------------------------------------------------- NorMuon
+// g: gradient of one matrix (bf16 / fp32, flat); m: bf16 momentum (updated); returns (u bf16 = Nesterov blend, sumsq fp32[1])
+std::vector<Tensor> normuon_momentum(const Tensor& g, Tensor& m, const Tensor& hp, double mu) {
+    TORCH_CHECK(g.is_cuda() && g.is_contiguous() && m.is_contiguous() && m.scalar_type() == at::kBFloat16 && m.numel() == g.numel(), "normuon_momentum operands");
+    TORCH_CHECK(g.scalar_type() == at::kFloat || g.scalar_type() == at::kBFloat16, "gradient: fp32 or bf16");
+    const c10::cuda::CUDAGuard guard(g.device());
+    Tensor u = torch::empty(g.sizes(), g.options().dtype(at::kBFloat16));
+    Tensor sumsq = torch::zeros({1}, g.options().dtype(at::kFloat));
+    sg_count_launch(1);
+    sg::normuon_momentum(g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(), u.data_ptr(), sumsq.data_ptr<float>(), hp.data_ptr<float>(),
+                         static_cast<float>(mu), g.numel(), sms(), cur_stream());
+    return {u, sumsq};
+}
+void normuon_normalise(Tensor& x, const Tensor& sumsq) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x: contiguous bf16");
+    const c10::cuda::CUDAGuard guard(x.device());
+    sg_count_launch(1);
+    sg::normuon_normalise(x.data_ptr(), sumsq.data_ptr<float>(), x.numel(), sms(), cur_stream());
+}
+// x [R, C] bf16 (the orthogonalised update); v fp32 [R] (updated); returns sums fp32[2]
+Tensor normuon_row_stats(const Tensor& x, Tensor& v, const Tensor& hp, double beta2) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && v.scalar_type() == at::kFloat && v.numel() == x.size(0),
+                "normuon_row_stats operands");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor sums = torch::zeros({2}, x.options().dtype(at::kFloat));
+    sg_count_launch(1);
+    sg::normuon_row_stats(x.data_ptr(), v.data_ptr<float>(), sums.data_ptr<float>(), hp.data_ptr<float>(), static_cast<float>(beta2), static_cast<int>(x.size(0)),
+                          static_cast<int>(x.size(1)), cur_stream());
+    return sums;
+}
+// w: the slice [first, first + w.numel()) of the row-major parameter (bf16 / fp32 master), updated in place
+void normuon_apply(Tensor& w, const Tensor& x, const Tensor& v, const Tensor& sums, const Tensor& hp, double update_scale, bool cautious, int64_t first) {
+    TORCH_CHECK(w.is_cuda() && w.is_contiguous() && (w.scalar_type() == at::kFloat || w.scalar_type() == at::kBFloat16), "w: contiguous fp32 / bf16");
+    TORCH_CHECK(x.dim() == 2 && first >= 0 && first + w.numel() <= x.numel(), "normuon_apply: slice outside the matrix");
+    const c10::cuda::CUDAGuard guard(w.device());
+    sg_count_launch(1);
+    sg::normuon_apply(w.data_ptr(), w.scalar_type() == at::kFloat, x.data_ptr(), v.data_ptr<float>(), sums.data_ptr<float>(), hp.data_ptr<float>(),
+                      static_cast<float>(update_scale), cautious, static_cast<int>(x.size(1)), static_cast<size_t>(first), static_cast<size_t>(w.numel()), sms(),
+                      cur_stream());
+}
+
 // ---------------------------------------------------------------------------------------- QLoRA storage -> bf16
 // kind: "bnb_nf4" (a = absmax fp32, or a = int8 codes with b = fp32 scales per 256 blocks and c = fp32 offset), "fp8_block" (a = fp32
 // scales), "nvfp4" (a = UE4M3 scale bytes, b = fp32 tensor de-scale), "mxfp4" (a = E8M0 scale bytes).
@@ -518,6 +560,10 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("flash_attn_fwd_profile", &flash_attn_fwd_profile, "per-phase cycle counters of one softmax thread (development aid)");
     m.def("dequant_blockwise", &dequant_blockwise, pybind11::arg("kind"), pybind11::arg("codes"), pybind11::arg("a"), pybind11::arg("b") = c10::optional<Tensor>(),
           pybind11::arg("c") = c10::optional<Tensor>(), pybind11::arg("n"), pybind11::arg("block") = 0);
+    m.def("normuon_momentum", &normuon_momentum);
+    m.def("normuon_normalise", &normuon_normalise);
+    m.def("normuon_row_stats", &normuon_row_stats);
+    m.def("normuon_apply", &normuon_apply);
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_row_positions", &ep_row_positions);

@@ -44,6 +44,26 @@ def polar_express(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
     return X.t() if transposed else X
 
 
+def polar_express_device(X: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """The same iteration on the tcgen05 GEMM, for a bf16 matrix already scaled to spectral norm < 1; returns a bf16 matrix of the
+    same shape.  No transposed copies: a tall matrix [R, C] (R > C) iterates with A = X^T X ([C, C], both operands read MN-major)
+    and X <- a X + X (bA + cA^2) (A is symmetric); a wide one with A = X X^T and X <- a X + (bA + cA^2) X."""
+    from ..runtime.ops_cuda import gemm
+
+    tall = X.shape[0] > X.shape[1]
+    for a, b, c in POLAR_EXPRESS_COEFFS[:steps]:
+        A = gemm(X, X, a_mn=True, b_mn=True) if tall else gemm(X, X)          # [m, m], m = min(R, C)
+        B = A * b
+        gemm(A, A, B, accumulate=True, alpha=c)                               # b A + c A A^T  (A = A^T)
+        Xn = X * a
+        if tall:
+            gemm(X, B, Xn, accumulate=True)                                   # X B^T = X B
+        else:
+            gemm(B, X, Xn, b_mn=True, accumulate=True)                        # B X
+        X = Xn
+    return X
+
+
 class NorMuon(AdamW8bit):
     def __init__(self, cfg: OptimizerConfig, store):
         super().__init__(cfg, store)
@@ -63,9 +83,14 @@ class NorMuon(AdamW8bit):
             return super().step_bucket(b, grad, hp, hp_host)
         before = b.master.clone()
         super().step_bucket(b, grad, hp, hp_host)
+        if self.use_kernels and grad.dtype in (torch.bfloat16, torch.float32) and b.master.dtype in (torch.bfloat16, torch.float32):
+            return self._step_matrices_device(b, grad, hp, before, matrices, lo, hi)
         lr, _, _, eps, wd, _, _ = hp_host
         mu, beta2 = self.cfg.normuon_momentum, self.cfg.normuon_beta2
         gs = hp[7]
+        if float(gs) == 0.0:   # skipped update (non-finite gradient norm)
+            b.master.copy_(before)
+            return
         for s in matrices:
             a, z = s.offset, s.offset + s.numel
             if store.sharded and not (a >= lo and z <= hi):
@@ -102,3 +127,40 @@ class NorMuon(AdamW8bit):
             else:
                 decay = wd * lr * w
             b.master[seg] = (w - decay - lr * scale * u).to(b.master.dtype)
+
+    # ------------------------------------------------------------------ device path
+    def _step_matrices_device(self, b, grad, hp, before, matrices, lo, hi) -> None:
+        """Matrix parameters on the GPU: momentum / Nesterov blend / Frobenius norm (one kernel), normalisation (one kernel), five
+        Polar-Express iterations on the tcgen05 GEMM, row statistics (one kernel) and the update with cautious weight decay (one kernel).
+        Momentum is kept in bf16, the row second moments in fp32; hyper-parameters and the clip scale are read from the device vector, so
+        nothing here synchronises with the host.  A matrix that straddles a shard boundary is orthogonalised by every rank that owns a
+        part of it (from the gathered gradient) and each rank applies its own slice."""
+        store, ext = self.store, self.ext
+        mu, beta2 = float(self.cfg.normuon_momentum), float(self.cfg.normuon_beta2)
+        for s in matrices:
+            a, z = s.offset, s.offset + s.numel
+            pa, pz = max(a, lo), min(z, hi)
+            if store.sharded and not (a >= lo and z <= hi):
+                g_full = store.grad_of(s.name).reshape(-1).contiguous()       # collective: every rank takes part
+            else:
+                g_full = grad[a - lo:z - lo].contiguous()
+            if pa >= pz:
+                continue
+            if g_full.dtype not in (torch.bfloat16, torch.float32):
+                g_full = g_full.float()
+            m = self.mom.get(s.name)
+            if m is None or m.dtype != torch.bfloat16:
+                m = self.mom[s.name] = torch.zeros(s.numel, dtype=torch.bfloat16, device=store.device)
+            u, sumsq = ext.normuon_momentum(g_full, m.view(-1), hp, mu)
+            ext.normuon_normalise(u, sumsq)
+            X = polar_express_device(u.view(s.shape))
+            v = self.second.get(s.name)
+            if v is None or v.numel() != s.shape[0]:
+                v = self.second[s.name] = torch.zeros(s.shape[0], dtype=torch.float32, device=store.device)
+            sums = ext.normuon_row_stats(X.contiguous(), v.view(-1), hp, beta2)
+            seg = slice(pa - lo, pz - lo)
+            w = before[seg].clone()          # the AdamW pass above also touched these elements: start again from the old values
+            scale = 0.2 * max(s.shape[0], s.shape[1]) ** 0.5 * self.cfg.normuon_lr_scale
+            ext.normuon_apply(w, X.contiguous(), v.view(-1), sums, hp, float(scale), bool(self.cfg.normuon_cautious_wd), pa - a)
+            b.master[seg] = w
+

@@ -354,3 +354,31 @@ def test_biased_and_relu2_experts_on_the_grouped_gemm_path(arch):
         # bf16 kernels against fp32-accumulating PyTorch ops on a tiny model: a few routing decisions flip, tiny gradients (attention
         # sinks) are noise
         assert ea < 0.2 or float(den) < 1e-2, f"{name}: rel err {ea.item():.4f}"
+
+
+def test_normuon_device_path_follows_the_pytorch_oracle():
+    """NorMuon on the kernels (momentum / normalise / row statistics / apply kernels and Polar-Express on the tcgen05 GEMM) against
+    the PyTorch statement of the optimizer (optim/normuon.py, kept as the oracle): same weights after two steps up to the bf16
+    momentum and bf16 iteration, and no library matrix product on the device path."""
+    import torch.nn.functional  # noqa: F401
+
+    x, y = _batch(6)
+    dev, ora = _trainer("cuda", optimizer="normuon"), _trainer("cuda", optimizer="normuon")
+    ora.optimizer.use_kernels = False          # AdamW part and matrix part both through the PyTorch statements
+    start = {n: t.clone() for n, t in dev.store.named_full_tensors()}
+    for _ in range(2):
+        a, b = dev.step(x, y), ora.step(x, y)
+    assert abs(a["loss"] - b["loss"]) < 2e-2 * b["loss"], (a, b)
+    checked = 0
+    ref = dict(ora.store.named_full_tensors())
+    for n, t in dev.store.named_full_tensors():
+        if t.dim() != 2 or "blocks" not in n:
+            continue
+        d_dev, d_ora = t.float() - start[n].float(), ref[n].float() - start[n].float()
+        if d_ora.norm() == 0:
+            continue
+        rel = ((d_dev - d_ora).norm() / d_ora.norm()).item()
+        assert rel < 0.08, (n, rel)
+        checked += 1
+    assert checked >= 4
+    assert all(m.dtype == torch.bfloat16 for m in dev.optimizer.mom.values()) and dev.optimizer.mom
