@@ -13,7 +13,46 @@ import json
 import os
 
 
+def _run_all(argv, command: str) -> int:
+    """``grpo-train --train T.yaml --infer I.yaml --orch O.yaml --trainer-gpus 0-3 --vllm-gpus 4-7`` (disjoint GPU sets) and
+    ``grpo-colocate --train T.yaml --infer I.yaml --orch O.yaml [--gpus 0-7]`` (shared GPUs): one supervisor, three components."""
+    from ..grpo.runners import Supervisor, plan_colocate, plan_split
+
+    p = argparse.ArgumentParser(prog=f"surogate {command}")
+    p.add_argument("--train", required=True)
+    p.add_argument("--infer", required=True)
+    p.add_argument("--orch", required=True)
+    p.add_argument("--max-steps", type=int, default=None, dest="max_steps")
+    p.add_argument("--dry-run", action="store_true", help="print the component commands and exit")
+    if command == "grpo-train":
+        p.add_argument("--trainer-gpus", required=True)
+        p.add_argument("--vllm-gpus", required=True)
+        p.add_argument("--judge-config", default=None)
+        p.add_argument("--judge-gpus", default=None)
+    else:
+        p.add_argument("--gpus", default=None)
+        p.add_argument("--engine-memory-fraction", type=float, default=None)
+    a = p.parse_args(argv)
+    from ..config.loader import read_yaml
+
+    raw = read_yaml(a.infer)
+    tp, dp = int(raw.get("tensor_parallel_size", 1)), int(raw.get("data_parallel_size", 1))
+    if command == "grpo-train":
+        jtp = int(read_yaml(a.judge_config).get("tensor_parallel_size", 1)) if a.judge_config else 1
+        comps = plan_split(a.train, a.infer, a.orch, a.trainer_gpus, a.vllm_gpus, tp, dp, a.judge_config, a.judge_gpus, jtp, max_steps=a.max_steps)
+    else:
+        comps = plan_colocate(a.train, a.infer, a.orch, a.gpus, max_steps=a.max_steps,
+                              engine_memory_fraction=a.engine_memory_fraction or float(raw.get("gpu_memory_utilization", 0.45)))
+    if a.dry_run:
+        for c in comps:
+            print(json.dumps({"name": c.name, "argv": c.argv, "env": c.env}))
+        return 0
+    return Supervisor(comps).run()
+
+
 def main(argv, command: str = "grpo") -> int:
+    if command in ("grpo-train", "grpo-colocate"):
+        return _run_all(argv, command)
     p = argparse.ArgumentParser(prog=f"surogate {command}")
     p.add_argument("config")
     p.add_argument("--trainer-gpus", default=None)

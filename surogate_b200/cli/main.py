@@ -1,6 +1,6 @@
 """``surogate`` command: argparse front end that dispatches to the workflow modules.
 
-Commands: sft, pt, merge, tokenize, debug, dpo, grpo, grpo-infer, grpo-orch, distill-capture,
+Commands: sft, pt, merge, tokenize, debug, dpo, grpo, grpo-infer, grpo-orch, grpo-train, grpo-colocate, distill-capture,
 transplant-tokenizer, eval, export, chat, monitor, vf-init, vf-eval, info.
 
 Parity: surogate/cli/main.py:42-58 (COMMAND_MAPPING), :193-204 (cli_main).
@@ -23,6 +23,8 @@ COMMAND_MAPPING: Dict[str, str] = {
     "grpo": "surogate_b200.cli.grpo",
     "grpo-infer": "surogate_b200.cli.grpo",
     "grpo-orch": "surogate_b200.cli.grpo",
+    "grpo-train": "surogate_b200.cli.grpo",
+    "grpo-colocate": "surogate_b200.cli.grpo",
     "distill-capture": "surogate_b200.cli.distill",
     "transplant-tokenizer": "surogate_b200.cli.transplant",
     "export": "surogate_b200.cli.export",
@@ -65,7 +67,7 @@ def cli_main(argv: Optional[List[str]] = None) -> int:
     if cmd not in COMMAND_MAPPING:
         print(f"unknown command '{cmd}' (known: {', '.join(sorted(COMMAND_MAPPING))})", file=sys.stderr)
         return 2
-    if cmd.startswith("grpo"):
+    if cmd in ("grpo", "grpo-infer", "grpo-orch"):
         mask_gpus_for_grpo(argv)
     if int(os.environ.get("RANK", "0")) == 0 and os.environ.get("SUROGATE_NO_BANNER") != "1":
         print_banner()

@@ -22,6 +22,9 @@ from .weight_broadcast import FilesystemBroadcast
 
 
 def server_command(cfg: InferenceConfig) -> List[str]:
+    frac = os.environ.get("SUROGATE_ENGINE_MEMORY_FRACTION")   # set by the colocate runner: the trainer shares these GPUs
+    if frac:
+        cfg.gpu_memory_utilization = min(cfg.gpu_memory_utilization, float(frac))
     cmd = [sys.executable, "-m", "vllm.entrypoints.openai.api_server", "--model", cfg.model, "--host", cfg.host, "--port", str(cfg.port),
            "--tensor-parallel-size", str(cfg.tensor_parallel_size), "--gpu-memory-utilization", str(cfg.gpu_memory_utilization)]
     if cfg.max_model_len:

@@ -1,0 +1,220 @@
+"""Asynchronous orchestrator loop: the scheduler keeps group requests in flight on a thread pool while finished groups are
+scored, filtered, turned into advantages and shipped to the trainer; the example buffer steers sampling away from prompts
+without signal; the depth budget caps multi-turn episodes; progress and buffer pools are checkpointed for resume.
+
+    while step < max_steps:
+        scheduler.on_policy_update(version published by the trainer)
+        scheduler.fill(step); scheduler.collect()
+        if scheduler.batch_ready():
+            groups  = scheduler.take_batch()
+            filters -> advantages -> buffer.update(groups) -> pack -> transport.send(step)
+
+Parity: surogate/grpo/orchestrator/grpo_orch.py:150-1011 (main loop), ckpt.py:26-119 (orchestrator checkpoints).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from concurrent.futures import Future, ThreadPoolExecutor
+from dataclasses import asdict, dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from ..packer import Rollout, pack_rollouts
+from .advantage import compute_advantages
+from .buffer import BufferConfig, ExampleBuffer
+from .depth import DepthObservation, RolloutDepthController
+from .filters import apply_filters, make_filters
+from .scheduler import RolloutScheduler, SchedulerConfig
+
+
+@dataclass
+class AsyncOrchestratorConfig:
+    group_size: int = 8
+    batch_size: int = 64                       # rollouts per trainer step
+    token_batch_size: Optional[int] = None
+    sequence_len: int = 2048
+    rows_per_step: int = 8
+    max_steps: int = 100
+    max_inflight: int = 16
+    max_async_level: int = 2
+    max_off_policy_steps: int = 4
+    workers: int = 16                          # threads that wait on the inference server
+    advantage: str = "default"                 # default | std | module:function
+    length_weighted_mean: bool = False
+    filters: List[Dict[str, Any]] = field(default_factory=list)
+    buffer: Dict[str, Any] = field(default_factory=dict)
+    depth: Dict[str, Any] = field(default_factory=lambda: {"enabled": False})
+    sampling: Dict[str, Any] = field(default_factory=lambda: {"max_tokens": 512, "temperature": 1.0})
+    checkpoint_dir: Optional[str] = None
+    checkpoint_every: int = 0
+    keep_checkpoints: int = 2
+    poll_s: float = 0.01
+    step_timeout_s: float = 3600.0
+    vocab_size: int = 32000
+    pad_token_id: int = 0
+
+
+@dataclass
+class Progress:
+    step: int = 0
+    total_tokens: int = 0
+    total_samples: int = 0
+    total_problems: int = 0
+
+
+class OrchestratorCheckpoints:
+    """``<dir>/step_N/{progress.json, buffer/*.jsonl}``; old steps are pruned."""
+
+    def __init__(self, directory: str, keep: int = 2):
+        self.dir, self.keep = directory, keep
+
+    def path(self, step: int) -> str:
+        return os.path.join(self.dir, f"step_{step}")
+
+    def save(self, progress: Progress, buffer: ExampleBuffer) -> str:
+        p = self.path(progress.step)
+        os.makedirs(p, exist_ok=True)
+        buffer.save(os.path.join(p, "buffer"))
+        tmp = os.path.join(p, "progress.json.tmp")
+        with open(tmp, "w") as f:
+            json.dump(asdict(progress), f)
+        os.replace(tmp, os.path.join(p, "progress.json"))
+        import shutil
+
+        for s in self.steps()[:-self.keep]:
+            shutil.rmtree(self.path(s), ignore_errors=True)
+        return p
+
+    def steps(self) -> List[int]:
+        if not os.path.isdir(self.dir):
+            return []
+        return sorted(int(d[5:]) for d in os.listdir(self.dir) if d.startswith("step_") and d[5:].isdigit()
+                      and os.path.exists(os.path.join(self.dir, d, "progress.json")))
+
+    def load_latest(self, buffer: ExampleBuffer) -> Optional[Progress]:
+        steps = self.steps()
+        if not steps:
+            return None
+        p = self.path(steps[-1])
+        with open(os.path.join(p, "progress.json")) as f:
+            prog = Progress(**json.load(f))
+        buffer.load(os.path.join(p, "buffer"))
+        return prog
+
+
+class AsyncOrchestrator:
+    """``generate_group(example, n, sampling, policy_version, server) -> [Rollout]`` does one prompt's group (single- or
+    multi-turn) and sets each rollout's ``reward``; it runs on a worker thread.  ``policy_version()`` reads the newest version
+    the trainer published; ``transport.send(step, arrays, meta)`` ships a packed batch."""
+
+    def __init__(self, cfg: AsyncOrchestratorConfig, examples: Sequence[Dict[str, Any]], generate_group: Callable[..., List[Rollout]], transport,
+                 policy_version: Callable[[], int], num_servers: int = 1, on_step: Optional[Callable[[Dict[str, float]], None]] = None):
+        self.cfg, self.transport, self.policy_version, self.on_step = cfg, transport, policy_version, on_step
+        self.buffer = ExampleBuffer(examples, BufferConfig(**cfg.buffer))
+        self.pool = ThreadPoolExecutor(max_workers=cfg.workers, thread_name_prefix="rollout")
+        self.generate_group = generate_group
+        sc = SchedulerConfig(batch_size=cfg.batch_size, token_batch_size=cfg.token_batch_size, group_size=cfg.group_size, max_inflight=cfg.max_inflight,
+                             max_async_level=cfg.max_async_level, max_off_policy_steps=cfg.max_off_policy_steps)
+        self.scheduler = RolloutScheduler(sc, self.buffer, self._submit, self._poll, self._cancel, num_servers)
+        self.scheduler.set_sampling_args(cfg.sampling)
+        self.filters = make_filters(cfg.filters, cfg.vocab_size)
+        self.depth = RolloutDepthController(**cfg.depth)
+        self.progress = Progress()
+        self.ckpt = OrchestratorCheckpoints(cfg.checkpoint_dir, cfg.keep_checkpoints) if cfg.checkpoint_dir else None
+        self.history: List[Dict[str, float]] = []
+
+    # ------------------------------------------------------------------ scheduler transport: futures on the pool
+    def _submit(self, example, version, server) -> Future:
+        return self.pool.submit(self.generate_group, example, self.cfg.group_size, dict(self.scheduler.sampling), version, server)
+
+    @staticmethod
+    def _poll(fut: Future):
+        return fut.result() if fut.done() else None
+
+    @staticmethod
+    def _cancel(fut: Future) -> None:
+        fut.cancel()   # a request already on the wire finishes and is discarded
+
+    # ------------------------------------------------------------------ one trainer batch
+    def resume(self) -> int:
+        if self.ckpt is not None:
+            got = self.ckpt.load_latest(self.buffer)
+            if got is not None:
+                self.progress = got
+        return self.progress.step
+
+    def _score(self, groups: List[List[Rollout]]) -> Dict[str, float]:
+        flat = [r for g in groups for r in g]
+        stats = apply_filters(self.filters, flat)
+        sizes = {len(g) for g in groups}
+        if len(sizes) == 1:
+            n = sizes.pop()
+            adv = compute_advantages([r.reward for r in flat], [len(r.completion_ids) for r in flat], n, self.cfg.advantage,
+                                     **({"length_weighted_mean": True} if self.cfg.length_weighted_mean and self.cfg.advantage == "default" else {}))
+        else:   # ragged groups (a request returned fewer completions): one group at a time
+            adv = []
+            for g in groups:
+                adv += compute_advantages([r.reward for r in g], [len(r.completion_ids) for r in g], len(g), self.cfg.advantage)
+        for r, a in zip(flat, adv):
+            r.advantage = a
+        rewards = np.array([r.reward for r in flat], dtype=np.float64) if flat else np.zeros(1)
+        stats.update({"reward/mean": float(rewards.mean()), "reward/std": float(rewards.std()),
+                      "completion_len/mean": float(np.mean([len(r.completion_ids) for r in flat])) if flat else 0.0})
+        return stats
+
+    def run_step(self, step: int) -> Dict[str, float]:
+        t0 = time.time()
+        s = self.scheduler
+        self.buffer.reset_step_metrics()
+        s.set_depth_cap(self.depth.cap_for_step(step))
+        kept: List[Rollout] = []
+        observations: List[DepthObservation] = []
+        stats: Dict[str, float] = {}
+        while True:
+            s.on_policy_update(max(0, self.policy_version()))
+            s.fill(step)
+            s.collect()
+            if s.batch_ready() or (not s.inflight and s.ready):
+                groups = s.take_batch()
+                stats = self._score(groups)
+                for g in groups:
+                    for r in g:
+                        observations.append(DepthObservation(int(r.meta.get("turns", 1)), float(r.reward), bool(r.meta.get("truncated", False))))
+                self.buffer.update(groups)
+                want = self.cfg.batch_size if not s.uses_token_batching else len(self.buffer.rollouts)
+                kept += self.buffer.sample_rollouts(want - len(kept) if not s.uses_token_batching else want)
+                if (len(kept) >= self.cfg.batch_size and not s.uses_token_batching) or (s.uses_token_batching and sum(len(r) for r in kept) >= s.batch_target):
+                    break
+                if kept and not s.inflight and not s.ready and not s.may_issue(step):
+                    break
+            if time.time() - t0 > self.cfg.step_timeout_s:
+                raise TimeoutError(f"step {step}: no full batch within {self.cfg.step_timeout_s}s ({len(kept)} rollouts with signal so far)")
+            time.sleep(self.cfg.poll_s)
+        self.depth.observe(step, observations)
+        batches = pack_rollouts(kept, self.cfg.sequence_len, self.cfg.rows_per_step, self.cfg.pad_token_id)
+        first = batches[0]
+        meta = {"policy_version": min(r.policy_version for r in kept), "n_samples": first.n_samples, "reward_mean": stats.get("reward/mean", 0.0)}
+        self.transport.send(step, first.arrays(), meta)
+        self.progress.step = step + 1
+        self.progress.total_samples += len(kept)
+        self.progress.total_tokens += sum(len(r) for r in kept)
+        self.progress.total_problems += len({r.meta.get("example_id") for r in kept})
+        out = {"step": float(step), "time/step_s": time.time() - t0, **stats, **s.metrics(), **self.buffer.metrics(), **self.depth.metrics(),
+               "progress/total_tokens": float(self.progress.total_tokens), "progress/total_samples": float(self.progress.total_samples)}
+        if self.ckpt is not None and self.cfg.checkpoint_every and (step + 1) % self.cfg.checkpoint_every == 0:
+            self.ckpt.save(self.progress, self.buffer)
+        self.history.append(out)
+        if self.on_step is not None:
+            self.on_step(out)
+        return out
+
+    def run(self) -> List[Dict[str, float]]:
+        try:
+            for step in range(self.resume(), self.cfg.max_steps):
+                self.run_step(step)
+        finally:
+            self.pool.shutdown(wait=False, cancel_futures=True)
+        return self.history

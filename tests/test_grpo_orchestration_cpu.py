@@ -124,3 +124,104 @@ def test_depth_budget_follows_the_depths_that_earned_reward():
     assert c.cap >= 20 and c.metrics()["depth/cap"] == c.cap
     off = RolloutDepthController(enabled=False, max_cap=12)
     assert off.cap_for_step(3) == 12 and not off.is_probe_step(0)
+
+
+def test_async_loop_ships_batches_with_signal_and_resumes_from_its_checkpoint(tmp_path):
+    import threading
+
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, AsyncOrchestratorConfig
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    examples = [{"prompt": f"q{i}", "kind": "solved" if i < 4 else "mixed"} for i in range(12)]
+    calls = {"n": 0}
+    lock = threading.Lock()
+
+    def generate_group(example, n, sampling, version, server):
+        with lock:
+            calls["n"] += 1
+        out = []
+        for k in range(n):
+            reward = 1.0 if example["kind"] == "solved" else float(k % 2)
+            out.append(Rollout(prompt_ids=[1, 2], completion_ids=list(range(3, 3 + 6 + k)), logprobs=[-0.5] * (6 + k), reward=reward, meta={"turns": 1 + k % 3}))
+        return out
+
+    version = {"v": 0}
+    cfg = AsyncOrchestratorConfig(group_size=4, batch_size=8, sequence_len=64, rows_per_step=4, max_steps=3, max_inflight=4, max_async_level=1, workers=4,
+                                  buffer={"easy_threshold": 1.0, "seed": 3}, checkpoint_dir=str(tmp_path / "ckpt"), checkpoint_every=1,
+                                  depth={"enabled": True, "min_observations": 4, "probe_every": 2, "max_cap": 9}, filters=[{"type": "repetition", "ngram": 2, "min_tokens": 1000}])
+    tr = FilesystemTransport(str(tmp_path / "rollouts"))
+    seen = []
+
+    def on_step(m):
+        seen.append(m)
+        version["v"] += 1     # the trainer consumed the batch and published
+
+    orch = AsyncOrchestrator(cfg, examples, generate_group, tr, lambda: version["v"], on_step=on_step)
+    hist = orch.run()
+    assert len(hist) == 3 and len(seen) == 3
+    for step in range(3):
+        arrays, meta = tr.receive(step, timeout_s=1)
+        assert arrays["inputs"].shape == (4, 64) and meta["n_samples"] == 8
+        adv = arrays["advantages"][arrays["targets"] != -100]
+        assert np.abs(adv).max() > 0 and set(np.round(np.unique(adv), 3)) == {-0.5, 0.5}     # only mixed-reward groups were shipped
+    assert orch.buffer.count("easy") >= 1 and hist[-1]["buffer/filtered_groups"] >= 0
+    assert hist[-1]["depth/cap"] >= 2 and hist[-1]["scheduler/off_policy_max"] <= cfg.max_off_policy_steps
+    # resume: progress and pools come back
+    again = AsyncOrchestrator(AsyncOrchestratorConfig(**{**cfg.__dict__, "max_steps": 4}), examples, generate_group, tr, lambda: 10)
+    assert again.resume() == 3 and again.buffer.count("easy") == orch.buffer.count("easy")
+    again.run()
+    assert tr.ready(3)
+
+
+def test_gpu_sets_are_validated_and_a_failing_component_takes_the_run_down(tmp_path):
+    import sys
+    import time
+
+    import pytest
+
+    from surogate_b200.grpo.runners import Component, Supervisor, check_disjoint, check_topology, parse_gpu_ids, plan_colocate, plan_split
+
+    assert parse_gpu_ids("0-2,5") == [0, 1, 2, 5] and parse_gpu_ids("") == []
+    with pytest.raises(ValueError, match="twice"):
+        parse_gpu_ids("0,0")
+    with pytest.raises(ValueError, match="both"):
+        check_disjoint(("trainer", [0, 1]), ("rollout engine", [1, 2]))
+    with pytest.raises(ValueError, match="needs 4"):
+        check_topology("rollout engine", [4, 5], tensor_parallel=2, data_parallel=2)
+    comps = plan_split("t.yaml", "i.yaml", "o.yaml", "0-3", "4-7", tensor_parallel=2, data_parallel=2, max_steps=5)
+    by = {c.name: c for c in comps}
+    assert by["trainer"].env["CUDA_VISIBLE_DEVICES"] == "0,1,2,3" and "--nproc-per-node=4" in by["trainer"].argv and "127.0.0.1" in by["trainer"].argv
+    assert by["rollout engine"].env["CUDA_VISIBLE_DEVICES"] == "4,5,6,7" and by["orchestrator"].env["CUDA_VISIBLE_DEVICES"] == ""
+    with pytest.raises(ValueError, match="judge"):
+        plan_split("t", "i", "o", "0", "1", judge_cfg="j.yaml")
+    co = plan_colocate("t.yaml", "i.yaml", "o.yaml", "0,1", engine_memory_fraction=0.4)
+    assert co[0].env["SUROGATE_ENGINE_MEMORY_FRACTION"] == "0.4" and co[1].env["SUROGATE_GRPO_COLOCATE"] == "1"
+    # supervision with stand-in processes: the engine sleeps, the orchestrator fails -> everything stops, its code is returned
+    marker = tmp_path / "engine_stopped"
+    engine = Component("rollout engine", [sys.executable, "-c", "import signal,sys,time,pathlib\n"
+                                          f"signal.signal(signal.SIGTERM, lambda *a: (pathlib.Path(r'{marker}').write_text('x'), sys.exit(0)))\n"
+                                          "time.sleep(60)"])
+    bad = Component("orchestrator", [sys.executable, "-c", "import sys,time; time.sleep(0.3); sys.exit(7)"])
+    log = []
+    t0 = time.time()
+    rc = Supervisor([engine, bad], grace_s=5, poll_s=0.05, log=log.append).run(timeout_s=30)
+    assert rc == 7 and time.time() - t0 < 20 and marker.exists() and engine.proc.poll() is not None
+    # trainer finishing ends the run with 0 and stops the engine
+    engine2 = Component("rollout engine", [sys.executable, "-c", "import time; time.sleep(60)"])
+    trainer = Component("trainer", [sys.executable, "-c", "print('done')"], ends_run_on_success=True)
+    assert Supervisor([engine2, trainer], grace_s=5, poll_s=0.05, log=log.append).run(timeout_s=30) == 0 and engine2.proc.poll() is not None
+
+
+def test_cli_dry_run_lists_the_three_components(tmp_path, capsys):
+    import json as _json
+
+    from surogate_b200.cli.main import cli_main
+
+    for n in ("t", "i", "o"):
+        (tmp_path / f"{n}.yaml").write_text("tensor_parallel_size: 1\n")
+    rc = cli_main(["grpo-train", "--train", str(tmp_path / "t.yaml"), "--infer", str(tmp_path / "i.yaml"), "--orch", str(tmp_path / "o.yaml"),
+                   "--trainer-gpus", "0", "--vllm-gpus", "1", "--dry-run"])
+    lines = [_json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert rc == 0 and [l["name"] for l in lines] == ["rollout engine", "trainer", "orchestrator"]
+    rc = cli_main(["grpo-colocate", "--train", str(tmp_path / "t.yaml"), "--infer", str(tmp_path / "i.yaml"), "--orch", str(tmp_path / "o.yaml"), "--dry-run"])
+    assert rc == 0 and "grpo-infer" in capsys.readouterr().out
