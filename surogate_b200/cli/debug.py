@@ -1,4 +1,6 @@
-"""``surogate debug {weights,registry,activations,gradients,diff,determinism,sanitize}``.  Parity: surogate/cli/debug.py."""
+"""``surogate debug {weights,registry,activations,gradients,diff,determinism,sanitize,tensor-arena,tensor-layout,tensor-aliasing,tensor-resolve}``.
+
+Parity: surogate/cli/debug.py."""
 from __future__ import annotations
 
 import argparse
@@ -18,7 +20,32 @@ def main(argv, command: str = "debug") -> int:
         s.add_argument("--seq-len", type=int, default=128)
         s.add_argument("--batch", type=int, default=1)
         s.add_argument("--seed", type=int, default=0)
+    for name in ("tensor-arena", "tensor-layout", "tensor-aliasing", "tensor-resolve"):
+        s = sub.add_parser(name, help="compile-only introspection of the buffer plan (no weights, no GPU)")
+        s.add_argument("model", help="model directory or config.json")
+        s.add_argument("--out", default=None)
+        s.add_argument("--seq-len", type=int, default=2048)
+        s.add_argument("--batch", type=int, default=1)
+        if name == "tensor-arena":
+            s.add_argument("--recompute", action="store_true")
+        if name == "tensor-aliasing":
+            s.add_argument("--mode", choices=["static", "runtime"], default="static")
+        if name == "tensor-resolve":
+            s.add_argument("--name", required=True)
     a = p.parse_args(argv)
+    if a.what.startswith("tensor-"):
+        from ..debug import tensor_tools as tt
+
+        if a.what == "tensor-arena":
+            rows = tt.tensor_arena(a.model, a.batch, a.seq_len, a.recompute, a.out)
+        elif a.what == "tensor-layout":
+            rows = tt.tensor_layout(a.model, a.batch, a.seq_len, a.out)
+        elif a.what == "tensor-aliasing":
+            rows = tt.tensor_aliasing(a.model, a.batch, min(a.seq_len, 256) if a.mode == "runtime" else a.seq_len, a.mode, a.out)
+        else:
+            rows = tt.tensor_resolve(a.model, a.name, a.batch, a.seq_len, a.out)
+        tt.main_json(rows)
+        return 0
     if a.what == "sanitize":
         from ..debug.sanitize import run
 

