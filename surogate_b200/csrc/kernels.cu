@@ -25,6 +25,11 @@ __device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(t.v[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
 }
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+    const bf162* t = reinterpret_cast<const bf162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(t[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
 __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
     Vec8 t;
 #pragma unroll
@@ -139,20 +144,28 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __r
         const size_t base = static_cast<size_t>(row) * C;
         const float rs = rstd[row];
         float dot = 0.f;
-        float gk[KEEP ? ITERS : 1][8], ak[KEEP ? ITERS : 1][8];
+        // the row stays in registers as packed bf16 between the two passes (KEEP), and the incoming residual gradient is requested
+        // together with dy and x, so that its latency hides behind the block reduction instead of following it
+        uint4 gk[KEEP ? ITERS : 1], ak[KEEP ? ITERS : 1], rk[KEEP ? ITERS : 1];
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int c = (it * blockDim.x + threadIdx.x) * 8;
             if (c < C) {
+                const uint4 graw = *reinterpret_cast<const uint4*>(dy + base + c);
+                const uint4 araw = *reinterpret_cast<const uint4*>(x + base + c);
+                if (KEEP) {
+                    gk[it] = graw;
+                    ak[it] = araw;
+                    if (d_res) rk[it] = *reinterpret_cast<const uint4*>(d_res + base + c);
+                }
                 float g[8], a[8];
-                load8(dy + base + c, g);
-                load8(x + base + c, a);
+                unpack8(graw, g);
+                unpack8(araw, a);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float xhat = a[i] * rs;
                     dot += g[i] * ww[it][i] * xhat;
                     dw[it][i] += g[i] * xhat;
-                    if (KEEP) { gk[it][i] = g[i]; ak[it][i] = a[i]; }
                 }
             }
         }
@@ -163,8 +176,8 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __r
             if (c < C) {
                 float g[8], a[8], o[8];
                 if (KEEP) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) { g[i] = gk[it][i]; a[i] = ak[it][i]; }
+                    unpack8(gk[it], g);
+                    unpack8(ak[it], a);
                 } else {
                     load8(dy + base + c, g);
                     load8(x + base + c, a);
@@ -173,7 +186,8 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const bf16* __r
                 for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[it][i] - a[i] * rs * dot);
                 if (d_res) {
                     float r[8];
-                    load8(d_res + base + c, r);
+                    if (KEEP) unpack8(rk[it], r);
+                    else load8(d_res + base + c, r);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] += r[i];
                 }
@@ -281,9 +295,16 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------ QK-norm + RoPE
-// One warp per (token, head); head_dim 128: lane l holds elements [4l, 4l+4); rotary partner (i +/- 64) lives in lane l^16.
+// Half a warp per (token, head); head_dim 128: lane s = lane & 15 of the half holds elements [8s, 8s+8) (one 16-byte access), the
+// rotary partner (i +/- 64) lives in lane s ^ 8 of the same half.  A warp works on one token at a time and walks all of its heads,
+// two at a time (one per half-warp), so the rotation angles (sin / cos of position x frequency) are evaluated once per token.
 // Layout per token: [Hq heads | Hkv heads (K) | Hkv heads (V)] x D.  V heads are copied (forward) / passed through (backward).
-constexpr int ROPE_HEAD_GROUP = 8;
+constexpr int ROPE_PAIRS_IN_FLIGHT = 4;      // head pairs whose loads are issued before the first is used
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
 template <bool BACKWARD>
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restrict__ in, const bf16* __restrict__ qkv_pre, const bf16* __restrict__ qw,
                                                            const bf16* __restrict__ kw, const int* __restrict__ pos, bf16* __restrict__ out,
@@ -294,6 +315,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
     // ``tokens`` entries (temporal, height, width) and frequency j uses the height row if j % 3 == 1 and j < lim_h, the width
     // row if j % 3 == 2 and j < lim_w, else the temporal row.
     constexpr int D = 128;
+    constexpr int U = ROPE_PAIRS_IN_FLIGHT;
     __shared__ float sdw[2][D];
     const bool multi_axis = (lim_h | lim_w) != 0;
     if (BACKWARD) {
@@ -302,135 +324,134 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const bf16* __restric
     }
     const int H = Hq + 2 * Hkv;
     const int lane = threadIdx.x & 31;
+    const int sub = lane & 15, hsel = lane >> 4;
     const size_t warps_total = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
-    // One work item = one token x a group of ROPE_HEAD_GROUP heads: the rotation angles depend only on the token and the lane, so
-    // sin / cos are evaluated once per item and reused for every head of the group; the frequencies depend only on the lane and
-    // are computed once per thread.
-    const int groups = (H + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP;
-    const size_t items = tokens * groups;
     const bool use_norm = qw != nullptr;
-    float dw_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // this lane's 4 elements: [q|k] norm-weight grads
-    float inv[4], wq4[4] = {1.f, 1.f, 1.f, 1.f}, wk4[4] = {1.f, 1.f, 1.f, 1.f};
-    int axis[4];
-    if (use_norm) {
+    float dw_acc[2][8];      // this lane's 8 elements: [q|k] norm-weight grads
+    float inv[8], wq8[8], wk8[8];
+    int axis[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            wq4[i] = __bfloat162float(qw[lane * 4 + i]);
-            wk4[i] = __bfloat162float(kw[lane * 4 + i]);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int j = (lane * 4 + i) & 63;
+    for (int i = 0; i < 8; ++i) {
+        dw_acc[0][i] = 0.f;
+        dw_acc[1][i] = 0.f;
+        wq8[i] = use_norm ? __bfloat162float(qw[sub * 8 + i]) : 1.f;
+        wk8[i] = use_norm ? __bfloat162float(kw[sub * 8 + i]) : 1.f;
+        const int j = (sub * 8 + i) & 63;
         inv[i] = exp2f(-log2_theta * (2.f * j) / D);
         const int m3 = j % 3;
         axis[i] = (m3 == 1 && j < lim_h) ? 1 : ((m3 == 2 && j < lim_w) ? 2 : 0);
     }
-    for (size_t it = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += warps_total) {
-        const size_t tok = it / groups;
-        const int h0 = static_cast<int>(it % groups) * ROPE_HEAD_GROUP;
-        const int h1 = min(H, h0 + ROPE_HEAD_GROUP);
+    const float sign = (sub < 8) ? -1.f : 1.f;  // first half of the head: x1*c - x2*s ; second half: x2*c + x1*s
+    for (size_t tok = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); tok < tokens; tok += warps_total) {
         const float p = static_cast<float>(pos[tok]);
         float p_h = p, p_w = p;
         if (multi_axis) {
             p_h = static_cast<float>(pos[tokens + tok]);
             p_w = static_cast<float>(pos[2 * tokens + tok]);
         }
-        float cs[4], sn[4];
+        float cs[8], sn[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sincosf((axis[i] == 1 ? p_h : (axis[i] == 2 ? p_w : p)) * inv[i], &sn[i], &cs[i]);
-        // all loads of the group are issued before any of them is used
-        uint2 raws[ROPE_HEAD_GROUP], pres[ROPE_HEAD_GROUP];
+        for (int i = 0; i < 8; ++i) sincosf((axis[i] == 1 ? p_h : (axis[i] == 2 ? p_w : p)) * inv[i], &sn[i], &cs[i]);
+        const size_t tbase = tok * static_cast<size_t>(H) * D + sub * 8;
+        for (int hb = 0; hb < H; hb += 2 * U) {
+            // all loads of this batch of head pairs are issued before any of them is used
+            uint4 raws[U], pres[U];
 #pragma unroll
-        for (int u = 0; u < ROPE_HEAD_GROUP; ++u) {
-            const int h = h0 + u;
-            if (h < h1) {
-                const size_t off = (tok * H + h) * D + lane * 4;
-                raws[u] = *reinterpret_cast<const uint2*>(in + off);
-                if (BACKWARD && use_norm && h < Hq + Hkv) pres[u] = *reinterpret_cast<const uint2*>(qkv_pre + off);
+            for (int u = 0; u < U; ++u) {
+                const int h = hb + 2 * u + hsel;
+                if (h < H) {
+                    const size_t off = tbase + static_cast<size_t>(h) * D;
+                    raws[u] = *reinterpret_cast<const uint4*>(in + off);
+                    if (BACKWARD && use_norm && h < Hq + Hkv) pres[u] = *reinterpret_cast<const uint4*>(qkv_pre + off);
+                }
             }
-        }
 #pragma unroll
-        for (int u = 0; u < ROPE_HEAD_GROUP; ++u) {
-            const int h = h0 + u;
-            if (h >= h1) break;
-            const size_t off = (tok * H + h) * D + lane * 4;
-            const uint2 raw = raws[u];
-            if (h >= Hq + Hkv) {  // V: identity
-                *reinterpret_cast<uint2*>(out + off) = raw;
-                continue;
-            }
-            const bool is_q = h < Hq;
-            float v[4];
-            {
-                const bf162* pb = reinterpret_cast<const bf162*>(&raw);
-                const float2 a = __bfloat1622float2(pb[0]), b = __bfloat1622float2(pb[1]);
-                v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-            }
-            const float sign = (lane < 16) ? -1.f : 1.f;  // first half: x1*c - x2*s ; second half: x2*c + x1*s
-            if (!BACKWARD) {
-                float rstd = 1.f;
-                if (use_norm) {
-                    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-                    ss = warp_sum(ss);
-                    rstd = rsqrtf(ss / D + eps);
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * (is_q ? wq4[i] : wk4[i]);
-                    if (lane == 0) {
-                        if (is_q) q_rstd[tok * Hq + h] = rstd;
-                        else k_rstd[tok * Hkv + (h - Hq)] = rstd;
+            for (int u = 0; u < U; ++u) {
+                const int h = hb + 2 * u + hsel;
+                // a half-warp whose head index ran past H still takes part in the shuffles of the other half's head
+                const bool live = h < H;
+                const bool is_v = h >= Hq + Hkv;
+                const bool is_q = h < Hq;
+                const size_t off = tbase + static_cast<size_t>(h) * D;
+                if (hb + 2 * u >= H) break;           // both halves past the end (uniform over the warp)
+                float v[8];
+                if (live) unpack8(raws[u], v);
+                else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+                }
+                if (!BACKWARD) {
+                    float rstd = 1.f;
+                    if (use_norm) {
+                        float ss = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+                        ss = half_warp_sum(ss);
+                        rstd = rsqrtf(ss / D + eps);
+                        if (live && !is_v) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * (is_q ? wq8[i] : wk8[i]);
+                            if (sub == 0) {
+                                if (is_q) q_rstd[tok * Hq + h] = rstd;
+                                else k_rstd[tok * Hkv + (h - Hq)] = rstd;
+                            }
+                        }
+                    }
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float partner = __shfl_xor_sync(0xffffffffu, v[i], 8);
+                        o[i] = v[i] * cs[i] + sign * partner * sn[i];
+                    }
+                    if (live) {
+                        if (is_v) *reinterpret_cast<uint4*>(out + off) = raws[u];
+                        else store8(out + off, o);
+                    }
+                } else {
+                    // v = d(out).  Inverse rotation: g1 = d1*c + d2*s ; g2 = d2*c - d1*s
+                    float g[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float partner = __shfl_xor_sync(0xffffffffu, v[i], 8);
+                        g[i] = v[i] * cs[i] - sign * partner * sn[i];
+                    }
+                    if (use_norm) {
+                        float xin[8];
+                        const bool normed = live && !is_v;
+                        if (normed) unpack8(pres[u], xin);
+                        else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) xin[i] = 0.f;
+                        }
+                        const float rstd = normed ? (is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)]) : 0.f;
+                        float dot = 0.f, dn[8], xhat[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            xhat[i] = xin[i] * rstd;
+                            dn[i] = g[i] * (is_q ? wq8[i] : wk8[i]);
+                            dot += dn[i] * xhat[i];
+                        }
+                        if (normed) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
+                        }
+                        dot = half_warp_sum(dot) / D;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) g[i] = rstd * (dn[i] - xhat[i] * dot);
+                    }
+                    if (live) {
+                        if (is_v) *reinterpret_cast<uint4*>(out + off) = raws[u];
+                        else store8(out + off, g);
                     }
                 }
-                float o[4];
-    #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                    o[i] = v[i] * cs[i] + sign * partner * sn[i];
-                }
-                uint2 w2;
-                bf162* pw = reinterpret_cast<bf162*>(&w2);
-                pw[0] = __floats2bfloat162_rn(o[0], o[1]);
-                pw[1] = __floats2bfloat162_rn(o[2], o[3]);
-                *reinterpret_cast<uint2*>(out + off) = w2;
-            } else {
-                // v = d(out).  Inverse rotation: g1 = d1*c + d2*s ; g2 = d2*c - d1*s
-                float g[4];
-    #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                    g[i] = v[i] * cs[i] - sign * partner * sn[i];
-                }
-                if (use_norm) {
-                    const uint2 xr = pres[u];
-                    const bf162* px = reinterpret_cast<const bf162*>(&xr);
-                    const float2 a = __bfloat1622float2(px[0]), b = __bfloat1622float2(px[1]);
-                    const float xin[4] = {a.x, a.y, b.x, b.y};
-                    const float rstd = is_q ? q_rstd[tok * Hq + h] : k_rstd[tok * Hkv + (h - Hq)];
-                    float dot = 0.f, dn[4], xhat[4];
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        xhat[i] = xin[i] * rstd;
-                        dn[i] = g[i] * (is_q ? wq4[i] : wk4[i]);
-                        dot += dn[i] * xhat[i];
-                        dw_acc[is_q ? 0 : 1][i] += g[i] * xhat[i];
-                    }
-                    dot = warp_sum(dot) / D;
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i) g[i] = rstd * (dn[i] - xhat[i] * dot);
-                }
-                uint2 w2;
-                bf162* pw = reinterpret_cast<bf162*>(&w2);
-                pw[0] = __floats2bfloat162_rn(g[0], g[1]);
-                pw[1] = __floats2bfloat162_rn(g[2], g[3]);
-                *reinterpret_cast<uint2*>(out + off) = w2;
             }
         }
     }
     if (BACKWARD && use_norm) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            atomicAdd(&sdw[0][lane * 4 + i], dw_acc[0][i]);
-            atomicAdd(&sdw[1][lane * 4 + i], dw_acc[1][i]);
+        for (int i = 0; i < 8; ++i) {
+            atomicAdd(&sdw[0][sub * 8 + i], dw_acc[0][i]);
+            atomicAdd(&sdw[1][sub * 8 + i], dw_acc[1][i]);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -902,7 +923,7 @@ static int rmsnorm_bwd_iters(int C) {
 }
 // CTAs for a [rows, C] problem: as many per SM as the register budget of the variant allows (see the kernel comment)
 int rmsnorm_bwd_blocks_wide(int rows, int C, int num_sms) {
-    const int per_sm = C <= 1024 ? 8 : 2;
+    const int per_sm = C <= 1024 ? 8 : (C <= 4096 ? 3 : 2);
     return rows < num_sms * per_sm ? rows : num_sms * per_sm;
 }
 void rmsnorm_bwd_n(const void* dy, const void* x, const void* w, const float* rstd, const void* d_res, void* dx, float* dw_partial, float* dw, int rows,
@@ -960,16 +981,14 @@ void zero_empty_groups(void* out, const int* offsets, int groups, size_t bytes_p
 }
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* out, float* q_rstd, float* k_rstd, size_t tokens, int Hq,
                       int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms, cudaStream_t s) {
-    const size_t items = tokens * ((Hq + 2 * Hkv + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP);
-    qk_norm_rope_kernel<false><<<grid_for(items * 32, 256, num_sms), 256, 0, s>>>((const bf16*)qkv, nullptr, (const bf16*)qw, (const bf16*)kw, pos,
+    qk_norm_rope_kernel<false><<<grid_for(tokens * 32, 256, num_sms, 8), 256, 0, s>>>((const bf16*)qkv, nullptr, (const bf16*)qw, (const bf16*)kw, pos,
                                                                                    (bf16*)out, q_rstd, k_rstd, nullptr, nullptr, tokens, Hq, Hkv, eps,
                                                                                    log2f(theta), lim_h, lim_w);
 }
 void qk_norm_rope_bwd(const void* d_out, const void* qkv_pre, const void* qw, const void* kw, const int* pos, void* d_qkv, float* q_rstd,
                       float* k_rstd, float* dqw, float* dkw, size_t tokens, int Hq, int Hkv, float eps, float theta, int lim_h, int lim_w, int num_sms,
                       cudaStream_t s) {
-    const size_t items = tokens * ((Hq + 2 * Hkv + ROPE_HEAD_GROUP - 1) / ROPE_HEAD_GROUP);
-    qk_norm_rope_kernel<true><<<grid_for(items * 32, 256, num_sms, 4), 256, 0, s>>>((const bf16*)d_out, (const bf16*)qkv_pre, (const bf16*)qw,
+    qk_norm_rope_kernel<true><<<grid_for(tokens * 32, 256, num_sms, 4), 256, 0, s>>>((const bf16*)d_out, (const bf16*)qkv_pre, (const bf16*)qw,
                                                                                      (const bf16*)kw, pos, (bf16*)d_qkv, q_rstd, k_rstd, dqw, dkw, tokens,
                                                                                      Hq, Hkv, eps, log2f(theta), lim_h, lim_w);
 }

@@ -187,11 +187,13 @@ def test_swiglu(ext):
     assert _rel_err(dx, ref) < 5e-3
 
 
-def test_qk_norm_rope(ext):
+@pytest.mark.parametrize("B,T,Hq,Hkv", [(2, 96, 8, 2), (1, 50, 3, 1), (1, 300, 32, 8), (2, 33, 5, 5)])
+def test_qk_norm_rope(ext, B, T, Hq, Hkv):
+    """Even and odd head counts (a half-warp without a head of its own still takes part in the shuffles), the benchmark's 32 / 8."""
     from surogate_b200.dsl.ir import OpNode
     from surogate_b200.runtime.ops_ref import RefOps
 
-    B, T, Hq, Hkv, D = 2, 96, 8, 2, 128
+    D = 128
     qkv = torch.randn(B, T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
     qw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
     kw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()

@@ -65,6 +65,19 @@ def test_regression_harness_detects_a_changed_loss():
     assert any("loss[1]" in p for p in compare(a, b, time_factor=100.0))
 
 
+def test_locked_regression_baselines_still_hold():
+    """The committed artifacts (regression_baselines/locked) against a fresh run of the same cases: losses, layout, parameter count."""
+    from surogate_b200.regression.runner import compare, default_matrix, run_case
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "regression_baselines", "locked")
+    assert len([f for f in os.listdir(root) if f.endswith(".json")]) >= 7
+    for name in ("dense-bf16-adamw", "moe-bf16"):
+        case = next(c for c in default_matrix(False) if c.name == name)
+        with open(os.path.join(root, name + ".json")) as f:
+            base = json.load(f)
+        assert compare(run_case(case), base, time_factor=1e9, mem_factor=1e9) == [], name
+
+
 def test_sft_workflow_with_adapter_resume(tmp_path):
     from surogate_b200.config.sft_config import SFTConfig
     from surogate_b200.train.sft import run_training
