@@ -50,26 +50,59 @@ def native_teacher(trainer) -> TeacherFn:
     return fn
 
 
-def api_teacher_rows(base_url: str, model: str, k: int, timeout_s: float = 600.0):
-    """vLLM-style ``prompt_logprobs``: returns a function rows -> (indices, logprobs) directly (no logits leave the server)."""
+def api_teacher_rows(base_url: str, model: str, k: int, timeout_s: float = 600.0, workers: int = 8, retries: int = 3, api_key: str = "EMPTY"):
+    """vLLM-style ``prompt_logprobs``: returns a function rows -> (indices, logprobs) directly (no logits leave the server).
+
+    Rows of a call are requested concurrently (``workers`` threads: the server batches them), a failed request is retried with
+    back-off, and a position for which the server returned fewer than ``k`` entries is padded with log-prob -30 on token 0
+    (weightless in the distillation term)."""
+    import time
+    from concurrent.futures import ThreadPoolExecutor
+
     url = base_url.rstrip("/") + "/completions"
+
+    def one(row):
+        body = {"model": model, "prompt": [int(t) for t in row], "max_tokens": 1, "prompt_logprobs": k, "temperature": 0.0}
+        req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json", "Authorization": f"Bearer {api_key}"})
+        last = None
+        for attempt in range(retries):
+            try:
+                with urllib.request.urlopen(req, timeout=timeout_s) as resp:
+                    return json.loads(resp.read())["choices"][0]["prompt_logprobs"]
+            except Exception as e:  # noqa: BLE001 -- connection reset, 5xx, malformed body: all retried
+                last = e
+                time.sleep(min(2.0 ** attempt * 0.1, 5.0))
+        raise RuntimeError(f"teacher at {url} failed {retries} times: {last}")
 
     def fn(tokens: np.ndarray):
         idx = np.zeros(tokens.shape + (k,), np.int32)
         lp = np.full(tokens.shape + (k,), -30.0, np.float32)
-        for r, row in enumerate(tokens):
-            body = {"model": model, "prompt": [int(t) for t in row], "max_tokens": 1, "prompt_logprobs": k, "temperature": 0.0}
-            req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
-            with urllib.request.urlopen(req, timeout=timeout_s) as resp:
-                pl = json.loads(resp.read())["choices"][0]["prompt_logprobs"]
+        with ThreadPoolExecutor(max_workers=max(1, min(workers, len(tokens)))) as pool:
+            results = list(pool.map(one, tokens))
+        for r, pl in enumerate(results):
             # entry t (t >= 1) is the distribution that predicted token t: store it at position t-1
-            for t in range(1, len(pl)):
-                items = sorted(((int(tok), d["logprob"]) for tok, d in (pl[t] or {}).items()), key=lambda x: -x[1])[:k]
+            for t in range(1, min(len(pl), tokens.shape[1])):
+                items = sorted(((int(tok), d["logprob"] if isinstance(d, dict) else float(d)) for tok, d in (pl[t] or {}).items()), key=lambda x: -x[1])[:k]
                 for j, (tok, l) in enumerate(items):
                     idx[r, t - 1, j], lp[r, t - 1, j] = tok, l
         return idx, lp
 
     return fn
+
+
+def sidecar_complete(shard: str, seq_len: int, top_k: int, path: Optional[str] = None) -> bool:
+    """True when a sidecar with the expected K and number of positions already stands next to the shard (resume skips it)."""
+    from ..data.tokfile import read_header
+    from .sidecar import SidecarReader
+
+    p = path or sidecar_path(shard)
+    if not os.path.exists(p):
+        return False
+    try:
+        r = SidecarReader(p)
+        return r.K == top_k and r.N == (read_header(shard)["n_tokens"] // seq_len) * seq_len
+    except Exception:  # noqa: BLE001 -- truncated or foreign file: capture again
+        return False
 
 
 def capture_shard(shard: str, teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, temperature: float = 1.0, rows_per_call: int = 4,
@@ -88,5 +121,11 @@ def capture_shard(shard: str, teacher: TeacherFn, seq_len: int, top_k: int, voca
     return w.path
 
 
-def capture(shards: Iterable[str], teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, **kw) -> List[str]:
-    return [capture_shard(s, teacher, seq_len, top_k, vocab, **kw) for s in shards]
+def capture(shards: Iterable[str], teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, resume: bool = True, **kw) -> List[str]:
+    out = []
+    for s in shards:
+        if resume and sidecar_complete(s, seq_len, top_k, kw.get("out_path")):
+            out.append(kw.get("out_path") or sidecar_path(s))
+            continue
+        out.append(capture_shard(s, teacher, seq_len, top_k, vocab, **kw))
+    return out

@@ -60,3 +60,67 @@ def test_capture_and_distill(tmp_path):
         first = v if first is None else first
         last = v
     assert last < 0.5 * first, (first, last)  # the student moves toward the teacher's distribution
+
+
+def test_api_teacher_against_a_local_openai_style_server(tmp_path):
+    """``prompt_logprobs`` of an OpenAI-compatible completions endpoint (what vLLM serves) captured into a sidecar: concurrent rows,
+    one injected failure retried, alignment (entry t predicts token t -> stored at t-1), resume skips a complete sidecar."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from surogate_b200.distill.capture import api_teacher_rows, capture, sidecar_complete
+
+    teacher = _trainer(5)
+    calls = {"n": 0, "failed": False}
+    lock = threading.Lock()
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            with lock:
+                calls["n"] += 1
+                fail = not calls["failed"]
+                calls["failed"] = True
+            if fail:
+                self.send_response(503)
+                self.end_headers()
+                return
+            row = np.asarray(body["prompt"], np.int32)[None]
+            with lock:
+                lp = torch.log_softmax(teacher.logits(row)[0], -1)
+            k = body["prompt_logprobs"]
+            out = [None]
+            for t in range(1, row.shape[1]):
+                top = lp[t - 1].topk(k)
+                out.append({str(int(i)): {"logprob": float(v)} for i, v in zip(top.indices, top.values)})
+            data = json.dumps({"choices": [{"prompt_logprobs": out}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    try:
+        shard = write_synthetic_tokens(os.path.join(tmp_path, "train-000.bin"), 4, 16, 96, seed=2)
+        direct = api_teacher_rows(f"http://127.0.0.1:{srv.server_port}/v1", "teacher", 4, workers=3, timeout_s=20)
+        (kd_path,) = capture([shard], None, 16, 4, 96, rows_per_call=4, direct=direct)
+        n_first = calls["n"]
+        assert n_first == 5 and sidecar_complete(shard, 16, 4)            # 4 rows + the retried one
+        assert capture([shard], None, 16, 4, 96, rows_per_call=4, direct=direct) == [kd_path] and calls["n"] == n_first     # resumed: no request
+    finally:
+        srv.shutdown()
+    from surogate_b200.data.tokfile import read_token_file
+
+    tok, _, _, _ = read_token_file(shard)
+    x = np.asarray(tok[:16]).reshape(1, 16)
+    want = torch.log_softmax(teacher.logits(x)[0], -1).topk(4)
+    i0, l0 = SidecarReader(kd_path).rows(0, 16)
+    assert np.array_equal(i0[:15], want.indices.numpy()[:15]) and np.allclose(l0[:15], want.values.numpy()[:15], atol=5e-3)
+    assert np.all(l0[15] == -30.0)          # nothing predicts past the last token of a row
