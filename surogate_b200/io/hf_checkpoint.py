@@ -73,6 +73,14 @@ class LazyCheckpoint:
 def import_hf_weights(cm: CompiledModel, store, path: str, strict: bool = True) -> Dict[str, int]:
     direct = os.environ.get("SUROGATE_DEVICE_LOAD", "0") == "1" or os.environ.get("SUROGATE_GDS", "0") == "1"
     ckpt = LazyCheckpoint(path, device=store.device if direct else None)
+    cfg_path = os.path.join(ckpt.dir, "config.json")
+    hf_cfg = None
+    if os.path.exists(cfg_path):
+        with open(cfg_path) as f:
+            hf_cfg = json.load(f)
+    from .prequant import wrap_if_quantized
+
+    ckpt = wrap_if_quantized(ckpt, hf_cfg)      # block-FP8 / NVFP4 / MXFP4 / bitsandbytes checkpoints hand out dequantised tensors
     loaded = missing = 0
     for p in cm.params:
         m = p.spec.hf
@@ -93,7 +101,10 @@ def import_hf_weights(cm: CompiledModel, store, path: str, strict: bool = True) 
         t = m.load(ckpt.get, p.layer)
         store.load_tensor(p.name, t)
         loaded += 1
-    return {"loaded": loaded, "missing": missing}
+    out = {"loaded": loaded, "missing": missing}
+    if hasattr(ckpt, "stats"):
+        out["dequantised"] = {k: v for k, v in ckpt.stats.items() if v and k != "plain"}
+    return out
 
 
 def export_hf_weights(cm: CompiledModel, store, out_dir: str, hf_config: Optional[Dict[str, Any]] = None, write: bool = True,
