@@ -251,6 +251,11 @@ class ExpertParallel:
 
         if not self.count_window:
             return {"layers": 0, "moved": 0}
+        if getattr(store, "expert_offload", None) is not None:
+            # frozen experts held quantised (possibly in host memory): their placement is fixed, moving them would mean re-quantising
+            for w in self.count_window.values():
+                w.zero_()
+            return {"layers": 0, "moved": 0, "skipped": "quantised experts"}
         layers = sorted(self.count_window)
         stacked = torch.stack([self.count_window[L] for L in layers])
         replica_comm = getattr(self, "replica_comm", None)

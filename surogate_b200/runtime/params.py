@@ -328,7 +328,8 @@ class ParamStore:
         name = self.resolve(name)
         b, s = self.where[name]
         if b.expert:
-            return self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
+            flat = self._dequantized(b) if getattr(b, "qstate", None) is not None else b.master
+            return self._gather_experts(flat[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
         if getattr(b, "qstate", None) is not None:
             return self._dequantized(b)[s.offset:s.offset + s.numel].reshape(s.shape)
         if not self.sharded:
@@ -354,8 +355,9 @@ class ParamStore:
     def named_full_tensors(self) -> Iterable[Tuple[str, torch.Tensor]]:
         for b in self.buckets.values():
             if b.expert:
+                flat = self._dequantized(b) if getattr(b, "qstate", None) is not None else b.master
                 for s in b.slots:
-                    yield s.name, self._gather_experts(b.master[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
+                    yield s.name, self._gather_experts(flat[s.offset:s.offset + s.numel].reshape(s.shape), b.layer)
                 continue
             if getattr(b, "qstate", None) is not None:
                 full = self._dequantized(b)
@@ -375,12 +377,12 @@ class ParamStore:
         if self.fp8_gather:
             self.refresh_weight_scales()
         for b in self.buckets.values():
+            if getattr(b, "qstate", None) is not None:   # frozen and quantised (dense layer buckets, managed expert buckets): rebuilt on use
+                b.work = None
+                continue
             if b.expert:
                 if b.work is not b.master:
                     b.work.copy_(b.master)
-                continue
-            if getattr(b, "qstate", None) is not None:
-                b.work = None
                 continue
             if getattr(b, "work_host", None) is not None and not getattr(b, "work_host_fresh", False):
                 b.work_host.copy_(b.master)  # host-side conversion (init / load); the CPU optimizer writes it itself afterwards
@@ -401,7 +403,7 @@ class ParamStore:
         """Replace the master copy of every frozen, non-expert layer bucket by its block-quantised form.  The bf16 work
         weights are then rebuilt per layer when the executor reaches it and dropped afterwards, so at any time only one or
         two layers exist in bf16.  Returns the number of bytes saved."""
-        assert self.zero_level == 0 or self.world == 1, "quantised base weights are replicated: use zero_level 0/1 with QLoRA"
+        assert self.zero_level == 0 or self.world == 1, "quantised base weights are replicated: use zero_level 0 with QLoRA on more than one rank"
         self.codec = codec
         saved = 0
         for b in self.buckets.values():
@@ -417,6 +419,9 @@ class ParamStore:
         return saved
 
     def _dequantized(self, b: Bucket) -> torch.Tensor:
+        mgr = getattr(b.qstate, "manager", None)      # expert buckets under the offload manager (runtime/expert_offload.py)
+        if mgr is not None:
+            return mgr.fetch(b.layer, self.param_dtype)
         return self.codec.dequantize(b.qstate, self.param_dtype)
 
     # ------------------------------------------------------------------ FP8 quantise-on-gather
@@ -570,6 +575,12 @@ class ParamStore:
         return self.buckets.get(f"layer{L}")
 
     def layer_start(self, L: int, phase: str) -> None:
+        mgr = getattr(self, "expert_offload", None)
+        if mgr is not None:       # quantised experts stream one MoE layer ahead of their use
+            mgr.prefetch(L)
+            nxt_moe = mgr.neighbours(L, phase)
+            if nxt_moe is not None:
+                mgr.prefetch(nxt_moe)
         if self.zero_level < 3:
             b = self._layer_bucket(L)
             if b is not None and getattr(b, "qstate", None) is not None:
@@ -586,14 +597,16 @@ class ParamStore:
         b = self._layer_bucket(L)
         if b is None:
             return
+        eb = self.buckets.get(f"layer{L}.experts")
         if phase == "bwd":
             self._reduce_bucket(b)
             self._release(b)
-            eb = self.buckets.get(f"layer{L}.experts")
             if eb is not None:
                 self._reduce_bucket(eb)
         elif not self.keep_gathered or getattr(b, "qstate", None) is not None:
             self._release(b)
+        if eb is not None and getattr(eb, "qstate", None) is not None:
+            eb.work = None          # the dequantised experts of this layer are rebuilt when it is next reached
 
     def group_start(self, group: str, phase: str) -> None:
         pass

@@ -71,6 +71,8 @@ class TrainerConfig:
     qlora_block_size: int = 64
     qlora_double_quant: bool = True
     qlora_four_over_six: bool = True
+    qlora_experts: bool = True            # MoE: frozen expert weights are stored quantised too (they are most of the model)
+    qlora_offload_experts: bool = False   # ... and wait in pinned host memory, streamed one MoE layer ahead
     fp4_four_over_six: bool = True   # NVFP4 recipe: per block of 16 keep the better of the abs-max -> 6 and abs-max -> 4 mappings (round-to-nearest operands)
     time_breakdown: bool = False            # per-step milliseconds of forward / LM head / backward / optimizer in Trainer.last_time_breakdown
     lmhead_drop_ignored_rows: bool = False  # only rows with a target go through the LM head
@@ -225,7 +227,13 @@ class Trainer:
 
         kw = {"bnb_nf4": dict(block=c.qlora_block_size, double_quant=c.qlora_double_quant), "fp8_block": dict(block=max(64, c.qlora_block_size)),
               "nvfp4": dict(four_over_six=c.qlora_four_over_six)}[c.qlora]
-        self.qlora_bytes_saved = self.store.quantize_frozen(make_codec(c.qlora, **kw))
+        codec = make_codec(c.qlora, **kw)
+        self.qlora_bytes_saved = self.store.quantize_frozen(codec)
+        if c.qlora_experts and any(b.expert and not b.trainable for b in self.store.buckets.values()):
+            from .expert_offload import ExpertOffloadManager
+
+            self.store.expert_offload = ExpertOffloadManager(self.store, codec, offload=c.qlora_offload_experts)
+            self.qlora_bytes_saved += self.store.expert_offload.attach()
 
     def init_weights(self, seed: Optional[int] = None) -> None:
         self.store.init_weights(seed if seed is not None else self.cfg.seed, zero_projections=self.cfg.init_projections_to_zero)

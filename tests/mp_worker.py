@@ -32,6 +32,7 @@ def main():
                         collectives=a.get("collectives", "auto"), keep_gathered=a.get("keep_gathered", True), ep_size=a.get("ep", 1),
                         lora=a.get("lora"), offload_master=a.get("offload_master", False), offload_optimizer=a.get("offload_optimizer", False),
                         cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5),
+                        qlora=a.get("qlora"), qlora_experts=a.get("qlora_experts", True), qlora_offload_experts=a.get("qlora_offload_experts", False),
                         use_cuda_graphs=a.get("graphs", False), ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
     pp = a.get("pp", False)
     if pp:  # pipeline stages: every rank gets the whole global batch and cuts it into world * grad_accum micro-batches
@@ -54,6 +55,10 @@ def main():
         losses.append(out["loss"])
         norms.append(out["norm"])
     extra = {}
+    if getattr(tr.store, "expert_offload", None) is not None:
+        extra["expert_offload"] = tr.store.expert_offload.stats()
+        extra["expert_master_elems"] = sum(b.master.numel() for b in tr.store.buckets.values() if b.expert)
+        extra["exported_expert_shape"] = list(tr.store.full_tensor("blocks.0.experts_down").shape)
     if pp:
         if a.get("export_dir"):
             tr.export_model(a["export_dir"])

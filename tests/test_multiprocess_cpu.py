@@ -141,3 +141,19 @@ def test_expert_parallel_mesh_matches_single_process(nproc, ep, zero, port):
         assert abs(a - b) < 3e-4 * abs(b), (r["losses"], one["losses"])
     for a, b in zip(r["norms"], one["norms"]):
         assert abs(a - b) < 2e-3 * abs(b), (r["norms"], one["norms"])
+
+
+def test_qlora_on_an_expert_parallel_model_keeps_frozen_experts_quantised():
+    """QLoRA on a MoE model with EP=2 over CPU ranks: the frozen expert buckets are held by the expert offload manager (quantised, their
+    master copies freed, rebuilt per layer when reached), training follows the run whose experts stay in full precision, and export
+    still returns all experts."""
+    lora = dict(rank=4, alpha=8, dropout=0.0, dtype="fp32", targets=["q_proj", "v_proj", "o_proj"], rslora=False, train_router=False)
+    base = dict(device="cpu", model=MOE_TINY, global_batch=4, seq_len=32, steps=3, zero=0, ep=2, lora=lora, qlora="fp8_block")
+    full = run_worker(2, dict(base, qlora_experts=False), port=29691)
+    q = run_worker(2, dict(base, qlora_experts=True), port=29692)
+    assert "expert_offload" not in full
+    st = q["expert_offload"]
+    assert st["expert_offload/layers"] == 2 and st["expert_offload/device_bytes_saved"] > 0 and q["expert_master_elems"] == 0
+    assert q["exported_expert_shape"][0] == 4                      # all four experts come back from the two ranks
+    for a, b in zip(q["losses"], full["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (q["losses"], full["losses"])
