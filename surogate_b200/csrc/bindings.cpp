@@ -354,11 +354,18 @@ Tensor cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::o
 }
 
 Tensor quantize_fp8(const Tensor& x, const c10::optional<Tensor>& scale, const c10::optional<Tensor>& amax_out, bool e5m2,
-                    const c10::optional<Tensor>& rows_limit) {
+                    const c10::optional<Tensor>& rows_limit, const c10::optional<Tensor>& out) {
     check_bf16(x, "x");
     TORCH_CHECK(x.numel() % 8 == 0, "quantize_fp8: numel must be a multiple of 8");
     const c10::cuda::CUDAGuard guard(x.device());
-    Tensor q = torch::empty(x.sizes(), x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+    Tensor q;
+    if (out.has_value() && out->defined()) {   // caller-owned destination (a slice of a peer-visible buffer): one byte per element
+        TORCH_CHECK(out->is_cuda() && out->is_contiguous() && out->element_size() == 1 && out->numel() == x.numel(), "quantize_fp8: out must hold numel bytes");
+        TORCH_CHECK(reinterpret_cast<uintptr_t>(out->data_ptr()) % 8 == 0, "quantize_fp8: out must be 8-byte aligned");
+        q = *out;
+    } else {
+        q = torch::empty(x.sizes(), x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+    }
     g_launches += 1;
     sg::quantize_fp8(x.data_ptr(), q.data_ptr(), opt_f32(scale), opt_f32_mut(amax_out), x.numel(), e5m2, num_sms(), cur_stream(), opt_i32(rows_limit),
                      static_cast<int>(x.size(-1)));
@@ -444,7 +451,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("write_grad"), py::arg("row_weight") = py::none(), py::arg("kd_idx") = py::none(), py::arg("kd_logp") = py::none(),
           py::arg("kd_weight") = 0.0, py::arg("kd_loss_out") = py::none());
     m.def("quantize_fp8", &quantize_fp8, pybind11::arg("x"), pybind11::arg("scale"), pybind11::arg("amax_out"), pybind11::arg("e5m2"),
-          pybind11::arg("rows_limit") = c10::optional<Tensor>());
+          pybind11::arg("rows_limit") = c10::optional<Tensor>(), pybind11::arg("out") = c10::optional<Tensor>());
     m.def("amax", &amax, pybind11::arg("x"), pybind11::arg("amax_out"), pybind11::arg("rows_limit") = c10::optional<Tensor>());
     m.def("sumsq", &sumsq);
     m.def("adamw_step", &adamw_step);

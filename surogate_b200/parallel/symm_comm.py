@@ -174,6 +174,19 @@ class SymmComm:
                 out_fp8.record_stream(self.stream)
         return self._done(async_op)
 
+    def all_gather_bytes(self, shard_u8: torch.Tensor, full_u8: torch.Tensor, arena: "Arena", segment, async_op: bool = False):
+        """Pull bytes ``[lo, hi)`` of the gathered bucket from the peers' byte shards (already-quantised FP8 weights: one byte per
+        weight crosses NVLink instead of two).  The gather kernel moves 16-byte vectors and never looks inside them, so the byte
+        buffers are passed as bf16 pairs with every count halved; ``lo`` / ``hi`` / the shard size must be multiples of 16."""
+        off = arena.offset_of(shard_u8)
+        lo, hi = segment
+        assert off is not None and shard_u8.dtype == torch.uint8 and full_u8.dtype == torch.uint8
+        assert lo % 16 == 0 and hi % 16 == 0 and shard_u8.numel() % 16 == 0 and off % 16 == 0, "byte gather: 16-byte granularity"
+        with self._side():
+            self.ext.all_gather_fused(arena.peer_bases, off, shard_u8.numel() // 2, lo // 2, hi // 2, full_u8.view(torch.bfloat16), None, None, self.max_blocks)
+            full_u8.record_stream(self.stream)
+        return self._done(async_op)
+
     def all_gather_from_host(self, host_shard: torch.Tensor, stage: torch.Tensor, full: torch.Tensor, async_op: bool = False):
         """ZeRO-3 gather of a shard that lives in pinned host memory: the H2D copy lands in a peer-visible arena slot, a
         device-side barrier says that every rank's copy has landed, then the gather kernel pulls the peers' slots.  All on

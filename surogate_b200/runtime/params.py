@@ -24,6 +24,8 @@ Parity: csrc/src/runtime/dsl/dsl_param_store, dsl_grad_store.cpp:457-678
 """
 from __future__ import annotations
 
+import os
+
 import math
 import zlib
 from collections import OrderedDict
@@ -448,6 +450,22 @@ class ParamStore:
         self.w_scale = torch.ones(n, dtype=torch.float32, device=self.device)
         self.w_scale_inv = torch.ones(n, dtype=torch.float32, device=self.device)
         self.fp8_gather = True
+        # Quantise-then-gather: every rank keeps an E4M3 copy of its own master shard in a second peer-visible arena, refreshed
+        # once per optimizer step, and the gather pulls those bytes: one byte per weight crosses NVLink instead of two, and the
+        # conversion work is done once by the owner instead of by every rank on arrival.
+        self.fp8_arena = None
+        alloc = getattr(self.comm, "_alloc_symmetric", None)
+        if alloc is not None and self.sharded and self.master_dtype == torch.bfloat16 and os.environ.get("SUROGATE_FP8_SHARDS", "1") != "0":
+            qb = [b for b in self.buckets.values() if b.layer is not None and not b.expert and any(sl.name in self.q_index for sl in b.slots)]
+            total = sum((b.shard_numel + 255) // 256 * 256 for b in qb) + 4096
+            try:
+                self.fp8_arena = alloc(total)
+                for b in qb:
+                    b.master_fp8 = self.fp8_arena.take(b.shard_numel, torch.uint8)
+            except Exception:  # noqa: BLE001 -- no room for a second arena: quantise on arrival as before
+                self.fp8_arena = None
+                for b in qb:
+                    b.master_fp8 = None
         return True
 
     def refresh_weight_scales(self) -> None:
@@ -468,6 +486,22 @@ class ParamStore:
         self.comm.all_reduce(self.w_amax, "max")
         torch.where(self.w_amax > 0, 448.0 / self.w_amax, torch.ones_like(self.w_amax), out=self.w_scale)
         torch.reciprocal(self.w_scale, out=self.w_scale_inv)
+        if getattr(self, "fp8_arena", None) is not None:
+            for b in self.buckets.values():
+                dst = getattr(b, "master_fp8", None)
+                if dst is None:
+                    continue
+                lo, hi = self.shard_range(b)
+                for sl in b.slots:
+                    i = self.q_index.get(sl.name)
+                    if i is None:
+                        continue
+                    a, z = max(sl.offset, lo), min((sl.offset + sl.numel + 15) // 16 * 16, hi)
+                    if a < z:
+                        e.quantize_fp8(b.master[a - lo:z - lo], self.w_scale[i:i + 1], None, False, None, dst[a - lo:z - lo])
+            fence = getattr(self.comm, "fence", None)
+            if fence is not None:
+                fence()      # the peers pull these bytes: every rank's copy must be complete before the first gather of the next step
 
     def get_fp8(self, name: str):
         """(E4M3 weight view, de-scale) of a parameter gathered in FP8, or None."""
@@ -490,7 +524,9 @@ class ParamStore:
         for sl in b.slots:
             end = (sl.offset + sl.numel + 7) // 8 * 8
             i = self.q_index.get(sl.name)
-            if i is not None:
+            if i is not None and getattr(b, "master_fp8", None) is not None:
+                w = self.comm.all_gather_bytes(b.master_fp8, b.work_fp8, self.fp8_arena, (sl.offset, (sl.offset + sl.numel + 15) // 16 * 16), async_op=True)
+            elif i is not None:
                 w = self.comm.all_gather(b.master, None, async_op=True, out_fp8=b.work_fp8, scale=self.w_scale[i:i + 1], segment=(sl.offset, end))
             else:
                 w = self.comm.all_gather(b.master, b.work, async_op=True, segment=(sl.offset, end))

@@ -96,7 +96,7 @@ def main():
     if info.rank == 0:
         print("RESULT " + json.dumps({"losses": losses, "norms": norms, "world": info.world, "comm": type(tr.comm).__name__,
                                       "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),
-                                      "fp8_gather": bool(tr.store.fp8_gather), "graph_replays": getattr(tr, "graph_replays", 0), "h2d_weight_bytes": int(tr.store.h2d_bytes),
+                                      "fp8_gather": bool(tr.store.fp8_gather), "fp8_shards": bool(getattr(tr.store, "fp8_arena", None) is not None), "graph_replays": getattr(tr, "graph_replays", 0), "h2d_weight_bytes": int(tr.store.h2d_bytes),
                                       "stage_slots": len(tr.store.stage_slots),
                                       "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0,
                                       "ep_moves": tr.ep.moves_done if tr.ep is not None else 0,

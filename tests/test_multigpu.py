@@ -32,9 +32,21 @@ def test_two_gpus_fp8_zero3_quantize_on_gather(single):
     a = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29731)
     b = run_worker(2, dict(ARGS, zero=3, collectives="nccl", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29732)
     assert a["fp8_gather"] and not b["fp8_gather"]
+    assert a["fp8_shards"], "each rank should publish an E4M3 copy of its own shard for the peers to pull"
     assert all(l == l for l in a["losses"])
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) < 5e-3 * abs(y), (a["losses"], b["losses"])
+    # quantise on arrival (peers pull bf16) gives the same bytes: same scale, same rounding
+    import os
+
+    os.environ["SUROGATE_FP8_SHARDS"] = "0"
+    try:
+        c = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29733)
+    finally:
+        del os.environ["SUROGATE_FP8_SHARDS"]
+    assert c["fp8_gather"] and not c["fp8_shards"]
+    for x, y in zip(a["losses"], c["losses"]):
+        assert abs(x - y) < 1e-4 * abs(y), (a["losses"], c["losses"])
 
 
 MOE = dict(architecture="Qwen3MoeForCausalLM", vocab_size=1024, d_model=256, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=128,
