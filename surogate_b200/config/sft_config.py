@@ -328,6 +328,7 @@ class SFTConfig:
             offload_master=self.offload_master and not self.cpu_training, cpu_training=self.cpu_training, long_context=self.long_context, sequence_chunks=self.sequence_chunks, use_cuda_graphs=self.use_cuda_graphs, lmhead_drop_ignored_rows=self.lmhead_drop_ignored_rows, time_breakdown=self.debug_time_breakdown, resident_layers=self.resident_layers,
             offload_saved_tensors=self.offload_saved_tensors or self.offload_residual,
             qlora="bnb_nf4" if self.qlora_bnb else "fp8_block" if self.qlora_fp8 else "nvfp4" if self.qlora_fp4 else None,
+            qlora_offload_experts=self.qlora_offload_experts,
             qlora_block_size=self.qlora_bnb_block_size if self.qlora_bnb else self.qlora_block_size, qlora_double_quant=self.qlora_bnb_double_quant,
             qlora_four_over_six=self.qlora_four_over_six, fp4_four_over_six=self.fp4_four_over_six,
             normuon_momentum=self.normuon_momentum, normuon_beta2=self.normuon_beta2, normuon_cautious_wd=self.normuon_cautious_wd,
