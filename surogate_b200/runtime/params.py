@@ -37,6 +37,7 @@ import torch
 from ..dsl.compiler import CompiledModel, ParamEntry
 
 ALIGN_ELEMS = 128
+FP8_SHARDS_DEFAULT = "0"   # quantise-then-gather of ZeRO-3 FP8 weights: opt-in (SUROGATE_FP8_SHARDS=1) until confirmed on 2+ GPUs
 
 
 @dataclass
@@ -455,7 +456,7 @@ class ParamStore:
         # conversion work is done once by the owner instead of by every rank on arrival.
         self.fp8_arena = None
         alloc = getattr(self.comm, "_alloc_symmetric", None)
-        if alloc is not None and self.sharded and self.master_dtype == torch.bfloat16 and os.environ.get("SUROGATE_FP8_SHARDS", "1") != "0":
+        if alloc is not None and self.sharded and self.master_dtype == torch.bfloat16 and os.environ.get("SUROGATE_FP8_SHARDS", FP8_SHARDS_DEFAULT) != "0":
             qb = [b for b in self.buckets.values() if b.layer is not None and not b.expert and any(sl.name in self.q_index for sl in b.slots)]
             total = sum((b.shard_numel + 255) // 256 * 256 for b in qb) + 4096
             try:

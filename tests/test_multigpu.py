@@ -29,7 +29,13 @@ def test_two_gpus_match_one_gpu(single, zero, collectives):
 def test_two_gpus_fp8_zero3_quantize_on_gather(single):
     """ZeRO-3 + FP8: the gather kernel writes E4M3 directly (same per-tensor scale as the separate quantiser would use),
     so the run matches the NCCL path that gathers bf16 and quantises afterwards."""
-    a = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29731)
+    import os
+
+    os.environ["SUROGATE_FP8_SHARDS"] = "1"
+    try:
+        a = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29731)
+    finally:
+        del os.environ["SUROGATE_FP8_SHARDS"]
     b = run_worker(2, dict(ARGS, zero=3, collectives="nccl", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29732)
     assert a["fp8_gather"] and not b["fp8_gather"]
     assert a["fp8_shards"], "each rank should publish an E4M3 copy of its own shard for the peers to pull"
@@ -37,8 +43,6 @@ def test_two_gpus_fp8_zero3_quantize_on_gather(single):
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) < 5e-3 * abs(y), (a["losses"], b["losses"])
     # quantise on arrival (peers pull bf16) gives the same bytes: same scale, same rounding
-    import os
-
     os.environ["SUROGATE_FP8_SHARDS"] = "0"
     try:
         c = run_worker(2, dict(ARGS, zero=3, collectives="symm", recipe="fp8_hybrid", optimizer="adamw_8bit"), port=29733)
