@@ -7,6 +7,7 @@
 #include <string>
 
 #include "attention_sm100.h"
+#include "conv1d_kernels.h"
 #include "normuon_kernels.h"
 #include "qlora_kernels.h"
 #include "comm_kernels.h"
@@ -493,6 +494,42 @@ void normuon_apply(Tensor& w, const Tensor& x, const Tensor& v, const Tensor& su
                       cur_stream());
 }
 
+// ---------------------------------------------------------------------------------------- depth-wise causal conv1d (channels-last)
+static void check_conv(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& seq_id) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3 && (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat), "x: contiguous [B, T, C] bf16 / fp32");
+    TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == at::kFloat && w.dim() == 2 && w.size(0) == x.size(2) && w.size(1) >= 1 && w.size(1) <= 4,
+                "w: contiguous fp32 [C, K] with K <= 4");
+    TORCH_CHECK(x.size(2) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "C must be a multiple of 8 and x 16-byte aligned");
+    if (seq_id.has_value() && seq_id->defined())
+        TORCH_CHECK(seq_id->is_cuda() && seq_id->is_contiguous() && seq_id->scalar_type() == at::kInt && seq_id->numel() == x.size(0) * x.size(1), "seq_id: int32 [B, T]");
+}
+Tensor causal_conv1d_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& seq_id, bool silu) {
+    check_conv(x, w, seq_id);
+    if (bias.has_value() && bias->defined()) TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == x.size(2), "bias: fp32 [C]");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = torch::empty_like(x);
+    sg_count_launch(1);
+    sg::causal_conv1d_fwd(x.data_ptr(), w.data_ptr<float>(), (bias.has_value() && bias->defined()) ? bias->data_ptr<float>() : nullptr,
+                          (seq_id.has_value() && seq_id->defined()) ? seq_id->data_ptr<int>() : nullptr, y.data_ptr(), x.scalar_type() == at::kFloat,
+                          static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), static_cast<int>(w.size(1)), silu, cur_stream());
+    return y;
+}
+// dz: gradient of the convolution output before any activation -> (dx, dw fp32 [C, K], dbias fp32 [C])
+std::vector<Tensor> causal_conv1d_bwd(const Tensor& dz, const Tensor& x, const Tensor& w, const c10::optional<Tensor>& seq_id) {
+    check_conv(x, w, seq_id);
+    TORCH_CHECK(dz.is_cuda() && dz.is_contiguous() && dz.sizes() == x.sizes() && dz.scalar_type() == x.scalar_type() && (reinterpret_cast<uintptr_t>(dz.data_ptr()) & 15) == 0,
+                "dz: same shape, type and alignment as x");
+    const c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx = torch::empty_like(x);
+    Tensor dw = torch::zeros_like(w);
+    Tensor db = torch::zeros({x.size(2)}, w.options());
+    sg_count_launch(1);
+    sg::causal_conv1d_bwd(dz.data_ptr(), x.data_ptr(), w.data_ptr<float>(), (seq_id.has_value() && seq_id->defined()) ? seq_id->data_ptr<int>() : nullptr,
+                          dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(), x.scalar_type() == at::kFloat, static_cast<int>(x.size(0)),
+                          static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), static_cast<int>(w.size(1)), cur_stream());
+    return {dx, dw, db};
+}
+
 // ---------------------------------------------------------------------------------------- QLoRA storage -> bf16
 // kind: "bnb_nf4" (a = absmax fp32, or a = int8 codes with b = fp32 scales per 256 blocks and c = fp32 offset), "fp8_block" (a = fp32
 // scales), "nvfp4" (a = UE4M3 scale bytes, b = fp32 tensor de-scale), "mxfp4" (a = E8M0 scale bytes).
@@ -564,6 +601,9 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("normuon_normalise", &normuon_normalise);
     m.def("normuon_row_stats", &normuon_row_stats);
     m.def("normuon_apply", &normuon_apply);
+    m.def("causal_conv1d_fwd", &causal_conv1d_fwd, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("bias") = c10::optional<Tensor>(),
+          pybind11::arg("seq_id") = c10::optional<Tensor>(), pybind11::arg("silu") = false);
+    m.def("causal_conv1d_bwd", &causal_conv1d_bwd, pybind11::arg("dz"), pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("seq_id") = c10::optional<Tensor>());
     m.def("ep_plan", &ep_plan);
     m.def("ep_dispatch", &ep_dispatch);
     m.def("ep_row_positions", &ep_row_positions);

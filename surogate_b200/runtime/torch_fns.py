@@ -278,12 +278,12 @@ def moe_biased_clamp_swiglu(x, router_w, router_b, gate_up, gate_up_b, down, dow
 @register("short_conv")
 def short_conv(x, in_w, conv_w, out_w, in_b=None, conv_b=None, out_b=None, *, kernel: int = 3):
     """Gated depth-wise causal convolution: (B, C, x') = in_proj(x) split in three; y = out_proj(C * conv1d(B * x'))."""
+    from ..ops.conv1d import causal_conv1d
+
     Bx, T, D = x.shape
-    bcx = F.linear(x, in_w, in_b).transpose(1, 2)  # [B, 3D, T]
-    b, c, xx = bcx.chunk(3, dim=1)
-    u = b * xx
-    conv = F.conv1d(F.pad(u, (kernel - 1, 0)), conv_w.reshape(D, 1, kernel).to(u.dtype), conv_b, groups=D)
-    return F.linear((c * conv).transpose(1, 2).contiguous(), out_w, out_b)
+    b, c, xx = F.linear(x, in_w, in_b).chunk(3, dim=-1)          # channels-last throughout: no transposes around the convolution
+    conv = causal_conv1d((b * xx).contiguous(), conv_w.reshape(D, kernel), conv_b)
+    return F.linear(c * conv, out_w, out_b)
 
 
 # ---------------------------------------------------------------------------------------------- Mamba-2 mixer (Nemotron-H)
@@ -338,8 +338,9 @@ def mamba2_mixer(x, in_w, conv_w, conv_b, dt_bias, A_log, D, norm_w, out_w, *, n
     inner = H * P
     proj = F.linear(x, in_w, in_b).float()
     z, xBC, dt = torch.split(proj, [inner, inner + 2 * G * N, H], dim=-1)
-    xBC = F.conv1d(F.pad(xBC.transpose(1, 2), (conv_kernel - 1, 0)), conv_w.float().reshape(-1, 1, conv_kernel), conv_b.float(), groups=xBC.shape[-1])
-    xBC = F.silu(xBC.transpose(1, 2))
+    from ..ops.conv1d import causal_conv1d
+
+    xBC = causal_conv1d(xBC.contiguous(), conv_w.float().reshape(-1, conv_kernel), conv_b.float(), activation="silu")
     xs, Bm, Cm = torch.split(xBC, [inner, G * N, G * N], dim=-1)
     dt = F.softplus(dt + dt_bias.float())
     y = ssd_scan(xs.reshape(Bsz, T, H, P), dt, -torch.exp(A_log.float()), Bm.reshape(Bsz, T, G, N), Cm.reshape(Bsz, T, G, N), D.float(), chunk=chunk)
@@ -529,8 +530,9 @@ def qwen35_gated_delta_net(x, qkv_w, z_w, b_w, a_w, conv_w, dt_bias, A_log, norm
     B, T, _ = x.shape
     Hk, Hv, Dk, Dv = num_k_heads, num_v_heads, head_k_dim, head_v_dim
     key_dim, value_dim = Hk * Dk, Hv * Dv
-    mixed = F.linear(x, qkv_w).float().transpose(1, 2)
-    mixed = F.silu(F.conv1d(F.pad(mixed, (conv_kernel - 1, 0)), conv_w.float().reshape(-1, 1, conv_kernel), None, groups=mixed.shape[1])).transpose(1, 2)
+    from ..ops.conv1d import causal_conv1d
+
+    mixed = causal_conv1d(F.linear(x, qkv_w).float().contiguous(), conv_w.float().reshape(-1, conv_kernel), None, activation="silu")
     q, k, v = torch.split(mixed, [key_dim, key_dim, value_dim], dim=-1)
     q, k, v = q.reshape(B, T, Hk, Dk), k.reshape(B, T, Hk, Dk), v.reshape(B, T, Hv, Dv)
     beta = torch.sigmoid(F.linear(x, b_w).float())

@@ -539,3 +539,33 @@ def test_barrier_wait_runs_out_and_reports_instead_of_hanging():
     x = torch.ones(8, device="cuda")
     assert float((x * 2).sum()) == 16.0  # the context survived
     check_device_errors()
+
+
+@pytest.mark.parametrize("dtype,K,silu,packed", [(torch.bfloat16, 4, True, False), (torch.float32, 3, False, False), (torch.float32, 4, True, True),
+                                                  (torch.bfloat16, 2, False, True)])
+def test_causal_conv1d_forward_and_backward(ext, dtype, K, silu, packed):
+    """Depth-wise causal convolution kernels against the PyTorch statement in fp32: tiles that need a halo (T > 64), a channel count that
+    is not a multiple of the block, packed documents, the activation folded into backward."""
+    from surogate_b200.ops.conv1d import causal_conv1d, causal_conv1d_reference
+
+    torch.manual_seed(1)
+    B, T, C = 3, 150, 264
+    x = torch.randn(B, T, C, device=DEV).to(dtype).requires_grad_(True)
+    w = (torch.randn(C, K, device=DEV) * 0.5).requires_grad_(True)
+    b = torch.randn(C, device=DEV).requires_grad_(True)
+    ids = None
+    if packed:
+        ids = torch.zeros(B, T, dtype=torch.int32, device=DEV)
+        ids[:, 63:] = 1          # boundaries next to and inside tile edges
+        ids[:, 64:] = 2
+        ids[:, 130:] = 3
+    y = causal_conv1d(x, w, b, "silu" if silu else None, ids)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    got = (y.detach(), x.grad.clone(), w.grad.clone(), b.grad.clone())
+    xr, wr, br = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = causal_conv1d_reference(xr, wr, br, "silu" if silu else None, ids)
+    yr.backward(dy.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    for name, a, r in zip(("y", "dx", "dw", "db"), got, (yr.detach(), xr.grad, wr.grad, br.grad)):
+        assert _rel_err(a, r) < tol, (name, _rel_err(a, r))
