@@ -33,11 +33,19 @@ def geglu(x, *, approximate: str = "tanh", gate_first: bool = False):
     """x = [up | gate] (or [gate | up]); y = gelu(gate) * up."""
     a, b = x.chunk(2, dim=-1)
     up, gate = (b, a) if gate_first else (a, b)
+    if x.is_cuda and approximate == "tanh":      # one run-time compiled kernel each way instead of five element-wise passes
+        from ..ops.jit import GEGLU_TANH
+
+        return GEGLU_TANH(gate.contiguous(), up.contiguous())
     return F.gelu(gate.float(), approximate=approximate).to(x.dtype) * up
 
 
 @register("relu2")
 def relu2(x):
+    if x.is_cuda:
+        from ..ops.jit import RELU2
+
+        return RELU2(x)
     return F.relu(x).square()
 
 
@@ -195,6 +203,10 @@ def scale_by(x, s):
 
 @register("softcap")
 def softcap(x, *, cap: float):
+    if x.is_cuda:
+        from ..ops.jit import SOFTCAP
+
+        return SOFTCAP(x, cap=float(cap))
     return torch.tanh(x.float() / cap).mul(cap).to(x.dtype)
 
 

@@ -569,3 +569,35 @@ def test_causal_conv1d_forward_and_backward(ext, dtype, K, silu, packed):
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     for name, a, r in zip(("y", "dx", "dw", "db"), got, (yr.detach(), xr.grad, wr.grad, br.grad)):
         assert _rel_err(a, r) < tol, (name, _rel_err(a, r))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_runtime_compiled_elementwise_ops(dtype):
+    """Kernels compiled at run time (nvcc -> cubin -> driver API) against their PyTorch statements, forward and backward, and through
+    the model-family functions that use them."""
+    from surogate_b200.ops import jit
+    from surogate_b200.runtime import torch_fns
+
+    torch.manual_seed(0)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
+    x = torch.randn(3, 1000, 264, device=DEV).to(dtype)
+    for op, ref, kw in ((jit.RELU2, jit._relu2_ref, {}), (jit.SOFTCAP, jit._softcap_ref, {"cap": 2.5})):
+        a = x.clone().requires_grad_(True)
+        b = x.clone().float().requires_grad_(True)
+        y, yr = op(a, **kw), ref(b, **kw)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        yr.backward(dy.float())
+        assert _rel_err(y.detach(), yr.detach()) < tol and _rel_err(a.grad, b.grad) < tol, op.name
+    g, u = torch.randn(2, 500, 512, device=DEV).to(dtype), torch.randn(2, 500, 512, device=DEV).to(dtype)
+    ga, ua = g.clone().requires_grad_(True), u.clone().requires_grad_(True)
+    gb, ub = g.clone().float().requires_grad_(True), u.clone().float().requires_grad_(True)
+    y, yr = jit.GEGLU_TANH(ga, ua), jit._geglu_ref(gb, ub)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    assert _rel_err(y.detach(), yr.detach()) < tol and _rel_err(ga.grad, gb.grad) < tol and _rel_err(ua.grad, ub.grad) < tol
+    packed = torch.cat([u, g], -1)            # [up | gate]
+    assert _rel_err(torch_fns.geglu(packed), yr.detach()) < tol
+    odd = torch.randn(7, 3, device=DEV).to(dtype)      # not a multiple of the vector width: the PyTorch statement answers
+    assert torch.equal(torch_fns.relu2(odd), torch.relu(odd) ** 2)
