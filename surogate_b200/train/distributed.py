@@ -122,13 +122,20 @@ def launch_over_ssh(hosts: List[str], config_path: str, command: str, gpus_per_n
     return [p.wait() for p in procs]
 
 
-def launch_with_ray(config_path: str, command: str, num_nodes: int, gpus_per_node: int, master_port: int = 29500, ray_address: Optional[str] = None):
-    """One Ray task per node (placement: one bundle of ``gpus_per_node`` GPUs each); each task runs its node's launcher command."""
+def launch_with_ray(config_path: str, command: str, num_nodes: int, gpus_per_node: int, master_port: int = 29500, ray_address: Optional[str] = None,
+                    extra_args: Optional[List[str]] = None):
+    """One Ray task per node: a placement group with one bundle of ``gpus_per_node`` GPUs per node (strict spread, so no two bundles
+    share a node), node 0's address becomes the rendezvous address, every task runs its node's launcher command.  Returns the exit
+    codes in node order; the placement group is removed afterwards."""
     try:
         import ray
+        from ray.util.placement_group import placement_group, remove_placement_group
+        from ray.util.scheduling_strategies import PlacementGroupSchedulingStrategy
     except ImportError as e:
         raise RuntimeError("Ray is not installed: use torchrun on every node (plan_launch) or launch_over_ssh") from e
     ray.init(address=ray_address or "auto", ignore_reinit_error=True)
+    pg = placement_group([{"GPU": gpus_per_node, "CPU": 1} for _ in range(num_nodes)], strategy="STRICT_SPREAD" if num_nodes > 1 else "PACK")
+    ray.get(pg.ready())
 
     @ray.remote(num_gpus=gpus_per_node)
     def node_task(cmd, env):
@@ -140,6 +147,12 @@ def launch_with_ray(config_path: str, command: str, num_nodes: int, gpus_per_nod
     def node_ip():
         return ray.util.get_node_ip_address()
 
-    head_ip = ray.get(node_ip.remote())
-    plan = plan_launch(config_path, command, num_nodes, gpus_per_node, head_ip, master_port)
-    return ray.get([node_task.remote(p.command, p.env) for p in plan])
+    def on(bundle):
+        return PlacementGroupSchedulingStrategy(placement_group=pg, placement_group_bundle_index=bundle)
+
+    try:
+        head_ip = ray.get(node_ip.options(scheduling_strategy=on(0)).remote())
+        plan = plan_launch(config_path, command, num_nodes, gpus_per_node, head_ip, master_port, extra_args)
+        return ray.get([node_task.options(scheduling_strategy=on(p.node_rank)).remote(p.command, p.env) for p in plan])
+    finally:
+        remove_placement_group(pg)

@@ -92,3 +92,62 @@ def test_sft_workflow_with_adapter_resume(tmp_path):
     r2 = run_training(SFTConfig.from_dict(dict(base, output_dir=str(tmp_path / "b"), adapter_path=str(tmp_path / "a" / "adapter"), adapter_init_mode="resume")))
     assert r2["steps"] == 3 and np.isfinite(r2["final"]["loss"])
     assert os.path.getsize(tmp_path / "metrics.jsonl") > 0
+
+
+def test_ray_launcher_places_one_task_per_node_on_a_stand_in_ray(monkeypatch):
+    """``launch_with_ray`` against a minimal stand-in of the Ray API (Ray is not installed here): one bundle per node, strict spread,
+    node 0's address as rendezvous address, one launcher command per bundle, placement group removed at the end."""
+    import subprocess
+    import sys
+    import types
+
+    log = {"bundles": None, "strategy": None, "placed": [], "removed": False}
+
+    class _Remote:
+        def __init__(self, fn, bundle=None):
+            self.fn, self.bundle = fn, bundle
+
+        def options(self, scheduling_strategy=None, **_):
+            return _Remote(self.fn, scheduling_strategy.placement_group_bundle_index)
+
+        def remote(self, *a):
+            log["placed"].append((self.fn.__name__, self.bundle))
+            return self.fn(*a)
+
+    ray = types.ModuleType("ray")
+    ray.init = lambda **kw: None
+    ray.get = lambda x: x
+    ray.remote = lambda **kw: (lambda fn: _Remote(fn))
+    util = types.ModuleType("ray.util")
+    util.get_node_ip_address = lambda: "10.1.2.3"
+    pgm = types.ModuleType("ray.util.placement_group")
+
+    class _PG:
+        def ready(self):
+            return True
+
+    def placement_group(bundles, strategy):
+        log["bundles"], log["strategy"] = bundles, strategy
+        return _PG()
+
+    pgm.placement_group = placement_group
+    pgm.remove_placement_group = lambda pg: log.__setitem__("removed", True)
+    ss = types.ModuleType("ray.util.scheduling_strategies")
+
+    class PlacementGroupSchedulingStrategy:
+        def __init__(self, placement_group, placement_group_bundle_index):
+            self.placement_group, self.placement_group_bundle_index = placement_group, placement_group_bundle_index
+
+    ss.PlacementGroupSchedulingStrategy = PlacementGroupSchedulingStrategy
+    ray.util = util
+    for name, mod in (("ray", ray), ("ray.util", util), ("ray.util.placement_group", pgm), ("ray.util.scheduling_strategies", ss)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    calls = []
+    monkeypatch.setattr(subprocess, "call", lambda cmd, env=None: calls.append((cmd, env)) or 0)
+    from surogate_b200.train import distributed as d
+
+    rcs = d.launch_with_ray("cfg.yaml", "sft", num_nodes=3, gpus_per_node=8, master_port=29555)
+    assert rcs == [0, 0, 0] and log["removed"] and log["strategy"] == "STRICT_SPREAD" and log["bundles"] == [{"GPU": 8, "CPU": 1}] * 3
+    assert log["placed"] == [("node_ip", 0), ("node_task", 0), ("node_task", 1), ("node_task", 2)]
+    for node, (cmd, env) in enumerate(calls):
+        assert f"--node-rank={node}" in cmd and "--nnodes=3" in cmd and cmd[cmd.index("--master-addr") + 1] == "10.1.2.3" and env["SUROGATE_NODE_RANK"] == str(node)
