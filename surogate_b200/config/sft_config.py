@@ -130,6 +130,7 @@ class SFTConfig:
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
     normuon_cautious_wd: bool = True
+    normuon_momentum_8bit: bool = False
     auto_lr_reduction: bool = False
     early_stop: bool = False
     epoch_adjustment: bool = False
@@ -331,7 +332,7 @@ class SFTConfig:
             qlora_offload_experts=self.qlora_offload_experts,
             qlora_block_size=self.qlora_bnb_block_size if self.qlora_bnb else self.qlora_block_size, qlora_double_quant=self.qlora_bnb_double_quant,
             qlora_four_over_six=self.qlora_four_over_six, fp4_four_over_six=self.fp4_four_over_six,
-            normuon_momentum=self.normuon_momentum, normuon_beta2=self.normuon_beta2, normuon_cautious_wd=self.normuon_cautious_wd,
+            normuon_momentum=self.normuon_momentum, normuon_beta2=self.normuon_beta2, normuon_cautious_wd=self.normuon_cautious_wd, normuon_momentum_8bit=self.normuon_momentum_8bit,
             init_projections_to_zero=self.init_projections_to_zero, seed=self.train_seed, collectives=self.collectives)
 
     def to_json(self) -> str:

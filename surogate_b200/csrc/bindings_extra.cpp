@@ -466,6 +466,21 @@ std::vector<Tensor> normuon_momentum(const Tensor& g, Tensor& m, const Tensor& h
                          static_cast<float>(mu), g.numel(), sms(), cur_stream());
     return {u, sumsq};
 }
+// 8-bit momentum: m8 int8 codes, ms fp16 scales per 128 values (both updated); numel % 128 == 0
+std::vector<Tensor> normuon_momentum8(const Tensor& g, Tensor& m8, Tensor& ms, const Tensor& hp, double mu) {
+    TORCH_CHECK(g.is_cuda() && g.is_contiguous() && m8.is_contiguous() && m8.scalar_type() == at::kChar && m8.numel() == g.numel() && g.numel() % 128 == 0,
+                "normuon_momentum8: int8 codes of the gradient's size, a multiple of 128");
+    TORCH_CHECK(ms.is_contiguous() && ms.scalar_type() == at::kHalf && ms.numel() == g.numel() / 128, "normuon_momentum8: one fp16 scale per 128 values");
+    TORCH_CHECK(g.scalar_type() == at::kFloat || g.scalar_type() == at::kBFloat16, "gradient: fp32 or bf16");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(g.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(m8.data_ptr()) & 3) == 0, "normuon_momentum8: alignment");
+    const c10::cuda::CUDAGuard guard(g.device());
+    Tensor u = torch::empty(g.sizes(), g.options().dtype(at::kBFloat16));
+    Tensor sumsq = torch::zeros({1}, g.options().dtype(at::kFloat));
+    sg_count_launch(1);
+    sg::normuon_momentum8(g.data_ptr(), g.scalar_type() == at::kFloat, m8.data_ptr(), ms.data_ptr(), u.data_ptr(), sumsq.data_ptr<float>(), hp.data_ptr<float>(),
+                          static_cast<float>(mu), g.numel(), sms(), cur_stream());
+    return {u, sumsq};
+}
 void normuon_normalise(Tensor& x, const Tensor& sumsq) {
     TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x: contiguous bf16");
     const c10::cuda::CUDAGuard guard(x.device());
@@ -598,6 +613,7 @@ void sg_register_extra(pybind11::module_& m) {
     m.def("dequant_blockwise", &dequant_blockwise, pybind11::arg("kind"), pybind11::arg("codes"), pybind11::arg("a"), pybind11::arg("b") = c10::optional<Tensor>(),
           pybind11::arg("c") = c10::optional<Tensor>(), pybind11::arg("n"), pybind11::arg("block") = 0);
     m.def("normuon_momentum", &normuon_momentum);
+    m.def("normuon_momentum8", &normuon_momentum8);
     m.def("normuon_normalise", &normuon_normalise);
     m.def("normuon_row_stats", &normuon_row_stats);
     m.def("normuon_apply", &normuon_apply);

@@ -12,6 +12,7 @@
 // Hyper-parameters come from the device vector hp = [lr, beta1, beta2, eps, wd, bc1, bc2, clip]: a zero clip scale skips the update.
 // Replaces csrc/src/runtime/optimizers/normuon.cu of the reference.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -52,6 +53,65 @@ __global__ void __launch_bounds__(256) normuon_momentum_kernel(const G* __restri
         u[i] = ub;
         const float uf = __bfloat162float(ub);
         acc += uf * uf;
+    }
+    acc = nm_block_sum(acc, sh);
+    if (threadIdx.x == 0 && acc != 0.f) atomicAdd(sumsq, acc);
+}
+
+// 8-bit momentum: int8 codes with one fp16 scale per 128 values (linear, symmetric: value = code / 127 * scale).  A warp owns one
+// group (4 values per lane), so the group's new absolute maximum is one warp reduction.  n % 128 == 0.
+template <typename G>
+__global__ void __launch_bounds__(256) normuon_momentum8_kernel(const G* __restrict__ g, int8_t* __restrict__ m8, __half* __restrict__ ms, bf16* __restrict__ u,
+                                                                float* __restrict__ sumsq, const float* __restrict__ hp, float mu, size_t n) {
+    __shared__ float sh[32];
+    const float gs = hp[7];
+    if (gs == 0.f) return;
+    float acc = 0.f;
+    const int lane = threadIdx.x & 31;
+    const size_t groups = n / 128;
+    const size_t warps = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
+    for (size_t grp = blockIdx.x * static_cast<size_t>(blockDim.x >> 5) + (threadIdx.x >> 5); grp < groups; grp += warps) {
+        const size_t i = grp * 128 + lane * 4;
+        const float scale = __half2float(ms[grp]) * (1.f / 127.f);
+        const char4 c = *reinterpret_cast<const char4*>(m8 + i);
+        float gv[4];
+        if constexpr (sizeof(G) == 2) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(g + i);
+            const __nv_bfloat162* t = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a = __bfloat1622float2(t[0]), b = __bfloat1622float2(t[1]);
+            gv[0] = a.x; gv[1] = a.y; gv[2] = b.x; gv[3] = b.y;
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(g + i);
+            gv[0] = a.x; gv[1] = a.y; gv[2] = a.z; gv[3] = a.w;
+        }
+        const float mo[4] = {c.x * scale, c.y * scale, c.z * scale, c.w * scale};
+        float mv[4], amax = 0.f;
+        uint2 uo;
+        __nv_bfloat162* ub = reinterpret_cast<__nv_bfloat162*>(&uo);
+        float uv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float gk = gv[k] * gs;
+            mv[k] = mu * mo[k] + (1.f - mu) * gk;
+            uv[k] = (1.f - mu) * gk + mu * mv[k];
+            amax = fmaxf(amax, fabsf(mv[k]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const __half hs = __float2half_ru(amax);              // rounded up: no code can exceed 127
+        const float inv = amax > 0.f ? 127.f / __half2float(hs) : 0.f;
+        char4 co;
+        co.x = static_cast<signed char>(__float2int_rn(mv[0] * inv));
+        co.y = static_cast<signed char>(__float2int_rn(mv[1] * inv));
+        co.z = static_cast<signed char>(__float2int_rn(mv[2] * inv));
+        co.w = static_cast<signed char>(__float2int_rn(mv[3] * inv));
+        *reinterpret_cast<char4*>(m8 + i) = co;
+        if (lane == 0) ms[grp] = hs;
+        ub[0] = __floats2bfloat162_rn(uv[0], uv[1]);
+        ub[1] = __floats2bfloat162_rn(uv[2], uv[3]);
+        *reinterpret_cast<uint2*>(u + i) = uo;
+        const float2 r0 = __bfloat1622float2(ub[0]), r1 = __bfloat1622float2(ub[1]);
+        acc += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
     }
     acc = nm_block_sum(acc, sh);
     if (threadIdx.x == 0 && acc != 0.f) atomicAdd(sumsq, acc);
@@ -113,6 +173,14 @@ static int nm_grid(size_t n, int num_sms) {
 void normuon_momentum(const void* g, int g_fp32, void* m, void* u, float* sumsq, const float* hp, float mu, size_t n, int num_sms, cudaStream_t s) {
     if (g_fp32) normuon_momentum_kernel<float><<<nm_grid(n, num_sms), 256, 0, s>>>((const float*)g, (bf16*)m, (bf16*)u, sumsq, hp, mu, n);
     else normuon_momentum_kernel<bf16><<<nm_grid(n, num_sms), 256, 0, s>>>((const bf16*)g, (bf16*)m, (bf16*)u, sumsq, hp, mu, n);
+}
+void normuon_momentum8(const void* g, int g_fp32, void* m8, void* ms, void* u, float* sumsq, const float* hp, float mu, size_t n, int num_sms, cudaStream_t s) {
+    const size_t warps = n / 128;
+    size_t grid = (warps + 7) / 8;
+    const size_t cap = static_cast<size_t>(num_sms) * 8;
+    grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
+    if (g_fp32) normuon_momentum8_kernel<float><<<static_cast<int>(grid), 256, 0, s>>>((const float*)g, (int8_t*)m8, (__half*)ms, (bf16*)u, sumsq, hp, mu, n);
+    else normuon_momentum8_kernel<bf16><<<static_cast<int>(grid), 256, 0, s>>>((const bf16*)g, (int8_t*)m8, (__half*)ms, (bf16*)u, sumsq, hp, mu, n);
 }
 void normuon_normalise(void* x, const float* sumsq, size_t n, int num_sms, cudaStream_t s) {
     normuon_normalise_kernel<<<nm_grid(n, num_sms), 256, 0, s>>>((bf16*)x, sumsq, n);

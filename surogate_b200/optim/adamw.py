@@ -30,6 +30,7 @@ class OptimizerConfig:
     normuon_beta2: float = 0.95
     normuon_cautious_wd: bool = True
     normuon_lr_scale: float = 1.0
+    normuon_momentum_8bit: bool = False   # momentum as int8 codes with an fp16 scale per 128 values instead of bf16
 
 
 def _softsign_quant_reference(mi, vi):

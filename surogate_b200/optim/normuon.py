@@ -68,7 +68,9 @@ class NorMuon(AdamW8bit):
     def __init__(self, cfg: OptimizerConfig, store):
         super().__init__(cfg, store)
         self.mom: Dict[str, torch.Tensor] = {}
+        self.mom_scales: Dict[str, torch.Tensor] = {}
         self.second: Dict[str, torch.Tensor] = {}
+        self.momentum_8bit = bool(getattr(cfg, "normuon_momentum_8bit", False))
 
     @staticmethod
     def is_matrix_param(slot) -> bool:
@@ -132,7 +134,7 @@ class NorMuon(AdamW8bit):
     def _step_matrices_device(self, b, grad, hp, before, matrices, lo, hi) -> None:
         """Matrix parameters on the GPU: momentum / Nesterov blend / Frobenius norm (one kernel), normalisation (one kernel), five
         Polar-Express iterations on the tcgen05 GEMM, row statistics (one kernel) and the update with cautious weight decay (one kernel).
-        Momentum is kept in bf16, the row second moments in fp32; hyper-parameters and the clip scale are read from the device vector, so
+        Momentum is kept in bf16 (or, with ``normuon_momentum_8bit``, as int8 codes with an fp16 scale per 128 values), the row second moments in fp32; hyper-parameters and the clip scale are read from the device vector, so
         nothing here synchronises with the host.  A matrix that straddles a shard boundary is orthogonalised by every rank that owns a
         part of it (from the gathered gradient) and each rank applies its own slice."""
         store, ext = self.store, self.ext
@@ -148,10 +150,17 @@ class NorMuon(AdamW8bit):
                 continue
             if g_full.dtype not in (torch.bfloat16, torch.float32):
                 g_full = g_full.float()
-            m = self.mom.get(s.name)
-            if m is None or m.dtype != torch.bfloat16:
-                m = self.mom[s.name] = torch.zeros(s.numel, dtype=torch.bfloat16, device=store.device)
-            u, sumsq = ext.normuon_momentum(g_full, m.view(-1), hp, mu)
+            if self.momentum_8bit and s.numel % 128 == 0:     # int8 codes + one fp16 scale per 128 values (1.02 bytes per parameter)
+                m = self.mom.get(s.name)
+                if m is None or m.dtype != torch.int8:
+                    m = self.mom[s.name] = torch.zeros(s.numel, dtype=torch.int8, device=store.device)
+                    self.mom_scales[s.name] = torch.zeros(s.numel // 128, dtype=torch.float16, device=store.device)
+                u, sumsq = ext.normuon_momentum8(g_full, m, self.mom_scales[s.name], hp, mu)
+            else:
+                m = self.mom.get(s.name)
+                if m is None or m.dtype != torch.bfloat16:
+                    m = self.mom[s.name] = torch.zeros(s.numel, dtype=torch.bfloat16, device=store.device)
+                u, sumsq = ext.normuon_momentum(g_full, m.view(-1), hp, mu)
             ext.normuon_normalise(u, sumsq)
             X = polar_express_device(u.view(s.shape))
             v = self.second.get(s.name)

@@ -85,6 +85,7 @@ class TrainerConfig:
     normuon_momentum: float = 0.95
     normuon_beta2: float = 0.95
     normuon_cautious_wd: bool = True
+    normuon_momentum_8bit: bool = False
     init_projections_to_zero: bool = False
     seed: int = 0
 
@@ -176,7 +177,7 @@ class Trainer:
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd, lmhead_drop_ignored_rows=cfg.lmhead_drop_ignored_rows,
                                                      offload_saved=cfg.offload_saved_tensors, time_breakdown=cfg.time_breakdown), device=self.device, ep=self.ep, lora=self.lora)
         self.opt_cfg = OptimizerConfig(cfg.optimizer, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm,
-                                       cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd)
+                                       cfg.normuon_momentum, cfg.normuon_beta2, cfg.normuon_cautious_wd, normuon_momentum_8bit=cfg.normuon_momentum_8bit)
         self.streamed = None
         if cfg.async_optimizer and not cfg.cpu_training:
             raise ValueError("async_optimizer overlaps the HOST update with device compute: it needs cpu_training")

@@ -356,6 +356,10 @@ def test_biased_and_relu2_experts_on_the_grouped_gemm_path(arch):
         assert ea < 0.2 or float(den) < 1e-2, f"{name}: rel err {ea.item():.4f}"
 
 
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
 def test_normuon_device_path_follows_the_pytorch_oracle():
     """NorMuon on the kernels (momentum / normalise / row statistics / apply kernels and Polar-Express on the tcgen05 GEMM) against
     the PyTorch statement of the optimizer (optim/normuon.py, kept as the oracle).  The quintic iteration multiplies small singular
@@ -399,6 +403,16 @@ def test_normuon_device_path_follows_the_pytorch_oracle():
             wr = w0[first:first + count]
             decay = 0.1 * 1e-2 * wr * (((upd * wr) > 0).float() if cautious else 1.0)
             assert torch.allclose(w, wr - decay - 1e-2 * 2.5 * upd, atol=1e-5, rtol=1e-4), (cautious, first)
+    # 8-bit momentum: same update up to the 8-bit rounding of the state, codes bounded, state is one byte per value
+    m8, ms = torch.zeros(n, dtype=torch.int8, device=dev0), torch.zeros(n // 128, dtype=torch.float16, device=dev0)
+    m_ref8 = torch.zeros(n, device=dev0)
+    for _ in range(3):
+        u8, ss8 = ext.normuon_momentum8(grad, m8, ms, hp, mu)
+        m_ref8 = mu * m_ref8 + (1 - mu) * gv
+        u_ref8 = (1 - mu) * gv + mu * m_ref8
+    deq = m8.float().view(-1, 128) / 127.0 * ms.float()[:, None]
+    assert _rel(deq.view(-1), m_ref8) < 0.02 and _rel(u8.float(), u_ref8) < 0.02 and m8.abs().max().item() <= 127
+    assert abs(ss8.item() - u8.float().pow(2).sum().item()) < 1e-3 * ss8.item()
     # 2. the iteration on the own GEMM: matrices whose singular values are spread over one decade, wide and tall
     for shape in ((256, 512), (512, 256), (384, 384)):
         A = torch.randn(shape, generator=g)
