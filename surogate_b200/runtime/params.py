@@ -37,7 +37,7 @@ import torch
 from ..dsl.compiler import CompiledModel, ParamEntry
 
 ALIGN_ELEMS = 128
-FP8_SHARDS_DEFAULT = "0"   # quantise-then-gather of ZeRO-3 FP8 weights: opt-in (SUROGATE_FP8_SHARDS=1) until confirmed on 2+ GPUs
+FP8_SHARDS_DEFAULT = "1"   # quantise-then-gather of ZeRO-3 FP8 weights (SUROGATE_FP8_SHARDS=0: peers pull bf16 and quantise on arrival)
 
 
 @dataclass
