@@ -286,8 +286,11 @@ Tensor ep_row_positions(const Tensor& topk_idx, int64_t num_experts) {
 
 void ep_dispatch(const Tensor& x, const c10::optional<Tensor>& topk_idx, const c10::optional<Tensor>& w, const c10::optional<Tensor>& dst_base,
                  const c10::optional<Tensor>& cursors, Tensor& row_map, const std::vector<int64_t>& recv, int64_t recv_byte_offset, int64_t K,
-                 int64_t experts_per_rank, int64_t capacity_rows, bool reuse_map) {
+                 int64_t experts_per_rank, int64_t capacity_rows, bool reuse_map, const c10::optional<Tensor>& q_scale, const c10::optional<Tensor>& amax_out) {
     TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x: bf16 contiguous");
+    const float* qs = (q_scale.has_value() && q_scale->defined()) ? q_scale->data_ptr<float>() : nullptr;
+    float* am = (amax_out.has_value() && amax_out->defined()) ? amax_out->data_ptr<float>() : nullptr;
+    TORCH_CHECK(!(qs && w.has_value() && w->defined()), "ep_dispatch: FP8 rows carry no per-row weights");
     const int C = static_cast<int>(x.size(-1));
     const int tokens = static_cast<int>(x.numel() / C);
     TORCH_CHECK(C % 8 == 0 && K <= 16 && row_map.numel() == static_cast<int64_t>(tokens) * K, "ep_dispatch shapes");
@@ -295,7 +298,7 @@ void ep_dispatch(const Tensor& x, const c10::optional<Tensor>& topk_idx, const c
     const float* wp = (w.has_value() && w->defined()) ? w->data_ptr<float>() : nullptr;
     sg_count_launch(1);
     sg::ep_dispatch(x.data_ptr(), iptr(topk_idx), wp, iptr(dst_base), iptr(cursors), row_map.data_ptr<int>(), to_peers(recv, recv_byte_offset), tokens, C,
-                    static_cast<int>(K), static_cast<int>(experts_per_rank), static_cast<int>(capacity_rows), reuse_map, cur_stream());
+                    static_cast<int>(K), static_cast<int>(experts_per_rank), static_cast<int>(capacity_rows), reuse_map, qs, am, cur_stream());
 }
 
 std::vector<Tensor> ep_combine(const std::vector<int64_t>& outs, int64_t out_byte_offset, const c10::optional<Tensor>& w, const Tensor& row_map,
@@ -621,7 +624,10 @@ void sg_register_extra(pybind11::module_& m) {
           pybind11::arg("seq_id") = c10::optional<Tensor>(), pybind11::arg("silu") = false);
     m.def("causal_conv1d_bwd", &causal_conv1d_bwd, pybind11::arg("dz"), pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("seq_id") = c10::optional<Tensor>());
     m.def("ep_plan", &ep_plan);
-    m.def("ep_dispatch", &ep_dispatch);
+    m.def("ep_dispatch", &ep_dispatch, pybind11::arg("x"), pybind11::arg("topk_idx"), pybind11::arg("w"), pybind11::arg("dst_base"), pybind11::arg("row_pos"),
+          pybind11::arg("row_map"), pybind11::arg("recv"), pybind11::arg("recv_byte_offset"), pybind11::arg("K"), pybind11::arg("experts_per_rank"),
+          pybind11::arg("capacity_rows"), pybind11::arg("reuse_map"), pybind11::arg("q_scale") = c10::optional<Tensor>(),
+          pybind11::arg("amax_out") = c10::optional<Tensor>());
     m.def("ep_row_positions", &ep_row_positions);
     m.def("ep_zero_pad_rows", &ep_zero_pad_rows);
     m.def("copy_rows_upto", &copy_rows_upto);

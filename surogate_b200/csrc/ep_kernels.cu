@@ -15,6 +15,7 @@
 // Replaces csrc/src/runtime/ep/ep_strategy.cpp:621-856 (split exchange + grouped ncclSend/Recv + host syncs) and
 // csrc/src/kernels/ep_dispatch.cu of the reference.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -141,9 +142,13 @@ __global__ void __launch_bounds__(256) ep_row_positions_kernel(const int* __rest
 // row_pos[tok*K+k] = position of the copy among this rank's copies for that expert (ep_row_positions_kernel).
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const bf16* __restrict__ x, const int* __restrict__ topk_idx, const float* __restrict__ w,
                                                           const int* __restrict__ dst_base, const int* __restrict__ row_pos, int* __restrict__ row_map,
-                                                          PeerPtrs recv, int C, int K, int El, int capacity_rows, int reuse_map) {
+                                                          PeerPtrs recv, int C, int K, int El, int capacity_rows, int reuse_map,
+                                                          const float* __restrict__ q_scale, float* __restrict__ amax_out) {
+    // q_scale != null: rows cross NVLink as E4M3 (value * *q_scale), one byte per element into a [capacity, C] byte buffer, and the
+    // abs-max of what was sent is recorded for the next step's scale (delayed scaling; the scale is the same on every rank).
     __shared__ long long dst[16];
     __shared__ float ws[16];
+    __shared__ float red[8];
     const int tok = blockIdx.x;
     if (threadIdx.x < K) {
         long long code = -1;
@@ -160,6 +165,40 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const bf16* __restrict
     }
     __syncthreads();
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(tok) * C);
+    if (q_scale) {
+        const float qs = __ldg(q_scale);
+        float amax = 0.f;
+        for (int c = threadIdx.x; c < C / 8; c += blockDim.x) {
+            const uint4 v = src[c];
+            const bf162* p = reinterpret_cast<const bf162*>(&v);
+            uint2 q;
+            uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+                qb[2 * i] = __nv_cvt_float_to_fp8(f.x * qs, __NV_SATFINITE, __NV_E4M3);
+                qb[2 * i + 1] = __nv_cvt_float_to_fp8(f.y * qs, __NV_SATFINITE, __NV_E4M3);
+            }
+            for (int k = 0; k < K; ++k) {
+                if (dst[k] < 0) continue;
+                const int owner = static_cast<int>(dst[k] / capacity_rows);
+                const size_t row = static_cast<size_t>(dst[k] - static_cast<long long>(owner) * capacity_rows);
+                reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(recv.p[owner]) + row * C)[c] = q;
+            }
+        }
+        if (amax_out) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+                if (amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(amax_out), __float_as_uint(amax));
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < C / 8; c += blockDim.x) {
         const uint4 v = src[c];
         for (int k = 0; k < K; ++k) {
@@ -284,8 +323,9 @@ void copy_rows_upto(const void* src, void* dst, const int* n_rows, int C, int nu
     copy_rows_upto_kernel<<<num_sms * 8, 256, 0, s>>>((const uint4*)src, (uint4*)dst, n_rows, C);
 }
 void ep_dispatch(const void* x, const int* topk_idx, const float* w, const int* dst_base, const int* row_pos, int* row_map, const PeerPtrs& recv, int tokens,
-                 int C, int K, int El, int capacity_rows, int reuse_map, cudaStream_t s) {
-    ep_dispatch_kernel<<<tokens, 256, 0, s>>>((const bf16*)x, topk_idx, w, dst_base, row_pos, row_map, recv, C, K, El, capacity_rows, reuse_map);
+                 int C, int K, int El, int capacity_rows, int reuse_map, const float* q_scale, float* amax_out, cudaStream_t s) {
+    ep_dispatch_kernel<<<tokens, 256, 0, s>>>((const bf16*)x, topk_idx, w, dst_base, row_pos, row_map, recv, C, K, El, capacity_rows, reuse_map, q_scale,
+                                              amax_out);
 }
 void ep_row_positions(const int* topk_idx, int* pos, int n_entries, int E, cudaStream_t s) {
     ep_row_positions_kernel<<<E, 256, 0, s>>>(topk_idx, pos, n_entries);

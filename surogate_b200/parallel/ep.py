@@ -167,15 +167,27 @@ class ExpertParallel:
         pb = b["arena"].peer_bases
         self.ext.ep_plan(pb, b["counts_off"], self.comm.ctrl.peer_bases, pre.counts, offsets, dst_base, cursors, self.rank, self.epoch & 0x7FFFFFFF,
                          SLOT_EP, cap, self.err, self.comm.wait_budget_s)
+        rec = getattr(ctx, "recipe", None)
+        fp8 = rec.dispatch_fp8(ctx, x2) if (rec is not None and hasattr(rec, "dispatch_fp8")) else None
+        # FP8 rows are one byte per element: the same receive buffer seen as [cap, C] bytes = [cap, C / 2] 16-bit units, so the
+        # row-wise helpers (pad clearing, copy of the rows in use) work on it unchanged
+        recv = b["recv_x"] if fp8 is None else b["recv_x"].view(-1).view(torch.uint8)[:cap * C].view(torch.bfloat16).view(cap, C // 2)
         # pad rows feed the wgrad contraction and must be zero; only they are touched, so peers may already be storing real rows
-        self.ext.ep_zero_pad_rows(b["recv_x"], offsets, El, cap)
+        self.ext.ep_zero_pad_rows(recv, offsets, El, cap)
         # rows are taken in token order (a stable counting sort per expert), not claimed with atomics: same layout in every run
         row_pos = self.ext.ep_row_positions(pre.topk_idx.reshape(-1).contiguous(), E)
-        self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, row_pos, row_map, pb, b["recv_x_off"], K, El, cap, False)
+        if fp8 is None:
+            self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, row_pos, row_map, pb, b["recv_x_off"], K, El, cap, False)
+        else:
+            self.ext.ep_dispatch(x2.contiguous(), pre.topk_idx, None, dst_base, row_pos, row_map, pb, b["recv_x_off"], K, El, cap, False, fp8[0], fp8[2])
         self._barrier()  # every rank's rows have landed
-        xp = torch.empty_like(b["recv_x"])  # rows beyond the used range stay uninitialised: nothing downstream reads them into a result
+        xp = torch.empty_like(recv)         # rows beyond the used range stay uninitialised: nothing downstream reads them into a result
         used = offsets[El:El + 1]           # padded rows in use this step (device side): element-wise kernels downstream stop there
-        self.ext.copy_rows_upto(b["recv_x"], xp, used)
+        self.ext.copy_rows_upto(recv, xp, used)
+        if fp8 is not None:
+            xp = xp.view(torch.uint8).view(cap, C).view(torch.float8_e4m3fn)
+            xp._sg_inv = fp8[1]
+            self.fp8_dispatches = getattr(self, "fp8_dispatches", 0) + 1
         xp._sg_rows = used
         if ctx.layer is not None and ctx.phase == "fwd":
             gc = b["counts"].view(self.ep, E).sum(0)

@@ -50,6 +50,10 @@ class GroupedFp8Mixin:
         st = self.__dict__.get("_g_state")
         if st is None:
             return
+        comm = self.__dict__.get("ep_group_comm")
+        if comm is not None and self.dispatch_in_fp8:
+            # rows quantised by different ranks meet in one receive buffer: every rank of the expert group must derive the same scale
+            comm.all_reduce(st["amax"], "max")
         s = torch.where(st["amax"] > 0, st["fmax"] / st["amax"], st["scale"])
         st["scale"].copy_(torch.where(torch.isfinite(s), s, st["scale"]))
         st["inv"].copy_(1.0 / st["scale"])
@@ -92,7 +96,28 @@ class GroupedFp8Mixin:
     def _grouped_active(self, ctx, op, x, w) -> bool:
         role = op.attrs.get("role", "")
         return (self.quantize_experts and ctx.layer is not None and ctx.layer not in self.skip and role in EXPERT_ROLES and torch.is_tensor(x)
-                and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3 and w.shape[1] % 16 == 0 and w.shape[2] % 16 == 0)
+                and (x.dtype == torch.bfloat16 or self._arrived_fp8(x)) and w.dtype == torch.bfloat16 and w.dim() == 3 and w.shape[1] % 16 == 0
+                and w.shape[2] % 16 == 0)
+
+    # ------------------------------------------------------------------ rows that crossed NVLink already quantised
+    import os as _os
+
+    dispatch_in_fp8 = _os.environ.get("SUROGATE_EP_FP8_DISPATCH", "0") == "1"
+
+    @staticmethod
+    def _arrived_fp8(x) -> bool:
+        return x.dtype == torch.float8_e4m3fn and getattr(x, "_sg_inv", None) is not None
+
+    def dispatch_fp8(self, ctx, x):
+        """(scale, de-scale, abs-max slot) when the expert-parallel dispatch of this layer may send E4M3 rows: the first expert GEMM
+        then reads them as they arrive and the bf16 rows are never stored on the receiving side.  Needs a scale from an earlier step
+        (the same on every rank of the expert group, see ``grouped_end_step``) and no adapter reading the rows in bf16."""
+        st = self.__dict__.get("_g_state")
+        if (not self.dispatch_in_fp8 or st is None or not st["have"] or not self.quantize_experts or ctx.layer is None or ctx.layer in self.skip
+                or getattr(ctx, "lora", None) is not None or x.dtype != torch.bfloat16 or x.shape[-1] % 16 != 0):
+            return None
+        q = self._gslot(ctx.layer, "experts_gate_up", "x")
+        return st["scale"][q:q + 1], st["inv"][q:q + 1], st["amax"][q:q + 1]
 
     def forward_grouped(self, ctx, op, x, w, plan):
         if not self._grouped_active(ctx, op, x, w):
@@ -102,7 +127,10 @@ class GroupedFp8Mixin:
         ext = _ext()
         role = op.attrs["role"]
         used = getattr(x, "_sg_rows", None)
-        x8, x_inv = self._gq(ext, x, False, used, self._gslot(ctx.layer, role, "x"))
+        if self._arrived_fp8(x):
+            x8, x_inv = x, x._sg_inv
+        else:
+            x8, x_inv = self._gq(ext, x, False, used, self._gslot(ctx.layer, role, "x"))
         w8, w_inv = self._expert_weight(ctx, ext, role, w)
         y = (torch.empty if used is not None else torch.zeros)(x.shape[0], w.shape[1], dtype=torch.bfloat16, device=x.device)
         ext.gemm_grouped(x8, w8, y, plan.offsets, 1, False, False, 1.0, x_inv, w_inv, ext.error_flag_tensor())
@@ -124,14 +152,17 @@ class GroupedFp8Mixin:
             used = getattr(x, "_sg_rows", None)
         dy8, dy_inv = self._gq(ext, dy, True, used, self._gslot(ctx.layer, role, "dy"))
         w8, w_inv = self._expert_weight(ctx, ext, role, w)
-        dx = (torch.empty_like if used is not None else torch.zeros_like)(x)
+        dx = (torch.empty if used is not None else torch.zeros)(x.shape, dtype=torch.bfloat16, device=x.device)
         ext.gemm_grouped(dy8, w8, dx, plan.offsets, 1, True, False, 1.0, dy_inv, w_inv, err)          # dy [R, N] . W[e] [N, K]
         if used is not None:
             dx._sg_rows = used
         tgt, acc = ctx.grad_target(op.outputs[1])
         if tgt is not None:
             # re-quantised from the saved bf16 rows with the scale the forward used: a second FP8 copy per layer is not kept
-            x8, x_inv = self._gq(ext, x, False, used, self._gslot(ctx.layer, role, "x"))
+            if self._arrived_fp8(x):
+                x8, x_inv = x, x._sg_inv
+            else:
+                x8, x_inv = self._gq(ext, x, False, used, self._gslot(ctx.layer, role, "x"))
             ext.gemm_grouped(dy8, x8, tgt, plan.offsets, 2, True, acc, 1.0, dy_inv, x_inv, err)         # dW[e] (+)= dy[e]^T . x[e]
             if not acc:
                 ext.zero_empty_groups(tgt, plan.offsets)

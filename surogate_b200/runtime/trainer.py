@@ -168,6 +168,8 @@ class Trainer:
 
                     group_comm = symm.try_create(self.ep_comm, self.device, required=True)
                 self.ep = ExpertParallel(group_comm, cfg.ep_size, self.device, capacity_factor=cfg.ep_capacity_factor)
+                if hasattr(self.recipe, "dispatch_fp8"):
+                    self.recipe.ep_group_comm = group_comm     # delayed scales of dispatched rows are agreed inside the expert group
                 self.ep.replica_comm = self.expert_dp_comm
             else:                              # PyTorch backend (CPU ranks over gloo included): the library all-to-all
                 from ..parallel.ep_ref import AllToAllExpertParallel

@@ -98,7 +98,7 @@ def main():
                                       "fused_norm": bool(tr.store.fused_sumsq is not None and tr.store.sumsq_valid),
                                       "fp8_gather": bool(tr.store.fp8_gather), "fp8_shards": bool(getattr(tr.store, "fp8_arena", None) is not None), "graph_replays": getattr(tr, "graph_replays", 0), "h2d_weight_bytes": int(tr.store.h2d_bytes),
                                       "stage_slots": len(tr.store.stage_slots),
-                                      "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0,
+                                      "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0, "fp8_dispatches": int(getattr(tr.ep, "fp8_dispatches", 0)) if tr.ep is not None else 0,
                                       "ep_moves": tr.ep.moves_done if tr.ep is not None else 0,
                                       "ep_imbalance": tr.ep.imbalance() if tr.ep is not None else 1.0, **extra}), flush=True)
     if info.world > 1:

@@ -74,6 +74,18 @@ def test_expert_parallel_with_fp8_experts_trains_like_one_gpu():
     two = run_worker(2, dict(ARGS, model=MOE, recipe="fp8_hybrid", ep=2, zero=1, collectives="symm"), port=29743)
     for a, b in zip(two["losses"], one["losses"]):
         assert abs(a - b) < 4e-2 * abs(b), (two["losses"], one["losses"])
+    # rows quantised by the sender (E4M3 over NVLink with the expert group's shared delayed scale, from the second step on)
+    import os
+
+    os.environ["SUROGATE_EP_FP8_DISPATCH"] = "1"
+    try:
+        q = run_worker(2, dict(ARGS, model=MOE, recipe="fp8_hybrid", ep=2, zero=1, collectives="symm"), port=29744)
+    finally:
+        del os.environ["SUROGATE_EP_FP8_DISPATCH"]
+    assert q["fp8_dispatches"] > 0 and two["fp8_dispatches"] == 0
+    assert q["losses"][0] == two["losses"][0]            # the first step has no scale yet: same path
+    for a, b in zip(q["losses"], two["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (q["losses"], two["losses"])
 
 
 LORA = dict(rank=8, alpha=16, dropout=0.0, dtype="fp32", targets=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
