@@ -320,13 +320,8 @@ def main():
     if args.model == "qwen3-8b" and world >= 2 and not args.no_secondary and args.impl == "native" and not args.layers:
         # the second half of the headline metric; a failure there must not lose the first half
         try:
-            import gc
-
-            import torch
-
-            gc.collect()                 # the first model's buckets, arena slices and activations go back to the driver before
-            torch.cuda.synchronize()     # the second one (147 GB per GPU at EP=2) is built
-            torch.cuda.empty_cache()
+            # The first trainer is NOT torn down in between: releasing its peer-mapped (symmetric) buffers and allocating new ones right
+            # after made the two ranks wait on each other until the run was killed, so its memory stays until the process ends.
             sec = measure(args, "qwen3-30b-a3b", info, comm, dev)
         except Exception as e:  # noqa: BLE001
             sec = {"error": f"{type(e).__name__}: {e}"[:400]}
