@@ -39,6 +39,9 @@ class _Work:
         torch.cuda.current_stream().wait_event(self.event)
 
 
+_ARENAS_ALIVE: List["Arena"] = []
+
+
 class Arena:
     def __init__(self, tensor: torch.Tensor, peer_bases: List[int], mc_base: int):
         self.tensor = tensor  # uint8 view of the whole local arena
@@ -109,6 +112,11 @@ class SymmComm:
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
         a = Arena(t, bases, mc)
         a.handle = hdl
+        # Peer-mapped blocks are kept until the process ends: a run that released such buffers and allocated new ones right afterwards
+        # stalled (both ranks waited on each other until the job was killed), most likely because the new block reused the address and
+        # the cached peer mappings of the old one.  A trainer that is rebuilt inside one process (out-of-memory retry with a smaller
+        # micro-batch, a second model in a benchmark) therefore adds arenas instead of replacing them.
+        _ARENAS_ALIVE.append(a)
         return a
 
     def create_arena(self, nbytes: int) -> Arena:
