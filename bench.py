@@ -120,6 +120,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "library"])
+    ap.add_argument("--ep-refresh", type=int, default=16, dest="ep_refresh", help="steps between expert re-placement decisions (expert parallel)")
     ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
     ap.add_argument("--recipe", default=None)
     ap.add_argument("--optimizer", default=None)
@@ -172,7 +173,8 @@ def measure(args, model_key, info, comm, dev):
                         # router stays below 2x, and rows that would not fit are counted and reported in the JSON line (expected: 0)
                         ep_capacity_factor=float(max(1, min(ep, 3))),
                         resident_layers=args.resident_layers, use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
-                        ep_plan_refresh_interval=4)            # counts are summed over 4 steps per decision; refreshes after warm-up are inside the timed region
+                        ep_plan_refresh_interval=args.ep_refresh)   # the framework's (and the reference's) default: a placement decision every 16 steps;
+                                                                     # a decision costs about 250 ms at EP=2 (experts and their optimizer state move)
     if spec.get("recompute"):
         cfg.recompute = True
     tr = Trainer(cfg, device=dev, comm=comm)
@@ -274,6 +276,7 @@ def measure(args, model_key, info, comm, dev):
             "config": {"model": spec["label"], "global_batch": world * mb, "seq_len": seq, "parallelism": par, "recipe": recipe,
                        "optimizer": cfg.optimizer, "attention": args.attention, "recompute": bool(cfg.recompute), "micro_batch_per_gpu": mb,
                        "lora_rank": (spec.get("lora") or {}).get("rank"), "offload": bool(cfg.offload_master),
+                       "ep_plan_refresh_interval": int(cfg.ep_plan_refresh_interval) if ep > 1 else None,
                        "keep_gathered": bool(cfg.keep_gathered and zero >= 3),   # ZeRO-3: gathered layer weights stay from forward to backward (one gather per step, not two)
                        "cuda_graphs": bool(getattr(tr, "graph_replays", 0)), "drop_ignored_rows": bool(cfg.lmhead_drop_ignored_rows), "resident_layers": int(args.resident_layers),
                        "weight_h2d_bytes_per_step": int(tr.store.h2d_bytes // max(1, args.steps + args.warmup + (0 if args.no_e2e else args.steps + 1))),
