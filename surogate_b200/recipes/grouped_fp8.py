@@ -102,7 +102,7 @@ class GroupedFp8Mixin:
     # ------------------------------------------------------------------ rows that crossed NVLink already quantised
     import os as _os
 
-    dispatch_in_fp8 = _os.environ.get("SUROGATE_EP_FP8_DISPATCH", "0") == "1"
+    dispatch_in_fp8 = _os.environ.get("SUROGATE_EP_FP8_DISPATCH", "1") == "1"    # 0: bf16 rows cross NVLink and the owner quantises them
 
     @staticmethod
     def _arrived_fp8(x) -> bool:
