@@ -778,9 +778,9 @@ __device__ __forceinline__ float rcp_fast(float x) {
 __device__ __forceinline__ float2 splat2(float x) { return make_float2(x, x); }
 constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23: adding it rounds to the nearest integer and leaves it in the low mantissa bits
 
-// MINB = resident CTAs per SM asked of the compiler: 3 keeps everything in registers (80), 4 caps them at 64 for more warps in flight
-template <typename P, typename G, bool BLOCK_MASK, int MINB = 3>
-__global__ void __launch_bounds__(256, MINB) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
+// 3 resident CTAs per SM keep everything in registers (80); capping them at 64 for a fourth CTA spills 80 bytes and measured the same
+template <typename P, typename G, bool BLOCK_MASK>
+__global__ void __launch_bounds__(256, 3) adamw_8bit_kernel(P* __restrict__ p, const G* __restrict__ g, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
                                                             __half* __restrict__ ms, __half* __restrict__ vs, const uint8_t* __restrict__ decay_mask,
                                                             const float* __restrict__ hp, size_t n) {
     // softsign decode table of the momentum code, indexed by code + 128: y = c/127, m = y / (2 - |y|) (times the group scale)
@@ -1038,11 +1038,6 @@ void adamw_fp32(void* p, int p_fp32, const void* g, int g_fp32, float* m, float*
 void adamw_8bit(void* p, int p_fp32, const void* g, int g_fp32, void* m8, void* v8, void* ms, void* vs, const uint8_t* mask, int block_mask,
                 const float* hp, size_t n, int num_sms, cudaStream_t s) {
     const int grid = grid_for(n / 16, 256, num_sms, 16);
-    static const bool occ4 = [] { const char* e = getenv("SUROGATE_ADAMW_OCC4"); return e && e[0] == '1'; }();
-    if (occ4 && block_mask && !p_fp32 && !g_fp32) {   // the training configuration (bf16 weights and gradients) at 4 CTAs per SM
-        adamw_8bit_kernel<bf16, bf16, true, 4><<<grid, 256, 0, s>>>((bf16*)p, (const bf16*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n);
-        return;
-    }
 #define SG_A8(PT, GT, BM) adamw_8bit_kernel<PT, GT, BM><<<grid, 256, 0, s>>>((PT*)p, (const GT*)g, (int8_t*)m8, (uint8_t*)v8, (__half*)ms, (__half*)vs, mask, hp, n)
     if (block_mask) {
         if (p_fp32 && g_fp32) SG_A8(float, float, true); else if (p_fp32) SG_A8(float, bf16, true); else if (g_fp32) SG_A8(bf16, float, true); else SG_A8(bf16, bf16, true);
