@@ -114,7 +114,8 @@ class GroupedFp8Mixin:
         (the same on every rank of the expert group, see ``grouped_end_step``) and no adapter reading the rows in bf16."""
         st = self.__dict__.get("_g_state")
         if (not self.dispatch_in_fp8 or st is None or not st["have"] or not self.quantize_experts or ctx.layer is None or ctx.layer in self.skip
-                or getattr(ctx, "lora", None) is not None or x.dtype != torch.bfloat16 or x.shape[-1] % 16 != 0):
+                or getattr(ctx, "lora", None) is not None or x.dtype != torch.bfloat16 or x.shape[-1] % 16 != 0
+                or getattr(getattr(ctx, "ex", None), "offload", None) is not None):   # parked saved tensors come back without their scale tag
             return None
         q = self._gslot(ctx.layer, "experts_gate_up", "x")
         return st["scale"][q:q + 1], st["inv"][q:q + 1], st["amax"][q:q + 1]
