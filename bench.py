@@ -177,8 +177,17 @@ def measure(args, model_key, info, comm, dev):
                                                                      # a decision costs about 250 ms at EP=2 (experts and their optimizer state move)
     if spec.get("recompute"):
         cfg.recompute = True
+    trace = os.environ.get("SUROGATE_BENCH_TRACE") == "1"     # progress marks on stderr from every rank (where does a stalled run stop?)
+
+    def mark(what):
+        if trace:
+            print(f"[trace r{info.rank} {time.strftime('%H:%M:%S')}] {model_key}: {what}", file=sys.stderr, flush=True)
+
+    mark("building the trainer")
     tr = Trainer(cfg, device=dev, comm=comm)
+    mark("initialising weights")
     tr.init_weights(seed=0)
+    mark("weights ready")
     V = spec["model"]["vocab_size"]
     rng = np.random.default_rng(1234 + info.rank)
     n_dev = args.warmup + args.steps          # device-timed region: one fresh batch per step, resident before the clock starts
@@ -207,7 +216,15 @@ def measure(args, model_key, info, comm, dev):
     ext = tr.backend.ext if tr.backend.name == "cuda" else None
     for i in range(args.warmup):
         device_step(i)
+        if trace:      # a step at a time: synchronise, report, and fail at the first bounded wait that ran out
+            torch.cuda.synchronize()
+            mark(f"warm-up step {i} done")
+            if ext is not None:
+                from surogate_b200.ops import check_device_errors
+
+                check_device_errors()
     barrier()
+    mark("timed region starts")
     sampler = ClockSampler(info.local_rank)
     sampler.start()
     launches0 = ext.launch_count() if ext is not None else 0
@@ -218,6 +235,7 @@ def measure(args, model_key, info, comm, dev):
         device_step(args.warmup + i)
     ev1.record()
     barrier()
+    mark("timed region done")
     ms = ev0.elapsed_time(ev1)
     if ext is not None:
         from surogate_b200.ops import check_device_errors

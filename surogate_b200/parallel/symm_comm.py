@@ -16,6 +16,8 @@ Ordering rules the kernels rely on:
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional
 
 import torch
@@ -81,7 +83,7 @@ class SymmComm:
         self.epochs = {SLOT_MAIN: 0, SLOT_SIDE: 0}
         self.ar_epoch = 0
         self.max_blocks = 96
-        self.wait_budget_s = 20.0
+        self.wait_budget_s = float(os.environ.get("SUROGATE_WAIT_BUDGET_S", "20"))   # every cross-GPU wait gives up after this long and raises the error flag
         self.use_multimem = False
         # control block: signal pad + small all-reduce scratch, in its own small symmetric allocation
         self.ctrl = self._alloc_symmetric(PAD_WORDS * 4 + SCRATCH_FLOATS * 4)
