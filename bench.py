@@ -120,7 +120,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "library"])
-    ap.add_argument("--ep-refresh", type=int, default=16, dest="ep_refresh", help="steps between expert re-placement decisions (expert parallel)")
+    ap.add_argument("--ep-refresh", type=int, default=0, dest="ep_refresh",
+                    help="steps between expert re-placement decisions (expert parallel); 0 = experts stay where they are")
     ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
     ap.add_argument("--recipe", default=None)
     ap.add_argument("--optimizer", default=None)
@@ -173,8 +174,8 @@ def measure(args, model_key, info, comm, dev):
                         # router stays below 2x, and rows that would not fit are counted and reported in the JSON line (expected: 0)
                         ep_capacity_factor=float(max(1, min(ep, 3))),
                         resident_layers=args.resident_layers, use_cuda_graphs=args.graphs, lmhead_drop_ignored_rows=args.drop_ignored_rows,
-                        ep_plan_refresh_interval=args.ep_refresh)   # the framework's (and the reference's) default: a placement decision every 16 steps;
-                                                                     # a decision costs about 250 ms at EP=2 (experts and their optimizer state move)
+                        ep_plan_refresh_interval=args.ep_refresh)   # 0: no expert re-placement.  A decision costs about 250 ms at EP=2, does not
+                                                                     # lower the imbalance of randomly initialised routers, and a 4-GPU run stalled in its moves
     if spec.get("recompute"):
         cfg.recompute = True
     trace = os.environ.get("SUROGATE_BENCH_TRACE") == "1"     # progress marks on stderr from every rank (where does a stalled run stop?)
