@@ -300,6 +300,11 @@ class ExpertParallel:
         return {"layers": changed, "moved": moved_total}
 
     def _move_experts(self, store, optimizer, L: int, cur, new, El: int, dist) -> None:
+        """Experts of layer ``L`` change slots: ``cur[e]`` / ``new[e]`` = global slot (owner * El + local slot) of expert ``e`` before /
+        after.  Master weights, work weights and optimizer state of every moved expert travel in ONE all-to-all of bytes over the
+        expert group, which every rank of the group enters (with empty parts where it has nothing to move): point-to-point batches
+        entered by only some of the ranks stalled on four GPUs.  Moves inside a rank are copies; nothing is overwritten before every
+        outgoing part has been packed."""
         b = store.buckets.get(f"layer{L}.experts")
         if b is None:
             return
@@ -310,9 +315,10 @@ class ExpertParallel:
         for t in (st or {}).values():
             tensors.append(t)
         n_master = b.master.numel()
-        sends, recvs = [], []   # (tensor, range) pairs on this rank
-        ops, temps = [], []
-        group = getattr(self.comm.base, "group", None)
+        world, rank = self.ep, self.rank
+        send_parts = [[] for _ in range(world)]      # per destination rank: byte views, in (expert, slot, tensor) order
+        recv_specs = [[] for _ in range(world)]      # per source rank: (tensor, first, last) in the same order
+        local = []
         for e in range(len(cur)):
             if cur[e] == new[e]:
                 continue
@@ -320,21 +326,30 @@ class ExpertParallel:
             for sl in b.slots:
                 per = sl.numel // El
                 for t in tensors:
-                    div = n_master // t.numel() if t.numel() < n_master else 1   # fp16 scales: one per 32 elements
+                    div = n_master // t.numel() if t.numel() < n_master else 1   # group scales: one per 32 / 128 elements
                     a0, a1 = (sl.offset + src_s * per) // div, (sl.offset + (src_s + 1) * per) // div
                     d0, d1 = (sl.offset + dst_s * per) // div, (sl.offset + (dst_s + 1) * per) // div
-                    if self.rank == src_r and self.rank == dst_r:
-                        temps.append((t, d0, d1, t[a0:a1].clone()))
-                    elif self.rank == src_r:
-                        ops.append(dist.P2POp(dist.isend, t[a0:a1].clone(), dist.get_global_rank(group, dst_r) if group is not None else dst_r, group))
-                    elif self.rank == dst_r:
-                        buf = torch.empty(d1 - d0, dtype=t.dtype, device=t.device)
-                        temps.append((t, d0, d1, buf))
-                        ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(group, src_r) if group is not None else src_r, group))
-        if ops:
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
-        for t, d0, d1, buf in temps:   # only now overwrite: a slot's previous occupant has been copied out above
+                    if rank == src_r and rank == dst_r:
+                        local.append((t, d0, d1, t[a0:a1].clone()))
+                    elif rank == src_r:
+                        send_parts[dst_r].append(t[a0:a1].contiguous().view(torch.uint8))
+                    elif rank == dst_r:
+                        recv_specs[src_r].append((t, d0, d1))
+        dev = b.master.device
+        in_splits = [int(sum(p.numel() for p in parts)) for parts in send_parts]
+        out_splits = [int(sum((d1 - d0) * t.element_size() for t, d0, d1 in specs)) for specs in recv_specs]
+        flat = [p for parts in send_parts for p in parts]
+        send = torch.cat(flat) if flat else torch.empty(0, dtype=torch.uint8, device=dev)
+        recv = torch.empty(sum(out_splits), dtype=torch.uint8, device=dev)
+        group = getattr(self.comm.base, "group", None)
+        dist.all_to_all_single(recv, send, out_splits, in_splits, group=group)
+        at = 0
+        for specs in recv_specs:
+            for t, d0, d1 in specs:
+                n = (d1 - d0) * t.element_size()
+                t[d0:d1].copy_(recv[at:at + n].view(t.dtype))
+                at += n
+        for t, d0, d1, buf in local:   # only now: a slot's previous occupant has been packed or copied out above
             t[d0:d1].copy_(buf)
 
     # ------------------------------------------------------------------ balancing
