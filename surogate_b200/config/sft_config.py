@@ -175,7 +175,7 @@ class SFTConfig:
     memcpy_send_recv: bool = False
     ep_size: int = 1
     ep_load_balance_threshold: float = 1.3
-    ep_plan_refresh_interval: int = 0
+    ep_plan_refresh_interval: int = 16
     async_optimizer: Optional[str] = None                   # with cpu_training: overlap | inline (host update one step behind, overlapped with compute)
     trainable_param_substrings: Optional[List[str]] = None  # full fine-tuning of a subset: names containing one of these train
     gradient_mask_mode: Optional[str] = None                # allow_substrings | mlp_growth_new_half

@@ -59,7 +59,7 @@ class TrainerConfig:
     ep_load_balance_threshold: float = 1.3   # re-place experts when a layer's busiest rank exceeds this multiple of the mean load
     trainable_param_substrings: Optional[List[str]] = None  # partial-update runs: only parameters whose name contains one of these train
     gradient_mask_mode: Optional[str] = None  # allow_substrings | mlp_growth_new_half (None: the SUROGATE_GRADIENT_MASK_MODE variable)
-    ep_plan_refresh_interval: int = 0       # steps between placement refreshes (0 = never)
+    ep_plan_refresh_interval: int = 16       # steps between placement refreshes (0 = never)
     lora: Optional[Dict[str, Any]] = None
     fp8_amax_history: int = 16
     skip_quant_first_layers: int = 0
