@@ -86,6 +86,20 @@ def main(argv, command: str = "grpo") -> int:
                             make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="producer"),
                             lambda: (b.latest() or {"version": -1})["version"])
         orch.load_prompts()
+        if raw.get("async_scheduler") or raw.get("scheduler") == "async":
+            # asynchronous loop: bounded in-flight requests on a thread pool, difficulty pools, rollout filters, depth budget
+            from ..grpo.orchestration import AsyncOrchestrator, async_config_from, make_generate_group
+
+            urls = raw.get("base_urls") or [cfg.base_url]
+            if len(urls) > 1:
+                orch.client = [OpenAIClient(u, cfg.model, cfg.request_timeout_s) for u in urls]
+            tok = orch.tok
+            acfg = async_config_from(cfg, raw, vocab_size=getattr(tok, "vocab_size", 32000), pad_token_id=max(0, getattr(tok, "pad_token_id", 0)))
+            loop = AsyncOrchestrator(acfg, orch.prompts, make_generate_group(orch), orch.transport, lambda: (b.latest() or {"version": -1})["version"],
+                                     num_servers=len(urls))
+            hist = loop.run()
+            print(json.dumps({"steps": len(hist), "last_reward_mean": hist[-1].get("reward/mean") if hist else None}))
+            return 0
         hist = orch.run()
         print(json.dumps({"steps": len(hist), "last_reward_mean": hist[-1].reward_mean if hist else None}))
         return 0

@@ -8,4 +8,4 @@ from .buffer import BufferConfig, ExampleBuffer  # noqa: F401
 from .depth import DepthObservation, RolloutDepthController  # noqa: F401
 from .filters import FilterResult, GibberishFilter, RepetitionFilter, apply_filters, make_filters  # noqa: F401
 from .scheduler import RolloutScheduler, SchedulerConfig  # noqa: F401
-from .loop import AsyncOrchestrator, AsyncOrchestratorConfig, OrchestratorCheckpoints, Progress  # noqa: F401
+from .loop import AsyncOrchestrator, AsyncOrchestratorConfig, OrchestratorCheckpoints, Progress, async_config_from, make_generate_group  # noqa: F401

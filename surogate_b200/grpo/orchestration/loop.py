@@ -218,3 +218,67 @@ class AsyncOrchestrator:
         finally:
             self.pool.shutdown(wait=False, cancel_futures=True)
         return self.history
+
+
+# ------------------------------------------------------------------------------------------ wiring to the synchronous orchestrator's parts
+
+
+def make_generate_group(orch) -> Callable[..., List[Rollout]]:
+    """``generate_group`` for ``AsyncOrchestrator`` built from a configured ``grpo.orchestrator.Orchestrator`` (tokenizer, inference
+    client(s), reward function or environment): one prompt's group, single- or multi-turn, rewards set, advantages left to the loop.
+    ``orch.client`` may be a list of clients (one per inference server): the scheduler's ``server`` index picks one."""
+    from ..orchestrator import Orchestrator  # noqa: F401  (type only)
+
+    def pick(server: int):
+        c = orch.client
+        return c[server % len(c)] if isinstance(c, (list, tuple)) else c
+
+    def generate_group(example, n, sampling, version, server):
+        env = orch.env
+        out: List[Rollout] = []
+        if env is not None and hasattr(env, "env_response"):
+            saved_client, saved_n = orch.client, orch.cfg.group_size
+            orch.client, orch.cfg.group_size = pick(server), n
+            try:
+                cap = (example.get("info") or {}).get("max_turns")
+                if cap is not None and hasattr(env, "max_turns"):
+                    old_turns, env.max_turns = env.max_turns, min(int(env.max_turns), int(cap))
+                try:
+                    eps = orch.multi_turn_group(example, sampling)
+                finally:
+                    if cap is not None and hasattr(env, "max_turns"):
+                        env.max_turns = old_turns
+            finally:
+                orch.client, orch.cfg.group_size = saved_client, saved_n
+            for pids, ids, lps, mask, r in eps:
+                if ids:
+                    turns = 1 + sum(1 for a, b in zip(mask, mask[1:]) if a == 0 and b == 1)
+                    out.append(Rollout(pids, ids, lps, 0.0, float(r), version, 0, {"turns": turns, "truncated": cap is not None and turns >= int(cap)}, completion_mask=mask))
+            return out
+        pids = orch._prompt_ids(example)
+        gens = pick(server).generate(pids, n, sampling)
+        rewards = [float(r) for r in orch.reward_fn(example, [t for _, _, t in gens])]
+        if orch.cfg.length_penalty:
+            rewards = [r - orch.cfg.length_penalty * len(ids) for r, (ids, _, _) in zip(rewards, gens)]
+        for (ids, lps, _), r in zip(gens, rewards):
+            if ids and len(lps) == len(ids):
+                out.append(Rollout(pids, ids, lps, 0.0, r, version, 0, {"turns": 1}))
+        return out
+
+    return generate_group
+
+
+def async_config_from(cfg, raw: Optional[Dict[str, Any]] = None, vocab_size: int = 32000, pad_token_id: int = 0) -> AsyncOrchestratorConfig:
+    """``OrchestratorConfig`` (+ the raw YAML dict for the keys only the asynchronous loop knows) -> ``AsyncOrchestratorConfig``."""
+    raw = raw or {}
+    a = AsyncOrchestratorConfig(group_size=cfg.group_size, batch_size=int(raw.get("batch_size", cfg.group_size * cfg.prompts_per_step)),
+                                token_batch_size=raw.get("token_batch_size"), sequence_len=cfg.sequence_len, rows_per_step=cfg.rows_per_step,
+                                max_steps=cfg.max_steps, max_inflight=int(raw.get("max_inflight", 2 * cfg.prompts_per_step)), max_async_level=cfg.max_async_level,
+                                max_off_policy_steps=int(raw.get("max_off_policy_steps", 4)), workers=int(raw.get("workers", 2 * cfg.prompts_per_step)),
+                                advantage=str(raw.get("advantage", "default")), length_weighted_mean=bool(raw.get("length_weighted_mean", False)),
+                                filters=list(raw.get("filters", [])), buffer=dict(raw.get("buffer", {"seed": cfg.seed, "online_difficulty_filtering": cfg.filter_zero_advantage})),
+                                depth=dict(raw.get("depth", {"enabled": False})),
+                                sampling={"max_tokens": cfg.max_tokens, "temperature": cfg.temperature, "top_p": cfg.top_p, **cfg.extra_sampling},
+                                checkpoint_dir=raw.get("checkpoint_dir"), checkpoint_every=int(raw.get("checkpoint_every", 0)), vocab_size=vocab_size,
+                                pad_token_id=pad_token_id)
+    return a

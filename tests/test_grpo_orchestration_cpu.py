@@ -225,3 +225,40 @@ def test_cli_dry_run_lists_the_three_components(tmp_path, capsys):
     assert rc == 0 and [l["name"] for l in lines] == ["rollout engine", "trainer", "orchestrator"]
     rc = cli_main(["grpo-colocate", "--train", str(tmp_path / "t.yaml"), "--infer", str(tmp_path / "i.yaml"), "--orch", str(tmp_path / "o.yaml"), "--dry-run"])
     assert rc == 0 and "grpo-infer" in capsys.readouterr().out
+
+
+def test_async_loop_runs_on_the_parts_of_a_configured_orchestrator(tmp_path):
+    """``make_generate_group`` + ``async_config_from``: the asynchronous loop driven by the same tokenizer / client / reward objects
+    the synchronous orchestrator uses (a fake client and tokenizer stand in for the server)."""
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, async_config_from, make_generate_group
+    from surogate_b200.grpo.orchestrator import Orchestrator
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    class Tok:
+        pad_token_id, vocab_size = 0, 100
+
+        def apply_chat_template_and_encode(self, messages, add_generation_prompt=True):
+            return [1] + [2 + (ord(c) % 50) for c in messages[-1]["content"]][:6]
+
+    class Client:
+        def __init__(self):
+            self.calls = 0
+
+        def generate(self, prompt_ids, n, sampling):
+            self.calls += 1
+            return [([10 + k, 11, 12], [-0.1, -0.2, -0.3], "yes" if k % 2 else "no") for k in range(n)]
+
+    cfg = OrchestratorConfig(model="m", group_size=4, prompts_per_step=2, sequence_len=32, rows_per_step=2, max_steps=2, max_async_level=4, reward="exact_match")
+    clients = [Client(), Client()]
+    tr = FilesystemTransport(str(tmp_path))
+    orch = Orchestrator(cfg, Tok(), clients, tr, lambda: 0, reward_fn=lambda row, texts: [1.0 if t == row["answer"] else 0.0 for t in texts])
+    orch.load_prompts([{"prompt": f"q{i}", "answer": "yes"} for i in range(6)])
+    acfg = async_config_from(cfg, {"max_inflight": 4, "workers": 2, "filters": [{"type": "repetition"}]}, vocab_size=100)
+    assert acfg.batch_size == 8 and acfg.sampling["max_tokens"] == cfg.max_tokens and acfg.filters
+    loop = AsyncOrchestrator(acfg, orch.prompts, make_generate_group(orch), tr, lambda: 0, num_servers=2)
+    hist = loop.run()
+    assert len(hist) == 2 and clients[0].calls > 0 and clients[1].calls > 0          # both servers were used
+    arrays, meta = tr.receive(1, timeout_s=1)
+    adv = arrays["advantages"][arrays["targets"] != -100]
+    assert meta["n_samples"] == 8 and set(np.round(np.unique(adv), 3)) == {-0.5, 0.5}
