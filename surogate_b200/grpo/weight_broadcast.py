@@ -21,8 +21,10 @@ import torch
 
 
 class FilesystemBroadcast:
-    def __init__(self, directory: str, keep: int = 2):
-        self.dir, self.keep = directory, keep
+    def __init__(self, directory: str, keep: int = 2, noise=None, total_steps: int = 0):
+        """``noise``: a ``grpo.noise.NoiseConfig``; with it every published version carries exploration noise on its normalisation
+        weights (full models) or at least the sigma in force (adapters), following the schedule over ``total_steps`` versions."""
+        self.dir, self.keep, self.noise, self.total_steps = directory, keep, noise, total_steps
         os.makedirs(directory, exist_ok=True)
 
     def publish(self, trainer, version: int, hf_config: Optional[Dict] = None) -> str:
@@ -33,6 +35,10 @@ class FilesystemBroadcast:
             trainer.export_adapter(out)
         else:
             trainer.export_model(out, hf_config)
+        if trainer.rank == 0 and self.noise is not None and self.noise.enabled:
+            from .noise import add_noise_to_directory, sigma_at
+
+            add_noise_to_directory(out, sigma_at(version, self.total_steps, self.noise), seed=self.noise.seed + version)
         if trainer.rank == 0:
             with open(os.path.join(self.dir, "LATEST.tmp"), "w") as f:
                 json.dump({"version": version, "path": out, "time": time.time(), "kind": "adapter" if trainer.lora is not None else "model"}, f)

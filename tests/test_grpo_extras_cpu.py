@@ -1,0 +1,48 @@
+"""Turn-resolved statistics and exploration noise of published weights."""
+import json
+import os
+
+import numpy as np
+import torch
+from safetensors.torch import load_file, save_file
+
+from surogate_b200.grpo.noise import NoiseConfig, add_noise_to_directory, read_sigma, sigma_at
+from surogate_b200.grpo.turn_stats import TurnStats, turn_ids_from_mask, turn_weights
+
+
+def test_turn_ids_statistics_and_weights():
+    mask = np.array([1, 1, 0, 0, 1, 1, 1, 0, 1], dtype=np.int32)
+    ids = turn_ids_from_mask(mask)
+    assert ids.tolist() == [0, 0, -1, -1, 1, 1, 1, -1, 2]
+    st = TurnStats()
+    new = np.array([-1.0, -1.0, 0, 0, -0.5, -0.5, -0.5, 0, -2.0])
+    old = np.array([-0.5, -0.5, 0, 0, -0.5, -0.5, -0.5, 0, -1.0])
+    st.add_sample(ids, mask, new, old, token_loss=np.abs(new - old))
+    st.add_sample(ids[:4], mask[:4], new[:4], old[:4], token_loss=np.abs(new - old)[:4])          # a sample that stopped after turn 0
+    rows = {r["turn"]: r for r in st.rows()}
+    assert rows[0]["tokens"] == 4 and rows[0]["survivors"] == 2 and rows[2]["survivors"] == 1
+    assert abs(rows[0]["mean_kl"] + 0.5) < 1e-9 and rows[1]["mean_abs_kl"] == 0.0 and abs(rows[2]["mean_kl"] + 1.0) < 1e-9
+    assert abs(sum(r["token_share"] for r in rows.values()) - 1) < 1e-9 and abs(sum(r["abs_kl_share"] for r in rows.values()) - 1) < 1e-9
+    s = st.summary()
+    assert s["turns/max_depth"] == 3 and s["turns/deep_survivor_fraction"] == 0.5 and s["turns/deep_over_shallow_abs_kl"] == 2.0
+    w0, w1 = turn_weights(ids, mask, 0.0), turn_weights(ids, mask, 1.0)
+    sup = mask.astype(bool)
+    assert np.allclose(w0[sup], 1.0) and abs(w1.sum() - sup.sum()) < 1e-5 and np.all(w0[~sup] == 0)
+    per_turn = [w1[ids == t].sum() for t in range(3)]
+    assert np.allclose(per_turn, [2.0, 2.0, 2.0], atol=1e-5)            # every turn carries the same total weight
+
+
+def test_noise_schedule_and_injection(tmp_path):
+    cfg = NoiseConfig(enabled=True, sigma_start=1e-2, sigma_end=1e-4, stages=5)
+    sig = [sigma_at(s, 100, cfg) for s in range(0, 100, 10)]
+    assert sig[0] == 0.0 and sig[1] == 0.0 and abs(sig[2] - 1e-2) < 1e-12 and abs(sig[-1] - 1e-4) < 1e-12
+    assert all(a >= b for a, b in zip(sig[2:], sig[3:])) and sigma_at(5, 100, NoiseConfig()) == 0.0
+    tensors = {"model.layers.0.input_layernorm.weight": torch.ones(16, dtype=torch.bfloat16), "model.layers.0.self_attn.q_norm.weight": torch.ones(8),
+               "model.norm.weight": torch.ones(16), "model.layers.0.mlp.up_proj.weight": torch.ones(4, 4)}
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    assert add_noise_to_directory(str(tmp_path), 0.05, seed=1) == 3
+    out = load_file(str(tmp_path / "model.safetensors"))
+    assert torch.equal(out["model.layers.0.mlp.up_proj.weight"], torch.ones(4, 4)) and out["model.layers.0.input_layernorm.weight"].dtype == torch.bfloat16
+    d = (out["model.norm.weight"] - 1).abs()
+    assert 0 < d.max() < 0.3 and read_sigma(str(tmp_path)) == {"sigma": 0.05, "tensors_changed": 3}
+    assert add_noise_to_directory(str(tmp_path), 0.0) == 0 and read_sigma(str(tmp_path))["sigma"] == 0.0
