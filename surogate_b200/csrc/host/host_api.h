@@ -114,4 +114,13 @@ struct GpuTelemetry {
 };
 GpuTelemetry query_gpu(int index);  // read-only NVML queries through a dlopen'ed libnvidia-ml
 
+// buffer_planner.cpp
+struct BufferPlanResult {
+    std::vector<int64_t> offsets;
+    int64_t total = 0;
+};
+BufferPlanResult plan_buffer_offsets(const std::vector<int64_t>& nbytes, const std::vector<int64_t>& first, const std::vector<int64_t>& last);
+std::string validate_buffer_plan(const std::vector<int64_t>& nbytes, const std::vector<int64_t>& first, const std::vector<int64_t>& last,
+                                 const std::vector<int64_t>& offsets, int64_t total);
+
 }  // namespace sg

@@ -192,6 +192,17 @@ PYBIND11_MODULE(sg_b200_host, m) {
               return py::make_tuple(p, moved);
           }, py::arg("counts"), py::arg("ep_size"), py::arg("current"), py::arg("tolerance") = 0.05f);
 
+    m.def("plan_buffer_offsets", [](const std::vector<int64_t>& nbytes, const std::vector<int64_t>& first, const std::vector<int64_t>& last) {
+        if (first.size() != nbytes.size() || last.size() != nbytes.size()) throw std::invalid_argument("plan_buffer_offsets: the three lists must have one entry per tensor");
+        BufferPlanResult r = plan_buffer_offsets(nbytes, first, last);
+        return py::make_tuple(r.offsets, r.total);
+    });
+    m.def("validate_buffer_plan", [](const std::vector<int64_t>& nbytes, const std::vector<int64_t>& first, const std::vector<int64_t>& last,
+                                      const std::vector<int64_t>& offsets, int64_t total) {
+        if (first.size() != nbytes.size() || last.size() != nbytes.size() || offsets.size() != nbytes.size())
+            throw std::invalid_argument("validate_buffer_plan: the lists must have one entry per tensor");
+        return validate_buffer_plan(nbytes, first, last, offsets, total);
+    });
     m.def("install_crash_handler", &install_crash_handler, py::arg("tag") = "surogate_b200");
     m.def("query_gpu", [](int index) {
         GpuTelemetry t = query_gpu(index);

@@ -315,8 +315,25 @@ def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
 
 
-def _pack(ts: List[PlannedTensor]) -> int:
-    """Interval colouring: largest tensors first, each at the lowest offset that is free during its whole lifetime."""
+def _native_planner():
+    try:
+        from ..ops import host
+
+        h = host()
+        return h if hasattr(h, "plan_buffer_offsets") else None
+    except Exception:  # noqa: BLE001 -- the host runtime is not built: the Python statement below is used
+        return None
+
+
+def _pack(ts: List[PlannedTensor], use_native: bool = True) -> int:
+    """Interval colouring: largest tensors first, each at the lowest offset that is free during its whole lifetime.  Runs in the
+    native host runtime (csrc/host/buffer_planner.cpp) when it is built; the Python loop below is the same procedure and its oracle."""
+    h = _native_planner() if use_native else None
+    if h is not None and ts:
+        offsets, total = h.plan_buffer_offsets([int(t.nbytes) for t in ts], [int(t.first) for t in ts], [int(t.last) for t in ts])
+        for t, off in zip(ts, offsets):
+            t.offset = int(off)
+        return int(total)
     placed: List[PlannedTensor] = []
     top = 0
     for t in sorted(ts, key=lambda t: (-t.nbytes, t.first)):

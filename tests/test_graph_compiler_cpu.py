@@ -185,3 +185,29 @@ def test_tensor_debug_commands(tmp_path, capsys):
     assert tt.tensor_resolve(str(cfgp), "nope")[0]["error"]
     assert cli_main(["debug", "tensor-resolve", str(cfgp), "--name", "ln2", "--seq-len", "64"]) == 0
     assert "TENSOR_RESOLVE" in capsys.readouterr().out
+
+
+def test_native_buffer_planner_equals_the_python_statement_and_validates_plans():
+    import random
+
+    from surogate_b200.dsl.graph_compiler import PlannedTensor, _pack
+    from surogate_b200.ops import host
+
+    h = host()
+    rnd = random.Random(0)
+    for trial in range(20):
+        n = rnd.randint(1, 60)
+        specs = []
+        for i in range(n):
+            a = rnd.randint(0, 40)
+            specs.append((rnd.choice([0, 64, 256, 1000, 4096, 70000]), a, a + rnd.randint(0, 12)))
+        py = [PlannedTensor(f"t{i}", "temp", nb, f, l) for i, (nb, f, l) in enumerate(specs)]
+        nat = [PlannedTensor(f"t{i}", "temp", nb, f, l) for i, (nb, f, l) in enumerate(specs)]
+        total_py, total_nat = _pack(py, use_native=False), _pack(nat, use_native=True)
+        assert total_py == total_nat and [t.offset for t in py] == [t.offset for t in nat], trial
+        nb, fi, la = [s[0] for s in specs], [s[1] for s in specs], [s[2] for s in specs]
+        assert h.validate_buffer_plan(nb, fi, la, [t.offset for t in nat], total_nat) == ""
+        assert total_nat <= sum((x + 255) // 256 * 256 for x in nb)
+    # two tensors alive together at the same offset are reported
+    assert "alias" in h.validate_buffer_plan([512, 512], [0, 1], [5, 3], [0, 256], 1024)
+    assert "aligned" in h.validate_buffer_plan([512], [0], [1], [8], 1024) and "outside" in h.validate_buffer_plan([512], [0], [1], [768], 1024)
