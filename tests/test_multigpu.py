@@ -141,7 +141,7 @@ def test_pipeline_stages_on_two_gpus_match_one_gpu(stage_layers):
     model = dict(architecture="Qwen3ForCausalLM", vocab_size=1024, d_model=256, n_layers=4, num_query_heads=2, num_kv_heads=1, head_size=128, d_ff=512,
                  tie_word_embeddings=True)
     one = run_worker(1, dict(ARGS, model=model, zero=0, grad_accum=2))
-    r = run_worker(2, dict(ARGS, model=model, pp=True, grad_accum=1, stage_layers=stage_layers), port=29761 + stage_layers)
+    r = run_worker(2, dict(ARGS, model=model, pp=True, grad_accum=1, stage_layers=stage_layers), port=29781 + stage_layers)
     assert r["world"] == 2 and len(r["stages"]) == (4 if stage_layers else 2)
     for a, b in zip(r["losses"], one["losses"]):
         assert abs(a - b) < 2e-2 * abs(b), (r["losses"], one["losses"])
@@ -152,7 +152,7 @@ def test_pipeline_stages_on_two_gpus_match_one_gpu(stage_layers):
 @pytest.mark.parametrize("collectives", ["nccl", "symm"])
 def test_two_gpus_graph_replay_with_deferred_reductions(single, collectives):
     """Forward + backward replayed from CUDA graphs on each rank, gradient reduce-scatter issued after the replay."""
-    r = run_worker(2, dict(ARGS, zero=1, collectives=collectives, graphs=True, steps=6), port=29771 + (1 if collectives == "symm" else 0))
+    r = run_worker(2, dict(ARGS, zero=1, collectives=collectives, graphs=True, steps=6), port=29785 + (1 if collectives == "symm" else 0))
     one = run_worker(1, dict(ARGS, steps=6))
     assert r["graph_replays"] == 4, r["graph_replays"]
     for a, b in zip(r["losses"], one["losses"]):
