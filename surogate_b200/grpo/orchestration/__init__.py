@@ -9,3 +9,4 @@ from .depth import DepthObservation, RolloutDepthController  # noqa: F401
 from .filters import FilterResult, GibberishFilter, RepetitionFilter, apply_filters, make_filters  # noqa: F401
 from .scheduler import RolloutScheduler, SchedulerConfig  # noqa: F401
 from .loop import AsyncOrchestrator, AsyncOrchestratorConfig, OrchestratorCheckpoints, Progress, async_config_from, make_generate_group  # noqa: F401
+from .evaluation import evaluate_policy, pass_at_k  # noqa: F401

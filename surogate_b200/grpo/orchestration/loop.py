@@ -51,6 +51,10 @@ class AsyncOrchestratorConfig:
     checkpoint_dir: Optional[str] = None
     checkpoint_every: int = 0
     keep_checkpoints: int = 2
+    eval_every: int = 0                        # evaluate on ``eval_examples`` every this many steps (0 = never)
+    eval_samples: int = 4
+    eval_ks: Sequence[int] = (1, 4)
+    eval_pass_threshold: float = 1.0
     poll_s: float = 0.01
     step_timeout_s: float = 3600.0
     vocab_size: int = 32000
@@ -111,8 +115,10 @@ class AsyncOrchestrator:
     the trainer published; ``transport.send(step, arrays, meta)`` ships a packed batch."""
 
     def __init__(self, cfg: AsyncOrchestratorConfig, examples: Sequence[Dict[str, Any]], generate_group: Callable[..., List[Rollout]], transport,
-                 policy_version: Callable[[], int], num_servers: int = 1, on_step: Optional[Callable[[Dict[str, float]], None]] = None):
+                 policy_version: Callable[[], int], num_servers: int = 1, on_step: Optional[Callable[[Dict[str, float]], None]] = None,
+                 eval_examples: Optional[Sequence[Dict[str, Any]]] = None):
         self.cfg, self.transport, self.policy_version, self.on_step = cfg, transport, policy_version, on_step
+        self.eval_examples, self.num_servers = list(eval_examples or []), max(1, num_servers)
         self.buffer = ExampleBuffer(examples, BufferConfig(**cfg.buffer))
         self.pool = ThreadPoolExecutor(max_workers=cfg.workers, thread_name_prefix="rollout")
         self.generate_group = generate_group
@@ -204,6 +210,11 @@ class AsyncOrchestrator:
         self.progress.total_problems += len({r.meta.get("example_id") for r in kept})
         out = {"step": float(step), "time/step_s": time.time() - t0, **stats, **s.metrics(), **self.buffer.metrics(), **self.depth.metrics(),
                "progress/total_tokens": float(self.progress.total_tokens), "progress/total_samples": float(self.progress.total_samples)}
+        if self.eval_examples and self.cfg.eval_every and (step + 1) % self.cfg.eval_every == 0:
+            from .evaluation import evaluate_policy
+
+            out.update(evaluate_policy(self.eval_examples, self.generate_group, self.cfg.eval_samples, self.cfg.sampling, max(0, self.policy_version()),
+                                       self.cfg.eval_ks, self.cfg.eval_pass_threshold, self.num_servers))
         if self.ckpt is not None and self.cfg.checkpoint_every and (step + 1) % self.cfg.checkpoint_every == 0:
             self.ckpt.save(self.progress, self.buffer)
         self.history.append(out)

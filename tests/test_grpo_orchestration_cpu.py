@@ -262,3 +262,28 @@ def test_async_loop_runs_on_the_parts_of_a_configured_orchestrator(tmp_path):
     arrays, meta = tr.receive(1, timeout_s=1)
     adv = arrays["advantages"][arrays["targets"] != -100]
     assert meta["n_samples"] == 8 and set(np.round(np.unique(adv), 3)) == {-0.5, 0.5}
+
+
+def test_periodic_evaluation_reports_pass_at_k_without_feeding_the_trainer(tmp_path):
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, AsyncOrchestratorConfig, evaluate_policy, pass_at_k
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    assert pass_at_k(4, 0, 2) == 0.0 and pass_at_k(4, 4, 1) == 1.0 and abs(pass_at_k(4, 1, 1) - 0.25) < 1e-12 and abs(pass_at_k(4, 1, 2) - 0.5) < 1e-12
+    assert pass_at_k(2, 1, 8) == 1.0            # k is capped at n
+
+    def generate_group(example, n, sampling, version, server):
+        solved = {"always": n, "half": n // 2, "never": 0}[example["kind"]]
+        return [_rollout(1.0 if k < solved else 0.0, n=5 + k) for k in range(n)]
+
+    held_out = [{"prompt": "a", "kind": "always"}, {"prompt": "b", "kind": "half"}, {"prompt": "c", "kind": "never"}]
+    m = evaluate_policy(held_out, generate_group, 4, {}, ks=(1, 2))
+    assert abs(m["eval/mean_reward"] - 0.5) < 1e-12 and abs(m["eval/pass@1"] - 0.5) < 1e-12 and abs(m["eval/unsolved_fraction"] - 1 / 3) < 1e-12
+    assert abs(m["eval/pass@2"] - (1 + (1 - 1 / 6) + 0) / 3) < 1e-12
+    train = [{"prompt": f"q{i}", "kind": "half"} for i in range(6)]
+    cfg = AsyncOrchestratorConfig(group_size=4, batch_size=8, sequence_len=64, rows_per_step=4, max_steps=2, max_inflight=4, workers=2, eval_every=2, eval_samples=4,
+                                  eval_ks=(1, 2))
+    tr = FilesystemTransport(str(tmp_path))
+    hist = AsyncOrchestrator(cfg, train, generate_group, tr, lambda: 0, eval_examples=held_out).run()
+    assert "eval/pass@1" not in hist[0] and abs(hist[1]["eval/pass@1"] - 0.5) < 1e-12
+    _, meta = tr.receive(1, timeout_s=1)
+    assert meta["n_samples"] == 8              # the evaluation rollouts did not join the batch
