@@ -190,6 +190,15 @@ def test_every_example_configuration_loads_and_validates():
             cfg = InferenceConfig(**d)
         elif rel == os.path.join("grpo", "orch.yaml"):
             cfg = OrchestratorConfig(**d)
+        elif rel == os.path.join("grpo", "orch-async.yaml"):
+            from surogate_b200.grpo.orchestration import async_config_from, make_filters
+            from surogate_b200.grpo.orchestration.buffer import BufferConfig
+            from surogate_b200.grpo.orchestration.depth import RolloutDepthController
+
+            cfg = OrchestratorConfig(**{k: v for k, v in d.items() if k in OrchestratorConfig.__dataclass_fields__})
+            a = async_config_from(cfg, d, vocab_size=1000)
+            assert a.batch_size == 128 and a.max_inflight == 48 and len(make_filters(a.filters, 1000)) == 2 and d["scheduler"] == "async"
+            assert BufferConfig(**a.buffer).min_normal == 256 and RolloutDepthController(**a.depth).max_cap == 24
         else:
             cfg = SFTConfig.from_dict(d)
         assert cfg.model, rel
