@@ -56,6 +56,7 @@ class InferenceConfig:
     enable_lora: bool = True
     max_lora_rank: int = 64
     weight_dir: str = "output/grpo/weights"
+    weight_broadcast: str = "filesystem"   # filesystem | nccl | colocate: which receiver the engine's workers mix in (grpo/vllm_worker.py)
     extra_args: List[str] = field(default_factory=list)
 
 

@@ -31,6 +31,11 @@ def server_command(cfg: InferenceConfig) -> List[str]:
         cmd += ["--max-model-len", str(cfg.max_model_len)]
     if cfg.enable_lora:
         cmd += ["--enable-lora", "--max-lora-rank", str(cfg.max_lora_rank)]
+    from .vllm_worker import WORKER_EXTENSIONS
+
+    ext = WORKER_EXTENSIONS.get(getattr(cfg, "weight_broadcast", "filesystem"))
+    if ext:   # the workers gain update_weights_from_path / receive_weights / receive_ipc_handles, callable through collective_rpc
+        cmd += ["--worker-extension-cls", ext]
     return cmd + list(cfg.extra_args)
 
 

@@ -46,3 +46,49 @@ def test_noise_schedule_and_injection(tmp_path):
     d = (out["model.norm.weight"] - 1).abs()
     assert 0 < d.max() < 0.3 and read_sigma(str(tmp_path)) == {"sigma": 0.05, "tensors_changed": 3}
     assert add_noise_to_directory(str(tmp_path), 0.0) == 0 and read_sigma(str(tmp_path))["sigma"] == 0.0
+
+
+def test_engine_side_weight_receivers_on_a_stand_in_worker(tmp_path):
+    """The three receivers the rollout engine's workers mix in: files, broadcast over a group of their own, shared-memory handles."""
+    import threading
+
+    from surogate_b200.grpo.noise import add_noise_to_directory
+    from surogate_b200.grpo.vllm_worker import WORKER_EXTENSIONS, ColocateWeightReceiver, FilesystemWeightReceiver, NCCLWeightReceiver, _bcast_opts
+
+    class Model:
+        def __init__(self):
+            self.got = {}
+
+        def load_weights(self, weights):
+            for n, t in weights:
+                self.got[n] = t.clone()
+
+    def worker(cls):
+        w = cls()
+        w.model_runner = type("R", (), {"model": Model()})()
+        w.device = "cpu"
+        return w
+
+    assert set(WORKER_EXTENSIONS) == {"filesystem", "nccl", "colocate"}
+    named = {"model.layers.0.self_attn.q_proj.lora_A.weight": torch.randn(4, 8), "model.norm.weight": torch.ones(8)}
+    save_file(named, str(tmp_path / "adapter_model.safetensors"))
+    add_noise_to_directory(str(tmp_path), 0.0)
+    fw = worker(FilesystemWeightReceiver)
+    r = fw.update_weights_from_path(str(tmp_path))
+    assert r == {"tensors": 2, "version": 1, "noise_sigma": 0.0} and torch.equal(fw.model_runner.model.got["model.norm.weight"], torch.ones(8))
+    # broadcast: "trainer" = rank 0 in this thread, the engine worker = rank 1 in another
+    header = [{"name": n, "shape": list(t.shape), "dtype": str(t.dtype).replace("torch.", "")} for n, t in named.items()]
+    nw = worker(NCCLWeightReceiver)
+    out = {}
+    th = threading.Thread(target=lambda: (nw.init_weight_group("127.0.0.1", 29795, 2, 1, "gloo"), out.update(nw.receive_weights(header))))
+    th.start()
+    sender = NCCLWeightReceiver()
+    sender.init_weight_group("127.0.0.1", 29795, 2, 0, "gloo")
+    for t in named.values():
+        sender._weight_group.broadcast([t.clone()], _bcast_opts(0)).wait()
+    th.join(timeout=60)
+    assert out == {"tensors": 2} and all(torch.equal(nw.model_runner.model.got[n], t) for n, t in named.items())
+    # handles: any (rebuild function, args) pair; on a GPU these are CUDA IPC handles
+    cw = worker(ColocateWeightReceiver)
+    payload = {"version": 7, "handles": {n: ((lambda x: x), (t,)) for n, t in named.items()}}
+    assert cw.receive_ipc_handles(payload) == {"tensors": 2, "version": 7} and len(cw.model_runner.model.got) == 2
