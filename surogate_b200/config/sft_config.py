@@ -176,6 +176,8 @@ class SFTConfig:
     ep_size: int = 1
     ep_load_balance_threshold: float = 1.3
     ep_plan_refresh_interval: int = 16
+    ep_spill_threshold: float = 0.0
+    ep_spill_min_rows: int = 64
     async_optimizer: Optional[str] = None                   # with cpu_training: overlap | inline (host update one step behind, overlapped with compute)
     trainable_param_substrings: Optional[List[str]] = None  # full fine-tuning of a subset: names containing one of these train
     gradient_mask_mode: Optional[str] = None                # allow_substrings | mlp_growth_new_half
@@ -322,7 +324,8 @@ class SFTConfig:
             recompute=self.recompute, grad_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.gradient_dtype or "", "bf16"),
             master_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.master_dtype or "", None),
             lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, ep_load_balance_threshold=self.ep_load_balance_threshold,
-            ep_plan_refresh_interval=self.ep_plan_refresh_interval, lora=self.lora_dict(),
+            ep_plan_refresh_interval=self.ep_plan_refresh_interval, ep_spill_threshold=self.ep_spill_threshold, ep_spill_min_rows=self.ep_spill_min_rows,
+            lora=self.lora_dict(),
             async_optimizer=self.async_optimizer, trainable_param_substrings=self.trainable_param_substrings, gradient_mask_mode=self.gradient_mask_mode,
             fp8_amax_history=self.fp8_amax_history, skip_quant_first_layers=self.skip_quant_first_layers,
             skip_quant_last_layers=self.skip_quant_last_layers, offload_optimizer=self.offload_optimizer and not self.cpu_training,

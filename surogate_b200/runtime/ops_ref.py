@@ -719,6 +719,8 @@ class RefOps:
     def moe_grouped_gemm(self, ctx, op, x, w, plan):
         y = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
         w = ctx.local_experts(w)
+        if getattr(plan, "send_idx", None) is not None:     # least-loaded step: foreign expert slots, their weights shipped by the owners
+            w = ctx.ep.extend_weights(ctx, op.attrs.get("role", ""), w, plan)
         for e, s, t in self._expert_ranges(plan):
             y[s:t] = x[s:t] @ w[e].to(x.dtype).t()
         if ctx.lora is not None:
@@ -733,10 +735,22 @@ class RefOps:
             tgt = ctx.local_experts(tgt)
             if not acc:
                 tgt.zero_()
+        spilled = getattr(plan, "send_idx", None) is not None
+        if spilled:
+            role = op.attrs.get("role", "")
+            n_native = wl.shape[0]
+            wl = ctx.ep.extend_weights(ctx, role, wl, plan)
+            d_foreign = [torch.zeros(wl.shape[1:], dtype=torch.float32, device=x.device) for _ in range(wl.shape[0] - n_native)]
         for e, s, t in self._expert_ranges(plan):
             dx[s:t] = dy[s:t] @ wl[e].to(dy.dtype)
             if tgt is not None:
-                tgt[e] += (dy[s:t].t() @ x[s:t]).to(tgt.dtype)
+                if spilled and e >= n_native:
+                    d_foreign[e - n_native] += (dy[s:t].t() @ x[s:t]).float()
+                else:
+                    tgt[e] += (dy[s:t].t() @ x[s:t]).to(tgt.dtype)
+        if spilled and tgt is not None:   # the helpers' share of every expert's weight gradient returns to the expert's owner
+            for e_local, gsum in ctx.ep.return_weight_grads(ctx, role, d_foreign, plan, torch.zeros((1,) + tuple(wl.shape[1:]), dtype=torch.float32, device=x.device)):
+                tgt[e_local] += gsum.to(tgt.dtype)
         if ctx.lora is not None:
             extra = ctx.lora.backward_grouped(ctx, op, dy, x, plan)
             if extra is not None:

@@ -57,6 +57,8 @@ class TrainerConfig:
     ep_size: int = 1
     ep_capacity_factor: float = 1.5
     ep_load_balance_threshold: float = 1.3   # re-place experts when a layer's busiest rank exceeds this multiple of the mean load
+    ep_spill_threshold: float = 0.0          # > 0 (PyTorch backend): per step, row ranges of overloaded experts go to helper ranks above this imbalance
+    ep_spill_min_rows: int = 64              # smallest chunk worth shipping an expert's weights for
     trainable_param_substrings: Optional[List[str]] = None  # partial-update runs: only parameters whose name contains one of these train
     gradient_mask_mode: Optional[str] = None  # allow_substrings | mlp_growth_new_half (None: the SUROGATE_GRADIENT_MASK_MODE variable)
     ep_plan_refresh_interval: int = 16       # steps between placement refreshes (0 = never)
@@ -174,7 +176,8 @@ class Trainer:
             else:                              # PyTorch backend (CPU ranks over gloo included): the library all-to-all
                 from ..parallel.ep_ref import AllToAllExpertParallel
 
-                self.ep = AllToAllExpertParallel(getattr(group_comm, "base", group_comm), cfg.ep_size, self.device)
+                self.ep = AllToAllExpertParallel(getattr(group_comm, "base", group_comm), cfg.ep_size, self.device, spill_threshold=cfg.ep_spill_threshold,
+                                                 spill_min_rows=cfg.ep_spill_min_rows)
         self.executor = Executor(self.cm, self.store, self.backend, recipe=self.recipe,
                                  options=ExecOptions(recompute=cfg.recompute, act_dtype=pd, lmhead_drop_ignored_rows=cfg.lmhead_drop_ignored_rows,
                                                      offload_saved=cfg.offload_saved_tensors, time_breakdown=cfg.time_breakdown), device=self.device, ep=self.ep, lora=self.lora)

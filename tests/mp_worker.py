@@ -32,6 +32,7 @@ def main():
                         collectives=a.get("collectives", "auto"), keep_gathered=a.get("keep_gathered", True), ep_size=a.get("ep", 1),
                         lora=a.get("lora"), offload_master=a.get("offload_master", False), offload_optimizer=a.get("offload_optimizer", False),
                         cpu_training=a.get("cpu_training", False), ep_capacity_factor=a.get("ep_capacity_factor", 1.5),
+                        ep_spill_threshold=a.get("ep_spill", 0.0), ep_spill_min_rows=a.get("ep_spill_min_rows", 64),
                         qlora=a.get("qlora"), qlora_experts=a.get("qlora_experts", True), qlora_offload_experts=a.get("qlora_offload_experts", False),
                         use_cuda_graphs=a.get("graphs", False), ep_plan_refresh_interval=a.get("ep_refresh", 16), ep_load_balance_threshold=a.get("ep_threshold", 1.3))
     pp = a.get("pp", False)
@@ -99,7 +100,7 @@ def main():
                                       "fp8_gather": bool(tr.store.fp8_gather), "fp8_shards": bool(getattr(tr.store, "fp8_arena", None) is not None), "graph_replays": getattr(tr, "graph_replays", 0), "h2d_weight_bytes": int(tr.store.h2d_bytes),
                                       "stage_slots": len(tr.store.stage_slots),
                                       "ep_dropped": tr.ep.dropped_rows() if tr.ep is not None else 0, "fp8_dispatches": int(getattr(tr.ep, "fp8_dispatches", 0)) if tr.ep is not None else 0,
-                                      "ep_moves": tr.ep.moves_done if tr.ep is not None else 0,
+                                      "ep_moves": tr.ep.moves_done if tr.ep is not None else 0, "ep_spilled_layers": int(getattr(tr.ep, "spilled_layers", 0)) if tr.ep is not None else 0,
                                       "ep_imbalance": tr.ep.imbalance() if tr.ep is not None else 1.0, **extra}), flush=True)
     if info.world > 1:
         import torch.distributed as dist

@@ -157,3 +157,18 @@ def test_qlora_on_an_expert_parallel_model_keeps_frozen_experts_quantised():
     assert q["exported_expert_shape"][0] == 4                      # all four experts come back from the two ranks
     for a, b in zip(q["losses"], full["losses"]):
         assert abs(a - b) < 2e-2 * abs(b), (q["losses"], full["losses"])
+
+
+@pytest.mark.parametrize("nproc,port", [(2, 29693), (4, 29694)])
+def test_least_loaded_spilling_keeps_the_math(nproc, port):
+    """Per-step least-loaded balancing on the portable expert-parallel path: with a spill threshold of 1.0 every MoE layer of every step
+    cuts the busiest experts' rows into chunks for helper ranks (weights shipped forward, weight gradients returned in backward);
+    losses and gradient norms still equal the single-process run."""
+    model = dict(MOE_TINY, num_experts=8)
+    one = run_worker(1, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0))
+    r = run_worker(nproc, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0, ep=nproc, ep_spill=1.0, ep_spill_min_rows=1), port=port)
+    assert r["ep_spilled_layers"] >= 3, r["ep_spilled_layers"]
+    for a, b in zip(r["losses"], one["losses"]):
+        assert abs(a - b) < 3e-4 * abs(b), (r["losses"], one["losses"])
+    for a, b in zip(r["norms"], one["norms"]):
+        assert abs(a - b) < 2e-3 * abs(b), (r["norms"], one["norms"])
