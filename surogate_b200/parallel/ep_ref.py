@@ -205,6 +205,7 @@ class AllToAllExpertParallel:
         for pos, i in enumerate(by_owner):
             ordered[i] = got[pos]
         w_ext = torch.cat([w_local] + [x.unsqueeze(0) for x in ordered]) if ordered else w_local
+        assert w_ext.shape[0] == int(plan.counts.numel()), (role, tuple(w_ext.shape), int(plan.counts.numel()), plan.foreign, me, El)
         plan.w_ext[role] = w_ext
         return w_ext
 

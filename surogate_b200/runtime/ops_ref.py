@@ -763,7 +763,8 @@ class RefOps:
         no host sync, and padding rows between experts (kernel plans pad each expert's range) are marked invalid.
         Plans with a ``counts`` tensor keep [E + 1] range starts in ``offsets``; expert-parallel receive plans keep
         [El + 1 starts, overflow, El real counts] in one tensor."""
-        p = getattr(plan, "local", None) or plan
+        # an expert-parallel receive plan describes the rows as they lie on the experts' owner; its ``local`` is the sender's plan
+        p = plan if hasattr(plan, "recv_splits") else (getattr(plan, "local", None) or plan)
         off = p.offsets.to(device=device, dtype=torch.int64)
         counts = getattr(p, "counts", None)
         if counts is not None:
@@ -780,6 +781,8 @@ class RefOps:
     def moe_expert_bias_add(self, ctx, op, y, bias, plan):
         eid, valid = self._row_experts(plan, y.shape[0], y.device)
         b = ctx.local_experts(bias)
+        if getattr(plan, "send_idx", None) is not None:     # least-loaded step: the foreign slots' biases come from their owners
+            b = ctx.ep.extend_weights(ctx, "bias:" + str(op.outputs[0]), b, plan)
         return (y + (b.to(y.dtype)[eid] * valid.unsqueeze(-1)),)
 
     def moe_expert_bias_add_backward(self, ctx, op, dy, bias, plan):
@@ -787,7 +790,15 @@ class RefOps:
         tgt, acc = ctx.grad_target(op.outputs[1])
         if tgt is not None:
             tgt = ctx.local_experts(tgt)
-            g = torch.zeros(tgt.shape, dtype=torch.float32, device=dy.device).index_add_(0, eid, dy.float() * valid.unsqueeze(-1))
+            spilled = getattr(plan, "send_idx", None) is not None
+            slots = int(plan.counts.numel()) if spilled else tgt.shape[0]
+            g = torch.zeros((slots,) + tuple(tgt.shape[1:]), dtype=torch.float32, device=dy.device).index_add_(0, eid, dy.float() * valid.unsqueeze(-1))
+            if spilled:     # the foreign slots' bias gradients return to the experts' owners
+                n = tgt.shape[0]
+                back = ctx.ep.return_weight_grads(ctx, "bias", [g[i] for i in range(n, slots)], plan, g[:1])
+                g = g[:n].clone()
+                for e_local, part in back:
+                    g[e_local] += part
             if acc:
                 tgt.add_(g.to(tgt.dtype))
             else:

@@ -172,3 +172,19 @@ def test_least_loaded_spilling_keeps_the_math(nproc, port):
         assert abs(a - b) < 3e-4 * abs(b), (r["losses"], one["losses"])
     for a, b in zip(r["norms"], one["norms"]):
         assert abs(a - b) < 2e-3 * abs(b), (r["norms"], one["norms"])
+
+
+def test_biased_experts_under_expert_parallelism_with_and_without_spilling():
+    """Experts with per-expert biases (GPT-OSS) on the portable expert-parallel path: the bias of a row is looked up in the RECEIVE
+    plan's slot order, and on least-loaded steps the foreign slots' biases (and their gradients) travel like the weights."""
+    model = dict(architecture="GptOssForCausalLM", vocab_size=256, d_model=64, n_layers=2, num_query_heads=2, num_kv_heads=1, head_size=32, d_ff=32,
+                 num_experts=4, num_experts_per_tok=2, sliding_window=16, max_seq=128)
+    one = run_worker(1, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0))
+    plain = run_worker(2, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0, ep=2), port=29698)
+    spill = run_worker(2, dict(device="cpu", model=model, global_batch=4, seq_len=32, steps=3, zero=0, ep=2, ep_spill=1.0, ep_spill_min_rows=1), port=29697)
+    assert spill["ep_spilled_layers"] >= 3 and plain["ep_spilled_layers"] == 0
+    for r in (plain, spill):
+        for a, b in zip(r["losses"], one["losses"]):
+            assert abs(a - b) < 3e-4 * abs(b), (r["losses"], one["losses"])
+        for a, b in zip(r["norms"], one["norms"]):
+            assert abs(a - b) < 2e-3 * abs(b), (r["norms"], one["norms"])
