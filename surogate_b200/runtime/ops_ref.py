@@ -765,7 +765,8 @@ class RefOps:
         [El + 1 starts, overflow, El real counts] in one tensor."""
         # an expert-parallel receive plan describes the rows as they lie on the experts' owner; its ``local`` is the sender's plan
         p = plan if hasattr(plan, "recv_splits") else (getattr(plan, "local", None) or plan)
-        off = p.offsets.to(device=device, dtype=torch.int64)
+        layout = getattr(p, "layout", None)     # kernel expert-parallel plans: the full [El + 1 starts, overflow, El real counts] tensor
+        off = (layout if (layout is not None and getattr(p, "counts", None) is None) else p.offsets).to(device=device, dtype=torch.int64)
         counts = getattr(p, "counts", None)
         if counts is not None:
             E = counts.numel()

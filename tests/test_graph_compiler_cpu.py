@@ -211,3 +211,24 @@ def test_native_buffer_planner_equals_the_python_statement_and_validates_plans()
     # two tensors alive together at the same offset are reported
     assert "alias" in h.validate_buffer_plan([512, 512], [0, 1], [5, 3], [0, 256], 1024)
     assert "aligned" in h.validate_buffer_plan([512], [0], [1], [8], 1024) and "outside" in h.validate_buffer_plan([512], [0], [1], [768], 1024)
+
+
+def test_row_to_expert_lookup_for_the_three_plan_kinds():
+    """Which expert slot a permuted row belongs to, and whether it is a real row: local plans ([E + 1] starts + counts), portable
+    expert-parallel receive plans (their own offsets, not the sender's), kernel expert-parallel plans (padded layout tensor)."""
+    from types import SimpleNamespace
+
+    from surogate_b200.runtime.ops_ref import RefOps
+
+    local = SimpleNamespace(offsets=torch.tensor([0, 2, 2, 5], dtype=torch.int32), counts=torch.tensor([2, 0, 3], dtype=torch.int32), local=None)
+    eid, valid = RefOps._row_experts(local, 5, torch.device("cpu"))
+    assert eid.tolist() == [0, 0, 2, 2, 2] and valid.all()
+    sender = SimpleNamespace(offsets=torch.tensor([0, 1, 2, 3, 4], dtype=torch.int32), counts=torch.tensor([1, 1, 1, 1], dtype=torch.int32), local=None)
+    recv = SimpleNamespace(offsets=torch.tensor([0, 3, 4], dtype=torch.int32), counts=torch.tensor([3, 1], dtype=torch.int32), local=sender, recv_splits=[2, 2])
+    eid, valid = RefOps._row_experts(recv, 4, torch.device("cpu"))
+    assert eid.tolist() == [0, 0, 0, 1] and valid.all()
+    # kernel plan: 2 local experts, padded starts 0 / 128 / 256, real rows 3 and 5: rows 3..127 and 133..255 are padding
+    layout = torch.tensor([0, 128, 256, 0, 3, 5], dtype=torch.int32)
+    kernel = SimpleNamespace(offsets=layout[:3], layout=layout, local=None)
+    eid, valid = RefOps._row_experts(kernel, 256, torch.device("cpu"))
+    assert eid[:128].eq(0).all() and eid[128:].eq(1).all() and valid.nonzero().flatten().tolist() == [0, 1, 2, 128, 129, 130, 131, 132]
