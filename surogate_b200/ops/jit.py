@@ -28,7 +28,7 @@ import subprocess
 import tempfile
 import threading
 from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Sequence, Tuple
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo"]

@@ -1,9 +1,6 @@
 """Expert re-placement moves (weights + optimizer state of experts changing owner) as one all-to-all over four CPU ranks."""
 import os
-import sys
-import tempfile
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

@@ -4,9 +4,8 @@ import pytest
 import torch
 
 from surogate_b200.dsl.compiler import compile_model, model_from_hf_config
-from surogate_b200.dsl.graph_compiler import (FUSION_RULES, annotate_consumers, apply_fusion_rules, bake_program, plan_buffers, plan_model,
-                                              register_fusion_rule)
-from surogate_b200.dsl.ir import Graph, OpNode, ParamSpec
+from surogate_b200.dsl.graph_compiler import FUSION_RULES, apply_fusion_rules, bake_program, plan_buffers, plan_model, register_fusion_rule
+from surogate_b200.dsl.ir import Graph, ParamSpec
 
 QWEN = dict(model_type="qwen3", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
             vocab_size=256, max_position_embeddings=128, rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=False)

@@ -1,7 +1,4 @@
 """Turn-resolved statistics and exploration noise of published weights."""
-import json
-import os
-
 import numpy as np
 import torch
 from safetensors.torch import load_file, save_file

@@ -3,12 +3,11 @@ import json
 import os
 
 import numpy as np
-import pytest
 import torch
 from safetensors.torch import save_file
 
 from surogate_b200.io.hf_checkpoint import LazyCheckpoint
-from surogate_b200.io.prequant import E2M1, DequantizingCheckpoint, dequant_mxfp4, wrap_if_quantized
+from surogate_b200.io.prequant import E2M1, DequantizingCheckpoint, wrap_if_quantized
 
 
 def _fp4_codes(x):
