@@ -64,7 +64,32 @@ class FeedState:
             self.last_update = time.time()
         return n
 
+    @staticmethod
+    def normalise(rec: Dict[str, Any]) -> Dict[str, Any]:
+        """A feed record in the dashboard schema (``train/loss``, ``type: gpu`` ...) as the ``{"log": kind, ...}`` form
+        ``consume`` reads; records already in that form pass through."""
+        if "log" in rec:
+            return rec
+        kind = rec.get("type")
+        if kind == "config":
+            return {"log": "options", "config": {k: v for k, v in rec.items() if k not in ("type", "ts")}}
+        if kind in ("gpu", "moe"):
+            out = {"log": kind, **{k: v for k, v in rec.items() if k != "type"}}
+            if kind == "gpu":
+                for ours, theirs in (("gpu_util", "gpu_utilization"), ("power_w", "power"), ("temperature_c", "temperature"), ("index", "gpu_id")):
+                    if ours not in out and theirs in out:
+                        out[ours] = out[theirs]
+            return out
+        if kind is None and "step" in rec:
+            if any(k.startswith("eval/") for k in rec):
+                return {"log": "eval", "step": rec["step"], "loss": rec.get("eval/loss", float("nan"))}
+            return {"log": "step", "step": rec["step"], "loss": rec.get("train/loss"), "lr": rec.get("train/lr"),
+                    "norm": rec.get("train/norm", rec.get("train/grad_norm")), "tps": rec.get("train/tokens_per_second"),
+                    "max_steps": rec.get("max_steps"), "phase": rec.get("train/phase", rec.get("phase"))}
+        return rec
+
     def consume(self, rec: Dict[str, Any]) -> None:
+        rec = self.normalise(rec)
         kind = rec.get("log")
         if kind == "step":
             self.steps.append(int(rec.get("step", len(self.steps) + 1)))

@@ -37,8 +37,13 @@ class JsonlReporter(Reporter):
         self.f = open(path, "a")
 
     def log(self, step: int, metrics: Dict[str, Any]) -> None:
-        self.f.write(json.dumps({"time": time.time(), "run": self.run, "step": step, **metrics}, default=str) + "\n")
-        self.f.flush()
+        from .logging import feed_record
+
+        rec = {"time": time.time(), "run": self.run, "step": step, **metrics}
+        rec = feed_record(rec) if "log" in rec else rec  # log records go out in the dashboard's schema, anything else as it is
+        if rec is not None:
+            self.f.write(json.dumps(rec, default=str) + "\n")
+            self.f.flush()
 
     def log_config(self, config: Dict[str, Any]) -> None:
         self.log(0, {"log": "options", "config": config})

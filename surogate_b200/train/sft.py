@@ -24,7 +24,7 @@ from ..io.checkpoint import clean_old_checkpoints, find_latest_checkpoint
 from ..parallel.dist import TorchComm, init_distributed
 from ..runtime.trainer import Trainer
 from ..utils.sol import speed_of_light_fraction, transformer_flops_per_token
-from .logging import TrainingRunLogger
+from .logging import TrainingRunLogger, resolve_metrics_path
 from .lr_schedule import LRSchedule
 from .monitors import EarlyStopping, GradientTracker, LossGuard, MoEMonitor, PhaseDetector, TrainingAdvisor
 
@@ -122,7 +122,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
         trainer = PipelineTrainer(tcfg, device=device, stage_layers=int(cfg.dispatch_pp.get("stage_layers", cfg.dispatch_pp.get("stage_blocks", 0)) or 0))
     else:
         trainer = Trainer(tcfg, device=device, comm=comm)
-    logger = TrainingRunLogger(cfg.log_file, cfg.surogate_metrics_path if "surogate" in cfg.report_to else None, is_main=info.is_main)
+    logger = TrainingRunLogger(cfg.log_file, resolve_metrics_path(cfg.surogate_metrics_path) if "surogate" in cfg.report_to else None, is_main=info.is_main)
     logger.log_record("options", config=json.loads(cfg.to_json()))
 
     B, GA, T = cfg.per_device_train_batch_size, cfg.gradient_accumulation_steps, cfg.sequence_len

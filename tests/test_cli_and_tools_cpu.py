@@ -328,3 +328,43 @@ def test_config_values_written_as_text_reach_their_declared_type(tmp_path, monke
     p.write_text("model: m\nlearning_rate: fast\n")
     with pytest.raises(ValueError, match="learning_rate"):
         load_config(SFTConfig, str(p))
+
+
+def test_metrics_feed_uses_the_dashboard_schema_and_the_monitor_reads_it(tmp_path, monkeypatch):
+    """The feed's records carry the dashboard's field names (``train/loss``, ``type: gpu`` ...), the monitor reads them, and the
+    feed path falls back to the environment variable a launcher sets."""
+    from surogate_b200.cli import monitor
+    from surogate_b200.train.logging import TrainingRunLogger, feed_record, resolve_metrics_path
+
+    feed = tmp_path / "feed.jsonl"
+    monkeypatch.setenv("SUROGATE_METRICS_PATH", str(feed))
+    assert resolve_metrics_path("/tmp/surogate_metrics.jsonl") == str(feed)
+    assert resolve_metrics_path(str(tmp_path / "explicit.jsonl")) == str(tmp_path / "explicit.jsonl")
+
+    import io
+
+    lg = TrainingRunLogger(None, resolve_metrics_path(None), stream=io.StringIO())
+    lg.log_record("options", config={"run_name": "r1", "model": "Qwen/Qwen3-0.6B", "recipe": "fp8-hybrid", "max_steps": 10, "nested": {"a": 1}})
+    for i in range(3):
+        lg.log_step(i + 1, 10, 0.1 * i, 3.0 - i, 1.5, 1e-3, 8192, 100.0, phase="converging")
+    lg.log_eval(3, 2.5)
+    lg.log_record("gpu", step=3, name="B200", temperature_c=55, power_w=700.0, gpu_util=97, mem_util=40, mem_used=2**30, mem_total=2**31)
+    lg.log_record("moe", step=3, imbalance=1.5, aux_loss=0.01)
+    lg.message("not part of the feed")
+    lg.close()
+    recs = [json.loads(l) for l in open(feed)]
+    assert len(recs) == 7
+    cfg, s1, ev, gpu = recs[0], recs[1], recs[4], recs[5]
+    assert cfg["type"] == "config" and cfg["model"] == "Qwen/Qwen3-0.6B" and cfg["recipe"] == "fp8-hybrid" and "nested" not in cfg
+    assert "type" not in s1 and s1["step"] == 1 and s1["train/loss"] == 3.0 and s1["train/norm"] == 1.5 and s1["train/lr"] == 1e-3
+    assert abs(s1["train/tokens_per_second"] - 81920.0) < 1e-6 and s1["train/phase"] == "converging" and "ts" in s1
+    assert ev["eval/loss"] == 2.5 and "train/loss" not in ev
+    assert gpu["type"] == "gpu" and gpu["gpu_id"] == 0 and gpu["temperature"] == 55 and gpu["power"] == 700.0 and gpu["gpu_utilization"] == 97
+    assert feed_record({"log": "message", "text": "x"}) is None
+
+    st = monitor.FeedState(str(feed))
+    assert st.poll() == 7
+    assert st.steps == [1, 2, 3] and st.series["loss"] == [3.0, 2.0, 1.0] and st.max_steps == 10 and st.run_name == "r1"
+    assert st.evals == [(3, 2.5)] and st.gpu["gpu_util"] == 97 and st.moe["imbalance"] == 1.5
+    frame = monitor.render(st, width=100)
+    assert "step 3/10" in frame and "MoE" in frame and "gpu0" in frame
