@@ -32,6 +32,7 @@ COMMAND_MAPPING: Dict[str, str] = {
     "info": "surogate_b200.cli.info",
     "chat": "surogate_b200.cli.chat",
     "monitor": "surogate_b200.cli.monitor",
+    "launch": "surogate_b200.cli.launch",
     "vf-init": "surogate_b200.cli.vf",
     "vf-eval": "surogate_b200.cli.vf",
 }

@@ -6,7 +6,7 @@ layout of panels: loss curve, step progress, throughput, GPUs (from the feed, or
 ``--once`` renders a single frame (used by tests and for piping into a file); ``launch`` starts a run with the ``surogate``
 command, locally or over SSH, and then monitors it.
 
-Parity: jackalope/ (terminal dashboard that tails the same feed; its HuggingFace browser and cloud launchers are not rebuilt).
+Parity: jackalope/ (terminal dashboard that tails the same feed; its launch back ends are ``surogate_b200/launch`` behind ``surogate launch``).
 """
 from __future__ import annotations
 
