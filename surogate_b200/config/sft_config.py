@@ -68,12 +68,39 @@ class DistributedConfig:
 
 @dataclass
 class DistillationConfig:
-    enabled: bool = False
-    teacher: Optional[str] = None
-    top_k: int = 64
+    """Offline top-K distillation: training mixes ``kd_weight * tau^2 * KL(teacher || student)`` into the loss from ``.kd`` sidecars
+    written by ``surogate distill-capture``.  A ``distillation:`` section switches it on unless it says ``enabled: false``.
+    ``teacher_model`` / ``kd_dir`` are the other spellings of ``teacher`` / ``sidecar_dir``.  Keys marked capture are read by the
+    capture command only.  Parity: surogate/core/config/sft_config.py:48-90."""
+    enabled: Optional[bool] = None
+    teacher: Optional[str] = None            # capture: model id / directory, or the served model's name with teacher_api_base
+    teacher_model: Optional[str] = None
+    top_k: int = 32
     temperature: float = 1.0
     kd_weight: float = 0.5
-    sidecar_dir: Optional[str] = None
+    ce_weight: Optional[float] = None        # default 1 - kd_weight
+    teacher_batch_size: int = 4              # capture: rows per teacher forward
+    sidecar_dir: Optional[str] = None        # sidecars live here instead of next to the token shards
+    kd_dir: Optional[str] = None
+    teacher_api_base: Optional[str] = None   # capture: OpenAI-compatible base URL of a served teacher (prompt_logprobs)
+    teacher_api_key_var: Optional[str] = "VLLM_API_KEY"
+    teacher_api_concurrency: int = 8
+    teacher_api_timeout: int = 1200
+
+    def __post_init__(self):
+        self.teacher = self.teacher or self.teacher_model
+        self.sidecar_dir = self.sidecar_dir or self.kd_dir
+        if self.enabled is None:
+            self.enabled = True
+        if not 1 <= int(self.top_k) <= 1024:
+            raise ValueError("[E115] distillation.top_k must be in 1..1024")
+        if not float(self.temperature) > 0:
+            raise ValueError("[E115] distillation.temperature must be > 0")
+        if self.ce_weight is None:
+            self.ce_weight = 1.0 - float(self.kd_weight)
+
+    def api_key(self) -> str:
+        return (os.environ.get(self.teacher_api_key_var) if self.teacher_api_key_var else None) or "EMPTY"
 
 
 @dataclass
@@ -175,6 +202,7 @@ class SFTConfig:
     memcpy_send_recv: bool = False
     ep_size: int = 1
     ep_load_balance_threshold: float = 1.3
+    ep_capacity_factor: float = 1.5  # receive-buffer rows per rank relative to a perfectly balanced step; copies beyond it are dropped and counted
     ep_plan_refresh_interval: int = 16
     ep_spill_threshold: float = 0.0
     ep_spill_min_rows: int = 64
@@ -323,7 +351,7 @@ class SFTConfig:
             eps=self.adamw_epsilon, weight_decay=self.weight_decay, max_grad_norm=self.max_grad_norm, zero_level=self.zero_level,
             recompute=self.recompute, grad_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.gradient_dtype or "", "bf16"),
             master_dtype={"fp32": "fp32", "float32": "fp32"}.get(self.master_dtype or "", None),
-            lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, ep_load_balance_threshold=self.ep_load_balance_threshold,
+            lmhead_chunk_rows=self.auto_lmhead_rows(tokens, vocab), ep_size=self.ep_size, ep_load_balance_threshold=self.ep_load_balance_threshold, ep_capacity_factor=self.ep_capacity_factor,
             ep_plan_refresh_interval=self.ep_plan_refresh_interval, ep_spill_threshold=self.ep_spill_threshold, ep_spill_min_rows=self.ep_spill_min_rows,
             lora=self.lora_dict(),
             async_optimizer=self.async_optimizer, trainable_param_substrings=self.trainable_param_substrings, gradient_mask_mode=self.gradient_mask_mode,

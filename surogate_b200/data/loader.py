@@ -12,6 +12,7 @@ Parity: csrc/src/runtime/training/dataloader.{h,cpp} (DataLoader dataloader.h:39
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -170,8 +171,11 @@ class DataLoader:
 class DistillationFeed:
     """Teacher top-K log-probs (``.kd`` sidecars) for the rows a numpy-path ``DataLoader`` just served."""
 
-    def __init__(self, loader: "DataLoader"):
-        from ..distill.sidecar import SidecarReader, sidecar_path
+    def __init__(self, loader: "DataLoader", sidecar_dir: Optional[str] = None):
+        from ..distill.sidecar import SidecarReader, sidecar_path as _next_to_shard
+
+        def sidecar_path(f):
+            return os.path.join(sidecar_dir, os.path.basename(_next_to_shard(f))) if sidecar_dir else _next_to_shard(f)
 
         if loader._nat is not None:
             raise ValueError("distillation needs DataLoader(native=False): the sidecar rows follow the loader's row bookkeeping")

@@ -121,11 +121,17 @@ def capture_shard(shard: str, teacher: TeacherFn, seq_len: int, top_k: int, voca
     return w.path
 
 
-def capture(shards: Iterable[str], teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, resume: bool = True, **kw) -> List[str]:
+def capture(shards: Iterable[str], teacher: TeacherFn, seq_len: int, top_k: int, vocab: int, resume: bool = True, out_dir: Optional[str] = None,
+            **kw) -> List[str]:
+    """One sidecar per shard, next to it or (``out_dir``) under another directory with the same file name; with ``resume`` a
+    complete sidecar of the expected K and length is kept."""
     out = []
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
     for s in shards:
-        if resume and sidecar_complete(s, seq_len, top_k, kw.get("out_path")):
-            out.append(kw.get("out_path") or sidecar_path(s))
+        path = kw.get("out_path") or (os.path.join(out_dir, os.path.basename(sidecar_path(s))) if out_dir else None)
+        if resume and sidecar_complete(s, seq_len, top_k, path):
+            out.append(path or sidecar_path(s))
             continue
-        out.append(capture_shard(s, teacher, seq_len, top_k, vocab, **kw))
+        out.append(capture_shard(s, teacher, seq_len, top_k, vocab, **dict(kw, out_path=path)))
     return out

@@ -139,7 +139,7 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     if distill:
         from ..data.loader import DistillationFeed
 
-        kd_feed = DistillationFeed(loader)  # needs train-NNN.kd next to every shard (surogate distill-capture)
+        kd_feed = DistillationFeed(loader, distill.sidecar_dir)  # needs train-NNN.kd for every shard (surogate distill-capture)
     eval_loader = DataLoader(files["eval"], B, T, seed=cfg.eval_seed, rank=0 if pp else info.rank, world=1 if pp else info.world,
                              shuffle=False) if files.get("eval") else None
     steps_per_epoch = max(1, loader.steps_per_epoch())
@@ -250,7 +250,7 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
         kd = None
         if kd_feed is not None:
             ki, kl = kd_feed.batch()
-            kd = {"idx": ki, "logp": kl, "weight": distill.kd_weight, "ce_weight": 1.0 - distill.kd_weight}
+            kd = {"idx": ki, "logp": kl, "weight": distill.kd_weight, "ce_weight": distill.ce_weight}
         out = trainer.step(x, y, p if (cfg.sample_packing or cfg.train_vision) else None, lr=lr, kd=kd)
         ms = (time.perf_counter() - t0) * 1e3
         if cfg.debug_time_breakdown and getattr(trainer, "last_time_breakdown", None):

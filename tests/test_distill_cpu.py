@@ -1,7 +1,9 @@
 """KD sidecars: format round trip, capture from a teacher held by the Trainer, training with the distillation term."""
+import json
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from surogate_b200.data.loader import write_synthetic_tokens
@@ -124,3 +126,67 @@ def test_api_teacher_against_a_local_openai_style_server(tmp_path):
     i0, l0 = SidecarReader(kd_path).rows(0, 16)
     assert np.array_equal(i0[:15], want.indices.numpy()[:15]) and np.allclose(l0[:15], want.values.numpy()[:15], atol=5e-3)
     assert np.all(l0[15] == -30.0)          # nothing predicts past the last token of a row
+
+
+def test_distillation_section_spellings_and_sidecar_directory(tmp_path, monkeypatch):
+    """The ``distillation`` section accepts both spellings of its keys, is on when present, validates K and temperature; sidecars
+    captured into ``kd_dir`` are the ones a training run with the same section reads."""
+    from surogate_b200.config.sft_config import DistillationConfig, SFTConfig
+    from surogate_b200.distill.capture import capture
+    from surogate_b200.distill.sidecar import sidecar_path
+
+    d = DistillationConfig(teacher_model="T", kd_dir="/x", kd_weight=0.3)
+    assert d.enabled and d.teacher == "T" and d.sidecar_dir == "/x" and abs(d.ce_weight - 0.7) < 1e-12 and d.top_k == 32
+    assert DistillationConfig(kd_weight=0.5, ce_weight=1.0).ce_weight == 1.0 and not DistillationConfig(enabled=False).enabled
+    monkeypatch.setenv("MY_KEY", "secret")
+    assert DistillationConfig(teacher_api_key_var="MY_KEY").api_key() == "secret" and DistillationConfig(teacher_api_key_var="UNSET_VAR_X").api_key() == "EMPTY"
+    for bad in (dict(top_k=0), dict(top_k=2000), dict(temperature=0.0)):
+        with pytest.raises(ValueError, match="E115"):
+            DistillationConfig(**bad)
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=96, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64, tie_word_embeddings=True)
+    kd_dir = str(tmp_path / "kd")
+    base = dict(model=json.dumps(model), synthetic_data=True, sequence_len=16, per_device_train_batch_size=2, gradient_accumulation_steps=1, max_steps=2, lora=False,
+                optimizer="adamw", learning_rate=1e-2, save_steps=0, eval_steps=0, recipe="bf16", zero_level=0, from_scratch=True, output_dir=str(tmp_path / "run"),
+                distillation=dict(teacher_model="unused", top_k=4, kd_weight=1.0, kd_dir=kd_dir))
+    cfg = SFTConfig.from_dict(base)
+    assert cfg.distillation.enabled and cfg.distillation.sidecar_dir == kd_dir
+    from surogate_b200.train.sft import prepare_data, resolve_model_config, run_training
+
+    shards = prepare_data(cfg, resolve_model_config(cfg), rank=0)["train"]
+    teacher = _trainer(3)
+    out = capture(shards, native_teacher(teacher), 16, 4, 96, out_dir=kd_dir)
+    assert [os.path.dirname(p) for p in out] == [kd_dir] * len(shards) and not os.path.exists(sidecar_path(shards[0]))
+    assert capture(shards, None, 16, 4, 96, out_dir=kd_dir) == out  # complete sidecars are kept: no teacher is called
+    r = run_training(cfg)
+    assert r["steps"] == 2 and np.isfinite(r["final"]["loss"])
+
+
+def test_distill_capture_command_reads_the_config(tmp_path, monkeypatch, capsys):
+    """``surogate distill-capture config.yaml`` tokenises like the run will, takes teacher / K / directory from the section and
+    writes one sidecar per shard."""
+    import yaml
+
+    from surogate_b200.cli import distill as cli
+    from surogate_b200.distill import capture as cap
+
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=96, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64, tie_word_embeddings=True)
+    cfg = dict(model=json.dumps(model), synthetic_data=True, sequence_len=16, per_device_train_batch_size=2, output_dir=str(tmp_path / "run"), lora=False,
+               distillation=dict(teacher_model="my-teacher", top_k=4, temperature=2.0, teacher_batch_size=3, kd_dir=str(tmp_path / "kd")))
+    path = tmp_path / "cfg.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    seen = {}
+    teacher = _trainer(3)
+
+    def fake_hf_teacher(name, device):
+        seen.update(name=name, device=device)
+        return native_teacher(teacher)
+
+    monkeypatch.setattr(cap, "hf_teacher", fake_hf_teacher)
+    assert cli.main([str(path), "--device", "cpu"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["sidecars"]
+    assert seen == {"name": "my-teacher", "device": "cpu"} and out and all(p.startswith(str(tmp_path / "kd")) for p in out)
+    r = SidecarReader(out[0])
+    assert r.K == 4 and abs(r.temperature - 2.0) < 1e-6
+    with pytest.raises(SystemExit):
+        cli.main([])
