@@ -1,10 +1,17 @@
-"""``surogate grpo | grpo-orch | grpo-infer config.yaml``: the three processes of asynchronous GRPO.
+"""The GRPO commands.
 
-``grpo`` is the trainer (consumes rollout batches, publishes weights), ``grpo-orch`` the orchestrator (prompts -> rollouts
--> rewards -> batches), ``grpo-infer`` launches the rollout engine and keeps it on the newest published weights.
-``grpo --trainer-gpus 0,1`` pins the trainer's devices before CUDA is initialised (handled in cli/main.py).
+    surogate grpo          --train T.yaml --infer I.yaml --orch O.yaml --trainer-gpus 0,1 --vllm-gpus 2,3 [--judge-infer J.yaml --judge-gpus 4]
+    surogate grpo-colocate --train T.yaml --infer I.yaml --orch O.yaml [--gpus 0,1]
+    surogate grpo-train  T.yaml      surogate grpo-orch  O.yaml      surogate grpo-infer  I.yaml
 
-Parity: surogate/cli (grpo, grpo-orch, grpo-infer), surogate/grpo/{trainer,split,colocate}.py.
+``grpo`` runs trainer, rollout engine and orchestrator on disjoint GPU sets under one supervisor, ``grpo-colocate`` on shared
+GPUs; ``grpo-train`` is the trainer alone (consumes rollout batches, publishes weights), ``grpo-orch`` the orchestrator (prompts
+-> rollouts -> rewards -> batches), ``grpo-infer`` launches the rollout engine and keeps it on the newest published weights.
+``grpo`` and ``grpo-train`` are told apart by their arguments, so either name works for either form: with ``--train`` it is
+the supervised three-component run, with one positional config it is the trainer.  ``--trainer-gpus 0,1`` on the trainer pins
+its devices before CUDA is initialised (handled in cli/main.py).
+
+Parity: surogate/cli/{grpo,grpo_colocate,grpo_train,grpo_orch,grpo_infer}.py, surogate/grpo/{trainer,split,colocate}.py.
 """
 from __future__ import annotations
 
@@ -13,9 +20,15 @@ import json
 import os
 
 
+def is_supervised(argv) -> bool:
+    """True for the three-component form (``--train T.yaml ...``), False for the trainer's ``config.yaml`` form."""
+    return any(a == "--train" or a.startswith("--train=") for a in argv)
+
+
 def _run_all(argv, command: str) -> int:
-    """``grpo-train --train T.yaml --infer I.yaml --orch O.yaml --trainer-gpus 0-3 --vllm-gpus 4-7`` (disjoint GPU sets) and
+    """``grpo --train T.yaml --infer I.yaml --orch O.yaml --trainer-gpus 0-3 --vllm-gpus 4-7`` (disjoint GPU sets) and
     ``grpo-colocate --train T.yaml --infer I.yaml --orch O.yaml [--gpus 0-7]`` (shared GPUs): one supervisor, three components."""
+    split = command != "grpo-colocate"
     from ..grpo.runners import Supervisor, plan_colocate, plan_split
 
     p = argparse.ArgumentParser(prog=f"surogate {command}")
@@ -24,10 +37,10 @@ def _run_all(argv, command: str) -> int:
     p.add_argument("--orch", required=True)
     p.add_argument("--max-steps", type=int, default=None, dest="max_steps")
     p.add_argument("--dry-run", action="store_true", help="print the component commands and exit")
-    if command == "grpo-train":
+    if split:
         p.add_argument("--trainer-gpus", required=True)
         p.add_argument("--vllm-gpus", required=True)
-        p.add_argument("--judge-config", default=None)
+        p.add_argument("--judge-infer", "--judge-config", dest="judge_config", default=None, help="inference config of a judge engine started next to the rollout engine")
         p.add_argument("--judge-gpus", default=None)
     else:
         p.add_argument("--gpus", default=None)
@@ -37,7 +50,7 @@ def _run_all(argv, command: str) -> int:
 
     raw = read_yaml(a.infer)
     tp, dp = int(raw.get("tensor_parallel_size", 1)), int(raw.get("data_parallel_size", 1))
-    if command == "grpo-train":
+    if split:
         jtp = int(read_yaml(a.judge_config).get("tensor_parallel_size", 1)) if a.judge_config else 1
         comps = plan_split(a.train, a.infer, a.orch, a.trainer_gpus, a.vllm_gpus, tp, dp, a.judge_config, a.judge_gpus, jtp, max_steps=a.max_steps)
     else:
@@ -51,8 +64,10 @@ def _run_all(argv, command: str) -> int:
 
 
 def main(argv, command: str = "grpo") -> int:
-    if command in ("grpo-train", "grpo-colocate"):
+    if command == "grpo-colocate" or (command in ("grpo", "grpo-train") and is_supervised(argv)):
         return _run_all(argv, command)
+    if command == "grpo-train":
+        command = "grpo"
     p = argparse.ArgumentParser(prog=f"surogate {command}")
     p.add_argument("config")
     p.add_argument("--trainer-gpus", default=None)

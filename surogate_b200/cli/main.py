@@ -33,6 +33,7 @@ COMMAND_MAPPING: Dict[str, str] = {
     "chat": "surogate_b200.cli.chat",
     "monitor": "surogate_b200.cli.monitor",
     "launch": "surogate_b200.cli.launch",
+    "jackalope": "surogate_b200.cli.monitor",  # the dashboard's name in the reference
     "vf-init": "surogate_b200.cli.vf",
     "vf-eval": "surogate_b200.cli.vf",
 }
@@ -68,7 +69,7 @@ def cli_main(argv: Optional[List[str]] = None) -> int:
     if cmd not in COMMAND_MAPPING:
         print(f"unknown command '{cmd}' (known: {', '.join(sorted(COMMAND_MAPPING))})", file=sys.stderr)
         return 2
-    if cmd in ("grpo", "grpo-infer", "grpo-orch"):
+    if cmd in ("grpo", "grpo-train", "grpo-infer", "grpo-orch") and "--train" not in argv:  # the trainer alone; a supervised run masks per component
         mask_gpus_for_grpo(argv)
     if int(os.environ.get("RANK", "0")) == 0 and os.environ.get("SUROGATE_NO_BANNER") != "1":
         print_banner()

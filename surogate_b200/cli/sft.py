@@ -17,12 +17,23 @@ def build_parser(prog: str) -> argparse.ArgumentParser:
     p.add_argument("--model", default=None)
     p.add_argument("--recipe", default=None, help="override `recipe` (bf16 | fp8-hybrid | nvfp4)")
     p.add_argument("--synthetic-data", action="store_true", default=None, dest="synthetic_data")
+    p.add_argument("--hub_token", "--hub-token", dest="hub_token", default=None, help="HuggingFace token for private models and datasets")
     return p
+
+
+def take_hub_token(args) -> None:
+    """``--hub_token`` reaches the hub helpers through ``HF_TOKEN``; it is not a config key."""
+    token = getattr(args, "hub_token", None)
+    if token:
+        os.environ["HF_TOKEN"] = token
+    if hasattr(args, "hub_token"):
+        del args.hub_token
 
 
 def launch(args, command: str, entry) -> int:
     from ..config.loader import read_yaml
 
+    take_hub_token(args)
     overrides = {k: v for k, v in vars(args).items() if k != "config" and v is not None}
     gpus = overrides.get("gpus") or read_yaml(args.config).get("gpus", 1)
     if gpus > 1 and "RANK" not in os.environ:

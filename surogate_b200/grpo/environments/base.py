@@ -92,15 +92,32 @@ class MultiTurnEnv(Environment):
 
 
 # ---------------------------------------------------------------------------------------------- policies
-def openai_policy(base_url: str, model: str, temperature: float = 0.7, max_tokens: int = 1024, api_key: str = "EMPTY", timeout_s: float = 300.0) -> Policy:
-    """Chat-completions endpoint (vLLM, or any OpenAI-compatible server) as a policy."""
+def openai_policy(base_url: str, model: str, temperature: Optional[float] = 0.7, max_tokens: Optional[int] = 1024, api_key: str = "EMPTY",
+                  timeout_s: float = 300.0, headers: Optional[Dict[str, str]] = None, sampling_args: Optional[Dict[str, Any]] = None,
+                  max_retries: int = 0) -> Policy:
+    """Chat-completions endpoint (vLLM, or any OpenAI-compatible server) as a policy.  ``sampling_args`` are merged into the request
+    body (``top_p``, ``stop``, ...); ``temperature`` / ``max_tokens`` of None leave the server's defaults; a failed request is
+    retried ``max_retries`` times with back-off."""
+    import time
 
     def call(messages: Messages) -> str:
-        body = json.dumps({"model": model, "messages": messages, "temperature": temperature, "max_tokens": max_tokens}).encode()
-        req = urllib.request.Request(base_url.rstrip("/") + "/chat/completions", data=body,
-                                     headers={"Content-Type": "application/json", "Authorization": f"Bearer {api_key}"})
-        with urllib.request.urlopen(req, timeout=timeout_s) as r:
-            return json.loads(r.read())["choices"][0]["message"]["content"]
+        body: Dict[str, Any] = {"model": model, "messages": messages}
+        if temperature is not None:
+            body["temperature"] = temperature
+        if max_tokens is not None:
+            body["max_tokens"] = max_tokens
+        body.update(sampling_args or {})
+        req = urllib.request.Request(base_url.rstrip("/") + "/chat/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json", "Authorization": f"Bearer {api_key}", **(headers or {})})
+        for attempt in range(max_retries + 1):
+            try:
+                with urllib.request.urlopen(req, timeout=timeout_s) as r:
+                    return json.loads(r.read())["choices"][0]["message"]["content"] or ""
+            except Exception:  # noqa: BLE001 - connection reset, 5xx, malformed body: retried alike
+                if attempt == max_retries:
+                    raise
+                time.sleep(min(0.1 * 2.0 ** attempt, 5.0))
+        return ""
 
     return call
 
@@ -110,9 +127,9 @@ BUILTIN = {"markdown-table-qa": "surogate_b200.grpo.environments.markdown_table_
            "ruler-task": "surogate_b200.grpo.environments.ruler_task"}
 
 
-def load_environment(env_id: str, path: Optional[str] = None, **kwargs) -> Environment:
-    """Built-in id, or a module ``<path>/<env_id with _>/<env_id with _>.py`` (what ``vf-init`` scaffolds) exposing
-    ``load_environment(**kwargs)``."""
+def load_environment(env_id: str, path: Optional[str] = None, import_path: Optional[str] = None, **kwargs) -> Environment:
+    """Built-in id, a module ``<path>/<env_id with _>/<env_id with _>.py`` (what ``vf-init`` scaffolds), or (``import_path``: a
+    directory put in front of ``sys.path``) an importable package named after the id, each exposing ``load_environment(**kwargs)``."""
     key = env_id.replace("_", "-")
     if key in BUILTIN:
         return importlib.import_module(BUILTIN[key]).load_environment(**kwargs)
@@ -120,6 +137,12 @@ def load_environment(env_id: str, path: Optional[str] = None, **kwargs) -> Envir
     from importlib import util as importlib_util
 
     mod_name = env_id.replace("-", "_")
+    if import_path:
+        import sys
+
+        if import_path not in sys.path:
+            sys.path.insert(0, import_path)
+        return importlib.import_module(mod_name).load_environment(**kwargs)
     for cand in (os.path.join(path or "./environments", mod_name, mod_name + ".py"), os.path.join(path or "./environments", key, mod_name + ".py")):
         if os.path.exists(cand):
             spec = importlib_util.spec_from_file_location(mod_name, cand)
@@ -129,19 +152,35 @@ def load_environment(env_id: str, path: Optional[str] = None, **kwargs) -> Envir
     raise KeyError(f"unknown environment '{env_id}' (built in: {sorted(BUILTIN)}; looked under {path or './environments'})")
 
 
-def evaluate(env: Environment, policy: Policy, num_examples: int = 20, rollouts_per_example: int = 1, use_eval_split: bool = True) -> Dict[str, Any]:
+def evaluate(env: Environment, policy: Policy, num_examples: int = 20, rollouts_per_example: int = 1, use_eval_split: bool = True,
+             max_concurrent: int = 1, on_sample: Optional[Callable[[Dict[str, Any]], None]] = None) -> Dict[str, Any]:
+    """Roll the policy out on the first ``num_examples`` examples (``rollouts_per_example`` times each), at most
+    ``max_concurrent`` rollouts in flight; results keep the order of the examples whatever order they finish in."""
     data = (env.eval_dataset if (use_eval_split and env.eval_dataset) else env.dataset)[:num_examples]
     rewards: List[float] = []
     parts: Dict[str, List[float]] = {}
     samples = []
-    for ex in data:
-        for _ in range(rollouts_per_example):
-            state = env.rollout(policy, ex)
-            total, p = env.score(ex, state)
-            rewards.append(total)
-            for k, v in p.items():
-                parts.setdefault(k, []).append(v)
-            samples.append({"answer": ex.get("answer"), "completion": state["completion"], "reward": total, "turns": state.get("turns", 1)})
+    jobs = [ex for ex in data for _ in range(rollouts_per_example)]
+
+    def one(ex):
+        state = env.rollout(policy, ex)
+        total, p = env.score(ex, state)
+        return ex, state, total, p
+
+    if max_concurrent > 1 and len(jobs) > 1:
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=min(max_concurrent, len(jobs))) as pool:
+            results = list(pool.map(one, jobs))
+    else:
+        results = [one(ex) for ex in jobs]
+    for ex, state, total, p in results:
+        rewards.append(total)
+        for k, v in p.items():
+            parts.setdefault(k, []).append(v)
+        samples.append({"answer": ex.get("answer"), "completion": state["completion"], "reward": total, "turns": state.get("turns", 1)})
+        if on_sample is not None:
+            on_sample(samples[-1])
     return {"env": env.env_id, "n": len(rewards), "mean_reward": statistics.fmean(rewards) if rewards else 0.0,
             "std_reward": statistics.pstdev(rewards) if len(rewards) > 1 else 0.0, "metrics": {k: statistics.fmean(v) for k, v in parts.items()},
             "samples": samples}
