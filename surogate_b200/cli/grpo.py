@@ -18,6 +18,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 
 def is_supervised(argv) -> bool:
@@ -49,9 +50,10 @@ def _run_all(argv, command: str) -> int:
     from ..config.loader import read_yaml
 
     raw = read_yaml(a.infer)
-    tp, dp = int(raw.get("tensor_parallel_size", 1)), int(raw.get("data_parallel_size", 1))
+    tp, dp = int(raw.get("tp") or raw.get("tensor_parallel_size", 1)), int(raw.get("dp") or raw.get("data_parallel_size", 1))
     if split:
-        jtp = int(read_yaml(a.judge_config).get("tensor_parallel_size", 1)) if a.judge_config else 1
+        jraw = read_yaml(a.judge_config) if a.judge_config else {}
+        jtp = int(jraw.get("tp") or jraw.get("tensor_parallel_size", 1))
         comps = plan_split(a.train, a.infer, a.orch, a.trainer_gpus, a.vllm_gpus, tp, dp, a.judge_config, a.judge_gpus, jtp, max_steps=a.max_steps)
     else:
         comps = plan_colocate(a.train, a.infer, a.orch, a.gpus, max_steps=a.max_steps,
@@ -85,6 +87,11 @@ def main(argv, command: str = "grpo") -> int:
         return 0
     raw = read_yaml(a.config)
     if command == "grpo-orch":
+        from ..grpo.config_compat import flatten_orchestrator_config
+
+        raw, notes = flatten_orchestrator_config(raw)   # a config in the nested orchestrator schema becomes this package's flat keys
+        for n in notes:
+            print(f"[grpo-orch] {n}", file=sys.stderr)
         from ..data.tokenizer import Tokenizer
         from ..grpo.config import OrchestratorConfig
         from ..grpo.orchestrator import OpenAIClient, Orchestrator
@@ -97,7 +104,14 @@ def main(argv, command: str = "grpo") -> int:
         if a.max_steps:
             cfg.max_steps = a.max_steps
         b = FilesystemBroadcast(cfg.weight_dir)
-        orch = Orchestrator(cfg, Tokenizer.from_pretrained(cfg.model), OpenAIClient(cfg.base_url, cfg.model, cfg.request_timeout_s),
+        served = raw.get("served_model") or cfg.model            # the name requests carry (an adapter registered with the engine, or the model)
+        key = (os.environ.get(raw["api_key_var"]) if raw.get("api_key_var") else None) or "EMPTY"
+        headers = raw.get("headers") or {}
+
+        def client(url):
+            return OpenAIClient(url, served, cfg.request_timeout_s, api_key=key, headers=headers)
+
+        orch = Orchestrator(cfg, Tokenizer.from_pretrained(cfg.model), client(cfg.base_url),
                             make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="producer"),
                             lambda: (b.latest() or {"version": -1})["version"])
         orch.load_prompts()
@@ -107,11 +121,14 @@ def main(argv, command: str = "grpo") -> int:
 
             urls = raw.get("base_urls") or [cfg.base_url]
             if len(urls) > 1:
-                orch.client = [OpenAIClient(u, cfg.model, cfg.request_timeout_s) for u in urls]
+                orch.client = [client(u) for u in urls]
             tok = orch.tok
             acfg = async_config_from(cfg, raw, vocab_size=getattr(tok, "vocab_size", 32000), pad_token_id=max(0, getattr(tok, "pad_token_id", 0)))
+            eval_rows = None
+            if acfg.eval_every and orch.env is not None and getattr(orch.env, "eval_dataset", None):
+                eval_rows = [dict(ex, prompt=orch.env.initial_messages(ex)) for ex in orch.env.eval_dataset][:raw.get("eval_examples") or None]
             loop = AsyncOrchestrator(acfg, orch.prompts, make_generate_group(orch), orch.transport, lambda: (b.latest() or {"version": -1})["version"],
-                                     num_servers=len(urls))
+                                     num_servers=len(urls), eval_examples=eval_rows)
             hist = loop.run()
             print(json.dumps({"steps": len(hist), "last_reward_mean": hist[-1].get("reward/mean") if hist else None}))
             return 0
@@ -123,6 +140,9 @@ def main(argv, command: str = "grpo") -> int:
 
     from ..config.loader import coerce_fields
 
+    unknown = sorted(k for k in raw if k not in InferenceConfig.__dataclass_fields__)
+    if unknown:
+        print(f"[grpo-infer] keys without effect: {', '.join(unknown)}", file=sys.stderr)
     cfg = InferenceConfig(**coerce_fields(InferenceConfig, {k: v for k, v in raw.items() if k in InferenceConfig.__dataclass_fields__}))
     proc = launch_server(cfg)
     try:

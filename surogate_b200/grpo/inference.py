@@ -27,10 +27,33 @@ def server_command(cfg: InferenceConfig) -> List[str]:
         cfg.gpu_memory_utilization = min(cfg.gpu_memory_utilization, float(frac))
     cmd = [sys.executable, "-m", "vllm.entrypoints.openai.api_server", "--model", cfg.model, "--host", cfg.host, "--port", str(cfg.port),
            "--tensor-parallel-size", str(cfg.tensor_parallel_size), "--gpu-memory-utilization", str(cfg.gpu_memory_utilization)]
-    if cfg.max_model_len:
-        cmd += ["--max-model-len", str(cfg.max_model_len)]
+    if cfg.data_parallel_size > 1:
+        cmd += ["--data-parallel-size", str(cfg.data_parallel_size)]
+    if cfg.api_server_count > 1:
+        cmd += ["--api-server-count", str(cfg.api_server_count)]
+    if cfg.dtype and cfg.dtype != "auto":
+        cmd += ["--dtype", cfg.dtype]
+    # valued options: passed only when set, so the engine keeps its own defaults otherwise
+    for flag, value in (("--max-model-len", cfg.max_model_len), ("--max-num-seqs", cfg.max_num_seqs), ("--kv-cache-dtype", cfg.kv_cache_dtype),
+                        ("--attention-backend", cfg.attention_backend), ("--reasoning-parser", cfg.reasoning_parser), ("--all2all-backend", cfg.all2all_backend)):
+        if value:
+            cmd += [flag, str(value)]
+    if cfg.rope_scaling:
+        cmd += ["--rope-scaling", cfg.rope_scaling if isinstance(cfg.rope_scaling, str) else json.dumps(cfg.rope_scaling)]
+    if cfg.seed:
+        cmd += ["--seed", str(cfg.seed)]
+    for flag, on in (("--enforce-eager", cfg.enforce_eager), ("--trust-remote-code", cfg.trust_remote_code), ("--enable-expert-parallel", cfg.enable_expert_parallel),
+                     ("--enable-eplb", cfg.enable_eplb)):
+        if on:
+            cmd.append(flag)
+    if cfg.enable_auto_tool_choice:
+        cmd += ["--enable-auto-tool-choice"] + (["--tool-call-parser", cfg.tool_call_parser] if cfg.tool_call_parser else [])
+    if cfg.enable_prefix_caching is not None:
+        cmd.append("--enable-prefix-caching" if cfg.enable_prefix_caching else "--no-enable-prefix-caching")
     if cfg.enable_lora:
-        cmd += ["--enable-lora", "--max-lora-rank", str(cfg.max_lora_rank)]
+        cmd += ["--enable-lora", "--max-loras", str(cfg.max_loras), "--max-cpu-loras", str(cfg.max_cpu_loras)]
+        if cfg.max_lora_rank is not None:
+            cmd += ["--max-lora-rank", str(cfg.max_lora_rank)]
     from .vllm_worker import WORKER_EXTENSIONS
 
     ext = WORKER_EXTENSIONS.get(getattr(cfg, "weight_broadcast", "filesystem"))

@@ -14,7 +14,18 @@ number of masked tokens (token normalisation) or per-sequence lengths averaged o
 dL/dl = m_t / Z * ( -A r [unclipped] + kl_coef (1 - exp(l_ref - l)) ), and since l_t = -CE_t the kernel weight on the CE
 gradient of token t is -dL/dl.
 
-Parity: surogate/grpo/loss.py (numpy reference), csrc/src/kernels/fused_classifier.cu (grpo_custom_dloss_kernel).
+A second objective, ``type: ipo`` (probability-difference masking with a squared log-ratio penalty):
+
+    keep_t   = m_t and not (p - p_old > mask_high or p - p_old < -mask_low)      with p = exp(l), p_old = exp(l_old)
+    A'_t     = adv_tau A_t + teacher_tau (l_teacher - l)                           (the teacher term is detached)
+    loss     L = sum_t ( -keep_t A'_t r_t + kl_tau m_t (l - l_old)^2 ) / Z,       Z = number of completion tokens
+    dL/dl    = ( -keep_t A'_t min(r_t, ratio_clip) + 2 kl_tau m_t (l - l_old) ) / Z
+
+i.e. a token whose probability moved further than the mask thresholds since the rollout stops contributing to the policy term
+(but still feels the penalty that pulls it back), and the ratio that multiplies the gradient is capped at ``ratio_clip``.
+
+Parity: surogate/grpo/loss.py (numpy reference; its objective is the ``ipo`` one), csrc/src/kernels/fused_classifier.cu
+(grpo_custom_dloss_kernel).
 """
 from __future__ import annotations
 
@@ -84,6 +95,51 @@ def grpo_token_weights(logp: torch.Tensor, old_logp: torch.Tensor, advantages: t
     msum = m.sum().clamp_min(1.0)
     metrics = {"ratio_mean": (ratio * m).sum() / msum, "clip_frac": ((1 - unclipped) * m).sum() / msum, "kl": (kl * m).sum() / msum,
                "masked_by_cap": (mask.float() - m).sum()}
+    return loss, weights, metrics
+
+
+def ipo_loss_reference(logp: torch.Tensor, old_logp: torch.Tensor, advantages: torch.Tensor, mask: torch.Tensor, teacher_logp: Optional[torch.Tensor] = None,
+                       ipo_mask_low: float = 0.2, ipo_mask_high: float = 0.2, adv_tau: float = 1.0, teacher_tau: float = 0.0, kl_tau: float = 1e-3,
+                       ratio_clip: float = 7.389056, normalization: str = "token", seq_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Differentiable surrogate whose gradient with respect to ``logp`` is the ``ipo`` gradient (the oracle of ``ipo_token_weights``):
+    mask, advantage, teacher term and the capped ratio are detached, as they are in the objective's definition."""
+    with torch.no_grad():
+        ratio = torch.exp(logp - old_logp)
+        pdiff = torch.exp(logp) - torch.exp(old_logp)
+        keep = mask.bool() & ~((pdiff > ipo_mask_high) | (pdiff < -ipo_mask_low))
+        adv = adv_tau * advantages + (teacher_tau * (teacher_logp - logp) if teacher_logp is not None else 0.0)
+        coef = keep.float() * adv * ratio.clamp(max=ratio_clip)
+        z = _normaliser(mask.float(), seq_ids, normalization)
+    return ((-coef * logp + kl_tau * mask.float() * (logp - old_logp) ** 2) * z).sum()
+
+
+@torch.no_grad()
+def ipo_token_weights(logp: torch.Tensor, old_logp: torch.Tensor, advantages: torch.Tensor, mask: torch.Tensor, teacher_logp: Optional[torch.Tensor] = None,
+                      ipo_mask_low: float = 0.2, ipo_mask_high: float = 0.2, adv_tau: float = 1.0, teacher_tau: float = 0.0, kl_tau: float = 1e-3,
+                      ratio_clip: float = 7.389056, normalization: str = "token", seq_ids: Optional[torch.Tensor] = None):
+    """(loss, per-token CE weights, metrics) of the ``ipo`` objective; same contract as ``grpo_token_weights``."""
+    m = mask.float()
+    log_ratio = logp - old_logp
+    ratio = torch.exp(log_ratio)
+    pdiff = torch.exp(logp) - torch.exp(old_logp)
+    high, low = pdiff > ipo_mask_high, pdiff < -ipo_mask_low
+    masked = high | low
+    keep = m * (~masked).float()
+    adv = adv_tau * advantages
+    if teacher_logp is not None:
+        adv = adv + teacher_tau * (teacher_logp - logp)
+    z = _normaliser(m, seq_ids, normalization)
+    per_tok = -keep * adv * ratio + kl_tau * m * log_ratio ** 2
+    dl = -keep * adv * ratio.clamp(max=ratio_clip) + 2.0 * kl_tau * m * log_ratio
+    loss = (per_tok * z).sum()
+    weights = -(dl * z)
+    msum, ksum = m.sum().clamp_min(1.0), keep.sum().clamp_min(1.0)
+    mismatch = ratio - log_ratio - 1.0
+    metrics = {"ratio_mean": (ratio * m).sum() / msum, "mismatch_kl": (mismatch * m).sum() / msum, "unmasked_mismatch_kl": (mismatch * keep).sum() / ksum,
+               "is_masked": (masked.float() * m).sum() / msum, "is_masked_low": (low.float() * m).sum() / msum, "is_masked_high": (high.float() * m).sum() / msum,
+               "keep_tokens": keep.sum(), "ratio_clipped": ((ratio > ratio_clip).float() * keep).sum() / ksum, "kl": (log_ratio ** 2 * m).sum() / msum}
+    if teacher_logp is not None:
+        metrics["teacher_kl"] = ((teacher_logp - logp) * m).sum() / msum
     return loss, weights, metrics
 
 

@@ -55,6 +55,7 @@ class AsyncOrchestratorConfig:
     eval_samples: int = 4
     eval_ks: Sequence[int] = (1, 4)
     eval_pass_threshold: float = 1.0
+    temperature_schedule: Optional[Dict[str, Any]] = None   # {type: linear | cosine, start, end, total_steps}: sampling temperature by step
     poll_s: float = 0.01
     step_timeout_s: float = 3600.0
     vocab_size: int = 32000
@@ -176,6 +177,11 @@ class AsyncOrchestrator:
         s = self.scheduler
         self.buffer.reset_step_metrics()
         s.set_depth_cap(self.depth.cap_for_step(step))
+        if self.cfg.temperature_schedule:
+            from ..config_compat import temperature_at
+
+            temp = temperature_at(step, self.cfg.temperature_schedule, self.cfg.max_steps)
+            s.set_sampling_args(dict(self.cfg.sampling, temperature=temp))
         kept: List[Rollout] = []
         observations: List[DepthObservation] = []
         stats: Dict[str, float] = {}
@@ -290,6 +296,7 @@ def async_config_from(cfg, raw: Optional[Dict[str, Any]] = None, vocab_size: int
                                 filters=list(raw.get("filters", [])), buffer=dict(raw.get("buffer", {"seed": cfg.seed, "online_difficulty_filtering": cfg.filter_zero_advantage})),
                                 depth=dict(raw.get("depth", {"enabled": False})),
                                 sampling={"max_tokens": cfg.max_tokens, "temperature": cfg.temperature, "top_p": cfg.top_p, **cfg.extra_sampling},
-                                checkpoint_dir=raw.get("checkpoint_dir"), checkpoint_every=int(raw.get("checkpoint_every", 0)), vocab_size=vocab_size,
-                                pad_token_id=pad_token_id)
+                                checkpoint_dir=raw.get("checkpoint_dir"), checkpoint_every=int(raw.get("checkpoint_every", 0)),
+                                keep_checkpoints=int(raw.get("keep_checkpoints", 2)), eval_every=int(raw.get("eval_every", 0)), eval_samples=int(raw.get("eval_samples", 4)),
+                                temperature_schedule=raw.get("temperature_schedule"), vocab_size=vocab_size, pad_token_id=pad_token_id)
     return a

@@ -27,13 +27,14 @@ from .rewards import resolve_reward
 
 
 class OpenAIClient:
-    def __init__(self, base_url: str, model: str, timeout_s: float = 600.0, api_key: str = "EMPTY"):
+    def __init__(self, base_url: str, model: str, timeout_s: float = 600.0, api_key: str = "EMPTY", headers: Optional[Dict[str, str]] = None):
         self.url, self.model, self.timeout, self.key = base_url.rstrip("/") + "/completions", model, timeout_s, api_key
+        self.headers = dict(headers or {})
 
     def generate(self, prompt_ids: List[int], n: int, sampling: Dict[str, Any]) -> List[Tuple[List[int], List[float], str]]:
         body = {"model": self.model, "prompt": prompt_ids, "n": n, "logprobs": 1, "return_token_ids": True, **sampling}
         req = urllib.request.Request(self.url, data=json.dumps(body).encode(),
-                                     headers={"Content-Type": "application/json", "Authorization": f"Bearer {self.key}"})
+                                     headers={"Content-Type": "application/json", "Authorization": f"Bearer {self.key}", **self.headers})
         with urllib.request.urlopen(req, timeout=self.timeout) as r:
             resp = json.loads(r.read())
         out = []

@@ -18,7 +18,7 @@ import torch
 
 from ..runtime.trainer import Trainer
 from .config import GRPOConfig, GRPOLossConfig
-from .loss import grpo_token_weights
+from .loss import grpo_token_weights, ipo_token_weights
 
 
 class GRPOTrainer:
@@ -26,6 +26,7 @@ class GRPOTrainer:
         self.t = trainer
         self.loss = loss or GRPOLossConfig()
         self.policy_version = 0
+        self.turn_diagnostics = False
 
     def _slice(self, a: np.ndarray) -> np.ndarray:
         t = self.t
@@ -46,8 +47,13 @@ class GRPOTrainer:
         if L.advantage_clip:
             adv = adv.clamp(-L.advantage_clip, L.advantage_clip)
         logp = t.token_logprobs(x, y, pos)
-        ref = t.token_logprobs(x, y, pos, use_adapters=False) if (L.kl_coef and t.lora is not None) else None
-        loss, w, metrics = grpo_token_weights(logp, old, adv, mask, ref, L.clip_eps_low, L.clip_eps_high, L.kl_coef, L.ratio_cap, L.normalization, seq)
+        if L.type == "ipo":
+            teacher = torch.from_numpy(self._slice(batch["teacher_logprobs"])).to(dev) if (L.teacher_tau and "teacher_logprobs" in batch) else None
+            loss, w, metrics = ipo_token_weights(logp, old, adv, mask, teacher, L.ipo_mask_low, L.ipo_mask_high, L.adv_tau, L.teacher_tau, L.kl_tau, L.ratio_clip,
+                                                 L.normalization, seq)
+        else:
+            ref = t.token_logprobs(x, y, pos, use_adapters=False) if (L.kl_coef and t.lora is not None) else None
+            loss, w, metrics = grpo_token_weights(logp, old, adv, mask, ref, L.clip_eps_low, L.clip_eps_high, L.kl_coef, L.ratio_cap, L.normalization, seq)
         if t.world > 1:  # the normaliser above is per rank: average the ranks' objectives
             w = w / t.world
         t.forward_backward(x, y, pos, row_weights=w, loss_scale_override=1.0)
@@ -62,7 +68,23 @@ class GRPOTrainer:
             vals = red
         host = vals.to("cpu").tolist()
         out = {"loss": host[0], "norm": host[1], **{k: v for k, v in zip(keys, host[2:])}}
+        if self.turn_diagnostics:
+            out.update(self._turn_summary(logp, old, mask, seq, w))
         return out
+
+    @staticmethod
+    def _turn_summary(logp, old, mask, seq, weights) -> Dict[str, float]:
+        """Per-turn shares of tokens, |log-ratio| and loss weight over this rank's samples (``grpo/turn_stats.py``): in a packed row a
+        sample is one value of ``seq_ids``, a turn one run of supervised tokens inside it."""
+        from .turn_stats import TurnStats, turn_ids_from_mask
+
+        lp, lo, m, s, w = (a.detach().float().cpu().numpy() for a in (logp, old, mask.float(), seq.float(), weights))
+        stats = TurnStats()
+        for r in range(lp.shape[0]):
+            for sid in np.unique(s[r][s[r] >= 0]):
+                sel = s[r] == sid
+                stats.add_sample(turn_ids_from_mask(m[r][sel]), m[r][sel], lp[r][sel], lo[r][sel], w[r][sel])
+        return stats.summary()
 
 
 def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
@@ -85,10 +107,18 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
     else:
         trainer.init_weights(cfg.train_seed)
     transport = make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="consumer")
-    bcast = FilesystemBroadcast(cfg.weight_dir)
-    g = GRPOTrainer(trainer, cfg.loss)
-    bcast.publish(trainer, 0, hf_cfg)  # version 0 = the initial policy: lets the orchestrator start
     max_steps = cfg.max_steps if cfg.max_steps > 0 else 100
+    noise = None
+    if cfg.noise_scheduler and cfg.noise_scheduler.get("enabled"):
+        from .noise import NoiseConfig
+
+        ns = cfg.noise_scheduler
+        noise = NoiseConfig(enabled=True, sigma_start=float(ns.get("sigma_start", 5e-2)), sigma_end=float(ns.get("sigma_end", 5e-4)),
+                            stages=int(ns.get("num_stages", ns.get("stages", 10))), seed=cfg.train_seed)
+    bcast = FilesystemBroadcast(cfg.weight_dir, noise=noise, total_steps=max_steps // max(1, cfg.broadcast_every))
+    g = GRPOTrainer(trainer, cfg.loss)
+    g.turn_diagnostics = bool(cfg.turn_diagnostics)
+    bcast.publish(trainer, 0, hf_cfg)  # version 0 = the initial policy: lets the orchestrator start
     sched = LRSchedule(cfg.learning_rate, max_steps, cfg.warmup_steps, cfg.cooldown_steps, cfg.final_lr_fraction * cfg.learning_rate,
                        cfg.lr_scheduler_type, cfg.wsd_decay_steps_fraction)
     logger = TrainingRunLogger(cfg.log_file, None, is_main=info.is_main)

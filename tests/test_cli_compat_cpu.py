@@ -170,3 +170,101 @@ def test_hub_token_and_dashboard_alias(monkeypatch):
     take_hub_token(a)
     assert os.environ["HF_TOKEN"] == "hf_abc" and not hasattr(a, "hub_token")
     monkeypatch.delenv("HF_TOKEN", raising=False)
+
+
+def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.config_compat import flatten_orchestrator_config, is_nested_schema, temperature_at
+
+    flat_in = {"model": "m", "group_size": 4, "environment": "markdown-table-qa"}
+    assert not is_nested_schema(flat_in) and flatten_orchestrator_config(flat_in) == (flat_in, [])
+    nested = {
+        "model": {"name": "Qwen/Qwen3-4B", "lora_adapter": "policy"},
+        "client": {"base_url": ["http://a:8000/v1", "http://b:8000/v1"], "timeout": 900, "api_key_var": "MYKEY", "headers": {"X-A": "1"}, "skip_model_check": True},
+        "sampling": {"temp_scheduler": {"type": "cosine", "start_temperature": 1.2, "end_temperature": 0.6, "total_steps": 100}, "top_p": 0.95, "max_tokens": 768,
+                     "repetition_penalty": 1.1, "min_tokens": 0, "extra_body": {"top_k": 50}},
+        "env": [{"id": "multihop-tools", "args": {"hops": 2}}, {"id": "other"}],
+        "batch_size": 64, "rollouts_per_example": 8, "sequence_len": 4096, "max_steps": 300, "max_off_policy_steps": 6, "max_async_level": 1, "seed": 7,
+        "max_inflight_rollouts": 256, "output_dir": "outputs/run1",
+        "buffer": {"easy_threshold": 1.0, "hard_threshold": 0.0, "online_difficulty_filtering": True, "normal_pool_min_examples": 100, "hash_keys": ["task", "prompt"]},
+        "rollout_depth": {"enabled": True, "quantile": 0.8, "min_depth": 2, "max_depth": 16, "probe_interval": 8, "ema": 0.3},
+        "advantage": {"type": "custom", "import_path": "my_pkg.adv.compute", "kwargs": {"a": 1}},
+        "filters": [{"type": "gibberish", "token_id_threshold": 100000, "logprob_offset": 2.0}, {"type": "repetition", "window": 3000, "prob_threshold": 0.99, "enforce": True}],
+        "ckpt": {"interval": 25, "keep_last": 3}, "eval": {"interval": 50, "rollouts_per_example": 2, "num_examples": 32},
+        "weight_broadcast": {"type": "nccl", "port": 29501}, "rollout_transport": {"type": "zmq", "host": "10.0.0.1", "port": 5566},
+        "ruler": {"enabled": True, "judge_model": "j"}, "tasks_per_minute": 10.0,
+    }
+    flat, notes = flatten_orchestrator_config(nested)
+    assert flat["scheduler"] == "async" and flat["model"] == "Qwen/Qwen3-4B" and flat["served_model"] == "policy"
+    assert flat["base_url"] == "http://a:8000/v1" and len(flat["base_urls"]) == 2 and flat["request_timeout_s"] == 900.0 and flat["api_key_var"] == "MYKEY"
+    assert flat["temperature_schedule"] == {"type": "cosine", "start": 1.2, "end": 0.6, "total_steps": 100} and flat["top_p"] == 0.95 and flat["max_tokens"] == 768
+    assert flat["extra_sampling"] == {"top_k": 50, "repetition_penalty": 1.1}
+    assert flat["environment"] == "multihop-tools" and flat["environment_args"] == {"hops": 2}
+    assert flat["group_size"] == 8 and flat["batch_size"] == 64 and flat["prompts_per_step"] == 8 and flat["max_inflight"] == 32 and flat["rows_per_step"] == 16
+    assert flat["buffer"] == {"easy_threshold": 1.0, "hard_threshold": 0.0, "online_difficulty_filtering": True, "min_normal": 100}
+    assert flat["depth"] == {"enabled": True, "quantile": 0.8, "min_cap": 2, "max_cap": 16, "probe_every": 8}
+    assert flat["advantage"] == "my_pkg.adv:compute" and flat["filters"][0]["enforce"] is False and flat["filters"][1]["enforce"] is True
+    assert flat["checkpoint_every"] == 25 and flat["keep_checkpoints"] == 3 and flat["checkpoint_dir"] == os.path.join("outputs/run1", "orch_checkpoints")
+    assert flat["eval_every"] == 50 and flat["eval_samples"] == 2 and flat["eval_examples"] == 32
+    assert flat["weight_broadcast"] == "nccl" and flat["transport"] == "zmq" and flat["zmq_endpoint"] == "tcp://10.0.0.1:5566"
+    assert flat["weight_dir"] == os.path.join("outputs/run1", "weights") and flat["transport_dir"] == os.path.join("outputs/run1", "rollouts")
+    text = "\n".join(notes)
+    assert "only the first" in text and "ruler" in text and "tasks_per_minute" in text and "rows_per_step not given" in text and "skip_model_check" not in text
+    # the flat result is a valid orchestrator config of this package
+    from surogate_b200.config.loader import coerce_fields
+
+    cfg = OrchestratorConfig(**coerce_fields(OrchestratorConfig, {k: v for k, v in flat.items() if k in OrchestratorConfig.__dataclass_fields__}))
+    assert cfg.group_size == 8 and cfg.transport == "zmq" and cfg.extra_sampling["top_k"] == 50
+    with pytest.raises(ValueError):
+        flatten_orchestrator_config({"sampling": {"temperature": 1.0, "temp_scheduler": {"start_temperature": 1.0, "end_temperature": 0.5}}})
+    sch = flat["temperature_schedule"]
+    assert temperature_at(0, sch, 300) == 1.2 and abs(temperature_at(50, sch, 300) - 0.9) < 1e-9 and temperature_at(100, sch, 300) == temperature_at(500, sch, 300) == 0.6
+    assert abs(temperature_at(5, {"type": "linear", "start": 1.0, "end": 0.0, "total_steps": None}, 10) - 0.5) < 1e-12
+
+
+def test_per_token_filter_rules_and_enforce_flag():
+    from surogate_b200.grpo.orchestration.filters import apply_filters, make_filters
+    from surogate_b200.grpo.packer import Rollout
+    import math
+
+    V = 1000
+    thr = -math.log(V) - 2.0
+    ok = Rollout([1], [5, 999, 7], [-0.1, thr + 0.1, -0.2], 0.0, 1.0, 0, 0, {})
+    rare = Rollout([1], [5, 999, 7], [-0.1, thr - 0.1, -0.2], 0.0, 1.0, 0, 0, {})           # a rare id sampled below the threshold
+    common = Rollout([1], [5, 100, 7], [-0.1, thr - 0.1, -0.2], 0.0, 1.0, 0, 0, {})        # same surprise on a common id: fine
+    loop = Rollout([1], list(range(10)), [-0.001] * 10, 0.0, 1.0, 0, 0, {})                 # ten near-certain tokens in a row
+    brk = Rollout([1], list(range(10)), [-0.001] * 4 + [-1.0] + [-0.001] * 5, 0.0, 1.0, 0, 0, {})
+    fs = make_filters([{"type": "gibberish", "token_id_threshold": 500, "logprob_offset": 2.0, "enforce": False}, {"type": "repetition", "window": 6, "prob_threshold": 0.99}], V)
+    rs = [ok, rare, common, loop, brk]
+    for r in rs:
+        r.completion_mask = [1] * len(r.completion_ids)
+    stats = apply_filters(fs, rs)
+    assert stats == {"filter/gibberish": 0.2, "filter/repetition": 0.2}
+    assert rare.meta["filtered"] == "gibberish" and sum(rare.completion_mask) == 3           # counted only: enforce is off
+    assert loop.meta["filtered"] == "repetition" and sum(loop.completion_mask) == 0          # enforced: leaves the loss
+    assert "filtered" not in ok.meta and "filtered" not in common.meta and "filtered" not in brk.meta
+
+
+def test_inference_config_takes_the_short_keys_and_builds_the_engine_command(monkeypatch):
+    from surogate_b200.grpo.config import InferenceConfig
+    from surogate_b200.grpo.inference import server_command
+
+    monkeypatch.delenv("SUROGATE_ENGINE_MEMORY_FRACTION", raising=False)
+    cfg = InferenceConfig(model="m", tp=2, dp=2, max_lora_rank=24, weight_broadcast_type="nccl", kv_cache_dtype="fp8", max_num_seqs=256, enforce_eager=True,
+                          enable_auto_tool_choice=True, reasoning_parser="qwen3", enable_prefix_caching=False, seed=3, dtype="bfloat16", enable_expert_parallel=True,
+                          rope_scaling={"rope_type": "yarn", "factor": 2.0}, api_server_count=4)
+    assert (cfg.tensor_parallel_size, cfg.data_parallel_size, cfg.max_lora_rank, cfg.weight_broadcast, cfg.api_server_count) == (2, 2, 32, "nccl", 1)
+    cmd = server_command(cfg)
+    text = " ".join(cmd)
+    for part in ("--tensor-parallel-size 2", "--data-parallel-size 2", "--kv-cache-dtype fp8", "--max-num-seqs 256", "--enforce-eager", "--enable-auto-tool-choice --tool-call-parser hermes",
+                 "--reasoning-parser qwen3", "--no-enable-prefix-caching", "--seed 3", "--dtype bfloat16", "--enable-expert-parallel", "--enable-lora --max-loras 8 --max-cpu-loras 100 --max-lora-rank 32",
+                 "--worker-extension-cls"):
+        assert part in text, part
+    assert json.loads(cmd[cmd.index("--rope-scaling") + 1]) == {"rope_type": "yarn", "factor": 2.0} and "--api-server-count" not in cmd
+    assert InferenceConfig(model="m", enable_lora=False, dp=4).api_server_count == 4
+    plain = " ".join(server_command(InferenceConfig(model="m")))
+    assert "--kv-cache-dtype" not in plain and "--dtype" not in plain and "--seed" not in plain and "prefix-caching" not in plain
+    with pytest.raises(ValueError):
+        InferenceConfig(model="m", max_lora_rank=1024)
+    with pytest.raises(ValueError):
+        InferenceConfig(model="m", weight_broadcast="carrier-pigeon")

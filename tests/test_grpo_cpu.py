@@ -1,5 +1,6 @@
 """GRPO pieces on CPU: token-weight gradient vs autograd, packer alignment, transport, orchestrator with a fake engine."""
 import numpy as np
+import pytest
 import torch
 
 from surogate_b200.grpo.loss import group_advantages, grpo_loss_reference, grpo_token_weights
@@ -272,3 +273,85 @@ def test_orchestrator_runs_multi_turn_tool_episodes(tmp_path):
     arrays, meta = orch.transport.receive(0, timeout_s=1)
     trained = arrays["targets"] != -100
     assert trained.sum() == sum(sum(r.completion_mask) for r in rollouts) and np.all(arrays["old_logprobs"][trained] == -0.25)
+
+
+def test_ipo_objective_weights_match_autograd_and_mask_drifted_tokens():
+    """``type: ipo``: the per-token weights equal minus the autograd gradient of the surrogate; a token whose probability moved past
+    the mask thresholds keeps only the penalty term; the ratio that multiplies the gradient is capped."""
+    from surogate_b200.grpo.loss import ipo_loss_reference, ipo_token_weights
+
+    torch.manual_seed(0)
+    R, T = 3, 12
+    old = -torch.rand(R, T) * 2.0 - 0.05
+    logp = (old + 0.3 * torch.randn(R, T)).clamp(max=-1e-3)
+    logp[0, 0], old[0, 0] = -0.05, -2.5      # probability rose by ~0.87 > 0.2: masked (high)
+    logp[0, 1], old[0, 1] = -3.0, -0.1       # fell by ~0.85: masked (low)
+    logp[1, 2], old[1, 2] = -0.9, -3.2       # ratio ~10 > e^2 but probability difference 0.37 -> masked as well
+    logp[2, 3], old[2, 3] = -4.0, -6.5       # ratio ~12, probability difference tiny: kept, ratio capped at e^2
+    adv = torch.randn(R, T)
+    teacher = old + 0.1 * torch.randn(R, T)
+    mask = (torch.rand(R, T) > 0.2).float()
+    mask[0, :2] = mask[1, 2] = mask[2, 3] = 1.0
+    seq = torch.arange(R)[:, None].expand(R, T).contiguous()
+    for kw in (dict(), dict(teacher_logp=teacher, teacher_tau=0.3, adv_tau=0.7, kl_tau=0.05), dict(normalization="sequence", seq_ids=seq)):
+        lp = logp.clone().requires_grad_(True)
+        ipo_loss_reference(lp, old, adv, mask, **kw).backward()
+        loss, w, metrics = ipo_token_weights(logp, old, adv, mask, **kw)
+        assert torch.allclose(w, -lp.grad, atol=1e-6), kw
+        assert torch.isfinite(loss)
+    loss, w, metrics = ipo_token_weights(logp, old, adv, mask, kl_tau=0.0)
+    Z = mask.sum()
+    for r, t in ((0, 0), (0, 1), (1, 2)):
+        assert w[r, t] == 0.0                                     # masked tokens leave the policy term; no penalty with kl_tau 0
+    assert torch.allclose(w[2, 3], adv[2, 3] * 7.389056 / Z, atol=1e-6)      # kept, capped ratio
+    assert float(metrics["is_masked"]) >= 3.0 / float(Z) - 1e-6 and float(metrics["is_masked_high"]) > 0 and float(metrics["is_masked_low"]) > 0
+    _, w2, _ = ipo_token_weights(logp, old, adv, mask, kl_tau=0.5)
+    assert torch.allclose(w2[0, 0], -2 * 0.5 * (logp[0, 0] - old[0, 0]) / Z, atol=1e-6)   # the penalty still pulls a masked token back
+
+
+def test_loss_section_selects_the_objective_and_trainer_keys_have_both_spellings():
+    from surogate_b200.grpo.config import GRPOConfig, GRPOLossConfig
+
+    assert GRPOLossConfig().type == "clip" and GRPOLossConfig(kl_tau=1e-2).type == "ipo" and GRPOLossConfig(type="ipo").ipo_mask_low == 0.2
+    assert abs(GRPOLossConfig(type="ipo").ratio_clip - 7.389056) < 1e-9 and GRPOLossConfig(clip_eps_high=0.3).type == "clip"
+    with pytest.raises(ValueError):
+        GRPOLossConfig(type="dpo")
+    model = dict(architecture="Qwen3ForCausalLM", vocab_size=64, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16, d_ff=64, tie_word_embeddings=True)
+    import json
+
+    cfg = GRPOConfig.from_dict(dict(model=json.dumps(model), transport_type="zmq", weight_broadcast_type="nccl", max_async_level=1, turn_diagnostics=True,
+                                    noise_scheduler=dict(enabled=True, sigma_start=0.05, sigma_end=0.0005, num_stages=4),
+                                    loss=dict(ipo_mask_low=0.1, ipo_mask_high=0.3, kl_tau=0.01, adv_tau=1.0, teacher_tau=0.0, ratio_clip=5.0)))
+    assert cfg.transport == "zmq" and cfg.weight_broadcast == "nccl" and cfg.loss.type == "ipo" and cfg.loss.ipo_mask_high == 0.3 and cfg.turn_diagnostics
+    assert cfg.noise_scheduler["num_stages"] == 4
+
+
+def test_grpo_trainer_step_with_the_ipo_objective_and_turn_diagnostics():
+    from surogate_b200.grpo.config import GRPOLossConfig
+    from surogate_b200.grpo.trainer import GRPOTrainer
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    torch.manual_seed(0)
+    tr = Trainer(TrainerConfig(model=dict(architecture="Qwen3ForCausalLM", vocab_size=64, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16,
+                                          d_ff=64, tie_word_embeddings=True), batch_size=2, seq_len=16, recipe="bf16", optimizer="adamw", learning_rate=5e-2, backend="torch"))
+    tr.init_weights(seed=0)
+    g = GRPOTrainer(tr, GRPOLossConfig(type="ipo", kl_tau=1e-3))
+    g.turn_diagnostics = True
+    rng = np.random.default_rng(0)
+    x = rng.integers(0, 64, (2, 16)).astype(np.int32)
+    y = np.roll(x, -1, axis=1).astype(np.int32)
+    y[:, :4] = -100
+    y[:, 8:10] = -100       # an environment span: two turns per sample
+    y[:, -1] = -100
+    pos = np.tile(np.arange(16, dtype=np.int32), (2, 1))
+    old = tr.token_logprobs(x, y, pos).cpu().numpy()
+    adv = np.where(np.arange(2)[:, None] == 0, 1.0, -1.0).astype(np.float32) * np.ones((2, 16), np.float32)
+    batch = {"inputs": x, "targets": y, "position_ids": pos, "advantages": adv, "old_logprobs": old, "seq_ids": np.tile(np.arange(2, dtype=np.int32)[:, None], (1, 16))}
+    before = tr.token_logprobs(x, y, pos).cpu().numpy()
+    out = None
+    for _ in range(3):
+        out = g.step(batch)
+    after = tr.token_logprobs(x, y, pos).cpu().numpy()
+    m = y != -100
+    assert after[0][m[0]].mean() > before[0][m[0]].mean() and after[1][m[1]].mean() < before[1][m[1]].mean()   # rewarded up, punished down
+    assert "is_masked" in out and "mismatch_kl" in out and out["turns/samples"] == 2.0 and out["turns/max_depth"] == 2.0
