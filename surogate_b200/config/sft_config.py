@@ -46,6 +46,7 @@ class DatasetConfig:
     prompt_field: str = "prompt"
     chosen_field: str = "chosen"
     rejected_field: str = "rejected"
+    enable_thinking_field: Optional[str] = None  # preference rows: column with a bool that switches the chat template's thinking prefix (default "enable_thinking" when present)
     fields: Dict[str, str] = field(default_factory=dict)
 
     @staticmethod
@@ -124,6 +125,11 @@ class SFTConfig:
     log_file: Optional[str] = None
     report_to: List[str] = field(default_factory=list)
     log_gpu_util: int = 100
+    wandb_project: Optional[str] = None     # default "Surogate"
+    wandb_name: Optional[str] = None        # default run_name
+    aim_experiment: Optional[str] = None    # default "Surogate"
+    aim_repo: Optional[str] = None          # Aim repository path or URL (default: the working directory's)
+    aim_name: Optional[str] = None          # default run_name
     surogate_metrics_path: str = "/tmp/surogate_metrics.jsonl"
     apply_recommended_values: bool = False
     # batch / data

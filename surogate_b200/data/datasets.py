@@ -237,7 +237,14 @@ def preprocess_preference(cfg, row) -> Optional[Dict[str, Any]]:
     system = _system(cfg, row)
     if system and (not prompt_msgs or prompt_msgs[0]["role"] != "system"):
         prompt_msgs = [{"role": "system", "content": system}] + prompt_msgs
-    return {"prompt": prompt_msgs, "chosen": str(chosen), "rejected": str(rejected)}
+    out = {"prompt": prompt_msgs, "chosen": str(chosen), "rejected": str(rejected)}
+    field = getattr(cfg, "enable_thinking_field", None)
+    if field and field not in row:
+        raise ValueError(f"enable-thinking field '{field}' is missing from the dataset; columns: {sorted(row)}")
+    flag = row.get(field or "enable_thinking")
+    if flag is not None:
+        out["enable_thinking"] = bool(flag) if not isinstance(flag, str) else flag.strip().lower() in ("1", "true", "yes")
+    return out
 
 
 PREPROCESSORS = {"text": preprocess_text, "instruction": preprocess_instruction, "alpaca": preprocess_alpaca, "conversation": preprocess_conversation,

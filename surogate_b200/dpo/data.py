@@ -15,7 +15,7 @@ IGNORE = -100
 
 
 def encode_pair(tok, row: Dict[str, Any], seq_len: int, max_prompt_len: int) -> Tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]:
-    prompt_text = tok.apply_chat_template(row["prompt"], add_generation_prompt=True)
+    prompt_text = tok.apply_chat_template(row["prompt"], add_generation_prompt=True, enable_thinking=row.get("enable_thinking"))
     p = tok.encode(prompt_text)[-max_prompt_len:]
     eos = [tok.eos_token_id] if tok.eos_token_id >= 0 else []
 

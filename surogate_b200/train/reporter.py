@@ -71,10 +71,10 @@ class WandbReporter(Reporter):
 class AimReporter(Reporter):
     name = "aim"
 
-    def __init__(self, experiment: str, run_name: str, config: Optional[Dict[str, Any]] = None):
+    def __init__(self, experiment: str, run_name: str, config: Optional[Dict[str, Any]] = None, repo: Optional[str] = None):
         from aim import Run  # type: ignore
 
-        self.run = Run(experiment=experiment)
+        self.run = Run(experiment=experiment, **({"repo": repo} if repo else {}))
         self.run.name = run_name
         if config:
             self.run["hparams"] = config
@@ -88,15 +88,18 @@ class AimReporter(Reporter):
         self.run.close()
 
 
-def make_reporters(report_to: List[str], run_name: str, project: str = "surogate", metrics_path: str = "/tmp/surogate_metrics.jsonl",
+def make_reporters(report_to: List[str], run_name: str, project: str = "Surogate", metrics_path: str = "/tmp/surogate_metrics.jsonl",
                    config: Optional[Dict[str, Any]] = None) -> List[Reporter]:
+    """``config`` (the run's options) also carries the reporters' own keys: ``wandb_project`` / ``wandb_name``, ``aim_experiment`` /
+    ``aim_repo`` / ``aim_name``; each falls back to ``project`` / ``run_name``."""
     out: List[Reporter] = []
+    c = config or {}
     for name in report_to or []:
         try:
             if name == "wandb":
-                out.append(WandbReporter(project, run_name, config))
+                out.append(WandbReporter(c.get("wandb_project") or project, c.get("wandb_name") or run_name, config))
             elif name == "aim":
-                out.append(AimReporter(project, run_name, config))
+                out.append(AimReporter(c.get("aim_experiment") or project, c.get("aim_name") or run_name, config, c.get("aim_repo")))
             elif name in ("surogate", "jsonl"):
                 out.append(JsonlReporter(metrics_path, run_name))
             else:

@@ -268,3 +268,59 @@ def test_inference_config_takes_the_short_keys_and_builds_the_engine_command(mon
         InferenceConfig(model="m", max_lora_rank=1024)
     with pytest.raises(ValueError):
         InferenceConfig(model="m", weight_broadcast="carrier-pigeon")
+
+
+def test_reporter_keys_and_enable_thinking_field(monkeypatch):
+    import sys
+    import types
+
+    from surogate_b200.config.sft_config import DatasetConfig, SFTConfig
+    from surogate_b200.data.datasets import preprocess_preference
+    from surogate_b200.train.reporter import make_reporters
+
+    cfg = SFTConfig.from_dict(dict(model=json.dumps(_tiny_model()), synthetic_data=True, wandb_project="P", wandb_name="N", aim_experiment="E", aim_repo="/r", aim_name="A"))
+    seen = {}
+    wandb = types.ModuleType("wandb")
+    wandb.init = lambda **kw: seen.setdefault("wandb", kw) and types.SimpleNamespace(finish=lambda: None)
+    aim = types.ModuleType("aim")
+
+    class Run(dict):
+        def __init__(self, **kw):
+            seen["aim"] = kw
+
+        def track(self, *a, **k):
+            pass
+
+        def close(self):
+            pass
+
+    aim.Run = Run
+    monkeypatch.setitem(sys.modules, "wandb", wandb)
+    monkeypatch.setitem(sys.modules, "aim", aim)
+    reps = make_reporters(["wandb", "aim"], "run-1", config=json.loads(cfg.to_json()))
+    assert seen["wandb"]["project"] == "P" and seen["wandb"]["name"] == "N" and seen["aim"] == {"experiment": "E", "repo": "/r"} and reps[1].run.name == "A"
+    seen.clear()
+    make_reporters(["wandb", "aim"], "run-1", config={})
+    assert seen["wandb"]["project"] == "Surogate" and seen["wandb"]["name"] == "run-1" and seen["aim"] == {"experiment": "Surogate"}
+
+    row = {"prompt": "q", "chosen": "a", "rejected": "b", "enable_thinking": False, "think": "true"}
+    assert preprocess_preference(DatasetConfig(type="preference"), row)["enable_thinking"] is False
+    assert preprocess_preference(DatasetConfig(type="preference", enable_thinking_field="think"), row)["enable_thinking"] is True
+    assert "enable_thinking" not in preprocess_preference(DatasetConfig(type="preference"), {"prompt": "q", "chosen": "a", "rejected": "b"})
+    with pytest.raises(ValueError, match="enable-thinking field"):
+        preprocess_preference(DatasetConfig(type="preference", enable_thinking_field="nope"), row)
+
+    class Tok:
+        eos_token_id, pad_token_id = 1, 0
+
+        def apply_chat_template(self, msgs, add_generation_prompt=False, enable_thinking=None):
+            seen["thinking"] = enable_thinking
+            return "p"
+
+        def encode(self, text):
+            return [5, 6] if text == "p" else [7]
+
+    from surogate_b200.dpo.data import encode_pair
+
+    encode_pair(Tok(), {"prompt": [{"role": "user", "content": "q"}], "chosen": "a", "rejected": "b", "enable_thinking": False}, 8, 4)
+    assert seen["thinking"] is False
