@@ -607,7 +607,8 @@ class Trainer:
 
     def update_with_config(self, opt_config: Any, step: Optional[int] = None) -> Dict[str, float]:
         """Optimizer update after one or more ``forward_backward`` calls, with hyper-parameters taken from ``opt_config`` (a dict
-        or an object with learning_rate / weight_decay / beta1 / beta2 / eps / max_grad_norm).  Returns {"norm": ...}.
+        or an object with learning_rate / weight_decay / beta1 / beta2 / eps / max_grad_norm).  ``step`` is the 1-based number of
+        this update (the ``t`` of Adam's bias correction), as callers of the reference API pass it.  Returns {"norm": ...}.
         Parity: SurogateTrainer.update_with_config."""
         get = opt_config.get if isinstance(opt_config, dict) else (lambda k, d=None: getattr(opt_config, k, d))
         for mine, theirs in (("weight_decay", "weight_decay"), ("beta1", "beta1"), ("beta2", "beta2"), ("eps", "eps"), ("max_grad_norm", "max_grad_norm"),
@@ -616,7 +617,7 @@ class Trainer:
             if v is not None:
                 setattr(self.opt_cfg, mine, float(v))
         if step is not None:
-            self.step_index = int(step)
+            self.step_index = max(0, int(step) - 1)  # optimizer_step counts this update itself
         norm = self.optimizer_step(get("learning_rate", None))
         return {"norm": float(norm)}
 
