@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Callable, Dict, Optional
+from typing import Any, Callable, Dict, List, Optional
 
 import torch
 from safetensors import safe_open
@@ -163,6 +163,30 @@ def export_hf_weights(cm: CompiledModel, store, out_dir: str, hf_config: Optiona
     if hf_config is not None:
         with open(os.path.join(out_dir, "config.json"), "w") as f:
             json.dump(to_hf_config(cm, hf_config), f, indent=1)
+
+
+TOKENIZER_FILES = ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "vocab.json", "merges.txt", "added_tokens.json", "tokenizer.model",
+                   "chat_template.jinja", "chat_template.json", "generation_config.json", "preprocessor_config.json", "video_preprocessor_config.json")
+
+
+def copy_tokenizer_files(src_dir: Optional[str], out_dir: str) -> List[str]:
+    """Tokenizer, chat template, generation and pre-processor files of the source model next to exported weights, so the export
+    loads in transformers / an inference engine without the original directory.  Files already present are kept."""
+    import shutil
+
+    copied: List[str] = []
+    if not src_dir:
+        return copied
+    src_dir = src_dir if os.path.isdir(src_dir) else os.path.dirname(src_dir)
+    if not os.path.isdir(src_dir) or os.path.abspath(src_dir) == os.path.abspath(out_dir):
+        return copied
+    os.makedirs(out_dir, exist_ok=True)
+    for fn in TOKENIZER_FILES:
+        s, d = os.path.join(src_dir, fn), os.path.join(out_dir, fn)
+        if os.path.isfile(s) and not os.path.exists(d):
+            shutil.copy2(s, d)
+            copied.append(fn)
+    return copied
 
 
 def to_hf_config(cm: CompiledModel, cfg: Dict[str, Any]) -> Dict[str, Any]:

@@ -264,6 +264,10 @@ class Trainer:
 
         export_hf_weights(self.cm, self.store, out_dir, hf_config or self.cfg.model, write=self.rank == 0,
                           passthrough_from=getattr(self, "_imported_from", None))
+        if self.rank == 0:
+            from ..io.hf_checkpoint import copy_tokenizer_files
+
+            copy_tokenizer_files(getattr(self, "tokenizer_source", None) or getattr(self, "_imported_from", None), out_dir)
 
     def export_adapter(self, out_dir: str, base_model: str = "") -> None:
         if self.lora is None:

@@ -201,7 +201,14 @@ def run_training(cfg: SFTConfig) -> Dict[str, Any]:
     finally:
         if watchdog is not None:
             watchdog.stop()
-    # final artefacts: adapter (LoRA) or full model in HF format
+    # final artefacts: adapter (LoRA) or full model in HF format (with the tokenizer files of the source model)
+    if isinstance(cfg.model, str) and not cfg.model.strip().startswith("{"):
+        try:
+            from ..hub import download_model
+
+            trainer.tokenizer_source = cfg.model if os.path.isdir(cfg.model) else download_model(cfg.model)
+        except Exception:  # noqa: BLE001 - no local copy of the model: the export carries weights and config only
+            pass
     if trainer.lora is not None:
         trainer.export_adapter(os.path.join(cfg.output_dir, "adapter"), base_model=cfg.model if isinstance(cfg.model, str) else "")
         if cfg.merge_adapter:

@@ -324,3 +324,22 @@ def test_reporter_keys_and_enable_thinking_field(monkeypatch):
 
     encode_pair(Tok(), {"prompt": [{"role": "user", "content": "q"}], "chosen": "a", "rejected": "b", "enable_thinking": False}, 8, 4)
     assert seen["thinking"] is False
+
+
+def test_export_carries_the_tokenizer_files(tmp_path):
+    from surogate_b200.io.hf_checkpoint import copy_tokenizer_files
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    src = tmp_path / "src"
+    os.makedirs(src)
+    for fn in ("tokenizer.json", "tokenizer_config.json", "generation_config.json", "unrelated.txt"):
+        (src / fn).write_text(fn)
+    tr = Trainer(TrainerConfig(model=_tiny_model(), batch_size=1, seq_len=8, backend="torch", recipe="bf16", optimizer="adamw"), device=torch.device("cpu"))
+    tr.init_weights(0)
+    tr.tokenizer_source = str(src)
+    out = tmp_path / "out"
+    tr.export_model(str(out))
+    assert sorted(os.listdir(out)) == ["config.json", "generation_config.json", "model.safetensors", "tokenizer.json", "tokenizer_config.json"]
+    (out / "tokenizer.json").write_text("kept")
+    assert copy_tokenizer_files(str(src), str(out)) == [] and (out / "tokenizer.json").read_text() == "kept"
+    assert copy_tokenizer_files(None, str(out)) == [] and copy_tokenizer_files(str(out), str(out)) == []
