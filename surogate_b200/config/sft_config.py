@@ -145,7 +145,7 @@ class SFTConfig:
     dataloader_num_workers: int = 0
     truncation_strategy: str = "right"
     use_chat_template: bool = True
-    loss_scale: str = "default"  # default (assistant tokens) | all
+    loss_scale: str = "default"  # default (assistant turns) | last_round (assistant turns after the last user message) | all; a message's own `loss` field (0 / 1) overrides it
     # optimisation
     optimizer: str = "adamw_8bit"
     learning_rate: float = 2e-4

@@ -147,7 +147,7 @@ def _norm_messages(raw, mappings: Dict[str, str]) -> List[Dict[str, Any]]:
             role_key, content_key = "from", "value"
         role = ROLE_ALIASES.get(str(m.get(role_key, "")).lower(), str(m.get(role_key, "user")))
         msg = {"role": role, "content": m.get(content_key) if m.get(content_key) is not None else ""}
-        for extra in ("tool_calls", "reasoning_content", "name", "tool_call_id"):
+        for extra in ("tool_calls", "reasoning_content", "name", "tool_call_id", "loss"):
             if m.get(extra) is not None:
                 msg[extra] = m[extra]
         out.append(msg)

@@ -146,12 +146,26 @@ class Tokenizer:
         messages = list(messages)
         full = self.apply_chat_template(messages, False, enable_thinking, tools)
         ids = self.encode(full)
-        if train_on == "all":
+        if train_on == "all" and not any(m.get("loss") is not None for m in messages):
             return ids, list(ids)
+        if train_on == "all":  # every token except the turns whose ``loss`` field switches them off
+            labels = list(ids)
+            for i, m in enumerate(messages):
+                if m.get("role") == "assistant" and m.get("loss") is not None and not float(m["loss"]):
+                    prefix = self.apply_chat_template(messages[:i], True, enable_thinking, tools)
+                    upto = os.path.commonprefix([self.apply_chat_template(messages[:i + 1], False, enable_thinking, tools), full])
+                    prefix = os.path.commonprefix([prefix, upto])
+                    for k in range(len(self.encode(prefix)), min(len(self.encode(upto)), len(ids))):
+                        labels[k] = IGNORE
+            return ids, labels
         labels = [IGNORE] * len(ids)
         turns = [i for i, m in enumerate(messages) if m.get("role") == "assistant"]
-        if train_on == "last":
-            turns = turns[-1:]
+        if train_on == "last":  # the assistant turns after the last user message (the last round)
+            users = [i for i, m in enumerate(messages) if m.get("role") == "user"]
+            turns = [i for i in turns if not users or i > users[-1]] or turns[-1:]
+        # a message's own ``loss`` field overrides the mode: 0 / false leaves the turn out, anything else trains it
+        forced = {i: bool(float(m["loss"])) for i, m in enumerate(messages) if m.get("role") == "assistant" and m.get("loss") is not None}
+        turns = sorted((set(turns) | {i for i, on in forced.items() if on}) - {i for i, on in forced.items() if not on})
         for i in turns:
             prefix = self.apply_chat_template(messages[:i], True, enable_thinking, tools)
             upto = self.apply_chat_template(messages[:i + 1], False, enable_thinking, tools)

@@ -24,6 +24,19 @@ from ..data.datasets import load_dataset_rows
 from ..data.tokfile import TokenFileWriter
 
 IGNORE = -100
+LOSS_SCALE_MODES = {"default": "assistant", "all": "all", "last_round": "last"}
+
+
+def loss_scale_mode(loss_scale: str) -> str:
+    """``loss_scale`` -> the tokenizer's ``train_on``: ``default`` (assistant turns), ``last_round`` (the assistant turns after the last
+    user message), ``all`` (every token); the ``<base>+<name>`` spelling is accepted with ``-`` / a base name as ``<name>``.  A message's
+    own ``loss`` field (0 or 1) overrides the mode for that turn.  Parity: surogate/core/model/loss_scale/loss_scale.py."""
+    base, _, name = (loss_scale or "default").partition("+")
+    if base not in LOSS_SCALE_MODES:
+        base, name = "default", base
+    if name not in ("", "-", *LOSS_SCALE_MODES):
+        raise ValueError(f"unknown loss_scale '{loss_scale}' (default | last_round | all)")
+    return LOSS_SCALE_MODES[base]
 ROWS_PER_SHARD = 1 << 14
 
 
@@ -146,7 +159,7 @@ class TokenizeDatasets:
                 text = "\n".join(str(m["content"]) for m in row["messages"])
                 ids = np.asarray(tok.encode(text) + ([tok.eos_token_id] if tok.eos_token_id >= 0 else []), np.int32)
                 return ids, np.ones(len(ids), np.uint8)
-            ids, labels = tok.encode_for_training(row["messages"], train_on="all" if c.loss_scale == "all" else "assistant", tools=row.get("tools"))
+            ids, labels = tok.encode_for_training(row["messages"], train_on=loss_scale_mode(c.loss_scale), tools=row.get("tools"))
             ids_a, lab = np.asarray(ids, np.int32), np.asarray(labels, np.int64)
             return ids_a, (lab != IGNORE).astype(np.uint8)
         return None

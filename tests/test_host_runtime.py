@@ -73,6 +73,22 @@ def test_chat_template_training_mask(tmp_path):
     _, last = tok.encode_for_training(msgs, train_on="last")
     assert tok.decode([l for l in last if l != IGNORE]) == "done<|im_end|>\n"
     assert tok.eos_token_id == tok.core.token_to_id(b"<|im_end|>")
+    # a message's own ``loss`` field overrides the mode for that turn
+    off = [dict(m, loss=0) if m["content"] == "It's a test" else m for m in msgs]
+    assert tok.decode([l for l in tok.encode_for_training(off)[1] if l != IGNORE]) == "done<|im_end|>\n"
+    on = [dict(m, loss=1) if m["content"] == "It's a test" else m for m in msgs]
+    assert tok.decode([l for l in tok.encode_for_training(on, train_on="last")[1] if l != IGNORE]) == "It's a test<|im_end|>\ndone<|im_end|>\n"
+    all_ids, all_labels = tok.encode_for_training(off, train_on="all")
+    assert "It's a test" not in tok.decode([l for l in all_labels if l != IGNORE]) and "Hello world" in tok.decode([l for l in all_labels if l != IGNORE])
+    # two assistant turns after the last user message are both "the last round"
+    tail = msgs[:4] + [{"role": "assistant", "content": "one"}, {"role": "tool", "content": "r"}, {"role": "assistant", "content": "two"}]
+    got = tok.decode([l for l in tok.encode_for_training(tail, train_on="last")[1] if l != IGNORE])
+    assert "one" in got and "two" in got and "It's a test" not in got
+    from surogate_b200.train.tokenize import loss_scale_mode
+
+    assert [loss_scale_mode(x) for x in ("default", "all", "last_round", "last_round+-", "-", "default+default")] == ["assistant", "all", "last", "last", "assistant", "assistant"]
+    with pytest.raises(ValueError):
+        loss_scale_mode("react")
 
 
 def test_token_loader_native_matches_python_and_resumes(tmp_path):

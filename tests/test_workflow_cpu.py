@@ -4,6 +4,7 @@ import os
 import sys
 
 import numpy as np
+import pytest
 
 from surogate_b200.train.dispatch_pp import plan_stages, wavefront
 
@@ -92,6 +93,14 @@ def test_sft_workflow_with_adapter_resume(tmp_path):
     r2 = run_training(SFTConfig.from_dict(dict(base, output_dir=str(tmp_path / "b"), adapter_path=str(tmp_path / "a" / "adapter"), adapter_init_mode="resume")))
     assert r2["steps"] == 3 and np.isfinite(r2["final"]["loss"])
     assert os.path.getsize(tmp_path / "metrics.jsonl") > 0
+    # ``trainable`` = resume with the parent checked against this run's LoRA settings
+    r3 = run_training(SFTConfig.from_dict(dict(base, output_dir=str(tmp_path / "c"), adapter_path=str(tmp_path / "a" / "adapter"), adapter_init_mode="trainable")))
+    assert r3["steps"] == 3 and abs(r3["losses"][0] - r2["losses"][0]) < 1e-6
+    with pytest.raises(ValueError, match="rank"):
+        run_training(SFTConfig.from_dict(dict(base, lora_rank=8, output_dir=str(tmp_path / "d"), adapter_path=str(tmp_path / "a" / "adapter"), adapter_init_mode="trainable")))
+    os.remove(tmp_path / "a" / "adapter" / "adapter_config.json")
+    with pytest.raises(FileNotFoundError, match="adapter_config.json"):
+        run_training(SFTConfig.from_dict(dict(base, output_dir=str(tmp_path / "e"), adapter_path=str(tmp_path / "a" / "adapter"), adapter_init_mode="merge")))
 
 
 def test_ray_launcher_places_one_task_per_node_on_a_stand_in_ray(monkeypatch):
