@@ -605,7 +605,7 @@ class SurogateTrainer:
 
     def get_lora_gradients(self, gpu_id: int = 0) -> Dict[str, Any]:
         lora = self.trainer.lora
-        return {} if lora is None else {name: g for name, g in lora.named_grads()} if hasattr(lora, "named_grads") else {}
+        return {} if lora is None else {name: g.detach().clone() for name, g in lora.named_grads()}
 
     def get_allocator_info(self, gpu_id: int = 0) -> Dict[str, int]:
         return dict(self.trainer.memory_breakdown())

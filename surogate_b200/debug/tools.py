@@ -95,25 +95,35 @@ def activation_stats(trainer, inputs: np.ndarray, targets: np.ndarray, out: Opti
     return write_jsonl(out, rows)
 
 
-def gradient_stats(trainer, inputs: np.ndarray, targets: np.ndarray, out: Optional[str] = None) -> List[Dict[str, Any]]:
-    trainer.forward_backward(inputs, targets)
-    rows = []
-    for name, g in trainer.get_gradients().items():
-        if g is not None:
-            rows.append({"param": name, **_stats(g)})
-    trainer.store.release_grads()
-    rows.sort(key=lambda r: -r["absmax"])
+def gradient_stats(trainer, inputs: np.ndarray, targets: np.ndarray, out: Optional[str] = None, steps: int = 1) -> List[Dict[str, Any]]:
+    """Per-parameter gradient statistics; with ``steps`` > 1 an optimizer update follows each capture, so degradation after a few
+    updates shows (rows carry ``step``)."""
+    rows: List[Dict[str, Any]] = []
+    for step in range(max(1, steps)):
+        trainer.forward_backward(inputs, targets)
+        now = [{"step": step, "param": name, **_stats(g)} for name, g in trainer.get_gradients().items() if g is not None]
+        if getattr(trainer, "lora", None) is not None:  # the base is frozen under LoRA: the adapters carry the gradients
+            now += [{"step": step, "param": name, **_stats(g)} for name, g in trainer.lora.named_grads()]
+        now.sort(key=lambda r: -r["absmax"])
+        rows += now
+        if step + 1 < steps:
+            trainer.optimizer_step()
+        else:
+            trainer.store.release_grads()
     return write_jsonl(out, rows)
 
 
-def diff_against_transformers(model_dir: str, tokens: np.ndarray, device: str = "cpu", out: Optional[str] = None, backend: str = "auto"):
-    """Hidden state after every block (and the logits) from both implementations on the same tokens."""
+def diff_against_transformers(model_dir: str, tokens: np.ndarray, device: str = "cpu", out: Optional[str] = None, backend: str = "auto",
+                              reference: Optional[str] = None, rtol: float = 1e-2, atol: float = 1e-3):
+    """Hidden state after every block (and the logits) from both implementations on the same tokens.  ``reference``: the
+    transformers model to compare with (default: ``model_dir``).  Rows carry ``diverged`` by the allclose rule
+    ``|a - b| <= atol + rtol |b|`` and the report ends with the first layer that diverged."""
     from transformers import AutoModelForCausalLM
 
     from ..dsl.compiler import load_hf_config
     from ..runtime.trainer import Trainer, TrainerConfig
 
-    hf = AutoModelForCausalLM.from_pretrained(model_dir, torch_dtype=torch.float32).to(device).eval()
+    hf = AutoModelForCausalLM.from_pretrained(reference or model_dir, torch_dtype=torch.float32).to(device).eval()
     with torch.no_grad():
         ref = hf(torch.from_numpy(tokens.astype(np.int64)).to(device), output_hidden_states=True)
     cfg = load_hf_config(model_dir)
@@ -138,9 +148,12 @@ def diff_against_transformers(model_dir: str, tokens: np.ndarray, device: str = 
         r = ref.hidden_states[L + 1].float()
         if L == len(mine) - 1 and r.shape == h.shape and (r - h).abs().max() > 1.0:
             continue  # transformers applies the final norm to the last hidden state
-        rows.append({"layer": L, "max_abs_diff": float((h - r).abs().max()), "rel": float((h - r).norm() / (r.norm() + 1e-12))})
-    rows.append({"logits": True, "max_abs_diff": float((logits - ref.logits.float()).abs().max()),
-                 "rel": float((logits - ref.logits.float()).norm() / (ref.logits.float().norm() + 1e-12))})
+        rows.append({"layer": L, "max_abs_diff": float((h - r).abs().max()), "rel": float((h - r).norm() / (r.norm() + 1e-12)),
+                     "diverged": not bool(torch.allclose(h, r, rtol=rtol, atol=atol))})
+    rl = ref.logits.float()
+    rows.append({"logits": True, "max_abs_diff": float((logits - rl).abs().max()), "rel": float((logits - rl).norm() / (rl.norm() + 1e-12)),
+                 "diverged": not bool(torch.allclose(logits.float(), rl, rtol=rtol, atol=atol))})
+    rows.append({"summary": True, "first_diverged_layer": next((r["layer"] for r in rows if r.get("diverged") and "layer" in r), None), "rtol": rtol, "atol": atol})
     return write_jsonl(out, rows)
 
 

@@ -361,6 +361,17 @@ class LoRAManager:
                 out[self._hf_key(g.layer, t.name, "B")] = self._B(self.master, t).detach().float().cpu().contiguous()
         return out
 
+    def named_grads(self):
+        """(PEFT key, gradient view) of every adapter matrix, over the flat fp32 gradient buffer (for debugging tools)."""
+        for g in self.groups.values():
+            for t in g.targets:
+                if g.experts:
+                    yield f"base_model.model.model.layers.{g.layer}.mlp.experts.*.{t.name}.lora_A.weight", self._EA(self.grad, g, t)
+                    yield f"base_model.model.model.layers.{g.layer}.mlp.experts.*.{t.name}.lora_B.weight", self._EB(self.grad, g, t)
+                else:
+                    yield self._hf_key(g.layer, t.name, "A"), self._A(self.grad, g, t)
+                    yield self._hf_key(g.layer, t.name, "B"), self._B(self.grad, t)
+
     def export_peft(self, out_dir: str, base_model: str = "", write: bool = True) -> None:
         if not write:
             return

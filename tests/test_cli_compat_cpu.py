@@ -343,3 +343,30 @@ def test_export_carries_the_tokenizer_files(tmp_path):
     (out / "tokenizer.json").write_text("kept")
     assert copy_tokenizer_files(str(src), str(out)) == [] and (out / "tokenizer.json").read_text() == "kept"
     assert copy_tokenizer_files(None, str(out)) == [] and copy_tokenizer_files(str(out), str(out)) == []
+
+
+def test_debug_commands_take_a_training_config(tmp_path, capsys):
+    """``surogate debug <sub> config.yaml --output report.jsonl``: model, sequence length and micro-batch come from the config; the
+    tracing commands build the model as the run would (LoRA), gradients can be followed over several updates."""
+    from surogate_b200.cli import debug as cli
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    model = dict(_tiny_model(), n_layers=2)
+    tr = Trainer(TrainerConfig(model=model, batch_size=1, seq_len=16, backend="torch", recipe="bf16", optimizer="adamw"), device=torch.device("cpu"))
+    tr.init_weights(0)
+    base = str(tmp_path / "base")
+    tr.export_model(base, model)
+    cfg = tmp_path / "cfg.yaml"
+    cfg.write_text(yaml.safe_dump(dict(model=base, sequence_len=24, per_device_train_batch_size=2, lora=True, lora_rank=4, lora_alpha=8, recipe="bf16", optimizer="adamw",
+                                       datasets=[{"path": "x.jsonl"}])))
+    target = cli.resolve_target(str(cfg))
+    assert target[0] == base and target[1:3] == (24, 2) and target[3].lora and cli.resolve_target(base) == (base, 128, 1, None)
+    assert cli.resolve_target(str(cfg), seq_len=8, batch=1)[1:3] == (8, 1)
+    out = tmp_path / "grads.jsonl"
+    assert cli.main(["gradients", str(cfg), "--output", str(out), "--steps", "2", "--seq-len", "12"]) == 0
+    rows = [json.loads(l) for l in open(out)]
+    assert {r["step"] for r in rows} == {0, 1} and all("lora" in r["param"].lower() for r in rows) and all(r["absmax"] == r["absmax"] for r in rows)
+    assert cli.main(["activations", str(cfg), "--output", str(tmp_path / "acts.jsonl")]) == 0
+    assert cli.main(["weights", str(cfg)]) == 0 and cli.main(["tensor-arena", str(cfg), "--output", str(tmp_path / "arena.jsonl")]) == 0
+    capsys.readouterr()
+    assert os.path.getsize(tmp_path / "acts.jsonl") > 0 and os.path.getsize(tmp_path / "arena.jsonl") > 0
