@@ -153,7 +153,7 @@ class OrchestratorConfig:
     top_p: float = 1.0
     seed: int = 0
     sequence_len: int = 2048
-    rows_per_step: int = 8               # packed rows handed to the trainer per optimizer step (all ranks together)
+    rows_per_step: int = 8               # packed rows handed to the trainer per optimizer step (all ranks together); 0 = as many as needed
     max_async_level: int = 2
     transport: str = "filesystem"
     transport_dir: str = "output/grpo/rollouts"

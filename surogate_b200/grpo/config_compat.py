@@ -103,9 +103,8 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
     flat["sequence_len"] = seq
     if raw.get("rows_per_step"):
         flat["rows_per_step"] = int(raw["rows_per_step"])
-    else:  # a guess from the batch's worst-case token count; the trainer consumes a fixed number of rows per step
-        flat["rows_per_step"] = max(1, -(-batch * min(seq, int(flat.get("max_tokens", seq)) + 256) // seq))
-        notes.append(f"rows_per_step not given: using {flat['rows_per_step']}; it must equal the trainer's per_device_train_batch_size x gradient_accumulation_steps x gpus")
+    else:  # as many packed rows as a step's rollouts need; the trainer pads them to a multiple of its micro-batch
+        flat["rows_per_step"] = 0
     for theirs, ours in (("max_steps", "max_steps"), ("max_off_policy_steps", "max_off_policy_steps"), ("max_async_level", "max_async_level"), ("seed", "seed"),
                          ("max_inflight_rollouts", "max_inflight"), ("max_concurrent", "workers")):
         if raw.get(theirs) is not None:

@@ -64,7 +64,8 @@ def _truncate(r: Rollout, T: int) -> Rollout:
 
 
 def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: int = 0) -> List[PackedBatch]:
-    """Pack into as many batches of ``rows`` rows as needed (the last one is padded with empty rows)."""
+    """Pack into as many batches of ``rows`` rows as needed (the last one is padded with empty rows).  ``rows <= 0``: one batch
+    with exactly as many rows as the samples need (the trainer pads it to a multiple of its micro-batch)."""
     T = seq_len
     samples = [_truncate(r, T) for r in rollouts if r.completion_ids]
     order = sorted(range(len(samples)), key=lambda i: -len(samples[i]))
@@ -80,6 +81,8 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
         else:
             bins.append([i])
             space.append(T - n)
+    if rows <= 0:
+        rows = max(1, len(bins))
     while len(bins) % rows != 0 or not bins:
         bins.append([])
     out: List[PackedBatch] = []

@@ -36,8 +36,24 @@ class GRPOTrainer:
         assert a.shape[0] == rows, f"batch has {a.shape[0]} rows, expected {rows} per rank"
         return a
 
+    def fit_rows(self, batch: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
+        """A batch with any number of rows: padded with empty rows (no targets, zero advantage) to a multiple of
+        ``batch_size x ranks``, and the number of micro-batches of this step set from it."""
+        t = self.t
+        unit = t.cfg.batch_size * t.world
+        n = batch["inputs"].shape[0]
+        padded = -(-n // unit) * unit
+        if padded != n:
+            fill = {"targets": -100, "seq_ids": -1}
+            batch = {k: (np.concatenate([v, np.full((padded - n,) + v.shape[1:], fill.get(k, 0), v.dtype)]) if isinstance(v, np.ndarray) and v.shape[:1] == (n,) else v)
+                     for k, v in batch.items()}
+        t.cfg.grad_accum = padded // unit
+        return batch
+
     def step(self, batch: Dict[str, np.ndarray], lr: Optional[float] = None) -> Dict[str, float]:
         t, L = self.t, self.loss
+        if batch["inputs"].shape[0] not in (t.cfg.batch_size * t.cfg.grad_accum, t.cfg.batch_size * t.cfg.grad_accum * t.world):
+            batch = self.fit_rows(batch)
         x, y, pos = self._slice(batch["inputs"]), self._slice(batch["targets"]), self._slice(batch["position_ids"])
         dev = t.device
         adv = torch.from_numpy(self._slice(batch["advantages"])).to(dev)

