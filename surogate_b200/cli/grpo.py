@@ -114,6 +114,8 @@ def main(argv, command: str = "grpo") -> int:
         orch = Orchestrator(cfg, Tokenizer.from_pretrained(cfg.model), client(cfg.base_url),
                             make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="producer"),
                             lambda: (b.latest() or {"version": -1})["version"])
+        if orch.judge is not None:
+            orch.judge.pool.wait_for_ready()   # a judge engine started next to this run needs a while to load
         orch.load_prompts()
         if raw.get("async_scheduler") or raw.get("scheduler") == "async":
             # asynchronous loop: bounded in-flight requests on a thread pool, difficulty pools, rollout filters, depth budget

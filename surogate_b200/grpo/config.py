@@ -165,3 +165,4 @@ class OrchestratorConfig:
     length_penalty: float = 0.0
     request_timeout_s: float = 600.0
     extra_sampling: Dict[str, Any] = field(default_factory=dict)
+    ruler: Dict[str, Any] = field(default_factory=dict)   # LLM-judge group reward (grpo/ruler.py): enabled, mode, judge_model, judge {base_url, ...}, rubric, weight ...

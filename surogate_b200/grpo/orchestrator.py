@@ -84,11 +84,23 @@ class Orchestrator:
             self.env = load_environment(cfg.environment, path=cfg.environments_path, **cfg.environment_args)
             reward_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
         self.reward_fn = reward_fn or resolve_reward(cfg.reward)
+        self.judge = None
+        if getattr(cfg, "ruler", None) and cfg.ruler.get("enabled"):
+            self.set_judge(cfg.ruler)
         self.depth = DepthController(cfg.max_async_level, policy_version)
         self.rng = np.random.default_rng(cfg.seed)
         self.prompts: List[Dict[str, Any]] = []
         self.buffer: List[Rollout] = []
         self.history: List[StepStats] = []
+
+    def set_judge(self, ruler, scorer=None) -> None:
+        """Switch the LLM-judge group reward on (``ruler``: the config section; ``scorer``: a ready ``RulerScorer``).  Single-turn
+        groups are judged through the reward function, multi-turn episodes with their whole conversation."""
+        from .ruler import build_ruler
+
+        self.judge = scorer or build_ruler(ruler)
+        if self.judge is not None:
+            self.reward_fn = self.judge.wrap_reward_fn(self.reward_fn)
 
     def load_prompts(self, rows: Optional[Sequence[Dict[str, Any]]] = None) -> None:
         if rows is None and self.env is not None:
@@ -112,6 +124,7 @@ class Orchestrator:
         Returns [(prompt_ids, token_ids, logprobs, mask, reward)]."""
         env = self.env
         out = []
+        conversations = []
         for _ in range(self.cfg.group_size):
             msgs = env.initial_messages(row)
             state = dict(env.setup_state(row), example=row)
@@ -140,6 +153,10 @@ class Orchestrator:
                 ctx = new_ctx
             reward, _ = env.score(row, dict(state, messages=msgs, completion=text, turns=turns))
             out.append((prompt0, comp, lps, mask, float(reward)))
+            conversations.append(msgs)
+        if self.judge is not None and out:
+            judged, _ = self.judge.apply(conversations, [o[4] for o in out])
+            out = [o[:4] + (float(r),) for o, r in zip(out, judged)]
         return out
 
     def collect(self, step: int, version: int) -> Tuple[List[Rollout], Dict[str, float]]:

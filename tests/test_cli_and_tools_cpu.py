@@ -186,10 +186,15 @@ def test_every_example_configuration_loads_and_validates():
             cfg = DPOConfig.from_dict(d)
         elif rel == os.path.join("grpo", "train.yaml"):
             cfg = GRPOConfig.from_dict(d)
-        elif rel == os.path.join("grpo", "infer.yaml"):
+        elif rel in (os.path.join("grpo", "infer.yaml"), os.path.join("ruler", "judge.yaml")):
             cfg = InferenceConfig(**d)
         elif rel == os.path.join("grpo", "orch.yaml"):
             cfg = OrchestratorConfig(**d)
+        elif rel == os.path.join("ruler", "orch.yaml"):
+            from surogate_b200.grpo.ruler import RulerConfig
+
+            cfg = OrchestratorConfig(**d)
+            assert RulerConfig.from_dict(cfg.ruler).mode == "replace" and cfg.rows_per_step == 0
         elif rel == os.path.join("grpo", "orch-async.yaml"):
             from surogate_b200.grpo.orchestration import async_config_from, make_filters
             from surogate_b200.grpo.orchestration.buffer import BufferConfig

@@ -209,7 +209,7 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
     assert flat["weight_broadcast"] == "nccl" and flat["transport"] == "zmq" and flat["zmq_endpoint"] == "tcp://10.0.0.1:5566"
     assert flat["weight_dir"] == os.path.join("outputs/run1", "weights") and flat["transport_dir"] == os.path.join("outputs/run1", "rollouts")
     text = "\n".join(notes)
-    assert "only the first" in text and "ruler" in text and "tasks_per_minute" in text and "skip_model_check" not in text
+    assert "only the first" in text and "ruler" not in text and flat["ruler"]["judge_model"] == "j" and "tasks_per_minute" in text and "skip_model_check" not in text
     # the flat result is a valid orchestrator config of this package
     from surogate_b200.config.loader import coerce_fields
 
