@@ -165,4 +165,5 @@ class OrchestratorConfig:
     length_penalty: float = 0.0
     request_timeout_s: float = 600.0
     extra_sampling: Dict[str, Any] = field(default_factory=dict)
+    teacher: Dict[str, Any] = field(default_factory=dict)  # {model, base_url, api_key_var, timeout}: a served teacher that scores every rollout's tokens (loss.teacher_tau)
     ruler: Dict[str, Any] = field(default_factory=dict)   # LLM-judge group reward (grpo/ruler.py): enabled, mode, judge_model, judge {base_url, ...}, rubric, weight ...

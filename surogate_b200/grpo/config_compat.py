@@ -167,7 +167,9 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
 
     if raw.get("ruler"):
         flat["ruler"] = dict(raw["ruler"])
-    for k in ("teacher_model", "val", "verification", "tasks_per_minute", "strict_async_level", "bench", "use_token_client", "dump_metrics", "learning_rate", "log", "report_to"):
+    if raw.get("teacher_model"):
+        flat["teacher"] = dict(raw["teacher_model"])
+    for k in ("val", "verification", "tasks_per_minute", "strict_async_level", "bench", "use_token_client", "dump_metrics", "learning_rate", "log", "report_to"):
         v = raw.get(k)
         if v not in (None, {}, [], False) and not (k == "verification" and v == {"enabled": True}) and k not in ("log", "report_to", "learning_rate", "use_token_client"):
             notes.append(f"{k}: not supported by this orchestrator, ignored")

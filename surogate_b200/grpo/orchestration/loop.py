@@ -271,6 +271,8 @@ def make_generate_group(orch) -> Callable[..., List[Rollout]]:
                 if ids:
                     turns = 1 + sum(1 for a, b in zip(mask, mask[1:]) if a == 0 and b == 1)
                     out.append(Rollout(pids, ids, lps, 0.0, float(r), version, 0, {"turns": turns, "truncated": cap is not None and turns >= int(cap)}, completion_mask=mask))
+            if getattr(orch, "teacher", None) is not None:
+                orch.teacher.score(out)
             return out
         pids = orch._prompt_ids(example)
         gens = pick(server).generate(pids, n, sampling)
@@ -280,6 +282,8 @@ def make_generate_group(orch) -> Callable[..., List[Rollout]]:
         for (ids, lps, _), r in zip(gens, rewards):
             if ids and len(lps) == len(ids):
                 out.append(Rollout(pids, ids, lps, 0.0, r, version, 0, {"turns": 1}))
+        if getattr(orch, "teacher", None) is not None:
+            orch.teacher.score(out)
         return out
 
     return generate_group

@@ -85,6 +85,11 @@ class Orchestrator:
             reward_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
         self.reward_fn = reward_fn or resolve_reward(cfg.reward)
         self.judge = None
+        self.teacher = None
+        if getattr(cfg, "teacher", None):
+            from .teacher import TeacherScorer
+
+            self.teacher = TeacherScorer.from_config(cfg.teacher)
         if getattr(cfg, "ruler", None) and cfg.ruler.get("enabled"):
             self.set_judge(cfg.ruler)
         self.depth = DepthController(cfg.max_async_level, policy_version)
@@ -194,6 +199,8 @@ class Orchestrator:
             for (ids, lps, _), a, r in zip(gens, adv, rewards):
                 if ids and len(lps) == len(ids):
                     rollouts.append(Rollout(pids, ids, lps, a, r, version, g))
+        if self.teacher is not None:
+            self.teacher.score(rollouts)
         stats = {"reward_mean": float(np.mean(rewards_all)) if rewards_all else 0.0, "reward_std": float(np.std(rewards_all)) if rewards_all else 0.0,
                  "completion_len": float(np.mean(lens)) if lens else 0.0, "groups_kept": kept, "groups_total": len(idx)}
         return rollouts, stats

@@ -30,6 +30,8 @@ class Rollout:
     # multi-turn rollouts: 1 for tokens the policy produced, 0 for environment tokens (tool results, turn markers) that sit
     # between its turns; None means every completion token is the policy's
     completion_mask: Optional[List[int]] = None
+    # log-prob of each completion token under a teacher model (``loss.teacher_tau``); None when no teacher scored the rollout
+    teacher_logprobs: Optional[List[float]] = None
 
     def __len__(self) -> int:
         return len(self.prompt_ids) + len(self.completion_ids)
@@ -45,10 +47,14 @@ class PackedBatch:
     seq_ids: np.ndarray       # int32 [rows, T]   (-1 = padding)
     policy_version: int = 0
     n_samples: int = 0
+    teacher_logprobs: Optional[np.ndarray] = None   # float32 [rows, T], present when every packed rollout carries teacher scores
 
     def arrays(self) -> Dict[str, np.ndarray]:
-        return {"inputs": self.inputs, "targets": self.targets, "position_ids": self.position_ids, "advantages": self.advantages,
-                "old_logprobs": self.old_logprobs, "seq_ids": self.seq_ids}
+        out = {"inputs": self.inputs, "targets": self.targets, "position_ids": self.position_ids, "advantages": self.advantages,
+               "old_logprobs": self.old_logprobs, "seq_ids": self.seq_ids}
+        if self.teacher_logprobs is not None:
+            out["teacher_logprobs"] = self.teacher_logprobs
+        return out
 
 
 def _truncate(r: Rollout, T: int) -> Rollout:
@@ -57,10 +63,11 @@ def _truncate(r: Rollout, T: int) -> Rollout:
     keep_c = max(1, T - len(r.prompt_ids))
     if keep_c < len(r.completion_ids) and len(r.prompt_ids) < T:
         return Rollout(r.prompt_ids, r.completion_ids[:keep_c], r.logprobs[:keep_c], r.advantage, r.reward, r.policy_version, r.group, r.meta,
-                       r.completion_mask[:keep_c] if r.completion_mask is not None else None)
+                       r.completion_mask[:keep_c] if r.completion_mask is not None else None,
+                       r.teacher_logprobs[:keep_c] if r.teacher_logprobs is not None else None)
     p = r.prompt_ids[-(T - 1):]
     return Rollout(p, r.completion_ids[:1], r.logprobs[:1], r.advantage, r.reward, r.policy_version, r.group, r.meta,
-                   r.completion_mask[:1] if r.completion_mask is not None else None)
+                   r.completion_mask[:1] if r.completion_mask is not None else None, r.teacher_logprobs[:1] if r.teacher_logprobs is not None else None)
 
 
 def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: int = 0) -> List[PackedBatch]:
@@ -87,6 +94,7 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
         bins.append([])
     out: List[PackedBatch] = []
     sid = 0
+    with_teacher = bool(samples) and all(s.teacher_logprobs is not None and len(s.teacher_logprobs) == len(s.completion_ids) for s in samples)
     for b0 in range(0, len(bins), rows):
         R = rows
         x = np.full((R, T), pad_id, np.int32)
@@ -95,6 +103,7 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
         adv = np.zeros((R, T), np.float32)
         old = np.zeros((R, T), np.float32)
         seq = np.full((R, T), -1, np.int32)
+        teach = np.zeros((R, T), np.float32) if with_teacher else None
         n_samples, version = 0, None
         for r, members in enumerate(bins[b0:b0 + rows]):
             at = 0
@@ -110,9 +119,13 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
                     lo += 1
                     y[r, lo:hi] = ids[1:]
                     old[r, lo:hi] = np.asarray(s.logprobs[1:], np.float32)
+                    if teach is not None:
+                        teach[r, lo:hi] = np.asarray(s.teacher_logprobs[1:], np.float32)
                 else:
                     y[r, lo:hi] = ids[P:]
                     old[r, lo:hi] = np.asarray(s.logprobs, np.float32)
+                    if teach is not None:
+                        teach[r, lo:hi] = np.asarray(s.teacher_logprobs, np.float32)
                 adv[r, lo:hi] = s.advantage
                 if s.completion_mask is not None:  # environment tokens are context only
                     m = np.asarray(s.completion_mask[(1 if P == 0 else 0):], bool)
@@ -124,5 +137,5 @@ def pack_rollouts(rollouts: Sequence[Rollout], seq_len: int, rows: int, pad_id: 
                 n_samples += 1
                 version = s.policy_version if version is None else min(version, s.policy_version)
             pos[r, at:] = np.arange(T - at)
-        out.append(PackedBatch(x, y, pos, adv, old, seq, version or 0, n_samples))
+        out.append(PackedBatch(x, y, pos, adv, old, seq, version or 0, n_samples, teach))
     return out

@@ -177,3 +177,63 @@ def test_orchestrator_uses_the_judge_for_single_and_multi_turn_groups():
         assert [round(e[4], 6) for e in eps] == [0.25 + 0.3, 0.25 + 0.6] and all(e[1] == [7, 8] for e in eps)
     finally:
         j.close()
+
+
+def test_teacher_scores_travel_from_the_server_to_the_packed_batch():
+    """A served teacher's ``prompt_logprobs`` become per-token ``teacher_logprobs`` of the rollouts, aligned with the targets in the
+    packed batch, and reach the ``ipo`` objective's teacher term."""
+    import numpy as np
+    import torch
+
+    from surogate_b200.grpo.config_compat import flatten_orchestrator_config
+    from surogate_b200.grpo.loss import ipo_token_weights
+    from surogate_b200.grpo.packer import Rollout, pack_rollouts
+    from surogate_b200.grpo.teacher import TeacherScorer
+
+    seen = []
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            seen.append(body)
+            ids = body["prompt"]
+            # position t: the teacher's log-prob of token t is -(t + 1) / 10; a second, wrong candidate is listed too
+            entries = [None] + [{str(tok): {"logprob": -(t + 1) / 10.0}, "99999": {"logprob": -9.0}} for t, tok in enumerate(ids[1:], 1)]
+            data = json.dumps({"choices": [{"prompt_logprobs": entries}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        flat, notes = flatten_orchestrator_config({"model": {"name": "m"}, "teacher_model": {"model": {"name": "big"}, "client": {"base_url": [f"http://127.0.0.1:{srv.server_port}/v1"],
+                                                                                                                   "api_key_var": None}}})
+        assert not any("teacher" in n for n in notes)
+        t = TeacherScorer.from_config(flat["teacher"])
+        rs = [Rollout([1, 2, 3], [4, 5], [-0.5, -0.6], 1.0), Rollout([7], [8, 9, 10], [-0.1, -0.2, -0.3], -1.0)]
+        t.score(rs)
+    finally:
+        srv.shutdown()
+    assert seen[0]["model"] == "big" and seen[0]["prompt"] == [1, 2, 3, 4, 5] and seen[0]["prompt_logprobs"] == 1
+    assert np.allclose(rs[0].teacher_logprobs, [-0.4, -0.5]) and np.allclose(rs[1].teacher_logprobs, [-0.2, -0.3, -0.4]) and t.tokens_scored == 5
+    batch = pack_rollouts(rs, 8, 0)[0].arrays()
+    y, teach, old = batch["targets"], batch["teacher_logprobs"], batch["old_logprobs"]
+    assert teach.shape == y.shape and ((teach != 0) == (y != -100)).all()
+    row = int(np.argmax((batch["inputs"][:, 0] == 1)))
+    assert np.allclose(teach[row][y[row] != -100], [-0.4, -0.5]) and np.allclose(old[row][y[row] != -100], [-0.5, -0.6])
+    assert "teacher_logprobs" not in pack_rollouts([Rollout([1], [2], [-0.1])], 8, 0)[0].arrays()
+    # the teacher term moves the weights: a token the teacher likes more than the policy gets a larger multiplier
+    logp = torch.from_numpy(old)
+    m = torch.from_numpy((y != -100).astype(np.float32))
+    adv = torch.from_numpy(batch["advantages"])
+    _, w0, _ = ipo_token_weights(logp, logp, adv, m, kl_tau=0.0)
+    _, w1, met = ipo_token_weights(logp, logp, adv, m, teacher_logp=torch.from_numpy(teach), teacher_tau=1.0, kl_tau=0.0)
+    assert torch.allclose((w1 - w0)[m.bool()], ((torch.from_numpy(teach) - logp) / m.sum())[m.bool()], atol=1e-7) and "teacher_kl" in met
+    with pytest.raises(ValueError):
+        TeacherScorer.from_config({"model": "x"})
+    assert TeacherScorer.from_config({}) is None
