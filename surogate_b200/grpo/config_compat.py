@@ -169,7 +169,14 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
         flat["ruler"] = dict(raw["ruler"])
     if raw.get("teacher_model"):
         flat["teacher"] = dict(raw["teacher_model"])
-    for k in ("val", "verification", "tasks_per_minute", "strict_async_level", "bench", "use_token_client", "dump_metrics", "learning_rate", "log", "report_to"):
+    if raw.get("tasks_per_minute"):
+        flat["tasks_per_minute"] = float(raw["tasks_per_minute"])
+    if raw.get("dump_metrics"):
+        flat["metrics_file"] = os.path.join(out_dir, "orchestrator_metrics.jsonl")
+    val = raw.get("val") or {}
+    if val:
+        flat.update(val_every=int(val.get("interval") or 10), val_examples=int(val.get("num_examples") or 16), val_samples=int(val.get("rollouts_per_example") or 1))
+    for k in ("verification", "strict_async_level", "bench", "use_token_client", "learning_rate", "log", "report_to"):
         v = raw.get(k)
         if v not in (None, {}, [], False) and not (k == "verification" and v == {"enabled": True}) and k not in ("log", "report_to", "learning_rate", "use_token_client"):
             notes.append(f"{k}: not supported by this orchestrator, ignored")

@@ -56,6 +56,11 @@ class AsyncOrchestratorConfig:
     eval_ks: Sequence[int] = (1, 4)
     eval_pass_threshold: float = 1.0
     temperature_schedule: Optional[Dict[str, Any]] = None   # {type: linear | cosine, start, end, total_steps}: sampling temperature by step
+    tasks_per_minute: Optional[float] = None   # cap on group requests per minute
+    val_every: int = 0                         # every this many steps: rollouts on ``val_examples`` training prompts, rewards logged, nothing trained
+    val_examples: int = 16
+    val_samples: int = 1
+    metrics_file: Optional[str] = None         # every step's metrics as one JSON line (``dump_metrics``)
     poll_s: float = 0.01
     step_timeout_s: float = 3600.0
     vocab_size: int = 32000
@@ -124,7 +129,7 @@ class AsyncOrchestrator:
         self.pool = ThreadPoolExecutor(max_workers=cfg.workers, thread_name_prefix="rollout")
         self.generate_group = generate_group
         sc = SchedulerConfig(batch_size=cfg.batch_size, token_batch_size=cfg.token_batch_size, group_size=cfg.group_size, max_inflight=cfg.max_inflight,
-                             max_async_level=cfg.max_async_level, max_off_policy_steps=cfg.max_off_policy_steps)
+                             max_async_level=cfg.max_async_level, max_off_policy_steps=cfg.max_off_policy_steps, tasks_per_minute=cfg.tasks_per_minute)
         self.scheduler = RolloutScheduler(sc, self.buffer, self._submit, self._poll, self._cancel, num_servers)
         self.scheduler.set_sampling_args(cfg.sampling)
         self.filters = make_filters(cfg.filters, cfg.vocab_size)
@@ -221,12 +226,30 @@ class AsyncOrchestrator:
 
             out.update(evaluate_policy(self.eval_examples, self.generate_group, self.cfg.eval_samples, self.cfg.sampling, max(0, self.policy_version()),
                                        self.cfg.eval_ks, self.cfg.eval_pass_threshold, self.num_servers))
+        if self.cfg.val_every and (step + 1) % self.cfg.val_every == 0:
+            out.update(self.validate())
+        if self.cfg.metrics_file:
+            os.makedirs(os.path.dirname(os.path.abspath(self.cfg.metrics_file)), exist_ok=True)
+            with open(self.cfg.metrics_file, "a") as f:
+                f.write(json.dumps(out, default=float) + "\n")
         if self.ckpt is not None and self.cfg.checkpoint_every and (step + 1) % self.cfg.checkpoint_every == 0:
             self.ckpt.save(self.progress, self.buffer)
         self.history.append(out)
         if self.on_step is not None:
             self.on_step(out)
         return out
+
+    def validate(self) -> Dict[str, float]:
+        """Rollouts on a fixed sample of the training prompts with the current policy: the reward trend on known prompts, outside
+        the training batches (no pools are updated, nothing is sent to the trainer)."""
+        from .evaluation import evaluate_policy
+
+        pool = [e for name in self.buffer.pools.values() for env in name.values() for e in env.values()]
+        pool.sort(key=lambda e: e.get("example_id", 0))
+        sample = pool[:max(1, self.cfg.val_examples)]
+        res = evaluate_policy(sample, self.generate_group, self.cfg.val_samples, self.cfg.sampling, max(0, self.policy_version()), (1,), self.cfg.eval_pass_threshold,
+                              self.num_servers)
+        return {k.replace("eval/", "val/"): v for k, v in res.items()}
 
     def run(self) -> List[Dict[str, float]]:
         try:
@@ -302,5 +325,7 @@ def async_config_from(cfg, raw: Optional[Dict[str, Any]] = None, vocab_size: int
                                 sampling={"max_tokens": cfg.max_tokens, "temperature": cfg.temperature, "top_p": cfg.top_p, **cfg.extra_sampling},
                                 checkpoint_dir=raw.get("checkpoint_dir"), checkpoint_every=int(raw.get("checkpoint_every", 0)),
                                 keep_checkpoints=int(raw.get("keep_checkpoints", 2)), eval_every=int(raw.get("eval_every", 0)), eval_samples=int(raw.get("eval_samples", 4)),
-                                temperature_schedule=raw.get("temperature_schedule"), vocab_size=vocab_size, pad_token_id=pad_token_id)
+                                temperature_schedule=raw.get("temperature_schedule"), tasks_per_minute=raw.get("tasks_per_minute"),
+                                val_every=int(raw.get("val_every", 0)), val_examples=int(raw.get("val_examples", 16)), val_samples=int(raw.get("val_samples", 1)),
+                                metrics_file=raw.get("metrics_file"), vocab_size=vocab_size, pad_token_id=pad_token_id)
     return a

@@ -29,6 +29,7 @@ class SchedulerConfig:
     max_inflight: int = 16               # group requests outstanding
     max_async_level: int = 2
     max_off_policy_steps: int = 4
+    tasks_per_minute: Optional[float] = None   # cap on group requests issued per minute (rate-limited inference APIs)
 
 
 @dataclass
@@ -51,6 +52,7 @@ class RolloutScheduler:
                  cancel: Optional[Callable[[Any], None]] = None, num_servers: int = 1):
         self.cfg, self.buffer, self._submit, self._poll, self._cancel = cfg, buffer, submit, poll, cancel
         self.num_servers = max(1, num_servers)
+        self.clock: Optional[Callable[[], float]] = None   # seconds; tests inject one, the default is time.monotonic
         self.inflight: List[_Inflight] = []
         self.ready: List[_Ready] = []
         self.requeued: List[Dict[str, Any]] = []
@@ -108,7 +110,7 @@ class RolloutScheduler:
     def fill(self, step: int) -> int:
         """Issue requests until ``max_inflight`` are outstanding (as long as generation may run at ``step``)."""
         issued = 0
-        while len(self.inflight) < self.cfg.max_inflight and self.may_issue(step):
+        while len(self.inflight) < self.cfg.max_inflight and self.may_issue(step) and self._rate_allows():
             ex = self.requeued.pop(0) if self.requeued else (self.buffer.sample_examples(1) or [None])[0]
             if ex is None:
                 break
@@ -118,6 +120,25 @@ class RolloutScheduler:
             self.inflight.append(_Inflight(handle, ex, self.trainer_version, server))
             issued += 1
         return issued
+
+    def _rate_allows(self) -> bool:
+        """Token bucket for ``tasks_per_minute``: one token per request, refilled continuously, at most one minute's worth saved up."""
+        rate = self.cfg.tasks_per_minute
+        if not rate or rate <= 0:
+            return True
+        import time
+
+        now = (self.clock or time.monotonic)()
+        last = getattr(self, "_rate_last", None)
+        tokens = getattr(self, "_rate_tokens", 1.0)
+        if last is not None:
+            tokens = min(float(rate), tokens + (now - last) * rate / 60.0)
+        self._rate_last = now
+        if tokens < 1.0:
+            self._rate_tokens = tokens
+            return False
+        self._rate_tokens = tokens - 1.0
+        return True
 
     def collect(self) -> int:
         """Move finished groups from in-flight to ready; returns how many finished."""

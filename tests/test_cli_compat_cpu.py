@@ -192,7 +192,7 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
         "filters": [{"type": "gibberish", "token_id_threshold": 100000, "logprob_offset": 2.0}, {"type": "repetition", "window": 3000, "prob_threshold": 0.99, "enforce": True}],
         "ckpt": {"interval": 25, "keep_last": 3}, "eval": {"interval": 50, "rollouts_per_example": 2, "num_examples": 32},
         "weight_broadcast": {"type": "nccl", "port": 29501}, "rollout_transport": {"type": "zmq", "host": "10.0.0.1", "port": 5566},
-        "ruler": {"enabled": True, "judge_model": "j"}, "tasks_per_minute": 10.0,
+        "ruler": {"enabled": True, "judge_model": "j"}, "tasks_per_minute": 10.0, "dump_metrics": True, "val": {"interval": 5, "num_examples": 8}, "strict_async_level": True,
     }
     flat, notes = flatten_orchestrator_config(nested)
     assert flat["scheduler"] == "async" and flat["model"] == "Qwen/Qwen3-4B" and flat["served_model"] == "policy"
@@ -209,7 +209,8 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
     assert flat["weight_broadcast"] == "nccl" and flat["transport"] == "zmq" and flat["zmq_endpoint"] == "tcp://10.0.0.1:5566"
     assert flat["weight_dir"] == os.path.join("outputs/run1", "weights") and flat["transport_dir"] == os.path.join("outputs/run1", "rollouts")
     text = "\n".join(notes)
-    assert "only the first" in text and "ruler" not in text and flat["ruler"]["judge_model"] == "j" and "tasks_per_minute" in text and "skip_model_check" not in text
+    assert "only the first" in text and "ruler" not in text and flat["ruler"]["judge_model"] == "j" and "strict_async_level" in text and "tasks_per_minute" not in text and flat["tasks_per_minute"] == 10.0
+    assert flat["metrics_file"].endswith("orchestrator_metrics.jsonl") and (flat["val_every"], flat["val_examples"], flat["val_samples"]) == (5, 8, 1) and "skip_model_check" not in text
     # the flat result is a valid orchestrator config of this package
     from surogate_b200.config.loader import coerce_fields
 

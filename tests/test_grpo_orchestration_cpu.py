@@ -287,3 +287,45 @@ def test_periodic_evaluation_reports_pass_at_k_without_feeding_the_trainer(tmp_p
     assert "eval/pass@1" not in hist[0] and abs(hist[1]["eval/pass@1"] - 0.5) < 1e-12
     _, meta = tr.receive(1, timeout_s=1)
     assert meta["n_samples"] == 8              # the evaluation rollouts did not join the batch
+
+
+def test_rate_limit_validation_rollouts_and_metrics_file(tmp_path):
+    import json
+
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, AsyncOrchestratorConfig
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    # token bucket: 30 requests per minute = one every two seconds, the first one at once
+    ex = [{"prompt": f"q{i}", "example_id": i} for i in range(50)]
+    buf = ExampleBuffer(ex, BufferConfig(seed=0))
+    issued = []
+    s = RolloutScheduler(SchedulerConfig(batch_size=8, group_size=4, max_inflight=100, max_async_level=4, tasks_per_minute=30.0), buf,
+                         lambda e, v, srv: issued.append(e) or len(issued), lambda h: None)
+    now = [100.0]
+    s.clock = lambda: now[0]
+    assert s.fill(0) == 1 and s.fill(0) == 0
+    now[0] += 1.9
+    assert s.fill(0) == 0
+    now[0] += 0.2
+    assert s.fill(0) == 1
+    now[0] += 600.0                                # a long pause saves up at most one minute's worth
+    assert s.fill(0) == 30
+    unlimited = RolloutScheduler(SchedulerConfig(batch_size=8, group_size=4, max_inflight=7, max_async_level=4), buf, lambda e, v, srv: 1, lambda h: None)
+    assert unlimited.fill(0) == 7
+
+    calls = {"n": 0}
+
+    def generate_group(example, n, sampling, version, server):
+        calls["n"] += 1
+        return [_rollout(float(k % 2), n=5 + k) for k in range(n)]
+
+    train = [{"prompt": f"q{i}"} for i in range(6)]
+    cfg = AsyncOrchestratorConfig(group_size=4, batch_size=8, sequence_len=64, rows_per_step=0, max_steps=2, max_inflight=4, workers=2, val_every=2, val_examples=3,
+                                  val_samples=2, metrics_file=str(tmp_path / "m" / "metrics.jsonl"))
+    tr = FilesystemTransport(str(tmp_path / "t"))
+    hist = AsyncOrchestrator(cfg, train, generate_group, tr, lambda: 0).run()
+    assert "val/mean_reward" not in hist[0] and abs(hist[1]["val/mean_reward"] - 0.5) < 1e-12 and hist[1]["val/examples"] == 3.0
+    rows = [json.loads(l) for l in open(tmp_path / "m" / "metrics.jsonl")]
+    assert len(rows) == 2 and rows[1]["val/mean_reward"] == 0.5 and "reward/mean" in rows[0]
+    batch, meta = tr.receive(1, timeout_s=1)
+    assert meta["n_samples"] == 8 and batch["inputs"].shape[0] >= 1      # validation rollouts did not join the batch; rows as needed
