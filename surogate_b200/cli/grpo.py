@@ -62,7 +62,7 @@ def _run_all(argv, command: str) -> int:
         for c in comps:
             print(json.dumps({"name": c.name, "argv": c.argv, "env": c.env}))
         return 0
-    return Supervisor(comps).run()
+    return Supervisor(comps, reap=True).run()
 
 
 def main(argv, command: str = "grpo") -> int:

@@ -71,11 +71,65 @@ class Component:
     proc: Optional[subprocess.Popen] = None
 
 
+PR_SET_CHILD_SUBREAPER = 36  # <linux/prctl.h>
+
+
+def set_child_subreaper() -> bool:
+    """Make this process the reaper of its orphaned descendants (``prctl(PR_SET_CHILD_SUBREAPER)``): a worker whose parent dies
+    mid-run then re-parents to the supervisor instead of to PID 1, so it stays inside the tree that the final walk of ``stop_all``
+    sees.  Engine workers started by ``multiprocessing`` spawn are the case in point: they sit outside the engine's session group
+    and outlive a ``killpg``.  Best effort: False where the call does not exist.
+    Parity: docs/superpowers/specs/2026-07-06-grpo-vllm-subprocess-reap-design.md (surogate/grpo/split.py)."""
+    try:
+        import ctypes
+
+        libc = ctypes.CDLL("libc.so.6", use_errno=True)
+        return libc.prctl(PR_SET_CHILD_SUBREAPER, 1, 0, 0, 0) == 0
+    except (OSError, AttributeError):
+        return False
+
+
+def reap_descendants(grace_s: float = 5.0, log=print, exclude=()) -> int:
+    """SIGTERM, then after ``grace_s`` SIGKILL, every process that is still a descendant of this one; by PID, so neither the
+    launching shell (a parent, never a descendant) nor anybody else's process can be hit.  Returns how many were found."""
+    try:
+        import psutil
+    except ImportError:
+        return 0
+    survivors = [p for p in psutil.Process().children(recursive=True) if p.pid not in exclude and p.is_running() and p.status() != psutil.STATUS_ZOMBIE]
+    for p in survivors:
+        try:
+            p.terminate()
+        except psutil.Error:
+            pass
+    _, alive = psutil.wait_procs(survivors, timeout=grace_s)
+    for p in alive:
+        try:
+            log(f"[grpo] pid {p.pid} ({p.name()}) survived SIGTERM: SIGKILL")
+            p.kill()
+        except psutil.Error:
+            pass
+    psutil.wait_procs(alive, timeout=grace_s)
+    return len(survivors)
+
+
 class Supervisor:
-    def __init__(self, components: Sequence[Component], grace_s: float = 10.0, poll_s: float = 0.2, log=print):
-        self.components, self.grace, self.poll, self.log = list(components), grace_s, poll_s, log
+    def __init__(self, components: Sequence[Component], grace_s: float = 10.0, poll_s: float = 0.2, log=print, reap: bool = False):
+        """``reap``: own the whole descendant tree (subreaper flag at start, a final walk that ends every descendant that was not
+        there before ``start``).  The command-line runs switch it on; a program that embeds a supervisor next to children of its
+        own leaves it off."""
+        self.components, self.grace, self.poll, self.log, self.reap = list(components), grace_s, poll_s, log, reap
+        self._before: set = set()
 
     def start(self) -> None:
+        if self.reap:
+            set_child_subreaper()   # before the first child: orphans of the components come back to this process
+            try:
+                import psutil
+
+                self._before = {p.pid for p in psutil.Process().children(recursive=True)}
+            except ImportError:
+                pass
         for c in self.components:
             env = dict(os.environ)
             env.update(c.env)
@@ -106,6 +160,10 @@ class Supervisor:
                     c.proc.wait(timeout=self.grace)
                 except subprocess.TimeoutExpired:
                     pass
+        if self.reap:   # workers that left their component's process group (re-parented to this process by the subreaper flag)
+            n = reap_descendants(min(self.grace, 5.0), self.log, exclude=self._before)
+            if n:
+                self.log(f"[grpo] reaped {n} leftover process(es)")
 
     def wait(self, timeout_s: Optional[float] = None) -> int:
         """Returns the run's exit code: 0 when the trainer finished, else the failing component's code."""

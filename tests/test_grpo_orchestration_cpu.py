@@ -329,3 +329,36 @@ def test_rate_limit_validation_rollouts_and_metrics_file(tmp_path):
     assert len(rows) == 2 and rows[1]["val/mean_reward"] == 0.5 and "reward/mean" in rows[0]
     batch, meta = tr.receive(1, timeout_s=1)
     assert meta["n_samples"] == 8 and batch["inputs"].shape[0] >= 1      # validation rollouts did not join the batch; rows as needed
+
+
+def test_supervisor_reaps_workers_that_left_their_process_group(tmp_path):
+    """A component starts a worker in a session of its own and dies: with the subreaper flag the worker re-parents to the
+    supervisor's process and the final walk ends it (a ``killpg`` of the component's group alone would miss it)."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    import time
+
+    import psutil
+
+    script = textwrap.dedent(f"""
+        import os, sys, time
+        sys.path.insert(0, {os.getcwd()!r})
+        from surogate_b200.grpo.runners import Component, Supervisor
+        worker = "import time, os; open({str(tmp_path / 'worker.pid')!r}, 'w').write(str(os.getpid())); time.sleep(300)"
+        comp = ("import subprocess, sys, time; subprocess.Popen([sys.executable, '-c', " + repr(worker) + "], start_new_session=True); time.sleep(1.0); sys.exit(3)")
+        sup = Supervisor([Component("engine", [sys.executable, "-c", comp], {{}})], grace_s=2.0, poll_s=0.05, log=lambda m: print(m, flush=True), reap=True)
+        rc = sup.run(timeout_s=30)
+        print("rc", rc, flush=True)
+    """)
+    p = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=120)
+    assert "rc 3" in p.stdout, p.stdout + p.stderr
+    pid = int(open(tmp_path / "worker.pid").read())
+    deadline = time.time() + 5
+    while psutil.pid_exists(pid) and time.time() < deadline:
+        time.sleep(0.05)
+    gone = not psutil.pid_exists(pid) or psutil.Process(pid).status() == psutil.STATUS_ZOMBIE
+    if not gone:
+        os.kill(pid, 9)
+    assert gone and "reaped 1 leftover" in p.stdout, p.stdout
