@@ -127,6 +127,18 @@ def test_upcycle_quantize_and_generate(tmp_path):
     assert torch.allclose(a, b, atol=2e-2, rtol=2e-2)  # bf16 export in between
     out = generate(tr, None, tok[0, :4].tolist(), max_new_tokens=5, eos_id=None)
     assert len(out) == 5 and all(0 <= t < 600 for t in out)
+    # health check: fresh experts are clones and the near-zero router is close to random; noisy experts have diverged
+    from surogate_b200.utils.expert_divergence import expert_divergence, verdict
+
+    rep = expert_divergence(moe_dir, tokens=64)
+    assert rep["num_experts"] == 4 and rep["expert_similarity"] > 0.9999 and rep["experts"].startswith("clones") and set(rep["projections"]) == {"gate_proj", "up_proj", "down_proj"}
+    assert rep["router"]["random_level"] == 0.25 and rep["router"]["mean_top1_probability"] < 0.35
+    noisy = os.path.join(tmp_path, "moe_noisy")
+    upcycle(src, noisy, num_experts=4, top_k=2, noise=0.5)
+    assert expert_divergence(noisy, layer=0, tokens=0)["expert_similarity"] < 0.99
+    assert verdict(0.9995).startswith("barely") and verdict(0.5) == "specialised"
+    with pytest.raises(ValueError, match="not a mixture-of-experts"):
+        expert_divergence(src)
     q_dir = os.path.join(tmp_path, "fp8")
     rep = quantize_checkpoint(src, q_dir)
     assert rep["quantized"] == 2 * 7  # q, k, v, o, gate, up, down per layer; embeddings, norms and the head keep their dtype
