@@ -146,6 +146,7 @@ class OrchestratorConfig:
     environment: str = ""                # an environment id (grpo/environments, or a scaffolded one): supplies prompts and the reward
     environment_args: Dict[str, Any] = field(default_factory=dict)
     environments_path: str = "./environments"
+    environment_import_path: str = ""    # a directory put in front of sys.path before importing the environment's package (a local checkout)
     group_size: int = 8                  # rollouts per prompt
     prompts_per_step: int = 8
     max_tokens: int = 512

@@ -86,7 +86,7 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
         flat["environment"] = e0.get("id") or e0.get("name") or ""
         flat["environment_args"] = dict(e0.get("args") or {}, **(e0.get("extra_env_kwargs") or {}))
         if e0.get("path"):
-            flat["environments_path"] = e0["path"]
+            flat["environment_import_path"] = e0["path"]
         if e0.get("address"):
             notes.append("env[0].address: environments run inside the orchestrator process here, no environment server is contacted")
         if len(envs) > 1:
@@ -99,7 +99,7 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
     flat["prompts_per_step"] = max(1, batch // max(1, rollouts))
     if raw.get("token_batch_size"):
         flat["token_batch_size"] = int(raw["token_batch_size"])
-    seq = int(raw.get("sequence_len") or 2048)
+    seq = int(raw.get("sequence_len") or raw.get("seq_len") or 2048)
     flat["sequence_len"] = seq
     if raw.get("rows_per_step"):
         flat["rows_per_step"] = int(raw["rows_per_step"])

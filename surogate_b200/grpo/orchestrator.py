@@ -81,7 +81,8 @@ class Orchestrator:
         if cfg.environment and reward_fn is None:  # single-turn scoring of the sampled completions by the environment's rubric
             from .environments import as_reward_fn, load_environment
 
-            self.env = load_environment(cfg.environment, path=cfg.environments_path, **cfg.environment_args)
+            self.env = load_environment(cfg.environment, path=cfg.environments_path, import_path=getattr(cfg, "environment_import_path", "") or None,
+                                        **cfg.environment_args)
             reward_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
         self.reward_fn = reward_fn or resolve_reward(cfg.reward)
         self.judge = None
