@@ -124,7 +124,15 @@ def make_example(rng: random.Random) -> Dict[str, Any]:
     return {"prompt": [{"role": "user", "content": f"{md}\n\n{q}"}], "answer": answer, "info": {"qtype": qtype, "column": col, "region": region, "table": md}}
 
 
-def load_environment(num_train: int = 512, num_eval: int = 64, seed: int = 0, **_) -> SingleTurnEnv:
+def load_environment(num_train: int = 512, num_eval: int = 64, seed: int = 0, max_examples: int = -1, **other) -> SingleTurnEnv:
+    """Tables and questions are generated from the seed (nothing is downloaded), so ``hf_repo`` / ``split`` / ``focus_types`` of
+    configs written for a hosted copy of the task are accepted without effect; ``max_examples`` > 0 is the other spelling of
+    ``num_train``."""
+    unknown = sorted(k for k in other if k not in ("hf_repo", "split", "focus_types", "score_rollouts", "max_seq_len", "seq_len"))
+    if unknown:
+        raise ValueError(f"unrecognised arguments for markdown-table-qa: {unknown}")
+    if max_examples and int(max_examples) > 0:
+        num_train = int(max_examples)
     rng = random.Random(seed)
     env = SingleTurnEnv([make_example(rng) for _ in range(num_train)], Rubric([correctness_reward]), [make_example(rng) for _ in range(num_eval)], SYSTEM_PROMPT)
     env.env_id = "markdown-table-qa"

@@ -81,12 +81,26 @@ def correctness_reward(completion, answer, **_) -> float:
     return 1.0 if m and norm(m.group(1)) == norm(str(answer)) else 0.0
 
 
-def load_environment(num_train: int = 256, num_eval: int = 32, hops: int = 3, max_turns: int = 8, seed: int = 0, **_) -> MultiHopToolEnv:
+IGNORED_ARGS = ("score_rollouts", "max_seq_len", "seq_len", "n_chains")  # set by orchestrators of other layouts; nothing here depends on them
+
+
+def load_environment(num_train: int = 256, num_eval: int = 32, hops: int = 3, max_turns: int = 8, seed: int = 0, num_examples: int = 0, min_hops: int = 0,
+                     max_hops: int = 0, **other) -> MultiHopToolEnv:
+    """``num_examples`` is the other spelling of ``num_train``; ``min_hops`` / ``max_hops`` draw the number of hops per question from
+    a range instead of the fixed ``hops``."""
+    unknown = sorted(k for k in other if k not in IGNORED_ARGS)
+    if unknown:
+        raise ValueError(f"unrecognised arguments for multihop-tools: {unknown}")
     rng = random.Random(seed)
+    num_train = int(num_examples) or num_train
+    lo, hi = (int(min_hops) or hops, int(max_hops) or hops) if (min_hops or max_hops) else (hops, hops)
+    if lo > hi:
+        raise ValueError(f"min_hops {lo} exceeds max_hops {hi}")
 
     def example():
         world = build_world(rng)
-        q, a = make_question(world, rng, hops)
-        return {"prompt": [{"role": "user", "content": q}], "answer": a, "info": {"world": world, "hops": hops}}
+        n = rng.randint(lo, hi)
+        q, a = make_question(world, rng, n)
+        return {"prompt": [{"role": "user", "content": q}], "answer": a, "info": {"world": world, "hops": n}}
 
     return MultiHopToolEnv([example() for _ in range(num_train)], Rubric([correctness_reward]), [example() for _ in range(num_eval)], SYSTEM_PROMPT, max_turns=max_turns)

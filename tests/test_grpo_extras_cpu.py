@@ -89,3 +89,34 @@ def test_engine_side_weight_receivers_on_a_stand_in_worker(tmp_path):
     cw = worker(ColocateWeightReceiver)
     payload = {"version": 7, "handles": {n: ((lambda x: x), (t,)) for n, t in named.items()}}
     assert cw.receive_ipc_handles(payload) == {"tensors": 2, "version": 7} and len(cw.model_runner.model.got) == 2
+
+
+def test_built_in_environments_take_both_spellings_of_their_arguments(tmp_path):
+    import json
+
+    import pytest
+
+    from surogate_b200.grpo.environments import load_environment
+
+    env = load_environment("multihop-tools", num_examples=12, n_chains=120, min_hops=2, max_hops=4, max_turns=12, seed=1, score_rollouts=True)
+    hops = {ex["info"]["hops"] for ex in env.dataset}
+    assert len(env.dataset) == 12 and hops <= {2, 3, 4} and len(hops) > 1 and env.max_turns == 12
+    assert {ex["info"]["hops"] for ex in load_environment("multihop-tools", num_train=5, hops=3).dataset} == {3}
+    with pytest.raises(ValueError, match="unrecognised"):
+        load_environment("multihop-tools", num_exampels=3)
+    with pytest.raises(ValueError, match="exceeds"):
+        load_environment("multihop-tools", min_hops=5, max_hops=2)
+    assert len(load_environment("markdown-table-qa", max_examples=7, hf_repo="x/y", split="train", focus_types="lookup").dataset) == 7
+    with pytest.raises(ValueError, match="unrecognised"):
+        load_environment("markdown-table-qa", rows=3)
+    data = tmp_path / "tasks.jsonl"
+    data.write_text("".join(json.dumps({"input": f"task {i}", "question": f"q{i}", "answer": str(i)}) + "\n" for i in range(10)))
+    a = load_environment("ruler-task", task_name="support", dataset=str(data), max_examples=4, system_prompt="be kind", seed=3, shuffle=True)
+    assert len(a.dataset) == 4 and a.dataset[0]["prompt"][0]["content"].startswith("task ") and a.dataset[0]["task"] == "support" and a.system_prompt == "be kind"
+    assert {ex["info"]["task_name"] for ex in a.dataset} == {"support"}
+    b = load_environment("ruler-task", dataset_path=str(data), max_examples=-1)
+    assert len(b.dataset) == 10 and b.dataset[2]["prompt"][0]["content"] == "q2"
+    with pytest.raises(ValueError, match="unrecognised"):
+        load_environment("ruler-task", dataset=str(data), taskname="x")
+    with pytest.raises(ValueError, match="needs dataset_path"):
+        load_environment("ruler-task")
