@@ -130,7 +130,7 @@ def main(argv, command: str = "grpo") -> int:
             if acfg.eval_every and orch.env is not None and getattr(orch.env, "eval_dataset", None):
                 eval_rows = [dict(ex, prompt=orch.env.initial_messages(ex)) for ex in orch.env.eval_dataset][:raw.get("eval_examples") or None]
             loop = AsyncOrchestrator(acfg, orch.prompts, make_generate_group(orch), orch.transport, lambda: (b.latest() or {"version": -1})["version"],
-                                     num_servers=len(urls), eval_examples=eval_rows)
+                                     num_servers=len(urls), eval_examples=eval_rows, env_names=list(orch.envs) or None)
             hist = loop.run()
             print(json.dumps({"steps": len(hist), "last_reward_mean": hist[-1].get("reward/mean") if hist else None}))
             return 0

@@ -145,6 +145,7 @@ class OrchestratorConfig:
     reward: str = "exact_match"          # name in grpo.rewards.REWARDS or "module:function"
     environment: str = ""                # an environment id (grpo/environments, or a scaffolded one): supplies prompts and the reward
     environment_args: Dict[str, Any] = field(default_factory=dict)
+    environments: List[Dict[str, Any]] = field(default_factory=list)   # several environments training together: [{id, name, args, path}]; prompts carry `task` = name
     environments_path: str = "./environments"
     environment_import_path: str = ""    # a directory put in front of sys.path before importing the environment's package (a local checkout)
     group_size: int = 8                  # rollouts per prompt

@@ -90,7 +90,8 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
         if e0.get("address"):
             notes.append("env[0].address: environments run inside the orchestrator process here, no environment server is contacted")
         if len(envs) > 1:
-            notes.append(f"env: {len(envs)} environments given, only the first ('{flat['environment']}') is used")
+            flat["environments"] = [{"id": e.get("id") or e.get("name"), "name": e.get("name"), "args": dict(e.get("args") or {}), "path": e.get("path"),
+                                     "extra_env_kwargs": dict(e.get("extra_env_kwargs") or {})} for e in envs]
 
     rollouts = int(raw.get("rollouts_per_example") or 1)
     batch = int(raw.get("batch_size") or 128)

@@ -122,10 +122,10 @@ class AsyncOrchestrator:
 
     def __init__(self, cfg: AsyncOrchestratorConfig, examples: Sequence[Dict[str, Any]], generate_group: Callable[..., List[Rollout]], transport,
                  policy_version: Callable[[], int], num_servers: int = 1, on_step: Optional[Callable[[Dict[str, float]], None]] = None,
-                 eval_examples: Optional[Sequence[Dict[str, Any]]] = None):
+                 eval_examples: Optional[Sequence[Dict[str, Any]]] = None, env_names: Optional[Sequence[str]] = None):
         self.cfg, self.transport, self.policy_version, self.on_step = cfg, transport, policy_version, on_step
         self.eval_examples, self.num_servers = list(eval_examples or []), max(1, num_servers)
-        self.buffer = ExampleBuffer(examples, BufferConfig(**cfg.buffer))
+        self.buffer = ExampleBuffer(examples, BufferConfig(**cfg.buffer), env_names)   # ``env_names`` fixes the order ``buffer.env_ratios`` refers to
         self.pool = ThreadPoolExecutor(max_workers=cfg.workers, thread_name_prefix="rollout")
         self.generate_group = generate_group
         sc = SchedulerConfig(batch_size=cfg.batch_size, token_batch_size=cfg.token_batch_size, group_size=cfg.group_size, max_inflight=cfg.max_inflight,
@@ -274,22 +274,12 @@ def make_generate_group(orch) -> Callable[..., List[Rollout]]:
         return c[server % len(c)] if isinstance(c, (list, tuple)) else c
 
     def generate_group(example, n, sampling, version, server):
-        env = orch.env
+        env = orch.env_for(example) if hasattr(orch, "env_for") else orch.env
         out: List[Rollout] = []
         if env is not None and hasattr(env, "env_response"):
-            saved_client, saved_n = orch.client, orch.cfg.group_size
-            orch.client, orch.cfg.group_size = pick(server), n
-            try:
-                cap = (example.get("info") or {}).get("max_turns")
-                if cap is not None and hasattr(env, "max_turns"):
-                    old_turns, env.max_turns = env.max_turns, min(int(env.max_turns), int(cap))
-                try:
-                    eps = orch.multi_turn_group(example, sampling)
-                finally:
-                    if cap is not None and hasattr(env, "max_turns"):
-                        env.max_turns = old_turns
-            finally:
-                orch.client, orch.cfg.group_size = saved_client, saved_n
+            # everything an episode needs travels as arguments: this function runs on several worker threads at once
+            cap = (example.get("info") or {}).get("max_turns")
+            eps = orch.multi_turn_group(example, sampling, env=env, client=pick(server), group_size=n, max_turns=cap)
             for pids, ids, lps, mask, r in eps:
                 if ids:
                     turns = 1 + sum(1 for a, b in zip(mask, mask[1:]) if a == 0 and b == 1)

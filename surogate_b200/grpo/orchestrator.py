@@ -78,7 +78,23 @@ class Orchestrator:
     def __init__(self, cfg: OrchestratorConfig, tokenizer, client, transport, policy_version: Callable[[], int], reward_fn=None):
         self.cfg, self.tok, self.client, self.transport = cfg, tokenizer, client, transport
         self.env = None
-        if cfg.environment and reward_fn is None:  # single-turn scoring of the sampled completions by the environment's rubric
+        self.envs: Dict[str, Any] = {}          # task name -> environment, when several environments train together
+        self.env_reward_fns: Dict[str, Callable] = {}
+        if getattr(cfg, "environments", None) and reward_fn is None:
+            from .environments import as_reward_fn, load_environment
+
+            for spec in cfg.environments:
+                name = spec.get("name") or str(spec["id"]).split("@")[0]
+                if name in self.envs or name == "all":
+                    raise ValueError(f"environment name '{name}' is {'reserved' if name == 'all' else 'used twice'}")
+                env = load_environment(spec["id"], path=cfg.environments_path, import_path=spec.get("path") or None,
+                                       **dict(spec.get("args") or {}, **(spec.get("extra_env_kwargs") or {})))
+                self.envs[name] = env
+                self.env_reward_fns[name] = getattr(env, "score_group", None) or as_reward_fn(env)
+            self.env = next(iter(self.envs.values()))
+            first = next(iter(self.env_reward_fns.values()))
+            reward_fn = lambda row, completions: self.env_reward_fns.get(row.get("task"), first)(row, completions)  # noqa: E731
+        elif cfg.environment and reward_fn is None:  # single-turn scoring of the sampled completions by the environment's rubric
             from .environments import as_reward_fn, load_environment
 
             self.env = load_environment(cfg.environment, path=cfg.environments_path, import_path=getattr(cfg, "environment_import_path", "") or None,
@@ -108,7 +124,16 @@ class Orchestrator:
         if self.judge is not None:
             self.reward_fn = self.judge.wrap_reward_fn(self.reward_fn)
 
+    def env_for(self, row: Dict[str, Any]):
+        """The environment a prompt belongs to (its ``task``), or the only one."""
+        return self.envs.get(row.get("task"), self.env) if self.envs else self.env
+
     def load_prompts(self, rows: Optional[Sequence[Dict[str, Any]]] = None) -> None:
+        if rows is None and self.envs:
+            rows = []
+            for name, env in self.envs.items():
+                multi = hasattr(env, "env_response")
+                rows += [dict(ex, task=name) if multi else dict(ex, prompt=env.initial_messages(ex), task=name) for ex in env.dataset]
         if rows is None and self.env is not None:
             rows = [dict(ex, prompt=self.env.initial_messages(ex)) for ex in self.env.dataset] if not hasattr(self.env, "env_response") else list(self.env.dataset)
         if rows is None:
@@ -122,22 +147,24 @@ class Orchestrator:
             return self.tok.apply_chat_template_and_encode(p, add_generation_prompt=True)
         return self.tok.apply_chat_template_and_encode([{"role": "user", "content": str(p)}], add_generation_prompt=True)
 
-    def multi_turn_group(self, row: Dict[str, Any], sampling: Dict[str, Any]):
+    def multi_turn_group(self, row: Dict[str, Any], sampling: Dict[str, Any], env=None, client=None, group_size: Optional[int] = None, max_turns: Optional[int] = None):
         """``group_size`` episodes of a multi-turn environment for one example.  Each episode alternates a sampled assistant turn
         and the environment's reply; the conversation is re-encoded with the chat template after every reply and the tokens
         it added (end-of-turn marker, tool message, next generation prompt) join the sequence as context that is not trained
         on.  If re-encoding does not reproduce the tokens sampled so far the episode ends at that turn.
         Returns [(prompt_ids, token_ids, logprobs, mask, reward)]."""
-        env = self.env
+        env = env or self.env_for(row)
+        client = client or self.client
+        turn_cap = min(int(env.max_turns), int(max_turns)) if max_turns is not None else env.max_turns
         out = []
         conversations = []
-        for _ in range(self.cfg.group_size):
+        for _ in range(group_size or self.cfg.group_size):
             msgs = env.initial_messages(row)
             state = dict(env.setup_state(row), example=row)
             prompt0 = self.tok.apply_chat_template_and_encode(msgs, add_generation_prompt=True)
             ctx, comp, lps, mask, text, turns = list(prompt0), [], [], [], "", 0
-            while turns < env.max_turns and len(ctx) < self.cfg.sequence_len:
-                ids, lp, text = self.client.generate(ctx, 1, sampling)[0]
+            while turns < turn_cap and len(ctx) < self.cfg.sequence_len:
+                ids, lp, text = client.generate(ctx, 1, sampling)[0]
                 if not ids or len(lp) != len(ids):
                     break
                 comp += ids
@@ -173,7 +200,7 @@ class Orchestrator:
         rewards_all, lens, kept = [], [], 0
         for g, i in enumerate(idx):
             row = self.prompts[int(i)]
-            if self.env is not None and hasattr(self.env, "env_response"):  # multi-turn environment: episodes instead of single completions
+            if self.env_for(row) is not None and hasattr(self.env_for(row), "env_response"):  # multi-turn environment: episodes instead of single completions
                 eps = self.multi_turn_group(row, sampling)
                 rewards = [e[4] for e in eps]
                 rewards_all += rewards

@@ -209,7 +209,7 @@ def test_nested_orchestrator_schema_is_translated_to_the_flat_keys():
     assert flat["weight_broadcast"] == "nccl" and flat["transport"] == "zmq" and flat["zmq_endpoint"] == "tcp://10.0.0.1:5566"
     assert flat["weight_dir"] == os.path.join("outputs/run1", "weights") and flat["transport_dir"] == os.path.join("outputs/run1", "rollouts")
     text = "\n".join(notes)
-    assert "only the first" in text and "ruler" not in text and flat["ruler"]["judge_model"] == "j" and "strict_async_level" in text and "tasks_per_minute" not in text and flat["tasks_per_minute"] == 10.0
+    assert [e["id"] for e in flat["environments"]] == ["multihop-tools", "other"] and "ruler" not in text and flat["ruler"]["judge_model"] == "j" and "strict_async_level" in text and "tasks_per_minute" not in text and flat["tasks_per_minute"] == 10.0
     assert flat["metrics_file"].endswith("orchestrator_metrics.jsonl") and (flat["val_every"], flat["val_examples"], flat["val_samples"]) == (5, 8, 1) and "skip_model_check" not in text
     # the flat result is a valid orchestrator config of this package
     from surogate_b200.config.loader import coerce_fields

@@ -120,3 +120,55 @@ def test_built_in_environments_take_both_spellings_of_their_arguments(tmp_path):
         load_environment("ruler-task", dataset=str(data), taskname="x")
     with pytest.raises(ValueError, match="needs dataset_path"):
         load_environment("ruler-task")
+
+
+def test_several_environments_train_together(tmp_path):
+    """Prompts of two environments (one single-turn, one multi-turn) in one run: each prompt is rolled out and scored by its own
+    environment, the buffer samples them by the configured ratios, episodes take their client and turn cap as arguments."""
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.config_compat import flatten_orchestrator_config
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, AsyncOrchestratorConfig, make_generate_group
+    from surogate_b200.grpo.orchestrator import Orchestrator
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    flat, notes = flatten_orchestrator_config({"model": {"name": "m"}, "env": [{"id": "markdown-table-qa", "name": "tables", "args": {"num_train": 6, "num_eval": 2}},
+                                                                                {"id": "multihop-tools", "args": {"num_train": 6, "num_eval": 2, "hops": 2, "max_turns": 3}}],
+                                               "buffer": {"env_ratios": [0.5, 0.5]}, "rollouts_per_example": 2, "batch_size": 4})
+    assert [e["name"] or e["id"] for e in flat["environments"]] == ["tables", "multihop-tools"] and not any("only the first" in n for n in notes)
+    cfg = OrchestratorConfig(**{k: v for k, v in flat.items() if k in OrchestratorConfig.__dataclass_fields__})
+
+    class Tok:
+        pad_token_id = 0
+
+        def apply_chat_template_and_encode(self, msgs, add_generation_prompt=False):
+            return list(range(1, 4 + 2 * len(msgs)))
+
+    class Client:
+        def __init__(self, tag):
+            self.tag, self.calls = tag, 0
+
+        def generate(self, ctx, n, sampling):
+            self.calls += 1
+            return [([50 + k, 51], [-0.1, -0.2], "<answer>x</answer>" if k % 2 else "no idea") for k in range(n)]
+
+    clients = [Client("a"), Client("b")]
+    orch = Orchestrator(cfg, Tok(), clients, FilesystemTransport(str(tmp_path / "t")), lambda: 0)
+    assert list(orch.envs) == ["tables", "multihop-tools"]
+    orch.load_prompts()
+    tasks = [p["task"] for p in orch.prompts]
+    assert tasks.count("tables") == 6 and tasks.count("multihop-tools") == 6
+    table_row = next(p for p in orch.prompts if p["task"] == "tables")
+    hop_row = next(p for p in orch.prompts if p["task"] == "multihop-tools")
+    assert orch.env_for(table_row) is orch.envs["tables"] and hasattr(orch.env_for(hop_row), "env_response") and not hasattr(orch.env_for(table_row), "env_response")
+    gen = make_generate_group(orch)
+    single = gen(table_row, 2, {}, 0, 0)
+    multi = gen(dict(hop_row, info=dict(hop_row["info"], max_turns=1)), 2, {}, 0, 1)
+    assert len(single) == 2 and all(r.completion_mask is None for r in single) and clients[0].calls == 1
+    assert len(multi) == 2 and all(r.completion_mask is not None and r.meta["turns"] == 1 for r in multi) and clients[1].calls == 2   # one call per episode, on server 1
+    assert orch.envs["multihop-tools"].max_turns == 3                                        # the cap travelled as an argument, the environment is untouched
+    acfg = AsyncOrchestratorConfig(group_size=2, batch_size=4, sequence_len=64, rows_per_step=0, max_steps=1, max_inflight=4, workers=2,
+                                   buffer={"env_ratios": [0.5, 0.5], "online_difficulty_filtering": False})
+    loop = AsyncOrchestrator(acfg, orch.prompts, gen, orch.transport, lambda: 0, num_servers=2, env_names=list(orch.envs))
+    assert loop.buffer.env_names == ["tables", "multihop-tools"]
+    hist = loop.run()
+    assert len(hist) == 1 and hist[0]["progress/total_samples"] >= 4
