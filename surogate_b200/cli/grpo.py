@@ -127,7 +127,9 @@ def main(argv, command: str = "grpo") -> int:
             tok = orch.tok
             acfg = async_config_from(cfg, raw, vocab_size=getattr(tok, "vocab_size", 32000), pad_token_id=max(0, getattr(tok, "pad_token_id", 0)))
             eval_rows = None
-            if acfg.eval_every and orch.env is not None and getattr(orch.env, "eval_dataset", None):
+            if acfg.eval_every and raw.get("eval_environments"):
+                eval_rows = orch.add_eval_environments(raw["eval_environments"], raw.get("eval_examples"))
+            elif acfg.eval_every and orch.env is not None and getattr(orch.env, "eval_dataset", None):
                 eval_rows = [dict(ex, prompt=orch.env.initial_messages(ex)) for ex in orch.env.eval_dataset][:raw.get("eval_examples") or None]
             loop = AsyncOrchestrator(acfg, orch.prompts, make_generate_group(orch), orch.transport, lambda: (b.latest() or {"version": -1})["version"],
                                      num_servers=len(urls), eval_examples=eval_rows, env_names=list(orch.envs) or None)

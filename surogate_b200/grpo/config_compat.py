@@ -155,7 +155,8 @@ def flatten_orchestrator_config(raw: Dict[str, Any]) -> Tuple[Dict[str, Any], Li
         if ev.get("num_examples") not in (None, -1):
             flat["eval_examples"] = int(ev["num_examples"])
         if ev.get("env"):
-            notes.append("eval.env: evaluation uses the training environment's evaluation split here")
+            flat["eval_environments"] = [{"id": e.get("id") or e.get("name"), "name": e.get("name"), "args": dict(e.get("args") or {}), "path": e.get("path"),
+                                          "num_examples": e.get("num_examples")} for e in ev["env"]]
 
     wb = raw.get("weight_broadcast") or {}
     flat["weight_broadcast"] = (wb.get("type") if isinstance(wb, dict) else wb) or "filesystem"

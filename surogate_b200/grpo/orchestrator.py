@@ -99,7 +99,8 @@ class Orchestrator:
 
             self.env = load_environment(cfg.environment, path=cfg.environments_path, import_path=getattr(cfg, "environment_import_path", "") or None,
                                         **cfg.environment_args)
-            reward_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
+            base_fn = getattr(self.env, "score_group", None) or as_reward_fn(self.env)
+            reward_fn = lambda row, completions: self.env_reward_fns.get(row.get("task"), base_fn)(row, completions)  # noqa: E731 - rows of evaluation-only environments carry their task
         self.reward_fn = reward_fn or resolve_reward(cfg.reward)
         self.judge = None
         self.teacher = None
@@ -123,6 +124,28 @@ class Orchestrator:
         self.judge = scorer or build_ruler(ruler)
         if self.judge is not None:
             self.reward_fn = self.judge.wrap_reward_fn(self.reward_fn)
+
+    def add_eval_environments(self, specs: Sequence[Dict[str, Any]], default_examples: Optional[int] = None) -> List[Dict[str, Any]]:
+        """Environments that are only evaluated on: registered under their names (so their examples are rolled out and scored by
+        them) and returned as evaluation rows: the environment's evaluation split, or the head of its dataset."""
+        from .environments import as_reward_fn, load_environment
+
+        rows: List[Dict[str, Any]] = []
+        for spec in specs:
+            name = spec.get("name") or str(spec["id"]).split("@")[0]
+            env = self.envs.get(name)
+            if env is None:
+                env = load_environment(spec["id"], path=self.cfg.environments_path, import_path=spec.get("path") or None, **dict(spec.get("args") or {}))
+                if not self.envs and self.env is not None:   # a single training environment so far: keep it reachable by task name
+                    self.envs[getattr(self.env, "env_id", "default")] = self.env
+                self.envs[name] = env
+                self.env_reward_fns[name] = getattr(env, "score_group", None) or as_reward_fn(env)
+            data = list(env.eval_dataset or env.dataset)
+            n = spec.get("num_examples") or default_examples
+            data = data[:int(n)] if n and int(n) > 0 else data
+            multi = hasattr(env, "env_response")
+            rows += [dict(ex, task=name) if multi else dict(ex, prompt=env.initial_messages(ex), task=name) for ex in data]
+        return rows
 
     def env_for(self, row: Dict[str, Any]):
         """The environment a prompt belongs to (its ``task``), or the only one."""

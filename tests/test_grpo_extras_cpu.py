@@ -172,3 +172,22 @@ def test_several_environments_train_together(tmp_path):
     assert loop.buffer.env_names == ["tables", "multihop-tools"]
     hist = loop.run()
     assert len(hist) == 1 and hist[0]["progress/total_samples"] >= 4
+
+
+def test_evaluation_only_environments_score_their_own_rows(tmp_path):
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.config_compat import flatten_orchestrator_config
+    from surogate_b200.grpo.orchestrator import Orchestrator
+
+    flat, _ = flatten_orchestrator_config({"model": {"name": "m"}, "env": [{"id": "markdown-table-qa", "args": {"num_train": 4, "num_eval": 2}}],
+                                           "eval": {"interval": 5, "num_examples": 3, "env": [{"id": "multihop-tools", "name": "hops", "args": {"num_train": 2, "num_eval": 5, "hops": 2}}]}})
+    assert flat["eval_environments"][0]["name"] == "hops" and flat["eval_examples"] == 3
+    cfg = OrchestratorConfig(**{k: v for k, v in flat.items() if k in OrchestratorConfig.__dataclass_fields__})
+    orch = Orchestrator(cfg, tokenizer=None, client=None, transport=None, policy_version=lambda: 0)
+    rows = orch.add_eval_environments(flat["eval_environments"], flat["eval_examples"])
+    assert len(rows) == 3 and {r["task"] for r in rows} == {"hops"} and set(orch.envs) == {"markdown-table-qa", "hops"}
+    assert hasattr(orch.env_for(rows[0]), "env_response") and not hasattr(orch.env_for({"task": "markdown-table-qa"}), "env_response")
+    gold = rows[0]["answer"]
+    assert orch.reward_fn(rows[0], [f"<answer>{gold}</answer>", "<answer>nope</answer>"]) == [1.0, 0.0]     # scored by the evaluation environment's rubric
+    train_row = dict(orch.env.dataset[0], task="markdown-table-qa")
+    assert len(orch.reward_fn(train_row, ["x"])) == 1
