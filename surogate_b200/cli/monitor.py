@@ -4,7 +4,7 @@ It does not import the training code: it tails the feed file (default ``/tmp/sur
 (loss / learning-rate / throughput / gradient-norm series, evaluation points, the last GPU and MoE records) and redraws a
 layout of panels: loss curve, step progress, throughput, GPUs (from the feed, or read live through NVML), MoE balance.
 ``--once`` renders a single frame (used by tests and for piping into a file); ``launch`` starts a run with the ``surogate``
-command, locally or over SSH, and then monitors it.
+command, locally or over SSH, and then monitors it; ``--interactive`` opens the paged dashboard (``cli/dashboard.py``).
 
 Parity: jackalope/ (terminal dashboard that tails the same feed; its launch back ends are ``surogate_b200/launch`` behind ``surogate launch``).
 """
@@ -302,7 +302,13 @@ def main(argv, command: str = "monitor") -> int:
     p.add_argument("--ssh", default=None)
     p.add_argument("--gpus", type=int, default=0)
     p.add_argument("--command", default="sft")
+    p.add_argument("--interactive", "-i", action="store_true", help="the paged dashboard (Monitor, GPUs, Models, Datasets, Launch, Runs) with keyboard navigation")
+    p.add_argument("--runs-dir", default=None)
     a = p.parse_args(argv)
+    if (a.interactive or (command == "jackalope" and a.action == "watch" and not a.once)) and sys.stdin.isatty():
+        from .dashboard import Dashboard, run
+
+        return run(Dashboard(a.feed, a.runs_dir))
     if a.action in ("models", "datasets", "runs"):
         if not a.config:
             p.error(f"{a.action} needs a search text or a path")

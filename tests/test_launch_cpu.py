@@ -345,3 +345,116 @@ def test_launch_command_line(tmp_path, capsys):
     rd.write_meta(mode="sft", max_steps=1)
     assert cli.main(["--runs-dir", root, "runs"]) == 0 and rd.id in capsys.readouterr().out
     assert cli.main(["--runs-dir", root, "stop", rd.id]) == 1 and cli.main(["--runs-dir", root, "fetch", rd.id]) == 0
+
+
+def test_interactive_dashboard_state_machine(tmp_path):
+    """Keys drive the pages: search and line up a model and a dataset, edit launch fields, start a run (through an injected
+    launcher), follow it in Monitor, stop it from Runs; every frame renders at any size."""
+    from surogate_b200.cli.dashboard import EDITABLE, KEYMAP, PAGES, Dashboard
+
+    feed = tmp_path / "feed.jsonl"
+    feed.write_text(json.dumps({"step": 1, "ts": 0, "train/loss": 2.5, "max_steps": 10}) + "\n")
+    started = []
+
+    def launcher(target, text, label):
+        started.append((target, yaml.safe_load(text), label))
+        rd = new_run(f"local-{label}", str(tmp_path / "runs"))
+        with open(rd.feed, "w") as f:
+            f.write(json.dumps({"step": 3, "ts": 0, "train/loss": 1.25, "max_steps": 7}) + "\n")
+        rd.write_meta(mode="sft", model="m", max_steps=7)
+        return {"ok": True, "feed": rd.feed, "run": rd}
+
+    d = Dashboard(str(feed), str(tmp_path / "runs"), gpus=lambda: [{"index": 0, "name": "B200", "mem_total": 180 * 2**30, "mem_used": 2**30, "gpu_util": 10}],
+                  search_models=lambda q, n: [{"id": "Qwen/Qwen3-0.6B", "architectures": ["Qwen3ForCausalLM"], "downloads": 5}, {"id": "x/y", "architectures": ["Nope"], "downloads": 1}],
+                  search_datasets=lambda q, n: [{"id": "org/data", "downloads": 3}], launcher=launcher)
+    d.state.poll()
+    assert "step 1/10" in d.render(100, 30) and d.name == "Monitor"
+    for key in "3/":
+        d.on_key(key)
+    for ch in "qwen":
+        d.on_key(ch)                                   # typed into the search box: 'q' does not quit here
+    assert d.input == "qwen" and not d.quit
+    d.on_key("backspace")
+    d.on_key("enter")
+    assert len(d.rows["Models"]) == 2 and "2 result(s) for 'qwe'" in d.message
+    frame = d.render(120, 30)
+    assert "> " in frame and "Qwen/Qwen3-0.6B" in frame and "yes" in frame
+    d.on_key("enter")
+    assert d.fields.model == "Qwen/Qwen3-0.6B"
+    d.on_key("down")
+    d.on_key("enter")
+    assert d.fields.model == "x/y" and "not supported" in d.message
+    d.on_key("up")
+    d.on_key("enter")
+    d.on_key("4")
+    d.on_key("/")
+    for ch in "data":
+        d.on_key(ch)
+    d.on_key("enter")
+    d.on_key("enter")
+    assert d.fields.dataset_path == "org/data"
+    d.on_key("2")
+    assert "GB per GPU" in d.render(100, 30) and "fits" in d.render(100, 30)
+    d.on_key("5")
+    i = EDITABLE.index("max_steps")
+    for _ in range(i):
+        d.on_key("down")
+    d.on_key("enter")
+    assert d.input == "200"
+    for _ in range(3):
+        d.on_key("backspace")
+    for ch in "7x":
+        d.on_key(ch)
+    d.on_key("enter")
+    assert d.fields.max_steps == 200 and "not a valid value" in d.message          # '7x' is refused, the old value stays
+    d.on_key("enter")
+    for _ in range(3):
+        d.on_key("backspace")
+    d.on_key("7")
+    d.on_key("enter")
+    assert d.fields.max_steps == 7
+    lora = EDITABLE.index("lora")
+    for _ in range(lora - i):
+        d.on_key("down")
+    d.on_key("enter")
+    assert d.fields.lora is False                                                    # booleans toggle
+    d.on_key("t")
+    d.on_key("+")
+    assert d.target == "ssh" and d.gpu_count == 2 and "ssh (h: set host)" in d.render(100, 40)
+    for _ in range(3):
+        d.on_key("t")
+    assert d.target == "local"
+    for _ in range(len(EDITABLE) - lora):
+        d.on_key("down")
+    d.on_key("enter")                                                                # [ start the run ]
+    assert started and started[0][0] == "local" and started[0][1]["max_steps"] == 7 and started[0][1]["lora"] is False and started[0][1]["gpus"] == 2
+    assert d.name == "Monitor" and "started on local" in d.message
+    d.state.poll()
+    assert "step 3/7" in d.render(100, 30)
+    d.on_key("6")
+    assert len(d.rows["Runs"]) == 1 and "running" in d.render(140, 30)
+    d.on_key("s")
+    assert d.message.startswith("stop:")
+    d.on_key("enter")
+    assert d.name == "Monitor" and "following" in d.message
+    d.on_key("?")
+    assert "switch page" in d.render(100, 40)
+    d.on_key("x")
+    assert not d.help
+    d.on_key("tab")
+    assert d.name == "GPUs"
+    for size in ((60, 10), (200, 60), (20, 5)):
+        for page in range(len(PAGES)):
+            d.go(page)
+            frame = d.render(*size)
+            assert len(frame.splitlines()) <= max(size[1], 8) + 2 and all(len(l) <= max(60, size[0]) for l in frame.splitlines())
+    empty = Dashboard(str(tmp_path / "none.jsonl"), str(tmp_path / "no-runs"), gpus=lambda: [])
+    empty.on_key("5")
+    for _ in range(len(EDITABLE)):
+        empty.on_key("down")
+    empty.on_key("enter")
+    assert "cannot start: no model picked" in empty.message
+    empty.on_key("6")
+    assert "(nothing yet)" in empty.render(100, 20)
+    empty.on_key("q")
+    assert empty.quit and KEYMAP["\x1b[A"] == "up" and KEYMAP["\r"] == "enter"
