@@ -11,6 +11,7 @@ Parity: surogate/train/tokenize.py (TokenizedDataFileWriter :113-214, packing :2
 """
 from __future__ import annotations
 
+import contextlib
 import dataclasses
 import glob
 import hashlib
@@ -38,6 +39,34 @@ def loss_scale_mode(loss_scale: str) -> str:
         raise ValueError(f"unknown loss_scale '{loss_scale}' (default | last_round | all)")
     return LOSS_SCALE_MODES[base]
 ROWS_PER_SHARD = 1 << 14
+
+
+@contextlib.contextmanager
+def directory_lock(directory: str, name: str = ".tokenize.lock"):
+    """Exclusive advisory lock on a file inside ``directory`` (held while shards are written, released on every way out)."""
+    import fcntl
+
+    path = os.path.join(directory, name)
+    with open(path, "a+") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield path
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
+
+
+def progress(rows, label: str):
+    """The rows, with a progress bar on a terminal (tokenising a large dataset takes minutes); plain iteration elsewhere."""
+    import sys
+
+    if not sys.stderr.isatty() or os.environ.get("SUROGATE_NO_PROGRESS") == "1":
+        return rows
+    try:
+        from tqdm import tqdm
+
+        return tqdm(rows, desc=label, unit="row", leave=False)
+    except ImportError:
+        return rows
 
 
 def _file_digest(path: str) -> str:
@@ -198,13 +227,21 @@ class TokenizeDatasets:
         if not write:  # another rank writes; the caller synchronises and re-reads the manifest
             return {"train": [os.path.join(self.out_dir, "train-000.bin")], "eval": [os.path.join(self.out_dir, "eval.bin")]}
         os.makedirs(self.out_dir, exist_ok=True)
+        with directory_lock(self.out_dir):   # two runs that share an output directory: the second waits, then finds the shards cached
+            cached = self._cached(h)
+            if cached is not None:
+                return cached
+            return self._tokenise(h)
+
+    def _tokenise(self, h: str) -> Dict[str, List[str]]:
+        c = self.cfg
         tok = self.tokenizer()
         pad = tok.pad_token_id if tok.pad_token_id >= 0 else 0
 
         def encode_all(datasets) -> List[Tuple[np.ndarray, np.ndarray]]:
             docs = []
             for ds in datasets:
-                for row in load_dataset_rows(ds):
+                for row in progress(load_dataset_rows(ds), f"tokenising {os.path.basename(str(ds.path).rstrip('/')) or 'dataset'}"):
                     enc = self.encode_row(row)
                     if enc is None:
                         continue

@@ -385,3 +385,23 @@ def test_metrics_feed_uses_the_dashboard_schema_and_the_monitor_reads_it(tmp_pat
     assert st.evals == [(3, 2.5)] and st.gpu["gpu_util"] == 97 and st.moe["imbalance"] == 1.5
     frame = monitor.render(st, width=100)
     assert "step 3/10" in frame and "MoE" in frame and "gpu0" in frame
+
+
+def test_tokenisation_lock_serialises_two_writers(tmp_path):
+    """Two processes that want to write shards into the same directory: the second enters only after the first has left."""
+    import subprocess
+    import sys
+    import time
+
+    from surogate_b200.train.tokenize import directory_lock, progress
+
+    d = str(tmp_path)
+    child = (f"import sys, time; sys.path.insert(0, {os.getcwd()!r}); from surogate_b200.train.tokenize import directory_lock\n"
+             f"with directory_lock({d!r}):\n    open({os.path.join(d, 'child_in')!r}, 'w').write(str(time.time()))\n")
+    with directory_lock(d):
+        p = subprocess.Popen([sys.executable, "-c", child])
+        time.sleep(1.5)
+        assert not os.path.exists(os.path.join(d, "child_in"))      # blocked while this process holds the lock
+        released = time.time()
+    assert p.wait(timeout=60) == 0 and float(open(os.path.join(d, "child_in")).read()) >= released - 0.05
+    assert list(progress(iter(range(3)), "x")) == [0, 1, 2]
