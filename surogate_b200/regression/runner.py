@@ -86,7 +86,13 @@ def run_case(case: Case, device: Optional[str] = None) -> Dict[str, Any]:
         norms.append(out["norm"])
     mem = tr.memory_breakdown()
     ts = sorted(times[1:] or times)
-    return {"case": dataclasses.asdict(case), "device": dev.type, "losses": losses, "norms": norms,
+    try:   # the graph compiler's static buffer plan: a changed fusion rule or liveness analysis shows up here before it shows in memory
+        plan = tr.activation_plan()
+        plan_summary = {"saved_bytes": int(plan.saved_bytes), "temp_bytes": int(plan.temp_bytes),
+                        "tensors": {bt: {ph: len(p.tensors) for ph, p in phases.items()} for bt, phases in plan.per_block.items()}}
+    except Exception:  # noqa: BLE001 - a model whose graphs the planner does not cover: the artifact goes without
+        plan_summary = None
+    return {"case": dataclasses.asdict(case), "device": dev.type, "losses": losses, "norms": norms, "plan": plan_summary,
             "step_ms_p50": statistics.median(ts), "step_ms_p95": ts[min(len(ts) - 1, int(0.95 * len(ts)))],
             "peak_memory": mem.get("peak", 0), "store": {"buckets": len(tr.store.buckets), **{k: v for k, v in mem.items() if k in ("master", "work", "grad", "host_master")}},
             "num_parameters": tr.num_parameters()}
@@ -106,6 +112,8 @@ def compare(new: Dict[str, Any], base: Dict[str, Any], loss_rtol: float = 2e-2, 
         problems.append(f"peak memory {new['peak_memory']} > {mem_factor}x baseline {base['peak_memory']}")
     if new["store"]["buckets"] != base["store"]["buckets"] or new["num_parameters"] != base["num_parameters"]:
         problems.append("parameter-store layout changed")
+    if base.get("plan") and new.get("plan") and (new["plan"]["saved_bytes"] != base["plan"]["saved_bytes"] or new["plan"]["tensors"] != base["plan"]["tensors"]):
+        problems.append(f"buffer plan changed: saved bytes {new['plan']['saved_bytes']} vs {base['plan']['saved_bytes']}, tensors {new['plan']['tensors']} vs {base['plan']['tensors']}")
     return problems
 
 
