@@ -115,7 +115,14 @@ class PretrainedConfig:
 
     @classmethod
     def from_name(cls, name: str, dtype: str = "bf16") -> "PretrainedConfig":
-        return cls.from_pretrained(name, dtype)
+        """An architecture preset by name (``qwen3-8b``, ``Qwen/Qwen3-8B``, ``llama-3.1-8b`` ...; ``models/presets.py``); names without a
+        preset fall back to ``from_pretrained``."""
+        from .models.presets import preset_config
+
+        try:
+            return cls.from_hf_dict(preset_config(name), dtype)
+        except KeyError:
+            return cls.from_pretrained(name, dtype)
 
     @classmethod
     def from_hf_dict(cls, hf: Dict[str, Any], dtype: str = "bf16") -> "PretrainedConfig":

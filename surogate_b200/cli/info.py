@@ -16,8 +16,16 @@ def main(argv, command: str = "info") -> int:
 
     out = {"system": system_info()}
     if a.model:
-        from ..hub import download_model, model_info
+        from ..models.presets import is_preset, preset_config
 
-        out["model"] = model_info(download_model(a.model))
+        if is_preset(a.model):   # an architecture preset: its config and parameter count, no files involved
+            from ..dsl.compiler import compile_model, model_from_hf_config
+
+            cfg = preset_config(a.model)
+            out["model"] = {"preset": a.model, "config": cfg, "parameters": compile_model(model_from_hf_config(cfg)).num_parameters()}
+        else:
+            from ..hub import download_model, model_info
+
+            out["model"] = model_info(download_model(a.model))
     print(json.dumps(out, indent=1, default=str))
     return 0

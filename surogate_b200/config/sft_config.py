@@ -108,6 +108,7 @@ class DistillationConfig:
 class SFTConfig:
     # model
     model: str = ""
+    tokenizer_path: Optional[str] = None    # tokenizer directory when `model` is an inline config or `preset:<name>` (default: the model's own)
     torch_dtype: str = "bfloat16"
     max_model_len: Optional[int] = None
     rope_scaling: Optional[Dict[str, Any]] = None

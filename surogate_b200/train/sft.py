@@ -36,6 +36,10 @@ def resolve_model_config(cfg: SFTConfig) -> Dict[str, Any]:
         return dict(m)
     if m.strip().startswith("{"):
         return json.loads(m)
+    from ..models.presets import is_preset, preset_config
+
+    if is_preset(m):   # ``model: preset:qwen3-8b``: the architecture by name, no weights (from_scratch runs, planning)
+        return preset_config(m)
     if os.path.exists(m):
         return load_hf_config(m)
     from ..hub import download_model

@@ -41,6 +41,25 @@ def loss_scale_mode(loss_scale: str) -> str:
 ROWS_PER_SHARD = 1 << 14
 
 
+def tokenizer_dir(cfg) -> Optional[str]:
+    """Where the run's tokenizer lives: ``tokenizer_path`` when set, else the model directory, else the hub model's local copy."""
+    explicit = getattr(cfg, "tokenizer_path", None)
+    if explicit:
+        return explicit
+    m = cfg.model
+    if not isinstance(m, str) or m.strip().startswith("{") or m.lower().startswith("preset:"):
+        return None
+    if os.path.isdir(m):
+        return m
+    try:
+        from ..hub import download_model
+
+        d = download_model(m)
+        return d if os.path.isdir(d) else None
+    except Exception:  # noqa: BLE001 - offline and not cached
+        return None
+
+
 @contextlib.contextmanager
 def directory_lock(directory: str, name: str = ".tokenize.lock"):
     """Exclusive advisory lock on a file inside ``directory`` (held while shards are written, released on every way out)."""
@@ -143,15 +162,16 @@ class TokenizeDatasets:
         if self._tok is None:
             from ..data.tokenizer import Tokenizer
 
-            model_dir = self.cfg.model if isinstance(self.cfg.model, str) and os.path.isdir(self.cfg.model) else None
+            model_dir = tokenizer_dir(self.cfg)
             if model_dir is None:
-                raise FileNotFoundError("tokenising datasets needs a model directory with tokenizer.json (set `model:` to a local path)")
+                raise FileNotFoundError("tokenising datasets needs tokenizer.json: set `model:` to a model directory or a hub id, or `tokenizer_path:` "
+                                        "next to an inline / preset model")
             self._tok = Tokenizer.from_pretrained(model_dir)
         return self._tok
 
     def content_hash(self) -> str:
         c = self.cfg
-        tok_dir = c.model if isinstance(c.model, str) and os.path.isdir(c.model) else None
+        tok_dir = tokenizer_dir(c)
         tok_files = {}
         if tok_dir:
             for name in ("tokenizer.json", "tokenizer_config.json", "chat_template.jinja"):

@@ -125,3 +125,29 @@ def test_loader_fills_caller_arrays(tmp_path):
     assert not dl.has_kd()
     with pytest.raises(RuntimeError):
         dl.enable_kd(4)
+
+
+def test_architecture_presets(tmp_path):
+    from surogate_b200.config.sft_config import SFTConfig
+    from surogate_b200.dsl.compiler import compile_model, model_from_hf_config
+    from surogate_b200.models.presets import PRESETS, list_presets, normalise, preset_config
+    from surogate_b200.train.sft import resolve_model_config
+
+    assert normalise("Qwen/Qwen3-8B") == "qwen3-8b" and normalise("preset:meta-llama/Llama-3.1-8B-Instruct") == "llama-3.1-8b" and "qwen3-30b-a3b" in list_presets()
+    c = PretrainedConfig.from_name("Qwen/Qwen3-8B")
+    assert (c.hidden_size, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.intermediate_size, c.head_size) == (4096, 36, 32, 8, 12288, 128)
+    assert not c.tie_word_embeddings and PretrainedConfig.from_name("qwen3-0.6b").tie_word_embeddings
+    with pytest.raises(KeyError, match="known:"):
+        preset_config("gpt-5")
+    # every preset builds a model of the named size (parameter counts within 3% of the names)
+    expect = {"qwen3-0.6b": 0.6, "qwen3-8b": 8.2, "qwen3-32b": 32.8, "qwen3-30b-a3b": 30.5, "qwen2.5-7b": 7.6, "llama-3.1-8b": 8.0, "llama-3.2-1b": 1.24, "mistral-7b-v0.3": 7.25}
+    for name in PRESETS:
+        cm = compile_model(model_from_hf_config(preset_config(name)))
+        billions = cm.num_parameters() / 1e9
+        if name in expect:
+            assert abs(billions - expect[name]) / expect[name] < 0.03, (name, billions)
+    cfg = SFTConfig.from_dict(dict(model="preset:qwen3-0.6b", synthetic_data=True, from_scratch=True, lora=False, tokenizer_path=str(tmp_path)))
+    assert resolve_model_config(cfg)["hidden_size"] == 1024
+    from surogate_b200.train.tokenize import tokenizer_dir
+
+    assert tokenizer_dir(cfg) == str(tmp_path) and tokenizer_dir(SFTConfig.from_dict(dict(model="preset:qwen3-0.6b", synthetic_data=True))) is None
