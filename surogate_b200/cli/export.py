@@ -14,6 +14,9 @@ def main(argv, command: str = "export") -> int:
     p.add_argument("config", help="the training config the checkpoint was written with")
     p.add_argument("--checkpoint", default=None, help="checkpoint directory (default: the config's checkpoint_dir, latest step)")
     p.add_argument("--output", required=True)
+    p.add_argument("--push-to-hub", default=None, metavar="REPO_ID", help="upload the exported directory to this model repository afterwards")
+    p.add_argument("--private", action="store_true")
+    p.add_argument("--hub_token", "--hub-token", dest="hub_token", default=None)
     a = p.parse_args(argv)
     import torch
 
@@ -31,5 +34,11 @@ def main(argv, command: str = "export") -> int:
         tr.export_adapter(os.path.join(a.output, "adapter"), base_model=cfg.model if isinstance(cfg.model, str) else "")
         tr.lora.merge_into(tr.store)
     tr.export_model(a.output, hf)
-    print(json.dumps({"step": meta["run"]["step"], "output": a.output}))
+    out = {"step": meta["run"]["step"], "output": a.output}
+    if a.push_to_hub:
+        from ..hub import push_to_hub
+
+        push_to_hub(a.push_to_hub, a.output, private=a.private, token=a.hub_token, commit_message=f"step {meta['run']['step']}")
+        out["pushed_to"] = a.push_to_hub
+    print(json.dumps(out))
     return 0

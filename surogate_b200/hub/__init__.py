@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Sequence
 
 WEIGHT_PATTERNS = ["*.safetensors", "*.json", "*.jinja", "tokenizer.model", "*.txt"]
 
@@ -84,3 +84,34 @@ def model_info(model_dir: str) -> Dict[str, Any]:
                 nbytes += v["data_offsets"][1] - v["data_offsets"][0]
     info.update(num_parameters=n_params, weight_bytes=nbytes, weight_files=files)
     return info
+
+
+def try_login(token: Optional[str] = None) -> bool:
+    """True when the hub accepts the token (``token``, else ``HF_TOKEN``, else the stored login)."""
+    try:
+        from huggingface_hub import HfApi
+
+        HfApi().whoami(token=token or os.environ.get("HF_TOKEN"))
+        return True
+    except Exception:  # noqa: BLE001 - not installed, offline, or refused
+        return False
+
+
+def push_to_hub(repo_id: str, folder_path: str, path_in_repo: Optional[str] = None, commit_message: Optional[str] = None, private: bool = False,
+                revision: Optional[str] = None, ignore_patterns: Optional[Sequence[str]] = None, token: Optional[str] = None, api=None) -> Any:
+    """Upload a directory (an exported model or adapter) to a model repository, creating it when missing.  ``revision`` ``master`` /
+    None means ``main``.  ``api``: an object with ``create_repo`` / ``upload_folder`` (tests inject one; default ``huggingface_hub.HfApi``).
+    Parity: surogate/core/hub/huggingface.py (create_model_repo, push_to_hub)."""
+    if not os.path.isdir(folder_path):
+        raise HubError(f"nothing to upload: {folder_path} is not a directory")
+    if api is None:
+        try:
+            from huggingface_hub import HfApi
+        except ImportError as e:
+            raise HubError("pushing to the hub needs the `huggingface_hub` package") from e
+        api = HfApi()
+    token = token or os.environ.get("HF_TOKEN")
+    api.create_repo(repo_id, token=token, private=private, exist_ok=True)
+    return api.upload_folder(repo_id=repo_id, folder_path=folder_path, path_in_repo=path_in_repo, commit_message=commit_message or f"Upload {os.path.basename(folder_path.rstrip('/'))}",
+                             token=token, revision="main" if revision in (None, "master") else revision,
+                             ignore_patterns=list(ignore_patterns) if ignore_patterns else ["tokens/*", "step_*", "*.log", "log.jsonl"])

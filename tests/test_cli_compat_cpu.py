@@ -371,3 +371,27 @@ def test_debug_commands_take_a_training_config(tmp_path, capsys):
     assert cli.main(["weights", str(cfg)]) == 0 and cli.main(["tensor-arena", str(cfg), "--output", str(tmp_path / "arena.jsonl")]) == 0
     capsys.readouterr()
     assert os.path.getsize(tmp_path / "acts.jsonl") > 0 and os.path.getsize(tmp_path / "arena.jsonl") > 0
+
+
+def test_push_to_hub_creates_the_repository_and_uploads_the_directory(tmp_path):
+    from surogate_b200.hub import HubError, push_to_hub
+
+    calls = []
+
+    class Api:
+        def create_repo(self, repo_id, **kw):
+            calls.append(("create", repo_id, kw))
+
+        def upload_folder(self, **kw):
+            calls.append(("upload", kw))
+            return "commit-url"
+
+    out = tmp_path / "model"
+    os.makedirs(out)
+    (out / "config.json").write_text("{}")
+    assert push_to_hub("me/my-model", str(out), private=True, revision="master", token="t", api=Api()) == "commit-url"
+    assert calls[0] == ("create", "me/my-model", {"token": "t", "private": True, "exist_ok": True})
+    up = calls[1][1]
+    assert up["repo_id"] == "me/my-model" and up["revision"] == "main" and up["folder_path"] == str(out) and "step_*" in up["ignore_patterns"] and up["commit_message"] == "Upload model"
+    with pytest.raises(HubError, match="not a directory"):
+        push_to_hub("me/x", str(tmp_path / "missing"), api=Api())
