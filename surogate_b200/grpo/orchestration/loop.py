@@ -162,7 +162,18 @@ class AsyncOrchestrator:
         flat = [r for g in groups for r in g]
         stats = apply_filters(self.filters, flat)
         sizes = {len(g) for g in groups}
-        if len(sizes) == 1:
+        if any("episode" in r.meta for r in flat):
+            # multi-turn groups: an episode may have produced several samples; the advantage belongs to the episode
+            adv = []
+            for g in groups:
+                order = sorted({r.meta.get("episode", i) for i, r in enumerate(g)})
+                first = {k: next(r for i, r in enumerate(g) if r.meta.get("episode", i) == k) for k in order}
+                length = {k: sum(len(r.completion_ids) for i, r in enumerate(g) if r.meta.get("episode", i) == k) for k in order}
+                a = compute_advantages([first[k].reward for k in order], [length[k] for k in order], len(order), self.cfg.advantage,
+                                       **({"length_weighted_mean": True} if self.cfg.length_weighted_mean and self.cfg.advantage == "default" else {}))
+                by = dict(zip(order, a))
+                adv += [by[r.meta.get("episode", i)] for i, r in enumerate(g)]
+        elif len(sizes) == 1:
             n = sizes.pop()
             adv = compute_advantages([r.reward for r in flat], [len(r.completion_ids) for r in flat], n, self.cfg.advantage,
                                      **({"length_weighted_mean": True} if self.cfg.length_weighted_mean and self.cfg.advantage == "default" else {}))
@@ -280,10 +291,14 @@ def make_generate_group(orch) -> Callable[..., List[Rollout]]:
             # everything an episode needs travels as arguments: this function runs on several worker threads at once
             cap = (example.get("info") or {}).get("max_turns")
             eps = orch.multi_turn_group(example, sampling, env=env, client=pick(server), group_size=n, max_turns=cap)
-            for pids, ids, lps, mask, r in eps:
+            depth: Dict[int, int] = {}
+            for _, _, _, mask, _, k in eps:   # turns of an episode = policy spans over all of its samples
+                depth[k] = depth.get(k, 0) + (1 + sum(1 for a, b in zip(mask, mask[1:]) if a == 0 and b == 1) if mask else 0)
+            for pids, ids, lps, mask, r, k in eps:
                 if ids:
-                    turns = 1 + sum(1 for a, b in zip(mask, mask[1:]) if a == 0 and b == 1)
-                    out.append(Rollout(pids, ids, lps, 0.0, float(r), version, 0, {"turns": turns, "truncated": cap is not None and turns >= int(cap)}, completion_mask=mask))
+                    turns = depth[k]
+                    out.append(Rollout(pids, ids, lps, 0.0, float(r), version, 0, {"turns": turns, "truncated": cap is not None and turns >= int(cap), "episode": k},
+                                       completion_mask=mask))
             if getattr(orch, "teacher", None) is not None:
                 orch.teacher.score(out)
             return out

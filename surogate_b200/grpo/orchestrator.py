@@ -174,8 +174,11 @@ class Orchestrator:
         """``group_size`` episodes of a multi-turn environment for one example.  Each episode alternates a sampled assistant turn
         and the environment's reply; the conversation is re-encoded with the chat template after every reply and the tokens
         it added (end-of-turn marker, tool message, next generation prompt) join the sequence as context that is not trained
-        on.  If re-encoding does not reproduce the tokens sampled so far the episode ends at that turn.
-        Returns [(prompt_ids, token_ids, logprobs, mask, reward)]."""
+        on.  When re-encoding does not reproduce the tokens sampled so far (a template that rewrites earlier turns, e.g. drops
+        old reasoning), the sample is closed there and the episode goes on in a NEW sample whose prompt is the re-encoded
+        conversation, so no turn is lost: an episode yields one sample while the extension property holds and up to one per
+        turn when it never does.  All samples of an episode carry its reward.
+        Returns [(prompt_ids, token_ids, logprobs, mask, reward, episode_index)], one or more entries per episode."""
         env = env or self.env_for(row)
         client = client or self.client
         turn_cap = min(int(env.max_turns), int(max_turns)) if max_turns is not None else env.max_turns
@@ -186,6 +189,7 @@ class Orchestrator:
             state = dict(env.setup_state(row), example=row)
             prompt0 = self.tok.apply_chat_template_and_encode(msgs, add_generation_prompt=True)
             ctx, comp, lps, mask, text, turns = list(prompt0), [], [], [], "", 0
+            segments = []     # samples of this episode that were closed because the extension property broke
             while turns < turn_cap and len(ctx) < self.cfg.sequence_len:
                 ids, lp, text = client.generate(ctx, 1, sampling)[0]
                 if not ids or len(lp) != len(ids):
@@ -200,19 +204,26 @@ class Orchestrator:
                 msgs = msgs + env.env_response(msgs, state)
                 new_ctx = self.tok.apply_chat_template_and_encode(msgs, add_generation_prompt=True)
                 full = prompt0 + comp
-                if new_ctx[:len(full)] != full:
-                    break
+                if new_ctx[:len(full)] != full:   # the template rewrote what came before: close this sample, go on in a new one
+                    segments.append((prompt0, comp, lps, mask))
+                    prompt0, comp, lps, mask, ctx = list(new_ctx), [], [], [], new_ctx
+                    continue
                 extra = new_ctx[len(full):]
                 comp += extra
                 lps += [0.0] * len(extra)
                 mask += [0] * len(extra)
                 ctx = new_ctx
             reward, _ = env.score(row, dict(state, messages=msgs, completion=text, turns=turns))
-            out.append((prompt0, comp, lps, mask, float(reward)))
+            episode = len(conversations)
+            for seg in segments + ([(prompt0, comp, lps, mask)] if comp or not segments else []):
+                out.append(seg + (float(reward), episode))
             conversations.append(msgs)
         if self.judge is not None and out:
-            judged, _ = self.judge.apply(conversations, [o[4] for o in out])
-            out = [o[:4] + (float(r),) for o, r in zip(out, judged)]
+            first = {}
+            for o in out:
+                first.setdefault(o[5], o[4])
+            judged, _ = self.judge.apply(conversations, [first[e] for e in range(len(conversations))])
+            out = [o[:4] + (float(judged[o[5]]), o[5]) for o in out]
         return out
 
     def collect(self, step: int, version: int) -> Tuple[List[Rollout], Dict[str, float]]:
@@ -225,14 +236,18 @@ class Orchestrator:
             row = self.prompts[int(i)]
             if self.env_for(row) is not None and hasattr(self.env_for(row), "env_response"):  # multi-turn environment: episodes instead of single completions
                 eps = self.multi_turn_group(row, sampling)
-                rewards = [e[4] for e in eps]
+                by_episode = {}
+                for e in eps:
+                    by_episode.setdefault(e[5], e[4])
+                rewards = [by_episode[k] for k in sorted(by_episode)]          # one reward per episode, however many samples it produced
                 rewards_all += rewards
-                lens += [sum(e[3]) for e in eps]
-                adv = group_advantages(torch.tensor(rewards), len(rewards), c.advantage_std_eps).tolist()
+                lens += [sum(sum(e[3]) for e in eps if e[5] == k) for k in sorted(by_episode)]
+                adv_by_episode = dict(zip(sorted(by_episode), group_advantages(torch.tensor(rewards), len(rewards), c.advantage_std_eps).tolist()))
                 if c.filter_zero_advantage and max(rewards) - min(rewards) < 1e-12:
                     continue
                 kept += 1
-                for (pids, ids, lps, mask, r), a in zip(eps, adv):
+                for (pids, ids, lps, mask, r, k) in eps:
+                    a = adv_by_episode[k]
                     if ids:
                         rollouts.append(Rollout(pids, ids, lps, a, r, version, g, completion_mask=mask))
                 continue

@@ -191,3 +191,73 @@ def test_evaluation_only_environments_score_their_own_rows(tmp_path):
     assert orch.reward_fn(rows[0], [f"<answer>{gold}</answer>", "<answer>nope</answer>"]) == [1.0, 0.0]     # scored by the evaluation environment's rubric
     train_row = dict(orch.env.dataset[0], task="markdown-table-qa")
     assert len(orch.reward_fn(train_row, ["x"])) == 1
+
+
+def test_episode_continues_in_a_new_sample_when_the_template_rewrites_earlier_turns(tmp_path):
+    """A chat template that drops earlier reasoning breaks the token-prefix property after every turn: the episode still runs to its
+    end, as one sample per turn, all with the episode's reward and advantage."""
+    from surogate_b200.grpo.config import OrchestratorConfig
+    from surogate_b200.grpo.orchestration import AsyncOrchestrator, AsyncOrchestratorConfig, make_generate_group
+    from surogate_b200.grpo.orchestrator import Orchestrator
+    from surogate_b200.grpo.transport.filesystem import FilesystemTransport
+
+    class Env:
+        max_turns = 3
+        env_id = "two-step"
+        dataset = [{"prompt": "go", "answer": "x"}]
+        eval_dataset = []
+
+        def initial_messages(self, row):
+            return [{"role": "user", "content": row["prompt"]}]
+
+        def setup_state(self, row):
+            return {"n": 0}
+
+        def is_completed(self, msgs, state):
+            state["n"] += 1
+            return state["n"] >= 3
+
+        def env_response(self, msgs, state):
+            return [{"role": "tool", "content": "ok"}]
+
+        def score(self, row, state):
+            return (1.0 if state["example"].get("good") else 0.0) + 0.0 * state["turns"], {}
+
+    class Tok:
+        """user = 10, tool = 30, assistant = header 99 + answer 20 + reasoning 21; only the LAST assistant message keeps its reasoning
+        token: earlier turns are rewritten, as templates of reasoning models do."""
+        pad_token_id = 0
+
+        def apply_chat_template_and_encode(self, msgs, add_generation_prompt=False):
+            ids = []
+            last_assistant = max((i for i, m in enumerate(msgs) if m["role"] == "assistant"), default=-1)
+            for i, m in enumerate(msgs):
+                ids += {"user": [10], "tool": [30]}.get(m["role"], [99, 20, 21] if i == last_assistant else [99, 20])
+            return ids + ([99] if add_generation_prompt else [])
+
+    class Client:
+        def generate(self, ctx, n, sampling):
+            return [([20, 21], [-0.1, -0.2], "thinking...answer")]
+
+    cfg = OrchestratorConfig(model="m", group_size=2, sequence_len=64)
+    orch = Orchestrator(cfg, Tok(), Client(), FilesystemTransport(str(tmp_path)), lambda: 0, reward_fn=lambda r, c: [0.0] * len(c))
+    orch.env = Env()
+    eps = orch.multi_turn_group({"prompt": "go", "good": True}, {})
+    assert len(eps) == 2 * 2 and {e[5] for e in eps} == {0, 1} and all(e[4] == 1.0 for e in eps)
+    first = [e for e in eps if e[5] == 0]
+    # turns 1 and 2 extend each other (one sample, the tool reply and the next header as context); after turn 2 the template drops
+    # turn 1's reasoning, the prefix no longer matches, and turn 3 lives in a second sample that starts from the re-encoded conversation
+    assert first[0][0] == [10, 99] and first[0][1] == [20, 21, 30, 99, 20, 21] and first[0][3] == [1, 1, 0, 0, 1, 1]
+    assert first[1][0] == [10, 99, 20, 30, 99, 20, 21, 30, 99] and first[1][1] == [20, 21] and first[1][3] == [1, 1]
+    gen = make_generate_group(orch)
+    rollouts = gen({"prompt": "go", "good": True, "example_id": 0}, 2, {}, 0, 0)
+    assert len(rollouts) == 4 and {r.meta["episode"] for r in rollouts} == {0, 1} and all(r.meta["turns"] == 3 for r in rollouts)
+    # advantages are per episode: episode 0 rewarded, episode 1 not -> every sample of an episode gets the same advantage
+    for r in rollouts:
+        r.reward = 1.0 if r.meta["episode"] == 0 else 0.0
+    loop = AsyncOrchestrator(AsyncOrchestratorConfig(group_size=2, batch_size=2, sequence_len=64, rows_per_step=0, max_steps=1, workers=1), [{"prompt": "go"}], gen,
+                             orch.transport, lambda: 0)
+    loop._score([rollouts])
+    adv = {r.meta["episode"]: {x.advantage for x in rollouts if x.meta["episode"] == r.meta["episode"]} for r in rollouts}
+    assert adv[0] == {0.5} and adv[1] == {-0.5}
+    loop.pool.shutdown(wait=False)
