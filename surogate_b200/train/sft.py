@@ -295,7 +295,7 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
         if trainer.last_moe_stats:
             stats = trainer.get_moe_stats()
             if (step + 1) % max(1, cfg.logging_steps) == 0:
-                logger.log_record("moe", step=step + 1, **stats)
+                logger.log_record("moe", step=step + 1, aux_loss=out.get("aux_loss", 0.0), **stats)
             for w in moe_mon.check(stats):
                 logger.message(f"[moe] {w}")
         if cfg.log_gpu_util and (step + 1) % cfg.log_gpu_util == 0 and device.type == "cuda":

@@ -23,6 +23,7 @@ def summarize(stats: List[Tuple[int, torch.Tensor, torch.Tensor]]) -> Dict[str, 
         "num_layers": float(counts.shape[0]),
         "expert_utilization": float((counts > 0).float().mean()),
         "active_experts": float((counts > 0).float().sum(1).mean()),
+        "dead_experts": float((counts == 0).float().sum(1).mean()),   # experts that received no token, per layer on average
         "load_imbalance": float((frac.max(1).values / mean.squeeze(1)).mean()),
         "max_fraction": float(frac.max()),
         "min_fraction": float(frac.min()),
