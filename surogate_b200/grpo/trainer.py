@@ -138,6 +138,10 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
     sched = LRSchedule(cfg.learning_rate, max_steps, cfg.warmup_steps, cfg.cooldown_steps, cfg.final_lr_fraction * cfg.learning_rate,
                        cfg.lr_scheduler_type, cfg.wsd_decay_steps_fraction)
     logger = TrainingRunLogger(cfg.log_file, None, is_main=info.is_main)
+    if cfg.weight_broadcast != "filesystem":
+        # the tensor-level publishers (process group of trainer + engine workers, CUDA IPC handles) exist in grpo/weight_broadcast.py with
+        # their receivers in grpo/vllm_worker.py; this loop publishes through the watched directory, which works with every engine set-up
+        logger.message(f"[grpo] weight_broadcast: {cfg.weight_broadcast} is not wired into this trainer loop: publishing versions under {cfg.weight_dir} instead")
     history = []
     for step in range(max_steps):
         t0 = time.perf_counter()
