@@ -17,6 +17,8 @@ replay_layer_forward compiled_ops_execute.cpp:85).
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Sequence, Set, Tuple
 
@@ -271,6 +273,10 @@ class Executor:
         self.backend = backend
         self.recipe = recipe
         self.options = options or ExecOptions()
+        if self.options.dump_tensors is None and os.environ.get("SUROGATE_DEBUG_DUMP_TENSORS"):
+            from ..debug.dump import env_dump_hook  # file dumps of named tensors, switched on by the environment
+
+            self.options.dump_tensors = env_dump_hook()
         self.device = device or torch.device("cpu")
         self.ep = ep
         self.lora = lora

@@ -1,0 +1,61 @@
+"""Named tensors written to files during a run, switched on by environment variables (``surogate_b200/debug/dump.py``)."""
+import json
+import os
+
+import numpy as np
+import torch
+
+from surogate_b200.debug.dump import env_dump_hook, load_dump, parse_names, qualified, sanitise
+from surogate_b200.runtime.trainer import Trainer, TrainerConfig
+
+HF = dict(architectures=["Qwen3ForCausalLM"], vocab_size=96, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+          head_dim=16, rms_norm_eps=1e-6, tie_word_embeddings=True, rope_theta=10000.0, max_position_embeddings=128)
+
+
+def test_names_and_file_names():
+    everything, wanted = parse_names("blocks[3].ln1, d_blocks[2].d_x ,loss,all")
+    assert everything and wanted == {(3, "ln1"), (2, "d_x"), (None, "loss")}
+    assert sanitise("blocks[3].ln1") == "blocks_3_.ln1" and qualified("ln1", 3) == "blocks[3].ln1" and qualified("d_x", 0) == "d_blocks[0].d_x" and qualified("loss", None) == "loss"
+    assert env_dump_hook({}) is None and env_dump_hook({"SUROGATE_DEBUG_DUMP_TENSORS": "x"}) is None
+
+
+def test_a_step_writes_the_named_tensors(tmp_path, monkeypatch):
+    def trainer():
+        t = Trainer(TrainerConfig(model=HF, batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", param_dtype="fp32", backend="torch", use_cuda_graphs=False),
+                    device=torch.device("cpu"))
+        t.init_weights(0)
+        return t
+
+    x = torch.randint(0, 96, (2, 16))
+    y = torch.roll(x, -1, 1)
+    # which names a block produces: record them with the programmatic hook first
+    seen = []
+    t = trainer()
+    t.executor.options.dump_tensors = lambda name, layer, val: seen.append((name, layer, tuple(val.shape), val.is_floating_point()))
+    t.step(x, y)
+    block_names = [n for n, l, _, fp in seen if l == 1 and fp]
+    assert block_names
+    name = block_names[0]
+    shape = next(s for n, l, s, _ in seen if n == name and l == 1)
+
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_TENSORS", f"blocks[1].{name}")
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_DIR", str(tmp_path / "one"))
+    t = trainer()
+    assert t.executor.options.dump_tensors is not None
+    t.step(x, y)
+    files = sorted(os.listdir(tmp_path / "one"))
+    assert files == [sanitise(f"blocks[1].{name}") + ".bin", sanitise(f"blocks[1].{name}") + ".json"]
+    meta = json.load(open(tmp_path / "one" / files[1]))
+    assert meta == {"name": f"blocks[1].{name}", "dtype": "float32", "shape": list(shape)}
+    arr = load_dump(str(tmp_path / "one"), f"blocks[1].{name}")
+    assert arr.shape == shape and np.isfinite(arr).all() and os.path.getsize(tmp_path / "one" / files[0]) == arr.size * 4
+
+    # a bare name dumps every layer; the layer filter narrows it again
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_TENSORS", name)
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_DIR", str(tmp_path / "every"))
+    trainer().step(x, y)
+    assert {f for f in os.listdir(tmp_path / "every") if f.endswith(".bin")} == {sanitise(f"blocks[{l}].{name}") + ".bin" for l in (0, 1)}
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_LAYER", "0")
+    monkeypatch.setenv("SUROGATE_DEBUG_DUMP_DIR", str(tmp_path / "layer0"))
+    trainer().step(x, y)
+    assert {f for f in os.listdir(tmp_path / "layer0") if f.endswith(".bin")} == {sanitise(f"blocks[0].{name}") + ".bin"}
