@@ -88,6 +88,42 @@ def progress(rows, label: str):
         return rows
 
 
+PARALLEL_MIN_ROWS = 8192   # below this a pool's start-up (each worker imports the package and loads the tokenizer) costs more than it saves
+MAX_DATASET_PROCESSES = 8
+
+
+def dataset_processes(cfg=None) -> int:
+    """How many processes tokenise a dataset: ``dataloader_num_workers`` when set, else ``SUROGATE_DATASET_PROCESSES``, else
+    ``RUNPOD_CPU_COUNT`` (containers whose ``os.cpu_count()`` shows the host's cores), else the core count; at most 8.
+
+    Parity: surogate/core/config/train_dataset_config.py:9-15, :64."""
+    n = int(getattr(cfg, "dataloader_num_workers", 0) or 0)
+    if n <= 0:
+        for var in ("SUROGATE_DATASET_PROCESSES", "RUNPOD_CPU_COUNT"):
+            if os.environ.get(var):
+                n = int(os.environ[var])
+                break
+        else:
+            n = os.cpu_count() or 1
+    return max(1, min(n, MAX_DATASET_PROCESSES))
+
+
+_worker = None  # a pool worker's own TokenizeDatasets
+
+
+def _worker_init(fields: Dict[str, Any], hf_config: Dict[str, Any], model_dir: str) -> None:
+    import types
+
+    from ..data.tokenizer import Tokenizer
+
+    global _worker
+    _worker = TokenizeDatasets(types.SimpleNamespace(**fields), hf_config, "", tokenizer=Tokenizer.from_pretrained(model_dir))
+
+
+def _worker_encode(rows: List[Dict[str, Any]]) -> List[Optional[Tuple[np.ndarray, np.ndarray]]]:
+    return [_worker.encode_kept(r) for r in rows]
+
+
 def _file_digest(path: str) -> str:
     h = hashlib.sha256()
     with open(path, "rb") as f:
@@ -156,6 +192,7 @@ class TokenizeDatasets:
     def __init__(self, cfg, hf_config: Dict[str, Any], out_dir: str, tokenizer=None):
         self.cfg, self.hf_config, self.out_dir = cfg, hf_config, out_dir
         self._tok = tokenizer
+        self._tok_from_dir = tokenizer is None
 
     # ------------------------------------------------------------------ hashing / cache
     def tokenizer(self):
@@ -213,6 +250,37 @@ class TokenizeDatasets:
             return ids_a, (lab != IGNORE).astype(np.uint8)
         return None
 
+    def encode_kept(self, row: Dict[str, Any]) -> Optional[Tuple[np.ndarray, np.ndarray]]:
+        """A row as (ids, mask) after truncation, or None when nothing of it trains (unknown shape, deleted, no trained token)."""
+        enc = self.encode_row(row)
+        if enc is None:
+            return None
+        enc = self._truncate(*enc)
+        if enc is not None and len(enc[0]) > 1 and enc[1].any():
+            return enc
+        return None
+
+    def encode_rows(self, rows: List[Dict[str, Any]], label: str = "tokenising") -> List[Tuple[np.ndarray, np.ndarray]]:
+        """All rows, in order.  Large datasets go through a pool of processes (the chat template is rendered in Python, one core per
+        process); each worker loads its own tokenizer from the model directory, so a tokenizer object handed in by the caller, or a
+        small dataset, stays in this process."""
+        n = dataset_processes(self.cfg)
+        model_dir = tokenizer_dir(self.cfg) if self._tok_from_dir else None
+        if n > 1 and model_dir and len(rows) >= PARALLEL_MIN_ROWS:
+            import multiprocessing as mp
+
+            c = self.cfg
+            fields = {"use_chat_template": c.use_chat_template, "loss_scale": c.loss_scale, "sequence_len": c.sequence_len, "truncation_strategy": c.truncation_strategy}
+            chunk = max(64, min(2048, len(rows) // (n * 8)))
+            chunks = [rows[i:i + chunk] for i in range(0, len(rows), chunk)]
+            out: List[Tuple[np.ndarray, np.ndarray]] = []
+            # spawn, not fork: the parent may already hold CUDA and communicator state that a forked child must not touch
+            with mp.get_context("spawn").Pool(n, initializer=_worker_init, initargs=(fields, self.hf_config, model_dir)) as pool:
+                for part in progress(pool.imap(_worker_encode, chunks), f"{label} ({n} processes, chunks of {chunk})"):
+                    out.extend(e for e in part if e is not None)
+            return out
+        return [e for e in (self.encode_kept(r) for r in progress(rows, label)) if e is not None]
+
     def _truncate(self, ids: np.ndarray, mask: np.ndarray):
         T = self.cfg.sequence_len
         if len(ids) <= T:
@@ -261,13 +329,7 @@ class TokenizeDatasets:
         def encode_all(datasets) -> List[Tuple[np.ndarray, np.ndarray]]:
             docs = []
             for ds in datasets:
-                for row in progress(load_dataset_rows(ds), f"tokenising {os.path.basename(str(ds.path).rstrip('/')) or 'dataset'}"):
-                    enc = self.encode_row(row)
-                    if enc is None:
-                        continue
-                    enc = self._truncate(*enc)
-                    if enc is not None and len(enc[0]) > 1 and enc[1].any():
-                        docs.append(enc)
+                docs.extend(self.encode_rows(load_dataset_rows(ds), f"tokenising {os.path.basename(str(ds.path).rstrip('/')) or 'dataset'}"))
             return docs
 
         train_docs = encode_all(c.datasets)
