@@ -77,8 +77,9 @@ def fetch_remote(url: str, split: str = "train", cache_dir: Optional[str] = None
         names = [url]
     if not names:
         raise FileNotFoundError(f"{url}: no data files ({', '.join(exts)}) found")
-    root = cache_dir or os.path.join(os.environ.get("SUROGATE_CACHE", os.path.expanduser("~/.cache/surogate_b200")), "datasets",
-                                     hashlib.sha1(url.encode()).hexdigest()[:16])
+    from ..utils.fs import get_cache_dir
+
+    root = cache_dir or os.path.join(get_cache_dir(), "datasets", hashlib.sha1(url.encode()).hexdigest()[:16])
     os.makedirs(root, exist_ok=True)
     out = []
     for n in names:

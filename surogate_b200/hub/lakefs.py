@@ -60,7 +60,9 @@ class LakeFSHub:
 
     def download(self, uri: str, cache_dir: Optional[str] = None) -> str:
         repo, ref, prefix = self.parse_uri(uri)
-        root = os.path.join(cache_dir or os.path.expanduser("~/.cache/surogate_b200/lakefs"), repo, ref, prefix.strip("/"))
+        from ..utils.fs import get_cache_dir
+
+        root = os.path.join(cache_dir or os.path.join(get_cache_dir(), "lakefs"), repo, ref, prefix.strip("/"))
         os.makedirs(root, exist_ok=True)
         for obj in self.list_objects(repo, ref, prefix):
             rel = obj["path"][len(prefix):].lstrip("/")
