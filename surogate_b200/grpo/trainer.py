@@ -103,7 +103,23 @@ class GRPOTrainer:
         return stats.summary()
 
 
+def start_step_override() -> Optional[int]:
+    """``SUROGATE_GRPO_START_STEP``: the step a trainer without a checkpoint starts at (it then waits for that step's batch instead of
+    replaying the rollout history from step 0, e.g. beside an orchestrator that was resumed).  Parity: surogate/grpo/runs.py:20-30."""
+    raw = os.environ.get("SUROGATE_GRPO_START_STEP")
+    if raw is None or raw == "":
+        return None
+    try:
+        step = int(raw)
+    except ValueError as e:
+        raise ValueError(f"Invalid SUROGATE_GRPO_START_STEP={raw!r}; expected an integer") from e
+    if step < 0:
+        raise ValueError(f"Invalid SUROGATE_GRPO_START_STEP={raw!r}; expected a non-negative integer")
+    return step
+
+
 def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
+    from ..io.checkpoint import clean_old_checkpoints, find_latest_checkpoint
     from ..parallel.dist import TorchComm, init_distributed
     from ..train.logging import TrainingRunLogger
     from ..train.lr_schedule import LRSchedule
@@ -122,6 +138,15 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
             trainer.lora.init_weights(cfg.train_seed)
     else:
         trainer.init_weights(cfg.train_seed)
+    start_step, start_version = 0, 0
+    latest = find_latest_checkpoint(cfg.checkpoint_dir) if (cfg.resume_from_checkpoint and cfg.checkpoint_dir) else None
+    if latest is not None:  # weights (or the adapter over the base loaded above), optimizer state, step and policy version continue
+        meta = trainer.load_checkpoint(cfg.checkpoint_dir, latest)
+        start_step = int(meta["run"]["step"])
+        start_version = int((meta.get("data-loader") or {}).get("policy_version", start_step // max(1, cfg.broadcast_every)))
+    else:
+        start_step = start_step_override() or 0
+        start_version = start_step // max(1, cfg.broadcast_every)
     transport = make_transport(cfg.transport, directory=cfg.transport_dir, endpoint=cfg.zmq_endpoint, role="consumer")
     max_steps = cfg.max_steps if cfg.max_steps > 0 else 100
     noise = None
@@ -134,7 +159,8 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
     bcast = FilesystemBroadcast(cfg.weight_dir, noise=noise, total_steps=max_steps // max(1, cfg.broadcast_every))
     g = GRPOTrainer(trainer, cfg.loss)
     g.turn_diagnostics = bool(cfg.turn_diagnostics)
-    bcast.publish(trainer, 0, hf_cfg)  # version 0 = the initial policy: lets the orchestrator start
+    g.policy_version = start_version
+    bcast.publish(trainer, start_version, hf_cfg)  # the policy the orchestrator starts from: version 0, or the one a resumed run had reached
     sched = LRSchedule(cfg.learning_rate, max_steps, cfg.warmup_steps, cfg.cooldown_steps, cfg.final_lr_fraction * cfg.learning_rate,
                        cfg.lr_scheduler_type, cfg.wsd_decay_steps_fraction)
     logger = TrainingRunLogger(cfg.log_file, None, is_main=info.is_main)
@@ -142,8 +168,11 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
         # the tensor-level publishers (process group of trainer + engine workers, CUDA IPC handles) exist in grpo/weight_broadcast.py with
         # their receivers in grpo/vllm_worker.py; this loop publishes through the watched directory, which works with every engine set-up
         logger.message(f"[grpo] weight_broadcast: {cfg.weight_broadcast} is not wired into this trainer loop: publishing versions under {cfg.weight_dir} instead")
+    if start_step:
+        logger.message(f"[grpo] continuing at step {start_step}, policy version {start_version}"
+                       + (f" (checkpoint {cfg.checkpoint_dir}/step_{latest:08d})" if latest is not None else " (SUROGATE_GRPO_START_STEP)"))
     history = []
-    for step in range(max_steps):
+    for step in range(start_step, max_steps):
         t0 = time.perf_counter()
         batch, meta = transport.receive(step)
         wait_ms = (time.perf_counter() - t0) * 1e3
@@ -157,5 +186,12 @@ def run_grpo(cfg: GRPOConfig) -> Dict[str, Any]:
             transport.ack(step)
         logger.log_record("grpo", step=step + 1, **out)
         history.append(out)
+        if cfg.save_steps > 0 and cfg.checkpoint_dir and (step + 1) % cfg.save_steps == 0 and step + 1 < max_steps:
+            try:
+                trainer.save_checkpoint(cfg.checkpoint_dir, step + 1, {"data_loader": {"policy_version": g.policy_version}})
+                if info.is_main:
+                    clean_old_checkpoints(cfg.checkpoint_dir, cfg.save_total_limit)
+            except OSError as e:  # a failed save must not end the run; save_checkpoint raises on every rank together
+                logger.message(f"[checkpoint] save failed: {e}")
     logger.close()
     return {"steps": len(history), "history": history}
