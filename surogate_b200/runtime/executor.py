@@ -278,6 +278,11 @@ class Executor:
 
             self.options.dump_tensors = env_dump_hook()
         self.device = device or torch.device("cpu")
+        self.op_profile = None  # debug.op_profile.OpProfile: time per op kind (SUROGATE_OP_PROFILE=1, or set by the caller)
+        if os.environ.get("SUROGATE_OP_PROFILE"):
+            from ..debug.op_profile import env_op_profile
+
+            self.op_profile = env_op_profile(self.device)
         self.ep = ep
         self.lora = lora
         self._liveness: Dict[int, Dict[str, int]] = {}
@@ -319,7 +324,7 @@ class Executor:
                 outs = self._block_stack_backward(op, env, ctx)
             else:
                 ins = [None if c == 0 else (get_param(ctx.full_name(n)) if c == 1 else env.get(n)) for c, n in baked.sources]
-                outs = baked.fn(ctx, op, *ins)
+                outs = baked.fn(ctx, op, *ins) if self.op_profile is None else self.op_profile.timed(op.kind, baked.fn, ctx, op, *ins)
             if self.timer is not None and op.kind == "fused_lm_head_loss":
                 self.timer.mark("lm_head")  # in training mode this includes the head's own backward (fused)
             for name, val in zip(op.outputs, outs):

@@ -59,3 +59,30 @@ def test_a_step_writes_the_named_tensors(tmp_path, monkeypatch):
     monkeypatch.setenv("SUROGATE_DEBUG_DUMP_DIR", str(tmp_path / "layer0"))
     trainer().step(x, y)
     assert {f for f in os.listdir(tmp_path / "layer0") if f.endswith(".bin")} == {sanitise(f"blocks[0].{name}") + ".bin"}
+
+
+def test_op_profile_counts_every_dispatched_op(monkeypatch, capsys):
+    import io
+
+    monkeypatch.setenv("SUROGATE_OP_PROFILE", "1")
+    t = Trainer(TrainerConfig(model=HF, batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", param_dtype="fp32", backend="torch", use_cuda_graphs=True),
+                device=torch.device("cpu"))
+    t.init_weights(0)
+    prof = t.executor.op_profile
+    assert prof is not None and not t._graphs_allowed(None, None, None)
+    x = torch.randint(0, 96, (2, 16))
+    t.step(x, torch.roll(x, -1, 1))
+    rows = prof.rows()
+    kinds = {r[0] for r in rows}
+    assert "fused_lm_head_loss" in kinds and any("rmsnorm" in k for k in kinds) and any("matmul" in k or "linear" in k for k in kinds)
+    assert abs(sum(r[4] for r in rows) - 1.0) < 1e-6 and all(r[2] >= 1 and r[1] >= 0 for r in rows) and rows == sorted(rows, key=lambda r: -r[1])
+    per_layer = next(r for r in rows if "rmsnorm" in r[0])
+    assert per_layer[2] >= 2  # two layers: the kind was dispatched at least once per layer
+    buf = io.StringIO()
+    prof.report(buf)
+    assert "[op-profile]" in buf.getvalue() and "fused_lm_head_loss" in buf.getvalue()
+    prof.reset()
+    assert prof.rows() == []
+    monkeypatch.setenv("SUROGATE_OP_PROFILE", "0")
+    t2 = Trainer(TrainerConfig(model=HF, batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", param_dtype="fp32", backend="torch"), device=torch.device("cpu"))
+    assert t2.executor.op_profile is None
