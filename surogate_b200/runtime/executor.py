@@ -277,6 +277,8 @@ class Executor:
             from ..debug.dump import env_dump_hook  # file dumps of named tensors, switched on by the environment
 
             self.options.dump_tensors = env_dump_hook()
+        if os.environ.get("SUROGATE_DEBUG_CHECK_NONFINITE", "0") not in ("", "0"):
+            self.options.check_finite = True  # every op output is tested; the first NaN / Inf raises with the tensor, layer and op named
         self.device = device or torch.device("cpu")
         self.op_profile = None  # debug.op_profile.OpProfile: time per op kind (SUROGATE_OP_PROFILE=1, or set by the caller)
         if os.environ.get("SUROGATE_OP_PROFILE"):

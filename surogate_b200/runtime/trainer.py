@@ -416,8 +416,8 @@ class Trainer:
         first two steps of this process run eagerly, also after a resume: they are the warm-up that graph capture requires)."""
         c = self.cfg
         multi_ok = self.world == 1 or c.zero_level <= 1  # replicated weights: the gradient reductions run after the replay, outside the graph
-        if self.executor.op_profile is not None or self.executor.options.dump_tensors is not None:
-            return False  # both read results back op by op, which a captured region cannot do
+        if self.executor.op_profile is not None or self.executor.options.dump_tensors is not None or self.executor.options.check_finite:
+            return False  # all three read results back op by op, which a captured region cannot do
         return bool(c.use_cuda_graphs and self.device.type == "cuda" and self.backend.name == "cuda" and multi_ok and self.lora is None
                     and self.ep is None and not (c.offload_master or c.offload_optimizer or c.cpu_training or c.qlora or c.offload_saved_tensors or c.lmhead_drop_ignored_rows or c.time_breakdown)
                     and c.sequence_chunks <= 1

@@ -86,3 +86,22 @@ def test_op_profile_counts_every_dispatched_op(monkeypatch, capsys):
     monkeypatch.setenv("SUROGATE_OP_PROFILE", "0")
     t2 = Trainer(TrainerConfig(model=HF, batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", param_dtype="fp32", backend="torch"), device=torch.device("cpu"))
     assert t2.executor.op_profile is None
+
+
+def test_nonfinite_check_names_the_first_bad_tensor(monkeypatch):
+    import pytest
+
+    monkeypatch.setenv("SUROGATE_DEBUG_CHECK_NONFINITE", "1")
+    t = Trainer(TrainerConfig(model=HF, batch_size=2, seq_len=16, grad_accum=1, recipe="bf16", optimizer="adamw", param_dtype="fp32", backend="torch", use_cuda_graphs=True),
+                device=torch.device("cpu"))
+    t.init_weights(0)
+    assert t.executor.options.check_finite and not t._graphs_allowed(None, None, None)
+    x = torch.randint(0, 96, (2, 16))
+    t.step(x, torch.roll(x, -1, 1))  # a healthy step passes
+    name, w = next((n, w) for n, w in t.store.named_full_tensors() if "embed" in n)
+    w = w.clone().float()
+    w[0, :4] = float("nan")
+    t.store.load_tensor(name, w)
+    t.store.sync_work_from_master()
+    with pytest.raises(FloatingPointError, match="non-finite values in"):
+        t.step(x * 0, torch.roll(x, -1, 1))  # token 0 reads the poisoned embedding row
