@@ -117,15 +117,69 @@ def compare(new: Dict[str, Any], base: Dict[str, Any], loss_rtol: float = 2e-2, 
     return problems
 
 
+DEFAULT_RUN_TIMEOUT_S = int(os.environ.get("SUROGATE_REGRESSION_TIMEOUT_S", "1800"))
+
+
+def run_config(config_path: str, artifact_path: str, command: str = "sft", timeout_s: Optional[int] = None, extra_env: Optional[Dict[str, str]] = None) -> Dict[str, Any]:
+    """One real training config as a subprocess (``surogate <command> <config>``) that writes its artifact where
+    ``SUROGATE_REGRESSION_ARTIFACT`` points; returns the artifact.  A run that fails or outlasts ``timeout_s``
+    (``SUROGATE_REGRESSION_TIMEOUT_S``, default 1800) raises with the end of its output.
+    Parity: surogate/regression/baseline_runner.py:300-330."""
+    import subprocess
+
+    env = dict(os.environ, SUROGATE_REGRESSION_ARTIFACT=artifact_path, SUROGATE_NO_BANNER="1", **(extra_env or {}))
+    if os.path.exists(artifact_path):
+        os.remove(artifact_path)
+    try:
+        r = subprocess.run([sys.executable, "-m", "surogate_b200.cli.main", command, config_path], env=env, capture_output=True, text=True,
+                           timeout=timeout_s or DEFAULT_RUN_TIMEOUT_S)
+    except subprocess.TimeoutExpired as e:
+        raise RuntimeError(f"{config_path}: no result after {e.timeout:.0f} s") from e
+    if r.returncode != 0 or not os.path.exists(artifact_path):
+        raise RuntimeError(f"{config_path}: exit code {r.returncode}, artifact {'missing' if not os.path.exists(artifact_path) else 'present'}\n{(r.stdout + r.stderr)[-2000:]}")
+    with open(artifact_path) as f:
+        return json.load(f)
+
+
+def run_configs(paths: List[str], baselines: str, update: bool) -> int:
+    """Each config as a subprocess; baseline ``<baselines>/<config file name>.json`` written (first run / ``update``) or compared."""
+    from .artifact import compare_runs
+
+    failed = 0
+    for cfg in paths:
+        name = os.path.splitext(os.path.basename(cfg))[0]
+        base = os.path.join(baselines, name + ".json")
+        new = os.path.join(baselines, name + ".new.json")
+        try:
+            art = run_config(cfg, new)
+        except RuntimeError as e:
+            print(f"[FAIL] {name}: {e}")
+            failed += 1
+            continue
+        if update or not os.path.exists(base):
+            os.replace(new, base)
+            print(f"[baseline] {name}: wrote {base}")
+            continue
+        with open(base) as f:
+            problems = compare_runs(art, json.load(f))
+        os.remove(new)
+        print(f"[{'FAIL' if problems else ' ok '}] {name}" + ("".join("\n    " + x for x in problems)))
+        failed += bool(problems)
+    return failed
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m surogate_b200.regression.runner")
     p.add_argument("--baselines", default="regression_baselines")
     p.add_argument("--update", action="store_true", help="write / overwrite baselines instead of comparing")
     p.add_argument("--only", default=None)
+    p.add_argument("--config", action="append", default=[], help="a training config to run as a subprocess and compare (repeatable); without it the built-in matrix runs")
     a = p.parse_args(argv)
     import torch
 
     os.makedirs(a.baselines, exist_ok=True)
+    if a.config:
+        return 1 if run_configs(a.config, a.baselines, a.update) else 0
     failed = 0
     for case in default_matrix(torch.cuda.is_available()):
         if a.only and a.only not in case.name:

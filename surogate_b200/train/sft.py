@@ -249,6 +249,9 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
     stopper = EarlyStopping(cfg.early_stop)
     step_tokens = B * GA * T * info.world
     last: Dict[str, Any] = {}
+    from ..regression.artifact import RunArtifact
+
+    artifact = RunArtifact.from_env() if info.is_main else None  # SUROGATE_REGRESSION_ARTIFACT: curve + timings + plan summary of this run
     for step in range(start_step, max_steps):
         t0 = time.perf_counter()
         if watchdog is not None:
@@ -274,6 +277,8 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
             logger.log_record("memory", step=step + 1, **mem)
         losses.append(out["loss"])
         norms.append(out["norm"])
+        if artifact is not None:
+            artifact.add(step + 1, out["loss"], out["norm"], lr, ms, int(torch.cuda.max_memory_allocated(device)) if device.type == "cuda" else None)
         phase = phase_det.update(step, out["loss"])
         gstat = grads.update(out["norm"])
         act = guard.check(out["loss"], out["norm"])
@@ -317,6 +322,8 @@ def _run_steps(cfg, trainer, logger, loader, eval_loader, sched, watchdog, info,
         if stopper.should_stop(out["loss"], phase):
             logger.message("[early-stop] stopping")
             break
+    if artifact is not None:
+        logger.message(f"[regression] artifact written to {artifact.write(trainer)}")
     return last
 
 
