@@ -39,6 +39,11 @@ class Tokenizer:
         self.pad_token = _token_content(self.config.get("pad_token"))
         self.add_bos = bool(self.config.get("add_bos_token", False))
         self._jinja = None
+        if os.environ.get("SUROGATE_TOK_PROFILE"):
+            from . import tok_profile
+
+            if tok_profile.enabled():
+                tok_profile.instrument(self)
 
     # ------------------------------------------------------------------ construction
     @classmethod

@@ -61,3 +61,35 @@ def test_pool_equals_one_process(tmp_path, monkeypatch):
 
     own = tz.TokenizeDatasets(cfg, {"vocab_size": 600}, "", tokenizer=Tokenizer.from_pretrained(mdir))
     assert len(own.encode_rows(rows)) == len(serial)
+
+
+def test_tokenizer_profile(tmp_path, monkeypatch):
+    import io
+
+    pytest.importorskip("tokenizers")
+    from test_host_runtime import QWEN_PATTERN, _train_tokenizer
+
+    from surogate_b200.data import tok_profile
+    from surogate_b200.data.tokenizer import Tokenizer
+
+    _, mdir = _train_tokenizer(QWEN_PATTERN, str(tmp_path), "model")
+    with open(os.path.join(mdir, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<|im_end|>", "pad_token": "<|endoftext|>"}, f)
+    plain = Tokenizer.from_pretrained(mdir)
+    assert "encode" not in vars(plain)  # nothing wrapped without the variable
+    monkeypatch.setenv("SUROGATE_TOK_PROFILE", "1")
+    tok = Tokenizer.from_pretrained(mdir)
+    tok_profile.profile().reset()
+    msgs = [{"role": "user", "content": "Hello world"}, {"role": "assistant", "content": "It's a test"}]
+    want = plain.encode_for_training(msgs)
+    assert tok.encode_for_training(msgs) == want and tok.encode_for_training(msgs) == want
+    s = tok_profile.profile().summary()
+    assert s["calls"]["encode_for_training"] == 2 and s["calls"]["render"] >= 2 and s["calls"]["encode"] >= 2 and s["tokens"] == 2 * len(want[0])
+    assert s["ms"]["encode_for_training"] >= s["ms"]["render"] and s["align_and_label_ms"] >= 0 and s["tokens_per_second"] > 0
+    buf = io.StringIO()
+    tok_profile.profile().report(buf)
+    assert "[tok-profile]" in buf.getvalue() and "align + labels" in buf.getvalue()
+    tok_profile.profile().reset()
+    empty = io.StringIO()
+    tok_profile.profile().report(empty)
+    assert empty.getvalue() == ""
